@@ -1,0 +1,227 @@
+"""Container round trips, quantiser error bounds, tokenizer, LoRA files (CPU only)."""
+import os
+import struct
+import sys
+
+import numpy as np
+import pytest
+
+from zse_b200.format import (BPETokenizer, ModelConfig, QuantMethod, SectionType, ZSELoader, ZSEWriter, serializer,
+                             synth)
+from zse_b200.format import quantize as Q
+from zse_b200.format.header import FileHeader, SectionEntry, read_header_and_sections
+from zse_b200.format.lora_format import load_lora, read_lora_header, save_lora, estimate_lora_size
+from zse_b200.format.weight_index import WeightEntry, WeightIndex
+
+REF = "/root/reference/zse-engine"
+
+
+def test_serializer_roundtrip_and_wire_bytes():
+    obj = {"a": 1, "b": [1.5, None, True, False, "x", b"\x00\x01"], "c": {"d": -7}}
+    assert serializer.decode(serializer.encode(obj)) == obj
+    assert serializer.encode(5) == b"\x10" + struct.pack("<q", 5)
+    assert serializer.encode("é") == b"\x21\x02\x00\x00\x00\xc3\xa9"
+    assert serializer.encode([None]) == b"\x30\x01\x00\x00\x00\x00"
+    with pytest.raises(ValueError):
+        serializer.decode(b"\x99")
+    with pytest.raises(TypeError):
+        serializer.encode(object())
+
+
+def test_header_pack_unpack():
+    h = FileHeader(total_size=123456789012, flags=5, num_sections=4)
+    raw = h.pack()
+    assert len(raw) == 64 and raw[:4] == b"ZSE\x01"
+    assert FileHeader.unpack(raw) == h
+    e = SectionEntry(SectionType.WEIGHT_DATA, 4096, 1 << 33, 0xDEADBEEF)
+    assert len(e.pack()) == 32 and SectionEntry.unpack(e.pack()) == e
+    with pytest.raises(ValueError):
+        FileHeader.unpack(b"NOPE" + raw[4:])
+
+
+@pytest.mark.parametrize("n", [128, 256 * 688, 1000])
+def test_int4_quantise_error_bound(n):
+    rng = np.random.default_rng(n)
+    w = (rng.standard_normal(n) * 0.02).astype(np.float32)
+    p, s, z = Q.quantize_int4_arrays(w, 128)
+    assert p.size == Q.compute_packed_size(n)[0] and s.size == z.size == Q.compute_packed_size(n)[1] // 2
+    back = Q.dequantize_int4_arrays(p, s, z, n, 128)
+    pad = np.concatenate([w, np.zeros(-n % 128, np.float32)]).reshape(-1, 128)
+    step = (pad.max(1) - pad.min(1)) / 15
+    err = np.abs(np.concatenate([back, np.zeros(-n % 128, np.float32)]).reshape(-1, 128) - pad)
+    # half a step plus fp16 rounding of scale (x15) and zero
+    assert (err.max(1) <= step * 0.5 + 16 * 2e-3 * np.abs(pad).max(1) + 1e-6).all()
+
+
+def test_int4_nibble_order_and_constant_group():
+    w = np.zeros(128, np.float32)
+    w[0], w[1] = 0.0, 1.5
+    p, s, z = Q.quantize_int4_arrays(w, 128)
+    assert p[0] == (15 << 4) | 0          # low nibble = even index
+    assert float(z[0]) == 0.0 and abs(float(s[0]) - 0.1) < 1e-3
+    p, s, z = Q.quantize_int4_arrays(np.full(128, 0.25, np.float32), 128)
+    assert float(s[0]) == 1.0 and float(z[0]) == 0.25 and not p.any()
+
+
+def test_c_rounding_mode_differs_only_by_rounding():
+    rng = np.random.default_rng(1)
+    w = (rng.standard_normal(4096) * 0.02).astype(np.float32)
+    a = Q.dequantize_int4_arrays(*Q.quantize_int4_arrays(w, 128, "nearest"), 4096)
+    b = Q.dequantize_int4_arrays(*Q.quantize_int4_arrays(w, 128, "c"), 4096)
+    assert np.abs(a - b).max() < 0.02 * 6 / 15
+    h = Q.f32_to_f16_truncate(np.array([1.0, 0.1, 1e-8, 70000.0, -2.5], np.float32))
+    assert float(h[0]) == 1.0 and float(h[2]) == 0.0 and np.isinf(h[3]) and float(h[4]) == -2.5
+    assert float(h[1]) <= 0.1 < float(h[1]) + 1e-4
+
+
+def test_int8_roundtrip():
+    rng = np.random.default_rng(2)
+    w = (rng.standard_normal(1024) * 0.05).astype(np.float32)
+    q, s = Q.quantize_tensor_int8(w, 128)
+    back = Q.dequantize_tensor_int8(q, s, (1024,), 128)
+    assert np.abs(back - w).max() < np.abs(w).max() / 127 * 0.51 + 1e-3 * np.abs(w).max()
+
+
+def test_tile_untile_inverse():
+    rng = np.random.default_rng(3)
+    for n, k in ((64, 16), (100, 48), (256, 688)):
+        raw = rng.integers(0, 256, n * k // 2, dtype=np.uint8)
+        t = Q.tile_int4_64x8(raw, n, k)
+        assert t.size == ((n + 63) // 64) * ((k + 15) // 16) * 512
+        assert (Q.untile_int4_64x8(t, n, k) == raw).all()
+
+
+def test_write_read_full_file(tmp_path, tiny_zse):
+    with ZSELoader(tiny_zse) as l:
+        c = l.config
+        assert (c.num_layers, c.hidden_size, c.intermediate_size, c.vocab_size) == (2, 256, 688, 1024)
+        assert c.quant.int4_layout == "rowmajor"
+        off, size = l.weight_data_section()
+        assert off % 4096 == 0 and size == l.weight_index.total_data_bytes
+        for e in l.weight_index:
+            assert e.data_offset % 256 == 0
+            if e.dtype == "int4":
+                assert e.scale_offset == e.data_offset + e.data_nbytes
+                assert e.zeros_offset == e.scale_offset + e.scale_nbytes
+        types = [s.type for s in l._sections]
+        assert types == [SectionType.CONFIG, SectionType.TOKENIZER, SectionType.WEIGHT_DATA, SectionType.WEIGHT_INDEX]
+        e = l.weight_index.find("layers.1.mlp.down_proj.weight")
+        assert e.shape == (256, 688) and l.get_weight_as_float(e).shape == (256, 688)
+        assert l.tokenizer.decode(l.tokenizer.encode("the thin man", add_bos=False)) == "the thin man"
+
+
+def test_corruption_is_detected(tmp_path, tiny_zse):
+    raw = bytearray(open(tiny_zse, "rb").read())
+    p = tmp_path / "bad.zse"
+    hdr, secs = read_header_and_sections(bytes(raw[:4096]))
+    cfg = next(s for s in secs if s.type == SectionType.CONFIG)
+    raw[cfg.offset + 3] ^= 0xFF
+    p.write_bytes(raw)
+    with pytest.raises(ValueError, match="CRC"):
+        ZSELoader(str(p))
+    p.write_bytes(bytes(raw[:-10]))
+    with pytest.raises(ValueError, match="size mismatch"):
+        ZSELoader(str(p))
+
+
+def test_tiled_files_are_read_back_rowmajor(tmp_path):
+    """A file whose INT4 payloads were re-tiled 64x8 (what the reference's C converter emits) decodes to the
+    same weights: by size when padding gives it away, else through the explicit override."""
+    rng = np.random.default_rng(5)
+    c = synth.shape_config("tiny")
+    c.quant.int4_layout = None
+    w = rng.standard_normal((100, 256)).astype(np.float32) * 0.02     # N=100 -> tile padding changes the size
+    v = rng.standard_normal((128, 256)).astype(np.float32) * 0.02     # size-preserving
+    path = str(tmp_path / "tiled.zse")
+    wr = ZSEWriter(path)
+    wr._config = c                      # bypass set_config so no layout is recorded
+    wr.begin_weights()
+    for name, t in (("a.weight", w), ("b.weight", v)):
+        p, s, z = Q.quantize_int4_arrays(t, 128)
+        wr.add_weight_raw(name, t.shape, Q.tile_int4_64x8(p, *t.shape), s, z)
+    wr.finalize()
+    with ZSELoader(path) as l:
+        ea, eb = l.weight_index.find("a.weight"), l.weight_index.find("b.weight")
+        assert l.int4_layout_of(ea) == "tiled64x8" and l.int4_layout_of(eb) == "rowmajor"
+        assert np.abs(l.get_weight_as_float(ea) - w).max() < 0.01
+    with ZSELoader(path, int4_layout="tiled64x8") as l:
+        assert np.abs(l.get_weight_as_float(l.weight_index.find("b.weight")) - v).max() < 0.01
+
+
+def test_config_ignores_unknown_keys_and_keeps_gemma_fields():
+    c = ModelConfig(arch="gemma4", layer_types=["sliding_attention", "full_attention"], global_head_dim=512)
+    d = c.to_dict()
+    d["brand_new_key"] = 1
+    d["quant"]["another"] = 2
+    c2 = ModelConfig.from_dict(d)
+    assert c2.layer_types == c.layer_types and c2.global_head_dim == 512 and c2.quant.group_size == 128
+    assert "rope_scaling" not in c.to_dict()
+
+
+def test_tokenizer_bpe_and_serialisation():
+    tok = synth.byte_tokenizer()
+    ids = tok.encode("<|im_start|>the other<|im_end|>", add_bos=False)
+    assert ids[0] == tok.added_tokens["<|im_start|>"] and ids[-1] == tok.added_tokens["<|im_end|>"]
+    assert tok.vocab["the"] in ids
+    assert tok.decode(ids, skip_special=False) == "<|im_start|>the other<|im_end|>"
+    t2 = BPETokenizer.deserialize(tok.serialize())
+    text = "Zażółć gęślą jaźń 123  \n tabs\tand 'quotes'"
+    assert t2.encode(text) == tok.encode(text) and t2.decode(t2.encode(text)) == text
+    assert tok.encode("x", add_bos=True, add_eos=True)[0] == tok.special_tokens.bos_id
+
+
+def test_lora_file_roundtrip(tmp_path):
+    from zse_b200.lora.weights import LoRAAdapter
+    rng = np.random.default_rng(0)
+    ad = LoRAAdapter("a", rank=4, alpha=8.0, target_modules=["q_proj", "v_proj"], num_layers=3)
+    shapes = {"q_proj": (32, 64), "v_proj": (32, 16)}
+    data = {(l, t): (rng.standard_normal((4, shapes[t][0])).astype(np.float16),
+                     rng.standard_normal((shapes[t][1], 4)).astype(np.float16)) for l in range(3) for t in shapes}
+    path = str(tmp_path / "x.zse-lora")
+    save_lora(path, ad, data)
+    h = read_lora_header(path)
+    assert (h["rank"], h["alpha"], h["num_layers"], h["targets"]) == (4, 8.0, 3, ["q_proj", "v_proj"])
+    assert os.path.getsize(path) == 32 + 2 * 64 + h["total_bytes"]
+    ad2, d2 = load_lora(path, shapes)
+    assert ad2.scaling == 2.0 and len(d2) == 6
+    assert d2[(2, "v_proj")][1] == data[(2, "v_proj")][1].tobytes()
+    assert estimate_lora_size(16, 28, ["q_proj", "v_proj"], 3584, 18944, 28, 4, 128) == \
+        28 * 2 * 16 * (3584 + 3584 + 3584 + 512)
+    with pytest.raises(ValueError):
+        open(path, "r+b").write(b"XXXX")
+        read_lora_header(path)
+
+
+@pytest.mark.skipif(not os.path.isdir(REF), reason="reference tree not mounted")
+def test_reference_loader_reads_our_file_and_vice_versa(tmp_path, tiny_zse):
+    """Byte compatibility in both directions, checked with the reference's own pure-python reader/writer."""
+    sys.path.insert(0, REF)
+    try:
+        from zse_engine.format.loader import ZSELoader as RefLoader
+        from zse_engine.format.writer import ZSEWriter as RefWriter
+        from zse_engine.format.config import ModelConfig as RefConfig
+    finally:
+        sys.path.remove(REF)
+    ref = RefLoader(tiny_zse)
+    ours = ZSELoader(tiny_zse)
+    assert ref.config.hidden_size == 256 and len(ref.weight_index) == len(ours.weight_index)
+    e_ref = ref.weight_index.find("layers.0.self_attn.q_proj.weight")
+    e = ours.weight_index.find("layers.0.self_attn.q_proj.weight")
+    a = np.array(ref.get_weight_as_float(e_ref), dtype=np.float32)
+    assert np.array_equal(a, ours.get_weight_as_float(e).reshape(-1))
+    assert ref.tokenizer.encode("the cat") == ours.tokenizer.encode("the cat")
+    ref.close()
+    path = str(tmp_path / "ref.zse")
+    w = RefWriter(path)
+    w.set_config(RefConfig(num_layers=1, hidden_size=128, vocab_size=16))
+    w.begin_weights()
+    vals = [((i * 37) % 101 - 50) / 1000.0 for i in range(256)]
+    w.add_weight("layers.0.mlp.up_proj.weight", vals, (2, 128))
+    w.add_weight("norm.weight", [1.0] * 128, (128,), quantize=False)
+    w.finalize()
+    with ZSELoader(path) as l:
+        got = l.get_weight_as_float(l.weight_index.find("layers.0.mlp.up_proj.weight")).reshape(-1)
+        assert np.abs(got - np.array(vals, np.float32)).max() < 0.1 / 15 * 0.51 + 1e-4
+        p, s, z = Q.quantize_tensor(vals, 128)
+        e = l.weight_index.find("layers.0.mlp.up_proj.weight")
+        assert l.get_weight_data(e) == p and l.get_weight_scales(e) == s and l.get_weight_zeros(e) == z

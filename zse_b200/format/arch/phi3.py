@@ -1,0 +1,14 @@
+"""Phi-3 (zse-engine/zse_engine/format/arch/phi3.py): fused ``qkv_proj`` and ``gate_up_proj`` tensors are
+stored under their fused names; the runtime splits them when the model is built."""
+from .base import ArchAdapter, register_adapter
+
+
+@register_adapter
+class Phi3Adapter(ArchAdapter):
+    ARCH_NAME = "phi3"
+    LAYER_TENSORS = ("self_attn.qkv_proj.weight", "self_attn.o_proj.weight", "mlp.gate_up_proj.weight",
+                     "mlp.down_proj.weight", "input_layernorm.weight", "post_attention_layernorm.weight")
+
+    def config_from_hf(self, hf):
+        return self._common(hf, "phi3", max_seq=4096, theta=10000.0, eps=1e-5, tie=False,
+                            explicit_head_dim=False)

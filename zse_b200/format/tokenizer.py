@@ -1,0 +1,224 @@
+"""Byte-level BPE tokenizer stored inside ``.zse`` files.
+
+Behaviour matches zse-engine/zse_engine/format/tokenizer.py:25-436: GPT-2 byte<->unicode table,
+the GPT-2 pre-tokenisation regex, lowest-rank merge loop, added tokens split out before BPE,
+``encode(text, add_bos=True, add_eos=False)``, ``decode(ids, skip_special=True)``; the section
+stores ``{vocab, merges, special_tokens, added_tokens}``.  The merge loop here keeps the word as a
+list and re-scans only for the chosen pair; results are cached per pre-token.
+"""
+from __future__ import annotations
+
+import json
+import os
+import re
+from dataclasses import dataclass, field, fields
+from functools import lru_cache
+from typing import Dict, List, Optional, Tuple
+
+from . import serializer
+
+
+@lru_cache(maxsize=1)
+def _byte_table() -> Dict[int, str]:
+    keep = list(range(33, 127)) + list(range(161, 173)) + list(range(174, 256))
+    table, extra = {}, 0
+    for b in range(256):
+        if b in keep:
+            table[b] = chr(b)
+        else:
+            table[b] = chr(256 + extra)
+            extra += 1
+    return table
+
+
+BYTE_ENCODER = _byte_table()
+BYTE_DECODER = {c: b for b, c in BYTE_ENCODER.items()}
+_PRETOKEN = re.compile(r"""'s|'t|'re|'ve|'m|'ll|'d| ?\w+| ?\d+| ?[^\s\w]+|\s+(?!\S)|\s+""")
+
+
+@dataclass
+class SpecialTokens:
+    bos_id: int = 1
+    eos_id: int = 2
+    pad_id: int = 0
+    unk_id: int = 0
+
+    def to_dict(self) -> dict:
+        return {"bos_id": self.bos_id, "eos_id": self.eos_id, "pad_id": self.pad_id, "unk_id": self.unk_id}
+
+    @classmethod
+    def from_dict(cls, d: dict) -> "SpecialTokens":
+        names = {f.name for f in fields(cls)}
+        return cls(**{k: v for k, v in d.items() if k in names})
+
+
+@dataclass
+class BPETokenizer:
+    vocab: Dict[str, int] = field(default_factory=dict)
+    merges: List[Tuple[str, str]] = field(default_factory=list)
+    special_tokens: SpecialTokens = field(default_factory=SpecialTokens)
+    added_tokens: Dict[str, int] = field(default_factory=dict)
+
+    def __post_init__(self):
+        self._rebuild_caches()
+
+    def _rebuild_caches(self) -> None:
+        self._id_to_token = {i: t for t, i in self.vocab.items()}
+        self._id_to_token.update({i: t for t, i in self.added_tokens.items()})
+        self._ranks = {tuple(p): r for r, p in enumerate(self.merges)}
+        self._cache: Dict[str, Tuple[str, ...]] = {}
+        if self.added_tokens:
+            alts = sorted(self.added_tokens, key=len, reverse=True)
+            self._added_re: Optional[re.Pattern] = re.compile("(" + "|".join(re.escape(t) for t in alts) + ")")
+        else:
+            self._added_re = None
+
+    # ---- BPE -------------------------------------------------------------------------------
+    def _bpe(self, token: str) -> Tuple[str, ...]:
+        hit = self._cache.get(token)
+        if hit is not None:
+            return hit
+        word = list(token)
+        ranks = self._ranks
+        while len(word) > 1:
+            best, best_rank = None, None
+            for pair in zip(word, word[1:]):
+                r = ranks.get(pair)
+                if r is not None and (best_rank is None or r < best_rank):
+                    best, best_rank = pair, r
+            if best is None:
+                break
+            a, b = best
+            merged, i, n = [], 0, len(word)
+            while i < n:
+                if i + 1 < n and word[i] == a and word[i + 1] == b:
+                    merged.append(a + b)
+                    i += 2
+                else:
+                    merged.append(word[i])
+                    i += 1
+            word = merged
+        out = tuple(word)
+        if len(self._cache) < 200_000:
+            self._cache[token] = out
+        return out
+
+    def _encode_chunk(self, text: str) -> List[int]:
+        ids, vocab, unk, enc = [], self.vocab, self.special_tokens.unk_id, BYTE_ENCODER
+        for piece in _PRETOKEN.findall(text):
+            mapped = "".join(enc[b] for b in piece.encode("utf-8"))
+            for sym in self._bpe(mapped):
+                ids.append(vocab.get(sym, unk))
+        return ids
+
+    def encode(self, text: str, add_bos: bool = True, add_eos: bool = False) -> List[int]:
+        ids: List[int] = [self.special_tokens.bos_id] if add_bos else []
+        if self._added_re is not None:
+            for part in self._added_re.split(text):
+                if not part:
+                    continue
+                tid = self.added_tokens.get(part)
+                if tid is not None:
+                    ids.append(tid)
+                else:
+                    ids.extend(self._encode_chunk(part))
+        else:
+            ids.extend(self._encode_chunk(text))
+        if add_eos:
+            ids.append(self.special_tokens.eos_id)
+        return ids
+
+    def decode(self, ids, skip_special: bool = True) -> str:
+        st = self.special_tokens
+        skip = {st.bos_id, st.eos_id, st.pad_id} if skip_special else ()
+        out = bytearray()
+        for tid in ids:
+            if tid in skip:
+                continue
+            tok = self._id_to_token.get(int(tid))
+            if tok is None:
+                continue
+            for ch in tok:
+                b = BYTE_DECODER.get(ch)
+                if b is None:
+                    out += ch.encode("utf-8")
+                else:
+                    out.append(b)
+        return out.decode("utf-8", errors="replace")
+
+    def token_to_id(self, token: str) -> Optional[int]:
+        tid = self.added_tokens.get(token)
+        return tid if tid is not None else self.vocab.get(token)
+
+    @property
+    def vocab_size(self) -> int:
+        return len(self.vocab) + len(self.added_tokens)
+
+    # ---- section payload -------------------------------------------------------------------
+    def serialize(self) -> bytes:
+        return serializer.encode({"vocab": self.vocab, "merges": [list(m) for m in self.merges],
+                                  "special_tokens": self.special_tokens.to_dict(),
+                                  "added_tokens": self.added_tokens})
+
+    @classmethod
+    def deserialize(cls, data) -> "BPETokenizer":
+        d = serializer.decode(data)
+        return cls(vocab=d["vocab"], merges=[tuple(m) for m in d["merges"]],
+                   special_tokens=SpecialTokens.from_dict(d.get("special_tokens", {})),
+                   added_tokens=d.get("added_tokens", {}))
+
+    # ---- HuggingFace import ----------------------------------------------------------------
+    @classmethod
+    def from_hf_tokenizer_json(cls, path: str) -> "BPETokenizer":
+        with open(path, "r", encoding="utf-8") as f:
+            data = json.load(f)
+        model = data.get("model", {})
+        vocab = dict(model.get("vocab", {}))
+        merges: List[Tuple[str, str]] = []
+        for m in model.get("merges", []):
+            if isinstance(m, str):
+                a, sep, b = m.partition(" ")
+                if sep:
+                    merges.append((a, b))
+            elif len(m) == 2:
+                merges.append((m[0], m[1]))
+        special, added = SpecialTokens(), {}
+        for info in data.get("added_tokens", []):
+            content, tid = info.get("content", ""), info.get("id", 0)
+            if info.get("special", False):
+                low = content.lower()
+                squashed = low.replace("|", "").replace("_", "")
+                if "bos" in low or content == "<s>" or "beginoftext" in squashed:
+                    special.bos_id = tid
+                elif "eos" in low or content == "</s>" or "endoftext" in squashed:
+                    special.eos_id = tid
+                elif "pad" in low:
+                    special.pad_id = tid
+                elif "unk" in low:
+                    special.unk_id = tid
+            if content not in vocab:
+                added[content] = tid
+        return cls(vocab=vocab, merges=merges, special_tokens=special, added_tokens=added)
+
+    @classmethod
+    def from_hf_dir(cls, model_dir: str) -> "BPETokenizer":
+        path = os.path.join(model_dir, "tokenizer.json")
+        if not os.path.exists(path):
+            raise FileNotFoundError(f"no tokenizer.json in {model_dir} (a HuggingFace fast tokenizer is required)")
+        tok = cls.from_hf_tokenizer_json(path)
+        cfg_path = os.path.join(model_dir, "tokenizer_config.json")
+        if os.path.exists(cfg_path):
+            try:
+                with open(cfg_path, "r", encoding="utf-8") as f:
+                    tc = json.load(f)
+                for key, attr in (("eos_token", "eos_id"), ("bos_token", "bos_id")):
+                    val = tc.get(key)
+                    if isinstance(val, dict):
+                        val = val.get("content")
+                    if isinstance(val, str) and val:
+                        tid = tok.token_to_id(val)
+                        if tid is not None:
+                            setattr(tok.special_tokens, attr, tid)
+            except (OSError, ValueError):
+                pass
+        return tok

@@ -1,0 +1,89 @@
+"""LoRA adapter bookkeeping (zse-engine/zse_engine/orchestrator/lora_weights.py:22-167).
+
+An adapter holds, per (layer, module), ``A [rank, in]`` and ``B [out, rank]``; the update is
+``y += (alpha/rank) * B (A x)``.  Tensors live wherever the manager put them (CPU for tests, CUDA when serving).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Dict, List, Optional, Tuple
+
+
+@dataclass
+class LoRAWeight:
+    layer_name: str
+    rank: int
+    in_features: int
+    out_features: int
+    a: Any = None            # tensor [rank, in]
+    b: Any = None            # tensor [out, rank]
+
+    @property
+    def nbytes(self) -> int:
+        return 2 * self.rank * (self.in_features + self.out_features)
+
+    @property
+    def loaded(self) -> bool:
+        return self.a is not None and self.b is not None
+
+
+@dataclass
+class LoRAAdapter:
+    adapter_id: str
+    rank: int
+    alpha: float
+    target_modules: List[str]
+    num_layers: int
+    weights: Dict[Tuple[int, str], LoRAWeight] = field(default_factory=dict)
+    slot: int = -1           # index in the batched weight tables (-1 = not resident)
+
+    @property
+    def scaling(self) -> float:
+        return float(self.alpha) / float(self.rank) if self.rank else 0.0
+
+    def add_weight(self, layer: int, module: str, w: LoRAWeight) -> None:
+        self.weights[(layer, module)] = w
+
+    def get_weight(self, layer: int, module: str) -> Optional[LoRAWeight]:
+        return self.weights.get((layer, module))
+
+    def has_module(self, module: str) -> bool:
+        return module in self.target_modules
+
+    @property
+    def total_bytes(self) -> int:
+        return sum(w.nbytes for w in self.weights.values())
+
+
+class LoRAWeightStore:
+    """Adapters by id, with a byte budget."""
+
+    def __init__(self, max_bytes: int = 0):
+        self._adapters: Dict[str, LoRAAdapter] = {}
+        self.max_bytes = max_bytes
+
+    def add(self, adapter: LoRAAdapter) -> None:
+        if adapter.adapter_id in self._adapters:
+            raise ValueError(f"adapter '{adapter.adapter_id}' is already loaded")
+        if self.max_bytes and self.total_bytes + adapter.total_bytes > self.max_bytes:
+            raise MemoryError(f"adapter '{adapter.adapter_id}' does not fit the LoRA budget")
+        self._adapters[adapter.adapter_id] = adapter
+
+    def remove(self, adapter_id: str) -> Optional[LoRAAdapter]:
+        return self._adapters.pop(adapter_id, None)
+
+    def get(self, adapter_id: str) -> Optional[LoRAAdapter]:
+        return self._adapters.get(adapter_id)
+
+    def list_ids(self) -> List[str]:
+        return list(self._adapters)
+
+    def __contains__(self, adapter_id: str) -> bool:
+        return adapter_id in self._adapters
+
+    def __len__(self) -> int:
+        return len(self._adapters)
+
+    @property
+    def total_bytes(self) -> int:
+        return sum(a.total_bytes for a in self._adapters.values())
