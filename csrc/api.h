@@ -1,0 +1,87 @@
+// C ABI of libzse_b200.so.  Every function takes raw device pointers and a cudaStream_t (as void*), launches
+// asynchronously on that stream and returns 0 or a negative ZSE_ERR_* code; nothing here allocates device memory
+// unless its name says so.  A device-side failure (a bounded wait that ran out, an index check) is reported through
+// the 16-byte status word the caller passes in (see zse_status_*).
+#pragma once
+#include <stdint.h>
+
+#define ZSE_ERR_SHAPE (-1)
+#define ZSE_ERR_ALIGN (-2)
+#define ZSE_ERR_DRIVER (-3)
+#define ZSE_ERR_LAUNCH (-4)
+#define ZSE_ERR_LIMIT (-5)
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// ---- gemm.cu ------------------------------------------------------------------------------------------------
+// epilogue: 0 = fp16 store (+bias), 1 = SwiGLU (N counts gate+up rows, output has N/2 columns), 2 = fp32 partial planes
+int zse_gemm_w4(const void* w_tiled, const void* x, int x_rows_cap, const void* bias, void* out, int M, int N, int K,
+                int ldo, int epilogue, int k_split, void* status, void* stream);
+int zse_gemm_w4_splits(int M, int N, int K, int k_split);
+int zse_gemm_f16(const void* w, int w_rows_cap, const void* x, int x_rows_cap, const void* bias, void* out, int M,
+                 int N, int K, int ldo, int epilogue, int k_split, void* status, void* stream);
+int zse_gemm_f16_splits(int M, int N, int K, int k_split);
+
+// ---- repack.cu ----------------------------------------------------------------------------------------------
+// Row-major INT4 [N, K/2] + scales/zeros [N, K/128] -> tiled chunks.  interleave_rows > 0 builds a fused gate/up
+// tensor: `packed` holds gate rows [0, interleave_rows) then up rows; output tile t = 64 gate rows + 64 up rows.
+int64_t zse_w4_tiled_bytes(int N, int K);
+int zse_repack_w4(const void* packed, const void* scales, const void* zeros, void* out_tiled, int N, int K,
+                  int interleave_rows, void* stream);
+int zse_dequant_w4(const void* packed, const void* scales, const void* zeros, void* out_f16, int64_t n_elements,
+                   int group_size, void* stream);
+int zse_dequant_w8(const void* q, const void* scales, void* out_f16, int64_t n_elements, int group_size, void* stream);
+int zse_quantize_w4(const void* w_f16, void* packed, void* scales, void* zeros, int64_t n_groups, void* stream);
+
+// ---- elementwise.cu -----------------------------------------------------------------------------------------
+int zse_embedding(const void* table_f16, const void* ids_i32, void* out_f32, int M, int H, int vocab, float scale,
+                  void* status, void* stream);
+// residual[M,H] (fp32, in/out) += sum of n_partials fp32 planes (stride M*H) [+ add_f16]; out = rmsnorm(residual)*w
+int zse_add_rmsnorm(void* residual, const void* partials, int n_partials, const void* add_f16, const void* weight,
+                    void* out_f16, int M, int H, float eps, void* stream);
+int zse_rmsnorm_f16(const void* x_f16, const void* weight, void* out_f16, int M, int H, float eps, void* stream);
+// qkv fp16 [M, (nh+2nkv)*hd]; rotates q and k in place (rotate-half), writes k and v into the paged cache
+// kv_layer: [num_blocks][2][nkv][block_size][hd] fp16; slot = block*block_size + offset, -1 = skip;
+// inv_freq: fp32 [rotary_dim/2] (theta^(-2i/rotary_dim), with any rope scaling already applied by the host)
+int zse_rope_kv_write(void* qkv, void* kv_layer, const void* positions_i32, const void* slots_i64,
+                      const void* inv_freq_f32, int M, int nh, int nkv, int hd, int rotary_dim, int block_size,
+                      void* stream);
+int zse_swiglu(const void* gate_up_f16, void* out_f16, int M, int I, int gelu, void* stream);
+int zse_bias_add(void* x_f16, const void* bias_f16, int M, int N, void* stream);
+
+// ---- attention.cu -------------------------------------------------------------------------------------------
+int64_t zse_attn_decode_scratch_floats(int num_seqs, int nh, int hd, int max_splits);
+int zse_attn_decode(const void* q, int ldq, const void* kv_layer, const void* block_tables_i32, int max_blocks,
+                    const void* seq_lens_i32, void* out_f16, int ldo, void* scratch_f32, int num_seqs, int nh, int nkv,
+                    int hd, int block_size, int num_splits, float scale, void* stream);
+// causal attention of `total_q` query tokens (several sequences packed) over the paged cache.
+// cu_q: [num_seqs+1] prefix offsets of query tokens; q_pos0[s]: cache position of the first query token of seq s.
+int zse_attn_prefill(const void* q, int ldq, const void* kv_layer, const void* block_tables_i32, int max_blocks,
+                     const void* cu_q_i32, const void* q_pos0_i32, void* out_f16, int ldo, int num_seqs, int max_q_len,
+                     int nh, int nkv, int hd, int block_size, float scale, void* stream);
+
+// ---- sampling.cu --------------------------------------------------------------------------------------------
+int zse_argmax(const void* logits_f16, int ld, void* out_i32, int M, int V, void* stream);
+int zse_sample(const void* logits_f16, int ld, void* out_i32, int M, int V, const void* temperature_f32,
+               const void* top_k_i32, const void* top_p_f32, const void* seeds_u64, uint64_t step, void* stream);
+// sparse form: entry i scales logits[rows[i], tokens[i]] by penalty[rows[i]]^(1+log2(counts[i]))
+int zse_apply_repetition_penalty(void* logits_f16, int ld, const void* rows_i32, const void* tokens_i32,
+                                 const void* counts_i32, int n, const void* penalty_f32, int V, void* stream);
+
+// ---- lora.cu ------------------------------------------------------------------------------------------------
+// y[t, :] += scale[a] * B[a] (A[a] x[t, :]) with a = adapter_ids[t] (-1 = none); A: [n_adapters][r][K], B: [n_adapters][N][r]
+int zse_lora_shrink(const void* x_f16, int ldx, const void* a_f16, const void* adapter_ids_i32, void* tmp_f32, int M,
+                    int K, int rank, void* stream);
+int zse_lora_expand(const void* tmp_f32, const void* b_f16, const void* adapter_ids_i32, const void* scales_f32,
+                    void* y_f16, int ldy, int M, int N, int rank, void* stream);
+
+// ---- runtime.cu ---------------------------------------------------------------------------------------------
+int zse_status_read(const void* status_dev, uint32_t* out4);   // synchronous 16-byte copy
+int zse_device_info(int* sm_count, int* cc_major, int* cc_minor, int64_t* total_mem, int64_t* free_mem);
+const char* zse_build_info(void);
+
+#ifdef __cplusplus
+}
+#endif

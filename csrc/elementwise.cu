@@ -1,0 +1,246 @@
+// Bandwidth-bound row kernels of the decoder block.  Each one reads its operands once with 128-bit accesses and
+// fuses what the reference runs as separate launches (zse-engine/zse_engine/orchestrator/kernels.py: embedding
+// 1789-1806, residual add 1809-1821, RMSNorm 1421-1467, fused residual+RMSNorm 1824-1875, RoPE 246-299/1361-1413,
+// KV write 961-1071, SiLU*up 228-244, bias 317-329).
+#include "api.h"
+#include "common.cuh"
+
+namespace zse {
+
+// ---- embedding gather: fp16 table row -> fp32 residual row -----------------------------------------------
+__global__ void embedding_kernel(const __half* __restrict__ table, const int* __restrict__ ids,
+                                 float* __restrict__ out, int H, int vocab, float scale, Status* st) {
+  const int row = blockIdx.x;
+  int id = ids[row];
+  if (id < 0 || id >= vocab) {
+    if (threadIdx.x == 0) report(st, kBadArgument, 21, unsigned(id));
+    id = 0;
+  }
+  const uint4* src = reinterpret_cast<const uint4*>(table + size_t(id) * H);
+  float4* dst = reinterpret_cast<float4*>(out + size_t(row) * H);
+  for (int i = threadIdx.x; i < H / 8; i += blockDim.x) {
+    const uint4 v = src[i];
+    const __half2* h = reinterpret_cast<const __half2*>(&v);
+    const float2 a = __half22float2(h[0]), b = __half22float2(h[1]), c = __half22float2(h[2]),
+                 d = __half22float2(h[3]);
+    dst[2 * i] = make_float4(a.x * scale, a.y * scale, b.x * scale, b.y * scale);
+    dst[2 * i + 1] = make_float4(c.x * scale, c.y * scale, d.x * scale, d.y * scale);
+  }
+}
+
+// ---- residual += partial planes (+ fp16 addend); out = RMSNorm(residual) * w ------------------------------
+// One CTA per token row.  The row (up to 8192 values with 256 threads x 8 float4) stays in registers between the
+// sum and the normalisation, so the residual is read once and written once.
+constexpr int kNormThreads = 256;
+constexpr int kNormMaxVec = 8;      // float4 per thread -> H <= 8192
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  float t = lane < (blockDim.x >> 5) ? red[lane] : 0.f;
+  t = warp_sum(t);
+  __syncthreads();
+  return t;
+}
+
+__global__ void __launch_bounds__(kNormThreads)
+add_rmsnorm_kernel(float* __restrict__ residual, const float* __restrict__ partials, int n_partials,
+                   const __half* __restrict__ add_f16, const __half* __restrict__ weight, __half* __restrict__ out,
+                   int M, int H, float eps) {
+  __shared__ float red[32];
+  const int row = blockIdx.x;
+  const size_t base = size_t(row) * H;
+  const size_t plane = size_t(M) * H;
+  const int nvec = H / 4;
+  float4 v[kNormMaxVec];
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < kNormMaxVec; ++j) {
+    const int i = threadIdx.x + j * kNormThreads;
+    if (i < nvec) {
+      float4 x = residual != nullptr ? reinterpret_cast<const float4*>(residual + base)[i] : make_float4(0, 0, 0, 0);
+      for (int p = 0; p < n_partials; ++p) {
+        const float4 y = reinterpret_cast<const float4*>(partials + p * plane + base)[i];
+        x.x += y.x; x.y += y.y; x.z += y.z; x.w += y.w;
+      }
+      if (add_f16 != nullptr) {
+        const uint2 raw = reinterpret_cast<const uint2*>(add_f16 + base)[i];
+        const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
+        const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+        x.x += a.x; x.y += a.y; x.z += b.x; x.w += b.y;
+      }
+      if (residual != nullptr && (n_partials > 0 || add_f16 != nullptr))
+        reinterpret_cast<float4*>(residual + base)[i] = x;
+      v[j] = x;
+      ss += x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w;
+    }
+  }
+  if (out == nullptr) return;
+  const float inv = rsqrtf(block_sum(ss, red) / float(H) + eps);
+#pragma unroll
+  for (int j = 0; j < kNormMaxVec; ++j) {
+    const int i = threadIdx.x + j * kNormThreads;
+    if (i < nvec) {
+      const uint2 wr = reinterpret_cast<const uint2*>(weight)[i];
+      const float2 w0 = __half22float2(*reinterpret_cast<const __half2*>(&wr.x));
+      const float2 w1 = __half22float2(*reinterpret_cast<const __half2*>(&wr.y));
+      __half2 o0 = __floats2half2_rn(v[j].x * inv * w0.x, v[j].y * inv * w0.y);
+      __half2 o1 = __floats2half2_rn(v[j].z * inv * w1.x, v[j].w * inv * w1.y);
+      uint2 pk;
+      pk.x = *reinterpret_cast<uint32_t*>(&o0);
+      pk.y = *reinterpret_cast<uint32_t*>(&o1);
+      reinterpret_cast<uint2*>(out + base)[i] = pk;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kNormThreads)
+rmsnorm_f16_kernel(const __half* __restrict__ x, const __half* __restrict__ weight, __half* __restrict__ out, int H,
+                   float eps) {
+  __shared__ float red[32];
+  const size_t base = size_t(blockIdx.x) * H;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    const float f = __half2float(x[base + i]);
+    ss += f * f;
+  }
+  const float inv = rsqrtf(block_sum(ss, red) / float(H) + eps);
+  for (int i = threadIdx.x; i < H; i += blockDim.x)
+    out[base + i] = __float2half_rn(__half2float(x[base + i]) * inv * (weight ? __half2float(weight[i]) : 1.f));
+}
+
+// ---- RoPE (rotate-half, fp32 trig) on q and k in place + scatter of k, v into the paged cache ---------------
+// grid (M, nh + 2*nkv): one CTA per (token, head); hd/2 threads; q heads first, then k heads, then v heads.
+__global__ void rope_kv_write_kernel(__half* __restrict__ qkv, __half* __restrict__ kv_layer,
+                                     const int* __restrict__ positions, const long long* __restrict__ slots,
+                                     const float* __restrict__ inv_freq, int nh, int nkv, int hd, int rotary_dim,
+                                     int block_size) {
+  const int t = blockIdx.x, head = blockIdx.y;
+  const int ld = (nh + 2 * nkv) * hd;
+  __half* row = qkv + size_t(t) * ld + size_t(head) * hd;
+  const int i = threadIdx.x;                 // pair index, i < hd/2
+  const int half_rot = rotary_dim / 2;
+  const bool is_v = head >= nh + nkv;
+  float a, b;
+  int ia, ib;
+  if (i < half_rot) {
+    ia = i;
+    ib = i + half_rot;
+  } else {                                   // unrotated tail (partial rotary): pass through in pairs
+    ia = rotary_dim + 2 * (i - half_rot);
+    ib = ia + 1;
+  }
+  a = __half2float(row[ia]);
+  b = __half2float(row[ib]);
+  if (!is_v && i < half_rot) {
+    float s, c;
+    sincosf(float(positions[t]) * inv_freq[i], &s, &c);
+    const float ra = a * c - b * s, rb = b * c + a * s;
+    a = ra;
+    b = rb;
+    row[ia] = __float2half_rn(a);
+    row[ib] = __float2half_rn(b);
+  }
+  if (head >= nh) {
+    const long long slot = slots[t];
+    if (slot >= 0) {
+      const int kvh = is_v ? head - nh - nkv : head - nh;
+      const long long blk = slot / block_size, off = slot % block_size;
+      __half* dst = kv_layer + (((blk * 2 + (is_v ? 1 : 0)) * nkv + kvh) * block_size + off) * hd;
+      dst[ia] = __float2half_rn(a);
+      dst[ib] = __float2half_rn(b);
+    }
+  }
+}
+
+__global__ void swiglu_kernel(const __half2* __restrict__ gate_up, __half2* __restrict__ out, int M, int I2,
+                              int gelu) {
+  // gate_up: [M, 2*I] as half2 -> rows of 2*I2 half2; out [M, I2]
+  const size_t idx = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= size_t(M) * I2) return;
+  const size_t t = idx / I2, j = idx % I2;
+  const float2 g = __half22float2(gate_up[t * 2 * I2 + j]);
+  const float2 u = __half22float2(gate_up[t * 2 * I2 + I2 + j]);
+  float2 r;
+  if (gelu) {
+    auto gl = [](float x) { return 0.5f * x * (1.f + tanhf(0.7978845608f * (x + 0.044715f * x * x * x))); };
+    r = make_float2(gl(g.x) * u.x, gl(g.y) * u.y);
+  } else {
+    r = make_float2(silu_f(g.x) * u.x, silu_f(g.y) * u.y);
+  }
+  out[idx] = __floats2half2_rn(clamp_f16(r.x), clamp_f16(r.y));
+}
+
+__global__ void bias_add_kernel(__half* __restrict__ x, const __half* __restrict__ bias, size_t total, int N) {
+  const size_t idx = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx < total) x[idx] = __float2half_rn(__half2float(x[idx]) + __half2float(bias[idx % N]));
+}
+
+}  // namespace zse
+
+using namespace zse;
+#define ST(s) reinterpret_cast<cudaStream_t>(s)
+#define LAUNCH_OK() (cudaGetLastError() == cudaSuccess ? 0 : ZSE_ERR_LAUNCH)
+
+extern "C" int zse_embedding(const void* table, const void* ids, void* out, int M, int H, int vocab, float scale,
+                             void* status, void* stream) {
+  if (M <= 0) return 0;
+  if (H % 8) return ZSE_ERR_SHAPE;
+  embedding_kernel<<<M, 128, 0, ST(stream)>>>(reinterpret_cast<const __half*>(table),
+                                              reinterpret_cast<const int*>(ids), reinterpret_cast<float*>(out), H,
+                                              vocab, scale, reinterpret_cast<Status*>(status));
+  return LAUNCH_OK();
+}
+
+extern "C" int zse_add_rmsnorm(void* residual, const void* partials, int n_partials, const void* add_f16,
+                               const void* weight, void* out, int M, int H, float eps, void* stream) {
+  if (M <= 0) return 0;
+  if (H % 4 || H > 4 * kNormThreads * kNormMaxVec) return ZSE_ERR_SHAPE;
+  add_rmsnorm_kernel<<<M, kNormThreads, 0, ST(stream)>>>(
+      reinterpret_cast<float*>(residual), reinterpret_cast<const float*>(partials), n_partials,
+      reinterpret_cast<const __half*>(add_f16), reinterpret_cast<const __half*>(weight),
+      reinterpret_cast<__half*>(out), M, H, eps);
+  return LAUNCH_OK();
+}
+
+extern "C" int zse_rmsnorm_f16(const void* x, const void* weight, void* out, int M, int H, float eps, void* stream) {
+  if (M <= 0) return 0;
+  rmsnorm_f16_kernel<<<M, kNormThreads, 0, ST(stream)>>>(reinterpret_cast<const __half*>(x),
+                                                         reinterpret_cast<const __half*>(weight),
+                                                         reinterpret_cast<__half*>(out), H, eps);
+  return LAUNCH_OK();
+}
+
+extern "C" int zse_rope_kv_write(void* qkv, void* kv_layer, const void* positions, const void* slots,
+                                 const void* inv_freq, int M, int nh, int nkv, int hd, int rotary_dim, int block_size,
+                                 void* stream) {
+  if (M <= 0) return 0;
+  if (hd % 2 || hd > 2048 || rotary_dim % 2 || rotary_dim > hd || (hd - rotary_dim) % 2) return ZSE_ERR_SHAPE;
+  dim3 grid(M, nh + 2 * nkv);
+  rope_kv_write_kernel<<<grid, hd / 2, 0, ST(stream)>>>(reinterpret_cast<__half*>(qkv),
+                                                        reinterpret_cast<__half*>(kv_layer),
+                                                        reinterpret_cast<const int*>(positions),
+                                                        reinterpret_cast<const long long*>(slots),
+                                                        reinterpret_cast<const float*>(inv_freq), nh, nkv, hd,
+                                                        rotary_dim, block_size);
+  return LAUNCH_OK();
+}
+
+extern "C" int zse_swiglu(const void* gate_up, void* out, int M, int I, int gelu, void* stream) {
+  if (M <= 0) return 0;
+  if (I % 2) return ZSE_ERR_SHAPE;
+  const size_t total = size_t(M) * (I / 2);
+  swiglu_kernel<<<unsigned((total + 255) / 256), 256, 0, ST(stream)>>>(reinterpret_cast<const __half2*>(gate_up),
+                                                                       reinterpret_cast<__half2*>(out), M, I / 2, gelu);
+  return LAUNCH_OK();
+}
+
+extern "C" int zse_bias_add(void* x, const void* bias, int M, int N, void* stream) {
+  const size_t total = size_t(M) * N;
+  if (!total) return 0;
+  bias_add_kernel<<<unsigned((total + 255) / 256), 256, 0, ST(stream)>>>(reinterpret_cast<__half*>(x),
+                                                                         reinterpret_cast<const __half*>(bias), total, N);
+  return LAUNCH_OK();
+}

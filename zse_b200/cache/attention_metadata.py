@@ -1,0 +1,34 @@
+"""Block tables and lengths of a batch, padded for the attention kernels
+(zse-engine/zse_engine/cache/attention_metadata.py:13-89): ``block_tables[num_seqs][max_blocks]`` int32 with -1 for
+padding and for evicted holes, ``seq_lengths[num_seqs]`` int32."""
+from __future__ import annotations
+
+import struct
+from dataclasses import dataclass
+from typing import List, Optional
+
+import numpy as np
+
+
+@dataclass
+class AttentionMetadata:
+    block_tables: List[List[int]]
+    seq_lengths: List[int]
+    num_seqs: int
+    max_seq_len: int
+    max_blocks_per_seq: int
+    block_size: int
+    is_prefill: Optional[List[bool]] = None
+
+    def block_table_array(self, width: Optional[int] = None) -> np.ndarray:
+        w = self.max_blocks_per_seq if width is None else width
+        out = np.full((self.num_seqs, max(1, w)), -1, dtype=np.int32)
+        for i, row in enumerate(self.block_tables):
+            out[i, : len(row)] = row[:w]
+        return out
+
+    def pack_block_tables(self) -> bytes:
+        return self.block_table_array().astype("<i4").tobytes()
+
+    def pack_seq_lengths(self) -> bytes:
+        return struct.pack(f"<{self.num_seqs}i", *self.seq_lengths)

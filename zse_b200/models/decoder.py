@@ -1,0 +1,245 @@
+"""Llama / Mistral / Qwen2 / Phi-3 decoder over the paged KV cache.
+
+One ``DecoderModel`` lives on one device and holds this rank's shard of the weights.  ``forward`` runs a pass over
+``M`` packed tokens that are already in the persistent step buffers (token ids, positions, cache slots, block
+tables...), so a pass allocates nothing and can be replayed from a CUDA graph.  The same pass serves prefill,
+chunked prefill, speculative verification (``mode="prefill"``: causal attention over the cache) and batched decode
+(``mode="decode"``: one token per sequence).
+
+Launch sequence per layer (tp = 1): add+RMSNorm -> fused QKV GEMM (+bias) -> RoPE + KV write -> attention ->
+o_proj (split-K fp32 partials) -> add+RMSNorm (reduces the partials into the fp32 residual) -> gate/up GEMM with
+SwiGLU epilogue -> down_proj (split-K partials).  That is 8 launches where the reference issues about 18
+(zse-engine/zse_engine/orchestrator/model_runner.py:1299-1474), with an fp32 residual stream like the reference.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Dict, List, Optional
+
+import numpy as np
+import torch
+
+from ..format.loader import ZSELoader
+from ..format.config import ModelConfig
+from ..ops import reference as ref
+from ..ops.backend import LinearWeight, TorchOps, make_ops, np_to_dev
+from ..parallel.shard_plan import ShardPlan, make_plan
+
+SUPPORTED_ARCHS = ("llama", "mistral", "qwen2", "phi3")
+
+
+def _entry_part(loader: ZSELoader, name: str, rows=None, cols=None) -> dict:
+    """Numpy views of one stored tensor, optionally restricted to a row range and/or a column (K) range."""
+    e = loader.weight_index.find(name)
+    if e is None:
+        raise KeyError(name)
+    N, K = e.shape
+    r0, r1 = rows if rows is not None else (0, N)
+    c0, c1 = cols if cols is not None else (0, K)
+    gs = e.group_size
+    if e.dtype == "float16":
+        return {"dtype": "float16", "data": loader.view_data(e)[r0:r1, c0:c1], "shape": (r1 - r0, c1 - c0)}
+    if e.dtype == "int8":
+        if K % gs or c0 % gs or c1 % gs:
+            full = loader.get_weight_as_float(e)[r0:r1, c0:c1].astype(np.float16)
+            return {"dtype": "float16", "data": full, "shape": full.shape}
+        q = loader.view_data(e).reshape(N, K)[r0:r1, c0:c1]
+        s = loader.view_scales(e).reshape(N, K // gs)[r0:r1, c0 // gs: c1 // gs]
+        return {"dtype": "int8", "data": q, "scales": s, "shape": (r1 - r0, c1 - c0)}
+    packed = loader.int4_rowmajor(e)
+    if K % gs == 0 and c0 % gs == 0 and c1 % gs == 0:
+        p = packed.reshape(N, K // 2)[r0:r1, c0 // 2: c1 // 2]
+        s = loader.view_scales(e).reshape(N, K // gs)[r0:r1, c0 // gs: c1 // gs]
+        z = loader.view_zeros(e).reshape(N, K // gs)[r0:r1, c0 // gs: c1 // gs]
+        return {"dtype": "int4", "data": p, "scales": s, "zeros": z, "shape": (r1 - r0, c1 - c0)}
+    # groups of the flattened tensor straddle rows: keep the whole tensor and slice after dequantisation
+    return {"dtype": "int4", "flat_data": packed, "flat_scales": loader.view_scales(e),
+            "flat_zeros": loader.view_zeros(e), "flat_shape": (N, K), "rows": (r0, r1), "cols": (c0, c1),
+            "shape": (r1 - r0, c1 - c0)}
+
+
+def _vec(loader: ZSELoader, name: str, rows=None) -> Optional[np.ndarray]:
+    e = loader.weight_index.find(name)
+    if e is None:
+        return None
+    v = loader.view_data(e).reshape(-1)
+    return v if rows is None else v[rows[0]: rows[1]]
+
+
+@dataclass
+class LayerWeights:
+    ln1: torch.Tensor
+    ln2: torch.Tensor
+    qkv: LinearWeight
+    o: LinearWeight
+    gate_up: LinearWeight
+    down: LinearWeight
+
+
+class StepBuffers:
+    """Persistent device tensors one pass reads and writes."""
+
+    def __init__(self, c: ModelConfig, plan: ShardPlan, device, max_tokens: int, max_seqs: int, max_blocks: int,
+                 max_planes: int, logits_rows: int, attn_splits: int):
+        f16, f32, i32, i64 = torch.float16, torch.float32, torch.int32, torch.int64
+        H = c.hidden_size
+        z = lambda *s, dt: torch.zeros(*s, dtype=dt, device=device)
+        self.max_tokens, self.max_seqs, self.max_blocks = max_tokens, max_seqs, max_blocks
+        self.ids = z(max_tokens, dt=i32)
+        self.positions = z(max_tokens, dt=i32)
+        self.slots = torch.full((max_tokens,), -1, dtype=i64, device=device)
+        self.block_tables = torch.full((max_seqs, max_blocks), -1, dtype=i32, device=device)
+        self.seq_lens = z(max_seqs, dt=i32)
+        self.cu_q = z(max_seqs + 1, dt=i32)
+        self.q_pos0 = z(max_seqs, dt=i32)
+        self.logit_rows = z(logits_rows, dt=i64)
+        self.residual = z(max_tokens, H, dt=f32)
+        self.xnorm = z(max_tokens, H, dt=f16)
+        self.qkv = z(max_tokens, plan.q_dim + 2 * plan.kv_dim, dt=f16)
+        self.attn_out = z(max_tokens, plan.q_dim, dt=f16)
+        self.act = z(max_tokens, plan.inter_size, dt=f16)
+        self.partials = z(max_planes, max_tokens, H, dt=f32)
+        self.xsel = z(logits_rows, H, dt=f16)
+        self.logits = z(logits_rows, plan.vocab_size, dt=f16)
+        self.out_tokens = z(logits_rows, dt=i32)
+        self.attn_splits = attn_splits
+        self.attn_scratch = z(max(1, max_seqs * plan.num_heads * attn_splits * (c.head_dim + 2)), dt=f32)
+        # sampling parameters per logits row
+        self.temperature = torch.ones(logits_rows, dtype=f32, device=device)
+        self.top_k = z(logits_rows, dt=i32)
+        self.top_p = torch.ones(logits_rows, dtype=f32, device=device)
+        self.seeds = z(logits_rows, dt=i64)
+        # LoRA routing
+        self.adapter_ids = torch.full((max_tokens,), -1, dtype=i32, device=device)
+        self.lora_tmp = z(max_tokens, 64, dt=f32)
+
+    def nbytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in vars(self).values() if isinstance(t, torch.Tensor))
+
+
+class DecoderModel:
+    def __init__(self, config: ModelConfig, plan: ShardPlan, ops: TorchOps):
+        self.config, self.plan, self.ops = config, plan, ops
+        self.device = ops.device
+        self.layers: List[LayerWeights] = []
+        self.embed: Optional[torch.Tensor] = None
+        self.norm: Optional[torch.Tensor] = None
+        self.lm_head: Optional[LinearWeight] = None
+        self.inv_freq: Optional[torch.Tensor] = None
+        self.scale = 1.0 / math.sqrt(config.head_dim)
+        self.comm = None            # parallel.comm.TPComm when tp_size > 1
+        self.lora = None            # lora.manager.LoRAManager
+        self.weight_bytes = 0
+        self.embed_scale = math.sqrt(config.hidden_size) if config.embed_scale else 1.0
+
+    # ---- loading --------------------------------------------------------------------------------------
+    @classmethod
+    def from_loader(cls, loader: ZSELoader, device="cpu", tp_size: int = 1, rank: int = 0, ops=None,
+                    progress=None) -> "DecoderModel":
+        c = loader.config
+        if c.arch not in SUPPORTED_ARCHS:
+            raise NotImplementedError(f"architecture '{c.arch}' has a converter but no runtime here yet "
+                                      f"(supported: {', '.join(SUPPORTED_ARCHS)})")
+        plan = make_plan(c, tp_size, rank)
+        m = cls(c, plan, ops or make_ops(device))
+        m._load(loader, progress)
+        return m
+
+    def _load(self, loader: ZSELoader, progress=None) -> None:
+        c, p, ops, dev = self.config, self.plan, self.ops, self.device
+        gs = c.quant.group_size
+        has = lambda n: loader.weight_index.find(n) is not None
+        to_dev = lambda a: np_to_dev(a, dev)
+        self.embed = to_dev(loader.view_data(loader.weight_index.find("embed_tokens.weight")))
+        self.norm = to_dev(_vec(loader, "norm.weight"))
+        self.weight_bytes += self.embed.numel() * 2
+        q_dim_full = c.num_heads * c.head_dim
+        kv_dim_full = c.num_kv_heads * c.head_dim
+        for i in range(c.num_layers):
+            pre = f"layers.{i}."
+            if has(pre + "self_attn.qkv_proj.weight"):     # Phi-3: [q; k; v] stacked in one tensor
+                n = pre + "self_attn.qkv_proj.weight"
+                qp = _entry_part(loader, n, rows=p.q_rows)
+                kp = _entry_part(loader, n, rows=(q_dim_full + p.kv_rows[0], q_dim_full + p.kv_rows[1]))
+                vp = _entry_part(loader, n, rows=(q_dim_full + kv_dim_full + p.kv_rows[0],
+                                                  q_dim_full + kv_dim_full + p.kv_rows[1]))
+                bias = None
+            else:
+                qp = _entry_part(loader, pre + "self_attn.q_proj.weight", rows=p.q_rows)
+                kp = _entry_part(loader, pre + "self_attn.k_proj.weight", rows=p.kv_rows)
+                vp = _entry_part(loader, pre + "self_attn.v_proj.weight", rows=p.kv_rows)
+                bq = _vec(loader, pre + "self_attn.q_proj.bias", p.q_rows)
+                bias = None
+                if bq is not None:
+                    bias = np.concatenate([bq, _vec(loader, pre + "self_attn.k_proj.bias", p.kv_rows),
+                                           _vec(loader, pre + "self_attn.v_proj.bias", p.kv_rows)])
+            qkv = ops.make_linear([qp, kp, vp], c.hidden_size, gs, bias)
+            o = ops.make_linear([_entry_part(loader, pre + "self_attn.o_proj.weight", cols=p.q_rows)], p.q_dim, gs)
+            if has(pre + "mlp.gate_up_proj.weight"):       # Phi-3: [gate; up]
+                n = pre + "mlp.gate_up_proj.weight"
+                I = c.intermediate_size
+                gp = _entry_part(loader, n, rows=p.inter)
+                up = _entry_part(loader, n, rows=(I + p.inter[0], I + p.inter[1]))
+            else:
+                gp = _entry_part(loader, pre + "mlp.gate_proj.weight", rows=p.inter)
+                up = _entry_part(loader, pre + "mlp.up_proj.weight", rows=p.inter)
+            gate_up = ops.make_linear([gp, up], c.hidden_size, gs, swiglu=True)
+            down = ops.make_linear([_entry_part(loader, pre + "mlp.down_proj.weight", cols=p.inter)], p.inter_size, gs)
+            self.layers.append(LayerWeights(to_dev(_vec(loader, pre + "input_layernorm.weight")),
+                                            to_dev(_vec(loader, pre + "post_attention_layernorm.weight")),
+                                            qkv, o, gate_up, down))
+            self.weight_bytes += qkv.nbytes + o.nbytes + gate_up.nbytes + down.nbytes
+            if progress:
+                progress(i + 1, c.num_layers)
+        head_name = "lm_head.weight" if has("lm_head.weight") else "embed_tokens.weight"   # tied embeddings
+        self.lm_head = ops.make_linear([_entry_part(loader, head_name, rows=p.vocab)], c.hidden_size, gs)
+        self.weight_bytes += self.lm_head.nbytes
+        self.inv_freq = ref.inv_freq(c.head_dim, c.rope_theta, c.rope_scaling).to(dev)
+
+    # ---- buffers --------------------------------------------------------------------------------------
+    def make_buffers(self, max_tokens: int, max_seqs: int, max_blocks: int, logits_rows: Optional[int] = None,
+                     max_planes: int = 8, attn_splits: int = 1) -> StepBuffers:
+        return StepBuffers(self.config, self.plan, self.device, max_tokens, max_seqs, max_blocks, max_planes,
+                           logits_rows or max_seqs, attn_splits)
+
+    # ---- forward --------------------------------------------------------------------------------------
+    def _reduce(self, b: StepBuffers, planes: int, M: int) -> int:
+        """Row-parallel outputs: with tensor parallelism the partial planes of all ranks are summed into plane 0."""
+        if self.comm is not None:
+            return self.comm.all_reduce_partials(b.partials, planes, M)
+        return planes
+
+    def forward(self, b: StepBuffers, kv: torch.Tensor, M: int, mode: str, num_seqs: int, max_q_len: int = 1,
+                n_logit_rows: int = 0, attn_splits: int = 1) -> None:
+        """Runs the stack over tokens ``b.ids[:M]``; leaves fp16 logits of rows ``b.logit_rows[:n_logit_rows]`` in
+        ``b.logits``.  ``kv``: [layers, blocks, 2, nkv_local, block_size, hd]."""
+        c, p, ops = self.config, self.plan, self.ops
+        bs = kv.shape[4]
+        ops.embedding(self.embed, b.ids, b.residual, M, self.embed_scale)
+        planes = 0
+        for li, L in enumerate(self.layers):
+            ops.add_rmsnorm(b.residual, b.partials, planes, None, L.ln1, b.xnorm, M, c.rms_norm_eps)
+            ops.linear(L.qkv, b.xnorm, M, b.qkv)
+            if self.lora is not None:
+                self.lora.apply_qkv(li, b, M)
+            ops.rope_kv_write(b.qkv, kv[li], b.positions, b.slots, self.inv_freq, M, p.num_heads, p.num_kv_heads,
+                              c.head_dim, bs)
+            if mode == "decode":
+                ops.attn_decode(b.qkv, kv[li], b.block_tables, b.seq_lens, b.attn_out, num_seqs, p.num_heads,
+                                p.num_kv_heads, c.head_dim, bs, self.scale, b.attn_scratch, attn_splits)
+            else:
+                ops.attn_prefill(b.qkv, kv[li], b.block_tables, b.cu_q, b.q_pos0, b.attn_out, num_seqs, M, max_q_len,
+                                 p.num_heads, p.num_kv_heads, c.head_dim, bs, self.scale)
+            planes = self._reduce(b, ops.linear_partial(L.o, b.attn_out, M, b.partials), M)
+            ops.add_rmsnorm(b.residual, b.partials, planes, None, L.ln2, b.xnorm, M, c.rms_norm_eps)
+            ops.linear_swiglu(L.gate_up, b.xnorm, M, b.act)
+            planes = self._reduce(b, ops.linear_partial(L.down, b.act, M, b.partials), M)
+        ops.add_rmsnorm(b.residual, b.partials, planes, None, self.norm, b.xnorm, M, c.rms_norm_eps)
+        if n_logit_rows:
+            torch.index_select(b.xnorm, 0, b.logit_rows[:n_logit_rows], out=b.xsel[:n_logit_rows])
+            ops.linear(self.lm_head, b.xsel, n_logit_rows, b.logits)
+
+    def hidden_rows(self, b: StepBuffers, rows: int) -> torch.Tensor:
+        """Final-norm hidden states of the first ``rows`` tokens of the last pass (for embeddings / RAG)."""
+        return b.xnorm[:rows]

@@ -1,0 +1,273 @@
+"""The op set the decoder is written against, with two implementations.
+
+``CudaOps``  - the hand-written sm_100a kernels in ``libzse_b200.so`` (fails loudly when the library is missing).
+``TorchOps`` - ``ops.reference`` on any device; runs the engine on CPU-only machines and serves as the oracle.
+
+Both work in place on caller-owned buffers so that a step allocates nothing and can be captured in a CUDA graph.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Optional
+
+import numpy as np
+import torch
+
+from . import reference as ref
+
+EPI_F16, EPI_SWIGLU, EPI_PARTIAL = 0, 1, 2
+
+
+@dataclass
+class LinearWeight:
+    """One (possibly fused / sharded) linear layer ready for the device."""
+    kind: str                  # "w4t" tiled INT4 | "f16" dense fp16 | "ref" fp32 (TorchOps)
+    N: int                     # output rows as the kernel sees them (gate+up counted together for swiglu)
+    K: int
+    data: torch.Tensor
+    bias: Optional[torch.Tensor] = None
+    swiglu: bool = False       # rows are gate/up interleaved in 64-row halves (w4t) or [gate; up] stacked (f16/ref)
+    nbytes: int = 0
+
+
+def _np_to_dev(a: np.ndarray, device) -> torch.Tensor:
+    """Host array -> tensor on ``device``.  Arrays that view a read-only file mapping are copied on the CPU path so
+    the tensor never aliases the mapping."""
+    a = np.ascontiguousarray(a)
+    if torch.device(device).type == "cpu" or not a.flags.writeable:
+        a = np.array(a, copy=True)
+    return torch.from_numpy(a).to(device, non_blocking=False)
+
+
+np_to_dev = _np_to_dev
+
+
+class TorchOps:
+    name = "torch"
+
+    def __init__(self, device="cpu"):
+        self.device = torch.device(device)
+        self.status = None
+
+    # ---- weights --------------------------------------------------------------------------------------
+    def make_linear(self, parts, K: int, group_size: int, bias=None, swiglu: bool = False) -> LinearWeight:
+        """``parts``: list of dicts {dtype, data(np), scales(np), zeros(np), shape, row_major_group_ok}; rows are
+        concatenated in order (q,k,v or gate,up)."""
+        ws = []
+        for p in parts:
+            ws.append(_dense_f32(p, group_size, self.device))
+        w = torch.cat(ws, dim=0) if len(ws) > 1 else ws[0]
+        b = None if bias is None else _np_to_dev(bias, self.device)
+        return LinearWeight("ref", w.shape[0], K, w, b, swiglu, w.numel() * 4)
+
+    def check(self):
+        pass
+
+    # ---- ops ------------------------------------------------------------------------------------------
+    def linear(self, w: LinearWeight, x, M, out, x_cap=None):
+        out[:M, : w.N] = ref.linear(x[:M], w.data, w.bias)
+
+    def linear_swiglu(self, w: LinearWeight, x, M, out, x_cap=None, gelu=False):
+        y = x[:M].float() @ w.data.T
+        half = w.N // 2
+        out[:M, :half] = ref.swiglu(y[:, :half], y[:, half:], gelu)
+
+    def linear_partial(self, w: LinearWeight, x, M, partials, k_split=1, x_cap=None) -> int:
+        partials[0, :M, : w.N] = x[:M].float() @ w.data.T
+        return 1
+
+    def embedding(self, table, ids, out, M, scale=1.0):
+        out[:M] = table[ids[:M].long()].float() * scale
+
+    def add_rmsnorm(self, residual, partials, n_partials, add_f16, weight, out, M, eps):
+        H = residual.shape[1]
+        if n_partials:
+            residual[:M] += partials[:n_partials, :M, :H].sum(0)
+        if add_f16 is not None:
+            residual[:M] += add_f16[:M].float()
+        if out is not None:
+            out[:M] = ref.rmsnorm(residual[:M], weight, eps)
+
+    def rope_kv_write(self, qkv, kv_layer, positions, slots, inv_freq, M, nh, nkv, hd, block_size):
+        ref.rope_kv_write(qkv[:M], kv_layer, positions[:M], slots[:M], inv_freq, nh, nkv, hd, block_size)
+
+    def attn_decode(self, qkv, kv_layer, block_tables, seq_lens, out, S, nh, nkv, hd, block_size, scale, scratch=None,
+                    num_splits=1):
+        out[:S] = ref.attn_decode(qkv[:S, : nh * hd], kv_layer, block_tables[:S], seq_lens[:S], nh, nkv, hd,
+                                  block_size, scale)
+
+    def attn_prefill(self, qkv, kv_layer, block_tables, cu_q, q_pos0, out, num_seqs, total_q, max_q_len, nh, nkv, hd,
+                     block_size, scale):
+        out[:total_q] = ref.attn_prefill(qkv[:total_q, : nh * hd], kv_layer, block_tables[:num_seqs],
+                                         cu_q[: num_seqs + 1], q_pos0[:num_seqs], nh, nkv, hd, block_size, scale)
+
+    def argmax(self, logits, out, M):
+        out[:M] = logits[:M].float().argmax(dim=-1).to(out.dtype)
+
+    def sample(self, logits, out, M, temperature, top_k, top_p, seeds, step):
+        for r in range(M):
+            t = float(temperature[r])
+            if t <= 0 or int(top_k[r]) == 1:
+                out[r] = int(logits[r].float().argmax())
+                continue
+            p = ref.filtered_probs(logits[r], t, int(top_k[r]), float(top_p[r]))
+            g = torch.Generator(device="cpu").manual_seed((int(seeds[r]) * 1000003 + int(step) * 7919 + r) % (2 ** 63))
+            out[r] = int(torch.multinomial(p.cpu(), 1, generator=g))
+
+    def apply_repetition_penalty(self, logits, rows, tokens, counts, n, penalty):
+        for i in range(n):
+            r, t, c = int(rows[i]), int(tokens[i]), int(counts[i])
+            pen = float(penalty[r])
+            if c > 0 and pen != 1.0:
+                f = pen ** (1.0 + float(np.log2(c)))
+                v = float(logits[r, t])
+                logits[r, t] = v / f if v > 0 else v * f
+
+    def lora_apply(self, x, a_table, b_table, ids, scales, y, M, K, N, rank, tmp=None, y_col0=0):
+        for t in range(M):
+            a = int(ids[t])
+            if a >= 0:
+                d = ref.lora_delta(x[t: t + 1, :K], a_table[a], b_table[a], float(scales[a]))
+                y[t, y_col0: y_col0 + N] = (y[t, y_col0: y_col0 + N].float() + d[0]).clamp(-65504, 65504).to(y.dtype)
+
+
+def _dense_f32(p: dict, group_size: int, device) -> torch.Tensor:
+    shape = tuple(p["shape"])
+    if p["dtype"] == "float16":
+        return _np_to_dev(p["data"], device).reshape(shape).float()
+    if p["dtype"] == "int8":
+        return ref.dequant_int8(_np_to_dev(p["data"], device), _np_to_dev(p["scales"], device), shape, group_size)
+    if "flat_data" in p:   # a column slice of a tensor whose flat groups straddle rows: dequantise whole, slice
+        full = ref.dequant_int4(_np_to_dev(p["flat_data"], device), _np_to_dev(p["flat_scales"], device),
+                                _np_to_dev(p["flat_zeros"], device), p["flat_shape"], group_size)
+        (r0, r1), (c0, c1) = p["rows"], p["cols"]
+        return full[r0:r1, c0:c1].contiguous()
+    return ref.dequant_int4(_np_to_dev(p["data"], device), _np_to_dev(p["scales"], device),
+                            _np_to_dev(p["zeros"], device), shape, group_size)
+
+
+class CudaOps(TorchOps):
+    name = "cuda"
+
+    def __init__(self, device="cuda"):
+        from . import native
+        if not torch.cuda.is_available():
+            raise RuntimeError("CudaOps needs a CUDA device")
+        self.n = native
+        native.load(build_if_missing=True)
+        self.device = torch.device(device)
+        self.status = native.Status(self.device)
+        self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
+
+    def check(self):
+        self.status.check()
+
+    # ---- weights --------------------------------------------------------------------------------------
+    def make_linear(self, parts, K: int, group_size: int, bias=None, swiglu: bool = False) -> LinearWeight:
+        n = self.n
+        b = None if bias is None else _np_to_dev(bias, self.device)
+        tiled_ok = (K % 128 == 0 and group_size == 128
+                    and all(p["dtype"] == "int4" and "flat_data" not in p for p in parts))
+        if swiglu and tiled_ok:
+            tiled_ok = len(parts) == 2 and parts[0]["shape"][0] == parts[1]["shape"][0]
+        if tiled_ok:
+            packed = torch.cat([_np_to_dev(p["data"], self.device).reshape(p["shape"][0], K // 2) for p in parts])
+            scales = torch.cat([_np_to_dev(p["scales"], self.device).reshape(p["shape"][0], K // 128) for p in parts])
+            zeros = torch.cat([_np_to_dev(p["zeros"], self.device).reshape(p["shape"][0], K // 128) for p in parts])
+            N = packed.shape[0]
+            inter = N // 2 if swiglu else 0
+            n_tiles = (inter + 63) // 64 if swiglu else (N + 127) // 128
+            out = torch.empty(n_tiles * (K // 128) * 8704, dtype=torch.uint8, device=self.device)
+            n.repack_w4(packed, scales, zeros, out, N, K, inter)
+            torch.cuda.current_stream().synchronize()
+            return LinearWeight("w4t", N, K, out, b, swiglu, out.numel())
+        # anything else becomes dense fp16 for the SS-mode kernel
+        ws = [_dense_f32(p, group_size, self.device).to(torch.float16) for p in parts]
+        w = torch.cat(ws, dim=0).contiguous() if len(ws) > 1 else ws[0].contiguous()
+        return LinearWeight("f16", w.shape[0], K, w, b, swiglu, w.numel() * 2)
+
+    # ---- ops ------------------------------------------------------------------------------------------
+    def linear(self, w, x, M, out, x_cap=None):
+        cap = x.shape[0] if x_cap is None else x_cap
+        if w.kind == "w4t":
+            self.n.gemm_w4(w.data, x, cap, w.bias, out, M, w.N, w.K, out.stride(0), EPI_F16, 1, self.status.ptr)
+        else:
+            self.n.gemm_f16(w.data, w.N, x, cap, w.bias, out, M, w.N, w.K, out.stride(0), EPI_F16, 1, self.status.ptr)
+
+    def linear_swiglu(self, w, x, M, out, x_cap=None, gelu=False, tmp=None):
+        cap = x.shape[0] if x_cap is None else x_cap
+        if w.kind == "w4t" and not gelu:
+            self.n.gemm_w4(w.data, x, cap, None, out, M, w.N, w.K, out.stride(0), EPI_SWIGLU, 1, self.status.ptr)
+        else:
+            if w.kind == "w4t":
+                raise NotImplementedError("GeGLU needs the dense path")
+            gu = torch.empty(M, w.N, dtype=torch.float16, device=self.device) if tmp is None else tmp
+            self.n.gemm_f16(w.data, w.N, x, cap, None, gu, M, w.N, w.K, gu.stride(0), EPI_F16, 1, self.status.ptr)
+            self.n.swiglu(gu, out, M, w.N // 2, gelu)
+
+    def pick_k_split(self, w, M) -> int:
+        n_tiles = (w.N + 127) // 128
+        nt = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128 if M <= 128 else 256
+        ctas = n_tiles * ((M + nt - 1) // nt)
+        per_sm = 2 if nt <= 64 else 1
+        want = max(1, (self.sm_count * per_sm) // max(1, ctas))
+        stage_k = 128 if w.kind == "w4t" else 64
+        return max(1, min(want, 8, (w.K // stage_k) // 4 or 1))
+
+    def linear_partial(self, w, x, M, partials, k_split=None, x_cap=None) -> int:
+        cap = x.shape[0] if x_cap is None else x_cap
+        ks = self.pick_k_split(w, M) if k_split is None else k_split
+        ks = min(ks, partials.shape[0])
+        if w.kind == "w4t":
+            planes = self.n.gemm_w4_splits(M, w.N, w.K, ks)
+            self.n.gemm_w4(w.data, x, cap, None, partials, M, w.N, w.K, partials.stride(1), EPI_PARTIAL, ks,
+                           self.status.ptr)
+        else:
+            planes = self.n.gemm_f16_splits(M, w.N, w.K, ks)
+            self.n.gemm_f16(w.data, w.N, x, cap, None, partials, M, w.N, w.K, partials.stride(1), EPI_PARTIAL, ks,
+                            self.status.ptr)
+        return planes
+
+    def embedding(self, table, ids, out, M, scale=1.0):
+        self.n.embedding(table, ids, out, M, table.shape[1], table.shape[0], float(scale), self.status.ptr)
+
+    def add_rmsnorm(self, residual, partials, n_partials, add_f16, weight, out, M, eps):
+        # partial planes are laid out [plane][M rows][H]: the plane stride the kernel assumes is M*H
+        self.n.add_rmsnorm(residual, partials, n_partials, add_f16, weight, out, M, residual.shape[1], float(eps))
+
+    def rope_kv_write(self, qkv, kv_layer, positions, slots, inv_freq, M, nh, nkv, hd, block_size):
+        self.n.rope_kv_write(qkv, kv_layer, positions, slots, inv_freq, M, nh, nkv, hd, inv_freq.numel() * 2,
+                             block_size)
+
+    def attn_decode(self, qkv, kv_layer, block_tables, seq_lens, out, S, nh, nkv, hd, block_size, scale, scratch=None,
+                    num_splits=1):
+        self.n.attn_decode(qkv, qkv.stride(0), kv_layer, block_tables, block_tables.stride(0), seq_lens, out,
+                           out.stride(0), scratch, S, nh, nkv, hd, block_size, num_splits, float(scale))
+
+    def attn_prefill(self, qkv, kv_layer, block_tables, cu_q, q_pos0, out, num_seqs, total_q, max_q_len, nh, nkv, hd,
+                     block_size, scale):
+        self.n.attn_prefill(qkv, qkv.stride(0), kv_layer, block_tables, block_tables.stride(0), cu_q, q_pos0, out,
+                            out.stride(0), num_seqs, max_q_len, nh, nkv, hd, block_size, float(scale))
+
+    def argmax(self, logits, out, M):
+        self.n.argmax(logits, logits.stride(0), out, M, logits.shape[1])
+
+    def sample(self, logits, out, M, temperature, top_k, top_p, seeds, step):
+        self.n.sample(logits, logits.stride(0), out, M, logits.shape[1], temperature, top_k, top_p, seeds, int(step))
+
+    def apply_repetition_penalty(self, logits, rows, tokens, counts, n, penalty):
+        self.n.apply_repetition_penalty(logits, logits.stride(0), rows, tokens, counts, n, penalty, logits.shape[1])
+
+    def lora_apply(self, x, a_table, b_table, ids, scales, y, M, K, N, rank, tmp=None, y_col0=0):
+        if tmp is None:
+            tmp = torch.empty(M, rank, dtype=torch.float32, device=self.device)
+        self.n.lora_shrink(x, x.stride(0), a_table, ids, tmp, M, K, rank)
+        yv = y[:, y_col0:]
+        self.n.lora_expand(tmp, b_table, ids, scales, yv, y.stride(0), M, N, rank)
+
+
+def make_ops(device) -> TorchOps:
+    device = torch.device(device)
+    if device.type == "cuda":
+        return CudaOps(device)
+    return TorchOps(device)

@@ -1,0 +1,247 @@
+"""ctypes binding of ``libzse_b200.so`` (see ``csrc/api.h``) on torch tensors.
+
+Every call launches on ``torch.cuda.current_stream()``, so the kernels order with torch ops and are captured by
+``torch.cuda.graph``.  A negative return code raises ``NativeError``; device-side failures are read with
+``check_status``.  On a machine with a GPU a missing library is an error, never a silent fallback.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import c_char_p, c_float, c_int, c_int64, c_uint64, c_void_p, POINTER, c_uint32
+from typing import Optional
+
+import torch
+
+from . import build as _build
+
+_ERRORS = {-1: "unsupported shape", -2: "misaligned pointer or stride", -3: "CUDA driver call failed",
+           -4: "kernel launch failed", -5: "size beyond a built-in limit"}
+
+
+class NativeError(RuntimeError):
+    pass
+
+
+class DeviceStatusError(RuntimeError):
+    """A kernel reported a failure through the status word (bounded wait ran out, bad index, ...)."""
+
+
+_lib: Optional[ctypes.CDLL] = None
+
+_SIGS = {
+    "zse_gemm_w4": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                            c_void_p, c_void_p]),
+    "zse_gemm_w4_splits": (c_int, [c_int, c_int, c_int, c_int]),
+    "zse_gemm_f16": (c_int, [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                             c_int, c_void_p, c_void_p]),
+    "zse_gemm_f16_splits": (c_int, [c_int, c_int, c_int, c_int]),
+    "zse_w4_tiled_bytes": (c_int64, [c_int, c_int]),
+    "zse_repack_w4": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "zse_dequant_w4": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p]),
+    "zse_dequant_w8": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_void_p]),
+    "zse_quantize_w4": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p]),
+    "zse_embedding": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_void_p]),
+    "zse_add_rmsnorm": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float,
+                                c_void_p]),
+    "zse_rmsnorm_f16": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p]),
+    "zse_rope_kv_write": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                  c_int, c_void_p]),
+    "zse_swiglu": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "zse_bias_add": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p]),
+    "zse_attn_decode_scratch_floats": (c_int64, [c_int, c_int, c_int, c_int]),
+    "zse_attn_decode": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int,
+                                c_int, c_int, c_int, c_int, c_int, c_float, c_void_p]),
+    "zse_attn_prefill": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                                 c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p]),
+    "zse_argmax": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p]),
+    "zse_sample": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_uint64,
+                           c_void_p]),
+    "zse_apply_repetition_penalty": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
+                                             c_void_p]),
+    "zse_lora_shrink": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "zse_lora_expand": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                c_void_p]),
+    "zse_status_read": (c_int, [c_void_p, POINTER(c_uint32)]),
+    "zse_device_info": (c_int, [POINTER(c_int), POINTER(c_int), POINTER(c_int), POINTER(c_int64), POINTER(c_int64)]),
+    "zse_build_info": (c_char_p, []),
+}
+
+
+def lib_path() -> str:
+    return _build.LIB_PATH
+
+
+def load(build_if_missing: bool = True) -> ctypes.CDLL:
+    global _lib
+    if _lib is not None:
+        return _lib
+    path = lib_path()
+    if not os.path.exists(path):
+        if not build_if_missing:
+            raise NativeError(f"{path} is missing: run `python -m zse_b200.ops.build`")
+        _build.build()
+    lib = ctypes.CDLL(path)
+    for name, (res, args) in _SIGS.items():
+        fn = getattr(lib, name, None)
+        if fn is None:
+            continue   # optional entry points are looked up by their users
+        fn.restype, fn.argtypes = res, args
+    _lib = lib
+    return lib
+
+
+def available() -> bool:
+    return torch.cuda.is_available()
+
+
+def _p(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ck(rc: int, what: str) -> None:
+    if rc < 0:
+        raise NativeError(f"{what}: {_ERRORS.get(rc, rc)}")
+
+
+class Status:
+    """The 16-byte device status word shared by all launches of one engine."""
+
+    def __init__(self, device):
+        self.buf = torch.zeros(4, dtype=torch.int32, device=device)
+
+    @property
+    def ptr(self) -> int:
+        return self.buf.data_ptr()
+
+    def read(self):
+        out = (c_uint32 * 4)()
+        _ck(load().zse_status_read(self.ptr, out), "status read")
+        return tuple(out)
+
+    def check(self) -> None:
+        code, block, where, detail = self.read()
+        if code:
+            self.buf.zero_()
+            kind = {1: "wait timed out", 2: "bad argument", 3: "peer wait timed out"}.get(code, f"code {code}")
+            raise DeviceStatusError(f"device reported: {kind} (block {block}, site {where}, detail {detail})")
+
+
+# ---- thin wrappers (shapes are checked by the callers in ops/linear.py and the model runner) -------------------
+def gemm_w4(w_tiled, x, x_rows_cap, bias, out, M, N, K, ldo, epilogue, k_split, status):
+    _ck(load().zse_gemm_w4(_p(w_tiled), _p(x), x_rows_cap, _p(bias), _p(out), M, N, K, ldo, epilogue, k_split,
+                           status, _stream()), "gemm_w4")
+
+
+def gemm_f16(w, w_rows, x, x_rows_cap, bias, out, M, N, K, ldo, epilogue, k_split, status):
+    _ck(load().zse_gemm_f16(_p(w), w_rows, _p(x), x_rows_cap, _p(bias), _p(out), M, N, K, ldo, epilogue, k_split,
+                            status, _stream()), "gemm_f16")
+
+
+def gemm_w4_splits(M, N, K, k_split) -> int:
+    return load().zse_gemm_w4_splits(M, N, K, k_split)
+
+
+def gemm_f16_splits(M, N, K, k_split) -> int:
+    return load().zse_gemm_f16_splits(M, N, K, k_split)
+
+
+def w4_tiled_bytes(N, K) -> int:
+    return load().zse_w4_tiled_bytes(N, K)
+
+
+def repack_w4(packed, scales, zeros, out, N, K, interleave_rows=0):
+    _ck(load().zse_repack_w4(_p(packed), _p(scales), _p(zeros), _p(out), N, K, interleave_rows, _stream()),
+        "repack_w4")
+
+
+def dequant_w4(packed, scales, zeros, out, n_elements, group_size):
+    _ck(load().zse_dequant_w4(_p(packed), _p(scales), _p(zeros), _p(out), n_elements, group_size, _stream()),
+        "dequant_w4")
+
+
+def dequant_w8(q, scales, out, n_elements, group_size):
+    _ck(load().zse_dequant_w8(_p(q), _p(scales), _p(out), n_elements, group_size, _stream()), "dequant_w8")
+
+
+def quantize_w4(w, packed, scales, zeros, n_groups):
+    _ck(load().zse_quantize_w4(_p(w), _p(packed), _p(scales), _p(zeros), n_groups, _stream()), "quantize_w4")
+
+
+def embedding(table, ids, out, M, H, vocab, scale, status):
+    _ck(load().zse_embedding(_p(table), _p(ids), _p(out), M, H, vocab, scale, status, _stream()), "embedding")
+
+
+def add_rmsnorm(residual, partials, n_partials, add_f16, weight, out, M, H, eps):
+    _ck(load().zse_add_rmsnorm(_p(residual), _p(partials), n_partials, _p(add_f16), _p(weight), _p(out), M, H, eps,
+                               _stream()), "add_rmsnorm")
+
+
+def rmsnorm_f16(x, weight, out, M, H, eps):
+    _ck(load().zse_rmsnorm_f16(_p(x), _p(weight), _p(out), M, H, eps, _stream()), "rmsnorm_f16")
+
+
+def rope_kv_write(qkv, kv_layer, positions, slots, inv_freq, M, nh, nkv, hd, rotary_dim, block_size):
+    _ck(load().zse_rope_kv_write(_p(qkv), _p(kv_layer), _p(positions), _p(slots), _p(inv_freq), M, nh, nkv, hd,
+                                 rotary_dim, block_size, _stream()), "rope_kv_write")
+
+
+def swiglu(gate_up, out, M, I, gelu=False):
+    _ck(load().zse_swiglu(_p(gate_up), _p(out), M, I, int(gelu), _stream()), "swiglu")
+
+
+def bias_add(x, bias, M, N):
+    _ck(load().zse_bias_add(_p(x), _p(bias), M, N, _stream()), "bias_add")
+
+
+def attn_decode_scratch_floats(num_seqs, nh, hd, max_splits) -> int:
+    return load().zse_attn_decode_scratch_floats(num_seqs, nh, hd, max_splits)
+
+
+def attn_decode(q, ldq, kv_layer, block_tables, max_blocks, seq_lens, out, ldo, scratch, num_seqs, nh, nkv, hd,
+                block_size, num_splits, scale):
+    _ck(load().zse_attn_decode(_p(q), ldq, _p(kv_layer), _p(block_tables), max_blocks, _p(seq_lens), _p(out), ldo,
+                               _p(scratch), num_seqs, nh, nkv, hd, block_size, num_splits, scale, _stream()),
+        "attn_decode")
+
+
+def attn_prefill(q, ldq, kv_layer, block_tables, max_blocks, cu_q, q_pos0, out, ldo, num_seqs, max_q_len, nh, nkv,
+                 hd, block_size, scale):
+    _ck(load().zse_attn_prefill(_p(q), ldq, _p(kv_layer), _p(block_tables), max_blocks, _p(cu_q), _p(q_pos0), _p(out),
+                                ldo, num_seqs, max_q_len, nh, nkv, hd, block_size, scale, _stream()), "attn_prefill")
+
+
+def argmax(logits, ld, out, M, V):
+    _ck(load().zse_argmax(_p(logits), ld, _p(out), M, V, _stream()), "argmax")
+
+
+def sample(logits, ld, out, M, V, temperature, top_k, top_p, seeds, step):
+    _ck(load().zse_sample(_p(logits), ld, _p(out), M, V, _p(temperature), _p(top_k), _p(top_p), _p(seeds), step,
+                          _stream()), "sample")
+
+
+def apply_repetition_penalty(logits, ld, rows, tokens, counts, n, penalty, V):
+    _ck(load().zse_apply_repetition_penalty(_p(logits), ld, _p(rows), _p(tokens), _p(counts), n, _p(penalty), V,
+                                            _stream()), "repetition_penalty")
+
+
+def lora_shrink(x, ldx, a, ids, tmp, M, K, rank):
+    _ck(load().zse_lora_shrink(_p(x), ldx, _p(a), _p(ids), _p(tmp), M, K, rank, _stream()), "lora_shrink")
+
+
+def lora_expand(tmp, b, ids, scales, y, ldy, M, N, rank):
+    _ck(load().zse_lora_expand(_p(tmp), _p(b), _p(ids), _p(scales), _p(y), ldy, M, N, rank, _stream()), "lora_expand")
+
+
+def device_info() -> dict:
+    sm, maj, mnr, tot, free = c_int(), c_int(), c_int(), c_int64(), c_int64()
+    _ck(load().zse_device_info(sm, maj, mnr, tot, free), "device_info")
+    return {"sm_count": sm.value, "cc": (maj.value, mnr.value), "total_mem": tot.value, "free_mem": free.value}
+
+
+def build_info() -> str:
+    return load().zse_build_info().decode()

@@ -1,0 +1,279 @@
+"""ModelRunner: turns scheduler decisions into passes of the decoder.
+
+Capabilities of zse-engine/zse_engine/orchestrator/model_runner.py:51-2473 (``prefill``, ``decode_step``,
+``batched_decode``, ``verify_tokens``, ``embed_pooled``, graph variants) on the new stack:
+
+* ``prefill`` handles any chunk of any sequence at its true cache position (chunk >= 2 and speculative verification
+  attend to the whole past; the reference restarts at position 0, model_runner.py:305,761-841);
+* several sequences can be prefilled in one packed pass;
+* ``decode`` is always batched; per batch-size bucket the whole step (all layers, lm_head, sampling) is captured in
+  one CUDA graph and replayed with the inputs staged through pinned host memory;
+* token selection happens on the device (``argmax`` / ``sample``), only token ids come back.
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from ..cache.cache_manager import KVCacheManager
+from ..models.decoder import DecoderModel, StepBuffers
+
+
+@dataclass
+class SamplingRow:
+    temperature: float = 0.0      # 0 = greedy
+    top_k: int = 0
+    top_p: float = 1.0
+    seed: int = 0
+
+    @property
+    def greedy(self) -> bool:
+        return self.temperature <= 0.0 or self.top_k == 1
+
+
+GREEDY = SamplingRow()
+
+
+def _bucket(n: int, buckets: Sequence[int]) -> int:
+    for b in buckets:
+        if n <= b:
+            return b
+    return buckets[-1]
+
+
+class ModelRunner:
+    DECODE_BUCKETS = (1, 2, 4, 8, 16, 32, 64, 128, 256)
+
+    def __init__(self, model: DecoderModel, cache: KVCacheManager, max_batch_seqs: int = 64,
+                 max_tokens_per_pass: int = 2048, max_seq_len: Optional[int] = None, use_graphs: Optional[bool] = None,
+                 attn_splits: Optional[int] = None):
+        self.model, self.cache = model, cache
+        self.device = model.device
+        c = model.config
+        self.max_seq_len = min(max_seq_len or c.max_seq_len, c.max_seq_len)
+        self.max_batch_seqs = max_batch_seqs
+        self.max_tokens = max(max_tokens_per_pass, max_batch_seqs)
+        self.max_blocks = (self.max_seq_len + cache.block_size - 1) // cache.block_size
+        on_gpu = self.device.type == "cuda"
+        self.use_graphs = on_gpu if use_graphs is None else (use_graphs and on_gpu)
+        sm = torch.cuda.get_device_properties(self.device).multi_processor_count if on_gpu else 1
+        self._sm = sm
+        self.max_attn_splits = attn_splits or (16 if on_gpu else 1)
+        logits_rows = max(max_batch_seqs, 64)
+        self.buf = model.make_buffers(self.max_tokens, max_batch_seqs, self.max_blocks, logits_rows,
+                                      max_planes=8, attn_splits=self.max_attn_splits)
+        self._graphs: Dict[Tuple[int, int, bool], torch.cuda.CUDAGraph] = {}
+        self._step = 0
+        pin = on_gpu
+        mk = lambda shape, dt: torch.zeros(shape, dtype=dt, pin_memory=pin)
+        self.h_ids = mk(self.max_tokens, torch.int32)
+        self.h_pos = mk(self.max_tokens, torch.int32)
+        self.h_slots = mk(self.max_tokens, torch.int64)
+        self.h_bt = mk((max_batch_seqs, self.max_blocks), torch.int32)
+        self.h_lens = mk(max_batch_seqs, torch.int32)
+        self.h_cu = mk(max_batch_seqs + 1, torch.int32)
+        self.h_pos0 = mk(max_batch_seqs, torch.int32)
+        self.h_rows = mk(logits_rows, torch.int64)
+        self.h_temp = mk(logits_rows, torch.float32)
+        self.h_topk = mk(logits_rows, torch.int32)
+        self.h_topp = mk(logits_rows, torch.float32)
+        self.h_seed = mk(logits_rows, torch.int64)
+        self.h_adapter = mk(self.max_tokens, torch.int32)
+        self.h_out = mk(logits_rows, torch.int32)
+        self.timings = {"prefill_passes": 0, "decode_steps": 0, "graph_replays": 0, "graph_captures": 0}
+
+    # ---- staging ----------------------------------------------------------------------------------------
+    def _upload(self, dst: torch.Tensor, src: torch.Tensor, n) -> None:
+        dst[:n].copy_(src[:n], non_blocking=True)
+
+    def _stage_sampling(self, rows: Sequence[SamplingRow], n_pad: int) -> bool:
+        all_greedy = all(r.greedy for r in rows)
+        if not all_greedy:
+            n = len(rows)
+            self.h_temp[:n] = torch.tensor([r.temperature for r in rows])
+            self.h_topk[:n] = torch.tensor([r.top_k for r in rows], dtype=torch.int32)
+            self.h_topp[:n] = torch.tensor([r.top_p for r in rows])
+            self.h_seed[:n] = torch.tensor([r.seed & 0x7FFFFFFFFFFFFFFF for r in rows], dtype=torch.int64)
+            if n_pad > n:
+                self.h_temp[n:n_pad] = 0
+            b = self.buf
+            self._upload(b.temperature, self.h_temp, n_pad)
+            self._upload(b.top_k, self.h_topk, n_pad)
+            self._upload(b.top_p, self.h_topp, n_pad)
+            self._upload(b.seeds, self.h_seed, n_pad)
+        return all_greedy
+
+    def _stage_adapters(self, per_token: Optional[Sequence[int]], M: int, M_pad: int) -> None:
+        if self.model.lora is None:
+            return
+        if per_token is None:
+            self.h_adapter[:M_pad] = -1
+        else:
+            self.h_adapter[:M] = torch.as_tensor(list(per_token), dtype=torch.int32)
+            self.h_adapter[M:M_pad] = -1
+        self._upload(self.buf.adapter_ids, self.h_adapter, M_pad)
+
+    def _select(self, n_rows: int, greedy: bool) -> None:
+        b, ops = self.buf, self.model.ops
+        if self.model.comm is not None:
+            self.model.comm.select_tokens(self, n_rows, greedy, self._step)
+        elif greedy:
+            ops.argmax(b.logits, b.out_tokens, n_rows)
+        else:
+            ops.sample(b.logits, b.out_tokens, n_rows, b.temperature, b.top_k, b.top_p, b.seeds, self._step)
+
+    def _fetch_tokens(self, n: int) -> List[int]:
+        self.h_out[:n].copy_(self.buf.out_tokens[:n], non_blocking=True)
+        if self.device.type == "cuda":
+            torch.cuda.current_stream().synchronize()
+        self.model.ops.check()
+        return self.h_out[:n].tolist()
+
+    # ---- prefill / chunk / verify -------------------------------------------------------------------------
+    def prefill(self, items: Sequence[Tuple[int, Sequence[int], int]], sampling: Optional[Sequence[SamplingRow]] = None,
+                all_logits: bool = False, adapters: Optional[Sequence[int]] = None, select: bool = True):
+        """``items``: ``(seq_id, chunk_tokens, start_position)``; the cache must already hold blocks for positions
+        ``start .. start+len-1`` of each sequence.  Returns the token chosen after each chunk's last token, or (with
+        ``all_logits``) the fp16 logits of every row (device tensor view, valid until the next pass)."""
+        b, cache = self.buf, self.cache
+        S = len(items)
+        total = sum(len(t) for _, t, _ in items)
+        if S > self.max_batch_seqs or total > self.max_tokens:
+            raise ValueError(f"prefill pass of {total} tokens / {S} sequences exceeds the pass limits "
+                             f"({self.max_tokens} / {self.max_batch_seqs})")
+        at, max_q, rows = 0, 0, []
+        self.h_bt[:S].fill_(-1)
+        per_tok_adapter = [] if adapters is not None else None
+        for s, (sid, toks, start) in enumerate(items):
+            n = len(toks)
+            self.h_ids[at:at + n] = torch.as_tensor(list(toks), dtype=torch.int32)
+            self.h_pos[at:at + n] = torch.arange(start, start + n, dtype=torch.int32)
+            self.h_slots[at:at + n] = torch.from_numpy(cache.slots_for_range(sid, start, n))
+            ids = cache.get_block_ids(sid)
+            self.h_bt[s, :len(ids)] = torch.as_tensor(ids, dtype=torch.int32)
+            self.h_cu[s] = at
+            self.h_pos0[s] = start
+            if per_tok_adapter is not None:
+                per_tok_adapter += [adapters[s]] * n
+            rows += list(range(at, at + n)) if all_logits else [at + n - 1]
+            at += n
+            max_q = max(max_q, n)
+        self.h_cu[S] = at
+        n_rows = len(rows)
+        if n_rows > b.logits.shape[0]:
+            raise ValueError(f"{n_rows} logits rows requested, buffer holds {b.logits.shape[0]}")
+        self.h_rows[:n_rows] = torch.as_tensor(rows, dtype=torch.int64)
+        for dst, src, n in ((b.ids, self.h_ids, total), (b.positions, self.h_pos, total), (b.slots, self.h_slots, total),
+                            (b.block_tables, self.h_bt, S), (b.cu_q, self.h_cu, S + 1), (b.q_pos0, self.h_pos0, S),
+                            (b.logit_rows, self.h_rows, n_rows)):
+            self._upload(dst, src, n)
+        self._stage_adapters(per_tok_adapter, total, total)
+        greedy = self._stage_sampling(sampling or [GREEDY] * n_rows, n_rows) if select else True
+        self.model.forward(b, cache.slab, total, "prefill", S, max_q, n_rows)
+        self.timings["prefill_passes"] += 1
+        self._step += 1
+        for sid, toks, start in items:
+            cache.commit_tokens(sid, start + len(toks))
+        if all_logits and not select:
+            return b.logits[:n_rows]
+        self._select(n_rows, greedy)
+        toks = self._fetch_tokens(n_rows)
+        return (toks, b.logits[:n_rows]) if all_logits else toks
+
+    # ---- batched decode -----------------------------------------------------------------------------------
+    def _pick_splits(self, S: int, max_len: int) -> int:
+        if self.device.type != "cuda":
+            return 1
+        ctas = S * self.model.plan.num_kv_heads
+        want = (2 * self._sm + ctas - 1) // ctas
+        by_len = max(1, max_len // 256)
+        return int(max(1, min(want, by_len, self.max_attn_splits)))
+
+    def decode(self, seq_ids: Sequence[int], last_tokens: Sequence[int],
+               sampling: Optional[Sequence[SamplingRow]] = None, adapters: Optional[Sequence[int]] = None) -> List[int]:
+        """One new token for each sequence: ``last_tokens[i]`` is appended at the sequence's current length (the
+        cache must already have been extended by one), attention covers the whole sequence."""
+        b, cache = self.buf, self.cache
+        S = len(seq_ids)
+        if S == 0:
+            return []
+        if S > self.max_batch_seqs:
+            raise ValueError(f"decode batch {S} exceeds max_batch_seqs {self.max_batch_seqs}")
+        Sp = min(_bucket(S, self.DECODE_BUCKETS), self.max_batch_seqs) if self.use_graphs else S
+        bs = cache.block_size
+        self.h_bt[:Sp].fill_(-1)
+        max_len = 1
+        for s, sid in enumerate(seq_ids):
+            n = cache.num_tokens(sid)
+            ids = cache.get_block_ids(sid)
+            self.h_bt[s, :len(ids)] = torch.as_tensor(ids, dtype=torch.int32)
+            self.h_lens[s] = n
+            self.h_pos[s] = n - 1
+            blk = ids[(n - 1) // bs]
+            self.h_slots[s] = -1 if blk < 0 else blk * bs + (n - 1) % bs
+            max_len = max(max_len, n)
+        self.h_ids[:S] = torch.as_tensor(list(last_tokens), dtype=torch.int32)
+        if Sp > S:                                  # padding rows: empty sequences that write nothing
+            self.h_ids[S:Sp] = 0
+            self.h_pos[S:Sp] = 0
+            self.h_slots[S:Sp] = -1
+            self.h_lens[S:Sp] = 0
+        self.h_rows[:Sp] = torch.arange(Sp, dtype=torch.int64)
+        for dst, src, n in ((b.ids, self.h_ids, Sp), (b.positions, self.h_pos, Sp), (b.slots, self.h_slots, Sp),
+                            (b.block_tables, self.h_bt, Sp), (b.seq_lens, self.h_lens, Sp),
+                            (b.logit_rows, self.h_rows, Sp)):
+            self._upload(dst, src, n)
+        self._stage_adapters(adapters, S, Sp)
+        greedy = self._stage_sampling(sampling or [GREEDY] * S, Sp)
+        splits = self._pick_splits(Sp, max_len)
+        self._step += 1
+        if self.use_graphs and (self.model.comm is None or self.model.comm.graph_safe):
+            key = (Sp, splits, greedy)
+            g = self._graphs.get(key)
+            if g is None:
+                g = self._capture(Sp, splits, greedy)
+            g.replay()
+            self.timings["graph_replays"] += 1
+        else:
+            self.model.forward(b, cache.slab, Sp, "decode", Sp, 1, Sp, splits)
+            self._select(Sp, greedy)
+        self.timings["decode_steps"] += 1
+        return self._fetch_tokens(Sp)[:S]
+
+    def _capture(self, Sp: int, splits: int, greedy: bool) -> "torch.cuda.CUDAGraph":
+        b, cache = self.buf, self.cache
+        stream = torch.cuda.Stream(device=self.device)
+        stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(stream):            # warm-up outside capture (lazy attribute set-up, tensor maps)
+            self.model.forward(b, cache.slab, Sp, "decode", Sp, 1, Sp, splits)
+            self._select(Sp, greedy)
+        torch.cuda.current_stream().wait_stream(stream)
+        torch.cuda.synchronize(self.device)
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=stream):
+            self.model.forward(b, cache.slab, Sp, "decode", Sp, 1, Sp, splits)
+            self._select(Sp, greedy)
+        self._graphs[(Sp, splits, greedy)] = g
+        self.timings["graph_captures"] += 1
+        return g
+
+    # ---- convenience ----------------------------------------------------------------------------------------
+    def verify_tokens(self, seq_id: int, tokens: Sequence[int], start_position: int) -> torch.Tensor:
+        """Logits (fp32, host) after each of ``tokens`` placed at ``start_position...``; the caller has extended the
+        cache to cover them and truncates afterwards."""
+        logits = self.prefill([(seq_id, tokens, start_position)], all_logits=True, select=False)
+        return logits.float().cpu()
+
+    def embed_pooled(self, tokens: Sequence[int], seq_id: int = 1_000_000_000) -> torch.Tensor:
+        """Mean-pooled, L2-normalised final hidden state (dense retrieval embeddings), pooled on the device."""
+        self.cache.allocate_sequence(seq_id, num_tokens=len(tokens))
+        try:
+            self.prefill([(seq_id, tokens, 0)], select=False, all_logits=False)
+            h = self.model.hidden_rows(self.buf, len(tokens)).float().mean(dim=0)
+            return torch.nn.functional.normalize(h, dim=0).cpu()
+        finally:
+            self.cache.free_sequence(seq_id)
