@@ -1,0 +1,243 @@
+#!/usr/bin/env python
+"""Headline benchmark: INT4 Qwen2.5-14B-shaped decode throughput with continuous batching.
+
+    python bench.py --gpus N --steps K --warmup W            (N > 1: launched once per rank by torch.distributed.run)
+
+Workload: 64 concurrent requests, prompt lengths uniform in [128, 2048] random token ids, 256 output tokens each,
+random-init weights quantised to INT4 group-128, paged fp16 KV cache, tensor parallel over the N GPUs of one node.
+A step is one decode iteration of the whole batch (64 new tokens).  Two numbers are reported:
+
+* ``value``: tokens/s from the device time of K real decode steps (CUDA events around each step's kernels on the
+  launching stream, summed; maximum over ranks);
+* ``e2e``: tokens/s of the same K steps timed around the public ``ZStreamerEngine.step()`` call, which every step
+  copies its inputs from pinned host memory to the device and reads the chosen tokens back.
+
+``--impl reference`` runs the unmodified reference engine from ``baseline/_ref`` on the same model file.
+"""
+import argparse
+import json
+import os
+import random
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+BASELINE_14B_TOK_S = 37.0        # published single-sequence decode, Qwen2.5-14B INT4, A100-80GB (reference README.md:60)
+MODEL_SHAPE = "qwen2.5-14b"
+NUM_REQUESTS = 64
+PROMPT_RANGE = (128, 2048)
+OUTPUT_TOKENS = 256
+
+
+def parse_args():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=100)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--model", default=MODEL_SHAPE, help="shape name from zse_b200.format.synth.SHAPES")
+    ap.add_argument("--requests", type=int, default=NUM_REQUESTS)
+    ap.add_argument("--comm", default=None, help="tensor-parallel collectives: fused | nccl")
+    ap.add_argument("--model-path", default=None)
+    ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--workload", default="batch64", choices=["batch64", "single"],
+                    help="batch64: 64 requests, prompts uniform in [128, 2048] (the headline); single: one request "
+                         "with a 512-token prompt on the 7B shape (the case the reference publishes)")
+    a = ap.parse_args()
+    if a.workload == "single":
+        a.model = "qwen2.5-7b" if a.model == MODEL_SHAPE else a.model
+        a.requests = 1
+    return a
+
+
+def model_file(args, rank: int, barrier) -> str:
+    if args.model_path:
+        return args.model_path
+    path = os.path.join(tempfile.gettempdir(), f"zse_bench_{args.model}_int4.zse")
+    if rank == 0 and not os.path.exists(path):
+        from zse_b200.format import synth
+        t0 = time.time()
+        tmp = path + ".tmp"
+        synth.write_random_model(tmp, synth.shape_config(args.model), seed=0, fast=True)
+        os.replace(tmp, path)
+        print(f"[bench] wrote {path} ({os.path.getsize(path) / 2**30:.2f} GiB) in {time.time() - t0:.1f}s",
+              file=sys.stderr)
+    barrier()
+    return path
+
+
+def workload(n_requests: int, vocab: int, seed: int = 1234, kind: str = "batch64"):
+    rng = random.Random(seed)
+    if kind == "single":
+        return [[rng.randrange(vocab) for _ in range(512)] for _ in range(n_requests)]
+    return [[rng.randrange(vocab) for _ in range(rng.randint(*PROMPT_RANGE))] for _ in range(n_requests)]
+
+
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.proc, self.path = None, os.path.join(tempfile.gettempdir(), f"zse_clocks_{os.getpid()}.csv")
+        try:
+            self.fh = open(self.path, "w")
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits",
+                                          "-lms", "100", "-i", str(gpu_index)], stdout=self.fh,
+                                         stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        self.fh.close()
+        sm, mx, reasons, power = [], [], set(), []
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in open(self.path):
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+                power.append(float(f[3]))
+            except ValueError:
+                continue
+            for name, val in zip(names, f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        os.unlink(self.path)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus and world > 1:
+        args.gpus = world
+    torch.cuda.set_device(local)
+    comm = None
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
+        barrier = lambda: dist.barrier()
+    else:
+        barrier = lambda: None
+
+    from zse_b200.config import EngineConfig
+    from zse_b200.engine import ZStreamerEngine
+    from zse_b200.sched.request import RequestState
+
+    path = model_file(args, rank, barrier)
+    need_tokens = max(OUTPUT_TOKENS, args.steps + args.warmup + 48)
+    cfg = EngineConfig(tp_size=world, device_index=local, max_seq_len=PROMPT_RANGE[1] + need_tokens + 64,
+                       max_batch_seqs=max(args.requests, 1), max_batch_tokens=8192, prefill_chunk_size=2048,
+                       max_prefill_per_step=16, decode_per_prefill=0, max_queue_size=4 * args.requests,
+                       use_cuda_graphs=not args.no_graphs, comm_backend=args.comm or "fused", quiet=rank != 0)
+    if world > 1:
+        from zse_b200.parallel.comm import make_comm
+        comm = make_comm(cfg.comm_backend, rank, world, torch.device(f"cuda:{local}"))
+    t0 = time.time()
+    eng = ZStreamerEngine(path, config=cfg, comm=comm, tp_rank=rank)
+    cold = time.time() - t0
+    prompts = workload(args.requests, eng.model_config.vocab_size, kind=args.workload)
+    rids = [eng.add_request_tokens(p, max_tokens=need_tokens, temperature=0.0, stop_tokens=[]) for p in prompts]
+    assert all(r is not None for r in rids)
+    # untimed: prefill everything (chunked, packed), interleaved with decode of the sequences already admitted
+    t_pf = time.time()
+    guard = 0
+    while (eng.scheduler.num_waiting or eng.scheduler.num_prefilling) and guard < 10000:
+        eng.step()
+        guard += 1
+    torch.cuda.synchronize()
+    prefill_s = time.time() - t_pf
+    active = eng.scheduler.num_decoding
+    assert active == args.requests, f"{active} of {args.requests} sequences decoding"
+    for _ in range(args.warmup):
+        eng.step()
+    barrier()
+    torch.cuda.synchronize()
+    runner = eng.runner
+    from zse_b200.ops import native
+    runner.step_events = []
+    launches0 = runner.kernel_launches
+    tokens0 = eng.stats().total_tokens_generated
+    sampler = ClockSampler(local) if rank == 0 else None
+    t_start = time.perf_counter()
+    for _ in range(args.steps):
+        eng.step()
+    torch.cuda.synchronize()
+    t_e2e = time.perf_counter() - t_start
+    barrier()
+    clocks = sampler.stop() if sampler else None
+    dev_ms = sum(a.elapsed_time(b) for a, b in runner.step_events)
+    n_steps = len(runner.step_events)
+    runner.step_events = None
+    tokens = eng.stats().total_tokens_generated - tokens0
+    launches = runner.kernel_launches - launches0
+    if world > 1:
+        t = torch.tensor([dev_ms, t_e2e * 1000.0], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dev_ms, t_e2e = float(t[0]), float(t[1]) / 1000.0
+    assert n_steps == args.steps and tokens == args.steps * args.requests, (n_steps, tokens)
+    stats = eng.stats()
+    if rank == 0:
+        S = args.requests
+        h2d = S * (4 + 4 + 8 + 4 + 8) + S * runner.max_blocks * 4     # ids, positions, slots, lens, rows, block tables
+        d2h = S * 4
+        value = tokens / (dev_ms / 1000.0)
+        line = {
+            "metric": "INT4 Qwen2.5 decode tok/s (box, max over ranks)", "value": round(value, 1), "unit": "tok/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": round(dev_ms / args.steps, 4), "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": round(value / BASELINE_14B_TOK_S, 2), "dtype": "fp16", "data": "synthetic",
+            "config": {"model": f"{args.model}-shaped INT4 group-128 (random N(0,0.02)-like weights)",
+                       "global_batch": S, "seq_len": (f"prompts uniform {PROMPT_RANGE}, {OUTPUT_TOKENS} output tokens"
+                                   if args.workload == "batch64" else "512-token prompt, 256 output tokens"),
+                       "workload": args.workload,
+                       "parallelism": f"tp{world}", "kv_cache": "paged fp16", "tp_collectives": cfg.comm_backend,
+                       "cuda_graphs": cfg.use_cuda_graphs,
+                       "l2_policy": "inputs larger than L2: each step streams all INT4 weights and the KV cache",
+                       "baseline_note": "vs_baseline divides by the reference's published single-sequence 14B decode "
+                                        "rate on A100-80GB (37.0 tok/s); it publishes no batched or B200 number"},
+            "e2e": {"value": round(tokens / t_e2e, 1), "unit": "tok/s", "ms_per_step": round(t_e2e * 1000 / args.steps, 4),
+                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "api": "ZStreamerEngine.add_request_tokens + ZStreamerEngine.step"},
+            "gpu_launches": int(launches), "clocks": clocks,
+            "extra": {"cold_start_s": round(cold, 2), "prefill_s": round(prefill_s, 2),
+                      "init_times": {k: round(v, 2) for k, v in eng.init_times.items()},
+                      "kv_blocks": eng.kv_cache.num_total_blocks, "block_size": eng.kv_cache.block_size,
+                      "graph_replays": runner.timings["graph_replays"], "impl": "ours"},
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def run_reference(args):
+    from baseline.run_reference import run
+    run(args, model_file, workload, ClockSampler, BASELINE_14B_TOK_S, PROMPT_RANGE, OUTPUT_TOKENS)
+
+
+if __name__ == "__main__":
+    a = parse_args()
+    if a.impl == "reference":
+        run_reference(a)
+    else:
+        run_ours(a)

@@ -87,7 +87,7 @@ def write_random_model(path: str, config: ModelConfig, seed: int = 0, std: float
         elif fast and c.quant.method == QuantMethod.INT4_ASYM:
             total = n * k
             groups = (total + gs - 1) // gs
-            packed = rng.integers(0, 256, size=groups * gs // 2, dtype=np.uint8)
+            packed = np.frombuffer(rng.bytes(groups * gs // 2), dtype=np.uint8)
             # range of 128 N(0,std) samples is about 5.2 std wide, centred near 0
             half = (2.6 + 0.35 * rng.standard_normal(groups, dtype=np.float32)).clip(1.5, 4.0) * std
             w.add_weight_raw(name, (n, k), packed, (2 * half / 15).astype(np.float16), (-half).astype(np.float16), gs)
@@ -98,11 +98,10 @@ def write_random_model(path: str, config: ModelConfig, seed: int = 0, std: float
         w.add_weight_raw_fp16(name, shape, np.asarray(values, dtype=np.float16))
 
     def big_fp16(name, n, k):
-        if fast:  # N(0, std) keeps logits sane; build in row blocks to bound host memory
-            rows = max(1, (64 << 20) // (k * 4))
-            parts = [(rng.standard_normal((min(rows, n - r), k), dtype=np.float32) * std).astype(np.float16)
-                     for r in range(0, n, rows)]
-            fp16(name, (n, k), np.concatenate(parts, axis=0))
+        if fast:  # one random block of rows, repeated: N(0, std) entries, a fraction of the generation time
+            rows = min(n, 4096)
+            block = (rng.standard_normal((rows, k), dtype=np.float32) * std).astype(np.float16)
+            fp16(name, (n, k), np.tile(block, ((n + rows - 1) // rows, 1))[:n])
         else:
             fp16(name, (n, k), rng.standard_normal((n, k), dtype=np.float32) * std)
 

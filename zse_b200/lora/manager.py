@@ -1,0 +1,173 @@
+"""LoRA adapters resident on the device, hot-swappable while serving
+(zse-engine/zse_engine/orchestrator/lora_manager.py:37-396).
+
+All loaded adapters of one rank share padded weight tables per (layer, module): ``A [slots, rank, in]`` and
+``B [slots, out, rank]``; a request's adapter is a slot index carried per token, so a decode batch mixing adapters
+runs in one launch pair per projection (``ops.lora_apply``).  Supported targets are the column-parallel attention
+projections ``q_proj``, ``k_proj``, ``v_proj`` (applied on the fused QKV output before RoPE); under tensor
+parallelism ``A`` is replicated and ``B`` is row-sharded like the base weight.
+"""
+from __future__ import annotations
+
+import threading
+from typing import Dict, List, Optional, Tuple
+
+import numpy as np
+import torch
+
+from ..format.lora_format import load_lora, module_shapes
+from .weights import LoRAAdapter, LoRAWeight, LoRAWeightStore
+
+SUPPORTED_TARGETS = ("q_proj", "k_proj", "v_proj")
+
+
+class LoRAManager:
+    def __init__(self, model, device, max_adapters: int = 32, max_rank: int = 64):
+        self._model = model
+        self._device = torch.device(device)
+        self._lock = threading.Lock()
+        self._store = LoRAWeightStore()
+        self._max_adapters, self._max_rank = max_adapters, max_rank
+        self._slots: List[Optional[str]] = [None] * max_adapters
+        self._rank = 0                                   # common (padded) rank of the tables
+        self._a: Dict[Tuple[int, str], torch.Tensor] = {}
+        self._b: Dict[Tuple[int, str], torch.Tensor] = {}
+        self._scales = torch.zeros(max_adapters, dtype=torch.float32, device=self._device)
+        self._loads = self._unloads = 0
+
+    # ---- geometry -----------------------------------------------------------------------------------------
+    def _module_geometry(self, module: str):
+        """(in_features, full out_features, local row range, column offset inside the fused qkv output)."""
+        c, p = self._model.config, self._model.plan
+        if module == "q_proj":
+            return c.hidden_size, c.q_dim, p.q_rows, 0
+        if module == "k_proj":
+            return c.hidden_size, c.kv_dim, p.kv_rows, p.q_dim
+        if module == "v_proj":
+            return c.hidden_size, c.kv_dim, p.kv_rows, p.q_dim + p.kv_dim
+        raise KeyError(module)
+
+    def weight_shapes(self) -> Dict[str, Tuple[int, int]]:
+        c = self._model.config
+        return module_shapes(c.hidden_size, c.intermediate_size, c.num_heads, c.num_kv_heads, c.head_dim)
+
+    # ---- load / unload --------------------------------------------------------------------------------------
+    def load_adapter(self, adapter_id: str, path: str) -> LoRAAdapter:
+        adapter, data = load_lora(path, self.weight_shapes())
+        adapter.adapter_id = adapter_id
+        arrays = {}
+        for (layer, mod), (a_bytes, b_bytes) in data.items():
+            w = adapter.get_weight(layer, mod)
+            arrays[(layer, mod)] = (np.frombuffer(a_bytes, np.float16).reshape(w.rank, w.in_features),
+                                    np.frombuffer(b_bytes, np.float16).reshape(w.out_features, w.rank))
+        return self.load_adapter_from_arrays(adapter_id, adapter.rank, adapter.alpha, adapter.target_modules,
+                                             adapter.num_layers, arrays)
+
+    def load_adapter_from_arrays(self, adapter_id: str, rank: int, alpha: float, target_modules: List[str],
+                                 num_layers: int, arrays: Dict[Tuple[int, str], tuple]) -> LoRAAdapter:
+        """``arrays[(layer, module)] = (A [rank, in], B [out, rank])`` as numpy / torch tensors (full, unsharded)."""
+        unsupported = [t for t in target_modules if t not in SUPPORTED_TARGETS]
+        if unsupported:
+            raise ValueError(f"LoRA targets {unsupported} are not supported (supported: {SUPPORTED_TARGETS})")
+        if rank > self._max_rank or rank % 2:
+            raise ValueError(f"LoRA rank {rank} must be even and <= {self._max_rank}")
+        with self._lock:
+            if adapter_id in self._store:
+                raise ValueError(f"adapter '{adapter_id}' is already loaded")
+            try:
+                slot = self._slots.index(None)
+            except ValueError:
+                raise MemoryError(f"all {self._max_adapters} adapter slots are in use") from None
+            if rank > self._rank:
+                self._grow_rank(rank)
+            ad = LoRAAdapter(adapter_id, rank, alpha, list(target_modules), num_layers)
+            for (layer, mod), (a, b) in arrays.items():
+                fin, fout, rows, _ = self._module_geometry(mod)
+                a_t = torch.as_tensor(np.asarray(a) if not isinstance(a, torch.Tensor) else a).to(torch.float16)
+                b_t = torch.as_tensor(np.asarray(b) if not isinstance(b, torch.Tensor) else b).to(torch.float16)
+                if tuple(a_t.shape) != (rank, fin) or tuple(b_t.shape) != (fout, rank):
+                    raise ValueError(f"bad LoRA shapes for layer {layer} {mod}: A {tuple(a_t.shape)}, "
+                                     f"B {tuple(b_t.shape)}")
+                ta, tb = self._tables(layer, mod)
+                ta[slot].zero_()
+                tb[slot].zero_()
+                ta[slot, :rank].copy_(a_t.to(self._device))
+                tb[slot, :, :rank].copy_(b_t[rows[0]:rows[1]].to(self._device))
+                ad.add_weight(layer, mod, LoRAWeight(f"model.layers.{layer}.{mod}", rank, fin, fout, ta[slot], tb[slot]))
+            ad.slot = slot
+            self._slots[slot] = adapter_id
+            self._scales[slot] = ad.scaling
+            self._store.add(ad)
+            self._loads += 1
+            self._model.lora = self
+            return ad
+
+    def _tables(self, layer: int, mod: str):
+        key = (layer, mod)
+        if key not in self._a:
+            fin, _, rows, _ = self._module_geometry(mod)
+            self._a[key] = torch.zeros(self._max_adapters, self._rank, fin, dtype=torch.float16, device=self._device)
+            self._b[key] = torch.zeros(self._max_adapters, rows[1] - rows[0], self._rank, dtype=torch.float16,
+                                       device=self._device)
+        return self._a[key], self._b[key]
+
+    def _grow_rank(self, rank: int) -> None:
+        for key in list(self._a):
+            a, b = self._a[key], self._b[key]
+            na = torch.zeros(a.shape[0], rank, a.shape[2], dtype=a.dtype, device=a.device)
+            nb = torch.zeros(b.shape[0], b.shape[1], rank, dtype=b.dtype, device=b.device)
+            na[:, : a.shape[1]] = a
+            nb[:, :, : b.shape[2]] = b
+            self._a[key], self._b[key] = na, nb
+        self._rank = rank
+
+    def unload_adapter(self, adapter_id: str) -> bool:
+        with self._lock:
+            ad = self._store.remove(adapter_id)
+            if ad is None:
+                return False
+            self._slots[ad.slot] = None
+            self._scales[ad.slot] = 0.0
+            for (layer, mod) in ad.weights:
+                if (layer, mod) in self._a:
+                    self._a[(layer, mod)][ad.slot].zero_()
+                    self._b[(layer, mod)][ad.slot].zero_()
+            self._unloads += 1
+            if len(self._store) == 0:
+                self._model.lora = None
+            return True
+
+    # ---- queries --------------------------------------------------------------------------------------------
+    def is_loaded(self, adapter_id: str) -> bool:
+        return adapter_id in self._store
+
+    def slot_of(self, adapter_id: Optional[str]) -> int:
+        ad = self._store.get(adapter_id) if adapter_id else None
+        return -1 if ad is None else ad.slot
+
+    def list_adapters(self) -> List[dict]:
+        return [{"adapter_id": i, "rank": a.rank, "alpha": a.alpha, "target_modules": a.target_modules,
+                 "num_layers": a.num_layers, "bytes": a.total_bytes, "slot": a.slot}
+                for i, a in ((i, self._store.get(i)) for i in self._store.list_ids())]
+
+    def stats(self) -> dict:
+        return {"num_adapters": len(self._store), "max_adapters": self._max_adapters, "table_rank": self._rank,
+                "total_bytes": self._store.total_bytes, "loads": self._loads, "unloads": self._unloads,
+                "table_bytes": sum(t.numel() * 2 for t in list(self._a.values()) + list(self._b.values()))}
+
+    # ---- hot path -------------------------------------------------------------------------------------------
+    def apply_qkv(self, layer: int, b, M: int) -> None:
+        """Adds every resident adapter's update to the fused QKV output of ``layer`` for the first ``M`` tokens."""
+        ops = self._model.ops
+        for mod in SUPPORTED_TARGETS:
+            key = (layer, mod)
+            if key not in self._a:
+                continue
+            fin, _, rows, col0 = self._module_geometry(mod)
+            ops.lora_apply(b.xnorm, self._a[key], self._b[key], b.adapter_ids, self._scales, b.qkv, M, fin,
+                           rows[1] - rows[0], self._rank, tmp=b.lora_tmp, y_col0=col0)
+
+    def destroy(self) -> None:
+        with self._lock:
+            self._a.clear()
+            self._b.clear()

@@ -103,9 +103,13 @@ def _stream() -> int:
     return torch.cuda.current_stream().cuda_stream
 
 
-def _ck(rc: int, what: str) -> None:
+LAUNCHES = [0]      # kernels launched through this module (graph replays are accounted by the runner)
+
+
+def _ck(rc: int, what: str, launches: int = 1) -> None:
     if rc < 0:
         raise NativeError(f"{what}: {_ERRORS.get(rc, rc)}")
+    LAUNCHES[0] += launches
 
 
 class Status:
@@ -120,7 +124,7 @@ class Status:
 
     def read(self):
         out = (c_uint32 * 4)()
-        _ck(load().zse_status_read(self.ptr, out), "status read")
+        _ck(load().zse_status_read(self.ptr, out), "status read", 0)
         return tuple(out)
 
     def check(self) -> None:
@@ -206,7 +210,7 @@ def attn_decode(q, ldq, kv_layer, block_tables, max_blocks, seq_lens, out, ldo, 
                 block_size, num_splits, scale):
     _ck(load().zse_attn_decode(_p(q), ldq, _p(kv_layer), _p(block_tables), max_blocks, _p(seq_lens), _p(out), ldo,
                                _p(scratch), num_seqs, nh, nkv, hd, block_size, num_splits, scale, _stream()),
-        "attn_decode")
+        "attn_decode", 2 if num_splits > 1 else 1)
 
 
 def attn_prefill(q, ldq, kv_layer, block_tables, max_blocks, cu_q, q_pos0, out, ldo, num_seqs, max_q_len, nh, nkv,
@@ -239,7 +243,7 @@ def lora_expand(tmp, b, ids, scales, y, ldy, M, N, rank):
 
 def device_info() -> dict:
     sm, maj, mnr, tot, free = c_int(), c_int(), c_int(), c_int64(), c_int64()
-    _ck(load().zse_device_info(sm, maj, mnr, tot, free), "device_info")
+    _ck(load().zse_device_info(sm, maj, mnr, tot, free), "device_info", 0)
     return {"sm_count": sm.value, "cc": (maj.value, mnr.value), "total_mem": tot.value, "free_mem": free.value}
 
 

@@ -67,6 +67,9 @@ class ModelRunner:
         self.buf = model.make_buffers(self.max_tokens, max_batch_seqs, self.max_blocks, logits_rows,
                                       max_planes=8, attn_splits=self.max_attn_splits)
         self._graphs: Dict[Tuple[int, int, bool], torch.cuda.CUDAGraph] = {}
+        self._graph_launches: Dict[Tuple[int, int, bool], int] = {}
+        self.kernel_launches = 0          # own kernels launched by decode steps (graph replays included)
+        self.step_events = None           # list collecting (start, end) CUDA events of decode steps when set
         self._step = 0
         pin = on_gpu
         mk = lambda shape, dt: torch.zeros(shape, dtype=dt, pin_memory=pin)
@@ -193,8 +196,27 @@ class ModelRunner:
         by_len = max(1, max_len // 256)
         return int(max(1, min(want, by_len, self.max_attn_splits)))
 
+    def _apply_penalties(self, penalties, n_rows: int) -> None:
+        """``penalties[i] = (penalty, {token: count})`` for logits row i (zse-engine/zse_engine/orchestrator/
+        sampler.py:64-80), applied in place on the device through a sparse (row, token, count) list."""
+        rows, toks, cnts, pens = [], [], [], []
+        for i, (pen, counts) in enumerate(penalties[:n_rows]):
+            pens.append(float(pen))
+            if pen != 1.0:
+                for t, c in counts.items():
+                    rows.append(i)
+                    toks.append(t)
+                    cnts.append(c)
+        if not rows:
+            return
+        dev = self.device
+        mk = lambda v, dt: torch.tensor(v, dtype=dt, device=dev)
+        self.model.ops.apply_repetition_penalty(self.buf.logits, mk(rows, torch.int32), mk(toks, torch.int32),
+                                                mk(cnts, torch.int32), len(rows), mk(pens, torch.float32))
+
     def decode(self, seq_ids: Sequence[int], last_tokens: Sequence[int],
-               sampling: Optional[Sequence[SamplingRow]] = None, adapters: Optional[Sequence[int]] = None) -> List[int]:
+               sampling: Optional[Sequence[SamplingRow]] = None, adapters: Optional[Sequence[int]] = None,
+               penalties=None) -> List[int]:
         """One new token for each sequence: ``last_tokens[i]`` is appended at the sequence's current length (the
         cache must already have been extended by one), attention covers the whole sequence."""
         b, cache = self.buf, self.cache
@@ -231,16 +253,33 @@ class ModelRunner:
         greedy = self._stage_sampling(sampling or [GREEDY] * S, Sp)
         splits = self._pick_splits(Sp, max_len)
         self._step += 1
-        if self.use_graphs and (self.model.comm is None or self.model.comm.graph_safe):
+        counter = self._launch_counter()
+        before = counter[0]
+        graphed = penalties is None and self.use_graphs and (self.model.comm is None or self.model.comm.graph_safe)
+        g = None
+        if graphed:
             key = (Sp, splits, greedy)
             g = self._graphs.get(key)
             if g is None:
                 g = self._capture(Sp, splits, greedy)
+                before = counter[0]
+        ev = None
+        if self.step_events is not None:
+            ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+            ev[0].record()
+        if g is not None:
             g.replay()
             self.timings["graph_replays"] += 1
+            self.kernel_launches += self._graph_launches[key]
         else:
             self.model.forward(b, cache.slab, Sp, "decode", Sp, 1, Sp, splits)
+            if penalties is not None:
+                self._apply_penalties(penalties, S)
             self._select(Sp, greedy)
+            self.kernel_launches += counter[0] - before
+        if ev is not None:
+            ev[1].record()
+            self.step_events.append(ev)
         self.timings["decode_steps"] += 1
         return self._fetch_tokens(Sp)[:S]
 
@@ -254,12 +293,21 @@ class ModelRunner:
         torch.cuda.current_stream().wait_stream(stream)
         torch.cuda.synchronize(self.device)
         g = torch.cuda.CUDAGraph()
+        counter = self._launch_counter()
+        n0 = counter[0]
         with torch.cuda.graph(g, stream=stream):
             self.model.forward(b, cache.slab, Sp, "decode", Sp, 1, Sp, splits)
             self._select(Sp, greedy)
         self._graphs[(Sp, splits, greedy)] = g
+        self._graph_launches[(Sp, splits, greedy)] = counter[0] - n0
         self.timings["graph_captures"] += 1
         return g
+
+    def _launch_counter(self):
+        if self.device.type == "cuda":
+            from ..ops import native
+            return native.LAUNCHES
+        return [0]
 
     # ---- convenience ----------------------------------------------------------------------------------------
     def verify_tokens(self, seq_id: int, tokens: Sequence[int], start_position: int) -> torch.Tensor:

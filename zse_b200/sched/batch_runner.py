@@ -1,0 +1,190 @@
+"""Executes one scheduler decision on the model runner.
+
+Role of zse-engine/zse_engine/zstreamer/batch_runner.py:33-371 with these differences: all chunks scheduled for a
+step run as ONE packed pass (the reference runs one ``prefill`` per request); decode is one batched pass for every
+sequence whatever its adapter (per-token adapter routing instead of grouping by ``lora_id``); tokens are chosen on
+the device; speculative decoding is wired in (the reference builds ``BatchRunner(spec_runner=None)``).
+"""
+from __future__ import annotations
+
+import threading
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional
+
+from ..runtime.runner import ModelRunner, SamplingRow
+from .request import FinishReason, InferenceRequest, RequestOutput, RequestState
+from .scheduler import Scheduler, SchedulerOutput
+
+
+@dataclass
+class StepResult:
+    num_prefill_tokens: int = 0
+    num_decode_tokens: int = 0
+    tokens_generated: int = 0
+    finished: List[RequestOutput] = field(default_factory=list)
+    errors: List[str] = field(default_factory=list)
+
+
+def _sampling_row(r: InferenceRequest) -> SamplingRow:
+    p = r.params
+    if p.greedy:
+        return SamplingRow()
+    seed = p.seed if p.seed is not None else (hash(r.request_id) & 0x7FFFFFFF)
+    return SamplingRow(float(p.temperature), int(p.top_k), float(p.top_p), int(seed))
+
+
+class BatchRunner:
+    def __init__(self, runner: ModelRunner, scheduler: Scheduler, spec_runner=None, lora_manager=None):
+        self._runner = runner
+        self._cache = runner.cache
+        self._sched = scheduler
+        self._spec = spec_runner
+        self._lora = lora_manager
+        self._finalized: set = set()
+        self._lock = threading.Lock()
+
+    # ---- entry ----------------------------------------------------------------------------------------
+    def execute(self, plan: SchedulerOutput) -> StepResult:
+        res = StepResult()
+        for r in plan.preempt_requests:
+            self._release_kv(r)
+        for r in plan.finished_requests:
+            self._finalize(r, res)
+        if plan.prefill_requests:
+            self._run_prefill(plan, res)
+        if plan.decode_requests:
+            live = [r for r in plan.decode_requests if not r.is_finished]
+            if live:
+                if self._spec is not None and self._spec.k > 0:
+                    self._run_speculative(live, res)
+                else:
+                    self._run_decode(live, res)
+        for r in plan.prefill_requests + plan.decode_requests:
+            if r.is_finished:
+                self._finalize(r, res)
+        return res
+
+    # ---- helpers ----------------------------------------------------------------------------------------
+    def _adapter_slot(self, r: InferenceRequest) -> int:
+        if self._lora is None or r.lora_id is None:
+            return -1
+        return self._lora.slot_of(r.lora_id)
+
+    def _release_kv(self, r: InferenceRequest) -> None:
+        if r.seq_id is not None and self._cache.has_sequence(r.seq_id):
+            self._cache.free_sequence(r.seq_id)
+
+    def _finalize(self, r: InferenceRequest, res: StepResult) -> None:
+        with self._lock:
+            if r.request_id in self._finalized:
+                return
+            self._finalized.add(r.request_id)
+            if len(self._finalized) > 100_000:
+                self._finalized.clear()
+        self._release_kv(r)
+        if self._spec is not None:
+            self._spec.forget(r.request_id)
+        out = RequestOutput.from_request(r)
+        res.finished.append(out)
+        if r.on_finish is not None:
+            try:
+                r.on_finish(out)
+            except Exception as exc:   # a client callback must not take the engine down
+                res.errors.append(f"{r.request_id}: on_finish raised {exc!r}")
+
+    def _fail(self, r: InferenceRequest, exc: Exception, res: StepResult) -> None:
+        self._sched.on_request_error(r, f"{type(exc).__name__}: {exc}")
+        res.errors.append(f"{r.request_id}: {exc}")
+
+    # ---- prefill ----------------------------------------------------------------------------------------
+    def _run_prefill(self, plan: SchedulerOutput, res: StepResult) -> None:
+        items, owners = [], []
+        for r, n in zip(plan.prefill_requests, plan.prefill_chunk_sizes):
+            if r.is_finished or n <= 0:
+                continue
+            try:
+                toks = r.prefill_tokens
+                if not self._cache.has_sequence(r.seq_id):
+                    h = self._cache.allocate_sequence(r.seq_id, toks)
+                    self._cache.mark_active(r.seq_id)
+                    if h.num_cached_tokens and r.prefill_offset == 0:
+                        r.prefill_offset = h.num_cached_tokens        # prefix already in the cache
+                        n = min(n, r.remaining_prefill)
+                start = r.prefill_offset
+                items.append((r.seq_id, toks[start:start + n], start))
+                owners.append((r, n))
+            except Exception as exc:
+                self._fail(r, exc, res)
+        if not items:
+            return
+        # split into passes that respect the runner's limits
+        passes, cur, cur_tok = [], [], 0
+        for it, ow in zip(items, owners):
+            if cur and (cur_tok + len(it[1]) > self._runner.max_tokens or len(cur) >= self._runner.max_batch_seqs):
+                passes.append(cur)
+                cur, cur_tok = [], 0
+            cur.append((it, ow))
+            cur_tok += len(it[1])
+        passes.append(cur)
+        for group in passes:
+            its = [g[0] for g in group]
+            ows = [g[1] for g in group]
+            try:
+                toks = self._runner.prefill(its, sampling=[_sampling_row(o[0]) for o in ows],
+                                            adapters=[self._adapter_slot(o[0]) for o in ows]
+                                            if self._lora is not None else None)
+            except Exception as exc:
+                for r, _ in ows:
+                    self._fail(r, exc, res)
+                continue
+            for (r, n), tok in zip(ows, toks):
+                res.num_prefill_tokens += n
+                resumed = r.num_generated > 0            # re-prefill after preemption: next input is known
+                self._sched.on_prefill_complete(r, n)
+                if r.state == RequestState.DECODING and not resumed:
+                    self._sched.on_token_generated(r, int(tok))
+                    res.tokens_generated += 1
+
+    # ---- decode -----------------------------------------------------------------------------------------
+    def _run_decode(self, reqs: List[InferenceRequest], res: StepResult) -> None:
+        ready = []
+        for r in reqs:
+            try:
+                self._cache.extend_sequence(r.seq_id, 1)
+                ready.append(r)
+            except Exception as exc:
+                self._fail(r, exc, res)
+        if not ready:
+            return
+        pen = None
+        if any(r.params.repetition_penalty != 1.0 for r in ready):
+            pen = [(r.params.repetition_penalty, r.past_tokens) for r in ready]
+        try:
+            toks = self._runner.decode([r.seq_id for r in ready], [r.output_tokens[-1] for r in ready],
+                                       sampling=[_sampling_row(r) for r in ready],
+                                       adapters=[self._adapter_slot(r) for r in ready] if self._lora is not None
+                                       else None, penalties=pen)
+        except Exception as exc:
+            for r in ready:
+                self._fail(r, exc, res)
+            return
+        for r, tok in zip(ready, toks):
+            self._sched.on_token_generated(r, int(tok))
+        res.num_decode_tokens += len(ready)
+        res.tokens_generated += len(ready)
+
+    def _run_speculative(self, reqs: List[InferenceRequest], res: StepResult) -> None:
+        greedy = [r for r in reqs if r.params.greedy and r.params.repetition_penalty == 1.0]
+        other = [r for r in reqs if r not in greedy]
+        if other:
+            self._run_decode(other, res)
+        if greedy:
+            try:
+                produced = self._spec.step(greedy, self._sched,
+                                           adapters=[self._adapter_slot(r) for r in greedy]
+                                           if self._lora is not None else None)
+                res.num_decode_tokens += len(greedy)
+                res.tokens_generated += produced
+            except Exception as exc:
+                for r in greedy:
+                    self._fail(r, exc, res)
