@@ -45,6 +45,8 @@ def parse_args():
     ap.add_argument("--comm", default=None, help="tensor-parallel collectives: fused | nccl")
     ap.add_argument("--model-path", default=None)
     ap.add_argument("--no-graphs", action="store_true")
+    ap.add_argument("--profile-region", action="store_true",
+                    help="bracket the timed steps with cudaProfilerStart/Stop (for `ncu --profile-from-start off`)")
     ap.add_argument("--workload", default="batch64", choices=["batch64", "single"],
                     help="batch64: 64 requests, prompts uniform in [128, 2048] (the headline); single: one request "
                          "with a 512-token prompt on the 7B shape (the case the reference publishes)")
@@ -151,7 +153,9 @@ def run_ours(args):
                        use_cuda_graphs=not args.no_graphs, comm_backend=args.comm or "fused", quiet=rank != 0)
     if world > 1:
         from zse_b200.parallel.comm import make_comm
-        comm = make_comm(cfg.comm_backend, rank, world, torch.device(f"cuda:{local}"))
+        from zse_b200.format import synth as _synth
+        comm = make_comm(cfg.comm_backend, rank, world, torch.device(f"cuda:{local}"),
+                         hidden_size=_synth.SHAPES[args.model]["hidden_size"], max_tokens=cfg.max_batch_tokens)
     t0 = time.time()
     eng = ZStreamerEngine(path, config=cfg, comm=comm, tp_rank=rank)
     cold = time.time() - t0
@@ -178,11 +182,15 @@ def run_ours(args):
     launches0 = runner.kernel_launches
     tokens0 = eng.stats().total_tokens_generated
     sampler = ClockSampler(local) if rank == 0 else None
+    if args.profile_region:
+        torch.cuda.profiler.start()
     t_start = time.perf_counter()
     for _ in range(args.steps):
         eng.step()
     torch.cuda.synchronize()
     t_e2e = time.perf_counter() - t_start
+    if args.profile_region:
+        torch.cuda.profiler.stop()
     barrier()
     clocks = sampler.stop() if sampler else None
     dev_ms = sum(a.elapsed_time(b) for a, b in runner.step_events)

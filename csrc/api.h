@@ -77,6 +77,23 @@ int zse_lora_shrink(const void* x_f16, int ldx, const void* a_f16, const void* a
 int zse_lora_expand(const void* tmp_f32, const void* b_f16, const void* adapter_ids_i32, const void* scales_f32,
                     void* y_f16, int ldy, int M, int N, int rank, void* stream);
 
+// ---- comm.cu ------------------------------------------------------------------------------------------------
+// Tensor-parallel context: peer-mapped symmetric buffers of every rank (row data [2][m_cap][H] fp16, flags
+// [2][tp][m_cap] u32, exchange words [2][tp][m_cap] u64 + flags), optional multicast view of the row data.
+void* zse_tp_ctx_create(int tp, int rank, int m_cap, int H, const uint64_t* data_ptrs, const uint64_t* flag_ptrs,
+                        uint64_t mc_data, const uint64_t* xchg_ptrs, const uint64_t* xflag_ptrs);
+void zse_tp_ctx_destroy(void* ctx);
+int zse_tp_reduce_add_rmsnorm(void* ctx, void* residual, const void* partials, int n_planes, const void* weight,
+                              void* out, int M, float eps, int slot, int use_multimem, void* status,
+                              void* stream);
+int zse_tp_reduce_add_rmsnorm_emulated(void* ctx, const uint64_t* residuals, const uint64_t* partials, int n_planes,
+                                       const void* weight, const uint64_t* outs, int M, float eps,
+                                       int slot, void* status, void* stream);
+int zse_tp_argmax(void* ctx, const void* logits, int ld, void* out, int M, int V_local, int vocab_stride,
+                  int slot, void* status, void* stream);
+int zse_tp_argmax_emulated(void* ctx, const uint64_t* logits, int ld, const uint64_t* outs, int M, int V_local,
+                           int vocab_stride, int slot, void* status, void* stream);
+
 // ---- runtime.cu ---------------------------------------------------------------------------------------------
 int zse_status_read(const void* status_dev, uint32_t* out4);   // synchronous 16-byte copy
 int zse_device_info(int* sm_count, int* cc_major, int* cc_minor, int64_t* total_mem, int64_t* free_mem);

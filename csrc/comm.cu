@@ -1,0 +1,432 @@
+// Tensor-parallel reductions done inside the consuming kernel, over NVLink peer memory.
+//
+// tp_reduce_add_rmsnorm - what follows every row-parallel projection (o_proj, down_proj):
+//     residual += sum over ranks of (sum of this rank's split-K planes);  out = RMSNorm(residual) * w
+//   One CTA per token row.  Phase A sums the local fp32 planes, rounds to fp16 and stores the row into this rank's
+//   symmetric buffer, then raises a per-row flag in every peer's flag array with st.release.sys.  Phase B waits
+//   (bounded) until the flags of all ranks for this row are up, takes them down again, then either pulls the row from every peer
+//   with plain 16-byte loads over NVLink and adds them in rank order, or - when a multicast mapping exists - lets
+//   the NVSwitch add them with multimem.ld_reduce.  Residual add and RMSNorm run on the row while it is in
+//   registers.  No NCCL call, no separate all-reduce kernel, no grid-wide barrier: row r of one rank only depends on
+//   row r of the others.  The reference does ncclAllReduce + residual_add + rmsnorm as three steps on the NULL
+//   stream (zse-engine/zse_engine/orchestrator/model_runner.py:2622-2635,2694-2705).
+// tp_argmax             - greedy token selection over a vocabulary-sharded lm_head: local arg-max, 8-byte exchange
+//                         through the same flag protocol, global arg-max (ties -> lowest token id).
+//
+// Buffers alternate between two slots so that a fast rank starting call c+2 cannot overwrite what a slow rank still
+// reads for call c (a rank can only enter call c+2 after every rank finished its part of call c+1); for the same
+// reason a flag taken down in call c is not raised again before call c+2.  Flags carry no epoch, so a launch can be
+// replayed from a CUDA graph unchanged.
+// Waits give up after kWaitLimitNs and report through the status word; the kernel then finishes normally.
+//
+// Emulation: with grid.y == tp the launch plays every rank itself (blockIdx.y = rank) on buffers of one GPU; it is
+// started cooperatively so that all CTAs are resident.  That is how the protocol is tested on a single GPU.
+#include <cooperative_groups.h>
+
+#include "api.h"
+#include "common.cuh"
+
+namespace zse {
+
+constexpr int kMaxTp = 8;
+constexpr int kRedThreads = 256;
+constexpr int kRedMaxChunks = 4;          // 8-element chunks per thread -> H <= 8192
+
+struct TpTable {
+  __half* data[kMaxTp];        // data[r]: rank r's row buffer [2][m_cap][H] as mapped into this process
+  uint32_t* flags[kMaxTp];     // flags[r]: rank r's flag words [2][tp][m_cap]
+  const __half* mc_data;       // multicast view of the row buffer (null: peer loads)
+  int tp;
+  int m_cap;
+};
+
+struct TpRankArgs {            // per emulated rank (index 0 in a real launch)
+  float* residual;
+  const float* partials;
+  __half* out;
+  int rank;
+};
+
+struct TpReduceArgs {
+  TpRankArgs r[kMaxTp];
+  const __half* weight;
+  int n_planes, M, H, row0;
+  float eps;
+  int slot;
+  Status* status;
+};
+
+__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint4 ld_relaxed_sys_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ uint4 multimem_ld_reduce_f16x8(const void* mc_ptr) {
+  uint4 v;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(mc_ptr)
+               : "memory");
+  return v;
+}
+
+// Bounded wait until *flag is raised, then takes it down.  Returns false on timeout.
+__device__ __forceinline__ bool wait_flag(uint32_t* flag, Status* st, unsigned where, unsigned detail) {
+  if (ld_acquire_sys(flag) == 0u) {
+    const uint64_t t0 = globaltimer_ns();
+    unsigned spins = 0;
+    while (ld_acquire_sys(flag) == 0u) {
+      if ((++spins & 0x3F) == 0 && globaltimer_ns() - t0 > kWaitLimitNs) {
+        report(st, kPeerTimeout, where, detail);
+        return false;
+      }
+    }
+  }
+  *reinterpret_cast<volatile uint32_t*>(flag) = 0u;
+  return true;
+}
+
+__device__ __forceinline__ void acc_h8(float* a, const uint4& v) {
+  const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __half22float2(h[i]);
+    a[2 * i] += f.x;
+    a[2 * i + 1] += f.y;
+  }
+}
+
+template <bool kMultimem>
+__global__ void __launch_bounds__(kRedThreads)
+tp_reduce_add_rmsnorm_kernel(const TpTable tb, const TpReduceArgs a) {
+  __shared__ float red[32];
+  __shared__ int ok_flag;
+  const int er = blockIdx.y;                      // emulated rank slot (0 in a real launch)
+  const TpRankArgs me = a.r[er];
+  const int rank = me.rank;
+  const int row = a.row0 + blockIdx.x;
+  const int H = a.H, nch = H / 8;
+  const size_t slot_off = size_t(a.slot) * tb.m_cap * H;
+  const size_t row_off = slot_off + size_t(row) * H;
+  const size_t plane = size_t(a.M) * H;
+  if (threadIdx.x == 0) ok_flag = 1;
+
+  // ---- phase A: local planes -> fp16 row in this rank's symmetric buffer ------------------------------------
+#pragma unroll
+  for (int j = 0; j < kRedMaxChunks; ++j) {
+    const int c = threadIdx.x + j * kRedThreads;
+    if (c < nch) {
+      float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int p = 0; p < a.n_planes; ++p) {
+        const float4* src = reinterpret_cast<const float4*>(me.partials + p * plane + size_t(row) * H) + 2 * c;
+        const float4 x = src[0], y = src[1];
+        v[0] += x.x; v[1] += x.y; v[2] += x.z; v[3] += x.w;
+        v[4] += y.x; v[5] += y.y; v[6] += y.z; v[7] += y.w;
+      }
+      uint4 pk;
+      pk.x = pack_half2(v[0], v[1]);
+      pk.y = pack_half2(v[2], v[3]);
+      pk.z = pack_half2(v[4], v[5]);
+      pk.w = pack_half2(v[6], v[7]);
+      reinterpret_cast<uint4*>(tb.data[rank] + row_off)[c] = pk;
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x < tb.tp) {
+    __threadfence_system();
+    st_release_sys(tb.flags[threadIdx.x] + (size_t(a.slot) * tb.tp + rank) * tb.m_cap + row, 1u);
+  }
+  // ---- phase B: wait for every rank's row, reduce, residual add, RMSNorm -------------------------------------
+  if (threadIdx.x < tb.tp) {
+    if (!wait_flag(tb.flags[rank] + (size_t(a.slot) * tb.tp + threadIdx.x) * tb.m_cap + row, a.status, 31,
+                   threadIdx.x))
+      ok_flag = 0;
+  }
+  __syncthreads();
+  const bool ok = ok_flag != 0;                   // on timeout the row keeps its old residual; the host sees the status
+  float vals[kRedMaxChunks][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < kRedMaxChunks; ++j) {
+    const int c = threadIdx.x + j * kRedThreads;
+    if (c < nch) {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      if (ok) {
+        if (kMultimem) {
+          acc_h8(acc, multimem_ld_reduce_f16x8(tb.mc_data + row_off + size_t(c) * 8));
+        } else {
+          uint4 got[kMaxTp];
+#pragma unroll
+          for (int r = 0; r < kMaxTp; ++r)
+            if (r < tb.tp) got[r] = ld_relaxed_sys_v4(tb.data[r] + row_off + size_t(c) * 8);
+#pragma unroll
+          for (int r = 0; r < kMaxTp; ++r)
+            if (r < tb.tp) acc_h8(acc, got[r]);
+        }
+      }
+      float4* res = reinterpret_cast<float4*>(me.residual + size_t(row) * H) + 2 * c;
+      float4 x = res[0], y = res[1];
+      x.x += acc[0]; x.y += acc[1]; x.z += acc[2]; x.w += acc[3];
+      y.x += acc[4]; y.y += acc[5]; y.z += acc[6]; y.w += acc[7];
+      res[0] = x;
+      res[1] = y;
+      vals[j][0] = x.x; vals[j][1] = x.y; vals[j][2] = x.z; vals[j][3] = x.w;
+      vals[j][4] = y.x; vals[j][5] = y.y; vals[j][6] = y.z; vals[j][7] = y.w;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ss += vals[j][i] * vals[j][i];
+    }
+  }
+  if (me.out == nullptr) return;
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = (threadIdx.x & 31) < (kRedThreads >> 5) ? red[threadIdx.x & 31] : 0.f;
+  tot = warp_sum(tot);
+  const float inv = rsqrtf(tot / float(H) + a.eps);
+#pragma unroll
+  for (int j = 0; j < kRedMaxChunks; ++j) {
+    const int c = threadIdx.x + j * kRedThreads;
+    if (c < nch) {
+      const uint4 wr = reinterpret_cast<const uint4*>(a.weight)[c];
+      const __half2* wh = reinterpret_cast<const __half2*>(&wr);
+      uint4 pk;
+      uint32_t* po = reinterpret_cast<uint32_t*>(&pk);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 w = __half22float2(wh[i]);
+        po[i] = pack_half2(vals[j][2 * i] * inv * w.x, vals[j][2 * i + 1] * inv * w.y);
+      }
+      reinterpret_cast<uint4*>(me.out + size_t(row) * H)[c] = pk;
+    }
+  }
+}
+
+// ---- greedy selection over a vocabulary-sharded lm_head --------------------------------------------------
+struct TpArgmaxArgs {
+  const __half* logits[kMaxTp];   // per emulated rank: [M, ld] local logits
+  int* out[kMaxTp];
+  int rank[kMaxTp];
+  unsigned long long* xchg[kMaxTp];   // xchg[r]: rank r's exchange words [2][tp][m_cap] as mapped here
+  uint32_t* flags[kMaxTp];
+  int ld, V_local, vocab_stride;      // global token id = rank * vocab_stride + local index
+  int tp, m_cap;
+  int slot;
+  Status* status;
+};
+
+__device__ __forceinline__ uint32_t f16_key(__half h) {
+  const uint32_t b = __half_as_ushort(h);
+  return (b & 0x8000u) ? (~b & 0xFFFFu) : (b | 0x8000u);
+}
+
+__global__ void __launch_bounds__(1024) tp_argmax_kernel(const TpArgmaxArgs a) {
+  __shared__ unsigned long long red[32];
+  __shared__ int ok_flag;
+  const int er = blockIdx.y, rank = a.rank[er], row = blockIdx.x;
+  const __half* lrow = a.logits[er] + size_t(row) * a.ld;
+  if (threadIdx.x == 0) ok_flag = 1;
+  unsigned long long best = 0ull;
+  for (int i = threadIdx.x; i < a.V_local; i += blockDim.x) {
+    const unsigned gid = unsigned(rank) * unsigned(a.vocab_stride) + unsigned(i);
+    const unsigned long long cand = ((unsigned long long)f16_key(lrow[i]) << 32) | (0xFFFFFFFFu - gid);
+    best = cand > best ? cand : best;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+    best = other > best ? other : best;
+  }
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = best;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    unsigned long long t = red[threadIdx.x];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const unsigned long long other = __shfl_xor_sync(0xffffffffu, t, o);
+      t = other > t ? other : t;
+    }
+    best = t;
+  }
+  const size_t base = size_t(a.slot) * a.tp * a.m_cap;
+  if (threadIdx.x < a.tp) {
+    // push my candidate into peer threadIdx.x's exchange area, then raise the flag there
+    const size_t idx = base + size_t(rank) * a.m_cap + row;
+    a.xchg[threadIdx.x][idx] = __shfl_sync((1u << a.tp) - 1u, best, 0);
+    __threadfence_system();
+    st_release_sys(a.flags[threadIdx.x] + idx, 1u);
+    if (!wait_flag(a.flags[rank] + base + size_t(threadIdx.x) * a.m_cap + row, a.status, 41, threadIdx.x))
+      ok_flag = 0;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    unsigned long long g = 0ull;
+    if (ok_flag) {
+      for (int r = 0; r < a.tp; ++r) {
+        const unsigned long long c = *reinterpret_cast<volatile unsigned long long*>(
+            a.xchg[rank] + base + size_t(r) * a.m_cap + row);
+        g = c > g ? c : g;
+      }
+    } else {
+      g = best;
+    }
+    a.out[er][row] = int(0xFFFFFFFFu - unsigned(g & 0xFFFFFFFFull));
+  }
+}
+
+}  // namespace zse
+
+using namespace zse;
+
+// Host-side description of one tensor-parallel group member (filled by the Python side after the rendezvous).
+struct zse_tp_ctx {
+  TpTable table;
+  unsigned long long* xchg[kMaxTp];
+  uint32_t* xflags[kMaxTp];
+  int rank;
+  int H;
+};
+
+extern "C" void* zse_tp_ctx_create(int tp, int rank, int m_cap, int H, const uint64_t* data_ptrs,
+                                   const uint64_t* flag_ptrs, uint64_t mc_data, const uint64_t* xchg_ptrs,
+                                   const uint64_t* xflag_ptrs) {
+  if (tp < 1 || tp > kMaxTp) return nullptr;
+  zse_tp_ctx* c = new zse_tp_ctx();
+  c->table.tp = tp;
+  c->table.m_cap = m_cap;
+  c->table.mc_data = reinterpret_cast<const __half*>(mc_data);
+  for (int r = 0; r < tp; ++r) {
+    c->table.data[r] = reinterpret_cast<__half*>(data_ptrs[r]);
+    c->table.flags[r] = reinterpret_cast<uint32_t*>(flag_ptrs[r]);
+    c->xchg[r] = reinterpret_cast<unsigned long long*>(xchg_ptrs[r]);
+    c->xflags[r] = reinterpret_cast<uint32_t*>(xflag_ptrs[r]);
+  }
+  c->rank = rank;
+  c->H = H;
+  return c;
+}
+
+extern "C" void zse_tp_ctx_destroy(void* ctx) { delete reinterpret_cast<zse_tp_ctx*>(ctx); }
+
+static int launch_reduce(const zse_tp_ctx* c, TpReduceArgs& a, int rows, int emulate, bool multimem,
+                         cudaStream_t st) {
+  dim3 grid(rows, emulate > 0 ? emulate : 1);
+  if (emulate > 0) {
+    void* params[] = {const_cast<TpTable*>(&c->table), &a};
+    const void* fn = multimem ? (const void*)tp_reduce_add_rmsnorm_kernel<true>
+                              : (const void*)tp_reduce_add_rmsnorm_kernel<false>;
+    return cudaLaunchCooperativeKernel(fn, grid, dim3(kRedThreads), params, 0, st) == cudaSuccess ? 0 : ZSE_ERR_LAUNCH;
+  }
+  if (multimem)
+    tp_reduce_add_rmsnorm_kernel<true><<<grid, kRedThreads, 0, st>>>(c->table, a);
+  else
+    tp_reduce_add_rmsnorm_kernel<false><<<grid, kRedThreads, 0, st>>>(c->table, a);
+  return cudaGetLastError() == cudaSuccess ? 0 : ZSE_ERR_LAUNCH;
+}
+
+// Real launch: residual/partials/out are this rank's.  Rows are processed in launches of at most 512 so that every
+// CTA of a launch is resident on every rank (a CTA waits for its peers' CTAs of the same row).
+extern "C" int zse_tp_reduce_add_rmsnorm(void* ctx, void* residual, const void* partials, int n_planes,
+                                         const void* weight, void* out, int M, float eps, int slot,
+                                         int use_multimem, void* status, void* stream) {
+  zse_tp_ctx* c = reinterpret_cast<zse_tp_ctx*>(ctx);
+  if (M <= 0) return 0;
+  if (c == nullptr || c->H % 8 || c->H > 8 * kRedThreads * kRedMaxChunks || M > c->table.m_cap) return ZSE_ERR_SHAPE;
+  if (use_multimem && c->table.mc_data == nullptr) return ZSE_ERR_SHAPE;
+  TpReduceArgs a{};
+  a.r[0] = TpRankArgs{reinterpret_cast<float*>(residual), reinterpret_cast<const float*>(partials),
+                      reinterpret_cast<__half*>(out), c->rank};
+  a.weight = reinterpret_cast<const __half*>(weight);
+  a.n_planes = n_planes;
+  a.M = M;
+  a.H = c->H;
+  a.eps = eps;
+  a.slot = slot & 1;
+  a.status = reinterpret_cast<Status*>(status);
+  for (int row0 = 0; row0 < M; row0 += 512) {
+    a.row0 = row0;
+    if (int rc = launch_reduce(c, a, min(512, M - row0), 0, use_multimem != 0, reinterpret_cast<cudaStream_t>(stream)))
+      return rc;
+  }
+  return 0;
+}
+
+// Single-GPU emulation of all ranks in one cooperative launch (tests): arrays hold one pointer per rank.
+extern "C" int zse_tp_reduce_add_rmsnorm_emulated(void* ctx, const uint64_t* residuals, const uint64_t* partials,
+                                                  int n_planes, const void* weight, const uint64_t* outs, int M,
+                                                  float eps, int slot, void* status, void* stream) {
+  zse_tp_ctx* c = reinterpret_cast<zse_tp_ctx*>(ctx);
+  if (c == nullptr || M <= 0 || M > c->table.m_cap || M * c->table.tp > 256) return ZSE_ERR_SHAPE;
+  TpReduceArgs a{};
+  for (int r = 0; r < c->table.tp; ++r)
+    a.r[r] = TpRankArgs{reinterpret_cast<float*>(residuals[r]), reinterpret_cast<const float*>(partials[r]),
+                        reinterpret_cast<__half*>(outs[r]), r};
+  a.weight = reinterpret_cast<const __half*>(weight);
+  a.n_planes = n_planes;
+  a.M = M;
+  a.H = c->H;
+  a.eps = eps;
+  a.slot = slot & 1;
+  a.row0 = 0;
+  a.status = reinterpret_cast<Status*>(status);
+  return launch_reduce(c, a, M, c->table.tp, false, reinterpret_cast<cudaStream_t>(stream));
+}
+
+extern "C" int zse_tp_argmax(void* ctx, const void* logits, int ld, void* out, int M, int V_local, int vocab_stride,
+                             int slot, void* status, void* stream) {
+  zse_tp_ctx* c = reinterpret_cast<zse_tp_ctx*>(ctx);
+  if (M <= 0) return 0;
+  if (c == nullptr || M > c->table.m_cap) return ZSE_ERR_SHAPE;
+  TpArgmaxArgs a{};
+  a.logits[0] = reinterpret_cast<const __half*>(logits);
+  a.out[0] = reinterpret_cast<int*>(out);
+  a.rank[0] = c->rank;
+  for (int r = 0; r < c->table.tp; ++r) {
+    a.xchg[r] = c->xchg[r];
+    a.flags[r] = c->xflags[r];
+  }
+  a.ld = ld;
+  a.V_local = V_local;
+  a.vocab_stride = vocab_stride;
+  a.tp = c->table.tp;
+  a.m_cap = c->table.m_cap;
+  a.slot = slot & 1;
+  a.status = reinterpret_cast<Status*>(status);
+  tp_argmax_kernel<<<dim3(M, 1), 1024, 0, reinterpret_cast<cudaStream_t>(stream)>>>(a);
+  return cudaGetLastError() == cudaSuccess ? 0 : ZSE_ERR_LAUNCH;
+}
+
+extern "C" int zse_tp_argmax_emulated(void* ctx, const uint64_t* logits, int ld, const uint64_t* outs, int M,
+                                      int V_local, int vocab_stride, int slot, void* status,
+                                      void* stream) {
+  zse_tp_ctx* c = reinterpret_cast<zse_tp_ctx*>(ctx);
+  if (c == nullptr || M <= 0 || M > c->table.m_cap || M * c->table.tp > 128) return ZSE_ERR_SHAPE;
+  TpArgmaxArgs a{};
+  for (int r = 0; r < c->table.tp; ++r) {
+    a.logits[r] = reinterpret_cast<const __half*>(logits[r]);
+    a.out[r] = reinterpret_cast<int*>(outs[r]);
+    a.rank[r] = r;
+    a.xchg[r] = c->xchg[r];
+    a.flags[r] = c->xflags[r];
+  }
+  a.ld = ld;
+  a.V_local = V_local;
+  a.vocab_stride = vocab_stride;
+  a.tp = c->table.tp;
+  a.m_cap = c->table.m_cap;
+  a.slot = slot & 1;
+  a.status = reinterpret_cast<Status*>(status);
+  void* params[] = {&a};
+  return cudaLaunchCooperativeKernel((const void*)tp_argmax_kernel, dim3(M, c->table.tp), dim3(1024), params, 0,
+                                     reinterpret_cast<cudaStream_t>(stream)) == cudaSuccess
+             ? 0
+             : ZSE_ERR_LAUNCH;
+}

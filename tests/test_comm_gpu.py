@@ -1,0 +1,112 @@
+"""Fused tensor-parallel reduction kernels.
+
+On one GPU the protocol (per-row flags, two slots, pull over peer pointers, flag take-down) is exercised by the
+emulated entry points: one cooperative launch plays every rank on buffers of the same device.  With two or more
+GPUs the real kernels run in child processes over symmetric memory, against NCCL and against an fp32 restatement.
+"""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+from zse_b200.ops import reference as ref
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _emulated_ctx(tp, m_cap, H):
+    from zse_b200.ops import native
+    dev = "cuda"
+    data = [torch.zeros(2 * m_cap * H, dtype=torch.float16, device=dev) for _ in range(tp)]
+    flags = [torch.zeros(2 * tp * m_cap, dtype=torch.int32, device=dev) for _ in range(tp)]
+    xchg = [torch.zeros(2 * tp * m_cap, dtype=torch.int64, device=dev) for _ in range(tp)]
+    xflags = [torch.zeros(2 * tp * m_cap, dtype=torch.int32, device=dev) for _ in range(tp)]
+    ctx = native.tp_ctx_create(tp, 0, m_cap, H, [t.data_ptr() for t in data], [t.data_ptr() for t in flags], 0,
+                               [t.data_ptr() for t in xchg], [t.data_ptr() for t in xflags])
+    return ctx, (data, flags, xchg, xflags)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("tp,M,H,planes", [(2, 5, 512, 1), (4, 16, 1024, 3), (8, 7, 5120, 2)])
+def test_reduce_add_rmsnorm_emulated_ranks(tp, M, H, planes):
+    from zse_b200.ops import native
+    ctx, keep = _emulated_ctx(tp, 32, H)
+    status = native.Status("cuda")
+    w = (1 + 0.1 * torch.randn(H, device="cuda")).half()
+    res0 = torch.randn(M, H, device="cuda")
+    residuals = [res0.clone() for _ in range(tp)]
+    partials = [torch.randn(planes, M, H, device="cuda") for _ in range(tp)]
+    outs = [torch.zeros(M, H, dtype=torch.float16, device="cuda") for _ in range(tp)]
+    for call in range(4):            # several calls: slots alternate, flags are taken down and raised again
+        native.tp_reduce_add_rmsnorm_emulated(ctx, residuals, partials, planes, w, outs, M, 1e-6, call & 1, status.ptr)
+        torch.cuda.synchronize()
+        status.check()
+        total = sum(p.sum(0).half().float() for p in partials)     # each rank's row is rounded to fp16 on the wire
+        want_res = res0 + (call + 1) * total
+        for r in range(tp):
+            assert torch.allclose(residuals[r], want_res, atol=2e-3, rtol=1e-4), (call, r)
+            assert torch.equal(residuals[r], residuals[0])          # every rank holds bit-identical residuals
+            got, want = outs[r].float(), ref.rmsnorm(want_res, w, 1e-6).float()
+            assert (got - want).abs().max() < 1e-2
+        assert all(int(f.abs().sum()) == 0 for f in keep[1])        # all flags are down again
+    native.tp_ctx_destroy(ctx)
+
+
+@pytest.mark.gpu
+def test_tp_argmax_emulated_ranks():
+    from zse_b200.ops import native
+    tp, M, V_local = 4, 6, 1000
+    ctx, keep = _emulated_ctx(tp, 32, 512)
+    status = native.Status("cuda")
+    full = (torch.randn(M, tp * V_local, device="cuda") * 3).half()
+    full[1, 10] = full[1, 3010] = 60.0            # a tie across ranks: the lower token id wins
+    shards = [full[:, r * V_local:(r + 1) * V_local].contiguous() for r in range(tp)]
+    outs = [torch.zeros(M, dtype=torch.int32, device="cuda") for _ in range(tp)]
+    for _ in range(2):
+        native.tp_argmax_emulated(ctx, shards, V_local, outs, M, V_local, V_local, 0, status.ptr)
+        torch.cuda.synchronize()
+        status.check()
+        want = full.float().argmax(-1).int()
+        assert int(want[1]) == 10
+        for r in range(tp):
+            assert torch.equal(outs[r], want)
+    native.tp_ctx_destroy(ctx)
+
+
+@pytest.mark.gpu
+def test_peer_wait_times_out_with_status_instead_of_hanging():
+    """A flag that nothing raises: the bounded wait gives up, the kernel returns, the context stays usable and the
+    host sees a 'peer wait timed out' status.  (One real rank whose peer table points at a rank that never runs.)"""
+    from zse_b200.ops import native
+    tp, H, M = 2, 512, 1
+    ctx, keep = _emulated_ctx(tp, 8, H)
+    status = native.Status("cuda")
+    res = torch.zeros(M, H, device="cuda")
+    part = torch.ones(1, M, H, device="cuda")
+    out = torch.zeros(M, H, dtype=torch.float16, device="cuda")
+    w = torch.ones(H, dtype=torch.float16, device="cuda")
+    # the real (non-emulated) entry point runs rank 0 only; rank 1 never raises its flag
+    native.tp_reduce_add_rmsnorm(ctx, res, part, 1, w, out, M, 1e-6, 0, False, status.ptr)
+    torch.cuda.synchronize()
+    code, _, where, detail = status.read()
+    assert (code, where, detail) == (3, 31, 1)
+    with pytest.raises(native.DeviceStatusError):
+        status.check()
+    assert float(res.abs().sum()) == 0.0          # the row was left alone
+    assert float((torch.ones(4, device="cuda") * 2).sum()) == 8.0     # device still answers
+    native.tp_ctx_destroy(ctx)
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
+def test_fused_comm_matches_nccl_on_real_gpus():
+    n = min(torch.cuda.device_count(), 4)
+    env = dict(os.environ, NCCL_NVLS_ENABLE=os.environ.get("NCCL_NVLS_ENABLE", "1"))
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
+                        "--master-addr", "127.0.0.1", "--master-port", "29633",
+                        os.path.join(ROOT, "tests", "dist_fused_comm_worker.py")], capture_output=True, text=True,
+                       timeout=600, env=env, cwd=ROOT)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "FUSED_COMM_OK" in r.stdout

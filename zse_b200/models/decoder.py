@@ -204,11 +204,17 @@ class DecoderModel:
                            logits_rows or max_seqs, attn_splits)
 
     # ---- forward --------------------------------------------------------------------------------------
-    def _reduce(self, b: StepBuffers, planes: int, M: int) -> int:
-        """Row-parallel outputs: with tensor parallelism the partial planes of all ranks are summed into plane 0."""
-        if self.comm is not None:
-            return self.comm.all_reduce_partials(b.partials, planes, M)
-        return planes
+    def _add_norm(self, b: StepBuffers, planes: int, weight: torch.Tensor, M: int) -> None:
+        """residual += (row-parallel output summed over split-K planes and, with tensor parallelism, over ranks);
+        xnorm = RMSNorm(residual) * weight."""
+        ops, eps = self.ops, self.config.rms_norm_eps
+        if self.comm is None or planes == 0:
+            ops.add_rmsnorm(b.residual, b.partials, planes, None, weight, b.xnorm, M, eps)
+        elif self.comm.fused_norm:
+            self.comm.reduce_add_rmsnorm(ops, b.residual, b.partials, planes, weight, b.xnorm, M, eps)
+        else:
+            planes = self.comm.all_reduce_partials(b.partials, planes, M)
+            ops.add_rmsnorm(b.residual, b.partials, planes, None, weight, b.xnorm, M, eps)
 
     def forward(self, b: StepBuffers, kv: torch.Tensor, M: int, mode: str, num_seqs: int, max_q_len: int = 1,
                 n_logit_rows: int = 0, attn_splits: int = 1) -> None:
@@ -216,10 +222,12 @@ class DecoderModel:
         ``b.logits``.  ``kv``: [layers, blocks, 2, nkv_local, block_size, hd]."""
         c, p, ops = self.config, self.plan, self.ops
         bs = kv.shape[4]
+        if self.comm is not None and self.comm.fused_norm:
+            self.comm.begin_pass()
         ops.embedding(self.embed, b.ids, b.residual, M, self.embed_scale)
         planes = 0
         for li, L in enumerate(self.layers):
-            ops.add_rmsnorm(b.residual, b.partials, planes, None, L.ln1, b.xnorm, M, c.rms_norm_eps)
+            self._add_norm(b, planes, L.ln1, M)
             ops.linear(L.qkv, b.xnorm, M, b.qkv)
             if self.lora is not None:
                 self.lora.apply_qkv(li, b, M)
@@ -231,11 +239,11 @@ class DecoderModel:
             else:
                 ops.attn_prefill(b.qkv, kv[li], b.block_tables, b.cu_q, b.q_pos0, b.attn_out, num_seqs, M, max_q_len,
                                  p.num_heads, p.num_kv_heads, c.head_dim, bs, self.scale)
-            planes = self._reduce(b, ops.linear_partial(L.o, b.attn_out, M, b.partials), M)
-            ops.add_rmsnorm(b.residual, b.partials, planes, None, L.ln2, b.xnorm, M, c.rms_norm_eps)
+            planes = ops.linear_partial(L.o, b.attn_out, M, b.partials)
+            self._add_norm(b, planes, L.ln2, M)
             ops.linear_swiglu(L.gate_up, b.xnorm, M, b.act)
-            planes = self._reduce(b, ops.linear_partial(L.down, b.act, M, b.partials), M)
-        ops.add_rmsnorm(b.residual, b.partials, planes, None, self.norm, b.xnorm, M, c.rms_norm_eps)
+            planes = ops.linear_partial(L.down, b.act, M, b.partials)
+        self._add_norm(b, planes, self.norm, M)
         if n_logit_rows:
             torch.index_select(b.xnorm, 0, b.logit_rows[:n_logit_rows], out=b.xsel[:n_logit_rows])
             ops.linear(self.lm_head, b.xsel, n_logit_rows, b.logits)

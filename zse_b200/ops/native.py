@@ -62,6 +62,16 @@ _SIGS = {
     "zse_lora_shrink": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "zse_lora_expand": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                 c_void_p]),
+    "zse_tp_ctx_create": (c_void_p, [c_int, c_int, c_int, c_int, POINTER(c_uint64), POINTER(c_uint64), c_uint64,
+                                     POINTER(c_uint64), POINTER(c_uint64)]),
+    "zse_tp_ctx_destroy": (None, [c_void_p]),
+    "zse_tp_reduce_add_rmsnorm": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_float,
+                                          c_int, c_int, c_void_p, c_void_p]),
+    "zse_tp_reduce_add_rmsnorm_emulated": (c_int, [c_void_p, POINTER(c_uint64), POINTER(c_uint64), c_int, c_void_p,
+                                                   POINTER(c_uint64), c_int, c_float, c_int, c_void_p, c_void_p]),
+    "zse_tp_argmax": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "zse_tp_argmax_emulated": (c_int, [c_void_p, POINTER(c_uint64), c_int, POINTER(c_uint64), c_int, c_int, c_int,
+                                       c_int, c_void_p, c_void_p]),
     "zse_status_read": (c_int, [c_void_p, POINTER(c_uint32)]),
     "zse_device_info": (c_int, [POINTER(c_int), POINTER(c_int), POINTER(c_int), POINTER(c_int64), POINTER(c_int64)]),
     "zse_build_info": (c_char_p, []),
@@ -239,6 +249,46 @@ def lora_shrink(x, ldx, a, ids, tmp, M, K, rank):
 
 def lora_expand(tmp, b, ids, scales, y, ldy, M, N, rank):
     _ck(load().zse_lora_expand(_p(tmp), _p(b), _p(ids), _p(scales), _p(y), ldy, M, N, rank, _stream()), "lora_expand")
+
+
+def _u64s(vals):
+    return (c_uint64 * len(vals))(*[int(v) for v in vals])
+
+
+def tp_ctx_create(tp, rank, m_cap, H, data_ptrs, flag_ptrs, mc_data, xchg_ptrs, xflag_ptrs) -> int:
+    ctx = load().zse_tp_ctx_create(tp, rank, m_cap, H, _u64s(data_ptrs), _u64s(flag_ptrs), int(mc_data or 0),
+                                   _u64s(xchg_ptrs), _u64s(xflag_ptrs))
+    if not ctx:
+        raise NativeError("tp_ctx_create: unsupported tensor-parallel size")
+    return ctx
+
+
+def tp_ctx_destroy(ctx) -> None:
+    load().zse_tp_ctx_destroy(ctx)
+
+
+def tp_reduce_add_rmsnorm(ctx, residual, partials, n_planes, weight, out, M, eps, slot, use_multimem, status):
+    _ck(load().zse_tp_reduce_add_rmsnorm(ctx, _p(residual), _p(partials), n_planes, _p(weight), _p(out), M, eps,
+                                         slot, int(use_multimem), status, _stream()), "tp_reduce_add_rmsnorm",
+        (M + 511) // 512)
+
+
+def tp_reduce_add_rmsnorm_emulated(ctx, residuals, partials, n_planes, weight, outs, M, eps, slot, status):
+    _ck(load().zse_tp_reduce_add_rmsnorm_emulated(ctx, _u64s([t.data_ptr() for t in residuals]),
+                                                  _u64s([t.data_ptr() for t in partials]), n_planes, _p(weight),
+                                                  _u64s([t.data_ptr() for t in outs]), M, eps, slot, status,
+                                                  _stream()), "tp_reduce_add_rmsnorm_emulated")
+
+
+def tp_argmax(ctx, logits, ld, out, M, V_local, vocab_stride, slot, status):
+    _ck(load().zse_tp_argmax(ctx, _p(logits), ld, _p(out), M, V_local, vocab_stride, slot, status, _stream()),
+        "tp_argmax")
+
+
+def tp_argmax_emulated(ctx, logits, ld, outs, M, V_local, vocab_stride, slot, status):
+    _ck(load().zse_tp_argmax_emulated(ctx, _u64s([t.data_ptr() for t in logits]), ld,
+                                      _u64s([t.data_ptr() for t in outs]), M, V_local, vocab_stride, slot,
+                                      status, _stream()), "tp_argmax_emulated")
 
 
 def device_info() -> dict:

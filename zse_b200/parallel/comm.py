@@ -1,0 +1,157 @@
+"""Tensor-parallel collectives of the decoder.
+
+Two back ends behind one interface:
+
+``FusedComm`` (product path) - the reduction after every row-parallel projection happens inside
+  ``tp_reduce_add_rmsnorm`` (csrc/comm.cu): split-K planes -> fp16 row in symmetric memory -> per-row flags pushed to
+  the peers -> rows pulled over NVLink (or reduced in the NVSwitch with ``multimem.ld_reduce``) -> residual add ->
+  RMSNorm, all in one kernel and without a NCCL call; greedy token selection over the vocabulary-sharded lm_head uses
+  the same flag protocol (``tp_argmax``).  Symmetric buffers come from ``torch.distributed._symmetric_memory``.
+``NcclComm`` (baseline) - ``dist.all_reduce`` between the unfused kernels, like the reference's ``ncclAllReduce``
+  after o_proj and down_proj (zse-engine/zse_engine/orchestrator/model_runner.py:2622-2635,2694-2705).
+
+Both are SPMD: every rank runs the same engine on the same requests, so no control plane is needed in the hot loop.
+"""
+from __future__ import annotations
+
+import os
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+
+class NcclComm:
+    name = "nccl"
+    graph_safe = True          # NCCL collectives can be captured in CUDA graphs
+    fused_norm = False
+
+    def __init__(self, rank: int, world: int, device, group=None):
+        self.rank, self.world, self.device, self.group = rank, world, device, group
+        self._gather = None
+
+    def all_reduce_partials(self, partials: torch.Tensor, planes: int, M: int) -> int:
+        """Sums this rank's planes into plane 0 and all-reduces it; returns the number of planes left (1)."""
+        p0 = partials[0, :M]
+        if planes > 1:
+            torch.sum(partials[:planes, :M], dim=0, out=p0)
+        dist.all_reduce(p0, group=self.group)
+        return 1
+
+    def select_tokens(self, runner, n_rows: int, greedy: bool, step: int) -> None:
+        b, ops, plan = runner.buf, runner.model.ops, runner.model.plan
+        V = plan.vocab_size
+        stride = (runner.model.config.vocab_size + self.world - 1) // self.world
+        if greedy:
+            vals, idx = b.logits[:n_rows, :V].float().max(dim=-1)
+            both = torch.stack([vals, (idx + plan.vocab[0]).float()], dim=-1).contiguous()
+            gathered = torch.empty(self.world, n_rows, 2, dtype=torch.float32, device=self.device)
+            dist.all_gather_into_tensor(gathered, both, group=self.group)
+            best = gathered[:, :, 0].argmax(dim=0)       # first rank wins ties -> lowest token id
+            b.out_tokens[:n_rows] = gathered[best, torch.arange(n_rows, device=self.device), 1].to(torch.int32)
+        else:
+            full = self.gather_logits(runner, n_rows)
+            ops.sample(full, b.out_tokens, n_rows, b.temperature, b.top_k, b.top_p, b.seeds, step)
+
+    def gather_logits(self, runner, n_rows: int) -> torch.Tensor:
+        """Full-vocabulary fp16 logits [n_rows, vocab] on every rank (shards may be uneven by one row)."""
+        b, plan = runner.buf, runner.model.plan
+        vocab = runner.model.config.vocab_size
+        width = (vocab + self.world - 1) // self.world
+        local = torch.full((n_rows, width), float("-inf"), dtype=torch.float16, device=self.device)
+        local[:, : plan.vocab_size] = b.logits[:n_rows, : plan.vocab_size]
+        out = torch.empty(self.world, n_rows, width, dtype=torch.float16, device=self.device)
+        dist.all_gather_into_tensor(out, local, group=self.group)
+        from .shard_plan import split_units
+        parts = [out[r, :, : hi - lo] for r, (lo, hi) in enumerate(split_units(vocab, self.world))]
+        return torch.cat(parts, dim=1).contiguous()
+
+    def barrier(self) -> None:
+        dist.barrier(group=self.group)
+
+    def close(self) -> None:
+        pass
+
+
+class FusedComm(NcclComm):
+    name = "fused"
+    graph_safe = True
+    fused_norm = True
+
+    def __init__(self, rank: int, world: int, device, hidden_size: int, max_tokens: int, group=None,
+                 use_multimem: Optional[bool] = None):
+        super().__init__(rank, world, device, group)
+        import torch.distributed._symmetric_memory as symm
+        from ..ops import native
+        self._n = native
+        self.m_cap = max_tokens
+        self.H = hidden_size
+        grp = group or dist.group.WORLD
+        # one symmetric allocation, carved into: row data, row flags, exchange words, exchange flags
+        data_bytes = 2 * max_tokens * hidden_size * 2
+        flag_bytes = 2 * world * max_tokens * 4
+        xchg_bytes = 2 * world * max_tokens * 8
+        align = lambda n: (n + 255) // 256 * 256
+        offs = [0, align(data_bytes)]
+        offs.append(offs[-1] + align(flag_bytes))
+        offs.append(offs[-1] + align(xchg_bytes))
+        total = offs[-1] + align(flag_bytes)
+        self._buf = symm.empty(total, dtype=torch.uint8, device=device)
+        self._buf.zero_()
+        self._hdl = symm.rendezvous(self._buf, grp)
+        torch.cuda.synchronize(device)
+        dist.barrier(group=grp)
+        ptrs = [int(p) for p in self._hdl.buffer_ptrs]
+        want_mm = use_multimem if use_multimem is not None else os.environ.get("ZSE_TP_MULTIMEM", "1") != "0"
+        mc = 0
+        if want_mm:
+            try:
+                mc = int(self._hdl.multicast_ptr or 0)     # 0 when the fabric has no NVLS multicast
+            except Exception:
+                mc = 0
+        self.use_multimem = bool(mc) and want_mm
+        self._ctx = native.tp_ctx_create(world, rank, max_tokens, hidden_size, [p + offs[0] for p in ptrs],
+                                         [p + offs[1] for p in ptrs], (mc + offs[0]) if mc else 0,
+                                         [p + offs[2] for p in ptrs], [p + offs[3] for p in ptrs])
+        self._calls = 0
+
+    def begin_pass(self) -> None:
+        """Every pass makes an even number of reductions (two per layer), so restarting the slot sequence at 0 keeps
+        consecutive calls on alternating slots across passes and across CUDA-graph replays."""
+        self._calls = 0
+
+    # The decoder calls this instead of (all_reduce_partials + add_rmsnorm).
+    def reduce_add_rmsnorm(self, ops, residual, partials, planes, weight, out, M, eps) -> None:
+        self._n.tp_reduce_add_rmsnorm(self._ctx, residual, partials, planes, weight, out, M, float(eps),
+                                      self._calls & 1, self.use_multimem, ops.status.ptr)
+        self._calls += 1
+
+    def select_tokens(self, runner, n_rows: int, greedy: bool, step: int) -> None:
+        if not greedy:
+            return super().select_tokens(runner, n_rows, greedy, step)
+        b, plan = runner.buf, runner.model.plan
+        from .shard_plan import split_units
+        bounds = split_units(runner.model.config.vocab_size, self.world)
+        # shards are contiguous and (nearly) even: rank r starts at bounds[r][0]; the kernel wants a stride, so it is
+        # only exact when the split is even - otherwise fall back to the gather path
+        sizes = {hi - lo for lo, hi in bounds}
+        if len(sizes) != 1:
+            return super().select_tokens(runner, n_rows, greedy, step)
+        self._n.tp_argmax(self._ctx, b.logits, b.logits.stride(0), b.out_tokens, n_rows, plan.vocab_size,
+                          bounds[1][0] - bounds[0][0] if self.world > 1 else plan.vocab_size, 0,
+                          runner.model.ops.status.ptr)
+
+    def close(self) -> None:
+        if self._ctx:
+            self._n.tp_ctx_destroy(self._ctx)
+            self._ctx = None
+
+
+def make_comm(backend: str, rank: int, world: int, device, hidden_size: int = 0, max_tokens: int = 0, group=None):
+    if world <= 1:
+        return None
+    if backend == "nccl":
+        return NcclComm(rank, world, device, group)
+    if backend == "fused":
+        return FusedComm(rank, world, device, hidden_size, max_tokens, group)
+    raise ValueError(f"unknown tensor-parallel comm backend '{backend}' (fused | nccl)")
