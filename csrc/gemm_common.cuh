@@ -1,0 +1,51 @@
+// Definitions shared by the tensor-core GEMM kernels (gemm.cu: fp16 weights, gemm_w4.cu: INT4 weights).
+#pragma once
+#include <cuda.h>
+
+#include "api.h"
+#include "common.cuh"
+
+namespace zse {
+
+constexpr int kTileN = 128;          // weight rows per CTA (UMMA M)
+constexpr int kW4StageK = 128;       // K per pipeline stage of the INT4 kernel (= quantisation group)
+constexpr int kW4ChunkBytes = 8704;  // 8192 nibble bytes + 512 bytes of {scale, zero}
+constexpr int kGemmThreads = 320;    // fp16 kernel: warp 0 producer, warp 1 MMA issuer, warps 2..9 epilogue
+
+enum Epilogue : int { kEpiF16 = 0, kEpiSwiGLU = 1, kEpiPartialF32 = 2 };
+
+struct GemmArgs {
+  const uint8_t* w;        // W4: tiled chunks [n_tiles][k_stages][8704]; F16: unused (tensor map)
+  const __half* bias;      // [N] or null (kEpiF16 only)
+  void* out;               // fp16 [M, ldo] / fp32 planes [M, ldo] (fp16 kernel: one plane per K split)
+  int M, N, K;
+  int ldo;                 // output row stride in elements
+  int k_stages;            // total K stages
+  int stages_per_split;
+  Status* status;
+};
+
+
+
+// fp16 [rows, cols] row-major tensor map: box = 64 columns x box_rows rows, 128-byte swizzle, zero fill out of
+// bounds; cached per (pointer, shape, box).  Defined in gemm.cu.
+int get_tmap(const void* ptr, uint64_t rows, uint64_t cols, uint32_t box_rows, CUtensorMap* out);
+
+inline int pick_nt(int M) {
+  if (M <= 16) return 16;
+  if (M <= 32) return 32;
+  if (M <= 64) return 64;
+  if (M <= 128) return 128;
+  return 256;
+}
+
+#define ZSE_DISPATCH_NT(nt, CALL)   \
+  switch (nt) {                     \
+    case 16: { constexpr int NT = 16; CALL; } break;   \
+    case 32: { constexpr int NT = 32; CALL; } break;   \
+    case 64: { constexpr int NT = 64; CALL; } break;   \
+    case 128: { constexpr int NT = 128; CALL; } break; \
+    default: { constexpr int NT = 256; CALL; } break;  \
+  }
+
+}  // namespace zse

@@ -1,0 +1,458 @@
+// INT4 group-128 weight linear layers on the 5th-generation tensor cores.
+//
+//   Y[t, n] = sum_k X[t, k] * (nibble[n, k] * scale[n, k/128] + zero[n, k/128])
+//
+// Computed transposed ("swap AB"): UMMA M (128) runs over weight rows, UMMA N (16..256) over tokens, so a decode step
+// with a few tokens fills the TMEM lanes and the weight stream is read exactly once.
+//
+// Data flow of one CTA (608 threads):
+//   warp 0      streams 8704-byte weight chunks (8192 B nibbles + 128 x {scale, zero}) with 1-D bulk TMA copies
+//               into a deep ring (up to 12 chunks in flight: this ring is what hides HBM latency);
+//   warp 18     streams the activation tile (tiled TMA, 128-byte swizzle) into a short ring (it comes from L2);
+//   warps 2-17  turn a chunk into fp16 in registers (lop3 nibble extraction, exact q*s+z in half2) and write it with
+//               tcgen05.st straight into TMEM;
+//   warp 1      issues tcgen05.mma with A from TMEM and B (activations) from shared memory; accumulators in TMEM.
+// The dequantised weights never touch shared memory.  A CTA owns R = 1 or 2 adjacent 128-row weight tiles and reuses
+// every activation stage for all of them (the activation tile is re-read from L2 by every CTA, so R halves that
+// traffic).  Split-K runs as a thread-block cluster along K: the non-leading CTAs park their accumulators in their
+// shared memory, the leading CTA adds them through distributed shared memory and runs the epilogue, so split-K costs
+// no global-memory traffic and works with every epilogue.
+//
+// Epilogues: fp16 store (+bias), SwiGLU (tile rows 0..63 = gate, 64..127 = up of the same 64 outputs), fp32 store
+// (row-parallel projections; consumed by add_rmsnorm / tp_reduce_add_rmsnorm together with the residual).
+//
+// Replaces the scalar dequant GEMV / 32x32 tiled matmul kernels of the reference
+// (zse-engine/zse_engine/orchestrator/kernels.py:1129-1192,1906-2073,2114-2203).
+#include "gemm_common.cuh"
+
+namespace zse {
+
+constexpr int kW4Threads = 608;        // 19 warps
+constexpr int kDqWarps = 16;
+constexpr int kXWarp = 18;
+
+template <int NT, int R>
+struct W4Cfg {
+  static constexpr int kXBytes = NT * 128;                         // one 64-wide K sub-tile of X
+  static constexpr int kXStage = 2 * kXBytes;
+  static constexpr int kSX = NT <= 64 ? 4 : (NT == 128 ? 3 : 2);   // activation stages
+  static constexpr int kSW = NT <= 64 ? 12 : (NT == 128 ? 10 : 8); // weight chunks in flight
+  static constexpr int kAcc = R * NT;                              // accumulator columns
+  static constexpr int kSA = (512 - kAcc) / 64 > 6 ? 6 : (512 - kAcc) / 64;   // A slots in TMEM
+  static constexpr int kRingBytes = kSX * kXStage + kSW * kW4ChunkBytes;
+  static constexpr int kParkBytes = R * NT * 128 * 4;              // accumulators parked for the cluster reduce
+  static constexpr int kDataBytes = ((kRingBytes > kParkBytes ? kRingBytes : kParkBytes) + 15) & ~15;
+  static constexpr int kXchBytes = 8 * 32 * 16 * 4;               // SwiGLU gate/up exchange (after the barriers)
+  static constexpr int kSmemBytes = kDataBytes + 512 + kXchBytes + 1024;
+  static_assert(kSA >= 2, "not enough TMEM for the A ring");
+};
+
+struct W4Bars {
+  uint64_t w_full[12], w_empty[12];
+  uint64_t x_full[4], x_empty[4];
+  uint64_t a_ready[6], a_empty[6];
+  uint64_t acc_ready;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+struct W4Args {
+  const uint8_t* w;        // tiled chunks [n_tiles][k_stages][8704]
+  const __half* bias;      // [N] or null (kEpiF16)
+  void* out;
+  int M, N, K, ldo;
+  int k_stages;            // K / 128
+  int stages_per_split;    // K stages handled by one CTA of the cluster
+  int cluster_k;           // CTAs per cluster (= gridDim.z)
+  Status* status;
+};
+
+// Nibble order inside every 32-bit word of a chunk (fixed by repack_w4): positions 0..7 hold the K elements
+// e0,e2,e4,e6,e1,e3,e5,e7 so that masking with 0x000f000f yields the adjacent pair (e0,e1) as a half2.
+__device__ __forceinline__ void dequant_word(uint32_t w, __half2 s2, __half2 z2, uint32_t* out4) {
+  const __half2 k1024 = __half2half2(__ushort_as_half(0x6400));
+  const __half2 k16th = __half2half2(__ushort_as_half(0x2C00));   // 1/16
+  const __half2 kNeg64 = __half2half2(__ushort_as_half(0xD400));  // -64
+  uint32_t t0, t1, t2, t3;
+  const uint32_t w8 = w >> 8;
+  asm("lop3.b32 %0, %1, 0x000f000f, 0x64006400, 0xEA;" : "=r"(t0) : "r"(w));
+  asm("lop3.b32 %0, %1, 0x00f000f0, 0x64006400, 0xEA;" : "=r"(t1) : "r"(w));
+  asm("lop3.b32 %0, %1, 0x000f000f, 0x64006400, 0xEA;" : "=r"(t2) : "r"(w8));
+  asm("lop3.b32 %0, %1, 0x00f000f0, 0x64006400, 0xEA;" : "=r"(t3) : "r"(w8));
+  __half2 e0 = __hsub2(*reinterpret_cast<__half2*>(&t0), k1024);
+  __half2 e1 = __hfma2(*reinterpret_cast<__half2*>(&t1), k16th, kNeg64);
+  __half2 e2 = __hsub2(*reinterpret_cast<__half2*>(&t2), k1024);
+  __half2 e3 = __hfma2(*reinterpret_cast<__half2*>(&t3), k16th, kNeg64);
+  e0 = __hfma2(e0, s2, z2);
+  e1 = __hfma2(e1, s2, z2);
+  e2 = __hfma2(e2, s2, z2);
+  e3 = __hfma2(e3, s2, z2);
+  out4[0] = *reinterpret_cast<uint32_t*>(&e0);
+  out4[1] = *reinterpret_cast<uint32_t*>(&e1);
+  out4[2] = *reinterpret_cast<uint32_t*>(&e2);
+  out4[3] = *reinterpret_cast<uint32_t*>(&e3);
+}
+
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+__device__ __forceinline__ float ld_dsmem_f32(uint32_t local_smem_addr, uint32_t cta_rank) {
+  uint32_t remote;
+  float v;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local_smem_addr), "r"(cta_rank));
+  asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(remote) : "memory");
+  return v;
+}
+
+// Drain helper for an aborted producer: every issued copy must land before the CTA may exit.
+__device__ __forceinline__ void drain(uint64_t* full, int ring, int issued) {
+  for (int it = max(0, issued - ring); it < issued; ++it) {
+    const uint64_t t0 = globaltimer_ns();
+    while (!mbar_try_wait(&full[it % ring], (it / ring) & 1) && globaltimer_ns() - t0 < kWaitLimitNs) {
+    }
+  }
+}
+
+template <int NT, int R, int EPI>
+__global__ void __launch_bounds__(kW4Threads, 1)
+gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4Args a) {
+  using Cfg = W4Cfg<NT, R>;
+  constexpr int SW = Cfg::kSW, SX = Cfg::kSX, SA = Cfg::kSA;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* x_ring = smem;                                    // [SX][2][NT*128]
+  uint8_t* w_ring = smem + SX * Cfg::kXStage;                // [SW][8704]
+  W4Bars* bars = reinterpret_cast<W4Bars*>(smem + Cfg::kDataBytes);
+  float* xch_base = reinterpret_cast<float*>(smem + Cfg::kDataBytes + 512);
+  float* park = reinterpret_cast<float*>(smem);              // reused after the main loop: [R*NT cols][128 rows]
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int s_begin = blockIdx.z * a.stages_per_split;
+  const int n_k = max(0, min(a.k_stages, s_begin + a.stages_per_split) - s_begin);
+  const int n_units = n_k * R;
+  const int tile0 = blockIdx.x * R;                          // first weight tile of this CTA
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < SW; ++i) {
+      mbar_init(&bars->w_full[i], 1);
+      mbar_init(&bars->w_empty[i], kDqWarps);
+    }
+    for (int i = 0; i < SX; ++i) {
+      mbar_init(&bars->x_full[i], 1);
+      mbar_init(&bars->x_empty[i], 1);
+    }
+    for (int i = 0; i < SA; ++i) {
+      mbar_init(&bars->a_ready[i], kDqWarps);
+      mbar_init(&bars->a_empty[i], 1);
+    }
+    mbar_init(&bars->acc_ready, 1);
+    bars->abort_flag = 0;
+    mbar_fence_init();
+    prefetch_tmap(&tmap_x);
+  }
+  if (warp == 1) {
+    tmem_alloc(&bars->tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = bars->tmem_base;
+  const uint32_t a_base = tmem + Cfg::kAcc;
+  volatile int* abort_flag = &bars->abort_flag;
+  bool acc_ok = false;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ weight producer
+    if (lane == 0) {
+      int issued = 0;
+      for (int u = 0; u < n_units; ++u) {
+        const int s = u % SW;
+        if (u >= SW && !mbar_wait(&bars->w_empty[s], ((u / SW) - 1) & 1, abort_flag, a.status, 1, u)) break;
+        const int kk = u / R, r = u - kk * R;
+        const uint8_t* src = a.w + (size_t(tile0 + r) * a.k_stages + (s_begin + kk)) * kW4ChunkBytes;
+        mbar_arrive_expect_tx(&bars->w_full[s], kW4ChunkBytes);
+        bulk_g2s(w_ring + s * kW4ChunkBytes, src, kW4ChunkBytes, &bars->w_full[s]);
+        issued = u + 1;
+      }
+      if (*abort_flag) drain(bars->w_full, SW, issued);
+    }
+  } else if (warp == kXWarp) {
+    // ------------------------------------------------------------------ activation producer
+    if (lane == 0) {
+      int issued = 0;
+      for (int kk = 0; kk < n_k; ++kk) {
+        const int s = kk % SX;
+        if (kk >= SX && !mbar_wait(&bars->x_empty[s], ((kk / SX) - 1) & 1, abort_flag, a.status, 2, kk)) break;
+        mbar_arrive_expect_tx(&bars->x_full[s], Cfg::kXStage);
+        const int k0 = (s_begin + kk) * kW4StageK;
+        tma_load_2d(x_ring + s * Cfg::kXStage, &tmap_x, k0, blockIdx.y * NT, &bars->x_full[s]);
+        tma_load_2d(x_ring + s * Cfg::kXStage + Cfg::kXBytes, &tmap_x, k0 + 64, blockIdx.y * NT, &bars->x_full[s]);
+        issued = kk + 1;
+      }
+      if (*abort_flag) drain(bars->x_full, SX, issued);
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_f16(kTileN, NT);
+      for (int u = 0; u < n_units; ++u) {
+        const int kk = u / R, r = u - kk * R;
+        const int sx = kk % SX, sa = u % SA;
+        if (r == 0 && !mbar_wait(&bars->x_full[sx], (kk / SX) & 1, abort_flag, a.status, 3, kk)) break;
+        if (!mbar_wait(&bars->a_ready[sa], (u / SA) & 1, abort_flag, a.status, 4, u)) break;
+        tc_fence_after_sync();
+        const uint32_t xb = smem_u32(x_ring + sx * Cfg::kXStage);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const uint64_t bdesc = make_desc_sw128(xb + (j >> 2) * Cfg::kXBytes + (j & 3) * 32);
+          umma_ts(tmem + r * NT, a_base + sa * 64 + j * 8, bdesc, idesc, (kk | j) != 0);
+        }
+        tc_commit(&bars->a_empty[sa]);
+        if (r == R - 1) tc_commit(&bars->x_empty[sx]);
+      }
+      tc_commit(&bars->acc_ready);
+    }
+  } else {
+    // ------------------------------------------------------------------ dequant: chunk -> fp16 -> TMEM
+    const int q = warp & 3;                  // TMEM lane quarter this warp may touch
+    const int part = (warp - 2) >> 2;        // which 32 of the 128 K values of a chunk
+    const int row = q * 32 + lane;           // weight row inside the tile
+    for (int u = 0; u < n_units; ++u) {
+      const int sw = u % SW, sa = u % SA;
+      if (!mbar_wait(&bars->w_full[sw], (u / SW) & 1, abort_flag, a.status, 5, u)) break;
+      const uint8_t* chunk = w_ring + sw * kW4ChunkBytes;
+      const uint4 pk = *reinterpret_cast<const uint4*>(chunk + (part * 128 + row) * 16);
+      const __half2 sz = *reinterpret_cast<const __half2*>(chunk + 8192 + row * 4);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->w_empty[sw]);          // the chunk is in registers: its slot may be refilled
+      if (u >= SA && !mbar_wait(&bars->a_empty[sa], ((u / SA) - 1) & 1, abort_flag, a.status, 6, u)) break;
+      tc_fence_after_sync();
+      const __half2 s2 = __half2half2(__low2half(sz)), z2 = __half2half2(__high2half(sz));
+      uint32_t o[16];
+      dequant_word(pk.x, s2, z2, o + 0);
+      dequant_word(pk.y, s2, z2, o + 4);
+      dequant_word(pk.z, s2, z2, o + 8);
+      dequant_word(pk.w, s2, z2, o + 12);
+      ZSE_TMEM_ST_X16(a_base + (uint32_t(q * 32) << 16) + sa * 64 + part * 16, o);
+      tc_wait_st();
+      tc_fence_before_sync();
+      if (lane == 0) mbar_arrive(&bars->a_ready[sa]);
+    }
+    acc_ok = mbar_wait(&bars->acc_ready, 0, abort_flag, a.status, 7, 0);
+    tc_fence_after_sync();
+  }
+
+  // ---------------------------------------------------------------------- cluster reduce + epilogue
+  // one verdict for the whole CTA, so that paired warps never disagree about taking part in the exchange barriers
+  const bool dq_role = warp >= 2 && warp < 2 + kDqWarps;
+  acc_ok = __syncthreads_and(dq_role ? int(acc_ok) : 1) != 0;
+  const bool in_cluster = a.cluster_k > 1;
+  const uint32_t crank = in_cluster ? cluster_ctarank() : 0u;
+  const bool dq = warp >= 2 && warp < 2 + kDqWarps;
+  const int q = warp & 3;
+  const int cg = (warp - 2) >> 2;                               // column group of this warp (0..3)
+  constexpr int kGroups = NT >= 64 ? 4 : (NT == 32 ? 2 : 1);
+  constexpr int kColsPerGroup = NT / kGroups;                   // >= 16
+  const bool has_cols = dq && cg < kGroups;
+  const int col0 = cg * kColsPerGroup;
+  const int row = q * 32 + lane;
+
+  if (in_cluster && crank != 0) {
+    // park the accumulators: park[(r*NT + col) * 128 + row]
+    if (has_cols && acc_ok) {
+#pragma unroll 1
+      for (int r = 0; r < R; ++r) {
+#pragma unroll 1
+        for (int c = 0; c < kColsPerGroup; c += 16) {
+          uint32_t v[16];
+          ZSE_TMEM_LD_X16(v, tmem + (uint32_t(q * 32) << 16) + r * NT + col0 + c);
+          tc_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 16; ++i) park[(r * NT + col0 + c + i) * 128 + row] = __uint_as_float(v[i]);
+        }
+      }
+    }
+    cluster_sync_all();        // parked values visible to the leader
+    cluster_sync_all();        // leader is done reading
+  } else {
+    if (in_cluster) cluster_sync_all();
+    if (has_cols && acc_ok) {
+      const int t0 = blockIdx.y * NT;
+#pragma unroll 1
+      for (int r = 0; r < R; ++r) {
+        const int n_tile = tile0 + r;
+        const int n = (EPI == kEpiSwiGLU) ? n_tile * 64 + (q & 1) * 32 + lane : n_tile * kTileN + row;
+        float bias = 0.f;
+        if (EPI == kEpiF16 && a.bias != nullptr && n < a.N) bias = __half2float(a.bias[n]);
+#pragma unroll 1
+        for (int c = 0; c < kColsPerGroup; c += 16) {
+          uint32_t raw[16];
+          ZSE_TMEM_LD_X16(raw, tmem + (uint32_t(q * 32) << 16) + r * NT + col0 + c);
+          tc_wait_ld();
+          float v[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(raw[i]);
+          if (in_cluster) {
+            for (int peer = 1; peer < a.cluster_k; ++peer) {
+#pragma unroll
+              for (int i = 0; i < 16; ++i)
+                v[i] += ld_dsmem_f32(smem_u32(park + (r * NT + col0 + c + i) * 128 + row), uint32_t(peer));
+            }
+          }
+          if (EPI == kEpiSwiGLU) {
+            // rows 64..127 (q = 2, 3) hold `up`: hand them to the warp that holds the matching `gate` rows
+            float* xch = xch_base + ((q & 1) + 2 * cg) * (32 * 16);
+            const int bar_id = 1 + (q & 1) + 2 * cg;
+            if (q >= 2) {
+#pragma unroll
+              for (int i = 0; i < 16; ++i) xch[i * 32 + lane] = v[i];
+              asm volatile("bar.sync %0, 64;" ::"r"(bar_id) : "memory");
+              asm volatile("bar.sync %0, 64;" ::"r"(bar_id) : "memory");
+            } else {
+              asm volatile("bar.sync %0, 64;" ::"r"(bar_id) : "memory");
+              __half* out = reinterpret_cast<__half*>(a.out);
+#pragma unroll
+              for (int i = 0; i < 16; ++i) {
+                const int t = t0 + col0 + c + i;
+                if (t < a.M && n < a.N / 2)
+                  out[size_t(t) * a.ldo + n] = __float2half_rn(clamp_f16(silu_f(v[i]) * xch[i * 32 + lane]));
+              }
+              asm volatile("bar.sync %0, 64;" ::"r"(bar_id) : "memory");
+            }
+          } else {
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              const int t = t0 + col0 + c + i;
+              if (t < a.M && n < a.N) {
+                if (EPI == kEpiF16)
+                  reinterpret_cast<__half*>(a.out)[size_t(t) * a.ldo + n] = __float2half_rn(clamp_f16(v[i] + bias));
+                else
+                  reinterpret_cast<float*>(a.out)[size_t(t) * a.ldo + n] = v[i];
+              }
+            }
+          }
+        }
+      }
+    }
+    if (in_cluster) cluster_sync_all();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem, 512);
+}
+
+template <int NT, int R, int EPI>
+static int launch_w4(const CUtensorMap& tx, const W4Args& a, dim3 grid, cudaStream_t st) {
+  auto kern = gemm_w4_kernel<NT, R, EPI>;
+  using Cfg = W4Cfg<NT, R>;
+  constexpr int smem = Cfg::kSmemBytes;
+  static bool attr_done = false;
+  if (!attr_done) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+      return ZSE_ERR_LAUNCH;
+    attr_done = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(kW4Threads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = grid.z;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, tx, a) == cudaSuccess ? 0 : ZSE_ERR_LAUNCH;
+}
+
+template <int NT, int R>
+static int launch_w4_epi(int epilogue, const CUtensorMap& tx, const W4Args& a, dim3 grid, cudaStream_t st) {
+  if (epilogue == kEpiF16) return launch_w4<NT, R, kEpiF16>(tx, a, grid, st);
+  if (epilogue == kEpiSwiGLU) return launch_w4<NT, R, kEpiSwiGLU>(tx, a, grid, st);
+  if (epilogue == kEpiPartialF32) return launch_w4<NT, R, kEpiPartialF32>(tx, a, grid, st);
+  return ZSE_ERR_SHAPE;
+}
+
+// How the launcher tiles a problem: weight tiles per CTA (R) and CTAs per K cluster.
+static void plan_w4(int M, int N, int K, int epilogue, int sm_count, int want_split, int* R_out, int* ks_out) {
+  const int nt = pick_nt(M);
+  const int n_tiles = epilogue == kEpiSwiGLU ? (N / 2 + 63) / 64 : (N + kTileN - 1) / kTileN;
+  const int m_tiles = (M + nt - 1) / nt;
+  const int k_stages = K / kW4StageK;
+  int R = (nt <= 128 && n_tiles % 2 == 0) ? 2 : 1;
+  // with very few tiles, single-tile CTAs give the scheduler more to spread
+  if (R == 2 && (n_tiles / 2) * m_tiles * min(8, k_stages) < sm_count) R = 1;
+  const int ctas = (n_tiles / R) * m_tiles;
+  int best = 1;
+  if (want_split <= 0) {
+    long best_cost = -1;
+    for (int ks = 1; ks <= min(8, k_stages); ++ks) {
+      const long waves = (long(ctas) * ks + sm_count - 1) / sm_count;
+      const long cost = waves * (((k_stages + ks - 1) / ks) * R + 4);     // chunk times incl. fixed per-CTA cost
+      if (best_cost < 0 || cost < best_cost) {
+        best_cost = cost;
+        best = ks;
+      }
+    }
+  } else {
+    best = max(1, min(want_split, min(8, k_stages)));
+  }
+  *R_out = R;
+  *ks_out = best;
+}
+
+}  // namespace zse
+
+using namespace zse;
+
+extern "C" int zse_gemm_w4(const void* w_tiled, const void* x, int x_rows_cap, const void* bias, void* out, int M,
+                           int N, int K, int ldo, int epilogue, int k_split, void* status, void* stream) {
+  if (M <= 0) return 0;
+  if (K % kW4StageK != 0 || N <= 0 || K <= 0) return ZSE_ERR_SHAPE;
+  static int sm_count = 0;
+  if (sm_count == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+    if (sm_count <= 0) sm_count = 148;
+  }
+  const int k_stages = K / kW4StageK;
+  int R = 1, ks = 1;
+  plan_w4(M, N, K, epilogue, sm_count, k_split, &R, &ks);
+  const int spp = (k_stages + ks - 1) / ks;
+  ks = (k_stages + spp - 1) / spp;                     // no empty CTA in a cluster
+  const int nt = pick_nt(M);
+  const int n_tiles = epilogue == kEpiSwiGLU ? (N / 2 + 63) / 64 : (N + kTileN - 1) / kTileN;
+  CUtensorMap tx;
+  if (int rc = get_tmap(x, uint64_t(max(x_rows_cap, M)), uint64_t(K), uint32_t(nt), &tx)) return rc;
+  W4Args a{reinterpret_cast<const uint8_t*>(w_tiled), reinterpret_cast<const __half*>(bias), out, M, N, K, ldo,
+           k_stages, spp, ks, reinterpret_cast<Status*>(status)};
+  dim3 grid(n_tiles / R, (M + nt - 1) / nt, ks);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  int rc = ZSE_ERR_SHAPE;
+  if (R == 2) {
+    switch (nt) {
+      case 16: rc = launch_w4_epi<16, 2>(epilogue, tx, a, grid, st); break;
+      case 32: rc = launch_w4_epi<32, 2>(epilogue, tx, a, grid, st); break;
+      case 64: rc = launch_w4_epi<64, 2>(epilogue, tx, a, grid, st); break;
+      default: rc = launch_w4_epi<128, 2>(epilogue, tx, a, grid, st); break;
+    }
+  } else {
+    ZSE_DISPATCH_NT(nt, rc = (launch_w4_epi<NT, 1>(epilogue, tx, a, grid, st)))
+  }
+  return rc;
+}
+
+// Kept for callers that size a plane buffer: the INT4 kernel reduces its K splits on chip and writes one plane.
+extern "C" int zse_gemm_w4_splits(int M, int N, int K, int k_split) {
+  (void)M; (void)N; (void)K; (void)k_split;
+  return 1;
+}

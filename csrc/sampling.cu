@@ -45,12 +45,25 @@ __device__ __forceinline__ unsigned long long block_max_u64(unsigned long long v
   return r;
 }
 
-// (key, lowest index) of the row maximum
+// (key, lowest index) of the row maximum; 16-byte loads when the row is 16-byte aligned
 __device__ __forceinline__ unsigned long long row_argmax(const __half* row, int V, unsigned long long* red) {
   unsigned long long best = 0ull;
-  for (int i = threadIdx.x; i < V; i += blockDim.x) {
-    const unsigned long long cand = ((unsigned long long)key_of(row[i]) << 32) | (0xFFFFFFFFu - (unsigned)i);
+  auto consider = [&](__half h, int i) {
+    const unsigned long long cand = ((unsigned long long)key_of(h) << 32) | (0xFFFFFFFFu - (unsigned)i);
     best = cand > best ? cand : best;
+  };
+  if ((reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+    const int nvec = V / 8;
+    const uint4* rv = reinterpret_cast<const uint4*>(row);
+    for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+      const uint4 v = rv[i];
+      const __half* h = reinterpret_cast<const __half*>(&v);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) consider(h[j], i * 8 + j);
+    }
+    for (int i = nvec * 8 + threadIdx.x; i < V; i += blockDim.x) consider(row[i], i);
+  } else {
+    for (int i = threadIdx.x; i < V; i += blockDim.x) consider(row[i], i);
   }
   return block_max_u64(best, red);
 }

@@ -33,6 +33,8 @@ class LinearWeight:
 def _np_to_dev(a: np.ndarray, device) -> torch.Tensor:
     """Host array -> tensor on ``device``.  Arrays that view a read-only file mapping are copied on the CPU path so
     the tensor never aliases the mapping."""
+    if isinstance(a, torch.Tensor):
+        return a.to(device)
     a = np.ascontiguousarray(a)
     if torch.device(device).type == "cpu" or not a.flags.writeable:
         a = np.array(a, copy=True)
@@ -190,14 +192,14 @@ class CudaOps(TorchOps):
     def linear(self, w, x, M, out, x_cap=None):
         cap = x.shape[0] if x_cap is None else x_cap
         if w.kind == "w4t":
-            self.n.gemm_w4(w.data, x, cap, w.bias, out, M, w.N, w.K, out.stride(0), EPI_F16, 1, self.status.ptr)
+            self.n.gemm_w4(w.data, x, cap, w.bias, out, M, w.N, w.K, out.stride(0), EPI_F16, 0, self.status.ptr)
         else:
             self.n.gemm_f16(w.data, w.N, x, cap, w.bias, out, M, w.N, w.K, out.stride(0), EPI_F16, 1, self.status.ptr)
 
     def linear_swiglu(self, w, x, M, out, x_cap=None, gelu=False, tmp=None):
         cap = x.shape[0] if x_cap is None else x_cap
         if w.kind == "w4t" and not gelu:
-            self.n.gemm_w4(w.data, x, cap, None, out, M, w.N, w.K, out.stride(0), EPI_SWIGLU, 1, self.status.ptr)
+            self.n.gemm_w4(w.data, x, cap, None, out, M, w.N, w.K, out.stride(0), EPI_SWIGLU, 0, self.status.ptr)
         else:
             if w.kind == "w4t":
                 raise NotImplementedError("GeGLU needs the dense path")
@@ -206,26 +208,26 @@ class CudaOps(TorchOps):
             self.n.swiglu(gu, out, M, w.N // 2, gelu)
 
     def pick_k_split(self, w, M) -> int:
+        """fp16 kernel only (the INT4 kernel plans its own on-chip split): planes so that the grid fills the GPU."""
         n_tiles = (w.N + 127) // 128
         nt = 16 if M <= 16 else 32 if M <= 32 else 64 if M <= 64 else 128 if M <= 128 else 256
         ctas = n_tiles * ((M + nt - 1) // nt)
-        per_sm = 2 if nt <= 64 else 1
-        want = max(1, (self.sm_count * per_sm) // max(1, ctas))
-        stage_k = 128 if w.kind == "w4t" else 64
-        return max(1, min(want, 8, (w.K // stage_k) // 4 or 1))
+        want = max(1, (self.sm_count * (2 if nt <= 64 else 1)) // max(1, ctas))
+        return max(1, min(want, 8, (w.K // 64) // 4 or 1))
 
     def linear_partial(self, w, x, M, partials, k_split=None, x_cap=None) -> int:
+        """fp32 result planes in ``partials`` [planes, M, N]; returns how many planes were written (the INT4 kernel
+        reduces its K split on chip and always writes one)."""
         cap = x.shape[0] if x_cap is None else x_cap
+        if w.kind == "w4t":
+            self.n.gemm_w4(w.data, x, cap, None, partials, M, w.N, w.K, partials.stride(1), EPI_PARTIAL,
+                           0 if k_split is None else k_split, self.status.ptr)
+            return 1
         ks = self.pick_k_split(w, M) if k_split is None else k_split
         ks = min(ks, partials.shape[0])
-        if w.kind == "w4t":
-            planes = self.n.gemm_w4_splits(M, w.N, w.K, ks)
-            self.n.gemm_w4(w.data, x, cap, None, partials, M, w.N, w.K, partials.stride(1), EPI_PARTIAL, ks,
-                           self.status.ptr)
-        else:
-            planes = self.n.gemm_f16_splits(M, w.N, w.K, ks)
-            self.n.gemm_f16(w.data, w.N, x, cap, None, partials, M, w.N, w.K, partials.stride(1), EPI_PARTIAL, ks,
-                            self.status.ptr)
+        planes = self.n.gemm_f16_splits(M, w.N, w.K, ks)
+        self.n.gemm_f16(w.data, w.N, x, cap, None, partials, M, w.N, w.K, partials.stride(1), EPI_PARTIAL, ks,
+                        self.status.ptr)
         return planes
 
     def embedding(self, table, ids, out, M, scale=1.0):
