@@ -252,96 +252,98 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4Args a) {
   // one verdict for the whole CTA, so that paired warps never disagree about taking part in the exchange barriers
   const bool dq_role = warp >= 2 && warp < 2 + kDqWarps;
   acc_ok = __syncthreads_and(dq_role ? int(acc_ok) : 1) != 0;
-  const bool in_cluster = a.cluster_k > 1;
+  const int ks = a.cluster_k;
+  const bool in_cluster = ks > 1;
   const uint32_t crank = in_cluster ? cluster_ctarank() : 0u;
-  const bool dq = warp >= 2 && warp < 2 + kDqWarps;
-  const int q = warp & 3;
-  const int cg = (warp - 2) >> 2;                               // column group of this warp (0..3)
-  constexpr int kGroups = NT >= 64 ? 4 : (NT == 32 ? 2 : 1);
-  constexpr int kColsPerGroup = NT / kGroups;                   // >= 16
-  const bool has_cols = dq && cg < kGroups;
-  const int col0 = cg * kColsPerGroup;
+  const int q = warp & 3;                                       // TMEM lane quarter / row quarter
+  const int cgw = (warp - 2) >> 2;                              // 0..3: which chunks of the CTA this warp takes
   const int row = q * 32 + lane;
+  constexpr int kChunks = R * (NT / 16);                        // 16-column chunks of the CTA's accumulators
 
-  if (in_cluster && crank != 0) {
-    // park the accumulators: park[(r*NT + col) * 128 + row]
-    if (has_cols && acc_ok) {
+  if (in_cluster) {
+    // every CTA parks its accumulators: park[(chunk*16 + i) * 128 + row]; chunk = r * (NT/16) + column group
+    if (dq_role && acc_ok) {
 #pragma unroll 1
-      for (int r = 0; r < R; ++r) {
-#pragma unroll 1
-        for (int c = 0; c < kColsPerGroup; c += 16) {
-          uint32_t v[16];
-          ZSE_TMEM_LD_X16(v, tmem + (uint32_t(q * 32) << 16) + r * NT + col0 + c);
-          tc_wait_ld();
+      for (int ch = cgw; ch < kChunks; ch += 4) {
+        uint32_t v[16];
+        ZSE_TMEM_LD_X16(v, tmem + (uint32_t(q * 32) << 16) + ch * 16);
+        tc_wait_ld();
 #pragma unroll
-          for (int i = 0; i < 16; ++i) park[(r * NT + col0 + c + i) * 128 + row] = __uint_as_float(v[i]);
-        }
+        for (int i = 0; i < 16; ++i) park[(ch * 16 + i) * 128 + row] = __uint_as_float(v[i]);
       }
     }
-    cluster_sync_all();        // parked values visible to the leader
-    cluster_sync_all();        // leader is done reading
-  } else {
-    if (in_cluster) cluster_sync_all();
-    if (has_cols && acc_ok) {
-      const int t0 = blockIdx.y * NT;
+    cluster_sync_all();
+  }
+  if (dq_role && acc_ok) {
+    const int t0 = blockIdx.y * NT;
+    // chunk ch belongs to the CTA with rank ch % ks; inside the CTA the four warp groups take its chunks in turn
+    int mine = 0;
 #pragma unroll 1
-      for (int r = 0; r < R; ++r) {
-        const int n_tile = tile0 + r;
-        const int n = (EPI == kEpiSwiGLU) ? n_tile * 64 + (q & 1) * 32 + lane : n_tile * kTileN + row;
+    for (int ch = int(crank); ch < kChunks; ch += ks, ++mine) {
+      if ((mine & 3) != cgw) continue;
+      const int r = ch / (NT / 16), c0 = (ch % (NT / 16)) * 16;
+      float v[16];
+      if (in_cluster) {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v[i] = 0.f;
+        const uint32_t base = smem_u32(park + (ch * 16) * 128 + row);
+        for (int peer = 0; peer < ks; ++peer) {                 // fixed order: the sum is reproducible
+          float tmp[16];
+          uint32_t remote;
+          asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(base), "r"(peer));
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(tmp[i]) : "r"(remote + i * 512));
+#pragma unroll
+          for (int i = 0; i < 16; ++i) v[i] += tmp[i];
+        }
+      } else {
+        uint32_t raw[16];
+        ZSE_TMEM_LD_X16(raw, tmem + (uint32_t(q * 32) << 16) + ch * 16);
+        tc_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(raw[i]);
+      }
+      const int n_tile = tile0 + r;
+      if (EPI == kEpiSwiGLU) {
+        // rows 64..127 (q = 2, 3) hold `up`: hand them to the warp that holds the matching `gate` rows
+        float* xch = xch_base + ((q & 1) + 2 * cgw) * (32 * 16);
+        const int bar_id = 1 + (q & 1) + 2 * cgw;
+        const int n = n_tile * 64 + (q & 1) * 32 + lane;
+        if (q >= 2) {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) xch[i * 32 + lane] = v[i];
+          asm volatile("bar.sync %0, 64;" ::"r"(bar_id) : "memory");
+          asm volatile("bar.sync %0, 64;" ::"r"(bar_id) : "memory");
+        } else {
+          asm volatile("bar.sync %0, 64;" ::"r"(bar_id) : "memory");
+          __half* out = reinterpret_cast<__half*>(a.out);
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const int t = t0 + c0 + i;
+            if (t < a.M && n < a.N / 2)
+              out[size_t(t) * a.ldo + n] = __float2half_rn(clamp_f16(silu_f(v[i]) * xch[i * 32 + lane]));
+          }
+          asm volatile("bar.sync %0, 64;" ::"r"(bar_id) : "memory");
+        }
+      } else {
+        const int n = n_tile * kTileN + row;
         float bias = 0.f;
         if (EPI == kEpiF16 && a.bias != nullptr && n < a.N) bias = __half2float(a.bias[n]);
-#pragma unroll 1
-        for (int c = 0; c < kColsPerGroup; c += 16) {
-          uint32_t raw[16];
-          ZSE_TMEM_LD_X16(raw, tmem + (uint32_t(q * 32) << 16) + r * NT + col0 + c);
-          tc_wait_ld();
-          float v[16];
 #pragma unroll
-          for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(raw[i]);
-          if (in_cluster) {
-            for (int peer = 1; peer < a.cluster_k; ++peer) {
-#pragma unroll
-              for (int i = 0; i < 16; ++i)
-                v[i] += ld_dsmem_f32(smem_u32(park + (r * NT + col0 + c + i) * 128 + row), uint32_t(peer));
-            }
-          }
-          if (EPI == kEpiSwiGLU) {
-            // rows 64..127 (q = 2, 3) hold `up`: hand them to the warp that holds the matching `gate` rows
-            float* xch = xch_base + ((q & 1) + 2 * cg) * (32 * 16);
-            const int bar_id = 1 + (q & 1) + 2 * cg;
-            if (q >= 2) {
-#pragma unroll
-              for (int i = 0; i < 16; ++i) xch[i * 32 + lane] = v[i];
-              asm volatile("bar.sync %0, 64;" ::"r"(bar_id) : "memory");
-              asm volatile("bar.sync %0, 64;" ::"r"(bar_id) : "memory");
-            } else {
-              asm volatile("bar.sync %0, 64;" ::"r"(bar_id) : "memory");
-              __half* out = reinterpret_cast<__half*>(a.out);
-#pragma unroll
-              for (int i = 0; i < 16; ++i) {
-                const int t = t0 + col0 + c + i;
-                if (t < a.M && n < a.N / 2)
-                  out[size_t(t) * a.ldo + n] = __float2half_rn(clamp_f16(silu_f(v[i]) * xch[i * 32 + lane]));
-              }
-              asm volatile("bar.sync %0, 64;" ::"r"(bar_id) : "memory");
-            }
-          } else {
-#pragma unroll
-            for (int i = 0; i < 16; ++i) {
-              const int t = t0 + col0 + c + i;
-              if (t < a.M && n < a.N) {
-                if (EPI == kEpiF16)
-                  reinterpret_cast<__half*>(a.out)[size_t(t) * a.ldo + n] = __float2half_rn(clamp_f16(v[i] + bias));
-                else
-                  reinterpret_cast<float*>(a.out)[size_t(t) * a.ldo + n] = v[i];
-              }
-            }
+        for (int i = 0; i < 16; ++i) {
+          const int t = t0 + c0 + i;
+          if (t < a.M && n < a.N) {
+            if (EPI == kEpiF16)
+              reinterpret_cast<__half*>(a.out)[size_t(t) * a.ldo + n] = __float2half_rn(clamp_f16(v[i] + bias));
+            else
+              reinterpret_cast<float*>(a.out)[size_t(t) * a.ldo + n] = v[i];
           }
         }
       }
     }
-    if (in_cluster) cluster_sync_all();
   }
+  if (in_cluster) cluster_sync_all();          // nobody leaves while its parked values may still be read
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem, 512);
@@ -381,32 +383,39 @@ static int launch_w4_epi(int epilogue, const CUtensorMap& tx, const W4Args& a, d
   return ZSE_ERR_SHAPE;
 }
 
-// How the launcher tiles a problem: weight tiles per CTA (R) and CTAs per K cluster.
+// How the launcher tiles a problem: weight tiles per CTA (R) and CTAs per K cluster (ks).  The model counts time in
+// "chunk times" (one 8704-byte weight chunk at this SM's share of HBM bandwidth): a K stage costs R chunks plus the
+// activation tile every CTA re-reads from L2, a CTA has a fixed start/epilogue cost, and a cluster of ks CTAs must fit
+// into one GPC, which limits how many CTAs run at the same time.
 static void plan_w4(int M, int N, int K, int epilogue, int sm_count, int want_split, int* R_out, int* ks_out) {
   const int nt = pick_nt(M);
   const int n_tiles = epilogue == kEpiSwiGLU ? (N / 2 + 63) / 64 : (N + kTileN - 1) / kTileN;
   const int m_tiles = (M + nt - 1) / nt;
   const int k_stages = K / kW4StageK;
-  int R = (nt <= 128 && n_tiles % 2 == 0) ? 2 : 1;
-  // with very few tiles, single-tile CTAs give the scheduler more to spread
-  if (R == 2 && (n_tiles / 2) * m_tiles * min(8, k_stages) < sm_count) R = 1;
-  const int ctas = (n_tiles / R) * m_tiles;
-  int best = 1;
-  if (want_split <= 0) {
-    long best_cost = -1;
+  const int gpc_sms = max(1, sm_count / 8);
+  double best_cost = -1.0;
+  int best_r = 1, best_ks = 1;
+  for (int R = 1; R <= 4; ++R) {
+    if (n_tiles % R != 0) continue;
+    if (R > 1 && (R * nt > 256)) continue;                      // accumulators + A ring must fit 512 TMEM columns
+    const long ctas = long(n_tiles / R) * m_tiles;
     for (int ks = 1; ks <= min(8, k_stages); ++ks) {
-      const long waves = (long(ctas) * ks + sm_count - 1) / sm_count;
-      const long cost = waves * (((k_stages + ks - 1) / ks) * R + 4);     // chunk times incl. fixed per-CTA cost
-      if (best_cost < 0 || cost < best_cost) {
+      if (want_split > 0 && ks != min(want_split, min(8, k_stages))) continue;
+      const long conc = ks == 1 ? sm_count : min(long(sm_count), long(8) * (gpc_sms / ks) * ks);
+      if (conc <= 0) continue;
+      const long waves = (ctas * ks + conc - 1) / conc;
+      const double stage = double(R) + 0.5 * double(nt) / 64.0;
+      const double fixed = 5.0 + (ks > 1 ? 3.0 : 0.0);
+      const double cost = double(waves) * (double((k_stages + ks - 1) / ks) * stage + fixed);
+      if (best_cost < 0 || cost < best_cost - 1e-9 || (cost < best_cost + 1e-9 && R > best_r)) {
         best_cost = cost;
-        best = ks;
+        best_r = R;
+        best_ks = ks;
       }
     }
-  } else {
-    best = max(1, min(want_split, min(8, k_stages)));
   }
-  *R_out = R;
-  *ks_out = best;
+  *R_out = best_r;
+  *ks_out = best_ks;
 }
 
 }  // namespace zse
@@ -438,15 +447,27 @@ extern "C" int zse_gemm_w4(const void* w_tiled, const void* x, int x_rows_cap, c
   dim3 grid(n_tiles / R, (M + nt - 1) / nt, ks);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   int rc = ZSE_ERR_SHAPE;
-  if (R == 2) {
+  if (R == 1) {
+    ZSE_DISPATCH_NT(nt, rc = (launch_w4_epi<NT, 1>(epilogue, tx, a, grid, st)))
+  } else if (R == 2) {
     switch (nt) {
       case 16: rc = launch_w4_epi<16, 2>(epilogue, tx, a, grid, st); break;
       case 32: rc = launch_w4_epi<32, 2>(epilogue, tx, a, grid, st); break;
       case 64: rc = launch_w4_epi<64, 2>(epilogue, tx, a, grid, st); break;
       default: rc = launch_w4_epi<128, 2>(epilogue, tx, a, grid, st); break;
     }
+  } else if (R == 3) {
+    switch (nt) {
+      case 16: rc = launch_w4_epi<16, 3>(epilogue, tx, a, grid, st); break;
+      case 32: rc = launch_w4_epi<32, 3>(epilogue, tx, a, grid, st); break;
+      default: rc = launch_w4_epi<64, 3>(epilogue, tx, a, grid, st); break;
+    }
   } else {
-    ZSE_DISPATCH_NT(nt, rc = (launch_w4_epi<NT, 1>(epilogue, tx, a, grid, st)))
+    switch (nt) {
+      case 16: rc = launch_w4_epi<16, 4>(epilogue, tx, a, grid, st); break;
+      case 32: rc = launch_w4_epi<32, 4>(epilogue, tx, a, grid, st); break;
+      default: rc = launch_w4_epi<64, 4>(epilogue, tx, a, grid, st); break;
+    }
   }
   return rc;
 }

@@ -1,0 +1,124 @@
+"""Per-kernel microbenchmarks with roofline fractions:  ``python -m zse_b200.runtime.microbench --shape qwen2.5-14b
+--tokens 64``.
+
+Times the kernels of one decoder layer (plus lm_head and token selection) at the given decode batch, cold-cache, with
+CUDA events, and prints achieved GB/s (algorithmic bytes / time) against the measured copy bandwidth."""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+
+import torch
+
+from ..format import synth
+from ..ops import native
+from ..ops.backend import CudaOps
+from ..ops import reference as ref
+from .profiler import KernelProfiler, measured_peaks
+
+
+def _w4(ops, N, K, swiglu=False, seed=0):
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    parts = []
+    for i in range(2 if swiglu else 1):
+        packed = torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, device="cuda", generator=g)
+        sc = torch.full((N, K // 128), 0.008, dtype=torch.float16, device="cuda")
+        zr = torch.full((N, K // 128), -0.06, dtype=torch.float16, device="cuda")
+        parts.append({"dtype": "int4", "data": packed, "scales": sc, "zeros": zr, "shape": (N, K)})
+    return ops.make_linear(parts, K, 128, swiglu=swiglu)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--shape", default="qwen2.5-14b")
+    ap.add_argument("--tokens", type=int, default=64)
+    ap.add_argument("--ctx", type=int, default=1216, help="cached tokens per sequence for the attention kernel")
+    ap.add_argument("--tp", type=int, default=1)
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--only", default="", help="comma separated kernel names")
+    ap.add_argument("--json", default="")
+    a = ap.parse_args()
+    c = synth.shape_config(a.shape)
+    ops = CudaOps("cuda")
+    prof = KernelProfiler(iters=a.iters)
+    peaks = measured_peaks()
+    M, H, tp = a.tokens, c.hidden_size, a.tp
+    nh, nkv, hd = c.num_heads // tp, c.num_kv_heads // tp, c.head_dim
+    q_dim, kv_dim, I = nh * hd, nkv * hd, c.intermediate_size // tp
+    only = set(x for x in a.only.split(",") if x)
+    rows = []
+    x = (torch.randn(M, H, device="cuda") * 0.5).half()
+    w4_bytes = lambda N, K: N * K // 2 + N * (K // 128) * 4
+
+    def run(name, fn, nbytes, flops=0):
+        if only and name not in only:
+            return
+        r = prof.time(name, fn, nbytes, flops)
+        rows.append(r.row(peaks))
+        ops.check()
+
+    # linear layers
+    wqkv = _w4(ops, q_dim + 2 * kv_dim, H)
+    qkv = torch.zeros(M, q_dim + 2 * kv_dim, dtype=torch.float16, device="cuda")
+    run("qkv_gemm", lambda: ops.linear(wqkv, x, M, qkv), w4_bytes(q_dim + 2 * kv_dim, H) + M * H * 2,
+        2 * M * H * (q_dim + 2 * kv_dim))
+    wo = _w4(ops, H, q_dim)
+    xa = (torch.randn(M, q_dim, device="cuda") * 0.5).half()
+    planes = torch.zeros(8, M, H, dtype=torch.float32, device="cuda")
+    run("o_gemm", lambda: ops.linear_partial(wo, xa, M, planes), w4_bytes(H, q_dim) + M * q_dim * 2, 2 * M * H * q_dim)
+    wgu = _w4(ops, I, H, swiglu=True)
+    act = torch.zeros(M, I, dtype=torch.float16, device="cuda")
+    run("gate_up_gemm", lambda: ops.linear_swiglu(wgu, x, M, act), 2 * w4_bytes(I, H) + M * H * 2, 4 * M * H * I)
+    wd = _w4(ops, H, I)
+    xi = (torch.randn(M, I, device="cuda") * 0.5).half()
+    run("down_gemm", lambda: ops.linear_partial(wd, xi, M, planes), w4_bytes(H, I) + M * I * 2, 2 * M * H * I)
+    # norms
+    resid = torch.randn(M, H, device="cuda")
+    wn = torch.ones(H, dtype=torch.float16, device="cuda")
+    xn = torch.zeros(M, H, dtype=torch.float16, device="cuda")
+    run("add_rmsnorm", lambda: ops.add_rmsnorm(resid, planes, 1, None, wn, xn, M, 1e-6), M * H * (4 + 4 + 4 + 2))
+    # attention over a paged cache
+    bs = 16
+    nblk = (a.ctx + bs - 1) // bs
+    kv = (torch.randn(M * nblk + 1, 2, nkv, bs, hd, device="cuda") * 0.3).half()
+    bt = torch.randperm(M * nblk, device="cuda").int().view(M, nblk).contiguous()
+    lens = torch.full((M,), a.ctx, dtype=torch.int32, device="cuda")
+    ao = torch.zeros(M, q_dim, dtype=torch.float16, device="cuda")
+    for splits in (1, 2, 4):
+        scratch = torch.zeros(M * nh * splits * (hd + 2), device="cuda")
+        run(f"attn_decode_s{splits}",
+            lambda s=splits, sc=scratch: ops.attn_decode(qkv, kv, bt, lens, ao, M, nh, nkv, hd, bs, 1 / math.sqrt(hd),
+                                                          sc, s),
+            M * a.ctx * nkv * hd * 2 * 2)
+    pos = torch.full((M,), a.ctx - 1, dtype=torch.int32, device="cuda")
+    slots = (bt[:, -1].long() * bs + (a.ctx - 1) % bs).contiguous()
+    inv = ref.inv_freq(hd, c.rope_theta).cuda()
+    run("rope_kv_write", lambda: ops.rope_kv_write(qkv, kv, pos, slots, inv, M, nh, nkv, hd, bs),
+        M * (q_dim + 2 * kv_dim) * 2 * 2)
+    # lm_head + selection
+    V = c.vocab_size // tp
+    wl = ops.make_linear([{"dtype": "float16", "data": (torch.randn(V, H, device="cuda") * 0.02).half(),
+                           "shape": (V, H)}], H, 128)
+    logits = torch.zeros(M, V, dtype=torch.float16, device="cuda")
+    run("lm_head_gemm", lambda: ops.linear(wl, x, M, logits), V * H * 2 + M * V * 2, 2 * M * V * H)
+    out = torch.zeros(M, dtype=torch.int32, device="cuda")
+    run("argmax", lambda: ops.argmax(logits, out, M), M * V * 2)
+    temp = torch.full((M,), 0.8, device="cuda")
+    tk = torch.full((M,), 50, dtype=torch.int32, device="cuda")
+    tpp = torch.full((M,), 0.9, device="cuda")
+    seeds = torch.arange(M, dtype=torch.int64, device="cuda")
+    run("sample_topk_topp", lambda: ops.sample(logits, out, M, temp, tk, tpp, seeds, 1), M * V * 2 * 6)
+    hdr = f"{'kernel':22s} {'us':>9s} {'GB/s':>9s} {'of HBM':>7s} {'TFLOP/s':>9s} {'of tensor':>9s}"
+    print(f"shape {a.shape}, tokens {M}, tp {tp}, peaks {peaks}")
+    print(hdr)
+    for r in rows:
+        print(f"{r['name']:22s} {r['us']:9.1f} {r['GB/s']:9.1f} {str(r['frac_hbm']):>7s} {r['TFLOP/s']:9.2f} "
+              f"{str(r['frac_tensor']):>9s}")
+    if a.json:
+        with open(a.json, "w") as f:
+            json.dump({"shape": a.shape, "tokens": M, "tp": tp, "peaks": peaks, "rows": rows}, f, indent=1)
+
+
+if __name__ == "__main__":
+    main()

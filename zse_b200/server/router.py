@@ -1,0 +1,195 @@
+"""Minimal HTTP/1.1 plumbing for the asyncio server: request parsing, responses, a router with ``{param}`` path
+segments, a middleware chain and static files with a traversal guard
+(zse-engine/zse_engine/server/router.py:13-349).  No third-party web framework."""
+from __future__ import annotations
+
+import json
+import mimetypes
+import os
+import re
+from dataclasses import dataclass, field
+from typing import Any, Awaitable, Callable, Dict, List, Optional, Tuple
+from urllib.parse import parse_qs, unquote, urlsplit
+
+STATUS_TEXT = {200: "OK", 201: "Created", 204: "No Content", 400: "Bad Request", 401: "Unauthorized",
+               403: "Forbidden", 404: "Not Found", 405: "Method Not Allowed", 413: "Payload Too Large",
+               429: "Too Many Requests", 500: "Internal Server Error", 503: "Service Unavailable",
+               504: "Gateway Timeout"}
+ERROR_TYPES = {400: "invalid_request_error", 401: "authentication_error", 403: "permission_error",
+               404: "not_found_error", 429: "rate_limit_error", 500: "server_error", 503: "overloaded_error",
+               504: "timeout_error"}
+
+
+@dataclass
+class Request:
+    method: str
+    path: str
+    headers: Dict[str, str] = field(default_factory=dict)
+    body: bytes = b""
+    query: Dict[str, str] = field(default_factory=dict)
+    params: Dict[str, str] = field(default_factory=dict)
+    context: Dict[str, Any] = field(default_factory=dict)     # filled by middleware (auth result, ...)
+
+    @property
+    def json(self) -> Optional[Any]:
+        if not self.body:
+            return None
+        try:
+            return json.loads(self.body.decode("utf-8"))
+        except (ValueError, UnicodeDecodeError):
+            return None
+
+    @property
+    def authorization(self) -> Optional[str]:
+        return self.headers.get("authorization")
+
+
+@dataclass
+class Response:
+    status: int = 200
+    body: bytes = b""
+    headers: Dict[str, str] = field(default_factory=dict)
+    stream: Optional[Any] = None          # async iterator of bytes: sent as it is produced (SSE)
+
+    @classmethod
+    def json_response(cls, obj: Any, status: int = 200) -> "Response":
+        return cls(status, json.dumps(obj).encode("utf-8"), {"Content-Type": "application/json"})
+
+    @classmethod
+    def text(cls, text: str, status: int = 200, content_type: str = "text/plain; charset=utf-8") -> "Response":
+        return cls(status, text.encode("utf-8"), {"Content-Type": content_type})
+
+    @classmethod
+    def error(cls, message: str, status: int = 400, code: Optional[str] = None) -> "Response":
+        return cls.json_response({"error": {"message": message, "type": ERROR_TYPES.get(status, "error"),
+                                            "code": code or str(status)}}, status)
+
+    @classmethod
+    def sse(cls, iterator) -> "Response":
+        return cls(200, b"", {"Content-Type": "text/event-stream", "Cache-Control": "no-cache",
+                              "Connection": "keep-alive"}, iterator)
+
+
+Handler = Callable[[Request], Awaitable[Response]]
+Middleware = Callable[[Request, Handler], Awaitable[Response]]
+
+
+class Router:
+    def __init__(self):
+        self._routes: List[Tuple[str, re.Pattern, List[str], Handler]] = []
+        self._middleware: List[Middleware] = []
+        self._static: List[Tuple[str, str]] = []
+
+    def add(self, method: str, pattern: str, handler: Handler) -> None:
+        names = re.findall(r"\{(\w+)\}", pattern)
+        rx = re.compile("^" + re.sub(r"\{\w+\}", r"([^/]+)", pattern.rstrip("/") or "/") + "/?$")
+        self._routes.append((method.upper(), rx, names, handler))
+
+    def get(self, pattern: str, handler: Handler) -> None:
+        self.add("GET", pattern, handler)
+
+    def post(self, pattern: str, handler: Handler) -> None:
+        self.add("POST", pattern, handler)
+
+    def put(self, pattern: str, handler: Handler) -> None:
+        self.add("PUT", pattern, handler)
+
+    def delete(self, pattern: str, handler: Handler) -> None:
+        self.add("DELETE", pattern, handler)
+
+    def use(self, mw: Middleware) -> None:
+        self._middleware.append(mw)
+
+    def static(self, url_prefix: str, directory: str) -> None:
+        self._static.append((url_prefix.rstrip("/") + "/", os.path.abspath(directory)))
+
+    def routes(self) -> List[Tuple[str, str]]:
+        return [(m, rx.pattern) for m, rx, _, _ in self._routes]
+
+    async def handle(self, request: Request) -> Response:
+        if request.method == "OPTIONS":
+            return Response(204, b"", cors_headers())
+        path_matched = False
+        for method, rx, names, handler in self._routes:
+            m = rx.match(request.path)
+            if not m:
+                continue
+            path_matched = True
+            if method != request.method:
+                continue
+            request.params = {n: unquote(v) for n, v in zip(names, m.groups())}
+            call = handler
+            for mw in reversed(self._middleware):
+                call = (lambda h, w: (lambda req: w(req, h)))(call, mw)
+            try:
+                return await call(request)
+            except Exception as exc:      # a handler bug must not kill the connection loop
+                return Response.error(f"internal error: {type(exc).__name__}: {exc}", 500)
+        if path_matched:
+            return Response.error(f"method {request.method} not allowed for {request.path}", 405)
+        if request.method == "GET":
+            static = self._serve_static(request.path)
+            if static is not None:
+                return static
+        return Response.error(f"no route for {request.method} {request.path}", 404)
+
+    def _serve_static(self, path: str) -> Optional[Response]:
+        for prefix, root in self._static:
+            if path == prefix.rstrip("/") or path == prefix:
+                rel = "index.html"
+            elif path.startswith(prefix):
+                rel = path[len(prefix):]
+            else:
+                continue
+            full = os.path.abspath(os.path.join(root, unquote(rel)))
+            if not (full == root or full.startswith(root + os.sep)):
+                return Response.error("forbidden", 403)
+            if os.path.isfile(full):
+                ctype = mimetypes.guess_type(full)[0] or "application/octet-stream"
+                with open(full, "rb") as f:
+                    return Response(200, f.read(), {"Content-Type": ctype})
+        return None
+
+
+def cors_headers() -> Dict[str, str]:
+    return {"Access-Control-Allow-Origin": "*", "Access-Control-Allow-Methods": "GET, POST, PUT, DELETE, OPTIONS",
+            "Access-Control-Allow-Headers": "Content-Type, Authorization", "Access-Control-Max-Age": "86400"}
+
+
+MAX_REQUEST_BYTES = 1 << 20
+
+
+def parse_http_request(raw: bytes) -> Optional[Request]:
+    """Parses a complete request (head + body) from ``raw``; ``None`` if the head is malformed."""
+    head, sep, body = raw.partition(b"\r\n\r\n")
+    if not sep:
+        return None
+    lines = head.decode("latin-1").split("\r\n")
+    parts = lines[0].split(" ")
+    if len(parts) < 2:
+        return None
+    method, target = parts[0].upper(), parts[1]
+    headers = {}
+    for line in lines[1:]:
+        k, s, v = line.partition(":")
+        if s:
+            headers[k.strip().lower()] = v.strip()
+    url = urlsplit(target)
+    query = {k: v[-1] for k, v in parse_qs(url.query).items()}
+    return Request(method, unquote(url.path) or "/", headers, body, query)
+
+
+def content_length_of(head: bytes) -> int:
+    m = re.search(rb"(?i)\r\ncontent-length:\s*(\d+)", head)
+    return int(m.group(1)) if m else 0
+
+
+def format_http_response(resp: Response, keep_alive: bool = False) -> bytes:
+    headers = dict(cors_headers())
+    headers.update(resp.headers)
+    if resp.stream is None:
+        headers["Content-Length"] = str(len(resp.body))
+    headers.setdefault("Connection", "keep-alive" if keep_alive else "close")
+    head = f"HTTP/1.1 {resp.status} {STATUS_TEXT.get(resp.status, 'Unknown')}\r\n" + \
+        "".join(f"{k}: {v}\r\n" for k, v in headers.items()) + "\r\n"
+    return head.encode("latin-1") + (resp.body if resp.stream is None else b"")
