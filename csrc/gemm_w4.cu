@@ -9,8 +9,9 @@
 //   warp 0      streams 8704-byte weight chunks (8192 B nibbles + 128 x {scale, zero}) with 1-D bulk TMA copies
 //               into a deep ring (up to 12 chunks in flight: this ring is what hides HBM latency);
 //   warp 18     streams the activation tile (tiled TMA, 128-byte swizzle) into a short ring (it comes from L2);
-//   warps 2-17  turn a chunk into fp16 in registers (lop3 nibble extraction, exact q*s+z in half2) and write it with
-//               tcgen05.st straight into TMEM;
+//   warps 2-17  turn chunks into fp16 in registers (lop3 nibble extraction, exact q*s+z in half2) and write them
+//               with tcgen05.st straight into TMEM: four groups of four warps work on four chunks at a time, a thread
+//               owning one weight row of its chunk;
 //   warp 1      issues tcgen05.mma with A from TMEM and B (activations) from shared memory; accumulators in TMEM.
 // The dequantised weights never touch shared memory.  A CTA owns R = 1 or 2 adjacent 128-row weight tiles and reuses
 // every activation stage for all of them (the activation tile is re-read from L2 by every CTA, so R halves that
@@ -65,6 +66,7 @@ struct W4Args {
   int stages_per_split;    // K stages handled by one CTA of the cluster
   int cluster_k;           // CTAs per cluster (= gridDim.z)
   Status* status;
+  long long* timing;       // debug builds (ZSE_W4_TIMING): per-role cycle counters, else unused
 };
 
 // Nibble order inside every 32-bit word of a chunk (fixed by repack_w4): positions 0..7 hold the K elements
@@ -118,6 +120,14 @@ __device__ __forceinline__ void drain(uint64_t* full, int ring, int issued) {
   }
 }
 
+#ifdef ZSE_W4_TIMING
+#define TICK(var) long long var = clock64()
+#define ACC(slot, t0) tacc[slot] += clock64() - (t0)
+#else
+#define TICK(var)
+#define ACC(slot, t0)
+#endif
+
 template <int NT, int R, int EPI>
 __global__ void __launch_bounds__(kW4Threads, 1)
 gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4Args a) {
@@ -140,14 +150,14 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4Args a) {
   if (threadIdx.x == 0) {
     for (int i = 0; i < SW; ++i) {
       mbar_init(&bars->w_full[i], 1);
-      mbar_init(&bars->w_empty[i], kDqWarps);
+      mbar_init(&bars->w_empty[i], 4);
     }
     for (int i = 0; i < SX; ++i) {
       mbar_init(&bars->x_full[i], 1);
       mbar_init(&bars->x_empty[i], 1);
     }
     for (int i = 0; i < SA; ++i) {
-      mbar_init(&bars->a_ready[i], kDqWarps);
+      mbar_init(&bars->a_ready[i], 4);
       mbar_init(&bars->a_empty[i], 1);
     }
     mbar_init(&bars->acc_ready, 1);
@@ -166,34 +176,42 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4Args a) {
   const uint32_t a_base = tmem + Cfg::kAcc;
   volatile int* abort_flag = &bars->abort_flag;
   bool acc_ok = false;
+#ifdef ZSE_W4_TIMING
+  long long tacc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  const long long t_start = clock64();
+#endif
 
   if (warp == 0) {
     // ------------------------------------------------------------------ weight producer
     if (lane == 0) {
-      int issued = 0;
+      int issued = 0, s = 0, kk = 0, r = 0;
+      uint32_t ph = 1;                                   // parity of the *previous* completion of w_empty[s]
       for (int u = 0; u < n_units; ++u) {
-        const int s = u % SW;
-        if (u >= SW && !mbar_wait(&bars->w_empty[s], ((u / SW) - 1) & 1, abort_flag, a.status, 1, u)) break;
-        const int kk = u / R, r = u - kk * R;
+        TICK(tw);
+        if (u >= SW && !mbar_wait(&bars->w_empty[s], ph, abort_flag, a.status, 1, u)) break;
+        ACC(0, tw);
         const uint8_t* src = a.w + (size_t(tile0 + r) * a.k_stages + (s_begin + kk)) * kW4ChunkBytes;
         mbar_arrive_expect_tx(&bars->w_full[s], kW4ChunkBytes);
         bulk_g2s(w_ring + s * kW4ChunkBytes, src, kW4ChunkBytes, &bars->w_full[s]);
         issued = u + 1;
+        if (++r == R) { r = 0; ++kk; }
+        if (++s == SW) { s = 0; ph ^= 1; }
       }
       if (*abort_flag) drain(bars->w_full, SW, issued);
     }
   } else if (warp == kXWarp) {
     // ------------------------------------------------------------------ activation producer
     if (lane == 0) {
-      int issued = 0;
+      int issued = 0, s = 0;
+      uint32_t ph = 1;
       for (int kk = 0; kk < n_k; ++kk) {
-        const int s = kk % SX;
-        if (kk >= SX && !mbar_wait(&bars->x_empty[s], ((kk / SX) - 1) & 1, abort_flag, a.status, 2, kk)) break;
+        if (kk >= SX && !mbar_wait(&bars->x_empty[s], ph, abort_flag, a.status, 2, kk)) break;
         mbar_arrive_expect_tx(&bars->x_full[s], Cfg::kXStage);
         const int k0 = (s_begin + kk) * kW4StageK;
         tma_load_2d(x_ring + s * Cfg::kXStage, &tmap_x, k0, blockIdx.y * NT, &bars->x_full[s]);
         tma_load_2d(x_ring + s * Cfg::kXStage + Cfg::kXBytes, &tmap_x, k0 + 64, blockIdx.y * NT, &bars->x_full[s]);
         issued = kk + 1;
+        if (++s == SX) { s = 0; ph ^= 1; }
       }
       if (*abort_flag) drain(bars->x_full, SX, issued);
     }
@@ -201,52 +219,106 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4Args a) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       constexpr uint32_t idesc = make_idesc_f16(kTileN, NT);
+      const uint64_t desc0 = make_desc_sw128(smem_u32(x_ring));
+      int sx = 0, sa = 0, r = 0, kk = 0;
+      uint32_t xph = 0, aph = 0;
       for (int u = 0; u < n_units; ++u) {
-        const int kk = u / R, r = u - kk * R;
-        const int sx = kk % SX, sa = u % SA;
-        if (r == 0 && !mbar_wait(&bars->x_full[sx], (kk / SX) & 1, abort_flag, a.status, 3, kk)) break;
-        if (!mbar_wait(&bars->a_ready[sa], (u / SA) & 1, abort_flag, a.status, 4, u)) break;
+        TICK(tx);
+        if (r == 0 && !mbar_wait(&bars->x_full[sx], xph, abort_flag, a.status, 3, kk)) break;
+        ACC(0, tx);
+        TICK(ta);
+        if (!mbar_wait(&bars->a_ready[sa], aph, abort_flag, a.status, 4, u)) break;
+        ACC(1, ta);
+        TICK(ti);
         tc_fence_after_sync();
-        const uint32_t xb = smem_u32(x_ring + sx * Cfg::kXStage);
+        // the start-address field counts 16-byte units: a K step of 16 halfs is +2, the second 64-wide sub-tile
+        // is +kXBytes/16
+        const uint64_t bd = desc0 + uint64_t((sx * Cfg::kXStage) >> 4);
+        const uint32_t at = a_base + sa * 64, dt = tmem + r * NT;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const uint64_t bdesc = make_desc_sw128(xb + (j >> 2) * Cfg::kXBytes + (j & 3) * 32);
-          umma_ts(tmem + r * NT, a_base + sa * 64 + j * 8, bdesc, idesc, (kk | j) != 0);
-        }
+        for (int j = 0; j < 8; ++j)
+          umma_ts(dt, at + j * 8, bd + uint64_t((j >> 2) * (Cfg::kXBytes >> 4) + (j & 3) * 2), idesc,
+                  (kk | j) != 0);
         tc_commit(&bars->a_empty[sa]);
-        if (r == R - 1) tc_commit(&bars->x_empty[sx]);
+        ACC(2, ti);
+        if (++sa == SA) { sa = 0; aph ^= 1; }
+        if (++r == R) {
+          tc_commit(&bars->x_empty[sx]);
+          r = 0;
+          ++kk;
+          if (++sx == SX) { sx = 0; xph ^= 1; }
+        }
       }
       tc_commit(&bars->acc_ready);
     }
   } else {
     // ------------------------------------------------------------------ dequant: chunk -> fp16 -> TMEM
+    // Four groups of four warps; group g takes the units g, g+4, g+8, ...  A thread owns one weight row of the
+    // chunk: 128 nibbles in, 64 half2 out, written as two 32-column TMEM stores.
     const int q = warp & 3;                  // TMEM lane quarter this warp may touch
-    const int part = (warp - 2) >> 2;        // which 32 of the 128 K values of a chunk
-    const int row = q * 32 + lane;           // weight row inside the tile
-    for (int u = 0; u < n_units; ++u) {
-      const int sw = u % SW, sa = u % SA;
-      if (!mbar_wait(&bars->w_full[sw], (u / SW) & 1, abort_flag, a.status, 5, u)) break;
+    const int grp = (warp - 2) >> 2;
+    const int row = q * 32 + lane;
+    const uint32_t lane_addr = uint32_t(q * 32) << 16;
+    int sw = grp % SW, sa = grp % SA;
+    uint32_t wph = 0, aph = 1;               // aph: parity of the previous completion of a_empty[sa]
+    for (int u = grp; u < n_units; u += 4) {
+      TICK(t0);
+      if (!mbar_wait(&bars->w_full[sw], wph, abort_flag, a.status, 5, u)) break;
+      ACC(0, t0);
+      TICK(t1);
       const uint8_t* chunk = w_ring + sw * kW4ChunkBytes;
-      const uint4 pk = *reinterpret_cast<const uint4*>(chunk + (part * 128 + row) * 16);
+      uint4 pk[4];
+#pragma unroll
+      for (int p4 = 0; p4 < 4; ++p4) pk[p4] = *reinterpret_cast<const uint4*>(chunk + (p4 * 128 + row) * 16);
       const __half2 sz = *reinterpret_cast<const __half2*>(chunk + 8192 + row * 4);
       __syncwarp();
       if (lane == 0) mbar_arrive(&bars->w_empty[sw]);          // the chunk is in registers: its slot may be refilled
-      if (u >= SA && !mbar_wait(&bars->a_empty[sa], ((u / SA) - 1) & 1, abort_flag, a.status, 6, u)) break;
+      ACC(1, t1);
+      TICK(t2);
+      if (u >= SA && !mbar_wait(&bars->a_empty[sa], aph, abort_flag, a.status, 6, u)) break;
+      ACC(2, t2);
+      TICK(t3);
       tc_fence_after_sync();
       const __half2 s2 = __half2half2(__low2half(sz)), z2 = __half2half2(__high2half(sz));
-      uint32_t o[16];
-      dequant_word(pk.x, s2, z2, o + 0);
-      dequant_word(pk.y, s2, z2, o + 4);
-      dequant_word(pk.z, s2, z2, o + 8);
-      dequant_word(pk.w, s2, z2, o + 12);
-      ZSE_TMEM_ST_X16(a_base + (uint32_t(q * 32) << 16) + sa * 64 + part * 16, o);
+      const uint32_t dst = a_base + lane_addr + sa * 64;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t o[32];
+#pragma unroll
+        for (int p2 = 0; p2 < 2; ++p2) {
+          const uint4 w4 = pk[half * 2 + p2];
+          dequant_word(w4.x, s2, z2, o + p2 * 16 + 0);
+          dequant_word(w4.y, s2, z2, o + p2 * 16 + 4);
+          dequant_word(w4.z, s2, z2, o + p2 * 16 + 8);
+          dequant_word(w4.w, s2, z2, o + p2 * 16 + 12);
+        }
+        ZSE_TMEM_ST_X32(dst + half * 32, o);
+      }
+      ACC(3, t3);
+      TICK(t4);
       tc_wait_st();
       tc_fence_before_sync();
       if (lane == 0) mbar_arrive(&bars->a_ready[sa]);
+      ACC(4, t4);
+      sw += 4;
+      if (sw >= SW) { sw -= SW; wph ^= 1; }
+      sa += 4;
+      if (sa >= SA) { sa -= SA; aph ^= 1; }
     }
+    TICK(t5);
     acc_ok = mbar_wait(&bars->acc_ready, 0, abort_flag, a.status, 7, 0);
     tc_fence_after_sync();
+    ACC(5, t5);
   }
+#ifdef ZSE_W4_TIMING
+  if (a.timing != nullptr && lane == 0 && blockIdx.x == 1 && blockIdx.z == 0) {
+    // role rows: 0 = weight producer, 1 = MMA issuer, 2 = activation producer, 3.. = dequant warps (first group)
+    const int role = warp == 0 ? 0 : warp == 1 ? 1 : warp == kXWarp ? 2 : 3 + (warp - 2);
+    for (int i = 0; i < 8; ++i) a.timing[role * 8 + i] = tacc[i];
+    if (warp == 1) a.timing[19 * 8] = clock64() - t_start;
+  }
+  const long long t_epi = clock64();
+#endif
 
   // ---------------------------------------------------------------------- cluster reduce + epilogue
   // one verdict for the whole CTA, so that paired warps never disagree about taking part in the exchange barriers
@@ -344,6 +416,12 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4Args a) {
     }
   }
   if (in_cluster) cluster_sync_all();          // nobody leaves while its parked values may still be read
+#ifdef ZSE_W4_TIMING
+  if (a.timing != nullptr && threadIdx.x == 64 && blockIdx.x == 1 && blockIdx.z == 0) {
+    a.timing[19 * 8 + 1] = clock64() - t_epi;
+    a.timing[19 * 8 + 2] = n_units;
+  }
+#endif
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem, 512);
@@ -422,6 +500,10 @@ static void plan_w4(int M, int N, int K, int epilogue, int sm_count, int want_sp
 
 using namespace zse;
 
+static long long* g_w4_timing = nullptr;
+// Debug hook (only meaningful in builds with ZSE_W4_TIMING): device buffer of 20 x 8 counters.
+extern "C" void zse_gemm_w4_set_timing(void* dev_buffer) { g_w4_timing = reinterpret_cast<long long*>(dev_buffer); }
+
 extern "C" int zse_gemm_w4(const void* w_tiled, const void* x, int x_rows_cap, const void* bias, void* out, int M,
                            int N, int K, int ldo, int epilogue, int k_split, void* status, void* stream) {
   if (M <= 0) return 0;
@@ -443,7 +525,7 @@ extern "C" int zse_gemm_w4(const void* w_tiled, const void* x, int x_rows_cap, c
   CUtensorMap tx;
   if (int rc = get_tmap(x, uint64_t(max(x_rows_cap, M)), uint64_t(K), uint32_t(nt), &tx)) return rc;
   W4Args a{reinterpret_cast<const uint8_t*>(w_tiled), reinterpret_cast<const __half*>(bias), out, M, N, K, ldo,
-           k_stages, spp, ks, reinterpret_cast<Status*>(status)};
+           k_stages, spp, ks, reinterpret_cast<Status*>(status), g_w4_timing};
   dim3 grid(n_tiles / R, (M + nt - 1) / nt, ks);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   int rc = ZSE_ERR_SHAPE;
