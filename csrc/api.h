@@ -45,9 +45,11 @@ int zse_rmsnorm_f16(const void* x_f16, const void* weight, void* out_f16, int M,
 // qkv fp16 [M, (nh+2nkv)*hd]; rotates q and k in place (rotate-half), writes k and v into the paged cache
 // kv_layer: [num_blocks][2][nkv][block_size][hd] fp16; slot = block*block_size + offset, -1 = skip;
 // inv_freq: fp32 [rotary_dim/2] (theta^(-2i/rotary_dim), with any rope scaling already applied by the host)
+// planes != NULL: q/k/v are read as n_planes fp32 planes [n_planes][M][(nh+2nkv)*hd] plus bias_f16 (may be NULL)
+// instead of from qkv, and qkv only receives the rotated q
 int zse_rope_kv_write(void* qkv, void* kv_layer, const void* positions_i32, const void* slots_i64,
                       const void* inv_freq_f32, int M, int nh, int nkv, int hd, int rotary_dim, int block_size,
-                      void* stream);
+                      const void* planes_f32, int n_planes, const void* bias_f16, void* stream);
 int zse_swiglu(const void* gate_up_f16, void* out_f16, int M, int I, int gelu, void* stream);
 int zse_bias_add(void* x_f16, const void* bias_f16, int M, int N, void* stream);
 

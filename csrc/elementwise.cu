@@ -113,10 +113,13 @@ rmsnorm_f16_kernel(const __half* __restrict__ x, const __half* __restrict__ weig
 
 // ---- RoPE (rotate-half, fp32 trig) on q and k in place + scatter of k, v into the paged cache ---------------
 // grid (M, nh + 2*nkv): one CTA per (token, head); hd/2 threads; q heads first, then k heads, then v heads.
+// When `planes` is given, q/k/v come as n_planes fp32 split-K planes [n_planes][M][ld] (+ fp16 bias) instead of from
+// `qkv`, which then only receives the rotated q (k and v go to the cache).
 __global__ void rope_kv_write_kernel(__half* __restrict__ qkv, __half* __restrict__ kv_layer,
                                      const int* __restrict__ positions, const long long* __restrict__ slots,
                                      const float* __restrict__ inv_freq, int nh, int nkv, int hd, int rotary_dim,
-                                     int block_size) {
+                                     int block_size, const float* __restrict__ planes, int n_planes, int M,
+                                     const __half* __restrict__ bias) {
   const int t = blockIdx.x, head = blockIdx.y;
   const int ld = (nh + 2 * nkv) * hd;
   __half* row = qkv + size_t(t) * ld + size_t(head) * hd;
@@ -132,15 +135,31 @@ __global__ void rope_kv_write_kernel(__half* __restrict__ qkv, __half* __restric
     ia = rotary_dim + 2 * (i - half_rot);
     ib = ia + 1;
   }
-  a = __half2float(row[ia]);
-  b = __half2float(row[ib]);
+  if (planes != nullptr) {
+    const size_t off = size_t(t) * ld + size_t(head) * hd;
+    a = bias != nullptr ? __half2float(bias[head * hd + ia]) : 0.f;
+    b = bias != nullptr ? __half2float(bias[head * hd + ib]) : 0.f;
+    for (int p = 0; p < n_planes; ++p) {
+      const float* src = planes + size_t(p) * M * ld + off;
+      a += src[ia];
+      b += src[ib];
+    }
+  } else {
+    a = __half2float(row[ia]);
+    b = __half2float(row[ib]);
+  }
   if (!is_v && i < half_rot) {
     float s, c;
     sincosf(float(positions[t]) * inv_freq[i], &s, &c);
     const float ra = a * c - b * s, rb = b * c + a * s;
     a = ra;
     b = rb;
-    row[ia] = __float2half_rn(a);
+  }
+  if (head < nh && (planes != nullptr || i < half_rot)) {      // q: what attention reads
+    row[ia] = __float2half_rn(clamp_f16(a));
+    row[ib] = __float2half_rn(clamp_f16(b));
+  } else if (head >= nh && planes == nullptr && !is_v && i < half_rot) {
+    row[ia] = __float2half_rn(a);                               // keep the in-place contract of the fp16 path for k
     row[ib] = __float2half_rn(b);
   }
   if (head >= nh) {
@@ -149,8 +168,8 @@ __global__ void rope_kv_write_kernel(__half* __restrict__ qkv, __half* __restric
       const int kvh = is_v ? head - nh - nkv : head - nh;
       const long long blk = slot / block_size, off = slot % block_size;
       __half* dst = kv_layer + (((blk * 2 + (is_v ? 1 : 0)) * nkv + kvh) * block_size + off) * hd;
-      dst[ia] = __float2half_rn(a);
-      dst[ib] = __float2half_rn(b);
+      dst[ia] = __float2half_rn(clamp_f16(a));
+      dst[ib] = __float2half_rn(clamp_f16(b));
     }
   }
 }
@@ -215,7 +234,7 @@ extern "C" int zse_rmsnorm_f16(const void* x, const void* weight, void* out, int
 
 extern "C" int zse_rope_kv_write(void* qkv, void* kv_layer, const void* positions, const void* slots,
                                  const void* inv_freq, int M, int nh, int nkv, int hd, int rotary_dim, int block_size,
-                                 void* stream) {
+                                 const void* planes, int n_planes, const void* bias, void* stream) {
   if (M <= 0) return 0;
   if (hd % 2 || hd > 2048 || rotary_dim % 2 || rotary_dim > hd || (hd - rotary_dim) % 2) return ZSE_ERR_SHAPE;
   dim3 grid(M, nh + 2 * nkv);
@@ -224,7 +243,9 @@ extern "C" int zse_rope_kv_write(void* qkv, void* kv_layer, const void* position
                                                         reinterpret_cast<const int*>(positions),
                                                         reinterpret_cast<const long long*>(slots),
                                                         reinterpret_cast<const float*>(inv_freq), nh, nkv, hd,
-                                                        rotary_dim, block_size);
+                                                        rotary_dim, block_size,
+                                                        reinterpret_cast<const float*>(planes), n_planes, M,
+                                                        reinterpret_cast<const __half*>(bias));
   return LAUNCH_OK();
 }
 

@@ -31,6 +31,7 @@ namespace zse {
 constexpr int kW4Threads = 608;        // 19 warps
 constexpr int kDqWarps = 16;
 constexpr int kXWarp = 18;
+constexpr int kMaxPlanes = 8;
 
 template <int NT, int R>
 struct W4Cfg {
@@ -64,7 +65,7 @@ struct W4Args {
   int M, N, K, ldo;
   int k_stages;            // K / 128
   int stages_per_split;    // K stages handled by one CTA of the cluster
-  int cluster_k;           // CTAs per cluster (= gridDim.z)
+  int cluster_k;           // CTAs per cluster along K (1: every K split writes its own fp32 plane)
   Status* status;
   long long* timing;       // debug builds (ZSE_W4_TIMING): per-role cycle counters, else unused
 };
@@ -348,6 +349,7 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4Args a) {
   }
   if (dq_role && acc_ok) {
     const int t0 = blockIdx.y * NT;
+    const int plane_z = in_cluster ? 0 : int(blockIdx.z);
     // chunk ch belongs to the CTA with rank ch % ks; inside the CTA the four warp groups take its chunks in turn
     int mine = 0;
 #pragma unroll 1
@@ -409,7 +411,7 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4Args a) {
             if (EPI == kEpiF16)
               reinterpret_cast<__half*>(a.out)[size_t(t) * a.ldo + n] = __float2half_rn(clamp_f16(v[i] + bias));
             else
-              reinterpret_cast<float*>(a.out)[size_t(t) * a.ldo + n] = v[i];
+              reinterpret_cast<float*>(a.out)[(size_t(plane_z) * a.M + t) * a.ldo + n] = v[i];
           }
         }
       }
@@ -447,7 +449,7 @@ static int launch_w4(const CUtensorMap& tx, const W4Args& a, dim3 grid, cudaStre
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 1;
   attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = grid.z;
+  attr[0].val.clusterDim.z = a.cluster_k;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
   return cudaLaunchKernelEx(&cfg, kern, tx, a) == cudaSuccess ? 0 : ZSE_ERR_LAUNCH;
@@ -461,36 +463,41 @@ static int launch_w4_epi(int epilogue, const CUtensorMap& tx, const W4Args& a, d
   return ZSE_ERR_SHAPE;
 }
 
-// How the launcher tiles a problem: weight tiles per CTA (R) and CTAs per K cluster (ks).  The model counts time in
-// "chunk times" (one 8704-byte weight chunk at this SM's share of HBM bandwidth): a K stage costs R chunks plus the
-// activation tile every CTA re-reads from L2, a CTA has a fixed start/epilogue cost, and a cluster of ks CTAs must fit
-// into one GPC, which limits how many CTAs run at the same time.
-static void plan_w4(int M, int N, int K, int epilogue, int sm_count, int want_split, int* R_out, int* ks_out) {
+// How the launcher tiles a problem: weight tiles per CTA (R) and K splits (ks).  Measured on B200: a tcgen05.mma of
+// M=128, K=16 occupies the tensor pipe for about 50 cycles whatever N <= 64 is, so a 128x128 weight chunk costs about
+// 450 cycles on one SM and a CTA is tensor-issue bound, not bandwidth bound; what matters is an even spread of chunks
+// over the SMs and a small fixed cost per CTA.  Row-parallel projections (fp32 epilogue) split K into planes that the
+// consumer adds; the other epilogues need the whole K in one CTA (or an explicit cluster split).
+static void plan_w4(int M, int N, int K, int epilogue, int sm_count, int want_split, int* R_out, int* ks_out,
+                    int* cluster_out) {
   const int nt = pick_nt(M);
   const int n_tiles = epilogue == kEpiSwiGLU ? (N / 2 + 63) / 64 : (N + kTileN - 1) / kTileN;
   const int m_tiles = (M + nt - 1) / nt;
   const int k_stages = K / kW4StageK;
-  const int gpc_sms = max(1, sm_count / 8);
+  const bool planes_ok = epilogue == kEpiPartialF32;
   double best_cost = -1.0;
   int best_r = 1, best_ks = 1;
   for (int R = 1; R <= 4; ++R) {
     if (n_tiles % R != 0) continue;
     if (R > 1 && (R * nt > 256)) continue;                      // accumulators + A ring must fit 512 TMEM columns
     const long ctas = long(n_tiles / R) * m_tiles;
-    for (int ks = 1; ks <= min(8, k_stages); ++ks) {
-      if (want_split > 0 && ks != min(want_split, min(8, k_stages))) continue;
-      const long conc = ks == 1 ? sm_count : min(long(sm_count), long(8) * (gpc_sms / ks) * ks);
-      if (conc <= 0) continue;
-      const long waves = (ctas * ks + conc - 1) / conc;
-      const double stage = double(R) + 0.5 * double(nt) / 64.0;
-      const double fixed = 5.0 + (ks > 1 ? 3.0 : 0.0);
-      const double cost = double(waves) * (double((k_stages + ks - 1) / ks) * stage + fixed);
+    const int max_ks = planes_ok ? min(kMaxPlanes, k_stages) : 1;
+    for (int ks = 1; ks <= max_ks; ++ks) {
+      const long waves = (ctas * ks + sm_count - 1) / sm_count;
+      const double unit = 1.0 + 0.1 * double(nt) / 64.0 / double(R);       // chunk + share of the activation stage
+      const double fixed = 8.0 + (ks > 1 ? 1.0 : 0.0);
+      const double cost = double(waves) * (double((k_stages + ks - 1) / ks) * double(R) * unit + fixed);
       if (best_cost < 0 || cost < best_cost - 1e-9 || (cost < best_cost + 1e-9 && R > best_r)) {
         best_cost = cost;
         best_r = R;
         best_ks = ks;
       }
     }
+  }
+  *cluster_out = 1;
+  if (want_split > 0) {                                         // explicit request: planes if possible, else a cluster
+    best_ks = max(1, min(want_split, min(8, k_stages)));
+    if (!planes_ok) *cluster_out = best_ks;
   }
   *R_out = best_r;
   *ks_out = best_ks;
@@ -516,16 +523,17 @@ extern "C" int zse_gemm_w4(const void* w_tiled, const void* x, int x_rows_cap, c
     if (sm_count <= 0) sm_count = 148;
   }
   const int k_stages = K / kW4StageK;
-  int R = 1, ks = 1;
-  plan_w4(M, N, K, epilogue, sm_count, k_split, &R, &ks);
+  int R = 1, ks = 1, cluster = 1;
+  plan_w4(M, N, K, epilogue, sm_count, k_split, &R, &ks, &cluster);
   const int spp = (k_stages + ks - 1) / ks;
-  ks = (k_stages + spp - 1) / spp;                     // no empty CTA in a cluster
+  ks = (k_stages + spp - 1) / spp;                     // no empty split
+  if (cluster > 1) cluster = ks;
   const int nt = pick_nt(M);
   const int n_tiles = epilogue == kEpiSwiGLU ? (N / 2 + 63) / 64 : (N + kTileN - 1) / kTileN;
   CUtensorMap tx;
   if (int rc = get_tmap(x, uint64_t(max(x_rows_cap, M)), uint64_t(K), uint32_t(nt), &tx)) return rc;
   W4Args a{reinterpret_cast<const uint8_t*>(w_tiled), reinterpret_cast<const __half*>(bias), out, M, N, K, ldo,
-           k_stages, spp, ks, reinterpret_cast<Status*>(status), g_w4_timing};
+           k_stages, spp, cluster, reinterpret_cast<Status*>(status), g_w4_timing};
   dim3 grid(n_tiles / R, (M + nt - 1) / nt, ks);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   int rc = ZSE_ERR_SHAPE;
@@ -554,8 +562,16 @@ extern "C" int zse_gemm_w4(const void* w_tiled, const void* x, int x_rows_cap, c
   return rc;
 }
 
-// Kept for callers that size a plane buffer: the INT4 kernel reduces its K splits on chip and writes one plane.
+// Number of fp32 planes zse_gemm_w4 writes for an fp32-epilogue call with these arguments (the caller sizes the plane
+// buffer and tells the consumer how many planes to add).
 extern "C" int zse_gemm_w4_splits(int M, int N, int K, int k_split) {
-  (void)M; (void)N; (void)K; (void)k_split;
-  return 1;
+  if (M <= 0 || K % kW4StageK != 0 || K <= 0) return 1;
+  int sm_count = 148, dev = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
+  if (sm_count <= 0) sm_count = 148;
+  int R = 1, ks = 1, cluster = 1;
+  plan_w4(M, N, K, kEpiPartialF32, sm_count, k_split, &R, &ks, &cluster);
+  const int k_stages = K / kW4StageK;
+  const int spp = (k_stages + ks - 1) / ks;
+  return (k_stages + spp - 1) / spp;
 }

@@ -74,7 +74,7 @@ def test_gemm_w4_splitk_partials_and_add_rmsnorm(ops, M, N, K, ks):
     planes = ops.linear_partial(w, x, M, partials, k_split=ks)
     torch.cuda.synchronize()
     ops.check()
-    assert planes == 1            # K splits are reduced on chip (cluster + distributed shared memory)
+    assert 1 <= planes <= ks
     want = x.float() @ wd.T
     got = partials[:planes].sum(0)
     assert _rel(got, want) < 2e-3
@@ -126,18 +126,63 @@ def test_gemm_w4_model_shapes(ops, M, N, K, epi):
             ops.linear(w, x, M, out)
             want = ref.linear(x, wd, bias)
         else:
-            planes = torch.zeros(2, M, N, dtype=torch.float32, device="cuda")
-            assert ops.linear_partial(w, x, M, planes) == 1
-            out, want = planes[0], x.float() @ wd.T
+            planes = torch.zeros(8, M, N, dtype=torch.float32, device="cuda")
+            n_pl = ops.linear_partial(w, x, M, planes)
+            out, want = planes[:n_pl].sum(0), x.float() @ wd.T
     torch.cuda.synchronize()
     ops.check()
     assert _rel(out, want) < 3e-3, _rel(out, want)
     # determinism: the on-chip reduction adds the K splits in a fixed order
     if epi == "partial":
-        again = torch.zeros(2, M, N, dtype=torch.float32, device="cuda")
+        again = torch.zeros(8, M, N, dtype=torch.float32, device="cuda")
         ops.linear_partial(w, x, M, again)
         torch.cuda.synchronize()
-        assert torch.equal(again[0], out)
+        assert torch.equal(again[:n_pl].sum(0), out)
+
+
+@pytest.mark.parametrize("ks", [2, 3, 4])
+def test_gemm_w4_cluster_split_with_fused_epilogues(ops, ks):
+    """Explicit K split on an epilogue that needs the whole sum: the CTAs of a cluster add their accumulators through
+    distributed shared memory before bias / SwiGLU are applied."""
+    from zse_b200.ops import native
+    M, N, K = 48, 1024, 2048
+    p, wd = _w4_parts_gpu(N, K, 5)
+    bias = (torch.randn(N, device="cuda") * 0.1).half()
+    w = ops.make_linear([p], K, 128, bias)
+    x = (torch.randn(M, K, device="cuda") * 0.5).half()
+    out = torch.zeros(M, N, dtype=torch.float16, device="cuda")
+    native.gemm_w4(w.data, x, M, w.bias, out, M, N, K, N, 0, ks, ops.status.ptr)
+    g, gd = _w4_parts_gpu(N, K, 6)
+    u, ud = _w4_parts_gpu(N, K, 7)
+    wg = ops.make_linear([g, u], K, 128, swiglu=True)
+    act = torch.zeros(M, N, dtype=torch.float16, device="cuda")
+    native.gemm_w4(wg.data, x, M, None, act, M, 2 * N, K, N, 1, ks, ops.status.ptr)
+    torch.cuda.synchronize()
+    ops.check()
+    assert _rel(out, ref.linear(x, wd, bias)) < 3e-3
+    assert _rel(act, ref.swiglu(x.float() @ gd.T, x.float() @ ud.T)) < 3e-3
+
+
+def test_rope_kv_write_from_planes(ops):
+    """QKV produced as fp32 split-K planes: the RoPE kernel adds the planes and the bias, rotates, stores q as fp16
+    and k/v into the cache - same result as the fp16 path."""
+    hd, nh, nkv, bs, M, blocks = 128, 6, 2, 16, 19, 8
+    ld = (nh + 2 * nkv) * hd
+    planes = torch.randn(3, M, ld, device="cuda")
+    bias = (torch.randn(ld, device="cuda") * 0.1).half()
+    full = (planes.sum(0) + bias.float()).half()
+    kv_a = torch.zeros(blocks, 2, nkv, bs, hd, dtype=torch.float16, device="cuda")
+    kv_b = kv_a.clone()
+    pos = torch.randint(0, 2000, (M,), device="cuda", dtype=torch.int32)
+    slots = torch.randperm(blocks * bs, device="cuda")[:M].long()
+    freqs = ref.inv_freq(hd, 1e6).cuda()
+    want = full.clone()
+    ref.rope_kv_write(want, kv_a, pos, slots, freqs, nh, nkv, hd, bs)
+    got = torch.zeros(M, ld, dtype=torch.float16, device="cuda")
+    ops.rope_kv_write(got, kv_b, pos, slots, freqs, M, nh, nkv, hd, bs, planes=planes, n_planes=3, bias=bias)
+    torch.cuda.synchronize()
+    assert (got[:, : nh * hd].float() - want[:, : nh * hd].float()).abs().max() < 2e-2
+    assert (kv_b.float() - kv_a.float()).abs().max() < 2e-2
 
 
 @pytest.mark.parametrize("M,N,K", [(1, 1000, 256), (20, 128, 688), (64, 4096, 512), (200, 300, 264)])

@@ -98,6 +98,9 @@ class StepBuffers:
         self.xnorm = z(max_tokens, H, dt=f16)
         self.qkv = z(max_tokens, plan.q_dim + 2 * plan.kv_dim, dt=f16)
         self.attn_out = z(max_tokens, plan.q_dim, dt=f16)
+        # decode-sized passes take QKV as fp32 split-K planes (summed, biased and rotated by the RoPE kernel)
+        self.qkv_plane_rows = min(max_tokens, 256)
+        self.qkv_planes = z(8, self.qkv_plane_rows, plan.q_dim + 2 * plan.kv_dim, dt=f32)
         self.act = z(max_tokens, plan.inter_size, dt=f16)
         self.partials = z(max_planes, max_tokens, H, dt=f32)
         self.xsel = z(logits_rows, H, dt=f16)
@@ -228,11 +231,16 @@ class DecoderModel:
         planes = 0
         for li, L in enumerate(self.layers):
             self._add_norm(b, planes, L.ln1, M)
-            ops.linear(L.qkv, b.xnorm, M, b.qkv)
-            if self.lora is not None:
-                self.lora.apply_qkv(li, b, M)
-            ops.rope_kv_write(b.qkv, kv[li], b.positions, b.slots, self.inv_freq, M, p.num_heads, p.num_kv_heads,
-                              c.head_dim, bs)
+            if self.lora is None and M <= b.qkv_plane_rows and L.qkv.kind == "w4t":
+                n_q = ops.linear_partial(L.qkv, b.xnorm, M, b.qkv_planes)
+                ops.rope_kv_write(b.qkv, kv[li], b.positions, b.slots, self.inv_freq, M, p.num_heads, p.num_kv_heads,
+                                  c.head_dim, bs, planes=b.qkv_planes, n_planes=n_q, bias=L.qkv.bias)
+            else:
+                ops.linear(L.qkv, b.xnorm, M, b.qkv)
+                if self.lora is not None:
+                    self.lora.apply_qkv(li, b, M)
+                ops.rope_kv_write(b.qkv, kv[li], b.positions, b.slots, self.inv_freq, M, p.num_heads,
+                                  p.num_kv_heads, c.head_dim, bs)
             if mode == "decode":
                 ops.attn_decode(b.qkv, kv[li], b.block_tables, b.seq_lens, b.attn_out, num_seqs, p.num_heads,
                                 p.num_kv_heads, c.head_dim, bs, self.scale, b.attn_scratch, attn_splits)

@@ -75,7 +75,8 @@ class TorchOps:
         out[:M, :half] = ref.swiglu(y[:, :half], y[:, half:], gelu)
 
     def linear_partial(self, w: LinearWeight, x, M, partials, k_split=1, x_cap=None) -> int:
-        partials[0, :M, : w.N] = x[:M].float() @ w.data.T
+        # planes are laid out [plane][M rows][N] with the *actual* M as the row count, like the CUDA kernels do
+        partials.view(-1)[: M * w.N].view(M, w.N).copy_(x[:M].float() @ w.data.T)
         return 1
 
     def embedding(self, table, ids, out, M, scale=1.0):
@@ -84,13 +85,20 @@ class TorchOps:
     def add_rmsnorm(self, residual, partials, n_partials, add_f16, weight, out, M, eps):
         H = residual.shape[1]
         if n_partials:
-            residual[:M] += partials[:n_partials, :M, :H].sum(0)
+            residual[:M] += partials.view(-1)[: n_partials * M * H].view(n_partials, M, H).sum(0)
         if add_f16 is not None:
             residual[:M] += add_f16[:M].float()
         if out is not None:
             out[:M] = ref.rmsnorm(residual[:M], weight, eps)
 
-    def rope_kv_write(self, qkv, kv_layer, positions, slots, inv_freq, M, nh, nkv, hd, block_size):
+    def rope_kv_write(self, qkv, kv_layer, positions, slots, inv_freq, M, nh, nkv, hd, block_size, planes=None,
+                      n_planes=0, bias=None):
+        if planes is not None:
+            ld = qkv.shape[1]
+            full = planes.view(-1)[: n_planes * M * ld].view(n_planes, M, ld).sum(0)
+            if bias is not None:
+                full = full + bias.float()
+            qkv[:M] = full.clamp(-65504, 65504).to(qkv.dtype)
         ref.rope_kv_write(qkv[:M], kv_layer, positions[:M], slots[:M], inv_freq, nh, nkv, hd, block_size)
 
     def attn_decode(self, qkv, kv_layer, block_tables, seq_lens, out, S, nh, nkv, hd, block_size, scale, scratch=None,
@@ -216,13 +224,18 @@ class CudaOps(TorchOps):
         return max(1, min(want, 8, (w.K // 64) // 4 or 1))
 
     def linear_partial(self, w, x, M, partials, k_split=None, x_cap=None) -> int:
-        """fp32 result planes in ``partials`` [planes, M, N]; returns how many planes were written (the INT4 kernel
-        reduces its K split on chip and always writes one)."""
+        """fp32 result planes in ``partials`` [planes, M, N] (plane stride M*N); returns how many planes were written.
+        The consumer (``add_rmsnorm`` / the tensor-parallel reduce) adds them in plane order."""
         cap = x.shape[0] if x_cap is None else x_cap
         if w.kind == "w4t":
-            self.n.gemm_w4(w.data, x, cap, None, partials, M, w.N, w.K, partials.stride(1), EPI_PARTIAL,
-                           0 if k_split is None else k_split, self.status.ptr)
-            return 1
+            ks = 0 if k_split is None else min(k_split, partials.shape[0])
+            planes = self.n.gemm_w4_splits(M, w.N, w.K, ks)
+            if planes > partials.shape[0]:
+                ks = partials.shape[0]
+                planes = self.n.gemm_w4_splits(M, w.N, w.K, ks)
+            self.n.gemm_w4(w.data, x, cap, None, partials, M, w.N, w.K, partials.stride(1), EPI_PARTIAL, ks,
+                           self.status.ptr)
+            return planes
         ks = self.pick_k_split(w, M) if k_split is None else k_split
         ks = min(ks, partials.shape[0])
         planes = self.n.gemm_f16_splits(M, w.N, w.K, ks)
@@ -237,9 +250,10 @@ class CudaOps(TorchOps):
         # partial planes are laid out [plane][M rows][H]: the plane stride the kernel assumes is M*H
         self.n.add_rmsnorm(residual, partials, n_partials, add_f16, weight, out, M, residual.shape[1], float(eps))
 
-    def rope_kv_write(self, qkv, kv_layer, positions, slots, inv_freq, M, nh, nkv, hd, block_size):
+    def rope_kv_write(self, qkv, kv_layer, positions, slots, inv_freq, M, nh, nkv, hd, block_size, planes=None,
+                      n_planes=0, bias=None):
         self.n.rope_kv_write(qkv, kv_layer, positions, slots, inv_freq, M, nh, nkv, hd, inv_freq.numel() * 2,
-                             block_size)
+                             block_size, planes, n_planes, bias)
 
     def attn_decode(self, qkv, kv_layer, block_tables, seq_lens, out, S, nh, nkv, hd, block_size, scale, scratch=None,
                     num_splits=1):

@@ -46,7 +46,7 @@ _SIGS = {
                                 c_void_p]),
     "zse_rmsnorm_f16": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p]),
     "zse_rope_kv_write": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                                  c_int, c_void_p]),
+                                  c_int, c_void_p, c_int, c_void_p, c_void_p]),
     "zse_swiglu": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "zse_bias_add": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "zse_attn_decode_scratch_floats": (c_int64, [c_int, c_int, c_int, c_int]),
@@ -199,9 +199,10 @@ def rmsnorm_f16(x, weight, out, M, H, eps):
     _ck(load().zse_rmsnorm_f16(_p(x), _p(weight), _p(out), M, H, eps, _stream()), "rmsnorm_f16")
 
 
-def rope_kv_write(qkv, kv_layer, positions, slots, inv_freq, M, nh, nkv, hd, rotary_dim, block_size):
+def rope_kv_write(qkv, kv_layer, positions, slots, inv_freq, M, nh, nkv, hd, rotary_dim, block_size, planes=None,
+                  n_planes=0, bias=None):
     _ck(load().zse_rope_kv_write(_p(qkv), _p(kv_layer), _p(positions), _p(slots), _p(inv_freq), M, nh, nkv, hd,
-                                 rotary_dim, block_size, _stream()), "rope_kv_write")
+                                 rotary_dim, block_size, _p(planes), n_planes, _p(bias), _stream()), "rope_kv_write")
 
 
 def swiglu(gate_up, out, M, I, gelu=False):
