@@ -35,24 +35,32 @@ constexpr int kMaxPlanes = 8;
 
 template <int NT, int R>
 struct W4Cfg {
+  static_assert(R == 1 || R == 2, "a CTA owns one or two weight tiles");
+  static_assert(!(R == 2 && NT > 128), "two accumulators of 256 columns do not fit next to the A ring");
   static constexpr int kXBytes = NT * 128;                         // one 64-wide K sub-tile of X
   static constexpr int kXStage = 2 * kXBytes;
-  static constexpr int kSX = NT <= 64 ? 4 : (NT == 128 ? 3 : 2);   // activation stages
-  static constexpr int kSW = NT <= 64 ? 12 : (NT == 128 ? 10 : 8); // weight chunks in flight
+  // Two consecutive chunks form a pair that is released by ONE tcgen05.commit (a commit costs about as much tensor
+  // pipe time as two MMAs).  Where possible the activation ring is laid out so that the same commit also frees an
+  // activation stage: R = 2 -> one pair per K stage (kSX == kSP); R = 1 -> one pair per two K stages (kSX == 2 kSP).
+  static constexpr bool kTiedX = NT <= 128;
+  static constexpr int kSP = (R == 2) ? (NT <= 64 ? 3 : 2) : (NT <= 64 ? 3 : 2);       // pair slots in TMEM
+  static constexpr int kSX = kTiedX ? (R == 2 ? kSP : 2 * kSP) : 2;                     // activation stages
+  static constexpr int kSW = NT <= 64 ? 12 : (NT == 128 ? (R == 2 ? 10 : 8) : 8);      // weight chunks in flight
   static constexpr int kAcc = R * NT;                              // accumulator columns
-  static constexpr int kSA = (512 - kAcc) / 64 > 6 ? 6 : (512 - kAcc) / 64;   // A slots in TMEM
+  static_assert(kAcc + kSP * 128 <= 512, "TMEM budget");
   static constexpr int kRingBytes = kSX * kXStage + kSW * kW4ChunkBytes;
   static constexpr int kParkBytes = R * NT * 128 * 4;              // accumulators parked for the cluster reduce
   static constexpr int kDataBytes = ((kRingBytes > kParkBytes ? kRingBytes : kParkBytes) + 15) & ~15;
   static constexpr int kXchBytes = 8 * 32 * 16 * 4;               // SwiGLU gate/up exchange (after the barriers)
   static constexpr int kSmemBytes = kDataBytes + 512 + kXchBytes + 1024;
-  static_assert(kSA >= 2, "not enough TMEM for the A ring");
+  static_assert(kSmemBytes <= 232448, "shared memory budget");
 };
 
 struct W4Bars {
   uint64_t w_full[12], w_empty[12];
-  uint64_t x_full[4], x_empty[4];
-  uint64_t a_ready[6], a_empty[6];
+  uint64_t x_full[6], x_empty[6];
+  uint64_t a_ready[6];            // [pair slot][half]
+  uint64_t pair_done[3];
   uint64_t acc_ready;
   uint32_t tmem_base;
   int abort_flag;
@@ -133,7 +141,8 @@ template <int NT, int R, int EPI>
 __global__ void __launch_bounds__(kW4Threads, 1)
 gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4Args a) {
   using Cfg = W4Cfg<NT, R>;
-  constexpr int SW = Cfg::kSW, SX = Cfg::kSX, SA = Cfg::kSA;
+  constexpr int SW = Cfg::kSW, SX = Cfg::kSX, SP = Cfg::kSP;
+  constexpr bool kTied = Cfg::kTiedX;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* x_ring = smem;                                    // [SX][2][NT*128]
@@ -157,9 +166,10 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4Args a) {
       mbar_init(&bars->x_full[i], 1);
       mbar_init(&bars->x_empty[i], 1);
     }
-    for (int i = 0; i < SA; ++i) {
-      mbar_init(&bars->a_ready[i], 4);
-      mbar_init(&bars->a_empty[i], 1);
+    for (int i = 0; i < SP; ++i) {
+      mbar_init(&bars->a_ready[2 * i], 4);
+      mbar_init(&bars->a_ready[2 * i + 1], 4);
+      mbar_init(&bars->pair_done[i], 1);
     }
     mbar_init(&bars->acc_ready, 1);
     bars->abort_flag = 0;
@@ -206,7 +216,11 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4Args a) {
       int issued = 0, s = 0;
       uint32_t ph = 1;
       for (int kk = 0; kk < n_k; ++kk) {
-        if (kk >= SX && !mbar_wait(&bars->x_empty[s], ph, abort_flag, a.status, 2, kk)) break;
+        if (kk >= SX) {
+          // tied: the commit that ends the pair holding this stage's last chunk frees the stage as well
+          uint64_t* freed = kTied ? &bars->pair_done[R == 2 ? s : (s >> 1)] : &bars->x_empty[s];
+          if (!mbar_wait(freed, ph, abort_flag, a.status, 2, kk)) break;
+        }
         mbar_arrive_expect_tx(&bars->x_full[s], Cfg::kXStage);
         const int k0 = (s_begin + kk) * kW4StageK;
         tma_load_2d(x_ring + s * Cfg::kXStage, &tmap_x, k0, blockIdx.y * NT, &bars->x_full[s]);
@@ -221,34 +235,37 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4Args a) {
     if (lane == 0) {
       constexpr uint32_t idesc = make_idesc_f16(kTileN, NT);
       const uint64_t desc0 = make_desc_sw128(smem_u32(x_ring));
-      int sx = 0, sa = 0, r = 0, kk = 0;
-      uint32_t xph = 0, aph = 0;
+      int sx = 0, slot = 0, r = 0, kk = 0;
+      uint32_t xph = 0, cyc = 0;
       for (int u = 0; u < n_units; ++u) {
+        const int half = u & 1;
         TICK(tx);
         if (r == 0 && !mbar_wait(&bars->x_full[sx], xph, abort_flag, a.status, 3, kk)) break;
         ACC(0, tx);
         TICK(ta);
-        if (!mbar_wait(&bars->a_ready[sa], aph, abort_flag, a.status, 4, u)) break;
+        if (!mbar_wait(&bars->a_ready[2 * slot + half], cyc, abort_flag, a.status, 4, u)) break;
         ACC(1, ta);
         TICK(ti);
         tc_fence_after_sync();
         // the start-address field counts 16-byte units: a K step of 16 halfs is +2, the second 64-wide sub-tile
         // is +kXBytes/16
         const uint64_t bd = desc0 + uint64_t((sx * Cfg::kXStage) >> 4);
-        const uint32_t at = a_base + sa * 64, dt = tmem + r * NT;
+        const uint32_t at = a_base + slot * 128 + half * 64, dt = tmem + r * NT;
 #pragma unroll
         for (int j = 0; j < 8; ++j)
           umma_ts(dt, at + j * 8, bd + uint64_t((j >> 2) * (Cfg::kXBytes >> 4) + (j & 3) * 2), idesc,
                   (kk | j) != 0);
-        tc_commit(&bars->a_empty[sa]);
-        ACC(2, ti);
-        if (++sa == SA) { sa = 0; aph ^= 1; }
         if (++r == R) {
-          tc_commit(&bars->x_empty[sx]);
+          if (!kTied) tc_commit(&bars->x_empty[sx]);
           r = 0;
           ++kk;
           if (++sx == SX) { sx = 0; xph ^= 1; }
         }
+        if (half == 1 || u == n_units - 1) {
+          tc_commit(&bars->pair_done[slot]);
+          if (++slot == SP) { slot = 0; cyc ^= 1; }
+        }
+        ACC(2, ti);
       }
       tc_commit(&bars->acc_ready);
     }
@@ -260,8 +277,9 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4Args a) {
     const int grp = (warp - 2) >> 2;
     const int row = q * 32 + lane;
     const uint32_t lane_addr = uint32_t(q * 32) << 16;
-    int sw = grp % SW, sa = grp % SA;
-    uint32_t wph = 0, aph = 1;               // aph: parity of the previous completion of a_empty[sa]
+    int sw = grp % SW, slot = grp >> 1;      // unit u -> pair u/2 -> slot (u/2) % SP, half u & 1
+    const int half = grp & 1;
+    uint32_t wph = 0, cyc = 0;               // cyc = (u/2) / SP: how often this pair slot has been used before
     for (int u = grp; u < n_units; u += 4) {
       TICK(t0);
       if (!mbar_wait(&bars->w_full[sw], wph, abort_flag, a.status, 5, u)) break;
@@ -276,35 +294,35 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4Args a) {
       if (lane == 0) mbar_arrive(&bars->w_empty[sw]);          // the chunk is in registers: its slot may be refilled
       ACC(1, t1);
       TICK(t2);
-      if (u >= SA && !mbar_wait(&bars->a_empty[sa], aph, abort_flag, a.status, 6, u)) break;
+      if (cyc > 0 && !mbar_wait(&bars->pair_done[slot], (cyc - 1) & 1, abort_flag, a.status, 6, u)) break;
       ACC(2, t2);
       TICK(t3);
       tc_fence_after_sync();
       const __half2 s2 = __half2half2(__low2half(sz)), z2 = __half2half2(__high2half(sz));
-      const uint32_t dst = a_base + lane_addr + sa * 64;
+      const uint32_t dst = a_base + lane_addr + slot * 128 + half * 64;
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
+      for (int hh = 0; hh < 2; ++hh) {
         uint32_t o[32];
 #pragma unroll
         for (int p2 = 0; p2 < 2; ++p2) {
-          const uint4 w4 = pk[half * 2 + p2];
+          const uint4 w4 = pk[hh * 2 + p2];
           dequant_word(w4.x, s2, z2, o + p2 * 16 + 0);
           dequant_word(w4.y, s2, z2, o + p2 * 16 + 4);
           dequant_word(w4.z, s2, z2, o + p2 * 16 + 8);
           dequant_word(w4.w, s2, z2, o + p2 * 16 + 12);
         }
-        ZSE_TMEM_ST_X32(dst + half * 32, o);
+        ZSE_TMEM_ST_X32(dst + hh * 32, o);
       }
       ACC(3, t3);
       TICK(t4);
       tc_wait_st();
       tc_fence_before_sync();
-      if (lane == 0) mbar_arrive(&bars->a_ready[sa]);
+      if (lane == 0) mbar_arrive(&bars->a_ready[2 * slot + half]);
       ACC(4, t4);
       sw += 4;
       if (sw >= SW) { sw -= SW; wph ^= 1; }
-      sa += 4;
-      if (sa >= SA) { sa -= SA; aph ^= 1; }
+      slot += 2;
+      if (slot >= SP) { slot -= SP; ++cyc; }
     }
     TICK(t5);
     acc_ok = mbar_wait(&bars->acc_ready, 0, abort_flag, a.status, 7, 0);
@@ -477,9 +495,9 @@ static void plan_w4(int M, int N, int K, int epilogue, int sm_count, int want_sp
   const bool planes_ok = epilogue == kEpiPartialF32;
   double best_cost = -1.0;
   int best_r = 1, best_ks = 1;
-  for (int R = 1; R <= 4; ++R) {
+  for (int R = 1; R <= 2; ++R) {
     if (n_tiles % R != 0) continue;
-    if (R > 1 && (R * nt > 256)) continue;                      // accumulators + A ring must fit 512 TMEM columns
+    if (R == 2 && nt > 128) continue;                           // accumulators + A ring must fit 512 TMEM columns
     const long ctas = long(n_tiles / R) * m_tiles;
     const int max_ks = planes_ok ? min(kMaxPlanes, k_stages) : 1;
     for (int ks = 1; ks <= max_ks; ++ks) {
@@ -545,18 +563,6 @@ extern "C" int zse_gemm_w4(const void* w_tiled, const void* x, int x_rows_cap, c
       case 32: rc = launch_w4_epi<32, 2>(epilogue, tx, a, grid, st); break;
       case 64: rc = launch_w4_epi<64, 2>(epilogue, tx, a, grid, st); break;
       default: rc = launch_w4_epi<128, 2>(epilogue, tx, a, grid, st); break;
-    }
-  } else if (R == 3) {
-    switch (nt) {
-      case 16: rc = launch_w4_epi<16, 3>(epilogue, tx, a, grid, st); break;
-      case 32: rc = launch_w4_epi<32, 3>(epilogue, tx, a, grid, st); break;
-      default: rc = launch_w4_epi<64, 3>(epilogue, tx, a, grid, st); break;
-    }
-  } else {
-    switch (nt) {
-      case 16: rc = launch_w4_epi<16, 4>(epilogue, tx, a, grid, st); break;
-      case 32: rc = launch_w4_epi<32, 4>(epilogue, tx, a, grid, st); break;
-      default: rc = launch_w4_epi<64, 4>(epilogue, tx, a, grid, st); break;
     }
   }
   return rc;

@@ -1,0 +1,131 @@
+"""Admin routes (admin key required): API keys, engine statistics, usage, dashboard chat sessions
+(zse-engine/zse_engine/server/api_admin.py:20-289)."""
+from __future__ import annotations
+
+import dataclasses
+import secrets
+
+from .router import Request, Response
+
+
+class AdminAPI:
+    def __init__(self, db, auth, engine=None):
+        self._db, self._auth, self._engine = db, auth, engine
+
+    def register(self, router) -> None:
+        router.post("/v1/admin/keys/create", self.create_key)
+        router.get("/v1/admin/keys/list", self.list_keys)
+        router.post("/v1/admin/keys/revoke", self.revoke_key)
+        router.post("/v1/admin/keys/update", self.update_key)
+        router.get("/v1/admin/stats", self.stats)
+        router.get("/v1/admin/usage", self.usage)
+        router.post("/v1/dashboard/session", self.session_create)
+        router.get("/v1/dashboard/sessions", self.session_list)
+        router.get("/v1/dashboard/session/{session_id}", self.session_get)
+        router.post("/v1/dashboard/session/{session_id}/message", self.session_add_message)
+        router.delete("/v1/dashboard/session/{session_id}", self.session_delete)
+
+    def _deny(self, request: Request):
+        if not self._auth.is_admin(request.authorization):
+            return Response.error("Admin access required", 403)
+        return None
+
+    async def create_key(self, request: Request) -> Response:
+        if (r := self._deny(request)) is not None:
+            return r
+        b = request.json or {}
+        key, info = self._db.create_key(str(b.get("name", "")), int(b.get("rate_limit_rpm", 60)),
+                                        int(b.get("rate_limit_tpm", 100000)), str(b.get("allowed_models", "*")),
+                                        b.get("expires_in_days"))
+        out = info.to_public()
+        out["key"] = key            # shown once
+        return Response.json_response(out, 201)
+
+    async def list_keys(self, request: Request) -> Response:
+        if (r := self._deny(request)) is not None:
+            return r
+        return Response.json_response({"keys": [k.to_public() for k in self._db.list_keys()]})
+
+    async def revoke_key(self, request: Request) -> Response:
+        if (r := self._deny(request)) is not None:
+            return r
+        b = request.json or {}
+        if "id" in b:
+            ok = self._db.revoke_key(int(b["id"]))
+        elif "prefix" in b:
+            ok = self._db.revoke_key_by_prefix(str(b["prefix"]))
+        else:
+            return Response.error("'id' or 'prefix' required")
+        return Response.json_response({"revoked": ok}) if ok else Response.error("key not found", 404)
+
+    async def update_key(self, request: Request) -> Response:
+        if (r := self._deny(request)) is not None:
+            return r
+        b = request.json or {}
+        if "id" not in b:
+            return Response.error("'id' required")
+        ok = self._db.update_key_limits(int(b["id"]), b.get("rate_limit_rpm"), b.get("rate_limit_tpm"),
+                                        b.get("allowed_models"))
+        return Response.json_response({"updated": ok}) if ok else Response.error("key not found or nothing to update", 404)
+
+    async def stats(self, request: Request) -> Response:
+        if (r := self._deny(request)) is not None:
+            return r
+        out = {"usage": self._db.get_usage_stats(), "num_keys": len(self._db.list_keys())}
+        e = self._engine
+        if e is not None:
+            out["engine"] = dataclasses.asdict(e.stats())
+            out["scheduler"] = e.scheduler.stats()
+            out["kv_cache"] = dataclasses.asdict(e.kv_cache.stats())
+            out["lora"] = e.lora_manager.stats() if e.lora_manager is not None else {}
+            spec = getattr(e, "_spec_runner", None)
+            if spec is not None:
+                out["speculative"] = spec.stats()
+            out["init_times"] = getattr(e, "init_times", {})
+        return Response.json_response(out)
+
+    async def usage(self, request: Request) -> Response:
+        if (r := self._deny(request)) is not None:
+            return r
+        kid = request.query.get("key_id")
+        return Response.json_response(self._db.get_usage_stats(int(kid) if kid else None))
+
+    # ---- dashboard sessions (any authenticated key; the admin key works too) --------------------------------
+    def _key_id(self, request: Request):
+        res = self._auth.authenticate(request.authorization)
+        return res.key.id if res.authenticated else None
+
+    async def session_create(self, request: Request) -> Response:
+        if self._key_id(request) is None:
+            return Response.error("authentication required", 401)
+        return Response.json_response({"session_id": secrets.token_hex(8)}, 201)
+
+    async def session_list(self, request: Request) -> Response:
+        kid = self._key_id(request)
+        if kid is None:
+            return Response.error("authentication required", 401)
+        return Response.json_response({"sessions": self._db.list_sessions(None if kid == 0 else kid)})
+
+    async def session_get(self, request: Request) -> Response:
+        if self._key_id(request) is None:
+            return Response.error("authentication required", 401)
+        msgs = self._db.get_session_messages(request.params["session_id"])
+        return Response.json_response({"session_id": request.params["session_id"],
+                                       "messages": [{"role": m.role, "content": m.content, "model": m.model,
+                                                     "created_at": m.created_at} for m in msgs]})
+
+    async def session_add_message(self, request: Request) -> Response:
+        kid = self._key_id(request)
+        if kid is None:
+            return Response.error("authentication required", 401)
+        b = request.json or {}
+        if not b.get("role") or "content" not in b:
+            return Response.error("'role' and 'content' required")
+        mid = self._db.save_message(kid, request.params["session_id"], str(b["role"]), str(b["content"]),
+                                    str(b.get("model", "")), b.get("lora_id"))
+        return Response.json_response({"id": mid}, 201)
+
+    async def session_delete(self, request: Request) -> Response:
+        if self._key_id(request) is None:
+            return Response.error("authentication required", 401)
+        return Response.json_response({"deleted": self._db.delete_session(request.params["session_id"])})
