@@ -45,8 +45,9 @@ class NcclComm:
         if greedy:
             vals, idx = b.logits[:n_rows, :V].float().max(dim=-1)
             both = torch.stack([vals, (idx + plan.vocab[0]).float()], dim=-1).contiguous()
-            gathered = torch.empty(self.world, n_rows, 2, dtype=torch.float32, device=self.device)
-            dist.all_gather_into_tensor(gathered, both, group=self.group)
+            parts = [torch.empty_like(both) for _ in range(self.world)]
+            dist.all_gather(parts, both, group=self.group)
+            gathered = torch.stack(parts, dim=0)
             best = gathered[:, :, 0].argmax(dim=0)       # first rank wins ties -> lowest token id
             b.out_tokens[:n_rows] = gathered[best, torch.arange(n_rows, device=self.device), 1].to(torch.int32)
         else:
@@ -60,10 +61,10 @@ class NcclComm:
         width = (vocab + self.world - 1) // self.world
         local = torch.full((n_rows, width), float("-inf"), dtype=torch.float16, device=self.device)
         local[:, : plan.vocab_size] = b.logits[:n_rows, : plan.vocab_size]
-        out = torch.empty(self.world, n_rows, width, dtype=torch.float16, device=self.device)
-        dist.all_gather_into_tensor(out, local, group=self.group)
+        out = [torch.empty_like(local) for _ in range(self.world)]
+        dist.all_gather(out, local, group=self.group)
         from .shard_plan import split_units
-        parts = [out[r, :, : hi - lo] for r, (lo, hi) in enumerate(split_units(vocab, self.world))]
+        parts = [out[r][:, : hi - lo] for r, (lo, hi) in enumerate(split_units(vocab, self.world))]
         return torch.cat(parts, dim=1).contiguous()
 
     def barrier(self) -> None:

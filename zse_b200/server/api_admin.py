@@ -75,8 +75,10 @@ class AdminAPI:
         e = self._engine
         if e is not None:
             out["engine"] = dataclasses.asdict(e.stats())
-            out["scheduler"] = e.scheduler.stats()
-            out["kv_cache"] = dataclasses.asdict(e.kv_cache.stats())
+            if hasattr(e, "scheduler"):
+                out["scheduler"] = e.scheduler.stats()
+            if hasattr(e, "kv_cache"):
+                out["kv_cache"] = dataclasses.asdict(e.kv_cache.stats())
             out["lora"] = e.lora_manager.stats() if e.lora_manager is not None else {}
             spec = getattr(e, "_spec_runner", None)
             if spec is not None:
