@@ -119,10 +119,12 @@ class KVCacheManager:
                 b = self._pool.get_block(bid)
                 self._pool.increment_ref(b)
                 e.blocks.append(b)
+            e.touch()
             e.num_tokens = len(shared) * bs
             if fresh_tokens:
                 self._page_table.append_tokens(seq_id, fresh_tokens)
             self._prompt_lengths[seq_id] = n
+            self._track_blocks(e, 0)
             if prompt_tokens is not None:
                 self._prompt_tokens[seq_id] = prompt_tokens
             self._registered_upto[seq_id] = len(shared)
@@ -162,9 +164,47 @@ class KVCacheManager:
             if need > self._pool.num_free and not self._evict_locked(need):
                 raise RuntimeError(f"cannot extend sequence {seq_id}: need {need} KV blocks, "
                                    f"{self._pool.num_free} free")
-            self._page_table.append_tokens(seq_id, num_new_tokens)
+            new_ids = self._page_table.append_tokens(seq_id, num_new_tokens)
+            if new_ids:
+                e = self._page_table.get_entry(seq_id)
+                self._track_blocks(e, max(0, len(e.blocks) - len(new_ids) - 1))
             if self._config.sliding_window and self._config.sliding_window > 0:
                 self._trim_sliding_window(seq_id)
+
+    def _track_blocks(self, e, first_idx: int) -> None:
+        """Tells the evictor about blocks ``first_idx..`` of a sequence (new, shared or copied ones)."""
+        bs = self._block_size
+        prompt = self._prompt_lengths.get(e.seq_id, 0)
+        for idx in range(first_idx, len(e.blocks)):
+            if idx not in e.evicted_indices:
+                b = e.blocks[idx]
+                self._evictor.record_access(e.seq_id, idx, b.block_id, b.num_tokens or bs, idx * bs,
+                                            idx * bs < prompt)
+
+    def extend_batch(self, seq_ids) -> list:
+        """One more token for each sequence (a decode step).  Returns one entry per sequence: None, or the exception
+        that extending it raised.  A sequence whose private tail block still has room takes a short path that touches
+        neither the pool nor the evictor."""
+        errs = [None] * len(seq_ids)
+        bs, limit = self._block_size, self._config.max_seq_len
+        windowed = bool(self._config.sliding_window and self._config.sliding_window > 0)
+        with self._lock:
+            for i, sid in enumerate(seq_ids):
+                e = self._page_table.get_entry_or_none(sid)
+                if e is not None and not windowed:
+                    n = e.num_tokens
+                    fill = n % bs
+                    if fill and n < limit and e.blocks:
+                        tail = e.blocks[-1]
+                        if tail.ref_count == 1 and (len(e.blocks) - 1) not in e.evicted_indices:
+                            tail.num_tokens = fill + 1
+                            e.num_tokens = n + 1
+                            continue
+                try:
+                    self.extend_sequence(sid, 1)
+                except Exception as exc:          # reported per sequence: the rest of the batch still runs
+                    errs[i] = exc
+        return errs
 
     def free_sequence(self, seq_id: int) -> None:
         with self._lock:
@@ -195,6 +235,7 @@ class KVCacheManager:
                 return
             bs = self._block_size
             keep_blocks = (keep_tokens + bs - 1) // bs
+            e.touch()
             while len(e.blocks) > keep_blocks:
                 b = e.blocks.pop()
                 idx = len(e.blocks)
@@ -266,6 +307,33 @@ class KVCacheManager:
     def get_block_ids(self, seq_id: int) -> List[int]:
         with self._lock:
             return self._page_table.get_block_ids(seq_id)
+
+    def block_ids_np(self, seq_id: int):
+        with self._lock:
+            return self._page_table.block_ids_np(seq_id)
+
+    def stage_decode(self, seq_ids, block_tables, seq_lens, positions, slots) -> int:
+        """Fills the decode-step arrays (numpy views of the runner's pinned staging buffers) for ``seq_ids`` in one
+        pass: block table rows (-1 padded), lengths, the position of each sequence's newest token and the cache slot
+        that token is written to (-1 when its block was evicted).  Returns the longest sequence length."""
+        S = len(seq_ids)
+        bs = self._block_size
+        with self._lock:
+            entries = [self._page_table.get_entry(sid) for sid in seq_ids]
+            now = self._evictor.now()
+            for sid in seq_ids:
+                self._evictor.touch_sequence(sid, now)
+            block_tables[:S].fill(-1)
+            for s, e in enumerate(entries):
+                ids = e.block_ids_np()
+                block_tables[s, :ids.shape[0]] = ids
+            seq_lens[:S] = [e.num_tokens for e in entries]
+        n = seq_lens[:S]
+        last = n - 1
+        positions[:S] = last
+        blk = block_tables[np.arange(S), np.maximum(last, 0) // bs].astype(np.int64)
+        slots[:S] = np.where(blk < 0, -1, blk * bs + last % bs)
+        return int(n.max()) if S else 0
 
     def num_tokens(self, seq_id: int) -> int:
         return self._page_table.num_tokens(seq_id)

@@ -40,6 +40,7 @@ class Evictor:
         self._policy = policy
         self._clock = clock
         self._info: Dict[tuple, BlockAccessInfo] = {}     # (seq_id, block_id) -> info
+        self._seq_touch: Dict[int, float] = {}            # seq_id -> time of the sequence's last step
         self._evictions = 0
         self._tokens_evicted = 0
 
@@ -73,6 +74,13 @@ class Evictor:
             if bid >= 0:
                 self.record_access(seq_id, idx, bid, block_size, idx * block_size, idx * block_size < prompt_len, now)
 
+    def now(self) -> float:
+        return self._clock()
+
+    def touch_sequence(self, seq_id: int, now: Optional[float] = None) -> None:
+        """Marks every block of the sequence as used now (one dictionary store per step instead of one per block)."""
+        self._seq_touch[seq_id] = self._clock() if now is None else now
+
     def remove_block(self, block_id: int, seq_id: Optional[int] = None) -> None:
         for key in [k for k in self._info if k[1] == block_id and (seq_id is None or k[0] == seq_id)]:
             del self._info[key]
@@ -80,13 +88,15 @@ class Evictor:
     def remove_sequence(self, seq_id: int) -> None:
         for key in [k for k in self._info if k[0] == seq_id]:
             del self._info[key]
+        self._seq_touch.pop(seq_id, None)
 
     def _score(self, info: BlockAccessInfo, now: float) -> float:
+        last = max(info.last_access_time, self._seq_touch.get(info.seq_id, 0.0))
         if self._policy == "lru":
-            return info.last_access_time
+            return last
         if self._policy == "lfu":
             return float(info.access_count)
-        age = max(0.0, now - info.last_access_time)
+        age = max(0.0, now - last)
         return info.access_count / (1.0 + age) + (2.0 if info.is_prompt else 0.5)
 
     def select_victims(self, num_blocks: int, exclude_seq_ids: Optional[Set[int]] = None) -> List[EvictionCandidate]:

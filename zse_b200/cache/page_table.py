@@ -9,6 +9,8 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Set
 
+import numpy as np
+
 from .block_pool import Block, BlockPool
 
 
@@ -19,6 +21,21 @@ class SequenceEntry:
     num_tokens: int = 0                      # logical length (positions 0..num_tokens-1), holes included
     evicted_indices: Set[int] = field(default_factory=set)
     tokens_evicted: int = 0
+    version: int = 0                         # bumped by every change of `blocks` / `evicted_indices`
+    _ids_np: Optional[np.ndarray] = field(default=None, repr=False, compare=False)
+    _ids_version: int = field(default=-1, repr=False, compare=False)
+
+    def touch(self) -> None:
+        self.version += 1
+
+    def block_ids_np(self) -> np.ndarray:
+        """int32 block ids in order, -1 at holes; rebuilt only after the block list changed."""
+        if self._ids_version != self.version or self._ids_np is None:
+            ev = self.evicted_indices
+            self._ids_np = np.fromiter((-1 if i in ev else b.block_id for i, b in enumerate(self.blocks)),
+                                       dtype=np.int32, count=len(self.blocks))
+            self._ids_version = self.version
+        return self._ids_np
 
     @property
     def num_blocks(self) -> int:
@@ -71,6 +88,7 @@ class PageTable:
                 b.token_start = len(e.blocks) * bs
                 e.blocks.append(b)
                 new_ids.append(b.block_id)
+                e.touch()
             fill = e.num_tokens - (len(e.blocks) - 1) * bs
             tail_idx = len(e.blocks) - 1
             tail = e.blocks[tail_idx]
@@ -81,6 +99,7 @@ class PageTable:
                 self._pool.free(tail)
                 e.blocks[tail_idx] = tail = fresh
                 new_ids.append(fresh.block_id)
+                e.touch()
             take = min(remaining, bs - fill)
             tail.num_tokens = fill + take
             e.num_tokens += take
@@ -90,6 +109,9 @@ class PageTable:
     def get_block_ids(self, seq_id: int) -> List[int]:
         e = self._seqs[seq_id]
         return [-1 if i in e.evicted_indices else b.block_id for i, b in enumerate(e.blocks)]
+
+    def block_ids_np(self, seq_id: int) -> np.ndarray:
+        return self._seqs[seq_id].block_ids_np()
 
     def get_blocks(self, seq_id: int) -> List[Block]:
         e = self._seqs.get(seq_id)
@@ -120,6 +142,7 @@ class PageTable:
             dst.blocks.append(b)
         dst.num_tokens = src.num_tokens
         dst.evicted_indices = set(src.evicted_indices)
+        dst.touch()
         return dst
 
     def evict_block(self, seq_id: int, block_idx: int) -> Optional[Block]:
@@ -128,6 +151,7 @@ class PageTable:
             return None
         b = e.blocks[block_idx]
         e.evicted_indices.add(block_idx)
+        e.touch()
         e.tokens_evicted += b.num_tokens
         self._pool.free(b)
         return b

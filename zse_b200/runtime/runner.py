@@ -87,6 +87,11 @@ class ModelRunner:
         self.h_seed = mk(logits_rows, torch.int64)
         self.h_adapter = mk(self.max_tokens, torch.int32)
         self.h_out = mk(logits_rows, torch.int32)
+        # numpy views of the pinned staging buffers: per-step host work is numpy slicing, not tensor indexing
+        self._np = {"ids": self.h_ids.numpy(), "pos": self.h_pos.numpy(), "slots": self.h_slots.numpy(),
+                    "bt": self.h_bt.numpy(), "lens": self.h_lens.numpy(), "rows": self.h_rows.numpy(),
+                    "out": self.h_out.numpy()}
+        self._arange = np.arange(max(logits_rows, self.max_tokens), dtype=np.int64)
         self.timings = {"prefill_passes": 0, "decode_steps": 0, "graph_replays": 0, "graph_captures": 0}
 
     # ---- staging ----------------------------------------------------------------------------------------
@@ -216,35 +221,29 @@ class ModelRunner:
 
     def decode(self, seq_ids: Sequence[int], last_tokens: Sequence[int],
                sampling: Optional[Sequence[SamplingRow]] = None, adapters: Optional[Sequence[int]] = None,
-               penalties=None) -> List[int]:
+               penalties=None, defer: bool = False):
         """One new token for each sequence: ``last_tokens[i]`` is appended at the sequence's current length (the
-        cache must already have been extended by one), attention covers the whole sequence."""
+        cache must already have been extended by one), attention covers the whole sequence.  With ``defer`` the step
+        is only launched and a callable is returned that waits for it and gives the tokens, so that the caller can
+        do host work while the device runs."""
         b, cache = self.buf, self.cache
         S = len(seq_ids)
         if S == 0:
-            return []
+            return (lambda: []) if defer else []
         if S > self.max_batch_seqs:
             raise ValueError(f"decode batch {S} exceeds max_batch_seqs {self.max_batch_seqs}")
         Sp = min(_bucket(S, self.DECODE_BUCKETS), self.max_batch_seqs) if self.use_graphs else S
         bs = cache.block_size
-        self.h_bt[:Sp].fill_(-1)
-        max_len = 1
-        for s, sid in enumerate(seq_ids):
-            n = cache.num_tokens(sid)
-            ids = cache.get_block_ids(sid)
-            self.h_bt[s, :len(ids)] = torch.as_tensor(ids, dtype=torch.int32)
-            self.h_lens[s] = n
-            self.h_pos[s] = n - 1
-            blk = ids[(n - 1) // bs]
-            self.h_slots[s] = -1 if blk < 0 else blk * bs + (n - 1) % bs
-            max_len = max(max_len, n)
-        self.h_ids[:S] = torch.as_tensor(list(last_tokens), dtype=torch.int32)
+        n_ = self._np
+        max_len = max(1, cache.stage_decode(seq_ids, n_["bt"], n_["lens"], n_["pos"], n_["slots"]))
+        n_["ids"][:S] = last_tokens
         if Sp > S:                                  # padding rows: empty sequences that write nothing
-            self.h_ids[S:Sp] = 0
-            self.h_pos[S:Sp] = 0
-            self.h_slots[S:Sp] = -1
-            self.h_lens[S:Sp] = 0
-        self.h_rows[:Sp] = torch.arange(Sp, dtype=torch.int64)
+            n_["bt"][S:Sp].fill(-1)
+            n_["ids"][S:Sp] = 0
+            n_["pos"][S:Sp] = 0
+            n_["slots"][S:Sp] = -1
+            n_["lens"][S:Sp] = 0
+        n_["rows"][:Sp] = self._arange[:Sp]
         for dst, src, n in ((b.ids, self.h_ids, Sp), (b.positions, self.h_pos, Sp), (b.slots, self.h_slots, Sp),
                             (b.block_tables, self.h_bt, Sp), (b.seq_lens, self.h_lens, Sp),
                             (b.logit_rows, self.h_rows, Sp)):
@@ -281,6 +280,8 @@ class ModelRunner:
             ev[1].record()
             self.step_events.append(ev)
         self.timings["decode_steps"] += 1
+        if defer:
+            return lambda: self._fetch_tokens(Sp)[:S]
         return self._fetch_tokens(Sp)[:S]
 
     def _capture(self, Sp: int, splits: int, greedy: bool) -> "torch.cuda.CUDAGraph":

@@ -147,12 +147,16 @@ class BatchRunner:
 
     # ---- decode -----------------------------------------------------------------------------------------
     def _run_decode(self, reqs: List[InferenceRequest], res: StepResult) -> None:
+        # a request that was extended ahead of time (while the previous step ran on the device) is ready as it is
+        todo = [r for r in reqs if not r.pre_extended]
+        errs = dict(zip((id(r) for r in todo), self._cache.extend_batch([r.seq_id for r in todo])))
         ready = []
         for r in reqs:
-            try:
-                self._cache.extend_sequence(r.seq_id, 1)
+            exc = None if r.pre_extended else errs[id(r)]
+            r.pre_extended = False
+            if exc is None:
                 ready.append(r)
-            except Exception as exc:
+            else:
                 self._fail(r, exc, res)
         if not ready:
             return
@@ -160,10 +164,17 @@ class BatchRunner:
         if any(r.params.repetition_penalty != 1.0 for r in ready):
             pen = [(r.params.repetition_penalty, r.past_tokens) for r in ready]
         try:
-            toks = self._runner.decode([r.seq_id for r in ready], [r.output_tokens[-1] for r in ready],
-                                       sampling=[_sampling_row(r) for r in ready],
-                                       adapters=[self._adapter_slot(r) for r in ready] if self._lora is not None
-                                       else None, penalties=pen)
+            pending = self._runner.decode([r.seq_id for r in ready], [r.output_tokens[-1] for r in ready],
+                                          sampling=[_sampling_row(r) for r in ready],
+                                          adapters=[self._adapter_slot(r) for r in ready] if self._lora is not None
+                                          else None, penalties=pen, defer=True)
+            # host work that overlaps the device step: the cache slot of the token after this one, for every
+            # request that cannot end on this token by length (a stop token frees the sequence, slot included)
+            ahead = [r for r in ready if r.num_generated + 1 < r.params.max_tokens
+                     and r.params.timeout_ms is None]
+            for r, exc in zip(ahead, self._cache.extend_batch([r.seq_id for r in ahead])):
+                r.pre_extended = exc is None
+            toks = pending()
         except Exception as exc:
             for r in ready:
                 self._fail(r, exc, res)

@@ -67,6 +67,7 @@ class InferenceRequest:
     past_tokens: Dict[int, int] = field(default_factory=dict)
     error: Optional[str] = None
     num_preemptions: int = 0
+    pre_extended: bool = False           # the cache slot of the next decode token is already allocated
     # speculative decoding statistics
     spec_drafted: int = 0
     spec_accepted: int = 0
@@ -125,6 +126,7 @@ class InferenceRequest:
 
     def mark_preempted(self) -> None:
         self.state = RequestState.PREEMPTED
+        self.pre_extended = False
         self.num_preemptions += 1
 
     def mark_finished(self, reason: FinishReason) -> None:
