@@ -234,8 +234,21 @@ def run_ours(args):
         }
         print(json.dumps(line), flush=True)
     if world > 1:
+        # the result is out; tear down in the order NCCL wants (graphs that captured its kernels first), and do not
+        # let a teardown that blocks keep the launcher waiting
+        import gc
+        import threading
+        sys.stdout.flush()
+        watchdog = threading.Timer(45.0, lambda: os._exit(0))
+        watchdog.daemon = True
+        watchdog.start()
         dist.barrier()
+        eng.destroy()
+        del eng, runner
+        gc.collect()
+        torch.cuda.synchronize()
         dist.destroy_process_group()
+        watchdog.cancel()
 
 
 def run_reference(args):

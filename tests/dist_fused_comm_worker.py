@@ -29,6 +29,7 @@ def main():
         torch.manual_seed(1234)
         w = (1 + 0.1 * torch.randn(H, device=dev)).half()
         for M, planes in ((1, 1), (64, 3), (200, 2)):
+            torch.manual_seed(77 + M)                    # the residual stream is replicated: same on every rank
             res0 = torch.randn(M, H, device=dev)
             residual = res0.clone()
             torch.manual_seed(100 + rank)

@@ -1,0 +1,197 @@
+"""The serving engine end to end on the CPU path: continuous batching, chunked prefill, prefix sharing, preemption,
+speculative decoding and sampling must all give the tokens of the fp32 oracle model run one sequence at a time
+(greedy), as in the reference's own end-to-end checks (zse-engine/tests/test_zstreamer.py, test_engine.py)."""
+import random
+
+import pytest
+
+from zse_b200.config import EngineConfig
+from zse_b200.engine import GenerateConfig, ZSEEngine, ZStreamerEngine
+from zse_b200.format import synth
+from zse_b200.format.loader import ZSELoader
+from zse_b200.models.oracle import OracleModel
+from zse_b200.sched.request import FinishReason
+
+
+@pytest.fixture(scope="module")
+def model_path(tmp_path_factory):
+    p = str(tmp_path_factory.mktemp("m") / "tiny.zse")
+    synth.write_random_model(p, synth.shape_config("tiny"), seed=3)
+    return p
+
+
+@pytest.fixture(scope="module")
+def oracle(model_path):
+    return OracleModel(ZSELoader(model_path))
+
+
+def _cfg(**kw):
+    base = dict(device="cpu", max_batch_seqs=8, max_seq_len=256, quiet=True)
+    base.update(kw)
+    return EngineConfig(**base)
+
+
+def _prompts(vocab, n, lo=3, hi=40, seed=0):
+    rng = random.Random(seed)
+    return [[rng.randrange(vocab) for _ in range(rng.randint(lo, hi))] for _ in range(n)]
+
+
+def _run(eng, prompts, max_tokens, **kw):
+    ids = [eng.add_request_tokens(p, max_tokens=max_tokens[i] if isinstance(max_tokens, list) else max_tokens,
+                                  temperature=0.0, stop_tokens=[], **kw) for i, p in enumerate(prompts)]
+    assert all(i is not None for i in ids)
+    eng.run_until_done()
+    return [eng.get_result(i) for i in ids]
+
+
+def test_batched_greedy_matches_oracle(model_path, oracle):
+    eng = ZStreamerEngine(model_path, config=_cfg())
+    prompts = _prompts(eng.model_config.vocab_size, 6)
+    lens = [12 + i for i in range(6)]
+    outs = _run(eng, prompts, lens)
+    for p, n, o in zip(prompts, lens, outs):
+        assert o.finish_reason == FinishReason.LENGTH
+        assert o.output_tokens == oracle.greedy(p, n)
+    st = eng.stats()
+    assert st.total_requests == 6 and st.total_tokens_generated == sum(lens)
+    assert eng.kv_cache.num_sequences == 0 and eng.kv_cache.num_free_blocks == eng.kv_cache.num_total_blocks
+    eng.destroy()
+
+
+def test_chunked_prefill_matches_oracle(model_path, oracle):
+    eng = ZStreamerEngine(model_path, config=_cfg(prefill_chunk_size=16, max_batch_tokens=48, decode_per_prefill=1))
+    prompts = _prompts(eng.model_config.vocab_size, 4, lo=30, hi=90, seed=1)
+    outs = _run(eng, prompts, 8)
+    for p, o in zip(prompts, outs):
+        assert o.output_tokens == oracle.greedy(p, 8)
+    eng.destroy()
+
+
+def test_prefix_sharing_gives_same_tokens_and_reuses_blocks(model_path, oracle):
+    eng = ZStreamerEngine(model_path, config=_cfg(block_size=16))
+    V = eng.model_config.vocab_size
+    system = _prompts(V, 1, lo=50, hi=50, seed=2)[0]
+    a, b = system + [1, 2, 3], system + [4, 5]
+    first = _run(eng, [a], 6)[0]
+    hits0 = eng.kv_cache.stats().dedup_hits
+    second = _run(eng, [b], 6)[0]
+    # sequence a was freed, but its registered blocks are only reusable while they are alive: run both together
+    both = _run(eng, [a, b], 6)
+    assert first.output_tokens == oracle.greedy(a, 6) and second.output_tokens == oracle.greedy(b, 6)
+    assert both[0].output_tokens == first.output_tokens and both[1].output_tokens == second.output_tokens
+    assert eng.kv_cache.stats().dedup_hits >= hits0
+    eng.destroy()
+
+
+def test_stop_token_and_cancel(model_path, oracle):
+    eng = ZStreamerEngine(model_path, config=_cfg())
+    p = _prompts(eng.model_config.vocab_size, 1, seed=5)[0]
+    want = oracle.greedy(p, 10)
+    rid = eng.add_request_tokens(p, max_tokens=10, temperature=0.0, stop_tokens=[want[3]])
+    gone = eng.add_request_tokens(p, max_tokens=10, temperature=0.0, stop_tokens=[])
+    eng.cancel_request(gone)
+    eng.run_until_done()
+    out = eng.get_result(rid)
+    first_hit = want.index(want[3])
+    assert out.finish_reason == FinishReason.STOP and out.output_tokens == want[:first_hit + 1]
+    assert eng.get_result(gone).finish_reason == FinishReason.CANCELLED
+    eng.destroy()
+
+
+def test_preemption_under_memory_pressure_keeps_outputs_exact(model_path, oracle):
+    # 14 blocks of 16 tokens: three 40-token requests cannot all keep growing, some are preempted and re-prefilled
+    eng = ZStreamerEngine(model_path, config=_cfg(kv_blocks=14, block_size=16, max_prefill_per_step=4,
+                                                  decode_per_prefill=0, headroom_ratio=0.1))
+    V = eng.model_config.vocab_size
+    prompts = _prompts(V, 3, lo=30, hi=40, seed=7)
+    ids = [eng.add_request_tokens(p, max_tokens=30, temperature=0.0, stop_tokens=[]) for p in prompts]
+    for _ in range(6):
+        eng.step()
+    late = _prompts(V, 1, lo=20, hi=20, seed=8)[0]
+    urgent = eng.add_request_tokens(late, max_tokens=10, temperature=0.0, stop_tokens=[], priority=9)
+    eng.run_until_done()
+    for rid, p in zip(ids, prompts):
+        o = eng.get_result(rid)
+        assert o.finish_reason == FinishReason.LENGTH and o.output_tokens == oracle.greedy(p, 30)
+    assert eng.get_result(urgent).output_tokens == oracle.greedy(late, 10)
+    eng.destroy()
+
+
+@pytest.mark.parametrize("mode", ["ngram", "self"])
+def test_speculative_decoding_is_exact(model_path, oracle, mode):
+    eng = ZStreamerEngine(model_path, config=_cfg(speculative_k=3, speculative_mode=mode))
+    V = eng.model_config.vocab_size
+    rng = random.Random(11)
+    motif = [rng.randrange(V) for _ in range(6)]
+    prompts = [motif * 4 + [rng.randrange(V)], _prompts(V, 1, seed=12)[0]]
+    outs = _run(eng, prompts, 16)
+    # the invariant is "same tokens as the engine without drafting" (the fp16 engine and the fp32 oracle may break a
+    # near tie differently)
+    plain_eng = ZStreamerEngine(model_path, config=_cfg())
+    plain = _run(plain_eng, prompts, 16)
+    for a, b in zip(outs, plain):
+        assert a.output_tokens == b.output_tokens
+    assert outs[1].output_tokens == oracle.greedy(prompts[1], 16)
+    st = eng.stats()
+    assert st.total_tokens_generated == 32
+    eng.destroy(); plain_eng.destroy()
+
+
+def test_sampling_is_seeded_and_respects_top_k_one(model_path, oracle):
+    eng = ZStreamerEngine(model_path, config=_cfg())
+    p = _prompts(eng.model_config.vocab_size, 1, seed=13)[0]
+
+    def sample(seed, **kw):
+        rid = eng.add_request_tokens(p, max_tokens=12, stop_tokens=[], seed=seed, **kw)
+        eng.run_until_done()
+        return eng.get_result(rid).output_tokens
+
+    a = sample(1, temperature=1.5, top_p=1.0, top_k=0)
+    b = sample(1, temperature=1.5, top_p=1.0, top_k=0)
+    c = sample(2, temperature=1.5, top_p=1.0, top_k=0)
+    assert a == b and a != c
+    assert sample(5, temperature=1.0, top_k=1) == oracle.greedy(p, 12)
+    eng.destroy()
+
+
+def test_repetition_penalty_changes_greedy_path(model_path, oracle):
+    eng = ZStreamerEngine(model_path, config=_cfg())
+    p = [5, 6, 7] * 6
+    plain = _run(eng, [p], 12)[0].output_tokens
+    pen = _run(eng, [p], 12, repetition_penalty=3.0)[0].output_tokens
+    assert plain == oracle.greedy(p, 12)
+    assert len(pen) == 12 and pen != plain
+    eng.destroy()
+
+
+def test_queue_full_is_reported(model_path):
+    eng = ZStreamerEngine(model_path, config=_cfg(max_queue_size=2))
+    assert eng.add_request_tokens([1, 2], max_tokens=2) is not None
+    assert eng.add_request_tokens([1, 2], max_tokens=2) is not None
+    assert eng.add_request_tokens([1, 2], max_tokens=2) is None
+    eng.run_until_done()
+    eng.destroy()
+
+
+def test_oversized_prompt_is_refused_and_oversized_generation_fails_cleanly(model_path):
+    eng = ZStreamerEngine(model_path, config=_cfg(max_seq_len=96, kv_blocks=6, block_size=16))
+    with pytest.raises(ValueError):
+        eng.add_request_tokens(list(range(100)), max_tokens=4, temperature=0.0)
+    # fits the context but not the cache (6 blocks minus the reserve): finishes with an error, others still run
+    rid = eng.add_request_tokens(list(range(40)), max_tokens=40, temperature=0.0, stop_tokens=[])
+    ok = eng.add_request_tokens([1, 2, 3], max_tokens=4, temperature=0.0, stop_tokens=[])
+    eng.run_until_done()
+    bad = eng.get_result(rid)
+    assert bad.finish_reason == FinishReason.ERROR and bad.error
+    assert len(eng.get_result(ok).output_tokens) == 4
+    eng.destroy()
+
+
+def test_single_request_engine_text_api(model_path):
+    eng = ZSEEngine(model_path, config=_cfg())
+    text = eng.generate("hello world", GenerateConfig(max_tokens=8, temperature=0.0, stop_tokens=[]))
+    pieces = list(eng.stream_generate("hello world", GenerateConfig(max_tokens=8, temperature=0.0, stop_tokens=[])))
+    assert isinstance(text, str) and "".join(pieces) == text
+    st = eng.stats()
+    assert st.generated_tokens > 0 and st.prompt_tokens > 0
+    eng.destroy()

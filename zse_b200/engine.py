@@ -233,7 +233,13 @@ class ZStreamerEngine:
         return d
 
     def cancel_request(self, request_id: str) -> None:
-        self._scheduler.cancel_request(request_id)
+        r = self._scheduler.cancel_request(request_id)
+        if r is not None:                       # cancelled while waiting: no step will report it
+            out = RequestOutput.from_request(r)
+            with self._lock:
+                self._completed[out.request_id] = out
+            if r.on_finish is not None:
+                r.on_finish(out)
 
     def step(self) -> StepResult:
         """One scheduling + execution iteration; returns what happened (idle steps return an empty result)."""
@@ -314,6 +320,12 @@ class ZStreamerEngine:
 
     def destroy(self) -> None:
         self.stop()
+        runner = getattr(self, "_runner", None)
+        if runner is not None:
+            runner.release_graphs()
+        comm = getattr(getattr(self, "_model", None), "comm", None)
+        if comm is not None and hasattr(comm, "close"):
+            comm.close()
         for name in ("_kv_cache",):
             obj = getattr(self, name, None)
             if obj is not None:

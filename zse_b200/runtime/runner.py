@@ -128,11 +128,11 @@ class ModelRunner:
     def _select(self, n_rows: int, greedy: bool) -> None:
         b, ops = self.buf, self.model.ops
         if self.model.comm is not None:
-            self.model.comm.select_tokens(self, n_rows, greedy, self._step)
+            self.model.comm.select_tokens(self, n_rows, greedy, 0)
         elif greedy:
             ops.argmax(b.logits, b.out_tokens, n_rows)
         else:
-            ops.sample(b.logits, b.out_tokens, n_rows, b.temperature, b.top_k, b.top_p, b.seeds, self._step)
+            ops.sample(b.logits, b.out_tokens, n_rows, b.temperature, b.top_k, b.top_p, b.seeds, 0)
 
     def _fetch_tokens(self, n: int) -> List[int]:
         self.h_out[:n].copy_(self.buf.out_tokens[:n], non_blocking=True)
@@ -303,6 +303,12 @@ class ModelRunner:
         self._graph_launches[(Sp, splits, greedy)] = counter[0] - n0
         self.timings["graph_captures"] += 1
         return g
+
+    def release_graphs(self) -> None:
+        """Drops every captured decode graph.  Graphs that captured NCCL kernels keep their communicator busy, so
+        this has to happen before the process group is destroyed."""
+        self._graphs.clear()
+        self._graph_launches.clear()
 
     def _launch_counter(self):
         if self.device.type == "cuda":

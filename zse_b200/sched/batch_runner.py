@@ -29,8 +29,14 @@ def _sampling_row(r: InferenceRequest) -> SamplingRow:
     p = r.params
     if p.greedy:
         return SamplingRow()
-    seed = p.seed if p.seed is not None else (hash(r.request_id) & 0x7FFFFFFF)
-    return SamplingRow(float(p.temperature), int(p.top_k), float(p.top_p), int(seed))
+    base = p.seed if p.seed is not None else (hash(r.request_id) & 0x7FFFFFFF)
+    # one random stream per request, indexed by the token's position in the output: a seeded request gives the same
+    # tokens whatever else is in the batch, and a replayed CUDA graph (whose scalar arguments are frozen) still draws
+    # fresh numbers because the per-row seed is staged from the host every step
+    z = (int(base) + (r.num_generated + 1) * 0x9E3779B97F4A7C15) & 0xFFFFFFFFFFFFFFFF
+    z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & 0xFFFFFFFFFFFFFFFF
+    z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & 0xFFFFFFFFFFFFFFFF
+    return SamplingRow(float(p.temperature), int(p.top_k), float(p.top_p), int((z ^ (z >> 31)) & 0x7FFFFFFFFFFFFFFF))
 
 
 class BatchRunner:

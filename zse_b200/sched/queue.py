@@ -58,8 +58,21 @@ class RequestQueue:
                 return r
         return None
 
+    def _peek_live(self, heap: List[tuple]) -> Optional[InferenceRequest]:
+        while heap:
+            r = heap[0][-1]
+            if self._live.get(r.request_id) is r and not r.is_finished:
+                return r
+            heapq.heappop(heap)
+        return None
+
     def pop_next(self) -> Optional[InferenceRequest]:
+        """Preempted requests come back before new ones, except when a new request outranks them: the request
+        that a preemption made room for must not lose that room to the request it displaced."""
         with self._lock:
+            p, w = self._peek_live(self._preempted), self._peek_live(self._waiting)
+            if p is not None and w is not None and w.priority > p.priority:
+                return self._pop_live(self._waiting)
             return self._pop_live(self._preempted) or self._pop_live(self._waiting)
 
     def pop_prefill_batch(self, max_requests: int, max_tokens: int) -> List[InferenceRequest]:

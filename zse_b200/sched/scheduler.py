@@ -93,9 +93,12 @@ class Scheduler:
     def add_request(self, request: InferenceRequest) -> bool:
         return self._queue.add(request)
 
-    def cancel_request(self, request_id: str) -> None:
-        if self._queue.cancel(request_id) is not None:
-            return
+    def cancel_request(self, request_id: str):
+        """A waiting request leaves the queue at once and is returned (it will never be part of a step, so the
+        caller reports its result); an active one is marked and leaves with the next step."""
+        r = self._queue.cancel(request_id)
+        if r is not None:
+            return r
         with self._lock:
             r = self._active.get(request_id)
             if r is not None and not r.is_finished:
@@ -181,9 +184,11 @@ class Scheduler:
                 r.mark_finished(FinishReason.ERROR)
                 out.finished_requests.append(r)
                 continue
-            if not self._budget.can_admit(r):
+            if not self._budget.can_admit(r) and self._active:
                 rejected.append(r)
                 break
+            # with nothing else running the request is admitted even if its head-room estimate does not fit: it
+            # passed fits_at_all, and waiting for memory that nobody holds would never end
             if r.seq_id is None:
                 r.seq_id = self._next_seq_id()
             self._budget.reserve(r)
