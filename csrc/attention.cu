@@ -534,3 +534,56 @@ extern "C" int zse_attn_prefill(const void* q, int ldq, const void* kv_layer, co
                               nh, nkv, block_size, scale, st);
   return ZSE_ERR_SHAPE;
 }
+
+// ---- decode attention with library-owned scratch (attn_decode_static.h) -------------------------------------------
+#include "attn_decode_static.h"
+
+static __device__ __align__(256) float g_attn_static_scratch[ZSE_ATTN_STATIC_SCRATCH_FLOATS];
+
+namespace {
+constexpr int kMaxStaticDevices = 64;
+float* g_static_scratch_ptr[kMaxStaticDevices] = {};
+
+// address of the scratch array on the current device, looked up once per device; nullptr with *err set on failure
+float* static_scratch(int* err) {
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxStaticDevices) {
+    *err = ZSE_ERR_DRIVER;
+    return nullptr;
+  }
+  if (g_static_scratch_ptr[dev] == nullptr) {
+    float* p = nullptr;
+    if (cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_attn_static_scratch) != cudaSuccess || p == nullptr) {
+      (void)cudaGetLastError();
+      *err = ZSE_ERR_DRIVER;
+      return nullptr;
+    }
+    g_static_scratch_ptr[dev] = p;
+  }
+  *err = 0;
+  return g_static_scratch_ptr[dev];
+}
+}  // namespace
+
+extern "C" int64_t zse_attn_decode_static_max_floats(void) { return ZSE_ATTN_STATIC_SCRATCH_FLOATS; }
+
+extern "C" int zse_attn_decode_static_setup(void) {
+  int err = 0;
+  static_scratch(&err);
+  return err;
+}
+
+extern "C" int zse_attn_decode_static(const void* q, int ldq, const void* kv_layer, const void* block_tables,
+                                      int max_blocks, const void* seq_lens, void* out, int ldo, int num_seqs, int nh,
+                                      int nkv, int hd, int block_size, int num_splits, float scale, void* stream) {
+  if (num_seqs <= 0) return 0;
+  if (num_splits < 1 || nh <= 0 || hd <= 0) return ZSE_ERR_SHAPE;
+  if (num_splits > 1 &&
+      zse_attn_decode_scratch_floats(num_seqs, nh, hd, num_splits) > int64_t(ZSE_ATTN_STATIC_SCRATCH_FLOATS))
+    return ZSE_ERR_LIMIT;
+  int err = 0;
+  float* scratch = static_scratch(&err);
+  if (scratch == nullptr) return err;
+  return zse_attn_decode(q, ldq, kv_layer, block_tables, max_blocks, seq_lens, out, ldo, scratch, num_seqs, nh, nkv,
+                         hd, block_size, num_splits, scale, stream);
+}
