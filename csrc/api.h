@@ -15,6 +15,11 @@
 extern "C" {
 #endif
 
+// ---- runtime.cu ---------------------------------------------------------------------------------------------
+// Programmatic dependent launch for the kernels of the decode path (on by default; ZSE_PDL=0 switches it off).
+void zse_set_pdl(int on);
+int zse_get_pdl(void);
+
 // ---- gemm.cu ------------------------------------------------------------------------------------------------
 // epilogue: 0 = fp16 store (+bias), 1 = SwiGLU (N counts gate+up rows, output has N/2 columns), 2 = fp32 partial planes
 int zse_gemm_w4(const void* w_tiled, const void* x, int x_rows_cap, const void* bias, void* out, int M, int N, int K,

@@ -68,6 +68,8 @@ attn_decode_kernel(const __half* __restrict__ q, int ldq, const __half* __restri
   constexpr int kKSteps = HD / 16;
   constexpr int kNTilesO = HD / 8;
   extern __shared__ __align__(128) uint8_t smem[];
+  pdl_launch_dependents();
+  pdl_wait();
   const int kvh = blockIdx.x, seq = blockIdx.y, split = blockIdx.z;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int G = nh / nkv;
@@ -262,6 +264,8 @@ attn_decode_kernel(const __half* __restrict__ q, int ldq, const __half* __restri
 template <int HD>
 __global__ void attn_combine_kernel(const float* __restrict__ scratch, __half* __restrict__ out, int ldo, int nh,
                                     int num_splits) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int head = blockIdx.x, seq = blockIdx.y, d = threadIdx.x;
   const float* src = scratch + size_t(seq * nh + head) * num_splits * (HD + 2);
   float M = -INFINITY;
@@ -472,15 +476,16 @@ static int launch_decode(const void* q, int ldq, const void* kv, const void* bt,
     attr = true;
   }
   dim3 grid(nkv, num_seqs, splits);
-  attn_decode_kernel<HD><<<grid, kDecWarps * 32, smem, st>>>(
-      reinterpret_cast<const __half*>(q), ldq, reinterpret_cast<const __half*>(kv), reinterpret_cast<const int*>(bt),
-      max_blocks, reinterpret_cast<const int*>(lens), reinterpret_cast<__half*>(out), ldo,
-      reinterpret_cast<float*>(scratch), nh, nkv, block_size, splits, scale * kLog2e);
-  if (cudaGetLastError() != cudaSuccess) return ZSE_ERR_LAUNCH;
+  if (launch_pdl(attn_decode_kernel<HD>, grid, dim3(kDecWarps * 32), smem, st, reinterpret_cast<const __half*>(q),
+                 ldq, reinterpret_cast<const __half*>(kv), reinterpret_cast<const int*>(bt), max_blocks,
+                 reinterpret_cast<const int*>(lens), reinterpret_cast<__half*>(out), ldo,
+                 reinterpret_cast<float*>(scratch), nh, nkv, block_size, splits, scale * kLog2e) != cudaSuccess)
+    return ZSE_ERR_LAUNCH;
   if (splits > 1) {
-    attn_combine_kernel<HD><<<dim3(nh, num_seqs), HD, 0, st>>>(reinterpret_cast<const float*>(scratch),
-                                                                reinterpret_cast<__half*>(out), ldo, nh, splits);
-    if (cudaGetLastError() != cudaSuccess) return ZSE_ERR_LAUNCH;
+    if (launch_pdl(attn_combine_kernel<HD>, dim3(nh, num_seqs), dim3(HD), 0, st,
+                   reinterpret_cast<const float*>(scratch), reinterpret_cast<__half*>(out), ldo, nh,
+                   splits) != cudaSuccess)
+      return ZSE_ERR_LAUNCH;
   }
   return 0;
 }

@@ -36,6 +36,15 @@ __device__ __forceinline__ void report(Status* st, unsigned code, unsigned where
   }
 }
 
+// ---- programmatic dependent launch ----------------------------------------------------------------------------
+// A kernel launched with launch_pdl() may start while the kernel before it on the stream is still running.
+// pdl_wait() returns once that kernel has finished and its writes are visible: everything a kernel reads from or
+// writes to memory that an earlier kernel of the stream touches has to come after it.  Work that only needs
+// constant data (weights, tensor maps, barrier set-up, TMEM allocation) may come before.  Both calls do nothing in a
+// kernel that was launched the ordinary way.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;"); }
+
 __device__ __forceinline__ uint64_t globaltimer_ns() {
   uint64_t t;
   asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -225,5 +234,24 @@ __device__ __forceinline__ uint32_t pack_half2(float a, float b) {
 }
 __device__ __forceinline__ float silu_f(float g) { return g / (1.0f + __expf(-g)); }
 __device__ __forceinline__ float clamp_f16(float v) { return fminf(fmaxf(v, -65504.0f), 65504.0f); }
+
+// ---- host side: launch with the programmatic-serialization attribute (see pdl_wait) ---------------------------
+int pdl_enabled();   // runtime.cu; 1 unless switched off by zse_set_pdl(0) or ZSE_PDL=0
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                              Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);
+}
 
 }  // namespace zse

@@ -10,6 +10,8 @@ namespace zse {
 // ---- embedding gather: fp16 table row -> fp32 residual row -----------------------------------------------
 __global__ void embedding_kernel(const __half* __restrict__ table, const int* __restrict__ ids,
                                  float* __restrict__ out, int H, int vocab, float scale, Status* st) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int row = blockIdx.x;
   int id = ids[row];
   if (id < 0 || id >= vocab) {
@@ -50,6 +52,8 @@ add_rmsnorm_kernel(float* __restrict__ residual, const float* __restrict__ parti
                    const __half* __restrict__ add_f16, const __half* __restrict__ weight, __half* __restrict__ out,
                    int M, int H, float eps) {
   __shared__ float red[32];
+  pdl_launch_dependents();
+  pdl_wait();
   const int row = blockIdx.x;
   const size_t base = size_t(row) * H;
   const size_t plane = size_t(M) * H;
@@ -120,6 +124,8 @@ __global__ void rope_kv_write_kernel(__half* __restrict__ qkv, __half* __restric
                                      const float* __restrict__ inv_freq, int nh, int nkv, int hd, int rotary_dim,
                                      int block_size, const float* __restrict__ planes, int n_planes, int M,
                                      const __half* __restrict__ bias) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x, head = blockIdx.y;
   const int ld = (nh + 2 * nkv) * hd;
   __half* row = qkv + size_t(t) * ld + size_t(head) * hd;
@@ -207,21 +213,19 @@ extern "C" int zse_embedding(const void* table, const void* ids, void* out, int 
                              void* status, void* stream) {
   if (M <= 0) return 0;
   if (H % 8) return ZSE_ERR_SHAPE;
-  embedding_kernel<<<M, 128, 0, ST(stream)>>>(reinterpret_cast<const __half*>(table),
-                                              reinterpret_cast<const int*>(ids), reinterpret_cast<float*>(out), H,
-                                              vocab, scale, reinterpret_cast<Status*>(status));
-  return LAUNCH_OK();
+  return launch_pdl(embedding_kernel, dim3(M), dim3(128), 0, ST(stream), reinterpret_cast<const __half*>(table),
+                    reinterpret_cast<const int*>(ids), reinterpret_cast<float*>(out), H, vocab, scale,
+                    reinterpret_cast<Status*>(status)) == cudaSuccess ? 0 : ZSE_ERR_LAUNCH;
 }
 
 extern "C" int zse_add_rmsnorm(void* residual, const void* partials, int n_partials, const void* add_f16,
                                const void* weight, void* out, int M, int H, float eps, void* stream) {
   if (M <= 0) return 0;
   if (H % 4 || H > 4 * kNormThreads * kNormMaxVec) return ZSE_ERR_SHAPE;
-  add_rmsnorm_kernel<<<M, kNormThreads, 0, ST(stream)>>>(
-      reinterpret_cast<float*>(residual), reinterpret_cast<const float*>(partials), n_partials,
-      reinterpret_cast<const __half*>(add_f16), reinterpret_cast<const __half*>(weight),
-      reinterpret_cast<__half*>(out), M, H, eps);
-  return LAUNCH_OK();
+  return launch_pdl(add_rmsnorm_kernel, dim3(M), dim3(kNormThreads), 0, ST(stream),
+                    reinterpret_cast<float*>(residual), reinterpret_cast<const float*>(partials), n_partials,
+                    reinterpret_cast<const __half*>(add_f16), reinterpret_cast<const __half*>(weight),
+                    reinterpret_cast<__half*>(out), M, H, eps) == cudaSuccess ? 0 : ZSE_ERR_LAUNCH;
 }
 
 extern "C" int zse_rmsnorm_f16(const void* x, const void* weight, void* out, int M, int H, float eps, void* stream) {
@@ -238,15 +242,11 @@ extern "C" int zse_rope_kv_write(void* qkv, void* kv_layer, const void* position
   if (M <= 0) return 0;
   if (hd % 2 || hd > 2048 || rotary_dim % 2 || rotary_dim > hd || (hd - rotary_dim) % 2) return ZSE_ERR_SHAPE;
   dim3 grid(M, nh + 2 * nkv);
-  rope_kv_write_kernel<<<grid, hd / 2, 0, ST(stream)>>>(reinterpret_cast<__half*>(qkv),
-                                                        reinterpret_cast<__half*>(kv_layer),
-                                                        reinterpret_cast<const int*>(positions),
-                                                        reinterpret_cast<const long long*>(slots),
-                                                        reinterpret_cast<const float*>(inv_freq), nh, nkv, hd,
-                                                        rotary_dim, block_size,
-                                                        reinterpret_cast<const float*>(planes), n_planes, M,
-                                                        reinterpret_cast<const __half*>(bias));
-  return LAUNCH_OK();
+  return launch_pdl(rope_kv_write_kernel, grid, dim3(hd / 2), 0, ST(stream), reinterpret_cast<__half*>(qkv),
+                    reinterpret_cast<__half*>(kv_layer), reinterpret_cast<const int*>(positions),
+                    reinterpret_cast<const long long*>(slots), reinterpret_cast<const float*>(inv_freq), nh, nkv, hd,
+                    rotary_dim, block_size, reinterpret_cast<const float*>(planes), n_planes, M,
+                    reinterpret_cast<const __half*>(bias)) == cudaSuccess ? 0 : ZSE_ERR_LAUNCH;
 }
 
 extern "C" int zse_swiglu(const void* gate_up, void* out, int M, int I, int gelu, void* stream) {

@@ -127,6 +127,7 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   PipeBars* bars = reinterpret_cast<PipeBars*>(smem + S * Cfg::kStageBytes);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  pdl_launch_dependents();
   const int s_begin = blockIdx.z * a.stages_per_split;
   const int n_iter = min(a.k_stages, s_begin + a.stages_per_split) - s_begin;
 
@@ -154,6 +155,7 @@ gemm_f16_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_constan
   if (warp == 0) {
     if (lane == 0) {
       int issued = 0;
+      pdl_wait();                                        // the activations come from the previous kernel
       for (int it = 0; it < n_iter; ++it) {
         const int s = it % S;
         if (it >= S && !mbar_wait(&bars->empty[s], ((it / S) - 1) & 1, abort_flag, a.status, 11, it)) break;
@@ -269,8 +271,9 @@ static int launch_f16(const CUtensorMap& tw, const CUtensorMap& tx, const GemmAr
       return ZSE_ERR_LAUNCH;
     attr_done = true;
   }
-  kern<<<grid, kGemmThreads, F16Cfg<NT>::kSmemBytes, st>>>(tw, tx, a);
-  return cudaGetLastError() == cudaSuccess ? 0 : ZSE_ERR_LAUNCH;
+  return launch_pdl(kern, grid, dim3(kGemmThreads), size_t(F16Cfg<NT>::kSmemBytes), st, tw, tx, a) == cudaSuccess
+             ? 0
+             : ZSE_ERR_LAUNCH;
 }
 
 }  // namespace zse

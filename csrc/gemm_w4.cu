@@ -152,6 +152,10 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4Args a) {
   float* park = reinterpret_cast<float*>(smem);              // reused after the main loop: [R*NT cols][128 rows]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // The next kernel of the stream may start its own set-up now.  This kernel in turn starts before the one ahead
+  // of it has finished: barrier set-up, the TMEM allocation and the weight stream (constant data) run at once,
+  // while the activation producer and the epilogue wait for the producer of the activations (pdl_wait below).
+  pdl_launch_dependents();
   const int s_begin = blockIdx.z * a.stages_per_split;
   const int n_k = max(0, min(a.k_stages, s_begin + a.stages_per_split) - s_begin);
   const int n_units = n_k * R;
@@ -215,6 +219,7 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4Args a) {
     if (lane == 0) {
       int issued = 0, s = 0;
       uint32_t ph = 1;
+      pdl_wait();                                        // the activations come from the previous kernel
       for (int kk = 0; kk < n_k; ++kk) {
         if (kk >= SX) {
           // tied: the commit that ends the pair holding this stage's last chunk frees the stage as well
@@ -343,6 +348,7 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4Args a) {
   // one verdict for the whole CTA, so that paired warps never disagree about taking part in the exchange barriers
   const bool dq_role = warp >= 2 && warp < 2 + kDqWarps;
   acc_ok = __syncthreads_and(dq_role ? int(acc_ok) : 1) != 0;
+  pdl_wait();                                            // output buffers may still be read by the previous kernel
   const int ks = a.cluster_k;
   const bool in_cluster = ks > 1;
   const uint32_t crank = in_cluster ? cluster_ctarank() : 0u;
@@ -463,13 +469,15 @@ static int launch_w4(const CUtensorMap& tx, const W4Args& a, dim3 grid, cudaStre
   cfg.blockDim = dim3(kW4Threads);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
   attr[0].id = cudaLaunchAttributeClusterDimension;
   attr[0].val.clusterDim.x = 1;
   attr[0].val.clusterDim.y = 1;
   attr[0].val.clusterDim.z = a.cluster_k;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = 1;
+  cfg.numAttrs = pdl_enabled() ? 2 : 1;
   return cudaLaunchKernelEx(&cfg, kern, tx, a) == cudaSuccess ? 0 : ZSE_ERR_LAUNCH;
 }
 

@@ -1,5 +1,6 @@
 // Small host-side services of the library: status word readback, device facts, build string.
 #include <cuda_runtime.h>
+#include <stdlib.h>
 
 #include "api.h"
 
@@ -21,5 +22,19 @@ extern "C" int zse_device_info(int* sm_count, int* cc_major, int* cc_minor, int6
   *free_mem = int64_t(f);
   return 0;
 }
+
+namespace zse {
+static int g_pdl = -1;
+int pdl_enabled() {
+  if (g_pdl < 0) {
+    const char* e = getenv("ZSE_PDL");
+    g_pdl = (e != nullptr && e[0] == '0') ? 0 : 1;
+  }
+  return g_pdl;
+}
+}  // namespace zse
+
+extern "C" void zse_set_pdl(int on) { zse::g_pdl = on ? 1 : 0; }
+extern "C" int zse_get_pdl(void) { return zse::pdl_enabled(); }
 
 extern "C" const char* zse_build_info(void) { return "zse_b200 native library, sm_100a, " __DATE__ " " __TIME__; }

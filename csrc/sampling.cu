@@ -71,6 +71,8 @@ __device__ __forceinline__ unsigned long long row_argmax(const __half* row, int 
 __global__ void __launch_bounds__(kSampleThreads)
 argmax_kernel(const __half* __restrict__ logits, int ld, int* __restrict__ out, int V) {
   __shared__ unsigned long long red[32];
+  pdl_launch_dependents();
+  pdl_wait();
   const unsigned long long b = row_argmax(logits + size_t(blockIdx.x) * ld, V, red);
   if (threadIdx.x == 0) out[blockIdx.x] = int(0xFFFFFFFFu - unsigned(b & 0xFFFFFFFFull));
 }
@@ -269,9 +271,10 @@ using namespace zse;
 
 extern "C" int zse_argmax(const void* logits, int ld, void* out, int M, int V, void* stream) {
   if (M <= 0) return 0;
-  argmax_kernel<<<M, kSampleThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
-      reinterpret_cast<const __half*>(logits), ld, reinterpret_cast<int*>(out), V);
-  return cudaGetLastError() == cudaSuccess ? 0 : ZSE_ERR_LAUNCH;
+  return launch_pdl(argmax_kernel, dim3(M), dim3(kSampleThreads), 0, reinterpret_cast<cudaStream_t>(stream),
+                    reinterpret_cast<const __half*>(logits), ld, reinterpret_cast<int*>(out), V) == cudaSuccess
+             ? 0
+             : ZSE_ERR_LAUNCH;
 }
 
 extern "C" int zse_sample(const void* logits, int ld, void* out, int M, int V, const void* temperature,

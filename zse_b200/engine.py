@@ -11,6 +11,7 @@ re-tiled on the device, then step buffers and the KV cache are sized from what i
 """
 from __future__ import annotations
 
+import sys
 import threading
 import time
 from collections import deque
@@ -141,7 +142,7 @@ class ZStreamerEngine:
         if not self._quiet:
             print(f"[zse] ready in {self.init_times['total']:.2f}s (open {self.init_times['open']:.2f}, weights "
                   f"{self.init_times['weights']:.2f}, runtime {self.init_times['runtime']:.2f}); "
-                  f"{self._kv_cache.summary()}")
+                  f"{self._kv_cache.summary()}", file=sys.stderr)
 
     # ---- public API -------------------------------------------------------------------------------------
     @property

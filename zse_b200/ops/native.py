@@ -75,6 +75,8 @@ _SIGS = {
     "zse_status_read": (c_int, [c_void_p, POINTER(c_uint32)]),
     "zse_device_info": (c_int, [POINTER(c_int), POINTER(c_int), POINTER(c_int), POINTER(c_int64), POINTER(c_int64)]),
     "zse_build_info": (c_char_p, []),
+    "zse_set_pdl": (None, [c_int]),
+    "zse_get_pdl": (c_int, []),
 }
 
 
@@ -296,6 +298,15 @@ def device_info() -> dict:
     sm, maj, mnr, tot, free = c_int(), c_int(), c_int(), c_int64(), c_int64()
     _ck(load().zse_device_info(sm, maj, mnr, tot, free), "device_info", 0)
     return {"sm_count": sm.value, "cc": (maj.value, mnr.value), "total_mem": tot.value, "free_mem": free.value}
+
+
+def set_pdl(on: bool) -> None:
+    """Programmatic dependent launch between the kernels of a step (on by default, ``ZSE_PDL=0`` switches it off)."""
+    load().zse_set_pdl(1 if on else 0)
+
+
+def pdl_enabled() -> bool:
+    return bool(load().zse_get_pdl())
 
 
 def build_info() -> str:
