@@ -126,7 +126,20 @@ tp_reduce_add_rmsnorm_kernel(const TpTable tb, const TpReduceArgs a) {
     const int c = threadIdx.x + j * kRedThreads;
     if (c < nch) {
       float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-      for (int p = 0; p < a.n_planes; ++p) {
+      // the first eight planes are loaded together (predicated, unrolled) so that the loads overlap
+      float4 px[8], py[8];
+#pragma unroll
+      for (int p = 0; p < 8; ++p) {
+        const float4* src = reinterpret_cast<const float4*>(me.partials + p * plane + size_t(row) * H) + 2 * c;
+        px[p] = p < a.n_planes ? __ldcs(src) : make_float4(0, 0, 0, 0);
+        py[p] = p < a.n_planes ? __ldcs(src + 1) : make_float4(0, 0, 0, 0);
+      }
+#pragma unroll
+      for (int p = 0; p < 8; ++p) {
+        v[0] += px[p].x; v[1] += px[p].y; v[2] += px[p].z; v[3] += px[p].w;
+        v[4] += py[p].x; v[5] += py[p].y; v[6] += py[p].z; v[7] += py[p].w;
+      }
+      for (int p = 8; p < a.n_planes; ++p) {
         const float4* src = reinterpret_cast<const float4*>(me.partials + p * plane + size_t(row) * H) + 2 * c;
         const float4 x = src[0], y = src[1];
         v[0] += x.x; v[1] += x.y; v[2] += x.z; v[3] += x.w;

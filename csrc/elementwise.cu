@@ -47,30 +47,50 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
   return t;
 }
 
+// A row is split over the CTAs of a thread-block cluster (gridDim.x = cluster size, 1..8): each CTA owns H/cs
+// columns, the sum of squares is combined through distributed shared memory.  With few rows (a decode step has
+// <= 64) one CTA per row would leave most SMs idle and make every SM pull a whole row of every plane by itself.
+constexpr int kNormMaxPlanes = 8;
+
 __global__ void __launch_bounds__(kNormThreads)
 add_rmsnorm_kernel(float* __restrict__ residual, const float* __restrict__ partials, int n_partials,
                    const __half* __restrict__ add_f16, const __half* __restrict__ weight, __half* __restrict__ out,
                    int M, int H, float eps) {
   __shared__ float red[32];
+  __shared__ float cluster_ss;
   pdl_launch_dependents();
   pdl_wait();
-  const int row = blockIdx.x;
+  const int row = blockIdx.y;
+  const int cs = gridDim.x;                          // CTAs per row (= cluster size)
   const size_t base = size_t(row) * H;
   const size_t plane = size_t(M) * H;
-  const int nvec = H / 4;
+  const int nvec_cta = H / 4 / cs;                   // float4 per CTA
+  const int vec0 = blockIdx.x * nvec_cta;
   float4 v[kNormMaxVec];
   float ss = 0.f;
 #pragma unroll
   for (int j = 0; j < kNormMaxVec; ++j) {
-    const int i = threadIdx.x + j * kNormThreads;
-    if (i < nvec) {
+    const int li = threadIdx.x + j * kNormThreads;
+    if (li < nvec_cta) {
+      const int i = vec0 + li;
+      // all loads of this vector are issued before the first add: one DRAM round trip instead of one per plane
+      float4 y[kNormMaxPlanes];
+#pragma unroll
+      for (int p = 0; p < kNormMaxPlanes; ++p)
+        y[p] = p < n_partials ? __ldcs(reinterpret_cast<const float4*>(partials + p * plane + base) + i)
+                              : make_float4(0, 0, 0, 0);
       float4 x = residual != nullptr ? reinterpret_cast<const float4*>(residual + base)[i] : make_float4(0, 0, 0, 0);
-      for (int p = 0; p < n_partials; ++p) {
-        const float4 y = reinterpret_cast<const float4*>(partials + p * plane + base)[i];
-        x.x += y.x; x.y += y.y; x.z += y.z; x.w += y.w;
+      uint2 raw = make_uint2(0, 0);
+      if (add_f16 != nullptr) raw = reinterpret_cast<const uint2*>(add_f16 + base)[i];
+#pragma unroll
+      for (int p = 0; p < kNormMaxPlanes; ++p) {
+        x.x += y[p].x; x.y += y[p].y; x.z += y[p].z; x.w += y[p].w;
+      }
+      for (int p = kNormMaxPlanes; p < n_partials; ++p) {
+        const float4 z = reinterpret_cast<const float4*>(partials + p * plane + base)[i];
+        x.x += z.x; x.y += z.y; x.z += z.z; x.w += z.w;
       }
       if (add_f16 != nullptr) {
-        const uint2 raw = reinterpret_cast<const uint2*>(add_f16 + base)[i];
         const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
         const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
         x.x += a.x; x.y += a.y; x.z += b.x; x.w += b.y;
@@ -81,12 +101,29 @@ add_rmsnorm_kernel(float* __restrict__ residual, const float* __restrict__ parti
       ss += x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w;
     }
   }
-  if (out == nullptr) return;
-  const float inv = rsqrtf(block_sum(ss, red) / float(H) + eps);
+  if (out == nullptr) return;                        // uniform over the cluster: no CTA waits for one that left
+  float total = block_sum(ss, red);
+  if (cs > 1) {
+    if (threadIdx.x == 0) cluster_ss = total;
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+    total = 0.f;
+    const uint32_t local = smem_u32(&cluster_ss);
+    for (int r = 0; r < cs; ++r) {                   // same order in every CTA: identical sums
+      uint32_t remote;
+      float t;
+      asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(r));
+      asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(t) : "r"(remote) : "memory");
+      total += t;
+    }
+    // nobody exits while its value may still be read
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+  }
+  const float inv = rsqrtf(total / float(H) + eps);
 #pragma unroll
   for (int j = 0; j < kNormMaxVec; ++j) {
-    const int i = threadIdx.x + j * kNormThreads;
-    if (i < nvec) {
+    const int li = threadIdx.x + j * kNormThreads;
+    if (li < nvec_cta) {
+      const int i = vec0 + li;
       const uint2 wr = reinterpret_cast<const uint2*>(weight)[i];
       const float2 w0 = __half22float2(*reinterpret_cast<const __half2*>(&wr.x));
       const float2 w1 = __half22float2(*reinterpret_cast<const __half2*>(&wr.y));
@@ -145,7 +182,20 @@ __global__ void rope_kv_write_kernel(__half* __restrict__ qkv, __half* __restric
     const size_t off = size_t(t) * ld + size_t(head) * hd;
     a = bias != nullptr ? __half2float(bias[head * hd + ia]) : 0.f;
     b = bias != nullptr ? __half2float(bias[head * hd + ib]) : 0.f;
-    for (int p = 0; p < n_planes; ++p) {
+    // loads of all planes first (predicated, fully unrolled), adds after: one memory round trip
+    float pa[kNormMaxPlanes], pb[kNormMaxPlanes];
+#pragma unroll
+    for (int p = 0; p < kNormMaxPlanes; ++p) {
+      const float* src = planes + size_t(p) * M * ld + off;
+      pa[p] = p < n_planes ? __ldcs(src + ia) : 0.f;
+      pb[p] = p < n_planes ? __ldcs(src + ib) : 0.f;
+    }
+#pragma unroll
+    for (int p = 0; p < kNormMaxPlanes; ++p) {
+      a += pa[p];
+      b += pb[p];
+    }
+    for (int p = kNormMaxPlanes; p < n_planes; ++p) {
       const float* src = planes + size_t(p) * M * ld + off;
       a += src[ia];
       b += src[ib];
@@ -222,10 +272,28 @@ extern "C" int zse_add_rmsnorm(void* residual, const void* partials, int n_parti
                                const void* weight, void* out, int M, int H, float eps, void* stream) {
   if (M <= 0) return 0;
   if (H % 4 || H > 4 * kNormThreads * kNormMaxVec) return ZSE_ERR_SHAPE;
-  return launch_pdl(add_rmsnorm_kernel, dim3(M), dim3(kNormThreads), 0, ST(stream),
-                    reinterpret_cast<float*>(residual), reinterpret_cast<const float*>(partials), n_partials,
-                    reinterpret_cast<const __half*>(add_f16), reinterpret_cast<const __half*>(weight),
-                    reinterpret_cast<__half*>(out), M, H, eps) == cudaSuccess ? 0 : ZSE_ERR_LAUNCH;
+  // CTAs per row: enough to put >= ~2 CTAs on every SM for small M, and few enough that H/4 splits evenly
+  int cs = 1;
+  while (cs < 8 && M * cs < 256 && (H / 4) % (cs * 2) == 0 && H / 4 / (cs * 2) >= 64) cs *= 2;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(cs, M);
+  cfg.blockDim = dim3(kNormThreads);
+  cfg.stream = ST(stream);
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = cs;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 2 : 1;
+  return cudaLaunchKernelEx(&cfg, add_rmsnorm_kernel, reinterpret_cast<float*>(residual),
+                            reinterpret_cast<const float*>(partials), n_partials,
+                            reinterpret_cast<const __half*>(add_f16), reinterpret_cast<const __half*>(weight),
+                            reinterpret_cast<__half*>(out), M, H, eps) == cudaSuccess
+             ? 0
+             : ZSE_ERR_LAUNCH;
 }
 
 extern "C" int zse_rmsnorm_f16(const void* x, const void* weight, void* out, int M, int H, float eps, void* stream) {

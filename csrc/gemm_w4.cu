@@ -28,32 +28,41 @@
 
 namespace zse {
 
-constexpr int kW4Threads = 608;        // 19 warps
-constexpr int kDqWarps = 16;
-constexpr int kXWarp = 18;
 constexpr int kMaxPlanes = 8;
 
-template <int NT, int R>
+// Two shapes of CTA.  The wide one (608 threads, all 512 TMEM columns, most of the shared memory) lives alone on its
+// SM.  The narrow one (DUAL: 352 threads, 256 TMEM columns, < 113 KB) is for N <= 64 tokens, where an MMA costs the
+// same tensor-pipe time whatever N is and one CTA leaves the pipe idle while it waits for data: two of them share an
+// SM and fill each other's gaps.
+template <int NT, int R, bool DUAL>
 struct W4Cfg {
   static_assert(R == 1 || R == 2, "a CTA owns one or two weight tiles");
   static_assert(!(R == 2 && NT > 128), "two accumulators of 256 columns do not fit next to the A ring");
+  static_assert(!DUAL || (R == 1 && NT <= 64), "the narrow CTA holds one accumulator of at most 64 columns");
+  static constexpr int kGroups = DUAL ? 2 : 4;                     // dequant groups of four warps
+  static constexpr int kDqWarps = 4 * kGroups;
+  static constexpr int kXWarp = 2 + kDqWarps;
+  static constexpr int kThreads = 32 * (kXWarp + 1);
+  static constexpr int kMinBlocks = DUAL ? 2 : 1;
+  static constexpr int kTmemCols = DUAL ? 256 : 512;
   static constexpr int kXBytes = NT * 128;                         // one 64-wide K sub-tile of X
   static constexpr int kXStage = 2 * kXBytes;
-  // Two consecutive chunks form a pair that is released by ONE tcgen05.commit (a commit costs about as much tensor
-  // pipe time as two MMAs).  Where possible the activation ring is laid out so that the same commit also frees an
-  // activation stage: R = 2 -> one pair per K stage (kSX == kSP); R = 1 -> one pair per two K stages (kSX == 2 kSP).
+  // A slot of the TMEM ring holds kCPS consecutive chunks and is released by ONE tcgen05.commit (a commit costs
+  // about as much tensor pipe time as two MMAs).  Where possible the activation ring is laid out so that the same
+  // commit also frees the activation stages the slot used: kCPS / R stages per slot.
+  static constexpr int kCPS = DUAL ? 1 : 2;                        // chunks per slot
   static constexpr bool kTiedX = NT <= 128;
-  static constexpr int kSP = (R == 2) ? (NT <= 64 ? 3 : 2) : (NT <= 64 ? 3 : 2);       // pair slots in TMEM
-  static constexpr int kSX = kTiedX ? (R == 2 ? kSP : 2 * kSP) : 2;                     // activation stages
-  static constexpr int kSW = NT <= 64 ? 12 : (NT == 128 ? (R == 2 ? 10 : 8) : 8);      // weight chunks in flight
+  static constexpr int kSP = DUAL ? 3 : (NT <= 64 ? 3 : 2);        // slots in TMEM
+  static constexpr int kSX = kTiedX ? kSP * kCPS / R : 2;          // activation stages
+  static constexpr int kSW = DUAL ? 6 : (NT <= 64 ? 12 : (NT == 128 ? (R == 2 ? 10 : 8) : 8));   // chunks in flight
   static constexpr int kAcc = R * NT;                              // accumulator columns
-  static_assert(kAcc + kSP * 128 <= 512, "TMEM budget");
+  static_assert(kAcc + kSP * kCPS * 64 <= kTmemCols, "TMEM budget");
   static constexpr int kRingBytes = kSX * kXStage + kSW * kW4ChunkBytes;
   static constexpr int kParkBytes = R * NT * 128 * 4;              // accumulators parked for the cluster reduce
   static constexpr int kDataBytes = ((kRingBytes > kParkBytes ? kRingBytes : kParkBytes) + 15) & ~15;
-  static constexpr int kXchBytes = 8 * 32 * 16 * 4;               // SwiGLU gate/up exchange (after the barriers)
+  static constexpr int kXchBytes = 2 * kGroups * 32 * 16 * 4;     // SwiGLU gate/up exchange (after the barriers)
   static constexpr int kSmemBytes = kDataBytes + 512 + kXchBytes + 1024;
-  static_assert(kSmemBytes <= 232448, "shared memory budget");
+  static_assert(kSmemBytes <= (DUAL ? 115712 : 232448), "shared memory budget");
 };
 
 struct W4Bars {
@@ -137,11 +146,12 @@ __device__ __forceinline__ void drain(uint64_t* full, int ring, int issued) {
 #define ACC(slot, t0)
 #endif
 
-template <int NT, int R, int EPI>
-__global__ void __launch_bounds__(kW4Threads, 1)
+template <int NT, int R, int EPI, bool DUAL>
+__global__ void __launch_bounds__((W4Cfg<NT, R, DUAL>::kThreads), (W4Cfg<NT, R, DUAL>::kMinBlocks))
 gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4Args a) {
-  using Cfg = W4Cfg<NT, R>;
-  constexpr int SW = Cfg::kSW, SX = Cfg::kSX, SP = Cfg::kSP;
+  using Cfg = W4Cfg<NT, R, DUAL>;
+  constexpr int SW = Cfg::kSW, SX = Cfg::kSX, SP = Cfg::kSP, CPS = Cfg::kCPS, G = Cfg::kGroups;
+  constexpr int kDqWarps = Cfg::kDqWarps, kXWarp = Cfg::kXWarp;
   constexpr bool kTied = Cfg::kTiedX;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -171,8 +181,7 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4Args a) {
       mbar_init(&bars->x_empty[i], 1);
     }
     for (int i = 0; i < SP; ++i) {
-      mbar_init(&bars->a_ready[2 * i], 4);
-      mbar_init(&bars->a_ready[2 * i + 1], 4);
+      for (int h = 0; h < CPS; ++h) mbar_init(&bars->a_ready[CPS * i + h], 4);
       mbar_init(&bars->pair_done[i], 1);
     }
     mbar_init(&bars->acc_ready, 1);
@@ -181,7 +190,7 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4Args a) {
     prefetch_tmap(&tmap_x);
   }
   if (warp == 1) {
-    tmem_alloc(&bars->tmem_base, 512);
+    tmem_alloc(&bars->tmem_base, Cfg::kTmemCols);
     tmem_relinquish();
   }
   tc_fence_before_sync();
@@ -223,7 +232,7 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4Args a) {
       for (int kk = 0; kk < n_k; ++kk) {
         if (kk >= SX) {
           // tied: the commit that ends the pair holding this stage's last chunk frees the stage as well
-          uint64_t* freed = kTied ? &bars->pair_done[R == 2 ? s : (s >> 1)] : &bars->x_empty[s];
+          uint64_t* freed = kTied ? &bars->pair_done[s / (CPS / R)] : &bars->x_empty[s];
           if (!mbar_wait(freed, ph, abort_flag, a.status, 2, kk)) break;
         }
         mbar_arrive_expect_tx(&bars->x_full[s], Cfg::kXStage);
@@ -243,19 +252,19 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4Args a) {
       int sx = 0, slot = 0, r = 0, kk = 0;
       uint32_t xph = 0, cyc = 0;
       for (int u = 0; u < n_units; ++u) {
-        const int half = u & 1;
+        const int half = u % CPS;
         TICK(tx);
         if (r == 0 && !mbar_wait(&bars->x_full[sx], xph, abort_flag, a.status, 3, kk)) break;
         ACC(0, tx);
         TICK(ta);
-        if (!mbar_wait(&bars->a_ready[2 * slot + half], cyc, abort_flag, a.status, 4, u)) break;
+        if (!mbar_wait(&bars->a_ready[CPS * slot + half], cyc, abort_flag, a.status, 4, u)) break;
         ACC(1, ta);
         TICK(ti);
         tc_fence_after_sync();
         // the start-address field counts 16-byte units: a K step of 16 halfs is +2, the second 64-wide sub-tile
         // is +kXBytes/16
         const uint64_t bd = desc0 + uint64_t((sx * Cfg::kXStage) >> 4);
-        const uint32_t at = a_base + slot * 128 + half * 64, dt = tmem + r * NT;
+        const uint32_t at = a_base + (slot * CPS + half) * 64, dt = tmem + r * NT;
 #pragma unroll
         for (int j = 0; j < 8; ++j)
           umma_ts(dt, at + j * 8, bd + uint64_t((j >> 2) * (Cfg::kXBytes >> 4) + (j & 3) * 2), idesc,
@@ -266,7 +275,7 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4Args a) {
           ++kk;
           if (++sx == SX) { sx = 0; xph ^= 1; }
         }
-        if (half == 1 || u == n_units - 1) {
+        if (half == CPS - 1 || u == n_units - 1) {
           tc_commit(&bars->pair_done[slot]);
           if (++slot == SP) { slot = 0; cyc ^= 1; }
         }
@@ -276,16 +285,18 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4Args a) {
     }
   } else {
     // ------------------------------------------------------------------ dequant: chunk -> fp16 -> TMEM
-    // Four groups of four warps; group g takes the units g, g+4, g+8, ...  A thread owns one weight row of the
+    // G groups of four warps; group g takes the units g, g+G, g+2G, ...  A thread owns one weight row of the
     // chunk: 128 nibbles in, 64 half2 out, written as two 32-column TMEM stores.
     const int q = warp & 3;                  // TMEM lane quarter this warp may touch
     const int grp = (warp - 2) >> 2;
     const int row = q * 32 + lane;
     const uint32_t lane_addr = uint32_t(q * 32) << 16;
-    int sw = grp % SW, slot = grp >> 1;      // unit u -> pair u/2 -> slot (u/2) % SP, half u & 1
-    const int half = grp & 1;
-    uint32_t wph = 0, cyc = 0;               // cyc = (u/2) / SP: how often this pair slot has been used before
-    for (int u = grp; u < n_units; u += 4) {
+    int sw = grp % SW;
+    uint32_t wph = 0;
+    for (int u = grp; u < n_units; u += G) {
+      // unit u -> slot (u / CPS) % SP, position u % CPS inside it; cyc = how often the slot has been used before
+      const int su = u / CPS, half = u % CPS;
+      const int slot = su % SP, cyc = su / SP;
       TICK(t0);
       if (!mbar_wait(&bars->w_full[sw], wph, abort_flag, a.status, 5, u)) break;
       ACC(0, t0);
@@ -304,7 +315,7 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4Args a) {
       TICK(t3);
       tc_fence_after_sync();
       const __half2 s2 = __half2half2(__low2half(sz)), z2 = __half2half2(__high2half(sz));
-      const uint32_t dst = a_base + lane_addr + slot * 128 + half * 64;
+      const uint32_t dst = a_base + lane_addr + (slot * CPS + half) * 64;
 #pragma unroll
       for (int hh = 0; hh < 2; ++hh) {
         uint32_t o[32];
@@ -322,12 +333,10 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4Args a) {
       TICK(t4);
       tc_wait_st();
       tc_fence_before_sync();
-      if (lane == 0) mbar_arrive(&bars->a_ready[2 * slot + half]);
+      if (lane == 0) mbar_arrive(&bars->a_ready[CPS * slot + half]);
       ACC(4, t4);
-      sw += 4;
+      sw += G;
       if (sw >= SW) { sw -= SW; wph ^= 1; }
-      slot += 2;
-      if (slot >= SP) { slot -= SP; ++cyc; }
     }
     TICK(t5);
     acc_ok = mbar_wait(&bars->acc_ready, 0, abort_flag, a.status, 7, 0);
@@ -353,7 +362,7 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4Args a) {
   const bool in_cluster = ks > 1;
   const uint32_t crank = in_cluster ? cluster_ctarank() : 0u;
   const int q = warp & 3;                                       // TMEM lane quarter / row quarter
-  const int cgw = (warp - 2) >> 2;                              // 0..3: which chunks of the CTA this warp takes
+  const int cgw = (warp - 2) >> 2;                              // 0..G-1: which chunks of the CTA this warp takes
   const int row = q * 32 + lane;
   constexpr int kChunks = R * (NT / 16);                        // 16-column chunks of the CTA's accumulators
 
@@ -361,7 +370,7 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4Args a) {
     // every CTA parks its accumulators: park[(chunk*16 + i) * 128 + row]; chunk = r * (NT/16) + column group
     if (dq_role && acc_ok) {
 #pragma unroll 1
-      for (int ch = cgw; ch < kChunks; ch += 4) {
+      for (int ch = cgw; ch < kChunks; ch += G) {
         uint32_t v[16];
         ZSE_TMEM_LD_X16(v, tmem + (uint32_t(q * 32) << 16) + ch * 16);
         tc_wait_ld();
@@ -378,7 +387,7 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4Args a) {
     int mine = 0;
 #pragma unroll 1
     for (int ch = int(crank); ch < kChunks; ch += ks, ++mine) {
-      if ((mine & 3) != cgw) continue;
+      if ((mine % G) != cgw) continue;
       const int r = ch / (NT / 16), c0 = (ch % (NT / 16)) * 16;
       float v[16];
       if (in_cluster) {
@@ -450,13 +459,13 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4Args a) {
 #endif
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem, 512);
+  if (warp == 1) tmem_dealloc(tmem, Cfg::kTmemCols);
 }
 
-template <int NT, int R, int EPI>
+template <int NT, int R, int EPI, bool DUAL>
 static int launch_w4(const CUtensorMap& tx, const W4Args& a, dim3 grid, cudaStream_t st) {
-  auto kern = gemm_w4_kernel<NT, R, EPI>;
-  using Cfg = W4Cfg<NT, R>;
+  auto kern = gemm_w4_kernel<NT, R, EPI, DUAL>;
+  using Cfg = W4Cfg<NT, R, DUAL>;
   constexpr int smem = Cfg::kSmemBytes;
   static bool attr_done = false;
   if (!attr_done) {
@@ -466,7 +475,7 @@ static int launch_w4(const CUtensorMap& tx, const W4Args& a, dim3 grid, cudaStre
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;
-  cfg.blockDim = dim3(kW4Threads);
+  cfg.blockDim = dim3(Cfg::kThreads);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = st;
   cudaLaunchAttribute attr[2];
@@ -481,42 +490,68 @@ static int launch_w4(const CUtensorMap& tx, const W4Args& a, dim3 grid, cudaStre
   return cudaLaunchKernelEx(&cfg, kern, tx, a) == cudaSuccess ? 0 : ZSE_ERR_LAUNCH;
 }
 
-template <int NT, int R>
+template <int NT, int R, bool DUAL = false>
 static int launch_w4_epi(int epilogue, const CUtensorMap& tx, const W4Args& a, dim3 grid, cudaStream_t st) {
-  if (epilogue == kEpiF16) return launch_w4<NT, R, kEpiF16>(tx, a, grid, st);
-  if (epilogue == kEpiSwiGLU) return launch_w4<NT, R, kEpiSwiGLU>(tx, a, grid, st);
-  if (epilogue == kEpiPartialF32) return launch_w4<NT, R, kEpiPartialF32>(tx, a, grid, st);
+  if (epilogue == kEpiF16) return launch_w4<NT, R, kEpiF16, DUAL>(tx, a, grid, st);
+  if (epilogue == kEpiSwiGLU) return launch_w4<NT, R, kEpiSwiGLU, DUAL>(tx, a, grid, st);
+  if (epilogue == kEpiPartialF32) return launch_w4<NT, R, kEpiPartialF32, DUAL>(tx, a, grid, st);
   return ZSE_ERR_SHAPE;
 }
+
+// 0 = the planner decides, 1 = wide CTAs only, 2 = narrow (two per SM) CTAs wherever they are allowed
+static int g_w4_mode = 0;
 
 // How the launcher tiles a problem: weight tiles per CTA (R) and K splits (ks).  Measured on B200: a tcgen05.mma of
 // M=128, K=16 occupies the tensor pipe for about 50 cycles whatever N <= 64 is, so a 128x128 weight chunk costs about
 // 450 cycles on one SM and a CTA is tensor-issue bound, not bandwidth bound; what matters is an even spread of chunks
 // over the SMs and a small fixed cost per CTA.  Row-parallel projections (fp32 epilogue) split K into planes that the
 // consumer adds; the other epilogues need the whole K in one CTA (or an explicit cluster split).
+// Relative cost of a chunk in a narrow CTA: when two CTAs share the SM's tensor pipe (per CTA) and when one runs alone.
+constexpr double kW4DualPairCost = 0.65;
+constexpr double kW4DualSoloCost = 0.95;
+
 static void plan_w4(int M, int N, int K, int epilogue, int sm_count, int want_split, int* R_out, int* ks_out,
-                    int* cluster_out) {
+                    int* cluster_out, int* dual_out) {
   const int nt = pick_nt(M);
   const int n_tiles = epilogue == kEpiSwiGLU ? (N / 2 + 63) / 64 : (N + kTileN - 1) / kTileN;
   const int m_tiles = (M + nt - 1) / nt;
   const int k_stages = K / kW4StageK;
   const bool planes_ok = epilogue == kEpiPartialF32;
   double best_cost = -1.0;
-  int best_r = 1, best_ks = 1;
-  for (int R = 1; R <= 2; ++R) {
-    if (n_tiles % R != 0) continue;
-    if (R == 2 && nt > 128) continue;                           // accumulators + A ring must fit 512 TMEM columns
-    const long ctas = long(n_tiles / R) * m_tiles;
-    const int max_ks = planes_ok ? min(kMaxPlanes, k_stages) : 1;
-    for (int ks = 1; ks <= max_ks; ++ks) {
-      const long waves = (ctas * ks + sm_count - 1) / sm_count;
-      const double unit = 1.0 + 0.1 * double(nt) / 64.0 / double(R);       // chunk + share of the activation stage
-      const double fixed = 8.0 + (ks > 1 ? 1.0 : 0.0);
-      const double cost = double(waves) * (double((k_stages + ks - 1) / ks) * double(R) * unit + fixed);
-      if (best_cost < 0 || cost < best_cost - 1e-9 || (cost < best_cost + 1e-9 && R > best_r)) {
-        best_cost = cost;
-        best_r = R;
-        best_ks = ks;
+  int best_r = 1, best_ks = 1, best_dual = 0;
+  for (int dual = 0; dual <= 1; ++dual) {
+    if (dual && (nt > 64 || g_w4_mode == 1)) continue;
+    if (!dual && g_w4_mode == 2 && nt <= 64) continue;
+    for (int R = 1; R <= (dual ? 1 : 2); ++R) {
+      if (n_tiles % R != 0) continue;
+      if (R == 2 && nt > 128) continue;                         // accumulators + A ring must fit 512 TMEM columns
+      const long ctas = long(n_tiles / R) * m_tiles;
+      const int max_ks = planes_ok ? min(kMaxPlanes, k_stages) : 1;
+      for (int ks = 1; ks <= max_ks; ++ks) {
+        const long total = ctas * ks;
+        const long cap = long(sm_count) * (dual ? 2 : 1);
+        const long waves = (total + cap - 1) / cap;
+        const long last = total - (waves - 1) * cap;            // CTAs of the last wave
+        const double chunks = double((k_stages + ks - 1) / ks) * double(R);
+        // time of one chunk in units of a wide CTA's chunk: activation share, and for narrow CTAs the tensor pipe
+        // shared by the two CTAs of an SM (each runs slower, together they are faster)
+        const double xshare = 0.1 * double(nt) / 64.0 / double(R);
+        const double pair_chunk = 2.0 * kW4DualPairCost, solo_chunk = kW4DualSoloCost;
+        double cost;
+        if (!dual) {
+          cost = double(waves) * (chunks * (1.0 + xshare) + 8.0);
+        } else {
+          const double full = chunks * (pair_chunk + 2.0 * xshare) + 9.0;      // an SM with two CTAs
+          const double tail = last > sm_count ? full : chunks * (solo_chunk + xshare) + 8.0;
+          cost = double(waves - 1) * full + tail;
+        }
+        cost += ks > 1 ? 1.0 : 0.0;
+        if (best_cost < 0 || cost < best_cost - 1e-9 || (cost < best_cost + 1e-9 && !dual && R > best_r)) {
+          best_cost = cost;
+          best_r = R;
+          best_ks = ks;
+          best_dual = dual;
+        }
       }
     }
   }
@@ -527,6 +562,7 @@ static void plan_w4(int M, int N, int K, int epilogue, int sm_count, int want_sp
   }
   *R_out = best_r;
   *ks_out = best_ks;
+  *dual_out = best_dual;
 }
 
 }  // namespace zse
@@ -536,6 +572,8 @@ using namespace zse;
 static long long* g_w4_timing = nullptr;
 // Debug hook (only meaningful in builds with ZSE_W4_TIMING): device buffer of 20 x 8 counters.
 extern "C" void zse_gemm_w4_set_timing(void* dev_buffer) { g_w4_timing = reinterpret_cast<long long*>(dev_buffer); }
+// Tuning hook: 0 = planner decides between wide and narrow CTAs, 1 = wide only, 2 = narrow wherever allowed.
+extern "C" void zse_gemm_w4_set_mode(int mode) { zse::g_w4_mode = mode; }
 
 extern "C" int zse_gemm_w4(const void* w_tiled, const void* x, int x_rows_cap, const void* bias, void* out, int M,
                            int N, int K, int ldo, int epilogue, int k_split, void* status, void* stream) {
@@ -549,8 +587,8 @@ extern "C" int zse_gemm_w4(const void* w_tiled, const void* x, int x_rows_cap, c
     if (sm_count <= 0) sm_count = 148;
   }
   const int k_stages = K / kW4StageK;
-  int R = 1, ks = 1, cluster = 1;
-  plan_w4(M, N, K, epilogue, sm_count, k_split, &R, &ks, &cluster);
+  int R = 1, ks = 1, cluster = 1, dual = 0;
+  plan_w4(M, N, K, epilogue, sm_count, k_split, &R, &ks, &cluster, &dual);
   const int spp = (k_stages + ks - 1) / ks;
   ks = (k_stages + spp - 1) / spp;                     // no empty split
   if (cluster > 1) cluster = ks;
@@ -563,7 +601,13 @@ extern "C" int zse_gemm_w4(const void* w_tiled, const void* x, int x_rows_cap, c
   dim3 grid(n_tiles / R, (M + nt - 1) / nt, ks);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   int rc = ZSE_ERR_SHAPE;
-  if (R == 1) {
+  if (dual) {
+    switch (nt) {
+      case 16: rc = launch_w4_epi<16, 1, true>(epilogue, tx, a, grid, st); break;
+      case 32: rc = launch_w4_epi<32, 1, true>(epilogue, tx, a, grid, st); break;
+      default: rc = launch_w4_epi<64, 1, true>(epilogue, tx, a, grid, st); break;
+    }
+  } else if (R == 1) {
     ZSE_DISPATCH_NT(nt, rc = (launch_w4_epi<NT, 1>(epilogue, tx, a, grid, st)))
   } else if (R == 2) {
     switch (nt) {
@@ -583,8 +627,8 @@ extern "C" int zse_gemm_w4_splits(int M, int N, int K, int k_split) {
   int sm_count = 148, dev = 0;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
   if (sm_count <= 0) sm_count = 148;
-  int R = 1, ks = 1, cluster = 1;
-  plan_w4(M, N, K, kEpiPartialF32, sm_count, k_split, &R, &ks, &cluster);
+  int R = 1, ks = 1, cluster = 1, dual = 0;
+  plan_w4(M, N, K, kEpiPartialF32, sm_count, k_split, &R, &ks, &cluster, &dual);
   const int k_stages = K / kW4StageK;
   const int spp = (k_stages + ks - 1) / ks;
   return (k_stages + spp - 1) / spp;

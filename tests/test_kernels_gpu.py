@@ -140,6 +140,45 @@ def test_gemm_w4_model_shapes(ops, M, N, K, epi):
         assert torch.equal(again[:n_pl].sum(0), out)
 
 
+@pytest.mark.parametrize("mode", [1, 2])
+@pytest.mark.parametrize("M,N,K,epi", [(64, 5120, 5120, "partial"), (64, 13824, 5120, "swiglu"), (1, 3584, 2048, "f16"),
+                                       (17, 1024, 4096, "partial"), (40, 2560, 1024, "swiglu"), (64, 640, 1152, "f16")])
+def test_gemm_w4_wide_and_narrow_ctas_agree(ops, mode, M, N, K, epi):
+    """Both CTA shapes (one wide CTA per SM / two narrow CTAs per SM) against the oracle, cluster split included."""
+    from zse_b200.ops import native
+    native.gemm_w4_set_mode(mode)
+    try:
+        x = (torch.randn(M, K, device="cuda") * 0.5).half()
+        if epi == "swiglu":
+            g, gd = _w4_parts_gpu(N, K, 11)
+            u, ud = _w4_parts_gpu(N, K, 12)
+            w = ops.make_linear([g, u], K, 128, swiglu=True)
+            out = torch.zeros(M, N, dtype=torch.float16, device="cuda")
+            ops.linear_swiglu(w, x, M, out)
+            split = torch.zeros(M, N, dtype=torch.float16, device="cuda")
+            native.gemm_w4(w.data, x, M, None, split, M, 2 * N, K, N, 1, 2, ops.status.ptr)
+            want = ref.swiglu(x.float() @ gd.T, x.float() @ ud.T)
+            torch.cuda.synchronize()
+            assert _rel(split, want) < 3e-3
+        else:
+            p, wd = _w4_parts_gpu(N, K, 13)
+            bias = (torch.randn(N, device="cuda") * 0.1).half() if epi == "f16" else None
+            w = ops.make_linear([p], K, 128, bias)
+            if epi == "f16":
+                out = torch.zeros(M, N, dtype=torch.float16, device="cuda")
+                ops.linear(w, x, M, out)
+                want = ref.linear(x, wd, bias)
+            else:
+                planes = torch.zeros(8, M, N, dtype=torch.float32, device="cuda")
+                n_pl = ops.linear_partial(w, x, M, planes)
+                out, want = planes[:n_pl].sum(0), x.float() @ wd.T
+        torch.cuda.synchronize()
+        ops.check()
+        assert _rel(out, want) < 3e-3, _rel(out, want)
+    finally:
+        native.gemm_w4_set_mode(0)
+
+
 @pytest.mark.parametrize("ks", [2, 3, 4])
 def test_gemm_w4_cluster_split_with_fused_epilogues(ops, ks):
     """Explicit K split on an epilogue that needs the whole sum: the CTAs of a cluster add their accumulators through

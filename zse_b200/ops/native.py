@@ -76,6 +76,7 @@ _SIGS = {
     "zse_device_info": (c_int, [POINTER(c_int), POINTER(c_int), POINTER(c_int), POINTER(c_int64), POINTER(c_int64)]),
     "zse_build_info": (c_char_p, []),
     "zse_set_pdl": (None, [c_int]),
+    "zse_gemm_w4_set_mode": (None, [c_int]),
     "zse_get_pdl": (c_int, []),
 }
 
@@ -298,6 +299,12 @@ def device_info() -> dict:
     sm, maj, mnr, tot, free = c_int(), c_int(), c_int(), c_int64(), c_int64()
     _ck(load().zse_device_info(sm, maj, mnr, tot, free), "device_info", 0)
     return {"sm_count": sm.value, "cc": (maj.value, mnr.value), "total_mem": tot.value, "free_mem": free.value}
+
+
+def gemm_w4_set_mode(mode: int) -> None:
+    """Tuning hook for the INT4 GEMM: 0 = the planner picks the CTA shape, 1 = wide CTAs only, 2 = narrow CTAs (two per
+    SM) wherever they are allowed."""
+    load().zse_gemm_w4_set_mode(int(mode))
 
 
 def set_pdl(on: bool) -> None:

@@ -38,7 +38,11 @@ def main():
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--only", default="", help="comma separated kernel names")
     ap.add_argument("--json", default="")
+    ap.add_argument("--w4-mode", type=int, default=0, help="INT4 GEMM CTA shape: 0 planner, 1 wide, 2 narrow (2 per SM)")
     a = ap.parse_args()
+    if a.w4_mode:
+        from ..ops import native
+        native.gemm_w4_set_mode(a.w4_mode)
     c = synth.shape_config(a.shape)
     ops = CudaOps("cuda")
     prof = KernelProfiler(iters=a.iters)
@@ -63,6 +67,9 @@ def main():
     qkv = torch.zeros(M, q_dim + 2 * kv_dim, dtype=torch.float16, device="cuda")
     run("qkv_gemm", lambda: ops.linear(wqkv, x, M, qkv), w4_bytes(q_dim + 2 * kv_dim, H) + M * H * 2,
         2 * M * H * (q_dim + 2 * kv_dim))
+    planes_q = torch.zeros(8, M, q_dim + 2 * kv_dim, dtype=torch.float32, device="cuda")
+    run("qkv_gemm_planes", lambda: ops.linear_partial(wqkv, x, M, planes_q),
+        w4_bytes(q_dim + 2 * kv_dim, H) + M * H * 2, 2 * M * H * (q_dim + 2 * kv_dim))
     wo = _w4(ops, H, q_dim)
     xa = (torch.randn(M, q_dim, device="cuda") * 0.5).half()
     planes = torch.zeros(8, M, H, dtype=torch.float32, device="cuda")
@@ -77,7 +84,9 @@ def main():
     resid = torch.randn(M, H, device="cuda")
     wn = torch.ones(H, dtype=torch.float16, device="cuda")
     xn = torch.zeros(M, H, dtype=torch.float16, device="cuda")
-    run("add_rmsnorm", lambda: ops.add_rmsnorm(resid, planes, 1, None, wn, xn, M, 1e-6), M * H * (4 + 4 + 4 + 2))
+    n_pl = ops.linear_partial(wd, xi, M, planes)
+    run("add_rmsnorm", lambda: ops.add_rmsnorm(resid, planes, n_pl, None, wn, xn, M, 1e-6),
+        M * H * (4 + 4 + 4 * n_pl + 2))
     # attention over a paged cache
     bs = 16
     nblk = (a.ctx + bs - 1) // bs
