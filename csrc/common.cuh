@@ -82,6 +82,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// Same test, but the thread may stay suspended for up to `hint_ns` before it reports "not yet": a waiting warp then
+// costs the scheduler almost nothing (the hardware wakes it when the phase completes).
+__device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
 
 // Bounded wait.  Returns false when it gave up (timeout, or another thread of the CTA aborted).
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, Status* st,
@@ -89,8 +102,8 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = globaltimer_ns();
   unsigned spins = 0;
-  while (!mbar_try_wait(bar, parity)) {
-    if ((++spins & 0xFF) == 0) {
+  while (!mbar_try_wait_hint(bar, parity, 20000u)) {
+    if ((++spins & 0xF) == 0) {
       if (*abort_flag) return false;
       if (globaltimer_ns() - t0 > kWaitLimitNs) {
         report(st, kWaitTimeout, where, detail);

@@ -31,9 +31,11 @@ namespace zse {
 constexpr int kMaxPlanes = 8;
 
 // Two shapes of CTA.  The wide one (608 threads, all 512 TMEM columns, most of the shared memory) lives alone on its
-// SM.  The narrow one (DUAL: 352 threads, 256 TMEM columns, < 113 KB) is for N <= 64 tokens, where an MMA costs the
-// same tensor-pipe time whatever N is and one CTA leaves the pipe idle while it waits for data: two of them share an
-// SM and fill each other's gaps.
+// SM.  The narrow one (DUAL: 384 threads, 256 TMEM columns, < 113 KB) is for N <= 64 tokens.  Measured on B200: one
+// thread cannot issue tcgen05.mma faster than one per ~50 cycles whatever N is, while the tensor pipe itself needs
+// only 32 cycles at N = 64 and 8 at N = 16; several issuing threads (in one CTA or in two CTAs of an SM) add up
+// until the pipe is full.  So the narrow CTA runs TWO independent pipelines - dequant group p + MMA warp p work on
+// the chunks of parity p with their own accumulator and their own TMEM slot - and two such CTAs share an SM.
 template <int NT, int R, bool DUAL>
 struct W4Cfg {
   static_assert(R == 1 || R == 2, "a CTA owns one or two weight tiles");
@@ -42,7 +44,7 @@ struct W4Cfg {
   static constexpr int kGroups = DUAL ? 2 : 4;                     // dequant groups of four warps
   static constexpr int kDqWarps = 4 * kGroups;
   static constexpr int kXWarp = 2 + kDqWarps;
-  static constexpr int kThreads = 32 * (kXWarp + 1);
+  static constexpr int kThreads = 32 * (kXWarp + 1) + (DUAL ? 32 : 0);      // DUAL: second MMA warp at the end
   static constexpr int kMinBlocks = DUAL ? 2 : 1;
   static constexpr int kTmemCols = DUAL ? 256 : 512;
   static constexpr int kXBytes = NT * 128;                         // one 64-wide K sub-tile of X
@@ -51,17 +53,19 @@ struct W4Cfg {
   // about as much tensor pipe time as two MMAs).  Where possible the activation ring is laid out so that the same
   // commit also frees the activation stages the slot used: kCPS / R stages per slot.
   static constexpr int kCPS = DUAL ? 1 : 2;                        // chunks per slot
-  static constexpr bool kTiedX = NT <= 128;
-  static constexpr int kSP = DUAL ? 3 : (NT <= 64 ? 3 : 2);        // slots in TMEM
-  static constexpr int kSX = kTiedX ? kSP * kCPS / R : 2;          // activation stages
-  static constexpr int kSW = DUAL ? 6 : (NT <= 64 ? 12 : (NT == 128 ? (R == 2 ? 10 : 8) : 8));   // chunks in flight
-  static constexpr int kAcc = R * NT;                              // accumulator columns
+  static constexpr bool kTiedX = !DUAL && NT <= 128;
+  static constexpr int kSP = DUAL ? 2 : (NT <= 64 ? 3 : 2);        // slots in TMEM (DUAL: one per pipeline)
+  static constexpr int kSX = DUAL ? 4 : (kTiedX ? kSP * kCPS / R : 2);      // activation stages
+  static constexpr int kSW = DUAL ? (NT == 64 ? 5 : 6) : (NT <= 64 ? 12 : (NT == 128 ? (R == 2 ? 10 : 8) : 8));
+  static constexpr int kAcc = (DUAL ? 2 : R) * NT;                 // accumulator columns (DUAL: one per pipeline)
   static_assert(kAcc + kSP * kCPS * 64 <= kTmemCols, "TMEM budget");
   static constexpr int kRingBytes = kSX * kXStage + kSW * kW4ChunkBytes;
   static constexpr int kParkBytes = R * NT * 128 * 4;              // accumulators parked for the cluster reduce
   static constexpr int kDataBytes = ((kRingBytes > kParkBytes ? kRingBytes : kParkBytes) + 15) & ~15;
-  static constexpr int kXchBytes = 2 * kGroups * 32 * 16 * 4;     // SwiGLU gate/up exchange (after the barriers)
-  static constexpr int kSmemBytes = kDataBytes + 512 + kXchBytes + 1024;
+  // SwiGLU gate/up exchange: after the barriers, or (DUAL) inside the idle rings behind the parked accumulators
+  static constexpr int kXchBytes = 2 * kGroups * 32 * 16 * 4;
+  static_assert(!DUAL || kParkBytes + kXchBytes <= kRingBytes, "exchange buffer must fit behind the park area");
+  static constexpr int kSmemBytes = kDataBytes + 512 + (DUAL ? 0 : kXchBytes) + 1024;
   static_assert(kSmemBytes <= (DUAL ? 115712 : 232448), "shared memory budget");
 };
 
@@ -158,7 +162,7 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4Args a) {
   uint8_t* x_ring = smem;                                    // [SX][2][NT*128]
   uint8_t* w_ring = smem + SX * Cfg::kXStage;                // [SW][8704]
   W4Bars* bars = reinterpret_cast<W4Bars*>(smem + Cfg::kDataBytes);
-  float* xch_base = reinterpret_cast<float*>(smem + Cfg::kDataBytes + 512);
+  float* xch_base = reinterpret_cast<float*>(DUAL ? smem + Cfg::kParkBytes : smem + Cfg::kDataBytes + 512);
   float* park = reinterpret_cast<float*>(smem);              // reused after the main loop: [R*NT cols][128 rows]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -184,7 +188,7 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4Args a) {
       for (int h = 0; h < CPS; ++h) mbar_init(&bars->a_ready[CPS * i + h], 4);
       mbar_init(&bars->pair_done[i], 1);
     }
-    mbar_init(&bars->acc_ready, 1);
+    mbar_init(&bars->acc_ready, DUAL ? 2 : 1);
     bars->abort_flag = 0;
     mbar_fence_init();
     prefetch_tmap(&tmap_x);
@@ -205,6 +209,131 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4Args a) {
   const long long t_start = clock64();
 #endif
 
+  if constexpr (DUAL) {
+    // ================================================================== narrow CTA: two pipelines
+    // chunk u (= K stage u, R is 1) belongs to pipeline p = u & 1: dequant group p fills TMEM slot p, MMA warp p
+    // accumulates into accumulator p.  Weight ring and activation ring are shared and filled in chunk order.
+    constexpr int kIssuer1 = kXWarp + 1;
+    if (warp == 0) {
+      if (lane == 0) {
+        int issued = 0, s = 0;
+        uint32_t ph = 1;
+        for (int u = 0; u < n_units; ++u) {
+          TICK(tw);
+          if (u >= SW && !mbar_wait(&bars->w_empty[s], ph, abort_flag, a.status, 1, u)) break;
+          ACC(0, tw);
+          const uint8_t* src = a.w + (size_t(tile0) * a.k_stages + (s_begin + u)) * kW4ChunkBytes;
+          mbar_arrive_expect_tx(&bars->w_full[s], kW4ChunkBytes);
+          bulk_g2s(w_ring + s * kW4ChunkBytes, src, kW4ChunkBytes, &bars->w_full[s]);
+          issued = u + 1;
+          if (++s == SW) { s = 0; ph ^= 1; }
+        }
+        if (*abort_flag) drain(bars->w_full, SW, issued);
+      }
+    } else if (warp == kXWarp) {
+      if (lane == 0) {
+        int issued = 0, s = 0;
+        uint32_t ph = 1;
+        pdl_wait();                                      // the activations come from the previous kernel
+        for (int kk = 0; kk < n_k; ++kk) {
+          if (kk >= SX && !mbar_wait(&bars->x_empty[s], ph, abort_flag, a.status, 2, kk)) break;
+          mbar_arrive_expect_tx(&bars->x_full[s], Cfg::kXStage);
+          const int k0 = (s_begin + kk) * kW4StageK;
+          tma_load_2d(x_ring + s * Cfg::kXStage, &tmap_x, k0, blockIdx.y * NT, &bars->x_full[s]);
+          tma_load_2d(x_ring + s * Cfg::kXStage + Cfg::kXBytes, &tmap_x, k0 + 64, blockIdx.y * NT, &bars->x_full[s]);
+          issued = kk + 1;
+          if (++s == SX) { s = 0; ph ^= 1; }
+        }
+        if (*abort_flag) drain(bars->x_full, SX, issued);
+      }
+    } else if (warp == 1 || warp == kIssuer1) {
+      const int p = warp == 1 ? 0 : 1;
+      if (lane == 0) {
+        constexpr uint32_t idesc = make_idesc_f16(kTileN, NT);
+        const uint64_t desc0 = make_desc_sw128(smem_u32(x_ring));
+        const uint32_t at = a_base + p * 64, dt = tmem + p * NT;
+        uint32_t aph = 0;
+        for (int u = p; u < n_units; u += 2) {
+          const int sx = u % SX;
+          TICK(tx);
+          if (!mbar_wait(&bars->x_full[sx], (u / SX) & 1, abort_flag, a.status, 3, u)) break;
+          ACC(0, tx);
+          TICK(ta);
+          if (!mbar_wait(&bars->a_ready[p], aph, abort_flag, a.status, 4, u)) break;
+          ACC(1, ta);
+          TICK(ti);
+          tc_fence_after_sync();
+          // slot p was refilled for this chunk only after the MMAs of chunk u-2 had completed, so the activation
+          // stage that chunk used is free as well
+          if (u >= 2) mbar_arrive(&bars->x_empty[(u - 2) % SX]);
+          const uint64_t bd = desc0 + uint64_t((sx * Cfg::kXStage) >> 4);
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            umma_ts(dt, at + j * 8, bd + uint64_t((j >> 2) * (Cfg::kXBytes >> 4) + (j & 3) * 2), idesc,
+                    (u >= 2) || (j != 0));
+          tc_commit(&bars->pair_done[p]);
+          aph ^= 1;
+          ACC(2, ti);
+        }
+        tc_commit(&bars->acc_ready);
+      }
+    } else {
+      const int q = warp & 3;                  // TMEM lane quarter this warp may touch
+      const int p = (warp - 2) >> 2;           // pipeline = dequant group
+      const int row = q * 32 + lane;
+      const uint32_t dst = a_base + (uint32_t(q * 32) << 16) + p * 64;
+      int sw = p % SW;
+      uint32_t wph = 0, dph = 0;
+      for (int u = p; u < n_units; u += 2) {
+        TICK(t0);
+        if (!mbar_wait(&bars->w_full[sw], wph, abort_flag, a.status, 5, u)) break;
+        ACC(0, t0);
+        TICK(t1);
+        const uint8_t* chunk = w_ring + sw * kW4ChunkBytes;
+        uint4 pk[4];
+#pragma unroll
+        for (int p4 = 0; p4 < 4; ++p4) pk[p4] = *reinterpret_cast<const uint4*>(chunk + (p4 * 128 + row) * 16);
+        const __half2 sz = *reinterpret_cast<const __half2*>(chunk + 8192 + row * 4);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->w_empty[sw]);        // the chunk is in registers: its slot may be refilled
+        ACC(1, t1);
+        TICK(t2);
+        if (u >= 2) {
+          if (!mbar_wait(&bars->pair_done[p], dph, abort_flag, a.status, 6, u)) break;
+          dph ^= 1;
+        }
+        ACC(2, t2);
+        TICK(t3);
+        tc_fence_after_sync();
+        const __half2 s2 = __half2half2(__low2half(sz)), z2 = __half2half2(__high2half(sz));
+#pragma unroll
+        for (int hh = 0; hh < 2; ++hh) {
+          uint32_t o[32];
+#pragma unroll
+          for (int p2 = 0; p2 < 2; ++p2) {
+            const uint4 w4 = pk[hh * 2 + p2];
+            dequant_word(w4.x, s2, z2, o + p2 * 16 + 0);
+            dequant_word(w4.y, s2, z2, o + p2 * 16 + 4);
+            dequant_word(w4.z, s2, z2, o + p2 * 16 + 8);
+            dequant_word(w4.w, s2, z2, o + p2 * 16 + 12);
+          }
+          ZSE_TMEM_ST_X32(dst + hh * 32, o);
+        }
+        ACC(3, t3);
+        TICK(t4);
+        tc_wait_st();
+        tc_fence_before_sync();
+        if (lane == 0) mbar_arrive(&bars->a_ready[p]);
+        ACC(4, t4);
+        sw += 2;
+        if (sw >= SW) { sw -= SW; wph ^= 1; }
+      }
+      TICK(t5);
+      acc_ok = mbar_wait(&bars->acc_ready, 0, abort_flag, a.status, 7, 0);
+      tc_fence_after_sync();
+      ACC(5, t5);
+    }
+  } else
   if (warp == 0) {
     // ------------------------------------------------------------------ weight producer
     if (lane == 0) {
@@ -374,6 +503,13 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4Args a) {
         uint32_t v[16];
         ZSE_TMEM_LD_X16(v, tmem + (uint32_t(q * 32) << 16) + ch * 16);
         tc_wait_ld();
+        if (DUAL && n_units > 1) {                               // second pipeline's accumulator
+          uint32_t v1[16];
+          ZSE_TMEM_LD_X16(v1, tmem + (uint32_t(q * 32) << 16) + NT + ch * 16);
+          tc_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 16; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) + __uint_as_float(v1[i]));
+        }
 #pragma unroll
         for (int i = 0; i < 16; ++i) park[(ch * 16 + i) * 128 + row] = __uint_as_float(v[i]);
       }
@@ -410,6 +546,12 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4Args a) {
         tc_wait_ld();
 #pragma unroll
         for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(raw[i]);
+        if (DUAL && n_units > 1) {                               // second pipeline's accumulator
+          ZSE_TMEM_LD_X16(raw, tmem + (uint32_t(q * 32) << 16) + NT + ch * 16);
+          tc_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 16; ++i) v[i] += __uint_as_float(raw[i]);
+        }
       }
       const int n_tile = tile0 + r;
       if (EPI == kEpiSwiGLU) {
