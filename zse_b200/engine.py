@@ -77,6 +77,7 @@ class ZStreamerEngine:
         self._start_time: Optional[float] = None
         self._request_counter = 0
         self._lock = threading.Lock()
+        self._step_lock = threading.RLock()        # one user of the model runner at a time (steps, embeddings)
         self._total_requests = self._total_tokens = self._total_steps = 0
         self._ttft_samples: deque = deque(maxlen=10000)
         self._tpot_samples: deque = deque(maxlen=10000)
@@ -246,8 +247,9 @@ class ZStreamerEngine:
         """One scheduling + execution iteration; returns what happened (idle steps return an empty result)."""
         if self._start_time is None:
             self._start_time = time.monotonic()
-        plan = self._scheduler.schedule_step()
-        res = self._batch_runner.execute(plan)
+        with self._step_lock:
+            plan = self._scheduler.schedule_step()
+            res = self._batch_runner.execute(plan)
         with self._lock:
             if not plan.is_idle:
                 self._total_steps += 1
@@ -262,6 +264,23 @@ class ZStreamerEngine:
                     self._completed.pop(next(iter(self._completed)))
         res.idle = plan.is_idle and not res.finished
         return res
+
+    # ---- model access for retrieval (between steps of the serving loop) -----------------------------------
+    def embed_tokens(self, tokens: List[int]):
+        """Mean-pooled, L2-normalised final hidden state of ``tokens`` (fp32 host tensor)."""
+        limit = min(self._runner.max_tokens, self._max_seq_len - 1)
+        with self._step_lock:
+            if self.device.type == "cuda":
+                torch.cuda.set_device(self.device)
+            return self._runner.embed_pooled(list(tokens)[:limit])
+
+    def last_token_logits(self, tokens: List[int]):
+        """fp32 host logits after the last of ``tokens``."""
+        limit = min(self._runner.max_tokens, self._max_seq_len - 1)
+        with self._step_lock:
+            if self.device.type == "cuda":
+                torch.cuda.set_device(self.device)
+            return self._runner.last_logits(list(tokens)[-limit:])
 
     def has_work(self) -> bool:
         return self._scheduler.num_active > 0 or self._scheduler.num_waiting > 0

@@ -83,8 +83,8 @@ class LoRAManager:
             ad = LoRAAdapter(adapter_id, rank, alpha, list(target_modules), num_layers)
             for (layer, mod), (a, b) in arrays.items():
                 fin, fout, rows, _ = self._module_geometry(mod)
-                a_t = torch.as_tensor(np.asarray(a) if not isinstance(a, torch.Tensor) else a).to(torch.float16)
-                b_t = torch.as_tensor(np.asarray(b) if not isinstance(b, torch.Tensor) else b).to(torch.float16)
+                a_t = (a if isinstance(a, torch.Tensor) else torch.from_numpy(np.array(a))).to(torch.float16)
+                b_t = (b if isinstance(b, torch.Tensor) else torch.from_numpy(np.array(b))).to(torch.float16)
                 if tuple(a_t.shape) != (rank, fin) or tuple(b_t.shape) != (fout, rank):
                     raise ValueError(f"bad LoRA shapes for layer {layer} {mod}: A {tuple(a_t.shape)}, "
                                      f"B {tuple(b_t.shape)}")

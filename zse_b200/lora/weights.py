@@ -87,3 +87,25 @@ class LoRAWeightStore:
     @property
     def total_bytes(self) -> int:
         return sum(a.total_bytes for a in self._adapters.values())
+
+
+def random_adapter_file(path: str, config, rank: int = 8, alpha: float = 16.0,
+                        target_modules: Optional[List[str]] = None, seed: int = 0, std: float = 0.05) -> LoRAAdapter:
+    """Writes a ``.zse-lora`` file with random A/B matrices for a model config (tests, benchmarks, smoke runs)."""
+    import numpy as np
+
+    from ..format.lora_format import module_shapes, save_lora
+    targets = list(target_modules or ["q_proj", "k_proj", "v_proj"])
+    shapes = module_shapes(config.hidden_size, config.intermediate_size, config.num_heads, config.num_kv_heads,
+                           config.head_dim)
+    rng = np.random.default_rng(seed)
+    ad = LoRAAdapter("", rank, alpha, targets, config.num_layers)
+    data = {}
+    for layer in range(config.num_layers):
+        for t in targets:
+            fin, fout = shapes[t]
+            data[(layer, t)] = ((rng.standard_normal((rank, fin)) * std).astype(np.float16),
+                                (rng.standard_normal((fout, rank)) * std).astype(np.float16))
+            ad.add_weight(layer, t, LoRAWeight(f"model.layers.{layer}.{t}", rank, fin, fout))
+    save_lora(path, ad, data)
+    return ad

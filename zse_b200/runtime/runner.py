@@ -323,6 +323,16 @@ class ModelRunner:
         logits = self.prefill([(seq_id, tokens, start_position)], all_logits=True, select=False)
         return logits.float().cpu()
 
+    def last_logits(self, tokens: Sequence[int], seq_id: int = 1_000_000_001) -> torch.Tensor:
+        """fp32 host logits after the last of ``tokens`` (one prefill pass on a scratch sequence): what a Yes/No
+        reranker reads."""
+        self.cache.allocate_sequence(seq_id, num_tokens=len(tokens))
+        try:
+            self.prefill([(seq_id, tokens, 0)])
+            return self.buf.logits[0].float().cpu()
+        finally:
+            self.cache.free_sequence(seq_id)
+
     def embed_pooled(self, tokens: Sequence[int], seq_id: int = 1_000_000_000) -> torch.Tensor:
         """Mean-pooled, L2-normalised final hidden state (dense retrieval embeddings), pooled on the device."""
         self.cache.allocate_sequence(seq_id, num_tokens=len(tokens))

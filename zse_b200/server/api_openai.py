@@ -205,6 +205,12 @@ class OpenAIAPI:
                     out = val
                     self._record(request, model, params.get("lora_id"), rid, len(out.prompt_tokens),
                                  len(out.output_tokens), t0)
+                    # text held back while it ended inside a multi-byte character goes out with the last chunk
+                    text = self._decode(ids)
+                    if len(text) > len(sent):
+                        piece, sent = text[len(sent):], text
+                        yield chat_chunk(completion_id, model, content=piece) if chat else \
+                            completion_chunk(completion_id, model, piece)
                     fin = out.finish_reason.value
                     yield chat_chunk(completion_id, model, finish_reason=fin) if chat else \
                         completion_chunk(completion_id, model, "", fin)

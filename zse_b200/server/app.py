@@ -55,8 +55,8 @@ class ZSEServer:
                 from .api_rag import RAGAPI
                 rag_db = ":memory:" if db_path == ":memory:" else os.path.expanduser(db_path) + ".rag"
                 self._rag_engine = RAGEngine(rag_db, tokenizer=tok)
-                if self._engine is not None and hasattr(self._engine, "runner"):
-                    self._rag_engine.set_model_runner(self._engine.runner, tok)
+                if self._engine is not None and hasattr(self._engine, "embed_tokens"):
+                    self._rag_engine.set_model_runner(self._engine)
                 RAGAPI(self._rag_engine, self._auth).register(self.router)
                 self._openai.set_rag_engine(self._rag_engine)
             except ImportError:
@@ -83,8 +83,9 @@ class ZSEServer:
 
     # ---- middleware / basic routes ------------------------------------------------------------------------
     async def _auth_middleware(self, request: Request, handler) -> Response:
-        needs_key = self.require_auth and request.path.startswith("/v1/") and not request.path.startswith(
+        guarded = request.path.startswith("/v1/") and not request.path.startswith(
             ("/v1/health", "/v1/admin", "/v1/dashboard", "/v1/lora"))
+        needs_key = self.require_auth and guarded
         header = request.authorization
         if header:
             res = self._auth.authenticate(header)
@@ -99,7 +100,7 @@ class ZSEServer:
                         chk = self._auth.check_model_access(res.key, model)
                     if not chk.authenticated:
                         return Response.error(chk.error, chk.status_code)
-            elif needs_key:
+            elif guarded:            # a key that is presented must be valid, even where keys are optional
                 return Response.error(res.error, res.status_code)
         elif needs_key:
             return Response.error("Missing Authorization header", 401)
