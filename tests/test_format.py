@@ -225,3 +225,24 @@ def test_reference_loader_reads_our_file_and_vice_versa(tmp_path, tiny_zse):
         p, s, z = Q.quantize_tensor(vals, 128)
         e = l.weight_index.find("layers.0.mlp.up_proj.weight")
         assert l.get_weight_data(e) == p and l.get_weight_scales(e) == s and l.get_weight_zeros(e) == z
+
+
+def test_native_host_quantiser_is_bit_identical_to_numpy():
+    """csrc/host/quant.cpp (the converter's fast path) against format/quantize.py, INT4 and INT8, ragged tail."""
+    from zse_b200.format.quantize import quantize_int4_arrays, quantize_int8_arrays
+    from zse_b200.ops import build, host_native
+    build.build()
+    assert host_native.available()
+    rng = np.random.default_rng(3)
+    for n in (128, 1000, 128 * 513 + 5):
+        v = (rng.standard_normal(n) * 0.05).astype(np.float32)
+        v[:128] = 0.25                                   # a constant group (range below the epsilon)
+        p, s, z = host_native.quantize(v, 1, 128)
+        p2, s2, z2 = quantize_int4_arrays(v, 128)
+        assert np.array_equal(p, p2) and np.array_equal(s.view(np.uint16), s2.view(np.uint16))
+        assert np.array_equal(z.view(np.uint16), z2.view(np.uint16))
+        q, s = host_native.quantize(v, 2, 128)
+        q2, s2 = quantize_int8_arrays(v, 128)
+        assert np.array_equal(q, q2) and np.array_equal(s.view(np.uint16), s2.view(np.uint16))
+    bf = rng.integers(0, 65535, 1000).astype(np.uint16)
+    assert np.array_equal(host_native.bf16_to_f32(bf).view(np.uint32), bf.astype(np.uint32) << 16)
