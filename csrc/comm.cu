@@ -110,6 +110,9 @@ __global__ void __launch_bounds__(kRedThreads)
 tp_reduce_add_rmsnorm_kernel(const TpTable tb, const TpReduceArgs a) {
   __shared__ float red[32];
   __shared__ int ok_flag;
+  // the next kernel (a GEMM) may set itself up and stream weights while this one waits for its peers
+  pdl_launch_dependents();
+  pdl_wait();
   const int er = blockIdx.y;                      // emulated rank slot (0 in a real launch)
   const TpRankArgs me = a.r[er];
   const int rank = me.rank;
@@ -338,11 +341,11 @@ static int launch_reduce(const zse_tp_ctx* c, TpReduceArgs& a, int rows, int emu
                               : (const void*)tp_reduce_add_rmsnorm_kernel<false>;
     return cudaLaunchCooperativeKernel(fn, grid, dim3(kRedThreads), params, 0, st) == cudaSuccess ? 0 : ZSE_ERR_LAUNCH;
   }
-  if (multimem)
-    tp_reduce_add_rmsnorm_kernel<true><<<grid, kRedThreads, 0, st>>>(c->table, a);
-  else
-    tp_reduce_add_rmsnorm_kernel<false><<<grid, kRedThreads, 0, st>>>(c->table, a);
-  return cudaGetLastError() == cudaSuccess ? 0 : ZSE_ERR_LAUNCH;
+  const cudaError_t e = multimem ? launch_pdl(tp_reduce_add_rmsnorm_kernel<true>, grid, dim3(kRedThreads), 0, st,
+                                              c->table, a)
+                                 : launch_pdl(tp_reduce_add_rmsnorm_kernel<false>, grid, dim3(kRedThreads), 0, st,
+                                              c->table, a);
+  return e == cudaSuccess ? 0 : ZSE_ERR_LAUNCH;
 }
 
 // Real launch: residual/partials/out are this rank's.  Rows are processed in launches of at most 512 so that every

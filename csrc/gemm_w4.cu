@@ -668,8 +668,12 @@ static void plan_w4(int M, int N, int K, int epilogue, int sm_count, int want_sp
       if (n_tiles % R != 0) continue;
       if (R == 2 && nt > 128) continue;                         // accumulators + A ring must fit 512 TMEM columns
       const long ctas = long(n_tiles / R) * m_tiles;
-      const int max_ks = planes_ok ? min(kMaxPlanes, k_stages) : 1;
+      // K splits: fp32 planes where the consumer adds them; otherwise a thread-block cluster along K that adds the
+      // accumulators through distributed shared memory before the epilogue (worth it only when tiles alone cannot
+      // fill the machine, e.g. a tensor-parallel shard of the gate/up projection)
+      const int max_ks = min(kMaxPlanes, k_stages);
       for (int ks = 1; ks <= max_ks; ++ks) {
+        if (!planes_ok && ks != 1 && ks != 2 && ks != 4 && ks != 8) continue;
         const long total = ctas * ks;
         const long cap = long(sm_count) * (dual ? 2 : 1);
         const long waves = (total + cap - 1) / cap;
@@ -687,7 +691,7 @@ static void plan_w4(int M, int N, int K, int epilogue, int sm_count, int want_sp
           const double tail = last > sm_count ? full : chunks * (solo_chunk + xshare) + 8.0;
           cost = double(waves - 1) * full + tail;
         }
-        cost += ks > 1 ? 1.0 : 0.0;
+        cost += ks > 1 ? (planes_ok ? 1.0 : 6.0 + 0.5 * ks) : 0.0;
         if (best_cost < 0 || cost < best_cost - 1e-9 || (cost < best_cost + 1e-9 && !dual && R > best_r)) {
           best_cost = cost;
           best_r = R;
@@ -697,7 +701,7 @@ static void plan_w4(int M, int N, int K, int epilogue, int sm_count, int want_sp
       }
     }
   }
-  *cluster_out = 1;
+  *cluster_out = (!planes_ok && best_ks > 1) ? best_ks : 1;
   if (want_split > 0) {                                         // explicit request: planes if possible, else a cluster
     best_ks = max(1, min(want_split, min(8, k_stages)));
     if (!planes_ok) *cluster_out = best_ks;

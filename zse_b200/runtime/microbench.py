@@ -48,8 +48,10 @@ def main():
     prof = KernelProfiler(iters=a.iters)
     peaks = measured_peaks()
     M, H, tp = a.tokens, c.hidden_size, a.tp
-    nh, nkv, hd = c.num_heads // tp, c.num_kv_heads // tp, c.head_dim
-    q_dim, kv_dim, I = nh * hd, nkv * hd, c.intermediate_size // tp
+    from ..parallel.shard_plan import make_plan
+    plan = make_plan(c, tp, 0)              # rank 0's shard: group-aligned, so possibly the larger of two sizes
+    nh, nkv, hd = plan.num_heads, plan.num_kv_heads, c.head_dim
+    q_dim, kv_dim, I = nh * hd, nkv * hd, plan.inter_size
     only = set(x for x in a.only.split(",") if x)
     rows = []
     x = (torch.randn(M, H, device="cuda") * 0.5).half()
