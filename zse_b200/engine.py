@@ -101,6 +101,7 @@ class ZStreamerEngine:
         if on_gpu:
             torch.cuda.synchronize(self.device)
         self.init_times["weights"] = time.monotonic() - t1
+        self.init_times.update(self._model.load_stats)
 
         t2 = time.monotonic()
         mc = self._config

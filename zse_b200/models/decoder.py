@@ -14,6 +14,7 @@ SwiGLU epilogue -> down_proj (split-K partials).  That is 8 launches where the r
 from __future__ import annotations
 
 import math
+import os
 from dataclasses import dataclass
 from typing import Dict, List, Optional
 
@@ -29,8 +30,9 @@ from ..parallel.shard_plan import ShardPlan, make_plan
 SUPPORTED_ARCHS = ("llama", "mistral", "qwen2", "phi3")
 
 
-def _entry_part(loader: ZSELoader, name: str, rows=None, cols=None) -> dict:
-    """Numpy views of one stored tensor, optionally restricted to a row range and/or a column (K) range."""
+def _entry_part(loader: ZSELoader, name: str, rows=None, cols=None, mirror=None) -> dict:
+    """Views of one stored tensor, optionally restricted to a row range and/or a column (K) range: numpy views of the
+    file mapping, or (with ``mirror``, a DeviceMirror of the weight section) device views."""
     e = loader.weight_index.find(name)
     if e is None:
         raise KeyError(name)
@@ -38,6 +40,17 @@ def _entry_part(loader: ZSELoader, name: str, rows=None, cols=None) -> dict:
     r0, r1 = rows if rows is not None else (0, N)
     c0, c1 = cols if cols is not None else (0, K)
     gs = e.group_size
+    if mirror is not None:
+        if e.dtype == "float16":
+            t = mirror.view(e.data_offset, e.data_nbytes, "float16").reshape(N, K)
+            return {"dtype": "float16", "data": t[r0:r1, c0:c1], "shape": (r1 - r0, c1 - c0)}
+        if (e.dtype == "int4" and loader.int4_layout_of(e) == "rowmajor" and K % gs == 0 and c0 % gs == 0
+                and c1 % gs == 0):
+            p = mirror.view(e.data_offset, N * K // 2).reshape(N, K // 2)[r0:r1, c0 // 2: c1 // 2]
+            s = mirror.view(e.scale_offset, N * (K // gs) * 2, "float16").reshape(N, K // gs)[r0:r1, c0 // gs: c1 // gs]
+            z = mirror.view(e.zeros_offset, N * (K // gs) * 2, "float16").reshape(N, K // gs)[r0:r1, c0 // gs: c1 // gs]
+            return {"dtype": "int4", "data": p, "scales": s, "zeros": z, "shape": (r1 - r0, c1 - c0)}
+        # anything else (INT8, tiled INT4 files, groups that straddle rows) takes the host path below
     if e.dtype == "float16":
         return {"dtype": "float16", "data": loader.view_data(e)[r0:r1, c0:c1], "shape": (r1 - r0, c1 - c0)}
     if e.dtype == "int8":
@@ -134,6 +147,7 @@ class DecoderModel:
         self.comm = None            # parallel.comm.TPComm when tp_size > 1
         self.lora = None            # lora.manager.LoRAManager
         self.weight_bytes = 0
+        self.load_stats: Dict[str, float] = {}
         self.embed_scale = math.sqrt(config.hidden_size) if config.embed_scale else 1.0
 
     # ---- loading --------------------------------------------------------------------------------------
@@ -154,7 +168,19 @@ class DecoderModel:
         gs = c.quant.group_size
         has = lambda n: loader.weight_index.find(n) is not None
         to_dev = lambda a: np_to_dev(a, dev)
-        self.embed = to_dev(loader.view_data(loader.weight_index.find("embed_tokens.weight")))
+        mirror = None
+        if dev.type == "cuda" and p.tp_size == 1 and os.environ.get("ZSE_STREAM_WEIGHTS", "1") != "0":
+            from ..runtime.weight_stream import DeviceMirror
+            mirror = DeviceMirror(loader, dev)
+            self.load_stats["stream_s"] = round(mirror.seconds, 3)
+            self.load_stats["stream_gbs"] = round(mirror.size / max(mirror.seconds, 1e-9) / 1e9, 2)
+        _part = lambda name, rows=None, cols=None: _entry_part(loader, name, rows, cols, mirror)
+        e_embed = loader.weight_index.find("embed_tokens.weight")
+        if mirror is not None and e_embed.dtype == "float16":
+            self.embed = mirror.view(e_embed.data_offset, e_embed.data_nbytes, "float16").reshape(
+                e_embed.shape).clone()
+        else:
+            self.embed = to_dev(loader.view_data(e_embed))
         self.norm = to_dev(_vec(loader, "norm.weight"))
         self.weight_bytes += self.embed.numel() * 2
         q_dim_full = c.num_heads * c.head_dim
@@ -163,32 +189,32 @@ class DecoderModel:
             pre = f"layers.{i}."
             if has(pre + "self_attn.qkv_proj.weight"):     # Phi-3: [q; k; v] stacked in one tensor
                 n = pre + "self_attn.qkv_proj.weight"
-                qp = _entry_part(loader, n, rows=p.q_rows)
-                kp = _entry_part(loader, n, rows=(q_dim_full + p.kv_rows[0], q_dim_full + p.kv_rows[1]))
-                vp = _entry_part(loader, n, rows=(q_dim_full + kv_dim_full + p.kv_rows[0],
+                qp = _part(n, rows=p.q_rows)
+                kp = _part(n, rows=(q_dim_full + p.kv_rows[0], q_dim_full + p.kv_rows[1]))
+                vp = _part(n, rows=(q_dim_full + kv_dim_full + p.kv_rows[0],
                                                   q_dim_full + kv_dim_full + p.kv_rows[1]))
                 bias = None
             else:
-                qp = _entry_part(loader, pre + "self_attn.q_proj.weight", rows=p.q_rows)
-                kp = _entry_part(loader, pre + "self_attn.k_proj.weight", rows=p.kv_rows)
-                vp = _entry_part(loader, pre + "self_attn.v_proj.weight", rows=p.kv_rows)
+                qp = _part(pre + "self_attn.q_proj.weight", rows=p.q_rows)
+                kp = _part(pre + "self_attn.k_proj.weight", rows=p.kv_rows)
+                vp = _part(pre + "self_attn.v_proj.weight", rows=p.kv_rows)
                 bq = _vec(loader, pre + "self_attn.q_proj.bias", p.q_rows)
                 bias = None
                 if bq is not None:
                     bias = np.concatenate([bq, _vec(loader, pre + "self_attn.k_proj.bias", p.kv_rows),
                                            _vec(loader, pre + "self_attn.v_proj.bias", p.kv_rows)])
             qkv = ops.make_linear([qp, kp, vp], c.hidden_size, gs, bias)
-            o = ops.make_linear([_entry_part(loader, pre + "self_attn.o_proj.weight", cols=p.q_rows)], p.q_dim, gs)
+            o = ops.make_linear([_part(pre + "self_attn.o_proj.weight", cols=p.q_rows)], p.q_dim, gs)
             if has(pre + "mlp.gate_up_proj.weight"):       # Phi-3: [gate; up]
                 n = pre + "mlp.gate_up_proj.weight"
                 I = c.intermediate_size
-                gp = _entry_part(loader, n, rows=p.inter)
-                up = _entry_part(loader, n, rows=(I + p.inter[0], I + p.inter[1]))
+                gp = _part(n, rows=p.inter)
+                up = _part(n, rows=(I + p.inter[0], I + p.inter[1]))
             else:
-                gp = _entry_part(loader, pre + "mlp.gate_proj.weight", rows=p.inter)
-                up = _entry_part(loader, pre + "mlp.up_proj.weight", rows=p.inter)
+                gp = _part(pre + "mlp.gate_proj.weight", rows=p.inter)
+                up = _part(pre + "mlp.up_proj.weight", rows=p.inter)
             gate_up = ops.make_linear([gp, up], c.hidden_size, gs, swiglu=True)
-            down = ops.make_linear([_entry_part(loader, pre + "mlp.down_proj.weight", cols=p.inter)], p.inter_size, gs)
+            down = ops.make_linear([_part(pre + "mlp.down_proj.weight", cols=p.inter)], p.inter_size, gs)
             self.layers.append(LayerWeights(to_dev(_vec(loader, pre + "input_layernorm.weight")),
                                             to_dev(_vec(loader, pre + "post_attention_layernorm.weight")),
                                             qkv, o, gate_up, down))
@@ -196,8 +222,10 @@ class DecoderModel:
             if progress:
                 progress(i + 1, c.num_layers)
         head_name = "lm_head.weight" if has("lm_head.weight") else "embed_tokens.weight"   # tied embeddings
-        self.lm_head = ops.make_linear([_entry_part(loader, head_name, rows=p.vocab)], c.hidden_size, gs)
+        self.lm_head = ops.make_linear([_part(head_name, rows=p.vocab)], c.hidden_size, gs)
         self.weight_bytes += self.lm_head.nbytes
+        if mirror is not None:
+            mirror.release()
         self.inv_freq = ref.inv_freq(c.head_dim, c.rope_theta, c.rope_scaling).to(dev)
 
     # ---- buffers --------------------------------------------------------------------------------------

@@ -189,9 +189,12 @@ class CudaOps(TorchOps):
             n_tiles = (inter + 63) // 64 if swiglu else (N + 127) // 128
             out = torch.empty(n_tiles * (K // 128) * 8704, dtype=torch.uint8, device=self.device)
             n.repack_w4(packed, scales, zeros, out, N, K, inter)
-            torch.cuda.current_stream().synchronize()
             return LinearWeight("w4t", N, K, out, b, swiglu, out.numel())
         # anything else becomes dense fp16 for the SS-mode kernel
+        if all(p["dtype"] == "float16" for p in parts):      # already fp16: one copy, no fp32 round trip
+            ws = [_np_to_dev(p["data"], self.device).reshape(tuple(p["shape"])) for p in parts]
+            w = torch.cat(ws, dim=0) if len(ws) > 1 else ws[0].clone(memory_format=torch.contiguous_format)
+            return LinearWeight("f16", w.shape[0], K, w, b, swiglu, w.numel() * 2)
         ws = [_dense_f32(p, group_size, self.device).to(torch.float16) for p in parts]
         w = torch.cat(ws, dim=0).contiguous() if len(ws) > 1 else ws[0].contiguous()
         return LinearWeight("f16", w.shape[0], K, w, b, swiglu, w.numel() * 2)
