@@ -172,6 +172,9 @@ def run_ours(args):
     prefill_s = time.time() - t_pf
     active = eng.scheduler.num_decoding
     assert active == args.requests, f"{active} of {args.requests} sequences decoding"
+    # time to first token of every request (all of them arrive at once, so queueing behind the others counts)
+    ttfts = sorted((r.first_token_time - r.arrival_time) * 1000.0 for r in eng.scheduler.active_requests()
+                   if r.first_token_time is not None)
     for _ in range(args.warmup):
         eng.step()
     barrier()
@@ -193,7 +196,8 @@ def run_ours(args):
         torch.cuda.profiler.stop()
     barrier()
     clocks = sampler.stop() if sampler else None
-    dev_ms = sum(a.elapsed_time(b) for a, b in runner.step_events)
+    step_ms = [a.elapsed_time(b) for a, b in runner.step_events]
+    dev_ms = sum(step_ms)
     n_steps = len(runner.step_events)
     runner.step_events = None
     tokens = eng.stats().total_tokens_generated - tokens0
@@ -230,7 +234,10 @@ def run_ours(args):
             "extra": {"cold_start_s": round(cold, 2), "prefill_s": round(prefill_s, 2),
                       "init_times": {k: round(v, 2) for k, v in eng.init_times.items()},
                       "kv_blocks": eng.kv_cache.num_total_blocks, "block_size": eng.kv_cache.block_size,
-                      "graph_replays": runner.timings["graph_replays"], "impl": "ours"},
+                      "graph_replays": runner.timings["graph_replays"], "impl": "ours",
+                      "ttft_p50_ms": round(ttfts[len(ttfts) // 2], 1) if ttfts else None,
+                      "ttft_max_ms": round(ttfts[-1], 1) if ttfts else None,
+                      "tpot_p50_ms": round(sorted(step_ms)[len(step_ms) // 2], 3) if step_ms else None},
         }
         print(json.dumps(line), flush=True)
     if world > 1:

@@ -96,6 +96,14 @@ int zse_tp_reduce_add_rmsnorm(void* ctx, void* residual, const void* partials, i
 int zse_tp_reduce_add_rmsnorm_emulated(void* ctx, const uint64_t* residuals, const uint64_t* partials, int n_planes,
                                        const void* weight, const uint64_t* outs, int M, float eps,
                                        int slot, void* status, void* stream);
+// Two-shot form for many rows (prefill): reduce-scatter by rows (row r is reduced by rank r % tp, which also keeps the
+// only current copy of the fp32 residual row) + all-gather of the normalised rows, in one kernel.
+int zse_tp_reduce_scatter_add_rmsnorm(void* ctx, void* residual, const void* partials, int n_planes,
+                                      const void* weight, void* out, int M, float eps, int slot, int use_multimem,
+                                      void* status, void* stream);
+int zse_tp_reduce_scatter_add_rmsnorm_emulated(void* ctx, const uint64_t* residuals, const uint64_t* partials,
+                                               int n_planes, const void* weight, const uint64_t* outs, int M,
+                                               float eps, int slot, void* status, void* stream);
 int zse_tp_argmax(void* ctx, const void* logits, int ld, void* out, int M, int V_local, int vocab_stride,
                   int slot, void* status, void* stream);
 int zse_tp_argmax_emulated(void* ctx, const uint64_t* logits, int ld, const uint64_t* outs, int M, int V_local,

@@ -23,6 +23,8 @@
 // started cooperatively so that all CTAs are resident.  That is how the protocol is tested on a single GPU.
 #include <cooperative_groups.h>
 
+#include <stdlib.h>
+
 #include "api.h"
 #include "common.cuh"
 
@@ -105,25 +107,12 @@ __device__ __forceinline__ void acc_h8(float* a, const uint4& v) {
   }
 }
 
-template <bool kMultimem>
-__global__ void __launch_bounds__(kRedThreads)
-tp_reduce_add_rmsnorm_kernel(const TpTable tb, const TpReduceArgs a) {
-  __shared__ float red[32];
-  __shared__ int ok_flag;
-  // the next kernel (a GEMM) may set itself up and stream weights while this one waits for its peers
-  pdl_launch_dependents();
-  pdl_wait();
-  const int er = blockIdx.y;                      // emulated rank slot (0 in a real launch)
-  const TpRankArgs me = a.r[er];
-  const int rank = me.rank;
-  const int row = a.row0 + blockIdx.x;
+// Phase A of both reductions: sum of this rank's fp32 split-K planes of one row, rounded to fp16, into the rank's
+// symmetric row buffer.
+__device__ __forceinline__ void reduce_phase_a(const TpTable& tb, const TpReduceArgs& a, const TpRankArgs& me, int rank,
+                                               int row, size_t row_off) {
   const int H = a.H, nch = H / 8;
-  const size_t slot_off = size_t(a.slot) * tb.m_cap * H;
-  const size_t row_off = slot_off + size_t(row) * H;
   const size_t plane = size_t(a.M) * H;
-  if (threadIdx.x == 0) ok_flag = 1;
-
-  // ---- phase A: local planes -> fp16 row in this rank's symmetric buffer ------------------------------------
 #pragma unroll
   for (int j = 0; j < kRedMaxChunks; ++j) {
     const int c = threadIdx.x + j * kRedThreads;
@@ -156,6 +145,27 @@ tp_reduce_add_rmsnorm_kernel(const TpTable tb, const TpReduceArgs a) {
       reinterpret_cast<uint4*>(tb.data[rank] + row_off)[c] = pk;
     }
   }
+}
+
+template <bool kMultimem>
+__global__ void __launch_bounds__(kRedThreads)
+tp_reduce_add_rmsnorm_kernel(const TpTable tb, const TpReduceArgs a) {
+  __shared__ float red[32];
+  __shared__ int ok_flag;
+  // the next kernel (a GEMM) may set itself up and stream weights while this one waits for its peers
+  pdl_launch_dependents();
+  pdl_wait();
+  const int er = blockIdx.y;                      // emulated rank slot (0 in a real launch)
+  const TpRankArgs me = a.r[er];
+  const int rank = me.rank;
+  const int row = a.row0 + blockIdx.x;
+  const int H = a.H, nch = H / 8;
+  const size_t slot_off = size_t(a.slot) * tb.m_cap * H;
+  const size_t row_off = slot_off + size_t(row) * H;
+  if (threadIdx.x == 0) ok_flag = 1;
+
+  // ---- phase A: local planes -> fp16 row in this rank's symmetric buffer ------------------------------------
+  reduce_phase_a(tb, a, me, rank, row, row_off);
   __syncthreads();
   if (threadIdx.x < tb.tp) {
     __threadfence_system();
@@ -223,6 +233,123 @@ tp_reduce_add_rmsnorm_kernel(const TpTable tb, const TpReduceArgs a) {
       }
       reinterpret_cast<uint4*>(me.out + size_t(row) * H)[c] = pk;
     }
+  }
+}
+
+// ---- two-shot variant for many rows (prefill): reduce-scatter + all-gather inside one kernel -------------------
+// Row r belongs to rank r % tp.  Every rank still sums its own planes of every row (phase A) and raises the row's flag,
+// but only at the owner.  The owner waits for all ranks, adds their rows (peer loads in rank order, or one
+// multimem.ld_reduce), adds its residual row and normalises: the fp32 residual stream is therefore sharded by rows -
+// nobody else needs it, because the same owner reduces that row in every layer of the pass.  The normalised fp16 row
+// goes to the owner's own output AND back into its symmetric row (whose phase-A content is spent), and a second flag is
+// raised at every peer; the other ranks wait for that flag and pull the finished row.  Per row and rank 1 row crosses
+// NVLink inwards in the scatter phase (owner: tp-1 rows) and 1 in the gather phase, instead of tp-1 rows for every
+// rank in the one-shot kernel: 2 (tp-1)/tp of a row per rank instead of tp-1.
+template <bool kMultimem>
+__global__ void __launch_bounds__(kRedThreads)
+tp_reduce_scatter_add_rmsnorm_kernel(const TpTable tb, const TpReduceArgs a) {
+  __shared__ float red[32];
+  __shared__ int ok_flag;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int er = blockIdx.y;
+  const TpRankArgs me = a.r[er];
+  const int rank = me.rank, tp = tb.tp;
+  const int row = a.row0 + blockIdx.x;
+  const int owner = row % tp;
+  const int H = a.H, nch = H / 8;
+  const size_t row_off = (size_t(a.slot) * tb.m_cap + size_t(row)) * H;
+  if (threadIdx.x == 0) ok_flag = 1;
+
+  reduce_phase_a(tb, a, me, rank, row, row_off);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence_system();
+    st_release_sys(tb.flags[owner] + (size_t(a.slot) * tp + rank) * tb.m_cap + row, 1u);
+  }
+  if (rank != owner) {
+    // ---- gather side: wait for the owner's finished row, copy it
+    if (threadIdx.x == 0 &&
+        !wait_flag(tb.flags[rank] + (size_t(a.slot) * tp + owner) * tb.m_cap + row, a.status, 33, owner))
+      ok_flag = 0;
+    __syncthreads();
+    if (ok_flag != 0) {
+#pragma unroll
+      for (int j = 0; j < kRedMaxChunks; ++j) {
+        const int c = threadIdx.x + j * kRedThreads;
+        if (c < nch)
+          reinterpret_cast<uint4*>(me.out + size_t(row) * H)[c] =
+              ld_relaxed_sys_v4(tb.data[owner] + row_off + size_t(c) * 8);
+      }
+    }
+    return;
+  }
+  // ---- owner: wait for every rank's row, reduce, residual add, RMSNorm, publish
+  if (threadIdx.x < tp) {
+    if (!wait_flag(tb.flags[rank] + (size_t(a.slot) * tp + threadIdx.x) * tb.m_cap + row, a.status, 32, threadIdx.x))
+      ok_flag = 0;
+  }
+  __syncthreads();
+  const bool ok = ok_flag != 0;
+  float vals[kRedMaxChunks][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < kRedMaxChunks; ++j) {
+    const int c = threadIdx.x + j * kRedThreads;
+    if (c < nch) {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      if (ok) {
+        if (kMultimem) {
+          acc_h8(acc, multimem_ld_reduce_f16x8(tb.mc_data + row_off + size_t(c) * 8));
+        } else {
+          uint4 got[kMaxTp];
+#pragma unroll
+          for (int r = 0; r < kMaxTp; ++r)
+            if (r < tp) got[r] = ld_relaxed_sys_v4(tb.data[r] + row_off + size_t(c) * 8);
+#pragma unroll
+          for (int r = 0; r < kMaxTp; ++r)
+            if (r < tp) acc_h8(acc, got[r]);
+        }
+      }
+      float4* res = reinterpret_cast<float4*>(me.residual + size_t(row) * H) + 2 * c;
+      float4 x = res[0], y = res[1];
+      x.x += acc[0]; x.y += acc[1]; x.z += acc[2]; x.w += acc[3];
+      y.x += acc[4]; y.y += acc[5]; y.z += acc[6]; y.w += acc[7];
+      res[0] = x;
+      res[1] = y;
+      vals[j][0] = x.x; vals[j][1] = x.y; vals[j][2] = x.z; vals[j][3] = x.w;
+      vals[j][4] = y.x; vals[j][5] = y.y; vals[j][6] = y.z; vals[j][7] = y.w;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ss += vals[j][i] * vals[j][i];
+    }
+  }
+  ss = warp_sum(ss);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();                                  // also: every thread has finished reading the symmetric rows
+  float tot = (threadIdx.x & 31) < (kRedThreads >> 5) ? red[threadIdx.x & 31] : 0.f;
+  tot = warp_sum(tot);
+  const float inv = rsqrtf(tot / float(H) + a.eps);
+#pragma unroll
+  for (int j = 0; j < kRedMaxChunks; ++j) {
+    const int c = threadIdx.x + j * kRedThreads;
+    if (c < nch) {
+      const uint4 wr = reinterpret_cast<const uint4*>(a.weight)[c];
+      const __half2* wh = reinterpret_cast<const __half2*>(&wr);
+      uint4 pk;
+      uint32_t* po = reinterpret_cast<uint32_t*>(&pk);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 w = __half22float2(wh[i]);
+        po[i] = pack_half2(vals[j][2 * i] * inv * w.x, vals[j][2 * i + 1] * inv * w.y);
+      }
+      reinterpret_cast<uint4*>(me.out + size_t(row) * H)[c] = pk;
+      reinterpret_cast<uint4*>(tb.data[rank] + row_off)[c] = pk;       // what the other ranks pull
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x < tp && threadIdx.x != rank) {
+    __threadfence_system();
+    st_release_sys(tb.flags[threadIdx.x] + (size_t(a.slot) * tp + owner) * tb.m_cap + row, 1u);
   }
 }
 
@@ -332,6 +459,18 @@ extern "C" void* zse_tp_ctx_create(int tp, int rank, int m_cap, int H, const uin
 
 extern "C" void zse_tp_ctx_destroy(void* ctx) { delete reinterpret_cast<zse_tp_ctx*>(ctx); }
 
+// Programmatic dependent launch for the reduce kernels: off unless ZSE_TP_PDL=1.  Measured on 2 GPUs: a reduce kernel
+// that starts early spins on its peers' flags while the GEMM before it still runs and slows the whole step
+// (7.5 ms vs 6.4 ms per decode step), so these kernels keep the ordinary stream order.
+static bool tp_pdl_allowed() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("ZSE_TP_PDL");
+    v = (e != nullptr && e[0] == '1') ? 1 : 0;
+  }
+  return v != 0;
+}
+
 static int launch_reduce(const zse_tp_ctx* c, TpReduceArgs& a, int rows, int emulate, bool multimem,
                          cudaStream_t st) {
   dim3 grid(rows, emulate > 0 ? emulate : 1);
@@ -341,10 +480,29 @@ static int launch_reduce(const zse_tp_ctx* c, TpReduceArgs& a, int rows, int emu
                               : (const void*)tp_reduce_add_rmsnorm_kernel<false>;
     return cudaLaunchCooperativeKernel(fn, grid, dim3(kRedThreads), params, 0, st) == cudaSuccess ? 0 : ZSE_ERR_LAUNCH;
   }
-  const cudaError_t e = multimem ? launch_pdl(tp_reduce_add_rmsnorm_kernel<true>, grid, dim3(kRedThreads), 0, st,
-                                              c->table, a)
-                                 : launch_pdl(tp_reduce_add_rmsnorm_kernel<false>, grid, dim3(kRedThreads), 0, st,
-                                              c->table, a);
+  const bool pdl = tp_pdl_allowed();
+  const cudaError_t e = multimem ? launch_pdl_if(pdl, tp_reduce_add_rmsnorm_kernel<true>, grid, dim3(kRedThreads), 0,
+                                                 st, c->table, a)
+                                 : launch_pdl_if(pdl, tp_reduce_add_rmsnorm_kernel<false>, grid, dim3(kRedThreads), 0,
+                                                 st, c->table, a);
+  return e == cudaSuccess ? 0 : ZSE_ERR_LAUNCH;
+}
+
+static int launch_reduce_scatter(const zse_tp_ctx* c, TpReduceArgs& a, int rows, int emulate, bool multimem,
+                                 cudaStream_t st) {
+  dim3 grid(rows, emulate > 0 ? emulate : 1);
+  if (emulate > 0) {
+    void* params[] = {const_cast<TpTable*>(&c->table), &a};
+    return cudaLaunchCooperativeKernel((const void*)tp_reduce_scatter_add_rmsnorm_kernel<false>, grid,
+                                       dim3(kRedThreads), params, 0, st) == cudaSuccess
+               ? 0
+               : ZSE_ERR_LAUNCH;
+  }
+  const bool pdl = tp_pdl_allowed();
+  const cudaError_t e = multimem ? launch_pdl_if(pdl, tp_reduce_scatter_add_rmsnorm_kernel<true>, grid,
+                                                 dim3(kRedThreads), 0, st, c->table, a)
+                                 : launch_pdl_if(pdl, tp_reduce_scatter_add_rmsnorm_kernel<false>, grid,
+                                                 dim3(kRedThreads), 0, st, c->table, a);
   return e == cudaSuccess ? 0 : ZSE_ERR_LAUNCH;
 }
 
@@ -373,6 +531,56 @@ extern "C" int zse_tp_reduce_add_rmsnorm(void* ctx, void* residual, const void* 
       return rc;
   }
   return 0;
+}
+
+// Two-shot variant (see the kernel): after it the fp32 residual is current only in the rows this rank owns
+// (row % tp == rank); `out` is complete on every rank.
+extern "C" int zse_tp_reduce_scatter_add_rmsnorm(void* ctx, void* residual, const void* partials, int n_planes,
+                                                 const void* weight, void* out, int M, float eps, int slot,
+                                                 int use_multimem, void* status, void* stream) {
+  zse_tp_ctx* c = reinterpret_cast<zse_tp_ctx*>(ctx);
+  if (M <= 0) return 0;
+  if (c == nullptr || out == nullptr || c->H % 8 || c->H > 8 * kRedThreads * kRedMaxChunks || M > c->table.m_cap)
+    return ZSE_ERR_SHAPE;
+  if (use_multimem && c->table.mc_data == nullptr) return ZSE_ERR_SHAPE;
+  TpReduceArgs a{};
+  a.r[0] = TpRankArgs{reinterpret_cast<float*>(residual), reinterpret_cast<const float*>(partials),
+                      reinterpret_cast<__half*>(out), c->rank};
+  a.weight = reinterpret_cast<const __half*>(weight);
+  a.n_planes = n_planes;
+  a.M = M;
+  a.H = c->H;
+  a.eps = eps;
+  a.slot = slot & 1;
+  a.status = reinterpret_cast<Status*>(status);
+  for (int row0 = 0; row0 < M; row0 += 512) {
+    a.row0 = row0;
+    if (int rc = launch_reduce_scatter(c, a, min(512, M - row0), 0, use_multimem != 0,
+                                       reinterpret_cast<cudaStream_t>(stream)))
+      return rc;
+  }
+  return 0;
+}
+
+extern "C" int zse_tp_reduce_scatter_add_rmsnorm_emulated(void* ctx, const uint64_t* residuals,
+                                                          const uint64_t* partials, int n_planes, const void* weight,
+                                                          const uint64_t* outs, int M, float eps, int slot,
+                                                          void* status, void* stream) {
+  zse_tp_ctx* c = reinterpret_cast<zse_tp_ctx*>(ctx);
+  if (c == nullptr || M <= 0 || M > c->table.m_cap || M * c->table.tp > 256) return ZSE_ERR_SHAPE;
+  TpReduceArgs a{};
+  for (int r = 0; r < c->table.tp; ++r)
+    a.r[r] = TpRankArgs{reinterpret_cast<float*>(residuals[r]), reinterpret_cast<const float*>(partials[r]),
+                        reinterpret_cast<__half*>(outs[r]), r};
+  a.weight = reinterpret_cast<const __half*>(weight);
+  a.n_planes = n_planes;
+  a.M = M;
+  a.H = c->H;
+  a.eps = eps;
+  a.slot = slot & 1;
+  a.row0 = 0;
+  a.status = reinterpret_cast<Status*>(status);
+  return launch_reduce_scatter(c, a, M, c->table.tp, false, reinterpret_cast<cudaStream_t>(stream));
 }
 
 // Single-GPU emulation of all ranks in one cooperative launch (tests): arrays hold one pointer per rank.

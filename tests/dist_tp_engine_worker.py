@@ -1,0 +1,62 @@
+"""Child process of tests/test_comm_gpu.py: the serving engine under tensor parallelism on real GPUs (one rank per GPU,
+launched by torch.distributed.run).  Prompts long enough for the two-shot prefill reduction, then decode through the
+one-shot kernel and the sharded lm_head; every rank must produce the tokens of the single-GPU engine."""
+import os
+import random
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = torch.device(f"cuda:{local}")
+    dist.init_process_group("nccl", device_id=dev)
+    from zse_b200.config import EngineConfig
+    from zse_b200.engine import ZStreamerEngine
+    from zse_b200.format import synth
+    from zse_b200.parallel.comm import make_comm
+    path = "/tmp/zse_tp_engine_test.zse"
+    if rank == 0:
+        synth.write_random_model(path, synth.shape_config("small-128"), seed=11)
+    dist.barrier()
+    rng = random.Random(5)
+    vocab = synth.shape_config("small-128").vocab_size
+    prompts = [[rng.randrange(vocab) for _ in range(n)] for n in (300, 17, 150, 64)]
+    results = {}
+    for backend in ("single", "fused", "nccl"):
+        tp = 1 if backend == "single" else world
+        cfg = EngineConfig(tp_size=tp, device_index=local, max_seq_len=512, max_batch_seqs=8, max_batch_tokens=1024,
+                           prefill_chunk_size=512, comm_backend=backend if tp > 1 else "fused", quiet=True)
+        comm = None
+        if tp > 1:
+            comm = make_comm(backend, rank, world, dev, hidden_size=synth.SHAPES["small-128"]["hidden_size"],
+                             max_tokens=cfg.max_batch_tokens)
+        eng = ZStreamerEngine(path, config=cfg, comm=comm, tp_rank=rank if tp > 1 else 0)
+        ids = [eng.add_request_tokens(p, max_tokens=12, temperature=0.0, stop_tokens=[]) for p in prompts]
+        eng.run_until_done()
+        results[backend] = [eng.get_result(i).output_tokens for i in ids]
+        eng.destroy()
+        torch.cuda.synchronize()
+        dist.barrier()
+    same_fused = sum(a == b for a, b in zip(results["fused"], results["single"]))
+    same_nccl = sum(a == b for a, b in zip(results["nccl"], results["single"]))
+    # fp16 rounding differs between one GPU and a sharded sum, so a near tie may flip a token: demand that every
+    # rank agrees with every other rank exactly, and that most sequences match the single-GPU run token by token
+    gathered = [None] * world
+    dist.all_gather_object(gathered, results["fused"])
+    assert all(g == gathered[0] for g in gathered), "ranks disagree"
+    assert same_fused >= len(prompts) - 1 and same_nccl >= len(prompts) - 1, (results, same_fused, same_nccl)
+    if rank == 0:
+        print(f"TP_ENGINE_OK fused {same_fused}/{len(prompts)} nccl {same_nccl}/{len(prompts)}")
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -55,6 +55,44 @@ def test_reduce_add_rmsnorm_emulated_ranks(tp, M, H, planes):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("tp,M,H,planes", [(2, 9, 512, 1), (4, 30, 1024, 3), (8, 17, 2048, 2)])
+def test_reduce_scatter_add_rmsnorm_emulated_ranks(tp, M, H, planes):
+    """Two-shot form: row r is reduced by rank r % tp only (its residual row is the only current one), the normalised
+    rows are complete and identical on every rank."""
+    from zse_b200.ops import native
+    ctx, keep = _emulated_ctx(tp, 32, H)
+    status = native.Status("cuda")
+    w = (1 + 0.1 * torch.randn(H, device="cuda")).half()
+    res0 = torch.randn(M, H, device="cuda")
+    residuals = [res0.clone() for _ in range(tp)]
+    partials = [torch.randn(planes, M, H, device="cuda") for _ in range(tp)]
+    outs = [torch.zeros(M, H, dtype=torch.float16, device="cuda") for _ in range(tp)]
+    rows = torch.arange(M, device="cuda")
+    for call in range(4):
+        native.tp_reduce_scatter_add_rmsnorm_emulated(ctx, residuals, partials, planes, w, outs, M, 1e-6, call & 1,
+                                                      status.ptr)
+        torch.cuda.synchronize()
+        status.check()
+        total = sum(p.sum(0).half().float() for p in partials)
+        want_res = res0 + (call + 1) * total
+        want_out = ref.rmsnorm(want_res, w, 1e-6).float()
+        for r in range(tp):
+            own = rows % tp == r
+            assert torch.allclose(residuals[r][own], want_res[own], atol=2e-3, rtol=1e-4), (call, r)
+            assert torch.equal(residuals[r][~own], res0[~own])      # rows of other owners are not touched
+            assert torch.equal(outs[r], outs[0])
+            assert (outs[r].float() - want_out).abs().max() < 1e-2
+        assert all(int(f.abs().sum()) == 0 for f in keep[1])        # all flags are down again
+    # mixing with the one-shot form afterwards works on the same context (flags are all down)
+    residuals = [res0.clone() for _ in range(tp)]
+    native.tp_reduce_add_rmsnorm_emulated(ctx, residuals, partials, planes, w, outs, M, 1e-6, 0, status.ptr)
+    torch.cuda.synchronize()
+    status.check()
+    assert torch.allclose(residuals[tp - 1], res0 + sum(p.sum(0).half().float() for p in partials), atol=2e-3, rtol=1e-4)
+    native.tp_ctx_destroy(ctx)
+
+
+@pytest.mark.gpu
 def test_tp_argmax_emulated_ranks():
     from zse_b200.ops import native
     tp, M, V_local = 4, 6, 1000
@@ -110,3 +148,17 @@ def test_fused_comm_matches_nccl_on_real_gpus():
                        timeout=600, env=env, cwd=ROOT)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     assert "FUSED_COMM_OK" in r.stdout
+
+
+@pytest.mark.gpu
+@pytest.mark.multigpu
+def test_tp_engine_on_real_gpus_matches_single_gpu():
+    n = min(torch.cuda.device_count(), 4)
+    if n < 2:
+        pytest.skip("needs at least two GPUs")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
+                        "--master-addr", "127.0.0.1", "--master-port", "29641",
+                        os.path.join(ROOT, "tests", "dist_tp_engine_worker.py")], capture_output=True, text=True,
+                       timeout=600, cwd=ROOT)
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert "TP_ENGINE_OK" in r.stdout

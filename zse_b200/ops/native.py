@@ -69,6 +69,10 @@ _SIGS = {
                                           c_int, c_int, c_void_p, c_void_p]),
     "zse_tp_reduce_add_rmsnorm_emulated": (c_int, [c_void_p, POINTER(c_uint64), POINTER(c_uint64), c_int, c_void_p,
                                                    POINTER(c_uint64), c_int, c_float, c_int, c_void_p, c_void_p]),
+    "zse_tp_reduce_scatter_add_rmsnorm": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_float,
+                                          c_int, c_int, c_void_p, c_void_p]),
+    "zse_tp_reduce_scatter_add_rmsnorm_emulated": (c_int, [c_void_p, POINTER(c_uint64), POINTER(c_uint64), c_int, c_void_p,
+                                                   POINTER(c_uint64), c_int, c_float, c_int, c_void_p, c_void_p]),
     "zse_tp_argmax": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
     "zse_tp_argmax_emulated": (c_int, [c_void_p, POINTER(c_uint64), c_int, POINTER(c_uint64), c_int, c_int, c_int,
                                        c_int, c_void_p, c_void_p]),
@@ -282,6 +286,19 @@ def tp_reduce_add_rmsnorm_emulated(ctx, residuals, partials, n_planes, weight, o
                                                   _u64s([t.data_ptr() for t in partials]), n_planes, _p(weight),
                                                   _u64s([t.data_ptr() for t in outs]), M, eps, slot, status,
                                                   _stream()), "tp_reduce_add_rmsnorm_emulated")
+
+
+def tp_reduce_scatter_add_rmsnorm(ctx, residual, partials, n_planes, weight, out, M, eps, slot, use_multimem, status):
+    _ck(load().zse_tp_reduce_scatter_add_rmsnorm(ctx, _p(residual), _p(partials), n_planes, _p(weight), _p(out), M, eps,
+                                         slot, int(use_multimem), status, _stream()), "tp_reduce_scatter_add_rmsnorm",
+        (M + 511) // 512)
+
+
+def tp_reduce_scatter_add_rmsnorm_emulated(ctx, residuals, partials, n_planes, weight, outs, M, eps, slot, status):
+    _ck(load().zse_tp_reduce_scatter_add_rmsnorm_emulated(ctx, _u64s([t.data_ptr() for t in residuals]),
+                                                  _u64s([t.data_ptr() for t in partials]), n_planes, _p(weight),
+                                                  _u64s([t.data_ptr() for t in outs]), M, eps, slot, status,
+                                                  _stream()), "tp_reduce_scatter_add_rmsnorm_emulated")
 
 
 def tp_argmax(ctx, logits, ld, out, M, V_local, vocab_stride, slot, status):

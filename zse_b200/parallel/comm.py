@@ -32,9 +32,11 @@ class NcclComm:
 
     def all_reduce_partials(self, partials: torch.Tensor, planes: int, M: int) -> int:
         """Sums this rank's planes into plane 0 and all-reduces it; returns the number of planes left (1)."""
-        p0 = partials[0, :M]
+        H = partials.shape[-1]
+        pl = partials.view(-1)[: planes * M * H].view(planes, M, H)      # planes are packed: [plane][M rows][H]
+        p0 = pl[0]
         if planes > 1:
-            torch.sum(partials[:planes, :M], dim=0, out=p0)
+            p0.add_(pl[1:].sum(dim=0))
         dist.all_reduce(p0, group=self.group)
         return 1
 
@@ -115,6 +117,14 @@ class FusedComm(NcclComm):
                                          [p + offs[1] for p in ptrs], (mc + offs[0]) if mc else 0,
                                          [p + offs[2] for p in ptrs], [p + offs[3] for p in ptrs])
         self._calls = 0
+        # passes with at least this many rows (prefill) use the two-shot kernel: reduce-scatter by rows + all-gather,
+        # 2(tp-1)/tp rows over NVLink per rank and row instead of tp-1
+        self.two_shot_min_rows = int(os.environ.get("ZSE_TP_TWO_SHOT_ROWS", 1 << 30))
+        # Large passes (prefill) go through ncclAllReduce of the fp16 row sums by default: measured on B200 x2/x4, the
+        # per-row kernels above lose to NCCL once a pass has hundreds of rows (they are built for latency, one CTA per
+        # row), while for decode-sized passes they win by 1.2-1.4x.  ZSE_TP_NCCL_ROWS moves the switch-over point.
+        self.nccl_min_rows = int(os.environ.get("ZSE_TP_NCCL_ROWS", 256))
+        self._f16: Optional[torch.Tensor] = None
 
     def begin_pass(self) -> None:
         """Every pass makes an even number of reductions (two per layer), so restarting the slot sequence at 0 keeps
@@ -123,8 +133,20 @@ class FusedComm(NcclComm):
 
     # The decoder calls this instead of (all_reduce_partials + add_rmsnorm).
     def reduce_add_rmsnorm(self, ops, residual, partials, planes, weight, out, M, eps) -> None:
-        self._n.tp_reduce_add_rmsnorm(self._ctx, residual, partials, planes, weight, out, M, float(eps),
-                                      self._calls & 1, self.use_multimem, ops.status.ptr)
+        if M >= self.nccl_min_rows and M < self.two_shot_min_rows:
+            H = partials.shape[-1]
+            if self._f16 is None or self._f16.shape[0] < M:
+                self._f16 = torch.empty(max(M, self.m_cap), H, dtype=torch.float16, device=self.device)
+            pl = partials.view(-1)[: planes * M * H].view(planes, M, H)
+            tmp = self._f16[:M]
+            tmp.copy_(pl[0] if planes == 1 else pl.sum(dim=0))
+            dist.all_reduce(tmp, group=self.group)
+            ops.add_rmsnorm(residual, partials, 0, tmp, weight, out, M, eps)
+            return
+        fn = self._n.tp_reduce_scatter_add_rmsnorm if (M >= self.two_shot_min_rows and out is not None) \
+            else self._n.tp_reduce_add_rmsnorm
+        fn(self._ctx, residual, partials, planes, weight, out, M, float(eps), self._calls & 1, self.use_multimem,
+           ops.status.ptr)
         self._calls += 1
 
     def select_tokens(self, runner, n_rows: int, greedy: bool, step: int) -> None:
