@@ -31,6 +31,12 @@ struct GemmArgs {
 // bounds; cached per (pointer, shape, box).  Defined in gemm.cu.
 int get_tmap(const void* ptr, uint64_t rows, uint64_t cols, uint32_t box_rows, CUtensorMap* out);
 
+// CUDA-core path for one or two tokens (gemv_w4.cu).  gemv_w4_plan returns the number of K splits (fp32 planes) the
+// GEMV would use, or 0 when the tensor-core kernel should run instead.
+int gemv_w4_plan(int M, int N, int K, int epilogue, int sm_count, int want_split);
+int gemv_w4_launch(const void* w_tiled, const void* x, const void* bias, void* out, int M, int N, int K, int ldo,
+                   int epilogue, int ks, cudaStream_t st);
+
 inline int pick_nt(int M) {
   if (M <= 16) return 16;
   if (M <= 32) return 32;

@@ -640,7 +640,8 @@ static int launch_w4_epi(int epilogue, const CUtensorMap& tx, const W4Args& a, d
   return ZSE_ERR_SHAPE;
 }
 
-// 0 = the planner decides, 1 = wide CTAs only, 2 = narrow (two per SM) CTAs wherever they are allowed
+// 0 = the planner decides, 1 = wide CTAs only, 2 = narrow (two per SM) CTAs wherever they are allowed;
+// adding 4 keeps one- and two-token calls on the tensor cores instead of the CUDA-core GEMV
 static int g_w4_mode = 0;
 
 // How the launcher tiles a problem: weight tiles per CTA (R) and K splits (ks).  Measured on B200: a tcgen05.mma of
@@ -662,8 +663,8 @@ static void plan_w4(int M, int N, int K, int epilogue, int sm_count, int want_sp
   double best_cost = -1.0;
   int best_r = 1, best_ks = 1, best_dual = 0;
   for (int dual = 0; dual <= 1; ++dual) {
-    if (dual && (nt > 64 || g_w4_mode == 1)) continue;
-    if (!dual && g_w4_mode == 2 && nt <= 64) continue;
+    if (dual && (nt > 64 || (g_w4_mode & 3) == 1)) continue;
+    if (!dual && (g_w4_mode & 3) == 2 && nt <= 64) continue;
     for (int R = 1; R <= (dual ? 1 : 2); ++R) {
       if (n_tiles % R != 0) continue;
       if (R == 2 && nt > 128) continue;                         // accumulators + A ring must fit 512 TMEM columns
@@ -732,6 +733,11 @@ extern "C" int zse_gemm_w4(const void* w_tiled, const void* x, int x_rows_cap, c
     cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
     if (sm_count <= 0) sm_count = 148;
   }
+  if (!(g_w4_mode & 4)) {
+    const int gks = gemv_w4_plan(M, N, K, epilogue, sm_count, k_split);
+    if (gks > 0)
+      return gemv_w4_launch(w_tiled, x, bias, out, M, N, K, ldo, epilogue, gks, reinterpret_cast<cudaStream_t>(stream));
+  }
   const int k_stages = K / kW4StageK;
   int R = 1, ks = 1, cluster = 1, dual = 0;
   plan_w4(M, N, K, epilogue, sm_count, k_split, &R, &ks, &cluster, &dual);
@@ -773,6 +779,10 @@ extern "C" int zse_gemm_w4_splits(int M, int N, int K, int k_split) {
   int sm_count = 148, dev = 0;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
   if (sm_count <= 0) sm_count = 148;
+  if (!(g_w4_mode & 4)) {
+    const int gks = gemv_w4_plan(M, N, K, kEpiPartialF32, sm_count, k_split);
+    if (gks > 0) return gks;
+  }
   int R = 1, ks = 1, cluster = 1, dual = 0;
   plan_w4(M, N, K, kEpiPartialF32, sm_count, k_split, &R, &ks, &cluster, &dual);
   const int k_stages = K / kW4StageK;

@@ -179,6 +179,50 @@ def test_gemm_w4_wide_and_narrow_ctas_agree(ops, mode, M, N, K, epi):
         native.gemm_w4_set_mode(0)
 
 
+@pytest.mark.parametrize("M,N,K,epi", [(1, 9472, 3584, "swiglu"), (2, 9472, 1024, "swiglu"), (2, 12288, 1024, "f16"),
+                                       (1, 3584, 18944, "partial"), (2, 5120, 5120, "partial"),
+                                       (1, 152064 // 8, 512, "f16")])
+def test_gemv_w4_one_and_two_tokens(ops, M, N, K, epi):
+    """CUDA-core GEMV path (taken for one or two tokens) against the oracle and against the tensor-core kernel."""
+    from zse_b200.ops import native
+    x = (torch.randn(M, K, device="cuda") * 0.5).half()
+
+    def run():
+        if epi == "swiglu":
+            out = torch.zeros(M, N, dtype=torch.float16, device="cuda")
+            ops.linear_swiglu(w, x, M, out)
+            return out
+        if epi == "f16":
+            out = torch.zeros(M, N, dtype=torch.float16, device="cuda")
+            ops.linear(w, x, M, out)
+            return out
+        planes = torch.zeros(8, M, N, dtype=torch.float32, device="cuda")
+        n_pl = ops.linear_partial(w, x, M, planes)
+        return planes.view(-1)[: n_pl * M * N].view(n_pl, M, N).sum(0)
+
+    if epi == "swiglu":
+        g, gd = _w4_parts_gpu(N, K, 21)
+        u, ud = _w4_parts_gpu(N, K, 22)
+        w = ops.make_linear([g, u], K, 128, swiglu=True)
+        want = ref.swiglu(x.float() @ gd.T, x.float() @ ud.T)
+    else:
+        p, wd = _w4_parts_gpu(N, K, 23)
+        bias = (torch.randn(N, device="cuda") * 0.1).half() if epi == "f16" else None
+        w = ops.make_linear([p], K, 128, bias)
+        want = ref.linear(x, wd, bias) if epi == "f16" else x.float() @ wd.T
+    got = run()
+    torch.cuda.synchronize()
+    ops.check()
+    assert _rel(got, want) < 3e-3, _rel(got, want)
+    native.gemm_w4_set_mode(4)                  # same call on the tensor cores
+    try:
+        tc = run()
+        torch.cuda.synchronize()
+    finally:
+        native.gemm_w4_set_mode(0)
+    assert _rel(got, tc) < 3e-3
+
+
 @pytest.mark.parametrize("ks", [2, 3, 4])
 def test_gemm_w4_cluster_split_with_fused_epilogues(ops, ks):
     """Explicit K split on an epilogue that needs the whole sum: the CTAs of a cluster add their accumulators through
