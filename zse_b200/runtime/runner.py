@@ -181,7 +181,8 @@ class ModelRunner:
             self._upload(dst, src, n)
         self._stage_adapters(per_tok_adapter, total, total)
         greedy = self._stage_sampling(sampling or [GREEDY] * n_rows, n_rows) if select else True
-        self.model.forward(b, cache.slab, total, "prefill", S, max_q, n_rows)
+        with self._nvtx(f"prefill[{total} tokens, {S} seqs]"):
+            self.model.forward(b, cache.slab, total, "prefill", S, max_q, n_rows)
         self.timings["prefill_passes"] += 1
         self._step += 1
         for sid, toks, start in items:
@@ -198,8 +199,9 @@ class ModelRunner:
             return 1
         ctas = S * self.model.plan.num_kv_heads
         want = (2 * self._sm + ctas - 1) // ctas
-        by_len = max(1, max_len // 256)
-        return int(max(1, min(want, by_len, self.max_attn_splits)))
+        by_len = max(1, max_len // 128)              # at least 128 cached tokens per split
+        n = int(max(1, min(want, by_len, self.max_attn_splits)))
+        return 1 << (n.bit_length() - 1)              # powers of two: few distinct CUDA graphs as sequences grow
 
     def _apply_penalties(self, penalties, n_rows: int) -> None:
         """``penalties[i] = (penalty, {token: count})`` for logits row i (zse-engine/zse_engine/orchestrator/
@@ -267,7 +269,8 @@ class ModelRunner:
             ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
             ev[0].record()
         if g is not None:
-            g.replay()
+            with self._nvtx(f"decode graph[{Sp} seqs]"):
+                g.replay()
             self.timings["graph_replays"] += 1
             self.kernel_launches += self._graph_launches[key]
         else:
@@ -309,6 +312,15 @@ class ModelRunner:
         this has to happen before the process group is destroyed."""
         self._graphs.clear()
         self._graph_launches.clear()
+
+    @staticmethod
+    def _nvtx(name: str):
+        """NVTX range around a phase when ZSE_NVTX=1 (timeline tools), else a no-op context."""
+        import contextlib
+        import os as _os
+        if _os.environ.get("ZSE_NVTX") == "1" and torch.cuda.is_available():
+            return torch.cuda.nvtx.range(name)
+        return contextlib.nullcontext()
 
     def _launch_counter(self):
         if self.device.type == "cuda":
