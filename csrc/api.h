@@ -104,6 +104,21 @@ int zse_tp_reduce_scatter_add_rmsnorm(void* ctx, void* residual, const void* par
 int zse_tp_reduce_scatter_add_rmsnorm_emulated(void* ctx, const uint64_t* residuals, const uint64_t* partials,
                                                int n_planes, const void* weight, const uint64_t* outs, int M,
                                                float eps, int slot, void* status, void* stream);
+// Push exchange: the row-parallel INT4 GEMM sends its fp16 partial rows to every rank's inbox from its own epilogue
+// (multimem.st through NVSwitch or one store per peer) and counts its CTAs in; the consumer waits for the counters,
+// adds the tp rows of its own inbox in rank order, adds the residual and applies RMSNorm.
+//   inbox_ptrs[r]  : rank r's inbox [2][tp][push_m_cap][H] fp16 as mapped into this process (symmetric memory)
+//   arrive_ptrs[r] : rank r's counters [2][tp] u32 (symmetric memory, zero at start)
+//   state_ptrs[r]  : 4 u32 of ordinary device memory of rank r (zero at start); only the own rank's is needed
+int zse_tp_ctx_set_push(void* ctx, int push_m_cap, const uint64_t* inbox_ptrs, uint64_t mc_inbox,
+                        const uint64_t* arrive_ptrs, uint64_t mc_arrive, const uint64_t* state_ptrs);
+// returns the number of CTAs launched (what the consumer waits for from every rank) or a negative error
+int zse_tp_gemm_w4_push(void* ctx, const void* w_tiled, const void* x, int x_rows_cap, int M, int N, int K, int slot,
+                        int use_multimem, int rank_override, void* status, void* stream);
+int zse_tp_sum_add_rmsnorm(void* ctx, void* residual, const void* weight, void* out, int M, float eps, int slot,
+                           int expected_add, void* status, void* stream);
+int zse_tp_sum_add_rmsnorm_emulated(void* ctx, const uint64_t* residuals, const void* weight, const uint64_t* outs,
+                                    int M, float eps, int slot, int expected_add, void* status, void* stream);
 int zse_tp_argmax(void* ctx, const void* logits, int ld, void* out, int M, int V_local, int vocab_stride,
                   int slot, void* status, void* stream);
 int zse_tp_argmax_emulated(void* ctx, const uint64_t* logits, int ld, const uint64_t* outs, int M, int V_local,

@@ -27,6 +27,7 @@
 
 #include "api.h"
 #include "common.cuh"
+#include "gemm_common.cuh"
 
 namespace zse {
 
@@ -353,6 +354,120 @@ tp_reduce_scatter_add_rmsnorm_kernel(const TpTable tb, const TpReduceArgs a) {
   }
 }
 
+// ---- consumer of the push exchange: the GEMM (gemm_w4.cu, kEpiPushF16) of every rank has written its fp16 partial
+// rows into slot `src` of this rank's inbox and counted its CTAs into arrive[slot][src].  This kernel waits until
+// every source has delivered `expected_add` more CTAs than before, adds the tp rows in rank order (the same order on
+// every rank, so the replicated residual stays bit-identical), adds the residual and normalises.  Nothing is read
+// from a peer here: the NVLink transfers happened while the GEMMs were still running.
+// The running total the counters must reach lives in device memory (state[slot]) and is advanced by the last CTA of
+// the launch, so a CUDA graph can replay the launch unchanged.
+struct TpSumArgs {
+  TpRankArgs r[kMaxTp];            // per emulated rank: residual, (unused), out, rank
+  const __half* inbox[kMaxTp];     // inbox[r]: rank r's own inbox [2][tp][m_cap][H]
+  const uint32_t* arrive[kMaxTp];  // arrive[r]: rank r's own counters [2][tp]
+  uint32_t* state[kMaxTp];         // state[r]: {expected slot 0, expected slot 1, ticket}
+  const __half* weight;
+  int tp, m_cap, M, H, slot;
+  uint32_t expected_add;
+  float eps;
+  Status* status;
+};
+
+__global__ void __launch_bounds__(kRedThreads)
+tp_sum_add_rmsnorm_kernel(const TpSumArgs a) {
+  __shared__ float red[32];
+  __shared__ int ok_flag;
+  pdl_launch_dependents();
+  pdl_wait();
+  const int er = blockIdx.y;
+  const TpRankArgs me = a.r[er];
+  const int rank = me.rank, tp = a.tp, row = blockIdx.x;
+  const int H = a.H, nch = H / 8;
+  if (threadIdx.x == 0) ok_flag = 1;
+  __syncthreads();
+  if (threadIdx.x < tp) {
+    const uint32_t target = a.state[rank][a.slot] + a.expected_add;
+    const uint32_t* ctr = a.arrive[rank] + a.slot * tp + threadIdx.x;
+    if (int32_t(ld_acquire_sys(ctr) - target) < 0) {
+      const uint64_t t0 = globaltimer_ns();
+      unsigned spins = 0;
+      while (int32_t(ld_acquire_sys(ctr) - target) < 0) {
+        if ((++spins & 0x3F) == 0 && globaltimer_ns() - t0 > kWaitLimitNs) {
+          report(a.status, kPeerTimeout, 34, threadIdx.x);
+          ok_flag = 0;
+          break;
+        }
+      }
+    }
+  }
+  __syncthreads();
+  const bool ok = ok_flag != 0;
+  const __half* box = a.inbox[rank] + size_t(a.slot) * tp * a.m_cap * H + size_t(row) * H;
+  float vals[kRedMaxChunks][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int j = 0; j < kRedMaxChunks; ++j) {
+    const int c = threadIdx.x + j * kRedThreads;
+    if (c < nch) {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      if (ok) {
+        uint4 got[kMaxTp];
+#pragma unroll
+        for (int r = 0; r < kMaxTp; ++r)
+          if (r < tp) got[r] = ld_relaxed_sys_v4(box + size_t(r) * a.m_cap * H + size_t(c) * 8);
+#pragma unroll
+        for (int r = 0; r < kMaxTp; ++r)
+          if (r < tp) acc_h8(acc, got[r]);
+      }
+      float4* res = reinterpret_cast<float4*>(me.residual + size_t(row) * H) + 2 * c;
+      float4 x = res[0], y = res[1];
+      x.x += acc[0]; x.y += acc[1]; x.z += acc[2]; x.w += acc[3];
+      y.x += acc[4]; y.y += acc[5]; y.z += acc[6]; y.w += acc[7];
+      res[0] = x;
+      res[1] = y;
+      vals[j][0] = x.x; vals[j][1] = x.y; vals[j][2] = x.z; vals[j][3] = x.w;
+      vals[j][4] = y.x; vals[j][5] = y.y; vals[j][6] = y.z; vals[j][7] = y.w;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) ss += vals[j][i] * vals[j][i];
+    }
+  }
+  if (me.out != nullptr) {
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = (threadIdx.x & 31) < (kRedThreads >> 5) ? red[threadIdx.x & 31] : 0.f;
+    tot = warp_sum(tot);
+    const float inv = rsqrtf(tot / float(H) + a.eps);
+#pragma unroll
+    for (int j = 0; j < kRedMaxChunks; ++j) {
+      const int c = threadIdx.x + j * kRedThreads;
+      if (c < nch) {
+        const uint4 wr = reinterpret_cast<const uint4*>(a.weight)[c];
+        const __half2* wh = reinterpret_cast<const __half2*>(&wr);
+        uint4 pk;
+        uint32_t* po = reinterpret_cast<uint32_t*>(&pk);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 w = __half22float2(wh[i]);
+          po[i] = pack_half2(vals[j][2 * i] * inv * w.x, vals[j][2 * i + 1] * inv * w.y);
+        }
+        reinterpret_cast<uint4*>(me.out + size_t(row) * H)[c] = pk;
+      }
+    }
+  }
+  // the last CTA of this rank's launch moves the running total on (every CTA has read it by then)
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const uint32_t t = atomicAdd(a.state[rank] + 2, 1u);
+    if (t == gridDim.x - 1) {
+      a.state[rank][a.slot] += a.expected_add;
+      a.state[rank][2] = 0u;
+      __threadfence();
+    }
+  }
+}
+
 // ---- greedy selection over a vocabulary-sharded lm_head --------------------------------------------------
 struct TpArgmaxArgs {
   const __half* logits[kMaxTp];   // per emulated rank: [M, ld] local logits
@@ -436,6 +551,13 @@ struct zse_tp_ctx {
   uint32_t* xflags[kMaxTp];
   int rank;
   int H;
+  // push exchange (GEMM epilogue -> inboxes): set by zse_tp_ctx_set_push
+  __half* inbox[kMaxTp] = {};
+  uint32_t* arrive[kMaxTp] = {};
+  uint32_t* state[kMaxTp] = {};      // state[r]: rank r's local words {expected slot 0, expected slot 1, ticket, -}
+  __half* mc_inbox = nullptr;
+  uint32_t* mc_arrive = nullptr;
+  int push_m_cap = 0;                // rows per source in the inbox
 };
 
 extern "C" void* zse_tp_ctx_create(int tp, int rank, int m_cap, int H, const uint64_t* data_ptrs,
@@ -458,6 +580,41 @@ extern "C" void* zse_tp_ctx_create(int tp, int rank, int m_cap, int H, const uin
 }
 
 extern "C" void zse_tp_ctx_destroy(void* ctx) { delete reinterpret_cast<zse_tp_ctx*>(ctx); }
+
+extern "C" int zse_tp_ctx_set_push(void* ctx, int push_m_cap, const uint64_t* inbox_ptrs, uint64_t mc_inbox,
+                                   const uint64_t* arrive_ptrs, uint64_t mc_arrive, const uint64_t* state_ptrs) {
+  zse_tp_ctx* c = reinterpret_cast<zse_tp_ctx*>(ctx);
+  if (c == nullptr || push_m_cap <= 0) return ZSE_ERR_SHAPE;
+  c->push_m_cap = push_m_cap;
+  for (int r = 0; r < c->table.tp; ++r) {
+    c->inbox[r] = reinterpret_cast<__half*>(inbox_ptrs[r]);
+    c->arrive[r] = reinterpret_cast<uint32_t*>(arrive_ptrs[r]);
+    c->state[r] = reinterpret_cast<uint32_t*>(state_ptrs[r]);
+  }
+  c->mc_inbox = reinterpret_cast<__half*>(mc_inbox);
+  c->mc_arrive = reinterpret_cast<uint32_t*>(mc_arrive);
+  return 0;
+}
+
+namespace zse {
+int tp_fill_push_table(const void* ctx, int slot, bool multimem, int rank_override, PushTable* out) {
+  const zse_tp_ctx* c = reinterpret_cast<const zse_tp_ctx*>(ctx);
+  if (c == nullptr || c->inbox[0] == nullptr) return ZSE_ERR_SHAPE;
+  if (multimem && (c->mc_inbox == nullptr || c->mc_arrive == nullptr)) return ZSE_ERR_SHAPE;
+  for (int r = 0; r < kPushMaxTp; ++r) {
+    out->inbox[r] = r < c->table.tp ? c->inbox[r] : nullptr;
+    out->arrive[r] = r < c->table.tp ? c->arrive[r] : nullptr;
+  }
+  out->mc_inbox = multimem ? c->mc_inbox : nullptr;
+  out->mc_arrive = multimem ? c->mc_arrive : nullptr;
+  out->tp = c->table.tp;
+  out->rank = rank_override >= 0 ? rank_override : c->rank;
+  out->m_cap = c->push_m_cap;
+  out->H = c->H;
+  out->slot = slot & 1;
+  return 0;
+}
+}  // namespace zse
 
 // Programmatic dependent launch for the reduce kernels: off unless ZSE_TP_PDL=1.  Measured on 2 GPUs: a reduce kernel
 // that starts early spins on its peers' flags while the GEMM before it still runs and slows the whole step
@@ -602,6 +759,59 @@ extern "C" int zse_tp_reduce_add_rmsnorm_emulated(void* ctx, const uint64_t* res
   a.row0 = 0;
   a.status = reinterpret_cast<Status*>(status);
   return launch_reduce(c, a, M, c->table.tp, false, reinterpret_cast<cudaStream_t>(stream));
+}
+
+static int fill_sum_args(const zse_tp_ctx* c, TpSumArgs& a, const void* weight, int M, float eps, int slot,
+                         int expected_add, void* status) {
+  if (c == nullptr || c->inbox[0] == nullptr || M <= 0 || M > c->push_m_cap || c->H % 8 ||
+      c->H > 8 * kRedThreads * kRedMaxChunks || expected_add <= 0)
+    return ZSE_ERR_SHAPE;
+  for (int r = 0; r < c->table.tp; ++r) {
+    a.inbox[r] = c->inbox[r];
+    a.arrive[r] = c->arrive[r];
+    a.state[r] = c->state[r];
+  }
+  a.weight = reinterpret_cast<const __half*>(weight);
+  a.tp = c->table.tp;
+  a.m_cap = c->push_m_cap;
+  a.M = M;
+  a.H = c->H;
+  a.slot = slot & 1;
+  a.expected_add = uint32_t(expected_add);
+  a.eps = eps;
+  a.status = reinterpret_cast<Status*>(status);
+  return 0;
+}
+
+// Consumer of the push exchange (see tp_sum_add_rmsnorm_kernel).  `expected_add`: what zse_tp_gemm_w4_push returned
+// for the GEMM of this call (its CTA count, the same on every rank).
+extern "C" int zse_tp_sum_add_rmsnorm(void* ctx, void* residual, const void* weight, void* out, int M, float eps,
+                                      int slot, int expected_add, void* status, void* stream) {
+  zse_tp_ctx* c = reinterpret_cast<zse_tp_ctx*>(ctx);
+  TpSumArgs a{};
+  if (int rc = fill_sum_args(c, a, weight, M, eps, slot, expected_add, status)) return rc;
+  if (c->state[c->rank] == nullptr) return ZSE_ERR_SHAPE;
+  a.r[0] = TpRankArgs{reinterpret_cast<float*>(residual), nullptr, reinterpret_cast<__half*>(out), c->rank};
+  return launch_pdl_if(tp_pdl_allowed(), tp_sum_add_rmsnorm_kernel, dim3(M, 1), dim3(kRedThreads), 0,
+                       reinterpret_cast<cudaStream_t>(stream), a) == cudaSuccess
+             ? 0
+             : ZSE_ERR_LAUNCH;
+}
+
+// All ranks of a single-GPU test in one launch (blockIdx.y = rank).  The producers have finished before it starts,
+// so nothing here waits for a kernel that is not running.
+extern "C" int zse_tp_sum_add_rmsnorm_emulated(void* ctx, const uint64_t* residuals, const void* weight,
+                                               const uint64_t* outs, int M, float eps, int slot, int expected_add,
+                                               void* status, void* stream) {
+  zse_tp_ctx* c = reinterpret_cast<zse_tp_ctx*>(ctx);
+  TpSumArgs a{};
+  if (int rc = fill_sum_args(c, a, weight, M, eps, slot, expected_add, status)) return rc;
+  for (int r = 0; r < c->table.tp; ++r) {
+    if (c->state[r] == nullptr) return ZSE_ERR_SHAPE;
+    a.r[r] = TpRankArgs{reinterpret_cast<float*>(residuals[r]), nullptr, reinterpret_cast<__half*>(outs[r]), r};
+  }
+  tp_sum_add_rmsnorm_kernel<<<dim3(M, c->table.tp), kRedThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(a);
+  return cudaGetLastError() == cudaSuccess ? 0 : ZSE_ERR_LAUNCH;
 }
 
 extern "C" int zse_tp_argmax(void* ctx, const void* logits, int ld, void* out, int M, int V_local, int vocab_stride,

@@ -12,7 +12,7 @@ constexpr int kW4StageK = 128;       // K per pipeline stage of the INT4 kernel 
 constexpr int kW4ChunkBytes = 8704;  // 8192 nibble bytes + 512 bytes of {scale, zero}
 constexpr int kGemmThreads = 320;    // fp16 kernel: warp 0 producer, warp 1 MMA issuer, warps 2..9 epilogue
 
-enum Epilogue : int { kEpiF16 = 0, kEpiSwiGLU = 1, kEpiPartialF32 = 2 };
+enum Epilogue : int { kEpiF16 = 0, kEpiSwiGLU = 1, kEpiPartialF32 = 2, kEpiPushF16 = 3 };
 
 struct GemmArgs {
   const uint8_t* w;        // W4: tiled chunks [n_tiles][k_stages][8704]; F16: unused (tensor map)
@@ -30,6 +30,21 @@ struct GemmArgs {
 // fp16 [rows, cols] row-major tensor map: box = 64 columns x box_rows rows, 128-byte swizzle, zero fill out of
 // bounds; cached per (pointer, shape, box).  Defined in gemm.cu.
 int get_tmap(const void* ptr, uint64_t rows, uint64_t cols, uint32_t box_rows, CUtensorMap* out);
+
+// Where a row-parallel GEMM sends its partial output tiles when the tensor-parallel exchange is part of the GEMM
+// (gemm_w4.cu, kEpiPushF16): rank r's tile goes, as fp16, into slot r of EVERY rank's inbox - one multimem.st through
+// the NVSwitch, or one store per peer - and each CTA then adds 1 to the counter `arrive[k][slot][r]` on every rank k.
+// The consumer (comm.cu, tp_sum_add_rmsnorm) waits for the counters and adds the tp rows from its own inbox.
+constexpr int kPushMaxTp = 8;
+struct PushTable {
+  __half* inbox[kPushMaxTp];       // inbox[k]: rank k's inbox [2 slots][tp sources][m_cap][H], as mapped here
+  uint32_t* arrive[kPushMaxTp];    // arrive[k]: rank k's counters [2 slots][tp sources]
+  __half* mc_inbox;                // multicast view of the inbox (null: plain peer stores)
+  uint32_t* mc_arrive;             // multicast view of the counters
+  int tp, rank, m_cap, H, slot;
+};
+// Fills `out` from a tensor-parallel context (comm.cu).  rank_override >= 0 plays another rank (single-GPU tests).
+int tp_fill_push_table(const void* ctx, int slot, bool multimem, int rank_override, PushTable* out);
 
 // CUDA-core path for one or two tokens (gemv_w4.cu).  gemv_w4_plan returns the number of K splits (fp32 planes) the
 // GEMV would use, or 0 when the tensor-core kernel should run instead.

@@ -89,7 +89,20 @@ struct W4Args {
   int cluster_k;           // CTAs per cluster along K (1: every K split writes its own fp32 plane)
   Status* status;
   long long* timing;       // debug builds (ZSE_W4_TIMING): per-role cycle counters, else unused
+  PushTable push;          // kEpiPushF16: where the partial tiles go (every rank's inbox over NVLink)
 };
+
+__device__ __forceinline__ void multimem_st_v4(void* mc_ptr, const uint4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f16x2 [%0], {%1,%2,%3,%4};" ::"l"(mc_ptr), "r"(v.x), "r"(v.y),
+               "r"(v.z), "r"(v.w)
+               : "memory");
+}
+__device__ __forceinline__ void multimem_red_add_release(uint32_t* mc_ptr, uint32_t v) {
+  asm volatile("multimem.red.release.sys.global.add.u32 [%0], %1;" ::"l"(mc_ptr), "r"(v) : "memory");
+}
+__device__ __forceinline__ void red_add_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 
 // Nibble order inside every 32-bit word of a chunk (fixed by repack_w4): positions 0..7 hold the K elements
 // e0,e2,e4,e6,e1,e3,e5,e7 so that masking with 0x000f000f yields the adjacent pair (e0,e1) as a half2.
@@ -575,6 +588,11 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4Args a) {
           }
           asm volatile("bar.sync %0, 64;" ::"r"(bar_id) : "memory");
         }
+      } else if (EPI == kEpiPushF16) {
+        // keep the finished sums in this CTA's park area, token-major, for the coalesced push below (the entries of
+        // the chunks a CTA owns are read by nobody else)
+#pragma unroll
+        for (int i = 0; i < 16; ++i) park[(ch * 16 + i) * 128 + row] = v[i];
       } else {
         const int n = n_tile * kTileN + row;
         float bias = 0.f;
@@ -589,6 +607,51 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4Args a) {
               reinterpret_cast<float*>(a.out)[(size_t(plane_z) * a.M + t) * a.ldo + n] = v[i];
           }
         }
+      }
+    }
+  }
+  if (EPI == kEpiPushF16 && dq_role && acc_ok) {
+    // ---- tensor-parallel exchange inside the GEMM: this rank's fp16 partial rows go to slot `rank` of every rank's
+    // inbox (one multimem.st through the switch, or one store per peer), 16 bytes per thread, 256 contiguous bytes
+    // per token and tile; then the CTA counts itself in on every rank.  Nothing here waits for a peer.
+    constexpr int kDqThreads = kDqWarps * 32;
+    asm volatile("bar.sync 15, %0;" ::"n"(kDqThreads) : "memory");
+    const PushTable& pt = a.push;
+    const int d = (warp - 2) * 32 + lane;
+    const int t0 = blockIdx.y * NT;
+    const int owned = int(crank) < kChunks ? (kChunks - int(crank) + ks - 1) / ks : 0;
+    for (int item = d; item < owned * 256; item += kDqThreads) {
+      const int ch = int(crank) + (item >> 8) * ks;
+      const int tok = (item & 255) >> 4, seg = item & 15;
+      const int r = ch / (NT / 16), c0 = (ch % (NT / 16)) * 16;
+      const int t = t0 + c0 + tok;
+      const int n = (tile0 + r) * kTileN + seg * 8;
+      if (t < a.M && n < a.N) {
+        const float4* src = reinterpret_cast<const float4*>(park + (ch * 16 + tok) * 128 + seg * 8);
+        const float4 lo = src[0], hi = src[1];
+        uint4 pk;
+        pk.x = pack_half2(lo.x, lo.y);
+        pk.y = pack_half2(lo.z, lo.w);
+        pk.z = pack_half2(hi.x, hi.y);
+        pk.w = pack_half2(hi.z, hi.w);
+        const size_t off = ((size_t(pt.slot) * pt.tp + pt.rank) * pt.m_cap + t) * pt.H + n;
+        if (pt.mc_inbox != nullptr) {
+          multimem_st_v4(pt.mc_inbox + off, pk);
+        } else {
+#pragma unroll
+          for (int k = 0; k < kPushMaxTp; ++k)
+            if (k < pt.tp) *reinterpret_cast<uint4*>(pt.inbox[k] + off) = pk;
+        }
+      }
+    }
+    asm volatile("bar.sync 15, %0;" ::"n"(kDqThreads) : "memory");
+    if (d == 0) {
+      __threadfence_system();
+      const int ctr = pt.slot * pt.tp + pt.rank;
+      if (pt.mc_arrive != nullptr) {
+        multimem_red_add_release(pt.mc_arrive + ctr, 1u);
+      } else {
+        for (int k = 0; k < pt.tp; ++k) red_add_release_sys(pt.arrive[k] + ctr, 1u);
       }
     }
   }
@@ -637,6 +700,7 @@ static int launch_w4_epi(int epilogue, const CUtensorMap& tx, const W4Args& a, d
   if (epilogue == kEpiF16) return launch_w4<NT, R, kEpiF16, DUAL>(tx, a, grid, st);
   if (epilogue == kEpiSwiGLU) return launch_w4<NT, R, kEpiSwiGLU, DUAL>(tx, a, grid, st);
   if (epilogue == kEpiPartialF32) return launch_w4<NT, R, kEpiPartialF32, DUAL>(tx, a, grid, st);
+  if (epilogue == kEpiPushF16) return launch_w4<NT, R, kEpiPushF16, DUAL>(tx, a, grid, st);
   return ZSE_ERR_SHAPE;
 }
 
@@ -722,8 +786,9 @@ extern "C" void zse_gemm_w4_set_timing(void* dev_buffer) { g_w4_timing = reinter
 // Tuning hook: 0 = planner decides between wide and narrow CTAs, 1 = wide only, 2 = narrow wherever allowed.
 extern "C" void zse_gemm_w4_set_mode(int mode) { zse::g_w4_mode = mode; }
 
-extern "C" int zse_gemm_w4(const void* w_tiled, const void* x, int x_rows_cap, const void* bias, void* out, int M,
-                           int N, int K, int ldo, int epilogue, int k_split, void* status, void* stream) {
+static int run_gemm_w4(const void* w_tiled, const void* x, int x_rows_cap, const void* bias, void* out, int M, int N,
+                       int K, int ldo, int epilogue, int k_split, void* status, void* stream, const PushTable* push,
+                       int* ctas_out) {
   if (M <= 0) return 0;
   if (K % kW4StageK != 0 || N <= 0 || K <= 0) return ZSE_ERR_SHAPE;
   static int sm_count = 0;
@@ -733,7 +798,7 @@ extern "C" int zse_gemm_w4(const void* w_tiled, const void* x, int x_rows_cap, c
     cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
     if (sm_count <= 0) sm_count = 148;
   }
-  if (!(g_w4_mode & 4)) {
+  if (!(g_w4_mode & 4) && push == nullptr) {
     const int gks = gemv_w4_plan(M, N, K, epilogue, sm_count, k_split);
     if (gks > 0)
       return gemv_w4_launch(w_tiled, x, bias, out, M, N, K, ldo, epilogue, gks, reinterpret_cast<cudaStream_t>(stream));
@@ -749,8 +814,10 @@ extern "C" int zse_gemm_w4(const void* w_tiled, const void* x, int x_rows_cap, c
   CUtensorMap tx;
   if (int rc = get_tmap(x, uint64_t(max(x_rows_cap, M)), uint64_t(K), uint32_t(nt), &tx)) return rc;
   W4Args a{reinterpret_cast<const uint8_t*>(w_tiled), reinterpret_cast<const __half*>(bias), out, M, N, K, ldo,
-           k_stages, spp, cluster, reinterpret_cast<Status*>(status), g_w4_timing};
+           k_stages, spp, cluster, reinterpret_cast<Status*>(status), g_w4_timing, PushTable{}};
+  if (push != nullptr) a.push = *push;
   dim3 grid(n_tiles / R, (M + nt - 1) / nt, ks);
+  if (ctas_out != nullptr) *ctas_out = int(grid.x * grid.y * grid.z);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   int rc = ZSE_ERR_SHAPE;
   if (dual) {
@@ -770,6 +837,28 @@ extern "C" int zse_gemm_w4(const void* w_tiled, const void* x, int x_rows_cap, c
     }
   }
   return rc;
+}
+
+extern "C" int zse_gemm_w4(const void* w_tiled, const void* x, int x_rows_cap, const void* bias, void* out, int M,
+                           int N, int K, int ldo, int epilogue, int k_split, void* status, void* stream) {
+  if (epilogue == kEpiPushF16) return ZSE_ERR_SHAPE;          // needs a tensor-parallel context: zse_tp_gemm_w4_push
+  return run_gemm_w4(w_tiled, x, x_rows_cap, bias, out, M, N, K, ldo, epilogue, k_split, status, stream, nullptr,
+                     nullptr);
+}
+
+// Row-parallel projection whose epilogue is the tensor-parallel exchange: every CTA sends its fp16 partial rows to
+// every rank's inbox and counts itself in (see PushTable).  Returns the number of CTAs launched - the amount the
+// consumer (zse_tp_sum_add_rmsnorm) must wait for from every rank - or a negative error.  N must equal the hidden
+// size of the context and M must fit its row capacity.  rank_override >= 0 plays another rank (single-GPU tests).
+extern "C" int zse_tp_gemm_w4_push(void* ctx, const void* w_tiled, const void* x, int x_rows_cap, int M, int N, int K,
+                                   int slot, int use_multimem, int rank_override, void* status, void* stream) {
+  PushTable pt;
+  if (int rc = tp_fill_push_table(ctx, slot, use_multimem != 0, rank_override, &pt)) return rc;
+  if (N != pt.H || M > pt.m_cap || N % 8) return ZSE_ERR_SHAPE;
+  int ctas = 0;
+  const int rc = run_gemm_w4(w_tiled, x, x_rows_cap, nullptr, nullptr, M, N, K, N, kEpiPushF16, 0, status, stream, &pt,
+                             &ctas);
+  return rc != 0 ? rc : ctas;
 }
 
 // Number of fp32 planes zse_gemm_w4 writes for an fp32-epilogue call with these arguments (the caller sizes the plane

@@ -29,13 +29,15 @@ def main():
     vocab = synth.shape_config("small-128").vocab_size
     prompts = [[rng.randrange(vocab) for _ in range(n)] for n in (300, 17, 150, 64)]
     results = {}
-    for backend in ("single", "fused", "nccl"):
+    for backend in ("single", "fused", "push", "nccl"):
         tp = 1 if backend == "single" else world
+        os.environ["ZSE_TP_PUSH"] = "1" if backend == "push" else "0"   # exchange inside the row-parallel GEMM
         cfg = EngineConfig(tp_size=tp, device_index=local, max_seq_len=512, max_batch_seqs=8, max_batch_tokens=1024,
-                           prefill_chunk_size=512, comm_backend=backend if tp > 1 else "fused", quiet=True)
+                           prefill_chunk_size=512, quiet=True,
+                           comm_backend={"single": "fused", "push": "fused"}.get(backend, backend))
         comm = None
         if tp > 1:
-            comm = make_comm(backend, rank, world, dev, hidden_size=synth.SHAPES["small-128"]["hidden_size"],
+            comm = make_comm(cfg.comm_backend, rank, world, dev, hidden_size=synth.SHAPES["small-128"]["hidden_size"],
                              max_tokens=cfg.max_batch_tokens)
         eng = ZStreamerEngine(path, config=cfg, comm=comm, tp_rank=rank if tp > 1 else 0)
         ids = [eng.add_request_tokens(p, max_tokens=12, temperature=0.0, stop_tokens=[]) for p in prompts]
@@ -46,14 +48,19 @@ def main():
         dist.barrier()
     same_fused = sum(a == b for a, b in zip(results["fused"], results["single"]))
     same_nccl = sum(a == b for a, b in zip(results["nccl"], results["single"]))
+    same_push = sum(a == b for a, b in zip(results["push"], results["single"]))
     # fp16 rounding differs between one GPU and a sharded sum, so a near tie may flip a token: demand that every
     # rank agrees with every other rank exactly, and that most sequences match the single-GPU run token by token
     gathered = [None] * world
     dist.all_gather_object(gathered, results["fused"])
     assert all(g == gathered[0] for g in gathered), "ranks disagree"
     assert same_fused >= len(prompts) - 1 and same_nccl >= len(prompts) - 1, (results, same_fused, same_nccl)
+    dist.all_gather_object(gathered, results["push"])
+    assert all(g == gathered[0] for g in gathered), "ranks disagree (push exchange)"
+    assert same_push >= len(prompts) - 1, (results, same_push)
     if rank == 0:
-        print(f"TP_ENGINE_OK fused {same_fused}/{len(prompts)} nccl {same_nccl}/{len(prompts)}")
+        print(f"TP_ENGINE_OK fused {same_fused}/{len(prompts)} push {same_push}/{len(prompts)} "
+              f"nccl {same_nccl}/{len(prompts)}")
     dist.barrier()
     dist.destroy_process_group()
 

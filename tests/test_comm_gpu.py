@@ -16,6 +16,12 @@ from zse_b200.ops import reference as ref
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
+@pytest.fixture(scope="module")
+def ops():
+    from zse_b200.ops.backend import CudaOps
+    return CudaOps("cuda")
+
+
 def _emulated_ctx(tp, m_cap, H):
     from zse_b200.ops import native
     dev = "cuda"
@@ -90,6 +96,58 @@ def test_reduce_scatter_add_rmsnorm_emulated_ranks(tp, M, H, planes):
     status.check()
     assert torch.allclose(residuals[tp - 1], res0 + sum(p.sum(0).half().float() for p in partials), atol=2e-3, rtol=1e-4)
     native.tp_ctx_destroy(ctx)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("tp,M,H,Kr", [(2, 5, 1024, 1024), (4, 64, 1024, 512), (8, 33, 5120, 640), (4, 64, 5120, 3456)])
+def test_gemm_push_exchange_emulated_ranks(ops, tp, M, H, Kr):
+    """The exchange inside the GEMM: every emulated rank runs its row-parallel INT4 GEMM, whose epilogue writes the fp16
+    partial rows into every rank's inbox and counts its CTAs in; the consumer then only adds local rows.  Producers
+    never wait, so running them one after the other on one GPU is a faithful test of the data path and counters."""
+    from zse_b200.ops import native
+    from test_kernels_gpu import _w4_parts_gpu
+    m_cap = 64
+    ctx, keep = _emulated_ctx(tp, m_cap, H)
+    inbox = [torch.zeros(2 * tp * m_cap * H, dtype=torch.float16, device="cuda") for _ in range(tp)]
+    arrive = [torch.zeros(2 * tp, dtype=torch.int32, device="cuda") for _ in range(tp)]
+    state = [torch.zeros(4, dtype=torch.int32, device="cuda") for _ in range(tp)]
+    native.tp_ctx_set_push(ctx, m_cap, [t.data_ptr() for t in inbox], 0, [t.data_ptr() for t in arrive], 0,
+                           [t.data_ptr() for t in state])
+    status = native.Status("cuda")
+    wn = (1 + 0.1 * torch.randn(H, device="cuda")).half()
+    res0 = torch.randn(M, H, device="cuda")
+    residuals = [res0.clone() for _ in range(tp)]
+    outs = [torch.zeros(M, H, dtype=torch.float16, device="cuda") for _ in range(tp)]
+    shards, xs, partial = [], [], []
+    for r in range(tp):
+        part, wd = _w4_parts_gpu(H, Kr, 40 + r)
+        shards.append(ops.make_linear([part], Kr, 128))
+        xs.append((torch.randn(M, Kr, device="cuda") * 0.5).half())
+        partial.append((xs[r].float() @ wd.T).half().float())     # what arrives: fp16 rows
+    want = res0.clone()
+    for call in range(3):
+        slot = call & 1
+        ctas = [native.tp_gemm_w4_push(ctx, shards[r].data, xs[r], M, M, H, Kr, slot, False, status.ptr,
+                                       rank_override=r) for r in range(tp)]
+        assert len(set(ctas)) == 1 and ctas[0] > 0
+        native.tp_sum_add_rmsnorm_emulated(ctx, residuals, wn, outs, M, 1e-6, slot, ctas[0], status.ptr)
+        torch.cuda.synchronize()
+        status.check()
+        want = want + sum(partial)
+        for r in range(tp):
+            assert _rel_close(residuals[r], want), (call, r)
+            assert torch.equal(residuals[r], residuals[0])
+            assert (outs[r].float() - ref.rmsnorm(want, wn, 1e-6).float()).abs().max() < 3e-2
+    # a consumer whose producers did not run gives up with a status instead of hanging
+    native.tp_sum_add_rmsnorm_emulated(ctx, residuals, wn, outs, M, 1e-6, 1, ctas[0], status.ptr)
+    torch.cuda.synchronize()
+    code, _, where, _ = status.read()
+    assert (code, where) == (3, 34)
+    native.tp_ctx_destroy(ctx)
+
+
+def _rel_close(a, b, tol=4e-3):
+    return float((a - b).abs().max()) <= tol * max(1.0, float(b.abs().max()))
 
 
 @pytest.mark.gpu

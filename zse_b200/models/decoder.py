@@ -239,13 +239,23 @@ class DecoderModel:
         """residual += (row-parallel output summed over split-K planes and, with tensor parallelism, over ranks);
         xnorm = RMSNorm(residual) * weight."""
         ops, eps = self.ops, self.config.rms_norm_eps
-        if self.comm is None or planes == 0:
+        if planes < 0:                 # the GEMM pushed its rows to every rank itself (-planes = its CTA count)
+            self.comm.sum_add_rmsnorm(ops, b.residual, weight, b.xnorm, M, eps, -planes)
+        elif self.comm is None or planes == 0:
             ops.add_rmsnorm(b.residual, b.partials, planes, None, weight, b.xnorm, M, eps)
         elif self.comm.fused_norm:
             self.comm.reduce_add_rmsnorm(ops, b.residual, b.partials, planes, weight, b.xnorm, M, eps)
         else:
             planes = self.comm.all_reduce_partials(b.partials, planes, M)
             ops.add_rmsnorm(b.residual, b.partials, planes, None, weight, b.xnorm, M, eps)
+
+    def _row_parallel(self, w: LinearWeight, x: torch.Tensor, M: int, b: StepBuffers) -> int:
+        """Row-parallel projection.  Returns the number of fp32 planes written to ``b.partials``, or - when the
+        tensor-parallel exchange ran inside the GEMM - minus the CTA count the consumer has to wait for."""
+        comm = self.comm
+        if comm is not None and getattr(comm, "push", False) and comm.can_push(w, M):
+            return -comm.linear_push(self.ops, w, x, M)
+        return self.ops.linear_partial(w, x, M, b.partials)
 
     def forward(self, b: StepBuffers, kv: torch.Tensor, M: int, mode: str, num_seqs: int, max_q_len: int = 1,
                 n_logit_rows: int = 0, attn_splits: int = 1) -> None:
@@ -275,10 +285,10 @@ class DecoderModel:
             else:
                 ops.attn_prefill(b.qkv, kv[li], b.block_tables, b.cu_q, b.q_pos0, b.attn_out, num_seqs, M, max_q_len,
                                  p.num_heads, p.num_kv_heads, c.head_dim, bs, self.scale)
-            planes = ops.linear_partial(L.o, b.attn_out, M, b.partials)
+            planes = self._row_parallel(L.o, b.attn_out, M, b)
             self._add_norm(b, planes, L.ln2, M)
             ops.linear_swiglu(L.gate_up, b.xnorm, M, b.act)
-            planes = ops.linear_partial(L.down, b.act, M, b.partials)
+            planes = self._row_parallel(L.down, b.act, M, b)
         self._add_norm(b, planes, self.norm, M)
         if n_logit_rows:
             torch.index_select(b.xnorm, 0, b.logit_rows[:n_logit_rows], out=b.xsel[:n_logit_rows])

@@ -73,6 +73,14 @@ _SIGS = {
                                           c_int, c_int, c_void_p, c_void_p]),
     "zse_tp_reduce_scatter_add_rmsnorm_emulated": (c_int, [c_void_p, POINTER(c_uint64), POINTER(c_uint64), c_int, c_void_p,
                                                    POINTER(c_uint64), c_int, c_float, c_int, c_void_p, c_void_p]),
+    "zse_tp_ctx_set_push": (c_int, [c_void_p, c_int, POINTER(c_uint64), c_uint64, POINTER(c_uint64), c_uint64,
+                                    POINTER(c_uint64)]),
+    "zse_tp_gemm_w4_push": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                    c_void_p, c_void_p]),
+    "zse_tp_sum_add_rmsnorm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_int, c_int, c_void_p,
+                                       c_void_p]),
+    "zse_tp_sum_add_rmsnorm_emulated": (c_int, [c_void_p, POINTER(c_uint64), c_void_p, POINTER(c_uint64), c_int,
+                                                c_float, c_int, c_int, c_void_p, c_void_p]),
     "zse_tp_argmax": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
     "zse_tp_argmax_emulated": (c_int, [c_void_p, POINTER(c_uint64), c_int, POINTER(c_uint64), c_int, c_int, c_int,
                                        c_int, c_void_p, c_void_p]),
@@ -299,6 +307,32 @@ def tp_reduce_scatter_add_rmsnorm_emulated(ctx, residuals, partials, n_planes, w
                                                   _u64s([t.data_ptr() for t in partials]), n_planes, _p(weight),
                                                   _u64s([t.data_ptr() for t in outs]), M, eps, slot, status,
                                                   _stream()), "tp_reduce_scatter_add_rmsnorm_emulated")
+
+
+def tp_ctx_set_push(ctx, push_m_cap, inbox_ptrs, mc_inbox, arrive_ptrs, mc_arrive, state_ptrs):
+    _ck(load().zse_tp_ctx_set_push(ctx, push_m_cap, _u64s(inbox_ptrs), int(mc_inbox), _u64s(arrive_ptrs), int(mc_arrive),
+                                   _u64s(state_ptrs)), "tp_ctx_set_push", 0)
+
+
+def tp_gemm_w4_push(ctx, w_tiled, x, x_rows_cap, M, N, K, slot, use_multimem, status, rank_override=-1) -> int:
+    """Row-parallel INT4 GEMM whose epilogue sends the partial rows to every rank.  Returns its CTA count."""
+    rc = load().zse_tp_gemm_w4_push(ctx, _p(w_tiled), _p(x), x_rows_cap, M, N, K, slot, int(use_multimem),
+                                    rank_override, status, _stream())
+    if rc < 0:
+        _ck(rc, "tp_gemm_w4_push")
+    LAUNCHES[0] += 1
+    return rc
+
+
+def tp_sum_add_rmsnorm(ctx, residual, weight, out, M, eps, slot, expected_add, status):
+    _ck(load().zse_tp_sum_add_rmsnorm(ctx, _p(residual), _p(weight), _p(out), M, eps, slot, expected_add, status,
+                                      _stream()), "tp_sum_add_rmsnorm")
+
+
+def tp_sum_add_rmsnorm_emulated(ctx, residuals, weight, outs, M, eps, slot, expected_add, status):
+    _ck(load().zse_tp_sum_add_rmsnorm_emulated(ctx, _u64s([t.data_ptr() for t in residuals]), _p(weight),
+                                               _u64s([t.data_ptr() for t in outs]), M, eps, slot, expected_add,
+                                               status, _stream()), "tp_sum_add_rmsnorm_emulated")
 
 
 def tp_argmax(ctx, logits, ld, out, M, V_local, vocab_stride, slot, status):

@@ -117,6 +117,13 @@ class FusedComm(NcclComm):
                                          [p + offs[1] for p in ptrs], (mc + offs[0]) if mc else 0,
                                          [p + offs[2] for p in ptrs], [p + offs[3] for p in ptrs])
         self._calls = 0
+        # Push exchange (ZSE_TP_PUSH=1): the row-parallel GEMM itself sends its fp16 rows to every rank's inbox
+        # (multimem.st through NVSwitch, or peer stores) and the consumer adds local rows only.
+        self.push = os.environ.get("ZSE_TP_PUSH", "0") == "1"
+        self.push_rows = min(256, max_tokens)
+        self._push_ready = False
+        if self.push:
+            self._init_push(symm, grp, world, rank, device, hidden_size, want_mm)
         # passes with at least this many rows (prefill) use the two-shot kernel: reduce-scatter by rows + all-gather,
         # 2(tp-1)/tp rows over NVLink per rank and row instead of tp-1
         self.two_shot_min_rows = int(os.environ.get("ZSE_TP_TWO_SHOT_ROWS", 1 << 30))
@@ -125,6 +132,43 @@ class FusedComm(NcclComm):
         # row), while for decode-sized passes they win by 1.2-1.4x.  ZSE_TP_NCCL_ROWS moves the switch-over point.
         self.nccl_min_rows = int(os.environ.get("ZSE_TP_NCCL_ROWS", 256))
         self._f16: Optional[torch.Tensor] = None
+
+    def _init_push(self, symm, grp, world, rank, device, H, want_mm) -> None:
+        align = lambda n: (n + 255) // 256 * 256
+        inbox_bytes = 2 * world * self.push_rows * H * 2
+        offs = [0, align(inbox_bytes)]
+        total = offs[1] + align(2 * world * 4)
+        self._pbuf = symm.empty(total, dtype=torch.uint8, device=device)
+        self._pbuf.zero_()
+        self._phdl = symm.rendezvous(self._pbuf, grp)
+        torch.cuda.synchronize(device)
+        dist.barrier(group=grp)
+        ptrs = [int(p) for p in self._phdl.buffer_ptrs]
+        mc = 0
+        if want_mm:
+            try:
+                mc = int(self._phdl.multicast_ptr or 0)
+            except Exception:
+                mc = 0
+        self.push_multimem = bool(mc)
+        self._pstate = torch.zeros(4, dtype=torch.int32, device=device)
+        state_ptrs = [self._pstate.data_ptr() if r == rank else 0 for r in range(world)]
+        self._n.tp_ctx_set_push(self._ctx, self.push_rows, [p + offs[0] for p in ptrs], (mc + offs[0]) if mc else 0,
+                                [p + offs[1] for p in ptrs], (mc + offs[1]) if mc else 0, state_ptrs)
+        self._push_ready = True
+
+    def can_push(self, w, M: int) -> bool:
+        return self._push_ready and w.kind == "w4t" and M <= self.push_rows and w.N == self.H and w.bias is None
+
+    def linear_push(self, ops, w, x, M: int) -> int:
+        """Row-parallel INT4 GEMM with the exchange in its epilogue; returns the CTA count for sum_add_rmsnorm."""
+        return self._n.tp_gemm_w4_push(self._ctx, w.data, x, x.shape[0], M, w.N, w.K, self._calls & 1,
+                                       self.push_multimem, ops.status.ptr)
+
+    def sum_add_rmsnorm(self, ops, residual, weight, out, M: int, eps: float, ctas: int) -> None:
+        self._n.tp_sum_add_rmsnorm(self._ctx, residual, weight, out, M, float(eps), self._calls & 1, ctas,
+                                   ops.status.ptr)
+        self._calls += 1
 
     def begin_pass(self) -> None:
         """Every pass makes an even number of reductions (two per layer), so restarting the slot sequence at 0 keeps
