@@ -100,8 +100,8 @@ __device__ __forceinline__ void multimem_st_v4(void* mc_ptr, const uint4& v) {
 __device__ __forceinline__ void multimem_red_add_release(uint32_t* mc_ptr, uint32_t v) {
   asm volatile("multimem.red.release.sys.global.add.u32 [%0], %1;" ::"l"(mc_ptr), "r"(v) : "memory");
 }
-__device__ __forceinline__ void red_add_release_sys(uint32_t* p, uint32_t v) {
-  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+__device__ __forceinline__ void red_add_relaxed_sys(uint32_t* p, uint32_t v) {
+  asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
 // Nibble order inside every 32-bit word of a chunk (fixed by repack_w4): positions 0..7 hold the K elements
@@ -651,7 +651,8 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4Args a) {
       if (pt.mc_arrive != nullptr) {
         multimem_red_add_release(pt.mc_arrive + ctr, 1u);
       } else {
-        for (int k = 0; k < pt.tp; ++k) red_add_release_sys(pt.arrive[k] + ctr, 1u);
+        // one system-scope fence (above) orders the CTA's stores before all of the counter updates
+        for (int k = 0; k < pt.tp; ++k) red_add_relaxed_sys(pt.arrive[k] + ctr, 1u);
       }
     }
   }
