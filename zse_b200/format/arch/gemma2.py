@@ -17,4 +17,8 @@ class Gemma2Adapter(ArchAdapter):
         c.attn_logit_softcapping = hf.get("attn_logit_softcapping")
         c.query_pre_attn_scalar = hf.get("query_pre_attn_scalar")
         c.embed_scale = True
+        # local (sliding-window) and global attention alternate, starting with a local layer
+        c.layer_types = hf.get("layer_types") or ["sliding_attention" if (i + 1) % 2 else "full_attention"
+                                                  for i in range(c.num_layers)]
+        c.sliding_window = hf.get("sliding_window", 4096)
         return c

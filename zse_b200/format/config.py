@@ -37,6 +37,19 @@ class QuantConfig:
 
 
 @dataclass
+class LayerSpec:
+    head_dim: int
+    num_kv_heads: int
+    rope_theta: float
+    rotary_dim: int          # leading pairs (i, i + head_dim/2), i < rotary_dim/2, rotate; the rest pass through
+    window: int              # 0 = full causal attention
+    k_is_v: bool             # no v_proj: V is the k_proj output before its norm
+    scale: float
+    softcap: float           # 0 = none
+    qk_norm: bool            # per-head RMSNorm of q and k (learned weight) and of v (no weight)
+
+
+@dataclass
 class ModelConfig:
     arch: str = "llama"
     num_layers: int = 32
@@ -116,6 +129,51 @@ class ModelConfig:
     @property
     def total_kv_cache_bytes_per_token(self) -> int:
         return self.kv_cache_bytes_per_token * self.num_layers
+
+    # ---- per-layer attention geometry (Gemma-family models mix layer kinds) -----------------------
+    @property
+    def is_gemma(self) -> bool:
+        return self.arch.startswith("gemma")
+
+    @property
+    def norm_weight_offset(self) -> float:
+        """Gemma-2 stores RMSNorm weights as ``w - 1`` (the norm multiplies by ``1 + w``); Gemma-4 and everything
+        else multiply by the stored weight (zse-engine/zse_engine/orchestrator/kernels.py:1475-1478)."""
+        return 1.0 if self.arch == "gemma2" else 0.0
+
+    def layer_kind(self, i: int) -> str:
+        if self.layer_types and i < len(self.layer_types):
+            return self.layer_types[i]
+        return "full_attention"
+
+    def layer_spec(self, i: int) -> "LayerSpec":
+        """Attention geometry of layer ``i`` (zse-engine/zse_engine/orchestrator/model_runner.py:132-152)."""
+        sliding = self.layer_kind(i) == "sliding_attention"
+        hd, nkv, theta, rot = self.head_dim, self.num_kv_heads, self.rope_theta, self.head_dim
+        shares = False
+        if self.arch == "gemma4" and not sliding:
+            hd = self.global_head_dim or self.head_dim
+            shares = bool(self.attention_k_eq_v)
+            nkv = (self.global_num_kv_heads or self.num_kv_heads) if shares else self.num_kv_heads
+            theta = self.global_rope_theta or self.rope_theta
+            rot = 2 * int((self.partial_rotary_factor or 1.0) * hd // 2)
+        if self.arch == "gemma4":
+            scale = 1.0                         # q/k norms carry the scaling
+        elif self.query_pre_attn_scalar:
+            scale = float(self.query_pre_attn_scalar) ** -0.5
+        else:
+            scale = float(hd) ** -0.5
+        window = int(self.sliding_window or 0) if (sliding or not self.layer_types) else 0
+        return LayerSpec(hd, nkv, float(theta), rot, window, shares, scale,
+                         float(self.attn_logit_softcapping or 0.0), self.arch == "gemma4")
+
+    def kv_pool_dims(self, num_kv_heads: Optional[int] = None):
+        """(kv_heads, head_dim) the KV pool is allocated with.  Models whose layers differ get rows of the widest
+        layer (``1 x max(kv_heads * head_dim)``); each layer lays its heads out inside that row."""
+        specs = {(s.num_kv_heads, s.head_dim) for s in (self.layer_spec(i) for i in range(self.num_layers))}
+        if len(specs) <= 1:
+            return (num_kv_heads or self.num_kv_heads), self.head_dim
+        return 1, max(n * d for n, d in specs)
 
     def linear_param_count(self) -> int:
         per_layer = (self.hidden_size * self.q_dim + 2 * self.hidden_size * self.kv_dim

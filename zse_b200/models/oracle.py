@@ -24,9 +24,12 @@ def load_fp32_weights(loader: ZSELoader) -> Dict[str, torch.Tensor]:
     return out
 
 
-def rope_cos_sin(positions: torch.Tensor, head_dim: int, theta: float):
+def rope_cos_sin(positions: torch.Tensor, head_dim: int, theta: float, rotary_dim: Optional[int] = None):
+    """cos/sin [T, head_dim/2]; pairs beyond ``rotary_dim/2`` get angle 0 (they pass through unrotated)."""
     half = head_dim // 2
     inv = theta ** (-torch.arange(half, dtype=torch.float64) * 2.0 / head_dim)
+    if rotary_dim is not None and rotary_dim < head_dim:
+        inv[rotary_dim // 2:] = 0.0
     ang = positions.to(torch.float64)[:, None] * inv[None, :]
     return torch.cos(ang).float(), torch.sin(ang).float()
 
@@ -39,8 +42,9 @@ def apply_rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.T
     return torch.cat([a * c - b * s, b * c + a * s], dim=-1)
 
 
-def rmsnorm(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Tensor:
-    return x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps) * w
+def rmsnorm(x: torch.Tensor, w: Optional[torch.Tensor], eps: float) -> torch.Tensor:
+    y = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps)
+    return y if w is None else y * w
 
 
 class OracleModel:
@@ -49,46 +53,89 @@ class OracleModel:
         self.w = load_fp32_weights(loader)
         if "lm_head.weight" not in self.w:
             self.w["lm_head.weight"] = self.w["embed_tokens.weight"]
+        off = self.config.norm_weight_offset
+        if off:
+            for name in self.w:
+                if name.endswith("norm.weight"):
+                    self.w[name] = self.w[name] + off
 
     def _get(self, name: str) -> Optional[torch.Tensor]:
         return self.w.get(name)
 
     @torch.no_grad()
     def forward(self, token_ids, return_hidden: bool = False) -> torch.Tensor:
-        """Full causal forward of one sequence; returns logits ``[T, vocab]`` (fp32)."""
+        """Full causal forward of one sequence; returns logits ``[T, vocab]`` (fp32).
+
+        Gemma-family layers (zse-engine/zse_engine/orchestrator/model_runner.py:428-540): four norms per layer (the
+        sub-layer output is normalised before it joins the residual), GeGLU, per-layer head_dim / kv heads / RoPE,
+        q/k/v head norms, V = un-normalised K on layers without ``v_proj``, a learned per-layer scalar, soft-capped
+        scores and logits, sliding-window layers."""
         c = self.config
         ids = torch.as_tensor(token_ids, dtype=torch.long)
         T = ids.numel()
         h = self.w["embed_tokens.weight"][ids]
-        cos, sin = rope_cos_sin(torch.arange(T), c.head_dim, c.rope_theta)
-        mask = torch.full((T, T), float("-inf")).triu(1)
-        rep = c.num_heads // c.num_kv_heads
+        if c.embed_scale:
+            h = h * (c.hidden_size ** 0.5)
+        gemma = c.is_gemma
+        gelu = (c.hidden_activation or "").startswith("gelu")
+        pos = torch.arange(T)
+        causal = pos[None, :] > pos[:, None]
         for i in range(c.num_layers):
             p = f"layers.{i}."
+            sp = c.layer_spec(i) if gemma else None
+            hd = sp.head_dim if sp else c.head_dim
+            nkv = sp.num_kv_heads if sp else c.num_kv_heads
+            cos, sin = rope_cos_sin(pos, hd, sp.rope_theta if sp else c.rope_theta, sp.rotary_dim if sp else None)
             x = rmsnorm(h, self.w[p + "input_layernorm.weight"], c.rms_norm_eps)
             q = x @ self.w[p + "self_attn.q_proj.weight"].T
             k = x @ self.w[p + "self_attn.k_proj.weight"].T
-            v = x @ self.w[p + "self_attn.v_proj.weight"].T
+            v = k.clone() if (sp and sp.k_is_v) else x @ self.w[p + "self_attn.v_proj.weight"].T
             for t, name in ((q, "q"), (k, "k"), (v, "v")):
                 b = self._get(p + f"self_attn.{name}_proj.bias")
                 if b is not None:
                     t += b
-            q = apply_rope(q.view(T, c.num_heads, c.head_dim), cos, sin)
-            k = apply_rope(k.view(T, c.num_kv_heads, c.head_dim), cos, sin)
-            v = v.view(T, c.num_kv_heads, c.head_dim)
+            q, k, v = q.view(T, c.num_heads, hd), k.view(T, nkv, hd), v.view(T, nkv, hd)
+            if sp and sp.qk_norm:
+                q = rmsnorm(q, self.w[p + "self_attn.q_norm.weight"], c.rms_norm_eps)
+                k = rmsnorm(k, self.w[p + "self_attn.k_norm.weight"], c.rms_norm_eps)
+                v = rmsnorm(v, None, c.rms_norm_eps)
+            q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
+            rep = c.num_heads // nkv
             k = k.repeat_interleave(rep, dim=1)
             v = v.repeat_interleave(rep, dim=1)
-            s = torch.einsum("thd,shd->hts", q, k) / (c.head_dim ** 0.5) + mask
-            a = torch.einsum("hts,shd->thd", torch.softmax(s, dim=-1), v).reshape(T, c.q_dim)
-            h = h + a @ self.w[p + "self_attn.o_proj.weight"].T
-            x = rmsnorm(h, self.w[p + "post_attention_layernorm.weight"], c.rms_norm_eps)
+            s = torch.einsum("thd,shd->hts", q, k) * (sp.scale if sp else hd ** -0.5)
+            if sp and sp.softcap:
+                s = torch.tanh(s / sp.softcap) * sp.softcap
+            hidden = causal
+            if sp and sp.window:
+                hidden = causal | (pos[None, :] <= pos[:, None] - sp.window)
+            s = s.masked_fill(hidden[None], float("-inf"))
+            a = torch.einsum("hts,shd->thd", torch.softmax(s, dim=-1), v).reshape(T, c.num_heads * hd)
+            a = a @ self.w[p + "self_attn.o_proj.weight"].T
+            if gemma:
+                h = h + rmsnorm(a, self.w[p + "post_attention_layernorm.weight"], c.rms_norm_eps)
+                x = rmsnorm(h, self.w[p + "pre_feedforward_layernorm.weight"], c.rms_norm_eps)
+            else:
+                h = h + a
+                x = rmsnorm(h, self.w[p + "post_attention_layernorm.weight"], c.rms_norm_eps)
             g = x @ self.w[p + "mlp.gate_proj.weight"].T
             u = x @ self.w[p + "mlp.up_proj.weight"].T
-            h = h + (torch.nn.functional.silu(g) * u) @ self.w[p + "mlp.down_proj.weight"].T
+            act = torch.nn.functional.gelu(g, approximate="tanh") if gelu else torch.nn.functional.silu(g)
+            m = (act * u) @ self.w[p + "mlp.down_proj.weight"].T
+            if gemma:
+                h = h + rmsnorm(m, self.w[p + "post_feedforward_layernorm.weight"], c.rms_norm_eps)
+                ls = self._get(p + "layer_scalar")
+                if ls is not None:
+                    h = h * ls.reshape(-1)[0]
+            else:
+                h = h + m
         hn = rmsnorm(h, self.w["norm.weight"], c.rms_norm_eps)
         if return_hidden:
             return hn
-        return hn @ self.w["lm_head.weight"].T
+        logits = hn @ self.w["lm_head.weight"].T
+        if c.final_logit_softcapping:
+            logits = torch.tanh(logits / c.final_logit_softcapping) * c.final_logit_softcapping
+        return logits
 
     @torch.no_grad()
     def greedy(self, prompt: List[int], max_new_tokens: int) -> List[int]:
