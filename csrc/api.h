@@ -58,6 +58,29 @@ int zse_rope_kv_write(void* qkv, void* kv_layer, const void* positions_i32, cons
 int zse_swiglu(const void* gate_up_f16, void* out_f16, int M, int I, int gelu, void* stream);
 int zse_bias_add(void* x_f16, const void* bias_f16, int M, int N, void* stream);
 
+// ---- gemma.cu: Gemma-family layers ------------------------------------------------------------------------------
+// qkv fp16 [M, ld]: q heads, k heads, v heads (no v columns when k_is_v: V is then the raw k projection).  Per head:
+// RMSNorm (q, k with the given fp16 weights [hd], NULL = none; v without weight when norm_v), RoPE on pairs
+// (i, i + hd/2) with freqs_f32[i] (0 = pair not rotated), q written back in place, k and v into the cache of this
+// layer: element (block, half, kv_head, offset, d) at block*blk_stride + half*half_stride + (kv_head*block_size +
+// offset)*hd + d.
+int zse_headnorm_rope_kv_write(void* qkv, int ld, void* kv_layer, int64_t blk_stride, int64_t half_stride,
+                               const void* positions_i32, const void* slots_i64, const void* freqs_f32,
+                               const void* q_norm_w, const void* k_norm_w, int norm_v, int k_is_v, float eps, int M,
+                               int nh, int nkv, int hd, int block_size, void* stream);
+// paged attention for any even head_dim <= 512.  Decode: cu_q = q_pos0 = NULL, query t belongs to sequence t at
+// position seq_lens[t]-1.  Prefill: queries packed by cu_q, first query of sequence s at position q_pos0[s].
+// softcap > 0: scores = softcap*tanh(scores/softcap); window > 0: only the last `window` positions are seen.
+int zse_attn_generic(const void* q, int ldq, const void* kv_layer, int64_t blk_stride, int64_t half_stride,
+                     const void* block_tables_i32, int max_blocks, const void* seq_lens_i32, const void* cu_q_i32,
+                     const void* q_pos0_i32, int num_seqs, void* out_f16, int ldo, int T, int nh, int nkv, int hd,
+                     int block_size, float scale, float softcap, int window, void* stream);
+// residual = (residual + RMSNorm(x)*w_post) * scalar_f16[0] (scalar may be NULL); out = RMSNorm(residual)*w_next
+// (out may be NULL)
+int zse_norm_add_rmsnorm(const void* x_f16, const void* w_post, void* residual_f32, const void* scalar_f16,
+                         const void* w_next, void* out_f16, int M, int H, float eps, void* stream);
+int zse_softcap_f16(void* x_f16, int ld, int M, int V, float cap, void* stream);
+
 // ---- attention.cu -------------------------------------------------------------------------------------------
 int64_t zse_attn_decode_scratch_floats(int num_seqs, int nh, int hd, int max_splits);
 int zse_attn_decode(const void* q, int ldq, const void* kv_layer, const void* block_tables_i32, int max_blocks,

@@ -1,0 +1,326 @@
+// Kernels of the Gemma family (Gemma-2, Gemma-4 text), for sm_100a.
+//
+// What these layers need beyond the Llama/Qwen2 path (zse-engine/zse_engine/orchestrator/kernels.py:1479-1786 and
+// model_runner.py:428-540 in the reference): per-head RMSNorm of q and k (learned weight) and of v (no weight),
+// partial rotary embedding with a per-layer base, layers whose head_dim / kv-head count differ from their neighbours,
+// V taken from the un-normalised K projection, soft-capped attention scores, sliding-window layers, a norm on each
+// sub-layer OUTPUT before it joins the residual, a learned scalar per layer, and soft-capped logits.
+//
+//   headnorm_rope_kv_write  q/k/v head norms + RoPE + paged-cache write in one pass over the projection output
+//   attn_generic            paged attention (decode and chunked prefill) for any even head_dim <= 512, with window,
+//                           soft-cap and cache holes; CUDA cores, online softmax, one warp per key
+//   norm_add_rmsnorm        residual = (residual + RMSNorm(x) * w_post) * scalar;  out = RMSNorm(residual) * w_next
+//   softcap                 x = cap * tanh(x / cap) on fp16 logits
+//
+// The cache of a layer is addressed with explicit strides (block, K/V half), so layers of different width can share
+// one pool whose rows are as wide as the widest layer.
+#include "api.h"
+#include "common.cuh"
+
+#define ST(s) reinterpret_cast<cudaStream_t>(s)
+#define LAUNCH_OK() (cudaGetLastError() == cudaSuccess ? 0 : ZSE_ERR_LAUNCH)
+
+namespace zse {
+namespace {
+
+constexpr int kGemmaMaxPairsPerLane = 8;   // head_dim <= 512: 256 rotation pairs over 32 lanes
+
+// grid (M, nh + 2*nkv), one warp per (token, head).  Head order: q heads, k heads, v heads.
+__global__ void __launch_bounds__(32)
+headnorm_rope_kv_write_kernel(__half* __restrict__ qkv, int ld, __half* __restrict__ kv_layer, long long blk_stride,
+                              long long half_stride, const int* __restrict__ positions,
+                              const long long* __restrict__ slots, const float* __restrict__ freqs,
+                              const __half* __restrict__ q_norm_w, const __half* __restrict__ k_norm_w, int norm_v,
+                              int k_is_v, float eps, int nh, int nkv, int hd, int block_size) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x, head = blockIdx.y, lane = threadIdx.x;
+  const bool is_q = head < nh, is_v = head >= nh + nkv;
+  const int kvh = is_q ? 0 : (is_v ? head - nh - nkv : head - nh);
+  // where the head's input sits in the row: v heads of a layer without v_proj read the k projection
+  const int col = is_q ? head * hd : (is_v && !k_is_v ? (nh + nkv + kvh) * hd : (nh + kvh) * hd);
+  const __half* src = qkv + size_t(t) * ld + col;
+  const int half = hd / 2;
+  float a[kGemmaMaxPairsPerLane], b[kGemmaMaxPairsPerLane];
+  float ss = 0.f;
+#pragma unroll
+  for (int r = 0; r < kGemmaMaxPairsPerLane; ++r) {
+    const int i = lane + 32 * r;
+    a[r] = i < half ? __half2float(src[i]) : 0.f;
+    b[r] = i < half ? __half2float(src[i + half]) : 0.f;
+    ss += a[r] * a[r] + b[r] * b[r];
+  }
+  const __half* w = is_q ? q_norm_w : (is_v ? nullptr : k_norm_w);
+  const bool normed = is_v ? norm_v != 0 : w != nullptr;
+  float inv = 1.f;
+  if (normed) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    inv = rsqrtf(ss / float(hd) + eps);
+  }
+  const float pos = float(positions[t]);
+  const long long slot = slots[t];
+  __half* dst = nullptr;
+  if (is_q) {
+    dst = qkv + size_t(t) * ld + col;
+  } else if (slot >= 0) {
+    const long long blk = slot / block_size, off = slot % block_size;
+    dst = kv_layer + blk * blk_stride + (is_v ? half_stride : 0) + (size_t(kvh) * block_size + off) * hd;
+  }
+  if (dst == nullptr) return;
+#pragma unroll
+  for (int r = 0; r < kGemmaMaxPairsPerLane; ++r) {
+    const int i = lane + 32 * r;
+    if (i >= half) break;
+    float x = a[r] * inv, y = b[r] * inv;
+    if (normed && w != nullptr) {
+      x *= __half2float(w[i]);
+      y *= __half2float(w[i + half]);
+    }
+    if (!is_v) {
+      const float f = freqs[i];
+      if (f != 0.f) {
+        float s, c;
+        sincosf(pos * f, &s, &c);
+        const float rx = x * c - y * s, ry = y * c + x * s;
+        x = rx;
+        y = ry;
+      }
+    }
+    dst[i] = __float2half_rn(clamp_f16(x));
+    dst[i + half] = __float2half_rn(clamp_f16(y));
+  }
+}
+
+// ---- generic paged attention ------------------------------------------------------------------------------------
+constexpr int kGenWarps = 4;
+
+// grid (T, nh), 4 warps.  Query token t: decode (cu_q == nullptr): sequence t, position seq_lens[t]-1;
+// prefill: sequence s with cu_q[s] <= t < cu_q[s+1], position q_pos0[s] + t - cu_q[s].
+// Lane l owns the half2 elements 2*(l + 32 r) of the head.  Warp w takes keys first+w, first+w+4, ...
+template <int R>
+__global__ void __launch_bounds__(32 * kGenWarps)
+attn_generic_kernel(const __half* __restrict__ q, int ldq, const __half* __restrict__ kv_layer, long long blk_stride,
+                    long long half_stride, const int* __restrict__ block_tables, int max_blocks,
+                    const int* __restrict__ seq_lens, const int* __restrict__ cu_q, const int* __restrict__ q_pos0,
+                    int num_seqs, __half* __restrict__ out, int ldo, int nh, int nkv, int hd, int block_size,
+                    float scale, float softcap, int window) {
+  pdl_launch_dependents();
+  pdl_wait();
+  extern __shared__ float gen_smem[];            // [kGenWarps][hd + 2]
+  const int t = blockIdx.x, head = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int seq = t, pos;
+  if (cu_q != nullptr) {
+    int lo = 0, hi = num_seqs - 1;               // last s with cu_q[s] <= t
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (cu_q[mid] <= t) lo = mid; else hi = mid - 1;
+    }
+    seq = lo;
+    pos = q_pos0[seq] + t - cu_q[seq];
+  } else {
+    pos = seq_lens[seq] - 1;
+  }
+  const int kvh = head / (nh / nkv);
+  const int hd2 = hd / 2;
+  float2 qv[R], acc[R];
+  const __half2* qp = reinterpret_cast<const __half2*>(q + size_t(t) * ldq + size_t(head) * hd);
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    const int e = lane + 32 * r;
+    qv[r] = e < hd2 ? __half22float2(qp[e]) : make_float2(0.f, 0.f);
+    acc[r] = make_float2(0.f, 0.f);
+  }
+  float m = -INFINITY, l = 0.f;
+  const int first = window > 0 ? max(0, pos + 1 - window) : 0;
+  const int* table = block_tables + size_t(seq) * max_blocks;
+  for (int j = first + warp; j <= pos; j += kGenWarps) {
+    const int blk = table[j / block_size];
+    if (blk < 0) continue;                       // evicted block: its tokens do not exist
+    const __half* kp = kv_layer + size_t(blk) * blk_stride + (size_t(kvh) * block_size + j % block_size) * hd;
+    const __half2* k2 = reinterpret_cast<const __half2*>(kp);
+    const __half2* v2 = reinterpret_cast<const __half2*>(kp + half_stride);
+    float s = 0.f;
+    float2 vv[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const int e = lane + 32 * r;
+      if (e < hd2) {
+        const float2 kf = __half22float2(k2[e]);
+        vv[r] = __half22float2(v2[e]);
+        s += qv[r].x * kf.x + qv[r].y * kf.y;
+      } else {
+        vv[r] = make_float2(0.f, 0.f);
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    s *= scale;
+    if (softcap > 0.f) s = softcap * tanhf(s / softcap);
+    const float m_new = fmaxf(m, s);
+    const float corr = __expf(m - m_new), p = __expf(s - m_new);
+    l = l * corr + p;
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      acc[r].x = acc[r].x * corr + p * vv[r].x;
+      acc[r].y = acc[r].y * corr + p * vv[r].y;
+    }
+    m = m_new;
+  }
+  float* mine = gen_smem + warp * (hd + 2);
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    const int e = lane + 32 * r;
+    if (e < hd2) {
+      mine[2 * e] = acc[r].x;
+      mine[2 * e + 1] = acc[r].y;
+    }
+  }
+  if (lane == 0) {
+    mine[hd] = m;
+    mine[hd + 1] = l;
+  }
+  __syncthreads();
+  float m_all = -INFINITY;
+#pragma unroll
+  for (int w2 = 0; w2 < kGenWarps; ++w2) m_all = fmaxf(m_all, gen_smem[w2 * (hd + 2) + hd]);
+  float l_all = 0.f, f[kGenWarps];
+#pragma unroll
+  for (int w2 = 0; w2 < kGenWarps; ++w2) {
+    const float mw = gen_smem[w2 * (hd + 2) + hd];
+    f[w2] = mw == -INFINITY ? 0.f : __expf(mw - m_all);
+    l_all += f[w2] * gen_smem[w2 * (hd + 2) + hd + 1];
+  }
+  const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
+  __half* op = out + size_t(t) * ldo + size_t(head) * hd;
+  for (int e = threadIdx.x; e < hd; e += blockDim.x) {
+    float v = 0.f;
+#pragma unroll
+    for (int w2 = 0; w2 < kGenWarps; ++w2) v += f[w2] * gen_smem[w2 * (hd + 2) + e];
+    op[e] = __float2half_rn(v * inv);
+  }
+}
+
+// ---- post-norm + residual + next pre-norm ---------------------------------------------------------------------------
+constexpr int kPostNormThreads = 256;
+
+__device__ __forceinline__ float cta_sum(float v, float* red) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  __syncthreads();                                // `red` may still be read from the previous call
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+  __syncthreads();
+  float total = 0.f;
+  for (int i = 0; i < (blockDim.x >> 5); ++i) total += red[i];
+  return total;
+}
+
+__global__ void __launch_bounds__(kPostNormThreads)
+norm_add_rmsnorm_kernel(const __half* __restrict__ x, const __half* __restrict__ w_post, float* __restrict__ residual,
+                        const __half* __restrict__ scalar, const __half* __restrict__ w_next,
+                        __half* __restrict__ out, int H, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  __shared__ float red[32];
+  const size_t base = size_t(blockIdx.x) * H;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    const float f = __half2float(x[base + i]);
+    ss += f * f;
+  }
+  const float inv = rsqrtf(cta_sum(ss, red) / float(H) + eps);
+  const float sc = scalar != nullptr ? __half2float(scalar[0]) : 1.f;
+  float ss2 = 0.f;
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    const float y = __half2float(x[base + i]) * inv * __half2float(w_post[i]);
+    const float r = (residual[base + i] + y) * sc;
+    residual[base + i] = r;
+    ss2 += r * r;
+  }
+  if (out == nullptr) return;
+  const float inv2 = rsqrtf(cta_sum(ss2, red) / float(H) + eps);
+  for (int i = threadIdx.x; i < H; i += blockDim.x)      // each thread re-reads what it wrote itself
+    out[base + i] = __float2half_rn(clamp_f16(residual[base + i] * inv2 * __half2float(w_next[i])));
+}
+
+__global__ void softcap_kernel(__half* __restrict__ x, int ld, int V, float cap) {
+  const size_t row = blockIdx.y;
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < V) {
+    __half* p = x + row * ld + i;
+    *p = __float2half_rn(cap * tanhf(__half2float(*p) / cap));
+  }
+}
+
+}  // namespace
+}  // namespace zse
+
+using namespace zse;
+
+extern "C" int zse_headnorm_rope_kv_write(void* qkv, int ld, void* kv_layer, int64_t blk_stride, int64_t half_stride,
+                                          const void* positions, const void* slots, const void* freqs,
+                                          const void* q_norm_w, const void* k_norm_w, int norm_v, int k_is_v,
+                                          float eps, int M, int nh, int nkv, int hd, int block_size, void* stream) {
+  if (M <= 0) return 0;
+  if (hd % 2 || hd > 64 * kGemmaMaxPairsPerLane || nh <= 0 || nkv <= 0) return ZSE_ERR_SHAPE;
+  dim3 grid(M, nh + 2 * nkv);
+  return launch_pdl(headnorm_rope_kv_write_kernel, grid, dim3(32), 0, ST(stream), reinterpret_cast<__half*>(qkv), ld,
+                    reinterpret_cast<__half*>(kv_layer), (long long)blk_stride, (long long)half_stride,
+                    reinterpret_cast<const int*>(positions), reinterpret_cast<const long long*>(slots),
+                    reinterpret_cast<const float*>(freqs), reinterpret_cast<const __half*>(q_norm_w),
+                    reinterpret_cast<const __half*>(k_norm_w), norm_v, k_is_v, eps, nh, nkv, hd,
+                    block_size) == cudaSuccess ? 0 : ZSE_ERR_LAUNCH;
+}
+
+template <int R>
+static int launch_attn_generic(const void* q, int ldq, const void* kv_layer, int64_t blk_stride, int64_t half_stride,
+                               const void* block_tables, int max_blocks, const void* seq_lens, const void* cu_q,
+                               const void* q_pos0, int num_seqs, void* out, int ldo, int T, int nh, int nkv, int hd,
+                               int block_size, float scale, float softcap, int window, void* stream) {
+  dim3 grid(T, nh);
+  const size_t smem = size_t(kGenWarps) * (hd + 2) * sizeof(float);
+  return launch_pdl(attn_generic_kernel<R>, grid, dim3(32 * kGenWarps), smem, ST(stream),
+                    reinterpret_cast<const __half*>(q), ldq, reinterpret_cast<const __half*>(kv_layer),
+                    (long long)blk_stride, (long long)half_stride, reinterpret_cast<const int*>(block_tables),
+                    max_blocks, reinterpret_cast<const int*>(seq_lens), reinterpret_cast<const int*>(cu_q),
+                    reinterpret_cast<const int*>(q_pos0), num_seqs, reinterpret_cast<__half*>(out), ldo, nh, nkv, hd,
+                    block_size, scale, softcap, window) == cudaSuccess ? 0 : ZSE_ERR_LAUNCH;
+}
+
+extern "C" int zse_attn_generic(const void* q, int ldq, const void* kv_layer, int64_t blk_stride, int64_t half_stride,
+                                const void* block_tables, int max_blocks, const void* seq_lens, const void* cu_q,
+                                const void* q_pos0, int num_seqs, void* out, int ldo, int T, int nh, int nkv, int hd,
+                                int block_size, float scale, float softcap, int window, void* stream) {
+  if (T <= 0) return 0;
+  if (hd % 2 || hd > 512 || nkv <= 0 || nh % nkv || (cu_q == nullptr) != (q_pos0 == nullptr)) return ZSE_ERR_SHAPE;
+  if (cu_q == nullptr && seq_lens == nullptr) return ZSE_ERR_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(kv_layer)) & 3 || (ldq & 1) || (blk_stride & 1) ||
+      (half_stride & 1))
+    return ZSE_ERR_ALIGN;
+#define ZSE_GEN(R)                                                                                                    \
+  return launch_attn_generic<R>(q, ldq, kv_layer, blk_stride, half_stride, block_tables, max_blocks, seq_lens, cu_q,  \
+                                q_pos0, num_seqs, out, ldo, T, nh, nkv, hd, block_size, scale, softcap, window, stream)
+  if (hd <= 64) ZSE_GEN(1);
+  if (hd <= 128) ZSE_GEN(2);
+  if (hd <= 256) ZSE_GEN(4);
+  ZSE_GEN(8);
+#undef ZSE_GEN
+}
+
+extern "C" int zse_norm_add_rmsnorm(const void* x, const void* w_post, void* residual, const void* scalar,
+                                    const void* w_next, void* out, int M, int H, float eps, void* stream) {
+  if (M <= 0) return 0;
+  if (H <= 0 || (out != nullptr && w_next == nullptr)) return ZSE_ERR_SHAPE;
+  return launch_pdl(norm_add_rmsnorm_kernel, dim3(M), dim3(kPostNormThreads), 0, ST(stream),
+                    reinterpret_cast<const __half*>(x), reinterpret_cast<const __half*>(w_post),
+                    reinterpret_cast<float*>(residual), reinterpret_cast<const __half*>(scalar),
+                    reinterpret_cast<const __half*>(w_next), reinterpret_cast<__half*>(out), H,
+                    eps) == cudaSuccess ? 0 : ZSE_ERR_LAUNCH;
+}
+
+extern "C" int zse_softcap_f16(void* x, int ld, int M, int V, float cap, void* stream) {
+  if (M <= 0 || V <= 0) return 0;
+  if (!(cap > 0.f)) return ZSE_ERR_SHAPE;
+  softcap_kernel<<<dim3((V + 255) / 256, M), 256, 0, ST(stream)>>>(reinterpret_cast<__half*>(x), ld, V, cap);
+  return LAUNCH_OK();
+}

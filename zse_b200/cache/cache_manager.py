@@ -61,14 +61,18 @@ class KVCacheManager:
         self._block_size = block_size if block_size > 0 else self._auto_block_size(config)
         if self._block_size % 16:
             raise ValueError("block_size must be a multiple of 16")
-        nkv = num_kv_heads or config.num_kv_heads      # local kv heads under tensor parallelism
+        # local kv heads under tensor parallelism; rows of the widest layer when layers differ (Gemma-4)
+        nkv, pool_hd = config.kv_pool_dims(num_kv_heads)
         if num_blocks > 0:
-            self._pool = BlockPool(num_blocks, self._block_size, config.num_layers, nkv, config.head_dim, device)
+            self._pool = BlockPool(num_blocks, self._block_size, config.num_layers, nkv, pool_hd, device)
         else:
             if budget_bytes <= 0:
                 raise ValueError("either budget_bytes or num_blocks is required")
             self._pool = BlockPool.from_budget(budget_bytes, self._block_size, config.num_layers, nkv,
-                                               config.head_dim, device)
+                                               pool_hd, device)
+        # a uniform window (Mistral) lets old blocks go; models that mix local and global layers keep everything and
+        # apply the window inside attention
+        self._windowed = bool(config.sliding_window and config.sliding_window > 0 and not config.layer_types)
         self._page_table = PageTable(self._pool)
         self._evictor = Evictor(eviction_policy)
         self._dedup = BlockDedup(self._pool) if enable_dedup else None
@@ -168,7 +172,7 @@ class KVCacheManager:
             if new_ids:
                 e = self._page_table.get_entry(seq_id)
                 self._track_blocks(e, max(0, len(e.blocks) - len(new_ids) - 1))
-            if self._config.sliding_window and self._config.sliding_window > 0:
+            if self._windowed:
                 self._trim_sliding_window(seq_id)
 
     def _track_blocks(self, e, first_idx: int) -> None:
@@ -187,7 +191,7 @@ class KVCacheManager:
         neither the pool nor the evictor."""
         errs = [None] * len(seq_ids)
         bs, limit = self._block_size, self._config.max_seq_len
-        windowed = bool(self._config.sliding_window and self._config.sliding_window > 0)
+        windowed = self._windowed
         with self._lock:
             for i, sid in enumerate(seq_ids):
                 e = self._page_table.get_entry_or_none(sid)

@@ -123,8 +123,9 @@ class ModelConfig:
 
     @property
     def kv_cache_bytes_per_token(self) -> int:
-        """fp16 K and V of one token in one layer."""
-        return 2 * self.kv_dim * 2
+        """fp16 K and V of one token in one layer (of the widest layer when layers differ)."""
+        n, d = self.kv_pool_dims()
+        return 2 * n * d * 2
 
     @property
     def total_kv_cache_bytes_per_token(self) -> int:

@@ -25,6 +25,28 @@ SHAPES = {
     "small-128": dict(num_layers=2, hidden_size=512, num_heads=4, num_kv_heads=2, head_dim=128,
                       intermediate_size=1024, vocab_size=2048, rms_norm_eps=1e-6, rope_theta=1e6, arch="qwen2",
                       max_seq_len=4096),
+    # Gemma-2 block: four norms, GeGLU, soft-capped scores and logits, local/global layers alternate
+    "tiny-gemma2": dict(num_layers=4, hidden_size=256, num_heads=4, num_kv_heads=2, head_dim=64,
+                        intermediate_size=768, vocab_size=1024, rms_norm_eps=1e-6, rope_theta=10000.0, arch="gemma2",
+                        max_seq_len=2048, sliding_window=24, query_pre_attn_scalar=64.0, attn_logit_softcapping=50.0,
+                        final_logit_softcapping=30.0, hidden_activation="gelu_pytorch_tanh", embed_scale=True,
+                        tie_word_embeddings=True,
+                        layer_types=["sliding_attention", "full_attention"] * 2),
+    # Gemma-4 block: q/k/v head norms, local layers (head_dim 64) and global layers (head_dim 128, a quarter of it
+    # rotated, V = K projection, one kv head), learned layer scalars
+    "tiny-gemma4": dict(num_layers=3, hidden_size=256, num_heads=4, num_kv_heads=2, head_dim=64,
+                        intermediate_size=768, vocab_size=1024, rms_norm_eps=1e-6, rope_theta=10000.0, arch="gemma4",
+                        max_seq_len=2048, sliding_window=24, global_head_dim=128, global_num_kv_heads=1,
+                        global_rope_theta=1e6, partial_rotary_factor=0.25, attention_k_eq_v=True,
+                        final_logit_softcapping=30.0, hidden_activation="gelu_pytorch_tanh", embed_scale=True,
+                        tie_word_embeddings=True,
+                        layer_types=["sliding_attention", "sliding_attention", "full_attention"]),
+    "gemma2-9b": dict(num_layers=42, hidden_size=3584, num_heads=16, num_kv_heads=8, head_dim=256,
+                      intermediate_size=14336, vocab_size=256000, rms_norm_eps=1e-6, rope_theta=10000.0,
+                      arch="gemma2", max_seq_len=8192, sliding_window=4096, query_pre_attn_scalar=256.0,
+                      attn_logit_softcapping=50.0, final_logit_softcapping=30.0,
+                      hidden_activation="gelu_pytorch_tanh", embed_scale=True, tie_word_embeddings=True,
+                      layer_types=["sliding_attention", "full_attention"] * 21),
     "qwen2.5-7b": dict(num_layers=28, hidden_size=3584, num_heads=28, num_kv_heads=4, head_dim=128,
                        intermediate_size=18944, vocab_size=152064, rms_norm_eps=1e-6, rope_theta=1e6, arch="qwen2",
                        max_seq_len=32768),
@@ -62,11 +84,16 @@ def byte_tokenizer(vocab_size: int = 1024) -> BPETokenizer:
                         special_tokens=SpecialTokens(bos_id=nxt, eos_id=nxt, pad_id=nxt, unk_id=0))
 
 
-def layer_weight_shapes(c: ModelConfig):
-    return [("self_attn.q_proj", c.q_dim, c.hidden_size), ("self_attn.k_proj", c.kv_dim, c.hidden_size),
-            ("self_attn.v_proj", c.kv_dim, c.hidden_size), ("self_attn.o_proj", c.hidden_size, c.q_dim),
-            ("mlp.gate_proj", c.intermediate_size, c.hidden_size), ("mlp.up_proj", c.intermediate_size, c.hidden_size),
-            ("mlp.down_proj", c.hidden_size, c.intermediate_size)]
+def layer_weight_shapes(c: ModelConfig, layer: int = 0):
+    sp = c.layer_spec(layer) if c.is_gemma else None
+    q_dim = c.num_heads * sp.head_dim if sp else c.q_dim
+    kv_dim = sp.num_kv_heads * sp.head_dim if sp else c.kv_dim
+    out = [("self_attn.q_proj", q_dim, c.hidden_size), ("self_attn.k_proj", kv_dim, c.hidden_size)]
+    if not (sp and sp.k_is_v):
+        out.append(("self_attn.v_proj", kv_dim, c.hidden_size))
+    return out + [("self_attn.o_proj", c.hidden_size, q_dim), ("mlp.gate_proj", c.intermediate_size, c.hidden_size),
+                  ("mlp.up_proj", c.intermediate_size, c.hidden_size),
+                  ("mlp.down_proj", c.hidden_size, c.intermediate_size)]
 
 
 def write_random_model(path: str, config: ModelConfig, seed: int = 0, std: float = 0.02, fast: bool = False,
@@ -105,16 +132,31 @@ def write_random_model(path: str, config: ModelConfig, seed: int = 0, std: float
         else:
             fp16(name, (n, k), rng.standard_normal((n, k), dtype=np.float32) * std)
 
+    # stored norm weights: Gemma-2 files hold w - 1
+    norm_mean = 1.0 - c.norm_weight_offset
+
+    def norm(name, n):
+        fp16(name, (n,), norm_mean + 0.1 * rng.standard_normal(n))
+
     big_fp16("embed_tokens.weight", c.vocab_size, c.hidden_size)
     for i in range(c.num_layers):
         p = f"layers.{i}"
-        fp16(f"{p}.input_layernorm.weight", (c.hidden_size,), 1.0 + 0.1 * rng.standard_normal(c.hidden_size))
-        for name, n, k in layer_weight_shapes(c):
+        fp16(f"{p}.input_layernorm.weight", (c.hidden_size,), norm_mean + 0.1 * rng.standard_normal(c.hidden_size))
+        if c.is_gemma:
+            norm(f"{p}.pre_feedforward_layernorm.weight", c.hidden_size)
+            norm(f"{p}.post_feedforward_layernorm.weight", c.hidden_size)
+            sp = c.layer_spec(i)
+            if sp.qk_norm:
+                norm(f"{p}.self_attn.q_norm.weight", sp.head_dim)
+                norm(f"{p}.self_attn.k_norm.weight", sp.head_dim)
+                fp16(f"{p}.layer_scalar", (1,), [0.8 + 0.4 * rng.random()])
+        for name, n, k in layer_weight_shapes(c, i):
             linear(f"{p}.{name}.weight", n, k)
             if qkv_bias and name.split(".")[-1] in ("q_proj", "k_proj", "v_proj"):
                 fp16(f"{p}.{name}.bias", (n,), rng.standard_normal(n) * std)
-        fp16(f"{p}.post_attention_layernorm.weight", (c.hidden_size,), 1.0 + 0.1 * rng.standard_normal(c.hidden_size))
-    fp16("norm.weight", (c.hidden_size,), 1.0 + 0.1 * rng.standard_normal(c.hidden_size))
+        fp16(f"{p}.post_attention_layernorm.weight", (c.hidden_size,),
+             norm_mean + 0.1 * rng.standard_normal(c.hidden_size))
+    fp16("norm.weight", (c.hidden_size,), norm_mean + 0.1 * rng.standard_normal(c.hidden_size))
     if not c.tie_word_embeddings:
         big_fp16("lm_head.weight", c.vocab_size, c.hidden_size)
     w.finalize()

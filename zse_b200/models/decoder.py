@@ -1,4 +1,4 @@
-"""Llama / Mistral / Qwen2 / Phi-3 decoder over the paged KV cache.
+"""Llama / Mistral / Qwen2 / Phi-3 decoder over the paged KV cache (the Gemma family lives in ``gemma.py``).
 
 One ``DecoderModel`` lives on one device and holds this rank's shard of the weights.  ``forward`` runs a pass over
 ``M`` packed tokens that are already in the persistent step buffers (token ids, positions, cache slots, block
@@ -27,7 +27,7 @@ from ..ops import reference as ref
 from ..ops.backend import LinearWeight, TorchOps, make_ops, np_to_dev
 from ..parallel.shard_plan import ShardPlan, make_plan
 
-SUPPORTED_ARCHS = ("llama", "mistral", "qwen2", "phi3")
+SUPPORTED_ARCHS = ("llama", "mistral", "qwen2", "phi3", "gemma2", "gemma4")
 
 
 def _entry_part(loader: ZSELoader, name: str, rows=None, cols=None, mirror=None) -> dict:
@@ -159,6 +159,9 @@ class DecoderModel:
             raise NotImplementedError(f"architecture '{c.arch}' has a converter but no runtime here yet "
                                       f"(supported: {', '.join(SUPPORTED_ARCHS)})")
         plan = make_plan(c, tp_size, rank)
+        if c.is_gemma and cls is DecoderModel:
+            from .gemma import GemmaDecoderModel
+            cls = GemmaDecoderModel
         m = cls(c, plan, ops or make_ops(device))
         m._load(loader, progress)
         return m

@@ -102,14 +102,32 @@ class TorchOps:
         ref.rope_kv_write(qkv[:M], kv_layer, positions[:M], slots[:M], inv_freq, nh, nkv, hd, block_size)
 
     def attn_decode(self, qkv, kv_layer, block_tables, seq_lens, out, S, nh, nkv, hd, block_size, scale, scratch=None,
-                    num_splits=1):
-        out[:S] = ref.attn_decode(qkv[:S, : nh * hd], kv_layer, block_tables[:S], seq_lens[:S], nh, nkv, hd,
-                                  block_size, scale)
+                    num_splits=1, softcap=0.0, window=0):
+        out[:S, : nh * hd] = ref.attn_decode(qkv[:S, : nh * hd], kv_layer, block_tables[:S], seq_lens[:S], nh, nkv, hd,
+                                             block_size, scale, softcap, window)
 
     def attn_prefill(self, qkv, kv_layer, block_tables, cu_q, q_pos0, out, num_seqs, total_q, max_q_len, nh, nkv, hd,
-                     block_size, scale):
-        out[:total_q] = ref.attn_prefill(qkv[:total_q, : nh * hd], kv_layer, block_tables[:num_seqs],
-                                         cu_q[: num_seqs + 1], q_pos0[:num_seqs], nh, nkv, hd, block_size, scale)
+                     block_size, scale, softcap=0.0, window=0):
+        out[:total_q, : nh * hd] = ref.attn_prefill(qkv[:total_q, : nh * hd], kv_layer, block_tables[:num_seqs],
+                                                    cu_q[: num_seqs + 1], q_pos0[:num_seqs], nh, nkv, hd, block_size,
+                                                    scale, softcap, window)
+
+    # ---- Gemma-family ops ---------------------------------------------------------------------------
+    def headnorm_rope_kv_write(self, qkv, kv_layer, positions, slots, freqs, q_norm_w, k_norm_w, norm_v, k_is_v, eps,
+                               M, nh, nkv, hd, block_size):
+        ref.headnorm_rope_kv_write(qkv[:M], kv_layer, positions[:M], slots[:M], freqs, q_norm_w, k_norm_w, norm_v,
+                                   k_is_v, eps, nh, nkv, hd, block_size)
+
+    def norm_add_rmsnorm(self, x, w_post, residual, scalar, w_next, out, M, eps):
+        y = ref.norm_add_rmsnorm(x[:M], w_post, residual[:M], scalar, w_next, eps)
+        if out is not None and y is not None:
+            out[:M] = y
+
+    def glu(self, gate_up, out, M, I, gelu=False):
+        out[:M, :I] = ref.swiglu(gate_up[:M, :I], gate_up[:M, I: 2 * I], gelu)
+
+    def softcap(self, logits, M, cap):
+        logits[:M] = ref.softcap(logits[:M], cap)
 
     def argmax(self, logits, out, M):
         out[:M] = logits[:M].float().argmax(dim=-1).to(out.dtype)
@@ -258,15 +276,42 @@ class CudaOps(TorchOps):
         self.n.rope_kv_write(qkv, kv_layer, positions, slots, inv_freq, M, nh, nkv, hd, inv_freq.numel() * 2,
                              block_size, planes, n_planes, bias)
 
+    @staticmethod
+    def _needs_generic_attention(kv_layer, hd, softcap, window) -> bool:
+        """The tensor-core attention kernels cover head_dim 64/128 over a packed cache without soft-cap or window."""
+        return bool(softcap or window or hd not in (64, 128) or not kv_layer.is_contiguous())
+
     def attn_decode(self, qkv, kv_layer, block_tables, seq_lens, out, S, nh, nkv, hd, block_size, scale, scratch=None,
-                    num_splits=1):
+                    num_splits=1, softcap=0.0, window=0):
+        if self._needs_generic_attention(kv_layer, hd, softcap, window):
+            self.n.attn_generic(qkv, qkv.stride(0), kv_layer, block_tables, seq_lens, None, None, S, out,
+                                out.stride(0), S, nh, nkv, hd, block_size, scale, softcap, window)
+            return
         self.n.attn_decode(qkv, qkv.stride(0), kv_layer, block_tables, block_tables.stride(0), seq_lens, out,
                            out.stride(0), scratch, S, nh, nkv, hd, block_size, num_splits, float(scale))
 
     def attn_prefill(self, qkv, kv_layer, block_tables, cu_q, q_pos0, out, num_seqs, total_q, max_q_len, nh, nkv, hd,
-                     block_size, scale):
+                     block_size, scale, softcap=0.0, window=0):
+        if self._needs_generic_attention(kv_layer, hd, softcap, window):
+            self.n.attn_generic(qkv, qkv.stride(0), kv_layer, block_tables, None, cu_q, q_pos0, num_seqs, out,
+                                out.stride(0), total_q, nh, nkv, hd, block_size, scale, softcap, window)
+            return
         self.n.attn_prefill(qkv, qkv.stride(0), kv_layer, block_tables, block_tables.stride(0), cu_q, q_pos0, out,
                             out.stride(0), num_seqs, max_q_len, nh, nkv, hd, block_size, float(scale))
+
+    def headnorm_rope_kv_write(self, qkv, kv_layer, positions, slots, freqs, q_norm_w, k_norm_w, norm_v, k_is_v, eps,
+                               M, nh, nkv, hd, block_size):
+        self.n.headnorm_rope_kv_write(qkv, kv_layer, positions, slots, freqs, q_norm_w, k_norm_w, norm_v, k_is_v, eps,
+                                      M, nh, nkv, hd, block_size)
+
+    def norm_add_rmsnorm(self, x, w_post, residual, scalar, w_next, out, M, eps):
+        self.n.norm_add_rmsnorm(x, w_post, residual, scalar, w_next, out, M, residual.shape[1], eps)
+
+    def glu(self, gate_up, out, M, I, gelu=False):
+        self.n.swiglu(gate_up, out, M, I, gelu)
+
+    def softcap(self, logits, M, cap):
+        self.n.softcap(logits, M, logits.shape[1], cap)
 
     def argmax(self, logits, out, M):
         self.n.argmax(logits, logits.stride(0), out, M, logits.shape[1])

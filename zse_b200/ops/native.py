@@ -48,6 +48,15 @@ _SIGS = {
     "zse_rope_kv_write": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                   c_int, c_void_p, c_int, c_void_p, c_void_p]),
     "zse_swiglu": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "zse_headnorm_rope_kv_write": (c_int, [c_void_p, c_int, c_void_p, c_int64, c_int64, c_void_p, c_void_p, c_void_p,
+                                           c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_int, c_int, c_int,
+                                           c_int, c_void_p]),
+    "zse_attn_generic": (c_int, [c_void_p, c_int, c_void_p, c_int64, c_int64, c_void_p, c_int, c_void_p, c_void_p,
+                                 c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float,
+                                 c_int, c_void_p]),
+    "zse_norm_add_rmsnorm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                     c_float, c_void_p]),
+    "zse_softcap_f16": (c_int, [c_void_p, c_int, c_int, c_int, c_float, c_void_p]),
     "zse_bias_add": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "zse_attn_decode_scratch_floats": (c_int64, [c_int, c_int, c_int, c_int]),
     "zse_attn_decode": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int,
@@ -218,6 +227,32 @@ def rope_kv_write(qkv, kv_layer, positions, slots, inv_freq, M, nh, nkv, hd, rot
                   n_planes=0, bias=None):
     _ck(load().zse_rope_kv_write(_p(qkv), _p(kv_layer), _p(positions), _p(slots), _p(inv_freq), M, nh, nkv, hd,
                                  rotary_dim, block_size, _p(planes), n_planes, _p(bias), _stream()), "rope_kv_write")
+
+
+def headnorm_rope_kv_write(qkv, kv_layer, positions, slots, freqs, q_norm_w, k_norm_w, norm_v, k_is_v, eps, M, nh, nkv,
+                           hd, block_size):
+    """``kv_layer``: a (possibly strided) view [blocks, 2, nkv, block_size, hd] whose last three dims are packed."""
+    _ck(load().zse_headnorm_rope_kv_write(_p(qkv), qkv.stride(0), _p(kv_layer), kv_layer.stride(0), kv_layer.stride(1),
+                                          _p(positions), _p(slots), _p(freqs), _p(q_norm_w), _p(k_norm_w),
+                                          int(norm_v), int(k_is_v), float(eps), M, nh, nkv, hd, block_size,
+                                          _stream()), "headnorm_rope_kv_write")
+
+
+def attn_generic(q, ldq, kv_layer, block_tables, seq_lens, cu_q, q_pos0, num_seqs, out, ldo, T, nh, nkv, hd,
+                 block_size, scale, softcap=0.0, window=0):
+    _ck(load().zse_attn_generic(_p(q), ldq, _p(kv_layer), kv_layer.stride(0), kv_layer.stride(1), _p(block_tables),
+                                block_tables.stride(0), _p(seq_lens), _p(cu_q), _p(q_pos0), num_seqs, _p(out), ldo, T,
+                                nh, nkv, hd, block_size, float(scale), float(softcap), int(window), _stream()),
+        "attn_generic")
+
+
+def norm_add_rmsnorm(x, w_post, residual, scalar, w_next, out, M, H, eps):
+    _ck(load().zse_norm_add_rmsnorm(_p(x), _p(w_post), _p(residual), _p(scalar), _p(w_next), _p(out), M, H, float(eps),
+                                    _stream()), "norm_add_rmsnorm")
+
+
+def softcap(x, M, V, cap):
+    _ck(load().zse_softcap_f16(_p(x), x.stride(0), M, V, float(cap), _stream()), "softcap")
 
 
 def swiglu(gate_up, out, M, I, gelu=False):

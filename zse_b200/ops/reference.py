@@ -99,6 +99,52 @@ def rope_kv_write(qkv: torch.Tensor, kv_layer: torch.Tensor, positions: torch.Te
         kv_layer[blk, 1, :, off, :] = v[ok].to(kv_layer.dtype)
 
 
+def headnorm_rope_kv_write(qkv: torch.Tensor, kv_layer: torch.Tensor, positions: torch.Tensor, slots: torch.Tensor,
+                           freqs: torch.Tensor, q_norm_w, k_norm_w, norm_v: bool, k_is_v: bool, eps: float, nh: int,
+                           nkv: int, hd: int, block_size: int) -> None:
+    """Gemma-family variant of ``rope_kv_write``: per-head RMSNorm of q and k (weights [hd] or None) and of v (no
+    weight), RoPE with a full-length frequency table (0 = pair not rotated), V = raw k projection when ``k_is_v``
+    (zse-engine/zse_engine/orchestrator/model_runner.py:455-486).  q is rotated in place; k and v only go to the
+    cache."""
+    M = qkv.shape[0]
+
+    def hnorm(x, w):
+        y = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps)
+        return y if w is None else y * w.float()
+
+    q = qkv[:, : nh * hd].view(M, nh, hd)
+    k_raw = qkv[:, nh * hd: (nh + nkv) * hd].float().view(M, nkv, hd)
+    v = k_raw if k_is_v else qkv[:, (nh + nkv) * hd: (nh + 2 * nkv) * hd].float().view(M, nkv, hd)
+    qf = q.float()
+    if q_norm_w is not None:
+        qf = hnorm(qf, q_norm_w)
+    kf = hnorm(k_raw, k_norm_w) if k_norm_w is not None else k_raw
+    if norm_v:
+        v = hnorm(v, None)
+    q.copy_(rope_(qf, positions, freqs).clamp(-65504, 65504).to(q.dtype))
+    kf = rope_(kf, positions, freqs)
+    ok = slots >= 0
+    if ok.any():
+        blk, off = slots[ok] // block_size, slots[ok] % block_size
+        kv_layer[blk, 0, :, off, :] = kf[ok].clamp(-65504, 65504).to(kv_layer.dtype)
+        kv_layer[blk, 1, :, off, :] = v[ok].clamp(-65504, 65504).to(kv_layer.dtype)
+
+
+def norm_add_rmsnorm(x: torch.Tensor, w_post: torch.Tensor, residual: torch.Tensor, scalar, w_next, eps: float):
+    """residual (fp32, in place) = (residual + RMSNorm(x)*w_post) * scalar; returns RMSNorm(residual)*w_next in fp16
+    (or None without ``w_next``)."""
+    xf = x.float()
+    y = xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * w_post.float()
+    residual.add_(y)
+    if scalar is not None:
+        residual.mul_(float(scalar.reshape(-1)[0]))
+    return None if w_next is None else rmsnorm(residual, w_next, eps)
+
+
+def softcap(x: torch.Tensor, cap: float) -> torch.Tensor:
+    return (cap * torch.tanh(x.float() / cap)).to(x.dtype)
+
+
 def _gather_kv(kv_layer: torch.Tensor, table: torch.Tensor, length: int, block_size: int):
     """K, V [length, nkv, hd] plus a bool mask of positions that sit in holes (block id -1)."""
     nblk = (length + block_size - 1) // block_size
@@ -112,7 +158,8 @@ def _gather_kv(kv_layer: torch.Tensor, table: torch.Tensor, length: int, block_s
 
 
 def attn_decode(q: torch.Tensor, kv_layer: torch.Tensor, block_tables: torch.Tensor, seq_lens: torch.Tensor,
-                nh: int, nkv: int, hd: int, block_size: int, scale: float) -> torch.Tensor:
+                nh: int, nkv: int, hd: int, block_size: int, scale: float, softcap: float = 0.0,
+                window: int = 0) -> torch.Tensor:
     """q [S, nh*hd] -> out [S, nh*hd] fp16; sequence s attends to its first seq_lens[s] cached tokens."""
     S = q.shape[0]
     out = torch.zeros(S, nh * hd, dtype=torch.float16, device=q.device)
@@ -124,6 +171,10 @@ def attn_decode(q: torch.Tensor, kv_layer: torch.Tensor, block_tables: torch.Ten
         k, v, hole = _gather_kv(kv_layer, block_tables[s], n, block_size)
         qs = q[s].float().view(nh, hd)
         sc = torch.einsum("hd,thd->ht", qs, k.repeat_interleave(rep, dim=1)) * scale
+        if softcap:
+            sc = softcap * torch.tanh(sc / softcap)
+        if window:
+            hole = hole | (torch.arange(n, device=q.device) < n - window)
         sc = sc.masked_fill(hole[None, :], float("-inf"))
         p = torch.softmax(sc, dim=-1).nan_to_num(0.0)
         out[s] = torch.einsum("ht,thd->hd", p, v.repeat_interleave(rep, dim=1)).reshape(-1).to(torch.float16)
@@ -131,7 +182,8 @@ def attn_decode(q: torch.Tensor, kv_layer: torch.Tensor, block_tables: torch.Ten
 
 
 def attn_prefill(q: torch.Tensor, kv_layer: torch.Tensor, block_tables: torch.Tensor, cu_q: torch.Tensor,
-                 q_pos0: torch.Tensor, nh: int, nkv: int, hd: int, block_size: int, scale: float) -> torch.Tensor:
+                 q_pos0: torch.Tensor, nh: int, nkv: int, hd: int, block_size: int, scale: float,
+                 softcap: float = 0.0, window: int = 0) -> torch.Tensor:
     """Packed causal attention: query row r of sequence s sits at cache position q_pos0[s] + r and sees every
     cached token at or before it."""
     out = torch.zeros(q.shape[0], nh * hd, dtype=torch.float16, device=q.device)
@@ -145,9 +197,14 @@ def attn_prefill(q: torch.Tensor, kv_layer: torch.Tensor, block_tables: torch.Te
         k, v, hole = _gather_kv(kv_layer, block_tables[s], n, block_size)
         qs = q[a:b].float().view(b - a, nh, hd)
         sc = torch.einsum("qhd,thd->hqt", qs, k.repeat_interleave(rep, dim=1)) * scale
+        if softcap:
+            sc = softcap * torch.tanh(sc / softcap)
         pos_q = torch.arange(p0, n, device=q.device)[:, None]
         pos_k = torch.arange(n, device=q.device)[None, :]
-        sc = sc.masked_fill(((pos_k > pos_q) | hole[None, :])[None], float("-inf"))
+        hidden = (pos_k > pos_q) | hole[None, :]
+        if window:
+            hidden = hidden | (pos_k <= pos_q - window)
+        sc = sc.masked_fill(hidden[None], float("-inf"))
         p = torch.softmax(sc, dim=-1).nan_to_num(0.0)
         out[a:b] = torch.einsum("hqt,thd->qhd", p, v.repeat_interleave(rep, dim=1)).reshape(b - a, -1).to(torch.float16)
     return out
