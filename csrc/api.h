@@ -92,6 +92,19 @@ int zse_attn_prefill(const void* q, int ldq, const void* kv_layer, const void* b
                      const void* cu_q_i32, const void* q_pos0_i32, void* out_f16, int ldo, int num_seqs, int max_q_len,
                      int nh, int nkv, int hd, int block_size, float scale, void* stream);
 
+// the same kernels with an explicit cache addressing (element (block, half, kv_head, offset, d) at block*blk_stride +
+// half*half_stride + (kv_head*block_size + offset)*hd + d; strides in elements, multiples of 8), soft-capped scores
+// (softcap > 0: cap*tanh(score/cap)) and a sliding window (window > 0: only the last `window` positions are seen).
+// head_dim 64, 128 or 256.
+int zse_attn_decode_ext(const void* q, int ldq, const void* kv_layer, int64_t blk_stride, int64_t half_stride,
+                        const void* block_tables_i32, int max_blocks, const void* seq_lens_i32, void* out_f16, int ldo,
+                        void* scratch_f32, int num_seqs, int nh, int nkv, int hd, int block_size, int num_splits,
+                        float scale, float softcap, int window, void* stream);
+int zse_attn_prefill_ext(const void* q, int ldq, const void* kv_layer, int64_t blk_stride, int64_t half_stride,
+                         const void* block_tables_i32, int max_blocks, const void* cu_q_i32, const void* q_pos0_i32,
+                         void* out_f16, int ldo, int num_seqs, int max_q_len, int nh, int nkv, int hd, int block_size,
+                         float scale, float softcap, int window, void* stream);
+
 // ---- sampling.cu --------------------------------------------------------------------------------------------
 int zse_argmax(const void* logits_f16, int ld, void* out_i32, int M, int V, void* stream);
 int zse_sample(const void* logits_f16, int ld, void* out_i32, int M, int V, const void* temperature_f32,

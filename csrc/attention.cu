@@ -58,11 +58,15 @@ __device__ __forceinline__ uint32_t tile_off(int row, int chunk) {
   return uint32_t(row * (HD * 2) + ((chunk ^ (row & 7)) << 4));
 }
 
-template <int HD>
+// EXT adds what the Gemma family needs: scores soft-capped as cap*tanh(s/cap) and a sliding window (only the last
+// `window` tokens are seen).  The cache is addressed through strides (block, K->V), so a layer may be a view into a
+// pool with wider rows.
+template <int HD, bool EXT>
 __global__ void __launch_bounds__(kDecWarps * 32)
 attn_decode_kernel(const __half* __restrict__ q, int ldq, const __half* __restrict__ kv, const int* __restrict__ bt,
                    int max_blocks, const int* __restrict__ seq_lens, __half* __restrict__ out, int ldo,
-                   float* __restrict__ scratch, int nh, int nkv, int block_size, int num_splits, float scale_log2) {
+                   float* __restrict__ scratch, int nh, int nkv, int block_size, int num_splits, float scale_log2,
+                   long long blk_stride, long long half_stride, float softcap, int window) {
   constexpr int kTileBytes = 16 * HD * 2;              // one 16-token K (or V) tile
   constexpr int kChunksPerRow = HD / 8;
   constexpr int kKSteps = HD / 16;
@@ -74,16 +78,17 @@ attn_decode_kernel(const __half* __restrict__ q, int ldq, const __half* __restri
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int G = nh / nkv;
   const int len = seq_lens[seq];
+  const int first_tok = (EXT && window > 0) ? max(0, len - window) : 0;
   const int total_tiles = (len + 15) >> 4;
-  const int per_split = (total_tiles + num_splits - 1) / num_splits;
-  const int tile_begin = split * per_split;
+  const int tile0 = first_tok >> 4;
+  const int per_split = (total_tiles - tile0 + num_splits - 1) / num_splits;
+  const int tile_begin = tile0 + split * per_split;
   const int tile_end = min(total_tiles, tile_begin + per_split);
   const int my_count = tile_end > tile_begin + warp ? (tile_end - tile_begin - warp + kDecWarps - 1) / kDecWarps : 0;
 
   uint8_t* ring = smem + warp * (kDecStages * 2 * kTileBytes);
   const int* my_bt = bt + size_t(seq) * max_blocks;
   const size_t kv_head_stride = size_t(block_size) * HD;        // elements between kv heads inside a block half
-  const size_t blk_stride = size_t(2) * nkv * kv_head_stride;
 
   // Q fragments: rows = query heads of this kv head (zero beyond G)
   uint32_t qa[kKSteps][4];
@@ -107,7 +112,7 @@ attn_decode_kernel(const __half* __restrict__ q, int ldq, const __half* __restri
       const int blk = my_bt[tok / block_size];
       if (blk >= 0) {
         const __half* ksrc = kv + size_t(blk) * blk_stride + size_t(kvh) * kv_head_stride + size_t(tok % block_size) * HD;
-        const __half* vsrc = ksrc + size_t(nkv) * kv_head_stride;
+        const __half* vsrc = ksrc + half_stride;
         uint8_t* kd = ring + (i % kDecStages) * 2 * kTileBytes;
         uint8_t* vd = kd + kTileBytes;
 #pragma unroll
@@ -159,7 +164,12 @@ attn_decode_kernel(const __half* __restrict__ q, int ldq, const __half* __restri
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int t = tok + j * 8 + (lane & 3) * 2 + (e & 1);
-        const float v = t < len ? s[j][e] * scale_log2 : -INFINITY;
+        float v = s[j][e] * scale_log2;
+        if constexpr (EXT) {
+          if (softcap > 0.f) v = softcap * kLog2e * tanhf(v * (1.f / (kLog2e * softcap)));
+          if (t < first_tok) v = -INFINITY;
+        }
+        if (t >= len) v = -INFINITY;
         s[j][e] = v;
         if (e < 2) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
       }
@@ -182,10 +192,11 @@ attn_decode_kernel(const __half* __restrict__ q, int ldq, const __half* __restri
     }
     uint32_t pa[4];
     {
-      const float p00 = exp2f(s[0][0] - m0), p01 = exp2f(s[0][1] - m0), p02 = exp2f(s[0][2] - m1),
-                  p03 = exp2f(s[0][3] - m1);
-      const float p10 = exp2f(s[1][0] - m0), p11 = exp2f(s[1][1] - m0), p12 = exp2f(s[1][2] - m1),
-                  p13 = exp2f(s[1][3] - m1);
+      const float b0f = m0 == -INFINITY ? 0.f : m0, b1f = m1 == -INFINITY ? 0.f : m1;   // fully masked rows
+      const float p00 = exp2f(s[0][0] - b0f), p01 = exp2f(s[0][1] - b0f), p02 = exp2f(s[0][2] - b1f),
+                  p03 = exp2f(s[0][3] - b1f);
+      const float p10 = exp2f(s[1][0] - b0f), p11 = exp2f(s[1][1] - b0f), p12 = exp2f(s[1][2] - b1f),
+                  p13 = exp2f(s[1][3] - b1f);
       l0 += p00 + p01 + p10 + p11;
       l1 += p02 + p03 + p12 + p13;
       pa[0] = pack_h2(p00, p01);
@@ -284,11 +295,12 @@ __global__ void attn_combine_kernel(const float* __restrict__ scratch, __half* _
 constexpr int kPfWarps = 4;          // 16 query rows each -> 64 query rows per CTA
 constexpr int kPfKvTile = 64;
 
-template <int HD>
+template <int HD, bool EXT>
 __global__ void __launch_bounds__(kPfWarps * 32)
 attn_prefill_kernel(const __half* __restrict__ q, int ldq, const __half* __restrict__ kv, const int* __restrict__ bt,
                     int max_blocks, const int* __restrict__ cu_q, const int* __restrict__ q_pos0,
-                    __half* __restrict__ out, int ldo, int nh, int nkv, int block_size, float scale_log2) {
+                    __half* __restrict__ out, int ldo, int nh, int nkv, int block_size, float scale_log2,
+                    long long blk_stride, long long half_stride, float softcap, int window) {
   constexpr int kChunksPerRow = HD / 8;
   constexpr int kKSteps = HD / 16;
   constexpr int kNTilesO = HD / 8;
@@ -302,7 +314,6 @@ attn_prefill_kernel(const __half* __restrict__ q, int ldq, const __half* __restr
   const int kvh = head / (nh / nkv);
   const int* my_bt = bt + size_t(seq) * max_blocks;
   const size_t kv_head_stride = size_t(block_size) * HD;
-  const size_t blk_stride = size_t(2) * nkv * kv_head_stride;
 
   // this warp's 16 query rows
   const int r0 = qt * 64 + warp * 16 + (lane >> 2), r1 = r0 + 8;       // row index inside the sequence's chunk
@@ -337,7 +348,7 @@ attn_prefill_kernel(const __half* __restrict__ q, int ldq, const __half* __restr
           const __half* ksrc = kv + size_t(blk) * blk_stride + size_t(kvh) * kv_head_stride +
                                size_t(tok % block_size) * HD + ch * 8;
           cp_async16(kd + tile_off<HD>(row, ch), ksrc);
-          cp_async16(vd + tile_off<HD>(row, ch), ksrc + size_t(nkv) * kv_head_stride);
+          cp_async16(vd + tile_off<HD>(row, ch), ksrc + half_stride);
         } else {
           *reinterpret_cast<uint4*>(kd + tile_off<HD>(row, ch)) = make_uint4(0, 0, 0, 0);
           *reinterpret_cast<uint4*>(vd + tile_off<HD>(row, ch)) = make_uint4(0, 0, 0, 0);
@@ -353,8 +364,10 @@ attn_prefill_kernel(const __half* __restrict__ q, int ldq, const __half* __restr
   float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
   const int p0 = pos0 + r0, p1 = pos0 + r1;              // absolute positions of the two rows
 
-  issue(0);
-  for (int t = 0; t < n_tiles; ++t) {
+  // first tile any row of this CTA can see (its first row's window start)
+  const int t_begin = (EXT && window > 0) ? max(0, pos0 + qt * 64 - window + 1) / kPfKvTile : 0;
+  issue(t_begin);
+  for (int t = t_begin; t < n_tiles; ++t) {
     issue(t + 1);
     cp_async_wait<1>();
     __syncthreads();
@@ -390,7 +403,12 @@ attn_prefill_kernel(const __half* __restrict__ q, int ldq, const __half* __restr
         for (int e = 0; e < 4; ++e) {
           const int tk = tok0 + j * 8 + (lane & 3) * 2 + (e & 1);
           const int pos = e < 2 ? p0 : p1;
-          const float v = (tk <= pos && !hole) ? s[j][e] * scale_log2 : -INFINITY;
+          float v = s[j][e] * scale_log2;
+          if constexpr (EXT) {
+            if (softcap > 0.f) v = softcap * kLog2e * tanhf(v * (1.f / (kLog2e * softcap)));
+            if (window > 0 && tk <= pos - window) v = -INFINITY;
+          }
+          if (tk > pos || hole) v = -INFINITY;
           s[j][e] = v;
           if (e < 2) mx0 = fmaxf(mx0, v); else mx1 = fmaxf(mx1, v);
         }
@@ -462,24 +480,27 @@ extern "C" int64_t zse_attn_decode_scratch_floats(int num_seqs, int nh, int hd, 
   return int64_t(num_seqs) * nh * max_splits * (hd + 2);
 }
 
-template <int HD>
+template <int HD, bool EXT>
 static int launch_decode(const void* q, int ldq, const void* kv, const void* bt, int max_blocks, const void* lens,
                          void* out, int ldo, void* scratch, int num_seqs, int nh, int nkv, int block_size, int splits,
-                         float scale, cudaStream_t st) {
+                         float scale, long long blk_stride, long long half_stride, float softcap, int window,
+                         cudaStream_t st) {
   constexpr int ring = kDecWarps * kDecStages * 2 * 16 * HD * 2;
   constexpr int merge = kDecWarps * 16 * HD * 4 + kDecWarps * 16 * 2 * 4;
   constexpr int smem = ring > merge ? ring : merge;
   static bool attr = false;
   if (!attr) {
-    if (cudaFuncSetAttribute(attn_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+    if (cudaFuncSetAttribute(attn_decode_kernel<HD, EXT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
+        cudaSuccess)
       return ZSE_ERR_LAUNCH;
     attr = true;
   }
   dim3 grid(nkv, num_seqs, splits);
-  if (launch_pdl(attn_decode_kernel<HD>, grid, dim3(kDecWarps * 32), smem, st, reinterpret_cast<const __half*>(q),
-                 ldq, reinterpret_cast<const __half*>(kv), reinterpret_cast<const int*>(bt), max_blocks,
-                 reinterpret_cast<const int*>(lens), reinterpret_cast<__half*>(out), ldo,
-                 reinterpret_cast<float*>(scratch), nh, nkv, block_size, splits, scale * kLog2e) != cudaSuccess)
+  if (launch_pdl(attn_decode_kernel<HD, EXT>, grid, dim3(kDecWarps * 32), smem, st,
+                 reinterpret_cast<const __half*>(q), ldq, reinterpret_cast<const __half*>(kv),
+                 reinterpret_cast<const int*>(bt), max_blocks, reinterpret_cast<const int*>(lens),
+                 reinterpret_cast<__half*>(out), ldo, reinterpret_cast<float*>(scratch), nh, nkv, block_size, splits,
+                 scale * kLog2e, blk_stride, half_stride, softcap, window) != cudaSuccess)
     return ZSE_ERR_LAUNCH;
   if (splits > 1) {
     if (launch_pdl(attn_combine_kernel<HD>, dim3(nh, num_seqs), dim3(HD), 0, st,
@@ -490,54 +511,84 @@ static int launch_decode(const void* q, int ldq, const void* kv, const void* bt,
   return 0;
 }
 
-extern "C" int zse_attn_decode(const void* q, int ldq, const void* kv_layer, const void* block_tables, int max_blocks,
-                               const void* seq_lens, void* out, int ldo, void* scratch, int num_seqs, int nh, int nkv,
-                               int hd, int block_size, int num_splits, float scale, void* stream) {
+extern "C" int zse_attn_decode_ext(const void* q, int ldq, const void* kv_layer, int64_t blk_stride,
+                                   int64_t half_stride, const void* block_tables, int max_blocks, const void* seq_lens,
+                                   void* out, int ldo, void* scratch, int num_seqs, int nh, int nkv, int hd,
+                                   int block_size, int num_splits, float scale, float softcap, int window,
+                                   void* stream) {
   if (num_seqs <= 0) return 0;
-  if (nh % nkv || nh / nkv > 16 || block_size % 16 || num_splits < 1) return ZSE_ERR_SHAPE;
+  if (nh % nkv || nh / nkv > 16 || block_size % 16 || num_splits < 1 || softcap < 0.f || window < 0)
+    return ZSE_ERR_SHAPE;
   if (num_splits > 1 && scratch == nullptr) return ZSE_ERR_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(kv_layer) & 15) || (blk_stride & 7) || (half_stride & 7)) return ZSE_ERR_ALIGN;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (hd == 128)
-    return launch_decode<128>(q, ldq, kv_layer, block_tables, max_blocks, seq_lens, out, ldo, scratch, num_seqs, nh,
-                              nkv, block_size, num_splits, scale, st);
-  if (hd == 64)
-    return launch_decode<64>(q, ldq, kv_layer, block_tables, max_blocks, seq_lens, out, ldo, scratch, num_seqs, nh,
-                             nkv, block_size, num_splits, scale, st);
+  const bool ext = softcap > 0.f || window > 0;
+#define ZSE_DEC(HD_, EXT_)                                                                                           \
+  return launch_decode<HD_, EXT_>(q, ldq, kv_layer, block_tables, max_blocks, seq_lens, out, ldo, scratch, num_seqs, \
+                                  nh, nkv, block_size, num_splits, scale, blk_stride, half_stride, softcap, window, st)
+  if (hd == 128) { if (ext) ZSE_DEC(128, true); ZSE_DEC(128, false); }
+  if (hd == 64) { if (ext) ZSE_DEC(64, true); ZSE_DEC(64, false); }
+  if (hd == 256) ZSE_DEC(256, true);
+#undef ZSE_DEC
   return ZSE_ERR_SHAPE;
 }
 
-template <int HD>
+extern "C" int zse_attn_decode(const void* q, int ldq, const void* kv_layer, const void* block_tables, int max_blocks,
+                               const void* seq_lens, void* out, int ldo, void* scratch, int num_seqs, int nh, int nkv,
+                               int hd, int block_size, int num_splits, float scale, void* stream) {
+  const int64_t half = int64_t(nkv) * block_size * hd;
+  return zse_attn_decode_ext(q, ldq, kv_layer, 2 * half, half, block_tables, max_blocks, seq_lens, out, ldo, scratch,
+                             num_seqs, nh, nkv, hd, block_size, num_splits, scale, 0.f, 0, stream);
+}
+
+template <int HD, bool EXT>
 static int launch_prefill(const void* q, int ldq, const void* kv, const void* bt, int max_blocks, const void* cu_q,
                           const void* pos0, void* out, int ldo, int num_seqs, int max_q_len, int nh, int nkv,
-                          int block_size, float scale, cudaStream_t st) {
+                          int block_size, float scale, long long blk_stride, long long half_stride, float softcap,
+                          int window, cudaStream_t st) {
   constexpr int smem = 2 * 2 * kPfKvTile * HD * 2;
   static bool attr = false;
   if (!attr) {
-    if (cudaFuncSetAttribute(attn_prefill_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
+    if (cudaFuncSetAttribute(attn_prefill_kernel<HD, EXT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
+        cudaSuccess)
       return ZSE_ERR_LAUNCH;
     attr = true;
   }
   dim3 grid((max_q_len + 63) / 64, nh, num_seqs);
-  attn_prefill_kernel<HD><<<grid, kPfWarps * 32, smem, st>>>(
+  attn_prefill_kernel<HD, EXT><<<grid, kPfWarps * 32, smem, st>>>(
       reinterpret_cast<const __half*>(q), ldq, reinterpret_cast<const __half*>(kv), reinterpret_cast<const int*>(bt),
       max_blocks, reinterpret_cast<const int*>(cu_q), reinterpret_cast<const int*>(pos0),
-      reinterpret_cast<__half*>(out), ldo, nh, nkv, block_size, scale * kLog2e);
+      reinterpret_cast<__half*>(out), ldo, nh, nkv, block_size, scale * kLog2e, blk_stride, half_stride, softcap,
+      window);
   return cudaGetLastError() == cudaSuccess ? 0 : ZSE_ERR_LAUNCH;
+}
+
+extern "C" int zse_attn_prefill_ext(const void* q, int ldq, const void* kv_layer, int64_t blk_stride,
+                                    int64_t half_stride, const void* block_tables, int max_blocks, const void* cu_q,
+                                    const void* q_pos0, void* out, int ldo, int num_seqs, int max_q_len, int nh,
+                                    int nkv, int hd, int block_size, float scale, float softcap, int window,
+                                    void* stream) {
+  if (num_seqs <= 0 || max_q_len <= 0) return 0;
+  if (nh % nkv || block_size % 16 || softcap < 0.f || window < 0) return ZSE_ERR_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(kv_layer) & 15) || (blk_stride & 7) || (half_stride & 7)) return ZSE_ERR_ALIGN;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const bool ext = softcap > 0.f || window > 0;
+#define ZSE_PF(HD_, EXT_)                                                                                            \
+  return launch_prefill<HD_, EXT_>(q, ldq, kv_layer, block_tables, max_blocks, cu_q, q_pos0, out, ldo, num_seqs,     \
+                                   max_q_len, nh, nkv, block_size, scale, blk_stride, half_stride, softcap, window, st)
+  if (hd == 128) { if (ext) ZSE_PF(128, true); ZSE_PF(128, false); }
+  if (hd == 64) { if (ext) ZSE_PF(64, true); ZSE_PF(64, false); }
+  if (hd == 256) ZSE_PF(256, true);
+#undef ZSE_PF
+  return ZSE_ERR_SHAPE;
 }
 
 extern "C" int zse_attn_prefill(const void* q, int ldq, const void* kv_layer, const void* block_tables, int max_blocks,
                                 const void* cu_q, const void* q_pos0, void* out, int ldo, int num_seqs, int max_q_len,
                                 int nh, int nkv, int hd, int block_size, float scale, void* stream) {
-  if (num_seqs <= 0 || max_q_len <= 0) return 0;
-  if (nh % nkv || block_size % 16) return ZSE_ERR_SHAPE;
-  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (hd == 128)
-    return launch_prefill<128>(q, ldq, kv_layer, block_tables, max_blocks, cu_q, q_pos0, out, ldo, num_seqs, max_q_len,
-                               nh, nkv, block_size, scale, st);
-  if (hd == 64)
-    return launch_prefill<64>(q, ldq, kv_layer, block_tables, max_blocks, cu_q, q_pos0, out, ldo, num_seqs, max_q_len,
-                              nh, nkv, block_size, scale, st);
-  return ZSE_ERR_SHAPE;
+  const int64_t half = int64_t(nkv) * block_size * hd;
+  return zse_attn_prefill_ext(q, ldq, kv_layer, 2 * half, half, block_tables, max_blocks, cu_q, q_pos0, out, ldo,
+                              num_seqs, max_q_len, nh, nkv, hd, block_size, scale, 0.f, 0, stream);
 }
 
 // ---- decode attention with library-owned scratch (attn_decode_static.h) -------------------------------------------

@@ -8,7 +8,8 @@
 //
 //   headnorm_rope_kv_write  q/k/v head norms + RoPE + paged-cache write in one pass over the projection output
 //   attn_generic            paged attention (decode and chunked prefill) for any even head_dim <= 512, with window,
-//                           soft-cap and cache holes; CUDA cores, online softmax, one warp per key
+//                           soft-cap and cache holes; CUDA cores, online softmax, one warp per key, the query heads
+//                           of a kv head share its K/V loads
 //   norm_add_rmsnorm        residual = (residual + RMSNorm(x) * w_post) * scalar;  out = RMSNorm(residual) * w_next
 //   softcap                 x = cap * tanh(x / cap) on fp16 logits
 //
@@ -93,12 +94,24 @@ headnorm_rope_kv_write_kernel(__half* __restrict__ qkv, int ld, __half* __restri
 }
 
 // ---- generic paged attention ------------------------------------------------------------------------------------
-constexpr int kGenWarps = 4;
+constexpr int kGenWarps = 8;
 
-// grid (T, nh), 4 warps.  Query token t: decode (cu_q == nullptr): sequence t, position seq_lens[t]-1;
-// prefill: sequence s with cu_q[s] <= t < cu_q[s+1], position q_pos0[s] + t - cu_q[s].
-// Lane l owns the half2 elements 2*(l + 32 r) of the head.  Warp w takes keys first+w, first+w+4, ...
-template <int R>
+__device__ __forceinline__ void gen_cp_async16(void* smem_dst, const void* gmem_src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(smem_dst)), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void gen_cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void gen_cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// grid (T, nkv * ceil(G / GT)), 8 warps.  A CTA serves up to GT query heads of one kv head for one query token, so a
+// K/V row is loaded once for all of them.  Query token t: decode (cu_q == nullptr): sequence t, position
+// seq_lens[t]-1; prefill: sequence s with cu_q[s] <= t < cu_q[s+1], position q_pos0[s] + t - cu_q[s].
+// Warp w takes keys first+w, first+w+8, ... and streams their K and V rows through a private ring of STAGES slots in
+// shared memory (cp.async, 16 bytes per lane), so STAGES-1 rows per warp are in flight while one is reduced; no CTA
+// barrier in the loop.  Lane l owns the half2 elements l + 32 r of a head.  head_dim must be a multiple of 8.
+template <int R, int GT, int STAGES>
 __global__ void __launch_bounds__(32 * kGenWarps)
 attn_generic_kernel(const __half* __restrict__ q, int ldq, const __half* __restrict__ kv_layer, long long blk_stride,
                     long long half_stride, const int* __restrict__ block_tables, int max_blocks,
@@ -107,8 +120,13 @@ attn_generic_kernel(const __half* __restrict__ q, int ldq, const __half* __restr
                     float scale, float softcap, int window) {
   pdl_launch_dependents();
   pdl_wait();
-  extern __shared__ float gen_smem[];            // [kGenWarps][hd + 2]
-  const int t = blockIdx.x, head = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  // ring: [kGenWarps][STAGES][K row, V row] halfs; reused as [kGenWarps][GT][hd + 2] floats for the merge
+  extern __shared__ __align__(16) uint8_t gen_smem_raw[];
+  const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int G = nh / nkv, gchunks = (G + GT - 1) / GT;
+  const int kvh = blockIdx.y / gchunks, g0 = (blockIdx.y % gchunks) * GT;
+  const int ng = min(GT, G - g0);
+  const int head0 = kvh * G + g0;
   int seq = t, pos;
   if (cu_q != nullptr) {
     int lo = 0, hi = num_seqs - 1;               // last s with cu_q[s] <= t
@@ -121,83 +139,134 @@ attn_generic_kernel(const __half* __restrict__ q, int ldq, const __half* __restr
   } else {
     pos = seq_lens[seq] - 1;
   }
-  const int kvh = head / (nh / nkv);
   const int hd2 = hd / 2;
-  float2 qv[R], acc[R];
-  const __half2* qp = reinterpret_cast<const __half2*>(q + size_t(t) * ldq + size_t(head) * hd);
+  float2 qv[GT][R], acc[GT][R];
+  float m[GT], l[GT];
 #pragma unroll
-  for (int r = 0; r < R; ++r) {
-    const int e = lane + 32 * r;
-    qv[r] = e < hd2 ? __half22float2(qp[e]) : make_float2(0.f, 0.f);
-    acc[r] = make_float2(0.f, 0.f);
+  for (int g = 0; g < GT; ++g) {
+    const __half2* qp = reinterpret_cast<const __half2*>(q + size_t(t) * ldq + size_t(head0 + min(g, ng - 1)) * hd);
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const int e = lane + 32 * r;
+      qv[g][r] = (e < hd2 && g < ng) ? __half22float2(qp[e]) : make_float2(0.f, 0.f);
+      acc[g][r] = make_float2(0.f, 0.f);
+    }
+    m[g] = -INFINITY;
+    l[g] = 0.f;
   }
-  float m = -INFINITY, l = 0.f;
   const int first = window > 0 ? max(0, pos + 1 - window) : 0;
   const int* table = block_tables + size_t(seq) * max_blocks;
-  for (int j = first + warp; j <= pos; j += kGenWarps) {
+  const int count = pos >= first + warp ? (pos - first - warp) / kGenWarps + 1 : 0;   // keys of this warp
+  __half* ring = reinterpret_cast<__half*>(gen_smem_raw) + size_t(warp) * STAGES * 2 * hd;
+  const int chunks = hd / 8;                     // 16-byte pieces per row
+
+  auto row_of = [&](int i) -> const __half* {    // K row of this warp's i-th key, or nullptr (a hole)
+    const int j = first + warp + i * kGenWarps;
     const int blk = table[j / block_size];
-    if (blk < 0) continue;                       // evicted block: its tokens do not exist
-    const __half* kp = kv_layer + size_t(blk) * blk_stride + (size_t(kvh) * block_size + j % block_size) * hd;
-    const __half2* k2 = reinterpret_cast<const __half2*>(kp);
-    const __half2* v2 = reinterpret_cast<const __half2*>(kp + half_stride);
-    float s = 0.f;
-    float2 vv[R];
+    if (blk < 0) return nullptr;
+    return kv_layer + size_t(blk) * blk_stride + (size_t(kvh) * block_size + j % block_size) * hd;
+  };
+  auto issue = [&](int i) {                      // always commits a group, so that the wait counts stay aligned
+    if (i < count) {
+      const __half* kp = row_of(i);
+      if (kp != nullptr) {
+        __half* dst = ring + size_t(i % STAGES) * 2 * hd;
+        for (int c = lane; c < chunks; c += 32) {
+          gen_cp_async16(dst + c * 8, kp + c * 8);
+          gen_cp_async16(dst + hd + c * 8, kp + half_stride + c * 8);
+        }
+      }
+    }
+    gen_cp_async_commit();
+  };
+
+#pragma unroll
+  for (int i = 0; i < STAGES - 1; ++i) issue(i);
+  for (int i = 0; i < count; ++i) {
+    gen_cp_async_wait<STAGES - 2>();
+    __syncwarp();                                // slot (i-1) % STAGES is free for everyone; slot i is visible
+    issue(i + STAGES - 1);
+    if (row_of(i) == nullptr) continue;          // evicted block: its tokens do not exist
+    const __half2* k2 = reinterpret_cast<const __half2*>(ring + size_t(i % STAGES) * 2 * hd);
+    const __half2* v2 = k2 + hd2;
+    float s[GT];
+#pragma unroll
+    for (int g = 0; g < GT; ++g) s[g] = 0.f;
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const int e = lane + 32 * r;
+      const float2 kf = e < hd2 ? __half22float2(k2[e]) : make_float2(0.f, 0.f);
+#pragma unroll
+      for (int g = 0; g < GT; ++g) s[g] += qv[g][r].x * kf.x + qv[g][r].y * kf.y;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+      for (int g = 0; g < GT; ++g) s[g] += __shfl_xor_sync(0xffffffffu, s[g], o);
+    }
+    float p[GT];
+#pragma unroll
+    for (int g = 0; g < GT; ++g) {
+      float sc = s[g] * scale;
+      if (softcap > 0.f) sc = softcap * tanhf(sc / softcap);
+      const float m_new = fmaxf(m[g], sc);
+      const float corr = __expf(m[g] - m_new);
+      p[g] = __expf(sc - m_new);
+      l[g] = l[g] * corr + p[g];
+      m[g] = m_new;
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        acc[g][r].x *= corr;
+        acc[g][r].y *= corr;
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const int e = lane + 32 * r;
+      const float2 vf = e < hd2 ? __half22float2(v2[e]) : make_float2(0.f, 0.f);
+#pragma unroll
+      for (int g = 0; g < GT; ++g) {
+        acc[g][r].x += p[g] * vf.x;
+        acc[g][r].y += p[g] * vf.y;
+      }
+    }
+  }
+  gen_cp_async_wait<0>();
+  __syncthreads();                               // every warp is done with its ring
+
+  float* gen_smem = reinterpret_cast<float*>(gen_smem_raw);
+  const int stride = hd + 2;
+  float* mine = gen_smem + size_t(warp) * GT * stride;
+#pragma unroll
+  for (int g = 0; g < GT; ++g) {
 #pragma unroll
     for (int r = 0; r < R; ++r) {
       const int e = lane + 32 * r;
       if (e < hd2) {
-        const float2 kf = __half22float2(k2[e]);
-        vv[r] = __half22float2(v2[e]);
-        s += qv[r].x * kf.x + qv[r].y * kf.y;
-      } else {
-        vv[r] = make_float2(0.f, 0.f);
+        mine[g * stride + 2 * e] = acc[g][r].x;
+        mine[g * stride + 2 * e + 1] = acc[g][r].y;
       }
     }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-    s *= scale;
-    if (softcap > 0.f) s = softcap * tanhf(s / softcap);
-    const float m_new = fmaxf(m, s);
-    const float corr = __expf(m - m_new), p = __expf(s - m_new);
-    l = l * corr + p;
-#pragma unroll
-    for (int r = 0; r < R; ++r) {
-      acc[r].x = acc[r].x * corr + p * vv[r].x;
-      acc[r].y = acc[r].y * corr + p * vv[r].y;
+    if (lane == 0) {
+      mine[g * stride + hd] = m[g];
+      mine[g * stride + hd + 1] = l[g];
     }
-    m = m_new;
-  }
-  float* mine = gen_smem + warp * (hd + 2);
-#pragma unroll
-  for (int r = 0; r < R; ++r) {
-    const int e = lane + 32 * r;
-    if (e < hd2) {
-      mine[2 * e] = acc[r].x;
-      mine[2 * e + 1] = acc[r].y;
-    }
-  }
-  if (lane == 0) {
-    mine[hd] = m;
-    mine[hd + 1] = l;
   }
   __syncthreads();
-  float m_all = -INFINITY;
+  for (int idx = threadIdx.x; idx < ng * hd; idx += blockDim.x) {
+    const int g = idx / hd, e = idx % hd;
+    float m_all = -INFINITY;
 #pragma unroll
-  for (int w2 = 0; w2 < kGenWarps; ++w2) m_all = fmaxf(m_all, gen_smem[w2 * (hd + 2) + hd]);
-  float l_all = 0.f, f[kGenWarps];
+    for (int w2 = 0; w2 < kGenWarps; ++w2) m_all = fmaxf(m_all, gen_smem[(w2 * GT + g) * stride + hd]);
+    float l_all = 0.f, v = 0.f;
 #pragma unroll
-  for (int w2 = 0; w2 < kGenWarps; ++w2) {
-    const float mw = gen_smem[w2 * (hd + 2) + hd];
-    f[w2] = mw == -INFINITY ? 0.f : __expf(mw - m_all);
-    l_all += f[w2] * gen_smem[w2 * (hd + 2) + hd + 1];
-  }
-  const float inv = l_all > 0.f ? 1.f / l_all : 0.f;
-  __half* op = out + size_t(t) * ldo + size_t(head) * hd;
-  for (int e = threadIdx.x; e < hd; e += blockDim.x) {
-    float v = 0.f;
-#pragma unroll
-    for (int w2 = 0; w2 < kGenWarps; ++w2) v += f[w2] * gen_smem[w2 * (hd + 2) + e];
-    op[e] = __float2half_rn(v * inv);
+    for (int w2 = 0; w2 < kGenWarps; ++w2) {
+      const float* src = gen_smem + (w2 * GT + g) * stride;
+      const float f = src[hd] == -INFINITY ? 0.f : __expf(src[hd] - m_all);
+      l_all += f * src[hd + 1];
+      v += f * src[e];
+    }
+    out[size_t(t) * ldo + size_t(head0 + g) * hd + e] = __float2half_rn(l_all > 0.f ? v / l_all : 0.f);
   }
 }
 
@@ -272,19 +341,29 @@ extern "C" int zse_headnorm_rope_kv_write(void* qkv, int ld, void* kv_layer, int
                     block_size) == cudaSuccess ? 0 : ZSE_ERR_LAUNCH;
 }
 
-template <int R>
+template <int R, int GT, int STAGES>
 static int launch_attn_generic(const void* q, int ldq, const void* kv_layer, int64_t blk_stride, int64_t half_stride,
                                const void* block_tables, int max_blocks, const void* seq_lens, const void* cu_q,
                                const void* q_pos0, int num_seqs, void* out, int ldo, int T, int nh, int nkv, int hd,
                                int block_size, float scale, float softcap, int window, void* stream) {
-  dim3 grid(T, nh);
-  const size_t smem = size_t(kGenWarps) * (hd + 2) * sizeof(float);
-  return launch_pdl(attn_generic_kernel<R>, grid, dim3(32 * kGenWarps), smem, ST(stream),
-                    reinterpret_cast<const __half*>(q), ldq, reinterpret_cast<const __half*>(kv_layer),
-                    (long long)blk_stride, (long long)half_stride, reinterpret_cast<const int*>(block_tables),
-                    max_blocks, reinterpret_cast<const int*>(seq_lens), reinterpret_cast<const int*>(cu_q),
-                    reinterpret_cast<const int*>(q_pos0), num_seqs, reinterpret_cast<__half*>(out), ldo, nh, nkv, hd,
-                    block_size, scale, softcap, window) == cudaSuccess ? 0 : ZSE_ERR_LAUNCH;
+  const int G = nh / nkv;
+  dim3 grid(T, nkv * ((G + GT - 1) / GT));
+  const size_t ring = size_t(kGenWarps) * STAGES * 2 * hd * sizeof(__half);       // at most 64 KB
+  const size_t merge = size_t(kGenWarps) * GT * (hd + 2) * sizeof(float);         // at most 33 KB
+  const size_t smem = ring > merge ? ring : merge;
+  static bool configured = false;                 // per instantiation; the attribute is per kernel, any device
+  auto kern = attn_generic_kernel<R, GT, STAGES>;
+  if (!configured) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024) != cudaSuccess)
+      return ZSE_ERR_DRIVER;
+    configured = true;
+  }
+  return launch_pdl(kern, grid, dim3(32 * kGenWarps), smem, ST(stream), reinterpret_cast<const __half*>(q), ldq,
+                    reinterpret_cast<const __half*>(kv_layer), (long long)blk_stride, (long long)half_stride,
+                    reinterpret_cast<const int*>(block_tables), max_blocks, reinterpret_cast<const int*>(seq_lens),
+                    reinterpret_cast<const int*>(cu_q), reinterpret_cast<const int*>(q_pos0), num_seqs,
+                    reinterpret_cast<__half*>(out), ldo, nh, nkv, hd, block_size, scale, softcap,
+                    window) == cudaSuccess ? 0 : ZSE_ERR_LAUNCH;
 }
 
 extern "C" int zse_attn_generic(const void* q, int ldq, const void* kv_layer, int64_t blk_stride, int64_t half_stride,
@@ -292,18 +371,23 @@ extern "C" int zse_attn_generic(const void* q, int ldq, const void* kv_layer, in
                                 const void* q_pos0, int num_seqs, void* out, int ldo, int T, int nh, int nkv, int hd,
                                 int block_size, float scale, float softcap, int window, void* stream) {
   if (T <= 0) return 0;
-  if (hd % 2 || hd > 512 || nkv <= 0 || nh % nkv || (cu_q == nullptr) != (q_pos0 == nullptr)) return ZSE_ERR_SHAPE;
+  if (hd % 8 || hd > 512 || nkv <= 0 || nh % nkv || (cu_q == nullptr) != (q_pos0 == nullptr)) return ZSE_ERR_SHAPE;
   if (cu_q == nullptr && seq_lens == nullptr) return ZSE_ERR_SHAPE;
-  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(kv_layer)) & 3 || (ldq & 1) || (blk_stride & 1) ||
-      (half_stride & 1))
+  if ((reinterpret_cast<uintptr_t>(kv_layer) & 15) || (reinterpret_cast<uintptr_t>(q) & 3) || (ldq & 1) ||
+      (blk_stride & 7) || (half_stride & 7))
     return ZSE_ERR_ALIGN;
-#define ZSE_GEN(R)                                                                                                    \
-  return launch_attn_generic<R>(q, ldq, kv_layer, blk_stride, half_stride, block_tables, max_blocks, seq_lens, cu_q,  \
-                                q_pos0, num_seqs, out, ldo, T, nh, nkv, hd, block_size, scale, softcap, window, stream)
-  if (hd <= 64) ZSE_GEN(1);
-  if (hd <= 128) ZSE_GEN(2);
-  if (hd <= 256) ZSE_GEN(4);
-  ZSE_GEN(8);
+  const int G = nh / nkv;
+#define ZSE_GEN(R, GT, ST_)                                                                                           \
+  return launch_attn_generic<R, GT, ST_>(q, ldq, kv_layer, blk_stride, half_stride, block_tables, max_blocks,         \
+                                         seq_lens, cu_q, q_pos0, num_seqs, out, ldo, T, nh, nkv, hd, block_size,      \
+                                         scale, softcap, window, stream)
+  // heads per CTA: as many of the kv head's group as the registers allow; ring depth: 8 rows per warp in flight
+  // (4 at head_dim 512, where a K+V row pair is 2 KB)
+  if (hd <= 64) { if (G == 1) ZSE_GEN(1, 1, 8); if (G == 2) ZSE_GEN(1, 2, 8); ZSE_GEN(1, 4, 8); }
+  if (hd <= 128) { if (G == 1) ZSE_GEN(2, 1, 8); if (G == 2) ZSE_GEN(2, 2, 8); ZSE_GEN(2, 4, 8); }
+  if (hd <= 256) { if (G == 1) ZSE_GEN(4, 1, 8); if (G == 2) ZSE_GEN(4, 2, 8); ZSE_GEN(4, 4, 8); }
+  if (G == 1) ZSE_GEN(8, 1, 4);
+  ZSE_GEN(8, 2, 4);
 #undef ZSE_GEN
 }
 

@@ -80,9 +80,19 @@ def test_attn_generic_decode(ops, hd, nh, nkv, softcap, window, width):
     sl = torch.tensor(lens, dtype=torch.int32, device="cuda")
     out = torch.zeros(S, nh * hd, dtype=torch.float16, device="cuda")
     scale = 1 / math.sqrt(hd)
-    ops.attn_decode(q, kv, bt, sl, out, S, nh, nkv, hd, bs, scale, None, 1, softcap=softcap, window=window)
-    torch.cuda.synchronize()
     want = ref.attn_decode(q[:, : nh * hd], kv, bt, sl, nh, nkv, hd, bs, scale, softcap, window)
+    # the dispatching op (tensor-core kernel for head_dim 64/128/256, CUDA-core kernel otherwise), with and without
+    # a split of the keys, and the CUDA-core kernel on its own
+    for splits in (1, 3):
+        out.zero_()
+        scratch = torch.zeros(S * nh * splits * (hd + 2), device="cuda")
+        ops.attn_decode(q, kv, bt, sl, out, S, nh, nkv, hd, bs, scale, scratch, splits, softcap=softcap, window=window)
+        torch.cuda.synchronize()
+        assert (out.float() - want.float()).abs().max() < 3e-3, splits
+    out.zero_()
+    ops.n.attn_generic(q, q.stride(0), kv, bt, sl, None, None, S, out, out.stride(0), S, nh, nkv, hd, bs, scale,
+                       softcap, window)
+    torch.cuda.synchronize()
     assert (out.float() - want.float()).abs().max() < 3e-3
 
 
@@ -98,9 +108,14 @@ def test_attn_generic_prefill_chunks(ops, hd, nh, nkv, softcap, window, width):
     q = torch.randn(205, (nh + 2 * nkv) * hd, device="cuda").half()
     out = torch.zeros(205, nh * hd, dtype=torch.float16, device="cuda")
     scale = 1 / math.sqrt(hd)
+    want = ref.attn_prefill(q[:, : nh * hd], kv, bt, cu, p0, nh, nkv, hd, bs, scale, softcap, window)
     ops.attn_prefill(q, kv, bt, cu, p0, out, S, 205, 130, nh, nkv, hd, bs, scale, softcap=softcap, window=window)
     torch.cuda.synchronize()
-    want = ref.attn_prefill(q[:, : nh * hd], kv, bt, cu, p0, nh, nkv, hd, bs, scale, softcap, window)
+    assert (out.float() - want.float()).abs().max() < 3e-3
+    out.zero_()
+    ops.n.attn_generic(q, q.stride(0), kv, bt, None, cu, p0, S, out, out.stride(0), 205, nh, nkv, hd, bs, scale,
+                       softcap, window)
+    torch.cuda.synchronize()
     assert (out.float() - want.float()).abs().max() < 3e-3
 
 

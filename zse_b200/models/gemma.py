@@ -138,6 +138,9 @@ class GemmaDecoderModel(DecoderModel):
         b.attn_out = torch.zeros(max_tokens * attn_w, dtype=f16, device=self.device)
         b.qkv_planes = torch.zeros(1, dtype=torch.float32, device=self.device)
         b.partials = torch.zeros(1, 1, c.hidden_size, dtype=torch.float32, device=self.device)
+        max_hd = max(L.spec.head_dim for L in self.layers)
+        b.attn_scratch = torch.zeros(max(1, max_seqs * c.num_heads * attn_splits * (max_hd + 2)), dtype=torch.float32,
+                                     device=self.device)
         b.gate_up = torch.zeros(max_tokens, 2 * c.intermediate_size, dtype=f16, device=self.device)
         b.sub_out = torch.zeros(max_tokens, c.hidden_size, dtype=f16, device=self.device)
         # per-width 2-D views of the flat q/k/v and attention buffers (a layer's row length is its own)

@@ -277,27 +277,31 @@ class CudaOps(TorchOps):
                              block_size, planes, n_planes, bias)
 
     @staticmethod
-    def _needs_generic_attention(kv_layer, hd, softcap, window) -> bool:
-        """The tensor-core attention kernels cover head_dim 64/128 over a packed cache without soft-cap or window."""
-        return bool(softcap or window or hd not in (64, 128) or not kv_layer.is_contiguous())
+    def _tensor_core_attention(kv_layer, hd, nh, nkv, block_size) -> bool:
+        """The tensor-core attention kernels cover head_dim 64/128/256 with up to 16 query heads per kv head; other
+        shapes (Gemma-4 global layers with head_dim 512) take the CUDA-core kernel."""
+        return (hd in (64, 128, 256) and nh // nkv <= 16 and block_size % 16 == 0 and kv_layer.stride(0) % 8 == 0
+                and kv_layer.stride(1) % 8 == 0 and kv_layer.data_ptr() % 16 == 0)
 
     def attn_decode(self, qkv, kv_layer, block_tables, seq_lens, out, S, nh, nkv, hd, block_size, scale, scratch=None,
                     num_splits=1, softcap=0.0, window=0):
-        if self._needs_generic_attention(kv_layer, hd, softcap, window):
+        if not self._tensor_core_attention(kv_layer, hd, nh, nkv, block_size):
             self.n.attn_generic(qkv, qkv.stride(0), kv_layer, block_tables, seq_lens, None, None, S, out,
                                 out.stride(0), S, nh, nkv, hd, block_size, scale, softcap, window)
             return
-        self.n.attn_decode(qkv, qkv.stride(0), kv_layer, block_tables, block_tables.stride(0), seq_lens, out,
-                           out.stride(0), scratch, S, nh, nkv, hd, block_size, num_splits, float(scale))
+        if scratch is None or scratch.numel() < S * nh * num_splits * (hd + 2):
+            num_splits = 1
+        self.n.attn_decode_ext(qkv, qkv.stride(0), kv_layer, block_tables, seq_lens, out, out.stride(0), scratch, S,
+                               nh, nkv, hd, block_size, num_splits, scale, softcap, window)
 
     def attn_prefill(self, qkv, kv_layer, block_tables, cu_q, q_pos0, out, num_seqs, total_q, max_q_len, nh, nkv, hd,
                      block_size, scale, softcap=0.0, window=0):
-        if self._needs_generic_attention(kv_layer, hd, softcap, window):
+        if not self._tensor_core_attention(kv_layer, hd, nh, nkv, block_size):
             self.n.attn_generic(qkv, qkv.stride(0), kv_layer, block_tables, None, cu_q, q_pos0, num_seqs, out,
                                 out.stride(0), total_q, nh, nkv, hd, block_size, scale, softcap, window)
             return
-        self.n.attn_prefill(qkv, qkv.stride(0), kv_layer, block_tables, block_tables.stride(0), cu_q, q_pos0, out,
-                            out.stride(0), num_seqs, max_q_len, nh, nkv, hd, block_size, float(scale))
+        self.n.attn_prefill_ext(qkv, qkv.stride(0), kv_layer, block_tables, cu_q, q_pos0, out, out.stride(0),
+                                num_seqs, max_q_len, nh, nkv, hd, block_size, scale, softcap, window)
 
     def headnorm_rope_kv_write(self, qkv, kv_layer, positions, slots, freqs, q_norm_w, k_norm_w, norm_v, k_is_v, eps,
                                M, nh, nkv, hd, block_size):

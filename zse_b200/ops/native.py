@@ -63,6 +63,12 @@ _SIGS = {
                                 c_int, c_int, c_int, c_int, c_int, c_float, c_void_p]),
     "zse_attn_prefill": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
                                  c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p]),
+    "zse_attn_decode_ext": (c_int, [c_void_p, c_int, c_void_p, c_int64, c_int64, c_void_p, c_int, c_void_p, c_void_p,
+                                    c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int,
+                                    c_void_p]),
+    "zse_attn_prefill_ext": (c_int, [c_void_p, c_int, c_void_p, c_int64, c_int64, c_void_p, c_int, c_void_p, c_void_p,
+                                     c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float,
+                                     c_int, c_void_p]),
     "zse_argmax": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p]),
     "zse_sample": (c_int, [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_uint64,
                            c_void_p]),
@@ -272,6 +278,23 @@ def attn_decode(q, ldq, kv_layer, block_tables, max_blocks, seq_lens, out, ldo, 
     _ck(load().zse_attn_decode(_p(q), ldq, _p(kv_layer), _p(block_tables), max_blocks, _p(seq_lens), _p(out), ldo,
                                _p(scratch), num_seqs, nh, nkv, hd, block_size, num_splits, scale, _stream()),
         "attn_decode", 2 if num_splits > 1 else 1)
+
+
+def attn_decode_ext(q, ldq, kv_layer, block_tables, seq_lens, out, ldo, scratch, num_seqs, nh, nkv, hd, block_size,
+                    num_splits, scale, softcap=0.0, window=0):
+    """``kv_layer``: a (possibly strided) view [blocks, 2, nkv, block_size, hd] whose last three dims are packed."""
+    _ck(load().zse_attn_decode_ext(_p(q), ldq, _p(kv_layer), kv_layer.stride(0), kv_layer.stride(1), _p(block_tables),
+                                   block_tables.stride(0), _p(seq_lens), _p(out), ldo, _p(scratch), num_seqs, nh, nkv,
+                                   hd, block_size, num_splits, float(scale), float(softcap), int(window), _stream()),
+        "attn_decode_ext")
+
+
+def attn_prefill_ext(q, ldq, kv_layer, block_tables, cu_q, q_pos0, out, ldo, num_seqs, max_q_len, nh, nkv, hd,
+                     block_size, scale, softcap=0.0, window=0):
+    _ck(load().zse_attn_prefill_ext(_p(q), ldq, _p(kv_layer), kv_layer.stride(0), kv_layer.stride(1),
+                                    _p(block_tables), block_tables.stride(0), _p(cu_q), _p(q_pos0), _p(out), ldo,
+                                    num_seqs, max_q_len, nh, nkv, hd, block_size, float(scale), float(softcap),
+                                    int(window), _stream()), "attn_prefill_ext")
 
 
 def attn_prefill(q, ldq, kv_layer, block_tables, max_blocks, cu_q, q_pos0, out, ldo, num_seqs, max_q_len, nh, nkv,
