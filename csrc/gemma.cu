@@ -284,32 +284,72 @@ __device__ __forceinline__ float cta_sum(float v, float* red) {
   return total;
 }
 
+// One CTA per row.  Rows of up to kPostNormThreads * kPostNormRegs elements are held in registers (one read of x and
+// of the residual, all loads issued before the first reduction); longer rows take the looping version.
+constexpr int kPostNormRegs = 32;
+
+template <bool IN_REGS>
 __global__ void __launch_bounds__(kPostNormThreads)
 norm_add_rmsnorm_kernel(const __half* __restrict__ x, const __half* __restrict__ w_post, float* __restrict__ residual,
                         const __half* __restrict__ scalar, const __half* __restrict__ w_next,
                         __half* __restrict__ out, int H, float eps) {
   pdl_launch_dependents();
-  pdl_wait();
   __shared__ float red[32];
   const size_t base = size_t(blockIdx.x) * H;
-  float ss = 0.f;
-  for (int i = threadIdx.x; i < H; i += blockDim.x) {
-    const float f = __half2float(x[base + i]);
-    ss += f * f;
+  const float sc = scalar != nullptr ? __half2float(scalar[0]) : 1.f;     // weights do not depend on earlier kernels
+  if constexpr (IN_REGS) {
+    float wp[kPostNormRegs];
+#pragma unroll
+    for (int k = 0; k < kPostNormRegs; ++k) {
+      const int i = threadIdx.x + k * kPostNormThreads;
+      wp[k] = i < H ? __half2float(w_post[i]) : 0.f;
+    }
+    pdl_wait();
+    float xv[kPostNormRegs], rv[kPostNormRegs];
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < kPostNormRegs; ++k) {
+      const int i = threadIdx.x + k * kPostNormThreads;
+      xv[k] = i < H ? __half2float(x[base + i]) : 0.f;
+      rv[k] = i < H ? residual[base + i] : 0.f;
+      ss += xv[k] * xv[k];
+    }
+    const float inv = rsqrtf(cta_sum(ss, red) / float(H) + eps);
+    float ss2 = 0.f;
+#pragma unroll
+    for (int k = 0; k < kPostNormRegs; ++k) {
+      const int i = threadIdx.x + k * kPostNormThreads;
+      rv[k] = (rv[k] + xv[k] * inv * wp[k]) * sc;
+      if (i < H) residual[base + i] = rv[k];
+      ss2 += rv[k] * rv[k];
+    }
+    if (out == nullptr) return;
+    const float inv2 = rsqrtf(cta_sum(ss2, red) / float(H) + eps);
+#pragma unroll
+    for (int k = 0; k < kPostNormRegs; ++k) {
+      const int i = threadIdx.x + k * kPostNormThreads;
+      if (i < H) out[base + i] = __float2half_rn(clamp_f16(rv[k] * inv2 * __half2float(w_next[i])));
+    }
+  } else {
+    pdl_wait();
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+      const float f = __half2float(x[base + i]);
+      ss += f * f;
+    }
+    const float inv = rsqrtf(cta_sum(ss, red) / float(H) + eps);
+    float ss2 = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+      const float y = __half2float(x[base + i]) * inv * __half2float(w_post[i]);
+      const float r = (residual[base + i] + y) * sc;
+      residual[base + i] = r;
+      ss2 += r * r;
+    }
+    if (out == nullptr) return;
+    const float inv2 = rsqrtf(cta_sum(ss2, red) / float(H) + eps);
+    for (int i = threadIdx.x; i < H; i += blockDim.x)      // each thread re-reads what it wrote itself
+      out[base + i] = __float2half_rn(clamp_f16(residual[base + i] * inv2 * __half2float(w_next[i])));
   }
-  const float inv = rsqrtf(cta_sum(ss, red) / float(H) + eps);
-  const float sc = scalar != nullptr ? __half2float(scalar[0]) : 1.f;
-  float ss2 = 0.f;
-  for (int i = threadIdx.x; i < H; i += blockDim.x) {
-    const float y = __half2float(x[base + i]) * inv * __half2float(w_post[i]);
-    const float r = (residual[base + i] + y) * sc;
-    residual[base + i] = r;
-    ss2 += r * r;
-  }
-  if (out == nullptr) return;
-  const float inv2 = rsqrtf(cta_sum(ss2, red) / float(H) + eps);
-  for (int i = threadIdx.x; i < H; i += blockDim.x)      // each thread re-reads what it wrote itself
-    out[base + i] = __float2half_rn(clamp_f16(residual[base + i] * inv2 * __half2float(w_next[i])));
 }
 
 __global__ void softcap_kernel(__half* __restrict__ x, int ld, int V, float cap) {
@@ -395,11 +435,11 @@ extern "C" int zse_norm_add_rmsnorm(const void* x, const void* w_post, void* res
                                     const void* w_next, void* out, int M, int H, float eps, void* stream) {
   if (M <= 0) return 0;
   if (H <= 0 || (out != nullptr && w_next == nullptr)) return ZSE_ERR_SHAPE;
-  return launch_pdl(norm_add_rmsnorm_kernel, dim3(M), dim3(kPostNormThreads), 0, ST(stream),
-                    reinterpret_cast<const __half*>(x), reinterpret_cast<const __half*>(w_post),
-                    reinterpret_cast<float*>(residual), reinterpret_cast<const __half*>(scalar),
-                    reinterpret_cast<const __half*>(w_next), reinterpret_cast<__half*>(out), H,
-                    eps) == cudaSuccess ? 0 : ZSE_ERR_LAUNCH;
+  auto kern = H <= kPostNormThreads * kPostNormRegs ? norm_add_rmsnorm_kernel<true> : norm_add_rmsnorm_kernel<false>;
+  return launch_pdl(kern, dim3(M), dim3(kPostNormThreads), 0, ST(stream), reinterpret_cast<const __half*>(x),
+                    reinterpret_cast<const __half*>(w_post), reinterpret_cast<float*>(residual),
+                    reinterpret_cast<const __half*>(scalar), reinterpret_cast<const __half*>(w_next),
+                    reinterpret_cast<__half*>(out), H, eps) == cudaSuccess ? 0 : ZSE_ERR_LAUNCH;
 }
 
 extern "C" int zse_softcap_f16(void* x, int ld, int M, int V, float cap, void* stream) {
