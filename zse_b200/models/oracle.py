@@ -5,7 +5,8 @@ Weights are dequantised to fp32 exactly as the file defines them (INT4: ``nibble
 Llama/Qwen2 block is evaluated in fp32 with the numerics contract of the reference runner
 (zse-engine/zse_engine/orchestrator/model_runner.py:1123-1297): RMSNorm ``x*rsqrt(mean(x^2)+eps)*w``, rotate-half
 RoPE with ``freq_i = theta^(-2i/hd)``, GQA ``kv = head // (nh/nkv)``, scale ``1/sqrt(hd)``, causal softmax,
-``down(silu(gate)*up)``.  Nothing here is rounded to 16 bits.
+``down(silu(gate)*up)``.  Gemma-2 / Gemma-4 layers follow HuggingFace transformers (and the reference's Gemma-4
+path, model_runner.py:428-540).  Nothing here is rounded to 16 bits.
 """
 from __future__ import annotations
 

@@ -234,7 +234,7 @@ $("search").addEventListener("submit", async (ev) => {
   ev.preventDefault();
   const r = await api("/v1/rag/search", { method: "POST", body: JSON.stringify({ query: $("query").value, top_k: 5 }) });
   $("hits").textContent = r.ok ? (r.body.results || []).map((h) =>
-    `${(h.score ?? 0).toFixed ? h.score.toFixed(3) : h.score}  ${h.document || h.doc_name || ""}\n${(h.text || "").slice(0, 240)}`).join("\n\n")
+    `${Number(h.score || 0).toFixed(4)}  ${h.doc_name || ""}\n${(h.content || "").slice(0, 240)}`).join("\n\n")
     : "search failed";
 });
 $("mk").addEventListener("submit", async (ev) => {
