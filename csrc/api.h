@@ -57,6 +57,9 @@ int zse_rope_kv_write(void* qkv, void* kv_layer, const void* positions_i32, cons
                       const void* planes_f32, int n_planes, const void* bias_f16, void* stream);
 int zse_swiglu(const void* gate_up_f16, void* out_f16, int M, int I, int gelu, void* stream);
 int zse_bias_add(void* x_f16, const void* bias_f16, int M, int N, void* stream);
+// dst[r, :] = src[rows_i64[r], :] for r < n (fp16 rows of H elements, H and ld multiples of 8)
+int zse_gather_rows_f16(const void* src_f16, int ld, const void* rows_i64, void* dst_f16, int n, int H, int src_rows,
+                        void* status, void* stream);
 
 // ---- gemma.cu: Gemma-family layers ------------------------------------------------------------------------------
 // qkv fp16 [M, ld]: q heads, k heads, v heads (no v columns when k_is_v: V is then the raw k projection).  Per head:

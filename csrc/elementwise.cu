@@ -248,6 +248,22 @@ __global__ void swiglu_kernel(const __half2* __restrict__ gate_up, __half2* __re
   out[idx] = __floats2half2_rn(clamp_f16(r.x), clamp_f16(r.y));
 }
 
+// dst[r, :] = src[rows[r], :] (fp16 rows of H elements, 16-byte pieces); a row index outside [0, src_rows) is
+// reported through the status word and reads row 0
+__global__ void gather_rows_kernel(const __half* __restrict__ src, int ld, const long long* __restrict__ rows,
+                                   __half* __restrict__ dst, int H, int src_rows, Status* st) {
+  pdl_launch_dependents();
+  pdl_wait();
+  long long r = rows[blockIdx.x];
+  if (r < 0 || r >= src_rows) {
+    if (threadIdx.x == 0) report(st, kBadArgument, 22, unsigned(r));
+    r = 0;
+  }
+  const uint4* s = reinterpret_cast<const uint4*>(src + size_t(r) * ld);
+  uint4* d = reinterpret_cast<uint4*>(dst + size_t(blockIdx.x) * H);
+  for (int i = threadIdx.x; i < H / 8; i += blockDim.x) d[i] = s[i];
+}
+
 __global__ void bias_add_kernel(__half* __restrict__ x, const __half* __restrict__ bias, size_t total, int N) {
   const size_t idx = size_t(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx < total) x[idx] = __float2half_rn(__half2float(x[idx]) + __half2float(bias[idx % N]));
@@ -324,6 +340,15 @@ extern "C" int zse_swiglu(const void* gate_up, void* out, int M, int I, int gelu
   swiglu_kernel<<<unsigned((total + 255) / 256), 256, 0, ST(stream)>>>(reinterpret_cast<const __half2*>(gate_up),
                                                                        reinterpret_cast<__half2*>(out), M, I / 2, gelu);
   return LAUNCH_OK();
+}
+
+extern "C" int zse_gather_rows_f16(const void* src, int ld, const void* rows_i64, void* dst, int n, int H,
+                                   int src_rows, void* status, void* stream) {
+  if (n <= 0) return 0;
+  if (H % 8 || ld % 8) return ZSE_ERR_SHAPE;
+  return launch_pdl(gather_rows_kernel, dim3(n), dim3(128), 0, ST(stream), reinterpret_cast<const __half*>(src), ld,
+                    reinterpret_cast<const long long*>(rows_i64), reinterpret_cast<__half*>(dst), H, src_rows,
+                    reinterpret_cast<Status*>(status)) == cudaSuccess ? 0 : ZSE_ERR_LAUNCH;
 }
 
 extern "C" int zse_bias_add(void* x, const void* bias, int M, int N, void* stream) {

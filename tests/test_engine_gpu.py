@@ -146,3 +146,28 @@ def test_embeddings_and_last_logits_for_retrieval(model_path, oracle):
     assert logits.shape[0] == 2048 and int(logits.argmax()) == oracle.greedy(toks, 1)[0]
     assert eng.kv_cache.num_sequences == 0
     eng.destroy()
+
+
+@pytest.mark.parametrize("quant", ["int4", "fp16"])
+def test_native_step_driver_equals_python_wiring(tmp_path, monkeypatch, quant):
+    """The C++ step driver (csrc/step.cu) launches the same kernels with the same arguments as the Python wiring of
+    DecoderModel.forward: the logits of a prefill pass and of decode steps must be identical, bit for bit."""
+    path = str(tmp_path / "m.zse")
+    synth.write_random_model(path, synth.shape_config("small-128", quant), seed=11)
+    prompts = _prompts(4, 20, 150, seed=7)
+
+    def run(native: bool):
+        monkeypatch.setenv("ZSE_NATIVE_STEP", "1" if native else "0")
+        eng = ZStreamerEngine(path, config=_cfg(use_cuda_graphs=False))
+        model = eng.runner.model
+        used = model._native_step_for(eng.runner.buf) is not None
+        outs = _run(eng, prompts, 6)
+        logits = eng.runner.buf.logits[:4].clone()
+        eng.destroy()
+        return used, outs, logits
+
+    used_n, outs_n, logits_n = run(True)
+    used_p, outs_p, logits_p = run(False)
+    assert used_n and not used_p
+    assert outs_n == outs_p
+    assert torch.equal(logits_n, logits_p)

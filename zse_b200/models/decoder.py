@@ -266,6 +266,11 @@ class DecoderModel:
         ``b.logits``.  ``kv``: [layers, blocks, 2, nkv_local, block_size, hd]."""
         c, p, ops = self.config, self.plan, self.ops
         bs = kv.shape[4]
+        if self.comm is None and self.lora is None:
+            step = self._native_step_for(b)
+            if step is not None:       # one C call launches the whole pass (csrc/step.cu)
+                step.forward(kv, M, mode == "decode", num_seqs, max_q_len, n_logit_rows, attn_splits)
+                return
         if self.comm is not None and self.comm.fused_norm:
             self.comm.begin_pass()
         ops.embedding(self.embed, b.ids, b.residual, M, self.embed_scale)
@@ -296,6 +301,15 @@ class DecoderModel:
         if n_logit_rows:
             torch.index_select(b.xnorm, 0, b.logit_rows[:n_logit_rows], out=b.xsel[:n_logit_rows])
             ops.linear(self.lm_head, b.xsel, n_logit_rows, b.logits)
+
+    def _native_step_for(self, b: StepBuffers):
+        """The native step driver bound to these buffers (built on first use), or None where it does not apply."""
+        cache = self.__dict__.setdefault("_native_steps", {})
+        key = id(b)
+        if key not in cache:
+            from ..runtime import step_driver
+            cache[key] = step_driver.try_build(self, b)
+        return cache[key]
 
     def hidden_rows(self, b: StepBuffers, rows: int) -> torch.Tensor:
         """Final-norm hidden states of the first ``rows`` tokens of the last pass (for embeddings / RAG)."""
