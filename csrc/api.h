@@ -25,6 +25,9 @@ int zse_get_pdl(void);
 int zse_gemm_w4(const void* w_tiled, const void* x, int x_rows_cap, const void* bias, void* out, int M, int N, int K,
                 int ldo, int epilogue, int k_split, void* status, void* stream);
 int zse_gemm_w4_splits(int M, int N, int K, int k_split);
+// the launcher's plan for a call: out4 = {tiles per wide CTA, K splits, cluster size, CTA shape: 0 wide, 1 narrow,
+// -1 CUDA-core GEMV}
+void zse_gemm_w4_plan(int M, int N, int K, int epilogue, int k_split, int sm_count, int* out4);
 int zse_gemm_f16(const void* w, int w_rows_cap, const void* x, int x_rows_cap, const void* bias, void* out, int M,
                  int N, int K, int ldo, int epilogue, int k_split, void* status, void* stream);
 int zse_gemm_f16_splits(int M, int N, int K, int k_split);

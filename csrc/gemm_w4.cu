@@ -862,6 +862,20 @@ extern "C" int zse_tp_gemm_w4_push(void* ctx, const void* w_tiled, const void* x
   return rc != 0 ? rc : ctas;
 }
 
+// What the launcher would do for these arguments: out4 = {weight tiles per wide CTA, K splits, cluster size along K,
+// CTA shape (0 wide, 1 narrow)}; -1 in out4[3] = CUDA-core GEMV.
+extern "C" void zse_gemm_w4_plan(int M, int N, int K, int epilogue, int k_split, int sm_count, int* out4) {
+  if (sm_count <= 0) sm_count = 148;
+  if (!(g_w4_mode & 4)) {
+    const int gks = gemv_w4_plan(M, N, K, epilogue, sm_count, k_split);
+    if (gks > 0) {
+      out4[0] = 1, out4[1] = gks, out4[2] = 1, out4[3] = -1;
+      return;
+    }
+  }
+  plan_w4(M, N, K, epilogue, sm_count, k_split, &out4[0], &out4[1], &out4[2], &out4[3]);
+}
+
 // Number of fp32 planes zse_gemm_w4 writes for an fp32-epilogue call with these arguments (the caller sizes the plane
 // buffer and tells the consumer how many planes to add).
 extern "C" int zse_gemm_w4_splits(int M, int N, int K, int k_split) {
