@@ -256,7 +256,8 @@ class DecoderModel:
         """Row-parallel projection.  Returns the number of fp32 planes written to ``b.partials``, or - when the
         tensor-parallel exchange ran inside the GEMM - minus the CTA count the consumer has to wait for."""
         comm = self.comm
-        if comm is not None and getattr(comm, "push", False) and comm.can_push(w, M):
+        if (comm is not None and getattr(comm, "push", False) and w.K in self._uniform_shard_k()
+                and comm.can_push(w, M)):
             return -comm.linear_push(self.ops, w, x, M)
         return self.ops.linear_partial(w, x, M, b.partials)
 
@@ -301,6 +302,22 @@ class DecoderModel:
         if n_logit_rows:
             torch.index_select(b.xnorm, 0, b.logit_rows[:n_logit_rows], out=b.xsel[:n_logit_rows])
             ops.linear(self.lm_head, b.xsel, n_logit_rows, b.logits)
+
+    def _uniform_shard_k(self) -> set:
+        """Input widths of the row-parallel projections that are the same on every rank.  The exchange inside the GEMM
+        counts CTAs, and every rank must launch the same number: shards of unequal width (group-aligned splits of an
+        intermediate size that does not divide evenly, e.g. 13824 over 8 ranks) plan differently and stay on the
+        pull path."""
+        ok = self.__dict__.get("_uniform_k")
+        if ok is None:
+            plans = [make_plan(self.config, self.plan.tp_size, r) for r in range(self.plan.tp_size)]
+            ok = set()
+            if len({pl.q_dim for pl in plans}) == 1:
+                ok.add(self.plan.q_dim)
+            if len({pl.inter_size for pl in plans}) == 1:
+                ok.add(self.plan.inter_size)
+            self._uniform_k = ok
+        return ok
 
     def _native_step_for(self, b: StepBuffers):
         """The native step driver bound to these buffers (built on first use), or None where it does not apply."""
