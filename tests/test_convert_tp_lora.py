@@ -198,3 +198,19 @@ def test_lora_manager_slots_and_effect_on_outputs(tmp_path):
     assert mgr.unload_adapter("a") and not mgr.unload_adapter("a")
     assert gen() == base
     eng.destroy()
+
+
+@pytest.mark.timeout(300)
+def test_collectives_facade(tmp_path):
+    """all_reduce / all_gather / broadcast / reduce_scatter / barrier of the communication layer on three CPU ranks."""
+    import socket
+    import subprocess
+    import sys
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = str(s.getsockname()[1])
+    worker = os.path.join(os.path.dirname(os.path.abspath(__file__)), "dist_facade_worker.py")
+    procs = [subprocess.Popen([sys.executable, worker, str(r), "3", port], stdout=subprocess.PIPE,
+                              stderr=subprocess.STDOUT) for r in range(3)]
+    outs = [p.communicate(timeout=240)[0].decode() for p in procs]
+    assert all(p.returncode == 0 for p in procs), "\n".join(outs)

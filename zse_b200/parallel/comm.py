@@ -72,6 +72,37 @@ class NcclComm:
     def barrier(self) -> None:
         dist.barrier(group=self.group)
 
+    # ---- general collectives (the facade of the reference's TensorParallelGroup,
+    # zse-engine/zse_engine/orchestrator/tensor_parallel.py:158-203): sum all-reduce in place, all-gather along
+    # dim 0, broadcast from a rank, sum reduce-scatter along dim 0.  The decoder's hot loop uses the fused kernels;
+    # these serve model families without a fused path and user code.
+    def all_reduce(self, t: torch.Tensor) -> torch.Tensor:
+        dist.all_reduce(t, group=self.group)
+        return t
+
+    def all_gather(self, t: torch.Tensor) -> torch.Tensor:
+        parts = [torch.empty_like(t) for _ in range(self.world)]
+        dist.all_gather(parts, t.contiguous(), group=self.group)
+        return torch.cat(parts, dim=0)
+
+    def broadcast(self, t: torch.Tensor, src: int = 0) -> torch.Tensor:
+        dist.broadcast(t, src=src, group=self.group)
+        return t
+
+    def reduce_scatter(self, t: torch.Tensor) -> torch.Tensor:
+        """Rank r gets rows [r*n, (r+1)*n) of the sum over ranks; dim 0 must divide by the world size."""
+        if t.shape[0] % self.world:
+            raise ValueError(f"reduce_scatter: {t.shape[0]} rows do not divide by {self.world} ranks")
+        n = t.shape[0] // self.world
+        out = torch.empty((n,) + tuple(t.shape[1:]), dtype=t.dtype, device=t.device)
+        try:
+            dist.reduce_scatter_tensor(out, t.contiguous(), group=self.group)
+        except (RuntimeError, NotImplementedError):     # back ends without the primitive (gloo): reduce, then slice
+            full = t.clone()
+            dist.all_reduce(full, group=self.group)
+            out.copy_(full[self.rank * n: (self.rank + 1) * n])
+        return out
+
     def close(self) -> None:
         pass
 
