@@ -169,12 +169,15 @@ class ModelConfig:
                          float(self.attn_logit_softcapping or 0.0), self.arch == "gemma4")
 
     def kv_pool_dims(self, num_kv_heads: Optional[int] = None):
-        """(kv_heads, head_dim) the KV pool is allocated with.  Models whose layers differ get rows of the widest
-        layer (``1 x max(kv_heads * head_dim)``); each layer lays its heads out inside that row."""
+        """(kv_heads, head_dim) the KV pool is allocated with; ``num_kv_heads`` = this rank's share of
+        ``self.num_kv_heads`` under tensor parallelism.  Models whose layers differ get rows of the widest layer
+        (``1 x max(kv_heads * head_dim)`` of the local heads); each layer lays its heads out inside that row."""
+        local = num_kv_heads or self.num_kv_heads
+        tp = max(1, self.num_kv_heads // max(1, local))
         specs = {(s.num_kv_heads, s.head_dim) for s in (self.layer_spec(i) for i in range(self.num_layers))}
         if len(specs) <= 1:
-            return (num_kv_heads or self.num_kv_heads), self.head_dim
-        return 1, max(n * d for n, d in specs)
+            return local, self.head_dim
+        return 1, max(max(1, n // tp) * d for n, d in specs)
 
     def linear_param_count(self) -> int:
         per_layer = (self.hidden_size * self.q_dim + 2 * self.hidden_size * self.kv_dim

@@ -15,13 +15,14 @@ The reference runs this family through a dedicated prefill-only path with separa
 KV cache (zse-engine/zse_engine/orchestrator/model_runner.py:386-580); here it decodes, batches and shares the
 scheduler with every other model.  Layers of a model may differ in head_dim and kv heads (Gemma-4 local / global
 layers): the KV pool is allocated with rows of the widest layer and each layer addresses its own packing inside the
-row through strides.  Tensor parallelism is not wired for this family (one GPU holds a Gemma-2 27B in INT4 many
-times over).
+row through strides.  Tensor parallelism splits heads and the MLP like the other families, with a plain fp16
+all-reduce after the two row-parallel projections (no fused exchange kernel for this family).
 """
 from __future__ import annotations
 
 import math
 import os
+import dataclasses
 from dataclasses import dataclass
 from typing import Dict, List, Optional
 
@@ -66,8 +67,7 @@ def rope_table(head_dim: int, theta: float, rotary_dim: int) -> torch.Tensor:
 class GemmaDecoderModel(DecoderModel):
     def _load(self, loader: ZSELoader, progress=None) -> None:
         c, p, ops, dev = self.config, self.plan, self.ops, self.device
-        if p.tp_size != 1:
-            raise NotImplementedError("tensor parallelism is not wired for the Gemma family")
+        tp, rank = p.tp_size, p.rank
         gs = c.quant.group_size
         has = lambda n: loader.weight_index.find(n) is not None
         off = c.norm_weight_offset
@@ -81,7 +81,7 @@ class GemmaDecoderModel(DecoderModel):
             return np_to_dev(v, dev)
 
         mirror = None
-        if dev.type == "cuda" and os.environ.get("ZSE_STREAM_WEIGHTS", "1") != "0":
+        if dev.type == "cuda" and tp == 1 and os.environ.get("ZSE_STREAM_WEIGHTS", "1") != "0":
             from ..runtime.weight_stream import DeviceMirror
             mirror = DeviceMirror(loader, dev)
             self.load_stats["stream_s"] = round(mirror.seconds, 3)
@@ -93,15 +93,21 @@ class GemmaDecoderModel(DecoderModel):
         self.gelu = (c.hidden_activation or "gelu_pytorch_tanh").startswith("gelu")
         for i in range(c.num_layers):
             pre = f"layers.{i}."
-            sp = c.layer_spec(i)
-            parts = [part(pre + "self_attn.q_proj.weight"), part(pre + "self_attn.k_proj.weight")]
+            full = c.layer_spec(i)
+            # this rank's heads: query heads and kv heads are split evenly (column-parallel q/k/v, row-parallel o)
+            sp = dataclasses.replace(full, num_kv_heads=full.num_kv_heads // tp)
+            hd = sp.head_dim
+            q_rows = (rank * p.num_heads * hd, (rank + 1) * p.num_heads * hd)
+            kv_rows = (rank * sp.num_kv_heads * hd, (rank + 1) * sp.num_kv_heads * hd)
+            parts = [part(pre + "self_attn.q_proj.weight", rows=q_rows),
+                     part(pre + "self_attn.k_proj.weight", rows=kv_rows)]
             if not sp.k_is_v:
-                parts.append(part(pre + "self_attn.v_proj.weight"))
+                parts.append(part(pre + "self_attn.v_proj.weight", rows=kv_rows))
             qkv = ops.make_linear(parts, c.hidden_size, gs)
-            o = ops.make_linear([part(pre + "self_attn.o_proj.weight")], c.num_heads * sp.head_dim, gs)
-            gate_up = ops.make_linear([part(pre + "mlp.gate_proj.weight"), part(pre + "mlp.up_proj.weight")],
-                                      c.hidden_size, gs)
-            down = ops.make_linear([part(pre + "mlp.down_proj.weight")], c.intermediate_size, gs)
+            o = ops.make_linear([part(pre + "self_attn.o_proj.weight", cols=q_rows)], p.num_heads * hd, gs)
+            gate_up = ops.make_linear([part(pre + "mlp.gate_proj.weight", rows=p.inter),
+                                       part(pre + "mlp.up_proj.weight", rows=p.inter)], c.hidden_size, gs)
+            down = ops.make_linear([part(pre + "mlp.down_proj.weight", cols=p.inter)], p.inter_size, gs)
             key = (sp.head_dim, sp.rope_theta, sp.rotary_dim)
             if key not in tables:
                 tables[key] = rope_table(*key).to(dev)
@@ -118,7 +124,7 @@ class GemmaDecoderModel(DecoderModel):
             if progress:
                 progress(i + 1, c.num_layers)
         head_name = "lm_head.weight" if has("lm_head.weight") else "embed_tokens.weight"
-        self.lm_head = ops.make_linear([part(head_name)], c.hidden_size, gs)
+        self.lm_head = ops.make_linear([part(head_name, rows=p.vocab)], c.hidden_size, gs)
         self.weight_bytes += self.lm_head.nbytes
         if mirror is not None:
             mirror.release()
@@ -133,20 +139,21 @@ class GemmaDecoderModel(DecoderModel):
                         attn_splits)
         f16 = torch.float16
         qkv_w = max(L.qkv_width for L in self.layers)
-        attn_w = max(c.num_heads * L.spec.head_dim for L in self.layers)
+        attn_w = max(self.plan.num_heads * L.spec.head_dim for L in self.layers)
         b.qkv = torch.zeros(max_tokens * qkv_w, dtype=f16, device=self.device)
         b.attn_out = torch.zeros(max_tokens * attn_w, dtype=f16, device=self.device)
         b.qkv_planes = torch.zeros(1, dtype=torch.float32, device=self.device)
         b.partials = torch.zeros(1, 1, c.hidden_size, dtype=torch.float32, device=self.device)
         max_hd = max(L.spec.head_dim for L in self.layers)
-        b.attn_scratch = torch.zeros(max(1, max_seqs * c.num_heads * attn_splits * (max_hd + 2)), dtype=torch.float32,
+        b.attn_scratch = torch.zeros(max(1, max_seqs * self.plan.num_heads * attn_splits * (max_hd + 2)),
+                                     dtype=torch.float32,
                                      device=self.device)
-        b.gate_up = torch.zeros(max_tokens, 2 * c.intermediate_size, dtype=f16, device=self.device)
+        b.gate_up = torch.zeros(max_tokens, 2 * self.plan.inter_size, dtype=f16, device=self.device)
         b.sub_out = torch.zeros(max_tokens, c.hidden_size, dtype=f16, device=self.device)
         # per-width 2-D views of the flat q/k/v and attention buffers (a layer's row length is its own)
         b.qkv_views = {w: b.qkv[: max_tokens * w].view(max_tokens, w) for w in {L.qkv_width for L in self.layers}}
         b.attn_views = {w: b.attn_out[: max_tokens * w].view(max_tokens, w)
-                        for w in {c.num_heads * L.spec.head_dim for L in self.layers}}
+                        for w in {self.plan.num_heads * L.spec.head_dim for L in self.layers}}
         return b
 
     def _kv_view(self, kv: torch.Tensor, li: int, sp: LayerSpec) -> torch.Tensor:
@@ -172,7 +179,8 @@ class GemmaDecoderModel(DecoderModel):
     def forward(self, b: StepBuffers, kv: torch.Tensor, M: int, mode: str, num_seqs: int, max_q_len: int = 1,
                 n_logit_rows: int = 0, attn_splits: int = 1) -> None:
         c, ops = self.config, self.ops
-        eps, nh, I = c.rms_norm_eps, c.num_heads, c.intermediate_size
+        eps, nh, I = c.rms_norm_eps, self.plan.num_heads, self.plan.inter_size
+        comm = self.comm
         bs = kv.shape[4]
         ops.embedding(self.embed, b.ids, b.residual, M, self.embed_scale)
         ops.add_rmsnorm(b.residual, b.partials, 0, None, self.layers[0].ln_in, b.xnorm, M, eps)
@@ -192,10 +200,14 @@ class GemmaDecoderModel(DecoderModel):
                 ops.attn_prefill(qkv, kvv, b.block_tables, b.cu_q, b.q_pos0, attn_out, num_seqs, M, max_q_len, nh,
                                  nkv, hd, bs, sp.scale, softcap=sp.softcap, window=sp.window)
             ops.linear(L.o, attn_out, M, b.sub_out)
+            if comm is not None:                    # row-parallel: sum the ranks' partial outputs (fp16, as the
+                comm.all_reduce(b.sub_out[:M])      # reference does after o_proj and down_proj)
             ops.norm_add_rmsnorm(b.sub_out, L.ln_post_attn, b.residual, None, L.ln_pre_ffn, b.xnorm, M, eps)
             ops.linear(L.gate_up, b.xnorm, M, b.gate_up)
             ops.glu(b.gate_up, b.act, M, I, self.gelu)
             ops.linear(L.down, b.act, M, b.sub_out)
+            if comm is not None:
+                comm.all_reduce(b.sub_out[:M])
             nxt = self.layers[li + 1].ln_in if li + 1 < len(self.layers) else self.norm
             ops.norm_add_rmsnorm(b.sub_out, L.ln_post_ffn, b.residual, L.scalar, nxt, b.xnorm, M, eps)
         if n_logit_rows:

@@ -70,6 +70,10 @@ def validate_tp(config: ModelConfig, tp_size: int) -> List[str]:
         errs.append(f"num_heads ({config.num_heads}) not divisible by tp_size ({tp_size})")
     if config.num_kv_heads % tp_size:
         errs.append(f"num_kv_heads ({config.num_kv_heads}) not divisible by tp_size ({tp_size})")
+    if config.is_gemma:                                  # layers may differ in their kv-head count
+        for n in sorted({config.layer_spec(i).num_kv_heads for i in range(config.num_layers)}):
+            if n % tp_size:
+                errs.append(f"a layer kind has {n} kv heads, not divisible by tp_size ({tp_size})")
     if config.intermediate_size < tp_size:
         errs.append(f"intermediate_size ({config.intermediate_size}) smaller than tp_size ({tp_size})")
     return errs
