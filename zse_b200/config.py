@@ -34,6 +34,9 @@ class EngineConfig:
     speculative_k: int = 0
     speculative_mode: str = "ngram"       # "ngram" | "self"
     use_cuda_graphs: bool = True
+    # pipelined decode: launch step n+1 (its input tokens gathered on the device) before step n has been read, so the
+    # device does not wait for the host between steps; None = take ZSE_PIPELINE_DECODE (default off)
+    pipeline_decode: Optional[bool] = None
     comm_backend: str = "fused"           # tensor-parallel collectives: "fused" (in-kernel NVLink) | "nccl"
     headroom_ratio: float = 0.5
     kv_fraction: Optional[float] = None   # share of free memory for the KV cache (None = demand rule)
@@ -53,6 +56,8 @@ class EngineConfig:
             cast = type(cur) if cur is not None else str
             if f.name == "kv_fraction":
                 cast = float
+            if f.name == "pipeline_decode":
+                cast = bool
             setattr(c, f.name, _env(name, cur, cast))
         for k, v in overrides.items():
             if v is not None:

@@ -11,6 +11,8 @@ re-tiled on the device, then step buffers and the KV cache are sized from what i
 """
 from __future__ import annotations
 
+import os
+
 import sys
 import threading
 import time
@@ -137,8 +139,11 @@ class ZStreamerEngine:
             spec = SpeculativeRunner(self._runner, k=cfg.speculative_k, mode=cfg.speculative_mode,
                                      vocab_size=mc.vocab_size)
         self._spec_runner = spec
+        pipeline = cfg.pipeline_decode
+        if pipeline is None:
+            pipeline = os.environ.get("ZSE_PIPELINE_DECODE", "0") not in ("0", "", "false")
         self._batch_runner = BatchRunner(self._runner, self._scheduler, spec_runner=spec,
-                                         lora_manager=self._lora_manager)
+                                         lora_manager=self._lora_manager, pipeline_decode=pipeline)
         self.init_times["runtime"] = time.monotonic() - t2
         self.init_times["total"] = time.monotonic() - t0
         if not self._quiet:

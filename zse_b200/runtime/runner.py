@@ -87,6 +87,13 @@ class ModelRunner:
         self.h_seed = mk(logits_rows, torch.int64)
         self.h_adapter = mk(self.max_tokens, torch.int32)
         self.h_out = mk(logits_rows, torch.int32)
+        # pipelined decode: tokens (and the device status word) of a step are copied out behind the step itself and
+        # read after an event, into alternating buffers, while the next step already runs
+        self.h_out2 = [mk(logits_rows, torch.int32), mk(logits_rows, torch.int32)]
+        self.h_status2 = [mk(4, torch.int32), mk(4, torch.int32)]
+        self._flip = 0
+        self.h_src = mk(logits_rows, torch.int64)
+        self._src_rows = torch.zeros(logits_rows, dtype=torch.int64, device=self.device)
         # numpy views of the pinned staging buffers: per-step host work is numpy slicing, not tensor indexing
         self._np = {"ids": self.h_ids.numpy(), "pos": self.h_pos.numpy(), "slots": self.h_slots.numpy(),
                     "bt": self.h_bt.numpy(), "lens": self.h_lens.numpy(), "rows": self.h_rows.numpy(),
@@ -95,6 +102,21 @@ class ModelRunner:
         self.timings = {"prefill_passes": 0, "decode_steps": 0, "graph_replays": 0, "graph_captures": 0}
 
     # ---- staging ----------------------------------------------------------------------------------------
+    def _staging_begin(self) -> None:
+        """The pinned staging buffers may be rewritten only after the copies that read them have run.  With pipelined
+        decode the host can be a whole step ahead of the device, so this is checked, not assumed (the event has
+        normally completed long before)."""
+        ev = self.__dict__.get("_staged")
+        if ev is not None:
+            ev.synchronize()
+
+    def _staging_end(self) -> None:
+        if self.device.type == "cuda":
+            ev = self.__dict__.get("_staged")
+            if ev is None:
+                ev = self._staged = torch.cuda.Event()
+            ev.record()
+
     def _upload(self, dst: torch.Tensor, src: torch.Tensor, n) -> None:
         dst[:n].copy_(src[:n], non_blocking=True)
 
@@ -141,6 +163,29 @@ class ModelRunner:
         self.model.ops.check()
         return self.h_out[:n].tolist()
 
+    def _fetch_async(self, n: int):
+        """Enqueues the copy of the first ``n`` chosen tokens (and of the status word) to the host behind the work
+        launched so far and returns a callable that waits for that copy only - later launches keep running - and gives
+        the tokens."""
+        h, hs = self.h_out2[self._flip], self.h_status2[self._flip]
+        self._flip ^= 1
+        h[:n].copy_(self.buf.out_tokens[:n], non_blocking=True)
+        status = getattr(self.model.ops, "status", None)
+        ev = None
+        if self.device.type == "cuda":
+            if status is not None:
+                hs.copy_(status.buf, non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record()
+
+        def wait() -> List[int]:
+            if ev is not None:
+                ev.synchronize()
+                if status is not None and int(hs[0]) != 0:
+                    status.check()                   # reads, clears and raises
+            return h[:n].tolist()
+        return wait
+
     # ---- prefill / chunk / verify -------------------------------------------------------------------------
     def prefill(self, items: Sequence[Tuple[int, Sequence[int], int]], sampling: Optional[Sequence[SamplingRow]] = None,
                 all_logits: bool = False, adapters: Optional[Sequence[int]] = None, select: bool = True):
@@ -154,6 +199,7 @@ class ModelRunner:
             raise ValueError(f"prefill pass of {total} tokens / {S} sequences exceeds the pass limits "
                              f"({self.max_tokens} / {self.max_batch_seqs})")
         at, max_q, rows = 0, 0, []
+        self._staging_begin()
         self.h_bt[:S].fill_(-1)
         per_tok_adapter = [] if adapters is not None else None
         for s, (sid, toks, start) in enumerate(items):
@@ -181,6 +227,7 @@ class ModelRunner:
             self._upload(dst, src, n)
         self._stage_adapters(per_tok_adapter, total, total)
         greedy = self._stage_sampling(sampling or [GREEDY] * n_rows, n_rows) if select else True
+        self._staging_end()
         with self._nvtx(f"prefill[{total} tokens, {S} seqs]"):
             self.model.forward(b, cache.slab, total, "prefill", S, max_q, n_rows)
         self.timings["prefill_passes"] += 1
@@ -223,11 +270,13 @@ class ModelRunner:
 
     def decode(self, seq_ids: Sequence[int], last_tokens: Sequence[int],
                sampling: Optional[Sequence[SamplingRow]] = None, adapters: Optional[Sequence[int]] = None,
-               penalties=None, defer: bool = False):
+               penalties=None, defer: bool = False, ids_rows: Optional[Sequence[int]] = None):
         """One new token for each sequence: ``last_tokens[i]`` is appended at the sequence's current length (the
         cache must already have been extended by one), attention covers the whole sequence.  With ``defer`` the step
         is only launched and a callable is returned that waits for it and gives the tokens, so that the caller can
-        do host work while the device runs."""
+        do host work while the device runs.  With ``ids_rows`` the input tokens are not known to the host yet: row i
+        takes the token that the PREVIOUS decode step chose in its row ``ids_rows[i]`` (still on the device), which
+        lets the caller launch a step before it has read the one before."""
         b, cache = self.buf, self.cache
         S = len(seq_ids)
         if S == 0:
@@ -237,8 +286,14 @@ class ModelRunner:
         Sp = min(_bucket(S, self.DECODE_BUCKETS), self.max_batch_seqs) if self.use_graphs else S
         bs = cache.block_size
         n_ = self._np
+        self._staging_begin()
         max_len = max(1, cache.stage_decode(seq_ids, n_["bt"], n_["lens"], n_["pos"], n_["slots"]))
-        n_["ids"][:S] = last_tokens
+        if ids_rows is None:
+            n_["ids"][:S] = last_tokens
+        else:
+            src = self.h_src.numpy()
+            src[:S] = ids_rows
+            src[S:Sp] = 0
         if Sp > S:                                  # padding rows: empty sequences that write nothing
             n_["bt"][S:Sp].fill(-1)
             n_["ids"][S:Sp] = 0
@@ -246,12 +301,18 @@ class ModelRunner:
             n_["slots"][S:Sp] = -1
             n_["lens"][S:Sp] = 0
         n_["rows"][:Sp] = self._arange[:Sp]
-        for dst, src, n in ((b.ids, self.h_ids, Sp), (b.positions, self.h_pos, Sp), (b.slots, self.h_slots, Sp),
+        for dst, src, n in ((b.positions, self.h_pos, Sp), (b.slots, self.h_slots, Sp),
                             (b.block_tables, self.h_bt, Sp), (b.seq_lens, self.h_lens, Sp),
                             (b.logit_rows, self.h_rows, Sp)):
             self._upload(dst, src, n)
+        if ids_rows is None:
+            self._upload(b.ids, self.h_ids, Sp)
+        else:                                       # gather on the device, ordered behind the previous step's choice
+            self._upload(self._src_rows, self.h_src, Sp)
+            torch.index_select(b.out_tokens, 0, self._src_rows[:Sp], out=b.ids[:Sp])
         self._stage_adapters(adapters, S, Sp)
         greedy = self._stage_sampling(sampling or [GREEDY] * S, Sp)
+        self._staging_end()
         splits = self._pick_splits(Sp, max_len)
         self._step += 1
         counter = self._launch_counter()
@@ -283,9 +344,10 @@ class ModelRunner:
             ev[1].record()
             self.step_events.append(ev)
         self.timings["decode_steps"] += 1
+        wait = self._fetch_async(Sp)
         if defer:
-            return lambda: self._fetch_tokens(Sp)[:S]
-        return self._fetch_tokens(Sp)[:S]
+            return lambda: wait()[:S]
+        return wait()[:S]
 
     def _capture(self, Sp: int, splits: int, greedy: bool) -> "torch.cuda.CUDAGraph":
         b, cache = self.buf, self.cache

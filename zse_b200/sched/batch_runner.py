@@ -25,7 +25,8 @@ class StepResult:
     errors: List[str] = field(default_factory=list)
 
 
-def _sampling_row(r: InferenceRequest) -> SamplingRow:
+def _sampling_row(r: InferenceRequest, ahead: int = 0) -> SamplingRow:
+    """``ahead`` = tokens of the request that are still on their way when the row is staged (pipelined decode)."""
     p = r.params
     if p.greedy:
         return SamplingRow()
@@ -33,14 +34,27 @@ def _sampling_row(r: InferenceRequest) -> SamplingRow:
     # one random stream per request, indexed by the token's position in the output: a seeded request gives the same
     # tokens whatever else is in the batch, and a replayed CUDA graph (whose scalar arguments are frozen) still draws
     # fresh numbers because the per-row seed is staged from the host every step
-    z = (int(base) + (r.num_generated + 1) * 0x9E3779B97F4A7C15) & 0xFFFFFFFFFFFFFFFF
+    z = (int(base) + (r.num_generated + ahead + 1) * 0x9E3779B97F4A7C15) & 0xFFFFFFFFFFFFFFFF
     z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & 0xFFFFFFFFFFFFFFFF
     z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & 0xFFFFFFFFFFFFFFFF
     return SamplingRow(float(p.temperature), int(p.top_k), float(p.top_p), int((z ^ (z >> 31)) & 0x7FFFFFFFFFFFFFFF))
 
 
+@dataclass
+class _InFlight:
+    """A decode step that was launched before the step ahead of it had been read (pipelined decode)."""
+    requests: List[InferenceRequest]          # row i of the launch belongs to requests[i]
+    generated: List[int]                      # num_generated of each request when the step was launched
+    pending: object                           # callable: waits for the step's tokens
+
+
 class BatchRunner:
-    def __init__(self, runner: ModelRunner, scheduler: Scheduler, spec_runner=None, lora_manager=None):
+    def __init__(self, runner: ModelRunner, scheduler: Scheduler, spec_runner=None, lora_manager=None,
+                 pipeline_decode: bool = False):
+        self._pipeline = bool(pipeline_decode)
+        self._inflight: Optional[_InFlight] = None
+        self.ahead_launches = 0          # decode steps launched before the step ahead of them had been read
+        self.ahead_dropped = 0           # ... of which the result had to be thrown away
         self._runner = runner
         self._cache = runner.cache
         self._sched = scheduler
@@ -52,6 +66,9 @@ class BatchRunner:
     # ---- entry ----------------------------------------------------------------------------------------
     def execute(self, plan: SchedulerOutput) -> StepResult:
         res = StepResult()
+        if self._inflight is not None and (plan.preempt_requests or plan.prefill_requests
+                                           or not plan.decode_requests):
+            self._drop_inflight()          # the batch is being rearranged: take the next step the ordinary way
         for r in plan.preempt_requests:
             self._release_kv(r)
         for r in plan.finished_requests:
@@ -153,35 +170,67 @@ class BatchRunner:
 
     # ---- decode -----------------------------------------------------------------------------------------
     def _run_decode(self, reqs: List[InferenceRequest], res: StepResult) -> None:
-        # a request that was extended ahead of time (while the previous step ran on the device) is ready as it is
-        todo = [r for r in reqs if not r.pre_extended]
-        errs = dict(zip((id(r) for r in todo), self._cache.extend_batch([r.seq_id for r in todo])))
-        ready = []
-        for r in reqs:
-            exc = None if r.pre_extended else errs[id(r)]
-            r.pre_extended = False
-            if exc is None:
-                ready.append(r)
+        """One decode step for ``reqs``.
+
+        Ordinary order: extend the cache, stage and launch the step, do host work for the next step while the device
+        runs, read the tokens.  Pipelined (``pipeline_decode``): before the tokens of this step are read, the NEXT
+        step is launched as well - its input tokens are gathered on the device from this step's choices - so the
+        device never waits for the host between steps; the step after this call then only has to be read.  A launch
+        made ahead is used by the requests that are still decoding when its turn comes (rows of requests that ended on
+        a stop token in the meantime are ignored; the slot they wrote belongs to a sequence that no longer exists).
+        """
+        fly, self._inflight = self._inflight, None
+        rows: Optional[List[int]] = None
+        if fly is not None:
+            where = {id(r): i for i, r in enumerate(fly.requests)}
+            usable = all(id(r) in where and fly.generated[where[id(r)]] + 1 == r.num_generated
+                         and r.params.repetition_penalty == 1.0 for r in reqs)
+            if usable:
+                rows = [where[id(r)] for r in reqs]
+                ready, pending = list(reqs), fly.pending
             else:
-                self._fail(r, exc, res)
-        if not ready:
-            return
-        pen = None
-        if any(r.params.repetition_penalty != 1.0 for r in ready):
-            pen = [(r.params.repetition_penalty, r.past_tokens) for r in ready]
+                self._inflight = fly
+                self._drop_inflight()
+        if rows is None:
+            # a request that was extended ahead of time (while the previous step ran on the device) is ready as it is
+            todo = [r for r in reqs if not r.pre_extended]
+            errs = dict(zip((id(r) for r in todo), self._cache.extend_batch([r.seq_id for r in todo])))
+            ready = []
+            for r in reqs:
+                exc = None if r.pre_extended else errs[id(r)]
+                r.pre_extended = False
+                if exc is None:
+                    ready.append(r)
+                else:
+                    self._fail(r, exc, res)
+            if not ready:
+                return
+            pen = None
+            if any(r.params.repetition_penalty != 1.0 for r in ready):
+                pen = [(r.params.repetition_penalty, r.past_tokens) for r in ready]
+            try:
+                pending = self._runner.decode([r.seq_id for r in ready], [r.output_tokens[-1] for r in ready],
+                                              sampling=[_sampling_row(r) for r in ready],
+                                              adapters=[self._adapter_slot(r) for r in ready]
+                                              if self._lora is not None else None, penalties=pen, defer=True)
+            except Exception as exc:
+                for r in ready:
+                    self._fail(r, exc, res)
+                return
+            rows = list(range(len(ready)))
         try:
-            pending = self._runner.decode([r.seq_id for r in ready], [r.output_tokens[-1] for r in ready],
-                                          sampling=[_sampling_row(r) for r in ready],
-                                          adapters=[self._adapter_slot(r) for r in ready] if self._lora is not None
-                                          else None, penalties=pen, defer=True)
             # host work that overlaps the device step: the cache slot of the token after this one, for every
             # request that cannot end on this token by length (a stop token frees the sequence, slot included)
             ahead = [r for r in ready if r.num_generated + 1 < r.params.max_tokens
                      and r.params.timeout_ms is None]
             for r, exc in zip(ahead, self._cache.extend_batch([r.seq_id for r in ahead])):
                 r.pre_extended = exc is None
-            toks = pending()
+            if self._pipeline:
+                self._launch_ahead(ready, rows)
+            toks_all = pending()
+            toks = [toks_all[i] for i in rows]
         except Exception as exc:
+            self._inflight = None
             for r in ready:
                 self._fail(r, exc, res)
             return
@@ -189,6 +238,50 @@ class BatchRunner:
             self._sched.on_token_generated(r, int(tok))
         res.num_decode_tokens += len(ready)
         res.tokens_generated += len(ready)
+
+    def _launch_ahead(self, ready: List[InferenceRequest], rows: List[int]) -> None:
+        """Launches the decode step AFTER the one in progress for the requests that are sure to need it, unless
+        something may rearrange the batch before its turn (work waiting for prefill, penalties that need the token
+        history on the host, speculative decoding, a request without a slot for it)."""
+        if self._spec is not None and self._spec.k > 0:
+            return
+        if (self._sched.num_waiting > 0 or self._sched.num_prefilling > 0
+                or any(r.state != RequestState.DECODING for r in ready)):
+            return
+        nxt = [(r, row) for r, row in zip(ready, rows) if r.pre_extended]
+        if not nxt or any(r.params.repetition_penalty != 1.0 for r, _ in nxt):
+            return
+        reqs = [r for r, _ in nxt]
+        for r in reqs:
+            r.pre_extended = False                     # the slot is used by the launch below
+        try:
+            pending = self._runner.decode([r.seq_id for r in reqs], None,
+                                          sampling=[_sampling_row(r, ahead=1) for r in reqs],
+                                          adapters=[self._adapter_slot(r) for r in reqs]
+                                          if self._lora is not None else None, defer=True,
+                                          ids_rows=[row for _, row in nxt])
+        except Exception:
+            for r in reqs:
+                r.pre_extended = True
+            raise
+        self._inflight = _InFlight(reqs, [r.num_generated for r in reqs], pending)
+        self.ahead_launches += 1
+
+    def _drop_inflight(self) -> None:
+        """Waits for a step that was launched ahead and discards what it chose; the requests keep the cache slot it
+        used (the step that replaces it writes the same values there)."""
+        fly, self._inflight = self._inflight, None
+        if fly is None:
+            return
+        self.ahead_dropped += 1
+        try:
+            fly.pending()
+        except Exception:
+            pass
+        for r, g in zip(fly.requests, fly.generated):
+            if not r.is_finished and r.state == RequestState.DECODING and r.seq_id is not None \
+                    and self._cache.has_sequence(r.seq_id):
+                r.pre_extended = True
 
     def _run_speculative(self, reqs: List[InferenceRequest], res: StepResult) -> None:
         greedy = [r for r in reqs if r.params.greedy and r.params.repetition_penalty == 1.0]
