@@ -35,7 +35,7 @@ class EngineConfig:
     speculative_mode: str = "ngram"       # "ngram" | "self"
     use_cuda_graphs: bool = True
     # pipelined decode: launch step n+1 (its input tokens gathered on the device) before step n has been read, so the
-    # device does not wait for the host between steps; None = take ZSE_PIPELINE_DECODE (default off)
+    # device does not wait for the host between steps; None = take ZSE_PIPELINE_DECODE (default on)
     pipeline_decode: Optional[bool] = None
     comm_backend: str = "fused"           # tensor-parallel collectives: "fused" (in-kernel NVLink) | "nccl"
     headroom_ratio: float = 0.5

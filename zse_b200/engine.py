@@ -141,7 +141,7 @@ class ZStreamerEngine:
         self._spec_runner = spec
         pipeline = cfg.pipeline_decode
         if pipeline is None:
-            pipeline = os.environ.get("ZSE_PIPELINE_DECODE", "0") not in ("0", "", "false")
+            pipeline = os.environ.get("ZSE_PIPELINE_DECODE", "1").lower() not in ("0", "", "false", "off", "no")
         self._batch_runner = BatchRunner(self._runner, self._scheduler, spec_runner=spec,
                                          lora_manager=self._lora_manager, pipeline_decode=pipeline)
         self.init_times["runtime"] = time.monotonic() - t2
