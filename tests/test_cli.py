@@ -1,0 +1,141 @@
+"""The ``zse`` command line (same commands as zse-engine/zse_engine/cli.py:218-300: serve, convert, info, version,
+warm, keys; plus synth and bench-kernels), run as a subprocess the way a user does, and the HTTP server started by
+``zse serve`` in its mock mode and with a model on the CPU path."""
+import json
+import os
+import signal
+import socket
+import subprocess
+import sys
+import time
+import urllib.request
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def zse(*args, timeout=300, env=None):
+    e = dict(os.environ, PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    e.update(env or {})
+    return subprocess.run([sys.executable, "-m", "zse_b200", *map(str, args)], capture_output=True, text=True,
+                          timeout=timeout, env=e, cwd=ROOT)
+
+
+@pytest.fixture(scope="module")
+def tiny(tmp_path_factory):
+    p = str(tmp_path_factory.mktemp("cli") / "tiny.zse")
+    r = zse("synth", "tiny", p, "--seed", "4")
+    assert r.returncode == 0 and "wrote" in r.stdout, r.stderr
+    return p
+
+
+def test_version_info_warm(tiny):
+    r = zse("version")
+    assert r.returncode == 0 and "zse_b200" in r.stdout and "torch" in r.stdout
+    r = zse("info", tiny)
+    assert r.returncode == 0 and "llama" in r.stdout and "layers" in r.stdout.lower(), r.stdout + r.stderr
+    r = zse("warm", tiny)
+    assert r.returncode == 0 and "warmed" in r.stdout
+    assert zse("warm", tiny + ".missing").returncode == 1
+    r = zse()
+    assert r.returncode == 0 and "serve" in r.stdout               # no command: help
+
+
+def test_keys_create_list_revoke(tmp_path):
+    db = str(tmp_path / "k.db")
+    r = zse("keys", "--db-path", db, "create", "--name", "alice", "--rpm", "7")
+    assert r.returncode == 0 and "sk-zse-" in r.stdout
+    r = zse("keys", "--db-path", db, "list")
+    assert "alice" in r.stdout and "rpm=7" in r.stdout and "active" in r.stdout
+    key_id = r.stdout.split()[0]
+    assert zse("keys", "--db-path", db, "revoke", key_id).returncode == 0
+    assert "revoked" in zse("keys", "--db-path", db, "list").stdout
+    assert zse("keys", "--db-path", db, "revoke", "999").returncode == 1
+
+
+def test_convert_command_and_module_entry(tmp_path):
+    from zse_b200.format.convert import write_safetensors
+    from zse_b200.format.loader import ZSELoader
+    d = tmp_path / "hf"
+    d.mkdir()
+    cfg = {"architectures": ["LlamaForCausalLM"], "model_type": "llama", "hidden_size": 128, "intermediate_size": 256,
+           "num_hidden_layers": 1, "num_attention_heads": 4, "num_key_value_heads": 2, "vocab_size": 200,
+           "max_position_embeddings": 256, "rms_norm_eps": 1e-5, "tie_word_embeddings": False}
+    (d / "config.json").write_text(json.dumps(cfg))
+    rng = np.random.default_rng(0)
+    t = {"model.embed_tokens.weight": rng.standard_normal((200, 128)), "model.norm.weight": np.ones(128),
+         "lm_head.weight": rng.standard_normal((200, 128)), "model.layers.0.input_layernorm.weight": np.ones(128),
+         "model.layers.0.post_attention_layernorm.weight": np.ones(128)}
+    for name, shape in (("self_attn.q_proj", (128, 128)), ("self_attn.k_proj", (64, 128)),
+                        ("self_attn.v_proj", (64, 128)), ("self_attn.o_proj", (128, 128)),
+                        ("mlp.gate_proj", (256, 128)), ("mlp.up_proj", (256, 128)), ("mlp.down_proj", (128, 256))):
+        t[f"model.layers.0.{name}.weight"] = rng.standard_normal(shape) * 0.05
+    write_safetensors(str(d / "model.safetensors"), {k: v.astype(np.float32) for k, v in t.items()})
+    out = str(tmp_path / "m.zse")
+    r = zse("convert", d, out, "--quant", "int8", "--no-tokenizer", "-q")
+    assert r.returncode == 0, r.stderr
+    with ZSELoader(out) as l:
+        assert l.config.arch == "llama" and l.weight_index.find("layers.0.mlp.up_proj.weight").dtype == "int8"
+    out2 = str(tmp_path / "m2.zse")
+    e = dict(os.environ, PYTHONPATH=ROOT)
+    r = subprocess.run([sys.executable, "-m", "zse_b200.format", str(d), out2, "--quant", "fp16", "--no-tokenizer"],
+                       capture_output=True, text=True, env=e, cwd=ROOT, timeout=300)
+    assert r.returncode == 0 and os.path.getsize(out2) > os.path.getsize(out), r.stderr
+    assert zse("convert", tmp_path / "nowhere", out).returncode != 0
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _get(url, data=None, headers=None, timeout=60):
+    req = urllib.request.Request(url, data=None if data is None else json.dumps(data).encode(),
+                                 headers={"Content-Type": "application/json", **(headers or {})})
+    with urllib.request.urlopen(req, timeout=timeout) as r:
+        return json.loads(r.read())
+
+
+def _serve(args, port):
+    e = dict(os.environ, PYTHONPATH=ROOT)
+    proc = subprocess.Popen([sys.executable, "-m", "zse_b200", "serve", *args, "--port", str(port), "--host",
+                             "127.0.0.1", "-q"], env=e, cwd=ROOT, stdout=subprocess.PIPE, stderr=subprocess.STDOUT)
+    for _ in range(600):
+        try:
+            return proc, _get(f"http://127.0.0.1:{port}/health", timeout=2)
+        except Exception:
+            if proc.poll() is not None:
+                raise AssertionError(proc.stdout.read().decode())
+            time.sleep(0.2)
+    proc.kill()
+    raise AssertionError("server did not come up")
+
+
+@pytest.mark.timeout(300)
+def test_serve_mock_mode_and_cpu_model(tiny, tmp_path):
+    port = _free_port()
+    proc, health = _serve(["--db-path", str(tmp_path / "a.db"), "--admin-key", "adm"], port)
+    try:
+        assert health["engine"] == "mock"
+        out = _get(f"http://127.0.0.1:{port}/v1/chat/completions",
+                   {"model": "zse-model", "messages": [{"role": "user", "content": "ping"}]})
+        assert out["choices"][0]["message"]["role"] == "assistant"
+    finally:
+        proc.send_signal(signal.SIGTERM)
+        proc.wait(30)
+    port = _free_port()
+    proc, health = _serve([tiny, "--cpu", "--db-path", str(tmp_path / "b.db"), "--admin-key", "adm",
+                           "--max-seq-len", "256", "--max-batch-seqs", "4"], port)
+    try:
+        assert health["engine"] == "running"
+        out = _get(f"http://127.0.0.1:{port}/v1/completions", {"model": "zse-model", "prompt": "hello", "max_tokens": 5,
+                                                                 "temperature": 0})
+        assert out["usage"]["completion_tokens"] >= 1 and out["choices"][0]["finish_reason"] in ("length", "stop")
+        stats = _get(f"http://127.0.0.1:{port}/v1/admin/stats", headers={"Authorization": "Bearer adm"})
+        assert stats["engine"]["total_requests"] >= 1
+    finally:
+        proc.send_signal(signal.SIGTERM)
+        proc.wait(30)
