@@ -195,3 +195,21 @@ def test_single_request_engine_text_api(model_path):
     st = eng.stats()
     assert st.generated_tokens > 0 and st.prompt_tokens > 0
     eng.destroy()
+
+
+def test_client_callbacks_that_raise_do_not_stop_the_engine(model_path, oracle):
+    eng = ZStreamerEngine(model_path, config=_cfg())
+    p = _prompts(eng.model_config.vocab_size, 2, seed=21)
+
+    def bad_token(tok):
+        raise RuntimeError("client bug")
+
+    def bad_finish(out):
+        raise RuntimeError("client bug")
+
+    a = eng.add_request_tokens(p[0], max_tokens=6, temperature=0.0, stop_tokens=[], on_token=bad_token)
+    b = eng.add_request_tokens(p[1], max_tokens=6, temperature=0.0, stop_tokens=[], on_finish=bad_finish)
+    eng.run_until_done()
+    assert eng.get_result(a).output_tokens == oracle.greedy(p[0], 6)
+    assert eng.get_result(b).output_tokens == oracle.greedy(p[1], 6)
+    eng.destroy()

@@ -126,3 +126,76 @@ def test_speculative_decoding_is_left_alone(model_path, oracle):
     assert eng.get_result(rid).output_tokens == oracle.greedy(p, 12)
     assert _launched_ahead(eng) == (0, 0)
     eng.destroy()
+
+
+@pytest.mark.timeout(300)
+def test_serving_loop_under_concurrent_clients(model_path, oracle):
+    """The serving loop in its own thread while client threads submit, stream and cancel at random moments: every
+    finished request must carry exactly the greedy tokens that the engine gives the same prompt on its own in the
+    ordinary order (cut at its stop token), every token must have been streamed once and in order, and the cache must
+    be empty afterwards."""
+    import threading
+    import time
+    solo = ZStreamerEngine(model_path, config=_cfg(pipeline_decode=False))
+
+    def alone(prompt, n):
+        rid = solo.add_request_tokens(prompt, max_tokens=n, temperature=0.0, stop_tokens=[])
+        solo.run_until_done()
+        return solo.get_result(rid).output_tokens
+
+    eng = ZStreamerEngine(model_path, config=_cfg(max_batch_seqs=6, prefill_chunk_size=16, max_batch_tokens=64))
+    rng = random.Random(99)
+    jobs = []
+    for i in range(28):
+        p = _prompts(1, lo=3, hi=45, seed=100 + i)[0]
+        n = rng.randint(2, 18)
+        want = alone(p, n)
+        stop = [want[rng.randrange(len(want))]] if rng.random() < 0.4 else []
+        jobs.append({"prompt": p, "n": n, "want": want, "stop": stop, "cancel": rng.random() < 0.15,
+                     "streamed": [], "done": threading.Event(), "out": None})
+    solo.destroy()
+    loop = threading.Thread(target=eng.run, daemon=True)
+    loop.start()
+
+    def client(batch):
+        for j in batch:
+            def on_token(tok, j=j):
+                j["streamed"].append(tok)
+
+            def on_finish(out, j=j):
+                j["out"] = out
+                j["done"].set()
+
+            rid = None
+            while rid is None:                      # queue full: try again
+                rid = eng.add_request_tokens(j["prompt"], max_tokens=j["n"], temperature=0.0, stop_tokens=j["stop"],
+                                             on_token=on_token, on_finish=on_finish)
+                if rid is None:
+                    time.sleep(0.002)
+            if j["cancel"]:
+                time.sleep(rng.random() * 0.01)
+                eng.cancel_request(rid)
+            time.sleep(rng.random() * 0.004)
+
+    clients = [threading.Thread(target=client, args=(jobs[k::4],)) for k in range(4)]
+    for t in clients:
+        t.start()
+    for t in clients:
+        t.join(120)
+    for j in jobs:
+        assert j["done"].wait(120), "a request never finished"
+    eng.stop()
+    loop.join(30)
+    for j in jobs:
+        out, want = j["out"], j["want"]
+        if out.finish_reason == FinishReason.CANCELLED:
+            assert j["cancel"] and out.output_tokens == want[:len(out.output_tokens)]
+            continue
+        cut = want.index(j["stop"][0]) + 1 if j["stop"] else len(want)
+        assert out.output_tokens == want[:cut], (out.output_tokens, want[:cut], j["stop"])
+        assert out.finish_reason == (FinishReason.STOP if j["stop"] else FinishReason.LENGTH)
+        assert j["streamed"] == out.output_tokens
+    assert eng._batch_runner.ahead_launches > 0
+    eng.step()
+    assert eng.kv_cache.num_sequences == 0 and eng.kv_cache.num_free_blocks == eng.kv_cache.num_total_blocks
+    eng.destroy()

@@ -63,6 +63,7 @@ class InferenceRequest:
     finish_time: Optional[float] = None
     seq_id: Optional[int] = None
     on_token: Optional[Callable[[int], None]] = None
+    callback_error: Optional[str] = None
     on_finish: Optional[Callable[["RequestOutput"], None]] = None
     past_tokens: Dict[int, int] = field(default_factory=dict)
     error: Optional[str] = None
@@ -145,7 +146,11 @@ class InferenceRequest:
         if self.first_token_time is None:
             self.first_token_time = time.monotonic()
         if self.on_token is not None:
-            self.on_token(token_id)
+            try:
+                self.on_token(token_id)
+            except Exception as exc:     # a client's streaming callback must not take the serving loop down
+                self.callback_error = f"on_token raised {exc!r}"
+                self.on_token = None     # do not call it again
 
     def should_stop(self) -> Optional[FinishReason]:
         if self.num_generated >= self.params.max_tokens:
