@@ -201,3 +201,32 @@ def test_rag_routes_and_rag_flag(server):
     assert http(server, "DELETE", f"/v1/rag/document/{rep['doc_id']}")[0] == 200
     assert http(server, "DELETE", f"/v1/rag/document/{rep['doc_id']}")[0] == 404
     assert http(server, "POST", "/v1/rag/backfill_dense", {})[0] == 403
+
+
+def test_client_that_goes_away_mid_stream_is_cancelled(server):
+    """A streaming client closes its socket after the first chunks: the request must be cancelled (not generated to
+    the end for nobody) and its cache blocks returned."""
+    import socket
+    eng = server._engine
+    before = eng.stats().total_tokens_generated
+    body = json.dumps({"model": "tiny", "prompt": "go on for a long time", "max_tokens": 230, "stream": True,
+                       "temperature": 0}).encode()
+    req = (f"POST /v1/completions HTTP/1.1\r\nHost: x\r\nContent-Type: application/json\r\n"
+           f"Content-Length: {len(body)}\r\n\r\n").encode() + body
+    s = socket.create_connection(("127.0.0.1", server.port), timeout=30)
+    s.sendall(req)
+    got = b""
+    while got.count(b"data: ") < 2:
+        got += s.recv(4096)
+    s.setsockopt(socket.SOL_SOCKET, socket.SO_LINGER, __import__("struct").pack("ii", 1, 0))   # close with a reset
+    s.close()
+    deadline = time.time() + 20
+    while time.time() < deadline:
+        if eng.scheduler.num_active == 0 and eng.kv_cache.num_sequences == 0:
+            break
+        time.sleep(0.02)
+    assert eng.scheduler.num_active == 0 and eng.kv_cache.num_sequences == 0
+    produced = eng.stats().total_tokens_generated - before
+    assert produced < 200, produced            # it did not run to its 230 tokens
+    status, _, health = http(server, "GET", "/health")
+    assert status == 200 and health["status"] == "ok"

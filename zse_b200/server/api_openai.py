@@ -183,39 +183,46 @@ class OpenAIAPI:
         async def gen():
             ids: List[int] = []
             sent = ""
-            if chat:
-                yield chat_chunk(completion_id, model, role="assistant")
-            deadline = time.monotonic() + REQUEST_TIMEOUT_S
-            while True:
-                try:
-                    kind, val = await asyncio.wait_for(q.get(), max(0.1, deadline - time.monotonic()))
-                except asyncio.TimeoutError:
+            finished = False
+            try:
+                if chat:
+                    yield chat_chunk(completion_id, model, role="assistant")
+                deadline = time.monotonic() + REQUEST_TIMEOUT_S
+                while True:
+                    try:
+                        kind, val = await asyncio.wait_for(q.get(), max(0.1, deadline - time.monotonic()))
+                    except asyncio.TimeoutError:
+                        break
+                    if kind == "tok":
+                        if val in stops:
+                            continue
+                        ids.append(val)
+                        text = self._decode(ids)
+                        if len(text) > len(sent) and not text.endswith("\ufffd"):
+                            piece, sent = text[len(sent):], text
+                            yield chat_chunk(completion_id, model, content=piece) if chat else \
+                                completion_chunk(completion_id, model, piece)
+                    else:
+                        out = val
+                        finished = True
+                        self._record(request, model, params.get("lora_id"), rid, len(out.prompt_tokens),
+                                     len(out.output_tokens), t0)
+                        # text held back while it ended inside a multi-byte character goes out with the last chunk
+                        text = self._decode(ids)
+                        if len(text) > len(sent):
+                            piece, sent = text[len(sent):], text
+                            yield chat_chunk(completion_id, model, content=piece) if chat else \
+                                completion_chunk(completion_id, model, piece)
+                        fin = out.finish_reason.value
+                        yield chat_chunk(completion_id, model, finish_reason=fin) if chat else \
+                            completion_chunk(completion_id, model, "", fin)
+                        break
+                yield SSE_DONE
+            finally:
+                # the time-out above, or the client went away in the middle of the stream (the connection handler
+                # closes this generator): stop generating for nobody
+                if not finished:
                     self._engine.cancel_request(rid)
-                    break
-                if kind == "tok":
-                    if val in stops:
-                        continue
-                    ids.append(val)
-                    text = self._decode(ids)
-                    if len(text) > len(sent) and not text.endswith("�"):
-                        piece, sent = text[len(sent):], text
-                        yield chat_chunk(completion_id, model, content=piece) if chat else \
-                            completion_chunk(completion_id, model, piece)
-                else:
-                    out = val
-                    self._record(request, model, params.get("lora_id"), rid, len(out.prompt_tokens),
-                                 len(out.output_tokens), t0)
-                    # text held back while it ended inside a multi-byte character goes out with the last chunk
-                    text = self._decode(ids)
-                    if len(text) > len(sent):
-                        piece, sent = text[len(sent):], text
-                        yield chat_chunk(completion_id, model, content=piece) if chat else \
-                            completion_chunk(completion_id, model, piece)
-                    fin = out.finish_reason.value
-                    yield chat_chunk(completion_id, model, finish_reason=fin) if chat else \
-                        completion_chunk(completion_id, model, "", fin)
-                    break
-            yield SSE_DONE
 
         return Response.sse(gen())
 

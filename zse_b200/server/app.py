@@ -138,8 +138,17 @@ class ZSEServer:
                         async for chunk in resp.stream:
                             writer.write(chunk)
                             await writer.drain()
+                            if writer.is_closing():
+                                break
                     except (ConnectionError, asyncio.CancelledError):
                         pass
+                    finally:
+                        closer = getattr(resp.stream, "aclose", None)
+                        if closer is not None:      # lets the stream's clean-up run (cancels an abandoned request)
+                            try:
+                                await closer()
+                            except Exception:
+                                pass
                     break
                 writer.write(format_http_response(resp, keep))
                 await writer.drain()
