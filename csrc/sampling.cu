@@ -229,7 +229,10 @@ sample_kernel(const __half* __restrict__ logits, int ld, int* __restrict__ out, 
   __syncthreads();
   const float excl = scan[tid >> 5] + incl - mine;
   const float total = sh_total;
-  const uint64_t r = splitmix64((seeds ? seeds[rowi] : 0ull) ^ splitmix64(step * 0x2545F4914F6CDD1Dull + rowi));
+  // a row that brings its own seed draws from that seed alone: the token does not depend on which row of the batch
+  // the request happens to sit in; rows without seeds are told apart by their index
+  const uint64_t r = seeds ? splitmix64(seeds[rowi] ^ splitmix64(step * 0x2545F4914F6CDD1Dull))
+                           : splitmix64(splitmix64(step * 0x2545F4914F6CDD1Dull + rowi));
   const float u = float(r >> 40) * (1.0f / 16777216.0f) * total;
   if (mine > 0.f && u >= excl && u < excl + mine) {
     float run = excl;

@@ -139,7 +139,8 @@ class TorchOps:
                 out[r] = int(logits[r].float().argmax())
                 continue
             p = ref.filtered_probs(logits[r], t, int(top_k[r]), float(top_p[r]))
-            g = torch.Generator(device="cpu").manual_seed((int(seeds[r]) * 1000003 + int(step) * 7919 + r) % (2 ** 63))
+            # the row's own seed and nothing about its place in the batch (same rule as the CUDA kernel)
+            g = torch.Generator(device="cpu").manual_seed((int(seeds[r]) * 1000003 + int(step) * 7919) % (2 ** 63))
             out[r] = int(torch.multinomial(p.cpu(), 1, generator=g))
 
     def apply_repetition_penalty(self, logits, rows, tokens, counts, n, penalty):

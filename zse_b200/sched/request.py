@@ -153,10 +153,12 @@ class InferenceRequest:
                 self.on_token = None     # do not call it again
 
     def should_stop(self) -> Optional[FinishReason]:
-        if self.num_generated >= self.params.max_tokens:
-            return FinishReason.LENGTH
+        # a stop token that arrives as the last allowed token is still a natural end ("stop", not "length"; the
+        # reference tests the length first, zse-engine/zse_engine/zstreamer/request.py:172-181)
         if self.output_tokens and self.params.stop_tokens and self.output_tokens[-1] in self.params.stop_tokens:
             return FinishReason.STOP
+        if self.num_generated >= self.params.max_tokens:
+            return FinishReason.LENGTH
         if self.params.timeout_ms is not None and self.wait_time_ms > self.params.timeout_ms:
             return FinishReason.LENGTH
         return None
