@@ -1,0 +1,125 @@
+"""The byte-level BPE tokenizer against the HuggingFace ``tokenizers`` library on the same vocabulary: a small BPE is
+trained here (offline), written as ``tokenizer.json``, imported with ``BPETokenizer.from_hf_dir`` and both must
+produce the same ids for arbitrary text - pre-tokeniser regex, merge order, byte fallback and added tokens included
+(the reference imports the same files, zse-engine/zse_engine/format/tokenizer.py:25-436)."""
+import json
+import random
+
+import pytest
+
+tokenizers = pytest.importorskip("tokenizers")
+
+from zse_b200.format.tokenizer import BPETokenizer
+
+CORPUS = [
+    "The quick brown fox jumps over the lazy dog. " * 3,
+    "def f(x):\n    return x ** 2 + 3 * x  # comment\n" * 2,
+    "Tensor cores multiply 128x128 tiles; HBM3e streams the weights, isn't it?",
+    "naïve café déjà vu — Übergröße, 数学 と 物理, русский текст, emoji 🙂🚀",
+    "   leading spaces\tand\ttabs\n\nnew paragraphs  and  double  spaces ",
+    "numbers 12345 67 890 3.14159 2026-11-25 1e-6 0xFF",
+    "they're we'll I'm you've he'd it's o'clock",
+]
+
+
+@pytest.fixture(scope="module")
+def pair(tmp_path_factory):
+    from tokenizers import Tokenizer, decoders, models, pre_tokenizers, trainers
+    tok = Tokenizer(models.BPE())
+    tok.pre_tokenizer = pre_tokenizers.ByteLevel(add_prefix_space=False, use_regex=True)
+    tok.decoder = decoders.ByteLevel()
+    trainer = trainers.BpeTrainer(vocab_size=600, special_tokens=["<|endoftext|>", "<|im_start|>", "<|im_end|>"],
+                                  initial_alphabet=pre_tokenizers.ByteLevel.alphabet(), show_progress=False)
+    tok.train_from_iterator(CORPUS * 4, trainer)
+    d = tmp_path_factory.mktemp("tok")
+    tok.save(str(d / "tokenizer.json"))
+    (d / "tokenizer_config.json").write_text(json.dumps({"eos_token": "<|endoftext|>", "bos_token": None,
+                                                         "pad_token": "<|endoftext|>"}))
+    return tok, BPETokenizer.from_hf_dir(str(d))
+
+
+def _random_text(rng):
+    pools = ["abcdefghijklmnopqrstuvwxyz", "ABCDEFGHIJ", "0123456789", " \t\n", ".,;:!?'\"()[]{}<>|/\\-_=+*&^%$#@~`",
+             "àéîõüñçß", "数学物理日本語", "русский", "🙂🚀🔥", "'s't're've'll'd'm"]
+    out = []
+    for _ in range(rng.randint(1, 40)):
+        pool = rng.choice(pools)
+        out.append("".join(rng.choice(pool) for _ in range(rng.randint(1, 6))))
+        if rng.random() < 0.5:
+            out.append(" " * rng.randint(1, 3))
+    return "".join(out)
+
+
+def test_same_ids_as_the_tokenizers_library(pair):
+    hf, ours = pair
+    rng = random.Random(0)
+    texts = CORPUS + [_random_text(rng) for _ in range(300)] + ["", " ", "\n", "a", "  a  ", "'", "''ll"]
+    for text in texts:
+        want = hf.encode(text, add_special_tokens=False).ids
+        got = ours.encode(text, add_bos=False)
+        assert got == want, (text, got, want)
+        assert ours.decode(got) == text
+
+
+def test_added_tokens_split_the_text(pair):
+    hf, ours = pair
+    text = "<|im_start|>user\nhello<|im_end|>\n<|im_start|>assistant\n<|endoftext|>tail <|im_end"
+    want = hf.encode(text, add_special_tokens=False).ids
+    got = ours.encode(text, add_bos=False)
+    assert got == want
+    assert ours.decode(got, skip_special=False) == text
+    assert "<|im_start|>" not in ours.decode(got, skip_special=True)
+
+
+def test_serialised_tokenizer_behaves_the_same(pair):
+    _, ours = pair
+    again = BPETokenizer.deserialize(ours.serialize())
+    rng = random.Random(1)
+    for _ in range(50):
+        t = _random_text(rng)
+        assert again.encode(t, add_bos=False) == ours.encode(t, add_bos=False)
+
+
+QWEN2_SPLIT = (r"(?i:'s|'t|'re|'ve|'m|'ll|'d)|[^\r\n\p{L}\p{N}]?\p{L}+|\p{N}| ?[^\s\p{L}\p{N}]+[\r\n]*|\s*[\r\n]+"
+               r"|\s+(?!\S)|\s+")
+
+
+@pytest.fixture(scope="module")
+def qwen_pair(tmp_path_factory):
+    """A tokenizer with the split pattern of Qwen2 (single digits, case-insensitive contractions, newlines kept with
+    the symbols before them) instead of GPT-2's."""
+    from tokenizers import Regex, Tokenizer, decoders, models, pre_tokenizers, trainers
+    tok = Tokenizer(models.BPE())
+    tok.pre_tokenizer = pre_tokenizers.Sequence([
+        pre_tokenizers.Split(Regex(QWEN2_SPLIT), behavior="isolated", invert=False),
+        pre_tokenizers.ByteLevel(add_prefix_space=False, use_regex=False)])
+    tok.decoder = decoders.ByteLevel()
+    trainer = trainers.BpeTrainer(vocab_size=700, special_tokens=["<|endoftext|>", "<|im_start|>", "<|im_end|>"],
+                                  initial_alphabet=pre_tokenizers.ByteLevel.alphabet(), show_progress=False)
+    tok.train_from_iterator((CORPUS + ["abc123 x_y_z 2026-11-25 I'M HERE\r\n\r\nok!!\n", "a1b2c3 __init__ 007"]) * 4,
+                            trainer)
+    d = tmp_path_factory.mktemp("qtok")
+    tok.save(str(d / "tokenizer.json"))
+    return tok, BPETokenizer.from_hf_dir(str(d))
+
+
+def test_model_specific_split_pattern_is_honoured(qwen_pair):
+    hf, ours = qwen_pair
+    assert ours.pretoken_pattern == QWEN2_SPLIT
+    rng = random.Random(3)
+    texts = CORPUS + ["abc123", "x_y_z __init__", "I'M HERE, we'LL go", "line\r\n\r\nnext!!\n\n", "12345 6789", "a1b2c3"] \
+        + [_random_text(rng) for _ in range(300)]
+    for text in texts:
+        want = hf.encode(text, add_special_tokens=False).ids
+        got = ours.encode(text, add_bos=False)
+        assert got == want, (text, got, want)
+        assert ours.decode(got) == text
+    again = BPETokenizer.deserialize(ours.serialize())
+    assert again.pretoken_pattern == QWEN2_SPLIT
+    assert again.encode("abc123 4567", add_bos=False) == hf.encode("abc123 4567", add_special_tokens=False).ids
+
+
+def test_gpt2_pattern_separates_letters_digits_and_underscores(pair):
+    hf, ours = pair
+    for text in ["abc123def", "snake_case_name", "x1_y2", "__dunder__ 99bottles", "naïve123café"]:
+        assert ours.encode(text, add_bos=False) == hf.encode(text, add_special_tokens=False).ids, text

@@ -33,7 +33,43 @@ def _byte_table() -> Dict[int, str]:
 
 BYTE_ENCODER = _byte_table()
 BYTE_DECODER = {c: b for b, c in BYTE_ENCODER.items()}
-_PRETOKEN = re.compile(r"""'s|'t|'re|'ve|'m|'ll|'d| ?\w+| ?\d+| ?[^\s\w]+|\s+(?!\S)|\s+""")
+try:                                   # Unicode classes (\p{L}, \p{N}) as the pre-tokeniser patterns of real models use
+    import regex as _re_u
+except ImportError:                    # pragma: no cover - the plain module approximates them with \w / \d
+    _re_u = None
+
+# GPT-2's pattern: contractions, letters, numbers, other symbols (each with an optional leading space), whitespace
+GPT2_PATTERN = r"""'s|'t|'re|'ve|'m|'ll|'d| ?\p{L}+| ?\p{N}+| ?[^\s\p{L}\p{N}]+|\s+(?!\S)|\s+"""
+_PRETOKEN = (_re_u.compile(GPT2_PATTERN) if _re_u is not None else
+             re.compile(r"""'s|'t|'re|'ve|'m|'ll|'d| ?[^\W\d_]+| ?\d+| ?[^\s\w]+|_+|\s+(?!\S)|\s+"""))
+
+
+def _compile_pretoken(pattern: Optional[str]):
+    """The model's own split pattern (a ``Split`` pre-tokeniser of its tokenizer.json: Qwen2 splits numbers into
+    single digits, Llama-3 into groups of three, ...), or GPT-2's."""
+    if pattern and _re_u is not None:
+        try:
+            return _re_u.compile(pattern)
+        except Exception:
+            pass
+    return _PRETOKEN
+
+
+def _split_pattern_of(pre) -> Optional[str]:
+    """The regex of the first ``Split`` step of a tokenizer.json ``pre_tokenizer`` (possibly inside a ``Sequence``)."""
+    if not isinstance(pre, dict):
+        return None
+    if pre.get("type") == "Sequence":
+        for step in pre.get("pretokenizers", []):
+            got = _split_pattern_of(step)
+            if got:
+                return got
+        return None
+    if pre.get("type") == "Split" and str(pre.get("behavior", "")).lower() == "isolated" and not pre.get("invert"):
+        pat = pre.get("pattern", {})
+        if isinstance(pat, dict) and isinstance(pat.get("Regex"), str):
+            return pat["Regex"]
+    return None
 
 
 @dataclass
@@ -58,6 +94,7 @@ class BPETokenizer:
     merges: List[Tuple[str, str]] = field(default_factory=list)
     special_tokens: SpecialTokens = field(default_factory=SpecialTokens)
     added_tokens: Dict[str, int] = field(default_factory=dict)
+    pretoken_pattern: Optional[str] = None     # None: GPT-2's pattern
 
     def __post_init__(self):
         self._rebuild_caches()
@@ -67,6 +104,7 @@ class BPETokenizer:
         self._id_to_token.update({i: t for t, i in self.added_tokens.items()})
         self._ranks = {tuple(p): r for r, p in enumerate(self.merges)}
         self._cache: Dict[str, Tuple[str, ...]] = {}
+        self._pretoken = _compile_pretoken(self.pretoken_pattern)
         if self.added_tokens:
             alts = sorted(self.added_tokens, key=len, reverse=True)
             self._added_re: Optional[re.Pattern] = re.compile("(" + "|".join(re.escape(t) for t in alts) + ")")
@@ -105,7 +143,7 @@ class BPETokenizer:
 
     def _encode_chunk(self, text: str) -> List[int]:
         ids, vocab, unk, enc = [], self.vocab, self.special_tokens.unk_id, BYTE_ENCODER
-        for piece in _PRETOKEN.findall(text):
+        for piece in self._pretoken.findall(text):
             mapped = "".join(enc[b] for b in piece.encode("utf-8"))
             for sym in self._bpe(mapped):
                 ids.append(vocab.get(sym, unk))
@@ -156,16 +194,18 @@ class BPETokenizer:
 
     # ---- section payload -------------------------------------------------------------------
     def serialize(self) -> bytes:
-        return serializer.encode({"vocab": self.vocab, "merges": [list(m) for m in self.merges],
-                                  "special_tokens": self.special_tokens.to_dict(),
-                                  "added_tokens": self.added_tokens})
+        d = {"vocab": self.vocab, "merges": [list(m) for m in self.merges],
+             "special_tokens": self.special_tokens.to_dict(), "added_tokens": self.added_tokens}
+        if self.pretoken_pattern:          # an extra key: readers that do not know it keep GPT-2's pattern
+            d["pretoken_pattern"] = self.pretoken_pattern
+        return serializer.encode(d)
 
     @classmethod
     def deserialize(cls, data) -> "BPETokenizer":
         d = serializer.decode(data)
         return cls(vocab=d["vocab"], merges=[tuple(m) for m in d["merges"]],
                    special_tokens=SpecialTokens.from_dict(d.get("special_tokens", {})),
-                   added_tokens=d.get("added_tokens", {}))
+                   added_tokens=d.get("added_tokens", {}), pretoken_pattern=d.get("pretoken_pattern"))
 
     # ---- HuggingFace import ----------------------------------------------------------------
     @classmethod
@@ -196,9 +236,12 @@ class BPETokenizer:
                     special.pad_id = tid
                 elif "unk" in low:
                     special.unk_id = tid
-            if content not in vocab:
+            # every added token is matched as a whole before the BPE runs, also one that the model's own vocabulary
+            # lists as well (GPT-2's <|endoftext|>, Mistral's <s>): that is what the tokenizers library does
+            if content:
                 added[content] = tid
-        return cls(vocab=vocab, merges=merges, special_tokens=special, added_tokens=added)
+        return cls(vocab=vocab, merges=merges, special_tokens=special, added_tokens=added,
+                   pretoken_pattern=_split_pattern_of(data.get("pre_tokenizer")))
 
     @classmethod
     def from_hf_dir(cls, model_dir: str) -> "BPETokenizer":
