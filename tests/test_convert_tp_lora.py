@@ -214,3 +214,42 @@ def test_collectives_facade(tmp_path):
                               stderr=subprocess.STDOUT) for r in range(3)]
     outs = [p.communicate(timeout=240)[0].decode() for p in procs]
     assert all(p.returncode == 0 for p in procs), "\n".join(outs)
+
+
+def test_peft_adapter_import(tmp_path):
+    """adapter_config.json + adapter_model.safetensors (PEFT naming) -> .zse-lora with the same matrices."""
+    from zse_b200.format.convert import write_safetensors
+    from zse_b200.format.lora_convert import convert_peft_to_zse_lora
+    from zse_b200.format.lora_format import load_lora, module_shapes
+    d = tmp_path / "peft"
+    d.mkdir()
+    r, layers, H, kvd = 4, 2, 64, 32
+    (d / "adapter_config.json").write_text(json.dumps({"r": r, "lora_alpha": 8, "target_modules": ["q_proj", "v_proj"],
+                                                       "peft_type": "LORA"}))
+    rng = np.random.default_rng(0)
+    t = {}
+    for l in range(layers):
+        for mod, out in (("q_proj", H), ("v_proj", kvd)):
+            base = f"base_model.model.model.layers.{l}.self_attn.{mod}"
+            t[base + ".lora_A.weight"] = rng.standard_normal((r, H)).astype(np.float32)
+            t[base + ".lora_B.weight"] = rng.standard_normal((out, r)).astype(np.float32)
+    t["base_model.model.lm_head.lora_A.weight"] = np.zeros((r, H), np.float32)       # not a served projection
+    write_safetensors(str(d / "adapter_model.safetensors"), t)
+    out = str(tmp_path / "a.zse-lora")
+    info = convert_peft_to_zse_lora(str(d), out)
+    assert info["rank"] == r and info["alpha"] == 8.0 and info["targets"] == ["q_proj", "v_proj"]
+    assert info["num_layers"] == layers and len(info["skipped"]) == 1
+    shapes = module_shapes(H, 0, num_heads=4, num_kv_heads=2, head_dim=16)
+    adapter, data = load_lora(out, shapes)
+    assert adapter.rank == r and abs(adapter.scaling - 2.0) < 1e-6
+    a, b = data[(1, "v_proj")]
+    want_a = t["base_model.model.model.layers.1.self_attn.v_proj.lora_A.weight"].astype(np.float16)
+    want_b = t["base_model.model.model.layers.1.self_attn.v_proj.lora_B.weight"].astype(np.float16)
+    assert np.array_equal(np.frombuffer(a, np.float16).reshape(r, H), want_a)
+    assert np.array_equal(np.frombuffer(b, np.float16).reshape(kvd, r), want_b)
+    # a layer without one of the targets cannot be written
+    del t["base_model.model.model.layers.1.self_attn.q_proj.lora_B.weight"]
+    write_safetensors(str(d / "adapter_model.safetensors"), t)
+    with pytest.raises(ValueError):
+        convert_peft_to_zse_lora(str(d), out)
+    assert convert_peft_to_zse_lora(str(d), out, modules=["v_proj"])["targets"] == ["v_proj"]

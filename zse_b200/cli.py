@@ -62,6 +62,18 @@ def _cmd_convert(a) -> int:
     return convert_main(argv)
 
 
+def _cmd_convert_lora(a) -> int:
+    from .format.lora_convert import convert_peft_to_zse_lora
+    try:
+        info = convert_peft_to_zse_lora(a.adapter_dir, a.output, a.modules.split(",") if a.modules else None)
+    except (OSError, ValueError, KeyError) as exc:
+        print(f"error: {exc}", file=sys.stderr)
+        return 1
+    print(f"wrote {a.output}: rank {info['rank']}, alpha {info['alpha']:g}, {info['num_layers']} layers, targets "
+          f"{', '.join(info['targets'])}" + (f"; {len(info['skipped'])} tensors skipped" if info["skipped"] else ""))
+    return 0
+
+
 def _cmd_info(a) -> int:
     from .runtime.device import describe_devices
     print("zse_b200 device info")
@@ -180,6 +192,11 @@ def build_parser() -> argparse.ArgumentParser:
     c.add_argument("--no-tokenizer", action="store_true")
     c.add_argument("-q", "--quiet", action="store_true")
     c.set_defaults(fn=_cmd_convert)
+    cl = sub.add_parser("convert-lora", help="convert a HuggingFace PEFT LoRA adapter directory to .zse-lora")
+    cl.add_argument("adapter_dir")
+    cl.add_argument("output")
+    cl.add_argument("--modules", default="", help="comma separated projections to keep (default: all present)")
+    cl.set_defaults(fn=_cmd_convert_lora)
     i = sub.add_parser("info", help="GPUs and, optionally, a model file summary")
     i.add_argument("model", nargs="?", default=None)
     i.set_defaults(fn=_cmd_info)
