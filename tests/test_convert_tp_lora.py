@@ -253,3 +253,47 @@ def test_peft_adapter_import(tmp_path):
     with pytest.raises(ValueError):
         convert_peft_to_zse_lora(str(d), out)
     assert convert_peft_to_zse_lora(str(d), out, modules=["v_proj"])["targets"] == ["v_proj"]
+
+
+@pytest.mark.parametrize("quant", ["fp16", "int4"])
+def test_lora_on_every_projection_equals_merged_weights(tmp_path, quant):
+    """An adapter on all seven projections (the reference's set, model_runner.py:1000-1109): the engine's tokens must
+    be those of the fp32 oracle run on W + (alpha/r) B A."""
+    from zse_b200.format.lora_format import load_lora
+    from zse_b200.lora.weights import random_adapter_file
+    path = str(tmp_path / "m.zse")
+    cfg = synth.shape_config("tiny-aligned", quant)
+    synth.write_random_model(path, cfg, seed=6)
+    eng = ZStreamerEngine(path, config=EngineConfig(device="cpu", max_batch_seqs=4, max_seq_len=128, quiet=True))
+    targets = ["q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj"]
+    f = str(tmp_path / "all.zse-lora")
+    random_adapter_file(f, eng.model_config, rank=4, alpha=8.0, target_modules=targets, seed=3, std=0.08)
+    eng.lora_manager.load_adapter("all", f)
+    only_mlp = str(tmp_path / "mlp.zse-lora")
+    random_adapter_file(only_mlp, eng.model_config, rank=2, alpha=2.0, target_modules=["up_proj", "down_proj"], seed=4,
+                        std=0.08)
+    eng.lora_manager.load_adapter("mlp", only_mlp)
+
+    def merged_oracle(file):
+        orc = OracleModel(ZSELoader(path))
+        adapter, data = load_lora(file, eng.lora_manager.weight_shapes())
+        block = {"q_proj": "self_attn", "k_proj": "self_attn", "v_proj": "self_attn", "o_proj": "self_attn"}
+        for (layer, mod), (a, b) in data.items():
+            w = adapter.get_weight(layer, mod)
+            A = torch.from_numpy(np.frombuffer(a, np.float16).reshape(w.rank, w.in_features).astype(np.float32))
+            B = torch.from_numpy(np.frombuffer(b, np.float16).reshape(w.out_features, w.rank).astype(np.float32))
+            name = f"layers.{layer}.{block.get(mod, 'mlp')}.{mod}.weight"
+            orc.w[name] = orc.w[name] + adapter.scaling * (B @ A)
+        return orc
+
+    prompts = [[3, 1, 4, 1, 5, 9, 2, 6], [7, 7, 8, 100, 200, 300]]
+    ids = [eng.add_request_tokens(prompts[0], max_tokens=8, temperature=0.0, stop_tokens=[], lora_id="all"),
+           eng.add_request_tokens(prompts[1], max_tokens=8, temperature=0.0, stop_tokens=[], lora_id="mlp"),
+           eng.add_request_tokens(prompts[0], max_tokens=8, temperature=0.0, stop_tokens=[])]
+    eng.run_until_done()
+    got = [eng.get_result(i).output_tokens for i in ids]
+    assert got[0] == merged_oracle(f).greedy(prompts[0], 8)
+    assert got[1] == merged_oracle(only_mlp).greedy(prompts[1], 8)
+    assert got[2] == OracleModel(ZSELoader(path)).greedy(prompts[0], 8)
+    assert got[0] != got[2]
+    eng.destroy()

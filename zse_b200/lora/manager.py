@@ -3,9 +3,13 @@
 
 All loaded adapters of one rank share padded weight tables per (layer, module): ``A [slots, rank, in]`` and
 ``B [slots, out, rank]``; a request's adapter is a slot index carried per token, so a decode batch mixing adapters
-runs in one launch pair per projection (``ops.lora_apply``).  Supported targets are the column-parallel attention
-projections ``q_proj``, ``k_proj``, ``v_proj`` (applied on the fused QKV output before RoPE); under tensor
-parallelism ``A`` is replicated and ``B`` is row-sharded like the base weight.
+runs in one launch pair per projection (``ops.lora_apply``).  Targets, as in the reference
+(zse-engine/zse_engine/orchestrator/model_runner.py:1000-1109): ``q_proj``, ``k_proj``, ``v_proj`` (added to the fused
+QKV output before RoPE), ``o_proj`` and ``down_proj`` (their update is an fp16 addend of the fused residual + RMSNorm
+kernel that follows the projection), ``gate_proj`` and ``up_proj`` (the MLP then runs without the fused SwiGLU
+epilogue: projection, updates, activation).  Under tensor parallelism ``A`` is replicated and ``B`` is row-sharded like
+the base weight for the column-parallel targets; the row-parallel ones (``o_proj``, ``down_proj``) would need their
+update summed over the ranks and are accepted on one GPU only.
 """
 from __future__ import annotations
 
@@ -18,7 +22,10 @@ import torch
 from ..format.lora_format import load_lora, module_shapes
 from .weights import LoRAAdapter, LoRAWeight, LoRAWeightStore
 
-SUPPORTED_TARGETS = ("q_proj", "k_proj", "v_proj")
+QKV_TARGETS = ("q_proj", "k_proj", "v_proj")
+ROW_PARALLEL_TARGETS = ("o_proj", "down_proj")
+MLP_IN_TARGETS = ("gate_proj", "up_proj")
+SUPPORTED_TARGETS = QKV_TARGETS + ROW_PARALLEL_TARGETS + MLP_IN_TARGETS
 
 
 class LoRAManager:
@@ -37,8 +44,14 @@ class LoRAManager:
 
     # ---- geometry -----------------------------------------------------------------------------------------
     def _module_geometry(self, module: str):
-        """(in_features, full out_features, local row range, column offset inside the fused qkv output)."""
+        """(in_features, full out_features, local row range of B, column offset inside the fused qkv output)."""
         c, p = self._model.config, self._model.plan
+        if module == "o_proj":
+            return c.q_dim, c.hidden_size, (0, c.hidden_size), 0
+        if module == "down_proj":
+            return c.intermediate_size, c.hidden_size, (0, c.hidden_size), 0
+        if module in MLP_IN_TARGETS:
+            return c.hidden_size, c.intermediate_size, p.inter, 0
         if module == "q_proj":
             return c.hidden_size, c.q_dim, p.q_rows, 0
         if module == "k_proj":
@@ -71,6 +84,10 @@ class LoRAManager:
             raise ValueError(f"LoRA targets {unsupported} are not supported (supported: {SUPPORTED_TARGETS})")
         if rank > self._max_rank or rank % 2:
             raise ValueError(f"LoRA rank {rank} must be even and <= {self._max_rank}")
+        if self._model.plan.tp_size > 1 and any(t in ROW_PARALLEL_TARGETS for t in target_modules):
+            raise ValueError("LoRA on o_proj / down_proj needs a sum over the tensor-parallel ranks: one GPU only")
+        if type(self._model).__name__ != "DecoderModel":
+            raise ValueError("adapters are wired for the Llama / Mistral / Qwen2 / Phi-3 decoder only")
         with self._lock:
             if adapter_id in self._store:
                 raise ValueError(f"adapter '{adapter_id}' is already loaded")
@@ -156,10 +173,35 @@ class LoRAManager:
                 "table_bytes": sum(t.numel() * 2 for t in list(self._a.values()) + list(self._b.values()))}
 
     # ---- hot path -------------------------------------------------------------------------------------------
+    def has(self, layer: int, module: str) -> bool:
+        return (layer, module) in self._a
+
+    def _scratch(self, b, name: str, width: int) -> torch.Tensor:
+        """A [max_tokens, width] fp16 buffer that lives with the step buffers ``b`` (made on first use)."""
+        t = getattr(b, name, None)
+        if t is None or t.shape[1] != width:
+            t = torch.zeros(b.max_tokens, width, dtype=torch.float16, device=self._device)
+            setattr(b, name, t)
+        return t
+
+    def delta(self, layer: int, module: str, x: torch.Tensor, b, M: int) -> Optional[torch.Tensor]:
+        """fp16 ``[>= M, out]`` with the summed update of every resident adapter for ``module`` of ``layer`` applied
+        to ``x`` (rows of tokens without an adapter stay zero), or None when no adapter touches the module."""
+        key = (layer, module)
+        if key not in self._a:
+            return None
+        fin, _, rows, _ = self._module_geometry(module)
+        n_out = rows[1] - rows[0]
+        out = self._scratch(b, "lora_delta_" + ("h" if module in ROW_PARALLEL_TARGETS else module), n_out)
+        out[:M].zero_()
+        self._model.ops.lora_apply(x, self._a[key], self._b[key], b.adapter_ids, self._scales, out, M, fin, n_out,
+                                   self._rank, tmp=b.lora_tmp)
+        return out
+
     def apply_qkv(self, layer: int, b, M: int) -> None:
         """Adds every resident adapter's update to the fused QKV output of ``layer`` for the first ``M`` tokens."""
         ops = self._model.ops
-        for mod in SUPPORTED_TARGETS:
+        for mod in QKV_TARGETS:
             key = (layer, mod)
             if key not in self._a:
                 continue

@@ -238,11 +238,16 @@ class DecoderModel:
                            logits_rows or max_seqs, attn_splits)
 
     # ---- forward --------------------------------------------------------------------------------------
-    def _add_norm(self, b: StepBuffers, planes: int, weight: torch.Tensor, M: int) -> None:
-        """residual += (row-parallel output summed over split-K planes and, with tensor parallelism, over ranks);
+    def _add_norm(self, b: StepBuffers, planes: int, weight: torch.Tensor, M: int, add=None) -> None:
+        """residual += (row-parallel output summed over split-K planes and, with tensor parallelism, over ranks)
+        [+ ``add``: an fp16 addend, the LoRA update of that projection; single GPU only];
         xnorm = RMSNorm(residual) * weight."""
         ops, eps = self.ops, self.config.rms_norm_eps
-        if planes < 0:                 # the GEMM pushed its rows to every rank itself (-planes = its CTA count)
+        if add is not None:
+            if self.comm is not None:
+                raise RuntimeError("LoRA on a row-parallel projection is not wired for tensor parallelism")
+            ops.add_rmsnorm(b.residual, b.partials, planes, add, weight, b.xnorm, M, eps)
+        elif planes < 0:                 # the GEMM pushed its rows to every rank itself (-planes = its CTA count)
             self.comm.sum_add_rmsnorm(ops, b.residual, weight, b.xnorm, M, eps, -planes)
         elif self.comm is None or planes == 0:
             ops.add_rmsnorm(b.residual, b.partials, planes, None, weight, b.xnorm, M, eps)
@@ -275,9 +280,10 @@ class DecoderModel:
         if self.comm is not None and self.comm.fused_norm:
             self.comm.begin_pass()
         ops.embedding(self.embed, b.ids, b.residual, M, self.embed_scale)
-        planes = 0
+        planes, add = 0, None
+        lora = self.lora
         for li, L in enumerate(self.layers):
-            self._add_norm(b, planes, L.ln1, M)
+            self._add_norm(b, planes, L.ln1, M, add)
             if self.lora is None and M <= b.qkv_plane_rows and L.qkv.kind == "w4t":
                 n_q = ops.linear_partial(L.qkv, b.xnorm, M, b.qkv_planes)
                 ops.rope_kv_write(b.qkv, kv[li], b.positions, b.slots, self.inv_freq, M, p.num_heads, p.num_kv_heads,
@@ -295,13 +301,41 @@ class DecoderModel:
                 ops.attn_prefill(b.qkv, kv[li], b.block_tables, b.cu_q, b.q_pos0, b.attn_out, num_seqs, M, max_q_len,
                                  p.num_heads, p.num_kv_heads, c.head_dim, bs, self.scale)
             planes = self._row_parallel(L.o, b.attn_out, M, b)
-            self._add_norm(b, planes, L.ln2, M)
-            ops.linear_swiglu(L.gate_up, b.xnorm, M, b.act)
+            add = lora.delta(li, "o_proj", b.attn_out, b, M) if lora is not None else None
+            self._add_norm(b, planes, L.ln2, M, add)
+            if lora is not None and (lora.has(li, "gate_proj") or lora.has(li, "up_proj")):
+                self._mlp_in_with_lora(li, L, b, M)
+            else:
+                ops.linear_swiglu(L.gate_up, b.xnorm, M, b.act)
             planes = self._row_parallel(L.down, b.act, M, b)
-        self._add_norm(b, planes, self.norm, M)
+            add = lora.delta(li, "down_proj", b.act, b, M) if lora is not None else None
+        self._add_norm(b, planes, self.norm, M, add)
         if n_logit_rows:
             torch.index_select(b.xnorm, 0, b.logit_rows[:n_logit_rows], out=b.xsel[:n_logit_rows])
             ops.linear(self.lm_head, b.xsel, n_logit_rows, b.logits)
+
+    def _mlp_in_with_lora(self, li: int, L: LayerWeights, b: StepBuffers, M: int) -> None:
+        """act = silu(x Wg^T + dg) * (x Wu^T + du) without the fused SwiGLU epilogue: the projection is written out,
+        the adapters' updates are added and the activation is applied on top."""
+        ops, lora, p = self.ops, self.lora, self.plan
+        I = p.inter_size
+        gu = lora._scratch(b, "lora_gate_up", L.gate_up.N)
+        plain = LinearWeight(L.gate_up.kind, L.gate_up.N, L.gate_up.K, L.gate_up.data, None, False, L.gate_up.nbytes)
+        ops.linear(plain, b.xnorm, M, gu)
+        if L.gate_up.kind == "w4t" and L.gate_up.swiglu:    # tiles of 64 gate rows followed by their 64 up rows
+            if I % 64:
+                raise NotImplementedError("LoRA on gate/up needs an intermediate size that is a multiple of 64")
+            t = gu[:M].view(M, I // 64, 2, 64)
+            g, u = t[:, :, 0, :].reshape(M, I).float(), t[:, :, 1, :].reshape(M, I).float()
+        else:
+            g, u = gu[:M, :I].float(), gu[:M, I: 2 * I].float()
+        dg = lora.delta(li, "gate_proj", b.xnorm, b, M)
+        du = lora.delta(li, "up_proj", b.xnorm, b, M)
+        if dg is not None:
+            g = g + dg[:M].float()
+        if du is not None:
+            u = u + du[:M].float()
+        b.act[:M, :I] = ref.swiglu(g, u)
 
     def _uniform_shard_k(self) -> set:
         """Input widths of the row-parallel projections that are the same on every rank.  The exchange inside the GEMM
