@@ -297,3 +297,22 @@ def test_lora_on_every_projection_equals_merged_weights(tmp_path, quant):
     assert got[2] == OracleModel(ZSELoader(path)).greedy(prompts[0], 8)
     assert got[0] != got[2]
     eng.destroy()
+
+
+def test_lora_manager_reference_entry_points(tmp_path):
+    path = str(tmp_path / "m.zse")
+    synth.write_random_model(path, synth.shape_config("tiny"), seed=4)
+    eng = ZStreamerEngine(path, config=EngineConfig(device="cpu", max_batch_seqs=2, max_seq_len=128, quiet=True))
+    m = eng.lora_manager
+    m.load_adapter_random("r", rank=4, alpha=8.0, target_modules=["q_proj", "o_proj"], std=0.1)
+    shapes = m.weight_shapes()
+    rng = np.random.default_rng(0)
+    data = {(l, "v_proj"): ((rng.standard_normal((2, shapes["v_proj"][0])) * 0.1).astype(np.float16).tobytes(),
+                            (rng.standard_normal((shapes["v_proj"][1], 2)) * 0.1).astype(np.float16).tobytes())
+            for l in range(eng.model_config.num_layers)}
+    m.load_adapter_from_dict("d", 2, 4.0, eng.model_config.num_layers, ["v_proj"], data)
+    assert m.num_adapters == 2 and m.has_adapter("r") and m.get_adapter("d").rank == 2 and "slot" in m.summary()
+    rid = eng.add_request_tokens([1, 2, 3, 4], max_tokens=4, temperature=0.0, stop_tokens=[], lora_id="d")
+    eng.run_until_done()
+    assert len(eng.get_result(rid).output_tokens) == 4
+    eng.destroy()

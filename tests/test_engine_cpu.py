@@ -213,3 +213,31 @@ def test_client_callbacks_that_raise_do_not_stop_the_engine(model_path, oracle):
     assert eng.get_result(a).output_tokens == oracle.greedy(p[0], 6)
     assert eng.get_result(b).output_tokens == oracle.greedy(p[1], 6)
     eng.destroy()
+
+
+def test_single_request_engine_has_the_reference_call_signatures(model_path, oracle):
+    """``ZSEEngine`` as a user of the reference calls it (zse-engine/zse_engine/orchestrator/engine.py:263-360):
+    keyword sampling settings, token-level and text-level generators, stats with the reference's fields."""
+    eng = ZSEEngine(model_path, 0, 256, True, config=_cfg())
+    tok = eng.tokenizer
+    ids = tok.encode("hello world")
+    want = oracle.greedy(ids, 6)
+    assert eng.generate_tokens(ids, max_tokens=6, temperature=0.0, stop_tokens=[]) == want
+    assert list(eng.stream_generate_tokens("hello world", max_tokens=6, temperature=0.0, stop_tokens=[])) == want
+    text = eng.generate("hello world", max_tokens=6, temperature=0.0, top_p=0.9, top_k=50, repetition_penalty=1.0,
+                        stop_tokens=[], seed=None)
+    assert text == tok.decode(want)
+    assert "".join(eng.stream_generate("hello world", max_tokens=6, temperature=0.0, stop_tokens=[])) == text
+    assert eng.generate("hello world", GenerateConfig(max_tokens=6, temperature=0.0, stop_tokens=[])) == text
+    a = eng.generate("hello world", max_tokens=8, temperature=1.2, seed=5, stop_tokens=[])
+    assert a == eng.generate("hello world", max_tokens=8, temperature=1.2, seed=5, stop_tokens=[])
+    # a consumer that stops early does not leave the request running
+    gen = eng.stream_generate_tokens("hello world", max_tokens=50, temperature=0.0, stop_tokens=[])
+    next(gen)
+    gen.close()
+    assert not eng.streamer.has_work() and eng.streamer.kv_cache.num_sequences == 0
+    st = eng.stats()
+    assert st.model_arch == "llama" and st.model_path == model_path and st.total_tokens_generated >= 6 * 5
+    assert st.weight_bytes > 0 and st.kv_cache_bytes > 0 and st.scratch_bytes > 0 and st.avg_tokens_per_sec > 0
+    assert eng.config.hidden_size == 256 and "llama" in eng.summary()
+    eng.destroy()

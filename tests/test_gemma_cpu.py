@@ -93,5 +93,9 @@ def test_gemma2_tensor_parallel_cpu_ranks_match_single_engine(tmp_path):
         # the ranks round their partial outputs to fp16 before the sum, so a near tie may flip: first tokens exact
         assert [g[0] for g in got] == [w[0] for w in want]
         assert sum(g == w for g, w in zip(got, want)) >= 2, (got, want)
+        # the one-request calls of the reference's TPEngine (generate / stream_generate / config / summary)
+        text = e.generate("hello there", max_tokens=5, temperature=0.0, stop_tokens=[])
+        assert "".join(e.stream_generate("hello there", max_tokens=5, temperature=0.0, stop_tokens=[])) == text
+        assert e.config.arch == "gemma2" and e.tp_size == 2 and "2-way" in e.summary()
     finally:
         e.stop()

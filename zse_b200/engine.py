@@ -11,6 +11,7 @@ re-tiled on the device, then step buffers and the KV cache are sized from what i
 """
 from __future__ import annotations
 
+import dataclasses
 import os
 
 import sys
@@ -291,8 +292,11 @@ class ZStreamerEngine:
     def has_work(self) -> bool:
         return self._scheduler.num_active > 0 or self._scheduler.num_waiting > 0
 
-    def run(self, idle_sleep_s: float = 0.001) -> None:
-        """Serving loop (call from a dedicated thread); returns after ``stop()``."""
+    def run(self, idle_sleep_ms: float = 1.0, idle_sleep_s: Optional[float] = None) -> None:
+        """Serving loop (call from a dedicated thread); returns after ``stop()``.  ``idle_sleep_ms`` as in the
+        reference (zse-engine/zse_engine/zstreamer/engine.py:541); ``idle_sleep_s`` overrides it."""
+        if idle_sleep_s is None:
+            idle_sleep_s = idle_sleep_ms / 1000.0
         if self.device.type == "cuda":
             torch.cuda.set_device(self.device)
         self._running = True
@@ -369,10 +373,11 @@ class ZStreamerEngine:
 
 @dataclass
 class GenerateConfig:
+    """Sampling settings of one request; defaults as in the reference (zse-engine/zse_engine/orchestrator/engine.py:38-46)."""
     max_tokens: int = 128
-    temperature: float = 0.0
-    top_p: float = 1.0
-    top_k: int = 0
+    temperature: float = 1.0
+    top_p: float = 0.9
+    top_k: int = 50
     repetition_penalty: float = 1.0
     stop_tokens: Optional[List[int]] = None
     seed: Optional[int] = None
@@ -380,24 +385,47 @@ class GenerateConfig:
 
 @dataclass
 class EngineStats:
+    """Statistics of ``ZSEEngine``: the last request (first block) and the engine as a whole (second block, the fields
+    of the reference's ``EngineStats``, zse-engine/zse_engine/orchestrator/engine.py:49-68; ``kernel_compile_time_s``
+    is 0 because the kernels are compiled ahead of time)."""
     prompt_tokens: int = 0
     generated_tokens: int = 0
     ttft_ms: float = 0.0
     total_ms: float = 0.0
     tokens_per_sec: float = 0.0
     decode_tokens_per_sec: float = 0.0
+    model_path: str = ""
+    model_arch: str = ""
+    device_name: str = ""
+    vram_total_gb: float = 0.0
+    weight_load_time_s: float = 0.0
+    kernel_compile_time_s: float = 0.0
+    total_init_time_s: float = 0.0
+    total_tokens_generated: int = 0
+    total_prefill_tokens: int = 0
+    total_generate_time_s: float = 0.0
+    avg_tokens_per_sec: float = 0.0
+    weight_bytes: int = 0
+    kv_cache_bytes: int = 0
+    scratch_bytes: int = 0
 
 
 class ZSEEngine:
-    """One request at a time: ``generate`` (text in, text out), ``stream_generate`` (iterator of text pieces),
-    ``generate_tokens`` (ids in, ids out)."""
+    """One request at a time, with the call signatures of the reference's ``ZSEEngine``
+    (zse-engine/zse_engine/orchestrator/engine.py:70-524): ``generate(prompt, max_tokens=..., temperature=..., ...)``
+    (text in, text out), ``stream_generate`` (iterator of text pieces), ``generate_tokens`` (ids in, generated ids
+    out), ``stream_generate_tokens`` (iterator of ids).  A ``GenerateConfig`` may be passed instead of the keywords
+    (second positional argument or ``config=``)."""
 
     def __init__(self, model_path: str, device_index: int = 0, max_seq_len: int = 0, quiet: bool = True,
                  config: Optional[EngineConfig] = None):
         cfg = config or EngineConfig(device_index=device_index, max_seq_len=max_seq_len, quiet=quiet,
                                      max_batch_seqs=8, max_batch_tokens=2048)
+        self._model_path = model_path
         self._streamer = ZStreamerEngine(model_path, config=cfg)
         self._last = EngineStats()
+        self._total_tokens = self._total_prefill = 0
+        self._total_gen_time = 0.0
 
     @property
     def streamer(self) -> ZStreamerEngine:
@@ -407,62 +435,149 @@ class ZSEEngine:
     def tokenizer(self):
         return self._streamer.tokenizer
 
-    def generate_tokens(self, prompt_tokens: List[int], config: Optional[GenerateConfig] = None,
-                        on_token: Optional[Callable[[int], None]] = None) -> List[int]:
-        g = config or GenerateConfig()
+    @property
+    def config(self):
+        """The model's configuration (``ModelConfig``)."""
+        return self._streamer.model_config
+
+    @property
+    def device(self):
+        """``DeviceInfo`` of the GPU the engine runs on (None on the CPU path)."""
+        if self._streamer.device.type != "cuda":
+            return None
+        from .runtime.device import get_devices
+        devs = get_devices()
+        idx = self._streamer.device.index or 0
+        return devs[idx] if idx < len(devs) else None
+
+    @staticmethod
+    def _settings(max_tokens, temperature, top_p, top_k, repetition_penalty, stop_tokens, seed,
+                  config) -> GenerateConfig:
+        if isinstance(max_tokens, GenerateConfig):       # generate(prompt, GenerateConfig(...))
+            config = max_tokens
+        if config is not None:
+            return dataclasses.replace(config)
+        return GenerateConfig(int(max_tokens), float(temperature), float(top_p), int(top_k), float(repetition_penalty),
+                              None if stop_tokens is None else list(stop_tokens), seed)
+
+    def _run(self, prompt_tokens: List[int], g: GenerateConfig, on_token=None) -> Iterator[int]:
+        """Submits the request and drives the engine on the calling thread, yielding tokens as they are produced."""
         t0 = time.monotonic()
+        fresh: List[int] = []
+
+        def got(tok: int) -> None:
+            fresh.append(tok)
+            if on_token is not None:
+                on_token(tok)
+
         rid = self._streamer.add_request_tokens(prompt_tokens, max_tokens=g.max_tokens, temperature=g.temperature,
                                                 top_p=g.top_p, top_k=g.top_k, repetition_penalty=g.repetition_penalty,
-                                                stop_tokens=g.stop_tokens, seed=g.seed, on_token=on_token)
+                                                stop_tokens=g.stop_tokens, seed=g.seed, on_token=got)
         if rid is None:
             raise RuntimeError("request queue is full")
-        self._streamer.run_until_done()
-        out = self._streamer.get_result(rid)
+        try:
+            while self._streamer.has_work():
+                self._streamer.step()
+                while fresh:
+                    yield fresh.pop(0)
+            self._streamer.step()
+            while fresh:
+                yield fresh.pop(0)
+        finally:
+            if self._streamer.has_work():                # the consumer stopped early: do not leave the request running
+                self._streamer.cancel_request(rid)
+                self._streamer.run_until_done()
+            out = self._streamer.get_result(rid)
+            total = (time.monotonic() - t0) * 1000
+            if out is not None:
+                n = len(out.output_tokens)
+                self._total_tokens += n
+                self._total_prefill += len(prompt_tokens)
+                self._total_gen_time += total / 1000
+                self._last = dataclasses.replace(
+                    self.stats(), prompt_tokens=len(prompt_tokens), generated_tokens=n, ttft_ms=out.ttft_ms,
+                    total_ms=total, tokens_per_sec=n / (total / 1000) if total else 0.0,
+                    decode_tokens_per_sec=(n - 1) / ((total - out.ttft_ms) / 1000)
+                    if n > 1 and total > out.ttft_ms else 0.0)
         if out is None or out.finish_reason == FinishReason.ERROR:
             raise RuntimeError(f"generation failed: {out.error if out else 'no result'}")
-        total = (time.monotonic() - t0) * 1000
-        n = len(out.output_tokens)
-        self._last = EngineStats(len(prompt_tokens), n, out.ttft_ms, total, n / (total / 1000) if total else 0.0,
-                                 (n - 1) / ((total - out.ttft_ms) / 1000) if n > 1 and total > out.ttft_ms else 0.0)
-        return out.output_tokens
 
-    def generate(self, prompt: str, config: Optional[GenerateConfig] = None) -> str:
-        tok = self.tokenizer
-        g = config or GenerateConfig()
+    def generate_tokens(self, token_ids: List[int], max_tokens=128, temperature: float = 1.0, top_p: float = 0.9,
+                        top_k: int = 50, repetition_penalty: float = 1.0, stop_tokens: Optional[List[int]] = None,
+                        seed: Optional[int] = None, config: Optional[GenerateConfig] = None,
+                        on_token: Optional[Callable[[int], None]] = None) -> List[int]:
+        """Generated token ids for a prompt given as ids."""
+        g = self._settings(max_tokens, temperature, top_p, top_k, repetition_penalty, stop_tokens, seed, config)
+        return list(self._run(list(token_ids), g, on_token))
+
+    def stream_generate_tokens(self, prompt: str, max_tokens=128, temperature: float = 1.0, top_p: float = 0.9,
+                               top_k: int = 50, repetition_penalty: float = 1.0,
+                               stop_tokens: Optional[List[int]] = None, seed: Optional[int] = None,
+                               config: Optional[GenerateConfig] = None) -> Iterator[int]:
+        """Yields generated token ids one at a time."""
+        g = self._settings(max_tokens, temperature, top_p, top_k, repetition_penalty, stop_tokens, seed, config)
         if g.stop_tokens is None:
             g.stop_tokens = self._streamer.default_stop_tokens()
-        ids = self.generate_tokens(tok.encode(prompt), g)
-        stops = set(g.stop_tokens or [])
-        return tok.decode([t for t in ids if t not in stops])
+        return self._run(self.tokenizer.encode(prompt), g)
 
-    def stream_generate(self, prompt: str, config: Optional[GenerateConfig] = None) -> Iterator[str]:
-        """Yields decoded text increments.  Runs the engine loop on the calling thread between yields."""
-        tok = self.tokenizer
-        g = config or GenerateConfig()
+    def generate(self, prompt: str, max_tokens=128, temperature: float = 1.0, top_p: float = 0.9, top_k: int = 50,
+                 repetition_penalty: float = 1.0, stop_tokens: Optional[List[int]] = None,
+                 seed: Optional[int] = None, config: Optional[GenerateConfig] = None) -> str:
+        """Generated text (stop tokens removed)."""
+        g = self._settings(max_tokens, temperature, top_p, top_k, repetition_penalty, stop_tokens, seed, config)
         if g.stop_tokens is None:
             g.stop_tokens = self._streamer.default_stop_tokens()
         stops = set(g.stop_tokens or [])
-        fresh: List[int] = []
-        rid = self._streamer.add_request_tokens(tok.encode(prompt), max_tokens=g.max_tokens, temperature=g.temperature,
-                                                top_p=g.top_p, top_k=g.top_k, stop_tokens=g.stop_tokens, seed=g.seed,
-                                                repetition_penalty=g.repetition_penalty, on_token=fresh.append)
-        if rid is None:
-            raise RuntimeError("request queue is full")
-        emitted, text_so_far = [], ""
-        while self._streamer.has_work():
-            self._streamer.step()
-            if fresh:
-                emitted += [t for t in fresh if t not in stops]
-                fresh.clear()
-                text = tok.decode(emitted)
-                if not text.endswith("�") and len(text) > len(text_so_far):
-                    yield text[len(text_so_far):]
-                    text_so_far = text
-        self._streamer.step()
-        self._streamer.get_result(rid)
+        ids = list(self._run(self.tokenizer.encode(prompt), g))
+        return self.tokenizer.decode([t for t in ids if t not in stops])
+
+    def stream_generate(self, prompt: str, max_tokens=128, temperature: float = 1.0, top_p: float = 0.9,
+                        top_k: int = 50, repetition_penalty: float = 1.0, stop_tokens: Optional[List[int]] = None,
+                        seed: Optional[int] = None, config: Optional[GenerateConfig] = None) -> Iterator[str]:
+        """Yields decoded text increments (a piece is held back while it ends inside a multi-byte character)."""
+        g = self._settings(max_tokens, temperature, top_p, top_k, repetition_penalty, stop_tokens, seed, config)
+        if g.stop_tokens is None:
+            g.stop_tokens = self._streamer.default_stop_tokens()
+        stops = set(g.stop_tokens or [])
+        tok = self.tokenizer
+        emitted: List[int] = []
+        text_so_far = ""
+        for t in self._run(tok.encode(prompt), g):
+            if t in stops:
+                continue
+            emitted.append(t)
+            text = tok.decode(emitted)
+            if not text.endswith("\ufffd") and len(text) > len(text_so_far):
+                yield text[len(text_so_far):]
+                text_so_far = text
+        text = tok.decode(emitted)
+        if len(text) > len(text_so_far):
+            yield text[len(text_so_far):]
 
     def stats(self) -> EngineStats:
-        return self._last
+        s = self._streamer
+        times = s.init_times
+        dev = self.device
+        kv = s.kv_cache
+        return dataclasses.replace(
+            self._last, model_path=self._model_path, model_arch=s.model_config.arch,
+            device_name=dev.name if dev is not None else "cpu",
+            vram_total_gb=(dev.total_memory / 2 ** 30) if dev is not None else 0.0,
+            weight_load_time_s=float(times.get("weights", 0.0)), kernel_compile_time_s=0.0,
+            total_init_time_s=float(times.get("total", 0.0)), total_tokens_generated=self._total_tokens,
+            total_prefill_tokens=self._total_prefill, total_generate_time_s=self._total_gen_time,
+            avg_tokens_per_sec=self._total_tokens / self._total_gen_time if self._total_gen_time > 0 else 0.0,
+            weight_bytes=int(getattr(s.runner.model, "weight_bytes", 0)),
+            kv_cache_bytes=int(kv.num_total_blocks * kv.stats().block_bytes), scratch_bytes=int(s.runner.buf.nbytes()))
+
+    def summary(self) -> str:
+        s = self.stats()
+        return (f"ZSE engine summary:\n  model: {s.model_arch} ({s.model_path})\n"
+                f"  device: {s.device_name} ({s.vram_total_gb:.1f} GB)\n"
+                f"  init: {s.total_init_time_s:.2f}s (weights {s.weight_load_time_s:.2f}s)\n"
+                f"  memory: weights {s.weight_bytes / 2 ** 20:.1f} MB, kv {s.kv_cache_bytes / 2 ** 20:.1f} MB, "
+                f"scratch {s.scratch_bytes / 2 ** 20:.1f} MB\n"
+                f"  generated: {s.total_tokens_generated} tokens, {s.avg_tokens_per_sec:.1f} tok/s")
 
     def destroy(self) -> None:
         self._streamer.destroy()

@@ -154,6 +154,56 @@ class LoRAManager:
                 self._model.lora = None
             return True
 
+    # ---- the reference's entry points (zse-engine/zse_engine/orchestrator/lora_manager.py:88-246) -----------------
+    def load_adapter_from_file(self, adapter_id: str, path: str, weight_shapes=None) -> LoRAAdapter:
+        """``weight_shapes`` is accepted for compatibility; the shapes come from the model."""
+        return self.load_adapter(adapter_id, path)
+
+    def load_adapter_from_dict(self, adapter_id: str, rank: int, alpha: float, num_layers: int,
+                               target_modules: List[str], weights_data: Dict[Tuple[int, str], tuple],
+                               weight_shapes=None) -> LoRAAdapter:
+        """``weights_data[(layer, module)] = (A, B)`` as fp16 bytes, numpy arrays or tensors."""
+        shapes = self.weight_shapes()
+        arrays = {}
+        for (layer, mod), (a, b) in weights_data.items():
+            fin, fout = shapes[mod]
+            if isinstance(a, (bytes, bytearray, memoryview)):
+                a = np.frombuffer(a, np.float16).reshape(rank, fin)
+            if isinstance(b, (bytes, bytearray, memoryview)):
+                b = np.frombuffer(b, np.float16).reshape(fout, rank)
+            arrays[(layer, mod)] = (a, b)
+        return self.load_adapter_from_arrays(adapter_id, rank, alpha, list(target_modules), num_layers, arrays)
+
+    def load_adapter_random(self, adapter_id: str, rank: int = 8, alpha: float = 16.0, num_layers: int = 0,
+                            target_modules: Optional[List[str]] = None, seed: int = 0, std: float = 0.02,
+                            **_ignored) -> LoRAAdapter:
+        """An adapter with random matrices (tests and benchmarks); model dimensions come from the model."""
+        shapes = self.weight_shapes()
+        rng = np.random.default_rng(seed)
+        targets = list(target_modules or ["q_proj", "v_proj"])
+        layers = num_layers or self._model.config.num_layers
+        arrays = {(l, t): ((rng.standard_normal((rank, shapes[t][0])) * std).astype(np.float16),
+                           (rng.standard_normal((shapes[t][1], rank)) * std).astype(np.float16))
+                  for l in range(layers) for t in targets}
+        return self.load_adapter_from_arrays(adapter_id, rank, alpha, targets, layers, arrays)
+
+    def get_adapter(self, adapter_id: str) -> Optional[LoRAAdapter]:
+        return self._store.get(adapter_id)
+
+    def has_adapter(self, adapter_id: str) -> bool:
+        return adapter_id in self._store
+
+    @property
+    def num_adapters(self) -> int:
+        return len(self._store)
+
+    def summary(self) -> str:
+        lines = [f"LoRA adapters: {len(self._store)} of {self._max_adapters} slots, table rank {self._rank}"]
+        for a in self.list_adapters():
+            lines.append(f"  {a['adapter_id']}: rank {a['rank']}, alpha {a['alpha']:g}, "
+                         f"{', '.join(a['target_modules'])}, {a['bytes'] / 2 ** 20:.1f} MiB, slot {a['slot']}")
+        return "\n".join(lines)
+
     # ---- queries --------------------------------------------------------------------------------------------
     def is_loaded(self, adapter_id: str) -> bool:
         return adapter_id in self._store

@@ -24,7 +24,7 @@ import threading
 import time
 import traceback
 from dataclasses import dataclass
-from typing import Callable, Dict, List, Optional
+from typing import Callable, Dict, Iterator, List, Optional
 
 import torch
 import torch.multiprocessing as mp
@@ -139,16 +139,22 @@ class TPEngine:
 
     HEARTBEAT_TIMEOUT_S = 30.0
 
-    def __init__(self, model_path: str, tp_size: int = 2, config: Optional[EngineConfig] = None,
-                 start_timeout_s: float = 600.0):
+    def __init__(self, model_path: str, tp_size: int = 2, config=None, start_timeout_s: float = 600.0,
+                 quiet: Optional[bool] = None):
+        """``config``: an ``EngineConfig``; the reference's third argument is ``quiet`` (zse-engine/zse_engine/
+        orchestrator/tp_engine.py:46-63), so a bool given there is taken as that."""
         from ..format.loader import ZSELoader
+        if isinstance(config, bool):
+            quiet, config = config, None
         self.model_path, self.tp_size = model_path, tp_size
-        self.config = config or EngineConfig(tp_size=tp_size)
-        self.config.tp_size = tp_size
+        self.engine_config = config or EngineConfig(tp_size=tp_size)
+        self.engine_config.tp_size = tp_size
+        if quiet is not None:
+            self.engine_config.quiet = bool(quiet)
         with ZSELoader(model_path) as l:
             self._config = l.config
             self._tokenizer = l.tokenizer
-        self._max_seq_len = min(self.config.max_seq_len or self._config.max_seq_len, self._config.max_seq_len, 32768)
+        self._max_seq_len = min(self.engine_config.max_seq_len or self._config.max_seq_len, self._config.max_seq_len, 32768)
         self._lock = threading.Lock()
         self._pending: Dict[str, dict] = {}
         self._completed: Dict[str, RequestOutput] = {}
@@ -171,7 +177,7 @@ class TPEngine:
         self._beats = ctx.Array("q", self.tp_size, lock=False)
         port = _free_port()
         self._procs = [ctx.Process(target=_worker, daemon=True,
-                                   args=(r, self.tp_size, self.model_path, self.config, port, self._cmd_q,
+                                   args=(r, self.tp_size, self.model_path, self.engine_config, port, self._cmd_q,
                                          self._evt_q, self._beats, ready)) for r in range(self.tp_size)]
         for p in self._procs:
             p.start()
@@ -237,6 +243,11 @@ class TPEngine:
         return self._tokenizer
 
     @property
+    def config(self):
+        """The model's configuration, as ``TPEngine.config`` of the reference."""
+        return self._config
+
+    @property
     def model_config(self):
         return self._config
 
@@ -280,7 +291,7 @@ class TPEngine:
             raise ValueError("LoRA adapters are not available with --tp > 1 yet")
         kw.pop("lora_id", None)
         with self._lock:
-            if len(self._pending) >= self.config.max_queue_size + self.config.max_batch_seqs:
+            if len(self._pending) >= self.engine_config.max_queue_size + self.engine_config.max_batch_seqs:
                 return None
             self._counter += 1
             rid = request_id or f"req-{self._counter}"
@@ -364,6 +375,65 @@ class TPEngine:
 
     def has_work(self) -> bool:
         return bool(self._pending)
+
+    # ---- one request at a time (zse-engine/zse_engine/orchestrator/tp_engine.py:329-443) ------------------------
+    def stream_generate_tokens(self, prompt: str, max_tokens: int = 128, temperature: float = 1.0, top_k: int = 50,
+                               top_p: float = 0.9, stop_tokens: Optional[List[int]] = None,
+                               timeout_s: float = 600.0, **kw) -> Iterator[int]:
+        """Yields the generated token ids of one request while polling the ranks on the calling thread."""
+        fresh: List[int] = []
+        done: List[RequestOutput] = []
+        rid = self.add_request(prompt, max_tokens=max_tokens, temperature=temperature, top_k=top_k, top_p=top_p,
+                               stop_tokens=stop_tokens, on_token=fresh.append, on_finish=done.append, **kw)
+        if rid is None:
+            raise RuntimeError("the tensor-parallel engine is not accepting requests: " + str(self._last_error))
+        deadline = time.monotonic() + timeout_s
+        try:
+            while not done and time.monotonic() < deadline:
+                self.poll(0.01)
+                while fresh:
+                    yield fresh.pop(0)
+            while fresh:
+                yield fresh.pop(0)
+        finally:
+            if not done:
+                self.cancel_request(rid)
+        self.get_result(rid)
+        if not done:
+            raise TimeoutError(f"no answer from the ranks within {timeout_s}s")
+        if done[0].finish_reason == FinishReason.ERROR:
+            raise RuntimeError(f"generation failed: {done[0].error}")
+
+    def generate(self, prompt: str, max_tokens: int = 128, temperature: float = 1.0, top_k: int = 50,
+                 top_p: float = 0.9, stop_tokens: Optional[List[int]] = None, **kw) -> str:
+        stops = set(self.default_stop_tokens() if stop_tokens is None else stop_tokens)
+        ids = [t for t in self.stream_generate_tokens(prompt, max_tokens, temperature, top_k, top_p, stop_tokens, **kw)
+               if t not in stops]
+        return self._tokenizer.decode(ids)
+
+    def stream_generate(self, prompt: str, max_tokens: int = 128, temperature: float = 1.0, top_k: int = 50,
+                        **kw) -> Iterator[str]:
+        stops = set(self.default_stop_tokens() if kw.get("stop_tokens") is None else kw["stop_tokens"])
+        ids: List[int] = []
+        sent = ""
+        for t in self.stream_generate_tokens(prompt, max_tokens, temperature, top_k, **kw):
+            if t in stops:
+                continue
+            ids.append(t)
+            text = self._tokenizer.decode(ids)
+            if not text.endswith("\ufffd") and len(text) > len(sent):
+                yield text[len(sent):]
+                sent = text
+        text = self._tokenizer.decode(ids)
+        if len(text) > len(sent):
+            yield text[len(sent):]
+
+    def summary(self) -> str:
+        st = self.stats()
+        rate = st.total_tokens_generated / st.uptime_s if st.uptime_s > 0 else 0.0
+        return (f"TPEngine: {self.tp_size}-way tensor parallel ({'healthy' if st.healthy else 'unhealthy'})\n"
+                f"  model: {self.model_path}\n  init: {self.init_times.get('total', 0.0):.2f}s\n"
+                f"  tokens generated: {st.total_tokens_generated} ({rate:.1f} tok/s over the uptime)")
 
     def get_result(self, request_id: str) -> Optional[RequestOutput]:
         with self._lock:

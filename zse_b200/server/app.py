@@ -186,3 +186,5 @@ class ZSEServer:
     def close(self) -> None:
         self.stop()
         self._db.close()
+
+    destroy = close
