@@ -316,3 +316,23 @@ def test_lora_manager_reference_entry_points(tmp_path):
     eng.run_until_done()
     assert len(eng.get_result(rid).output_tokens) == 4
     eng.destroy()
+
+
+@pytest.mark.timeout(300)
+def test_tensor_parallel_group_facade():
+    """``tp_launch`` + ``TensorParallelGroup`` under the reference's names, on two CPU ranks."""
+    import sys
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from dist_tp_group_fn import rank_fn
+    from zse_b200.parallel.tensor_parallel import TPConfig, tp_launch
+    res = tp_launch(2, rank_fn, backend="cpu", timeout_s=240)
+    assert res[0]["sum"] == [3.0] * 4 and res[1]["gathered"] == [0.0, 1.0] and res[0]["bcast"] == [10.0]
+    assert res[0]["q"] == (0, 256) and res[1]["q"] == (256, 512)
+    assert res[0]["down"] == (0, 6912) and res[1]["down"] == (6912, 13824)
+    assert res[0]["strategy"] == ["row", "column", "replicated"]
+    cfg = TPConfig(tp_size=8)
+    assert cfg.is_enabled()
+    with pytest.raises(ValueError):
+        cfg.validate(40, 6, 13824)
+    with pytest.raises(ValueError):
+        tp_launch(1, rank_fn)
