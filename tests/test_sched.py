@@ -228,3 +228,60 @@ def test_lone_request_is_admitted_even_if_its_headroom_estimate_does_not_fit():
     s.add_request(r)
     out = s.schedule_step()
     assert out.prefill_requests == [r]
+
+
+def test_reference_named_helpers_of_queue_budget_and_speculation():
+    """Names a user of the reference's scheduler pieces relies on (zstreamer/queue.py, memory_budget.py,
+    draft_model.py, verifier.py)."""
+    import numpy as np
+    from zse_b200.sched.draft_model import NGramDraftModel, SelfDraftModel
+    from zse_b200.sched.memory_budget import MemoryBudget, MemoryReservation
+    from zse_b200.sched.queue import RequestQueue
+    from zse_b200.sched.request import GenerationParams, InferenceRequest
+    from zse_b200.sched.verifier import SpeculativeVerifier, acceptance_rate, effective_tokens_per_step
+
+    def req(i, n=10, m=8):
+        return InferenceRequest(f"r{i}", list(range(n)), GenerationParams(max_tokens=m))
+
+    q = RequestQueue(8)
+    a, b = req(1), req(2)
+    q.add(a)
+    q.add(b)
+    assert q.get("r1") is a and q.num_total == 2 and q.num_preempted == 0
+    popped = q.pop_next()
+    q.add_preempted(popped)
+    assert q.num_preempted == 1 and q.get("nope") is None
+
+    bud = MemoryBudget(total_blocks=12, block_size=16, headroom_ratio=0.5, reserve_blocks=2)
+    reqs = [req(i, n=40, m=16) for i in range(5)]          # 3 prompt blocks + 2 headroom each
+    assert bud.can_admit_n(reqs) == 2
+    for r in reqs[:2]:
+        bud.reserve(r)
+    assert bud.preemption_candidates(1) in (["r0"], ["r1"]) and len(bud.preemption_candidates(100)) == 2
+    assert MemoryReservation is not None
+
+    ng = NGramDraftModel(50, n=3, confidence=0.8)
+    toks, probs = ng.generate_drafts([1, 2, 3, 4, 1, 2, 3], 3)
+    assert toks == [4, 1, 2] and len(probs) == 3 and len(probs[0]) == 50 and abs(sum(probs[0]) - 1) < 1e-6
+    assert probs[0][4] == 0.8 and ng.vocab_size() == 50
+    toks, _ = ng.generate_drafts([7, 8, 9], 2)             # nothing to look up: still K drafts
+    assert len(toks) == 2
+    sd = SelfDraftModel(50)
+    logits = np.zeros(50, np.float16)
+    logits[17] = 3.0
+    sd.set_last_logits(logits.tobytes())
+    assert sd.propose(2) == [17, 17]
+
+    v = SpeculativeVerifier(seed=0)
+    rows = []
+    for t in (4, 9, 2):                                    # the target wants 4, then 9, then 2
+        r = np.full(50, -5.0, np.float16)
+        r[t] = 5.0
+        rows.append(r.tobytes())
+    acc, n = v.verify_and_accept([4, 1], [ng._dist(4), ng._dist(1)], rows, 50, temperature=0.0)
+    assert acc == [4, 9] and n == 1                         # first draft accepted, second replaced by the target's
+    acc, n = v.verify_and_accept([4, 9], [ng._dist(4), ng._dist(9)], rows, 50, temperature=0.0)
+    assert acc == [4, 9, 2] and n == 2                      # all accepted + bonus token
+    acc, n = v.verify_and_accept([4, 9], [ng._dist(4), ng._dist(9)], rows, 50, temperature=1.0)
+    assert acc[:2] == [4, 9] and n == 2
+    assert acceptance_rate(2, 4) == 0.5 and effective_tokens_per_step(3) == 3.0

@@ -26,6 +26,25 @@ class LoRAWeight:
     def loaded(self) -> bool:
         return self.a is not None and self.b is not None
 
+    # the reference's names (zse-engine/zse_engine/orchestrator/lora_weights.py:36-60)
+    @property
+    def total_gpu_bytes(self) -> int:
+        return self.nbytes
+
+    @property
+    def a_shape(self) -> Tuple[int, int]:
+        return (self.rank, self.in_features)
+
+    @property
+    def b_shape(self) -> Tuple[int, int]:
+        return (self.out_features, self.rank)
+
+    def make_a_tensor(self):
+        return self.a
+
+    def make_b_tensor(self):
+        return self.b
+
 
 @dataclass
 class LoRAAdapter:
@@ -50,9 +69,25 @@ class LoRAAdapter:
     def has_module(self, module: str) -> bool:
         return module in self.target_modules
 
+    def has_weight(self, layer: int, module: str) -> bool:
+        return (layer, module) in self.weights
+
+    @property
+    def num_weight_pairs(self) -> int:
+        return len(self.weights)
+
     @property
     def total_bytes(self) -> int:
         return sum(w.nbytes for w in self.weights.values())
+
+    @property
+    def total_gpu_bytes(self) -> int:
+        return self.total_bytes
+
+    def summary(self) -> str:
+        return (f"LoRA adapter '{self.adapter_id}': rank {self.rank}, alpha {self.alpha:g} (scaling "
+                f"{self.scaling:.3f}), {self.num_layers} layers x {', '.join(self.target_modules)}, "
+                f"{self.num_weight_pairs} weight pairs, {self.total_bytes / 2 ** 20:.2f} MiB")
 
 
 class LoRAWeightStore:
@@ -87,6 +122,26 @@ class LoRAWeightStore:
     @property
     def total_bytes(self) -> int:
         return sum(a.total_bytes for a in self._adapters.values())
+
+    # the reference's names (zse-engine/zse_engine/orchestrator/lora_weights.py:133-167)
+    def has(self, adapter_id: str) -> bool:
+        return adapter_id in self._adapters
+
+    @property
+    def num_adapters(self) -> int:
+        return len(self._adapters)
+
+    @property
+    def total_gpu_bytes(self) -> int:
+        return self.total_bytes
+
+    def list_adapters(self) -> List[str]:
+        return list(self._adapters)
+
+    def summary(self) -> str:
+        lines = [f"LoRA store: {len(self._adapters)} adapters, {self.total_bytes / 2 ** 20:.2f} MiB"]
+        lines += ["  " + a.summary() for a in self._adapters.values()]
+        return "\n".join(lines)
 
 
 def random_adapter_file(path: str, config, rank: int = 8, alpha: float = 16.0,

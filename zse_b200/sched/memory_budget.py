@@ -24,6 +24,9 @@ class _Commit:
         return self.prompt_blocks + max(self.headroom_blocks, self.decode_blocks)
 
 
+MemoryReservation = _Commit      # the reference's name for the per-request record
+
+
 class MemoryBudget:
     def __init__(self, total_blocks: int, block_size: int, headroom_ratio: float = 0.5, reserve_blocks: int = 2):
         self._total = total_blocks
@@ -59,6 +62,32 @@ class MemoryBudget:
             if req.request_id in self._commits:
                 return True
             return self._estimate(req).total <= self._total - self._reserve - self.committed_blocks
+
+    def can_admit_n(self, requests) -> int:
+        """How many of ``requests``, taken in order, fit next to what is committed already
+        (zse-engine/zse_engine/zstreamer/memory_budget.py:100-115)."""
+        with self._lock:
+            left = self._total - self._reserve - self.committed_blocks
+            n = 0
+            for req in requests:
+                cost = 0 if req.request_id in self._commits else self._estimate(req).total
+                if cost > left:
+                    break
+                left -= cost
+                n += 1
+            return n
+
+    def preemption_candidates(self, blocks_needed: int) -> list:
+        """Ids of committed requests, largest first, whose release frees at least ``blocks_needed`` blocks (all of
+        them when even that is not enough)."""
+        with self._lock:
+            out, freed = [], 0
+            for rid, c in sorted(self._commits.items(), key=lambda kv: -kv[1].total):
+                if freed >= blocks_needed:
+                    break
+                out.append(rid)
+                freed += c.total
+            return out
 
     def fits_at_all(self, req: InferenceRequest) -> bool:
         """False when the request could never run, even on an empty cache."""

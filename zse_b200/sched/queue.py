@@ -104,6 +104,20 @@ class RequestQueue:
         with self._lock:
             self._live.pop(request_id, None)
 
+    def get(self, request_id: str) -> Optional[InferenceRequest]:
+        """A queued (waiting or preempted) request by id."""
+        with self._lock:
+            return self._live.get(request_id)
+
+    @property
+    def num_preempted(self) -> int:
+        with self._lock:
+            return sum(1 for e in self._preempted if self._live.get(e[-1].request_id) is e[-1])
+
+    @property
+    def num_total(self) -> int:
+        return len(self._live)
+
     @property
     def is_empty(self) -> bool:
         return not self._live

@@ -10,12 +10,22 @@ row is compared with the drafts, so the output is exactly the non-speculative gr
 """
 from __future__ import annotations
 
+from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence
 
 from ..runtime.runner import ModelRunner
 from .draft_model import make_draft_model
 from .request import InferenceRequest
 from .verifier import SpeculativeVerifier
+
+
+@dataclass
+class SpeculativeResult:
+    """What one speculative step gave one sequence (zse-engine/zse_engine/zstreamer/spec_runner.py:29-35)."""
+    request_id: str
+    accepted_tokens: List[int]
+    num_draft_accepted: int
+    total_tokens: int
 
 
 class SpeculativeRunner:
@@ -87,6 +97,46 @@ class SpeculativeRunner:
             i = j
         self.tokens_emitted += emitted
         return emitted
+
+    # ---- the reference's per-request entry points and figures (spec_runner.py:73-245) -------------------------
+    def batched_speculative_step(self, requests: Sequence[InferenceRequest], scheduler, K: Optional[int] = None,
+                                 adapters: Optional[Sequence[int]] = None) -> List[SpeculativeResult]:
+        """One step for every request (ONE packed verification pass); a result per request with the tokens it got.
+        The tokens are delivered to ``scheduler.on_token_generated`` as in ``step``."""
+        before = [(r.num_generated, r.spec_accepted) for r in requests]
+        old_k = self.k
+        if K is not None:
+            self.k = int(K)
+        try:
+            self.step(requests, scheduler, adapters)
+        finally:
+            self.k = old_k
+        out = []
+        for r, (n0, a0) in zip(requests, before):
+            toks = list(r.output_tokens[n0:])
+            out.append(SpeculativeResult(r.request_id, toks, r.spec_accepted - a0, len(toks)))
+        return out
+
+    def speculative_step(self, request: InferenceRequest, scheduler, K: Optional[int] = None) -> SpeculativeResult:
+        return self.batched_speculative_step([request], scheduler, K)[0]
+
+    @property
+    def acceptance_rate(self) -> float:
+        return self._verifier.stats()["acceptance_rate"]
+
+    @property
+    def tokens_per_step(self) -> float:
+        return self.tokens_emitted / self.seq_steps if self.seq_steps else 0.0
+
+    @property
+    def speedup_factor(self) -> float:
+        """Tokens per pass of the target model (a plain decode step yields one)."""
+        return self.tokens_per_step
+
+    def summary(self) -> str:
+        s = self.stats()
+        return (f"Speculative decoding ({self.mode}, k={self.k}): {s['steps']} steps, {s['drafted']} drafts, "
+                f"{s['accepted']} accepted ({s['acceptance_rate']:.1%}), {self.tokens_per_step:.2f} tokens per step")
 
     def stats(self) -> dict:
         s = self._verifier.stats()

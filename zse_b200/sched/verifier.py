@@ -67,6 +67,26 @@ class SpeculativeVerifier:
         out.append(self._draw(target_probs[len(draft_tokens)].float()))
         return self._record(VerifyResult(out, len(draft_tokens), n_acc))
 
+    def verify_and_accept(self, draft_tokens: Sequence[int], draft_probs, target_logits_list, vocab_size: int,
+                          temperature: float = 1.0):
+        """The reference's entry point (zse-engine/zse_engine/zstreamer/verifier.py:37-110): ``target_logits_list`` holds
+        K+1 rows of raw fp16 logits (bytes) or tensors; returns ``(accepted_tokens, num_draft_accepted)``."""
+        import numpy as np
+        rows = []
+        for row in target_logits_list:
+            if isinstance(row, (bytes, bytearray, memoryview)):
+                row = torch.from_numpy(np.frombuffer(row, dtype=np.float16)[:vocab_size].astype(np.float32))
+            rows.append(torch.as_tensor(row, dtype=torch.float32)[:vocab_size])
+        if len(rows) != len(draft_tokens) + 1:
+            raise ValueError("one more row of target logits than drafts is required")
+        if temperature is None or temperature < 1e-6:
+            r = self.verify_greedy(draft_tokens, [int(x.argmax()) for x in rows])
+        else:
+            target = [torch.softmax(x / temperature, dim=-1) for x in rows]
+            draft = [torch.as_tensor(d, dtype=torch.float32)[:vocab_size] for d in draft_probs]
+            r = self.verify_stochastic(draft_tokens, draft, target)
+        return r.accepted_tokens, r.num_accepted
+
     def _draw(self, dist: torch.Tensor) -> int:
         u = self._rng.random() * float(dist.sum())
         c = torch.cumsum(dist, dim=0)
@@ -81,3 +101,12 @@ class SpeculativeVerifier:
     def stats(self) -> dict:
         return {"steps": self.total_steps, "drafted": self.total_drafted, "accepted": self.total_accepted,
                 "acceptance_rate": self.total_accepted / self.total_drafted if self.total_drafted else 0.0}
+
+
+def acceptance_rate(num_draft_accepted: int, K: int) -> float:
+    return num_draft_accepted / K if K > 0 else 0.0
+
+
+def effective_tokens_per_step(num_tokens_produced: int) -> float:
+    """Tokens one target pass yielded (1 without drafts, up to K+1 with them)."""
+    return float(num_tokens_produced)
