@@ -233,3 +233,38 @@ def test_pdf_ocr_hook_is_used_for_image_only_pages():
     calls = []
     pages = PDFParser().extract_pages(raw, "", ocr_fn=lambda data, hint: calls.append(hint) or "scanned text")
     assert pages == [""] and calls == []          # no images on the page: nothing to hand to the hook
+
+
+def test_reference_named_crypto_and_format_helpers(tmp_path):
+    """Function names of the reference's rag / format / cache modules that callers may import directly."""
+    import numpy as np
+    from helpers.make_pdf import make_pdf
+    from zse_b200.cache.attention_metadata import build_attention_metadata
+    from zse_b200.format import fast_quant
+    from zse_b200.format.spec import align_offset
+    from zse_b200.rag import pdf_crypto as pc
+    from zse_b200.rag.dense import dense_cosine
+    from zse_b200.rag.zpf import compress_csv, decompress_zpf
+    key, iv = bytes(range(16)), bytes(range(16, 32))
+    ct = pc.aes128_cbc_encrypt(key, iv, b"attack at dawn")
+    assert pc.aes128_cbc_decrypt(key, iv + ct) == b"attack at dawn"
+    k32 = bytes(range(32))
+    assert pc.aes256_cbc_decrypt(k32, pc.aes256_cbc_encrypt(k32, iv, b"x" * 40), iv=iv) == b"x" * 40
+    plain = make_pdf([["hello"]])
+    assert pc.detect_encryption(plain) is None
+    locked = make_pdf([["secret text"]], encrypt="aes128", user_pw="pw", owner_pw="own")
+    enc = pc.detect_encryption(locked)
+    assert enc is not None and enc.supported and enc.uses_aes_for_streams and enc.file_key is None
+    assert not enc.derive_file_key(b"nope") and enc.derive_file_key(b"pw") and enc.file_key
+    assert pc.find_stream_object_numbers(plain)
+    a = np.array([1.0, 0.0, 1.0], np.float32)
+    assert abs(dense_cosine(a.tobytes(), a.tobytes()) - 1.0) < 1e-6
+    assert abs(dense_cosine(a.astype(np.float16).tobytes(), a.astype(np.float16).tobytes(), np.float16) - 1.0) < 1e-3
+    doc = compress_csv("city,temp\nParis,20\nParis,21\nParis,19\nRome,25\n")
+    assert "Paris" in decompress_zpf(doc.compressed)
+    md = build_attention_metadata([[3, 4], [7]], [20, 5], 16)
+    assert md.num_seqs == 2 and md.max_blocks_per_seq == 2 and md.block_tables_nbytes == 16
+    assert align_offset(4097, 4096) == 8192
+    w = (np.arange(256) / 100.0).astype(np.float32)
+    p, s, z = fast_quant.quantize_tensor_fast(w.tobytes(), "F32", 256)
+    assert len(p) == 128 and len(s) == 4 and len(z) == 4

@@ -32,3 +32,19 @@ class AttentionMetadata:
 
     def pack_seq_lengths(self) -> bytes:
         return struct.pack(f"<{self.num_seqs}i", *self.seq_lengths)
+
+    @property
+    def block_tables_nbytes(self) -> int:
+        return self.num_seqs * max(1, self.max_blocks_per_seq) * 4
+
+    @property
+    def seq_lengths_nbytes(self) -> int:
+        return self.num_seqs * 4
+
+
+def build_attention_metadata(block_ids_per_seq: List[List[int]], seq_lengths: List[int],
+                             block_size: int) -> AttentionMetadata:
+    """From page-table state (zse-engine/zse_engine/cache/attention_metadata.py:66-89)."""
+    return AttentionMetadata([list(b) for b in block_ids_per_seq], list(seq_lengths), len(seq_lengths),
+                             max(seq_lengths, default=0), max((len(b) for b in block_ids_per_seq), default=0),
+                             block_size)

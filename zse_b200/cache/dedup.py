@@ -64,6 +64,18 @@ class BlockDedup:
         self._hash_of_block[block_id] = chain_hash
         self._pool.get_block(block_id).content_hash = chain_hash
 
+    def register_block(self, block_id: int, token_ids: Sequence[int], prev_hash: int = 0) -> Optional[int]:
+        """The reference's one-call form (zse-engine/zse_engine/cache/dedup.py:50-95): returns the id of an existing
+        block with the same content (and the same prefix chain, ``prev_hash``) after taking a reference on it, or
+        registers ``block_id`` and returns None."""
+        h = fnv1a_chain(prev_hash, token_ids)
+        hit = self.lookup(h, token_ids, prev_hash)
+        if hit is not None and hit != block_id:
+            self._pool.increment_ref(self._pool.get_block(hit))
+            return hit
+        self.register(block_id, h, token_ids, prev_hash)
+        return None
+
     def deregister_block(self, block_id: int) -> None:
         h = self._hash_of_block.pop(block_id, None)
         if h is not None:

@@ -48,6 +48,11 @@ def should_quantize(tensor_name: str) -> bool:
     return not any(s in low for s in KEEP_FP16_SUBSTRINGS)
 
 
+def align_offset(offset: int, alignment: int) -> int:
+    """The reference's name for ``align_up``."""
+    return align_up(offset, alignment)
+
+
 def align_up(offset: int, alignment: int) -> int:
     return (offset + alignment - 1) // alignment * alignment
 

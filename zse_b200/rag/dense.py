@@ -51,3 +51,14 @@ class DenseEmbedder:
             return 0.0
         d = float(np.linalg.norm(x) * np.linalg.norm(y))
         return float(np.dot(x, y)) / d if d > 0 else 0.0
+
+
+def dense_cosine(query_emb: bytes, doc_emb: bytes, dtype=np.float32) -> float:
+    """Cosine similarity of two stored embeddings (the reference's helper, zse-engine/zse_engine/rag/
+    dense_embedder.py:119-131).  Vectors of this package are fp32; pass ``dtype=np.float16`` for blobs written by the
+    reference."""
+    if not query_emb or not doc_emb or len(query_emb) != len(doc_emb):
+        return 0.0
+    x, y = np.frombuffer(query_emb, dtype).astype(np.float32), np.frombuffer(doc_emb, dtype).astype(np.float32)
+    d = float(np.linalg.norm(x) * np.linalg.norm(y))
+    return float(np.dot(x, y)) / d if d > 0 else 0.0

@@ -244,15 +244,18 @@ def apply_filters(data: bytes, d: bytes) -> bytes:
 
 # ---- document model ------------------------------------------------------------------------------------------------
 class PDFDocument:
-    def __init__(self, raw: bytes, password: str = ""):
+    def __init__(self, raw: bytes, password: Optional[str] = "", authenticate: bool = True):
+        """``authenticate=False`` only reads the /Encrypt parameters (no password check, no object streams)."""
         if not raw.lstrip()[:5].startswith(b"%PDF"):
             raise PDFError("not a PDF file")
         self.raw = raw
+        self._authenticate = authenticate
         self.objects: Dict[int, Tuple[int, bytes, Optional[Tuple[int, int]]]] = {}   # num -> (gen, dict/body, stream span)
         self.enc: Optional[PDFEncryption] = None
         self._scan()
         self._setup_encryption(password)
-        self._expand_object_streams()
+        if authenticate or self.enc is None:
+            self._expand_object_streams()
 
     def _scan(self) -> None:
         raw = self.raw
@@ -316,7 +319,7 @@ class PDFDocument:
                                  _string(_name_value(ed, b"/U")), p, file_id, not (em and em.strip() == b"false"),
                                  _string(_name_value(ed, b"/OE")), _string(_name_value(ed, b"/UE")), aes)
         self._encrypt_obj = int(m.group(1)) if m else -1
-        if not self.enc.authenticate(password or ""):
+        if self._authenticate and not self.enc.authenticate(password or ""):
             raise PDFError("password required" if not password else "wrong password")
 
     def stream(self, num: int) -> bytes:

@@ -155,6 +155,24 @@ def aes_cbc_decrypt(key: bytes, data: bytes, iv: Optional[bytes] = None, unpad: 
     return bytes(out)
 
 
+# the reference's names for the two key sizes (zse-engine/zse_engine/rag/pdf_crypto.py:182-337); the key length selects
+# the variant here
+def aes128_cbc_decrypt(key: bytes, data: bytes) -> bytes:
+    return aes_cbc_decrypt(key[:16], data)
+
+
+def aes128_cbc_encrypt(key: bytes, iv: bytes, data: bytes, pad: bool = True) -> bytes:
+    return aes_cbc_encrypt(key[:16], iv, data, pad)
+
+
+def aes256_cbc_decrypt(key: bytes, data: bytes, iv: Optional[bytes] = None, strip_pad: bool = True) -> bytes:
+    return aes_cbc_decrypt(key[:32], data, iv, strip_pad)
+
+
+def aes256_cbc_encrypt(key: bytes, iv: bytes, data: bytes, pad: bool = True) -> bytes:
+    return aes_cbc_encrypt(key[:32], iv, data, pad)
+
+
 # ---- key derivation -------------------------------------------------------------------------------------------------
 def _pad_password(pw: bytes) -> bytes:
     return (pw + PAD)[:32]
@@ -259,8 +277,62 @@ class PDFEncryption:
             h.update(b"sAlT")
         return h.digest()[:min(len(self.key) + 5, 16)]
 
+    # the reference's accessors (pdf_crypto.py:635-760)
+    @property
+    def supported(self) -> bool:
+        if self.v in (1, 2, 4) and self.r in (2, 3, 4):
+            return True
+        return self.v == 5 and self.r in (5, 6) and len(self.u) >= 48 and len(self.ue) == 32
+
+    @property
+    def uses_aes_for_streams(self) -> bool:
+        return self.v == 5 or bool(self.aes)
+
+    uses_aes_for_strings = uses_aes_for_streams
+
+    def derive_file_key(self, password: bytes = b"") -> bool:
+        pw = password.decode("utf-8" if self.r >= 5 else "latin-1", "replace") if isinstance(password, bytes) \
+            else str(password)
+        return self.supported and self.authenticate(pw)
+
+    @property
+    def file_key(self) -> Optional[bytes]:
+        return self.key
+
+    def decrypt_stream(self, obj_num: int, gen_num: int, data: bytes) -> bytes:
+        return b"" if self.key is None else self.decrypt(data, obj_num, gen_num)
+
+    decrypt_string = decrypt_stream
+
     def decrypt(self, data: bytes, num: int, gen: int) -> bytes:
         if self.key is None:
             raise RuntimeError("authenticate() first")
         k = self._object_key(num, gen)
         return aes_cbc_decrypt(k, data) if self.aes else rc4(k, data)
+
+
+def detect_encryption(raw: bytes) -> Optional[PDFEncryption]:
+    """The /Encrypt parameters of a PDF file, or None when it is not encrypted (or too damaged to tell)."""
+    from .pdf import PDFDocument, PDFError
+    try:
+        return PDFDocument(raw, password=None, authenticate=False).enc
+    except (PDFError, ValueError, KeyError, TypeError):
+        return None
+
+
+def find_stream_object_numbers(raw: bytes):
+    """``{offset of the stream data: (object number, generation)}`` for every ``N G obj ... stream`` in the file."""
+    import re
+    out = {}
+    for m in re.finditer(rb"(\d+)\s+(\d+)\s+obj\b", raw):
+        end = raw.find(b"endobj", m.end())
+        s = raw.find(b"stream", m.end(), end if end >= 0 else len(raw))
+        if s < 0:
+            continue
+        s += 6
+        if raw[s:s + 2] == b"\r\n":
+            s += 2
+        elif raw[s:s + 1] in (b"\n", b"\r"):
+            s += 1
+        out[s] = (int(m.group(1)), int(m.group(2)))
+    return out

@@ -218,3 +218,6 @@ def decompress(compressed: str) -> str:
                 continue
         out.append(line)
     return "\n".join(out)
+
+
+decompress_zpf = decompress      # the reference's name (zse-engine/zse_engine/rag/zpf_format.py:334)

@@ -20,6 +20,16 @@ ERROR_TYPES = {400: "invalid_request_error", 401: "authentication_error", 403: "
                504: "timeout_error"}
 
 
+class _JsonObject(dict):
+    def __call__(self):
+        return self
+
+
+class _JsonArray(list):
+    def __call__(self):
+        return self
+
+
 @dataclass
 class Request:
     method: str
@@ -32,16 +42,27 @@ class Request:
 
     @property
     def json(self) -> Optional[Any]:
+        """The decoded body (None when absent or malformed).  Objects and arrays can also be CALLED and return
+        themselves, so a handler written for the reference's ``request.json()`` method works unchanged."""
         if not self.body:
             return None
         try:
-            return json.loads(self.body.decode("utf-8"))
+            obj = json.loads(self.body.decode("utf-8"))
         except (ValueError, UnicodeDecodeError):
             return None
+        if isinstance(obj, dict):
+            return _JsonObject(obj)
+        if isinstance(obj, list):
+            return _JsonArray(obj)
+        return obj
 
     @property
     def authorization(self) -> Optional[str]:
         return self.headers.get("authorization")
+
+    @property
+    def content_type(self) -> str:
+        return self.headers.get("content-type", "")
 
 
 @dataclass
@@ -68,6 +89,22 @@ class Response:
     def sse(cls, iterator) -> "Response":
         return cls(200, b"", {"Content-Type": "text/event-stream", "Cache-Control": "no-cache",
                               "Connection": "keep-alive"}, iterator)
+
+    # the reference's constructor names (zse-engine/zse_engine/server/router.py:49-98)
+    @classmethod
+    def json(cls, data: Any, status: int = 200) -> "Response":
+        return cls.json_response(data, status)
+
+    @classmethod
+    def html(cls, content: str, status: int = 200) -> "Response":
+        return cls.text(content, status, "text/html; charset=utf-8")
+
+    @classmethod
+    def streaming(cls, iterator=None) -> "Response":
+        """Headers of an event stream; ``iterator`` (async, yielding bytes) is sent as the body."""
+        r = cls.sse(iterator)
+        r.headers["X-Accel-Buffering"] = "no"
+        return r
 
 
 Handler = Callable[[Request], Awaitable[Response]]
@@ -102,6 +139,10 @@ class Router:
 
     def static(self, url_prefix: str, directory: str) -> None:
         self._static.append((url_prefix.rstrip("/") + "/", os.path.abspath(directory)))
+
+    def set_static_dir(self, path: str) -> None:
+        """Serves files of ``path`` for non-API paths (the reference's name for ``static("/", path)``)."""
+        self.static("/", path)
 
     def routes(self) -> List[Tuple[str, str]]:
         return [(m, rx.pattern) for m, rx, _, _ in self._routes]

@@ -27,3 +27,18 @@ def chat_chunk(completion_id: str, model: str, content: Optional[str] = None, ro
 def completion_chunk(completion_id: str, model: str, text: str = "", finish_reason: Optional[str] = None) -> bytes:
     return sse_event({"id": completion_id, "object": "text_completion", "created": int(time.time()), "model": model,
                       "choices": [{"index": 0, "text": text, "finish_reason": finish_reason}]})
+
+
+# the reference's names (zse-engine/zse_engine/server/sse.py:18-85)
+def sse_done() -> bytes:
+    return SSE_DONE
+
+
+def sse_chat_chunk(completion_id: str, model: str, token_text: str, finish_reason: Optional[str] = None,
+                   role: Optional[str] = None) -> bytes:
+    return chat_chunk(completion_id, model, token_text if token_text else None, role, finish_reason)
+
+
+def sse_completion_chunk(completion_id: str, model: str, token_text: str,
+                         finish_reason: Optional[str] = None) -> bytes:
+    return completion_chunk(completion_id, model, token_text, finish_reason)
