@@ -162,6 +162,28 @@ def test_tp_engine_cpu_ranks_match_single_engine_and_survive_a_rank_failure(tmp_
         e.stop()
 
 
+@pytest.mark.timeout(600)
+def test_tp_engine_phi3_stacked_projections(tmp_path):
+    """Phi-3's stacked ``qkv_proj`` / ``gate_up_proj`` tensors are sharded part by part (each rank takes its heads from
+    the q, k and v sections, its rows from the gate and up sections)."""
+    path = str(tmp_path / "phi3.zse")
+    synth.write_random_model(path, synth.shape_config("tiny-phi3"), seed=6)
+    cfg = EngineConfig(device="cpu", kv_blocks=64, max_batch_seqs=4, max_batch_tokens=64, max_seq_len=256)
+    rng = random.Random(1)
+    prompts = [[rng.randrange(1024) for _ in range(10)] for _ in range(2)]
+    ref = ZStreamerEngine(path, config=cfg)
+    ids = [ref.add_request_tokens(x, max_tokens=6, temperature=0.0, stop_tokens=[]) for x in prompts]
+    ref.run_until_done()
+    want = [ref.get_result(i).output_tokens for i in ids]
+    e = _tp_engine(path, cfg)
+    try:
+        ids = [e.add_request_tokens(x, max_tokens=6, temperature=0.0, stop_tokens=[]) for x in prompts]
+        e.run_until_done(120)
+        assert [e.get_result(i).output_tokens for i in ids] == want
+    finally:
+        e.stop()
+
+
 # ---- LoRA manager ---------------------------------------------------------------------------------------------------
 def test_lora_manager_slots_and_effect_on_outputs(tmp_path):
     from zse_b200.lora.weights import random_adapter_file

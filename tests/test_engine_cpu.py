@@ -241,3 +241,19 @@ def test_single_request_engine_has_the_reference_call_signatures(model_path, ora
     assert st.weight_bytes > 0 and st.kv_cache_bytes > 0 and st.scratch_bytes > 0 and st.avg_tokens_per_sec > 0
     assert eng.config.hidden_size == 256 and "llama" in eng.summary()
     eng.destroy()
+
+
+@pytest.mark.parametrize("quant", ["int4", "fp16"])
+def test_phi3_stacked_projections_match_oracle(tmp_path, quant):
+    """Phi-3 files keep ``[q; k; v]`` and ``[gate; up]`` stacked (zse-engine/zse_engine/format/arch/phi3.py): the engine
+    splits them into the same fused projections as every other family."""
+    p = str(tmp_path / "phi3.zse")
+    synth.write_random_model(p, synth.shape_config("tiny-phi3", quant=quant), seed=6)
+    oracle = OracleModel(ZSELoader(p))
+    eng = ZStreamerEngine(p, config=_cfg())
+    assert eng.model_config.arch == "phi3"
+    prompts = _prompts(eng.model_config.vocab_size, 3, seed=4)
+    outs = _run(eng, prompts, 10)
+    for pr, o in zip(prompts, outs):
+        assert o.output_tokens == oracle.greedy(pr, 10)
+    eng.destroy()

@@ -35,6 +35,12 @@ def _qwen2():
     return Qwen2ForCausalLM(Qwen2Config(**COMMON, rms_norm_eps=1e-6, rope_theta=1e6, tie_word_embeddings=True))
 
 
+def _phi3():
+    from transformers import Phi3Config, Phi3ForCausalLM
+    return Phi3ForCausalLM(Phi3Config(**COMMON, rms_norm_eps=1e-5, rope_theta=10000.0, pad_token_id=0,
+                                      tie_word_embeddings=False))
+
+
 def _gemma2():
     from transformers import Gemma2Config, Gemma2ForCausalLM
     return Gemma2ForCausalLM(Gemma2Config(**COMMON, head_dim=32, sliding_window=8, query_pre_attn_scalar=24,
@@ -69,10 +75,10 @@ def _randomise(model, seed):
                 p.copy_(0.08 * torch.randn(p.shape, generator=g))
 
 
-@pytest.mark.parametrize("family", ["llama", "mistral", "qwen2", "gemma2", "gemma4", "gemma4_k_eq_v"])
+@pytest.mark.parametrize("family", ["llama", "mistral", "qwen2", "phi3", "gemma2", "gemma4", "gemma4_k_eq_v"])
 def test_oracle_matches_transformers(tmp_path, family):
     torch.manual_seed(0)
-    build = {"llama": _llama, "mistral": _mistral, "qwen2": _qwen2, "gemma2": _gemma2, "gemma4": _gemma4,
+    build = {"llama": _llama, "mistral": _mistral, "qwen2": _qwen2, "phi3": _phi3, "gemma2": _gemma2, "gemma4": _gemma4,
              "gemma4_k_eq_v": lambda: _gemma4(True)}[family]
     model = build().eval().float()
     _randomise(model, 1)

@@ -19,6 +19,21 @@ class AttentionMetadata:
     max_blocks_per_seq: int
     block_size: int
     is_prefill: Optional[List[bool]] = None
+    # device copies, set by ``upload`` (0 until then): int32 ``[num_seqs, max_blocks_per_seq]`` and ``[num_seqs]``
+    block_tables_gpu_ptr: int = 0
+    seq_lengths_gpu_ptr: int = 0
+    block_tables_gpu: Optional[object] = None
+    seq_lengths_gpu: Optional[object] = None
+
+    def upload(self, device) -> "AttentionMetadata":
+        """Copies both arrays to ``device`` and records their addresses.  The serving loop does not use this: it stages
+        the tables of a step through pinned buffers into fixed device buffers (``cache_manager.stage_decode``)."""
+        import torch
+        self.block_tables_gpu = torch.from_numpy(self.block_table_array()).to(device)
+        self.seq_lengths_gpu = torch.tensor(self.seq_lengths, dtype=torch.int32).to(device)
+        self.block_tables_gpu_ptr = int(self.block_tables_gpu.data_ptr())
+        self.seq_lengths_gpu_ptr = int(self.seq_lengths_gpu.data_ptr()) if self.num_seqs else 0
+        return self
 
     def block_table_array(self, width: Optional[int] = None) -> np.ndarray:
         w = self.max_blocks_per_seq if width is None else width

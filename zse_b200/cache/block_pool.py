@@ -24,9 +24,17 @@ class Block:
     token_start: int = 0
     num_tokens: int = 0
 
+    layer_block_bytes: int = 0       # bytes of this block inside one layer's section of the slab (K and V)
+
     @property
     def is_shared(self) -> bool:
         return self.ref_count > 1
+
+    @property
+    def gpu_offset(self) -> int:
+        """Byte offset of the block inside a layer's section of the slab (the slab is layer-major, so a block has
+        one such run per layer, all at this offset from their layer's start)."""
+        return self.block_id * self.layer_block_bytes
 
 
 class BlockPool:
@@ -88,11 +96,46 @@ class BlockPool:
     def utilization(self) -> float:
         return self.num_allocated / self._num_blocks
 
+    # ---- addresses (zse-engine/zse_engine/cache/block_pool.py:163-258, for this pool's layer-major slab) -------
+    @property
+    def layer_block_bytes(self) -> int:
+        _, _, two, kvh, bs, hd = self._shape
+        return two * kvh * bs * hd * 2
+
+    @property
+    def is_uniform_kv(self) -> bool:
+        """Every layer has the same row size in the pool: models whose layers differ (Gemma-4) get rows of the
+        widest layer and narrower layers use a strided view of them."""
+        return True
+
+    def layer_kv_elems(self, layer: int) -> int:
+        """K elements per token in the pool's rows (V is the same size)."""
+        return self._shape[3] * self._shape[5]
+
+    def layer_byte_offset(self, layer: int) -> int:
+        """Byte offset of a layer's section inside the slab."""
+        return layer * self._num_blocks * self.layer_block_bytes
+
+    def _base_ptr(self) -> int:
+        if self.slab is None:
+            raise RuntimeError("this pool only does bookkeeping (no device slab)")
+        return int(self.slab.data_ptr())
+
+    def gpu_ptr_for_block_layer(self, block: Block, layer: int) -> int:
+        """Address of the block's K run of ``layer`` (``[kv_heads, block_size, head_dim]`` fp16, V follows it)."""
+        return self._base_ptr() + self.layer_byte_offset(layer) + block.block_id * self.layer_block_bytes
+
+    def gpu_ptr_for_block(self, block: Block) -> int:
+        return self.gpu_ptr_for_block_layer(block, 0)
+
+    def gpu_ptr_for_kv(self, block: Block, layer: int, is_value: bool) -> int:
+        return self.gpu_ptr_for_block_layer(block, layer) + (self.layer_block_bytes // 2 if is_value else 0)
+
     # ---- alloc / free ---------------------------------------------------------------------------------
     def alloc(self, seq_id: Optional[int] = None) -> Block:
         if not self._free:
             raise MemoryError("KV block pool exhausted")
-        b = Block(self._free.popleft(), seq_id=seq_id)
+        b = Block(self._free.popleft(), seq_id=seq_id, layer_block_bytes=self.layer_block_bytes)
         self._blocks[b.block_id] = b
         return b
 

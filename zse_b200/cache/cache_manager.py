@@ -357,7 +357,12 @@ class KVCacheManager:
         return np.where(blk < 0, -1, blk * self._block_size + pos % self._block_size)
 
     def get_attention_metadata(self, seq_ids: Sequence[int], is_prefill: Optional[List[bool]] = None,
-                               record_access: bool = True) -> AttentionMetadata:
+                               record_access: bool = True, gpu_upload: bool = False) -> AttentionMetadata:
+        """Block tables and lengths of a batch.  ``gpu_upload`` also copies them to the pool's device and fills the
+        ``*_gpu_ptr`` fields (a list of booleans in second position is taken as ``is_prefill``, a bare ``True`` as the
+        reference's ``gpu_upload`` flag)."""
+        if isinstance(is_prefill, bool):
+            gpu_upload, is_prefill = is_prefill, None
         with self._lock:
             tables, lens = [], []
             for sid in seq_ids:
@@ -367,8 +372,11 @@ class KVCacheManager:
                 if record_access:
                     self._evictor.record_batch_access(sid, ids, self._block_size, self._prompt_lengths.get(sid, 0))
             width = max((len(t) for t in tables), default=0)
-            return AttentionMetadata(tables, lens, len(tables), max(lens, default=0), width, self._block_size,
+            meta = AttentionMetadata(tables, lens, len(tables), max(lens, default=0), width, self._block_size,
                                      is_prefill)
+        if gpu_upload and self._pool.slab is not None:
+            meta.upload(self._pool.slab.device)
+        return meta
 
     # ---- facts ----------------------------------------------------------------------------------------
     @property

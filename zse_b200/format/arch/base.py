@@ -71,7 +71,11 @@ class ArchAdapter:
                            rope_scaling=hf.get("rope_scaling"), sliding_window=hf.get("sliding_window"),
                            tie_word_embeddings=bool(hf.get("tie_word_embeddings", tie)))
 
+    #: explicit renames (HF name -> stored name) applied before the ``model.`` prefix is stripped
+    TENSOR_NAME_MAP: Dict[str, str] = {}
+
     def map_tensor_name(self, hf_name: str) -> str:
+        hf_name = self.TENSOR_NAME_MAP.get(hf_name, hf_name)
         return hf_name[6:] if hf_name.startswith("model.") else hf_name
 
     def should_quantize(self, tensor_name: str) -> bool:

@@ -22,6 +22,8 @@ SHAPES = {
     "tiny-aligned": dict(num_layers=2, hidden_size=256, num_heads=4, num_kv_heads=2, head_dim=64,
                          intermediate_size=768, vocab_size=1024, rms_norm_eps=1e-6, rope_theta=10000.0, arch="qwen2",
                          max_seq_len=2048),
+    "tiny-phi3": dict(num_layers=2, hidden_size=256, num_heads=4, num_kv_heads=2, head_dim=64, intermediate_size=768,
+                      vocab_size=1024, rms_norm_eps=1e-5, rope_theta=10000.0, arch="phi3", max_seq_len=2048),
     "small-128": dict(num_layers=2, hidden_size=512, num_heads=4, num_kv_heads=2, head_dim=128,
                       intermediate_size=1024, vocab_size=2048, rms_norm_eps=1e-6, rope_theta=1e6, arch="qwen2",
                       max_seq_len=4096),
@@ -88,6 +90,10 @@ def layer_weight_shapes(c: ModelConfig, layer: int = 0):
     sp = c.layer_spec(layer) if c.is_gemma else None
     q_dim = c.num_heads * sp.head_dim if sp else c.q_dim
     kv_dim = sp.num_kv_heads * sp.head_dim if sp else c.kv_dim
+    if c.arch == "phi3":        # [q; k; v] and [gate; up] are stored stacked
+        return [("self_attn.qkv_proj", q_dim + 2 * kv_dim, c.hidden_size), ("self_attn.o_proj", c.hidden_size, q_dim),
+                ("mlp.gate_up_proj", 2 * c.intermediate_size, c.hidden_size),
+                ("mlp.down_proj", c.hidden_size, c.intermediate_size)]
     out = [("self_attn.q_proj", q_dim, c.hidden_size), ("self_attn.k_proj", kv_dim, c.hidden_size)]
     if not (sp and sp.k_is_v):
         out.append(("self_attn.v_proj", kv_dim, c.hidden_size))

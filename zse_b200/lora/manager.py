@@ -248,6 +248,28 @@ class LoRAManager:
                                    self._rank, tmp=b.lora_tmp)
         return out
 
+    def apply_lora(self, out: torch.Tensor, inp: torch.Tensor, adapter, layer_idx: int, module_name: str, M: int,
+                   N: Optional[int] = None, K: Optional[int] = None) -> bool:
+        """``out[:M, :N] += (alpha / rank) * (inp[:M, :K] A^T) B^T`` for ONE adapter, on whatever device the tensors
+        live (zse-engine/zse_engine/orchestrator/lora_manager.py:255-330).  ``adapter``: a ``LoRAAdapter`` or its id.
+        For callers that apply an adapter to a projection themselves; the engine's passes use the batched tables
+        (``apply_qkv`` / ``delta``: one shrink and one expand launch for every adapter in the batch).  Returns False
+        when the adapter has no weights for the module."""
+        if isinstance(adapter, str):
+            adapter = self._store.get(adapter)
+        w = adapter.get_weight(layer_idx, module_name) if adapter is not None else None
+        if w is None or not w.loaded:
+            return False
+        N = w.out_features if N is None else N
+        K = w.in_features if K is None else K
+        if (N, K) != (w.out_features, w.in_features):
+            raise ValueError(f"{module_name} of layer {layer_idx} is [{w.out_features}, {w.in_features}], not [{N}, {K}]")
+        a, b_ = w.a.to(inp.device), w.b.to(inp.device)
+        tmp = inp[:M, :K].float() @ a.float().t()
+        # the resident tables are padded to the table rank (zeros) and, on a sharded model, hold this rank's rows
+        out[:M, : b_.shape[0]] += (adapter.scaling * (tmp @ b_.float().t())).to(out.dtype)
+        return True
+
     def apply_qkv(self, layer: int, b, M: int) -> None:
         """Adds every resident adapter's update to the fused QKV output of ``layer`` for the first ``M`` tokens."""
         ops = self._model.ops

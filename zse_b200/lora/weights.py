@@ -39,6 +39,19 @@ class LoRAWeight:
     def b_shape(self) -> Tuple[int, int]:
         return (self.out_features, self.rank)
 
+    @staticmethod
+    def _ptr(t) -> int:
+        return int(t.data_ptr()) if t is not None and hasattr(t, "data_ptr") else 0
+
+    @staticmethod
+    def _nbytes(t) -> int:
+        return int(t.numel() * t.element_size()) if t is not None and hasattr(t, "numel") else 0
+
+    a_ptr = property(lambda self: self._ptr(self.a))
+    b_ptr = property(lambda self: self._ptr(self.b))
+    a_nbytes = property(lambda self: self._nbytes(self.a))
+    b_nbytes = property(lambda self: self._nbytes(self.b))
+
     def make_a_tensor(self):
         return self.a
 
@@ -55,6 +68,8 @@ class LoRAAdapter:
     num_layers: int
     weights: Dict[Tuple[int, str], LoRAWeight] = field(default_factory=dict)
     slot: int = -1           # index in the batched weight tables (-1 = not resident)
+    base_model: str = ""     # free-form metadata, as in the reference's record
+    description: str = ""
 
     @property
     def scaling(self) -> float:

@@ -54,6 +54,17 @@ class OracleModel:
         self.w = load_fp32_weights(loader)
         if "lm_head.weight" not in self.w:
             self.w["lm_head.weight"] = self.w["embed_tokens.weight"]
+        c = self.config
+        for i in range(c.num_layers):               # Phi-3 stores [q; k; v] and [gate; up] stacked
+            p = f"layers.{i}."
+            qkv = self.w.pop(p + "self_attn.qkv_proj.weight", None)
+            if qkv is not None:
+                Q, KV = c.num_heads * c.head_dim, c.num_kv_heads * c.head_dim
+                for n, t in zip("qkv", torch.split(qkv, [Q, KV, KV], dim=0)):
+                    self.w[p + f"self_attn.{n}_proj.weight"] = t
+            gu = self.w.pop(p + "mlp.gate_up_proj.weight", None)
+            if gu is not None:
+                self.w[p + "mlp.gate_proj.weight"], self.w[p + "mlp.up_proj.weight"] = torch.chunk(gu, 2, dim=0)
         off = self.config.norm_weight_offset
         if off:
             for name in self.w:

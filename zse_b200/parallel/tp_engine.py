@@ -67,7 +67,13 @@ def _worker(rank: int, world: int, model_path: str, cfg: EngineConfig, port: int
                          max_tokens=max(cfg.max_batch_tokens, cfg.prefill_chunk_size))
         eng = ZStreamerEngine(model_path, config=cfg, comm=comm, tp_rank=rank)
         if rank == 0:
-            ready.put(("ready", eng.init_times))
+            info = dict(eng.init_times)
+            if on_gpu:
+                props = torch.cuda.get_device_properties(dev)
+                info["device_name"], info["device_vram_gb"] = props.name, props.total_memory / 2 ** 30
+            else:
+                info["device_name"], info["device_vram_gb"] = "cpu", 0.0
+            ready.put(("ready", info))
         fail_at = None
         while True:
             beats[rank] += 1
@@ -132,6 +138,20 @@ class TPStats:
     uptime_s: float
     restarts: int
     last_error: Optional[str]
+
+
+@dataclass
+class TPEngineStats:
+    """What start-up cost, under the reference's field names (zse-engine/zse_engine/orchestrator/tp_engine.py:54-62).
+    ``kernel_compile_time_s`` is the time to bring up buffers, graphs and the communication layer: the kernels are
+    built ahead of time."""
+    tp_size: int
+    backend: str
+    device_names: List[str]
+    total_vram_gb: float
+    weight_load_time_s: float
+    kernel_compile_time_s: float
+    total_init_time_s: float
 
 
 class TPEngine:
@@ -438,6 +458,14 @@ class TPEngine:
     def get_result(self, request_id: str) -> Optional[RequestOutput]:
         with self._lock:
             return self._completed.pop(request_id, None)
+
+    def init_stats(self) -> TPEngineStats:
+        t = self.init_times
+        name = str(t.get("device_name", "cpu"))
+        return TPEngineStats(self.tp_size, "cpu" if name == "cpu" else "cuda",
+                             [f"{name} #{r}" for r in range(self.tp_size)],
+                             float(t.get("device_vram_gb", 0.0)) * self.tp_size, float(t.get("weights", 0.0)),
+                             float(t.get("runtime", 0.0)), float(t.get("total", 0.0)))
 
     def stats(self) -> TPStats:
         return TPStats(self._healthy, self.tp_size, self._total_requests, self._total_tokens, len(self._pending),

@@ -68,6 +68,12 @@ class StoredChunk:
     original_tokens: int
     compressed_tokens: int
     has_dense: bool = False
+    dense_vector: Optional[bytes] = None     # filled by ``get_dense_vectors`` callers that want it on the chunk
+
+    @property
+    def token_count(self) -> int:
+        """Tokens of the stored (compressed) text: the reference's field name."""
+        return self.compressed_tokens
 
 
 @dataclass
@@ -80,6 +86,29 @@ class SearchResult:
     score: float
     metadata: Dict[str, Any] = field(default_factory=dict)
     scores: Dict[str, float] = field(default_factory=dict)
+
+    # the reference's per-signal fields (zse-engine/zse_engine/rag/store.py:53-61), read from ``scores``
+    @property
+    def cosine_score(self) -> float:
+        return float(self.scores.get("cosine", self.scores.get("tfidf", 0.0)))
+
+    @property
+    def bm25_score(self) -> float:
+        return float(self.scores.get("bm25", 0.0))
+
+    @property
+    def dense_score(self) -> float:
+        return float(self.scores.get("dense", 0.0))
+
+    @property
+    def rerank_score(self) -> Optional[float]:
+        return self.scores.get("rerank")
+
+    @property
+    def chunk(self) -> "StoredChunk":
+        """The hit as a chunk record (without its sparse vector, which search results do not carry)."""
+        return StoredChunk(self.chunk_id, self.doc_id, int(self.metadata.get("chunk_index", 0)), self.content,
+                           self.compressed, b"", self.metadata, 0, 0)
 
 
 class InvertedIndex:

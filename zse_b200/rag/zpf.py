@@ -90,6 +90,16 @@ class ZPFDocument:
     dictionary: Optional[ZPFDictionary] = None
     original_tokens: int = 0
     compressed_tokens: int = 0
+    doc_type: str = "text"           # "text" | "json" | "csv": which compressor produced it
+
+    # the reference's field names (zse-engine/zse_engine/rag/zpf_format.py:72-80)
+    @property
+    def original_text(self) -> str:
+        return self.original
+
+    @property
+    def compressed_text(self) -> str:
+        return self.compressed
 
     @property
     def savings_pct(self) -> float:
@@ -159,6 +169,12 @@ def compress_records(records: Sequence[Dict[str, Any]], tokenizer=None, original
 
 
 def compress_json(data: Any, tokenizer=None, original: Optional[str] = None) -> ZPFDocument:
+    doc = _compress_json(data, tokenizer, original)
+    doc.doc_type = "json"
+    return doc
+
+
+def _compress_json(data: Any, tokenizer=None, original: Optional[str] = None) -> ZPFDocument:
     if isinstance(data, list) and data and all(isinstance(x, dict) for x in data):
         return compress_records(data, tokenizer, original)
     original = original if original is not None else json.dumps(data, indent=2, ensure_ascii=False)
@@ -193,7 +209,9 @@ def compress_csv(text: str, tokenizer=None) -> ZPFDocument:
         return compress_text(text, tokenizer)
     header, data = rows[0], rows[1:]
     records = [{h: (r[i] if i < len(r) else "") for i, h in enumerate(header)} for r in data]
-    return compress_records(records, tokenizer, original=text)
+    doc = compress_records(records, tokenizer, original=text)
+    doc.doc_type = "csv"
+    return doc
 
 
 def decompress(compressed: str) -> str:

@@ -416,3 +416,113 @@ class ModelRunner:
             return torch.nn.functional.normalize(h, dim=0).cpu()
         finally:
             self.cache.free_sequence(seq_id)
+
+    # ---- the reference's call forms (zse-engine/zse_engine/orchestrator/model_runner.py:675-2010) ---------------
+    # There a caller passes the token, the sequence and its position, the runner extends the cache by one token
+    # itself, and the fp16 logits come back as bytes (or, in the graph variants, the greedy token).  These wrappers
+    # keep that contract on top of ``decode``; the serving loop uses ``decode`` / ``prefill`` directly.
+    @property
+    def hidden_size(self) -> int:
+        return self.model.config.hidden_size
+
+    @property
+    def vocab_size(self) -> int:
+        return self.model.config.vocab_size
+
+    def _logit_rows_bytes(self, n: int) -> List[bytes]:
+        rows = self.buf.logits[:n, : self.vocab_size].to(torch.float16).cpu().numpy()
+        return [rows[i].tobytes() for i in range(n)]
+
+    def batched_decode(self, token_ids: Sequence[int], seq_ids: Sequence[int], positions: Optional[Sequence[int]] = None,
+                       lora_adapter=None, skip_logits_download: bool = False) -> Optional[List[bytes]]:
+        """One token per sequence in one pass; ``positions`` must equal the sequences' current lengths (it is what the
+        cache already knows, and is checked when given).  ``lora_adapter``: an adapter slot for every row, or None."""
+        if len(token_ids) == 0:
+            return []
+        if positions is not None:
+            for sid, pos in zip(seq_ids, positions):
+                have = self.cache.num_tokens(sid)
+                if have != pos:
+                    raise ValueError(f"sequence {sid} holds {have} tokens, not {pos}")
+        for sid in seq_ids:
+            self.cache.extend_sequence(sid, 1)
+        adapters = None if lora_adapter is None else [int(lora_adapter)] * len(seq_ids)
+        self._last_tokens = self.decode(list(seq_ids), list(token_ids), adapters=adapters)
+        return None if skip_logits_download else self._logit_rows_bytes(len(seq_ids))
+
+    def decode_step(self, token_id: int, seq_id: int, position: Optional[int] = None, lora_adapter=None,
+                    skip_logits_download: bool = False) -> Optional[bytes]:
+        out = self.batched_decode([token_id], [seq_id], None if position is None else [position], lora_adapter,
+                                  skip_logits_download)
+        return None if out is None else out[0]
+
+    def gpu_argmax(self, row_idx: int = 0) -> int:
+        """Greedy token of row ``row_idx`` of the last decode pass: it was chosen on the device during the pass, so
+        this reads four bytes' worth of host memory and launches nothing."""
+        toks = getattr(self, "_last_tokens", None)
+        if toks is None or not 0 <= row_idx < len(toks):
+            raise IndexError(f"no decode row {row_idx} to read")
+        return int(toks[row_idx])
+
+    def batched_decode_graph(self, token_ids: Sequence[int], seq_ids: Sequence[int],
+                             positions: Optional[Sequence[int]] = None) -> List[int]:
+        """Greedy tokens of one batched step.  On a GPU the step replays the CUDA graph of its batch bucket (captured
+        on first use); there is no separate un-graphed greedy path to fall back from."""
+        self.batched_decode(token_ids, seq_ids, positions, skip_logits_download=True)
+        return [int(t) for t in self._last_tokens]
+
+    def decode_step_graph(self, token_id: int, seq_id: int, position: Optional[int] = None) -> int:
+        return self.batched_decode_graph([token_id], [seq_id], None if position is None else [position])[0]
+
+    def init_graph(self, max_seq_len: int = 2048) -> None:
+        """Kept for callers of the reference: graphs need no set-up here beyond ``use_graphs`` (buffers are fixed from
+        construction, buckets are captured on first use or by ``precapture_batched_graphs``)."""
+        if max_seq_len > self.max_seq_len:
+            raise ValueError(f"runner was built for sequences of {self.max_seq_len} tokens, not {max_seq_len}")
+
+    def destroy_graph(self) -> None:
+        self.release_graphs()
+
+    def precapture_batched_graphs(self, batch_sizes=(1, 2, 4, 8), warmup_seq_ids=None) -> int:
+        """Captures the decode graph of each batch size's bucket now rather than at its first use in serving.  Runs one
+        throw-away step per bucket on scratch sequences (``warmup_seq_ids`` are accepted and ignored: no caller state
+        is touched).  Returns how many graphs exist afterwards."""
+        if not self.use_graphs:
+            return 0
+        base = 1_000_100_000
+        for m in sorted({min(_bucket(int(x), self.DECODE_BUCKETS), self.max_batch_seqs) for x in batch_sizes}):
+            sids = list(range(base, base + m))
+            made = []
+            try:
+                for sid in sids:
+                    self.cache.allocate_sequence(sid, num_tokens=1)
+                    made.append(sid)
+                self.decode(sids, [0] * m)
+            finally:
+                for sid in made:
+                    self.cache.free_sequence(sid)
+        return len(self._graphs)
+
+
+class TPModelRunner(ModelRunner):
+    """A runner over this rank's shard of the model (zse-engine/zse_engine/orchestrator/model_runner.py:2476-2885).
+    The reference overrides the layer methods to add two all-reduces; here the model object carries the communication
+    layer (``DecoderModel(..., comm=...)``: fused reduce + residual + norm kernels over peer memory, or NCCL), so the
+    runner only checks that a sharded model has one and exposes the group's shape."""
+
+    def __init__(self, model: DecoderModel, cache: KVCacheManager, *args, tp_group=None, **kwargs):
+        if model.plan.tp_size > 1 and model.comm is None:
+            raise ValueError("a sharded model needs a communication layer (pass comm= when the model is built)")
+        if tp_group is not None and (tp_group.tp_size != model.plan.tp_size or tp_group.rank != model.plan.rank):
+            raise ValueError(f"model shard {model.plan.rank}/{model.plan.tp_size} does not belong to "
+                             f"rank {tp_group.rank}/{tp_group.tp_size}")
+        super().__init__(model, cache, *args, **kwargs)
+        self.tp_group = tp_group
+
+    @property
+    def tp_size(self) -> int:
+        return self.model.plan.tp_size
+
+    @property
+    def tp_rank(self) -> int:
+        return self.model.plan.rank

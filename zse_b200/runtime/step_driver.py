@@ -114,3 +114,4 @@ def try_build(model, buffers) -> Optional[NativeStep]:
         return NativeStep(model, buffers)
     except (ValueError, AttributeError):
         return None
+FastDecoder = NativeStep      # the reference's name for its C decode launcher (zse-engine/zse_engine/orchestrator/fast_dispatch.py:341-609)

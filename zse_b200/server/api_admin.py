@@ -131,3 +131,15 @@ class AdminAPI:
         if self._key_id(request) is None:
             return Response.error("authentication required", 401)
         return Response.json_response({"deleted": self._db.delete_session(request.params["session_id"])})
+
+    # the reference's handler names (zse-engine/zse_engine/server/api_admin.py:61-290)
+    handle_create_key = create_key
+    handle_list_keys = list_keys
+    handle_revoke_key = revoke_key
+    handle_update_key = update_key
+    handle_stats = stats
+    handle_usage = usage
+    handle_list_sessions = session_list
+    handle_get_session = session_get
+    handle_delete_session = session_delete
+    handle_save_message = session_add_message

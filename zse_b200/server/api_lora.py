@@ -60,3 +60,9 @@ class LoRAAPI:
         if not m.unload_adapter(str(b["adapter_id"])):
             return Response.error(f"adapter '{b['adapter_id']}' is not loaded", 404)
         return Response.json_response({"unloaded": b["adapter_id"]})
+
+    # the reference's handler names (zse-engine/zse_engine/server/api_lora.py:39-150)
+    handle_list = list_adapters
+    handle_load = load
+    handle_unload = unload
+    handle_stats = stats

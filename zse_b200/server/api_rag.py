@@ -110,3 +110,13 @@ class RAGAPI:
             return Response.error("Admin access required", 403)
         n = await asyncio.to_thread(self._rag.backfill_dense_embeddings)
         return Response.json_response({"embedded": n})
+
+    # the reference's handler names (zse-engine/zse_engine/server/api_rag.py:49-310)
+    handle_upload = upload
+    handle_replace = replace
+    handle_list = list_documents
+    handle_get = get_document
+    handle_delete = delete_document
+    handle_search = search
+    handle_stats = stats
+    handle_backfill_dense = backfill_dense

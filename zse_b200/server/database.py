@@ -56,6 +56,21 @@ class APIKey:
 
 
 @dataclass
+class UsageRecord:
+    """Token usage of one request (a row of the ``usage`` table; zse-engine/zse_engine/server/database.py:39-50)."""
+    id: int
+    key_id: int
+    timestamp: float
+    prompt_tokens: int
+    completion_tokens: int
+    total_tokens: int
+    model: str
+    lora_id: Optional[str]
+    request_id: str
+    latency_ms: float
+
+
+@dataclass
 class ChatMessage:
     id: int
     key_id: int
@@ -180,6 +195,16 @@ class ServerDatabase:
                 args).fetchone()
         return {"total_requests": int(r["n"]), "prompt_tokens": int(r["p"]), "completion_tokens": int(r["c"]),
                 "total_tokens": int(r["t"]), "avg_latency_ms": float(r["l"])}
+
+    def recent_usage(self, key_id: Optional[int] = None, limit: int = 100) -> List[UsageRecord]:
+        """The latest usage rows, newest first."""
+        where, args = ("WHERE key_id=?", (key_id,)) if key_id is not None else ("", ())
+        with self._lock:
+            rows = self._conn.execute(f"SELECT * FROM usage {where} ORDER BY id DESC LIMIT ?",
+                                      args + (int(limit),)).fetchall()
+        return [UsageRecord(r["id"], r["key_id"], r["timestamp"], r["prompt_tokens"], r["completion_tokens"],
+                            r["total_tokens"], r["model"], r["lora_id"], r["request_id"], r["latency_ms"])
+                for r in rows]
 
     def cleanup_old_usage(self, days: int = 30) -> int:
         with self._lock:

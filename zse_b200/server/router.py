@@ -64,6 +64,40 @@ class Request:
     def content_type(self) -> str:
         return self.headers.get("content-type", "")
 
+    # the reference's field names (zse-engine/zse_engine/server/router.py:14-23)
+    @property
+    def query_params(self) -> Dict[str, str]:
+        return self.query
+
+    @property
+    def path_params(self) -> Dict[str, str]:
+        return self.params
+
+    @property
+    def api_key(self) -> Any:
+        """The key record the auth middleware attached (None on open servers and exempt paths)."""
+        return self.context.get("api_key")
+
+    @api_key.setter
+    def api_key(self, key: Any) -> None:
+        self.context["api_key"] = key
+
+
+class Route:
+    """One registered route: ``match(method, path)`` gives the path parameters or None
+    (zse-engine/zse_engine/server/router.py:107-134).  ``*`` as the method matches every method."""
+
+    def __init__(self, method: str, path: str, handler: "Handler"):
+        self.method, self.path, self.handler = method.upper(), path, handler
+        self.names = re.findall(r"\{(\w+)\}", path)
+        self._rx = re.compile("^" + re.sub(r"\{\w+\}", r"([^/]+)", path.rstrip("/") or "/") + "/?$")
+
+    def match(self, method: str, path: str) -> Optional[Dict[str, str]]:
+        if self.method not in ("*", method.upper()):
+            return None
+        m = self._rx.match(path)
+        return None if m is None else {n: unquote(v) for n, v in zip(self.names, m.groups())}
+
 
 @dataclass
 class Response:
@@ -113,14 +147,12 @@ Middleware = Callable[[Request, Handler], Awaitable[Response]]
 
 class Router:
     def __init__(self):
-        self._routes: List[Tuple[str, re.Pattern, List[str], Handler]] = []
+        self._routes: List[Route] = []
         self._middleware: List[Middleware] = []
         self._static: List[Tuple[str, str]] = []
 
     def add(self, method: str, pattern: str, handler: Handler) -> None:
-        names = re.findall(r"\{(\w+)\}", pattern)
-        rx = re.compile("^" + re.sub(r"\{\w+\}", r"([^/]+)", pattern.rstrip("/") or "/") + "/?$")
-        self._routes.append((method.upper(), rx, names, handler))
+        self._routes.append(Route(method, pattern, handler))
 
     def get(self, pattern: str, handler: Handler) -> None:
         self.add("GET", pattern, handler)
@@ -145,21 +177,21 @@ class Router:
         self.static("/", path)
 
     def routes(self) -> List[Tuple[str, str]]:
-        return [(m, rx.pattern) for m, rx, _, _ in self._routes]
+        return [(r.method, r._rx.pattern) for r in self._routes]
 
     async def handle(self, request: Request) -> Response:
         if request.method == "OPTIONS":
             return Response(204, b"", cors_headers())
         path_matched = False
-        for method, rx, names, handler in self._routes:
-            m = rx.match(request.path)
-            if not m:
+        for route in self._routes:
+            if not route._rx.match(request.path):
                 continue
             path_matched = True
-            if method != request.method:
+            params = route.match(request.method, request.path)
+            if params is None:
                 continue
-            request.params = {n: unquote(v) for n, v in zip(names, m.groups())}
-            call = handler
+            request.params = params
+            call = route.handler
             for mw in reversed(self._middleware):
                 call = (lambda h, w: (lambda req: w(req, h)))(call, mw)
             try:
