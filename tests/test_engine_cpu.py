@@ -257,3 +257,22 @@ def test_phi3_stacked_projections_match_oracle(tmp_path, quant):
     for pr, o in zip(prompts, outs):
         assert o.output_tokens == oracle.greedy(pr, 10)
     eng.destroy()
+
+
+def test_step_result_names_the_tokens_of_the_step(model_path, oracle):
+    """``StepResult.new_tokens`` maps each request that advanced to its newest token, as the reference's does."""
+    eng = ZStreamerEngine(model_path, config=_cfg())
+    prompts = _prompts(eng.model_config.vocab_size, 2, seed=9)
+    ids = [eng.add_request_tokens(p, max_tokens=4, temperature=0.0, stop_tokens=[]) for p in prompts]
+    seen = {i: [] for i in ids}
+    for _ in range(50):
+        res = eng.step()
+        assert res.num_tokens == len(res.new_tokens) and res.preempted_ids == []
+        for rid, tok in res.new_tokens.items():
+            seen[rid].append(tok)
+        if not eng.has_work():
+            break
+    eng.step()
+    for rid, p in zip(ids, prompts):
+        assert seen[rid] == oracle.greedy(p, 4) == eng.get_result(rid).output_tokens
+    eng.destroy()

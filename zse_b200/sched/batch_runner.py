@@ -23,6 +23,14 @@ class StepResult:
     tokens_generated: int = 0
     finished: List[RequestOutput] = field(default_factory=list)
     errors: List[str] = field(default_factory=list)
+    # the reference's fields (zse-engine/zse_engine/zstreamer/batch_runner.py:34-47): the latest token of each request
+    # that produced one in this step (speculative steps may produce several; the last is kept), and who was preempted
+    new_tokens: Dict[str, int] = field(default_factory=dict)
+    preempted_ids: List[str] = field(default_factory=list)
+
+    @property
+    def num_tokens(self) -> int:
+        return len(self.new_tokens)
 
 
 def _sampling_row(r: InferenceRequest, ahead: int = 0) -> SamplingRow:
@@ -71,6 +79,7 @@ class BatchRunner:
             self._drop_inflight()          # the batch is being rearranged: take the next step the ordinary way
         for r in plan.preempt_requests:
             self._release_kv(r)
+            res.preempted_ids.append(r.request_id)
         for r in plan.finished_requests:
             self._finalize(r, res)
         if plan.prefill_requests:
@@ -166,6 +175,7 @@ class BatchRunner:
                 self._sched.on_prefill_complete(r, n)
                 if r.state == RequestState.DECODING and not resumed:
                     self._sched.on_token_generated(r, int(tok))
+                    res.new_tokens[r.request_id] = int(tok)
                     res.tokens_generated += 1
 
     # ---- decode -----------------------------------------------------------------------------------------
@@ -236,6 +246,7 @@ class BatchRunner:
             return
         for r, tok in zip(ready, toks):
             self._sched.on_token_generated(r, int(tok))
+            res.new_tokens[r.request_id] = int(tok)
         res.num_decode_tokens += len(ready)
         res.tokens_generated += len(ready)
 
@@ -295,6 +306,9 @@ class BatchRunner:
                                            if self._lora is not None else None)
                 res.num_decode_tokens += len(greedy)
                 res.tokens_generated += produced
+                for r in greedy:
+                    if r.output_tokens:
+                        res.new_tokens[r.request_id] = int(r.output_tokens[-1])
             except Exception as exc:
                 for r in greedy:
                     self._fail(r, exc, res)
