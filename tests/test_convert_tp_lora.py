@@ -352,6 +352,8 @@ def test_tensor_parallel_group_facade():
     assert res[0]["q"] == (0, 256) and res[1]["q"] == (256, 512)
     assert res[0]["down"] == (0, 6912) and res[1]["down"] == (6912, 13824)
     assert res[0]["strategy"] == ["row", "column", "replicated"]
+    assert res[1]["comm"] == {"rank": 1, "nranks": 2, "sum": [3.0] * 3, "rs": [5.0, 7.0]}
+    assert res[0]["comm"]["rs"] == [1.0, 3.0]
     cfg = TPConfig(tp_size=8)
     assert cfg.is_enabled()
     with pytest.raises(ValueError):

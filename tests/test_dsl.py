@@ -378,3 +378,44 @@ def test_autotune_sweeps_block_sizes_with_a_stub_timer():
     stub = Stub()
     res = rmsnorm.autotune(1000, (), block_sizes=(16, 48, 64, 128, 256), tuner=AutoTuner(stub))
     assert stub.seen == [64, 128, 256] and res["best"] == 128      # 16 and 48 are not whole warps
+
+
+@zse.kernel
+def wmma_matmul(a: zse.Tensor[zse.float16], b: zse.Tensor[zse.float16], c: zse.Tensor, n: int, k: int):
+    """One warp per 16x16 tile of C = A [m, k] @ B [k, n] (row-major), fp16 inputs, fp32 accumulation."""
+    acc = zse.wmma_fill(0.0)
+    for kk in range(0, k, 16):
+        fa = zse.wmma_load_a(a, zse.block_id(1) * 16, kk, k)
+        fb = zse.wmma_load_b(b, kk, zse.block_id(0) * 16, n)
+        acc = zse.wmma_mma(fa, fb, acc)
+    zse.wmma_store(c, zse.block_id(1) * 16, zse.block_id(0) * 16, n, acc)
+
+
+def test_tensor_core_tiles_through_wmma(tmp_path, monkeypatch):
+    g = torch.Generator().manual_seed(7)
+    a, b = torch.randn(32, 48, generator=g).half(), torch.randn(48, 16, generator=g).half()
+    c = torch.zeros(32, 16)
+    wmma_matmul.emulate((1, 2), (32,), (a, b, c, 16, 48))
+    torch.testing.assert_close(c, a.float() @ b.float(), atol=1e-4, rtol=1e-4)
+    src = wmma_matmul.source()
+    assert "#include <mma.h>" in src and "nvcuda::wmma::mma_sync(acc, fa, fb, acc);" in src
+    with pytest.raises(zse.KernelLaunchError, match="multiple of 32"):
+        wmma_matmul.emulate((1, 2), (16,), (a, b, c, 16, 48))
+    monkeypatch.setenv("ZSE_KERNEL_CACHE", str(tmp_path))
+    assert zse.RuntimeCompiler().compile(wmma_matmul.source(line_info=True), "wmma_matmul").cubin[:4] == b"\x7fELF"
+
+
+def test_prepacked_arguments_keep_their_storage():
+    x = torch.zeros(8)
+    pre = vector_add.prepack((x, x, x, 8))
+    addr, first = pre.address, pre.values[3].value
+    pre.set(3, 5)
+    y = torch.ones(8)
+    pre.set(0, y)
+    assert (first, pre.values[3].value, pre.address, len(pre)) == (8, 5, addr, 4)
+    assert pre.values[0].value == y.data_ptr() and pre.values[1].value == x.data_ptr()
+    with pytest.raises(zse.KernelTypeError):
+        pre.set(0, torch.zeros(8, dtype=torch.float16))
+    from zse_b200.dsl.dtypes import from_string
+    assert from_string("fp16") is zse.float16 and from_string("bfloat16") is zse.bfloat16
+    assert zse.infer_types(vector_add.ir).var_types["i"] == "int"

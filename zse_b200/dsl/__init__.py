@@ -22,14 +22,18 @@ from .compiler import CompiledKernel, RuntimeCompiler
 from .dtypes import (DType, Tensor, bfloat16, empty, float16, float32, int4, int8, int16, int32, uint4, uint8, uint16,
                      uint32, zeros)
 from .errors import KernelCompileError, KernelError, KernelLaunchError, KernelSyntaxError, KernelTypeError
+from .infer import infer as infer_types
+from .parser import validate_kernel
+
+KernelValidationError = KernelSyntaxError          # the reference's name for what its validator raises
 from .kernel import KernelFunction, fuse, kernel
-from .launcher import KernelLauncher, LaunchConfig
+from .launcher import KernelLauncher, LaunchConfig, PrepackedArgs
 from .memory import GPUMemory
 from .primitives import *          # noqa: F401,F403  (thread_id, warp_reduce_sum, ... for use inside kernels)
 from .primitives import __all__ as _prims
 
 __all__ = ["kernel", "fuse", "KernelFunction", "DType", "Tensor", "empty", "zeros", "float16", "float32", "bfloat16",
            "int32", "int16", "int8", "uint32", "uint16", "uint8", "int4", "uint4", "detect_backend", "get_devices",
-           "DeviceInfo", "GPUMemory", "RuntimeCompiler", "CompiledKernel", "KernelLauncher", "LaunchConfig",
+           "DeviceInfo", "GPUMemory", "RuntimeCompiler", "CompiledKernel", "KernelLauncher", "LaunchConfig", "PrepackedArgs",
            "KernelProfiler", "AutoTuner", "KernelError", "KernelSyntaxError", "KernelTypeError", "KernelCompileError",
            "KernelLaunchError"] + list(_prims)

@@ -15,7 +15,10 @@ from . import dtypes, ir
 from .infer import TypedKernel, widen
 
 _C_SCALAR = {"int": "int", "uint": "unsigned int", "float": "float", "bool": "bool", "half": "__half",
-             "bf16": "__nv_bfloat16", "float4": "float4", "half2": "__half2"}
+             "bf16": "__nv_bfloat16", "float4": "float4", "half2": "__half2",
+             "frag_a": "nvcuda::wmma::fragment<nvcuda::wmma::matrix_a, 16, 16, 16, __half, nvcuda::wmma::row_major>",
+             "frag_b": "nvcuda::wmma::fragment<nvcuda::wmma::matrix_b, 16, 16, 16, __half, nvcuda::wmma::row_major>",
+             "frag_c": "nvcuda::wmma::fragment<nvcuda::wmma::accumulator, 16, 16, 16, float>"}
 _AXIS = "xyz"
 _MATH1 = {"exp": "expf", "log": "logf", "sqrt": "sqrtf", "rsqrt": "rsqrtf", "cos": "cosf", "sin": "sinf",
           "tanh": "tanhf"}
@@ -137,6 +140,8 @@ class CudaEmitter:
         pad = "  " * d
         if isinstance(s, ir.Assign):
             t = self.k.var_types[s.name]
+            if t.startswith("frag_"):
+                return self._wmma_assign(s, pad)
             return [f"{pad}{s.name} = {self._as(s.value, t)};"]
         if isinstance(s, ir.Store):
             elem = self.k.ptr_elem[s.base]
@@ -339,8 +344,28 @@ class CudaEmitter:
             return f"reinterpret_cast<const __half2*>({a[0].name})[{self._val(a[1])}]"
         raise NotImplementedError(f"{n} cannot be used as a value")
 
+    def _wmma_assign(self, s: ir.Assign, pad: str) -> List[str]:
+        self._need("wmma", "#include <mma.h>\n")
+        v = s.value
+        if isinstance(v, ir.Var):
+            return [f"{pad}{s.name} = {v.name};"]
+        n, a = v.func, v.args
+        if n in ("wmma_load_a", "wmma_load_b"):
+            ld = self._as(a[3], "int")
+            return [f"{pad}nvcuda::wmma::load_matrix_sync({s.name}, {a[0].name} + (long long)({self._as(a[1], 'int')}) * "
+                    f"({ld}) + ({self._as(a[2], 'int')}), {ld});"]
+        if n == "wmma_fill":
+            val = self._as(a[0], "float") if a else "0.0f"
+            return [f"{pad}nvcuda::wmma::fill_fragment({s.name}, {val});"]
+        return [f"{pad}nvcuda::wmma::mma_sync({s.name}, {a[0].name}, {a[1].name}, {a[2].name});"]
+
     def _call_stmt(self, e: ir.Call, d: int) -> List[str]:
         pad, n, a = "  " * d, e.func, e.args
+        if n == "wmma_store":
+            self._need("wmma", "#include <mma.h>\n")
+            ld = self._as(a[3], "int")
+            return [f"{pad}nvcuda::wmma::store_matrix_sync({a[0].name} + (long long)({self._as(a[1], 'int')}) * ({ld}) + "
+                    f"({self._as(a[2], 'int')}), {a[4].name}, {ld}, nvcuda::wmma::mem_row_major);"]
         if n == "store_float4":
             vals = ", ".join(self._as(x, "float") for x in a[2:])
             return [f"{pad}reinterpret_cast<float4*>({a[0].name})[{self._val(a[1])}] = make_float4({vals});"]

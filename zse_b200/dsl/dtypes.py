@@ -48,6 +48,16 @@ uint4 = DType("uint4", 4, "unsigned char", "uint", None)
 ALL = {d.name: d for d in (float32, float16, bfloat16, int32, int16, int8, uint32, uint16, uint8, int4, uint4)}
 
 
+def from_string(name: str) -> DType:
+    """``"float16"`` / ``"fp16"`` / ``"half"`` ... -> element type."""
+    alias = {"fp32": "float32", "float": "float32", "fp16": "float16", "half": "float16", "bf16": "bfloat16",
+             "int": "int32", "uint": "uint32"}
+    key = alias.get(name.lower(), name.lower())
+    if key not in ALL:
+        raise ValueError(f"unknown element type '{name}'")
+    return ALL[key]
+
+
 def from_torch(dtype) -> DType:
     name = str(dtype).replace("torch.", "")
     for d in ALL.values():

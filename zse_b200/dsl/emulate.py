@@ -245,6 +245,19 @@ class _Thread:
             for j in range(w):
                 self._store(v[0], w * int(v[1]) + j, f32(v[2 + j]), e)
             return None
+        if n in ("wmma_load_a", "wmma_load_b"):
+            r0, c0, ld = int(v[1]), int(v[2]), int(v[3])
+            return np.array([[self._load(v[0], (r0 + r) * ld + c0 + c, e) for c in range(16)] for r in range(16)], f32)
+        if n == "wmma_fill":
+            return np.full((16, 16), f32(v[0]) if v else f32(0), f32)
+        if n == "wmma_mma":
+            return (v[0].astype(np.float64) @ v[1].astype(np.float64) + v[2]).astype(f32)
+        if n == "wmma_store":
+            r0, c0, ld = int(v[1]), int(v[2]), int(v[3])
+            for r in range(16):
+                for c in range(16):
+                    self._store(v[0], (r0 + r) * ld + c0 + c, v[4][r, c], e)
+            return None
         if n in ("unpack_int4", "unpack_uint4"):
             p, base = int(v[0]) & 0xFFFFFFFF, int(v[2])
             for j in range(8):
@@ -301,7 +314,8 @@ class _Thread:
         if isinstance(s, ir.Assign):
             v = yield from self.ge(s.value)
             t = self.b.k.var_types[s.name]
-            self.env[s.name] = v if t in ("float4", "half2") else _to_scalar(_narrow(v, t), t)
+            self.env[s.name] = (v if t in ("float4", "half2") or t.startswith("frag_")
+                                else _to_scalar(_narrow(v, t), t))
         elif isinstance(s, ir.Store):
             idx = yield from self.ge(s.index)
             v = yield from self.ge(s.value)

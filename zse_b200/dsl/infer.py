@@ -12,7 +12,7 @@ from typing import Dict, List, Optional
 
 from . import dtypes, ir
 from .errors import KernelTypeError
-from .primitives import PRIMITIVES
+from .primitives import FRAGMENTS, PRIMITIVES
 
 _RANK = {"bool": 0, "int": 1, "uint": 2, "float": 3}
 _ELEM_VALUE = {"float32": "float", "float16": "half", "bfloat16": "bf16", "int32": "int", "int16": "int",
@@ -102,7 +102,7 @@ class TypeInference:
     def _set_var(self, name: str, t: str, node) -> None:
         if name in self.k.ptr_elem:
             raise self._err(node, f"'{name}' names a tensor or array and cannot be assigned")
-        if t in ("float4", "half2", "void"):
+        if t in ("float4", "half2", "void") + FRAGMENTS:
             if t == "void":
                 raise self._err(node, "this call gives no value")
             old = self.k.var_types.get(name)
@@ -113,7 +113,7 @@ class TypeInference:
         if name in self._declared:
             return
         old = self.k.var_types.get(name)
-        if old in ("float4", "half2"):
+        if old in ("float4", "half2") + FRAGMENTS:
             raise self._err(node, f"'{name}' is a {old} elsewhere")
         self.k.var_types[name] = widen(t) if old is None else promote(old, t)
 
@@ -229,6 +229,26 @@ class TypeInference:
             for a in args[1:]:
                 self._scalar(a, "an argument")
             return vt
+        if name in ("wmma_load_a", "wmma_load_b", "wmma_store"):
+            want = "float32" if name == "wmma_store" else "float16"
+            if self._ptr_arg(args[0], "the first argument") != want:
+                raise self._err(e, f"{name} works on a {want} tensor or array")
+            for a in args[1:4]:
+                self._scalar(a, "a tile coordinate", integer=True)
+            if name == "wmma_store" and self._expr(args[4]) != "frag_c":
+                raise self._err(e, "wmma_store writes an accumulator fragment (from wmma_fill / wmma_mma)")
+            return rule
+        if name == "wmma_fill":
+            for a in args:
+                self._scalar(a, "the fill value")
+            return rule
+        if name == "wmma_mma":
+            got = tuple(self._expr(a) for a in args)
+            if not all(isinstance(a, ir.Var) for a in args):
+                raise self._err(e, "wmma_mma(a, b, c) takes named fragments")
+            if got != FRAGMENTS:
+                raise self._err(e, f"wmma_mma(a, b, c) takes an A, a B and an accumulator fragment, got {got}")
+            return rule
         if name in ("load_float4", "store_float4"):
             if self._ptr_arg(args[0], "the first argument") != "float32":
                 raise self._err(e, f"{name} needs a float32 tensor")

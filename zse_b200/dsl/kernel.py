@@ -15,9 +15,9 @@ from .compiler import CompiledKernel, RuntimeCompiler, default_compiler
 from .emulate import emulate as _emulate
 from .errors import KernelTypeError
 from .infer import TypedKernel, infer
-from .launcher import KernelLauncher, LaunchConfig, pack_args
+from .launcher import KernelLauncher, LaunchConfig, PrepackedArgs, pack_args
 from .parser import KernelParser, validate_kernel
-from .primitives import COLLECTIVES
+from .primitives import COLLECTIVES, WARP_WIDE
 
 Signature = Tuple[Tuple[str, str], ...]
 
@@ -110,7 +110,8 @@ class KernelFunction:
         return ck
 
     def uses_collectives(self) -> bool:
-        return any(isinstance(e, ir.Call) and e.func in COLLECTIVES and e.func not in ("syncthreads",)
+        return any(isinstance(e, ir.Call) and (e.func in COLLECTIVES or e.func in WARP_WIDE)
+                   and e.func not in ("syncthreads",)
                    for e in ir.walk_exprs(self._ir.body))
 
     def static_shared_bytes(self) -> int:
@@ -135,6 +136,17 @@ class KernelFunction:
         ctypes_ = [k.param_ctype(p) for p in self._ir.params]
         elems = [k.ptr_elem.get(p.name) if p.kind == "tensor" else None for p in self._ir.params]
         self._launcher.launch(ck, cfg, pack_args(ctypes_, args, elems), stream)
+
+    def prepack(self, args: Sequence[Any]) -> PrepackedArgs:
+        """Packs ``args`` once for repeated launches with ``launch_prepacked``; ``set(i, value)`` changes one."""
+        k = self.typed(dict(self._sig_of_args(args)))
+        return PrepackedArgs([k.param_ctype(p) for p in self._ir.params], args,
+                             [k.ptr_elem.get(p.name) if p.kind == "tensor" else None for p in self._ir.params])
+
+    def launch_prepacked(self, grid, block, prepacked: PrepackedArgs, dtypes: Optional[Dict[str, Any]] = None,
+                         shared_mem_bytes: int = 0, stream=None) -> None:
+        self._launcher.launch_prepacked(self.compile("cuda", dtypes), self._config(grid, block, shared_mem_bytes),
+                                        prepacked, stream)
 
     def emulate(self, grid, block, args: Sequence[Any], shared_mem_bytes: int = 0) -> None:
         """The same launch on the CPU (tensors are CPU tensors or numpy arrays, modified in place)."""

@@ -96,7 +96,33 @@ def pack_args(param_ctypes: Sequence[str], args: Sequence[Any], elems: Sequence[
     return out
 
 
+class PrepackedArgs:
+    """The argument array of a kernel, built once and changed in place (``set``): repeated launches skip the packing,
+    and the array keeps its address (zse-compiler/zse_compiler/runtime/launcher.py: ``PrepackedArgs``)."""
+
+    def __init__(self, param_ctypes: Sequence[str], args: Sequence[Any], elems: Sequence[Any] = ()):
+        self._ctypes, self._elems = list(param_ctypes), list(elems) or [None] * len(param_ctypes)
+        self.values = pack_args(param_ctypes, args, elems)
+        self.array = (ctypes.c_void_p * len(self.values))(
+            *[ctypes.cast(ctypes.pointer(v), ctypes.c_void_p) for v in self.values])
+
+    def set(self, index: int, value: Any) -> None:
+        new = pack_args([self._ctypes[index]], [value], [self._elems[index]])[0]
+        self.values[index].value = new.value            # same storage, so ``array`` stays valid
+
+    def __len__(self) -> int:
+        return len(self.values)
+
+    @property
+    def address(self) -> int:
+        return ctypes.addressof(self.array)
+
+
 class KernelLauncher:
+    def launch_prepacked(self, compiled: CompiledKernel, config: LaunchConfig, prepacked: PrepackedArgs,
+                         stream=None) -> None:
+        self.launch(compiled, config, prepacked.values, stream)
+
     def launch(self, compiled: CompiledKernel, config: LaunchConfig, packed: List[Any], stream=None) -> None:
         import torch
         if not torch.cuda.is_available():

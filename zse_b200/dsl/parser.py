@@ -379,6 +379,8 @@ class KernelParser:
             for i in (0, 4) if name == "tile_load" else (0, 1):
                 if not isinstance(args[i], ir.Var):
                     raise self._err(node, f"{name}(): '{order[i]}' must be a named tensor or array")
+        elif name == "wmma_store" and len(node.keywords) == 1 and node.keywords[0].arg == "frag":
+            args.append(self._expr(node.keywords[0].value))
         elif node.keywords:
             if name.startswith("warp_shuffle") and all(k.arg == "width" for k in node.keywords):
                 args.append(self._expr(node.keywords[0].value))
@@ -397,6 +399,10 @@ class KernelParser:
             raise self._err(node, f"{name}(target, ...): the target is an element, e.g. out[0]")
         if name in ("load_float4", "load_half2", "store_float4", "store_half2") and not isinstance(args[0], ir.Var):
             raise self._err(node, f"{name}(): the first argument is a named tensor or array")
+        if name in ("wmma_load_a", "wmma_load_b", "wmma_store") and not isinstance(args[0], ir.Var):
+            raise self._err(node, f"{name}(): the first argument is a named tensor or array")
+        if name == "wmma_store" and not isinstance(args[4], ir.Var):
+            raise self._err(node, "wmma_store(tensor, row, col, stride, frag): frag is an accumulator fragment")
         if name in ("unpack_int4", "unpack_uint4") and not isinstance(args[1], ir.Var):
             raise self._err(node, f"{name}(packed, buf, base): buf is a named array")
         return ir.Call(name, args)

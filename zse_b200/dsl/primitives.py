@@ -33,6 +33,10 @@ PRIMITIVES: Dict[str, Tuple[int, int, str]] = {
     "load_half2": (2, 2, "half2"), "store_half2": (4, 4, "void"),
     "unpack_int4": (3, 3, "void"), "unpack_uint4": (3, 3, "void"),
     "tile_load": (5, 8, "void"), "tile_store": (5, 8, "void"),
+    # warp-wide 16x16x16 fp16 -> fp32 tiles on the tensor cores through nvcuda::wmma (the portable, legacy path:
+    # the engine's own GEMMs issue tcgen05 instructions by hand, which a per-thread language cannot express)
+    "wmma_load_a": (4, 4, "frag_a"), "wmma_load_b": (4, 4, "frag_b"), "wmma_fill": (0, 1, "frag_c"),
+    "wmma_mma": (3, 3, "frag_c"), "wmma_store": (5, 5, "void"),
 }
 
 # handled by the parser as declarations rather than calls
@@ -44,6 +48,11 @@ BUILTINS = {"float": "float", "int": "int", "bool": "bool", "min": "min_val", "m
 COLLECTIVES = {"warp_shuffle_down", "warp_shuffle_up", "warp_shuffle_xor", "warp_shuffle", "warp_ballot", "warp_all",
                "warp_any", "warp_reduce_sum", "warp_reduce_max", "warp_reduce_min", "block_reduce_sum",
                "block_reduce_max", "block_reduce_min", "syncthreads", "tile_load", "tile_store"}
+
+
+# calls every lane of a warp must make together (no value is exchanged in the emulator, but the block must be whole warps)
+WARP_WIDE = {"wmma_load_a", "wmma_load_b", "wmma_fill", "wmma_mma", "wmma_store"}
+FRAGMENTS = ("frag_a", "frag_b", "frag_c")
 
 
 def _marker(name: str):

@@ -139,6 +139,62 @@ class TensorParallelGroup:
         return f"TensorParallelGroup(tp={self.tp_size}, rank={self.rank}, backend={self.backend})"
 
 
+def is_nccl_available(backend: str = "cuda") -> bool:
+    return bool(dist.is_available() and dist.is_nccl_available() and torch.cuda.is_available())
+
+
+class NcclCommunicator:
+    """The communicator of the reference's NCCL wrapper (zse-compiler/zse_compiler/runtime/nccl.py:174-410) for
+    callers that use it directly.  Buffers are tensors here (the reference passes raw device addresses and element
+    counts); collectives run on the current stream of the process group's backend."""
+
+    def __init__(self, nranks: int, rank: int, unique_id=None, backend: str = "cuda", stream: int = 0):
+        self._group = TensorParallelGroup(nranks, rank, backend, unique_id, stream)
+
+    @property
+    def rank(self) -> int:
+        return self._group.rank
+
+    @property
+    def nranks(self) -> int:
+        return self._group.tp_size
+
+    def all_reduce(self, sendbuf: torch.Tensor, recvbuf: Optional[torch.Tensor] = None, count: Optional[int] = None,
+                   dtype=None, op: str = "sum", stream=None) -> torch.Tensor:
+        out = sendbuf if recvbuf is None or recvbuf is sendbuf else recvbuf.copy_(sendbuf)
+        self._group.all_reduce_inplace(out, op)
+        return out
+
+    def all_reduce_inplace(self, buf: torch.Tensor, count: Optional[int] = None, dtype=None, op: str = "sum",
+                           stream=None) -> None:
+        self._group.all_reduce_inplace(buf, op)
+
+    def all_gather(self, sendbuf: torch.Tensor, recvbuf: Optional[torch.Tensor] = None, sendcount=None, dtype=None,
+                   stream=None) -> torch.Tensor:
+        got = self._group.all_gather(sendbuf)
+        return got if recvbuf is None else recvbuf.view(-1).copy_(got.view(-1)).view_as(recvbuf)
+
+    def broadcast(self, buf: torch.Tensor, count=None, dtype=None, root: int = 0, stream=None) -> torch.Tensor:
+        return self._group.broadcast(buf, root)
+
+    def reduce_scatter(self, sendbuf: torch.Tensor, recvbuf: Optional[torch.Tensor] = None, recvcount=None, dtype=None,
+                       op: str = "sum", stream=None) -> torch.Tensor:
+        got = self._group.reduce_scatter(sendbuf)
+        return got if recvbuf is None else recvbuf.view(-1).copy_(got.view(-1)).view_as(recvbuf)
+
+    def barrier(self) -> None:
+        self._group.barrier()
+
+    def stream_synchronize(self) -> None:
+        self._group.sync_stream()
+
+    def destroy(self) -> None:
+        self._group.destroy()
+
+    def __repr__(self) -> str:
+        return f"NcclCommunicator(rank={self.rank}, nranks={self.nranks})"
+
+
 def get_unique_id(backend: str = "cuda") -> bytes:
     """A rendezvous address on this host with a free port, in the place of the reference's NCCL unique id."""
     with socket.socket() as s:
