@@ -53,6 +53,13 @@ def test_keys_create_list_revoke(tmp_path):
     assert zse("keys", "--db-path", db, "revoke", key_id).returncode == 0
     assert "revoked" in zse("keys", "--db-path", db, "list").stdout
     assert zse("keys", "--db-path", db, "revoke", "999").returncode == 1
+    # the reference's spelling: options after the action, --rate-limit-rpm, revoke --id
+    r = zse("keys", "create", "--name", "bob", "--rate-limit-rpm", "9", "--db-path", db)
+    assert r.returncode == 0 and "sk-zse-" in r.stdout
+    listing = zse("keys", "list", "--db-path", db).stdout
+    bob = [l for l in listing.splitlines() if "bob" in l][0]
+    assert "rpm=9" in bob
+    assert zse("keys", "revoke", "--id", bob.split()[0], "--db-path", db).returncode == 0
 
 
 def test_convert_command_and_module_entry(tmp_path):

@@ -129,7 +129,13 @@ def _cmd_warm(a) -> int:
 
 def _cmd_keys(a) -> int:
     from .server.database import ServerDatabase
-    db = ServerDatabase(a.db_path)
+    db = ServerDatabase(getattr(a, "db_path_after", None) or a.db_path)
+    if a.keys_cmd == "revoke":
+        a.id = a.id if a.id is not None else a.id_flag
+        if a.id is None:
+            print("revoke needs a key id or prefix")
+            return 2
+        a.id = str(a.id)
     if a.keys_cmd == "create":
         key, info = db.create_key(a.name, a.rpm, a.tpm, a.models)
         print(f"created key {info.id} ({info.name or 'unnamed'}):\n  {key}\n  (shown once - save it)")
@@ -172,7 +178,7 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--db-path", default="~/.zse/server.db")
     s.add_argument("--model-name", default="zse-model")
     s.add_argument("-q", "--quiet", action="store_true")
-    s.add_argument("--tp", dest="tp_size", type=int, default=1, help="tensor-parallel GPUs")
+    s.add_argument("--tp", "--tensor-parallel", dest="tp_size", type=int, default=1, help="tensor-parallel GPUs")
     s.add_argument("--max-seq-len", type=int, default=0)
     s.add_argument("--max-batch-seqs", type=int, default=64)
     s.add_argument("--prefill-chunk-size", type=int, default=2048)
@@ -207,14 +213,18 @@ def build_parser() -> argparse.ArgumentParser:
     k = sub.add_parser("keys", help="manage API keys")
     k.add_argument("--db-path", default="~/.zse/server.db")
     ks = k.add_subparsers(dest="keys_cmd", required=True)
+    # ``--db-path`` is accepted before or after the action (the reference's CLI takes it after)
     kc = ks.add_parser("create")
     kc.add_argument("--name", default="")
-    kc.add_argument("--rpm", type=int, default=60)
-    kc.add_argument("--tpm", type=int, default=100000)
+    kc.add_argument("--rpm", "--rate-limit-rpm", dest="rpm", type=int, default=60)
+    kc.add_argument("--tpm", "--rate-limit-tpm", dest="tpm", type=int, default=100000)
     kc.add_argument("--models", default="*")
-    ks.add_parser("list")
+    kl = ks.add_parser("list")
     kr = ks.add_parser("revoke")
-    kr.add_argument("id", help="key id or key prefix")
+    kr.add_argument("id", nargs="?", default=None, help="key id or key prefix")
+    kr.add_argument("--id", dest="id_flag", default=None, help="key id (the reference's spelling)")
+    for sp in (kc, kl, kr):
+        sp.add_argument("--db-path", dest="db_path_after", default=None)
     k.set_defaults(fn=_cmd_keys)
     y = sub.add_parser("synth", help="write a random-weight model of a named shape")
     y.add_argument("shape")
