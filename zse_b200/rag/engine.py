@@ -99,6 +99,10 @@ class RAGEngine:
             return {"error": f"could not parse {filename}: {exc}"}
         if not chunks:
             return {"error": "No content could be extracted from the document"}
+        failed = [c for c in chunks if c.metadata.get("error")]
+        if failed and len(failed) == len(chunks):        # the parser's failure marker: nothing worth storing
+            return {"error": f"could not parse {filename}: {failed[0].text.strip('[]')}",
+                    "error_kind": failed[0].metadata["error"]}
         with self._lock:
             token_sets = [set(self._embedder.tokenize(c.text)) for c in chunks]
             self._embedder.update_idf(token_sets)

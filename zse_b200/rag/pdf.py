@@ -237,9 +237,68 @@ def apply_filters(data: bytes, d: bytes) -> bytes:
             data = _ascii85(data)
         elif name in (b"RunLengthDecode", b"RL"):
             data = _run_length(data)
+        elif name in (b"LZWDecode", b"LZW"):
+            data = _lzw(data, _int(parms, b"/EarlyChange", 1))
+            pred = _int(parms, b"/Predictor", 1)
+            if pred >= 10:
+                data = _png_predict(data, _int(parms, b"/Columns", 1), _int(parms, b"/Colors", 1),
+                                    _int(parms, b"/BitsPerComponent", 8))
+        elif name in IMAGE_FILTERS:
+            break              # compressed image data: handed on as it is (an OCR backend decodes it)
         else:
             raise PDFError(f"unsupported filter {name.decode()}")
     return data
+
+
+IMAGE_FILTERS = {b"DCTDecode": "jpeg", b"DCT": "jpeg", b"JPXDecode": "jp2", b"CCITTFaxDecode": "ccitt", b"CCF": "ccitt",
+                 b"JBIG2Decode": "jbig2"}
+
+
+def image_hint(d: bytes) -> str:
+    """What an image stream holds, from its filter names: jpeg, jp2, ccitt, jbig2, or raw samples."""
+    for name in re.findall(rb"/([A-Za-z0-9]+)", _name_value(d, b"/Filter") or b""):
+        if name in IMAGE_FILTERS:
+            return IMAGE_FILTERS[name]
+    return "raw"
+
+
+def _lzw(data: bytes, early_change: int = 1) -> bytes:
+    """LZW as PDF uses it: codes of 9 to 12 bits, most significant bit first, 256 = clear table, 257 = end of data;
+    the code width grows one code early unless ``/EarlyChange 0``."""
+    out = bytearray()
+    table: List[bytes] = []
+
+    def reset() -> None:
+        table[:] = [bytes([i]) for i in range(256)] + [b"", b""]
+
+    reset()
+    width, prev = 9, None
+    acc = bits = 0
+    for byte in data:
+        acc = (acc << 8) | byte
+        bits += 8
+        while bits >= width:
+            code = (acc >> (bits - width)) & ((1 << width) - 1)
+            bits -= width
+            if code == 256:
+                reset()
+                width, prev = 9, None
+                continue
+            if code == 257:
+                return bytes(out)
+            if prev is None:
+                entry = table[code] if code < len(table) else b""
+            elif code < len(table):
+                entry = table[code]
+                table.append(prev + entry[:1])
+            else:
+                entry = prev + prev[:1]
+                table.append(entry)
+            out += entry
+            prev = entry
+            n = len(table) + 1 + (1 if early_change else 0)      # the writer's table is one entry ahead of this one
+            width = 12 if n > 2048 else 11 if n > 1024 else 10 if n > 512 else 9
+    return bytes(out)
 
 
 # ---- document model ------------------------------------------------------------------------------------------------
@@ -300,6 +359,11 @@ class PDFDocument:
             return
         ev = _name_value(tr, b"/Encrypt")
         m = _REF.match(ev.strip()) if ev else None
+        if m and int(m.group(1)) not in self.objects:    # the dictionary may sit in an (unencrypted) object stream
+            try:
+                self._expand_object_streams()
+            except Exception:
+                pass
         ed = self.objects[int(m.group(1))][1] if m and int(m.group(1)) in self.objects else ev
         if not ed:
             raise PDFError("cannot read the /Encrypt dictionary")
@@ -319,8 +383,16 @@ class PDFDocument:
                                  _string(_name_value(ed, b"/U")), p, file_id, not (em and em.strip() == b"false"),
                                  _string(_name_value(ed, b"/OE")), _string(_name_value(ed, b"/UE")), aes)
         self._encrypt_obj = int(m.group(1)) if m else -1
-        if self._authenticate and not self.enc.authenticate(password or ""):
-            raise PDFError("password required" if not password else "wrong password")
+        if not self._authenticate:
+            return
+        if not self.enc.supported:
+            err = PDFError(f"encrypted with a security handler this reader does not have (V={v}, R={r})")
+            err.kind = "encrypted_unsupported"
+            raise err
+        if not self.enc.authenticate(password or ""):
+            err = PDFError("password required" if not password else "wrong password")
+            err.kind = "encrypted_password_required"
+            raise err
 
     def stream(self, num: int) -> bytes:
         gen, d, span = self.objects[num]
@@ -347,7 +419,12 @@ class PDFDocument:
             except Exception:
                 continue
             n, first = _int(d, b"/N"), _int(d, b"/First")
-            nums = [int(x) for x in data[:first].split()]
+            if first <= 0 or first > len(data):          # a header that does not fit the data: skip the container
+                continue
+            try:
+                nums = [int(x) for x in data[:first].split()]
+            except ValueError:
+                continue
             for i in range(min(n, len(nums) // 2)):
                 onum, off = nums[2 * i], nums[2 * i + 1]
                 nxt = nums[2 * i + 3] if 2 * i + 3 < len(nums) else len(data) - first
@@ -449,7 +526,7 @@ class PDFDocument:
                 data = self.raw[a:b]
                 if self.enc is not None:
                     data = self.enc.decrypt(data, n, self.objects[n][0])
-                hint = "jpeg" if b"/DCTDecode" in d else "jp2" if b"/JPXDecode" in d else "raw"
+                hint = image_hint(d)
                 if hint == "raw":
                     try:
                         data = apply_filters(data, d)
@@ -512,107 +589,155 @@ _TOKEN = re.compile(rb"\((?:\\.|[^\\()]|\((?:\\.|[^\\()])*\))*\)|<[0-9A-Fa-f\s]*
 
 
 def extract_text(content: bytes, fonts: Dict[bytes, ToUnicode]) -> str:
-    out: List[str] = []
-    stack: List[Any] = []
-    font = ToUnicode(b"")
-    arr: Optional[List[Any]] = None
-    last_y: Optional[float] = None
-
-    def show(s: bytes) -> None:
-        out.append(font.decode(s))
-
-    def tostr(tok: bytes) -> bytes:
-        return decode_literal(tok[1:-1]) if tok.startswith(b"(") else _string(tok)
-
-    def newline() -> None:
-        if out and not out[-1].endswith("\n"):
-            out.append("\n")
-
-    for m in _TOKEN.finditer(content):
-        t = m.group(0)
-        c = t[:1]
-        if c in b"(<" and t != b"<":
-            (arr if arr is not None else stack).append(tostr(t))
-        elif t == b"[":
-            arr = []
-        elif t == b"]":
-            stack.append(arr or [])
-            arr = None
-        elif c == b"/":
-            stack.append(t)
-        elif c in b"0123456789+-.":
-            try:
-                v = float(t)
-            except ValueError:
-                v = 0.0
-            (arr if arr is not None else stack).append(v)
-        else:
-            op = t
-            if op == b"Tf" and len(stack) >= 2 and isinstance(stack[-2], bytes):
-                font = fonts.get(stack[-2][1:], ToUnicode(b""))
-            elif op == b"Tj" and stack and isinstance(stack[-1], bytes):
-                show(stack[-1])
-            elif op == b"TJ" and stack and isinstance(stack[-1], list):
-                for item in stack[-1]:
-                    if isinstance(item, bytes):
-                        show(item)
-                    elif isinstance(item, float) and item < -200:       # a wide negative kern is a word gap
-                        out.append(" ")
-            elif op in (b"'", b'"') and stack and isinstance(stack[-1], bytes):
-                newline()
-                show(stack[-1])
-            elif op in (b"Td", b"TD") and len(stack) >= 2 and isinstance(stack[-1], float):
-                if abs(stack[-1]) > 0.5:
-                    newline()
-                elif isinstance(stack[-2], float) and stack[-2] > 1.0 and out and not out[-1].endswith((" ", "\n")):
-                    out.append(" ")
-            elif op == b"Tm" and len(stack) >= 6 and isinstance(stack[-1], float):
-                y = stack[-1]
-                if last_y is not None and abs(y - last_y) > 0.5:
-                    newline()
-                elif last_y is not None and out and not out[-1].endswith((" ", "\n")):
-                    out.append(" ")
-                last_y = y
-            elif op == b"T*":
-                newline()
-            elif op == b"ET":
-                newline()
-            stack = []
-    text = "".join(out)
+    """Text of one content stream in reading order (positions are followed and the fragments re-ordered into lines,
+    words and columns: ``pdf_layout``)."""
+    from .pdf_layout import extract_text as _layout
+    text = _layout(content, fonts)
     text = re.sub(r"[ \t]+\n", "\n", text)
     return re.sub(r"\n{3,}", "\n\n", text).strip()
 
 
-class PDFParser:
-    def __init__(self, chunk_size: int = 512, overlap: int = 64):
-        self.chunk_size, self.overlap = chunk_size, overlap
+_BARE_STREAM = re.compile(rb"<<((?:[^<>]|<(?!<)|>(?!>)|<<[^<>]*>>)*)>>\s*stream\r?\n")
 
-    def extract_pages(self, raw: bytes, password: str = "", ocr_fn: Optional[Callable[[bytes, str], str]] = None
-                      ) -> List[str]:
-        doc = PDFDocument(raw, password)
-        pages = []
+
+def bare_streams(raw: bytes) -> List[Tuple[bytes, bytes]]:
+    """(dictionary, data) of every ``<< ... >> stream ... endstream`` in the file, whether or not it sits inside a
+    numbered object: the fallback for damaged or minimal files without a page tree."""
+    out = []
+    for m in _BARE_STREAM.finditer(raw):
+        end = raw.find(b"endstream", m.end())
+        if end < 0:
+            continue
+        data = raw[m.end():end]
+        n = _int(m.group(1), b"/Length", -1)
+        if 0 <= n <= len(data):
+            data = data[:n]
+        else:
+            data = data.rstrip(b"\r\n")
+        out.append((m.group(1), data))
+    return out
+
+
+class PDFParser:
+    """PDF -> text chunks.  ``ocr_fn(image_bytes, format_hint) -> str`` (or a one-argument callable) is only asked
+    when a page has no extractable text; ``metadata["ocr_fn"]`` overrides the instance's.  Chunks that came from OCR
+    carry ``pdf_ocr: True``; a file that yields nothing gives one chunk with ``error: "extraction_failed"`` so that the
+    caller can tell (zse-engine/zse_engine/rag/parser.py: ``PDFParser``; zse-engine's tests/test_pdf_ocr.py)."""
+
+    def __init__(self, chunk_size: int = 512, overlap: int = 64, ocr_fn: Optional[Callable[..., str]] = None):
+        self.chunk_size, self.overlap, self.ocr_fn = chunk_size, overlap, ocr_fn
+        self._last_encrypted = False
+
+    # the reference's entry points for callers that use the pieces directly
+    @staticmethod
+    def _tokenize_content_stream(data):
+        from .pdf_layout import tokenize_content_stream
+        return tokenize_content_stream(data)
+
+    def _extract_text(self, raw, password: str = "") -> str:
+        raw = raw if isinstance(raw, (bytes, bytearray)) else raw.encode("latin-1", "replace")
+        return "\n\n".join(t for t, _ in self._pages(bytes(raw), password, None) if t)
+
+    def _extract_images(self, raw, password: str = "") -> List[Tuple[bytes, str]]:
+        raw = raw if isinstance(raw, (bytes, bytearray)) else raw.encode("latin-1", "replace")
+        doc = PDFDocument(bytes(raw), password)
+        out: List[Tuple[bytes, str]] = []
         for p in doc.pages():
-            text = extract_text(doc.page_content(p), doc.page_fonts(p))
-            if not text and ocr_fn is not None:
-                parts = []
-                for data, hint in doc.page_images(p):
+            out += doc.page_images(p)
+        if not out:
+            out = self._loose_images(bytes(raw))
+        return out
+
+    @staticmethod
+    def _loose_images(raw: bytes) -> List[Tuple[bytes, str]]:
+        out = []
+        for d, data in bare_streams(raw):
+            if re.search(rb"/Subtype\s*/Image", d):
+                hint = image_hint(d)
+                if hint == "raw":
                     try:
-                        parts.append(ocr_fn(data, hint) or "")
+                        data = apply_filters(data, d)
                     except Exception:
                         pass
-                text = "\n".join(x for x in parts if x).strip()
-            pages.append(text)
+                out.append((data, hint))
+        return out
+
+    @staticmethod
+    def _call_ocr(fn: Callable[..., str], data: bytes, hint: str) -> str:
+        try:
+            import inspect
+            params = [p for p in inspect.signature(fn).parameters.values()
+                      if p.kind in (p.POSITIONAL_ONLY, p.POSITIONAL_OR_KEYWORD, p.VAR_POSITIONAL)]
+            one = len(params) == 1 and params[0].kind != params[0].VAR_POSITIONAL
+        except (TypeError, ValueError):
+            one = False
+        return (fn(data) if one else fn(data, hint)) or ""
+
+    def _ocr(self, images: List[Tuple[bytes, str]], ocr_fn: Optional[Callable[..., str]]) -> str:
+        parts = []
+        for data, hint in images:
+            try:
+                parts.append(self._call_ocr(ocr_fn, data, hint))
+            except Exception:
+                continue               # one unreadable image must not lose the document
+        return "\n".join(x.strip() for x in parts if x and x.strip())
+
+    def _pages(self, raw: bytes, password: str, ocr_fn: Optional[Callable[..., str]]) -> List[Tuple[str, bool]]:
+        """(text, came from OCR) per page; files without a page tree are read as one page of loose streams."""
+        doc = PDFDocument(raw, password)
+        self._last_encrypted = doc.enc is not None
+        pages: List[Tuple[str, bool]] = []
+        for p in doc.pages():
+            text = extract_text(doc.page_content(p), doc.page_fonts(p))
+            used_ocr = False
+            if not text and ocr_fn is not None:
+                text = self._ocr(doc.page_images(p), ocr_fn)
+                used_ocr = bool(text)
+            pages.append((text, used_ocr))
+        if not pages:
+            texts = []
+            for d, data in bare_streams(raw):
+                if re.search(rb"/Subtype\s*/Image", d) or re.search(rb"/Type\s*/(XRef|ObjStm|Metadata)", d):
+                    continue
+                try:
+                    t = extract_text(apply_filters(data, d), {})
+                except Exception:
+                    continue
+                if t:
+                    texts.append(t)
+            text, used_ocr = "\n".join(texts), False
+            if not text and ocr_fn is not None:
+                text = self._ocr(self._loose_images(raw), ocr_fn)
+                used_ocr = bool(text)
+            pages.append((text, used_ocr))
         return pages
+
+    def extract_pages(self, raw: bytes, password: str = "", ocr_fn: Optional[Callable[..., str]] = None) -> List[str]:
+        return [t for t, _ in self._pages(raw, password, ocr_fn if ocr_fn is not None else self.ocr_fn)]
 
     def parse(self, text, tokenizer=None, metadata: Optional[Dict] = None) -> List[Chunk]:
         raw = text if isinstance(text, (bytes, bytearray)) else text.encode("latin-1", "replace")
         md = metadata or {}
-        pages = self.extract_pages(bytes(raw), md.get("pdf_password") or "", md.get("ocr_fn"))
+        ocr_fn = md.get("ocr_fn") or self.ocr_fn
         meta = _public_meta(md)
+        try:
+            pages = self._pages(bytes(raw), md.get("pdf_password") or "", ocr_fn)
+        except PDFError as exc:
+            kind = getattr(exc, "kind", None)
+            if kind is None:
+                raise
+            note = f"[PDF: {exc}]"
+            return [Chunk(note, note, {**meta, "error": kind, "pdf_encrypted": True, "chunk_index": 0})]
+        if self._last_encrypted:
+            meta["pdf_encrypted"] = True
         tp = TextParser(self.chunk_size, self.overlap)
         out: List[Chunk] = []
-        for i, page_text in enumerate(pages):
-            for c in tp.parse(page_text, tokenizer, {**meta, "page": i + 1}):
+        for i, (page_text, used_ocr) in enumerate(pages):
+            extra = {"page": i + 1, **({"pdf_ocr": True} if used_ocr else {})}
+            for c in tp.parse(page_text, tokenizer, {**meta, **extra}):
                 c.metadata["chunk_index"] = len(out)
                 out.append(c)
+        if not out:
+            note = "[PDF: no text could be extracted" + ("" if ocr_fn else "; no OCR backend is configured") + "]"
+            out.append(Chunk(note, note, {**meta, "error": "extraction_failed", "chunk_index": 0}))
         return out

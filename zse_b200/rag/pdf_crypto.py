@@ -279,6 +279,14 @@ class PDFEncryption:
 
     # the reference's accessors (pdf_crypto.py:635-760)
     @property
+    def version(self) -> int:
+        return self.v
+
+    @property
+    def revision(self) -> int:
+        return self.r
+
+    @property
     def supported(self) -> bool:
         if self.v in (1, 2, 4) and self.r in (2, 3, 4):
             return True
