@@ -184,6 +184,27 @@ def test_tp_engine_phi3_stacked_projections(tmp_path):
         e.stop()
 
 
+@pytest.mark.timeout(600)
+def test_sequence_parallel_prefill_matches_all_reduce(tmp_path, monkeypatch):
+    """Reduce-scatter after the row-parallel projections + all-gather before the column-parallel ones (the residual
+    stream split by rows) gives the hidden states and tokens of the all-reduce path, on two CPU ranks."""
+    import sys
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from dist_sp_fn import rank_fn
+    from zse_b200.models.oracle import OracleModel
+    from zse_b200.parallel.tensor_parallel import tp_launch
+    path = str(tmp_path / "m.zse")
+    synth.write_random_model(path, synth.shape_config("tiny-aligned"), seed=4)
+    monkeypatch.setenv("ZSE_TEST_MODEL", path)
+    res = tp_launch(2, rank_fn, backend="cpu", timeout_s=300)
+    layers = synth.shape_config("tiny-aligned").num_layers
+    for r in res:
+        assert r["tokens_equal"] and r["max_diff"] <= 2e-3 * max(1.0, r["scale"])
+        assert r["sp_passes"] == (0, 2 * layers)          # every norm after a row-parallel projection of the prefill
+    prompt = [(7 * i + 3) % 1024 for i in range(37)]
+    assert res[0]["tokens"] == res[1]["tokens"] == OracleModel(ZSELoader(path)).greedy(prompt, 2)
+
+
 # ---- LoRA manager ---------------------------------------------------------------------------------------------------
 def test_lora_manager_slots_and_effect_on_outputs(tmp_path):
     from zse_b200.lora.weights import random_adapter_file

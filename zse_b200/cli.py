@@ -185,7 +185,9 @@ def build_parser() -> argparse.ArgumentParser:
     s.add_argument("--speculative-k", type=int, default=0)
     s.add_argument("--speculative-mode", default="ngram", choices=["ngram", "self"])
     s.add_argument("--no-graphs", action="store_true")
-    s.add_argument("--comm", default="fused", choices=["fused", "nccl"])
+    s.add_argument("--comm", default="fused", choices=["fused", "nccl", "nccl-sp"],
+                   help="tensor-parallel collectives: fused in-kernel exchange, NCCL all-reduce, or NCCL with "
+                        "sequence-parallel prefill (reduce-scatter / all-gather, residual split by rows)")
     s.add_argument("--require-auth", action="store_true")
     s.add_argument("--cpu", action="store_true", help="run on the CPU reference path")
     s.set_defaults(fn=_cmd_serve)

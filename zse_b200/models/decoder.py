@@ -253,6 +253,8 @@ class DecoderModel:
             ops.add_rmsnorm(b.residual, b.partials, planes, None, weight, b.xnorm, M, eps)
         elif self.comm.fused_norm:
             self.comm.reduce_add_rmsnorm(ops, b.residual, b.partials, planes, weight, b.xnorm, M, eps)
+        elif self.comm.use_sequence_parallel(M):
+            self.comm.reduce_scatter_add_rmsnorm(ops, b.residual, b.partials, planes, weight, b.xnorm, M, eps)
         else:
             planes = self.comm.all_reduce_partials(b.partials, planes, M)
             ops.add_rmsnorm(b.residual, b.partials, planes, None, weight, b.xnorm, M, eps)

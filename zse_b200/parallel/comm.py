@@ -26,9 +26,65 @@ class NcclComm:
     graph_safe = True          # NCCL collectives can be captured in CUDA graphs
     fused_norm = False
 
-    def __init__(self, rank: int, world: int, device, group=None):
+    def __init__(self, rank: int, world: int, device, group=None, sequence_parallel: Optional[bool] = None):
         self.rank, self.world, self.device, self.group = rank, world, device, group
         self._gather = None
+        # sequence parallelism for passes of at least ``sp_min_rows`` tokens: the residual stream is split by rows,
+        # a reduce-scatter follows each row-parallel projection and an all-gather precedes each column-parallel one
+        if sequence_parallel is None:
+            sequence_parallel = os.environ.get("ZSE_TP_SP", "0") not in ("0", "", "false")
+        self.sequence_parallel = bool(sequence_parallel)
+        self.sp_min_rows = int(os.environ.get("ZSE_TP_SP_MIN_ROWS", 256))
+        self.sp_passes = 0
+        self._sp_bufs: dict = {}
+
+    def use_sequence_parallel(self, M: int) -> bool:
+        return self.sequence_parallel and M >= max(self.sp_min_rows, self.world)
+
+    def _sp_buf(self, name: str, rows: int, H: int, dtype) -> torch.Tensor:
+        t = self._sp_bufs.get(name)
+        if t is None or t.shape[0] < rows or t.shape[1] != H or t.dtype != dtype:
+            t = self._sp_bufs[name] = torch.zeros(rows, H, dtype=dtype, device=self.device)
+        return t[:rows]
+
+    def reduce_scatter_add_rmsnorm(self, ops, residual, partials, planes: int, weight, out, M: int, eps: float) -> None:
+        """Sequence-parallel form of "sum over ranks, add to the residual, normalise": every rank receives the sum of
+        its own ``ceil(M / world)`` rows only (reduce-scatter), adds them to its rows of the residual stream and
+        normalises those, and the normalised rows are gathered so that the column-parallel projection that follows
+        sees all ``M``.  Same bytes on the wire as the all-reduce, 1/world of the residual and norm work per rank,
+        and rows of the residual a rank does not own are never touched again after the embedding."""
+        H, w = partials.shape[-1], self.world
+        m = (M + w - 1) // w
+        pl = partials.view(-1)[: planes * M * H].view(planes, M, H)
+        full = self._sp_buf("send", m * w, H, pl.dtype)
+        if planes > 1:
+            torch.sum(pl, dim=0, out=full[:M])
+        else:
+            full[:M].copy_(pl[0])
+        if m * w > M:
+            full[M:].zero_()
+        mine = self._sp_buf("mine", m, H, pl.dtype)
+        try:
+            dist.reduce_scatter_tensor(mine, full, group=self.group)
+        except (RuntimeError, NotImplementedError):     # back ends without the primitive (gloo)
+            dist.all_reduce(full, group=self.group)
+            mine.copy_(full[self.rank * m: (self.rank + 1) * m])
+        r0 = self.rank * m
+        n = max(0, min(M, r0 + m) - r0)
+        normed = self._sp_buf("normed", m, H, out.dtype)
+        if n < m:
+            normed[n:].zero_()
+        if n > 0:
+            ops.add_rmsnorm(residual[r0:r0 + n], mine, 1, None, weight, normed, n, eps)
+        gathered = self._sp_buf("gathered", m * w, H, out.dtype)
+        try:
+            dist.all_gather_into_tensor(gathered, normed, group=self.group)
+        except (RuntimeError, NotImplementedError):
+            parts = [torch.empty_like(normed) for _ in range(w)]
+            dist.all_gather(parts, normed, group=self.group)
+            torch.cat(parts, dim=0, out=gathered)
+        out[:M].copy_(gathered[:M])
+        self.sp_passes += 1
 
     def all_reduce_partials(self, partials: torch.Tensor, planes: int, M: int) -> int:
         """Sums this rank's planes into plane 0 and all-reduces it; returns the number of planes left (1)."""
@@ -248,8 +304,8 @@ class FusedComm(NcclComm):
 def make_comm(backend: str, rank: int, world: int, device, hidden_size: int = 0, max_tokens: int = 0, group=None):
     if world <= 1:
         return None
-    if backend == "nccl":
-        return NcclComm(rank, world, device, group)
+    if backend in ("nccl", "nccl-sp"):       # "nccl-sp": sequence-parallel prefill on the NCCL path
+        return NcclComm(rank, world, device, group, sequence_parallel=True if backend == "nccl-sp" else None)
     if backend == "fused":
         return FusedComm(rank, world, device, hidden_size, max_tokens, group)
-    raise ValueError(f"unknown tensor-parallel comm backend '{backend}' (fused | nccl)")
+    raise ValueError(f"unknown tensor-parallel comm backend '{backend}' (fused | nccl | nccl-sp)")

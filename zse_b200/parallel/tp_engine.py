@@ -62,7 +62,8 @@ def _worker(rank: int, world: int, model_path: str, cfg: EngineConfig, port: int
         with ZSELoader(model_path) as l:
             hidden = l.config.hidden_size
         dev = torch.device(f"cuda:{rank}" if on_gpu else "cpu")
-        backend = cfg.comm_backend if on_gpu else "nccl"      # the plain collective path also runs on gloo
+        # the plain collective paths also run on gloo; the fused kernels need GPUs
+        backend = cfg.comm_backend if on_gpu or cfg.comm_backend.startswith("nccl") else "nccl"
         comm = make_comm(backend, rank, world, dev, hidden_size=hidden,
                          max_tokens=max(cfg.max_batch_tokens, cfg.prefill_chunk_size))
         eng = ZStreamerEngine(model_path, config=cfg, comm=comm, tp_rank=rank)
