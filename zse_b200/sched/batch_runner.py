@@ -102,6 +102,13 @@ class BatchRunner:
             return -1
         return self._lora.slot_of(r.lora_id)
 
+    def _resolve_lora(self, r: InferenceRequest):
+        """The adapter record a request asks for, or None (no manager, no ``lora_id``, or not loaded): the reference's
+        helper (zse-engine/zse_engine/zstreamer/batch_runner.py); the passes themselves use ``_adapter_slot``."""
+        if self._lora is None or r.lora_id is None:
+            return None
+        return self._lora.get_adapter(r.lora_id)
+
     def _release_kv(self, r: InferenceRequest) -> None:
         if r.seq_id is not None and self._cache.has_sequence(r.seq_id):
             self._cache.free_sequence(r.seq_id)

@@ -227,6 +227,10 @@ class OpenAIAPI:
         return Response.sse(gen())
 
     # ---- routes -----------------------------------------------------------------------------------------
+    def _format_chat_messages(self, messages: List[Dict]) -> str:
+        """The prompt text for a chat in this model's template (ChatML unless the architecture says otherwise)."""
+        return TEMPLATES[self._chat_template](messages)
+
     async def handle_chat_completions(self, request: Request) -> Response:
         body = request.json
         if not isinstance(body, dict):
@@ -239,7 +243,7 @@ class OpenAIAPI:
             return Response.error("invalid sampling parameter")
         if body.get("rag") and self._rag_engine is not None:
             messages = self._rag_engine.augment_messages(messages)
-        prompt = TEMPLATES[self._chat_template](messages)
+        prompt = self._format_chat_messages(messages)
         return await self._generate(request, prompt, f"chatcmpl-{secrets.token_hex(12)}", model, params, stream, True)
 
     async def handle_completions(self, request: Request) -> Response:

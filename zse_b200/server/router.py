@@ -106,6 +106,10 @@ class Response:
     headers: Dict[str, str] = field(default_factory=dict)
     stream: Optional[Any] = None          # async iterator of bytes: sent as it is produced (SSE)
 
+    @property
+    def _is_streaming(self) -> bool:
+        return self.headers.get("Content-Type", "").startswith("text/event-stream")
+
     @classmethod
     def json_response(cls, obj: Any, status: int = 200) -> "Response":
         return cls(status, json.dumps(obj).encode("utf-8"), {"Content-Type": "application/json"})
