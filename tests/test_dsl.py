@@ -419,3 +419,10 @@ def test_prepacked_arguments_keep_their_storage():
     from zse_b200.dsl.dtypes import from_string
     assert from_string("fp16") is zse.float16 and from_string("bfloat16") is zse.bfloat16
     assert zse.infer_types(vector_add.ir).var_types["i"] == "int"
+
+
+def test_resource_report():
+    r = rmsnorm.resources({"x": "float16", "w": "float16", "out": "float16"})
+    assert 0 < r["registers"] <= 64 and r["spill_stores"] == r["spill_loads"] == 0 and r["shared_bytes"] >= 128
+    from zse_b200.dsl import report
+    assert any(k.name == "wmma_matmul" for _, k in report.kernels_of(__file__))

@@ -137,6 +137,24 @@ class RuntimeCompiler:
             with open(out, "rb") as f:
                 return f.read()
 
+    def resource_usage(self, source: str, name: str) -> Dict[str, int]:
+        """What ptxas reports for the kernel (``-Xptxas -v``): registers per thread, spill bytes, static shared
+        memory, stack frame.  A separate nvcc run; nothing is cached."""
+        import re
+        with tempfile.TemporaryDirectory(prefix="zse_kernel_") as d:
+            src, out = os.path.join(d, name + ".cu"), os.path.join(d, name + ".cubin")
+            with open(src, "w") as f:
+                f.write(source)
+            res = subprocess.run([nvcc_path()] + ARCH_FLAGS + self.flags + ["-Xptxas", "-v", "-cubin", "-o", out, src],
+                                 capture_output=True, text=True)
+            if res.returncode != 0:
+                raise KernelCompileError(f"nvcc rejected kernel '{name}'", (res.stdout + res.stderr).strip(), source)
+        log = res.stdout + res.stderr
+        grab = lambda pat: int(m.group(1)) if (m := re.search(pat, log)) else 0
+        return {"registers": grab(r"Used (\d+) registers"), "spill_stores": grab(r"(\d+) bytes spill stores"),
+                "spill_loads": grab(r"(\d+) bytes spill loads"), "stack_frame": grab(r"(\d+) bytes stack frame"),
+                "shared_bytes": grab(r"(\d+) bytes smem"), "barriers": grab(r"used (\d+) barriers")}
+
     def clear_cache(self) -> None:
         with self._lock:
             self._mem.clear()

@@ -109,6 +109,11 @@ class KernelFunction:
             ck = self._compiled[sig] = comp.compile(self.source("cuda", dict(sig), line_info=True), self._name)
         return ck
 
+    def resources(self, dtypes: Optional[Dict[str, Any]] = None) -> Dict[str, int]:
+        """Registers, spills and shared memory of the compiled kernel, as ptxas reports them."""
+        comp = self._compiler or default_compiler()
+        return comp.resource_usage(self.source("cuda", dtypes, line_info=True), self._name)
+
     def uses_collectives(self) -> bool:
         return any(isinstance(e, ir.Call) and (e.func in COLLECTIVES or e.func in WARP_WIDE)
                    and e.func not in ("syncthreads",)
