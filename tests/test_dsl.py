@@ -426,3 +426,51 @@ def test_resource_report():
     assert 0 < r["registers"] <= 64 and r["spill_stores"] == r["spill_loads"] == 0 and r["shared_bytes"] >= 128
     from zse_b200.dsl import report
     assert any(k.name == "wmma_matmul" for _, k in report.kernels_of(__file__))
+
+
+# ---- race detection in the emulator -------------------------------------------------------------------------------------
+@zse.kernel
+def _racy_sum(x: zse.Tensor, out: zse.Tensor, n: int):
+    i = zse.global_id(0)
+    if i < n:
+        out[0] = out[0] + x[i]                 # every thread reads and writes out[0] without an atomic
+
+
+@zse.kernel
+def _racy_shared(x: zse.Tensor, out: zse.Tensor):
+    buf = zse.shared_memory(64, zse.float32)
+    t = zse.thread_id(0)
+    buf[t] = x[t]
+    out[t] = buf[63 - t]                       # reads a neighbour's slot with no barrier in between
+
+
+@zse.kernel
+def _ordered_shared(x: zse.Tensor, out: zse.Tensor):
+    buf = zse.shared_memory(64, zse.float32)
+    t = zse.thread_id(0)
+    buf[t] = x[t]
+    zse.syncthreads()
+    out[t] = buf[63 - t]
+    zse.syncthreads()
+    buf[63 - t] = 0.0                          # reuse after a second barrier is fine
+
+
+def test_emulator_finds_data_races():
+    x, out = torch.arange(64, dtype=torch.float32), torch.zeros(64)
+    with pytest.raises(zse.KernelRaceError) as err:
+        _racy_sum.emulate((2,), (32,), (x, out, 64), check_races=True)
+    assert any("out[0]" in r for r in err.value.races) and "line" in err.value.races[0]
+    with pytest.raises(zse.KernelRaceError, match="read-after-write race on buf"):
+        _racy_shared.emulate((1,), (64,), (x, out), check_races=True)
+    _ordered_shared.emulate((1,), (64,), (x, out), check_races=True)
+    assert out.tolist() == list(range(63, -1, -1))
+    # the kernels above that are meant to be correct are race free: atomics, reductions, tiles, tensor-core tiles
+    bins = torch.zeros(8, dtype=torch.int32)
+    histogram.emulate((2,), (32,), (torch.arange(64, dtype=torch.int32), bins, 64), check_races=True)
+    xs, w, o = torch.randn(2, 96), torch.ones(96), torch.zeros(2, 96)
+    rmsnorm.emulate((2,), (32,), (xs, w, o, 96, 1e-6), check_races=True)
+    src, dst = torch.randn(20, 37), torch.zeros(37, 20)
+    transpose_tile.emulate((3, 2), (64,), (src, dst, 20, 37), check_races=True)
+    a, b, c = torch.randn(16, 16).half(), torch.randn(16, 16).half(), torch.zeros(16, 16)
+    wmma_matmul.emulate((1, 1), (32,), (a, b, c, 16, 16), check_races=True)
+    torch.testing.assert_close(c, a.float() @ b.float(), atol=1e-4, rtol=1e-4)

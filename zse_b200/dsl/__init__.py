@@ -21,6 +21,7 @@ from ..runtime.profiler import AutoTuner, KernelProfiler
 from .compiler import CompiledKernel, RuntimeCompiler
 from .dtypes import (DType, Tensor, bfloat16, empty, float16, float32, int4, int8, int16, int32, uint4, uint8, uint16,
                      uint32, zeros)
+from .emulate import KernelRaceError, RaceTracker
 from .errors import KernelCompileError, KernelError, KernelLaunchError, KernelSyntaxError, KernelTypeError
 from .infer import infer as infer_types
 from .parser import validate_kernel
@@ -36,4 +37,4 @@ __all__ = ["kernel", "fuse", "KernelFunction", "DType", "Tensor", "empty", "zero
            "int32", "int16", "int8", "uint32", "uint16", "uint8", "int4", "uint4", "detect_backend", "get_devices",
            "DeviceInfo", "GPUMemory", "RuntimeCompiler", "CompiledKernel", "KernelLauncher", "LaunchConfig", "PrepackedArgs",
            "KernelProfiler", "AutoTuner", "KernelError", "KernelSyntaxError", "KernelTypeError", "KernelCompileError",
-           "KernelLaunchError"] + list(_prims)
+           "KernelLaunchError", "KernelRaceError", "RaceTracker"] + list(_prims)

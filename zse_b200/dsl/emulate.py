@@ -50,6 +50,61 @@ def _to_scalar(v, t: str):
     return int(v)
 
 
+class RaceTracker:
+    """Data-race detection for an emulated launch.  Two accesses to the same byte race when they come from different
+    threads, at least one writes, they are not both atomic, and nothing orders them: inside a block only a barrier
+    (``syncthreads``, a block reduction, a tile move) orders shared and global memory; between blocks of one launch
+    nothing does.  Every byte remembers its last writer and the readers since, each with the barrier epoch of its
+    block.  Races are collected (``races``) with the Python lines of both accesses; the first ``limit`` are kept."""
+
+    def __init__(self, limit: int = 20):
+        self.cells: Dict[Tuple[Any, int], list] = {}
+        self.races: List[str] = []
+        self.limit = limit
+        self._seen: set = set()
+
+    def _report(self, kind: str, what: str, idx: int, a, b) -> None:
+        key = (kind, what, a[2], b[2])
+        if key in self._seen:
+            return
+        self._seen.add(key)
+        if len(self.races) < self.limit:
+            self.races.append(f"{kind} race on {what}[{idx}]: block {a[0]} thread {a[1]} (line {a[2]}) and "
+                              f"block {b[0]} thread {b[1]} (line {b[2]})")
+
+    @staticmethod
+    def _unordered(prev, blk, epoch) -> bool:
+        return prev[0] != blk or prev[3] == epoch
+
+    def access(self, root, what: str, idx: int, byte0: int, nbytes: int, blk, tid: int, epoch: int, line: int,
+               write: bool, atomic: bool) -> None:
+        me = (blk, tid, line, epoch, atomic)
+        for byte in range(byte0, byte0 + nbytes):
+            cell = self.cells.get((root, byte))
+            if cell is None:
+                cell = self.cells[(root, byte)] = [None, {}]            # last writer, readers by (blk, tid)
+            w, readers = cell
+            if w is not None and (w[0], w[1]) != (blk, tid) and self._unordered(w, blk, epoch) \
+                    and not (atomic and w[4]):
+                self._report("write-write" if write else "read-after-write", what, idx, w, me)
+            if write:
+                for r in readers.values():
+                    if (r[0], r[1]) != (blk, tid) and self._unordered(r, blk, epoch):
+                        self._report("write-after-read", what, idx, r, me)
+                cell[0] = me
+                cell[1] = {}
+            else:
+                readers[(blk, tid)] = me
+
+
+class KernelRaceError(KernelLaunchError):
+    """``emulate(..., check_races=True)`` found unordered conflicting accesses; ``races`` lists them."""
+
+    def __init__(self, races: List[str]):
+        super().__init__(f"{len(races)} data race(s) found:\n  " + "\n  ".join(races))
+        self.races = races
+
+
 class _Block:
     """State shared by the threads of one block."""
 
@@ -65,6 +120,9 @@ class _Block:
                 esz = np.dtype(_NP[a.elem]).itemsize
                 self.mem[a.name] = np.zeros(max(1, dyn_smem_bytes // esz), _NP[a.elem])
         self.nthreads = block_dim[0] * block_dim[1] * block_dim[2]
+        self.epoch = 0                       # advanced at every block-wide barrier
+        self.tracker: Optional[RaceTracker] = None
+        self.shared_names = {a.name for a in k.arrays if a.space in ("shared", "dynamic_shared")}
 
 
 class _Thread:
@@ -78,6 +136,21 @@ class _Thread:
             if a.space == "local":
                 self.mem[a.name] = np.zeros(a.size, _NP[a.elem])
         self._coll: Dict[int, bool] = {}
+        self._local = {a.name for a in blk.k.arrays if a.space == "local"}
+        self._root: Dict[str, str] = {}      # reinterpreted pointer -> the array it aliases
+        self._quiet = False                  # warp-wide tile calls are one access by the warp, not 32 by its lanes
+
+    def _track(self, name: str, idx: int, node, write: bool, atomic: bool = False) -> None:
+        t = self.b.tracker
+        if t is None or self._quiet:
+            return
+        root = self._root.get(name, name)
+        if root in self._local:
+            return
+        size = int(self.mem[name].dtype.itemsize)
+        key = (root, self.b.block_idx) if root in self.b.shared_names else root
+        t.access(key, name, idx, idx * size, size, self.b.block_idx, self.tid, self.b.epoch,
+                 getattr(node, "lineno", 0), write, atomic)
 
     # ---- memory -------------------------------------------------------------------------------------------------
     def _arr(self, name: str, idx: int, node) -> np.ndarray:
@@ -87,11 +160,13 @@ class _Thread:
                              f"(block {self.b.block_idx}, thread {self.tid3})")
         return arr
 
-    def _load(self, name: str, idx: int, node):
+    def _load(self, name: str, idx: int, node, atomic: bool = False):
+        self._track(name, idx, node, False, atomic)
         v = self._arr(name, idx, node)[idx]
         return f32(v) if isinstance(v, np.floating) else int(v)
 
-    def _store(self, name: str, idx: int, value, node) -> None:
+    def _store(self, name: str, idx: int, value, node, atomic: bool = False) -> None:
+        self._track(name, idx, node, True, atomic)
         arr = self._arr(name, idx, node)
         if np.issubdtype(arr.dtype, np.integer):
             info = np.iinfo(arr.dtype)
@@ -204,7 +279,9 @@ class _Thread:
             return self.tid >> 5
         if n.startswith("atomic_"):
             base, idx = e.args[0].base, int(v[0])
+            self._quiet = True
             old = self._load(base, idx, e)
+            self._quiet = False
             if n == "atomic_add":
                 new = old + v[1]
             elif n == "atomic_max":
@@ -213,7 +290,7 @@ class _Thread:
                 new = min(old, int(v[1]))
             else:
                 new = v[2] if old == v[1] else old
-            self._store(base, idx, new, e)
+            self._store(base, idx, new, e, atomic=True)
             return old
         with np.errstate(all="ignore"):
             if n in ("exp", "log", "sqrt", "cos", "sin", "tanh"):
@@ -247,16 +324,24 @@ class _Thread:
             return None
         if n in ("wmma_load_a", "wmma_load_b"):
             r0, c0, ld = int(v[1]), int(v[2]), int(v[3])
-            return np.array([[self._load(v[0], (r0 + r) * ld + c0 + c, e) for c in range(16)] for r in range(16)], f32)
+            self._quiet = (self.tid & 31) != 0
+            try:
+                return self._wmma_tile(v[0], r0, c0, ld, e)
+            finally:
+                self._quiet = False
         if n == "wmma_fill":
             return np.full((16, 16), f32(v[0]) if v else f32(0), f32)
         if n == "wmma_mma":
             return (v[0].astype(np.float64) @ v[1].astype(np.float64) + v[2]).astype(f32)
         if n == "wmma_store":
             r0, c0, ld = int(v[1]), int(v[2]), int(v[3])
-            for r in range(16):
-                for c in range(16):
-                    self._store(v[0], (r0 + r) * ld + c0 + c, v[4][r, c], e)
+            self._quiet = (self.tid & 31) != 0
+            try:
+                for r in range(16):
+                    for c in range(16):
+                        self._store(v[0], (r0 + r) * ld + c0 + c, v[4][r, c], e)
+            finally:
+                self._quiet = False
             return None
         if n in ("unpack_int4", "unpack_uint4"):
             p, base = int(v[0]) & 0xFFFFFFFF, int(v[2])
@@ -267,6 +352,9 @@ class _Thread:
                 self._store(v[1], base + j, nib, e)
             return None
         raise NotImplementedError(n)
+
+    def _wmma_tile(self, name: str, r0: int, c0: int, ld: int, e) -> np.ndarray:
+        return np.array([[self._load(name, (r0 + r) * ld + c0 + c, e) for c in range(16)] for r in range(16)], f32)
 
     def _collective(self, e: ir.Call, v: List[Any]):
         n = e.func
@@ -323,6 +411,7 @@ class _Thread:
         elif isinstance(s, ir.PtrCast):
             src = self.mem[s.source]
             self.mem[s.name] = src.view(np.uint8).view(_NP[s.elem])
+            self._root[s.name] = self._root.get(s.source, s.source)
         elif isinstance(s, ir.ExprStmt):
             yield from self.ge(s.call)
         elif isinstance(s, ir.If):
@@ -481,15 +570,18 @@ def _run_block(blk: _Block) -> None:
             for t in gens:
                 resume[t] = value
             waiting.clear()
+            blk.epoch += 1
         if not resume:
             raise KernelLaunchError(f"block {blk.block_idx}: the threads wait for one another at different "
                                     f"collectives and none can proceed")
 
 
 def emulate(k: TypedKernel, grid: Sequence[int], block: Sequence[int], args: Sequence[Any],
-            shared_mem_bytes: int = 0) -> None:
+            shared_mem_bytes: int = 0, check_races: bool = False) -> None:
     """Runs the launch on the CPU, blocks one after another.  Tensor arguments (torch CPU tensors, numpy arrays or
-    ``dsl.Tensor`` objects holding one) are modified in place."""
+    ``dsl.Tensor`` objects holding one) are modified in place.  With ``check_races`` every access to global and
+    shared memory is checked for unordered conflicts (``RaceTracker``) and ``KernelRaceError`` is raised at the end if
+    any was seen."""
     grid = tuple(int(g) for g in grid) + (1,) * (3 - len(grid))
     block = tuple(int(b) for b in block) + (1,) * (3 - len(block))
     f = k.func
@@ -523,13 +615,18 @@ def emulate(k: TypedKernel, grid: Sequence[int], block: Sequence[int], args: Seq
         if arr.dtype != np.dtype(_NP[elem]):
             raise KernelTypeError(f"argument '{p.name}' holds {arr.dtype} but the kernel expects {elem}")
         mem[p.name] = arr
+    tracker = RaceTracker() if check_races else None
     for bz in range(grid[2]):
         for by in range(grid[1]):
             for bx in range(grid[0]):
-                _run_block(_Block(k, mem, scalars, (bx, by, bz), block, grid, shared_mem_bytes))
+                blk = _Block(k, mem, scalars, (bx, by, bz), block, grid, shared_mem_bytes)
+                blk.tracker = tracker
+                _run_block(blk)
     for t, arr in write_back:
         import torch
         t.copy_(torch.from_numpy(arr.reshape(tuple(t.shape))).to(torch.bfloat16))
+    if tracker is not None and tracker.races:
+        raise KernelRaceError(tracker.races)
 
 
 class _BF16View:

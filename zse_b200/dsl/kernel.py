@@ -153,10 +153,12 @@ class KernelFunction:
         self._launcher.launch_prepacked(self.compile("cuda", dtypes), self._config(grid, block, shared_mem_bytes),
                                         prepacked, stream)
 
-    def emulate(self, grid, block, args: Sequence[Any], shared_mem_bytes: int = 0) -> None:
-        """The same launch on the CPU (tensors are CPU tensors or numpy arrays, modified in place)."""
+    def emulate(self, grid, block, args: Sequence[Any], shared_mem_bytes: int = 0, check_races: bool = False) -> None:
+        """The same launch on the CPU (tensors are CPU tensors or numpy arrays, modified in place).  ``check_races``
+        also looks for unordered conflicting accesses to shared and global memory and raises ``KernelRaceError``."""
         cfg = self._config(grid, block, shared_mem_bytes)
-        _emulate(self.typed(dict(self._sig_of_args(args))), cfg.grid, cfg.block, list(args), shared_mem_bytes)
+        _emulate(self.typed(dict(self._sig_of_args(args))), cfg.grid, cfg.block, list(args), shared_mem_bytes,
+                 check_races)
 
     def profile(self, grid, block, args: Sequence[Any], shared_mem_bytes: int = 0, nbytes: int = 0, flops: int = 0,
                 profiler=None):
