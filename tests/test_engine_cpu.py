@@ -276,3 +276,33 @@ def test_step_result_names_the_tokens_of_the_step(model_path, oracle):
     for rid, p in zip(ids, prompts):
         assert seen[rid] == oracle.greedy(p, 4) == eng.get_result(rid).output_tokens
     eng.destroy()
+
+
+@pytest.mark.parametrize("scaling", [{"rope_type": "linear", "factor": 4.0},
+                                     {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0,
+                                      "high_freq_factor": 4.0, "original_max_position_embeddings": 32}])
+def test_rope_scaling_reaches_the_engine(tmp_path, scaling):
+    """The frequency table the kernels get (``ops.reference.inv_freq``) follows the same scaling rule as the oracle,
+    which is checked against transformers."""
+    p = str(tmp_path / "scaled.zse")
+    synth.write_random_model(p, synth.shape_config("tiny", rope_scaling=scaling, rope_theta=50000.0), seed=8)
+    oracle = OracleModel(ZSELoader(p))
+    plain = str(tmp_path / "plain.zse")
+    synth.write_random_model(plain, synth.shape_config("tiny", rope_theta=50000.0), seed=8)
+    eng = ZStreamerEngine(p, config=_cfg())
+    prompts = _prompts(eng.model_config.vocab_size, 2, lo=30, hi=60, seed=11)
+    outs = _run(eng, prompts, 8)
+    unscaled = OracleModel(ZSELoader(plain))
+    assert float((oracle.forward(prompts[0]) - unscaled.forward(prompts[0])).abs().max()) > 1e-5    # it matters
+    import torch
+    from zse_b200.models.oracle import rope_cos_sin
+    from zse_b200.ops import reference as ref
+    pos = torch.arange(0, 4000, 37)
+    cos, sin = rope_cos_sin(pos, 64, 50000.0, None, scaling)
+    ang = pos.double()[:, None] * ref.inv_freq(64, 50000.0, scaling).double()[None, :]
+    torch.testing.assert_close(torch.cos(ang).float(), cos, atol=2e-3, rtol=0)      # the table is rounded to fp32
+    torch.testing.assert_close(torch.sin(ang).float(), sin, atol=2e-3, rtol=0)
+    assert not torch.allclose(cos, rope_cos_sin(pos, 64, 50000.0)[0], atol=1e-2)
+    for pr, o in zip(prompts, outs):
+        assert o.output_tokens == oracle.greedy(pr, 8)
+    eng.destroy()

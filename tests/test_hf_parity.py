@@ -25,6 +25,22 @@ def _llama():
     return LlamaForCausalLM(LlamaConfig(**COMMON, rms_norm_eps=1e-5, rope_theta=10000.0, tie_word_embeddings=False))
 
 
+def _llama3_scaled():
+    from transformers import LlamaConfig, LlamaForCausalLM
+    scaling = {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+               "original_max_position_embeddings": 16}
+    # a base that is not the adapter's default either: it must be read from wherever this transformers puts it
+    return LlamaForCausalLM(LlamaConfig(**COMMON, rms_norm_eps=1e-5, rope_theta=500000.0, rope_scaling=scaling,
+                                        tie_word_embeddings=False))
+
+
+def _llama_linear():
+    from transformers import LlamaConfig, LlamaForCausalLM
+    return LlamaForCausalLM(LlamaConfig(**COMMON, rms_norm_eps=1e-5, rope_theta=10000.0,
+                                        rope_scaling={"rope_type": "linear", "factor": 4.0},
+                                        tie_word_embeddings=False))
+
+
 def _mistral():
     from transformers import MistralConfig, MistralForCausalLM
     return MistralForCausalLM(MistralConfig(**COMMON, sliding_window=None, head_dim=16, tie_word_embeddings=False))
@@ -75,10 +91,11 @@ def _randomise(model, seed):
                 p.copy_(0.08 * torch.randn(p.shape, generator=g))
 
 
-@pytest.mark.parametrize("family", ["llama", "mistral", "qwen2", "phi3", "gemma2", "gemma4", "gemma4_k_eq_v"])
+@pytest.mark.parametrize("family", ["llama", "llama_rope3", "llama_ropelinear", "mistral", "qwen2", "phi3", "gemma2", "gemma4",
+                                    "gemma4_k_eq_v"])
 def test_oracle_matches_transformers(tmp_path, family):
     torch.manual_seed(0)
-    build = {"llama": _llama, "mistral": _mistral, "qwen2": _qwen2, "phi3": _phi3, "gemma2": _gemma2, "gemma4": _gemma4,
+    build = {"llama": _llama, "llama_rope3": _llama3_scaled, "llama_ropelinear": _llama_linear, "mistral": _mistral, "qwen2": _qwen2, "phi3": _phi3, "gemma2": _gemma2, "gemma4": _gemma4,
              "gemma4_k_eq_v": lambda: _gemma4(True)}[family]
     model = build().eval().float()
     _randomise(model, 1)

@@ -48,6 +48,23 @@ def detect_architecture(hf_config: dict) -> str:
                      f"model_type={hf_config.get('model_type')})")
 
 
+def rope_settings(hf: dict, default_theta: float):
+    """(theta, scaling dict or None) from either spelling of a HuggingFace config: the older top-level
+    ``rope_theta`` / ``rope_scaling`` keys, or ``rope_parameters`` (transformers 5 writes the base and the scaling
+    parameters together there; ``rope_type: default`` means no scaling)."""
+    rp = hf.get("rope_parameters")
+    theta, scaling = hf.get("rope_theta"), hf.get("rope_scaling")
+    if isinstance(rp, dict) and ("rope_theta" in rp or "rope_type" in rp or "type" in rp):
+        theta = rp.get("rope_theta", theta)
+        if scaling is None:
+            scaling = {k: v for k, v in rp.items() if k != "rope_theta"}
+    if isinstance(scaling, dict):
+        kind = scaling.get("rope_type", scaling.get("type"))
+        if kind in (None, "default"):
+            scaling = None
+    return float(theta if theta is not None else default_theta), scaling
+
+
 class ArchAdapter:
     ARCH_NAME = "unknown"
     #: tensors every layer must have; subclasses extend
@@ -62,13 +79,14 @@ class ArchAdapter:
                 explicit_head_dim: bool) -> ModelConfig:
         h, nh = hf["hidden_size"], hf["num_attention_heads"]
         hd = hf.get("head_dim") if explicit_head_dim else None
+        rope_theta, rope_scaling = rope_settings(hf, theta)
         return ModelConfig(arch=arch, num_layers=hf["num_hidden_layers"], num_heads=nh,
                            num_kv_heads=hf.get("num_key_value_heads", nh), head_dim=hd or h // nh,
                            hidden_size=h, intermediate_size=hf["intermediate_size"], vocab_size=hf["vocab_size"],
                            max_seq_len=hf.get("max_position_embeddings", max_seq),
-                           rope_theta=float(hf.get("rope_theta", theta)),
+                           rope_theta=rope_theta,
                            rms_norm_eps=float(hf.get("rms_norm_eps", eps)),
-                           rope_scaling=hf.get("rope_scaling"), sliding_window=hf.get("sliding_window"),
+                           rope_scaling=rope_scaling, sliding_window=hf.get("sliding_window"),
                            tie_word_embeddings=bool(hf.get("tie_word_embeddings", tie)))
 
     #: explicit renames (HF name -> stored name) applied before the ``model.`` prefix is stripped
@@ -102,4 +120,8 @@ class ArchAdapter:
             w.append(f"hidden_size ({c.hidden_size}) not divisible by num_heads ({c.num_heads})")
         if c.num_heads % c.num_kv_heads:
             w.append(f"num_heads ({c.num_heads}) not divisible by num_kv_heads ({c.num_kv_heads})")
+        kind = (c.rope_scaling or {}).get("rope_type", (c.rope_scaling or {}).get("type"))
+        if kind not in (None, "default", "linear", "llama3"):
+            w.append(f"rope scaling of type '{kind}' is not applied by the runtime (linear and llama3 are): positions "
+                     f"beyond the original context length will be rotated with the unscaled frequencies")
         return w

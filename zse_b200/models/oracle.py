@@ -10,6 +10,7 @@ path, model_runner.py:428-540).  Nothing here is rounded to 16 bits.
 """
 from __future__ import annotations
 
+import math
 from typing import Dict, List, Optional
 
 import numpy as np
@@ -25,10 +26,31 @@ def load_fp32_weights(loader: ZSELoader) -> Dict[str, torch.Tensor]:
     return out
 
 
-def rope_cos_sin(positions: torch.Tensor, head_dim: int, theta: float, rotary_dim: Optional[int] = None):
-    """cos/sin [T, head_dim/2]; pairs beyond ``rotary_dim/2`` get angle 0 (they pass through unrotated)."""
+def rope_cos_sin(positions: torch.Tensor, head_dim: int, theta: float, rotary_dim: Optional[int] = None,
+                 rope_scaling: Optional[dict] = None):
+    """cos/sin [T, head_dim/2]; pairs beyond ``rotary_dim/2`` get angle 0 (they pass through unrotated).
+    ``rope_scaling`` of kind ``linear`` (all frequencies divided by the factor) and ``llama3`` (long wavelengths
+    divided by the factor, short ones kept, a smooth blend between) changes the frequencies, as in transformers."""
     half = head_dim // 2
     inv = theta ** (-torch.arange(half, dtype=torch.float64) * 2.0 / head_dim)
+    kind = (rope_scaling or {}).get("rope_type", (rope_scaling or {}).get("type"))
+    if kind == "linear":
+        inv = inv / float(rope_scaling["factor"])
+    elif kind == "llama3":
+        factor = float(rope_scaling["factor"])
+        low, high = float(rope_scaling.get("low_freq_factor", 1.0)), float(rope_scaling.get("high_freq_factor", 4.0))
+        old = float(rope_scaling.get("original_max_position_embeddings", 8192))
+        scaled = []
+        for f in inv.tolist():
+            wavelen = 2 * math.pi / f
+            if wavelen < old / high:
+                scaled.append(f)
+            elif wavelen > old / low:
+                scaled.append(f / factor)
+            else:
+                t = (old / wavelen - low) / (high - low)
+                scaled.append((1 - t) * f / factor + t * f)
+        inv = torch.tensor(scaled, dtype=torch.float64)
     if rotary_dim is not None and rotary_dim < head_dim:
         inv[rotary_dim // 2:] = 0.0
     ang = positions.to(torch.float64)[:, None] * inv[None, :]
@@ -97,7 +119,8 @@ class OracleModel:
             sp = c.layer_spec(i) if gemma else None
             hd = sp.head_dim if sp else c.head_dim
             nkv = sp.num_kv_heads if sp else c.num_kv_heads
-            cos, sin = rope_cos_sin(pos, hd, sp.rope_theta if sp else c.rope_theta, sp.rotary_dim if sp else None)
+            cos, sin = rope_cos_sin(pos, hd, sp.rope_theta if sp else c.rope_theta, sp.rotary_dim if sp else None,
+                                    None if gemma else c.rope_scaling)
             x = rmsnorm(h, self.w[p + "input_layernorm.weight"], c.rms_norm_eps)
             q = x @ self.w[p + "self_attn.q_proj.weight"].T
             k = x @ self.w[p + "self_attn.k_proj.weight"].T
