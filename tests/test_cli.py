@@ -146,3 +146,28 @@ def test_serve_mock_mode_and_cpu_model(tiny, tmp_path):
     finally:
         proc.send_signal(signal.SIGTERM)
         proc.wait(30)
+
+
+def test_info_lists_environment_switches(monkeypatch):
+    import os
+    r = subprocess.run([sys.executable, "-m", "zse_b200", "info", "--env"], capture_output=True, text=True,
+                       env={**os.environ, "ZSE_TP_SP": "1"}, timeout=240)
+    assert r.returncode == 0 and "ZSE_TP_SP=1  (set)" in r.stdout and "ZSE_LOAD_RING=6" in r.stdout
+    assert "ZSE_MAX_BATCH_SEQS" in r.stdout
+    from zse_b200.utils import env
+    monkeypatch.setenv("ZSE_NATIVE_STEP", "off")
+    monkeypatch.setenv("ZSE_LOAD_RING", "nine")
+    assert env.flag("ZSE_NATIVE_STEP") is False and env.flag("ZSE_PIPELINE_DECODE") is True
+    with pytest.raises(ValueError):
+        env.integer("ZSE_LOAD_RING")
+    with pytest.raises(KeyError):
+        env.flag("ZSE_NOT_DECLARED")
+    # every ZSE_* name the Python sources read is declared
+    import re
+    root = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "zse_b200")
+    used = set()
+    for d, _, files in os.walk(root):
+        for f in files:
+            if f.endswith(".py") and f != "env.py":
+                used |= set(re.findall(r"env\.(?:flag|integer|text)\(\"(ZSE_[A-Z0-9_]+)\"", open(os.path.join(d, f)).read()))
+    assert used and used <= set(env.KNOWN)

@@ -85,6 +85,12 @@ def _cmd_info(a) -> int:
         with ZSELoader(a.model) as l:
             print()
             print(l.summary())
+    if getattr(a, "env", False):
+        from .utils import env
+        print()
+        print("environment switches")
+        for line in env.describe():
+            print(line)
     return 0
 
 
@@ -207,6 +213,7 @@ def build_parser() -> argparse.ArgumentParser:
     cl.set_defaults(fn=_cmd_convert_lora)
     i = sub.add_parser("info", help="GPUs and, optionally, a model file summary")
     i.add_argument("model", nargs="?", default=None)
+    i.add_argument("--env", action="store_true", help="also list the ZSE_* environment switches and their values")
     i.set_defaults(fn=_cmd_info)
     sub.add_parser("version").set_defaults(fn=_cmd_version)
     w = sub.add_parser("warm", help="pull a model file into the page cache")

@@ -17,13 +17,14 @@ from typing import Dict, Optional
 
 from ..ops.build import nvcc_path
 from .errors import KernelCompileError, KernelLaunchError
+from ..utils import env
 
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 BASE_FLAGS = ["-O3", "-std=c++17", "-lineinfo"]
 
 
 def cache_dir() -> str:
-    d = os.environ.get("ZSE_KERNEL_CACHE") or os.path.join(os.path.expanduser("~"), ".cache", "zse_b200", "kernels")
+    d = os.path.expanduser(env.text("ZSE_KERNEL_CACHE"))
     os.makedirs(d, exist_ok=True)
     return d
 

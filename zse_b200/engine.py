@@ -33,6 +33,7 @@ from .sched.batch_runner import BatchRunner, StepResult
 from .sched.memory_budget import MemoryBudget
 from .sched.request import FinishReason, GenerationParams, InferenceRequest, RequestOutput
 from .sched.scheduler import Scheduler, SchedulerConfig
+from .utils import env
 
 CHAT_STOP_MARKERS = ("<|im_end|>", "<|im_start|>", "<|eot_id|>", "<end_of_turn>")
 
@@ -142,7 +143,7 @@ class ZStreamerEngine:
         self._spec_runner = spec
         pipeline = cfg.pipeline_decode
         if pipeline is None:
-            pipeline = os.environ.get("ZSE_PIPELINE_DECODE", "1").lower() not in ("0", "", "false", "off", "no")
+            pipeline = env.flag("ZSE_PIPELINE_DECODE")
         self._batch_runner = BatchRunner(self._runner, self._scheduler, spec_runner=spec,
                                          lora_manager=self._lora_manager, pipeline_decode=pipeline)
         self.init_times["runtime"] = time.monotonic() - t2

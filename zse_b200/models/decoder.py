@@ -26,6 +26,7 @@ from ..format.config import ModelConfig
 from ..ops import reference as ref
 from ..ops.backend import LinearWeight, TorchOps, make_ops, np_to_dev
 from ..parallel.shard_plan import ShardPlan, make_plan
+from ..utils import env
 
 SUPPORTED_ARCHS = ("llama", "mistral", "qwen2", "phi3", "gemma2", "gemma4")
 
@@ -172,7 +173,7 @@ class DecoderModel:
         has = lambda n: loader.weight_index.find(n) is not None
         to_dev = lambda a: np_to_dev(a, dev)
         mirror = None
-        if dev.type == "cuda" and p.tp_size == 1 and os.environ.get("ZSE_STREAM_WEIGHTS", "1") != "0":
+        if dev.type == "cuda" and p.tp_size == 1 and env.flag("ZSE_STREAM_WEIGHTS"):
             from ..runtime.weight_stream import DeviceMirror
             mirror = DeviceMirror(loader, dev)
             self.load_stats["stream_s"] = round(mirror.seconds, 3)

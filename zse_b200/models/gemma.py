@@ -33,6 +33,7 @@ from ..format.config import LayerSpec, ModelConfig
 from ..format.loader import ZSELoader
 from ..ops.backend import LinearWeight, np_to_dev
 from .decoder import DecoderModel, StepBuffers, _entry_part, _vec
+from ..utils import env
 
 
 @dataclass
@@ -81,7 +82,7 @@ class GemmaDecoderModel(DecoderModel):
             return np_to_dev(v, dev)
 
         mirror = None
-        if dev.type == "cuda" and tp == 1 and os.environ.get("ZSE_STREAM_WEIGHTS", "1") != "0":
+        if dev.type == "cuda" and tp == 1 and env.flag("ZSE_STREAM_WEIGHTS"):
             from ..runtime.weight_stream import DeviceMirror
             mirror = DeviceMirror(loader, dev)
             self.load_stats["stream_s"] = round(mirror.seconds, 3)

@@ -19,6 +19,7 @@ from typing import Optional
 
 import torch
 import torch.distributed as dist
+from ..utils import env
 
 
 class NcclComm:
@@ -32,9 +33,9 @@ class NcclComm:
         # sequence parallelism for passes of at least ``sp_min_rows`` tokens: the residual stream is split by rows,
         # a reduce-scatter follows each row-parallel projection and an all-gather precedes each column-parallel one
         if sequence_parallel is None:
-            sequence_parallel = os.environ.get("ZSE_TP_SP", "0") not in ("0", "", "false")
+            sequence_parallel = env.flag("ZSE_TP_SP")
         self.sequence_parallel = bool(sequence_parallel)
-        self.sp_min_rows = int(os.environ.get("ZSE_TP_SP_MIN_ROWS", 256))
+        self.sp_min_rows = env.integer("ZSE_TP_SP_MIN_ROWS")
         self.sp_passes = 0
         self._sp_bufs: dict = {}
 
@@ -192,7 +193,7 @@ class FusedComm(NcclComm):
         torch.cuda.synchronize(device)
         dist.barrier(group=grp)
         ptrs = [int(p) for p in self._hdl.buffer_ptrs]
-        want_mm = use_multimem if use_multimem is not None else os.environ.get("ZSE_TP_MULTIMEM", "1") != "0"
+        want_mm = use_multimem if use_multimem is not None else env.flag("ZSE_TP_MULTIMEM")
         mc = 0
         if want_mm:
             try:
@@ -206,18 +207,18 @@ class FusedComm(NcclComm):
         self._calls = 0
         # Push exchange (ZSE_TP_PUSH=1): the row-parallel GEMM itself sends its fp16 rows to every rank's inbox
         # (multimem.st through NVSwitch, or peer stores) and the consumer adds local rows only.
-        self.push = os.environ.get("ZSE_TP_PUSH", "0") == "1"
+        self.push = env.flag("ZSE_TP_PUSH")
         self.push_rows = min(256, max_tokens)
         self._push_ready = False
         if self.push:
             self._init_push(symm, grp, world, rank, device, hidden_size, want_mm)
         # passes with at least this many rows (prefill) use the two-shot kernel: reduce-scatter by rows + all-gather,
         # 2(tp-1)/tp rows over NVLink per rank and row instead of tp-1
-        self.two_shot_min_rows = int(os.environ.get("ZSE_TP_TWO_SHOT_ROWS", 1 << 30))
+        self.two_shot_min_rows = env.integer("ZSE_TP_TWO_SHOT_ROWS")
         # Large passes (prefill) go through ncclAllReduce of the fp16 row sums by default: measured on B200 x2/x4, the
         # per-row kernels above lose to NCCL once a pass has hundreds of rows (they are built for latency, one CTA per
         # row), while for decode-sized passes they win by 1.2-1.4x.  ZSE_TP_NCCL_ROWS moves the switch-over point.
-        self.nccl_min_rows = int(os.environ.get("ZSE_TP_NCCL_ROWS", 256))
+        self.nccl_min_rows = env.integer("ZSE_TP_NCCL_ROWS")
         self._f16: Optional[torch.Tensor] = None
 
     def _init_push(self, symm, grp, world, rank, device, H, want_mm) -> None:

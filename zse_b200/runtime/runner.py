@@ -379,8 +379,8 @@ class ModelRunner:
     def _nvtx(name: str):
         """NVTX range around a phase when ZSE_NVTX=1 (timeline tools), else a no-op context."""
         import contextlib
-        import os as _os
-        if _os.environ.get("ZSE_NVTX") == "1" and torch.cuda.is_available():
+        from ..utils import env as _env
+        if _env.flag("ZSE_NVTX") and torch.cuda.is_available():
             return torch.cuda.nvtx.range(name)
         return contextlib.nullcontext()
 

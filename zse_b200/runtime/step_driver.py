@@ -17,6 +17,7 @@ from typing import Optional
 import torch
 
 from ..ops import native
+from ..utils import env
 
 KIND = {"w4t": 0, "f16": 1}
 
@@ -52,7 +53,7 @@ def _linear(w) -> _Linear:
 
 
 def enabled() -> bool:
-    return os.environ.get("ZSE_NATIVE_STEP", "1") != "0"
+    return env.flag("ZSE_NATIVE_STEP")
 
 
 class NativeStep:

@@ -15,6 +15,7 @@ from typing import Dict, Optional
 
 import numpy as np
 import torch
+from ..utils import env
 
 _DTYPES = {"uint8": torch.uint8, "int8": torch.int8, "float16": torch.float16}
 
@@ -23,8 +24,8 @@ class DeviceMirror:
     def __init__(self, loader, device, chunk_mb: Optional[int] = None, ring: Optional[int] = None, readers: int = 4):
         self.offset, self.size = loader.weight_data_section()
         self.device = torch.device(device)
-        chunk = int(chunk_mb or os.environ.get("ZSE_LOAD_CHUNK_MB", 64)) << 20
-        ring = max(2, int(ring or os.environ.get("ZSE_LOAD_RING", 6)))
+        chunk = int(chunk_mb or env.integer("ZSE_LOAD_CHUNK_MB")) << 20
+        ring = max(2, int(ring or env.integer("ZSE_LOAD_RING")))
         readers = max(1, min(readers, ring - 1))
         t0 = time.monotonic()
         self.base = torch.empty(self.size, dtype=torch.uint8, device=self.device)
