@@ -243,6 +243,19 @@ def test_single_request_engine_has_the_reference_call_signatures(model_path, ora
     eng.destroy()
 
 
+def test_partial_rotary_matches_oracle(tmp_path):
+    """Phi-4-mini style: only the leading 3/4 of each head rotates."""
+    p = str(tmp_path / "partial.zse")
+    synth.write_random_model(p, synth.shape_config("tiny-phi3", partial_rotary_factor=0.75), seed=6)
+    oracle = OracleModel(ZSELoader(p))
+    eng = ZStreamerEngine(p, config=_cfg())
+    assert eng._model.inv_freq.numel() == 24             # 48 of 64 dims rotate
+    prompts = _prompts(eng.model_config.vocab_size, 2, seed=4)
+    for pr, o in zip(prompts, _run(eng, prompts, 10)):
+        assert o.output_tokens == oracle.greedy(pr, 10)
+    eng.destroy()
+
+
 @pytest.mark.parametrize("quant", ["int4", "fp16"])
 def test_phi3_stacked_projections_match_oracle(tmp_path, quant):
     """Phi-3 files keep ``[q; k; v]`` and ``[gate; up]`` stacked (zse-engine/zse_engine/format/arch/phi3.py): the engine

@@ -57,6 +57,12 @@ def _phi3():
                                       tie_word_embeddings=False))
 
 
+def _phi3_partial():
+    from transformers import Phi3Config, Phi3ForCausalLM
+    return Phi3ForCausalLM(Phi3Config(**COMMON, rms_norm_eps=1e-5, rope_theta=10000.0, pad_token_id=0,
+                                      partial_rotary_factor=0.5, tie_word_embeddings=False))
+
+
 def _gemma2():
     from transformers import Gemma2Config, Gemma2ForCausalLM
     return Gemma2ForCausalLM(Gemma2Config(**COMMON, head_dim=32, sliding_window=8, query_pre_attn_scalar=24,
@@ -91,11 +97,11 @@ def _randomise(model, seed):
                 p.copy_(0.08 * torch.randn(p.shape, generator=g))
 
 
-@pytest.mark.parametrize("family", ["llama", "llama_rope3", "llama_ropelinear", "mistral", "qwen2", "phi3", "gemma2", "gemma4",
+@pytest.mark.parametrize("family", ["llama", "llama_rope3", "llama_ropelinear", "mistral", "qwen2", "phi3", "phi3_partial", "gemma2", "gemma4",
                                     "gemma4_k_eq_v"])
 def test_oracle_matches_transformers(tmp_path, family):
     torch.manual_seed(0)
-    build = {"llama": _llama, "llama_rope3": _llama3_scaled, "llama_ropelinear": _llama_linear, "mistral": _mistral, "qwen2": _qwen2, "phi3": _phi3, "gemma2": _gemma2, "gemma4": _gemma4,
+    build = {"llama": _llama, "llama_rope3": _llama3_scaled, "llama_ropelinear": _llama_linear, "mistral": _mistral, "qwen2": _qwen2, "phi3": _phi3, "phi3_partial": _phi3_partial, "gemma2": _gemma2, "gemma4": _gemma4,
              "gemma4_k_eq_v": lambda: _gemma4(True)}[family]
     model = build().eval().float()
     _randomise(model, 1)
@@ -107,6 +113,10 @@ def test_oracle_matches_transformers(tmp_path, family):
     convert_hf_to_zse(str(hf_dir), out, quant_method=int(QuantMethod.NONE), skip_tokenizer=True)
     loader = ZSELoader(out)
     assert loader.config.arch == family.split("_")[0]
+    if family == "phi3_partial":
+        assert loader.config.partial_rotary_factor == 0.5
+    if family == "llama_rope3":
+        assert loader.config.rope_theta == 500000.0 and loader.config.rope_scaling["rope_type"] == "llama3"
     oracle = OracleModel(loader)
     # longer than the sliding window (8), so that local layers really drop tokens
     ids = torch.randint(0, COMMON["vocab_size"], (1, 21), generator=torch.Generator().manual_seed(2))

@@ -230,7 +230,10 @@ class DecoderModel:
         self.weight_bytes += self.lm_head.nbytes
         if mirror is not None:
             mirror.release()
-        self.inv_freq = ref.inv_freq(c.head_dim, c.rope_theta, c.rope_scaling).to(dev)
+        rot = c.head_dim
+        if c.partial_rotary_factor and not c.is_gemma:       # the leading part of each head rotates, the rest passes
+            rot = 2 * int(c.partial_rotary_factor * c.head_dim // 2)
+        self.inv_freq = ref.inv_freq(rot, c.rope_theta, c.rope_scaling).to(dev)
 
     # ---- buffers --------------------------------------------------------------------------------------
     def make_buffers(self, max_tokens: int, max_seqs: int, max_blocks: int, logits_rows: Optional[int] = None,

@@ -119,7 +119,10 @@ class OracleModel:
             sp = c.layer_spec(i) if gemma else None
             hd = sp.head_dim if sp else c.head_dim
             nkv = sp.num_kv_heads if sp else c.num_kv_heads
-            cos, sin = rope_cos_sin(pos, hd, sp.rope_theta if sp else c.rope_theta, sp.rotary_dim if sp else None,
+            lead = hd                  # Phi-style partial rotary: only the first ``lead`` dims of a head rotate
+            if not gemma and c.partial_rotary_factor:
+                lead = 2 * int(c.partial_rotary_factor * hd // 2)
+            cos, sin = rope_cos_sin(pos, lead, sp.rope_theta if sp else c.rope_theta, sp.rotary_dim if sp else None,
                                     None if gemma else c.rope_scaling)
             x = rmsnorm(h, self.w[p + "input_layernorm.weight"], c.rms_norm_eps)
             q = x @ self.w[p + "self_attn.q_proj.weight"].T
@@ -134,7 +137,11 @@ class OracleModel:
                 q = rmsnorm(q, self.w[p + "self_attn.q_norm.weight"], c.rms_norm_eps)
                 k = rmsnorm(k, self.w[p + "self_attn.k_norm.weight"], c.rms_norm_eps)
                 v = rmsnorm(v, None, c.rms_norm_eps)
-            q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
+            if lead < hd:
+                q = torch.cat([apply_rope(q[..., :lead], cos, sin), q[..., lead:]], dim=-1)
+                k = torch.cat([apply_rope(k[..., :lead], cos, sin), k[..., lead:]], dim=-1)
+            else:
+                q, k = apply_rope(q, cos, sin), apply_rope(k, cos, sin)
             rep = c.num_heads // nkv
             k = k.repeat_interleave(rep, dim=1)
             v = v.repeat_interleave(rep, dim=1)
