@@ -319,3 +319,22 @@ def test_rope_scaling_reaches_the_engine(tmp_path, scaling):
     for pr, o in zip(prompts, outs):
         assert o.output_tokens == oracle.greedy(pr, 8)
     eng.destroy()
+
+
+def test_uniform_sliding_window_matches_oracle(tmp_path):
+    """Mistral / Phi-3 style window: old blocks leave the cache, attention masks inside the oldest block that stays,
+    and the tokens are those of the oracle's exact mask (which is checked against transformers)."""
+    p = str(tmp_path / "window.zse")
+    synth.write_random_model(p, synth.shape_config("tiny", arch="mistral", sliding_window=24), seed=9)
+    oracle = OracleModel(ZSELoader(p))
+    full = str(tmp_path / "full.zse")
+    synth.write_random_model(full, synth.shape_config("tiny", arch="mistral"), seed=9)
+    eng = ZStreamerEngine(p, config=_cfg(block_size=16, prefill_chunk_size=32, max_batch_tokens=64))
+    assert eng._model.window == 24
+    prompts = _prompts(eng.model_config.vocab_size, 3, lo=40, hi=90, seed=12)
+    want = [oracle.greedy(pr, 12) for pr in prompts]
+    pr0 = prompts[0]
+    assert float((oracle.forward(pr0) - OracleModel(ZSELoader(full)).forward(pr0)).abs().max()) > 1e-5
+    for o, w in zip(_run(eng, prompts, 12), want):
+        assert o.output_tokens == w
+    eng.destroy()

@@ -46,6 +46,12 @@ def _mistral():
     return MistralForCausalLM(MistralConfig(**COMMON, sliding_window=None, head_dim=16, tie_word_embeddings=False))
 
 
+def _mistral_window():
+    from transformers import MistralConfig, MistralForCausalLM
+    return MistralForCausalLM(MistralConfig(**COMMON, sliding_window=8, head_dim=16, tie_word_embeddings=False,
+                                            attn_implementation="eager"))
+
+
 def _qwen2():
     from transformers import Qwen2Config, Qwen2ForCausalLM
     return Qwen2ForCausalLM(Qwen2Config(**COMMON, rms_norm_eps=1e-6, rope_theta=1e6, tie_word_embeddings=True))
@@ -97,11 +103,11 @@ def _randomise(model, seed):
                 p.copy_(0.08 * torch.randn(p.shape, generator=g))
 
 
-@pytest.mark.parametrize("family", ["llama", "llama_rope3", "llama_ropelinear", "mistral", "qwen2", "phi3", "phi3_partial", "gemma2", "gemma4",
+@pytest.mark.parametrize("family", ["llama", "llama_rope3", "llama_ropelinear", "mistral", "mistral_window", "qwen2", "phi3", "phi3_partial", "gemma2", "gemma4",
                                     "gemma4_k_eq_v"])
 def test_oracle_matches_transformers(tmp_path, family):
     torch.manual_seed(0)
-    build = {"llama": _llama, "llama_rope3": _llama3_scaled, "llama_ropelinear": _llama_linear, "mistral": _mistral, "qwen2": _qwen2, "phi3": _phi3, "phi3_partial": _phi3_partial, "gemma2": _gemma2, "gemma4": _gemma4,
+    build = {"llama": _llama, "llama_rope3": _llama3_scaled, "llama_ropelinear": _llama_linear, "mistral": _mistral, "qwen2": _qwen2, "mistral_window": _mistral_window, "phi3": _phi3, "phi3_partial": _phi3_partial, "gemma2": _gemma2, "gemma4": _gemma4,
              "gemma4_k_eq_v": lambda: _gemma4(True)}[family]
     model = build().eval().float()
     _randomise(model, 1)

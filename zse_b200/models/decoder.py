@@ -146,6 +146,9 @@ class DecoderModel:
         self.inv_freq: Optional[torch.Tensor] = None
         self.scale = 1.0 / math.sqrt(config.head_dim)
         self.comm = None            # parallel.comm.TPComm when tp_size > 1
+        # a uniform sliding window (Mistral, Phi-3): a token sees the last ``window`` positions, itself included; the
+        # cache lets blocks that fell out of every window go, attention masks inside the oldest block that is left
+        self.window = int(config.sliding_window or 0) if not config.layer_types else 0
         self.lora = None            # lora.manager.LoRAManager
         self.weight_bytes = 0
         self.load_stats: Dict[str, float] = {}
@@ -302,10 +305,11 @@ class DecoderModel:
                                   p.num_kv_heads, c.head_dim, bs)
             if mode == "decode":
                 ops.attn_decode(b.qkv, kv[li], b.block_tables, b.seq_lens, b.attn_out, num_seqs, p.num_heads,
-                                p.num_kv_heads, c.head_dim, bs, self.scale, b.attn_scratch, attn_splits)
+                                p.num_kv_heads, c.head_dim, bs, self.scale, b.attn_scratch, attn_splits,
+                                window=self.window)
             else:
                 ops.attn_prefill(b.qkv, kv[li], b.block_tables, b.cu_q, b.q_pos0, b.attn_out, num_seqs, M, max_q_len,
-                                 p.num_heads, p.num_kv_heads, c.head_dim, bs, self.scale)
+                                 p.num_heads, p.num_kv_heads, c.head_dim, bs, self.scale, window=self.window)
             planes = self._row_parallel(L.o, b.attn_out, M, b)
             add = lora.delta(li, "o_proj", b.attn_out, b, M) if lora is not None else None
             self._add_norm(b, planes, L.ln2, M, add)

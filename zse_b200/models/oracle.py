@@ -149,8 +149,9 @@ class OracleModel:
             if sp and sp.softcap:
                 s = torch.tanh(s / sp.softcap) * sp.softcap
             hidden = causal
-            if sp and sp.window:
-                hidden = causal | (pos[None, :] <= pos[:, None] - sp.window)
+            win = sp.window if sp else (int(c.sliding_window or 0) if not c.layer_types else 0)
+            if win:
+                hidden = causal | (pos[None, :] <= pos[:, None] - win)
             s = s.masked_fill(hidden[None], float("-inf"))
             a = torch.einsum("hts,shd->thd", torch.softmax(s, dim=-1), v).reshape(T, c.num_heads * hd)
             a = a @ self.w[p + "self_attn.o_proj.weight"].T

@@ -111,6 +111,8 @@ def try_build(model, buffers) -> Optional[NativeStep]:
     """A driver for this pair, or None when it does not apply (CPU, tensor parallelism, unsupported weights)."""
     if not enabled() or model.device.type != "cuda" or model.plan.tp_size != 1 or type(model).__name__ != "DecoderModel":
         return None
+    if getattr(model, "window", 0):          # the C++ driver calls the attention entry points without a window
+        return None
     try:
         return NativeStep(model, buffers)
     except (ValueError, AttributeError):
