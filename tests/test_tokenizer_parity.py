@@ -123,3 +123,51 @@ def test_gpt2_pattern_separates_letters_digits_and_underscores(pair):
     hf, ours = pair
     for text in ["abc123def", "snake_case_name", "x1_y2", "__dunder__ 99bottles", "naïve123café"]:
         assert ours.encode(text, add_bos=False) == hf.encode(text, add_special_tokens=False).ids, text
+
+
+# ---- SentencePiece-style BPE (Llama-2 / Mistral / Phi-3 / Gemma ship this form) -------------------------------------------
+def _sp_tokenizer(style: str):
+    from tokenizers import Tokenizer, decoders, models, normalizers, pre_tokenizers, trainers
+    byte_tokens = ["<0x%02X>" % b for b in range(256)]
+    tok = Tokenizer(models.BPE(unk_token="<unk>", byte_fallback=True, fuse_unk=True))
+    if style == "llama2":           # Prepend + Replace normalizers, no pre-tokenizer
+        tok.normalizer = normalizers.Sequence([normalizers.Prepend("▁"), normalizers.Replace(" ", "▁")])
+        tok.decoder = decoders.Sequence([decoders.Replace("▁", " "), decoders.ByteFallback(), decoders.Fuse(),
+                                         decoders.Strip(" ", 1, 0)])
+    elif style == "gemma":          # only the replacement, no dummy prefix
+        tok.normalizer = normalizers.Replace(" ", "▁")
+        tok.decoder = decoders.Sequence([decoders.Replace("▁", " "), decoders.ByteFallback(), decoders.Fuse()])
+    else:                           # a Metaspace pre-tokenizer: words split at U+2581
+        tok.pre_tokenizer = pre_tokenizers.Metaspace(replacement="▁", prepend_scheme="first", split=True)
+        tok.decoder = decoders.Sequence([decoders.Metaspace(replacement="▁", prepend_scheme="first"),
+                                         decoders.ByteFallback(), decoders.Fuse()])
+    trainer = trainers.BpeTrainer(vocab_size=900, special_tokens=["<unk>", "<s>", "</s>"] + byte_tokens,
+                                  show_progress=False)
+    ascii_only = [t for t in CORPUS if all(ord(c) < 128 for c in t)] + ["naive cafe  deja vu    wide   gaps"]
+    tok.train_from_iterator(ascii_only * 4, trainer)          # no accents or CJK in the vocabulary: they fall back
+    return tok
+
+
+@pytest.mark.parametrize("style", ["llama2", "gemma", "metaspace"])
+def test_sentencepiece_style_bpe_matches_the_tokenizers_library(tmp_path, style):
+    hf = _sp_tokenizer(style)
+    hf.save(str(tmp_path / "tokenizer.json"))
+    (tmp_path / "tokenizer_config.json").write_text(json.dumps({"eos_token": "</s>", "bos_token": "<s>"}))
+    ours = BPETokenizer.from_hf_dir(str(tmp_path))
+    assert ours.scheme == "metaspace" and ours.special_tokens.bos_id == hf.token_to_id("<s>")
+    assert ours.prepend == {"llama2": "always", "gemma": "never", "metaspace": "first"}[style]
+    rng = random.Random(3)
+    texts = CORPUS + ["", " ", "  two  spaces  ", "Hello world", "tab\there", "emoji \U0001F642 and 数学",
+                      "a</s>b <s> c", "</s>", "line\n\nbreaks\n"] + [_random_text(rng) for _ in range(150)]
+    for text in texts:
+        want = hf.encode(text, add_special_tokens=False).ids
+        got = ours.encode(text, add_bos=False)
+        assert got == want, (style, text, got[:12], want[:12])
+        if "<s>" not in text and "</s>" not in text:
+            assert ours.decode(got) == hf.decode(want, skip_special_tokens=False), (style, text)  # byte tokens are "special" in this toy vocabulary
+    again = BPETokenizer.deserialize(ours.serialize())
+    assert (again.scheme, again.prepend, again.split_words) == (ours.scheme, ours.prepend, ours.split_words)
+    assert again.encode("Hello  wide world \U0001F680", add_bos=False) == ours.encode("Hello  wide world \U0001F680",
+                                                                                   add_bos=False)
+    long_text = " ".join(CORPUS) * 40                        # ~20k characters in one piece: the heap keeps it quick
+    assert ours.encode(long_text, add_bos=False) == hf.encode(long_text, add_special_tokens=False).ids

@@ -5,6 +5,12 @@ the GPT-2 pre-tokenisation regex, lowest-rank merge loop, added tokens split out
 ``encode(text, add_bos=True, add_eos=False)``, ``decode(ids, skip_special=True)``; the section
 stores ``{vocab, merges, special_tokens, added_tokens}``.  The merge loop here keeps the word as a
 list and re-scans only for the chosen pair; results are cached per pre-token.
+
+Beyond the reference: SentencePiece-style BPE (``scheme = "metaspace"``), the form in which Llama-2, Mistral, Phi-3 and
+Gemma ship their ``tokenizer.json`` - spaces become U+2581 through a normalizer or a Metaspace pre-tokenizer, merges run
+over characters of the whole text (or of each word), characters outside the vocabulary become ``<0xNN>`` byte tokens.
+A byte-level-only reader mis-tokenises those models.  Both schemes are checked id for id against the ``tokenizers``
+library (``tests/test_tokenizer_parity.py``).
 """
 from __future__ import annotations
 
@@ -72,6 +78,43 @@ def _split_pattern_of(pre) -> Optional[str]:
     return None
 
 
+def _components(node) -> List[dict]:
+    """A normalizer / pre-tokenizer / decoder entry of tokenizer.json flattened (``Sequence`` holds a list)."""
+    if not isinstance(node, dict):
+        return []
+    if node.get("type") == "Sequence":
+        out: List[dict] = []
+        for key in ("normalizers", "pretokenizers", "decoders"):
+            for sub in node.get(key) or []:
+                out += _components(sub)
+        return out
+    return [node]
+
+
+def _scheme_of(data: dict) -> Tuple[str, str, bool]:
+    """(scheme, prepend, split_words) of a tokenizer.json: byte-level BPE (GPT-2, Qwen2, Llama-3) or SentencePiece-style
+    BPE (Llama-2, Mistral, Phi-3, Gemma: space -> U+2581 by a normalizer or a Metaspace pre-tokenizer)."""
+    pre, norm, dec = (_components(data.get(k)) for k in ("pre_tokenizer", "normalizer", "decoder"))
+    if any(c.get("type") == "ByteLevel" for c in pre + dec):
+        return "bytelevel", "never", False
+    meta_pre = next((c for c in pre if c.get("type") == "Metaspace"), None)
+    replaces = any(c.get("type") == "Replace" and (c.get("pattern") or {}).get("String") == " "
+                   and c.get("content") == "\u2581" for c in norm)
+    if meta_pre is None and not replaces and not (data.get("model") or {}).get("byte_fallback"):
+        return "bytelevel", "never", False
+    prepend = "never"
+    if any(c.get("type") == "Prepend" and c.get("prepend") == "\u2581" for c in norm):
+        prepend = "always"
+    split_words = False
+    if meta_pre is not None:
+        scheme = meta_pre.get("prepend_scheme")
+        if scheme is None:
+            scheme = "always" if meta_pre.get("add_prefix_space", True) else "never"
+        prepend = scheme if prepend == "never" else prepend
+        split_words = bool(meta_pre.get("split", True))
+    return "metaspace", prepend, split_words
+
+
 @dataclass
 class SpecialTokens:
     bos_id: int = 1
@@ -95,6 +138,12 @@ class BPETokenizer:
     special_tokens: SpecialTokens = field(default_factory=SpecialTokens)
     added_tokens: Dict[str, int] = field(default_factory=dict)
     pretoken_pattern: Optional[str] = None     # None: GPT-2's pattern
+    # "bytelevel": GPT-2 style (bytes mapped to printable characters, regex pre-tokens) - what the reference implements.
+    # "metaspace": SentencePiece-style BPE as Llama-2 / Mistral / Phi-3 / Gemma ship it in tokenizer.json: spaces
+    # become U+2581, merges run over characters, characters outside the vocabulary fall back to <0xNN> byte tokens
+    scheme: str = "bytelevel"
+    prepend: str = "never"                     # metaspace: U+2581 in front of "never" | "always" (every piece of text) | "first"
+    split_words: bool = False                  # metaspace: merges stop at word starts (a Metaspace pre-tokenizer)
 
     def __post_init__(self):
         self._rebuild_caches()
@@ -110,6 +159,94 @@ class BPETokenizer:
             self._added_re: Optional[re.Pattern] = re.compile("(" + "|".join(re.escape(t) for t in alts) + ")")
         else:
             self._added_re = None
+        self._byte_ids = [self.vocab.get("<0x%02X>" % b) for b in range(256)] if self.scheme == "metaspace" else []
+
+    # ---- SentencePiece-style pieces ----------------------------------------------------------
+    def _merge_long(self, symbols: List[str]) -> List[str]:
+        """BPE over an arbitrarily long symbol list: a heap of candidate merges over a linked list, so that a whole
+        paragraph (these tokenizers have no pre-tokens) costs n log n rather than n^2."""
+        import heapq
+        n = len(symbols)
+        if n < 2:
+            return symbols
+        ranks = self._ranks
+        sym = list(symbols)
+        prev, nxt = list(range(-1, n - 1)), list(range(1, n + 1))
+        alive = [True] * n
+        heap = []
+        for i in range(n - 1):
+            r = ranks.get((sym[i], sym[i + 1]))
+            if r is not None:
+                heap.append((r, i, sym[i], sym[i + 1]))
+        heapq.heapify(heap)
+        while heap:
+            r, i, a, b = heapq.heappop(heap)
+            j = nxt[i] if alive[i] else n
+            if not alive[i] or j >= n or not alive[j] or sym[i] != a or sym[j] != b:
+                continue                       # a stale entry: one of the two was merged away meanwhile
+            sym[i] = a + b
+            alive[j] = False
+            k = nxt[j]
+            nxt[i] = k
+            if k < n:
+                prev[k] = i
+            h = prev[i]
+            if h >= 0:
+                r2 = ranks.get((sym[h], sym[i]))
+                if r2 is not None:
+                    heapq.heappush(heap, (r2, h, sym[h], sym[i]))
+            if k < n:
+                r2 = ranks.get((sym[i], sym[k]))
+                if r2 is not None:
+                    heapq.heappush(heap, (r2, i, sym[i], sym[k]))
+        return [sym[i] for i in range(n) if alive[i]]
+
+    def _encode_metaspace(self, text: str, at_start: bool) -> List[int]:
+        if not text:
+            return []
+        text = text.replace(" ", "\u2581")
+        if self.prepend == "always" or (self.prepend == "first" and at_start):
+            if not (self.split_words and text.startswith("\u2581")):
+                text = "\u2581" + text
+        if self.split_words:                   # every U+2581 starts a new word; merges stay inside words
+            words, cur = [], ""
+            for ch in text:
+                if ch == "\u2581" and cur:
+                    words.append(cur)
+                    cur = ""
+                cur += ch
+            words.append(cur)
+        else:
+            words = [text]
+        ids, vocab, unk = [], self.vocab, self.special_tokens.unk_id
+        for w in words:
+            hit = self._cache.get(w) if len(w) < 64 else None
+            if hit is None:
+                hit = tuple(self._merge_long(list(w)))
+                if len(w) < 64 and len(self._cache) < 200_000:
+                    self._cache[w] = hit
+            for piece in hit:
+                tid = vocab.get(piece)
+                if tid is not None:
+                    ids.append(tid)
+                    continue
+                for b in piece.encode("utf-8"):            # a character the vocabulary does not have
+                    bid = self._byte_ids[b] if self._byte_ids else None
+                    ids.append(bid if bid is not None else unk)
+        return ids
+
+    def _decode_metaspace(self, toks: List[str]) -> str:
+        out = bytearray()
+        for t in toks:
+            if len(t) == 6 and t.startswith("<0x") and t.endswith(">"):
+                try:
+                    out.append(int(t[3:5], 16))
+                    continue
+                except ValueError:
+                    pass
+            out += t.encode("utf-8")
+        text = out.decode("utf-8", errors="replace").replace("\u2581", " ")
+        return text[1:] if self.prepend != "never" and text.startswith(" ") else text
 
     # ---- BPE -------------------------------------------------------------------------------
     def _bpe(self, token: str) -> Tuple[str, ...]:
@@ -151,7 +288,9 @@ class BPETokenizer:
 
     def encode(self, text: str, add_bos: bool = True, add_eos: bool = False) -> List[int]:
         ids: List[int] = [self.special_tokens.bos_id] if add_bos else []
+        meta = self.scheme == "metaspace"
         if self._added_re is not None:
+            at = 0
             for part in self._added_re.split(text):
                 if not part:
                     continue
@@ -159,9 +298,10 @@ class BPETokenizer:
                 if tid is not None:
                     ids.append(tid)
                 else:
-                    ids.extend(self._encode_chunk(part))
+                    ids.extend(self._encode_metaspace(part, at == 0) if meta else self._encode_chunk(part))
+                at += len(part)
         else:
-            ids.extend(self._encode_chunk(text))
+            ids.extend(self._encode_metaspace(text, True) if meta else self._encode_chunk(text))
         if add_eos:
             ids.append(self.special_tokens.eos_id)
         return ids
@@ -169,6 +309,9 @@ class BPETokenizer:
     def decode(self, ids, skip_special: bool = True) -> str:
         st = self.special_tokens
         skip = {st.bos_id, st.eos_id, st.pad_id} if skip_special else ()
+        if self.scheme == "metaspace":
+            toks = [self._id_to_token.get(int(t)) for t in ids if t not in skip]
+            return self._decode_metaspace([t for t in toks if t is not None])
         out = bytearray()
         for tid in ids:
             if tid in skip:
@@ -198,6 +341,8 @@ class BPETokenizer:
              "special_tokens": self.special_tokens.to_dict(), "added_tokens": self.added_tokens}
         if self.pretoken_pattern:          # an extra key: readers that do not know it keep GPT-2's pattern
             d["pretoken_pattern"] = self.pretoken_pattern
+        if self.scheme != "bytelevel":     # more extra keys; a reader without them would mis-tokenise such a model anyway
+            d["scheme"], d["prepend"], d["split_words"] = self.scheme, self.prepend, self.split_words
         return serializer.encode(d)
 
     @classmethod
@@ -205,7 +350,9 @@ class BPETokenizer:
         d = serializer.decode(data)
         return cls(vocab=d["vocab"], merges=[tuple(m) for m in d["merges"]],
                    special_tokens=SpecialTokens.from_dict(d.get("special_tokens", {})),
-                   added_tokens=d.get("added_tokens", {}), pretoken_pattern=d.get("pretoken_pattern"))
+                   added_tokens=d.get("added_tokens", {}), pretoken_pattern=d.get("pretoken_pattern"),
+                   scheme=d.get("scheme", "bytelevel"), prepend=d.get("prepend", "never"),
+                   split_words=bool(d.get("split_words", False)))
 
     # ---- HuggingFace import ----------------------------------------------------------------
     @classmethod
@@ -240,8 +387,10 @@ class BPETokenizer:
             # lists as well (GPT-2's <|endoftext|>, Mistral's <s>): that is what the tokenizers library does
             if content:
                 added[content] = tid
+        scheme, prepend, split_words = _scheme_of(data)
         return cls(vocab=vocab, merges=merges, special_tokens=special, added_tokens=added,
-                   pretoken_pattern=_split_pattern_of(data.get("pre_tokenizer")))
+                   pretoken_pattern=_split_pattern_of(data.get("pre_tokenizer")) if scheme == "bytelevel" else None,
+                   scheme=scheme, prepend=prepend, split_words=split_words)
 
     @classmethod
     def from_hf_dir(cls, model_dir: str) -> "BPETokenizer":
