@@ -171,3 +171,26 @@ def test_sentencepiece_style_bpe_matches_the_tokenizers_library(tmp_path, style)
                                                                                    add_bos=False)
     long_text = " ".join(CORPUS) * 40                        # ~20k characters in one piece: the heap keeps it quick
     assert ours.encode(long_text, add_bos=False) == hf.encode(long_text, add_special_tokens=False).ids
+
+
+def test_whole_pretokens_in_the_vocabulary_skip_the_merges(tmp_path):
+    """Llama-3's ``ignore_merges``: "abc" is a vocabulary entry that the merges alone would never produce."""
+    from tokenizers import Tokenizer, decoders, models, pre_tokenizers
+    alphabet = sorted(pre_tokenizers.ByteLevel.alphabet())
+    vocab = {ch: i for i, ch in enumerate(alphabet)}
+    for t in ("ab", "abc", "Ġab"):
+        vocab[t] = len(vocab)
+    merges = [("a", "b"), ("Ġ", "ab")]
+    for flag in (True, False):
+        hf = Tokenizer(models.BPE(vocab, merges, ignore_merges=flag))
+        hf.pre_tokenizer = pre_tokenizers.ByteLevel(add_prefix_space=False, use_regex=True)
+        hf.decoder = decoders.ByteLevel()
+        d = tmp_path / str(flag)
+        d.mkdir()
+        hf.save(str(d / "tokenizer.json"))
+        ours = BPETokenizer.from_hf_dir(str(d))
+        assert ours.ignore_merges is flag
+        for text in ("abc", "abc ab abcd", " abc"):
+            assert ours.encode(text, add_bos=False) == hf.encode(text, add_special_tokens=False).ids, (flag, text)
+        assert BPETokenizer.deserialize(ours.serialize()).ignore_merges is flag
+    assert len(ours.encode("abc", add_bos=False)) == 2            # without the flag: "ab" + "c"

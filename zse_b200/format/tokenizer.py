@@ -144,6 +144,7 @@ class BPETokenizer:
     scheme: str = "bytelevel"
     prepend: str = "never"                     # metaspace: U+2581 in front of "never" | "always" (every piece of text) | "first"
     split_words: bool = False                  # metaspace: merges stop at word starts (a Metaspace pre-tokenizer)
+    ignore_merges: bool = False                # byte-level: a pre-token that is in the vocabulary as a whole is taken as it is (Llama-3)
 
     def __post_init__(self):
         self._rebuild_caches()
@@ -282,6 +283,11 @@ class BPETokenizer:
         ids, vocab, unk, enc = [], self.vocab, self.special_tokens.unk_id, BYTE_ENCODER
         for piece in self._pretoken.findall(text):
             mapped = "".join(enc[b] for b in piece.encode("utf-8"))
+            if self.ignore_merges:
+                whole = vocab.get(mapped)
+                if whole is not None:
+                    ids.append(whole)
+                    continue
             for sym in self._bpe(mapped):
                 ids.append(vocab.get(sym, unk))
         return ids
@@ -343,6 +349,8 @@ class BPETokenizer:
             d["pretoken_pattern"] = self.pretoken_pattern
         if self.scheme != "bytelevel":     # more extra keys; a reader without them would mis-tokenise such a model anyway
             d["scheme"], d["prepend"], d["split_words"] = self.scheme, self.prepend, self.split_words
+        if self.ignore_merges:
+            d["ignore_merges"] = True
         return serializer.encode(d)
 
     @classmethod
@@ -352,7 +360,7 @@ class BPETokenizer:
                    special_tokens=SpecialTokens.from_dict(d.get("special_tokens", {})),
                    added_tokens=d.get("added_tokens", {}), pretoken_pattern=d.get("pretoken_pattern"),
                    scheme=d.get("scheme", "bytelevel"), prepend=d.get("prepend", "never"),
-                   split_words=bool(d.get("split_words", False)))
+                   split_words=bool(d.get("split_words", False)), ignore_merges=bool(d.get("ignore_merges", False)))
 
     # ---- HuggingFace import ----------------------------------------------------------------
     @classmethod
@@ -390,7 +398,8 @@ class BPETokenizer:
         scheme, prepend, split_words = _scheme_of(data)
         return cls(vocab=vocab, merges=merges, special_tokens=special, added_tokens=added,
                    pretoken_pattern=_split_pattern_of(data.get("pre_tokenizer")) if scheme == "bytelevel" else None,
-                   scheme=scheme, prepend=prepend, split_words=split_words)
+                   scheme=scheme, prepend=prepend, split_words=split_words,
+                   ignore_merges=bool(model.get("ignore_merges", False)))
 
     @classmethod
     def from_hf_dir(cls, model_dir: str) -> "BPETokenizer":
