@@ -230,3 +230,23 @@ def test_client_that_goes_away_mid_stream_is_cancelled(server):
     assert produced < 200, produced            # it did not run to its 230 tokens
     status, _, health = http(server, "GET", "/health")
     assert status == 200 and health["status"] == "ok"
+
+
+def test_chat_template_follows_the_tokenizer():
+    from zse_b200.server.api_openai import TEMPLATES, template_for_arch
+
+    class Tok:
+        def __init__(self, *tokens):
+            self.tokens = set(tokens)
+
+        def token_to_id(self, t):
+            return 1 if t in self.tokens else None
+
+    assert template_for_arch("llama") == "llama" and template_for_arch("qwen2") == "chatml"
+    assert template_for_arch("llama", Tok("<|start_header_id|>", "<|eot_id|>")) == "llama3"
+    assert template_for_arch("llama", Tok("<|im_start|>")) == "chatml"            # a ChatML fine-tune of a Llama
+    assert template_for_arch("phi3", Tok("<|assistant|>", "<|end|>")) == "phi3"
+    assert template_for_arch("phi3", Tok()) == "chatml" and template_for_arch("gemma2", Tok()) == "gemma"
+    msgs = [{"role": "system", "content": "be brief"}, {"role": "user", "content": "hi"}]
+    assert TEMPLATES["llama3"](msgs).endswith("hi<|eot_id|><|start_header_id|>assistant<|end_header_id|>\n\n")
+    assert TEMPLATES["phi3"](msgs) == "<|system|>\nbe brief<|end|>\n<|user|>\nhi<|end|>\n<|assistant|>\n"

@@ -35,7 +35,7 @@ from .sched.request import FinishReason, GenerationParams, InferenceRequest, Req
 from .sched.scheduler import Scheduler, SchedulerConfig
 from .utils import env
 
-CHAT_STOP_MARKERS = ("<|im_end|>", "<|im_start|>", "<|eot_id|>", "<end_of_turn>")
+CHAT_STOP_MARKERS = ("<|im_end|>", "<|im_start|>", "<|eot_id|>", "<end_of_turn>", "<|end|>")
 
 
 @dataclass

@@ -18,7 +18,7 @@ from typing import Dict, List, Optional
 from .router import Request, Response
 from .sse import SSE_DONE, chat_chunk, completion_chunk
 
-CHAT_MARKERS = ("<|im_end|>", "<|im_start|>", "<|eot_id|>", "<end_of_turn>", "</s>")
+CHAT_MARKERS = ("<|im_end|>", "<|im_start|>", "<|eot_id|>", "<end_of_turn>", "<|end|>", "</s>")
 REQUEST_TIMEOUT_S = 120.0
 
 
@@ -52,10 +52,36 @@ def format_gemma(messages: List[Dict]) -> str:
     return "\n".join(parts)
 
 
-TEMPLATES = {"chatml": format_chatml, "llama": format_llama, "gemma": format_gemma}
+def format_llama3(messages: List[Dict]) -> str:
+    parts = [f"<|start_header_id|>{m.get('role', 'user')}<|end_header_id|>\n\n{m.get('content', '')}<|eot_id|>"
+             for m in messages]
+    return "".join(parts) + "<|start_header_id|>assistant<|end_header_id|>\n\n"
 
 
-def template_for_arch(arch: str) -> str:
+def format_phi3(messages: List[Dict]) -> str:
+    parts = [f"<|{m.get('role', 'user')}|>\n{m.get('content', '')}<|end|>\n" for m in messages]
+    return "".join(parts) + "<|assistant|>\n"
+
+
+TEMPLATES = {"chatml": format_chatml, "llama": format_llama, "llama3": format_llama3, "phi3": format_phi3,
+             "gemma": format_gemma}
+
+
+def template_for_arch(arch: str, tokenizer=None) -> str:
+    """The chat layout of a model.  The tokenizer decides when it has one of the layouts' marker tokens (a Llama-3
+    file and a Llama-2 file share the architecture name but not the template); otherwise the architecture does."""
+    has = (lambda t: tokenizer.token_to_id(t) is not None) if tokenizer is not None else (lambda t: False)
+    try:
+        if has("<|im_start|>"):
+            return "chatml"
+        if has("<|start_header_id|>") and has("<|eot_id|>"):
+            return "llama3"
+        if has("<start_of_turn>"):
+            return "gemma"
+        if has("<|assistant|>") and has("<|end|>"):
+            return "phi3"
+    except Exception:
+        pass
     a = (arch or "").lower()
     if "llama" in a or "mistral" in a:
         return "llama"
@@ -79,7 +105,7 @@ class OpenAIAPI:
         self._db = db
         self._rag_engine = rag_engine
         arch = getattr(getattr(engine, "model_config", None), "arch", "") if engine is not None else ""
-        self._chat_template = template_for_arch(arch)
+        self._chat_template = template_for_arch(arch, tokenizer)
         self._created = int(time.time())
 
     def set_rag_engine(self, rag_engine) -> None:
