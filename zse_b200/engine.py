@@ -184,8 +184,13 @@ class ZStreamerEngine:
         if tok is None:
             return stops
         eos = tok.special_tokens.eos_id
-        if eos is not None and not (self._config.vocab_size > 50000 and eos < 100):
-            stops.append(eos)
+        if eos is not None:
+            # a tiny id in a large vocabulary is usually the default of a file without an end marker (the reference's
+            # rule) - unless the token at that id says that it is one (Gemma's <eos> is id 1 of 256000)
+            text = str(getattr(tok, "_id_to_token", {}).get(eos, "")).lower()
+            named = any(k in text for k in ("eos", "</s>", "endoftext", "end_of_text", "end_of_sentence"))
+            if named or not (self._config.vocab_size > 50000 and eos < 100):
+                stops.append(eos)
         for marker in CHAT_STOP_MARKERS:
             tid = tok.token_to_id(marker)
             if tid is not None and tid not in stops:
