@@ -194,3 +194,34 @@ def test_whole_pretokens_in_the_vocabulary_skip_the_merges(tmp_path):
             assert ours.encode(text, add_bos=False) == hf.encode(text, add_special_tokens=False).ids, (flag, text)
         assert BPETokenizer.deserialize(ours.serialize()).ignore_merges is flag
     assert len(ours.encode("abc", add_bos=False)) == 2            # without the flag: "ab" + "c"
+
+
+def test_sentencepiece_style_tokenizer_survives_conversion_and_serving(tmp_path):
+    """HF directory (tiny random Llama + a Llama-2 style tokenizer.json) -> .zse -> engine: the tokenizer inside the
+    file encodes like the library, and text generation round-trips through it."""
+    transformers = pytest.importorskip("transformers")
+    from transformers import LlamaConfig, LlamaForCausalLM
+    from zse_b200.config import EngineConfig
+    from zse_b200.engine import ZSEEngine
+    from zse_b200.format.convert import convert_hf_to_zse
+    from zse_b200.format.loader import ZSELoader
+    hf_tok = _sp_tokenizer("llama2")
+    vocab = hf_tok.get_vocab_size()
+    model = LlamaForCausalLM(LlamaConfig(vocab_size=vocab, hidden_size=64, intermediate_size=128, num_hidden_layers=2,
+                                         num_attention_heads=4, num_key_value_heads=2, max_position_embeddings=256,
+                                         bos_token_id=hf_tok.token_to_id("<s>"), eos_token_id=hf_tok.token_to_id("</s>")))
+    d = tmp_path / "hf"
+    model.save_pretrained(str(d), safe_serialization=True)
+    hf_tok.save(str(d / "tokenizer.json"))
+    (d / "tokenizer_config.json").write_text(json.dumps({"eos_token": "</s>", "bos_token": "<s>"}))
+    out = str(tmp_path / "m.zse")
+    convert_hf_to_zse(str(d), out, quant_method=0)
+    tok = ZSELoader(out).tokenizer
+    text = "The quick brown fox, naïve café 🙂"
+    assert tok.scheme == "metaspace" and tok.encode(text, add_bos=False) == hf_tok.encode(
+        text, add_special_tokens=False).ids
+    eng = ZSEEngine(out, config=EngineConfig(device="cpu", max_seq_len=128, quiet=True))
+    ids = eng.generate_tokens(tok.encode(text), max_tokens=6, temperature=0.0)
+    assert len(ids) <= 6 and isinstance(eng.generate(text, max_tokens=6, temperature=0.0), str)
+    assert tok.decode(tok.encode(text)) == text
+    eng.destroy()
