@@ -247,3 +247,29 @@ def test_small_reference_named_accessors(tmp_path):
     assert Renaming().map_tensor_name("transformer.wte.weight") == "embed_tokens.weight"
     assert "layers.0.self_attn.qkv_proj.weight" in get_adapter("phi3").expected_tensors(
         shape_config("tiny-phi3"))
+
+
+def test_package_level_names():
+    """What the reference exports from its sub-packages is reachable from the matching ones here."""
+    import importlib
+    wanted = {
+        "zse_b200.format": ["MAGIC", "VERSION", "SectionType", "Flags", "QuantMethod", "FileHeader", "SectionEntry",
+                            "read_header_and_sections", "ModelConfig", "QuantConfig", "WeightIndex", "WeightEntry",
+                            "quantize_tensor", "dequantize_tensor", "BPETokenizer", "ZSEWriter"],
+        "zse_b200.cache": ["BlockPool", "Block", "PageTable", "SequenceEntry", "Evictor", "EvictionCandidate",
+                           "BlockDedup", "KVCacheManager", "KVCacheHandle", "CacheStats", "AttentionMetadata",
+                           "build_attention_metadata"],
+        "zse_b200.sched": ["ZStreamerEngine", "SchedulerConfig", "Scheduler", "MemoryBudget", "RequestQueue",
+                           "BatchRunner", "InferenceRequest", "RequestOutput", "GenerationParams", "RequestState",
+                           "FinishReason"],
+        "zse_b200.server": ["ZSEServer", "ServerDatabase", "AuthManager"],
+        "zse_b200.runtime": ["ZSEEngine", "VRAMAllocator", "WeightLoader", "InferenceKernels", "ModelRunner",
+                             "CUDAGraphRunner", "FastDecoder"],
+        "zse_b200.parallel": ["TensorParallelGroup", "TPConfig", "tp_launch", "TPEngine", "TPWeightLoader",
+                              "NcclCommunicator"],
+    }
+    for mod, names in wanted.items():
+        m = importlib.import_module(mod)
+        assert not [n for n in names if not hasattr(m, n)], mod
+    with pytest.raises(AttributeError):
+        importlib.import_module("zse_b200.runtime").NoSuchThing

@@ -1,7 +1,8 @@
 """The ``.zse`` model container: reader, writer, quantisers, tokenizer, converters."""
 from .config import ModelConfig, QuantConfig
-from .header import FileHeader, SectionEntry
+from .header import FileHeader, SectionEntry, read_header_and_sections
 from .loader import ZSELoader
+from .quantize import dequantize_tensor, quantize_tensor
 from .spec import MAGIC, VERSION, Flags, QuantMethod, SectionType, should_quantize
 from .tokenizer import BPETokenizer, SpecialTokens
 from .weight_index import WeightEntry, WeightIndex
@@ -9,4 +10,4 @@ from .writer import ZSEWriter
 
 __all__ = ["ModelConfig", "QuantConfig", "FileHeader", "SectionEntry", "ZSELoader", "ZSEWriter", "MAGIC", "VERSION",
            "Flags", "QuantMethod", "SectionType", "should_quantize", "BPETokenizer", "SpecialTokens", "WeightEntry",
-           "WeightIndex"]
+           "WeightIndex", "read_header_and_sections", "quantize_tensor", "dequantize_tensor"]
