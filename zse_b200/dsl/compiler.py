@@ -45,7 +45,7 @@ class CompiledKernel:
             drv = _driver()
             import torch
             torch.cuda.init()
-            torch.cuda.current_stream()                      # makes torch's primary context current
+            torch.empty(1, device=f"cuda:{torch.cuda.current_device()}")     # torch's primary context is now current
             err, mod = drv.cuModuleLoadData(self.cubin)
             _check(err, f"loading the module of '{self.name}'")
             err, fn = drv.cuModuleGetFunction(mod, self.name.encode())
