@@ -474,3 +474,25 @@ def test_emulator_finds_data_races():
     a, b, c = torch.randn(16, 16).half(), torch.randn(16, 16).half(), torch.zeros(16, 16)
     wmma_matmul.emulate((1, 1), (32,), (a, b, c, 16, 16), check_races=True)
     torch.testing.assert_close(c, a.float() @ b.float(), atol=1e-4, rtol=1e-4)
+
+
+@zse.kernel
+def layernorm(x: zse.Tensor, weight: zse.Tensor, out: zse.Tensor, n: int):
+    """Two block reductions in a row (mean, then variance): the reduction's scratch is reused safely."""
+    tid = zse.thread_id(0)
+    idx = zse.block_id(0) * n + tid
+    val = x[idx] if tid < n else 0.0
+    mean = zse.block_reduce_sum(val) / float(n)
+    diff = val - mean if tid < n else 0.0
+    var = zse.block_reduce_sum(diff * diff) / float(n)
+    if tid < n:
+        out[idx] = weight[tid] * (diff * zse.rsqrt(var + 0.00001))
+
+
+def test_layernorm_with_two_reductions():
+    x, w = torch.randn(3, 50, generator=torch.Generator().manual_seed(8)), torch.rand(50) + 0.5
+    out = torch.zeros_like(x)
+    layernorm.emulate((3,), (64,), (x, w, out, 50), check_races=True)
+    want = torch.nn.functional.layer_norm(x, (50,), eps=1e-5) * w
+    torch.testing.assert_close(out, want, atol=1e-5, rtol=1e-4)
+    assert layernorm.source().count("zse_block_sum_float(") >= 3       # the helper and its two call sites
