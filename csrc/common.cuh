@@ -116,6 +116,27 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   return true;
 }
 
+// Same contract, for the one thread whose wake-up latency is on the critical path (an MMA issuer): it polls without
+// the suspend hint, so it sees the phase flip within a few cycles instead of after a scheduler wake-up.
+__device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity, volatile int* abort_flag, Status* st,
+                                               unsigned where, unsigned detail) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = globaltimer_ns();
+  unsigned spins = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++spins & 0xFF) == 0) {
+      if (*abort_flag) return false;
+      if (globaltimer_ns() - t0 > kWaitLimitNs) {
+        report(st, kWaitTimeout, where, detail);
+        *abort_flag = 1;
+        __threadfence_block();
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
 // ---- TMA -------------------------------------------------------------------------------------
 // 1-D bulk copy global -> shared (16-byte aligned addresses, size a multiple of 16).
 __device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_gmem, uint32_t bytes, uint64_t* bar) {

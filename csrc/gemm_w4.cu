@@ -155,6 +155,12 @@ __device__ __forceinline__ void drain(uint64_t* full, int ring, int issued) {
   }
 }
 
+#ifdef ZSE_W4_SPIN
+#define ZSE_W4_ISSUER_WAIT mbar_wait_spin
+#else
+#define ZSE_W4_ISSUER_WAIT mbar_wait
+#endif
+
 #ifdef ZSE_W4_TIMING
 #define TICK(var) long long var = clock64()
 #define ACC(slot, t0) tacc[slot] += clock64() - (t0)
@@ -179,6 +185,9 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4Args a) {
   float* park = reinterpret_cast<float*>(smem);              // reused after the main loop: [R*NT cols][128 rows]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#ifdef ZSE_W4_TIMING
+  const long long t_entry = clock64();
+#endif
   // The next kernel of the stream may start its own set-up now.  This kernel in turn starts before the one ahead
   // of it has finished: barrier set-up, the TMEM allocation and the weight stream (constant data) run at once,
   // while the activation producer and the epilogue wait for the producer of the activations (pdl_wait below).
@@ -220,6 +229,7 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4Args a) {
 #ifdef ZSE_W4_TIMING
   long long tacc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
   const long long t_start = clock64();
+  const long long t_setup = t_start - t_entry;
 #endif
 
   if constexpr (DUAL) {
@@ -269,16 +279,18 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4Args a) {
         for (int u = p; u < n_units; u += 2) {
           const int sx = u % SX;
           TICK(tx);
-          if (!mbar_wait(&bars->x_full[sx], (u / SX) & 1, abort_flag, a.status, 3, u)) break;
+          if (!ZSE_W4_ISSUER_WAIT(&bars->x_full[sx], (u / SX) & 1, abort_flag, a.status, 3, u)) break;
           ACC(0, tx);
           TICK(ta);
-          if (!mbar_wait(&bars->a_ready[p], aph, abort_flag, a.status, 4, u)) break;
+          if (!ZSE_W4_ISSUER_WAIT(&bars->a_ready[p], aph, abort_flag, a.status, 4, u)) break;
           ACC(1, ta);
           TICK(ti);
           tc_fence_after_sync();
           // slot p was refilled for this chunk only after the MMAs of chunk u-2 had completed, so the activation
           // stage that chunk used is free as well
+#ifndef ZSE_W4_EARLY_X
           if (u >= 2) mbar_arrive(&bars->x_empty[(u - 2) % SX]);
+#endif
           const uint64_t bd = desc0 + uint64_t((sx * Cfg::kXStage) >> 4);
 #pragma unroll
           for (int j = 0; j < 8; ++j)
@@ -301,6 +313,9 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4Args a) {
         TICK(t0);
         if (!mbar_wait(&bars->w_full[sw], wph, abort_flag, a.status, 5, u)) break;
         ACC(0, t0);
+#ifdef ZSE_W4_TIMING
+        if (u == p) tacc[6] = clock64() - t_start;
+#endif
         TICK(t1);
         const uint8_t* chunk = w_ring + sw * kW4ChunkBytes;
         uint4 pk[4];
@@ -310,25 +325,45 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4Args a) {
         __syncwarp();
         if (lane == 0) mbar_arrive(&bars->w_empty[sw]);        // the chunk is in registers: its slot may be refilled
         ACC(1, t1);
+        const __half2 s2 = __half2half2(__low2half(sz)), z2 = __half2half2(__high2half(sz));
+        uint32_t o[32];
+#ifdef ZSE_W4_HOIST
+        // the first half of the chunk is dequantised while the MMAs of this pipeline's previous chunk still run
+#pragma unroll
+        for (int p2 = 0; p2 < 2; ++p2) {
+          const uint4 w4 = pk[p2];
+          dequant_word(w4.x, s2, z2, o + p2 * 16 + 0);
+          dequant_word(w4.y, s2, z2, o + p2 * 16 + 4);
+          dequant_word(w4.z, s2, z2, o + p2 * 16 + 8);
+          dequant_word(w4.w, s2, z2, o + p2 * 16 + 12);
+        }
+#endif
         TICK(t2);
         if (u >= 2) {
           if (!mbar_wait(&bars->pair_done[p], dph, abort_flag, a.status, 6, u)) break;
           dph ^= 1;
+#ifdef ZSE_W4_EARLY_X
+          // the MMAs of chunk u-2 are complete: its activation stage may be refilled
+          if (q == 0 && lane == 0) mbar_arrive(&bars->x_empty[(u - 2) % SX]);
+#endif
         }
         ACC(2, t2);
         TICK(t3);
         tc_fence_after_sync();
-        const __half2 s2 = __half2half2(__low2half(sz)), z2 = __half2half2(__high2half(sz));
 #pragma unroll
         for (int hh = 0; hh < 2; ++hh) {
-          uint32_t o[32];
+#ifdef ZSE_W4_HOIST
+          if (hh == 1)
+#endif
+          {
 #pragma unroll
-          for (int p2 = 0; p2 < 2; ++p2) {
-            const uint4 w4 = pk[hh * 2 + p2];
-            dequant_word(w4.x, s2, z2, o + p2 * 16 + 0);
-            dequant_word(w4.y, s2, z2, o + p2 * 16 + 4);
-            dequant_word(w4.z, s2, z2, o + p2 * 16 + 8);
-            dequant_word(w4.w, s2, z2, o + p2 * 16 + 12);
+            for (int p2 = 0; p2 < 2; ++p2) {
+              const uint4 w4 = pk[hh * 2 + p2];
+              dequant_word(w4.x, s2, z2, o + p2 * 16 + 0);
+              dequant_word(w4.y, s2, z2, o + p2 * 16 + 4);
+              dequant_word(w4.z, s2, z2, o + p2 * 16 + 8);
+              dequant_word(w4.w, s2, z2, o + p2 * 16 + 12);
+            }
           }
           ZSE_TMEM_ST_X32(dst + hh * 32, o);
         }
@@ -345,6 +380,9 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4Args a) {
       acc_ok = mbar_wait(&bars->acc_ready, 0, abort_flag, a.status, 7, 0);
       tc_fence_after_sync();
       ACC(5, t5);
+#ifdef ZSE_W4_TIMING
+      tacc[7] = clock64() - t_start;
+#endif
     }
   } else
   if (warp == 0) {
@@ -661,6 +699,8 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4Args a) {
   if (a.timing != nullptr && threadIdx.x == 64 && blockIdx.x == 1 && blockIdx.z == 0) {
     a.timing[19 * 8 + 1] = clock64() - t_epi;
     a.timing[19 * 8 + 2] = n_units;
+    a.timing[19 * 8 + 3] = clock64() - t_start;
+    a.timing[19 * 8 + 4] = t_setup;
   }
 #endif
   tc_fence_before_sync();
@@ -860,6 +900,39 @@ extern "C" int zse_tp_gemm_w4_push(void* ctx, const void* w_tiled, const void* x
   const int rc = run_gemm_w4(w_tiled, x, x_rows_cap, nullptr, nullptr, M, N, K, N, kEpiPushF16, 0, status, stream, &pt,
                              &ctas);
   return rc != 0 ? rc : ctas;
+}
+
+// How many clusters of `cluster` CTAs of the 64-token kernel (narrow: two CTAs per SM, or wide) the device can hold at
+// once (cudaOccupancyMaxActiveClusters); -1 on error.  The planner's wave model and the tests use it.
+extern "C" int zse_gemm_w4_max_clusters(int narrow, int cluster) {
+  cudaLaunchConfig_t cfg = {};
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = cluster;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  cfg.gridDim = dim3(64, 1, cluster);
+  int n = -1;
+  if (narrow) {
+    using Cfg = W4Cfg<64, 1, true>;
+    auto kern = gemm_w4_kernel<64, 1, kEpiF16, true>;
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    if (cluster > 8) cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    cfg.blockDim = dim3(Cfg::kThreads);
+    cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) { cudaGetLastError(); return -1; }
+  } else {
+    using Cfg = W4Cfg<64, 1, false>;
+    auto kern = gemm_w4_kernel<64, 1, kEpiF16, false>;
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes);
+    if (cluster > 8) cudaFuncSetAttribute(kern, cudaFuncAttributeNonPortableClusterSizeAllowed, 1);
+    cfg.blockDim = dim3(Cfg::kThreads);
+    cfg.dynamicSmemBytes = Cfg::kSmemBytes;
+    if (cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess) { cudaGetLastError(); return -1; }
+  }
+  return n;
 }
 
 // What the launcher would do for these arguments: out4 = {weight tiles per wide CTA, K splits, cluster size along K,

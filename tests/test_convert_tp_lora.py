@@ -243,6 +243,57 @@ def test_lora_manager_slots_and_effect_on_outputs(tmp_path):
     eng.destroy()
 
 
+def test_prefix_cache_never_crosses_adapters(tmp_path):
+    """A prompt of several cache blocks, run with the base model and with two adapters at the same time and one after
+    the other: every request must produce what it produces alone (cached prefix blocks hold keys and values computed
+    with one set of weights and are only shared by requests that use the same weights)."""
+    from zse_b200.lora.weights import random_adapter_file
+    path = str(tmp_path / "m.zse")
+    synth.write_random_model(path, synth.shape_config("tiny"), seed=4)
+    cfg = EngineConfig(device="cpu", max_batch_seqs=4, max_seq_len=128, quiet=True)
+    rng = random.Random(7)
+    prompt = [rng.randrange(1024) for _ in range(45)]
+
+    def solo(lora_id, prefix_cache):
+        eng = ZStreamerEngine(path, config=EngineConfig(**{**cfg.__dict__, "enable_prefix_cache": prefix_cache}))
+        for name, seed in (("a", 1), ("b", 2)):
+            f = str(tmp_path / f"{name}.zse-lora")
+            random_adapter_file(f, eng.model_config, rank=4, alpha=8.0, seed=seed, std=0.2)
+            eng.lora_manager.load_adapter(name, f)
+        rid = eng.add_request_tokens(prompt, max_tokens=8, temperature=0.0, stop_tokens=[], lora_id=lora_id)
+        eng.run_until_done()
+        out = eng.get_result(rid).output_tokens
+        eng.destroy()
+        return out
+
+    want = {k: solo(k, False) for k in (None, "a", "b")}
+    assert want["a"] != want[None] or want["b"] != want[None]
+    eng = ZStreamerEngine(path, config=cfg)
+    for name in ("a", "b"):
+        eng.lora_manager.load_adapter(name, str(tmp_path / f"{name}.zse-lora"))
+    block = eng.cache_manager.block_size if hasattr(eng, "cache_manager") else 16
+    assert len(prompt) > 2 * block
+    # base first so that its blocks are registered, then the adapters while the base request is still live
+    r0 = eng.add_request_tokens(prompt, max_tokens=8, temperature=0.0, stop_tokens=[])
+    eng.step()
+    ra = eng.add_request_tokens(prompt, max_tokens=8, temperature=0.0, stop_tokens=[], lora_id="a")
+    rb = eng.add_request_tokens(prompt, max_tokens=8, temperature=0.0, stop_tokens=[], lora_id="b")
+    eng.run_until_done()
+    assert [eng.get_result(r).output_tokens for r in (r0, ra, rb)] == [want[None], want["a"], want["b"]]
+    # the same adapter again: it may (and does) reuse its own blocks, and still gives the same tokens
+    ra2 = eng.add_request_tokens(prompt, max_tokens=8, temperature=0.0, stop_tokens=[], lora_id="a")
+    r02 = eng.add_request_tokens(prompt, max_tokens=8, temperature=0.0, stop_tokens=[])
+    eng.run_until_done()
+    assert eng.get_result(ra2).output_tokens == want["a"] and eng.get_result(r02).output_tokens == want[None]
+    # a re-loaded adapter of the same name (other weights) must not see the old one's blocks
+    eng.lora_manager.unload_adapter("a")
+    eng.lora_manager.load_adapter("a", str(tmp_path / "b.zse-lora"))
+    ra3 = eng.add_request_tokens(prompt, max_tokens=8, temperature=0.0, stop_tokens=[], lora_id="a")
+    eng.run_until_done()
+    assert eng.get_result(ra3).output_tokens == want["b"]
+    eng.destroy()
+
+
 @pytest.mark.timeout(300)
 def test_collectives_facade(tmp_path):
     """all_reduce / all_gather / broadcast / reduce_scatter / barrier of the communication layer on three CPU ranks."""

@@ -79,6 +79,7 @@ class KVCacheManager:
         self._prompt_lengths: Dict[int, int] = {}
         self._prompt_tokens: Dict[int, Sequence[int]] = {}
         self._registered_upto: Dict[int, int] = {}
+        self._salts: Dict[int, int] = {}               # seq_id -> prefix-chain salt (sequences that run with an adapter)
         self._active: Set[int] = set()
 
     @staticmethod
@@ -91,8 +92,10 @@ class KVCacheManager:
 
     # ---- sequence life cycle --------------------------------------------------------------------------
     def allocate_sequence(self, seq_id: int, prompt_tokens: Optional[Sequence[int]] = None,
-                          num_tokens: Optional[int] = None) -> KVCacheHandle:
-        """Creates the sequence and reserves blocks for ``prompt_tokens`` (or ``num_tokens`` anonymous tokens)."""
+                          num_tokens: Optional[int] = None, salt: int = 0) -> KVCacheHandle:
+        """Creates the sequence and reserves blocks for ``prompt_tokens`` (or ``num_tokens`` anonymous tokens).
+        ``salt`` names the weights the sequence runs with (0: the base model; otherwise a value derived from the LoRA
+        adapter): cached prefix blocks are only shared between sequences of equal salt."""
         with self._lock:
             n = len(prompt_tokens) if prompt_tokens is not None else int(num_tokens or 0)
             if n > self._config.max_seq_len:
@@ -103,8 +106,8 @@ class KVCacheManager:
             shared: List[int] = []
             hashes: List[int] = []
             if self._dedup is not None and prompt_tokens is not None and n > bs:
-                hashes = self._dedup.chain_hashes(prompt_tokens)
-                prev = 0
+                hashes = self._dedup.chain_hashes(prompt_tokens, salt)
+                prev = salt
                 for i, h in enumerate(hashes):
                     if (i + 1) * bs >= n:          # keep at least one token to compute
                         break
@@ -132,6 +135,8 @@ class KVCacheManager:
             if prompt_tokens is not None:
                 self._prompt_tokens[seq_id] = prompt_tokens
             self._registered_upto[seq_id] = len(shared)
+            if salt:
+                self._salts[seq_id] = salt
             return KVCacheHandle(seq_id, e.num_tokens, len(e.blocks), len(shared) * bs)
 
     def commit_tokens(self, seq_id: int, num_computed: int) -> None:
@@ -149,11 +154,12 @@ class KVCacheManager:
             start = self._registered_upto.get(seq_id, 0)
             if upto <= start:
                 return
-            hashes = self._dedup.chain_hashes(toks[: upto * bs])
+            salt = self._salts.get(seq_id, 0)
+            hashes = self._dedup.chain_hashes(toks[: upto * bs], salt)
             for i in range(start, upto):
                 if i not in e.evicted_indices:
                     self._dedup.register(e.blocks[i].block_id, hashes[i], toks[i * bs:(i + 1) * bs],
-                                         hashes[i - 1] if i else 0)
+                                         hashes[i - 1] if i else salt)
             self._registered_upto[seq_id] = upto
 
     def extend_sequence(self, seq_id: int, num_new_tokens: int = 1) -> None:
@@ -220,7 +226,7 @@ class KVCacheManager:
                     self._dedup.deregister_block(b.block_id)
             self._evictor.remove_sequence(seq_id)
             self._page_table.remove_sequence(seq_id)
-            for d in (self._prompt_lengths, self._prompt_tokens, self._registered_upto):
+            for d in (self._prompt_lengths, self._prompt_tokens, self._registered_upto, self._salts):
                 d.pop(seq_id, None)
             self._active.discard(seq_id)
 

@@ -37,9 +37,11 @@ class BlockDedup:
         self._hash_of_block: Dict[int, int] = {}
         self._hits = self._misses = self._collisions = 0
 
-    def chain_hashes(self, tokens: Sequence[int]) -> List[int]:
+    def chain_hashes(self, tokens: Sequence[int], salt: int = 0) -> List[int]:
+        """Chain hash of every full block.  ``salt`` starts the chain: sequences whose keys and values are computed
+        with different weights (another LoRA adapter, or none) pass different salts and never share a block."""
         bs = self._pool.block_size_tokens
-        out, h = [], 0
+        out, h = [], salt & _MASK
         for i in range(len(tokens) // bs):
             h = fnv1a_chain(h, tokens[i * bs:(i + 1) * bs])
             out.append(h)

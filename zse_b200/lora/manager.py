@@ -116,6 +116,7 @@ class LoRAManager:
             self._scales[slot] = ad.scaling
             self._store.add(ad)
             self._loads += 1
+            ad.generation = self._loads            # tells a re-loaded adapter from the one that had this name before
             self._model.lora = self
             return ad
 
@@ -211,6 +212,18 @@ class LoRAManager:
     def slot_of(self, adapter_id: Optional[str]) -> int:
         ad = self._store.get(adapter_id) if adapter_id else None
         return -1 if ad is None else ad.slot
+
+    def cache_salt(self, adapter_id: Optional[str]) -> int:
+        """Non-zero value that names the loaded adapter in the prefix cache (0: base model).  Keys and values written
+        under one adapter must never be reused by a sequence that runs with another one or with none; the load
+        counter keeps blocks of an unloaded adapter from matching a later adapter of the same name.  The value is
+        the same in every tensor-parallel worker (no per-process hash)."""
+        ad = self._store.get(adapter_id) if adapter_id else None
+        if ad is None:
+            return 0
+        import zlib
+        return ((zlib.crc32(adapter_id.encode("utf-8")) << 24) ^ (int(getattr(ad, "generation", 0)) << 1) | 1) \
+            & 0xFFFFFFFFFFFFFFFF
 
     def list_adapters(self) -> List[dict]:
         return [{"adapter_id": i, "rank": a.rank, "alpha": a.alpha, "target_modules": a.target_modules,

@@ -70,6 +70,7 @@ class LoRAAdapter:
     slot: int = -1           # index in the batched weight tables (-1 = not resident)
     base_model: str = ""     # free-form metadata, as in the reference's record
     description: str = ""
+    generation: int = 0      # load counter of the manager when this adapter became resident
 
     @property
     def scaling(self) -> float:

@@ -33,6 +33,15 @@ _SIGS = {
     "zse_gemm_w4": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                             c_void_p, c_void_p]),
     "zse_gemm_w4_splits": (c_int, [c_int, c_int, c_int, c_int]),
+    "zse_gemm_w4_dec": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                c_void_p, c_void_p, c_void_p]),
+    "zse_gemm_w4_dec_qkv_rope": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                         c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                         c_void_p, c_void_p]),
+    "zse_gemm_w4_dec_workspace_bytes": (c_int64, [c_int]),
+    "zse_gemm_w4_dec_supported": (c_int, [c_int, c_int, c_int, c_int]),
+    "zse_gemm_w4_dec_plan": (None, [c_int, c_int, c_int, c_int, POINTER(c_int)]),
+    "zse_gemm_w4_dec_set_tuning": (None, [c_int, c_int]),
     "zse_gemm_f16": (c_int, [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                              c_int, c_void_p, c_void_p]),
     "zse_gemm_f16_splits": (c_int, [c_int, c_int, c_int, c_int]),
@@ -179,6 +188,35 @@ class Status:
 def gemm_w4(w_tiled, x, x_rows_cap, bias, out, M, N, K, ldo, epilogue, k_split, status):
     _ck(load().zse_gemm_w4(_p(w_tiled), _p(x), x_rows_cap, _p(bias), _p(out), M, N, K, ldo, epilogue, k_split,
                            status, _stream()), "gemm_w4")
+
+
+def gemm_w4_dec(w_tiled, x, x_rows_cap, bias, out, M, N, K, ldo, epilogue, workspace, status):
+    """Decode-sized INT4 GEMM (M <= 64) of the persistent kernel; epilogue 0 fp16 (+bias), 1 SwiGLU, 2 fp32."""
+    _ck(load().zse_gemm_w4_dec(_p(w_tiled), _p(x), x_rows_cap, _p(bias), _p(out), M, N, K, ldo, epilogue,
+                               _p(workspace), status, _stream()), "gemm_w4_dec")
+
+
+def gemm_w4_dec_qkv_rope(w_tiled, x, x_rows_cap, bias, qkv_out, ldo, M, K, nh, nkv, kv_layer, block_size, positions,
+                         slots, cos_sin, max_position, workspace, status):
+    _ck(load().zse_gemm_w4_dec_qkv_rope(_p(w_tiled), _p(x), x_rows_cap, _p(bias), _p(qkv_out), ldo, M, K, nh, nkv,
+                                        _p(kv_layer), block_size, _p(positions), _p(slots), _p(cos_sin), max_position,
+                                        _p(workspace), status, _stream()), "gemm_w4_dec_qkv_rope")
+
+
+def gemm_w4_dec_workspace(device, sm_count: int) -> torch.Tensor:
+    """Zeroed workspace (partial sums + synchronisation words) for the persistent decode GEMM on ``device``."""
+    n = int(load().zse_gemm_w4_dec_workspace_bytes(sm_count))
+    return torch.zeros((n + 15) // 16 * 16, dtype=torch.uint8, device=device)
+
+
+def gemm_w4_dec_supported(M, N, K, epilogue) -> bool:
+    return bool(load().zse_gemm_w4_dec_supported(M, N, K, epilogue))
+
+
+def gemm_w4_dec_plan(N, K, epilogue, sm_count):
+    out = (c_int * 2)()
+    load().zse_gemm_w4_dec_plan(N, K, epilogue, sm_count, out)
+    return out[0], out[1]
 
 
 def gemm_f16(w, w_rows, x, x_rows_cap, bias, out, M, N, K, ldo, epilogue, k_split, status):

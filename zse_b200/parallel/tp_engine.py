@@ -76,6 +76,10 @@ def _worker(rank: int, world: int, model_path: str, cfg: EngineConfig, port: int
                 info["device_name"], info["device_vram_gb"] = "cpu", 0.0
             ready.put(("ready", info))
         fail_at = None
+        # time-based decisions (time-outs, deadline order) use rank 0's clock of this iteration on every rank
+        from ..sched import request as _request
+        tick = [time.monotonic()]
+        _request.set_decision_clock(lambda: tick[0])
         while True:
             beats[rank] += 1
             if rank == 0:
@@ -86,10 +90,11 @@ def _worker(rank: int, world: int, model_path: str, cfg: EngineConfig, port: int
                         cmds.append(cmd_q.get_nowait())
                 except queue.Empty:
                     pass
-                box = [cmds]
+                box = [cmds, time.monotonic()]
             else:
-                box = [None]
+                box = [None, 0.0]
             dist.broadcast_object_list(box, src=0, group=ctrl)
+            tick[0] = box[1]
             stop = False
             for c in box[0]:
                 if c[0] == CMD_ADD:

@@ -7,6 +7,8 @@ the device; speculative decoding is wired in (the reference builds ``BatchRunner
 """
 from __future__ import annotations
 
+import zlib
+
 import threading
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional
@@ -38,7 +40,9 @@ def _sampling_row(r: InferenceRequest, ahead: int = 0) -> SamplingRow:
     p = r.params
     if p.greedy:
         return SamplingRow()
-    base = p.seed if p.seed is not None else (hash(r.request_id) & 0x7FFFFFFF)
+    # an unseeded request draws from a stream named by its id: crc32, not hash(), because str hashes differ between the
+    # worker processes of a tensor-parallel group and every rank must sample the same token
+    base = p.seed if p.seed is not None else (zlib.crc32(str(r.request_id).encode("utf-8")) & 0x7FFFFFFF)
     # one random stream per request, indexed by the token's position in the output: a seeded request gives the same
     # tokens whatever else is in the batch, and a replayed CUDA graph (whose scalar arguments are frozen) still draws
     # fresh numbers because the per-row seed is staged from the host every step
@@ -97,6 +101,12 @@ class BatchRunner:
         return res
 
     # ---- helpers ----------------------------------------------------------------------------------------
+    def _cache_salt(self, r: InferenceRequest) -> int:
+        """Prefix-cache salt of a request: 0 for the base model, the adapter's value otherwise."""
+        if self._lora is None or r.lora_id is None:
+            return 0
+        return self._lora.cache_salt(r.lora_id)
+
     def _adapter_slot(self, r: InferenceRequest) -> int:
         if self._lora is None or r.lora_id is None:
             return -1
@@ -144,7 +154,7 @@ class BatchRunner:
             try:
                 toks = r.prefill_tokens
                 if not self._cache.has_sequence(r.seq_id):
-                    h = self._cache.allocate_sequence(r.seq_id, toks)
+                    h = self._cache.allocate_sequence(r.seq_id, toks, salt=self._cache_salt(r))
                     self._cache.mark_active(r.seq_id)
                     if h.num_cached_tokens and r.prefill_offset == 0:
                         r.prefill_offset = h.num_cached_tokens        # prefix already in the cache

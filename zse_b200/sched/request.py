@@ -12,6 +12,22 @@ from enum import Enum, auto
 from typing import Callable, Dict, List, Optional
 
 
+# Clock of every time-based DECISION (time-out, TTFT-deadline urgency, arrival order).  One process: the monotonic clock.
+# Tensor-parallel workers install a clock that returns the value rank 0 broadcast for the current loop iteration, so
+# all ranks finish a timed-out request in the same step and order their queues alike (each rank deciding on its own
+# clock would split the group: different batch shapes, mismatched collectives).  Reported metrics keep the real clock.
+_decision_clock: Optional[Callable[[], float]] = None
+
+
+def set_decision_clock(fn: Optional[Callable[[], float]]) -> None:
+    global _decision_clock
+    _decision_clock = fn
+
+
+def decision_now() -> float:
+    return _decision_clock() if _decision_clock is not None else time.monotonic()
+
+
 class RequestState(Enum):
     WAITING = auto()
     PREFILLING = auto()
@@ -58,7 +74,7 @@ class InferenceRequest:
     finish_reason: Optional[FinishReason] = None
     prefill_offset: int = 0          # prompt (or re-prefill) tokens whose KV is in the cache
     chunk_size: int = 0
-    arrival_time: float = field(default_factory=time.monotonic)
+    arrival_time: float = field(default_factory=decision_now)
     first_token_time: Optional[float] = None
     finish_time: Optional[float] = None
     seq_id: Optional[int] = None
@@ -113,11 +129,11 @@ class InferenceRequest:
     def urgency(self) -> float:
         if self.deadline_ms is None:
             return float("inf")
-        return self.deadline_ms - (time.monotonic() - self.arrival_time) * 1000.0
+        return self.deadline_ms - (decision_now() - self.arrival_time) * 1000.0
 
     @property
     def wait_time_ms(self) -> float:
-        return (time.monotonic() - self.arrival_time) * 1000.0
+        return (decision_now() - self.arrival_time) * 1000.0
 
     def mark_prefilling(self) -> None:
         self.state = RequestState.PREFILLING
