@@ -44,8 +44,8 @@ namespace zse {
 
 constexpr int kDecWarps = 24;
 constexpr int kDecThreads = kDecWarps * 32;
-constexpr int kDecSX = 5;            // activation stages
-constexpr int kDecSW = 6;            // weight chunks per pipeline ring
+constexpr int kDecSX = 6;            // activation stages
+constexpr int kDecSW = 5;            // weight chunks per pipeline ring
 constexpr int kDecEpiWarp0 = 20;
 constexpr int kDecStageBytes = 64 * 128 * 4;     // finished sums of one tile: [token column][128 rows] fp32
 
@@ -56,6 +56,7 @@ struct DecBars {
   uint64_t x_full[kDecSX], x_empty[kDecSX];
   uint64_t a_ready[2][2], slot_free[2][2];
   uint64_t acc_full[2][2], acc_empty[2][2];
+  uint64_t bdesc[kDecSX][8];     // activation descriptors of every (stage, K step): the MMA issuers only load them
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -71,6 +72,8 @@ struct DecCfg {
   static constexpr int kSmemBytes = kBarsOff + 1024 + 1024;   // barriers + alignment slack
   static constexpr int kGranules = NT / 8;                    // 8-column granules of the token dimension
   static_assert(kSmemBytes <= 232448, "shared memory budget");
+  // split plan: the receive area [S][2][ceil(G/S)][8][128] fp32 lies over both rings (S * ceil(G/S) <= G + S - 1)
+  static_assert((kGranules + 7) * 2 * 8 * 128 * 4 <= kStageOff, "receive area of the split plan");
 };
 
 struct DecRope {
@@ -92,6 +95,7 @@ struct DecArgs {
   float* ws;                   // workspace: [grid][2][NT][128] fp32 partial sums
   uint32_t* sync;              // [0] launch epoch, [1] exit ticket, [8 + cta] partial-ready flags
   Status* status;
+  long long* timing;           // debug builds (ZSE_DEC_TIMING): per-role cycle counters of one CTA, else unused
   DecRope rope;
 };
 
@@ -148,6 +152,14 @@ __device__ __forceinline__ void dec_dequant_half(const uint4& w0, const uint4& w
   dec_dequant_word(w1.w, s2, z2, o + 28);
 }
 
+#ifdef ZSE_DEC_TIMING
+#define DTICK(var) long long var = clock64()
+#define DACC(slot, t0) tacc[slot] += clock64() - (t0)
+#else
+#define DTICK(var)
+#define DACC(slot, t0)
+#endif
+
 // Bounded wait until a flag word in global memory holds `want`.
 __device__ __forceinline__ bool dec_wait_flag(const uint32_t* flag, uint32_t want, volatile int* abort_flag, Status* st,
                                               unsigned where, unsigned detail) {
@@ -168,19 +180,6 @@ __device__ __forceinline__ bool dec_wait_flag(const uint32_t* flag, uint32_t wan
   return true;
 }
 
-__device__ __forceinline__ void epi_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
-// Barrier of the 128 epilogue threads that also ANDs a predicate: after a bounded wait all of them take the same
-// branch, so nobody is left alone at a later barrier.
-__device__ __forceinline__ bool epi_all(bool v) {
-  uint32_t r;
-  asm volatile(
-      "{\n\t.reg .pred p, q;\n\tsetp.ne.u32 p, %1, 0;\n\tbar.red.and.pred q, 1, 128, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
-      : "=r"(r)
-      : "r"(uint32_t(v))
-      : "memory");
-  return r != 0;
-}
-
 // First step of CTA c.  stream plan: balanced cut of the linear step space; split plan: segment (c % S) of pair c / S.
 __device__ __forceinline__ int dec_range_begin(const DecArgs& a, int c, int n_cta) {
   if (a.split > 0) {
@@ -189,6 +188,351 @@ __device__ __forceinline__ int dec_range_begin(const DecArgs& a, int c, int n_ct
     return pair * a.k_stages + int((long long)seg * a.k_stages / a.split);
   }
   return int((long long)c * a.total_steps / n_cta);
+}
+
+// Eight tcgen05.mma of one 128 x 128 chunk, back to back.  The issuing thread shares its scheduler with five busy
+// warps and gets an issue slot only every ten to thirty cycles, so what counts is the number of instructions it
+// executes per chunk: the eight activation descriptors of a stage come out of a table in shared memory (four 16-byte
+// loads), the eight TMEM operand addresses are loop-invariant registers, the predicate is set twice.
+__device__ __forceinline__ void dec_mma_chunk(uint32_t dt, const uint32_t (&at)[8], const uint64_t* bdesc_stage,
+                                              uint32_t idesc, uint32_t accumulate_first) {
+  const ulonglong2* tab = reinterpret_cast<const ulonglong2*>(bdesc_stage);
+  const ulonglong2 d01 = tab[0], d23 = tab[1], d45 = tab[2], d67 = tab[3];
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p, t;\n\t"
+      "setp.ne.b32 p, %17, 0;\n\t"
+      "setp.eq.b32 t, %18, %18;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %9, %18, p;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%2], %10, %18, t;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%3], %11, %18, t;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%4], %12, %18, t;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%5], %13, %18, t;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%6], %14, %18, t;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%7], %15, %18, t;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%8], %16, %18, t;\n\t"
+      "}" ::"r"(dt),
+      "r"(at[0]), "r"(at[1]), "r"(at[2]), "r"(at[3]), "r"(at[4]), "r"(at[5]), "r"(at[6]), "r"(at[7]), "l"(d01.x),
+      "l"(d01.y), "l"(d23.x), "l"(d23.y), "l"(d45.x), "l"(d45.y), "l"(d67.x), "l"(d67.y), "r"(accumulate_first),
+      "r"(idesc)
+      : "memory");
+}
+
+// Barriers of the threads that run an epilogue together: 128 (the four epilogue warps) or 640 (with the sixteen dequant
+// warps, for the last tile pair of a CTA, when those have nothing else left to do).
+__device__ __forceinline__ void epi_bar(int wide) {
+  if (wide)
+    asm volatile("bar.sync 2, 640;" ::: "memory");
+  else
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+}
+// Barrier that also ANDs a predicate: after a bounded wait all threads take the same branch, so nobody is left alone
+// at a later barrier.
+__device__ __forceinline__ bool epi_all(bool v, int wide) {
+  uint32_t r;
+  if (wide)
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\tsetp.ne.u32 p, %1, 0;\n\tbar.red.and.pred q, 2, 640, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
+        : "=r"(r)
+        : "r"(uint32_t(v))
+        : "memory");
+  else
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\tsetp.ne.u32 p, %1, 0;\n\tbar.red.and.pred q, 1, 128, p;\n\tselp.u32 %0, 1, 0, q;\n\t}"
+        : "=r"(r)
+        : "r"(uint32_t(v))
+        : "memory");
+  return r != 0;
+}
+
+// ---- epilogue ---------------------------------------------------------------------------------------------------
+// Finished sums reach the stores through a `fetch`: four consecutive rows of one token column of a tile.
+//   StageFetch  - the sums are in this CTA's shared memory (stream plan);
+//   RecvFetch   - split plan: the S partial sums of a column granule were pushed into the shared memory of the CTA
+//                 that finishes it; the fetch adds them in rank order.
+struct StageFetch {
+  const float* stage;                                 // [col][128]
+  __device__ __forceinline__ float4 get4(int col, int row) const {
+    return *reinterpret_cast<const float4*>(stage + col * 128 + row);
+  }
+};
+struct RecvFetch {
+  const float* recv;                                  // [S sources][2 tiles][go_max][8 cols][128] of this CTA
+  int S, r, j, go_max;                                // tile of the pair, index of the owned granule
+  __device__ __forceinline__ float4 get4(int col, int row) const {
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {                     // rank order: the sum is reproducible
+      if (c < S) {
+        const float4 t =
+            *reinterpret_cast<const float4*>(recv + ((((c * 2 + r) * go_max + j) * 8 + (col & 7)) * 128 + row));
+        v.x += t.x;
+        v.y += t.y;
+        v.z += t.z;
+        v.w += t.w;
+      }
+    }
+    return v;
+  }
+};
+
+__device__ __forceinline__ void cluster_sync_all_threads() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t dec_cluster_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+
+// One work item of the stores: token column `col` of tile `tile`, position e7 (0..127) inside the granule's 8 x 16
+// grid -> 16 bytes of output (8 bytes for SwiGLU).  `add_bias`: the fetch delivers sums without the bias.
+template <int NT, int EPI, typename Fetch>
+__device__ __forceinline__ void dec_store_item(const DecArgs& a, const Fetch& f, int tile, int col, int e7,
+                                               bool add_bias) {
+  const int t = col;
+  if (t >= a.M) return;
+  if (EPI == kDecF16 || EPI == kDecF32) {
+    const int r0 = (e7 & 15) * 8, n = tile * kTileN + r0;
+    if (n >= a.N) return;
+    float4 lo = f.get4(col, r0), hi = f.get4(col, r0 + 4);
+    if (add_bias && a.bias != nullptr) {
+      const uint4 bw = *reinterpret_cast<const uint4*>(a.bias + n);
+      const __half2* bh = reinterpret_cast<const __half2*>(&bw);
+      const float2 b0 = __half22float2(bh[0]), b1 = __half22float2(bh[1]), b2 = __half22float2(bh[2]),
+                   b3 = __half22float2(bh[3]);
+      lo.x += b0.x; lo.y += b0.y; lo.z += b1.x; lo.w += b1.y;
+      hi.x += b2.x; hi.y += b2.y; hi.z += b3.x; hi.w += b3.y;
+    }
+    if (EPI == kDecF16) {
+      uint4 pk;
+      pk.x = pack_half2(clamp_f16(lo.x), clamp_f16(lo.y));
+      pk.y = pack_half2(clamp_f16(lo.z), clamp_f16(lo.w));
+      pk.z = pack_half2(clamp_f16(hi.x), clamp_f16(hi.y));
+      pk.w = pack_half2(clamp_f16(hi.z), clamp_f16(hi.w));
+      *reinterpret_cast<uint4*>(reinterpret_cast<__half*>(a.out) + size_t(t) * a.ldo + n) = pk;
+    } else {
+      float* o = reinterpret_cast<float*>(a.out) + size_t(t) * a.ldo + n;
+      *reinterpret_cast<float4*>(o) = lo;
+      *reinterpret_cast<float4*>(o + 4) = hi;
+    }
+  } else if (EPI == kDecSwiGLU) {
+    // tile rows 0..63 = gate, 64..127 = up of the same 64 outputs: four outputs per work item
+    const int o0 = (e7 & 15) * 4, n = tile * 64 + o0;
+    if (n >= a.N / 2) return;
+    const float4 gt = f.get4(col, o0), up = f.get4(col, 64 + o0);
+    uint2 pk;
+    pk.x = pack_half2(clamp_f16(silu_f(gt.x) * up.x), clamp_f16(silu_f(gt.y) * up.y));
+    pk.y = pack_half2(clamp_f16(silu_f(gt.z) * up.z), clamp_f16(silu_f(gt.w) * up.w));
+    *reinterpret_cast<uint2*>(reinterpret_cast<__half*>(a.out) + size_t(t) * a.ldo + n) = pk;
+  } else if (EPI == kDecQkvRope) {
+    // tile = one head of 128 dims: q heads, then k heads, then v heads; eight dims per work item
+    const DecRope& rp = a.rope;
+    const int d0 = (e7 & 15) * 8, dl = d0 & 63;
+    float val[8];
+    if (tile < rp.nh + rp.nkv) {
+      float xa[8], xb[8];                           // dims dl.. of the first half, of the second half
+      *reinterpret_cast<float4*>(xa) = f.get4(col, dl);
+      *reinterpret_cast<float4*>(xa + 4) = f.get4(col, dl + 4);
+      *reinterpret_cast<float4*>(xb) = f.get4(col, 64 + dl);
+      *reinterpret_cast<float4*>(xb + 4) = f.get4(col, 64 + dl + 4);
+      if (add_bias && a.bias != nullptr) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          xa[i] += __half2float(a.bias[tile * 128 + dl + i]);
+          xb[i] += __half2float(a.bias[tile * 128 + 64 + dl + i]);
+        }
+      }
+      const int pos = min(max(rp.positions[t], 0), rp.max_position - 1);
+      const float2* cs = rp.cos_sin + size_t(pos) * 64 + dl;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        const float2 c2 = cs[i];
+        val[i] = d0 < 64 ? xa[i] * c2.x - xb[i] * c2.y : xb[i] * c2.x + xa[i] * c2.y;
+      }
+    } else {
+      *reinterpret_cast<float4*>(val) = f.get4(col, d0);
+      *reinterpret_cast<float4*>(val + 4) = f.get4(col, d0 + 4);
+      if (add_bias && a.bias != nullptr) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) val[i] += __half2float(a.bias[tile * 128 + d0 + i]);
+      }
+    }
+    uint4 pk;
+    pk.x = pack_half2(clamp_f16(val[0]), clamp_f16(val[1]));
+    pk.y = pack_half2(clamp_f16(val[2]), clamp_f16(val[3]));
+    pk.z = pack_half2(clamp_f16(val[4]), clamp_f16(val[5]));
+    pk.w = pack_half2(clamp_f16(val[6]), clamp_f16(val[7]));
+    if (tile < rp.nh) {                           // q: what attention reads
+      *reinterpret_cast<uint4*>(reinterpret_cast<__half*>(a.out) + size_t(t) * a.ldo + tile * 128 + d0) = pk;
+    } else if (tile < rp.nh + 2 * rp.nkv) {
+      const long long slot = rp.slots[t];
+      if (slot >= 0) {
+        const bool is_v = tile >= rp.nh + rp.nkv;
+        const int kvh = tile - rp.nh - (is_v ? rp.nkv : 0);
+        const long long blk = slot / rp.block_size, off = slot % rp.block_size;
+        __half* dstp = rp.kv_layer + (((blk * 2 + (is_v ? 1 : 0)) * rp.nkv + kvh) * rp.block_size + off) * 128;
+        *reinterpret_cast<uint4*>(dstp + d0) = pk;
+      }
+    }
+  }
+}
+
+// Stream plan: one tile pair of one CTA, from finished MMAs to memory.  Run by W warps per TMEM lane quarter (W = 1:
+// the epilogue warps alone, while the pipelines work on the next pair; W = 5: all twenty worker warps, for the CTA's
+// last pair); `wi` is this warp's index among them.  stage0 / stage1: where the finished sums of the two tiles are
+// staged (the same buffer for W = 1: the tiles then go one after the other).
+template <int NT, int EPI>
+__device__ __forceinline__ bool dec_epilogue_item(const DecArgs& a, DecBars* bars, float* stage0, float* stage1,
+                                                  uint32_t tmem, int cta, int n_cta, int pair, int ka, int len,
+                                                  int ntp, int b, int item, uint32_t epoch1, int q, int lane, int wi,
+                                                  int W, bool alive_in, long long* tacc) {
+  using Cfg = DecCfg<NT>;
+  constexpr int G = Cfg::kGranules;
+  const int ks = a.k_stages;
+  const int wide = W > 1;
+  const int row = q * 32 + lane, et = wi * 128 + row;
+  const uint32_t lane_addr = uint32_t(q * 32) << 16;
+  volatile int* abort_flag = &bars->abort_flag;
+  uint32_t* flags = a.sync + 8;
+  // the CTA that holds K stage 0 of the pair finishes it; src0 .. src0 + n_src - 1 are the CTAs whose partial sums
+  // it needs
+  const bool owner = ka == 0;
+  int src0 = cta + 1, n_src = 0;
+  if (owner && len < ks)
+    while (src0 + n_src < n_cta && dec_range_begin(a, src0 + n_src, n_cta) < (pair + 1) * ks) ++n_src;
+  DTICK(e0);
+  // every thread of the group comes through the vote below whatever happened before, so a failed wait anywhere ends
+  // the epilogue for all of them together
+  bool alive = alive_in && !*abort_flag;
+  for (int r = 0; r < ntp && alive; ++r)
+    alive = mbar_wait(&bars->acc_full[r][b], (item >> 1) & 1, abort_flag, a.status, 9, item);
+  if (owner && alive && lane == 0)
+    for (int j = wi; j < n_src && alive; j += W)
+      alive = dec_wait_flag(flags + src0 + j, epoch1, abort_flag, a.status, 10, src0 + j);
+  alive = epi_all(alive, wide);
+  if (!alive) return false;
+  DACC(0, e0);
+  DTICK(e1);
+  tc_fence_after_sync();
+  if (!owner) {
+    // ---- partial sums go to the workspace (units = granules of both tiles, dealt to the warps); the barrier orders
+    // every thread's stores before the one release that publishes them
+#pragma unroll 1
+    for (int u = wi; u < ntp * G; u += W) {
+      const int r = u / G, gr = u - r * G;
+      uint32_t v[8];
+      ZSE_TMEM_LD_X8(v, tmem + lane_addr + (2 * r + b) * 64 + gr * 8);
+      tc_wait_ld();
+      float* dstw = a.ws + ((size_t(cta) * 2 + r) * NT + gr * 8) * 128 + row;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) __stcg(dstw + i * 128, __uint_as_float(v[i]));
+    }
+    epi_bar(wide);
+    if (et == 0) {
+      __threadfence();
+      st_release_gpu_u32(flags + cta, epoch1);
+    }
+    DACC(1, e1);
+    return true;
+  }
+  const bool two_stages = stage0 != stage1;
+  for (int r0 = 0; r0 < ntp; r0 += (two_stages ? 2 : 1)) {
+    const int r1 = two_stages ? ntp : r0 + 1;
+    DTICK(e3);
+    // ---- phase 1: finished sums -> stage[col][row]
+    for (int r = r0; r < r1; ++r) {
+      float* stage = r == 0 ? stage0 : stage1;
+      float bias = 0.f;
+      const int tile = 2 * pair + r;
+      if ((EPI == kDecF16 || EPI == kDecQkvRope) && a.bias != nullptr && tile * kTileN + row < a.N)
+        bias = __half2float(a.bias[tile * kTileN + row]);
+#pragma unroll 1
+      for (int gr = wi; gr < G; gr += W) {
+        uint32_t raw[8];
+        ZSE_TMEM_LD_X8(raw, tmem + lane_addr + (2 * r + b) * 64 + gr * 8);
+        // partial sums of the other CTAs (at most a few): their loads are in flight together with the TMEM load
+        float t8[4][8];
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) {
+          const bool use = jj < n_src;
+          const float* srcw = a.ws + ((size_t(use ? src0 + jj : cta) * 2 + r) * NT + gr * 8) * 128 + row;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) t8[jj][i] = use ? __ldcg(srcw + i * 128) : 0.f;
+        }
+        tc_wait_ld();
+        float v[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(raw[i]) + bias;
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj)
+#pragma unroll
+          for (int i = 0; i < 8; ++i) v[i] += t8[jj][i];
+        for (int j = 4; j < n_src; ++j) {                       // rare: a pair cut into more than five pieces
+          const float* srcw = a.ws + ((size_t(src0 + j) * 2 + r) * NT + gr * 8) * 128 + row;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) v[i] += __ldcg(srcw + i * 128);
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) stage[(gr * 8 + i) * 128 + row] = v[i];
+      }
+    }
+    epi_bar(wide);
+    DACC(3, e3);
+    DTICK(e4);
+    // ---- phase 2: 16-byte stores; work item -> (tile, granule, column of the granule, 8 rows)
+#pragma unroll 1
+    for (int idx = et; idx < (r1 - r0) * G * 128; idx += 128 * W) {
+      const int r = r0 + idx / (G * 128), rem = idx % (G * 128);
+      StageFetch f{r == 0 ? stage0 : stage1};
+      dec_store_item<NT, EPI>(a, f, 2 * pair + r, (rem >> 7) * 8 + ((rem & 127) >> 4), rem & 127, false);
+    }
+    if (r1 < ntp) epi_bar(wide);                      // the stage is reused by the second tile
+    DACC(4, e4);
+  }
+  return true;
+}
+
+// Split plan: the S CTAs that share a tile pair form a thread-block cluster; segment `seg` finishes the column
+// granules g with g mod S == seg.  Once every CTA of the cluster is through its MMAs (first cluster barrier: all
+// rings are idle), each one sends its fp32 partial sums of every granule to the shared memory of the CTA that
+// finishes it - plain remote stores, nothing waits for a round trip - into slot [source rank]; after the second
+// cluster barrier the owner adds the S slots in rank order.  Remote loads are avoided on purpose: measured here, a
+// thread's loads from another SM's shared memory complete one after the other at ~800 cycles each.
+template <int NT>
+__device__ __forceinline__ void dec_split_push(float* recv, uint32_t tmem, int ntp, int seg, int S, int go_max, int q,
+                                               int lane, int wi) {
+  constexpr int G = DecCfg<NT>::kGranules;
+  const int row = q * 32 + lane;
+  const uint32_t lane_addr = uint32_t(q * 32) << 16;
+#pragma unroll 1
+  for (int u = wi; u < ntp * G; u += 5) {
+    const int r = u / G, gr = u - r * G;
+    const int owner = gr % S, j = gr / S;
+    uint32_t v[8];
+    ZSE_TMEM_LD_X8(v, tmem + lane_addr + (2 * r) * 64 + gr * 8);
+    tc_wait_ld();
+    const uint32_t local = smem_u32(recv + ((((seg * 2 + r) * go_max + j) * 8) * 128 + row));
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(owner));
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      asm volatile("st.shared::cluster.b32 [%0], %1;" ::"r"(remote + i * 512), "r"(v[i]) : "memory");
+  }
+}
+
+template <int NT, int EPI>
+__device__ __forceinline__ void dec_split_finish(const DecArgs& a, const float* recv, int pair, int ntp, int seg, int S,
+                                                 int go_max, int et) {
+  constexpr int G = DecCfg<NT>::kGranules;
+  const int Go = seg < G ? (G - seg + S - 1) / S : 0;               // granules per tile this CTA finishes
+#pragma unroll 1
+  for (int idx = et; idx < ntp * Go * 128; idx += 640) {
+    const int r = idx / (Go * 128), rem = idx - r * (Go * 128);
+    const int j = rem >> 7, gr = seg + j * S;
+    RecvFetch f{recv, S, r, j, go_max};
+    dec_store_item<NT, EPI>(a, f, 2 * pair + r, gr * 8 + ((rem & 127) >> 4), rem & 127, true);
+  }
 }
 
 template <int NT, int EPI>
@@ -204,6 +548,12 @@ gemm_w4_dec_kernel(const __grid_constant__ CUtensorMap tmap_x, const DecArgs a) 
   DecBars* bars = reinterpret_cast<DecBars*>(smem + Cfg::kBarsOff);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+#ifdef ZSE_DEC_TIMING
+  long long tacc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  const long long t_entry = clock64();
+#else
+  long long* tacc = nullptr;
+#endif
   // The next kernel of the stream may start its own set-up now; this kernel in turn starts before the one ahead of it
   // has finished: set-up, the weight stream and the dequantisation (constant data) run at once, the activation
   // producer and the epilogue wait for the producer of the activations (pdl_wait below).
@@ -213,10 +563,14 @@ gemm_w4_dec_kernel(const __grid_constant__ CUtensorMap tmap_x, const DecArgs a) 
   const int g0 = dec_range_begin(a, cta, n_cta);
   const int g1 = dec_range_begin(a, cta + 1, n_cta);
   const int n_steps = g1 - g0;
+  const int pair0 = g0 / ks, k_first = g0 - pair0 * ks;
   // the last pair of an odd tile count has one tile: pipeline 1 has nothing to do from `single_from` on
   const int single_from = (a.n_tiles & 1) ? (a.n_pairs - 1) * ks : a.total_steps;
   const int n_real1 = max(0, min(g1, single_from) - g0);        // steps of this CTA in which pipeline 1 has a chunk
+  // first step of the CTA's last tile pair (the pair whose epilogue all worker warps share)
+  const int last_begin = max(0, ((g1 - 1) / ks) * ks - g0);
 
+  int w_issued0 = 0, w_issued1 = 0;                             // weight producer: chunks issued before the barrier
   if (threadIdx.x == 0) {
     for (int p = 0; p < 2; ++p) {
       for (int i = 0; i < SW; ++i) {
@@ -236,11 +590,38 @@ gemm_w4_dec_kernel(const __grid_constant__ CUtensorMap tmap_x, const DecArgs a) 
     }
     bars->abort_flag = 0;
     mbar_fence_init();
+    // the first ring-full of weight chunks is requested before the CTA has even finished its set-up
+    int pair = pair0, k = k_first;
+    for (int s = 0; s < n_steps && s < SW; ++s) {
+      const uint8_t* src = a.w + (size_t(2 * pair) * ks + k) * kW4ChunkBytes;
+      mbar_arrive_expect_tx(&bars->w_full[0][s], kW4ChunkBytes);
+      bulk_g2s(w_ring + s * kW4ChunkBytes, src, kW4ChunkBytes, &bars->w_full[0][s]);
+      ++w_issued0;
+      if (s < n_real1) {
+        mbar_arrive_expect_tx(&bars->w_full[1][s], kW4ChunkBytes);
+        bulk_g2s(w_ring + (SW + s) * kW4ChunkBytes, src + size_t(ks) * kW4ChunkBytes, kW4ChunkBytes,
+                 &bars->w_full[1][s]);
+        ++w_issued1;
+      }
+      if (++k == ks) {
+        k = 0;
+        ++pair;
+      }
+    }
     prefetch_tmap(&tmap_x);
   }
   if (warp == 2) {
     tmem_alloc(&bars->tmem_base, 512);
     tmem_relinquish();
+  }
+  if (threadIdx.x == 96) {
+    // the start-address field counts 16-byte units: a K step of 16 halfs is +2, the second 64-wide K sub-tile of a
+    // stage is +kXBytes/16
+    const uint64_t desc0 = make_desc_sw128(smem_u32(x_ring));
+    for (int st = 0; st < SX; ++st)
+      for (int j = 0; j < 8; ++j)
+        bars->bdesc[st][j] =
+            desc0 + uint64_t(((st * Cfg::kXStage) >> 4) + (j >> 2) * (Cfg::kXBytes >> 4) + (j & 3) * 2);
   }
   tc_fence_before_sync();
   __syncthreads();
@@ -250,48 +631,68 @@ gemm_w4_dec_kernel(const __grid_constant__ CUtensorMap tmap_x, const DecArgs a) 
   // TMEM columns: accumulator (pipeline p, buffer b) at (2p + b) * 64; operand slot (pipeline p, slot s) at
   // 256 + (2p + s) * 64 (a dequantised 128 x 128 fp16 chunk = 64 columns of 32 bits)
 
+  bool split_ok = false;
   if (warp == 0) {
     // ------------------------------------------------------------------ weight producer (both rings)
     if (lane == 0) {
-      int cnt[2] = {0, 0};
-      bool ok = true;
-      for (int s = 0; s < n_steps && ok; ++s) {
-        const int g = g0 + s, pair = g / ks, k = g - pair * ks;
-        const int ntp = g < single_from ? 2 : 1;
-        for (int r = 0; r < ntp; ++r) {
-          const int slot = cnt[r] % SW, use = cnt[r] / SW;
-          if (use > 0 && !mbar_wait(&bars->w_empty[r][slot], (use - 1) & 1, abort_flag, a.status, 1, s)) {
-            ok = false;
-            break;
-          }
-          const uint8_t* src = a.w + (size_t(2 * pair + r) * ks + k) * kW4ChunkBytes;
-          mbar_arrive_expect_tx(&bars->w_full[r][slot], kW4ChunkBytes);
-          bulk_g2s(w_ring + (r * SW + slot) * kW4ChunkBytes, src, kW4ChunkBytes, &bars->w_full[r][slot]);
-          ++cnt[r];
+      int cnt0 = w_issued0, cnt1 = w_issued1;
+      int slot = 0;                               // both rings advance together while pipeline 1 has chunks
+      uint32_t ph = 0;                            // parity of the completion of w_empty that frees `slot` now
+      int pair = pair0, k = k_first + cnt0;
+      while (k >= ks) {
+        k -= ks;
+        ++pair;
+      }
+      for (int s = cnt0; s < n_steps; ++s) {
+        if (!mbar_wait(&bars->w_empty[0][slot], ph, abort_flag, a.status, 1, s)) break;
+        const uint8_t* src = a.w + (size_t(2 * pair) * ks + k) * kW4ChunkBytes;
+        mbar_arrive_expect_tx(&bars->w_full[0][slot], kW4ChunkBytes);
+        bulk_g2s(w_ring + slot * kW4ChunkBytes, src, kW4ChunkBytes, &bars->w_full[0][slot]);
+        ++cnt0;
+        if (s < n_real1) {
+          if (!mbar_wait(&bars->w_empty[1][slot], ph, abort_flag, a.status, 1, s)) break;
+          mbar_arrive_expect_tx(&bars->w_full[1][slot], kW4ChunkBytes);
+          bulk_g2s(w_ring + (SW + slot) * kW4ChunkBytes, src + size_t(ks) * kW4ChunkBytes, kW4ChunkBytes,
+                   &bars->w_full[1][slot]);
+          ++cnt1;
+        }
+        if (++k == ks) {
+          k = 0;
+          ++pair;
+        }
+        if (++slot == SW) {
+          slot = 0;
+          ph ^= 1;
         }
       }
       if (*abort_flag) {                       // every issued copy must land before the CTA may exit
-        for (int r = 0; r < 2; ++r)
-          for (int it = max(0, cnt[r] - SW); it < cnt[r]; ++it) {
+        for (int r = 0; r < 2; ++r) {
+          const int cnt = r == 0 ? cnt0 : cnt1;
+          for (int it = max(0, cnt - SW); it < cnt; ++it) {
             const uint64_t t0 = globaltimer_ns();
             while (!mbar_try_wait(&bars->w_full[r][it % SW], (it / SW) & 1) && globaltimer_ns() - t0 < kWaitLimitNs) {
             }
           }
+        }
       }
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------------ activation producer
     if (lane == 0) {
-      int issued = 0;
+      int issued = 0, st = 0, k = k_first;
+      uint32_t ph = 1;                                     // flips to 0 when the ring wraps for the first time
       pdl_wait();                                          // the activations come from the previous kernel
       for (int s = 0; s < n_steps; ++s) {
-        const int st = s % SX, use = s / SX;
-        if (use > 0 && !mbar_wait(&bars->x_empty[st], (use - 1) & 1, abort_flag, a.status, 2, s)) break;
-        const int k0 = ((g0 + s) % ks) * kW4StageK;
+        if (s >= SX && !mbar_wait(&bars->x_empty[st], ph, abort_flag, a.status, 2, s)) break;
         mbar_arrive_expect_tx(&bars->x_full[st], Cfg::kXStage);
-        tma_load_2d(x_ring + st * Cfg::kXStage, &tmap_x, k0, 0, &bars->x_full[st]);
-        tma_load_2d(x_ring + st * Cfg::kXStage + Cfg::kXBytes, &tmap_x, k0 + 64, 0, &bars->x_full[st]);
+        tma_load_2d(x_ring + st * Cfg::kXStage, &tmap_x, k * kW4StageK, 0, &bars->x_full[st]);
+        tma_load_2d(x_ring + st * Cfg::kXStage + Cfg::kXBytes, &tmap_x, k * kW4StageK + 64, 0, &bars->x_full[st]);
         issued = s + 1;
+        if (++k == ks) k = 0;
+        if (++st == SX) {
+          st = 0;
+          ph ^= 1;
+        }
       }
       if (*abort_flag) {
         for (int it = max(0, issued - SX); it < issued; ++it) {
@@ -303,272 +704,233 @@ gemm_w4_dec_kernel(const __grid_constant__ CUtensorMap tmap_x, const DecArgs a) 
     }
   } else if (warp == 2 || warp == 3) {
     // ------------------------------------------------------------------ MMA issuer of pipeline p
+    // Kept to as few instructions per step as possible: every index is carried along, nothing is divided.
     const int p = warp - 2;
     if (lane == 0) {
       constexpr uint32_t idesc = make_idesc_f16(kTileN, NT);
-      const uint64_t desc0 = make_desc_sw128(smem_u32(x_ring));
-      int c = 0, item = -1, prev_pair = -1;
-      for (int s = 0; s < n_steps; ++s) {
-        const int g = g0 + s, pair = g / ks, k = g - pair * ks;
-        const bool first = pair != prev_pair;
-        if (first) {
-          ++item;
-          prev_pair = pair;
-        }
-        const int st = s % SX;
-        if (!mbar_wait_spin(&bars->x_full[st], (s / SX) & 1, abort_flag, a.status, 3, s)) break;
-        if (p == 1 && g >= single_from) {                    // no second tile: only hand the stage back
-          mbar_arrive(&bars->x_empty[st]);
-          continue;
-        }
-        const int b = item & 1, sub = c & 1;
-        if (first && item >= 2 &&
-            !mbar_wait_spin(&bars->acc_empty[p][b], ((item >> 1) - 1) & 1, abort_flag, a.status, 4, item))
-          break;
-        if (!mbar_wait_spin(&bars->a_ready[p][sub], (c >> 1) & 1, abort_flag, a.status, 5, c)) break;
-        tc_fence_after_sync();
-        // the start-address field counts 16-byte units: a K step of 16 halfs is +2, the second 64-wide sub-tile is
-        // +kXBytes/16
-        const uint64_t bd = desc0 + uint64_t((st * Cfg::kXStage) >> 4);
-        const uint32_t at = tmem + 256 + (2 * p + sub) * 64, dt = tmem + (2 * p + b) * 64;
+      const uint32_t a_slot0 = tmem + 256 + (2 * p) * 64, acc0 = tmem + (2 * p) * 64;
+      uint32_t at0[8], at1[8];                             // operand slices of slot 0 / slot 1
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
-          umma_ts(dt, at + j * 8, bd + uint64_t((j >> 2) * (Cfg::kXBytes >> 4) + (j & 3) * 2), idesc,
-                  (!first) || (j != 0));
-        tc_commit(&bars->slot_free[p][sub]);
-        if (k == ks - 1 || s == n_steps - 1) tc_commit(&bars->acc_full[p][b]);
-        ++c;
+      for (int j = 0; j < 8; ++j) {
+        at0[j] = a_slot0 + j * 8;
+        at1[j] = a_slot0 + 64 + j * 8;
       }
-    }
-  } else if (warp < kDecEpiWarp0) {
-    // ------------------------------------------------------------------ dequant: chunk -> fp16 -> TMEM slot
-    // group = (pipeline p, slot sub): chunks sub, sub+2, ... of pipeline p.  A thread owns one weight row of the
-    // chunk: 128 nibbles in, 64 half2 out, written as two 32-column TMEM stores.  Chunk c of a pipeline belongs to
-    // step c of the CTA (pipeline 1 only runs out earlier when the last pair has a single tile).
-    const int q = warp & 3;
-    const int grp = (warp - 4) >> 2, p = grp >> 1, sub = grp & 1;
-    const int row = q * 32 + lane;
-    const int n_chunks = p == 0 ? n_steps : n_real1;
-    const uint32_t dst = tmem + (uint32_t(q * 32) << 16) + 256 + (2 * p + sub) * 64;
-    int last = -1;
-    for (int c = sub; c < n_chunks; c += 2) {
-      const int slot = c % SW;
-      if (!mbar_wait(&bars->w_full[p][slot], (c / SW) & 1, abort_flag, a.status, 6, c)) break;
-      const uint8_t* chunk = w_ring + (p * SW + slot) * kW4ChunkBytes;
-      uint4 pk[4];
+      const int my_steps = p == 0 ? n_steps : n_real1;
+      int k = k_first, st = 0, item = 0;
+      uint32_t xph = 0, aph = 0;
+      uint32_t first = 1;
+      int s = 0;
+      // two chunks per trip: slot 0, then slot 1
+      while (s < my_steps) {
 #pragma unroll
-      for (int p4 = 0; p4 < 4; ++p4) pk[p4] = *reinterpret_cast<const uint4*>(chunk + (p4 * 128 + row) * 16);
-      const __half2 sz = *reinterpret_cast<const __half2*>(chunk + 8192 + row * 4);
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&bars->w_empty[p][slot]);     // the chunk is in registers: its slot may be refilled
-      const __half2 s2 = __half2half2(__low2half(sz)), z2 = __half2half2(__high2half(sz));
-      uint32_t o[32];
-      // the first half is dequantised while the MMAs that still read this TMEM slot (chunk c-2) run
-      dec_dequant_half(pk[0], pk[1], s2, z2, o);
-      if (c >= 2) {
-        if (!mbar_wait(&bars->slot_free[p][sub], ((c >> 1) - 1) & 1, abort_flag, a.status, 7, c)) break;
-        // the MMAs of chunk c-2 are complete: its activation stage has one reader less
-        if (q == 0 && lane == 0) mbar_arrive(&bars->x_empty[(c - 2) % SX]);
+        for (int sub = 0; sub < 2; ++sub) {
+          if (s >= my_steps) break;
+          DTICK(tx);
+          if (!mbar_wait_spin(&bars->x_full[st], xph, abort_flag, a.status, 3, s)) goto issuer_done;
+          DACC(0, tx);
+          const uint32_t b = item & 1;
+          if (first && item >= 2 &&
+              !mbar_wait_spin(&bars->acc_empty[p][b], ((item >> 1) - 1) & 1, abort_flag, a.status, 4, item))
+            goto issuer_done;
+          DTICK(ta);
+          if (!mbar_wait_spin(&bars->a_ready[p][sub], aph, abort_flag, a.status, 5, s)) goto issuer_done;
+          DACC(1, ta);
+          DTICK(ti);
+          tc_fence_after_sync();
+          dec_mma_chunk(acc0 + b * 64, sub == 0 ? at0 : at1, bars->bdesc[st], idesc, first ^ 1u);
+          tc_commit(&bars->slot_free[p][sub]);
+          DACC(2, ti);
+          first = 0;
+          if (++k == ks || s == n_steps - 1) {
+            tc_commit(&bars->acc_full[p][b]);
+            k = 0;
+            ++item;
+            first = 1;
+          }
+          if (++st == SX) {
+            st = 0;
+            xph ^= 1;
+          }
+          ++s;
+        }
+        aph ^= 1;
       }
-      tc_fence_after_sync();
-      ZSE_TMEM_ST_X32(dst, o);
-      dec_dequant_half(pk[2], pk[3], s2, z2, o);
-      ZSE_TMEM_ST_X32(dst + 32, o);
-      tc_wait_st();
-      tc_fence_before_sync();
-      if (lane == 0) mbar_arrive(&bars->a_ready[p][sub]);
-      last = c;
-    }
-    // hand back the stage of this group's last chunk as well (the activation producer may still need it when the
-    // other pipeline goes on alone)
-    if (last >= 0 && !*abort_flag) {
-      if (mbar_wait(&bars->slot_free[p][sub], (last >> 1) & 1, abort_flag, a.status, 8, last)) {
-        if (q == 0 && lane == 0) mbar_arrive(&bars->x_empty[last % SX]);
+    issuer_done:
+      // no second tile in the rest of the range (pipeline 1 only): hand the stages back
+      for (; s < n_steps; ++s) {
+        if (!mbar_wait_spin(&bars->x_full[st], xph, abort_flag, a.status, 3, s)) break;
+        mbar_arrive(&bars->x_empty[st]);
+        if (++st == SX) {
+          st = 0;
+          xph ^= 1;
+        }
       }
+#ifdef ZSE_DEC_TIMING
+      tacc[3] = clock64() - t_entry;
+#endif
     }
   } else {
-    // ------------------------------------------------------------------ epilogue (128 threads)
-    const int q = warp & 3, row = q * 32 + lane, et = threadIdx.x - kDecEpiWarp0 * 32;
-    const uint32_t lane_addr = uint32_t(q * 32) << 16;
-    pdl_wait();                     // outputs, workspace and flags may still be in use by the previous kernel
-    const uint32_t epoch1 = ld_acquire_gpu_u32(a.sync) + 1u;
-    uint32_t* flags = a.sync + 8;
-    const int S = a.split;
-    const int seg = S > 0 ? cta % S : 0;
-    int s = 0, item = 0;
-    bool alive = true;
-    while (s < n_steps && alive) {
-      const int g = g0 + s, pair = g / ks, ka = g - pair * ks;
-      const int len = min(ks - ka, n_steps - s);
-      const int ntp = g < single_from ? 2 : 1;
-      const int b = item & 1;
-      // who adds what: `own_mod`/`own_res` select the column granules this CTA finishes (granule % own_mod == own_res;
-      // own_mod 0 = none); src0..src0+n_src-1 are the CTAs whose partial sums it needs (itself excluded)
-      int own_mod, own_res = 0, src0 = 0, n_src = 0;
-      if (S > 0) {
-        own_mod = S;
-        own_res = seg;
-        src0 = cta - seg;
-        n_src = S;
-      } else if (ka == 0) {
-        own_mod = 1;
-        src0 = cta + 1;
-        if (len < ks)
-          while (src0 + n_src < n_cta && dec_range_begin(a, src0 + n_src, n_cta) < (pair + 1) * ks) ++n_src;
-      } else {
-        own_mod = 0;
-      }
-      for (int r = 0; r < ntp && alive; ++r)
-        alive = mbar_wait(&bars->acc_full[r][b], (item >> 1) & 1, abort_flag, a.status, 9, item);
-      alive = epi_all(alive);
-      if (!alive) break;
-      tc_fence_after_sync();
-      // ---- partial sums this CTA does not finish go to the workspace
-      bool dumped = false;
-      for (int r = 0; r < ntp; ++r) {
-        float* dstw = a.ws + (size_t(cta) * 2 + r) * NT * 128 + row;
-#pragma unroll 1
-        for (int gr = 0; gr < Cfg::kGranules; ++gr) {
-          if (own_mod != 0 && gr % own_mod == own_res) continue;
-          uint32_t v[8];
-          ZSE_TMEM_LD_X8(v, tmem + lane_addr + (2 * r + b) * 64 + gr * 8);
-          tc_wait_ld();
+    const int q = warp & 3;
+    if (warp < kDecEpiWarp0) {
+      // ---------------------------------------------------------------- dequant: chunk -> fp16 -> TMEM slot
+      // group = (pipeline p, slot sub): chunks sub, sub+2, ... of pipeline p.  A thread owns one weight row of the
+      // chunk: 128 nibbles in, 64 half2 out, written as two 32-column TMEM stores.  Chunk c of a pipeline belongs to
+      // step c of the CTA (pipeline 1 only runs out earlier when the last pair has a single tile).
+      const int grp = (warp - 4) >> 2, p = grp >> 1, sub = grp & 1;
+      const int row = q * 32 + lane;
+      const int n_chunks = p == 0 ? n_steps : n_real1;
+      const uint32_t dst = tmem + (uint32_t(q * 32) << 16) + 256 + (2 * p + sub) * 64;
+      int last = -1;
+      int slot = sub, xst = sub;                 // weight-ring slot of chunk c; activation stage of chunk c - 2
+      uint32_t wph = 0, sph = 0;                 // parities: w_full of chunk c, slot_free of chunk c - 2
+      for (int c = sub; c < n_chunks; c += 2) {
+        DTICK(t0);
+        if (!mbar_wait(&bars->w_full[p][slot], wph, abort_flag, a.status, 6, c)) break;
+        DACC(0, t0);
+#ifdef ZSE_DEC_TIMING
+        if (c == sub) tacc[6] = clock64() - t_entry;
+#endif
+        DTICK(t1);
+        const uint8_t* chunk = w_ring + (p * SW + slot) * kW4ChunkBytes;
+        uint4 pk[4];
 #pragma unroll
-          for (int i = 0; i < 8; ++i) dstw[(gr * 8 + i) * 128] = __uint_as_float(v[i]);
-          dumped = true;
+        for (int p4 = 0; p4 < 4; ++p4) pk[p4] = *reinterpret_cast<const uint4*>(chunk + (p4 * 128 + row) * 16);
+        const __half2 sz = *reinterpret_cast<const __half2*>(chunk + 8192 + row * 4);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->w_empty[p][slot]);   // the chunk is in registers: its slot may be refilled
+        const __half2 s2 = __half2half2(__low2half(sz)), z2 = __half2half2(__high2half(sz));
+        uint32_t o[32];
+        // the first half is dequantised while the MMAs that still read this TMEM slot (chunk c-2) run
+        dec_dequant_half(pk[0], pk[1], s2, z2, o);
+        DACC(1, t1);
+        DTICK(t2);
+        if (c >= 2) {
+          if (!mbar_wait(&bars->slot_free[p][sub], sph, abort_flag, a.status, 7, c)) break;
+          sph ^= 1;
+          // the MMAs of chunk c-2 are complete: its activation stage has one reader less
+          if (q == 0 && lane == 0) mbar_arrive(&bars->x_empty[xst]);
+          xst += 2;
+          if (xst >= SX) xst -= SX;
+        }
+        DACC(2, t2);
+        DTICK(t3);
+        tc_fence_after_sync();
+        ZSE_TMEM_ST_X32(dst, o);
+        dec_dequant_half(pk[2], pk[3], s2, z2, o);
+        ZSE_TMEM_ST_X32(dst + 32, o);
+        DACC(3, t3);
+        DTICK(t4);
+        tc_wait_st();
+        tc_fence_before_sync();
+        if (lane == 0) mbar_arrive(&bars->a_ready[p][sub]);
+        DACC(4, t4);
+        last = c;
+        slot += 2;
+        if (slot >= SW) {
+          slot -= SW;
+          wph ^= 1;
         }
       }
-      if (dumped) {
-        __threadfence();
-        epi_bar();
-        if (et == 0) st_release_gpu_u32(flags + cta, epoch1);
-      }
-      if (own_mod != 0) {
-        // ---- wait for the other CTAs' partial sums of this pair
-        for (int j = 0; j < n_src && alive; ++j) {
-          const int c2 = src0 + j;
-          if (c2 == cta) continue;
-          if (lane == 0) alive = dec_wait_flag(flags + c2, epoch1, abort_flag, a.status, 10, c2);
-          __syncwarp();
-        }
-        alive = epi_all(alive);
-        for (int r = 0; r < ntp && alive; ++r) {
-          const int tile = 2 * pair + r;
-          // ---- phase 1: finished sums of the owned columns -> stage[col][row]
-          float bias = 0.f;
-          if ((EPI == kDecF16 || EPI == kDecQkvRope) && a.bias != nullptr && tile * kTileN + row < a.N)
-            bias = __half2float(a.bias[tile * kTileN + row]);
-#pragma unroll 1
-          for (int gr = own_res; gr < Cfg::kGranules; gr += own_mod) {
-            uint32_t raw[8];
-            ZSE_TMEM_LD_X8(raw, tmem + lane_addr + (2 * r + b) * 64 + gr * 8);
-            tc_wait_ld();
-            float v[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(raw[i]) + bias;
-            for (int j = 0; j < n_src; ++j) {                   // fixed order: the sum is reproducible
-              const int c2 = src0 + j;
-              if (c2 == cta) continue;
-              const float* srcw = a.ws + (size_t(c2) * 2 + r) * NT * 128 + row;
-              float t8[8];
-#pragma unroll
-              for (int i = 0; i < 8; ++i) t8[i] = __ldcg(srcw + (gr * 8 + i) * 128);
-#pragma unroll
-              for (int i = 0; i < 8; ++i) v[i] += t8[i];
-            }
-#pragma unroll
-            for (int i = 0; i < 8; ++i) stage[(gr * 8 + i) * 128 + row] = v[i];
-          }
-          epi_bar();
-          // ---- phase 2: 16-byte stores; thread -> (column et >> 4 of the granule, 8 rows from (et & 15) * 8)
-#pragma unroll 1
-          for (int gr = own_res; gr < Cfg::kGranules; gr += own_mod) {
-            const int col = gr * 8 + (et >> 4), t = col;
-            if (t >= a.M) continue;
-            if (EPI == kDecF16 || EPI == kDecF32) {
-              const int r0 = (et & 15) * 8, n = tile * kTileN + r0;
-              if (n >= a.N) continue;
-              const float4 lo = *reinterpret_cast<const float4*>(stage + col * 128 + r0);
-              const float4 hi = *reinterpret_cast<const float4*>(stage + col * 128 + r0 + 4);
-              if (EPI == kDecF16) {
-                uint4 pk;
-                pk.x = pack_half2(clamp_f16(lo.x), clamp_f16(lo.y));
-                pk.y = pack_half2(clamp_f16(lo.z), clamp_f16(lo.w));
-                pk.z = pack_half2(clamp_f16(hi.x), clamp_f16(hi.y));
-                pk.w = pack_half2(clamp_f16(hi.z), clamp_f16(hi.w));
-                *reinterpret_cast<uint4*>(reinterpret_cast<__half*>(a.out) + size_t(t) * a.ldo + n) = pk;
-              } else {
-                float* o = reinterpret_cast<float*>(a.out) + size_t(t) * a.ldo + n;
-                *reinterpret_cast<float4*>(o) = lo;
-                *reinterpret_cast<float4*>(o + 4) = hi;
-              }
-            } else if (EPI == kDecSwiGLU) {
-              // tile rows 0..63 = gate, 64..127 = up of the same 64 outputs: four outputs per thread
-              const int o0 = (et & 15) * 4, n = tile * 64 + o0;
-              if (n >= a.N / 2) continue;
-              const float4 gt = *reinterpret_cast<const float4*>(stage + col * 128 + o0);
-              const float4 up = *reinterpret_cast<const float4*>(stage + col * 128 + 64 + o0);
-              uint2 pk;
-              pk.x = pack_half2(clamp_f16(silu_f(gt.x) * up.x), clamp_f16(silu_f(gt.y) * up.y));
-              pk.y = pack_half2(clamp_f16(silu_f(gt.z) * up.z), clamp_f16(silu_f(gt.w) * up.w));
-              *reinterpret_cast<uint2*>(reinterpret_cast<__half*>(a.out) + size_t(t) * a.ldo + n) = pk;
-            } else if (EPI == kDecQkvRope) {
-              // tile = one head of 128 dims: q heads, then k heads, then v heads; eight dims per thread
-              const DecRope& rp = a.rope;
-              const int d0 = (et & 15) * 8;
-              const float* sv = stage + col * 128;
-              float val[8];
-              if (tile < rp.nh + rp.nkv) {
-                const int pos = min(max(rp.positions[t], 0), rp.max_position - 1);
-                const float2* cs = rp.cos_sin + size_t(pos) * 64 + (d0 & 63);
-                const float* xa = sv + (d0 & 63);           // first half of the head
-                const float* xb = xa + 64;                  // second half
-#pragma unroll
-                for (int i = 0; i < 8; ++i) {
-                  const float2 c2 = cs[i];
-                  val[i] = d0 < 64 ? xa[i] * c2.x - xb[i] * c2.y : xb[i] * c2.x + xa[i] * c2.y;
-                }
-              } else {
-#pragma unroll
-                for (int i = 0; i < 8; ++i) val[i] = sv[d0 + i];
-              }
-              uint4 pk;
-              pk.x = pack_half2(clamp_f16(val[0]), clamp_f16(val[1]));
-              pk.y = pack_half2(clamp_f16(val[2]), clamp_f16(val[3]));
-              pk.z = pack_half2(clamp_f16(val[4]), clamp_f16(val[5]));
-              pk.w = pack_half2(clamp_f16(val[6]), clamp_f16(val[7]));
-              if (tile < rp.nh) {                           // q: what attention reads
-                *reinterpret_cast<uint4*>(reinterpret_cast<__half*>(a.out) + size_t(t) * a.ldo + tile * 128 + d0) = pk;
-              } else if (tile < rp.nh + 2 * rp.nkv) {
-                const long long slot = rp.slots[t];
-                if (slot >= 0) {
-                  const bool is_v = tile >= rp.nh + rp.nkv;
-                  const int kvh = tile - rp.nh - (is_v ? rp.nkv : 0);
-                  const long long blk = slot / rp.block_size, off = slot % rp.block_size;
-                  __half* dstp = rp.kv_layer + (((blk * 2 + (is_v ? 1 : 0)) * rp.nkv + kvh) * rp.block_size + off) * 128;
-                  *reinterpret_cast<uint4*>(dstp + d0) = pk;
-                }
-              }
-            }
-          }
-          epi_bar();                                   // the stage is reused by the next tile
+      // hand back the stage of this group's last chunk as well (the activation producer may still need it when the
+      // other pipeline goes on alone)
+      if (last >= 0 && !*abort_flag) {
+        if (mbar_wait(&bars->slot_free[p][sub], sph, abort_flag, a.status, 8, last)) {
+          if (q == 0 && lane == 0) mbar_arrive(&bars->x_empty[xst]);
         }
       }
-      // the accumulators of this item are read: the pipelines may overwrite them (item + 2)
-      tc_fence_before_sync();
-      __syncwarp();
-      if (lane == 0)
-        for (int r = 0; r < ntp; ++r) mbar_arrive(&bars->acc_empty[r][b]);
-      s += len;
-      ++item;
     }
+    // ------------------------------------------------------------------ epilogue
+    pdl_wait();                     // outputs, workspace and flags may still be in use by the previous kernel
+    const bool is_epi = warp >= kDecEpiWarp0;
+    const int wi_wide = is_epi ? 4 : (warp - 4) >> 2;            // index among the five warps of this lane quarter
+#ifdef ZSE_DEC_TIMING
+    long long tdummy[8];
+    long long* tepi = is_epi ? tacc : tdummy;
+#else
+    long long* tepi = nullptr;
+#endif
+    if (a.split > 0) {
+      // split plan: one tile pair, cut into S segments that form a thread-block cluster (continued below, where all
+      // threads of the CTA meet at the cluster barriers)
+      bool alive = !*abort_flag;
+      const int ntp = g0 < single_from ? 2 : 1;
+      for (int r = 0; r < ntp && alive; ++r) alive = mbar_wait(&bars->acc_full[r][0], 0, abort_flag, a.status, 9, r);
+      split_ok = epi_all(alive, 1);
+      tc_fence_after_sync();
+#ifdef ZSE_DEC_TIMING
+      tacc[0] = clock64() - t_entry;
+#endif
+    } else {
+      // stream plan: the four epilogue warps take the tile pairs one after the other while the pipelines run ahead
+      // (accumulators are double-buffered).  The CTA's last pair is shared by all twenty worker warps: nothing is
+      // left to overlap it with, and the idle activation ring serves as the second staging buffer.
+      const uint32_t epoch1 = ld_acquire_gpu_u32(a.sync) + 1u;
+      int s = 0, item = 0, pair = pair0, ka = k_first;
+      bool ok = true;
+      while (s < n_steps) {
+        const int len = min(ks - ka, n_steps - s);
+        const int ntp = g0 + s < single_from ? 2 : 1;
+        const bool last_item = s + len == n_steps;
+        // all twenty warps call the last item (it begins with a vote of all of them), also after a failure
+        if (last_item)
+          ok = dec_epilogue_item<NT, EPI>(a, bars, stage, reinterpret_cast<float*>(x_ring), tmem, cta, n_cta, pair, ka,
+                                          len, ntp, item & 1, item, epoch1, q, lane, wi_wide, 5, ok, tepi);
+        else if (is_epi && ok)
+          ok = dec_epilogue_item<NT, EPI>(a, bars, stage, stage, tmem, cta, n_cta, pair, ka, len, ntp, item & 1, item,
+                                          epoch1, q, lane, 0, 1, ok, tepi);
+        if (is_epi && !last_item && ok) {
+          // the accumulators of this item are read: the pipelines may overwrite them (item + 2)
+          tc_fence_before_sync();
+          __syncwarp();
+          if (lane == 0)
+            for (int r = 0; r < ntp; ++r) mbar_arrive(&bars->acc_empty[r][item & 1]);
+        }
+        s += len;
+        ka = 0;
+        ++pair;
+        ++item;
+      }
+    }
+  }
+  __syncwarp();
+  if (a.split > 0) {
+    // every thread of every CTA of the cluster passes both barriers, whatever happened before.  First barrier: this
+    // CTA's MMAs are complete and its TMA copies have landed, i.e. its rings may be written by the peers.
+    const int S = a.split, seg = int(dec_cluster_rank()), ntp = g0 < single_from ? 2 : 1;
+    const int go_max = (Cfg::kGranules + S - 1) / S;
+    float* recv = reinterpret_cast<float*>(x_ring);      // [S][2][go_max][8][128] fp32 over the idle rings
+    const int wi = warp >= kDecEpiWarp0 ? 4 : (warp - 4) >> 2;
+    cluster_sync_all_threads();
+#ifdef ZSE_DEC_TIMING
+    if (warp >= kDecEpiWarp0) tacc[1] = clock64() - t_entry;
+#endif
+    if (warp >= 4 && split_ok) dec_split_push<NT>(recv, tmem, ntp, seg, S, go_max, warp & 3, lane, wi);
+    __syncwarp();
+#ifdef ZSE_DEC_TIMING
+    if (warp >= kDecEpiWarp0) tacc[2] = clock64() - t_entry;
+#endif
+    cluster_sync_all_threads();
+#ifdef ZSE_DEC_TIMING
+    if (warp >= kDecEpiWarp0) tacc[3] = clock64() - t_entry;
+#endif
+    if (warp >= 4 && split_ok)
+      dec_split_finish<NT, EPI>(a, recv, pair0, ntp, seg, S, go_max, wi * 128 + (warp & 3) * 32 + lane);
+#ifdef ZSE_DEC_TIMING
+    if (warp >= kDecEpiWarp0) tacc[4] = clock64() - t_entry;
+#endif
   }
 
   // ---------------------------------------------------------------------- exit
+#ifdef ZSE_DEC_TIMING
+  if (a.timing != nullptr && lane == 0 && cta == 1) {
+    tacc[7] = clock64() - t_entry;
+    for (int i = 0; i < 8; ++i) a.timing[warp * 8 + i] = tacc[i];
+  }
+#endif
   tc_fence_before_sync();
   __syncthreads();
   if (warp == 2) tmem_dealloc(tmem, 512);
-  if (threadIdx.x == kDecEpiWarp0 * 32) {
+  if (a.split == 0 && threadIdx.x == kDecEpiWarp0 * 32) {
     // the last CTA to leave moves the launch epoch on (every CTA read it after its pdl_wait, i.e. long ago)
     __threadfence();
     const uint32_t t = atomicAdd(a.sync + 1, 1u);
@@ -587,18 +949,24 @@ struct DecPlan {
 
 // tuning knobs (tests and the microbenchmark move them): smallest number of steps worth a CTA in the stream plan,
 // largest number of segments per pair in the split plan
+static long long* g_dec_timing = nullptr;
 static int g_dec_min_steps = 4;
 static int g_dec_max_split = 8;
+
+// Clusters of S CTAs of this kernel (one CTA per SM) that fit on the device at once.  Measured on B200 (148 SMs):
+// 148, 74, 45, 33, 26, 22, 15, 15 for S = 1..8; the driver is asked once per device, the table is the fallback.
+static int dec_max_clusters(int S);
 
 static DecPlan plan_dec(int n_pairs, int k_stages, int sm_count) {
   DecPlan p{1, 0};
   const int total = n_pairs * k_stages;
   if (2 * n_pairs <= sm_count) {
-    // split plan: S segments per pair, at least two steps per segment
-    int S = min(min(g_dec_max_split, sm_count / n_pairs), max(1, k_stages / 2));
-    S = max(1, S);
-    p.split = S;
-    p.n_cta = n_pairs * S;
+    // split plan: the largest S whose clusters are all resident at once (one wave), at least two steps per segment
+    int best = 1;
+    for (int S = 2; S <= min(g_dec_max_split, 8); ++S)
+      if (S <= max(1, k_stages / 2) && n_pairs <= dec_max_clusters(S) && n_pairs * S <= sm_count) best = S;
+    p.split = best;
+    p.n_cta = n_pairs * best;
   } else {
     p.split = 0;
     p.n_cta = max(1, min(sm_count, total / g_dec_min_steps));
@@ -619,8 +987,55 @@ static int launch_dec(const CUtensorMap& tx, const DecArgs& a, int n_cta, cudaSt
       return ZSE_ERR_LAUNCH;
     attr_done[dev] = true;
   }
-  return launch_pdl(kern, dim3(n_cta), dim3(kDecThreads), size_t(smem), st, tx, a) == cudaSuccess ? 0
-                                                                                                  : ZSE_ERR_LAUNCH;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(n_cta);
+  cfg.blockDim = dim3(kDecThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[2];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = a.split > 0 ? a.split : 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[1].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl_enabled() ? 2 : 1;
+  return cudaLaunchKernelEx(&cfg, kern, tx, a) == cudaSuccess ? 0 : ZSE_ERR_LAUNCH;
+}
+
+static int dec_max_clusters(int S) {
+  static const int kTable[9] = {0, 148, 74, 45, 33, 26, 22, 15, 15};
+  static int cached[64][9] = {};
+  if (S < 1 || S > 8) return 0;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    cudaGetLastError();
+    return kTable[S];
+  }
+  if (cached[dev][S] == 0) {
+    auto kern = gemm_w4_dec_kernel<64, kDecF16>;
+    constexpr int smem = DecCfg<64>::kSmemBytes;
+    int n = 0;
+    cudaLaunchConfig_t cfg = {};
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = S;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cfg.gridDim = dim3(S * 8);
+    cfg.blockDim = dim3(kDecThreads);
+    cfg.dynamicSmemBytes = smem;
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess ||
+        cudaOccupancyMaxActiveClusters(&n, kern, &cfg) != cudaSuccess || n <= 0) {
+      cudaGetLastError();
+      n = kTable[S];
+    }
+    cached[dev][S] = n;
+  }
+  return cached[dev][S];
 }
 
 template <int NT>
@@ -657,6 +1072,9 @@ extern "C" long long zse_gemm_w4_dec_workspace_bytes(int sm_count) {
   return (long long)sm_count * 2 * 64 * 128 * 4 + (8 + sm_count) * 4 + 256;
 }
 
+// Debug hook (only meaningful in builds with ZSE_DEC_TIMING): device buffer of 24 x 8 cycle counters.
+extern "C" void zse_gemm_w4_dec_set_timing(void* dev_buffer) { zse::g_dec_timing = reinterpret_cast<long long*>(dev_buffer); }
+
 extern "C" void zse_gemm_w4_dec_set_tuning(int min_steps, int max_split) {
   if (min_steps > 0) zse::g_dec_min_steps = min_steps;
   if (max_split > 0) zse::g_dec_max_split = min(max_split, 64);
@@ -682,7 +1100,9 @@ static int run_dec(const void* w_tiled, const void* x, int x_rows_cap, const voi
                    int K, int ldo, int epilogue, void* workspace, const DecRope* rope, void* status, void* stream) {
   if (M <= 0) return 0;
   if (!zse_gemm_w4_dec_supported(M, N, K, epilogue) || workspace == nullptr) return ZSE_ERR_SHAPE;
-  if ((reinterpret_cast<uintptr_t>(out) & 15) || (reinterpret_cast<uintptr_t>(workspace) & 15)) return ZSE_ERR_ALIGN;
+  if ((reinterpret_cast<uintptr_t>(out) & 15) || (reinterpret_cast<uintptr_t>(workspace) & 15) ||
+      (reinterpret_cast<uintptr_t>(bias) & 15))
+    return ZSE_ERR_ALIGN;
   if (epilogue == kDecF32 ? (ldo % 4) : (ldo % 8)) return ZSE_ERR_ALIGN;
   const int sm_count = dec_sm_count();
   const int k_stages = K / kW4StageK;
@@ -708,6 +1128,7 @@ static int run_dec(const void* w_tiled, const void* x, int x_rows_cap, const voi
   a.sync = reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(workspace) +
                                        (size_t)sm_count * 2 * 64 * 128 * 4);
   a.status = reinterpret_cast<Status*>(status);
+  a.timing = g_dec_timing;
   if (rope != nullptr) a.rope = *rope;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   switch (nt) {
