@@ -28,6 +28,24 @@ int zse_gemm_w4_splits(int M, int N, int K, int k_split);
 // the launcher's plan for a call: out4 = {tiles per wide CTA, K splits, cluster size, CTA shape: 0 wide, 1 narrow,
 // -1 CUDA-core GEMV}
 void zse_gemm_w4_plan(int M, int N, int K, int epilogue, int k_split, int sm_count, int* out4);
+// ---- gemm_w4_dec.cu -----------------------------------------------------------------------------------------
+// Decode-sized INT4 GEMM (M <= 64): one persistent CTA per SM over an even split of the weight stream.
+// epilogue: 0 = fp16 store (+bias), 1 = SwiGLU, 2 = fp32 store.  `workspace`: zse_gemm_w4_dec_workspace_bytes bytes,
+// zeroed once; one workspace serves the calls of ONE stream (calls that overlap on the GPU must not share it).
+long long zse_gemm_w4_dec_workspace_bytes(int sm_count);
+int zse_gemm_w4_dec_supported(int M, int N, int K, int epilogue);
+int zse_gemm_w4_dec(const void* w_tiled, const void* x, int x_rows_cap, const void* bias, void* out, int M, int N,
+                    int K, int ldo, int epilogue, void* workspace, void* status, void* stream);
+// Fused QKV projection, head_dim 128, full rotary: bias + rotate-half RoPE (cos/sin table [max_position][64] of
+// float2) + K/V rows into the paged cache [blocks][2][nkv][block_size][128]; qkv_out receives the rotated q heads.
+int zse_gemm_w4_dec_qkv_rope(const void* w_tiled, const void* x, int x_rows_cap, const void* bias, void* qkv_out,
+                             int ldo, int M, int K, int nh, int nkv, void* kv_layer, int block_size,
+                             const void* positions_i32, const void* slots_i64, const void* cos_sin_f32x2,
+                             int max_position, void* workspace, void* status, void* stream);
+// the plan of a call: out2 = {CTAs, K segments per tile pair (0: the stream plan)}
+void zse_gemm_w4_dec_plan(int N, int K, int epilogue, int sm_count, int* out2);
+void zse_gemm_w4_dec_set_tuning(int min_steps, int max_split);
+
 int zse_gemm_f16(const void* w, int w_rows_cap, const void* x, int x_rows_cap, const void* bias, void* out, int M,
                  int N, int K, int ldo, int epilogue, int k_split, void* status, void* stream);
 int zse_gemm_f16_splits(int M, int N, int K, int k_split);

@@ -10,14 +10,18 @@
 //    of bytes whatever the shape.  Two plans:
 //      stream  (many tile pairs)  range c = [c*T/n, (c+1)*T/n): a pair may start in one CTA and end in the next;
 //      split   (few tile pairs)   every pair is cut into S equal K segments, one CTA each.
-//  * Inside a CTA two pipelines run side by side, one per tile of the pair, and share every activation stage:
-//      warp 0      bulk-TMA producer of the weight chunks (one ring per pipeline),
-//      warp 1      tiled-TMA producer of the activation stages,
-//      warps 2,3   MMA issuers (tcgen05.mma, A = dequantised weights in TMEM, B = activations in shared memory),
-//      warps 4-19  dequant: four groups of four warps; a group owns ONE TMEM operand slot, two groups alternate on
-//                  the chunks of a pipeline, so dequantising chunk c+1 overlaps the MMAs of chunk c,
-//      warps 20-23 epilogue: accumulators are double-buffered in TMEM, so the epilogue of one tile pair runs while
-//                  the pipelines already work on the next.
+//  * Inside a CTA two pipelines run side by side, one per tile of the pair, and share every activation stage.  Each
+//    pipeline is worked by two lanes (even and odd K stages), and a lane is a closed loop of its own: a dequant group
+//    of four warps, one TMEM operand slot, one MMA-issuing warp and one accumulator.  Measured on B200, a thread that
+//    issues tcgen05.mma back to back gets one through every ~85 cycles (M 128, N 64, K 16, A in TMEM) whatever else
+//    it executes, while the tensor pipe needs 32: four issuing threads, one per scheduler, are what fills the pipe.
+//      warps 0-3   MMA issuers of lane (pipeline p, parity s) (tcgen05.mma, A = dequantised weights in TMEM, B =
+//                  activations in shared memory); the two accumulators of a tile are added in the epilogue,
+//      warp 4      producer: bulk TMA of the weight chunks (one ring per pipeline), tiled TMA of the activations,
+//      warps 5-20  dequant: four groups of four warps, group (p, s) fills the operand slot of lane (p, s), so
+//                  dequantising chunk c+1 (other lane) overlaps the MMAs of chunk c,
+//      warps 21-24 epilogue: takes the finished tile pairs one after the other; the pipelines only wait for it
+//                  until it has read the accumulators out of TMEM.
 //  * Partial sums of a tile pair that was cut meet in a workspace in global memory (it stays in L2):
 //      stream plan: the CTA that holds K stage 0 of the pair owns it; the others dump their fp32 partials first thing
 //                   (their piece of that pair is the head of their range) and the owner, which reaches the pair last,
@@ -42,11 +46,13 @@
 
 namespace zse {
 
-constexpr int kDecWarps = 24;
+constexpr int kDecWarps = 25;
 constexpr int kDecThreads = kDecWarps * 32;
 constexpr int kDecSX = 6;            // activation stages
 constexpr int kDecSW = 5;            // weight chunks per pipeline ring
-constexpr int kDecEpiWarp0 = 20;
+constexpr int kDecProducerWarp = 4;
+constexpr int kDecDqWarp0 = 5;
+constexpr int kDecEpiWarp0 = 21;
 constexpr int kDecStageBytes = 64 * 128 * 4;     // finished sums of one tile: [token column][128 rows] fp32
 
 enum DecEpilogue : int { kDecF16 = 0, kDecSwiGLU = 1, kDecF32 = 2, kDecQkvRope = 3, kDecAllReduceNorm = 4 };
@@ -378,6 +384,20 @@ __device__ __forceinline__ void dec_store_item(const DecArgs& a, const Fetch& f,
   }
 }
 
+// Eight columns of tile r's sum: the accumulators of the two lanes (even / odd K stages), whichever took part.
+__device__ __forceinline__ void dec_load_acc8(uint32_t tmem, uint32_t lane_addr, int r, int gr, bool lane0, bool lane1,
+                                              float (&v)[8]) {
+  uint32_t x[8], y[8];
+  // both are loaded whatever took part (an accumulator that was not written holds garbage that is not used): loads
+  // under a condition would force the arrays into local memory
+  ZSE_TMEM_LD_X8(x, tmem + lane_addr + (2 * r) * 64 + gr * 8);
+  ZSE_TMEM_LD_X8(y, tmem + lane_addr + (2 * r + 1) * 64 + gr * 8);
+  tc_wait_ld();
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+    v[i] = (lane0 ? __uint_as_float(x[i]) : 0.f) + (lane1 ? __uint_as_float(y[i]) : 0.f);
+}
+
 // Stream plan: one tile pair of one CTA, from finished MMAs to memory.  Run by W warps per TMEM lane quarter (W = 1:
 // the epilogue warps alone, while the pipelines work on the next pair; W = 5: all twenty worker warps, for the CTA's
 // last pair); `wi` is this warp's index among them.  stage0 / stage1: where the finished sums of the two tiles are
@@ -385,8 +405,9 @@ __device__ __forceinline__ void dec_store_item(const DecArgs& a, const Fetch& f,
 template <int NT, int EPI>
 __device__ __forceinline__ bool dec_epilogue_item(const DecArgs& a, DecBars* bars, float* stage0, float* stage1,
                                                   uint32_t tmem, int cta, int n_cta, int pair, int ka, int len,
-                                                  int ntp, int b, int item, uint32_t epoch1, int q, int lane, int wi,
-                                                  int W, bool alive_in, long long* tacc) {
+                                                  int ntp, bool lane0, bool lane1, uint32_t par0, uint32_t par1,
+                                                  bool release, uint32_t epoch1, int q, int lane, int wi, int W,
+                                                  bool alive_in, long long* tacc) {
   using Cfg = DecCfg<NT>;
   constexpr int G = Cfg::kGranules;
   const int ks = a.k_stages;
@@ -405,8 +426,10 @@ __device__ __forceinline__ bool dec_epilogue_item(const DecArgs& a, DecBars* bar
   // every thread of the group comes through the vote below whatever happened before, so a failed wait anywhere ends
   // the epilogue for all of them together
   bool alive = alive_in && !*abort_flag;
-  for (int r = 0; r < ntp && alive; ++r)
-    alive = mbar_wait(&bars->acc_full[r][b], (item >> 1) & 1, abort_flag, a.status, 9, item);
+  for (int r = 0; r < ntp && alive; ++r) {
+    if (lane0) alive = mbar_wait(&bars->acc_full[r][0], par0, abort_flag, a.status, 9, r);
+    if (lane1 && alive) alive = mbar_wait(&bars->acc_full[r][1], par1, abort_flag, a.status, 9, 2 + r);
+  }
   if (owner && alive && lane == 0)
     for (int j = wi; j < n_src && alive; j += W)
       alive = dec_wait_flag(flags + src0 + j, epoch1, abort_flag, a.status, 10, src0 + j);
@@ -421,12 +444,20 @@ __device__ __forceinline__ bool dec_epilogue_item(const DecArgs& a, DecBars* bar
 #pragma unroll 1
     for (int u = wi; u < ntp * G; u += W) {
       const int r = u / G, gr = u - r * G;
-      uint32_t v[8];
-      ZSE_TMEM_LD_X8(v, tmem + lane_addr + (2 * r + b) * 64 + gr * 8);
-      tc_wait_ld();
+      float v[8];
+      dec_load_acc8(tmem, lane_addr, r, gr, lane0, lane1, v);
       float* dstw = a.ws + ((size_t(cta) * 2 + r) * NT + gr * 8) * 128 + row;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) __stcg(dstw + i * 128, __uint_as_float(v[i]));
+      for (int i = 0; i < 8; ++i) __stcg(dstw + i * 128, v[i]);
+    }
+    if (release) {                                     // the accumulators are read: the lanes may go on
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0)
+        for (int r = 0; r < ntp; ++r) {
+          if (lane0) mbar_arrive(&bars->acc_empty[r][0]);
+          if (lane1) mbar_arrive(&bars->acc_empty[r][1]);
+        }
     }
     epi_bar(wide);
     if (et == 0) {
@@ -449,32 +480,35 @@ __device__ __forceinline__ bool dec_epilogue_item(const DecArgs& a, DecBars* bar
         bias = __half2float(a.bias[tile * kTileN + row]);
 #pragma unroll 1
       for (int gr = wi; gr < G; gr += W) {
-        uint32_t raw[8];
-        ZSE_TMEM_LD_X8(raw, tmem + lane_addr + (2 * r + b) * 64 + gr * 8);
-        // partial sums of the other CTAs (at most a few): their loads are in flight together with the TMEM load
-        float t8[4][8];
+        // partial sums of the other CTAs (one or two as a rule): their loads are in flight together with the TMEM
+        // loads; added in CTA order (the sum is reproducible)
+        float t8[2][8];
 #pragma unroll
-        for (int jj = 0; jj < 4; ++jj) {
+        for (int jj = 0; jj < 2; ++jj) {
           const bool use = jj < n_src;
           const float* srcw = a.ws + ((size_t(use ? src0 + jj : cta) * 2 + r) * NT + gr * 8) * 128 + row;
 #pragma unroll
           for (int i = 0; i < 8; ++i) t8[jj][i] = use ? __ldcg(srcw + i * 128) : 0.f;
         }
-        tc_wait_ld();
         float v[8];
+        dec_load_acc8(tmem, lane_addr, r, gr, lane0, lane1, v);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(raw[i]) + bias;
-#pragma unroll
-        for (int jj = 0; jj < 4; ++jj)
-#pragma unroll
-          for (int i = 0; i < 8; ++i) v[i] += t8[jj][i];
-        for (int j = 4; j < n_src; ++j) {                       // rare: a pair cut into more than five pieces
+        for (int i = 0; i < 8; ++i) v[i] = (v[i] + bias) + t8[0][i] + t8[1][i];
+        for (int j = 2; j < n_src; ++j) {                       // rare: a pair cut into more than three pieces
           const float* srcw = a.ws + ((size_t(src0 + j) * 2 + r) * NT + gr * 8) * 128 + row;
 #pragma unroll
           for (int i = 0; i < 8; ++i) v[i] += __ldcg(srcw + i * 128);
         }
 #pragma unroll
         for (int i = 0; i < 8; ++i) stage[(gr * 8 + i) * 128 + row] = v[i];
+      }
+      if (release) {                                   // tile r's accumulators are read: its lanes may go on
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) {
+          if (lane0) mbar_arrive(&bars->acc_empty[r][0]);
+          if (lane1) mbar_arrive(&bars->acc_empty[r][1]);
+        }
       }
     }
     epi_bar(wide);
@@ -500,8 +534,8 @@ __device__ __forceinline__ bool dec_epilogue_item(const DecArgs& a, DecBars* bar
 // cluster barrier the owner adds the S slots in rank order.  Remote loads are avoided on purpose: measured here, a
 // thread's loads from another SM's shared memory complete one after the other at ~800 cycles each.
 template <int NT>
-__device__ __forceinline__ void dec_split_push(float* recv, uint32_t tmem, int ntp, int seg, int S, int go_max, int q,
-                                               int lane, int wi) {
+__device__ __forceinline__ void dec_split_push(float* recv, uint32_t tmem, int ntp, bool lane0, bool lane1, int seg,
+                                               int S, int go_max, int q, int lane, int wi) {
   constexpr int G = DecCfg<NT>::kGranules;
   const int row = q * 32 + lane;
   const uint32_t lane_addr = uint32_t(q * 32) << 16;
@@ -509,15 +543,14 @@ __device__ __forceinline__ void dec_split_push(float* recv, uint32_t tmem, int n
   for (int u = wi; u < ntp * G; u += 5) {
     const int r = u / G, gr = u - r * G;
     const int owner = gr % S, j = gr / S;
-    uint32_t v[8];
-    ZSE_TMEM_LD_X8(v, tmem + lane_addr + (2 * r) * 64 + gr * 8);
-    tc_wait_ld();
+    float v[8];
+    dec_load_acc8(tmem, lane_addr, r, gr, lane0, lane1, v);
     const uint32_t local = smem_u32(recv + ((((seg * 2 + r) * go_max + j) * 8) * 128 + row));
     uint32_t remote;
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(remote) : "r"(local), "r"(owner));
 #pragma unroll
     for (int i = 0; i < 8; ++i)
-      asm volatile("st.shared::cluster.b32 [%0], %1;" ::"r"(remote + i * 512), "r"(v[i]) : "memory");
+      asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(remote + i * 512), "f"(v[i]) : "memory");
   }
 }
 
@@ -555,8 +588,8 @@ gemm_w4_dec_kernel(const __grid_constant__ CUtensorMap tmap_x, const DecArgs a) 
   long long* tacc = nullptr;
 #endif
   // The next kernel of the stream may start its own set-up now; this kernel in turn starts before the one ahead of it
-  // has finished: set-up, the weight stream and the dequantisation (constant data) run at once, the activation
-  // producer and the epilogue wait for the producer of the activations (pdl_wait below).
+  // has finished: set-up, the first ring-full of weights and their dequantisation (constant data) run at once, the
+  // activation loads and the epilogue wait for the producer of the activations (pdl_wait below).
   pdl_launch_dependents();
   const int cta = blockIdx.x, n_cta = gridDim.x;
   const int ks = a.k_stages;
@@ -567,11 +600,8 @@ gemm_w4_dec_kernel(const __grid_constant__ CUtensorMap tmap_x, const DecArgs a) 
   // the last pair of an odd tile count has one tile: pipeline 1 has nothing to do from `single_from` on
   const int single_from = (a.n_tiles & 1) ? (a.n_pairs - 1) * ks : a.total_steps;
   const int n_real1 = max(0, min(g1, single_from) - g0);        // steps of this CTA in which pipeline 1 has a chunk
-  // first step of the CTA's last tile pair (the pair whose epilogue all worker warps share)
-  const int last_begin = max(0, ((g1 - 1) / ks) * ks - g0);
 
-  int w_issued0 = 0, w_issued1 = 0;                             // weight producer: chunks issued before the barrier
-  if (threadIdx.x == 0) {
+  if (threadIdx.x == kDecProducerWarp * 32) {
     for (int p = 0; p < 2; ++p) {
       for (int i = 0; i < SW; ++i) {
         mbar_init(&bars->w_full[p][i], 1);
@@ -596,12 +626,10 @@ gemm_w4_dec_kernel(const __grid_constant__ CUtensorMap tmap_x, const DecArgs a) 
       const uint8_t* src = a.w + (size_t(2 * pair) * ks + k) * kW4ChunkBytes;
       mbar_arrive_expect_tx(&bars->w_full[0][s], kW4ChunkBytes);
       bulk_g2s(w_ring + s * kW4ChunkBytes, src, kW4ChunkBytes, &bars->w_full[0][s]);
-      ++w_issued0;
       if (s < n_real1) {
         mbar_arrive_expect_tx(&bars->w_full[1][s], kW4ChunkBytes);
         bulk_g2s(w_ring + (SW + s) * kW4ChunkBytes, src + size_t(ks) * kW4ChunkBytes, kW4ChunkBytes,
                  &bars->w_full[1][s]);
-        ++w_issued1;
       }
       if (++k == ks) {
         k = 0;
@@ -610,11 +638,11 @@ gemm_w4_dec_kernel(const __grid_constant__ CUtensorMap tmap_x, const DecArgs a) 
     }
     prefetch_tmap(&tmap_x);
   }
-  if (warp == 2) {
+  if (warp == 0) {
     tmem_alloc(&bars->tmem_base, 512);
     tmem_relinquish();
   }
-  if (threadIdx.x == 96) {
+  if (threadIdx.x == 32) {
     // the start-address field counts 16-byte units: a K step of 16 halfs is +2, the second 64-wide K sub-tile of a
     // stage is +kXBytes/16
     const uint64_t desc0 = make_desc_sw128(smem_u32(x_ring));
@@ -628,41 +656,126 @@ gemm_w4_dec_kernel(const __grid_constant__ CUtensorMap tmap_x, const DecArgs a) 
   tc_fence_after_sync();
   const uint32_t tmem = bars->tmem_base;
   volatile int* abort_flag = &bars->abort_flag;
-  // TMEM columns: accumulator (pipeline p, buffer b) at (2p + b) * 64; operand slot (pipeline p, slot s) at
-  // 256 + (2p + s) * 64 (a dequantised 128 x 128 fp16 chunk = 64 columns of 32 bits)
+  // TMEM columns: accumulator of lane (pipeline p, parity s) at (2p + s) * 64; its operand slot at 256 + (2p + s) * 64
+  // (a dequantised 128 x 128 fp16 chunk = 64 columns of 32 bits)
 
   bool split_ok = false;
-  if (warp == 0) {
-    // ------------------------------------------------------------------ weight producer (both rings)
+  if (warp < 4) {
+    // ------------------------------------------------------------------ MMA issuer of lane (p, sub)
+    // steps sub, sub + 2, ... of the CTA; waits are polled without the suspend hint (its wake-up is on the critical
+    // path); every index is carried along, nothing is divided
+    const int p = warp >> 1, sub = warp & 1;
     if (lane == 0) {
-      int cnt0 = w_issued0, cnt1 = w_issued1;
-      int slot = 0;                               // both rings advance together while pipeline 1 has chunks
-      uint32_t ph = 0;                            // parity of the completion of w_empty that frees `slot` now
-      int pair = pair0, k = k_first + cnt0;
+      constexpr uint32_t idesc = make_idesc_f16(kTileN, NT);
+      const uint32_t acc = tmem + (2 * p + sub) * 64;
+      uint32_t at[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) at[j] = tmem + 256 + (2 * p + sub) * 64 + j * 8;
+      const int my_steps = p == 0 ? n_steps : n_real1;
+      int k = k_first + sub, item = 0, cur_item = -1, uses = 0;
       while (k >= ks) {
         k -= ks;
-        ++pair;
+        ++item;
       }
-      for (int s = cnt0; s < n_steps; ++s) {
-        if (!mbar_wait(&bars->w_empty[0][slot], ph, abort_flag, a.status, 1, s)) break;
-        const uint8_t* src = a.w + (size_t(2 * pair) * ks + k) * kW4ChunkBytes;
-        mbar_arrive_expect_tx(&bars->w_full[0][slot], kW4ChunkBytes);
-        bulk_g2s(w_ring + slot * kW4ChunkBytes, src, kW4ChunkBytes, &bars->w_full[0][slot]);
-        ++cnt0;
-        if (s < n_real1) {
-          if (!mbar_wait(&bars->w_empty[1][slot], ph, abort_flag, a.status, 1, s)) break;
-          mbar_arrive_expect_tx(&bars->w_full[1][slot], kW4ChunkBytes);
-          bulk_g2s(w_ring + (SW + slot) * kW4ChunkBytes, src + size_t(ks) * kW4ChunkBytes, kW4ChunkBytes,
-                   &bars->w_full[1][slot]);
-          ++cnt1;
+      int st = sub % SX;
+      uint32_t xph = 0, aph = 0;
+      int s = sub;
+      for (; s < my_steps; s += 2) {
+        DTICK(tx);
+        if (!mbar_wait_spin(&bars->x_full[st], xph, abort_flag, a.status, 3, s)) break;
+        DACC(0, tx);
+        const bool first = item != cur_item;             // this lane's first chunk of a tile pair
+        if (first) {
+          if (uses > 0 && !mbar_wait_spin(&bars->acc_empty[p][sub], (uses - 1) & 1, abort_flag, a.status, 4, item))
+            break;
+          cur_item = item;
         }
-        if (++k == ks) {
-          k = 0;
-          ++pair;
+        DTICK(ta);
+        if (!mbar_wait_spin(&bars->a_ready[p][sub], aph, abort_flag, a.status, 5, s)) break;
+        DACC(1, ta);
+        DTICK(ti);
+        aph ^= 1;
+        tc_fence_after_sync();
+        dec_mma_chunk(acc, at, bars->bdesc[st], idesc, first ? 0u : 1u);
+        tc_commit(&bars->slot_free[p][sub]);
+        if (k + 2 >= ks || s + 2 >= n_steps) {             // this lane's last chunk of the pair
+          tc_commit(&bars->acc_full[p][sub]);
+          ++uses;
         }
-        if (++slot == SW) {
-          slot = 0;
-          ph ^= 1;
+        DACC(2, ti);
+        k += 2;
+        while (k >= ks) {
+          k -= ks;
+          ++item;
+        }
+        st += 2;
+        if (st >= SX) {
+          st -= SX;
+          xph ^= 1;
+        }
+      }
+      // no second tile in the rest of the range (pipeline 1 only): hand the stages back
+      if (!*abort_flag) {
+        for (; s < n_steps; s += 2) {
+          if (!mbar_wait_spin(&bars->x_full[st], xph, abort_flag, a.status, 3, s)) break;
+          mbar_arrive(&bars->x_empty[st]);
+          st += 2;
+          if (st >= SX) {
+            st -= SX;
+            xph ^= 1;
+          }
+        }
+      }
+#ifdef ZSE_DEC_TIMING
+      tacc[3] = clock64() - t_entry;
+#endif
+    }
+  } else if (warp == kDecProducerWarp) {
+    // ------------------------------------------------------------------ producer: activations, weights
+    if (lane == 0) {
+      int x_issued = 0, cnt0 = min(n_steps, SW), cnt1 = min(n_real1, SW);
+      int st = 0, wslot = 0, k = k_first;
+      uint32_t xph = 1, wph = 0;        // xph flips to 0 when the activation ring wraps for the first time
+      int pair_w = pair0, k_w = k_first + cnt0;         // position of weight step s + SW
+      while (k_w >= ks) {
+        k_w -= ks;
+        ++pair_w;
+      }
+      pdl_wait();                                          // the activations come from the previous kernel
+      for (int s = 0; s < n_steps; ++s) {
+        if (s >= SX && !mbar_wait(&bars->x_empty[st], xph, abort_flag, a.status, 2, s)) break;
+        mbar_arrive_expect_tx(&bars->x_full[st], Cfg::kXStage);
+        tma_load_2d(x_ring + st * Cfg::kXStage, &tmap_x, k * kW4StageK, 0, &bars->x_full[st]);
+        tma_load_2d(x_ring + st * Cfg::kXStage + Cfg::kXBytes, &tmap_x, k * kW4StageK + 64, 0, &bars->x_full[st]);
+        x_issued = s + 1;
+        if (++k == ks) k = 0;
+        if (++st == SX) {
+          st = 0;
+          xph ^= 1;
+        }
+        // weights of step s + SW go into the slots that the chunks of step s leave
+        const int sw = s + SW;
+        if (sw < n_steps) {
+          if (!mbar_wait(&bars->w_empty[0][wslot], wph, abort_flag, a.status, 1, sw)) break;
+          const uint8_t* src = a.w + (size_t(2 * pair_w) * ks + k_w) * kW4ChunkBytes;
+          mbar_arrive_expect_tx(&bars->w_full[0][wslot], kW4ChunkBytes);
+          bulk_g2s(w_ring + wslot * kW4ChunkBytes, src, kW4ChunkBytes, &bars->w_full[0][wslot]);
+          ++cnt0;
+          if (sw < n_real1) {
+            if (!mbar_wait(&bars->w_empty[1][wslot], wph, abort_flag, a.status, 1, sw)) break;
+            mbar_arrive_expect_tx(&bars->w_full[1][wslot], kW4ChunkBytes);
+            bulk_g2s(w_ring + (SW + wslot) * kW4ChunkBytes, src + size_t(ks) * kW4ChunkBytes, kW4ChunkBytes,
+                     &bars->w_full[1][wslot]);
+            ++cnt1;
+          }
+          if (++k_w == ks) {
+            k_w = 0;
+            ++pair_w;
+          }
+          if (++wslot == SW) {
+            wslot = 0;
+            wph ^= 1;
+          }
         }
       }
       if (*abort_flag) {                       // every issued copy must land before the CTA may exit
@@ -674,114 +787,26 @@ gemm_w4_dec_kernel(const __grid_constant__ CUtensorMap tmap_x, const DecArgs a) 
             }
           }
         }
-      }
-    }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------------ activation producer
-    if (lane == 0) {
-      int issued = 0, st = 0, k = k_first;
-      uint32_t ph = 1;                                     // flips to 0 when the ring wraps for the first time
-      pdl_wait();                                          // the activations come from the previous kernel
-      for (int s = 0; s < n_steps; ++s) {
-        if (s >= SX && !mbar_wait(&bars->x_empty[st], ph, abort_flag, a.status, 2, s)) break;
-        mbar_arrive_expect_tx(&bars->x_full[st], Cfg::kXStage);
-        tma_load_2d(x_ring + st * Cfg::kXStage, &tmap_x, k * kW4StageK, 0, &bars->x_full[st]);
-        tma_load_2d(x_ring + st * Cfg::kXStage + Cfg::kXBytes, &tmap_x, k * kW4StageK + 64, 0, &bars->x_full[st]);
-        issued = s + 1;
-        if (++k == ks) k = 0;
-        if (++st == SX) {
-          st = 0;
-          ph ^= 1;
-        }
-      }
-      if (*abort_flag) {
-        for (int it = max(0, issued - SX); it < issued; ++it) {
+        for (int it = max(0, x_issued - SX); it < x_issued; ++it) {
           const uint64_t t0 = globaltimer_ns();
           while (!mbar_try_wait(&bars->x_full[it % SX], (it / SX) & 1) && globaltimer_ns() - t0 < kWaitLimitNs) {
           }
         }
       }
     }
-  } else if (warp == 2 || warp == 3) {
-    // ------------------------------------------------------------------ MMA issuer of pipeline p
-    // Kept to as few instructions per step as possible: every index is carried along, nothing is divided.
-    const int p = warp - 2;
-    if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc_f16(kTileN, NT);
-      const uint32_t a_slot0 = tmem + 256 + (2 * p) * 64, acc0 = tmem + (2 * p) * 64;
-      uint32_t at0[8], at1[8];                             // operand slices of slot 0 / slot 1
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        at0[j] = a_slot0 + j * 8;
-        at1[j] = a_slot0 + 64 + j * 8;
-      }
-      const int my_steps = p == 0 ? n_steps : n_real1;
-      int k = k_first, st = 0, item = 0;
-      uint32_t xph = 0, aph = 0;
-      uint32_t first = 1;
-      int s = 0;
-      // two chunks per trip: slot 0, then slot 1
-      while (s < my_steps) {
-#pragma unroll
-        for (int sub = 0; sub < 2; ++sub) {
-          if (s >= my_steps) break;
-          DTICK(tx);
-          if (!mbar_wait_spin(&bars->x_full[st], xph, abort_flag, a.status, 3, s)) goto issuer_done;
-          DACC(0, tx);
-          const uint32_t b = item & 1;
-          if (first && item >= 2 &&
-              !mbar_wait_spin(&bars->acc_empty[p][b], ((item >> 1) - 1) & 1, abort_flag, a.status, 4, item))
-            goto issuer_done;
-          DTICK(ta);
-          if (!mbar_wait_spin(&bars->a_ready[p][sub], aph, abort_flag, a.status, 5, s)) goto issuer_done;
-          DACC(1, ta);
-          DTICK(ti);
-          tc_fence_after_sync();
-          dec_mma_chunk(acc0 + b * 64, sub == 0 ? at0 : at1, bars->bdesc[st], idesc, first ^ 1u);
-          tc_commit(&bars->slot_free[p][sub]);
-          DACC(2, ti);
-          first = 0;
-          if (++k == ks || s == n_steps - 1) {
-            tc_commit(&bars->acc_full[p][b]);
-            k = 0;
-            ++item;
-            first = 1;
-          }
-          if (++st == SX) {
-            st = 0;
-            xph ^= 1;
-          }
-          ++s;
-        }
-        aph ^= 1;
-      }
-    issuer_done:
-      // no second tile in the rest of the range (pipeline 1 only): hand the stages back
-      for (; s < n_steps; ++s) {
-        if (!mbar_wait_spin(&bars->x_full[st], xph, abort_flag, a.status, 3, s)) break;
-        mbar_arrive(&bars->x_empty[st]);
-        if (++st == SX) {
-          st = 0;
-          xph ^= 1;
-        }
-      }
-#ifdef ZSE_DEC_TIMING
-      tacc[3] = clock64() - t_entry;
-#endif
-    }
   } else {
     const int q = warp & 3;
     if (warp < kDecEpiWarp0) {
       // ---------------------------------------------------------------- dequant: chunk -> fp16 -> TMEM slot
-      // group = (pipeline p, slot sub): chunks sub, sub+2, ... of pipeline p.  A thread owns one weight row of the
-      // chunk: 128 nibbles in, 64 half2 out, written as two 32-column TMEM stores.  Chunk c of a pipeline belongs to
-      // step c of the CTA (pipeline 1 only runs out earlier when the last pair has a single tile).
-      const int grp = (warp - 4) >> 2, p = grp >> 1, sub = grp & 1;
+      // group = lane (pipeline p, parity sub): chunks sub, sub+2, ... of pipeline p.  A thread owns one weight row of
+      // the chunk: 128 nibbles in, 64 half2 out, written as two 32-column TMEM stores.  Chunk c of a pipeline belongs
+      // to step c of the CTA (pipeline 1 only runs out earlier when the last pair has a single tile).
+      const int grp = (warp - kDecDqWarp0) >> 2, p = grp >> 1, sub = grp & 1;
       const int row = q * 32 + lane;
       const int n_chunks = p == 0 ? n_steps : n_real1;
       const uint32_t dst = tmem + (uint32_t(q * 32) << 16) + 256 + (2 * p + sub) * 64;
       int last = -1;
-      int slot = sub, xst = sub;                 // weight-ring slot of chunk c; activation stage of chunk c - 2
+      int slot = sub % SW, xst = sub % SX;       // weight-ring slot of chunk c; activation stage of chunk c - 2
       uint32_t wph = 0, sph = 0;                 // parities: w_full of chunk c, slot_free of chunk c - 2
       for (int c = sub; c < n_chunks; c += 2) {
         DTICK(t0);
@@ -831,8 +856,8 @@ gemm_w4_dec_kernel(const __grid_constant__ CUtensorMap tmap_x, const DecArgs a) 
           wph ^= 1;
         }
       }
-      // hand back the stage of this group's last chunk as well (the activation producer may still need it when the
-      // other pipeline goes on alone)
+      // hand back the stage of this group's last chunk as well (the producer may still need it when the other
+      // pipeline goes on alone)
       if (last >= 0 && !*abort_flag) {
         if (mbar_wait(&bars->slot_free[p][sub], sph, abort_flag, a.status, 8, last)) {
           if (q == 0 && lane == 0) mbar_arrive(&bars->x_empty[xst]);
@@ -842,7 +867,7 @@ gemm_w4_dec_kernel(const __grid_constant__ CUtensorMap tmap_x, const DecArgs a) 
     // ------------------------------------------------------------------ epilogue
     pdl_wait();                     // outputs, workspace and flags may still be in use by the previous kernel
     const bool is_epi = warp >= kDecEpiWarp0;
-    const int wi_wide = is_epi ? 4 : (warp - 4) >> 2;            // index among the five warps of this lane quarter
+    const int wi_wide = is_epi ? 4 : (warp - kDecDqWarp0) >> 2;  // index among the five warps of this lane quarter
 #ifdef ZSE_DEC_TIMING
     long long tdummy[8];
     long long* tepi = is_epi ? tacc : tdummy;
@@ -854,41 +879,41 @@ gemm_w4_dec_kernel(const __grid_constant__ CUtensorMap tmap_x, const DecArgs a) 
       // threads of the CTA meet at the cluster barriers)
       bool alive = !*abort_flag;
       const int ntp = g0 < single_from ? 2 : 1;
-      for (int r = 0; r < ntp && alive; ++r) alive = mbar_wait(&bars->acc_full[r][0], 0, abort_flag, a.status, 9, r);
+      for (int r = 0; r < ntp && alive; ++r) {
+        alive = mbar_wait(&bars->acc_full[r][0], 0, abort_flag, a.status, 9, r);
+        if (alive && n_steps > 1) alive = mbar_wait(&bars->acc_full[r][1], 0, abort_flag, a.status, 9, 2 + r);
+      }
       split_ok = epi_all(alive, 1);
       tc_fence_after_sync();
 #ifdef ZSE_DEC_TIMING
       tacc[0] = clock64() - t_entry;
 #endif
     } else {
-      // stream plan: the four epilogue warps take the tile pairs one after the other while the pipelines run ahead
-      // (accumulators are double-buffered).  The CTA's last pair is shared by all twenty worker warps: nothing is
-      // left to overlap it with, and the idle activation ring serves as the second staging buffer.
+      // stream plan: the four epilogue warps take the tile pairs one after the other.  The lanes of the next pair run
+      // on as soon as the accumulators are out of TMEM.  The CTA's last pair is shared by all twenty worker warps:
+      // nothing is left to overlap it with, and the idle activation ring serves as the second staging buffer.
       const uint32_t epoch1 = ld_acquire_gpu_u32(a.sync) + 1u;
-      int s = 0, item = 0, pair = pair0, ka = k_first;
+      int s = 0, pair = pair0, ka = k_first;
+      uint32_t use0 = 0, use1 = 0;                          // tile pairs the even / odd lanes took part in so far
       bool ok = true;
       while (s < n_steps) {
         const int len = min(ks - ka, n_steps - s);
         const int ntp = g0 + s < single_from ? 2 : 1;
         const bool last_item = s + len == n_steps;
+        const bool lane0 = len >= 2 || (s & 1) == 0, lane1 = len >= 2 || (s & 1) == 1;
         // all twenty warps call the last item (it begins with a vote of all of them), also after a failure
         if (last_item)
           ok = dec_epilogue_item<NT, EPI>(a, bars, stage, reinterpret_cast<float*>(x_ring), tmem, cta, n_cta, pair, ka,
-                                          len, ntp, item & 1, item, epoch1, q, lane, wi_wide, 5, ok, tepi);
+                                          len, ntp, lane0, lane1, use0 & 1, use1 & 1, false, epoch1, q, lane, wi_wide, 5,
+                                          ok, tepi);
         else if (is_epi && ok)
-          ok = dec_epilogue_item<NT, EPI>(a, bars, stage, stage, tmem, cta, n_cta, pair, ka, len, ntp, item & 1, item,
-                                          epoch1, q, lane, 0, 1, ok, tepi);
-        if (is_epi && !last_item && ok) {
-          // the accumulators of this item are read: the pipelines may overwrite them (item + 2)
-          tc_fence_before_sync();
-          __syncwarp();
-          if (lane == 0)
-            for (int r = 0; r < ntp; ++r) mbar_arrive(&bars->acc_empty[r][item & 1]);
-        }
+          ok = dec_epilogue_item<NT, EPI>(a, bars, stage, stage, tmem, cta, n_cta, pair, ka, len, ntp, lane0, lane1,
+                                          use0 & 1, use1 & 1, true, epoch1, q, lane, 0, 1, ok, tepi);
+        use0 += lane0 ? 1 : 0;
+        use1 += lane1 ? 1 : 0;
         s += len;
         ka = 0;
         ++pair;
-        ++item;
       }
     }
   }
@@ -899,12 +924,13 @@ gemm_w4_dec_kernel(const __grid_constant__ CUtensorMap tmap_x, const DecArgs a) 
     const int S = a.split, seg = int(dec_cluster_rank()), ntp = g0 < single_from ? 2 : 1;
     const int go_max = (Cfg::kGranules + S - 1) / S;
     float* recv = reinterpret_cast<float*>(x_ring);      // [S][2][go_max][8][128] fp32 over the idle rings
-    const int wi = warp >= kDecEpiWarp0 ? 4 : (warp - 4) >> 2;
+    const int wi = warp >= kDecEpiWarp0 ? 4 : (warp - kDecDqWarp0) >> 2;
     cluster_sync_all_threads();
 #ifdef ZSE_DEC_TIMING
     if (warp >= kDecEpiWarp0) tacc[1] = clock64() - t_entry;
 #endif
-    if (warp >= 4 && split_ok) dec_split_push<NT>(recv, tmem, ntp, seg, S, go_max, warp & 3, lane, wi);
+    if (warp >= kDecDqWarp0 && split_ok)
+      dec_split_push<NT>(recv, tmem, ntp, true, n_steps > 1, seg, S, go_max, warp & 3, lane, wi);
     __syncwarp();
 #ifdef ZSE_DEC_TIMING
     if (warp >= kDecEpiWarp0) tacc[2] = clock64() - t_entry;
@@ -913,7 +939,7 @@ gemm_w4_dec_kernel(const __grid_constant__ CUtensorMap tmap_x, const DecArgs a) 
 #ifdef ZSE_DEC_TIMING
     if (warp >= kDecEpiWarp0) tacc[3] = clock64() - t_entry;
 #endif
-    if (warp >= 4 && split_ok)
+    if (warp >= kDecDqWarp0 && split_ok)
       dec_split_finish<NT, EPI>(a, recv, pair0, ntp, seg, S, go_max, wi * 128 + (warp & 3) * 32 + lane);
 #ifdef ZSE_DEC_TIMING
     if (warp >= kDecEpiWarp0) tacc[4] = clock64() - t_entry;
@@ -929,7 +955,7 @@ gemm_w4_dec_kernel(const __grid_constant__ CUtensorMap tmap_x, const DecArgs a) 
 #endif
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 2) tmem_dealloc(tmem, 512);
+  if (warp == 0) tmem_dealloc(tmem, 512);
   if (a.split == 0 && threadIdx.x == kDecEpiWarp0 * 32) {
     // the last CTA to leave moves the launch epoch on (every CTA read it after its pdl_wait, i.e. long ago)
     __threadfence();

@@ -104,7 +104,15 @@ extern "C" int zse_step_forward(const ZseStepModel* m, const ZseStepBuffers* b, 
     const ZseStepLayer& L = m->layers[li];
     void* kv_layer = static_cast<char*>(kv) + size_t(li) * size_t(kv_layer_stride) * 2;
     p.add_norm(planes, L.ln1);
-    if (M <= b->qkv_plane_rows && L.qkv.kind == ZSE_STEP_W4) {
+    if ((m->dec_mode & 2) && b->dec_ws != nullptr && m->rope_table != nullptr && L.qkv.kind == ZSE_STEP_W4 && M <= 64 &&
+        hd == 128 && m->rotary_dim == 128 &&
+        zse_gemm_w4_dec_supported(M, L.qkv.N, L.qkv.K, 3)) {
+      // decode-sized pass: projection, bias, RoPE and the cache write in one kernel
+      if (p.ok())
+        p.did(zse_gemm_w4_dec_qkv_rope(L.qkv.data, b->xnorm, b->max_tokens, L.qkv.bias, b->qkv, qkv_ld, M, L.qkv.K, nh,
+                                       nkv, kv_layer, block_size, b->positions, b->slots, m->rope_table,
+                                       m->max_position, b->dec_ws, b->status, stream));
+    } else if (M <= b->qkv_plane_rows && L.qkv.kind == ZSE_STEP_W4) {
       const int n_q = p.linear_partial(L.qkv, b->xnorm, b->qkv_planes, b->qkv_max_planes, b->max_tokens);
       if (p.ok())
         p.did(zse_rope_kv_write(b->qkv, kv_layer, b->positions, b->slots, m->inv_freq, M, nh, nkv, hd, m->rotary_dim,
@@ -126,7 +134,11 @@ extern "C" int zse_step_forward(const ZseStepModel* m, const ZseStepBuffers* b, 
     planes = p.linear_partial(L.o, b->attn_out, b->partials, b->max_planes, b->max_tokens);
     p.add_norm(planes, L.ln2);
     if (!p.ok()) break;
-    if (L.gate_up.kind == ZSE_STEP_W4) {
+    if (L.gate_up.kind == ZSE_STEP_W4 && (m->dec_mode & 1) && b->dec_ws != nullptr && M <= 64 && m->inter % 8 == 0 &&
+        zse_gemm_w4_dec_supported(M, L.gate_up.N, L.gate_up.K, kEpiSwiGLU)) {
+      p.did(zse_gemm_w4_dec(L.gate_up.data, b->xnorm, b->max_tokens, nullptr, b->act, M, L.gate_up.N, L.gate_up.K,
+                            m->inter, kEpiSwiGLU, b->dec_ws, b->status, stream));
+    } else if (L.gate_up.kind == ZSE_STEP_W4) {
       p.did(zse_gemm_w4(L.gate_up.data, b->xnorm, b->max_tokens, nullptr, b->act, M, L.gate_up.N, L.gate_up.K,
                         m->inter, kEpiSwiGLU, 0, b->status, stream));
     } else {

@@ -8,7 +8,8 @@ chunked prefill, speculative verification (``mode="prefill"``: causal attention 
 
 Launch sequence per layer (tp = 1): add+RMSNorm -> fused QKV GEMM (+bias) -> RoPE + KV write -> attention ->
 o_proj (split-K fp32 partials) -> add+RMSNorm (reduces the partials into the fp32 residual) -> gate/up GEMM with
-SwiGLU epilogue -> down_proj (split-K partials).  That is 8 launches where the reference issues about 18
+SwiGLU epilogue -> down_proj (split-K partials).  Decode-sized passes (<= 64 tokens, head_dim 128) do QKV, bias,
+RoPE and the cache write in ONE kernel.  That is 7-8 launches where the reference issues about 18
 (zse-engine/zse_engine/orchestrator/model_runner.py:1299-1474), with an fp32 residual stream like the reference.
 """
 from __future__ import annotations
@@ -237,6 +238,13 @@ class DecoderModel:
         if c.partial_rotary_factor and not c.is_gemma:       # the leading part of each head rotates, the rest passes
             rot = 2 * int(c.partial_rotary_factor * c.head_dim // 2)
         self.inv_freq = ref.inv_freq(rot, c.rope_theta, c.rope_scaling).to(dev)
+        # cos / sin of every (position, frequency) for the fused QKV epilogue of decode-sized passes (head_dim 128, full
+        # rotary): [max_seq_len, 64, 2] fp32, computed once with the same fp32 arithmetic as the oracle
+        self.rope_table = None
+        if dev.type == "cuda" and c.head_dim == 128 and rot == 128 and not c.is_gemma:
+            pos = torch.arange(max(int(c.max_seq_len), 1), dtype=torch.float32, device=dev)
+            ang = pos[:, None] * self.inv_freq[None, :]
+            self.rope_table = torch.stack([torch.cos(ang), torch.sin(ang)], dim=-1).contiguous()
 
     # ---- buffers --------------------------------------------------------------------------------------
     def make_buffers(self, max_tokens: int, max_seqs: int, max_blocks: int, logits_rows: Optional[int] = None,
@@ -293,7 +301,11 @@ class DecoderModel:
         lora = self.lora
         for li, L in enumerate(self.layers):
             self._add_norm(b, planes, L.ln1, M, add)
-            if self.lora is None and M <= b.qkv_plane_rows and L.qkv.kind == "w4t":
+            if (self.lora is None and self.rope_table is not None
+                    and ops.qkv_rope_fused_ok(L.qkv, M, c.head_dim, kv[li])):
+                ops.qkv_rope_fused(L.qkv, b.xnorm, M, b.qkv, kv[li], b.positions, b.slots, self.rope_table,
+                                   p.num_heads, p.num_kv_heads, bs)
+            elif self.lora is None and M <= b.qkv_plane_rows and L.qkv.kind == "w4t":
                 n_q = ops.linear_partial(L.qkv, b.xnorm, M, b.qkv_planes)
                 ops.rope_kv_write(b.qkv, kv[li], b.positions, b.slots, self.inv_freq, M, p.num_heads, p.num_kv_heads,
                                   c.head_dim, bs, planes=b.qkv_planes, n_planes=n_q, bias=L.qkv.bias)

@@ -91,6 +91,10 @@ class TorchOps:
         if out is not None:
             out[:M] = ref.rmsnorm(residual[:M], weight, eps)
 
+    def qkv_rope_fused_ok(self, w: LinearWeight, M: int, hd: int, kv_layer) -> bool:
+        """Whether ``qkv_rope_fused`` takes this pass (the torch implementation never does: it has the unfused ops)."""
+        return False
+
     def rope_kv_write(self, qkv, kv_layer, positions, slots, inv_freq, M, nh, nkv, hd, block_size, planes=None,
                       n_planes=0, bias=None):
         if planes is not None:
@@ -187,6 +191,17 @@ class CudaOps(TorchOps):
         self.device = torch.device(device)
         self.status = native.Status(self.device)
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
+        # decode-sized passes (<= 64 tokens) of the INT4 layers: bit 0 = gate/up + SwiGLU, bit 1 = fused QKV + bias +
+        # RoPE + KV-cache write, bit 2 = every other INT4 linear, through the persistent kernel (csrc/gemm_w4_dec.cu)
+        from ..utils import env
+        self.dec_mode = env.integer("ZSE_W4_DEC")
+        self._dec_ws = None
+
+    @property
+    def dec_ws(self) -> torch.Tensor:
+        if self._dec_ws is None:
+            self._dec_ws = self.n.gemm_w4_dec_workspace(self.device, self.sm_count)
+        return self._dec_ws
 
     def check(self):
         self.status.check()
@@ -221,14 +236,22 @@ class CudaOps(TorchOps):
     # ---- ops ------------------------------------------------------------------------------------------
     def linear(self, w, x, M, out, x_cap=None):
         cap = x.shape[0] if x_cap is None else x_cap
-        if w.kind == "w4t":
+        if (w.kind == "w4t" and (self.dec_mode & 4) and M <= 64 and out.stride(0) % 8 == 0
+                and self.n.gemm_w4_dec_supported(M, w.N, w.K, EPI_F16)):
+            self.n.gemm_w4_dec(w.data, x, cap, w.bias, out, M, w.N, w.K, out.stride(0), EPI_F16, self.dec_ws,
+                               self.status.ptr)
+        elif w.kind == "w4t":
             self.n.gemm_w4(w.data, x, cap, w.bias, out, M, w.N, w.K, out.stride(0), EPI_F16, 0, self.status.ptr)
         else:
             self.n.gemm_f16(w.data, w.N, x, cap, w.bias, out, M, w.N, w.K, out.stride(0), EPI_F16, 1, self.status.ptr)
 
     def linear_swiglu(self, w, x, M, out, x_cap=None, gelu=False, tmp=None):
         cap = x.shape[0] if x_cap is None else x_cap
-        if w.kind == "w4t" and not gelu:
+        if (w.kind == "w4t" and not gelu and (self.dec_mode & 1) and M <= 64 and out.stride(0) % 8 == 0
+                and self.n.gemm_w4_dec_supported(M, w.N, w.K, EPI_SWIGLU)):
+            self.n.gemm_w4_dec(w.data, x, cap, None, out, M, w.N, w.K, out.stride(0), EPI_SWIGLU, self.dec_ws,
+                               self.status.ptr)
+        elif w.kind == "w4t" and not gelu:
             self.n.gemm_w4(w.data, x, cap, None, out, M, w.N, w.K, out.stride(0), EPI_SWIGLU, 0, self.status.ptr)
         else:
             if w.kind == "w4t":
@@ -276,6 +299,17 @@ class CudaOps(TorchOps):
                       n_planes=0, bias=None):
         self.n.rope_kv_write(qkv, kv_layer, positions, slots, inv_freq, M, nh, nkv, hd, inv_freq.numel() * 2,
                              block_size, planes, n_planes, bias)
+
+    def qkv_rope_fused_ok(self, w, M, hd, kv_layer) -> bool:
+        return bool((self.dec_mode & 2) and w.kind == "w4t" and M <= 64 and hd == 128 and kv_layer.is_contiguous()
+                    and self.n.gemm_w4_dec_supported(M, w.N, w.K, 3))
+
+    def qkv_rope_fused(self, w, x, M, qkv, kv_layer, positions, slots, cos_sin, nh, nkv, block_size, x_cap=None):
+        """One kernel: fused QKV projection + bias + rotate-half RoPE + K/V rows into the paged cache; ``qkv`` gets
+        the rotated q heads.  head_dim 128, full rotary, ``cos_sin`` [max_position, 64, 2] fp32."""
+        cap = x.shape[0] if x_cap is None else x_cap
+        self.n.gemm_w4_dec_qkv_rope(w.data, x, cap, w.bias, qkv, qkv.stride(0), M, w.K, nh, nkv, kv_layer, block_size,
+                                    positions, slots, cos_sin, cos_sin.shape[0], self.dec_ws, self.status.ptr)
 
     @staticmethod
     def _tensor_core_attention(kv_layer, hd, nh, nkv, block_size) -> bool:

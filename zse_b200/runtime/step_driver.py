@@ -37,7 +37,8 @@ class _Model(Structure):
                                        "vocab_rows", "rotary_dim", "sm_count", "reserved")] + \
                [(n, c_float) for n in ("eps", "scale", "embed_scale", "reserved_f")] + \
                [("embed", c_void_p), ("final_norm", c_void_p), ("inv_freq", c_void_p), ("lm_head", _Linear),
-                ("layers", POINTER(_Layer))]
+                ("layers", POINTER(_Layer)), ("rope_table", c_void_p), ("max_position", c_int32),
+                ("dec_mode", c_int32)]
 
 
 class _Buffers(Structure):
@@ -45,7 +46,8 @@ class _Buffers(Structure):
                                        "logits_rows_cap", "logits_ld", "reserved")] + \
                [(n, c_void_p) for n in ("ids", "positions", "slots", "block_tables", "seq_lens", "cu_q", "q_pos0",
                                         "logit_rows", "residual", "xnorm", "qkv", "attn_out", "qkv_planes", "act",
-                                        "gate_up_tmp", "partials", "xsel", "logits", "attn_scratch", "status")]
+                                        "gate_up_tmp", "partials", "xsel", "logits", "attn_scratch", "status",
+                                        "dec_ws")]
 
 
 def _linear(w) -> _Linear:
@@ -80,7 +82,10 @@ class NativeStep:
             head_dim=c.head_dim, inter=p.inter_size, vocab_rows=model.embed.shape[0],
             rotary_dim=model.inv_freq.numel() * 2, sm_count=model.ops.sm_count, eps=c.rms_norm_eps, scale=model.scale,
             embed_scale=model.embed_scale, embed=model.embed.data_ptr(), final_norm=model.norm.data_ptr(),
-            inv_freq=model.inv_freq.data_ptr(), lm_head=_linear(model.lm_head), layers=self._layers)
+            inv_freq=model.inv_freq.data_ptr(), lm_head=_linear(model.lm_head), layers=self._layers,
+            rope_table=None if model.rope_table is None else model.rope_table.data_ptr(),
+            max_position=0 if model.rope_table is None else model.rope_table.shape[0],
+            dec_mode=int(getattr(model.ops, "dec_mode", 0)))
         dense_gate_up = any(L.gate_up.kind != "w4t" for L in model.layers)
         self._gate_up_tmp = (torch.empty(b.max_tokens, 2 * p.inter_size, dtype=torch.float16, device=model.device)
                              if dense_gate_up else None)
@@ -93,7 +98,7 @@ class NativeStep:
             logit_rows=ptr(b.logit_rows), residual=ptr(b.residual), xnorm=ptr(b.xnorm), qkv=ptr(b.qkv),
             attn_out=ptr(b.attn_out), qkv_planes=ptr(b.qkv_planes), act=ptr(b.act), gate_up_tmp=ptr(self._gate_up_tmp),
             partials=ptr(b.partials), xsel=ptr(b.xsel), logits=ptr(b.logits), attn_scratch=ptr(b.attn_scratch),
-            status=model.ops.status.ptr)
+            status=model.ops.status.ptr, dec_ws=model.ops.dec_ws.data_ptr() if model.ops.dec_mode else None)
         self._keep = (model, buffers)            # the structs hold raw pointers into these
         self._launches = c_int(0)
         if not lib.zse_step_supported(byref(self._model), byref(self._buffers)):

@@ -25,6 +25,8 @@ KNOWN: Dict[str, Tuple[str, str]] = {
     "ZSE_TP_NCCL_ROWS": ("256", "passes of at least this many rows take NCCL instead of the fused exchange"),
     "ZSE_TP_SP": ("0", "sequence-parallel prefill on the NCCL path (reduce-scatter / all-gather, residual split by rows)"),
     "ZSE_TP_SP_MIN_ROWS": ("256", "smallest pass that takes the sequence-parallel path"),
+    "ZSE_W4_DEC": ("3", "decode-sized INT4 layers through the persistent kernel: 1 gate/up + SwiGLU, 2 fused QKV + RoPE + "
+                        "cache write, 4 every other INT4 linear (sum of the bits; 0: the tiled kernel everywhere)"),
     "ZSE_PDL": ("1", "programmatic dependent launch between the kernels of a pass (read by the native library)"),
     "ZSE_TP_PDL": ("0", "programmatic dependent launch for the exchange kernels too (read by the native library)"),
     "ZSE_REFERENCE_DIR": ("", "where the tests look for an installed copy of the reference"),
