@@ -12,8 +12,14 @@ tree).  It is not run on the GPU any more:
   for) was run once through the reference's public API (``ZStreamerEngine.add_request`` + ``step``).  The engine
   started, and its first step failed inside the reference's own GPU code with CUDA error 700 (illegal address),
   reported by its next driver call as ``cuStreamCreate failed: 700``.  The record of that call is kept in
-  ``profiles/reference_arm_single_sequence_fault.txt``.  A GPU fault of the reference on inputs that were checked by
-  reading is not provoked a second time on shared GPUs.
+  ``profiles/reference_arm_single_sequence_fault.txt``.  The cause, found by reading afterwards: the logits scratch
+  buffer has ``min(max_seq_len, 64)`` rows (zse-engine/zse_engine/orchestrator/vram_allocator.py:279-296) while
+  prefill launches the lm_head matmul over all ``seq_len`` rows into it (orchestrator/model_runner.py:366-373), so
+  every prompt longer than 64 tokens writes past the buffer.  A prompt of at most 64 tokens stays inside that buffer
+  and inside the 64 x 256-entry decode block table, but the rest of that path (about twenty run-time-compiled kernels
+  with hand-computed launch geometry, a gcc-compiled C launcher for single-sequence decode) has not been audited
+  line by line, and after one recorded fault the reference's GPU code is not run again on shared GPUs without such
+  an audit.
 * ``add_request_tokens`` of the reference cannot be used at all: it stores the prompt as a ``set`` where its own
   ``add_token`` expects a ``dict`` (zstreamer/engine.py:485 vs zstreamer/request.py:164) and raises on the first
   generated token.
@@ -44,5 +50,6 @@ def run(args, model_file, workload, ClockSampler, baseline_tok_s, prompt_range, 
                      "orchestrator/model_runner.py:96-103,879-881")
     else:
         _unavailable("not run again: on B200 the reference's own GPU code raised CUDA error 700 (illegal address) in "
-                     "the first step of a 512-token prompt on the 7B shape (its next driver call reported "
-                     "'cuStreamCreate failed: 700'); record in profiles/reference_arm_single_sequence_fault.txt")
+                     "the first step of a 512-token prompt on the 7B shape (its logits scratch has min(S, 64) rows, "
+                     "vram_allocator.py:279-296, but prefill writes seq_len rows of logits, model_runner.py:366-373); "
+                     "record in profiles/reference_arm_single_sequence_fault.txt")

@@ -5,7 +5,11 @@
 
 Workload: 64 concurrent requests, prompt lengths uniform in [128, 2048] random token ids, 256 output tokens each,
 random-init weights quantised to INT4 group-128, paged fp16 KV cache, tensor parallel over the N GPUs of one node.
-A step is one decode iteration of the whole batch (64 new tokens).  Two numbers are reported:
+A step is one decode iteration of the whole batch (64 new tokens).  ``--workload`` selects the other measured
+configurations: ``single`` (7B shape, one sequence, 512-token prompt: cold start, memory, single-sequence decode),
+``spec32b`` (32B shape, 32 requests with 4096-token prompts of repeating spans, 2048-token prefill chunks, n-gram
+drafts of 4 tokens: accept rate and tok/s) and ``lora72b`` (72B shape, 256 requests, 32 rank-16 adapters on q/v).
+Two numbers are reported:
 
 * ``value``: tokens/s from the device time of K real decode steps (CUDA events around each step's kernels on the
   launching stream, summed; maximum over ranks);
@@ -28,10 +32,22 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 BASELINE_14B_TOK_S = 37.0        # published single-sequence decode, Qwen2.5-14B INT4, A100-80GB (reference README.md:60)
+BASELINE_7B_TOK_S = 48.6         # published single-sequence decode, Qwen2.5-7B INT4, A10G (reference README.md:61)
 MODEL_SHAPE = "qwen2.5-14b"
 NUM_REQUESTS = 64
 PROMPT_RANGE = (128, 2048)
 OUTPUT_TOKENS = 256
+# name -> model shape, requests, prompt rule, output tokens, speculative depth, (adapters, rank)
+WORKLOADS = {
+    "batch64": dict(model="qwen2.5-14b", requests=64, prompt=("uniform",) + PROMPT_RANGE, out=256, spec_k=0, lora=None,
+                    seq_len=f"prompts uniform {PROMPT_RANGE}, 256 output tokens"),
+    "single": dict(model="qwen2.5-7b", requests=1, prompt=("fixed", 512), out=256, spec_k=0, lora=None,
+                   seq_len="512-token prompt, 256 output tokens"),
+    "spec32b": dict(model="qwen2.5-32b", requests=32, prompt=("spans", 4096), out=512, spec_k=4, lora=None,
+                    seq_len="4096-token prompts (8-token spans of a 64-span pool repeat with p = 0.3), 512 output tokens"),
+    "lora72b": dict(model="qwen2.5-72b", requests=256, prompt=("fixed", 1024), out=512, spec_k=0, lora=(32, 16),
+                    seq_len="1024-token prompts, 512 output tokens, 32 rank-16 adapters on q_proj/v_proj"),
+}
 
 
 def parse_args():
@@ -47,13 +63,15 @@ def parse_args():
     ap.add_argument("--no-graphs", action="store_true")
     ap.add_argument("--profile-region", action="store_true",
                     help="bracket the timed steps with cudaProfilerStart/Stop (for `ncu --profile-from-start off`)")
-    ap.add_argument("--workload", default="batch64", choices=["batch64", "single"],
+    ap.add_argument("--workload", default="batch64", choices=sorted(WORKLOADS),
                     help="batch64: 64 requests, prompts uniform in [128, 2048] (the headline); single: one request "
-                         "with a 512-token prompt on the 7B shape (the case the reference publishes)")
+                         "with a 512-token prompt on the 7B shape (the case the reference publishes); spec32b: n-gram "
+                         "speculative decoding on the 32B shape; lora72b: 256 requests over 32 adapters on the 72B shape")
     a = ap.parse_args()
-    if a.workload == "single":
-        a.model = "qwen2.5-7b" if a.model == MODEL_SHAPE else a.model
-        a.requests = 1
+    if a.workload != "batch64":
+        w = WORKLOADS[a.workload]
+        a.model = w["model"] if a.model == MODEL_SHAPE else a.model
+        a.requests = w["requests"] if a.requests == NUM_REQUESTS else a.requests
     return a
 
 
@@ -75,9 +93,20 @@ def model_file(args, rank: int, barrier) -> str:
 
 def workload(n_requests: int, vocab: int, seed: int = 1234, kind: str = "batch64"):
     rng = random.Random(seed)
-    if kind == "single":
-        return [[rng.randrange(vocab) for _ in range(512)] for _ in range(n_requests)]
-    return [[rng.randrange(vocab) for _ in range(rng.randint(*PROMPT_RANGE))] for _ in range(n_requests)]
+    rule = WORKLOADS[kind]["prompt"]
+    if rule[0] == "fixed":
+        return [[rng.randrange(vocab) for _ in range(rule[1])] for _ in range(n_requests)]
+    if rule[0] == "spans":
+        # random token ids in which 8-token spans drawn from a pool of 64 spans repeat with probability 0.3
+        pool = [[rng.randrange(vocab) for _ in range(8)] for _ in range(64)]
+        out = []
+        for _ in range(n_requests):
+            p = []
+            while len(p) < rule[1]:
+                p += rng.choice(pool) if rng.random() < 0.3 else [rng.randrange(vocab) for _ in range(8)]
+            out.append(p[:rule[1]])
+        return out
+    return [[rng.randrange(vocab) for _ in range(rng.randint(rule[1], rule[2]))] for _ in range(n_requests)]
 
 
 class ClockSampler:
@@ -146,10 +175,14 @@ def run_ours(args):
     from zse_b200.sched.request import RequestState
 
     path = model_file(args, rank, barrier)
-    need_tokens = max(OUTPUT_TOKENS, args.steps + args.warmup + 48)
-    cfg = EngineConfig(tp_size=world, device_index=local, max_seq_len=PROMPT_RANGE[1] + need_tokens + 64,
+    wl = WORKLOADS[args.workload]
+    per_step = 1 + wl["spec_k"]                      # most tokens a request can gain in one engine step
+    need_tokens = max(wl["out"], (args.steps + args.warmup) * per_step + 48)
+    longest = wl["prompt"][-1]
+    cfg = EngineConfig(tp_size=world, device_index=local, max_seq_len=longest + need_tokens + 64,
                        max_batch_seqs=max(args.requests, 1), max_batch_tokens=8192, prefill_chunk_size=2048,
                        max_prefill_per_step=16, decode_per_prefill=0, max_queue_size=4 * args.requests,
+                       speculative_k=wl["spec_k"], speculative_mode="ngram",
                        use_cuda_graphs=not args.no_graphs, comm_backend=args.comm or "fused", quiet=rank != 0)
     if world > 1:
         from zse_b200.parallel.comm import make_comm
@@ -160,7 +193,19 @@ def run_ours(args):
     eng = ZStreamerEngine(path, config=cfg, comm=comm, tp_rank=rank)
     cold = time.time() - t0
     prompts = workload(args.requests, eng.model_config.vocab_size, kind=args.workload)
-    rids = [eng.add_request_tokens(p, max_tokens=need_tokens, temperature=0.0, stop_tokens=[]) for p in prompts]
+    lora_ids = [None] * len(prompts)
+    if wl["lora"]:
+        n_adapters, lora_rank = wl["lora"]
+        t_l = time.time()
+        for i in range(n_adapters):          # random N(0, 0.01) matrices on q_proj / v_proj, as the configuration asks
+            eng.lora_manager.load_adapter_random(f"adapter{i}", rank=lora_rank, alpha=2.0 * lora_rank,
+                                                 target_modules=["q_proj", "v_proj"], seed=100 + i, std=0.01)
+        route = random.Random(99)
+        lora_ids = [f"adapter{route.randrange(n_adapters)}" for _ in prompts]
+        if rank == 0:
+            print(f"[bench] {n_adapters} adapters loaded in {time.time() - t_l:.1f}s", file=sys.stderr)
+    rids = [eng.add_request_tokens(p, max_tokens=need_tokens, temperature=0.0, stop_tokens=[], lora_id=a)
+            for p, a in zip(prompts, lora_ids)]
     assert all(r is not None for r in rids)
     # untimed: prefill everything (chunked, packed), interleaved with decode of the sequences already admitted
     t_pf = time.time()
@@ -206,27 +251,51 @@ def run_ours(args):
         t = torch.tensor([dev_ms, t_e2e * 1000.0], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         dev_ms, t_e2e = float(t[0]), float(t[1]) / 1000.0
-    assert n_steps == args.steps and tokens == args.steps * args.requests, (n_steps, tokens)
+    if wl["spec_k"] == 0:
+        assert n_steps == args.steps and tokens == args.steps * args.requests, (n_steps, tokens)
+    else:
+        assert tokens >= args.steps * args.requests, (n_steps, tokens)
+    # every rank must hold the same output tokens (the collectives are part of what is measured)
+    import hashlib
+    digest = hashlib.sha256(repr([list(r.output_tokens) for r in eng.scheduler.active_requests()]).encode()).hexdigest()
+    ranks_agree = True
+    if world > 1:
+        all_d = [None] * world
+        dist.all_gather_object(all_d, digest)
+        ranks_agree = all(d == all_d[0] for d in all_d)
+    status_clean = True
+    try:
+        eng.runner.model.ops.check()
+    except Exception:
+        status_clean = False
+    accept_rate = None
+    if wl["spec_k"] and getattr(eng, "_spec_runner", None) is not None:
+        accept_rate = round(float(eng._spec_runner.acceptance_rate), 4)
+    mem_gb = round(torch.cuda.max_memory_allocated() / 2 ** 30, 2)
     stats = eng.stats()
     if rank == 0:
         S = args.requests
         h2d = S * (4 + 4 + 8 + 4 + 8) + S * runner.max_blocks * 4     # ids, positions, slots, lens, rows, block tables
         d2h = S * 4
         value = tokens / (dev_ms / 1000.0)
+        # like for like only: the reference publishes single-sequence rates (7B on A10G), nothing batched and nothing
+        # on this GPU, so only the `single` workload has a published number to divide by
+        vs_baseline = round(value / BASELINE_7B_TOK_S, 2) if args.workload == "single" else None
         line = {
             "metric": "INT4 Qwen2.5 decode tok/s (box, max over ranks)", "value": round(value, 1), "unit": "tok/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
             "ms_per_step": round(dev_ms / args.steps, 4), "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": round(value / BASELINE_14B_TOK_S, 2), "dtype": "fp16", "data": "synthetic",
+            "vs_baseline": vs_baseline, "dtype": "fp16", "data": "synthetic",
             "config": {"model": f"{args.model}-shaped INT4 group-128 (random N(0,0.02)-like weights)",
-                       "global_batch": S, "seq_len": (f"prompts uniform {PROMPT_RANGE}, {OUTPUT_TOKENS} output tokens"
-                                   if args.workload == "batch64" else "512-token prompt, 256 output tokens"),
+                       "global_batch": S, "seq_len": wl["seq_len"],
                        "workload": args.workload,
                        "parallelism": f"tp{world}", "kv_cache": "paged fp16", "tp_collectives": cfg.comm_backend,
                        "cuda_graphs": cfg.use_cuda_graphs,
                        "l2_policy": "inputs larger than L2: each step streams all INT4 weights and the KV cache",
-                       "baseline_note": "vs_baseline divides by the reference's published single-sequence 14B decode "
-                                        "rate on A100-80GB (37.0 tok/s); it publishes no batched or B200 number"},
+                       "baseline_note": ("vs_baseline = value / 48.6 tok/s, the reference's published single-sequence "
+                                         "7B INT4 decode rate (A10G)" if args.workload == "single" else
+                                         "the reference publishes no batched, tensor-parallel or B200 number for "
+                                         "this configuration: vs_baseline is null")},
             "e2e": {"value": round(tokens / t_e2e, 1), "unit": "tok/s", "ms_per_step": round(t_e2e * 1000 / args.steps, 4),
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "api": "ZStreamerEngine.add_request_tokens + ZStreamerEngine.step"},
@@ -237,7 +306,12 @@ def run_ours(args):
                       "graph_replays": runner.timings["graph_replays"], "impl": "ours",
                       "ttft_p50_ms": round(ttfts[len(ttfts) // 2], 1) if ttfts else None,
                       "ttft_max_ms": round(ttfts[-1], 1) if ttfts else None,
-                      "tpot_p50_ms": round(sorted(step_ms)[len(step_ms) // 2], 3) if step_ms else None},
+                      "tpot_p50_ms": round(sorted(step_ms)[len(step_ms) // 2], 3) if step_ms else None,
+                      "ranks_agree": ranks_agree, "status_clean": status_clean, "accept_rate": accept_rate,
+                      "tokens_per_step": round(tokens / max(args.steps, 1) / S, 3),
+                      "peak_device_memory_gb": mem_gb,
+                      "weights_gb": round(getattr(eng.runner.model, "weight_bytes", 0) / 2 ** 30, 2),
+                      "w4_dec_mode": int(getattr(eng.runner.model.ops, "dec_mode", 0))},
         }
         print(json.dumps(line), flush=True)
     if world > 1:

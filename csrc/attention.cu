@@ -480,6 +480,16 @@ extern "C" int64_t zse_attn_decode_scratch_floats(int num_seqs, int nh, int hd, 
   return int64_t(num_seqs) * nh * max_splits * (hd + 2);
 }
 
+// Shared memory the decode kernel asks for, raised once per device (host work: not a stream operation).
+template <int HD, bool EXT>
+static int prepare_decode() {
+  constexpr int ring = kDecWarps * kDecStages * 2 * 16 * HD * 2;
+  constexpr int merge = kDecWarps * 16 * HD * 4 + kDecWarps * 16 * 2 * 4;
+  constexpr int smem = ring > merge ? ring : merge;
+  if (int rc = prepare_decode<HD, EXT>()) return rc;
+  return 0;
+}
+
 template <int HD, bool EXT>
 static int launch_decode(const void* q, int ldq, const void* kv, const void* bt, int max_blocks, const void* lens,
                          void* out, int ldo, void* scratch, int num_seqs, int nh, int nkv, int block_size, int splits,
@@ -488,13 +498,7 @@ static int launch_decode(const void* q, int ldq, const void* kv, const void* bt,
   constexpr int ring = kDecWarps * kDecStages * 2 * 16 * HD * 2;
   constexpr int merge = kDecWarps * 16 * HD * 4 + kDecWarps * 16 * 2 * 4;
   constexpr int smem = ring > merge ? ring : merge;
-  static bool attr = false;
-  if (!attr) {
-    if (cudaFuncSetAttribute(attn_decode_kernel<HD, EXT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
-        cudaSuccess)
-      return ZSE_ERR_LAUNCH;
-    attr = true;
-  }
+  if (int rc = prepare_decode<HD, EXT>()) return rc;
   dim3 grid(nkv, num_seqs, splits);
   if (launch_pdl(attn_decode_kernel<HD, EXT>, grid, dim3(kDecWarps * 32), smem, st,
                  reinterpret_cast<const __half*>(q), ldq, reinterpret_cast<const __half*>(kv),
@@ -547,12 +551,13 @@ static int launch_prefill(const void* q, int ldq, const void* kv, const void* bt
                           int block_size, float scale, long long blk_stride, long long half_stride, float softcap,
                           int window, cudaStream_t st) {
   constexpr int smem = 2 * 2 * kPfKvTile * HD * 2;
-  static bool attr = false;
-  if (!attr) {
+  static bool attr[kMaxDevices] = {};
+  const int dev_slot = current_device_slot();
+  if (!attr[dev_slot]) {
     if (cudaFuncSetAttribute(attn_prefill_kernel<HD, EXT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
         cudaSuccess)
       return ZSE_ERR_LAUNCH;
-    attr = true;
+    attr[dev_slot] = true;
   }
   dim3 grid((max_q_len + 63) / 64, nh, num_seqs);
   attn_prefill_kernel<HD, EXT><<<grid, kPfWarps * 32, smem, st>>>(
@@ -624,9 +629,14 @@ float* static_scratch(int* err) {
 extern "C" int64_t zse_attn_decode_static_max_floats(void) { return ZSE_ATTN_STATIC_SCRATCH_FLOATS; }
 
 extern "C" int zse_attn_decode_static_setup(void) {
+  // everything the first call on a device would otherwise do on the host: the address of the scratch array and the
+  // shared-memory attribute of the kernels zse_attn_decode_static can reach (head_dim 64 / 128 / 256)
   int err = 0;
   static_scratch(&err);
-  return err;
+  if (err) return err;
+  if (int rc = prepare_decode<128, false>()) return rc;
+  if (int rc = prepare_decode<64, false>()) return rc;
+  return prepare_decode<256, true>();
 }
 
 extern "C" int zse_attn_decode_static(const void* q, int ldq, const void* kv_layer, const void* block_tables,
@@ -637,9 +647,12 @@ extern "C" int zse_attn_decode_static(const void* q, int ldq, const void* kv_lay
   if (num_splits > 1 &&
       zse_attn_decode_scratch_floats(num_seqs, nh, hd, num_splits) > int64_t(ZSE_ATTN_STATIC_SCRATCH_FLOATS))
     return ZSE_ERR_LIMIT;
-  int err = 0;
-  float* scratch = static_scratch(&err);
-  if (scratch == nullptr) return err;
+  float* scratch = nullptr;
+  if (num_splits > 1) {                       // one split needs no scratch: no lookup, nothing that can fail
+    int err = 0;
+    scratch = static_scratch(&err);
+    if (scratch == nullptr) return err;
+  }
   return zse_attn_decode(q, ldq, kv_layer, block_tables, max_blocks, seq_lens, out, ldo, scratch, num_seqs, nh, nkv,
                          hd, block_size, num_splits, scale, stream);
 }

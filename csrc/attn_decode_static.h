@@ -13,9 +13,12 @@
 // caller can choose a smaller num_splits up front.
 //
 // Set-up.  The first call on each device looks the array's address up (cudaGetSymbolAddress) and remembers it; that
-// lookup is host work, may synchronise with the device, and is not a stream operation.  Make one call (or call
-// zse_attn_decode_static_setup()) on each device before the first call that is part of a stream capture.  A failed
-// lookup returns ZSE_ERR_DRIVER and is retried by the next call.
+// lookup is host work, may synchronise with the device, and is not a stream operation; the same goes for the kernel's
+// shared-memory attribute, which is raised once per device.  zse_attn_decode_static_setup() does both for the current
+// device: call it on each device before the first call that is part of a stream capture, and from ONE host thread -
+// the per-device records are filled without a lock, so the first use of a device is not thread-safe (two threads
+// racing there write the same values, but nothing guarantees it).  A failed lookup returns ZSE_ERR_DRIVER and is
+// retried by the next call.  A call with num_splits == 1 needs no scratch and does no lookup.
 //
 // Sharing.  Every call on one device uses the same array.  Nothing in it has to start at zero: each call writes
 // every word it later reads.  Two calls that may run at the same time on one device (different streams without an
@@ -30,7 +33,7 @@ extern "C" {
 #endif
 
 int64_t zse_attn_decode_static_max_floats(void);
-// looks the scratch array up on the current device; 0 or ZSE_ERR_DRIVER
+// looks the scratch array up and raises the kernels' shared-memory attribute on the current device; 0 or an error code
 int zse_attn_decode_static_setup(void);
 // same arguments and results as zse_attn_decode, minus the scratch pointer
 int zse_attn_decode_static(const void* q, int ldq, const void* kv_layer, const void* block_tables_i32, int max_blocks,

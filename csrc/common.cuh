@@ -269,6 +269,16 @@ __device__ __forceinline__ uint32_t pack_half2(float a, float b) {
 __device__ __forceinline__ float silu_f(float g) { return g / (1.0f + __expf(-g)); }
 __device__ __forceinline__ float clamp_f16(float v) { return fminf(fmaxf(v, -65504.0f), 65504.0f); }
 
+// ---- host side: function attributes are per device ------------------------------------------------------------
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) applies to the current device only, so "already done" is kept per
+// device (a process that drives several GPUs raises it on each of them).
+constexpr int kMaxDevices = 64;
+inline int current_device_slot() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) dev = 0;
+  return dev;
+}
+
 // ---- host side: launch with the programmatic-serialization attribute (see pdl_wait) ---------------------------
 int pdl_enabled();   // runtime.cu; 1 unless switched off by zse_set_pdl(0) or ZSE_PDL=0
 

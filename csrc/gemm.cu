@@ -264,12 +264,13 @@ int get_tmap(const void* ptr, uint64_t rows, uint64_t cols, uint32_t box_rows, C
 template <int NT, int EPI>
 static int launch_f16(const CUtensorMap& tw, const CUtensorMap& tx, const GemmArgs& a, dim3 grid, cudaStream_t st) {
   auto kern = gemm_f16_kernel<NT, EPI>;
-  static bool attr_done = false;
-  if (!attr_done) {
+  static bool attr_done[kMaxDevices] = {};
+  const int dev_slot = current_device_slot();
+  if (!attr_done[dev_slot]) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, F16Cfg<NT>::kSmemBytes) !=
         cudaSuccess)
       return ZSE_ERR_LAUNCH;
-    attr_done = true;
+    attr_done[dev_slot] = true;
   }
   return launch_pdl(kern, grid, dim3(kGemmThreads), size_t(F16Cfg<NT>::kSmemBytes), st, tw, tx, a) == cudaSuccess
              ? 0

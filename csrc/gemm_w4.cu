@@ -713,11 +713,12 @@ static int launch_w4(const CUtensorMap& tx, const W4Args& a, dim3 grid, cudaStre
   auto kern = gemm_w4_kernel<NT, R, EPI, DUAL>;
   using Cfg = W4Cfg<NT, R, DUAL>;
   constexpr int smem = Cfg::kSmemBytes;
-  static bool attr_done = false;
-  if (!attr_done) {
+  static bool attr_done[kMaxDevices] = {};
+  const int dev_slot = current_device_slot();
+  if (!attr_done[dev_slot]) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
       return ZSE_ERR_LAUNCH;
-    attr_done = true;
+    attr_done[dev_slot] = true;
   }
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = grid;

@@ -221,11 +221,12 @@ int gemv_w4_plan(int M, int N, int K, int epilogue, int sm_count, int want_split
 template <int MT, int EPI>
 static int launch_gemv(const GemvArgs& a, dim3 grid, size_t smem, cudaStream_t st) {
   auto kern = gemv_w4_kernel<MT, EPI>;
-  static bool attr_done = false;
-  if (!attr_done) {
+  static bool attr_done[kMaxDevices] = {};
+  const int dev_slot = current_device_slot();
+  if (!attr_done[dev_slot]) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemvMaxSmem) != cudaSuccess)
       return ZSE_ERR_LAUNCH;
-    attr_done = true;
+    attr_done[dev_slot] = true;
   }
   return launch_pdl(kern, grid, dim3(kGemvThreads), smem, st, a) == cudaSuccess ? 0 : ZSE_ERR_LAUNCH;
 }

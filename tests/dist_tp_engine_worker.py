@@ -21,12 +21,15 @@ def main():
     from zse_b200.engine import ZStreamerEngine
     from zse_b200.format import synth
     from zse_b200.parallel.comm import make_comm
-    path = "/tmp/zse_tp_engine_test.zse"
+    # two kv heads only split over two ranks; larger groups take the shape with 8 kv heads and an MLP width that
+    # shards unevenly (ranks plan different tile counts there)
+    shape = "small-128" if world <= 2 else "small-uneven"
+    path = f"/tmp/zse_tp_engine_test_{shape}.zse"
     if rank == 0:
-        synth.write_random_model(path, synth.shape_config("small-128"), seed=11)
+        synth.write_random_model(path, synth.shape_config(shape), seed=11)
     dist.barrier()
     rng = random.Random(5)
-    vocab = synth.shape_config("small-128").vocab_size
+    vocab = synth.shape_config(shape).vocab_size
     prompts = [[rng.randrange(vocab) for _ in range(n)] for n in (300, 17, 150, 64)]
     results = {}
     for backend in ("single", "fused", "push", "nccl"):
@@ -37,7 +40,7 @@ def main():
                            comm_backend={"single": "fused", "push": "fused"}.get(backend, backend))
         comm = None
         if tp > 1:
-            comm = make_comm(cfg.comm_backend, rank, world, dev, hidden_size=synth.SHAPES["small-128"]["hidden_size"],
+            comm = make_comm(cfg.comm_backend, rank, world, dev, hidden_size=synth.SHAPES[shape]["hidden_size"],
                              max_tokens=cfg.max_batch_tokens)
         eng = ZStreamerEngine(path, config=cfg, comm=comm, tp_rank=rank if tp > 1 else 0)
         ids = [eng.add_request_tokens(p, max_tokens=12, temperature=0.0, stop_tokens=[]) for p in prompts]
@@ -46,6 +49,22 @@ def main():
         eng.destroy()
         torch.cuda.synchronize()
         dist.barrier()
+    # sampling without a seed: the default seed must not depend on the process, or the ranks pick different tokens
+    cfg = EngineConfig(tp_size=world, device_index=local, max_seq_len=512, max_batch_seqs=8, max_batch_tokens=1024,
+                       prefill_chunk_size=512, quiet=True, comm_backend="fused")
+    comm = make_comm("fused", rank, world, dev, hidden_size=synth.SHAPES[shape]["hidden_size"],
+                     max_tokens=cfg.max_batch_tokens)
+    eng = ZStreamerEngine(path, config=cfg, comm=comm, tp_rank=rank)
+    ids = [eng.add_request_tokens(p, max_tokens=10, temperature=0.9, top_k=40, stop_tokens=[], request_id=f"s{i}")
+           for i, p in enumerate(prompts)]
+    eng.run_until_done()
+    sampled = [eng.get_result(i).output_tokens for i in ids]
+    eng.destroy()
+    torch.cuda.synchronize()
+    dist.barrier()
+    gathered_s = [None] * world
+    dist.all_gather_object(gathered_s, sampled)
+    assert all(g == gathered_s[0] for g in gathered_s), "ranks sampled different tokens"
     same_fused = sum(a == b for a, b in zip(results["fused"], results["single"]))
     same_nccl = sum(a == b for a, b in zip(results["nccl"], results["single"]))
     same_push = sum(a == b for a, b in zip(results["push"], results["single"]))
@@ -59,7 +78,7 @@ def main():
     assert all(g == gathered[0] for g in gathered), "ranks disagree (push exchange)"
     assert same_push >= len(prompts) - 1, (results, same_push)
     if rank == 0:
-        print(f"TP_ENGINE_OK fused {same_fused}/{len(prompts)} push {same_push}/{len(prompts)} "
+        print(f"TP_ENGINE_OK ranks {world} shape {shape} fused {same_fused}/{len(prompts)} push {same_push}/{len(prompts)} "
               f"nccl {same_nccl}/{len(prompts)}")
     dist.barrier()
     dist.destroy_process_group()

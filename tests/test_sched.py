@@ -1,5 +1,7 @@
 """Request queue, memory budget and iteration-level scheduler (zse-engine/tests/test_zstreamer.py covers the same
 classes of the reference: queue ordering, back-pressure, token/sequence budgets, preemption)."""
+import os
+
 import pytest
 
 from zse_b200.sched.memory_budget import MemoryBudget
@@ -285,3 +287,22 @@ def test_reference_named_helpers_of_queue_budget_and_speculation():
     acc, n = v.verify_and_accept([4, 9], [ng._dist(4), ng._dist(9)], rows, 50, temperature=1.0)
     assert acc[:2] == [4, 9] and n == 2
     assert acceptance_rate(2, 4) == 0.5 and effective_tokens_per_step(3) == 3.0
+
+
+def test_default_sampling_seed_is_the_same_in_every_process():
+    """An unseeded request draws from a stream named by its id.  The name must not go through ``hash()``: str hashes
+    differ between interpreter processes, and the workers of a tensor-parallel group each sample for themselves."""
+    import subprocess
+    import sys
+    code = ("from zse_b200.sched.batch_runner import _sampling_row\n"
+            "from zse_b200.sched.request import InferenceRequest, GenerationParams\n"
+            "r = InferenceRequest('req-17', [1, 2, 3], GenerationParams(max_tokens=4, temperature=0.8))\n"
+            "print(_sampling_row(r).seed)\n")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    seeds = set()
+    for hs in ("1", "2", "random"):
+        out = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, cwd=root,
+                             env=dict(os.environ, PYTHONHASHSEED=hs))
+        assert out.returncode == 0, out.stderr[-2000:]
+        seeds.add(out.stdout.strip())
+    assert len(seeds) == 1 and seeds.pop().isdigit()

@@ -1,0 +1,207 @@
+"""Inference kernels written in the kernel language (importable, unlike test fixtures): the portable counterparts of
+the hand-written library, in the spirit of zse-engine/zse_engine/orchestrator/portable_kernels.py:28-813 (INT4 / INT8
+dequantising matmuls, a warp-per-row INT4 GEMV, RoPE with the cache write, plus the small element-wise and
+normalisation kernels).  They are not the engine's hot path - that is ``csrc/`` - but every one runs three ways:
+``emulate`` on the CPU (the oracle of the tests), ``compile`` to a cubin for sm_100a, and ``launch`` on the GPU.
+
+Conventions: weights are row-major ``[N, K]`` like the ``.zse`` file stores them (INT4: two values per byte, low
+nibble first, asymmetric groups of 128 with fp16 scale and zero point; INT8: symmetric groups with an fp16 scale),
+activations ``[M, K]``, outputs ``[M, N]``."""
+from __future__ import annotations
+
+from . import (Tensor, block_dim, block_id, block_reduce_sum, cos, exp, float16, global_id, int8, int32, kernel,
+               lane_id, local_array, reinterpret, rsqrt, sin, thread_id, uint8, uint32, unpack_uint4, warp_reduce_max,
+               warp_reduce_sum)
+
+
+@kernel
+def vector_add(a: Tensor, b: Tensor, out: Tensor, n: int):
+    i = global_id(0)
+    if i < n:
+        out[i] = a[i] + b[i]
+
+
+@kernel
+def add_bias(x: Tensor, bias: Tensor, out: Tensor, n: int, width: int):
+    i = global_id(0)
+    if i >= n:
+        return
+    out[i] = x[i] + bias[i % width]
+
+
+@kernel
+def silu(x: Tensor, out: Tensor, n: int):
+    i = global_id(0)
+    if i >= n:
+        return
+    v = x[i]
+    out[i] = v / (1.0 + exp(-v))
+
+
+@kernel
+def swiglu(gate: Tensor, up: Tensor, out: Tensor, n: int):
+    i = global_id(0)
+    if i < n:
+        g = gate[i]
+        out[i] = g / (1.0 + exp(-g)) * up[i]
+
+
+@kernel
+def rmsnorm(x: Tensor, w: Tensor, out: Tensor, n: int, eps: float):
+    """One block per row; strided partial sums, then a block reduction every thread receives."""
+    row = block_id(0)
+    tid = thread_id(0)
+    acc = 0.0
+    for i in range(tid, n, block_dim(0)):
+        v = x[row * n + i]
+        acc += v * v
+    total = block_reduce_sum(acc)
+    scale = rsqrt(total / float(n) + eps)
+    for i in range(tid, n, block_dim(0)):
+        out[row * n + i] = x[row * n + i] * scale * w[i]
+
+
+@kernel
+def layernorm(x: Tensor, weight: Tensor, out: Tensor, n: int):
+    """One block per row of at most block_dim values; two block reductions in a row (mean, then variance)."""
+    tid = thread_id(0)
+    idx = block_id(0) * n + tid
+    val = x[idx] if tid < n else 0.0
+    mean = block_reduce_sum(val) / float(n)
+    diff = val - mean if tid < n else 0.0
+    var = block_reduce_sum(diff * diff) / float(n)
+    if tid < n:
+        out[idx] = weight[tid] * (diff * rsqrt(var + 0.00001))
+
+
+@kernel
+def softmax_warp(x: Tensor, out: Tensor, n: int):
+    """One warp per row of up to 32 values."""
+    row = block_id(0)
+    lane = lane_id()
+    v = x[row * n + lane] if lane < n else -1e30
+    m = warp_reduce_max(v)
+    e = exp(v - m) if lane < n else 0.0
+    s = warp_reduce_sum(e)
+    if lane < n:
+        out[row * n + lane] = e / s
+
+
+@kernel
+def dequant_rows(packed: Tensor[uint8], scales: Tensor[float16], zeros: Tensor[float16], out: Tensor[float16],
+                 groups: int):
+    """INT4 asymmetric groups of 128 -> fp16: a thread expands one 32-bit word (8 values)."""
+    w = global_id(0)
+    if w < groups * 16:
+        words = reinterpret(packed, uint32)
+        buf = local_array(8, int32)
+        unpack_uint4(words[w], buf, 0)
+        g = w // 16
+        for j in range(8):
+            out[w * 8 + j] = buf[j] * scales[g] + zeros[g]
+
+
+@kernel
+def dequant_matmul_int4(x: Tensor[float16], packed: Tensor[uint8], scales: Tensor[float16], zeros: Tensor[float16],
+                        out: Tensor[float16], m_rows: int, n_rows: int, k: int):
+    """out[m, n] = sum_k x[m, k] * (q[n, k] * scale[n, k/128] + zero[n, k/128]); one thread per output, a 32-bit word
+    (eight weights) per step."""
+    idx = global_id(0)
+    if idx < m_rows * n_rows:
+        m = idx // n_rows
+        n = idx % n_rows
+        words = reinterpret(packed, uint32)
+        buf = local_array(8, int32)
+        acc = 0.0
+        for w in range(k // 8):
+            unpack_uint4(words[n * (k // 8) + w], buf, 0)
+            g = n * (k // 128) + w // 16
+            s = scales[g]
+            z = zeros[g]
+            for j in range(8):
+                acc += x[m * k + w * 8 + j] * (buf[j] * s + z)
+        out[idx] = acc
+
+
+@kernel
+def dequant_matmul_int8(x: Tensor[float16], q: Tensor[int8], scales: Tensor[float16], out: Tensor[float16],
+                        m_rows: int, n_rows: int, k: int, group: int):
+    """out[m, n] = sum_k x[m, k] * q[n, k] * scale[n, k/group]; one thread per output."""
+    idx = global_id(0)
+    if idx < m_rows * n_rows:
+        m = idx // n_rows
+        n = idx % n_rows
+        acc = 0.0
+        for g in range(k // group):
+            part = 0.0
+            for j in range(group):
+                part += x[m * k + g * group + j] * q[n * k + g * group + j]
+            acc += part * scales[n * (k // group) + g]
+        out[idx] = acc
+
+
+@kernel
+def gemv_int4_warp(x: Tensor[float16], packed: Tensor[uint8], scales: Tensor[float16], zeros: Tensor[float16],
+                   out: Tensor[float16], n_rows: int, k: int):
+    """Single-token GEMV: one warp per weight row, lanes stride over the row's 32-bit words, butterfly reduction."""
+    row = block_id(0) * (block_dim(0) // 32) + thread_id(0) // 32
+    lane = lane_id()
+    acc = 0.0
+    if row < n_rows:
+        words = reinterpret(packed, uint32)
+        buf = local_array(8, int32)
+        for w in range(lane, k // 8, 32):
+            unpack_uint4(words[row * (k // 8) + w], buf, 0)
+            g = row * (k // 128) + w // 16
+            s = scales[g]
+            z = zeros[g]
+            for j in range(8):
+                acc += x[w * 8 + j] * (buf[j] * s + z)
+    total = warp_reduce_sum(acc)
+    if row < n_rows and lane == 0:
+        out[row] = total
+
+
+@kernel
+def rope_kv_write(qkv: Tensor[float16], cache: Tensor[float16], positions: Tensor[int32], slots: Tensor[int32],
+                  inv_freq: Tensor, tokens: int, nh: int, nkv: int, hd: int, block_size: int):
+    """Rotate-half RoPE on the q and k heads of ``qkv`` [tokens, (nh + 2 nkv) * hd] in place and scatter of k / v into
+    the paged cache [blocks, 2, nkv, block_size, hd]; one thread per (token, head, rotation pair)."""
+    half = hd // 2
+    idx = global_id(0)
+    heads = nh + 2 * nkv
+    if idx < tokens * heads * half:
+        i = idx % half
+        head = (idx // half) % heads
+        t = idx // (half * heads)
+        base = (t * heads + head) * hd
+        a = qkv[base + i] * 1.0
+        b = qkv[base + i + half] * 1.0
+        if head < nh + nkv:
+            ang = positions[t] * inv_freq[i]
+            c = cos(ang)
+            s = sin(ang)
+            ra = a * c - b * s
+            rb = b * c + a * s
+            a = ra
+            b = rb
+            qkv[base + i] = a
+            qkv[base + i + half] = b
+        if head >= nh:
+            slot = slots[t]
+            if slot >= 0:
+                is_v = 1 if head >= nh + nkv else 0
+                kvh = head - nh - is_v * nkv
+                blk = slot // block_size
+                off = slot % block_size
+                dst = (((blk * 2 + is_v) * nkv + kvh) * block_size + off) * hd
+                cache[dst + i] = a
+                cache[dst + i + half] = b
+
+
+def _collect():
+    from .kernel import KernelFunction
+    return {name: obj for name, obj in globals().items() if isinstance(obj, KernelFunction)}
+
+
+ALL = _collect()

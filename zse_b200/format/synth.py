@@ -27,6 +27,11 @@ SHAPES = {
     "small-128": dict(num_layers=2, hidden_size=512, num_heads=4, num_kv_heads=2, head_dim=128,
                       intermediate_size=1024, vocab_size=2048, rms_norm_eps=1e-6, rope_theta=1e6, arch="qwen2",
                       max_seq_len=4096),
+    # an intermediate size whose 128-column groups (15) do not divide evenly over 2, 4 or 8 ranks, and 8 kv heads so
+    # that every rank count up to 8 gets whole heads: the small analogue of a 13824-wide MLP on 8 GPUs
+    "small-uneven": dict(num_layers=2, hidden_size=1024, num_heads=8, num_kv_heads=8, head_dim=128,
+                         intermediate_size=1920, vocab_size=2048, rms_norm_eps=1e-6, rope_theta=1e6, arch="qwen2",
+                         max_seq_len=4096),
     # Gemma-2 block: four norms, GeGLU, soft-capped scores and logits, local/global layers alternate
     "tiny-gemma2": dict(num_layers=4, hidden_size=256, num_heads=4, num_kv_heads=2, head_dim=64,
                         intermediate_size=768, vocab_size=1024, rms_norm_eps=1e-6, rope_theta=10000.0, arch="gemma2",

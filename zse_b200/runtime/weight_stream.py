@@ -44,12 +44,16 @@ class DeviceMirror:
         def reader() -> None:
             try:
                 while True:
+                    # a staging buffer first, the chunk index second: every claimed chunk then owns a buffer, and the
+                    # chunk the consumer waits for is always claimed by a reader that can fill it (claiming the index
+                    # first lets readers of later chunks hold every buffer while the next chunk's reader has none)
+                    slot = free_slots.get()
                     with cond:
                         k = counter[0]
                         if k >= len(chunks):
+                            free_slots.put(slot)
                             return
                         counter[0] += 1
-                    slot = free_slots.get()
                     pos, n = chunks[k]
                     got = 0
                     mv = memoryview(views[slot])[:n]
@@ -74,8 +78,12 @@ class DeviceMirror:
         with torch.cuda.stream(stream):
             for k, (pos, n) in enumerate(chunks):
                 with cond:
+                    waited = 0.0
                     while k not in ready and not errors:
                         cond.wait(0.5)
+                        waited += 0.5
+                        if waited > 300.0:
+                            raise TimeoutError(f"weight chunk {k} of {len(chunks)} did not arrive within 300 s")
                     if errors:
                         raise errors[0]
                     slot = ready.pop(k)
