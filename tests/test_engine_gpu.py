@@ -171,3 +171,108 @@ def test_native_step_driver_equals_python_wiring(tmp_path, monkeypatch, quant):
     assert used_n and not used_p
     assert outs_n == outs_p
     assert torch.equal(logits_n, logits_p)
+
+
+def test_lora_on_all_seven_projections_on_the_device(tmp_path):
+    """An adapter on q/k/v/o/gate/up/down on the GPU: the first tokens are those of the fp32 oracle run on the merged
+    weights W + (alpha / r) B A (fp16 rounding may flip a near tie later on), and a request without the adapter in
+    the same batch keeps the base model's tokens."""
+    import numpy as np
+    from zse_b200.format.lora_format import load_lora
+    from zse_b200.lora.weights import random_adapter_file
+    path = str(tmp_path / "m.zse")
+    synth.write_random_model(path, synth.shape_config("small-128"), seed=6)
+    eng = ZStreamerEngine(path, config=_cfg())
+    targets = ["q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj"]
+    f = str(tmp_path / "all.zse-lora")
+    random_adapter_file(f, eng.model_config, rank=4, alpha=8.0, target_modules=targets, seed=3, std=0.05)
+    eng.lora_manager.load_adapter("all", f)
+    orc = OracleModel(ZSELoader(path))
+    adapter, data = load_lora(f, eng.lora_manager.weight_shapes())
+    block = {"q_proj": "self_attn", "k_proj": "self_attn", "v_proj": "self_attn", "o_proj": "self_attn"}
+    for (layer, mod), (a, b) in data.items():
+        w = adapter.get_weight(layer, mod)
+        A = torch.from_numpy(np.frombuffer(a, np.float16).reshape(w.rank, w.in_features).astype(np.float32))
+        B = torch.from_numpy(np.frombuffer(b, np.float16).reshape(w.out_features, w.rank).astype(np.float32))
+        name = f"layers.{layer}.{block.get(mod, 'mlp')}.{mod}.weight"
+        orc.w[name] = orc.w[name] + adapter.scaling * (B @ A)
+    p = _prompts(1, 30, 30, seed=21)[0]
+    ids = [eng.add_request_tokens(p, max_tokens=10, temperature=0.0, stop_tokens=[], lora_id="all"),
+           eng.add_request_tokens(p, max_tokens=10, temperature=0.0, stop_tokens=[])]
+    eng.run_until_done()
+    with_adapter, base = (eng.get_result(i).output_tokens for i in ids)
+    want = orc.greedy(p, 10)
+    assert with_adapter[:3] == want[:3] and _agreement(with_adapter, want) >= 0.7, (with_adapter, want)
+    assert base == _run(eng, [p], 10)[0] and base != with_adapter
+    eng.destroy()
+
+
+def test_uniform_sliding_window_on_the_device(tmp_path):
+    """Mistral-style window on the GPU: the windowed variant of the tensor-core attention kernels, old blocks leaving
+    the cache; tokens follow the oracle's exact mask."""
+    p = str(tmp_path / "window.zse")
+    synth.write_random_model(p, synth.shape_config("small-128", arch="mistral", sliding_window=48), seed=9)
+    oracle = OracleModel(ZSELoader(p))
+    eng = ZStreamerEngine(p, config=_cfg(block_size=16, prefill_chunk_size=64, max_batch_tokens=128))
+    assert eng._model.window == 48
+    prompts = _prompts(3, 70, 150, seed=12)
+    got = _run(eng, prompts, 12)
+    want = [oracle.greedy(pr, 12) for pr in prompts]
+    for g, w in zip(got, want):
+        assert g[:2] == w[:2] and _agreement(g, w) >= 0.7, (g, w)
+    eng.destroy()
+
+
+def test_a_seeded_row_gets_the_same_token_wherever_it_sits_in_the_batch(model_path):
+    """Per-request seeding of the device sampler: the token of a seeded request does not depend on which batch row it
+    occupies nor on what else is in the batch."""
+    eng = ZStreamerEngine(model_path, config=_cfg())
+    target = _prompts(1, 24, 24, seed=31)[0]
+    others = _prompts(5, 10, 40, seed=32)
+
+    def tokens_with(before):
+        ids = [eng.add_request_tokens(o, max_tokens=8, temperature=1.1, top_k=40, seed=100 + i, stop_tokens=[])
+               for i, o in enumerate(others[:before])]
+        rid = eng.add_request_tokens(target, max_tokens=8, temperature=1.1, top_k=40, seed=7, stop_tokens=[])
+        ids += [eng.add_request_tokens(o, max_tokens=8, temperature=1.1, top_k=40, seed=200 + i, stop_tokens=[])
+                for i, o in enumerate(others[before:])]
+        eng.run_until_done()
+        return eng.get_result(rid).output_tokens
+
+    alone = tokens_with(0)[:]
+    assert tokens_with(2) == alone and tokens_with(5) == alone
+    eng.destroy()
+
+
+def test_cuda_graph_runner_replays_native_entry_points():
+    """``CUDAGraphRunner`` (the reference's capture / replay wrapper) around two entry points of the native library:
+    replay on new input data gives what eager launches give."""
+    from zse_b200.ops.backend import CudaOps
+    from zse_b200.ops import reference as ref
+    from zse_b200.runtime.graph import CUDAGraphRunner
+    ops = CudaOps("cuda")
+    M, H = 8, 1024
+    residual = torch.randn(M, H, device="cuda")
+    planes = torch.randn(2, M, H, device="cuda")
+    w = (1 + 0.1 * torch.randn(H, device="cuda")).half()
+    out = torch.zeros(M, H, dtype=torch.float16, device="cuda")
+    r = CUDAGraphRunner()
+    with pytest.raises(RuntimeError):
+        r.replay()
+    ops.add_rmsnorm(residual.clone(), planes, 2, None, w, out, M, 1e-6)        # warm-up outside the capture
+    work = residual.clone()
+    r.begin_capture()
+    ops.add_rmsnorm(work, planes, 2, None, w, out, M, 1e-6)
+    r.end_capture()
+    assert r.is_captured
+    for _ in range(2):
+        work.copy_(residual)
+        planes.normal_()
+        r.replay()
+        r.sync()
+        torch.cuda.synchronize()
+        want = ref.rmsnorm(residual + planes.sum(0), w, 1e-6)
+        assert (out.float() - want.float()).abs().max() < 2e-2
+    r.destroy()
+    assert not r.is_captured
+    ops.check()

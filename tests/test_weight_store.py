@@ -90,6 +90,10 @@ def test_kernel_registry_names():
         k.get("no_such_kernel")
     with pytest.raises(ValueError):
         InferenceKernels("rocm")
+    # a launch geometry cannot be imposed on entry points that plan their own: refused, not ignored
+    with pytest.raises(ValueError):
+        k.launch("paged_attention", (8, 1, 1), (128, 1, 1))
+    assert "mma.sync" in k.describe("paged_attention") and "tcgen05.st" in k.describe("tiled_dequant_matmul_int4")
 
 
 def test_vram_accounting_and_scratch():

@@ -177,7 +177,10 @@ class DecoderModel:
         has = lambda n: loader.weight_index.find(n) is not None
         to_dev = lambda a: np_to_dev(a, dev)
         mirror = None
-        if dev.type == "cuda" and p.tp_size == 1 and env.flag("ZSE_STREAM_WEIGHTS"):
+        # the weight section goes to the device in one streamed pass (every tensor-parallel rank mirrors the section and
+        # cuts its shard out on the device: the page cache serves all ranks, and a rank's shard of a row-parallel
+        # projection is a column range that no contiguous read could deliver anyway)
+        if dev.type == "cuda" and env.flag("ZSE_STREAM_WEIGHTS"):
             from ..runtime.weight_stream import DeviceMirror
             mirror = DeviceMirror(loader, dev)
             self.load_stats["stream_s"] = round(mirror.seconds, 3)

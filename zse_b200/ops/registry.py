@@ -36,10 +36,13 @@ KERNEL_TABLE: Dict[str, Tuple[str, str]] = {
     "gemma_rmsnorm_f32in": ("norm_add_rmsnorm", "post-norm, residual add, layer scalar and the next pre-norm in one"),
     "layer_scalar_mul_f32": ("norm_add_rmsnorm", "the scalar is an argument of the fused kernel"),
     "logit_softcap": ("softcap", ""),
-    "paged_attention": ("attn_decode", "tcgen05 QK^T and PV over the paged cache, split over the sequence"),
-    "prefill_attention": ("attn_prefill", "tcgen05, causal, reads earlier chunks from the paged cache"),
-    "tiled_fp16_matmul": ("gemm_f16", "tcgen05 + TMA"),
-    "tiled_dequant_matmul_int4": ("gemm_w4", "tcgen05: nibbles dequantised in shared memory, accumulators in TMEM"),
+    "paged_attention": ("attn_decode", "mma.sync m16n8k16 QK^T and PV over the paged cache (a decode query group is at "
+                                       "most 16 rows), cp.async rings, split over the sequence"),
+    "prefill_attention": ("attn_prefill", "mma.sync m16n8k16, causal, reads earlier chunks from the paged cache"),
+    "tiled_fp16_matmul": ("gemm_f16", "tcgen05 + TMA, operands in shared memory, accumulators in TMEM"),
+    "tiled_dequant_matmul_int4": ("gemm_w4", "tcgen05: nibbles dequantised in registers and written to TMEM with "
+                                             "tcgen05.st as the A operand, accumulators in TMEM; passes of at most "
+                                             "64 tokens can take the persistent kernel gemm_w4_dec"),
     "tiled_dequant_matmul_int8": ("dequant_w8", "INT8 weights are expanded once at load and run through gemm_f16"),
     "dequant_gemv_int4": ("gemm_w4", "M <= 2 takes the CUDA-core GEMV inside the same entry point"),
     "batched_dequant_gemv_int4": ("gemm_w4", "small batches take the narrow tensor-core tile"),
@@ -96,6 +99,12 @@ class InferenceKernels:
         return f"{name} -> ops.native.{entry}" + (f" ({note})" if note else "")
 
     def launch(self, name: str, grid: tuple, block: tuple, *args, **kwargs):
+        """Calls the entry point that serves ``name``.  The entry points plan their own grids and blocks (tile shapes,
+        split-K, clusters), so a launch geometry cannot be imposed from here: ``grid`` and ``block`` must be None or
+        empty, anything else is refused rather than silently ignored."""
+        if grid or block:
+            raise ValueError(f"{name}: the native entry points choose their own launch geometry; pass grid=None, "
+                             f"block=None (got grid={grid!r}, block={block!r})")
         return self.get(name)(*args, **kwargs)
 
     launch_prepacked = launch
