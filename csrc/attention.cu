@@ -486,7 +486,14 @@ static int prepare_decode() {
   constexpr int ring = kDecWarps * kDecStages * 2 * 16 * HD * 2;
   constexpr int merge = kDecWarps * 16 * HD * 4 + kDecWarps * 16 * 2 * 4;
   constexpr int smem = ring > merge ? ring : merge;
-  if (int rc = prepare_decode<HD, EXT>()) return rc;
+  static bool attr[kMaxDevices] = {};
+  const int dev_slot = current_device_slot();
+  if (!attr[dev_slot]) {
+    if (cudaFuncSetAttribute(attn_decode_kernel<HD, EXT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
+        cudaSuccess)
+      return ZSE_ERR_LAUNCH;
+    attr[dev_slot] = true;
+  }
   return 0;
 }
 

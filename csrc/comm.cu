@@ -614,6 +614,12 @@ int tp_fill_push_table(const void* ctx, int slot, bool multimem, int rank_overri
   out->slot = slot & 1;
   return 0;
 }
+uint32_t* tp_push_state(const void* ctx, int rank_override) {
+  const zse_tp_ctx* c = reinterpret_cast<const zse_tp_ctx*>(ctx);
+  if (c == nullptr) return nullptr;
+  const int r = rank_override >= 0 ? rank_override : c->rank;
+  return (r >= 0 && r < c->table.tp) ? c->state[r] : nullptr;
+}
 }  // namespace zse
 
 // Programmatic dependent launch for the reduce kernels: off unless ZSE_TP_PDL=1.  Measured on 2 GPUs: a reduce kernel

@@ -45,6 +45,8 @@ struct PushTable {
 };
 // Fills `out` from a tensor-parallel context (comm.cu).  rank_override >= 0 plays another rank (single-GPU tests).
 int tp_fill_push_table(const void* ctx, int slot, bool multimem, int rank_override, PushTable* out);
+// This rank's running totals of the push exchange {expected slot 0, expected slot 1, exit ticket} (comm.cu), or null.
+uint32_t* tp_push_state(const void* ctx, int rank_override);
 
 // CUDA-core path for one or two tokens (gemv_w4.cu).  gemv_w4_plan returns the number of K splits (fp32 planes) the
 // GEMV would use, or 0 when the tensor-core kernel should run instead.

@@ -48,8 +48,9 @@ namespace zse {
 
 constexpr int kDecWarps = 25;
 constexpr int kDecThreads = kDecWarps * 32;
-constexpr int kDecSX = 6;            // activation stages
-constexpr int kDecSW = 5;            // weight chunks per pipeline ring
+constexpr int kDecSX = 6;            // activation stages (INT4; INT8 chunks are twice as large: 5)
+constexpr int kDecSW = 5;            // weight chunks per pipeline ring (INT4; INT8: 3)
+constexpr int kW8ChunkBytes = 16640; // INT8 chunk: 128 rows x 128 K int8 + 128 fp16 scales
 constexpr int kDecProducerWarp = 4;
 constexpr int kDecDqWarp0 = 5;
 constexpr int kDecEpiWarp0 = 21;
@@ -67,12 +68,15 @@ struct DecBars {
   int abort_flag;
 };
 
-template <int NT>
+template <int NT, bool W8 = false>
 struct DecCfg {
+  static constexpr int kSX = W8 ? 5 : kDecSX;
+  static constexpr int kSW = W8 ? 3 : kDecSW;
+  static constexpr int kChunk = W8 ? kW8ChunkBytes : kW4ChunkBytes;
   static constexpr int kXBytes = NT * 128;                  // one 64-wide K sub-tile of X
   static constexpr int kXStage = 2 * kXBytes;
-  static constexpr int kXRing = ((kDecSX * kXStage + 1023) / 1024) * 1024;
-  static constexpr int kWRing = 2 * kDecSW * kW4ChunkBytes;
+  static constexpr int kXRing = ((kSX * kXStage + 1023) / 1024) * 1024;
+  static constexpr int kWRing = 2 * kSW * kChunk;
   static constexpr int kStageOff = kXRing + ((kWRing + 127) / 128) * 128;
   static constexpr int kBarsOff = kStageOff + kDecStageBytes;
   static constexpr int kSmemBytes = kBarsOff + 1024 + 1024;   // barriers + alignment slack
@@ -90,6 +94,25 @@ struct DecRope {
   int nh, nkv, block_size, max_position;
 };
 
+// Row-parallel projection whose epilogue is the tensor-parallel all-reduce, the residual add and the next RMSNorm
+// (kDecAllReduceNorm).  Every CTA sends the fp16 sums it finishes to slot `rank` of EVERY rank's inbox (one
+// multimem.st through the NVSwitch, or one store per peer) and adds the number of (tile, column granule) units it
+// finished to the counter [slot][rank] on every rank.  Then the CTAs that own a token row wait until every source's
+// counter has gained n_tiles * granules units, add the tp inbox rows in rank order (so the replicated residual stream
+// stays bit-identical on all ranks), add the fp32 residual and normalise.  Counting units instead of CTAs makes the
+// target the same whatever plan each rank chose for its own shard width.  The running total a counter must reach
+// lives in device memory (state[slot]) and is advanced by the last CTA to leave, so a CUDA graph replays the launch
+// unchanged; two inbox slots alternate between calls.
+struct DecTpNorm {
+  PushTable push;              // inboxes [2 slots][tp][m_cap][H] and counters [2 slots][tp] of every rank
+  uint32_t* state;             // this rank's words {expected slot 0, expected slot 1, exit ticket}
+  float* residual;             // fp32 [M, H], in/out
+  const __half* norm_w;        // fp16 [H]
+  __half* xnorm;               // fp16 [M, H] out (null: residual only)
+  float eps;
+  uint32_t units_total;        // what every source adds to its counter in one call
+};
+
 struct DecArgs {
   const uint8_t* w;            // tiled chunks [n_tiles][k_stages][8704]
   const __half* bias;          // [N] or null
@@ -103,6 +126,7 @@ struct DecArgs {
   Status* status;
   long long* timing;           // debug builds (ZSE_DEC_TIMING): per-role cycle counters of one CTA, else unused
   DecRope rope;
+  DecTpNorm tpn;
 };
 
 __device__ __forceinline__ uint32_t ld_acquire_gpu_u32(const uint32_t* p) {
@@ -112,6 +136,29 @@ __device__ __forceinline__ uint32_t ld_acquire_gpu_u32(const uint32_t* p) {
 }
 __device__ __forceinline__ void st_release_gpu_u32(uint32_t* p, uint32_t v) {
   asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+__device__ __forceinline__ void dec_multimem_st_v4(void* mc_ptr, const uint4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f16x2 [%0], {%1,%2,%3,%4};" ::"l"(mc_ptr), "r"(v.x), "r"(v.y),
+               "r"(v.z), "r"(v.w)
+               : "memory");
+}
+__device__ __forceinline__ void dec_multimem_red_add_release(uint32_t* mc_ptr, uint32_t v) {
+  asm volatile("multimem.red.release.sys.global.add.u32 [%0], %1;" ::"l"(mc_ptr), "r"(v) : "memory");
+}
+__device__ __forceinline__ void dec_red_add_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t dec_ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ uint4 dec_ld_relaxed_sys_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.relaxed.sys.global.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p)
+               : "memory");
+  return v;
 }
 
 #define ZSE_TMEM_LD_X8(r, taddr)                                                                               \
@@ -165,6 +212,23 @@ __device__ __forceinline__ void dec_dequant_half(const uint4& w0, const uint4& w
 #define DTICK(var)
 #define DACC(slot, t0)
 #endif
+
+// Sixteen int8 (one 16-byte part of a row: K = 16p .. 16p+15) -> eight half2 words, times the group's scale.  A byte b
+// is placed under the exponent of 1024 as 0x6400 | (b ^ 0x80), i.e. 1024 + (b + 128); subtracting 1152 leaves b
+// exactly, the multiplication by the scale rounds once.
+__device__ __forceinline__ void dec_dequant_w8_part(const uint4& w, __half2 s2, uint32_t* out8) {
+  const __half2 k1152 = __half2half2(__ushort_as_half(0x6480));      // 1152
+  const uint32_t in[4] = {w.x ^ 0x80808080u, w.y ^ 0x80808080u, w.z ^ 0x80808080u, w.w ^ 0x80808080u};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    uint32_t lo = __byte_perm(in[i], 0x64646464u, 0x4140);            // bytes 0, 1 -> (k, k+1)
+    uint32_t hi = __byte_perm(in[i], 0x64646464u, 0x4342);            // bytes 2, 3 -> (k+2, k+3)
+    __half2 a = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&lo), k1152), s2);
+    __half2 b = __hmul2(__hsub2(*reinterpret_cast<__half2*>(&hi), k1152), s2);
+    out8[2 * i] = *reinterpret_cast<uint32_t*>(&a);
+    out8[2 * i + 1] = *reinterpret_cast<uint32_t*>(&b);
+  }
+}
 
 // Bounded wait until a flag word in global memory holds `want`.
 __device__ __forceinline__ bool dec_wait_flag(const uint32_t* flag, uint32_t want, volatile int* abort_flag, Status* st,
@@ -298,6 +362,27 @@ __device__ __forceinline__ void dec_store_item(const DecArgs& a, const Fetch& f,
                                                bool add_bias) {
   const int t = col;
   if (t >= a.M) return;
+  if (EPI == kDecAllReduceNorm) {
+    // this rank's partial row segment (8 columns of the hidden dimension) -> slot `rank` of every rank's inbox
+    const int r0 = (e7 & 15) * 8, n = tile * kTileN + r0;
+    if (n >= a.N) return;
+    const float4 lo = f.get4(col, r0), hi = f.get4(col, r0 + 4);
+    uint4 pk;
+    pk.x = pack_half2(clamp_f16(lo.x), clamp_f16(lo.y));
+    pk.y = pack_half2(clamp_f16(lo.z), clamp_f16(lo.w));
+    pk.z = pack_half2(clamp_f16(hi.x), clamp_f16(hi.y));
+    pk.w = pack_half2(clamp_f16(hi.z), clamp_f16(hi.w));
+    const PushTable& pt = a.tpn.push;
+    const size_t off = ((size_t(pt.slot) * pt.tp + pt.rank) * pt.m_cap + t) * pt.H + n;
+    if (pt.mc_inbox != nullptr) {
+      dec_multimem_st_v4(pt.mc_inbox + off, pk);
+    } else {
+#pragma unroll
+      for (int k = 0; k < kPushMaxTp; ++k)
+        if (k < pt.tp) *reinterpret_cast<uint4*>(pt.inbox[k] + off) = pk;
+    }
+    return;
+  }
   if (EPI == kDecF16 || EPI == kDecF32) {
     const int r0 = (e7 & 15) * 8, n = tile * kTileN + r0;
     if (n >= a.N) return;
@@ -408,8 +493,7 @@ __device__ __forceinline__ bool dec_epilogue_item(const DecArgs& a, DecBars* bar
                                                   int ntp, bool lane0, bool lane1, uint32_t par0, uint32_t par1,
                                                   bool release, uint32_t epoch1, int q, int lane, int wi, int W,
                                                   bool alive_in, long long* tacc) {
-  using Cfg = DecCfg<NT>;
-  constexpr int G = Cfg::kGranules;
+  constexpr int G = NT / 8;
   const int ks = a.k_stages;
   const int wide = W > 1;
   const int row = q * 32 + lane, et = wi * 128 + row;
@@ -536,7 +620,7 @@ __device__ __forceinline__ bool dec_epilogue_item(const DecArgs& a, DecBars* bar
 template <int NT>
 __device__ __forceinline__ void dec_split_push(float* recv, uint32_t tmem, int ntp, bool lane0, bool lane1, int seg,
                                                int S, int go_max, int q, int lane, int wi) {
-  constexpr int G = DecCfg<NT>::kGranules;
+  constexpr int G = NT / 8;
   const int row = q * 32 + lane;
   const uint32_t lane_addr = uint32_t(q * 32) << 16;
 #pragma unroll 1
@@ -557,7 +641,7 @@ __device__ __forceinline__ void dec_split_push(float* recv, uint32_t tmem, int n
 template <int NT, int EPI>
 __device__ __forceinline__ void dec_split_finish(const DecArgs& a, const float* recv, int pair, int ntp, int seg, int S,
                                                  int go_max, int et) {
-  constexpr int G = DecCfg<NT>::kGranules;
+  constexpr int G = NT / 8;
   const int Go = seg < G ? (G - seg + S - 1) / S : 0;               // granules per tile this CTA finishes
 #pragma unroll 1
   for (int idx = et; idx < ntp * Go * 128; idx += 640) {
@@ -568,11 +652,130 @@ __device__ __forceinline__ void dec_split_finish(const DecArgs& a, const float* 
   }
 }
 
-template <int NT, int EPI>
+// Second half of kDecAllReduceNorm, run by the twenty worker warps (640 threads, index `et`) of every CTA after its
+// own sums are on their way: count this CTA's units in on every rank, then, for the token rows this CTA owns
+// (row = cta, cta + grid, ...), wait for all sources, add, residual, RMSNorm.
+__device__ __forceinline__ void dec_allreduce_norm_tail(const DecArgs& a, DecBars* bars, float* red, int cta,
+                                                        int n_cta, uint32_t my_units, bool pushed_ok, int et) {
+  const DecTpNorm& tn = a.tpn;
+  const PushTable& pt = tn.push;
+  volatile int* abort_flag = &bars->abort_flag;
+  const int tp = pt.tp, H = pt.H, nch = H / 8;
+  epi_bar(1);                                              // every store of this CTA has been issued
+  if (et == 0 && pushed_ok && my_units > 0) {
+    __threadfence_system();
+    const int ctr = pt.slot * tp + pt.rank;
+    if (pt.mc_arrive != nullptr) {
+      dec_multimem_red_add_release(pt.mc_arrive + ctr, my_units);
+    } else {
+      for (int k = 0; k < tp; ++k) dec_red_add_release_sys(pt.arrive[k] + ctr, my_units);
+    }
+  }
+  bool ok = pushed_ok;
+  if (cta < a.M) {
+    // ---- wait until every source has delivered its rows (bounded; a lost peer ends in a status, not a hang)
+    if (et < tp) {
+      const uint32_t target = tn.state[pt.slot] + tn.units_total;
+      const uint32_t* ctr = pt.arrive[pt.rank] + pt.slot * tp + et;
+      if (int32_t(dec_ld_acquire_sys(ctr) - target) < 0) {
+        const uint64_t t0 = globaltimer_ns();
+        unsigned spins = 0;
+        while (int32_t(dec_ld_acquire_sys(ctr) - target) < 0) {
+          if ((++spins & 0x3F) == 0 && (*abort_flag || globaltimer_ns() - t0 > kWaitLimitNs)) {
+            report(a.status, kPeerTimeout, 35, et);
+            ok = false;
+            break;
+          }
+        }
+      }
+    }
+    ok = epi_all(ok, 1);
+    for (int row = cta; row < a.M; row += n_cta) {
+      const __half* box = pt.inbox[pt.rank] + (size_t(pt.slot) * tp * pt.m_cap + row) * H;
+      float vals[2][8];
+      float ss = 0.f;
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int c = et + j * 640;
+        if (c < nch) {
+          float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+          if (ok) {
+            uint4 got[kPushMaxTp];
+#pragma unroll
+            for (int r = 0; r < kPushMaxTp; ++r)
+              if (r < tp) got[r] = dec_ld_relaxed_sys_v4(box + size_t(r) * pt.m_cap * H + size_t(c) * 8);
+#pragma unroll
+            for (int r = 0; r < kPushMaxTp; ++r) {           // rank order: the same sum on every rank
+              if (r < tp) {
+                const __half2* h = reinterpret_cast<const __half2*>(&got[r]);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                  const float2 fv = __half22float2(h[i]);
+                  acc[2 * i] += fv.x;
+                  acc[2 * i + 1] += fv.y;
+                }
+              }
+            }
+          }
+          float4* res = reinterpret_cast<float4*>(tn.residual + size_t(row) * H) + 2 * c;
+          float4 x = res[0], y = res[1];
+          x.x += acc[0]; x.y += acc[1]; x.z += acc[2]; x.w += acc[3];
+          y.x += acc[4]; y.y += acc[5]; y.z += acc[6]; y.w += acc[7];
+          res[0] = x;
+          res[1] = y;
+          vals[j][0] = x.x; vals[j][1] = x.y; vals[j][2] = x.z; vals[j][3] = x.w;
+          vals[j][4] = y.x; vals[j][5] = y.y; vals[j][6] = y.z; vals[j][7] = y.w;
+#pragma unroll
+          for (int i = 0; i < 8; ++i) ss += vals[j][i] * vals[j][i];
+        }
+      }
+      if (tn.xnorm != nullptr) {
+        ss = warp_sum(ss);
+        if ((et & 31) == 0) red[et >> 5] = ss;
+        epi_bar(1);
+        float tot = 0.f;
+#pragma unroll
+        for (int i = 0; i < 20; ++i) tot += red[i];
+        epi_bar(1);                                        // red is reused by the next row
+        const float inv = rsqrtf(tot / float(H) + tn.eps);
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          const int c = et + j * 640;
+          if (c < nch) {
+            const uint4 wr = reinterpret_cast<const uint4*>(tn.norm_w)[c];
+            const __half2* wh = reinterpret_cast<const __half2*>(&wr);
+            uint4 pk;
+            uint32_t* po = reinterpret_cast<uint32_t*>(&pk);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const float2 w2 = __half22float2(wh[i]);
+              po[i] = pack_half2(vals[j][2 * i] * inv * w2.x, vals[j][2 * i + 1] * inv * w2.y);
+            }
+            reinterpret_cast<uint4*>(tn.xnorm + size_t(row) * H)[c] = pk;
+          }
+        }
+      }
+    }
+  }
+  // the last CTA of the launch moves the running total on (every CTA that reads it has done so by then)
+  epi_bar(1);
+  if (et == 0) {
+    __threadfence();
+    const uint32_t t = atomicAdd(tn.state + 2, 1u);
+    if (t == uint32_t(n_cta) - 1u) {
+      tn.state[pt.slot] += tn.units_total;
+      tn.state[2] = 0u;
+      __threadfence();
+    }
+  }
+}
+
+template <int NT, int EPI, bool W8>
 __global__ void __launch_bounds__(kDecThreads, 1)
 gemm_w4_dec_kernel(const __grid_constant__ CUtensorMap tmap_x, const DecArgs a) {
-  using Cfg = DecCfg<NT>;
-  constexpr int SX = kDecSX, SW = kDecSW;
+  using Cfg = DecCfg<NT, W8>;
+  constexpr int SX = Cfg::kSX, SW = Cfg::kSW;
+  constexpr int kChunk = Cfg::kChunk;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* x_ring = smem;                                        // [SX][2][NT*128]
@@ -623,12 +826,12 @@ gemm_w4_dec_kernel(const __grid_constant__ CUtensorMap tmap_x, const DecArgs a) 
     // the first ring-full of weight chunks is requested before the CTA has even finished its set-up
     int pair = pair0, k = k_first;
     for (int s = 0; s < n_steps && s < SW; ++s) {
-      const uint8_t* src = a.w + (size_t(2 * pair) * ks + k) * kW4ChunkBytes;
-      mbar_arrive_expect_tx(&bars->w_full[0][s], kW4ChunkBytes);
-      bulk_g2s(w_ring + s * kW4ChunkBytes, src, kW4ChunkBytes, &bars->w_full[0][s]);
+      const uint8_t* src = a.w + (size_t(2 * pair) * ks + k) * kChunk;
+      mbar_arrive_expect_tx(&bars->w_full[0][s], kChunk);
+      bulk_g2s(w_ring + s * kChunk, src, kChunk, &bars->w_full[0][s]);
       if (s < n_real1) {
-        mbar_arrive_expect_tx(&bars->w_full[1][s], kW4ChunkBytes);
-        bulk_g2s(w_ring + (SW + s) * kW4ChunkBytes, src + size_t(ks) * kW4ChunkBytes, kW4ChunkBytes,
+        mbar_arrive_expect_tx(&bars->w_full[1][s], kChunk);
+        bulk_g2s(w_ring + (SW + s) * kChunk, src + size_t(ks) * kChunk, kChunk,
                  &bars->w_full[1][s]);
       }
       if (++k == ks) {
@@ -757,14 +960,14 @@ gemm_w4_dec_kernel(const __grid_constant__ CUtensorMap tmap_x, const DecArgs a) 
         const int sw = s + SW;
         if (sw < n_steps) {
           if (!mbar_wait(&bars->w_empty[0][wslot], wph, abort_flag, a.status, 1, sw)) break;
-          const uint8_t* src = a.w + (size_t(2 * pair_w) * ks + k_w) * kW4ChunkBytes;
-          mbar_arrive_expect_tx(&bars->w_full[0][wslot], kW4ChunkBytes);
-          bulk_g2s(w_ring + wslot * kW4ChunkBytes, src, kW4ChunkBytes, &bars->w_full[0][wslot]);
+          const uint8_t* src = a.w + (size_t(2 * pair_w) * ks + k_w) * kChunk;
+          mbar_arrive_expect_tx(&bars->w_full[0][wslot], kChunk);
+          bulk_g2s(w_ring + wslot * kChunk, src, kChunk, &bars->w_full[0][wslot]);
           ++cnt0;
           if (sw < n_real1) {
             if (!mbar_wait(&bars->w_empty[1][wslot], wph, abort_flag, a.status, 1, sw)) break;
-            mbar_arrive_expect_tx(&bars->w_full[1][wslot], kW4ChunkBytes);
-            bulk_g2s(w_ring + (SW + wslot) * kW4ChunkBytes, src + size_t(ks) * kW4ChunkBytes, kW4ChunkBytes,
+            mbar_arrive_expect_tx(&bars->w_full[1][wslot], kChunk);
+            bulk_g2s(w_ring + (SW + wslot) * kChunk, src + size_t(ks) * kChunk, kChunk,
                      &bars->w_full[1][wslot]);
             ++cnt1;
           }
@@ -816,33 +1019,63 @@ gemm_w4_dec_kernel(const __grid_constant__ CUtensorMap tmap_x, const DecArgs a) 
         if (c == sub) tacc[6] = clock64() - t_entry;
 #endif
         DTICK(t1);
-        const uint8_t* chunk = w_ring + (p * SW + slot) * kW4ChunkBytes;
-        uint4 pk[4];
-#pragma unroll
-        for (int p4 = 0; p4 < 4; ++p4) pk[p4] = *reinterpret_cast<const uint4*>(chunk + (p4 * 128 + row) * 16);
-        const __half2 sz = *reinterpret_cast<const __half2*>(chunk + 8192 + row * 4);
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&bars->w_empty[p][slot]);   // the chunk is in registers: its slot may be refilled
-        const __half2 s2 = __half2half2(__low2half(sz)), z2 = __half2half2(__high2half(sz));
+        const uint8_t* chunk = w_ring + (p * SW + slot) * kChunk;
         uint32_t o[32];
-        // the first half is dequantised while the MMAs that still read this TMEM slot (chunk c-2) run
-        dec_dequant_half(pk[0], pk[1], s2, z2, o);
-        DACC(1, t1);
-        DTICK(t2);
-        if (c >= 2) {
-          if (!mbar_wait(&bars->slot_free[p][sub], sph, abort_flag, a.status, 7, c)) break;
-          sph ^= 1;
-          // the MMAs of chunk c-2 are complete: its activation stage has one reader less
-          if (q == 0 && lane == 0) mbar_arrive(&bars->x_empty[xst]);
-          xst += 2;
-          if (xst >= SX) xst -= SX;
+        if constexpr (!W8) {
+          uint4 pk[4];
+#pragma unroll
+          for (int p4 = 0; p4 < 4; ++p4) pk[p4] = *reinterpret_cast<const uint4*>(chunk + (p4 * 128 + row) * 16);
+          const __half2 sz = *reinterpret_cast<const __half2*>(chunk + 8192 + row * 4);
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bars->w_empty[p][slot]); // the chunk is in registers: its slot may be refilled
+          const __half2 s2 = __half2half2(__low2half(sz)), z2 = __half2half2(__high2half(sz));
+          // the first half is dequantised while the MMAs that still read this TMEM slot (chunk c-2) run
+          dec_dequant_half(pk[0], pk[1], s2, z2, o);
+          DACC(1, t1);
+          DTICK(t2);
+          if (c >= 2) {
+            if (!mbar_wait(&bars->slot_free[p][sub], sph, abort_flag, a.status, 7, c)) break;
+            sph ^= 1;
+            // the MMAs of chunk c-2 are complete: its activation stage has one reader less
+            if (q == 0 && lane == 0) mbar_arrive(&bars->x_empty[xst]);
+            xst += 2;
+            if (xst >= SX) xst -= SX;
+          }
+          DACC(2, t2);
+          DTICK(t3);
+          tc_fence_after_sync();
+          ZSE_TMEM_ST_X32(dst, o);
+          dec_dequant_half(pk[2], pk[3], s2, z2, o);
+          ZSE_TMEM_ST_X32(dst + 32, o);
+        } else {
+          // INT8: a row is 128 bytes in eight 16-byte parts; K 0..63 first, the rest after the first TMEM store
+          uint4 pk[4];
+#pragma unroll
+          for (int p4 = 0; p4 < 4; ++p4) pk[p4] = *reinterpret_cast<const uint4*>(chunk + (p4 * 128 + row) * 16);
+          const __half2 s2 = __half2half2(*reinterpret_cast<const __half*>(chunk + 16384 + row * 2));
+#pragma unroll
+          for (int p4 = 0; p4 < 4; ++p4) dec_dequant_w8_part(pk[p4], s2, o + p4 * 8);
+          DACC(1, t1);
+          DTICK(t2);
+          if (c >= 2) {
+            if (!mbar_wait(&bars->slot_free[p][sub], sph, abort_flag, a.status, 7, c)) break;
+            sph ^= 1;
+            if (q == 0 && lane == 0) mbar_arrive(&bars->x_empty[xst]);
+            xst += 2;
+            if (xst >= SX) xst -= SX;
+          }
+          DACC(2, t2);
+          DTICK(t3);
+          tc_fence_after_sync();
+          ZSE_TMEM_ST_X32(dst, o);
+#pragma unroll
+          for (int p4 = 0; p4 < 4; ++p4) pk[p4] = *reinterpret_cast<const uint4*>(chunk + ((4 + p4) * 128 + row) * 16);
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bars->w_empty[p][slot]); // the chunk is in registers: its slot may be refilled
+#pragma unroll
+          for (int p4 = 0; p4 < 4; ++p4) dec_dequant_w8_part(pk[p4], s2, o + p4 * 8);
+          ZSE_TMEM_ST_X32(dst + 32, o);
         }
-        DACC(2, t2);
-        DTICK(t3);
-        tc_fence_after_sync();
-        ZSE_TMEM_ST_X32(dst, o);
-        dec_dequant_half(pk[2], pk[3], s2, z2, o);
-        ZSE_TMEM_ST_X32(dst + 32, o);
         DACC(3, t3);
         DTICK(t4);
         tc_wait_st();
@@ -944,6 +1177,12 @@ gemm_w4_dec_kernel(const __grid_constant__ CUtensorMap tmap_x, const DecArgs a) 
 #ifdef ZSE_DEC_TIMING
     if (warp >= kDecEpiWarp0) tacc[4] = clock64() - t_entry;
 #endif
+    if (EPI == kDecAllReduceNorm && warp >= kDecDqWarp0) {
+      constexpr int G = Cfg::kGranules;
+      const uint32_t units = seg < G ? uint32_t(ntp * ((G - seg + S - 1) / S)) : 0u;
+      // the staging buffer of the stream plan is idle in the split plan: scratch for the block reduction
+      dec_allreduce_norm_tail(a, bars, stage, cta, n_cta, units, split_ok, wi * 128 + (warp & 3) * 32 + lane);
+    }
   }
 
   // ---------------------------------------------------------------------- exit
@@ -1000,10 +1239,10 @@ static DecPlan plan_dec(int n_pairs, int k_stages, int sm_count) {
   return p;
 }
 
-template <int NT, int EPI>
+template <int NT, int EPI, bool W8>
 static int launch_dec(const CUtensorMap& tx, const DecArgs& a, int n_cta, cudaStream_t st) {
-  auto kern = gemm_w4_dec_kernel<NT, EPI>;
-  constexpr int smem = DecCfg<NT>::kSmemBytes;
+  auto kern = gemm_w4_dec_kernel<NT, EPI, W8>;
+  constexpr int smem = DecCfg<NT, W8>::kSmemBytes;
   static bool attr_done[64] = {};
   int dev = 0;
   cudaGetDevice(&dev);
@@ -1040,8 +1279,8 @@ static int dec_max_clusters(int S) {
     return kTable[S];
   }
   if (cached[dev][S] == 0) {
-    auto kern = gemm_w4_dec_kernel<64, kDecF16>;
-    constexpr int smem = DecCfg<64>::kSmemBytes;
+    auto kern = gemm_w4_dec_kernel<64, kDecF16, false>;
+    constexpr int smem = DecCfg<64, false>::kSmemBytes;
     int n = 0;
     cudaLaunchConfig_t cfg = {};
     cudaLaunchAttribute attr[1];
@@ -1064,13 +1303,14 @@ static int dec_max_clusters(int S) {
   return cached[dev][S];
 }
 
-template <int NT>
+template <int NT, bool W8>
 static int launch_dec_epi(int epi, const CUtensorMap& tx, const DecArgs& a, int n_cta, cudaStream_t st) {
   switch (epi) {
-    case kDecF16: return launch_dec<NT, kDecF16>(tx, a, n_cta, st);
-    case kDecSwiGLU: return launch_dec<NT, kDecSwiGLU>(tx, a, n_cta, st);
-    case kDecF32: return launch_dec<NT, kDecF32>(tx, a, n_cta, st);
-    case kDecQkvRope: return launch_dec<NT, kDecQkvRope>(tx, a, n_cta, st);
+    case kDecF16: return launch_dec<NT, kDecF16, W8>(tx, a, n_cta, st);
+    case kDecSwiGLU: return launch_dec<NT, kDecSwiGLU, W8>(tx, a, n_cta, st);
+    case kDecF32: return launch_dec<NT, kDecF32, W8>(tx, a, n_cta, st);
+    case kDecQkvRope: return launch_dec<NT, kDecQkvRope, W8>(tx, a, n_cta, st);
+    case kDecAllReduceNorm: return launch_dec<NT, kDecAllReduceNorm, W8>(tx, a, n_cta, st);
     default: return ZSE_ERR_SHAPE;
   }
 }
@@ -1119,11 +1359,13 @@ extern "C" int zse_gemm_w4_dec_supported(int M, int N, int K, int epilogue) {
   if (M <= 0 || M > 64 || K <= 0 || K % kW4StageK != 0 || N <= 0) return 0;
   if (epilogue == kDecSwiGLU) return (N % 8) == 0 ? 1 : 0;
   if (epilogue == kDecQkvRope) return (N % 128) == 0 ? 1 : 0;
+  if (epilogue == kDecAllReduceNorm) return (N % 8) == 0 && N <= 10240 ? 1 : 0;
   return (epilogue == kDecF16 || epilogue == kDecF32) && (N % 8) == 0 ? 1 : 0;
 }
 
-static int run_dec(const void* w_tiled, const void* x, int x_rows_cap, const void* bias, void* out, int M, int N,
-                   int K, int ldo, int epilogue, void* workspace, const DecRope* rope, void* status, void* stream) {
+static int run_dec(bool w8, const void* w_tiled, const void* x, int x_rows_cap, const void* bias, void* out, int M,
+                   int N, int K, int ldo, int epilogue, void* workspace, const DecRope* rope, void* status,
+                   void* stream, const DecTpNorm* tpn = nullptr) {
   if (M <= 0) return 0;
   if (!zse_gemm_w4_dec_supported(M, N, K, epilogue) || workspace == nullptr) return ZSE_ERR_SHAPE;
   if ((reinterpret_cast<uintptr_t>(out) & 15) || (reinterpret_cast<uintptr_t>(workspace) & 15) ||
@@ -1156,11 +1398,22 @@ static int run_dec(const void* w_tiled, const void* x, int x_rows_cap, const voi
   a.status = reinterpret_cast<Status*>(status);
   a.timing = g_dec_timing;
   if (rope != nullptr) a.rope = *rope;
+  if (epilogue == kDecAllReduceNorm) {
+    if (tpn == nullptr || p.split <= 0) return ZSE_ERR_SHAPE;      // the exchange is part of the split plan only
+    a.tpn = *tpn;
+    a.tpn.units_total = uint32_t(n_tiles) * uint32_t(nt / 8);
+  }
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   switch (nt) {
-    case 16: return launch_dec_epi<16>(epilogue, tx, a, p.n_cta, st);
-    case 32: return launch_dec_epi<32>(epilogue, tx, a, p.n_cta, st);
-    default: return launch_dec_epi<64>(epilogue, tx, a, p.n_cta, st);
+    case 16:
+      return w8 ? launch_dec_epi<16, true>(epilogue, tx, a, p.n_cta, st)
+                : launch_dec_epi<16, false>(epilogue, tx, a, p.n_cta, st);
+    case 32:
+      return w8 ? launch_dec_epi<32, true>(epilogue, tx, a, p.n_cta, st)
+                : launch_dec_epi<32, false>(epilogue, tx, a, p.n_cta, st);
+    default:
+      return w8 ? launch_dec_epi<64, true>(epilogue, tx, a, p.n_cta, st)
+                : launch_dec_epi<64, false>(epilogue, tx, a, p.n_cta, st);
   }
 }
 
@@ -1168,18 +1421,26 @@ static int run_dec(const void* w_tiled, const void* x, int x_rows_cap, const voi
 extern "C" int zse_gemm_w4_dec(const void* w_tiled, const void* x, int x_rows_cap, const void* bias, void* out, int M,
                                int N, int K, int ldo, int epilogue, void* workspace, void* status, void* stream) {
   if (epilogue != kDecF16 && epilogue != kDecSwiGLU && epilogue != kDecF32) return ZSE_ERR_SHAPE;
-  return run_dec(w_tiled, x, x_rows_cap, bias, out, M, N, K, ldo, epilogue, workspace, nullptr, status, stream);
+  return run_dec(false, w_tiled, x, x_rows_cap, bias, out, M, N, K, ldo, epilogue, workspace, nullptr, status, stream);
+}
+
+// The same for INT8 weights (symmetric groups of 128, tiled by zse_repack_w8): the weights stay 8 bits wide in memory
+// and are expanded in registers on their way to the tensor cores
+// (reference: tiled_dequant_matmul_int8, zse-engine/zse_engine/orchestrator/kernels.py:1195-1249).
+extern "C" int zse_gemm_w8_dec(const void* w_tiled, const void* x, int x_rows_cap, const void* bias, void* out, int M,
+                               int N, int K, int ldo, int epilogue, void* workspace, void* status, void* stream) {
+  if (epilogue != kDecF16 && epilogue != kDecSwiGLU && epilogue != kDecF32) return ZSE_ERR_SHAPE;
+  return run_dec(true, w_tiled, x, x_rows_cap, bias, out, M, N, K, ldo, epilogue, workspace, nullptr, status, stream);
 }
 
 // Fused QKV projection of a decode-sized pass, head_dim 128, full rotary: bias, rotate-half RoPE (cos/sin table
 // [max_position][64] of float2) and the K/V rows stored straight into the paged cache
 // (kv_layer [blocks][2][nkv][block_size][128], slot = block * block_size + offset, -1 = skip); `qkv_out` [M, ldo]
 // receives the rotated q heads (columns 0 .. nh*128).
-extern "C" int zse_gemm_w4_dec_qkv_rope(const void* w_tiled, const void* x, int x_rows_cap, const void* bias,
-                                        void* qkv_out, int ldo, int M, int K, int nh, int nkv, void* kv_layer,
-                                        int block_size, const void* positions_i32, const void* slots_i64,
-                                        const void* cos_sin_f32x2, int max_position, void* workspace, void* status,
-                                        void* stream) {
+static int run_qkv_rope(bool int8_weights, const void* w_tiled, const void* x, int x_rows_cap, const void* bias,
+                        void* qkv_out, int ldo, int M, int K, int nh, int nkv, void* kv_layer, int block_size,
+                        const void* positions_i32, const void* slots_i64, const void* cos_sin_f32x2, int max_position,
+                        void* workspace, void* status, void* stream) {
   if (nh <= 0 || nkv <= 0 || block_size <= 0 || max_position <= 0 || kv_layer == nullptr || positions_i32 == nullptr ||
       slots_i64 == nullptr || cos_sin_f32x2 == nullptr)
     return ZSE_ERR_SHAPE;
@@ -1194,6 +1455,52 @@ extern "C" int zse_gemm_w4_dec_qkv_rope(const void* w_tiled, const void* x, int 
   rp.nkv = nkv;
   rp.block_size = block_size;
   rp.max_position = max_position;
-  return run_dec(w_tiled, x, x_rows_cap, bias, qkv_out, M, (nh + 2 * nkv) * 128, K, ldo, kDecQkvRope, workspace, &rp,
-                 status, stream);
+  return run_dec(int8_weights, w_tiled, x, x_rows_cap, bias, qkv_out, M, (nh + 2 * nkv) * 128, K, ldo, kDecQkvRope,
+                 workspace, &rp, status, stream);
+}
+
+// Row-parallel projection + tensor-parallel all-reduce + residual add + RMSNorm in ONE kernel (see DecTpNorm):
+//   residual[M, H] += sum over ranks of x W^T;   xnorm = RMSNorm(residual) * norm_w
+// `ctx` is a tensor-parallel context with the push buffers set (zse_tp_ctx_set_push); N must be its hidden size and M
+// at most its row capacity.  tp = 1 works as well (no peers: the kernel then only fuses projection, residual and
+// norm).  `slot` alternates between consecutive calls.  rank_override >= 0 plays another rank (single-GPU tests).
+// Replaces ncclAllReduce + residual_add + rmsnorm of the reference
+// (zse-engine/zse_engine/orchestrator/model_runner.py:2622-2635,2694-2705).
+extern "C" int zse_tp_gemm_dec_allreduce_norm(void* ctx, const void* w_tiled, int int8_weights, const void* x,
+                                              int x_rows_cap, int M, int N, int K, int slot, int use_multimem,
+                                              int rank_override, void* residual, const void* norm_w, void* xnorm,
+                                              float eps, void* workspace, void* status, void* stream) {
+  DecTpNorm tn{};
+  if (int rc = tp_fill_push_table(ctx, slot, use_multimem != 0, rank_override, &tn.push)) return rc;
+  tn.state = tp_push_state(ctx, rank_override);
+  if (tn.state == nullptr || residual == nullptr || norm_w == nullptr) return ZSE_ERR_SHAPE;
+  if (N != tn.push.H || M > tn.push.m_cap) return ZSE_ERR_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(residual) & 15) || (reinterpret_cast<uintptr_t>(norm_w) & 15) ||
+      (reinterpret_cast<uintptr_t>(xnorm) & 15))
+    return ZSE_ERR_ALIGN;
+  tn.residual = reinterpret_cast<float*>(residual);
+  tn.norm_w = reinterpret_cast<const __half*>(norm_w);
+  tn.xnorm = reinterpret_cast<__half*>(xnorm);
+  tn.eps = eps;
+  // `out` is not written by this epilogue; the residual pointer stands in for the alignment check
+  return run_dec(int8_weights != 0, w_tiled, x, x_rows_cap, nullptr, residual, M, N, K, N, kDecAllReduceNorm, workspace,
+                 nullptr, status, stream, &tn);
+}
+
+extern "C" int zse_gemm_w4_dec_qkv_rope(const void* w_tiled, const void* x, int x_rows_cap, const void* bias,
+                                        void* qkv_out, int ldo, int M, int K, int nh, int nkv, void* kv_layer,
+                                        int block_size, const void* positions_i32, const void* slots_i64,
+                                        const void* cos_sin_f32x2, int max_position, void* workspace, void* status,
+                                        void* stream) {
+  return run_qkv_rope(false, w_tiled, x, x_rows_cap, bias, qkv_out, ldo, M, K, nh, nkv, kv_layer, block_size,
+                      positions_i32, slots_i64, cos_sin_f32x2, max_position, workspace, status, stream);
+}
+
+extern "C" int zse_gemm_w8_dec_qkv_rope(const void* w_tiled, const void* x, int x_rows_cap, const void* bias,
+                                        void* qkv_out, int ldo, int M, int K, int nh, int nkv, void* kv_layer,
+                                        int block_size, const void* positions_i32, const void* slots_i64,
+                                        const void* cos_sin_f32x2, int max_position, void* workspace, void* status,
+                                        void* stream) {
+  return run_qkv_rope(true, w_tiled, x, x_rows_cap, bias, qkv_out, ldo, M, K, nh, nkv, kv_layer, block_size,
+                      positions_i32, slots_i64, cos_sin_f32x2, max_position, workspace, status, stream);
 }

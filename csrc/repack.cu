@@ -79,6 +79,76 @@ __global__ void dequant_w8_kernel(const int8_t* __restrict__ q, const __half* __
   if (i < n) out[i] = __float2half_rn(float(q[i]) * __half2float(scales[i / gs]));
 }
 
+// ---- INT8 (symmetric, groups of 128 along K, fp16 scale) -----------------------------------------------------
+// Tiled chunk (n_tile, k_stage) = 16640 bytes:
+//   [part:8][row:128][16 B]   int8 values of K = k_stage*128 + part*16 + (0..15) of tile row `row`
+//   [row:128] scale fp16
+// Rows past N are zero with scale 0.  interleave_rows as for INT4 (64 gate rows + 64 up rows per tile).
+__global__ void repack_w8_kernel(const int8_t* __restrict__ q, const __half* __restrict__ scales,
+                                 uint8_t* __restrict__ out, int N, int K, int interleave_rows) {
+  const int ks = blockIdx.x, nt = blockIdx.y;
+  const int k_stages = K / 128;
+  const int r = threadIdx.x & 127, h = threadIdx.x >> 7;       // h: parts 4h .. 4h+3
+  int src_row;
+  bool valid;
+  if (interleave_rows > 0) {
+    const int local = nt * 64 + (r & 63);
+    valid = local < interleave_rows;
+    src_row = (r < 64 ? 0 : interleave_rows) + local;
+  } else {
+    src_row = nt * 128 + r;
+    valid = src_row < N;
+  }
+  uint8_t* chunk = out + (size_t(nt) * k_stages + ks) * 16640;
+  const uint4* src = reinterpret_cast<const uint4*>(q + size_t(src_row) * K + ks * 128) + h * 4;
+#pragma unroll
+  for (int p = 0; p < 4; ++p) {
+    const uint4 v = valid ? src[p] : make_uint4(0, 0, 0, 0);
+    *reinterpret_cast<uint4*>(chunk + ((h * 4 + p) * 128 + r) * 16) = v;
+  }
+  if (h == 0)
+    *reinterpret_cast<__half*>(chunk + 16384 + r * 2) =
+        valid ? scales[size_t(src_row) * k_stages + ks] : __ushort_as_half(0);
+}
+
+// Tiled INT8 chunks -> dense fp16 [N, K] row-major (gate rows then up rows for an interleaved tensor): what a pass of
+// more than 64 tokens runs through the fp16 GEMM, into a scratch buffer that every layer shares.
+__global__ void dequant_w8_tiled_kernel(const uint8_t* __restrict__ tiled, __half* __restrict__ out, int N, int K,
+                                        int interleave_rows) {
+  const int ks = blockIdx.x, nt = blockIdx.y;
+  const int k_stages = K / 128;
+  const int r = threadIdx.x & 127, h = threadIdx.x >> 7;
+  int dst_row;
+  bool valid;
+  if (interleave_rows > 0) {
+    const int local = nt * 64 + (r & 63);
+    valid = local < interleave_rows;
+    dst_row = (r < 64 ? 0 : interleave_rows) + local;
+  } else {
+    dst_row = nt * 128 + r;
+    valid = dst_row < N;
+  }
+  if (!valid) return;
+  const uint8_t* chunk = tiled + (size_t(nt) * k_stages + ks) * 16640;
+  const float s = __half2float(*reinterpret_cast<const __half*>(chunk + 16384 + r * 2));
+  __half* dst = out + size_t(dst_row) * K + ks * 128 + h * 64;
+#pragma unroll
+  for (int p = 0; p < 4; ++p) {
+    const uint4 v = *reinterpret_cast<const uint4*>(chunk + ((h * 4 + p) * 128 + r) * 16);
+    const int8_t* b = reinterpret_cast<const int8_t*>(&v);
+    uint4 lo, hi;
+    uint32_t* l = reinterpret_cast<uint32_t*>(&lo);
+    uint32_t* u = reinterpret_cast<uint32_t*>(&hi);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      l[i] = pack_half2(float(b[2 * i]) * s, float(b[2 * i + 1]) * s);
+      u[i] = pack_half2(float(b[8 + 2 * i]) * s, float(b[8 + 2 * i + 1]) * s);
+    }
+    reinterpret_cast<uint4*>(dst + p * 16)[0] = lo;
+    reinterpret_cast<uint4*>(dst + p * 16)[1] = hi;
+  }
+}
+
 // One warp per group of 128 fp16 values -> 64 bytes + scale + zero (round to nearest, like the python writer).
 __global__ void quantize_w4_kernel(const __half* __restrict__ w, uint8_t* __restrict__ packed,
                                    __half* __restrict__ scales, __half* __restrict__ zeros, int64_t n_groups) {
@@ -122,6 +192,36 @@ extern "C" int zse_repack_w4(const void* packed, const void* scales, const void*
   repack_w4_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
       reinterpret_cast<const uint8_t*>(packed), reinterpret_cast<const __half*>(scales),
       reinterpret_cast<const __half*>(zeros), reinterpret_cast<uint8_t*>(out_tiled), N, K, interleave_rows);
+  return cudaGetLastError() == cudaSuccess ? 0 : ZSE_ERR_LAUNCH;
+}
+
+extern "C" int64_t zse_w8_tiled_bytes(int N, int K) {
+  return int64_t((N + 127) / 128) * (K / 128) * 16640;
+}
+
+// Row-major INT8 [N, K] + fp16 scales [N, K/128] -> tiled chunks (interleave_rows as in zse_repack_w4).
+extern "C" int zse_repack_w8(const void* q, const void* scales, void* out_tiled, int N, int K, int interleave_rows,
+                             void* stream) {
+  if (K % 128 != 0 || N <= 0) return ZSE_ERR_SHAPE;
+  if (interleave_rows > 0 && N != 2 * interleave_rows) return ZSE_ERR_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(q) & 15) || (reinterpret_cast<uintptr_t>(out_tiled) & 15)) return ZSE_ERR_ALIGN;
+  const int n_tiles = interleave_rows > 0 ? (interleave_rows + 63) / 64 : (N + 127) / 128;
+  dim3 grid(K / 128, n_tiles);
+  repack_w8_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const int8_t*>(q), reinterpret_cast<const __half*>(scales),
+      reinterpret_cast<uint8_t*>(out_tiled), N, K, interleave_rows);
+  return cudaGetLastError() == cudaSuccess ? 0 : ZSE_ERR_LAUNCH;
+}
+
+// Tiled INT8 chunks -> fp16 [N, K] row-major.
+extern "C" int zse_dequant_w8_tiled(const void* tiled, void* out_f16, int N, int K, int interleave_rows,
+                                    void* stream) {
+  if (K % 128 != 0 || N <= 0) return ZSE_ERR_SHAPE;
+  if (reinterpret_cast<uintptr_t>(out_f16) & 15) return ZSE_ERR_ALIGN;
+  const int n_tiles = interleave_rows > 0 ? (interleave_rows + 63) / 64 : (N + 127) / 128;
+  dim3 grid(K / 128, n_tiles);
+  dequant_w8_tiled_kernel<<<grid, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const uint8_t*>(tiled), reinterpret_cast<__half*>(out_f16), N, K, interleave_rows);
   return cudaGetLastError() == cudaSuccess ? 0 : ZSE_ERR_LAUNCH;
 }
 

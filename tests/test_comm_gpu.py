@@ -146,6 +146,95 @@ def test_gemm_push_exchange_emulated_ranks(ops, tp, M, H, Kr):
     native.tp_ctx_destroy(ctx)
 
 
+def _k1_ctx(tp, m_cap, H):
+    from zse_b200.ops import native
+    ctx, keep = _emulated_ctx(tp, m_cap, H)
+    inbox = [torch.zeros(2 * tp * m_cap * H, dtype=torch.float16, device="cuda") for _ in range(tp)]
+    arrive = [torch.zeros(2 * tp, dtype=torch.int32, device="cuda") for _ in range(tp)]
+    state = [torch.zeros(4, dtype=torch.int32, device="cuda") for _ in range(tp)]
+    native.tp_ctx_set_push(ctx, m_cap, [t.data_ptr() for t in inbox], 0, [t.data_ptr() for t in arrive], 0,
+                           [t.data_ptr() for t in state])
+    return ctx, (keep, inbox, arrive, state)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M,H,K,int8", [(1, 1024, 512, False), (7, 1024, 1792, False), (64, 5120, 640, False),
+                                        (33, 2560, 1024, True), (64, 5120, 1792, False)])
+def test_projection_residual_norm_in_one_kernel_single_rank(ops, M, H, K, int8):
+    """kDecAllReduceNorm with one rank: projection, residual add and RMSNorm are one launch (no peers to wait for)."""
+    from zse_b200.ops import native
+    from test_kernels_gpu import _w4_parts_gpu
+    from test_gemm_dec_gpu import _parts8
+    ctx, keep = _k1_ctx(1, 64, H)
+    status = native.Status("cuda")
+    ws = native.gemm_w4_dec_workspace("cuda", ops.sm_count)
+    part, wd = _parts8(H, K, 3) if int8 else _w4_parts_gpu(H, K, 3)
+    w = ops.make_linear([part], K, 128)
+    assert w.kind == ("w8t" if int8 else "w4t")
+    x = (torch.randn(M, K, device="cuda") * 0.5).half()
+    wn = (1 + 0.1 * torch.randn(H, device="cuda")).half()
+    res0 = torch.randn(M + 2, H, device="cuda")
+    residual = res0.clone()
+    out = torch.full((M + 2, H), 3.0, dtype=torch.float16, device="cuda")
+    want = res0[:M].clone()
+    for call in range(3):
+        native.tp_gemm_dec_allreduce_norm(ctx, w.data, int8, x, M, M, H, K, call & 1, False, residual, wn, out, 1e-6,
+                                          ws, status.ptr)
+        torch.cuda.synchronize()
+        status.check()
+        want = want + (x.float() @ wd.T).half().float()
+        assert _rel_close(residual[:M], want), call
+        assert (out[:M].float() - ref.rmsnorm(want, wn, 1e-6).float()).abs().max() < 3e-2
+    assert torch.equal(residual[M:], res0[M:]) and torch.all(out[M:] == 3.0)      # rows past M untouched
+    native.tp_ctx_destroy(ctx)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("tp,M,H,K", [(2, 5, 1024, 512), (4, 64, 1024, 1024), (8, 40, 5120, 640)])
+def test_one_kernel_all_reduce_with_peers_that_have_delivered(ops, tp, M, H, K):
+    """The multi-rank data path on one GPU without any kernel waiting for another: this rank's launch finds the other
+    ranks' rows already in its inbox and their counters already at the target (written here by the host), sends its
+    own rows to every inbox, and must add all tp sources in rank order."""
+    from zse_b200.ops import native
+    from test_kernels_gpu import _w4_parts_gpu
+    m_cap = 64
+    ctx, (keep, inbox, arrive, state) = _k1_ctx(tp, m_cap, H)
+    status = native.Status("cuda")
+    ws = native.gemm_w4_dec_workspace("cuda", ops.sm_count)
+    me = 1 % tp
+    part, wd = _w4_parts_gpu(H, K, 11)
+    w = ops.make_linear([part], K, 128)
+    x = (torch.randn(M, K, device="cuda") * 0.5).half()
+    wn = (1 + 0.1 * torch.randn(H, device="cuda")).half()
+    res0 = torch.randn(M, H, device="cuda")
+    residual = res0.clone()
+    out = torch.zeros(M, H, dtype=torch.float16, device="cuda")
+    nt = 16 if M <= 16 else 32 if M <= 32 else 64
+    units = (H // 128) * (nt // 8)
+    want = res0.clone()
+    for call in range(4):
+        slot = call & 1
+        peers = {r: (torch.randn(M, H, device="cuda") * 0.3).half() for r in range(tp) if r != me}
+        box = inbox[me].view(2, tp, m_cap, H)
+        for r, rows in peers.items():
+            box[slot, r, :M] = rows
+            arrive[me].view(2, tp)[slot, r] += units                       # "rank r has delivered"
+        native.tp_gemm_dec_allreduce_norm(ctx, w.data, False, x, M, M, H, K, slot, False, residual, wn, out, 1e-6, ws,
+                                          status.ptr, rank_override=me)
+        torch.cuda.synchronize()
+        status.check()
+        mine = (x.float() @ wd.T).half().float()
+        want = want + mine + sum(p.float() for p in peers.values())
+        assert _rel_close(residual, want), call
+        assert (out.float() - ref.rmsnorm(want, wn, 1e-6).float()).abs().max() < 3e-2
+        # this rank's rows went to every rank's inbox and its units were counted in everywhere
+        for r in range(tp):
+            got = inbox[r].view(2, tp, m_cap, H)[slot, me, :M].float()
+            assert _rel_close(got, mine, tol=2e-3)
+            assert int(arrive[r].view(2, tp)[slot, me]) == units * (call // 2 + 1)
+    native.tp_ctx_destroy(ctx)
+
+
 def _rel_close(a, b, tol=4e-3):
     return float((a - b).abs().max()) <= tol * max(1.0, float(b.abs().max()))
 

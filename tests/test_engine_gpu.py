@@ -276,3 +276,23 @@ def test_cuda_graph_runner_replays_native_entry_points():
     r.destroy()
     assert not r.is_captured
     ops.check()
+
+
+def test_int8_model_runs_with_eight_bit_weights(tmp_path):
+    """An INT8 .zse model on the GPU: the layers stay 8 bits wide in device memory (tiled chunks for the decode kernel,
+    a shared fp16 scratch for large passes) and the tokens follow the fp32 oracle."""
+    path = str(tmp_path / "m8.zse")
+    synth.write_random_model(path, synth.shape_config("small-128", "int8"), seed=5)
+    eng = ZStreamerEngine(path, config=_cfg())
+    L = eng._model.layers[0]
+    assert {L.qkv.kind, L.o.kind, L.gate_up.kind, L.down.kind} == {"w8t"}
+    c = eng.model_config
+    dense_fp16 = 2 * c.hidden_size * (c.num_heads * c.head_dim)        # o_proj as fp16
+    assert L.o.nbytes < 0.6 * dense_fp16
+    oracle = OracleModel(ZSELoader(path))
+    prompts = _prompts(3, 20, 200, seed=41)                            # a prefill of more than 64 tokens among them
+    got = _run(eng, prompts, 10)
+    for g, p in zip(got, prompts):
+        w = oracle.greedy(p, 10)
+        assert g[:2] == w[:2] and _agreement(g, w) >= 0.7, (g, w)
+    eng.destroy()

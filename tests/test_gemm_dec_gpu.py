@@ -158,3 +158,50 @@ def test_dec_graph_replay_and_back_to_back(ops, ws):
         ops.check()
         for w, x, out, want, M, N, K, epi in cases:
             assert _rel(out, want) < 3e-3
+
+
+def _parts8(N, K, seed):
+    rng = np.random.default_rng(seed)
+    w = (rng.standard_normal((N, K)) * 0.02).astype(np.float32)
+    q, s = Q.quantize_int8_arrays(w, 128)
+    deq = (q.reshape(N, K // 128, 128).astype(np.float32) * s.reshape(N, K // 128, 1).astype(np.float32)).reshape(N, K)
+    part = {"dtype": "int8", "data": q.reshape(N, K), "scales": s.reshape(N, K // 128), "shape": (N, K)}
+    return part, torch.from_numpy(deq).cuda()
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 256, 256), (17, 640, 2048), (64, 1024, 4096), (48, 2560, 1792),
+                                   (64, 19456, 384), (64, 200, 256), (200, 512, 1024)])
+def test_int8_weights_stay_eight_bits_wide(ops, ws, M, N, K):
+    """INT8 layers: tiled 8-bit chunks on the device (a little over one byte per weight), expanded in registers by the
+    decode kernel; passes of more than 64 tokens expand into the shared fp16 scratch and take the fp16 GEMM."""
+    part, wd = _parts8(N, K, seed=N + M)
+    bias = (np.random.default_rng(1).standard_normal(N) * 0.1).astype(np.float16)
+    w = ops.make_linear([part], K, 128, bias)
+    assert w.kind == "w8t" and w.data.numel() == ((N + 127) // 128) * (K // 128) * 16640
+    x = (torch.randn(M + 3, K, device="cuda") * 0.5).half()
+    out = torch.full((M + 3, N), 7.0, dtype=torch.float16, device="cuda")
+    ops.linear(w, x, M, out)
+    planes = torch.zeros(8, M, N, dtype=torch.float32, device="cuda")
+    n_planes = ops.linear_partial(w, x, M, planes)
+    torch.cuda.synchronize()
+    ops.check()
+    want = ref.linear(x[:M], wd, torch.from_numpy(bias).cuda())
+    assert _rel(out[:M], want) < 2e-3, _rel(out[:M], want)
+    assert torch.all(out[M:] == 7.0)
+    got = planes.view(-1)[: n_planes * M * N].view(n_planes, M, N).sum(0)
+    assert _rel(got, x[:M].float() @ wd.T) < 2e-3
+
+
+@pytest.mark.parametrize("M,I,K", [(9, 192, 512), (64, 1728, 1024), (150, 320, 256)])
+def test_int8_gate_up_with_swiglu(ops, ws, M, I, K):
+    g, gd = _parts8(I, K, 3)
+    u, ud = _parts8(I, K, 4)
+    w = ops.make_linear([g, u], K, 128, swiglu=True)
+    assert w.kind == "w8t"
+    x = (torch.randn(M, K, device="cuda")).half()
+    out = torch.zeros(M, I, dtype=torch.float16, device="cuda")
+    ops.linear_swiglu(w, x, M, out)
+    torch.cuda.synchronize()
+    ops.check()
+    want = ref.swiglu(x.float() @ gd.T, x.float() @ ud.T)
+    assert _rel(out, want) < 3e-3, _rel(out, want)

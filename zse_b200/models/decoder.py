@@ -261,6 +261,8 @@ class DecoderModel:
         [+ ``add``: an fp16 addend, the LoRA update of that projection; single GPU only];
         xnorm = RMSNorm(residual) * weight."""
         ops, eps = self.ops, self.config.rms_norm_eps
+        if planes is None:               # the projection's own kernel reduced, added and normalised already
+            return
         if add is not None:
             if self.comm is not None:
                 raise RuntimeError("LoRA on a row-parallel projection is not wired for tensor parallelism")
@@ -277,10 +279,15 @@ class DecoderModel:
             planes = self.comm.all_reduce_partials(b.partials, planes, M)
             ops.add_rmsnorm(b.residual, b.partials, planes, None, weight, b.xnorm, M, eps)
 
-    def _row_parallel(self, w: LinearWeight, x: torch.Tensor, M: int, b: StepBuffers) -> int:
+    def _row_parallel(self, w: LinearWeight, x: torch.Tensor, M: int, b: StepBuffers, norm_w=None, add=None):
         """Row-parallel projection.  Returns the number of fp32 planes written to ``b.partials``, or - when the
-        tensor-parallel exchange ran inside the GEMM - minus the CTA count the consumer has to wait for."""
+        tensor-parallel exchange ran inside the GEMM - minus the CTA count the consumer has to wait for, or None when
+        one kernel did the projection, the all-reduce, the residual add and the RMSNorm with ``norm_w``."""
         comm = self.comm
+        if (comm is not None and norm_w is not None and add is None and getattr(comm, "fused_k1", False)
+                and comm.can_fuse_k1(self.ops, w, M)):
+            comm.linear_allreduce_norm(self.ops, w, x, M, b.residual, norm_w, b.xnorm, self.config.rms_norm_eps)
+            return None
         if (comm is not None and getattr(comm, "push", False) and w.K in self._uniform_shard_k()
                 and comm.can_push(w, M)):
             return -comm.linear_push(self.ops, w, x, M)
@@ -325,15 +332,16 @@ class DecoderModel:
             else:
                 ops.attn_prefill(b.qkv, kv[li], b.block_tables, b.cu_q, b.q_pos0, b.attn_out, num_seqs, M, max_q_len,
                                  p.num_heads, p.num_kv_heads, c.head_dim, bs, self.scale, window=self.window)
-            planes = self._row_parallel(L.o, b.attn_out, M, b)
             add = lora.delta(li, "o_proj", b.attn_out, b, M) if lora is not None else None
+            planes = self._row_parallel(L.o, b.attn_out, M, b, L.ln2, add)
             self._add_norm(b, planes, L.ln2, M, add)
             if lora is not None and (lora.has(li, "gate_proj") or lora.has(li, "up_proj")):
                 self._mlp_in_with_lora(li, L, b, M)
             else:
                 ops.linear_swiglu(L.gate_up, b.xnorm, M, b.act)
-            planes = self._row_parallel(L.down, b.act, M, b)
             add = lora.delta(li, "down_proj", b.act, b, M) if lora is not None else None
+            next_norm = self.layers[li + 1].ln1 if li + 1 < len(self.layers) else self.norm
+            planes = self._row_parallel(L.down, b.act, M, b, next_norm, add)
         self._add_norm(b, planes, self.norm, M, add)
         if n_logit_rows:
             torch.index_select(b.xnorm, 0, b.logit_rows[:n_logit_rows], out=b.xsel[:n_logit_rows])
@@ -347,7 +355,7 @@ class DecoderModel:
         gu = lora._scratch(b, "lora_gate_up", L.gate_up.N)
         plain = LinearWeight(L.gate_up.kind, L.gate_up.N, L.gate_up.K, L.gate_up.data, None, False, L.gate_up.nbytes)
         ops.linear(plain, b.xnorm, M, gu)
-        if L.gate_up.kind == "w4t" and L.gate_up.swiglu:    # tiles of 64 gate rows followed by their 64 up rows
+        if L.gate_up.kind in ("w4t", "w8t") and L.gate_up.swiglu:   # tiles of 64 gate rows followed by their 64 up rows
             if I % 64:
                 raise NotImplementedError("LoRA on gate/up needs an intermediate size that is a multiple of 64")
             t = gu[:M].view(M, I // 64, 2, 64)

@@ -21,7 +21,7 @@ EPI_F16, EPI_SWIGLU, EPI_PARTIAL = 0, 1, 2
 @dataclass
 class LinearWeight:
     """One (possibly fused / sharded) linear layer ready for the device."""
-    kind: str                  # "w4t" tiled INT4 | "f16" dense fp16 | "ref" fp32 (TorchOps)
+    kind: str                  # "w4t" tiled INT4 | "w8t" tiled INT8 | "f16" dense fp16 | "ref" fp32 (TorchOps)
     N: int                     # output rows as the kernel sees them (gate+up counted together for swiglu)
     K: int
     data: torch.Tensor
@@ -196,6 +196,19 @@ class CudaOps(TorchOps):
         from ..utils import env
         self.dec_mode = env.integer("ZSE_W4_DEC")
         self._dec_ws = None
+        # INT8 weights stay INT8 on the device (ZSE_W8_RESIDENT=0: expanded to fp16 at load, twice the memory)
+        self.int8_resident = env.flag("ZSE_W8_RESIDENT")
+        self._w8_scratch = None
+
+    def _w8_dense(self, w: "LinearWeight") -> torch.Tensor:
+        """fp16 [N, K] view of an INT8 weight in the scratch buffer that all layers share (rows: gate then up for a
+        fused gate/up tensor).  Valid until the next call."""
+        need = w.N * w.K
+        if self._w8_scratch is None or self._w8_scratch.numel() < need:
+            self._w8_scratch = torch.empty(need, dtype=torch.float16, device=self.device)
+        dense = self._w8_scratch[:need].view(w.N, w.K)
+        self.n.dequant_w8_tiled(w.data, dense, w.N, w.K, w.N // 2 if w.swiglu else 0)
+        return dense
 
     @property
     def dec_ws(self) -> torch.Tensor:
@@ -224,6 +237,22 @@ class CudaOps(TorchOps):
             out = torch.empty(n_tiles * (K // 128) * 8704, dtype=torch.uint8, device=self.device)
             n.repack_w4(packed, scales, zeros, out, N, K, inter)
             return LinearWeight("w4t", N, K, out, b, swiglu, out.numel())
+        # INT8 (symmetric groups of 128): kept 8 bits wide, tiled for the decode kernel.  Passes of more than 64 tokens
+        # expand the tensor into a scratch buffer that all layers share and run the fp16 GEMM on it.
+        w8_ok = (K % 128 == 0 and group_size == 128 and all(p["dtype"] == "int8" and "scales" in p for p in parts)
+                 and self.int8_resident)
+        if swiglu and w8_ok:
+            w8_ok = len(parts) == 2 and parts[0]["shape"][0] == parts[1]["shape"][0]
+        if w8_ok:
+            q = torch.cat([_np_to_dev(p["data"], self.device).reshape(p["shape"][0], K) for p in parts]).contiguous()
+            sc = torch.cat([_np_to_dev(p["scales"], self.device).reshape(p["shape"][0], K // 128)
+                            for p in parts]).contiguous()
+            N = q.shape[0]
+            inter = N // 2 if swiglu else 0
+            n_tiles = (inter + 63) // 64 if swiglu else (N + 127) // 128
+            out = torch.empty(n_tiles * (K // 128) * 16640, dtype=torch.uint8, device=self.device)
+            n.repack_w8(q.view(torch.int8) if q.dtype != torch.int8 else q, sc, out, N, K, inter)
+            return LinearWeight("w8t", N, K, out, b, swiglu, out.numel())
         # anything else becomes dense fp16 for the SS-mode kernel
         if all(p["dtype"] == "float16" for p in parts):      # already fp16: one copy, no fp32 round trip
             ws = [_np_to_dev(p["data"], self.device).reshape(tuple(p["shape"])) for p in parts]
@@ -236,7 +265,14 @@ class CudaOps(TorchOps):
     # ---- ops ------------------------------------------------------------------------------------------
     def linear(self, w, x, M, out, x_cap=None):
         cap = x.shape[0] if x_cap is None else x_cap
-        if (w.kind == "w4t" and (self.dec_mode & 4) and M <= 64 and out.stride(0) % 8 == 0
+        if w.kind == "w8t":
+            if M <= 64 and out.stride(0) % 8 == 0 and self.n.gemm_w4_dec_supported(M, w.N, w.K, EPI_F16):
+                self.n.gemm_w8_dec(w.data, x, cap, w.bias, out, M, w.N, w.K, out.stride(0), EPI_F16, self.dec_ws,
+                                   self.status.ptr)
+            else:
+                self.n.gemm_f16(self._w8_dense(w), w.N, x, cap, w.bias, out, M, w.N, w.K, out.stride(0), EPI_F16, 1,
+                                self.status.ptr)
+        elif (w.kind == "w4t" and (self.dec_mode & 4) and M <= 64 and out.stride(0) % 8 == 0
                 and self.n.gemm_w4_dec_supported(M, w.N, w.K, EPI_F16)):
             self.n.gemm_w4_dec(w.data, x, cap, w.bias, out, M, w.N, w.K, out.stride(0), EPI_F16, self.dec_ws,
                                self.status.ptr)
@@ -247,7 +283,17 @@ class CudaOps(TorchOps):
 
     def linear_swiglu(self, w, x, M, out, x_cap=None, gelu=False, tmp=None):
         cap = x.shape[0] if x_cap is None else x_cap
-        if (w.kind == "w4t" and not gelu and (self.dec_mode & 1) and M <= 64 and out.stride(0) % 8 == 0
+        if w.kind == "w8t":
+            if (not gelu and M <= 64 and out.stride(0) % 8 == 0
+                    and self.n.gemm_w4_dec_supported(M, w.N, w.K, EPI_SWIGLU)):
+                self.n.gemm_w8_dec(w.data, x, cap, None, out, M, w.N, w.K, out.stride(0), EPI_SWIGLU, self.dec_ws,
+                                   self.status.ptr)
+            else:
+                gu = torch.empty(M, w.N, dtype=torch.float16, device=self.device) if tmp is None else tmp
+                self.n.gemm_f16(self._w8_dense(w), w.N, x, cap, None, gu, M, w.N, w.K, gu.stride(0), EPI_F16, 1,
+                                self.status.ptr)
+                self.n.swiglu(gu, out, M, w.N // 2, gelu)
+        elif (w.kind == "w4t" and not gelu and (self.dec_mode & 1) and M <= 64 and out.stride(0) % 8 == 0
                 and self.n.gemm_w4_dec_supported(M, w.N, w.K, EPI_SWIGLU)):
             self.n.gemm_w4_dec(w.data, x, cap, None, out, M, w.N, w.K, out.stride(0), EPI_SWIGLU, self.dec_ws,
                                self.status.ptr)
@@ -272,6 +318,15 @@ class CudaOps(TorchOps):
         """fp32 result planes in ``partials`` [planes, M, N] (plane stride M*N); returns how many planes were written.
         The consumer (``add_rmsnorm`` / the tensor-parallel reduce) adds them in plane order."""
         cap = x.shape[0] if x_cap is None else x_cap
+        if w.kind == "w8t":
+            if M <= 64 and self.n.gemm_w4_dec_supported(M, w.N, w.K, EPI_PARTIAL):
+                # one fp32 plane (row stride N): the decode kernel adds its K splits on chip
+                self.n.gemm_w8_dec(w.data, x, cap, None, partials, M, w.N, w.K, w.N, EPI_PARTIAL, self.dec_ws,
+                                   self.status.ptr)
+                return 1
+            dense = self._w8_dense(w)
+            dw = LinearWeight("f16", w.N, w.K, dense, None, False, 0)
+            return self.linear_partial(dw, x, M, partials, k_split, x_cap)
         if w.kind == "w4t":
             ks = 0 if k_split is None else min(k_split, partials.shape[0])
             planes = self.n.gemm_w4_splits(M, w.N, w.K, ks)
@@ -301,15 +356,17 @@ class CudaOps(TorchOps):
                              block_size, planes, n_planes, bias)
 
     def qkv_rope_fused_ok(self, w, M, hd, kv_layer) -> bool:
-        return bool((self.dec_mode & 2) and w.kind == "w4t" and M <= 64 and hd == 128 and kv_layer.is_contiguous()
+        ok_kind = w.kind == "w8t" or (w.kind == "w4t" and (self.dec_mode & 2))
+        return bool(ok_kind and M <= 64 and hd == 128 and kv_layer.is_contiguous()
                     and self.n.gemm_w4_dec_supported(M, w.N, w.K, 3))
 
     def qkv_rope_fused(self, w, x, M, qkv, kv_layer, positions, slots, cos_sin, nh, nkv, block_size, x_cap=None):
         """One kernel: fused QKV projection + bias + rotate-half RoPE + K/V rows into the paged cache; ``qkv`` gets
         the rotated q heads.  head_dim 128, full rotary, ``cos_sin`` [max_position, 64, 2] fp32."""
         cap = x.shape[0] if x_cap is None else x_cap
-        self.n.gemm_w4_dec_qkv_rope(w.data, x, cap, w.bias, qkv, qkv.stride(0), M, w.K, nh, nkv, kv_layer, block_size,
-                                    positions, slots, cos_sin, cos_sin.shape[0], self.dec_ws, self.status.ptr)
+        fn = self.n.gemm_w8_dec_qkv_rope if w.kind == "w8t" else self.n.gemm_w4_dec_qkv_rope
+        fn(w.data, x, cap, w.bias, qkv, qkv.stride(0), M, w.K, nh, nkv, kv_layer, block_size, positions, slots, cos_sin,
+           cos_sin.shape[0], self.dec_ws, self.status.ptr)
 
     @staticmethod
     def _tensor_core_attention(kv_layer, hd, nh, nkv, block_size) -> bool:

@@ -38,6 +38,14 @@ _SIGS = {
     "zse_gemm_w4_dec_qkv_rope": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                          c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
                                          c_void_p, c_void_p]),
+    "zse_gemm_w8_dec": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                c_void_p, c_void_p, c_void_p]),
+    "zse_gemm_w8_dec_qkv_rope": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                         c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
+                                         c_void_p, c_void_p]),
+    "zse_w8_tiled_bytes": (c_int64, [c_int, c_int]),
+    "zse_repack_w8": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "zse_dequant_w8_tiled": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "zse_gemm_w4_dec_workspace_bytes": (c_int64, [c_int]),
     "zse_gemm_w4_dec_supported": (c_int, [c_int, c_int, c_int, c_int]),
     "zse_gemm_w4_dec_plan": (None, [c_int, c_int, c_int, c_int, POINTER(c_int)]),
@@ -101,6 +109,9 @@ _SIGS = {
                                     POINTER(c_uint64)]),
     "zse_tp_gemm_w4_push": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                     c_void_p, c_void_p]),
+    "zse_tp_gemm_dec_allreduce_norm": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                               c_int, c_int, c_void_p, c_void_p, c_void_p, c_float, c_void_p, c_void_p,
+                                               c_void_p]),
     "zse_tp_sum_add_rmsnorm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_int, c_int, c_void_p,
                                        c_void_p]),
     "zse_tp_sum_add_rmsnorm_emulated": (c_int, [c_void_p, POINTER(c_uint64), c_void_p, POINTER(c_uint64), c_int,
@@ -201,6 +212,27 @@ def gemm_w4_dec_qkv_rope(w_tiled, x, x_rows_cap, bias, qkv_out, ldo, M, K, nh, n
     _ck(load().zse_gemm_w4_dec_qkv_rope(_p(w_tiled), _p(x), x_rows_cap, _p(bias), _p(qkv_out), ldo, M, K, nh, nkv,
                                         _p(kv_layer), block_size, _p(positions), _p(slots), _p(cos_sin), max_position,
                                         _p(workspace), status, _stream()), "gemm_w4_dec_qkv_rope")
+
+
+def gemm_w8_dec(w_tiled, x, x_rows_cap, bias, out, M, N, K, ldo, epilogue, workspace, status):
+    """The decode-sized GEMM for INT8 weights tiled by ``repack_w8`` (the weights stay 8 bits wide in memory)."""
+    _ck(load().zse_gemm_w8_dec(_p(w_tiled), _p(x), x_rows_cap, _p(bias), _p(out), M, N, K, ldo, epilogue,
+                               _p(workspace), status, _stream()), "gemm_w8_dec")
+
+
+def gemm_w8_dec_qkv_rope(w_tiled, x, x_rows_cap, bias, qkv_out, ldo, M, K, nh, nkv, kv_layer, block_size, positions,
+                         slots, cos_sin, max_position, workspace, status):
+    _ck(load().zse_gemm_w8_dec_qkv_rope(_p(w_tiled), _p(x), x_rows_cap, _p(bias), _p(qkv_out), ldo, M, K, nh, nkv,
+                                        _p(kv_layer), block_size, _p(positions), _p(slots), _p(cos_sin), max_position,
+                                        _p(workspace), status, _stream()), "gemm_w8_dec_qkv_rope")
+
+
+def repack_w8(q, scales, out_tiled, N, K, interleave_rows=0):
+    _ck(load().zse_repack_w8(_p(q), _p(scales), _p(out_tiled), N, K, interleave_rows, _stream()), "repack_w8")
+
+
+def dequant_w8_tiled(tiled, out_f16, N, K, interleave_rows=0):
+    _ck(load().zse_dequant_w8_tiled(_p(tiled), _p(out_f16), N, K, interleave_rows, _stream()), "dequant_w8_tiled")
 
 
 def gemm_w4_dec_workspace(device, sm_count: int) -> torch.Tensor:
@@ -418,6 +450,14 @@ def tp_gemm_w4_push(ctx, w_tiled, x, x_rows_cap, M, N, K, slot, use_multimem, st
         _ck(rc, "tp_gemm_w4_push")
     LAUNCHES[0] += 1
     return rc
+
+
+def tp_gemm_dec_allreduce_norm(ctx, w_tiled, int8_weights, x, x_rows_cap, M, N, K, slot, use_multimem, residual,
+                               norm_w, xnorm, eps, workspace, status, rank_override=-1):
+    """Row-parallel projection + all-reduce + residual add + RMSNorm in one kernel (csrc/gemm_w4_dec.cu)."""
+    _ck(load().zse_tp_gemm_dec_allreduce_norm(ctx, _p(w_tiled), int(int8_weights), _p(x), x_rows_cap, M, N, K, slot,
+                                              int(use_multimem), rank_override, _p(residual), _p(norm_w), _p(xnorm),
+                                              eps, _p(workspace), status, _stream()), "tp_gemm_dec_allreduce_norm")
 
 
 def tp_sum_add_rmsnorm(ctx, residual, weight, out, M, eps, slot, expected_add, status):

@@ -210,7 +210,10 @@ class FusedComm(NcclComm):
         self.push = env.flag("ZSE_TP_PUSH")
         self.push_rows = min(256, max_tokens)
         self._push_ready = False
-        if self.push:
+        # Decode-sized passes: the row-parallel projection, the all-reduce, the residual add and the next RMSNorm are ONE
+        # kernel (csrc/gemm_w4_dec.cu, kDecAllReduceNorm); it uses the same inboxes and counters as the push exchange.
+        self.fused_k1 = env.flag("ZSE_TP_FUSED_K1")
+        if self.push or self.fused_k1:
             self._init_push(symm, grp, world, rank, device, hidden_size, want_mm)
         # passes with at least this many rows (prefill) use the two-shot kernel: reduce-scatter by rows + all-gather,
         # 2(tp-1)/tp rows over NVLink per rank and row instead of tp-1
@@ -244,6 +247,19 @@ class FusedComm(NcclComm):
         self._n.tp_ctx_set_push(self._ctx, self.push_rows, [p + offs[0] for p in ptrs], (mc + offs[0]) if mc else 0,
                                 [p + offs[1] for p in ptrs], (mc + offs[1]) if mc else 0, state_ptrs)
         self._push_ready = True
+
+    def can_fuse_k1(self, ops, w, M: int) -> bool:
+        """Whether ``linear_allreduce_norm`` takes this projection (tiled INT4 / INT8 weights, at most 64 rows)."""
+        return bool(self.fused_k1 and self._push_ready and w.kind in ("w4t", "w8t") and M <= min(64, self.push_rows)
+                    and w.N == self.H and w.bias is None and self._n.gemm_w4_dec_supported(M, w.N, w.K, 4)
+                    and self._n.gemm_w4_dec_plan(w.N, w.K, 4, ops.sm_count)[1] > 0)
+
+    def linear_allreduce_norm(self, ops, w, x, M: int, residual, weight, out, eps: float) -> None:
+        """residual += all-reduce(x W^T); out = RMSNorm(residual) * weight - one kernel, no NCCL, no separate reduce."""
+        self._n.tp_gemm_dec_allreduce_norm(self._ctx, w.data, w.kind == "w8t", x, x.shape[0], M, w.N, w.K,
+                                           self._calls & 1, self.push_multimem, residual, weight, out, float(eps),
+                                           ops.dec_ws, ops.status.ptr)
+        self._calls += 1
 
     def can_push(self, w, M: int) -> bool:
         return self._push_ready and w.kind == "w4t" and M <= self.push_rows and w.N == self.H and w.bias is None

@@ -21,12 +21,14 @@ KNOWN: Dict[str, Tuple[str, str]] = {
     "ZSE_KERNEL_CACHE": ("~/.cache/zse_b200/kernels", "directory of the kernel language's cubin cache"),
     "ZSE_TP_MULTIMEM": ("1", "use NVSwitch multimem loads in the fused exchange where the fabric offers them"),
     "ZSE_TP_PUSH": ("0", "let the row-parallel GEMM push its rows to the peers from its epilogue"),
+    "ZSE_TP_FUSED_K1": ("1", "decode-sized passes: row-parallel GEMM + all-reduce + residual + RMSNorm as one kernel"),
     "ZSE_TP_TWO_SHOT_ROWS": (str(1 << 30), "passes of at least this many rows take the two-shot reduce-scatter kernel"),
     "ZSE_TP_NCCL_ROWS": ("256", "passes of at least this many rows take NCCL instead of the fused exchange"),
     "ZSE_TP_SP": ("0", "sequence-parallel prefill on the NCCL path (reduce-scatter / all-gather, residual split by rows)"),
     "ZSE_TP_SP_MIN_ROWS": ("256", "smallest pass that takes the sequence-parallel path"),
     "ZSE_W4_DEC": ("3", "decode-sized INT4 layers through the persistent kernel: 1 gate/up + SwiGLU, 2 fused QKV + RoPE + "
                         "cache write, 4 every other INT4 linear (sum of the bits; 0: the tiled kernel everywhere)"),
+    "ZSE_W8_RESIDENT": ("1", "keep INT8 weights 8 bits wide on the device (0: expand them to fp16 at load)"),
     "ZSE_PDL": ("1", "programmatic dependent launch between the kernels of a pass (read by the native library)"),
     "ZSE_TP_PDL": ("0", "programmatic dependent launch for the exchange kernels too (read by the native library)"),
     "ZSE_REFERENCE_DIR": ("", "where the tests look for an installed copy of the reference"),
