@@ -63,6 +63,9 @@ def parse_args():
     ap.add_argument("--no-graphs", action="store_true")
     ap.add_argument("--profile-region", action="store_true",
                     help="bracket the timed steps with cudaProfilerStart/Stop (for `ncu --profile-from-start off`)")
+    ap.add_argument("--trace-kernels", default=None, metavar="FILE",
+                    help="after the result line, run five more steps under the CUPTI activity tracer and write rank "
+                         "0's per-kernel device times to FILE (a diagnostic: not part of any reported number)")
     ap.add_argument("--workload", default="batch64", choices=sorted(WORKLOADS),
                     help="batch64: 64 requests, prompts uniform in [128, 2048] (the headline); single: one request "
                          "with a 512-token prompt on the 7B shape (the case the reference publishes); spec32b: n-gram "
@@ -151,6 +154,33 @@ class ClockSampler:
         os.unlink(self.path)
         return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
                 "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def trace_kernels(eng, path, barrier, steps: int = 5) -> None:
+    """Per-kernel device time of `steps` more engine steps (every rank steps; rank 0 writes the table)."""
+    from torch.profiler import ProfilerActivity, profile
+    barrier()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for _ in range(steps):
+            eng.step()
+        torch.cuda.synchronize()
+    barrier()
+    if path is None:
+        return
+    rows = []
+    for e in prof.key_averages():
+        total = getattr(e, "device_time_total", None)
+        if total is None:
+            total = getattr(e, "cuda_time_total", 0.0)
+        if total > 0:
+            rows.append((float(total), int(e.count), e.key))
+    rows.sort(reverse=True)
+    whole = sum(r[0] for r in rows) or 1.0
+    with open(path, "w") as f:
+        f.write(f"# {steps} steps, device time per kernel name (us); total {whole:.0f} us = {whole / steps:.0f} us/step\n")
+        f.write("# total_us  share  launches  avg_us  name\n")
+        for total, count, name in rows:
+            f.write(f"{total:10.0f}  {100 * total / whole:5.1f}%  {count:6d}  {total / count:8.2f}  {name[:150]}\n")
 
 
 def run_ours(args):
@@ -314,6 +344,8 @@ def run_ours(args):
                       "w4_dec_mode": int(getattr(eng.runner.model.ops, "dec_mode", 0))},
         }
         print(json.dumps(line), flush=True)
+    if args.trace_kernels:
+        trace_kernels(eng, args.trace_kernels if rank == 0 else None, barrier)
     if world > 1:
         # the result is out; tear down in the order NCCL wants (graphs that captured its kernels first), and do not
         # let a teardown that blocks keep the launcher waiting

@@ -179,6 +179,25 @@ int zse_tp_sum_add_rmsnorm(void* ctx, void* residual, const void* weight, void* 
                            int expected_add, void* status, void* stream);
 int zse_tp_sum_add_rmsnorm_emulated(void* ctx, const uint64_t* residuals, const void* weight, const uint64_t* outs,
                                     int M, float eps, int slot, int expected_add, void* status, void* stream);
+// Sequence-parallel exchange for passes of more than 64 rows (prefill): token rows are owned in blocks of 64
+// (block b -> rank b % tp).  The row-parallel GEMM scatters its fp16 partial tiles to the owners from its epilogue;
+// the owner adds, applies residual + RMSNorm and stores the row into the gathered buffer of every rank; GEMMs that
+// read the gathered buffer wait, in their prologue, for the row blocks of their own token tile.
+//   inbox_ptrs[r]  : rank r's inbox [2][tp][own_cap][H] fp16   arrive_ptrs[r] : counters [2][tp][nblk_cap] u32
+//   xg_ptrs[r]     : gathered activations [nblk_cap * 64][H]    gflag_ptrs[r]  : flags [nblk_cap] u32
+//   state_ptrs[r]  : 4 + nblk_cap u32 of ordinary device memory of rank r (all zero at start)
+int zse_tp_ctx_set_sp(void* ctx, int own_cap, int nblk_cap, const uint64_t* inbox_ptrs, const uint64_t* arrive_ptrs,
+                      const uint64_t* xg_ptrs, uint64_t mc_xg, const uint64_t* gflag_ptrs, const uint64_t* state_ptrs);
+int zse_tp_gemm_w4_scatter(void* ctx, const void* w_tiled, const void* x, int x_rows_cap, int M, int N, int K,
+                           int slot, int rank_override, void* status, void* stream);
+int zse_tp_gemm_w4_gathered(void* ctx, const void* w_tiled, const void* x, int x_rows_cap, const void* bias, void* out,
+                            int M, int N, int K, int ldo, int epilogue, int k_split, int rank_override, void* status,
+                            void* stream);
+int zse_tp_sp_sum_norm_gather(void* ctx, void* residual, const void* weight, int M, float eps, int slot,
+                              int use_multimem, void* status, void* stream);
+int zse_tp_sp_sum_norm_gather_emulated(void* ctx, const uint64_t* residuals, const void* weight, int M, float eps,
+                                       int slot, void* status, void* stream);
+int zse_tp_sp_wait(void* ctx, int M, int rank_override, void* status, void* stream);
 int zse_tp_argmax(void* ctx, const void* logits, int ld, void* out, int M, int V_local, int vocab_stride,
                   int slot, void* status, void* stream);
 int zse_tp_argmax_emulated(void* ctx, const uint64_t* logits, int ld, const uint64_t* outs, int M, int V_local,

@@ -540,6 +540,168 @@ __global__ void __launch_bounds__(1024) tp_argmax_kernel(const TpArgmaxArgs a) {
   }
 }
 
+
+// ---- sequence-parallel exchange for passes of many rows: the reduce + all-gather half (see SpTable) -------------
+// One CTA per token row; rows this rank does not own leave at once.  The owner waits (bounded) until every source's
+// counter for the row's 64-row block holds `units`, adds the tp fp16 rows of its inbox in rank order, adds its fp32
+// residual row, normalises and stores the fp16 row into the gathered buffer of EVERY rank.  The CTA that finishes a
+// block last takes the block's counters down and publishes the pass epoch in the block's flag on every rank - the
+// GEMM that consumes the gathered rows (gemm_w4.cu, gather_wait_tile) and tp_sp_wait_kernel wait for exactly that.
+// The last CTA of the launch stores the epoch into state[0]; consumers launched after this kernel read it there.
+struct TpSpArgs {
+  SpTable sp;                      // sp.rank / sp.state are per emulated rank below
+  float* residual[kMaxTp];
+  uint32_t* state[kMaxTp];
+  int rank[kMaxTp];
+  const __half* weight;
+  int M;
+  float eps;
+  uint32_t units;
+  Status* status;
+};
+
+__device__ __forceinline__ void multimem_st_f16x8(void* mc_ptr, const uint4& v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f16x2 [%0], {%1,%2,%3,%4};" ::"l"(mc_ptr), "r"(v.x), "r"(v.y),
+               "r"(v.z), "r"(v.w)
+               : "memory");
+}
+
+__global__ void __launch_bounds__(kRedThreads)
+tp_sp_sum_norm_gather_kernel(const TpSpArgs a) {
+  __shared__ float red[32];
+  __shared__ int ok_flag;
+  const SpTable& sp = a.sp;
+  const int er = blockIdx.y;
+  const int rank = a.rank[er], tp = sp.tp, H = sp.H, nch = H / 8;
+  uint32_t* st = a.state[er];
+  const int row = blockIdx.x;
+  const int b = row / kSpRowBlock;
+  const uint32_t epoch = *reinterpret_cast<volatile uint32_t*>(st) + 1u;
+  if (threadIdx.x == 0) ok_flag = 1;
+  __syncthreads();
+  if (b % tp == rank) {
+    const int local = (b / tp) * kSpRowBlock + (row % kSpRowBlock);
+    if (threadIdx.x < tp) {
+      const uint32_t* ctr = sp.arrive[rank] + (size_t(sp.slot) * tp + threadIdx.x) * sp.nblk_cap + b;
+      if (int32_t(ld_acquire_sys(ctr) - a.units) < 0) {
+        const uint64_t t0 = globaltimer_ns();
+        unsigned spins = 0;
+        while (int32_t(ld_acquire_sys(ctr) - a.units) < 0) {
+          if ((++spins & 0x3F) == 0 && globaltimer_ns() - t0 > kWaitLimitNs) {
+            report(a.status, kPeerTimeout, 37, threadIdx.x);
+            ok_flag = 0;
+            break;
+          }
+        }
+      }
+    }
+    __syncthreads();
+    const bool ok = ok_flag != 0;
+    const __half* box = sp.inbox[rank] + (size_t(sp.slot) * tp * sp.own_cap + local) * H;
+    float vals[kRedMaxChunks][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < kRedMaxChunks; ++j) {
+      const int c = threadIdx.x + j * kRedThreads;
+      if (c < nch) {
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        if (ok) {
+          uint4 got[kMaxTp];
+#pragma unroll
+          for (int r = 0; r < kMaxTp; ++r)
+            if (r < tp) got[r] = ld_relaxed_sys_v4(box + size_t(r) * sp.own_cap * H + size_t(c) * 8);
+#pragma unroll
+          for (int r = 0; r < kMaxTp; ++r)
+            if (r < tp) acc_h8(acc, got[r]);
+        }
+        float4* res = reinterpret_cast<float4*>(a.residual[er] + size_t(row) * H) + 2 * c;
+        float4 x = res[0], y = res[1];
+        x.x += acc[0]; x.y += acc[1]; x.z += acc[2]; x.w += acc[3];
+        y.x += acc[4]; y.y += acc[5]; y.z += acc[6]; y.w += acc[7];
+        res[0] = x;
+        res[1] = y;
+        vals[j][0] = x.x; vals[j][1] = x.y; vals[j][2] = x.z; vals[j][3] = x.w;
+        vals[j][4] = y.x; vals[j][5] = y.y; vals[j][6] = y.z; vals[j][7] = y.w;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) ss += vals[j][i] * vals[j][i];
+      }
+    }
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float tot = (threadIdx.x & 31) < (kRedThreads >> 5) ? red[threadIdx.x & 31] : 0.f;
+    tot = warp_sum(tot);
+    const float inv = rsqrtf(tot / float(H) + a.eps);
+#pragma unroll
+    for (int j = 0; j < kRedMaxChunks; ++j) {
+      const int c = threadIdx.x + j * kRedThreads;
+      if (c < nch) {
+        const uint4 wr = reinterpret_cast<const uint4*>(a.weight)[c];
+        const __half2* wh = reinterpret_cast<const __half2*>(&wr);
+        uint4 pk;
+        uint32_t* po = reinterpret_cast<uint32_t*>(&pk);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 w = __half22float2(wh[i]);
+          po[i] = pack_half2(vals[j][2 * i] * inv * w.x, vals[j][2 * i + 1] * inv * w.y);
+        }
+        const size_t off = size_t(row) * H + size_t(c) * 8;
+        if (sp.mc_xg != nullptr) {
+          multimem_st_f16x8(sp.mc_xg + off, pk);
+        } else {
+#pragma unroll
+          for (int k = 0; k < kMaxTp; ++k)
+            if (k < tp) *reinterpret_cast<uint4*>(sp.xg[k] + off) = pk;
+        }
+      }
+    }
+    __syncthreads();                                 // every store of the row has been issued
+    if (threadIdx.x == 0) {
+      __threadfence_system();
+      const int rows_in_block = min(kSpRowBlock, a.M - b * kSpRowBlock);
+      const uint32_t tk = atomicAdd(st + 4 + b, 1u);
+      if (tk == uint32_t(rows_in_block) - 1u) {
+        // every row of the block has been stored (their fences precede their tickets): take the counters down for
+        // the call after next, then tell every rank that the block is complete
+        st[4 + b] = 0u;
+        for (int r = 0; r < tp; ++r)
+          *reinterpret_cast<volatile uint32_t*>(sp.arrive[rank] + (size_t(sp.slot) * tp + r) * sp.nblk_cap + b) = 0u;
+        __threadfence_system();
+        for (int k = 0; k < tp; ++k) st_release_sys(sp.gflag[k] + b, epoch);
+      }
+    }
+  }
+  // the last CTA of the launch moves the epoch on (every CTA has read it by then)
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    __threadfence();
+    const uint32_t t = atomicAdd(st + 1, 1u);
+    if (t == gridDim.x - 1u) {
+      st[1] = 0u;
+      *reinterpret_cast<volatile uint32_t*>(st) = epoch;
+      __threadfence();
+    }
+  }
+}
+
+// Waits (bounded) until every row block of a pass of M rows has been gathered on this rank: for readers of the
+// gathered buffer that are not GEMMs of this library (row selection before the lm_head, adapters).
+__global__ void __launch_bounds__(kRedThreads)
+tp_sp_wait_kernel(const uint32_t* flags, const uint32_t* epoch_word, int n_blocks, Status* status) {
+  const uint32_t want = *reinterpret_cast<const volatile uint32_t*>(epoch_word);
+  for (int b = threadIdx.x; b < n_blocks; b += kRedThreads) {
+    if (ld_acquire_sys(flags + b) == want) continue;
+    const uint64_t t0 = globaltimer_ns();
+    unsigned spins = 0;
+    while (ld_acquire_sys(flags + b) != want) {
+      if ((++spins & 0x3F) == 0 && globaltimer_ns() - t0 > kWaitLimitNs) {
+        report(status, kPeerTimeout, 38, b);
+        break;
+      }
+    }
+  }
+}
+
 }  // namespace zse
 
 using namespace zse;
@@ -558,6 +720,14 @@ struct zse_tp_ctx {
   __half* mc_inbox = nullptr;
   uint32_t* mc_arrive = nullptr;
   int push_m_cap = 0;                // rows per source in the inbox
+  // sequence-parallel exchange (set by zse_tp_ctx_set_sp)
+  __half* sp_inbox[kMaxTp] = {};
+  uint32_t* sp_arrive[kMaxTp] = {};
+  __half* sp_xg[kMaxTp] = {};
+  uint32_t* sp_gflag[kMaxTp] = {};
+  uint32_t* sp_state[kMaxTp] = {};   // sp_state[r]: rank r's local words {epoch, exit ticket, -, -, tickets[nblk_cap]}
+  __half* mc_xg = nullptr;
+  int sp_own_cap = 0, sp_nblk_cap = 0;
 };
 
 extern "C" void* zse_tp_ctx_create(int tp, int rank, int m_cap, int H, const uint64_t* data_ptrs,
@@ -621,6 +791,112 @@ uint32_t* tp_push_state(const void* ctx, int rank_override) {
   return (r >= 0 && r < c->table.tp) ? c->state[r] : nullptr;
 }
 }  // namespace zse
+
+// Buffers of the sequence-parallel exchange (see SpTable): per rank r the mapped addresses of its inbox
+// [2][tp][own_cap][H] fp16, counters [2][tp][nblk_cap] u32, gathered activations [nblk_cap * 64][H] fp16 and flags
+// [nblk_cap] u32; `state_ptrs[r]`: rank r's local words (4 + nblk_cap u32, zero-initialised; other ranks' entries may
+// be 0 outside single-GPU tests).  own_cap must hold ceil(nblk_cap / tp) blocks of 64 rows.
+extern "C" int zse_tp_ctx_set_sp(void* ctx, int own_cap, int nblk_cap, const uint64_t* inbox_ptrs,
+                                 const uint64_t* arrive_ptrs, const uint64_t* xg_ptrs, uint64_t mc_xg,
+                                 const uint64_t* gflag_ptrs, const uint64_t* state_ptrs) {
+  zse_tp_ctx* c = reinterpret_cast<zse_tp_ctx*>(ctx);
+  if (c == nullptr || nblk_cap <= 0) return ZSE_ERR_SHAPE;
+  const int tp = c->table.tp;
+  if (own_cap < ((nblk_cap + tp - 1) / tp) * kSpRowBlock) return ZSE_ERR_SHAPE;
+  c->sp_own_cap = own_cap;
+  c->sp_nblk_cap = nblk_cap;
+  for (int r = 0; r < tp; ++r) {
+    c->sp_inbox[r] = reinterpret_cast<__half*>(inbox_ptrs[r]);
+    c->sp_arrive[r] = reinterpret_cast<uint32_t*>(arrive_ptrs[r]);
+    c->sp_xg[r] = reinterpret_cast<__half*>(xg_ptrs[r]);
+    c->sp_gflag[r] = reinterpret_cast<uint32_t*>(gflag_ptrs[r]);
+    c->sp_state[r] = reinterpret_cast<uint32_t*>(state_ptrs[r]);
+  }
+  c->mc_xg = reinterpret_cast<__half*>(mc_xg);
+  return 0;
+}
+
+namespace zse {
+int tp_fill_sp_table(const void* ctx, int slot, bool multimem, int rank_override, SpTable* out) {
+  const zse_tp_ctx* c = reinterpret_cast<const zse_tp_ctx*>(ctx);
+  if (c == nullptr || c->sp_inbox[0] == nullptr) return ZSE_ERR_SHAPE;
+  if (multimem && c->mc_xg == nullptr) return ZSE_ERR_SHAPE;
+  const int rank = rank_override >= 0 ? rank_override : c->rank;
+  if (rank < 0 || rank >= c->table.tp || c->sp_state[rank] == nullptr) return ZSE_ERR_SHAPE;
+  for (int r = 0; r < kPushMaxTp; ++r) {
+    const bool in = r < c->table.tp;
+    out->inbox[r] = in ? c->sp_inbox[r] : nullptr;
+    out->arrive[r] = in ? c->sp_arrive[r] : nullptr;
+    out->xg[r] = in ? c->sp_xg[r] : nullptr;
+    out->gflag[r] = in ? c->sp_gflag[r] : nullptr;
+  }
+  out->mc_xg = multimem ? c->mc_xg : nullptr;
+  out->state = c->sp_state[rank];
+  out->tp = c->table.tp;
+  out->rank = rank;
+  out->H = c->H;
+  out->own_cap = c->sp_own_cap;
+  out->nblk_cap = c->sp_nblk_cap;
+  out->slot = slot & 1;
+  return 0;
+}
+}  // namespace zse
+
+static int fill_sp_args(const zse_tp_ctx* c, TpSpArgs& a, const void* weight, int M, float eps, int slot,
+                        bool multimem, void* status) {
+  if (c == nullptr || M <= 0 || c->H % kTileN || c->H > 8 * kRedThreads * kRedMaxChunks) return ZSE_ERR_SHAPE;
+  if (int rc = tp_fill_sp_table(c, slot, multimem, -1, &a.sp)) return rc;
+  if ((M + kSpRowBlock - 1) / kSpRowBlock > c->sp_nblk_cap) return ZSE_ERR_SHAPE;
+  a.weight = reinterpret_cast<const __half*>(weight);
+  a.M = M;
+  a.eps = eps;
+  a.units = uint32_t(kSpRowBlock / 16) * uint32_t(c->H / kTileN);   // (16-token chunks per block) x (weight tiles)
+  a.status = reinterpret_cast<Status*>(status);
+  return 0;
+}
+
+// residual[own rows] += sum over ranks of the scattered partial rows; gathered buffer of every rank = RMSNorm of
+// those rows (see tp_sp_sum_norm_gather_kernel).  Follows zse_tp_gemm_w4_scatter of the same slot on every rank.
+extern "C" int zse_tp_sp_sum_norm_gather(void* ctx, void* residual, const void* weight, int M, float eps, int slot,
+                                         int use_multimem, void* status, void* stream) {
+  zse_tp_ctx* c = reinterpret_cast<zse_tp_ctx*>(ctx);
+  TpSpArgs a{};
+  if (int rc = fill_sp_args(c, a, weight, M, eps, slot, use_multimem != 0, status)) return rc;
+  a.residual[0] = reinterpret_cast<float*>(residual);
+  a.state[0] = c->sp_state[c->rank];
+  a.rank[0] = c->rank;
+  tp_sp_sum_norm_gather_kernel<<<dim3(M, 1), kRedThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(a);
+  return cudaGetLastError() == cudaSuccess ? 0 : ZSE_ERR_LAUNCH;
+}
+
+// All ranks of a single-GPU test in one launch (blockIdx.y = rank).  The scatter GEMMs of every emulated rank have
+// finished before it starts, and no CTA of it waits for another CTA.
+extern "C" int zse_tp_sp_sum_norm_gather_emulated(void* ctx, const uint64_t* residuals, const void* weight, int M,
+                                                  float eps, int slot, void* status, void* stream) {
+  zse_tp_ctx* c = reinterpret_cast<zse_tp_ctx*>(ctx);
+  TpSpArgs a{};
+  if (int rc = fill_sp_args(c, a, weight, M, eps, slot, false, status)) return rc;
+  for (int r = 0; r < c->table.tp; ++r) {
+    if (c->sp_state[r] == nullptr) return ZSE_ERR_SHAPE;
+    a.residual[r] = reinterpret_cast<float*>(residuals[r]);
+    a.state[r] = c->sp_state[r];
+    a.rank[r] = r;
+  }
+  tp_sp_sum_norm_gather_kernel<<<dim3(M, c->table.tp), kRedThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(a);
+  return cudaGetLastError() == cudaSuccess ? 0 : ZSE_ERR_LAUNCH;
+}
+
+// Bounded wait until all row blocks of a pass of M rows have arrived in this rank's gathered buffer.
+extern "C" int zse_tp_sp_wait(void* ctx, int M, int rank_override, void* status, void* stream) {
+  zse_tp_ctx* c = reinterpret_cast<zse_tp_ctx*>(ctx);
+  SpTable sp;
+  if (int rc = tp_fill_sp_table(c, 0, false, rank_override, &sp)) return rc;
+  const int nb = (M + kSpRowBlock - 1) / kSpRowBlock;
+  if (M <= 0 || nb > sp.nblk_cap) return ZSE_ERR_SHAPE;
+  tp_sp_wait_kernel<<<1, kRedThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(sp.gflag[sp.rank], sp.state, nb,
+                                                                                 reinterpret_cast<Status*>(status));
+  return cudaGetLastError() == cudaSuccess ? 0 : ZSE_ERR_LAUNCH;
+}
 
 // Programmatic dependent launch for the reduce kernels: off unless ZSE_TP_PDL=1.  Measured on 2 GPUs: a reduce kernel
 // that starts early spins on its peers' flags while the GEMM before it still runs and slows the whole step

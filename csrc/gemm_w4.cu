@@ -90,6 +90,8 @@ struct W4Args {
   Status* status;
   long long* timing;       // debug builds (ZSE_W4_TIMING): per-role cycle counters, else unused
   PushTable push;          // kEpiPushF16: where the partial tiles go (every rank's inbox over NVLink)
+  SpTable sp;              // kEpiScatterF16: where the partial tiles go (the owner of each 64-row block)
+  GatherWait gather;       // the activations are a gathered buffer: wait for the row blocks of this CTA's token tile
 };
 
 __device__ __forceinline__ void multimem_st_v4(void* mc_ptr, const uint4& v) {
@@ -102,6 +104,39 @@ __device__ __forceinline__ void multimem_red_add_release(uint32_t* mc_ptr, uint3
 }
 __device__ __forceinline__ void red_add_relaxed_sys(uint32_t* p, uint32_t v) {
   asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+__device__ __forceinline__ void red_add_release_sys(uint32_t* p, uint32_t v) {
+  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t w4_ld_acquire_sys(const uint32_t* p) {
+  uint32_t v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+// All-gather in the prologue: the rows of token tile [t0, t0 + nt) were written into this GPU's memory by their
+// owners (other GPUs, plain or multicast stores); a row block is complete when its flag holds the pass epoch.  One
+// thread waits (bounded), then orders those writes before the TMA loads it is about to issue (async proxy).
+__device__ __forceinline__ bool gather_wait_tile(const GatherWait& g, int t0, int nt, int M, volatile int* abort_flag,
+                                                 Status* st) {
+  const uint32_t want = *reinterpret_cast<const volatile uint32_t*>(g.epoch);
+  bool ok = true;
+  for (int t = t0; t < t0 + nt && t < M && ok; t += kSpRowBlock) {
+    const uint32_t* f = g.flags + t / kSpRowBlock;
+    if (w4_ld_acquire_sys(f) == want) continue;
+    const uint64_t begin = globaltimer_ns();
+    unsigned spins = 0;
+    while (w4_ld_acquire_sys(f) != want) {
+      if ((++spins & 0x3F) == 0 && (*abort_flag || globaltimer_ns() - begin > kWaitLimitNs)) {
+        report(st, kPeerTimeout, 36, unsigned(t / kSpRowBlock));
+        *abort_flag = 1;
+        ok = false;
+        break;
+      }
+    }
+  }
+  asm volatile("fence.proxy.async;" ::: "memory");
+  return ok;
 }
 
 // Nibble order inside every 32-bit word of a chunk (fixed by repack_w4): positions 0..7 hold the K elements
@@ -409,7 +444,10 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4Args a) {
       int issued = 0, s = 0;
       uint32_t ph = 1;
       pdl_wait();                                        // the activations come from the previous kernel
-      for (int kk = 0; kk < n_k; ++kk) {
+      bool gathered = true;
+      if (a.gather.flags != nullptr)
+        gathered = gather_wait_tile(a.gather, blockIdx.y * NT, NT, a.M, abort_flag, a.status);
+      for (int kk = 0; kk < n_k && gathered; ++kk) {
         if (kk >= SX) {
           // tied: the commit that ends the pair holding this stage's last chunk frees the stage as well
           uint64_t* freed = kTied ? &bars->pair_done[s / (CPS / R)] : &bars->x_empty[s];
@@ -626,7 +664,7 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4Args a) {
           }
           asm volatile("bar.sync %0, 64;" ::"r"(bar_id) : "memory");
         }
-      } else if (EPI == kEpiPushF16) {
+      } else if (EPI == kEpiPushF16 || EPI == kEpiScatterF16) {
         // keep the finished sums in this CTA's park area, token-major, for the coalesced push below (the entries of
         // the chunks a CTA owns are read by nobody else)
 #pragma unroll
@@ -694,6 +732,55 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4Args a) {
       }
     }
   }
+  if (EPI == kEpiScatterF16 && dq_role && acc_ok) {
+    // ---- reduce-scatter inside the GEMM: every 64-row block of tokens has one owner; this rank's fp16 partial rows
+    // go to slot `rank` of the owner's inbox only, and the owner's counter of (source, block) gains one unit per
+    // (weight tile, 16-token chunk) - the same total whatever K split each rank's shard width made it choose.
+    constexpr int kDqThreads = kDqWarps * 32;
+    constexpr int kBlocksPerTile = NT / kSpRowBlock;
+    static_assert(EPI != kEpiScatterF16 || NT % kSpRowBlock == 0, "token tiles hold whole row blocks");
+    asm volatile("bar.sync 15, %0;" ::"n"(kDqThreads) : "memory");
+    const SpTable& sp = a.sp;
+    const int d = (warp - 2) * 32 + lane;
+    const int t0 = blockIdx.y * NT;
+    const int owned = int(crank) < kChunks ? (kChunks - int(crank) + ks - 1) / ks : 0;
+    for (int item = d; item < owned * 256; item += kDqThreads) {
+      const int ch = int(crank) + (item >> 8) * ks;
+      const int tok = (item & 255) >> 4, seg = item & 15;
+      const int r = ch / (NT / 16), c0 = (ch % (NT / 16)) * 16;
+      const int t = t0 + c0 + tok;
+      const int n = (tile0 + r) * kTileN + seg * 8;
+      if (t < a.M && n < a.N) {
+        const float4* src = reinterpret_cast<const float4*>(park + (ch * 16 + tok) * 128 + seg * 8);
+        const float4 lo = src[0], hi = src[1];
+        uint4 pk;
+        pk.x = pack_half2(clamp_f16(lo.x), clamp_f16(lo.y));
+        pk.y = pack_half2(clamp_f16(lo.z), clamp_f16(lo.w));
+        pk.z = pack_half2(clamp_f16(hi.x), clamp_f16(hi.y));
+        pk.w = pack_half2(clamp_f16(hi.z), clamp_f16(hi.w));
+        const int b = t / kSpRowBlock;
+        const int owner = b % sp.tp;
+        const int local = (b / sp.tp) * kSpRowBlock + (t % kSpRowBlock);
+        const size_t off = ((size_t(sp.slot) * sp.tp + sp.rank) * sp.own_cap + local) * sp.H + n;
+        *reinterpret_cast<uint4*>(sp.inbox[owner] + off) = pk;
+      }
+    }
+    asm volatile("bar.sync 15, %0;" ::"n"(kDqThreads) : "memory");
+    if (d < kBlocksPerTile) {
+      const int b = t0 / kSpRowBlock + d;
+      if (b * kSpRowBlock < a.M) {
+        uint32_t units = 0;
+        for (int i = 0; i < owned; ++i) {
+          const int ch = int(crank) + i * ks;
+          if (((ch % (NT / 16)) * 16) / kSpRowBlock == d) ++units;
+        }
+        if (units > 0) {
+          __threadfence_system();               // the CTA's stores (ordered by the barrier above) before the count
+          red_add_release_sys(sp.arrive[b % sp.tp] + (size_t(sp.slot) * sp.tp + sp.rank) * sp.nblk_cap + b, units);
+        }
+      }
+    }
+  }
   if (in_cluster) cluster_sync_all();          // nobody leaves while its parked values may still be read
 #ifdef ZSE_W4_TIMING
   if (a.timing != nullptr && threadIdx.x == 64 && blockIdx.x == 1 && blockIdx.z == 0) {
@@ -743,6 +830,9 @@ static int launch_w4_epi(int epilogue, const CUtensorMap& tx, const W4Args& a, d
   if (epilogue == kEpiSwiGLU) return launch_w4<NT, R, kEpiSwiGLU, DUAL>(tx, a, grid, st);
   if (epilogue == kEpiPartialF32) return launch_w4<NT, R, kEpiPartialF32, DUAL>(tx, a, grid, st);
   if (epilogue == kEpiPushF16) return launch_w4<NT, R, kEpiPushF16, DUAL>(tx, a, grid, st);
+  if constexpr (NT >= 128) {         // the row-block exchange is for passes of many rows
+    if (epilogue == kEpiScatterF16) return launch_w4<NT, R, kEpiScatterF16, DUAL>(tx, a, grid, st);
+  }
   return ZSE_ERR_SHAPE;
 }
 
@@ -830,7 +920,7 @@ extern "C" void zse_gemm_w4_set_mode(int mode) { zse::g_w4_mode = mode; }
 
 static int run_gemm_w4(const void* w_tiled, const void* x, int x_rows_cap, const void* bias, void* out, int M, int N,
                        int K, int ldo, int epilogue, int k_split, void* status, void* stream, const PushTable* push,
-                       int* ctas_out) {
+                       int* ctas_out, const SpTable* sp = nullptr, const GatherWait* gather = nullptr) {
   if (M <= 0) return 0;
   if (K % kW4StageK != 0 || N <= 0 || K <= 0) return ZSE_ERR_SHAPE;
   static int sm_count = 0;
@@ -840,6 +930,7 @@ static int run_gemm_w4(const void* w_tiled, const void* x, int x_rows_cap, const
     cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, dev);
     if (sm_count <= 0) sm_count = 148;
   }
+  if ((sp != nullptr || gather != nullptr) && M <= 64) return ZSE_ERR_SHAPE;   // wide CTAs (128 / 256 tokens) only
   if (!(g_w4_mode & 4) && push == nullptr) {
     const int gks = gemv_w4_plan(M, N, K, epilogue, sm_count, k_split);
     if (gks > 0)
@@ -856,8 +947,11 @@ static int run_gemm_w4(const void* w_tiled, const void* x, int x_rows_cap, const
   CUtensorMap tx;
   if (int rc = get_tmap(x, uint64_t(max(x_rows_cap, M)), uint64_t(K), uint32_t(nt), &tx)) return rc;
   W4Args a{reinterpret_cast<const uint8_t*>(w_tiled), reinterpret_cast<const __half*>(bias), out, M, N, K, ldo,
-           k_stages, spp, cluster, reinterpret_cast<Status*>(status), g_w4_timing, PushTable{}};
+           k_stages, spp, cluster, reinterpret_cast<Status*>(status), g_w4_timing, PushTable{}, SpTable{},
+           GatherWait{nullptr, nullptr}};
   if (push != nullptr) a.push = *push;
+  if (sp != nullptr) a.sp = *sp;
+  a.gather = gather != nullptr ? *gather : GatherWait{nullptr, nullptr};
   dim3 grid(n_tiles / R, (M + nt - 1) / nt, ks);
   if (ctas_out != nullptr) *ctas_out = int(grid.x * grid.y * grid.z);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
@@ -901,6 +995,33 @@ extern "C" int zse_tp_gemm_w4_push(void* ctx, const void* w_tiled, const void* x
   const int rc = run_gemm_w4(w_tiled, x, x_rows_cap, nullptr, nullptr, M, N, K, N, kEpiPushF16, 0, status, stream, &pt,
                              &ctas);
   return rc != 0 ? rc : ctas;
+}
+
+// Sequence-parallel prefill (see SpTable).  zse_tp_gemm_w4_scatter: row-parallel projection whose epilogue is the
+// reduce-scatter (N = hidden size of the context, more than 64 rows).  zse_tp_gemm_w4_gathered: any epilogue of
+// zse_gemm_w4, for a GEMM whose activations `x` are the context's gathered buffer - its prologue is the all-gather's
+// receiving side.  `wait_gather` != 0 on both: also wait for the gathered rows of the own token tile.
+// Replaces ncclAllReduce after o_proj / down_proj in the reference's prefill
+// (zse-engine/zse_engine/orchestrator/model_runner.py:2823-2827,2872-2876).
+extern "C" int zse_tp_gemm_w4_scatter(void* ctx, const void* w_tiled, const void* x, int x_rows_cap, int M, int N,
+                                      int K, int slot, int rank_override, void* status, void* stream) {
+  SpTable sp;
+  if (int rc = tp_fill_sp_table(ctx, slot, false, rank_override, &sp)) return rc;
+  if (N != sp.H || N % kTileN || M <= 64 || (M + kSpRowBlock - 1) / kSpRowBlock > sp.nblk_cap) return ZSE_ERR_SHAPE;
+  return run_gemm_w4(w_tiled, x, x_rows_cap, nullptr, nullptr, M, N, K, N, kEpiScatterF16, 0, status, stream, nullptr,
+                     nullptr, &sp, nullptr);
+}
+
+extern "C" int zse_tp_gemm_w4_gathered(void* ctx, const void* w_tiled, const void* x, int x_rows_cap,
+                                       const void* bias, void* out, int M, int N, int K, int ldo, int epilogue,
+                                       int k_split, int rank_override, void* status, void* stream) {
+  if (epilogue == kEpiPushF16 || epilogue == kEpiScatterF16) return ZSE_ERR_SHAPE;
+  SpTable sp;
+  if (int rc = tp_fill_sp_table(ctx, 0, false, rank_override, &sp)) return rc;
+  if (M <= 64 || (M + kSpRowBlock - 1) / kSpRowBlock > sp.nblk_cap) return ZSE_ERR_SHAPE;
+  const GatherWait g{sp.gflag[sp.rank], sp.state};
+  return run_gemm_w4(w_tiled, x, x_rows_cap, bias, out, M, N, K, ldo, epilogue, k_split, status, stream, nullptr,
+                     nullptr, nullptr, &g);
 }
 
 // How many clusters of `cluster` CTAs of the 64-token kernel (narrow: two CTAs per SM, or wide) the device can hold at

@@ -32,12 +32,16 @@ def main():
     vocab = synth.shape_config(shape).vocab_size
     prompts = [[rng.randrange(vocab) for _ in range(n)] for n in (300, 17, 150, 64)]
     results = {}
-    for backend in ("single", "fused", "push", "nccl"):
+    # "fused": decode passes run projection + all-reduce + residual + norm as ONE kernel; "two-kernel": the GEMM writes
+    # fp32 planes and a second kernel exchanges them; "push": the older exchange in the epilogue of the wide GEMM
+    for backend in ("single", "fused", "two-kernel", "push", "nccl"):
         tp = 1 if backend == "single" else world
-        os.environ["ZSE_TP_PUSH"] = "1" if backend == "push" else "0"   # exchange inside the row-parallel GEMM
+        os.environ["ZSE_TP_PUSH"] = "1" if backend == "push" else "0"
+        os.environ["ZSE_TP_FUSED_K1"] = "1" if backend == "fused" else "0"
+        os.environ["ZSE_TP_FUSED_SP_ROWS"] = "128" if backend == "fused" else "0"   # prefill: scatter / gather in the GEMMs
         cfg = EngineConfig(tp_size=tp, device_index=local, max_seq_len=512, max_batch_seqs=8, max_batch_tokens=1024,
                            prefill_chunk_size=512, quiet=True,
-                           comm_backend={"single": "fused", "push": "fused"}.get(backend, backend))
+                           comm_backend={"single": "fused", "push": "fused", "two-kernel": "fused"}.get(backend, backend))
         comm = None
         if tp > 1:
             comm = make_comm(cfg.comm_backend, rank, world, dev, hidden_size=synth.SHAPES[shape]["hidden_size"],
@@ -46,10 +50,14 @@ def main():
         ids = [eng.add_request_tokens(p, max_tokens=12, temperature=0.0, stop_tokens=[]) for p in prompts]
         eng.run_until_done()
         results[backend] = [eng.get_result(i).output_tokens for i in ids]
+        if backend == "fused":
+            assert comm.fused_k1 and comm.k1_calls > 0, "the one-kernel path did not run"
+            assert comm.sp_calls > 0, "the prefill passes did not take the scatter / gather path"
         eng.destroy()
         torch.cuda.synchronize()
         dist.barrier()
     # sampling without a seed: the default seed must not depend on the process, or the ranks pick different tokens
+    os.environ["ZSE_TP_PUSH"], os.environ["ZSE_TP_FUSED_K1"], os.environ["ZSE_TP_FUSED_SP_ROWS"] = "0", "1", "128"
     cfg = EngineConfig(tp_size=world, device_index=local, max_seq_len=512, max_batch_seqs=8, max_batch_tokens=1024,
                        prefill_chunk_size=512, quiet=True, comm_backend="fused")
     comm = make_comm("fused", rank, world, dev, hidden_size=synth.SHAPES[shape]["hidden_size"],
@@ -68,6 +76,7 @@ def main():
     same_fused = sum(a == b for a, b in zip(results["fused"], results["single"]))
     same_nccl = sum(a == b for a, b in zip(results["nccl"], results["single"]))
     same_push = sum(a == b for a, b in zip(results["push"], results["single"]))
+    same_two = sum(a == b for a, b in zip(results["two-kernel"], results["single"]))
     # fp16 rounding differs between one GPU and a sharded sum, so a near tie may flip a token: demand that every
     # rank agrees with every other rank exactly, and that most sequences match the single-GPU run token by token
     gathered = [None] * world
@@ -77,8 +86,11 @@ def main():
     dist.all_gather_object(gathered, results["push"])
     assert all(g == gathered[0] for g in gathered), "ranks disagree (push exchange)"
     assert same_push >= len(prompts) - 1, (results, same_push)
+    dist.all_gather_object(gathered, results["two-kernel"])
+    assert all(g == gathered[0] for g in gathered), "ranks disagree (two-kernel exchange)"
+    assert same_two >= len(prompts) - 1, (results, same_two)
     if rank == 0:
-        print(f"TP_ENGINE_OK ranks {world} shape {shape} fused {same_fused}/{len(prompts)} push {same_push}/{len(prompts)} "
+        print(f"TP_ENGINE_OK ranks {world} shape {shape} fused {same_fused}/{len(prompts)} two-kernel {same_two}/{len(prompts)} push {same_push}/{len(prompts)} "
               f"nccl {same_nccl}/{len(prompts)}")
     dist.barrier()
     dist.destroy_process_group()

@@ -146,6 +146,82 @@ def test_gemm_push_exchange_emulated_ranks(ops, tp, M, H, Kr):
     native.tp_ctx_destroy(ctx)
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("tp,M,H", [(2, 130, 1024), (4, 300, 1024), (8, 1000, 2560)])
+def test_scatter_reduce_gather_emulated_ranks(ops, tp, M, H):
+    """The prefill exchange on one GPU: every emulated rank runs its row-parallel INT4 GEMM, whose epilogue stores each
+    64-row block of fp16 partial sums into the inbox of the block's owner and counts (tile, chunk) units in - shards of
+    different width, hence different K splits, must add up to the same total.  The reduce kernel (all ranks in one
+    launch, nothing waits for a kernel that is not running) adds the rows, applies residual + RMSNorm on the owner and
+    stores the rows into every rank's gathered buffer; a GEMM reading that buffer passes its prologue wait."""
+    from zse_b200.ops import native
+    from test_kernels_gpu import _w4_parts_gpu
+    m_cap = 1024
+    nblk = m_cap // 64
+    own_cap = (nblk + tp - 1) // tp * 64
+    ctx, keep = _emulated_ctx(tp, 64, H)
+    z = lambda n, dt: [torch.zeros(n, dtype=dt, device="cuda") for _ in range(tp)]
+    inbox, arrive = z(2 * tp * own_cap * H, torch.float16), z(2 * tp * nblk, torch.int32)
+    xg, gflag, state = z(nblk * 64 * H, torch.float16), z(nblk, torch.int32), z(4 + nblk, torch.int32)
+    ptr = lambda ts: [t.data_ptr() for t in ts]
+    native.tp_ctx_set_sp(ctx, own_cap, nblk, ptr(inbox), ptr(arrive), ptr(xg), 0, ptr(gflag), ptr(state))
+    status = native.Status("cuda")
+    wn = (1 + 0.1 * torch.randn(H, device="cuda")).half()
+    res0 = torch.randn(M, H, device="cuda")
+    residuals = [res0.clone() for _ in range(tp)]
+    shards, xs, partial = [], [], []
+    for r in range(tp):
+        Kr = 512 + 384 * (r % 3)                      # uneven shards: the ranks plan different K splits
+        part, wd = _w4_parts_gpu(H, Kr, 70 + r)
+        shards.append(ops.make_linear([part], Kr, 128))
+        xs.append((torch.randn(M, Kr, device="cuda") * 0.5).half())
+        partial.append((xs[r].float() @ wd.T).half().float())
+    nb = (M + 63) // 64
+    owner_of_row = (torch.arange(M, device="cuda") // 64) % tp
+    want = res0.clone()
+    part2, wd2 = _w4_parts_gpu(256, H, 5)
+    w2 = ops.make_linear([part2], H, 128)
+    for call in range(3):
+        slot = call & 1
+        for r in range(tp):
+            native.tp_gemm_w4_scatter(ctx, shards[r].data, xs[r], M, M, H, shards[r].K, slot, status.ptr,
+                                      rank_override=r)
+        native.tp_sp_sum_norm_gather_emulated(ctx, residuals, wn, M, 1e-6, slot, status.ptr)
+        torch.cuda.synchronize()
+        status.check()
+        want = want + sum(partial)
+        normed = ref.rmsnorm(want, wn, 1e-6).float()
+        for r in range(tp):
+            mine = owner_of_row == r
+            assert _rel_close(residuals[r][mine], want[mine]), (call, r)
+            got = xg[r].view(nblk * 64, H)[:M].float()
+            assert (got - normed).abs().max() < 3e-2, (call, r)
+            assert torch.equal(xg[r], xg[0])                       # every rank holds the same gathered rows
+            assert torch.all(gflag[r][:nb] == call + 1) and int(state[r][0]) == call + 1
+            assert int(arrive[r].abs().sum()) == 0                 # counters taken down for the call after next
+        # rows a rank does not own keep their old residual (the stream is sharded by rows during such a pass)
+        other = owner_of_row != 0
+        assert torch.equal(residuals[0][other], res0[other])
+        # the consumer GEMM on the gathered buffer (prologue wait satisfied) equals the plain GEMM on the same rows
+        a = torch.zeros(M, 256, dtype=torch.float16, device="cuda")
+        bb = torch.zeros_like(a)
+        xv = xg[1 % tp].view(nblk * 64, H)
+        native.tp_gemm_w4_gathered(ctx, w2.data, xv, xv.shape[0], None, a, M, 256, H, 256, 0, 0, status.ptr,
+                                   rank_override=1 % tp)
+        native.gemm_w4(w2.data, xv, xv.shape[0], None, bb, M, 256, H, 256, 0, 0, status.ptr)
+        torch.cuda.synchronize()
+        status.check()
+        assert torch.equal(a, bb)
+    # rows that never arrive: the GEMM's prologue gives up with a status instead of hanging, and loads nothing
+    state[0][0] += 1                                               # rank 0 expects an epoch nobody has published
+    native.tp_gemm_w4_gathered(ctx, w2.data, xg[0].view(nblk * 64, H), nblk * 64, None, a, M, 256, H, 256, 0, 0,
+                               status.ptr, rank_override=0)
+    torch.cuda.synchronize()
+    code, _, where, _ = status.read()
+    assert (code, where) == (3, 36)
+    native.tp_ctx_destroy(ctx)
+
+
 def _k1_ctx(tp, m_cap, H):
     from zse_b200.ops import native
     ctx, keep = _emulated_ctx(tp, m_cap, H)

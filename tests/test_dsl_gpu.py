@@ -55,5 +55,5 @@ def test_gpu_memory_and_profile():
     x = torch.randn(1 << 16, device="cuda")
     o = torch.zeros_like(x)
     r = K.silu.profile(((1 << 16) // 256,), (256,), (x, o, 1 << 16), nbytes=2 * 4 * (1 << 16))
-    assert r.us > 0
+    assert r.ms > 0 and r.launches > 0
     torch.testing.assert_close(o, torch.nn.functional.silu(x), atol=1e-5, rtol=1e-4)

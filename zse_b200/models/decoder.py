@@ -252,8 +252,23 @@ class DecoderModel:
     # ---- buffers --------------------------------------------------------------------------------------
     def make_buffers(self, max_tokens: int, max_seqs: int, max_blocks: int, logits_rows: Optional[int] = None,
                      max_planes: int = 8, attn_splits: int = 1) -> StepBuffers:
-        return StepBuffers(self.config, self.plan, self.device, max_tokens, max_seqs, max_blocks, max_planes,
-                           logits_rows or max_seqs, attn_splits)
+        b = StepBuffers(self.config, self.plan, self.device, max_tokens, max_seqs, max_blocks, max_planes,
+                        logits_rows or max_seqs, attn_splits)
+        sp = getattr(self.comm, "sp_xnorm", None)
+        if sp is not None and sp.shape[0] >= max_tokens and sp.shape[1] == self.config.hidden_size:
+            # the normalised activations live in the symmetric buffer other ranks store gathered rows into
+            b.xnorm = sp[:max_tokens]
+        return b
+
+    @property
+    def _sp_weights_ok(self) -> bool:
+        """The row-block exchange handles a pass only as a whole: every projection INT4, no bias on o / down."""
+        ok = getattr(self, "_sp_ok_cache", None)
+        if ok is None:
+            ok = all(L.qkv.kind == L.o.kind == L.gate_up.kind == L.down.kind == "w4t" and L.o.bias is None
+                     and L.down.bias is None and L.gate_up.swiglu for L in self.layers) and not self.config.is_gemma
+            self._sp_ok_cache = ok
+        return ok
 
     # ---- forward --------------------------------------------------------------------------------------
     def _add_norm(self, b: StepBuffers, planes: int, weight: torch.Tensor, M: int, add=None) -> None:
@@ -284,6 +299,14 @@ class DecoderModel:
         tensor-parallel exchange ran inside the GEMM - minus the CTA count the consumer has to wait for, or None when
         one kernel did the projection, the all-reduce, the residual add and the RMSNorm with ``norm_w``."""
         comm = self.comm
+        if (comm is not None and norm_w is not None and add is None and self.lora is None
+                and getattr(comm, "sp_xnorm", None) is not None and b.xnorm.data_ptr() == comm.sp_xnorm.data_ptr()
+                and self._sp_weights_ok and comm.can_sp(w, M)):
+            # many rows: reduce-scatter in the GEMM's epilogue, reduce + norm on the owner, gather into every rank's
+            # b.xnorm; the GEMMs that read b.xnorm next wait for their rows themselves (self._sp_live)
+            comm.linear_scatter_norm(self.ops, w, x, M, b.residual, norm_w, self.config.rms_norm_eps)
+            self._sp_live = True
+            return None
         if (comm is not None and norm_w is not None and add is None and getattr(comm, "fused_k1", False)
                 and comm.can_fuse_k1(self.ops, w, M)):
             comm.linear_allreduce_norm(self.ops, w, x, M, b.residual, norm_w, b.xnorm, self.config.rms_norm_eps)
@@ -309,9 +332,15 @@ class DecoderModel:
         ops.embedding(self.embed, b.ids, b.residual, M, self.embed_scale)
         planes, add = 0, None
         lora = self.lora
+        self._sp_live = False          # b.xnorm currently arrives from other ranks (sequence-parallel exchange)
         for li, L in enumerate(self.layers):
             self._add_norm(b, planes, L.ln1, M, add)
-            if (self.lora is None and self.rope_table is not None
+            gather = self.comm._ctx if self._sp_live else None
+            if gather is not None:
+                ops.linear(L.qkv, b.xnorm, M, b.qkv, gather=gather)
+                ops.rope_kv_write(b.qkv, kv[li], b.positions, b.slots, self.inv_freq, M, p.num_heads,
+                                  p.num_kv_heads, c.head_dim, bs)
+            elif (self.lora is None and self.rope_table is not None
                     and ops.qkv_rope_fused_ok(L.qkv, M, c.head_dim, kv[li])):
                 ops.qkv_rope_fused(L.qkv, b.xnorm, M, b.qkv, kv[li], b.positions, b.slots, self.rope_table,
                                    p.num_heads, p.num_kv_heads, bs)
@@ -338,11 +367,14 @@ class DecoderModel:
             if lora is not None and (lora.has(li, "gate_proj") or lora.has(li, "up_proj")):
                 self._mlp_in_with_lora(li, L, b, M)
             else:
-                ops.linear_swiglu(L.gate_up, b.xnorm, M, b.act)
+                ops.linear_swiglu(L.gate_up, b.xnorm, M, b.act, gather=self.comm._ctx if self._sp_live else None)
             add = lora.delta(li, "down_proj", b.act, b, M) if lora is not None else None
             next_norm = self.layers[li + 1].ln1 if li + 1 < len(self.layers) else self.norm
             planes = self._row_parallel(L.down, b.act, M, b, next_norm, add)
         self._add_norm(b, planes, self.norm, M, add)
+        if self._sp_live:              # the final normalised rows come from their owners: wait for all of them
+            self.comm.sp_wait(ops, M)
+            self._sp_live = False
         if n_logit_rows:
             torch.index_select(b.xnorm, 0, b.logit_rows[:n_logit_rows], out=b.xsel[:n_logit_rows])
             ops.linear(self.lm_head, b.xsel, n_logit_rows, b.logits)

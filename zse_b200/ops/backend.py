@@ -66,10 +66,10 @@ class TorchOps:
         pass
 
     # ---- ops ------------------------------------------------------------------------------------------
-    def linear(self, w: LinearWeight, x, M, out, x_cap=None):
+    def linear(self, w: LinearWeight, x, M, out, x_cap=None, gather=None):
         out[:M, : w.N] = ref.linear(x[:M], w.data, w.bias)
 
-    def linear_swiglu(self, w: LinearWeight, x, M, out, x_cap=None, gelu=False):
+    def linear_swiglu(self, w: LinearWeight, x, M, out, x_cap=None, gelu=False, gather=None):
         y = x[:M].float() @ w.data.T
         half = w.N // 2
         out[:M, :half] = ref.swiglu(y[:, :half], y[:, half:], gelu)
@@ -263,9 +263,16 @@ class CudaOps(TorchOps):
         return LinearWeight("f16", w.shape[0], K, w, b, swiglu, w.numel() * 2)
 
     # ---- ops ------------------------------------------------------------------------------------------
-    def linear(self, w, x, M, out, x_cap=None):
+    def linear(self, w, x, M, out, x_cap=None, gather=None):
+        """``gather``: a tensor-parallel context whose gathered activation buffer ``x`` is - the GEMM then waits, tile
+        by tile, for the rows to arrive from the ranks that own them (INT4 weights, more than 64 rows)."""
         cap = x.shape[0] if x_cap is None else x_cap
-        if w.kind == "w8t":
+        if gather is not None:
+            if w.kind != "w4t" or M <= 64:
+                raise NotImplementedError("a gathered activation buffer is read by the wide INT4 GEMM only")
+            self.n.tp_gemm_w4_gathered(gather, w.data, x, cap, w.bias, out, M, w.N, w.K, out.stride(0), EPI_F16, 0,
+                                       self.status.ptr)
+        elif w.kind == "w8t":
             if M <= 64 and out.stride(0) % 8 == 0 and self.n.gemm_w4_dec_supported(M, w.N, w.K, EPI_F16):
                 self.n.gemm_w8_dec(w.data, x, cap, w.bias, out, M, w.N, w.K, out.stride(0), EPI_F16, self.dec_ws,
                                    self.status.ptr)
@@ -281,9 +288,14 @@ class CudaOps(TorchOps):
         else:
             self.n.gemm_f16(w.data, w.N, x, cap, w.bias, out, M, w.N, w.K, out.stride(0), EPI_F16, 1, self.status.ptr)
 
-    def linear_swiglu(self, w, x, M, out, x_cap=None, gelu=False, tmp=None):
+    def linear_swiglu(self, w, x, M, out, x_cap=None, gelu=False, tmp=None, gather=None):
         cap = x.shape[0] if x_cap is None else x_cap
-        if w.kind == "w8t":
+        if gather is not None:
+            if w.kind != "w4t" or M <= 64 or gelu:
+                raise NotImplementedError("a gathered activation buffer is read by the wide INT4 GEMM only")
+            self.n.tp_gemm_w4_gathered(gather, w.data, x, cap, None, out, M, w.N, w.K, out.stride(0), EPI_SWIGLU, 0,
+                                       self.status.ptr)
+        elif w.kind == "w8t":
             if (not gelu and M <= 64 and out.stride(0) % 8 == 0
                     and self.n.gemm_w4_dec_supported(M, w.N, w.K, EPI_SWIGLU)):
                 self.n.gemm_w8_dec(w.data, x, cap, None, out, M, w.N, w.K, out.stride(0), EPI_SWIGLU, self.dec_ws,

@@ -114,6 +114,17 @@ _SIGS = {
                                                c_void_p]),
     "zse_tp_sum_add_rmsnorm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_int, c_int, c_void_p,
                                        c_void_p]),
+    "zse_tp_ctx_set_sp": (c_int, [c_void_p, c_int, c_int, POINTER(c_uint64), POINTER(c_uint64), POINTER(c_uint64),
+                                  c_uint64, POINTER(c_uint64), POINTER(c_uint64)]),
+    "zse_tp_gemm_w4_scatter": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                                       c_void_p]),
+    "zse_tp_gemm_w4_gathered": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int,
+                                        c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "zse_tp_sp_sum_norm_gather": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_float, c_int, c_int, c_void_p,
+                                          c_void_p]),
+    "zse_tp_sp_sum_norm_gather_emulated": (c_int, [c_void_p, POINTER(c_uint64), c_void_p, c_int, c_float, c_int,
+                                                   c_void_p, c_void_p]),
+    "zse_tp_sp_wait": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p]),
     "zse_tp_sum_add_rmsnorm_emulated": (c_int, [c_void_p, POINTER(c_uint64), c_void_p, POINTER(c_uint64), c_int,
                                                 c_float, c_int, c_int, c_void_p, c_void_p]),
     "zse_tp_argmax": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
@@ -458,6 +469,40 @@ def tp_gemm_dec_allreduce_norm(ctx, w_tiled, int8_weights, x, x_rows_cap, M, N, 
     _ck(load().zse_tp_gemm_dec_allreduce_norm(ctx, _p(w_tiled), int(int8_weights), _p(x), x_rows_cap, M, N, K, slot,
                                               int(use_multimem), rank_override, _p(residual), _p(norm_w), _p(xnorm),
                                               eps, _p(workspace), status, _stream()), "tp_gemm_dec_allreduce_norm")
+
+
+def tp_ctx_set_sp(ctx, own_cap, nblk_cap, inbox_ptrs, arrive_ptrs, xg_ptrs, mc_xg, gflag_ptrs, state_ptrs):
+    _ck(load().zse_tp_ctx_set_sp(ctx, own_cap, nblk_cap, _u64s(inbox_ptrs), _u64s(arrive_ptrs), _u64s(xg_ptrs),
+                                 int(mc_xg), _u64s(gflag_ptrs), _u64s(state_ptrs)), "tp_ctx_set_sp", 0)
+
+
+def tp_gemm_w4_scatter(ctx, w_tiled, x, x_rows_cap, M, N, K, slot, status, rank_override=-1):
+    """Row-parallel INT4 GEMM whose epilogue is the reduce-scatter: each 64-row block of partial sums goes to the rank
+    that owns it (csrc/gemm_w4.cu, kEpiScatterF16)."""
+    _ck(load().zse_tp_gemm_w4_scatter(ctx, _p(w_tiled), _p(x), x_rows_cap, M, N, K, slot, rank_override, status,
+                                      _stream()), "tp_gemm_w4_scatter")
+
+
+def tp_gemm_w4_gathered(ctx, w_tiled, x, x_rows_cap, bias, out, M, N, K, ldo, epilogue, k_split, status,
+                        rank_override=-1):
+    """zse_gemm_w4 on the gathered activation buffer: the activation producer waits for the row blocks of its token
+    tile to arrive from their owners before it loads them (the all-gather's receiving side)."""
+    _ck(load().zse_tp_gemm_w4_gathered(ctx, _p(w_tiled), _p(x), x_rows_cap, _p(bias), _p(out), M, N, K, ldo, epilogue,
+                                       k_split, rank_override, status, _stream()), "tp_gemm_w4_gathered")
+
+
+def tp_sp_sum_norm_gather(ctx, residual, weight, M, eps, slot, use_multimem, status):
+    _ck(load().zse_tp_sp_sum_norm_gather(ctx, _p(residual), _p(weight), M, eps, slot, int(use_multimem), status,
+                                         _stream()), "tp_sp_sum_norm_gather")
+
+
+def tp_sp_sum_norm_gather_emulated(ctx, residuals, weight, M, eps, slot, status):
+    _ck(load().zse_tp_sp_sum_norm_gather_emulated(ctx, _u64s([t.data_ptr() for t in residuals]), _p(weight), M, eps,
+                                                  slot, status, _stream()), "tp_sp_sum_norm_gather_emulated")
+
+
+def tp_sp_wait(ctx, M, status, rank_override=-1):
+    _ck(load().zse_tp_sp_wait(ctx, M, rank_override, status, _stream()), "tp_sp_wait")
 
 
 def tp_sum_add_rmsnorm(ctx, residual, weight, out, M, eps, slot, expected_add, status):

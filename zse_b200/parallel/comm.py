@@ -213,6 +213,7 @@ class FusedComm(NcclComm):
         # Decode-sized passes: the row-parallel projection, the all-reduce, the residual add and the next RMSNorm are ONE
         # kernel (csrc/gemm_w4_dec.cu, kDecAllReduceNorm); it uses the same inboxes and counters as the push exchange.
         self.fused_k1 = env.flag("ZSE_TP_FUSED_K1")
+        self.k1_calls = 0
         if self.push or self.fused_k1:
             self._init_push(symm, grp, world, rank, device, hidden_size, want_mm)
         # passes with at least this many rows (prefill) use the two-shot kernel: reduce-scatter by rows + all-gather,
@@ -223,6 +224,15 @@ class FusedComm(NcclComm):
         # row), while for decode-sized passes they win by 1.2-1.4x.  ZSE_TP_NCCL_ROWS moves the switch-over point.
         self.nccl_min_rows = env.integer("ZSE_TP_NCCL_ROWS")
         self._f16: Optional[torch.Tensor] = None
+        # Passes of many rows (prefill): the row-parallel GEMM scatters its tiles to the owners of 64-row blocks, the
+        # owner reduces + normalises and stores the rows to every rank, and the next GEMM waits for its tiles' rows in
+        # its prologue (csrc/gemm_w4.cu kEpiScatterF16 / gather_wait_tile, csrc/comm.cu tp_sp_sum_norm_gather_kernel).
+        self.sp_min_rows = env.integer("ZSE_TP_FUSED_SP_ROWS")
+        self.sp_xnorm: Optional[torch.Tensor] = None
+        self.sp_calls = 0
+        self._sp_slot = 0
+        if self.sp_min_rows > 0 and hidden_size % 128 == 0 and hidden_size <= 8192:
+            self._init_sp(symm, grp, world, rank, device, hidden_size, max_tokens, want_mm)
 
     def _init_push(self, symm, grp, world, rank, device, H, want_mm) -> None:
         align = lambda n: (n + 255) // 256 * 256
@@ -248,6 +258,53 @@ class FusedComm(NcclComm):
                                 [p + offs[1] for p in ptrs], (mc + offs[1]) if mc else 0, state_ptrs)
         self._push_ready = True
 
+    def _init_sp(self, symm, grp, world, rank, device, H, max_tokens, want_mm) -> None:
+        align = lambda n: (n + 255) // 256 * 256
+        nblk = (max_tokens + 63) // 64
+        own_cap = (nblk + world - 1) // world * 64
+        sizes = [2 * world * own_cap * H * 2, 2 * world * nblk * 4, nblk * 64 * H * 2, nblk * 4]
+        offs = [0]
+        for n in sizes:
+            offs.append(offs[-1] + align(n))
+        self._sbuf = symm.empty(offs[-1], dtype=torch.uint8, device=device)
+        self._sbuf.zero_()
+        self._shdl = symm.rendezvous(self._sbuf, grp)
+        torch.cuda.synchronize(device)
+        dist.barrier(group=grp)
+        ptrs = [int(p) for p in self._shdl.buffer_ptrs]
+        mc = 0
+        if want_mm:
+            try:
+                mc = int(self._shdl.multicast_ptr or 0)
+            except Exception:
+                mc = 0
+        self.sp_multimem = bool(mc)
+        self._sstate = torch.zeros(4 + nblk, dtype=torch.int32, device=device)
+        state_ptrs = [self._sstate.data_ptr() if r == rank else 0 for r in range(world)]
+        self._n.tp_ctx_set_sp(self._ctx, own_cap, nblk, [p + offs[0] for p in ptrs], [p + offs[1] for p in ptrs],
+                              [p + offs[2] for p in ptrs], (mc + offs[2]) if mc else 0, [p + offs[3] for p in ptrs],
+                              state_ptrs)
+        # the gathered activations are the decoder's normalised-activation buffer itself
+        self.sp_xnorm = self._sbuf[offs[2]: offs[2] + nblk * 64 * H * 2].view(torch.float16).view(nblk * 64, H)
+
+    def can_sp(self, w, M: int) -> bool:
+        """Whether ``linear_scatter_norm`` takes this row-parallel projection."""
+        return bool(self.sp_xnorm is not None and M >= max(65, self.sp_min_rows) and M <= self.sp_xnorm.shape[0]
+                    and w.kind == "w4t" and w.N == self.H and w.bias is None)
+
+    def linear_scatter_norm(self, ops, w, x, M: int, residual, weight, eps: float) -> None:
+        """Own rows of ``residual`` += reduce-scatter(x W^T); ``sp_xnorm`` on every rank = RMSNorm of those rows.  Two
+        launches, no NCCL: the GEMM's epilogue is the scatter, the reduce kernel's stores are the gather."""
+        self._n.tp_gemm_w4_scatter(self._ctx, w.data, x, x.shape[0], M, w.N, w.K, self._sp_slot, ops.status.ptr)
+        self._n.tp_sp_sum_norm_gather(self._ctx, residual, weight, M, float(eps), self._sp_slot, self.sp_multimem,
+                                      ops.status.ptr)
+        self._sp_slot ^= 1
+        self.sp_calls += 1
+
+    def sp_wait(self, ops, M: int) -> None:
+        """Orders readers that are not gather-aware GEMMs after the arrival of all rows of the pass."""
+        self._n.tp_sp_wait(self._ctx, M, ops.status.ptr)
+
     def can_fuse_k1(self, ops, w, M: int) -> bool:
         """Whether ``linear_allreduce_norm`` takes this projection (tiled INT4 / INT8 weights, at most 64 rows)."""
         return bool(self.fused_k1 and self._push_ready and w.kind in ("w4t", "w8t") and M <= min(64, self.push_rows)
@@ -260,6 +317,7 @@ class FusedComm(NcclComm):
                                            self._calls & 1, self.push_multimem, residual, weight, out, float(eps),
                                            ops.dec_ws, ops.status.ptr)
         self._calls += 1
+        self.k1_calls += 1
 
     def can_push(self, w, M: int) -> bool:
         return self._push_ready and w.kind == "w4t" and M <= self.push_rows and w.N == self.H and w.bias is None
@@ -278,6 +336,7 @@ class FusedComm(NcclComm):
         """Every pass makes an even number of reductions (two per layer), so restarting the slot sequence at 0 keeps
         consecutive calls on alternating slots across passes and across CUDA-graph replays."""
         self._calls = 0
+        self._sp_slot = 0
 
     # The decoder calls this instead of (all_reduce_partials + add_rmsnorm).
     def reduce_add_rmsnorm(self, ops, residual, partials, planes, weight, out, M, eps) -> None:

@@ -24,6 +24,8 @@ KNOWN: Dict[str, Tuple[str, str]] = {
     "ZSE_TP_FUSED_K1": ("1", "decode-sized passes: row-parallel GEMM + all-reduce + residual + RMSNorm as one kernel"),
     "ZSE_TP_TWO_SHOT_ROWS": (str(1 << 30), "passes of at least this many rows take the two-shot reduce-scatter kernel"),
     "ZSE_TP_NCCL_ROWS": ("256", "passes of at least this many rows take NCCL instead of the fused exchange"),
+    "ZSE_TP_FUSED_SP_ROWS": ("128", "fused collectives: passes of at least this many rows scatter the row-parallel GEMM's "
+                                    "tiles to row-block owners and gather in the next GEMM's prologue (0: off)"),
     "ZSE_TP_SP": ("0", "sequence-parallel prefill on the NCCL path (reduce-scatter / all-gather, residual split by rows)"),
     "ZSE_TP_SP_MIN_ROWS": ("256", "smallest pass that takes the sequence-parallel path"),
     "ZSE_W4_DEC": ("3", "decode-sized INT4 layers through the persistent kernel: 1 gate/up + SwiGLU, 2 fused QKV + RoPE + "
