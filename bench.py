@@ -156,13 +156,21 @@ class ClockSampler:
                 "power_w_max": max(power) if power else None, "samples": len(sm), "reasons": sorted(reasons)}
 
 
-def trace_kernels(eng, path, barrier, steps: int = 5) -> None:
-    """Per-kernel device time of `steps` more engine steps (every rank steps; rank 0 writes the table)."""
+def trace_kernels(eng, path, barrier, steps: int = 5, until=None) -> None:
+    """Per-kernel device time of `steps` more engine steps, or of the steps until `until()` is false (every rank
+    steps; rank 0 writes the table)."""
+    import torch
     from torch.profiler import ProfilerActivity, profile
     barrier()
     with profile(activities=[ProfilerActivity.CUDA]) as prof:
-        for _ in range(steps):
-            eng.step()
+        if until is None:
+            for _ in range(steps):
+                eng.step()
+        else:
+            steps = 0
+            while until() and steps < 10000:
+                eng.step()
+                steps += 1
         torch.cuda.synchronize()
     barrier()
     if path is None:
@@ -240,8 +248,14 @@ def run_ours(args):
     # untimed: prefill everything (chunked, packed), interleaved with decode of the sequences already admitted
     t_pf = time.time()
     guard = 0
+    if args.trace_kernels:         # diagnostic run: the prefill passes under the tracer as well (prefill_s then includes it)
+        trace_kernels(eng, args.trace_kernels + ".prefill" if rank == 0 else None, barrier,
+                      until=lambda: bool(eng.scheduler.num_waiting or eng.scheduler.num_prefilling))
+    prefill_steps = []             # wall time of every step of the prefill phase (each step ends with a token read-back)
     while (eng.scheduler.num_waiting or eng.scheduler.num_prefilling) and guard < 10000:
+        t_s = time.perf_counter()
         eng.step()
+        prefill_steps.append(round((time.perf_counter() - t_s) * 1000.0, 1))
         guard += 1
     torch.cuda.synchronize()
     prefill_s = time.time() - t_pf
@@ -330,10 +344,12 @@ def run_ours(args):
                     "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "api": "ZStreamerEngine.add_request_tokens + ZStreamerEngine.step"},
             "gpu_launches": int(launches), "clocks": clocks,
-            "extra": {"cold_start_s": round(cold, 2), "prefill_s": round(prefill_s, 2),
+            "extra": {"cold_start_s": round(cold, 2), "prefill_s": round(prefill_s, 2), "prefill_step_ms": prefill_steps,
                       "init_times": {k: round(v, 2) for k, v in eng.init_times.items()},
                       "kv_blocks": eng.kv_cache.num_total_blocks, "block_size": eng.kv_cache.block_size,
-                      "graph_replays": runner.timings["graph_replays"], "impl": "ours",
+                      "graph_replays": runner.timings["graph_replays"],
+                      "graph_captures": runner.timings.get("graph_captures", 0),
+                      "graph_capture_s": round(runner.timings.get("graph_capture_s", 0.0), 3), "impl": "ours",
                       "ttft_p50_ms": round(ttfts[len(ttfts) // 2], 1) if ttfts else None,
                       "ttft_max_ms": round(ttfts[-1], 1) if ttfts else None,
                       "tpot_p50_ms": round(sorted(step_ms)[len(step_ms) // 2], 3) if step_ms else None,

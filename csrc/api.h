@@ -175,6 +175,12 @@ int zse_tp_ctx_set_push(void* ctx, int push_m_cap, const uint64_t* inbox_ptrs, u
 // returns the number of CTAs launched (what the consumer waits for from every rank) or a negative error
 int zse_tp_gemm_w4_push(void* ctx, const void* w_tiled, const void* x, int x_rows_cap, int M, int N, int K, int slot,
                         int use_multimem, int rank_override, void* status, void* stream);
+// Decode-sized passes (M <= 64): row-parallel projection (INT4 or INT8 tiles), the exchange of the partial rows, the
+// residual add and the next RMSNorm in ONE kernel (gemm_w4_dec.cu).  tp = 1 contexts work too (nothing to exchange).
+int zse_tp_gemm_dec_allreduce_norm(void* ctx, const void* w_tiled, int int8_weights, const void* x, int x_rows_cap,
+                                   int M, int N, int K, int slot, int use_multimem, int rank_override, void* residual,
+                                   const void* norm_w, void* xnorm, float eps, void* workspace, void* status,
+                                   void* stream);
 int zse_tp_sum_add_rmsnorm(void* ctx, void* residual, const void* weight, void* out, int M, float eps, int slot,
                            int expected_add, void* status, void* stream);
 int zse_tp_sum_add_rmsnorm_emulated(void* ctx, const uint64_t* residuals, const void* weight, const uint64_t* outs,

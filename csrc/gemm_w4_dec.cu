@@ -54,6 +54,7 @@ constexpr int kW8ChunkBytes = 16640; // INT8 chunk: 128 rows x 128 K int8 + 128 
 constexpr int kDecProducerWarp = 4;
 constexpr int kDecDqWarp0 = 5;
 constexpr int kDecEpiWarp0 = 21;
+constexpr int kDecWorkerWarps = 20;      // dequant + epilogue warps: what runs the tails of the kernel
 constexpr int kDecStageBytes = 64 * 128 * 4;     // finished sums of one tile: [token column][128 rows] fp32
 
 enum DecEpilogue : int { kDecF16 = 0, kDecSwiGLU = 1, kDecF32 = 2, kDecQkvRope = 3, kDecAllReduceNorm = 4 };
@@ -153,6 +154,12 @@ __device__ __forceinline__ uint32_t dec_ld_acquire_sys(const uint32_t* p) {
   uint32_t v;
   asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
+}
+__device__ __forceinline__ void dec_red_add_release_gpu(uint32_t* p, uint32_t v) {
+  asm volatile("red.release.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint32_t dec_ld_acquire(const uint32_t* p, bool device_scope) {
+  return device_scope ? ld_acquire_gpu_u32(p) : dec_ld_acquire_sys(p);
 }
 __device__ __forceinline__ uint4 dec_ld_relaxed_sys_v4(const void* p) {
   uint4 v;
@@ -656,31 +663,64 @@ __device__ __forceinline__ void dec_split_finish(const DecArgs& a, const float* 
 // own sums are on their way: count this CTA's units in on every rank, then, for the token rows this CTA owns
 // (row = cta, cta + grid, ...), wait for all sources, add, residual, RMSNorm.
 __device__ __forceinline__ void dec_allreduce_norm_tail(const DecArgs& a, DecBars* bars, float* red, int cta,
-                                                        int n_cta, uint32_t my_units, bool pushed_ok, int et) {
+                                                        int n_cta, uint32_t my_units, bool pushed_ok, int et,
+                                                        long long* tacc = nullptr, long long t_entry = 0) {
   const DecTpNorm& tn = a.tpn;
   const PushTable& pt = tn.push;
   volatile int* abort_flag = &bars->abort_flag;
   const int tp = pt.tp, H = pt.H, nch = H / 8;
-  epi_bar(1);                                              // every store of this CTA has been issued
-  if (et == 0 && pushed_ok && my_units > 0) {
-    __threadfence_system();
-    const int ctr = pt.slot * tp + pt.rank;
-    if (pt.mc_arrive != nullptr) {
-      dec_multimem_red_add_release(pt.mc_arrive + ctr, my_units);
-    } else {
-      for (int k = 0; k < tp; ++k) dec_red_add_release_sys(pt.arrive[k] + ctr, my_units);
+  const int ctr_i = pt.slot * tp + pt.rank;
+  const bool local_fast = pt.mc_arrive == nullptr;        // own counter at device scope, counted per warp
+  // ---- count in.  This GPU's own waiters are served first and cheaply: every worker warp releases its own stores
+  // at device scope (no CTA barrier, no system-scope fence on that path), so the own counter runs kDecWorkerWarps
+  // times as fast as the ones the peers see.
+  __syncwarp();
+  if (local_fast && (et & 31) == 0 && pushed_ok && my_units > 0)
+    dec_red_add_release_gpu(pt.arrive[pt.rank] + ctr_i, my_units);
+  // what does not depend on anybody else is fetched while the counters fill: the residual row and the norm weights
+  const bool owner = cta < a.M;
+  float4 rx[2], ry[2];
+  uint4 wr[2];
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    const int c = et + j * 640;
+    if (owner && c < nch) {
+      const float4* res = reinterpret_cast<const float4*>(tn.residual + size_t(cta) * H) + 2 * c;
+      rx[j] = res[0];
+      ry[j] = res[1];
+      wr[j] = reinterpret_cast<const uint4*>(tn.norm_w)[c];
     }
   }
+  if (tp > 1 || !local_fast) {
+    epi_bar(1);                                            // every store of this CTA has been issued
+    if (et == 0 && pushed_ok && my_units > 0) {
+      __threadfence_system();
+      if (pt.mc_arrive != nullptr) {
+        dec_multimem_red_add_release(pt.mc_arrive + ctr_i, my_units);
+      } else {
+        for (int k = 0; k < tp; ++k)
+          if (k != pt.rank) dec_red_add_release_sys(pt.arrive[k] + ctr_i, my_units);
+      }
+    }
+  }
+#ifdef ZSE_DEC_TIMING
+#define DTAIL(i) if (tacc != nullptr && cta == 1 && et == 512) a.timing[200 + (i)] = clock64() - t_entry
+#else
+#define DTAIL(i)
+#endif
+  DTAIL(0);
   bool ok = pushed_ok;
-  if (cta < a.M) {
+  if (owner) {
     // ---- wait until every source has delivered its rows (bounded; a lost peer ends in a status, not a hang)
     if (et < tp) {
-      const uint32_t target = tn.state[pt.slot] + tn.units_total;
+      const bool local = local_fast && et == pt.rank;
+      const uint32_t base = tn.state[pt.slot] + tn.units_total;
+      const uint32_t target = local ? base * uint32_t(kDecWorkerWarps) : base;
       const uint32_t* ctr = pt.arrive[pt.rank] + pt.slot * tp + et;
-      if (int32_t(dec_ld_acquire_sys(ctr) - target) < 0) {
+      if (int32_t(dec_ld_acquire(ctr, local) - target) < 0) {
         const uint64_t t0 = globaltimer_ns();
         unsigned spins = 0;
-        while (int32_t(dec_ld_acquire_sys(ctr) - target) < 0) {
+        while (int32_t(dec_ld_acquire(ctr, local) - target) < 0) {
           if ((++spins & 0x3F) == 0 && (*abort_flag || globaltimer_ns() - t0 > kWaitLimitNs)) {
             report(a.status, kPeerTimeout, 35, et);
             ok = false;
@@ -690,7 +730,11 @@ __device__ __forceinline__ void dec_allreduce_norm_tail(const DecArgs& a, DecBar
       }
     }
     ok = epi_all(ok, 1);
-    for (int row = cta; row < a.M; row += n_cta) {
+#ifdef ZSE_DEC_TIMING
+    if (tacc != nullptr) tacc[5] = clock64() - t_entry;
+#endif
+    int it = 0;
+    for (int row = cta; row < a.M; row += n_cta, ++it) {
       const __half* box = pt.inbox[pt.rank] + (size_t(pt.slot) * tp * pt.m_cap + row) * H;
       float vals[2][8];
       float ss = 0.f;
@@ -703,7 +747,8 @@ __device__ __forceinline__ void dec_allreduce_norm_tail(const DecArgs& a, DecBar
             uint4 got[kPushMaxTp];
 #pragma unroll
             for (int r = 0; r < kPushMaxTp; ++r)
-              if (r < tp) got[r] = dec_ld_relaxed_sys_v4(box + size_t(r) * pt.m_cap * H + size_t(c) * 8);
+              if (r < tp)         // ordered by the acquire above; L2 is where peer stores land, so bypass L1 only
+                got[r] = __ldcg(reinterpret_cast<const uint4*>(box + size_t(r) * pt.m_cap * H + size_t(c) * 8));
 #pragma unroll
             for (int r = 0; r < kPushMaxTp; ++r) {           // rank order: the same sum on every rank
               if (r < tp) {
@@ -717,10 +762,22 @@ __device__ __forceinline__ void dec_allreduce_norm_tail(const DecArgs& a, DecBar
               }
             }
           }
+#ifdef ZSE_DEC_TIMING
+          if (tacc != nullptr && cta == 1 && et == 512 && j == 0)
+            a.timing[204] = (clock64() - t_entry) + (__float_as_uint(acc[0]) & 1u);
+#endif
           float4* res = reinterpret_cast<float4*>(tn.residual + size_t(row) * H) + 2 * c;
-          float4 x = res[0], y = res[1];
+          if (it > 0) {                                     // rows after the first: nothing was fetched ahead
+            rx[j] = res[0];
+            ry[j] = res[1];
+          }
+          float4 x = rx[j], y = ry[j];
           x.x += acc[0]; x.y += acc[1]; x.z += acc[2]; x.w += acc[3];
           y.x += acc[4]; y.y += acc[5]; y.z += acc[6]; y.w += acc[7];
+#ifdef ZSE_DEC_TIMING
+          if (tacc != nullptr && cta == 1 && et == 512 && j == 0)
+            a.timing[205] = (clock64() - t_entry) + (__float_as_uint(x.x) & 1u);
+#endif
           res[0] = x;
           res[1] = y;
           vals[j][0] = x.x; vals[j][1] = x.y; vals[j][2] = x.z; vals[j][3] = x.w;
@@ -729,21 +786,22 @@ __device__ __forceinline__ void dec_allreduce_norm_tail(const DecArgs& a, DecBar
           for (int i = 0; i < 8; ++i) ss += vals[j][i] * vals[j][i];
         }
       }
+      DTAIL(1);
       if (tn.xnorm != nullptr) {
+        float* rd = red + (it & 1) * 32;                   // two buffers: one barrier per row is enough
         ss = warp_sum(ss);
-        if ((et & 31) == 0) red[et >> 5] = ss;
+        if ((et & 31) == 0) rd[et >> 5] = ss;
         epi_bar(1);
+        DTAIL(2);
         float tot = 0.f;
 #pragma unroll
-        for (int i = 0; i < 20; ++i) tot += red[i];
-        epi_bar(1);                                        // red is reused by the next row
+        for (int i = 0; i < kDecWorkerWarps; ++i) tot += rd[i];
         const float inv = rsqrtf(tot / float(H) + tn.eps);
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
           const int c = et + j * 640;
           if (c < nch) {
-            const uint4 wr = reinterpret_cast<const uint4*>(tn.norm_w)[c];
-            const __half2* wh = reinterpret_cast<const __half2*>(&wr);
+            const __half2* wh = reinterpret_cast<const __half2*>(&wr[j]);
             uint4 pk;
             uint32_t* po = reinterpret_cast<uint32_t*>(&pk);
 #pragma unroll
@@ -754,9 +812,13 @@ __device__ __forceinline__ void dec_allreduce_norm_tail(const DecArgs& a, DecBar
             reinterpret_cast<uint4*>(tn.xnorm + size_t(row) * H)[c] = pk;
           }
         }
+        DTAIL(3);
       }
     }
   }
+#ifdef ZSE_DEC_TIMING
+  if (tacc != nullptr) tacc[6] = clock64() - t_entry;
+#endif
   // the last CTA of the launch moves the running total on (every CTA that reads it has done so by then)
   epi_bar(1);
   if (et == 0) {
@@ -1047,6 +1109,7 @@ gemm_w4_dec_kernel(const __grid_constant__ CUtensorMap tmap_x, const DecArgs a) 
           ZSE_TMEM_ST_X32(dst, o);
           dec_dequant_half(pk[2], pk[3], s2, z2, o);
           ZSE_TMEM_ST_X32(dst + 32, o);
+          DACC(3, t3);
         } else {
           // INT8: a row is 128 bytes in eight 16-byte parts; K 0..63 first, the rest after the first TMEM store
           uint4 pk[4];
@@ -1075,8 +1138,8 @@ gemm_w4_dec_kernel(const __grid_constant__ CUtensorMap tmap_x, const DecArgs a) 
 #pragma unroll
           for (int p4 = 0; p4 < 4; ++p4) dec_dequant_w8_part(pk[p4], s2, o + p4 * 8);
           ZSE_TMEM_ST_X32(dst + 32, o);
+          DACC(3, t3);
         }
-        DACC(3, t3);
         DTICK(t4);
         tc_wait_st();
         tc_fence_before_sync();
@@ -1181,7 +1244,12 @@ gemm_w4_dec_kernel(const __grid_constant__ CUtensorMap tmap_x, const DecArgs a) 
       constexpr int G = Cfg::kGranules;
       const uint32_t units = seg < G ? uint32_t(ntp * ((G - seg + S - 1) / S)) : 0u;
       // the staging buffer of the stream plan is idle in the split plan: scratch for the block reduction
+#ifdef ZSE_DEC_TIMING
+      dec_allreduce_norm_tail(a, bars, stage, cta, n_cta, units, split_ok, wi * 128 + (warp & 3) * 32 + lane,
+                              warp >= kDecEpiWarp0 ? tacc : nullptr, t_entry);
+#else
       dec_allreduce_norm_tail(a, bars, stage, cta, n_cta, units, split_ok, wi * 128 + (warp & 3) * 32 + lane);
+#endif
     }
   }
 

@@ -71,8 +71,23 @@ struct Pass {
     return n;
   }
 
+  // o / down of a decode-sized pass with "residual += y; xnorm = RMSNorm(residual) * next_norm" in the GEMM kernel
+  // (the one-rank case of the tensor-parallel kernel).  Returns false when the layer has to take the two-kernel path.
+  bool row_fused(const ZseStepLinear& w, const void* x, const void* next_norm, int* slot) {
+    if (!ok() || !(m->dec_mode & 8) || b->norm_ctx == nullptr || b->dec_ws == nullptr || w.kind != ZSE_STEP_W4 ||
+        M > 64 || w.bias != nullptr || w.N != m->hidden || !zse_gemm_w4_dec_supported(M, w.N, w.K, 4))
+      return false;
+    int plan[2] = {0, 0};
+    zse_gemm_w4_dec_plan(w.N, w.K, 4, m->sm_count, plan);
+    if (plan[1] <= 0) return false;
+    did(zse_tp_gemm_dec_allreduce_norm(b->norm_ctx, w.data, 0, x, b->max_tokens, M, w.N, w.K, *slot, 0, -1, b->residual,
+                                       next_norm, b->xnorm, m->eps, b->dec_ws, b->status, stream));
+    *slot ^= 1;
+    return true;
+  }
+
   void add_norm(int planes, const void* weight) {
-    if (!ok()) return;
+    if (!ok() || planes < 0) return;          // planes < 0: the projection's own kernel added and normalised
     did(zse_add_rmsnorm(b->residual, b->partials, planes, nullptr, weight, b->xnorm, M, m->hidden, m->eps, stream));
   }
 };
@@ -99,7 +114,7 @@ extern "C" int zse_step_forward(const ZseStepModel* m, const ZseStepBuffers* b, 
   const int H = m->hidden, hd = m->head_dim, nh = m->num_heads, nkv = m->num_kv_heads;
   const int qkv_ld = (nh + 2 * nkv) * hd;
   p.did(zse_embedding(m->embed, b->ids, b->residual, M, H, m->vocab_rows, m->embed_scale, b->status, stream));
-  int planes = 0;
+  int planes = 0, slot = 0;
   for (int li = 0; li < m->num_layers && p.ok(); ++li) {
     const ZseStepLayer& L = m->layers[li];
     void* kv_layer = static_cast<char*>(kv) + size_t(li) * size_t(kv_layer_stride) * 2;
@@ -131,7 +146,9 @@ extern "C" int zse_step_forward(const ZseStepModel* m, const ZseStepBuffers* b, 
     else
       p.did(zse_attn_prefill(b->qkv, qkv_ld, kv_layer, b->block_tables, b->max_blocks, b->cu_q, b->q_pos0, b->attn_out,
                              nh * hd, num_seqs, max_q_len, nh, nkv, hd, block_size, m->scale, stream));
-    planes = p.linear_partial(L.o, b->attn_out, b->partials, b->max_planes, b->max_tokens);
+    planes = p.row_fused(L.o, b->attn_out, L.ln2, &slot) ? -1
+                                                          : p.linear_partial(L.o, b->attn_out, b->partials,
+                                                                             b->max_planes, b->max_tokens);
     p.add_norm(planes, L.ln2);
     if (!p.ok()) break;
     if (L.gate_up.kind == ZSE_STEP_W4 && (m->dec_mode & 1) && b->dec_ws != nullptr && M <= 64 && m->inter % 8 == 0 &&
@@ -146,7 +163,10 @@ extern "C" int zse_step_forward(const ZseStepModel* m, const ZseStepBuffers* b, 
                          L.gate_up.K, L.gate_up.N, kEpiF16, 1, b->status, stream));
       if (p.ok()) p.did(zse_swiglu(b->gate_up_tmp, b->act, M, L.gate_up.N / 2, 0, stream));
     }
-    planes = p.linear_partial(L.down, b->act, b->partials, b->max_planes, b->max_tokens);
+    const void* next_norm = li + 1 < m->num_layers ? m->layers[li + 1].ln1 : m->final_norm;
+    planes = p.row_fused(L.down, b->act, next_norm, &slot) ? -1
+                                                           : p.linear_partial(L.down, b->act, b->partials,
+                                                                              b->max_planes, b->max_tokens);
   }
   p.add_norm(planes, m->final_norm);
   if (n_logit_rows > 0 && p.ok()) {

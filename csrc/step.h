@@ -35,7 +35,8 @@ typedef struct {
   const ZseStepLayer* layers; /* host array of num_layers entries */
   const void* rope_table;     /* fp32 [max_position][64][2] cos/sin, or NULL (no fused QKV epilogue) */
   int32_t max_position;
-  int32_t dec_mode;           /* decode-sized INT4 layers through zse_gemm_w4_dec: 1 gate/up, 2 fused QKV, 4 the rest */
+  int32_t dec_mode;           /* decode-sized INT4 layers through zse_gemm_w4_dec: 1 gate/up, 2 fused QKV, 4 the rest,
+                                 8 o / down with the residual add and the next RMSNorm in the same kernel */
 } ZseStepModel;
 
 typedef struct {
@@ -61,6 +62,7 @@ typedef struct {
   void* attn_scratch; /* fp32, zse_attn_decode_scratch_floats(max_seqs, nh, hd, splits) */
   void* status;       /* 16-byte device status word */
   void* dec_ws;       /* workspace of zse_gemm_w4_dec (zse_gemm_w4_dec_workspace_bytes), or NULL */
+  void* norm_ctx;     /* one-rank tensor-parallel context with push buffers (dec_mode & 8), or NULL */
 } ZseStepBuffers;
 
 /* 1 when the driver can run this model with these buffers, else 0 (the caller keeps its own wiring) */

@@ -311,6 +311,12 @@ class DecoderModel:
                 and comm.can_fuse_k1(self.ops, w, M)):
             comm.linear_allreduce_norm(self.ops, w, x, M, b.residual, norm_w, b.xnorm, self.config.rms_norm_eps)
             return None
+        if (comm is None and norm_w is not None and add is None
+                and self.ops.residual_norm_fused_ok(w, M, self.config.hidden_size)):
+            self.ops.linear_residual_norm(w, x, M, b.residual, norm_w, b.xnorm, self.config.rms_norm_eps,
+                                          self._local_calls)
+            self._local_calls += 1
+            return None
         if (comm is not None and getattr(comm, "push", False) and w.K in self._uniform_shard_k()
                 and comm.can_push(w, M)):
             return -comm.linear_push(self.ops, w, x, M)
@@ -332,6 +338,7 @@ class DecoderModel:
         ops.embedding(self.embed, b.ids, b.residual, M, self.embed_scale)
         planes, add = 0, None
         lora = self.lora
+        self._local_calls = 0
         self._sp_live = False          # b.xnorm currently arrives from other ranks (sequence-parallel exchange)
         for li, L in enumerate(self.layers):
             self._add_norm(b, planes, L.ln1, M, add)

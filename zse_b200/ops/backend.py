@@ -95,6 +95,10 @@ class TorchOps:
         """Whether ``qkv_rope_fused`` takes this pass (the torch implementation never does: it has the unfused ops)."""
         return False
 
+    def residual_norm_fused_ok(self, w: LinearWeight, M: int, H: int) -> bool:
+        """Whether ``linear_residual_norm`` (projection + residual add + RMSNorm in one kernel) takes this layer."""
+        return False
+
     def rope_kv_write(self, qkv, kv_layer, positions, slots, inv_freq, M, nh, nkv, hd, block_size, planes=None,
                       n_planes=0, bias=None):
         if planes is not None:
@@ -199,6 +203,7 @@ class CudaOps(TorchOps):
         # INT8 weights stay INT8 on the device (ZSE_W8_RESIDENT=0: expanded to fp16 at load, twice the memory)
         self.int8_resident = env.flag("ZSE_W8_RESIDENT")
         self._w8_scratch = None
+        self._norm_ctx = None
 
     def _w8_dense(self, w: "LinearWeight") -> torch.Tensor:
         """fp16 [N, K] view of an INT8 weight in the scratch buffer that all layers share (rows: gate then up for a
@@ -209,6 +214,30 @@ class CudaOps(TorchOps):
         dense = self._w8_scratch[:need].view(w.N, w.K)
         self.n.dequant_w8_tiled(w.data, dense, w.N, w.K, w.N // 2 if w.swiglu else 0)
         return dense
+
+    def norm_ctx(self, H: int) -> int:
+        """A one-rank tensor-parallel context: lets a single GPU use the kernel that does a row-parallel projection,
+        the residual add and the next RMSNorm in one launch (there is simply no peer to exchange with)."""
+        if self._norm_ctx is None or self._norm_ctx[1] != H:
+            z = lambda n, dt: torch.zeros(n, dtype=dt, device=self.device)
+            keep = [z(8, torch.float16), z(8, torch.int32), z(8, torch.int64), z(8, torch.int32),
+                    z(2 * 64 * H, torch.float16), z(2, torch.int32), z(4, torch.int32)]
+            p = [t.data_ptr() for t in keep]
+            ctx = self.n.tp_ctx_create(1, 0, 64, H, [p[0]], [p[1]], 0, [p[2]], [p[3]])
+            self.n.tp_ctx_set_push(ctx, 64, [p[4]], 0, [p[5]], 0, [p[6]])
+            self._norm_ctx = (ctx, H, keep)
+        return self._norm_ctx[0]
+
+    def residual_norm_fused_ok(self, w, M: int, H: int) -> bool:
+        return bool((self.dec_mode & 8) and w.kind in ("w4t", "w8t") and M <= 64 and w.N == H and w.bias is None
+                    and self.n.gemm_w4_dec_supported(M, w.N, w.K, 4)
+                    and self.n.gemm_w4_dec_plan(w.N, w.K, 4, self.sm_count)[1] > 0)
+
+    def linear_residual_norm(self, w, x, M: int, residual, norm_w, out, eps: float, slot: int) -> None:
+        """residual += x W^T; out = RMSNorm(residual) * norm_w, one kernel (decode-sized passes, single GPU)."""
+        self.n.tp_gemm_dec_allreduce_norm(self.norm_ctx(w.N), w.data, w.kind == "w8t", x, x.shape[0], M, w.N, w.K,
+                                          slot & 1, False, residual, norm_w, out, float(eps), self.dec_ws,
+                                          self.status.ptr)
 
     @property
     def dec_ws(self) -> torch.Tensor:

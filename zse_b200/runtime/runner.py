@@ -351,6 +351,7 @@ class ModelRunner:
 
     def _capture(self, Sp: int, splits: int, greedy: bool) -> "torch.cuda.CUDAGraph":
         b, cache = self.buf, self.cache
+        t_begin = time.perf_counter()
         stream = torch.cuda.Stream(device=self.device)
         stream.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(stream):            # warm-up outside capture (lazy attribute set-up, tensor maps)
@@ -367,6 +368,7 @@ class ModelRunner:
         self._graphs[(Sp, splits, greedy)] = g
         self._graph_launches[(Sp, splits, greedy)] = counter[0] - n0
         self.timings["graph_captures"] += 1
+        self.timings["graph_capture_s"] = self.timings.get("graph_capture_s", 0.0) + time.perf_counter() - t_begin
         return g
 
     def release_graphs(self) -> None:

@@ -47,7 +47,7 @@ class _Buffers(Structure):
                [(n, c_void_p) for n in ("ids", "positions", "slots", "block_tables", "seq_lens", "cu_q", "q_pos0",
                                         "logit_rows", "residual", "xnorm", "qkv", "attn_out", "qkv_planes", "act",
                                         "gate_up_tmp", "partials", "xsel", "logits", "attn_scratch", "status",
-                                        "dec_ws")]
+                                        "dec_ws", "norm_ctx")]
 
 
 def _linear(w) -> _Linear:
@@ -98,7 +98,8 @@ class NativeStep:
             logit_rows=ptr(b.logit_rows), residual=ptr(b.residual), xnorm=ptr(b.xnorm), qkv=ptr(b.qkv),
             attn_out=ptr(b.attn_out), qkv_planes=ptr(b.qkv_planes), act=ptr(b.act), gate_up_tmp=ptr(self._gate_up_tmp),
             partials=ptr(b.partials), xsel=ptr(b.xsel), logits=ptr(b.logits), attn_scratch=ptr(b.attn_scratch),
-            status=model.ops.status.ptr, dec_ws=model.ops.dec_ws.data_ptr() if model.ops.dec_mode else None)
+            status=model.ops.status.ptr, dec_ws=model.ops.dec_ws.data_ptr() if model.ops.dec_mode else None,
+            norm_ctx=model.ops.norm_ctx(model.config.hidden_size) if (model.ops.dec_mode & 8) else None)
         self._keep = (model, buffers)            # the structs hold raw pointers into these
         self._launches = c_int(0)
         if not lib.zse_step_supported(byref(self._model), byref(self._buffers)):

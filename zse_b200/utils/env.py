@@ -29,7 +29,9 @@ KNOWN: Dict[str, Tuple[str, str]] = {
     "ZSE_TP_SP": ("0", "sequence-parallel prefill on the NCCL path (reduce-scatter / all-gather, residual split by rows)"),
     "ZSE_TP_SP_MIN_ROWS": ("256", "smallest pass that takes the sequence-parallel path"),
     "ZSE_W4_DEC": ("3", "decode-sized INT4 layers through the persistent kernel: 1 gate/up + SwiGLU, 2 fused QKV + RoPE + "
-                        "cache write, 4 every other INT4 linear (sum of the bits; 0: the tiled kernel everywhere)"),
+                         "cache write, 4 every other INT4 linear, 8 o / down with residual add + RMSNorm in the kernel "
+                         "(sum of the bits; 0: the tiled kernel everywhere; 8 measured slower than the separate "
+                         "add+norm kernel on one GPU, so it is off by default)"),
     "ZSE_W8_RESIDENT": ("1", "keep INT8 weights 8 bits wide on the device (0: expand them to fp16 at load)"),
     "ZSE_PDL": ("1", "programmatic dependent launch between the kernels of a pass (read by the native library)"),
     "ZSE_TP_PDL": ("0", "programmatic dependent launch for the exchange kernels too (read by the native library)"),
