@@ -143,6 +143,9 @@ int zse_lora_shrink(const void* x_f16, int ldx, const void* a_f16, const void* a
                     int K, int rank, void* stream);
 int zse_lora_expand(const void* tmp_f32, const void* b_f16, const void* adapter_ids_i32, const void* scales_f32,
                     void* y_f16, int ldy, int M, int N, int rank, void* stream);
+// shrink + expand in one launch, the activation row read once per token (rank even, <= 64)
+int zse_lora_apply(const void* x, int ldx, const void* a, const void* b, const void* ids, const void* scales, void* y,
+                   int ldy, int M, int K, int N, int rank, void* stream);
 
 // ---- comm.cu ------------------------------------------------------------------------------------------------
 // Tensor-parallel context: peer-mapped symmetric buffers of every rank (row data [2][m_cap][H] fp16, flags

@@ -776,7 +776,7 @@ gemm_w4_kernel(const __grid_constant__ CUtensorMap tmap_x, const W4Args a) {
         }
         if (units > 0) {
           __threadfence_system();               // the CTA's stores (ordered by the barrier above) before the count
-          red_add_release_sys(sp.arrive[b % sp.tp] + (size_t(sp.slot) * sp.tp + sp.rank) * sp.nblk_cap + b, units);
+          red_add_relaxed_sys(sp.arrive[b % sp.tp] + (size_t(sp.slot) * sp.tp + sp.rank) * sp.nblk_cap + b, units);
         }
       }
     }

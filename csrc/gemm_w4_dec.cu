@@ -147,8 +147,8 @@ __device__ __forceinline__ void dec_multimem_st_v4(void* mc_ptr, const uint4& v)
 __device__ __forceinline__ void dec_multimem_red_add_release(uint32_t* mc_ptr, uint32_t v) {
   asm volatile("multimem.red.release.sys.global.add.u32 [%0], %1;" ::"l"(mc_ptr), "r"(v) : "memory");
 }
-__device__ __forceinline__ void dec_red_add_release_sys(uint32_t* p, uint32_t v) {
-  asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+__device__ __forceinline__ void dec_red_add_relaxed_sys(uint32_t* p, uint32_t v) {
+  asm volatile("red.relaxed.sys.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 __device__ __forceinline__ uint32_t dec_ld_acquire_sys(const uint32_t* p) {
   uint32_t v;
@@ -699,7 +699,7 @@ __device__ __forceinline__ void dec_allreduce_norm_tail(const DecArgs& a, DecBar
         dec_multimem_red_add_release(pt.mc_arrive + ctr_i, my_units);
       } else {
         for (int k = 0; k < tp; ++k)
-          if (k != pt.rank) dec_red_add_release_sys(pt.arrive[k] + ctr_i, my_units);
+          if (k != pt.rank) dec_red_add_relaxed_sys(pt.arrive[k] + ctr_i, my_units);   // released by the fence above
       }
     }
   }

@@ -372,7 +372,7 @@ def test_fused_comm_matches_nccl_on_real_gpus():
                         "--master-addr", "127.0.0.1", "--master-port", "29633",
                         os.path.join(ROOT, "tests", "dist_fused_comm_worker.py")], capture_output=True, text=True,
                        timeout=600, env=env, cwd=ROOT)
-    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-12000:]
     assert "FUSED_COMM_OK" in r.stdout
 
 
@@ -386,5 +386,5 @@ def test_tp_engine_on_real_gpus_matches_single_gpu():
                         "--master-addr", "127.0.0.1", "--master-port", "29641",
                         os.path.join(ROOT, "tests", "dist_tp_engine_worker.py")], capture_output=True, text=True,
                        timeout=600, cwd=ROOT)
-    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
+    assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-12000:]
     assert "TP_ENGINE_OK" in r.stdout

@@ -393,6 +393,46 @@ def test_lora_on_every_projection_equals_merged_weights(tmp_path, quant):
     eng.destroy()
 
 
+@pytest.mark.timeout(600)
+def test_lora_on_every_projection_under_tensor_parallelism(tmp_path, monkeypatch):
+    """Two CPU ranks, an adapter on all seven projections: A of o_proj / down_proj is sharded by columns like the
+    projection's input, each rank's update joins its partial output and one all-reduce completes both.  Tokens must be
+    those of the fp32 oracle run on the merged weights."""
+    import sys
+    sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    from dist_lora_tp_fn import rank_fn
+    from zse_b200.format.lora_format import load_lora
+    from zse_b200.lora.weights import random_adapter_file
+    from zse_b200.parallel.tensor_parallel import tp_launch
+    path = str(tmp_path / "m.zse")
+    cfg = synth.shape_config("tiny-aligned")
+    synth.write_random_model(path, cfg, seed=6)
+    targets = ["q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj"]
+    f = str(tmp_path / "all.zse-lora")
+    eng = ZStreamerEngine(path, config=EngineConfig(device="cpu", max_batch_seqs=2, max_seq_len=128, quiet=True))
+    random_adapter_file(f, eng.model_config, rank=4, alpha=8.0, target_modules=targets, seed=3, std=0.08)
+    shapes = eng.lora_manager.weight_shapes()
+    eng.destroy()
+    monkeypatch.setenv("ZSE_TEST_MODEL", path)
+    monkeypatch.setenv("ZSE_TEST_ADAPTER", f)
+    res = tp_launch(2, rank_fn, backend="cpu", timeout_s=300)
+    orc = OracleModel(ZSELoader(path))
+    adapter, data = load_lora(f, shapes)
+    for (layer, mod), (a, b) in data.items():
+        w = adapter.get_weight(layer, mod)
+        A = torch.from_numpy(np.frombuffer(a, np.float16).reshape(w.rank, w.in_features).astype(np.float32))
+        B = torch.from_numpy(np.frombuffer(b, np.float16).reshape(w.out_features, w.rank).astype(np.float32))
+        name = f"layers.{layer}.{'self_attn' if mod in ('q_proj', 'k_proj', 'v_proj', 'o_proj') else 'mlp'}.{mod}.weight"
+        orc.w[name] = orc.w[name] + adapter.scaling * (B @ A)
+    want = orc.greedy([3, 1, 4, 1, 5, 9, 2, 6], 6)
+    assert res[0]["tokens"] == res[1]["tokens"] == want
+    assert want != OracleModel(ZSELoader(path)).greedy([3, 1, 4, 1, 5, 9, 2, 6], 6)      # the adapter matters
+    c = cfg
+    assert res[0]["a_cols"]["o_proj"][2] == c.num_heads * c.head_dim // 2                # half of the input columns
+    assert res[0]["a_cols"]["down_proj"][2] == c.intermediate_size // 2
+    assert res[0]["a_cols"]["q_proj"][2] == c.hidden_size
+
+
 def test_lora_manager_reference_entry_points(tmp_path):
     path = str(tmp_path / "m.zse")
     synth.write_random_model(path, synth.shape_config("tiny"), seed=4)

@@ -8,8 +8,9 @@ runs in one launch pair per projection (``ops.lora_apply``).  Targets, as in the
 QKV output before RoPE), ``o_proj`` and ``down_proj`` (their update is an fp16 addend of the fused residual + RMSNorm
 kernel that follows the projection), ``gate_proj`` and ``up_proj`` (the MLP then runs without the fused SwiGLU
 epilogue: projection, updates, activation).  Under tensor parallelism ``A`` is replicated and ``B`` is row-sharded like
-the base weight for the column-parallel targets; the row-parallel ones (``o_proj``, ``down_proj``) would need their
-update summed over the ranks and are accepted on one GPU only.
+the base weight for the column-parallel targets; for the row-parallel ones (``o_proj``, ``down_proj``) ``A`` is sharded by
+columns like the projection's input and ``B`` is whole, so that every rank's update is a partial sum that the
+projection's own all-reduce completes (no extra exchange).
 """
 from __future__ import annotations
 
@@ -43,6 +44,18 @@ class LoRAManager:
         self._loads = self._unloads = 0
 
     # ---- geometry -----------------------------------------------------------------------------------------
+    def _a_columns(self, module: str) -> Tuple[int, int]:
+        """Column range of ``A`` this rank holds: all of it, except for the row-parallel projections, whose input is
+        sharded (o_proj reads this rank's heads, down_proj this rank's slice of the intermediate dimension).  There the
+        rank's update B (A[:, cols] x[cols]) is a partial sum like the projection's own output, and the same
+        all-reduce completes both."""
+        c, p = self._model.config, self._model.plan
+        if module == "o_proj":
+            return tuple(p.q_rows) if p.tp_size > 1 else (0, c.q_dim)
+        if module == "down_proj":
+            return tuple(p.inter) if p.tp_size > 1 else (0, c.intermediate_size)
+        return (0, c.hidden_size)
+
     def _module_geometry(self, module: str):
         """(in_features, full out_features, local row range of B, column offset inside the fused qkv output)."""
         c, p = self._model.config, self._model.plan
@@ -84,8 +97,6 @@ class LoRAManager:
             raise ValueError(f"LoRA targets {unsupported} are not supported (supported: {SUPPORTED_TARGETS})")
         if rank > self._max_rank or rank % 2:
             raise ValueError(f"LoRA rank {rank} must be even and <= {self._max_rank}")
-        if self._model.plan.tp_size > 1 and any(t in ROW_PARALLEL_TARGETS for t in target_modules):
-            raise ValueError("LoRA on o_proj / down_proj needs a sum over the tensor-parallel ranks: one GPU only")
         if type(self._model).__name__ != "DecoderModel":
             raise ValueError("adapters are wired for the Llama / Mistral / Qwen2 / Phi-3 decoder only")
         with self._lock:
@@ -108,9 +119,11 @@ class LoRAManager:
                 ta, tb = self._tables(layer, mod)
                 ta[slot].zero_()
                 tb[slot].zero_()
-                ta[slot, :rank].copy_(a_t.to(self._device))
+                cols = self._a_columns(mod)
+                ta[slot, :rank].copy_(a_t[:, cols[0]:cols[1]].to(self._device))
                 tb[slot, :, :rank].copy_(b_t[rows[0]:rows[1]].to(self._device))
-                ad.add_weight(layer, mod, LoRAWeight(f"model.layers.{layer}.{mod}", rank, fin, fout, ta[slot], tb[slot]))
+                ad.add_weight(layer, mod, LoRAWeight(f"model.layers.{layer}.{mod}", rank, cols[1] - cols[0], fout, ta[slot],
+                                                            tb[slot]))
             ad.slot = slot
             self._slots[slot] = adapter_id
             self._scales[slot] = ad.scaling
@@ -123,8 +136,10 @@ class LoRAManager:
     def _tables(self, layer: int, mod: str):
         key = (layer, mod)
         if key not in self._a:
-            fin, _, rows, _ = self._module_geometry(mod)
-            self._a[key] = torch.zeros(self._max_adapters, self._rank, fin, dtype=torch.float16, device=self._device)
+            _, _, rows, _ = self._module_geometry(mod)
+            cols = self._a_columns(mod)
+            self._a[key] = torch.zeros(self._max_adapters, self._rank, cols[1] - cols[0], dtype=torch.float16,
+                                       device=self._device)
             self._b[key] = torch.zeros(self._max_adapters, rows[1] - rows[0], self._rank, dtype=torch.float16,
                                        device=self._device)
         return self._a[key], self._b[key]
@@ -253,7 +268,9 @@ class LoRAManager:
         key = (layer, module)
         if key not in self._a:
             return None
-        fin, _, rows, _ = self._module_geometry(module)
+        _, _, rows, _ = self._module_geometry(module)
+        cols = self._a_columns(module)
+        fin = cols[1] - cols[0]
         n_out = rows[1] - rows[0]
         out = self._scratch(b, "lora_delta_" + ("h" if module in ROW_PARALLEL_TARGETS else module), n_out)
         out[:M].zero_()

@@ -278,9 +278,15 @@ class DecoderModel:
         ops, eps = self.ops, self.config.rms_norm_eps
         if planes is None:               # the projection's own kernel reduced, added and normalised already
             return
+        if add is not None and self.comm is not None and planes > 0:
+            # tensor parallelism: the adapter update of a row-parallel projection is a partial sum like the projection's
+            # own output (its A is sharded by columns), so it joins plane 0 and the exchange below sums both
+            H = b.partials.shape[-1]
+            b.partials.view(-1)[: M * H].view(M, H).add_(add[:M])
+            add = None
         if add is not None:
             if self.comm is not None:
-                raise RuntimeError("LoRA on a row-parallel projection is not wired for tensor parallelism")
+                raise RuntimeError("an adapter update without a projection output to join")
             ops.add_rmsnorm(b.residual, b.partials, planes, add, weight, b.xnorm, M, eps)
         elif planes < 0:                 # the GEMM pushed its rows to every rank itself (-planes = its CTA count)
             self.comm.sum_add_rmsnorm(ops, b.residual, weight, b.xnorm, M, eps, -planes)
@@ -317,7 +323,7 @@ class DecoderModel:
                                           self._local_calls)
             self._local_calls += 1
             return None
-        if (comm is not None and getattr(comm, "push", False) and w.K in self._uniform_shard_k()
+        if (comm is not None and add is None and getattr(comm, "push", False) and w.K in self._uniform_shard_k()
                 and comm.can_push(w, M)):
             return -comm.linear_push(self.ops, w, x, M)
         return self.ops.linear_partial(w, x, M, b.partials)

@@ -460,10 +460,14 @@ class CudaOps(TorchOps):
         self.n.apply_repetition_penalty(logits, logits.stride(0), rows, tokens, counts, n, penalty, logits.shape[1])
 
     def lora_apply(self, x, a_table, b_table, ids, scales, y, M, K, N, rank, tmp=None, y_col0=0):
+        yv = y[:, y_col0:]
+        if rank % 2 == 0 and rank <= 64 and K % 8 == 0 and K * 2 + 256 <= 200 * 1024:
+            # one launch: the token's activation row is read once, nothing passes through global memory in between
+            self.n.lora_apply(x, x.stride(0), a_table, b_table, ids, scales, yv, y.stride(0), M, K, N, rank)
+            return
         if tmp is None:
             tmp = torch.empty(M, rank, dtype=torch.float32, device=self.device)
         self.n.lora_shrink(x, x.stride(0), a_table, ids, tmp, M, K, rank)
-        yv = y[:, y_col0:]
         self.n.lora_expand(tmp, b_table, ids, scales, yv, y.stride(0), M, N, rank)
 
 

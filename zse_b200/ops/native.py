@@ -92,6 +92,8 @@ _SIGS = {
     "zse_apply_repetition_penalty": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
                                              c_void_p]),
     "zse_lora_shrink": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "zse_lora_apply": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                               c_int, c_int, c_void_p]),
     "zse_lora_expand": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
                                 c_void_p]),
     "zse_tp_ctx_create": (c_void_p, [c_int, c_int, c_int, c_int, POINTER(c_uint64), POINTER(c_uint64), c_uint64,
@@ -400,6 +402,11 @@ def apply_repetition_penalty(logits, ld, rows, tokens, counts, n, penalty, V):
 
 def lora_shrink(x, ldx, a, ids, tmp, M, K, rank):
     _ck(load().zse_lora_shrink(_p(x), ldx, _p(a), _p(ids), _p(tmp), M, K, rank, _stream()), "lora_shrink")
+
+
+def lora_apply(x, ldx, a, b, ids, scales, y, ldy, M, K, N, rank):
+    _ck(load().zse_lora_apply(_p(x), ldx, _p(a), _p(b), _p(ids), _p(scales), _p(y), ldy, M, K, N, rank, _stream()),
+        "lora_apply")
 
 
 def lora_expand(tmp, b, ids, scales, y, ldy, M, N, rank):
