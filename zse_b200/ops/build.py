@@ -52,18 +52,18 @@ def _headers_digest() -> bytes:
     return h.digest()
 
 
-def _object_for(src: str, hdr: bytes) -> str:
+def _object_for(src: str, hdr: bytes, extra: tuple = ()) -> str:
     h = hashlib.sha256(hdr)
     with open(src, "rb") as f:
         h.update(f.read())
-    h.update(" ".join(NVCC_FLAGS).encode())
+    h.update(" ".join(NVCC_FLAGS + list(extra)).encode())
     return os.path.join(OBJ_DIR, f"{os.path.basename(src)}.{h.hexdigest()[:16]}.o")
 
 
-def _compile(nvcc: str, src: str, obj: str, verbose: bool) -> None:
+def _compile(nvcc: str, src: str, obj: str, verbose: bool, extra: tuple = ()) -> None:
     if os.path.exists(obj):
         return
-    cmd = [nvcc] + NVCC_FLAGS + ["-I", CSRC, "-c", src, "-o", obj + ".tmp"]
+    cmd = [nvcc] + NVCC_FLAGS + list(extra) + ["-I", CSRC, "-c", src, "-o", obj + ".tmp"]
     if verbose:
         print(" ".join(cmd), flush=True)
     res = subprocess.run(cmd, capture_output=True, text=True)
@@ -100,9 +100,48 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB_PATH
 
 
+# Instrumented variants of the library: the same sources with extra defines, linked beside the ordinary library as
+# libzse_b200.<name>.so.  ZSE_NATIVE_LIB=<path> makes a process load one (zse_b200/runtime/kernel_counters.py does).
+VARIANTS = {
+    # per-role cycle counters (clock64) in the INT4 GEMM kernels, written to a buffer set by zse_gemm_w4*_set_timing
+    "timing": ("-DZSE_DEC_TIMING", "-DZSE_W4_TIMING"),
+}
+
+
+def variant_path(name: str) -> str:
+    return os.path.join(OUT_DIR, f"libzse_b200.{name}.so")
+
+
+def build_variant(name: str, verbose: bool = False) -> str:
+    extra = VARIANTS[name]
+    nvcc = nvcc_path()
+    os.makedirs(OBJ_DIR, exist_ok=True)
+    os.makedirs(OUT_DIR, exist_ok=True)
+    hdr = _headers_digest()
+    srcs = sources()
+    objs = [_object_for(s, hdr, extra) for s in srcs]
+    out = variant_path(name)
+    stamp = out + ".stamp"
+    want = "\n".join(os.path.basename(o) for o in objs)
+    if os.path.exists(out) and os.path.exists(stamp) and open(stamp).read() == want:
+        return out
+    with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 2)) as pool:
+        list(pool.map(lambda so: _compile(nvcc, so[0], so[1], verbose, extra), zip(srcs, objs)))
+    res = subprocess.run([nvcc] + ARCH_FLAGS + ["-shared", "-o", out + ".tmp"] + objs, capture_output=True, text=True)
+    if res.returncode != 0:
+        raise RuntimeError(f"link failed:\n{res.stdout}\n{res.stderr}")
+    os.replace(out + ".tmp", out)
+    with open(stamp, "w") as f:
+        f.write(want)
+    return out
+
+
 def is_built() -> bool:
     return os.path.exists(LIB_PATH)
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    if "--variant" in sys.argv:
+        print(build_variant(sys.argv[sys.argv.index("--variant") + 1], verbose="-v" in sys.argv))
+    else:
+        print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))

@@ -142,7 +142,9 @@ _SIGS = {
 
 
 def lib_path() -> str:
-    return _build.LIB_PATH
+    """The library this process loads: the ordinary build, or the file ZSE_NATIVE_LIB names (an instrumented variant
+    built by ``python -m zse_b200.ops.build --variant NAME``)."""
+    return os.environ.get("ZSE_NATIVE_LIB") or _build.LIB_PATH
 
 
 def load(build_if_missing: bool = True) -> ctypes.CDLL:
