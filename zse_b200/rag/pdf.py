@@ -723,11 +723,12 @@ class PDFParser:
         try:
             pages = self._pages(bytes(raw), md.get("pdf_password") or "", ocr_fn)
         except PDFError as exc:
-            kind = getattr(exc, "kind", None)
-            if kind is None:
-                raise
+            # a file that cannot be read becomes ONE chunk that says why (the caller sees `error` in its metadata):
+            # the kinds the security handler reports, or `invalid_pdf` for input that is not a PDF at all
+            kind = getattr(exc, "kind", None) or "invalid_pdf"
             note = f"[PDF: {exc}]"
-            return [Chunk(note, note, {**meta, "error": kind, "pdf_encrypted": True, "chunk_index": 0})]
+            extra = {"pdf_encrypted": True} if kind.startswith("encrypted") else {}
+            return [Chunk(note, note, {**meta, "error": kind, **extra, "chunk_index": 0})]
         if self._last_encrypted:
             meta["pdf_encrypted"] = True
         tp = TextParser(self.chunk_size, self.overlap)
