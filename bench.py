@@ -260,7 +260,9 @@ def run_ours(args):
     torch.cuda.synchronize()
     prefill_s = time.time() - t_pf
     active = eng.scheduler.num_decoding
-    assert active == args.requests, f"{active} of {args.requests} sequences decoding"
+    assert active == args.requests, (f"{active} of {args.requests} sequences decoding: the KV cache does not hold all "
+                                     f"of them at once ({eng.kv_cache.num_total_blocks} blocks of "
+                                     f"{eng.kv_cache.block_size} tokens) - lower --requests or raise --gpus")
     # time to first token of every request (all of them arrive at once, so queueing behind the others counts)
     ttfts = sorted((r.first_token_time - r.arrival_time) * 1000.0 for r in eng.scheduler.active_requests()
                    if r.first_token_time is not None)

@@ -115,6 +115,12 @@ int zse_attn_decode(const void* q, int ldq, const void* kv_layer, const void* bl
 int zse_attn_prefill(const void* q, int ldq, const void* kv_layer, const void* block_tables_i32, int max_blocks,
                      const void* cu_q_i32, const void* q_pos0_i32, void* out_f16, int ldo, int num_seqs, int max_q_len,
                      int nh, int nkv, int hd, int block_size, float scale, void* stream);
+// The same on the tcgen05 tensor cores (attention_tc.cu): head_dim 128, contiguous cache layer of `num_blocks` blocks,
+// `total_rows` rows in q.  ZSE_ERR_SHAPE for shapes it does not cover.
+int zse_attn_prefill_tc(const void* q, int ldq, int total_rows, const void* kv_layer, int num_blocks,
+                        const void* block_tables, int max_blocks, const void* cu_q, const void* q_pos0, void* out,
+                        int ldo, int num_seqs, int max_q_len, int nh, int nkv, int hd, int block_size, float scale,
+                        int variant, void* status, void* stream);
 
 // the same kernels with an explicit cache addressing (element (block, half, kv_head, offset, d) at block*blk_stride +
 // half*half_stride + (kv_head*block_size + offset)*hd + d; strides in elements, multiples of 8), soft-capped scores

@@ -1,0 +1,335 @@
+// Chunked-prefill attention on the tcgen05 tensor cores (head_dim 128, fp16, causal over a paged KV cache, GQA).
+//
+// One CTA owns 128 query rows of one head of one sequence and walks the keys in tiles of 128 tokens:
+//   S = Q K^T     tcgen05.mma, both operands in shared memory (K-major, 128-byte swizzle, brought by TMA - the K tile
+//                 of a head is eight 16-token boxes fetched through the sequence's block table), S in TMEM
+//   softmax       128 threads, thread i owns TMEM lane i = query row i: two passes over its 128 scores with
+//                 tcgen05.ld (row maximum, then exp2 and the fp16 probabilities), no cross-thread reduction at all
+//   O += P V      tcgen05.mma with P as the A operand FROM TMEM (written by tcgen05.st over the scores it replaces) and
+//                 V from shared memory as an MN-major operand - the cache stores V as [token][head_dim], which is
+//                 exactly that layout, so nothing is transposed; O accumulates in TMEM across the tiles
+// The running maximum is only moved when a row's maximum grew by more than 2^8 (probabilities then stay below 256,
+// well inside fp16), so the rescaling pass over O (tcgen05.ld, multiply, tcgen05.st) is rare after the first tiles.
+// TMEM per CTA: 128 columns S / P + 128 columns O; shared memory: Q, one K and one V tile (96 KB); two CTAs share an
+// SM, so one CTA's softmax overlaps the other's MMAs.  K is released as soon as S is complete and V as soon as the
+// P V product is, so the next tile's loads run under the current tile's softmax.
+// Every wait is bounded and reports through the status word; on a failure the CTA frees its TMEM and leaves.
+//
+// Replaces the reference's flash_attention_prefill kernel (zse-engine/zse_engine/orchestrator/kernels.py:859-957) for
+// the shapes it covers; attention.cu::attn_prefill_kernel (mma.sync) keeps the rest (other head sizes, soft-capped
+// scores, sliding windows).
+#include "api.h"
+#include "common.cuh"
+#include "gemm_common.cuh"
+
+namespace zse {
+
+constexpr int kTcRows = 128;          // query rows per CTA (UMMA M)
+constexpr int kTcKv = 128;            // keys per tile (UMMA N of S, K of P V)
+constexpr int kTcHd = 128;
+constexpr int kTcThreads = 192;       // warps 0-3 softmax, warp 4 producer, warp 5 MMA issuer
+constexpr int kTcTileBytes = kTcKv * kTcHd * 2;                      // 32 KB: [2 halves of 64 columns][128 rows][128 B]
+constexpr int kTcSmemBytes = 3 * kTcTileBytes + 1024 + 256;           // Q, K, V + alignment + barriers
+
+struct TcBars {
+  uint64_t q_full, k_full, k_empty, v_full, v_empty, s_full, p_full, o_full;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+struct TcArgs {
+  const int* bt;            // block tables [num_seqs][max_blocks]
+  const int* cu_q;          // [num_seqs + 1]
+  const int* q_pos0;        // [num_seqs]
+  __half* out;
+  int ldo, max_blocks, nh, nkv, block_size;
+  float scale_log2;
+  int v_desc_swap;          // debugging aid: exchange the two strides of the MN-major descriptor
+  Status* status;
+};
+
+// MN-major operand in shared memory, 128-byte swizzle: rows of the K dimension are 128 bytes (64 MN elements) long,
+// groups of eight K rows lie `k8_bytes` apart, the next 64 MN elements `mn64_bytes` apart.
+__device__ __forceinline__ uint64_t make_desc_sw128_mn(uint32_t smem_addr, uint32_t mn64_bytes, uint32_t k8_bytes) {
+  uint64_t d = 0;
+  d |= uint64_t((smem_addr >> 4) & 0x3FFF);
+  d |= uint64_t((mn64_bytes >> 4) & 0x3FFF) << 16;     // leading dimension byte offset
+  d |= uint64_t((k8_bytes >> 4) & 0x3FFF) << 32;       // stride dimension byte offset
+  d |= uint64_t(1) << 46;
+  d |= uint64_t(2) << 61;                              // SWIZZLE_128B
+  return d;
+}
+
+__global__ void __launch_bounds__(kTcThreads, 2)
+attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_kv,
+                       const TcArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* q_s = smem;
+  uint8_t* k_s = smem + kTcTileBytes;
+  uint8_t* v_s = smem + 2 * kTcTileBytes;
+  TcBars* bars = reinterpret_cast<TcBars*>(smem + 3 * kTcTileBytes);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qt = blockIdx.x, head = blockIdx.y, seq = blockIdx.z;
+  pdl_launch_dependents();
+  const int q_begin = a.cu_q[seq], q_len = a.cu_q[seq + 1] - q_begin;
+  if (qt * kTcRows >= q_len) return;                     // before any barrier or TMEM use: the whole CTA leaves
+  const int pos0 = a.q_pos0[seq];
+  const int kvh = head / (a.nh / a.nkv);
+  const int last_row = min(q_len, qt * kTcRows + kTcRows) - 1;
+  const int kv_len = pos0 + last_row + 1;                // keys visible to the last query row of this CTA
+  const int n_tiles = (kv_len + kTcKv - 1) / kTcKv;
+  const int* my_bt = a.bt + size_t(seq) * a.max_blocks;
+
+  if (threadIdx.x == 0) {
+    mbar_init(&bars->q_full, 1);
+    mbar_init(&bars->k_full, 1);
+    mbar_init(&bars->k_empty, 1);
+    mbar_init(&bars->v_full, 1);
+    mbar_init(&bars->v_empty, 1);
+    mbar_init(&bars->s_full, 1);
+    mbar_init(&bars->p_full, 128);
+    mbar_init(&bars->o_full, 1);
+    bars->abort_flag = 0;
+    mbar_fence_init();
+    prefetch_tmap(&tmap_q);
+    prefetch_tmap(&tmap_kv);
+  }
+  // V must never hold a NaN bit pattern where a probability is zero (0 * NaN): clear it once; afterwards it only ever
+  // holds cache contents
+  for (int i = threadIdx.x; i < kTcTileBytes / 16; i += kTcThreads) reinterpret_cast<uint4*>(v_s)[i] = make_uint4(0, 0, 0, 0);
+  fence_proxy_async_smem();
+  if (warp == 5) {
+    tmem_alloc(&bars->tmem_base, 256);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = bars->tmem_base;
+  const uint32_t tm_s = tmem, tm_p = tmem, tm_o = tmem + 128;
+  volatile int* abort_flag = &bars->abort_flag;
+
+  if (warp == 4) {
+    // ------------------------------------------------------------------ producer
+    if (lane == 0) {
+      pdl_wait();                                      // q and the cache rows of this chunk come from the previous kernels
+      mbar_arrive_expect_tx(&bars->q_full, kTcTileBytes);
+      const int y = q_begin + qt * kTcRows;
+      tma_load_2d(q_s, &tmap_q, head * kTcHd, y, &bars->q_full);
+      tma_load_2d(q_s + kTcTileBytes / 2, &tmap_q, head * kTcHd + 64, y, &bars->q_full);
+      uint32_t ph = 1;                                 // "empty" barriers: the first wait passes
+      for (int t = 0; t < n_tiles; ++t) {
+        // which 16-token groups of this tile exist (the last tile may be short)
+        int rows[8];
+        int n_valid = 0;
+        for (int g = 0; g < 8; ++g) {
+          const int tok = t * kTcKv + g * 16;
+          int pb = -1;
+          if (tok < kv_len) pb = my_bt[tok / a.block_size];
+          rows[g] = pb >= 0 ? ((pb * 2) * a.nkv + kvh) * a.block_size + tok % a.block_size : -1;
+          n_valid += pb >= 0 ? 1 : 0;
+        }
+        const int v_off = a.nkv * a.block_size;        // rows between the K half and the V half of a block
+        if (!mbar_wait(&bars->k_empty, ph, abort_flag, a.status, 41, t)) break;
+        mbar_arrive_expect_tx(&bars->k_full, uint32_t(n_valid) * 4096u);
+        for (int g = 0; g < 8; ++g) {
+          if (rows[g] < 0) continue;
+          tma_load_2d(k_s + g * 2048, &tmap_kv, 0, rows[g], &bars->k_full);
+          tma_load_2d(k_s + kTcTileBytes / 2 + g * 2048, &tmap_kv, 64, rows[g], &bars->k_full);
+        }
+        if (!mbar_wait(&bars->v_empty, ph, abort_flag, a.status, 42, t)) break;
+        mbar_arrive_expect_tx(&bars->v_full, uint32_t(n_valid) * 4096u);
+        for (int g = 0; g < 8; ++g) {
+          if (rows[g] < 0) continue;
+          tma_load_2d(v_s + g * 2048, &tmap_kv, 0, rows[g] + v_off, &bars->v_full);
+          tma_load_2d(v_s + kTcTileBytes / 2 + g * 2048, &tmap_kv, 64, rows[g] + v_off, &bars->v_full);
+        }
+        ph ^= 1;
+      }
+    }
+  } else if (warp == 5) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_qk = make_idesc_f16(kTcRows, kTcKv);
+      constexpr uint32_t idesc_pv = make_idesc_f16(kTcRows, kTcHd) | (1u << 16);       // B is MN-major
+      const uint64_t q_desc = make_desc_sw128(smem_u32(q_s));
+      const uint64_t k_desc = make_desc_sw128(smem_u32(k_s));
+      const uint32_t mn64 = a.v_desc_swap ? 1024u : uint32_t(kTcTileBytes / 2);
+      const uint32_t k8 = a.v_desc_swap ? uint32_t(kTcTileBytes / 2) : 1024u;
+      bool ok = mbar_wait(&bars->q_full, 0, abort_flag, a.status, 43, 0);
+      uint32_t ph = 0;
+      for (int t = 0; t < n_tiles && ok; ++t) {
+        if (!mbar_wait(&bars->k_full, ph, abort_flag, a.status, 44, t)) break;
+        // the probabilities of the previous tile live in the columns this product overwrites: let P V finish reading
+        // them first (v_empty of tile t-1 is committed behind that product)
+        if (t > 0 && !mbar_wait(&bars->v_empty, ph ^ 1, abort_flag, a.status, 49, t)) break;
+        tc_fence_after_sync();
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const uint64_t adv = uint64_t((j >> 2) * (kTcTileBytes / 2 >> 4) + (j & 3) * 2);
+          umma_ss(tm_s, q_desc + adv, k_desc + adv, idesc_qk, j != 0);
+        }
+        tc_commit(&bars->s_full);                     // S complete (and every earlier MMA, i.e. the previous P V)
+        tc_commit(&bars->k_empty);
+        if (!mbar_wait(&bars->v_full, ph, abort_flag, a.status, 45, t)) break;
+        if (!mbar_wait(&bars->p_full, ph, abort_flag, a.status, 46, t)) break;
+        tc_fence_after_sync();
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {                 // 16 keys per step: two groups of eight cache rows
+          const uint64_t v_desc = make_desc_sw128_mn(smem_u32(v_s) + j * 2048, mn64, k8);
+          umma_ts(tm_o, tm_p + j * 8, v_desc, idesc_pv, (t != 0) || (j != 0));
+        }
+        tc_commit(&bars->v_empty);
+        if (t == n_tiles - 1) tc_commit(&bars->o_full);
+        ph ^= 1;
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax + epilogue: thread = query row
+    const int r = warp * 32 + lane;                   // row inside the CTA = TMEM lane
+    const int row = qt * kTcRows + r;                 // row inside the sequence's chunk
+    const int limit = pos0 + row;                     // last key this row may see
+    const uint32_t lane_addr = uint32_t(warp * 32) << 16;
+    float m_used = -INFINITY, l = 0.f;
+    uint32_t ph = 0;
+    bool ok = true;
+    for (int t = 0; t < n_tiles; ++t) {
+      // one verdict per warp: the tcgen05.ld / st below are warp-wide
+      if (!__all_sync(0xffffffffu, mbar_wait(&bars->s_full, ph, abort_flag, a.status, 47, t))) { ok = false; break; }
+      tc_fence_after_sync();
+      const int k0 = t * kTcKv;
+      // pass 1: row maximum of the visible scores
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < 8; ++c) {
+        uint32_t v[16];
+        ZSE_TMEM_LD_X16(v, tm_s + lane_addr + c * 16);
+        tc_wait_ld();
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+          if (k0 + c * 16 + i <= limit) mx = fmaxf(mx, __uint_as_float(v[i]));
+      }
+      mx *= a.scale_log2;                              // scale > 0: the maximum commutes with it
+      // move the reference maximum only when some row of the warp needs it (tcgen05.ld/st are warp-wide)
+      const bool grow = mx > m_used + 8.f;
+      if (__any_sync(0xffffffffu, grow)) {
+        const float m_new = fmaxf(m_used, mx);
+        const float alpha = (m_used == -INFINITY) ? 0.f : exp2f(m_used - m_new);
+        if (t > 0) {
+          // s_full of this tile means every earlier MMA has completed, the previous P V included: O is stable
+#pragma unroll 1
+          for (int c = 0; c < 8; ++c) {
+            uint32_t o[16];
+            ZSE_TMEM_LD_X16(o, tm_o + lane_addr + c * 16);
+            tc_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            ZSE_TMEM_ST_X16(tm_o + lane_addr + c * 16, o);
+          }
+          tc_wait_st();
+        }
+        l *= alpha;
+        m_used = m_new;
+      }
+      // pass 2: probabilities (fp16) over the scores they replace, and the row sum
+      const float m_ref = (m_used == -INFINITY) ? 0.f : m_used;
+      float psum = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < 8; ++c) {
+        uint32_t v[16];
+        ZSE_TMEM_LD_X16(v, tm_s + lane_addr + c * 16);
+        tc_wait_ld();
+        uint32_t pk[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          const int k = k0 + c * 16 + 2 * i;
+          const float p0 = k <= limit ? exp2f(__uint_as_float(v[2 * i]) * a.scale_log2 - m_ref) : 0.f;
+          const float p1 = k + 1 <= limit ? exp2f(__uint_as_float(v[2 * i + 1]) * a.scale_log2 - m_ref) : 0.f;
+          psum += p0 + p1;
+          pk[i] = pack_half2(p0, p1);
+        }
+        // P columns c*8 .. c*8+7 lie under score columns that this pass has already read
+        asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(tm_p + lane_addr + c * 8),
+                     "r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3]), "r"(pk[4]), "r"(pk[5]), "r"(pk[6]), "r"(pk[7])
+                     : "memory");
+      }
+      l += psum;
+      tc_wait_st();
+      tc_fence_before_sync();
+      mbar_arrive(&bars->p_full);
+      ph ^= 1;
+    }
+    // ---- epilogue: O / l -> fp16 rows
+    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_full, 0, abort_flag, a.status, 48, 0));
+    tc_fence_after_sync();
+    if (ok) {
+      // every lane takes part in the warp-wide tcgen05.ld (rows past the chunk included); only the stores are per row
+      const bool live = row < q_len;
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      __half* dst = a.out + size_t(q_begin + (live ? row : 0)) * a.ldo + size_t(head) * kTcHd;
+#pragma unroll 1
+      for (int c = 0; c < 8; ++c) {
+        uint32_t o[16];
+        ZSE_TMEM_LD_X16(o, tm_o + lane_addr + c * 16);
+        tc_wait_ld();
+        uint4 w0, w1;
+        w0.x = pack_half2(__uint_as_float(o[0]) * inv, __uint_as_float(o[1]) * inv);
+        w0.y = pack_half2(__uint_as_float(o[2]) * inv, __uint_as_float(o[3]) * inv);
+        w0.z = pack_half2(__uint_as_float(o[4]) * inv, __uint_as_float(o[5]) * inv);
+        w0.w = pack_half2(__uint_as_float(o[6]) * inv, __uint_as_float(o[7]) * inv);
+        w1.x = pack_half2(__uint_as_float(o[8]) * inv, __uint_as_float(o[9]) * inv);
+        w1.y = pack_half2(__uint_as_float(o[10]) * inv, __uint_as_float(o[11]) * inv);
+        w1.z = pack_half2(__uint_as_float(o[12]) * inv, __uint_as_float(o[13]) * inv);
+        w1.w = pack_half2(__uint_as_float(o[14]) * inv, __uint_as_float(o[15]) * inv);
+        if (live) {
+          *reinterpret_cast<uint4*>(dst + c * 16) = w0;
+          *reinterpret_cast<uint4*>(dst + c * 16 + 8) = w1;
+        }
+      }
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 5) tmem_dealloc(tmem, 256);
+}
+
+}  // namespace zse
+
+using namespace zse;
+
+// out[q_begin + r, head * 128 ...] = softmax(q K^T * scale, causal) V for every sequence's chunk of query rows.
+//   q [total_rows, ldq] fp16 (head h at columns h * 128), kv_layer [num_blocks][2][nkv][block_size][128] fp16,
+//   block_tables [num_seqs][max_blocks], cu_q [num_seqs + 1], q_pos0 [num_seqs] (position of each chunk's first row).
+// head_dim 128 only; block_size a multiple of 16.  Returns ZSE_ERR_SHAPE for anything else (the caller then uses
+// zse_attn_prefill).
+extern "C" int zse_attn_prefill_tc(const void* q, int ldq, int total_rows, const void* kv_layer, int num_blocks,
+                                   const void* block_tables, int max_blocks, const void* cu_q, const void* q_pos0,
+                                   void* out, int ldo, int num_seqs, int max_q_len, int nh, int nkv, int hd,
+                                   int block_size, float scale, int variant, void* status, void* stream) {
+  if (num_seqs <= 0 || max_q_len <= 0) return 0;
+  if (hd != kTcHd || nh % nkv || block_size % 16 || ldq % 8 || ldo % 8 || total_rows <= 0 || num_blocks <= 0)
+    return ZSE_ERR_SHAPE;
+  if ((reinterpret_cast<uintptr_t>(q) & 15) || (reinterpret_cast<uintptr_t>(kv_layer) & 15) ||
+      (reinterpret_cast<uintptr_t>(out) & 15))
+    return ZSE_ERR_ALIGN;
+  CUtensorMap tq, tkv;
+  if (int rc = get_tmap(q, uint64_t(total_rows), uint64_t(ldq), uint32_t(kTcRows), &tq)) return rc;
+  if (int rc = get_tmap(kv_layer, uint64_t(num_blocks) * 2 * nkv * block_size, uint64_t(kTcHd), 16u, &tkv)) return rc;
+  static bool attr[kMaxDevices] = {};
+  const int dev_slot = current_device_slot();
+  if (!attr[dev_slot]) {
+    if (cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kTcSmemBytes) !=
+        cudaSuccess)
+      return ZSE_ERR_LAUNCH;
+    attr[dev_slot] = true;
+  }
+  TcArgs a{reinterpret_cast<const int*>(block_tables), reinterpret_cast<const int*>(cu_q),
+           reinterpret_cast<const int*>(q_pos0), reinterpret_cast<__half*>(out), ldo, max_blocks, nh, nkv, block_size,
+           scale * 1.4426950408889634f, variant, reinterpret_cast<Status*>(status)};
+  dim3 grid((max_q_len + kTcRows - 1) / kTcRows, nh, num_seqs);
+  return launch_pdl(attn_prefill_tc_kernel, grid, dim3(kTcThreads), size_t(kTcSmemBytes),
+                    reinterpret_cast<cudaStream_t>(stream), tq, tkv, a) == cudaSuccess
+             ? 0
+             : ZSE_ERR_LAUNCH;
+}

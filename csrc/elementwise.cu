@@ -230,6 +230,56 @@ __global__ void rope_kv_write_kernel(__half* __restrict__ qkv, __half* __restric
   }
 }
 
+// The same operation for the common case (q/k/v already fp16 in `qkv`, full rotary, head_dim a multiple of 16), built
+// for passes of many rows: ONE CTA per token instead of one per (token, head).  A thread owns eight rotation pairs
+// (i .. i+7 and their partners half a head away): it computes their sines and cosines once, then walks the heads
+// with two 16-byte loads and two 16-byte stores each.  The one-CTA-per-head form above spends 271 us on a prefill pass
+// of 8 k tokens of the 14B shape (229 k CTAs of 64 threads, 2-byte accesses, a sincosf per element and head).
+__global__ void __launch_bounds__(256)
+rope_kv_write_vec_kernel(__half* __restrict__ qkv, __half* __restrict__ kv_layer, const int* __restrict__ positions,
+                         const long long* __restrict__ slots, const float* __restrict__ inv_freq, int nh, int nkv,
+                         int hd, int block_size) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int G = hd / 16;                       // threads per head
+  const int g = threadIdx.x % G, lane0 = threadIdx.x / G, lanes = blockDim.x / G;
+  const int half_rot = hd / 2, i0 = g * 8;
+  const int heads = nh + 2 * nkv;
+  const float pos = float(positions[t]);
+  float sn[8], cs[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) sincosf(pos * inv_freq[i0 + j], &sn[j], &cs[j]);
+  const long long slot = slots[t];
+  const long long blk = slot >= 0 ? slot / block_size : 0, off = slot >= 0 ? slot % block_size : 0;
+  __half* row = qkv + size_t(t) * heads * hd;
+  for (int head = lane0; head < heads; head += lanes) {
+    __half* p = row + size_t(head) * hd;
+    uint4 va = *reinterpret_cast<const uint4*>(p + i0), vb = *reinterpret_cast<const uint4*>(p + half_rot + i0);
+    const bool is_v = head >= nh + nkv;
+    if (!is_v) {
+      __half2* ha = reinterpret_cast<__half2*>(&va);
+      __half2* hb = reinterpret_cast<__half2*>(&vb);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 a = __half22float2(ha[j]), b = __half22float2(hb[j]);
+        const float ra0 = a.x * cs[2 * j] - b.x * sn[2 * j], rb0 = b.x * cs[2 * j] + a.x * sn[2 * j];
+        const float ra1 = a.y * cs[2 * j + 1] - b.y * sn[2 * j + 1], rb1 = b.y * cs[2 * j + 1] + a.y * sn[2 * j + 1];
+        ha[j] = __floats2half2_rn(clamp_f16(ra0), clamp_f16(ra1));
+        hb[j] = __floats2half2_rn(clamp_f16(rb0), clamp_f16(rb1));
+      }
+      *reinterpret_cast<uint4*>(p + i0) = va;                   // q for attention; k keeps the in-place contract
+      *reinterpret_cast<uint4*>(p + half_rot + i0) = vb;
+    }
+    if (head >= nh && slot >= 0) {
+      const int kvh = is_v ? head - nh - nkv : head - nh;
+      __half* dst = kv_layer + (((blk * 2 + (is_v ? 1 : 0)) * nkv + kvh) * block_size + off) * hd;
+      *reinterpret_cast<uint4*>(dst + i0) = va;
+      *reinterpret_cast<uint4*>(dst + half_rot + i0) = vb;
+    }
+  }
+}
+
 __global__ void swiglu_kernel(const __half2* __restrict__ gate_up, __half2* __restrict__ out, int M, int I2,
                               int gelu) {
   // gate_up: [M, 2*I] as half2 -> rows of 2*I2 half2; out [M, I2]
@@ -325,6 +375,12 @@ extern "C" int zse_rope_kv_write(void* qkv, void* kv_layer, const void* position
                                  const void* planes, int n_planes, const void* bias, void* stream) {
   if (M <= 0) return 0;
   if (hd % 2 || hd > 2048 || rotary_dim % 2 || rotary_dim > hd || (hd - rotary_dim) % 2) return ZSE_ERR_SHAPE;
+  if (planes == nullptr && rotary_dim == hd && hd % 16 == 0 && hd <= 512 &&
+      (reinterpret_cast<uintptr_t>(qkv) & 15) == 0 && (reinterpret_cast<uintptr_t>(kv_layer) & 15) == 0)
+    return launch_pdl(rope_kv_write_vec_kernel, dim3(M), dim3(256), 0, ST(stream), reinterpret_cast<__half*>(qkv),
+                      reinterpret_cast<__half*>(kv_layer), reinterpret_cast<const int*>(positions),
+                      reinterpret_cast<const long long*>(slots), reinterpret_cast<const float*>(inv_freq), nh, nkv, hd,
+                      block_size) == cudaSuccess ? 0 : ZSE_ERR_LAUNCH;
   dim3 grid(M, nh + 2 * nkv);
   return launch_pdl(rope_kv_write_kernel, grid, dim3(hd / 2), 0, ST(stream), reinterpret_cast<__half*>(qkv),
                     reinterpret_cast<__half*>(kv_layer), reinterpret_cast<const int*>(positions),

@@ -336,9 +336,10 @@ def test_embedding_and_rmsnorm(ops):
     assert _rel(y, ref.rmsnorm(out, w, 1e-5)) < 1e-3
 
 
-@pytest.mark.parametrize("hd,nh,nkv,bs", [(128, 8, 2, 16), (64, 4, 2, 32), (128, 5, 1, 16)])
-def test_rope_kv_write(ops, hd, nh, nkv, bs):
-    M, blocks = 23, 12
+@pytest.mark.parametrize("hd,nh,nkv,bs,M", [(128, 8, 2, 16, 23), (64, 4, 2, 32, 23), (128, 5, 1, 16, 23),
+                                            (128, 20, 4, 16, 300), (256, 3, 1, 16, 40), (96, 4, 2, 16, 23)])
+def test_rope_kv_write(ops, hd, nh, nkv, bs, M):
+    blocks = (M + bs - 1) // bs + 11
     qkv = torch.randn(M, (nh + 2 * nkv) * hd, device="cuda").half()
     kv = torch.zeros(blocks, 2, nkv, bs, hd, dtype=torch.float16, device="cuda")
     pos = torch.randint(0, 3000, (M,), device="cuda", dtype=torch.int32)
@@ -399,6 +400,35 @@ def test_attn_prefill_chunks(ops, hd, nh, nkv, bs):
     torch.cuda.synchronize()
     want = ref.attn_prefill(q[:, : nh * hd], kv, bt, cu, p0, nh, nkv, hd, bs, 1 / math.sqrt(hd))
     assert (out.float() - want.float()).abs().max() < 3e-3
+
+
+@pytest.mark.parametrize("nh,nkv,bs,variant", [(8, 2, 16, 0), (5, 1, 32, 0), (4, 4, 64, 0), (8, 2, 16, 1)])
+def test_attn_prefill_on_tcgen05(ops, nh, nkv, bs, variant):
+    """The tcgen05 prefill kernel (S = Q K^T and O = P V on the tensor cores, probabilities through TMEM, V as an
+    MN-major operand straight from the cache layout) against the fp32 oracle: a fresh prompt longer than two key tiles,
+    a chunk on top of cached tokens that starts inside a tile, a short verify chunk, a chunk of exactly one tile."""
+    from zse_b200.ops import native
+    hd = 128
+    q_lens, pos0 = [300, 70, 5, 128], [0, 100, 37, 256]
+    S = len(q_lens)
+    totals = [a + b for a, b in zip(q_lens, pos0)]
+    kv, bt = _make_cache(S, totals, nkv, hd, bs, 160 * 16 // bs)
+    cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32, device="cuda")
+    p0 = torch.tensor(pos0, dtype=torch.int32, device="cuda")
+    total = sum(q_lens)
+    q = torch.randn(total, (nh + 2 * nkv) * hd, device="cuda").half()
+    out = torch.full((total + 3, nh * hd), 7.0, dtype=torch.float16, device="cuda")
+    native.attn_prefill_tc(q, q.stride(0), total, kv, bt, cu, p0, out, out.stride(0), S, max(q_lens), nh, nkv, hd, bs,
+                           1 / math.sqrt(hd), ops.status.ptr, variant)
+    torch.cuda.synchronize()
+    ops.check()
+    want = ref.attn_prefill(q[:, : nh * hd], kv, bt, cu, p0, nh, nkv, hd, bs, 1 / math.sqrt(hd))
+    assert (out[:total].float() - want.float()).abs().max() < 4e-3
+    assert torch.all(out[total:] == 7.0)                       # nothing past the last row is written
+    old = torch.zeros(total, nh * hd, dtype=torch.float16, device="cuda")
+    ops.attn_prefill(q, kv, bt, cu, p0, old, S, total, max(q_lens), nh, nkv, hd, bs, 1 / math.sqrt(hd))
+    torch.cuda.synchronize()
+    assert (out[:total].float() - old.float()).abs().max() < 4e-3
 
 
 def test_argmax_and_sampling_distribution(ops):

@@ -204,6 +204,7 @@ class CudaOps(TorchOps):
         self.int8_resident = env.flag("ZSE_W8_RESIDENT")
         self._w8_scratch = None
         self._norm_ctx = None
+        self.attn_prefill_tc = env.flag("ZSE_ATTN_PREFILL_TC")
 
     def _w8_dense(self, w: "LinearWeight") -> torch.Tensor:
         """fp16 [N, K] view of an INT8 weight in the scratch buffer that all layers share (rows: gate then up for a
@@ -432,6 +433,12 @@ class CudaOps(TorchOps):
         if not self._tensor_core_attention(kv_layer, hd, nh, nkv, block_size):
             self.n.attn_generic(qkv, qkv.stride(0), kv_layer, block_tables, None, cu_q, q_pos0, num_seqs, out,
                                 out.stride(0), total_q, nh, nkv, hd, block_size, scale, softcap, window)
+            return
+        if (self.attn_prefill_tc and hd == 128 and softcap == 0.0 and window == 0 and kv_layer.is_contiguous()
+                and kv_layer.shape[1:] == (2, nkv, block_size, hd)):
+            self.n.attn_prefill_tc(qkv, qkv.stride(0), total_q, kv_layer, block_tables, cu_q, q_pos0, out,
+                                   out.stride(0), num_seqs, max_q_len, nh, nkv, hd, block_size, scale,
+                                   self.status.ptr)
             return
         self.n.attn_prefill_ext(qkv, qkv.stride(0), kv_layer, block_tables, cu_q, q_pos0, out, out.stride(0),
                                 num_seqs, max_q_len, nh, nkv, hd, block_size, scale, softcap, window)

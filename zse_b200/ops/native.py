@@ -92,6 +92,8 @@ _SIGS = {
     "zse_apply_repetition_penalty": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
                                              c_void_p]),
     "zse_lora_shrink": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "zse_attn_prefill_tc": (c_int, [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                                    c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p]),
     "zse_lora_apply": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                c_int, c_int, c_void_p]),
     "zse_lora_expand": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
@@ -386,6 +388,15 @@ def attn_prefill(q, ldq, kv_layer, block_tables, max_blocks, cu_q, q_pos0, out, 
                  hd, block_size, scale):
     _ck(load().zse_attn_prefill(_p(q), ldq, _p(kv_layer), _p(block_tables), max_blocks, _p(cu_q), _p(q_pos0), _p(out),
                                 ldo, num_seqs, max_q_len, nh, nkv, hd, block_size, scale, _stream()), "attn_prefill")
+
+
+def attn_prefill_tc(q, ldq, total_rows, kv_layer, block_tables, cu_q, q_pos0, out, ldo, num_seqs, max_q_len, nh, nkv, hd,
+                    block_size, scale, status, variant=0):
+    """Chunked-prefill attention on the tcgen05 tensor cores (csrc/attention_tc.cu); head_dim 128, contiguous cache."""
+    _ck(load().zse_attn_prefill_tc(_p(q), ldq, total_rows, _p(kv_layer), kv_layer.shape[0], _p(block_tables),
+                                   block_tables.stride(0), _p(cu_q), _p(q_pos0), _p(out), ldo, num_seqs, max_q_len, nh,
+                                   nkv, hd, block_size, float(scale), int(variant), status, _stream()),
+        "attn_prefill_tc")
 
 
 def argmax(logits, ld, out, M, V):

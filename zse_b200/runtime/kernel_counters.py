@@ -96,7 +96,8 @@ def main(argv=None) -> int:
         for lane in range(4):
             r = roles[lane]
             print(f"  mma lane {lane}: wait activations {int(r[0])}  wait TMEM slot {int(r[1])}  issuing {int(r[2])} "
-                  f"(~{int(r[2]) / max(1, 8 * k_steps):.0f} cycles per tcgen05.mma)  loop ends at {int(r[3])}")
+                  f"(~{int(r[2]) / max(1, 4 * k_steps):.0f} cycles per tcgen05.mma: a lane takes every other step of its tile, "
+                  f"eight MMAs each)  loop ends at {int(r[3])}")
         r = roles[5]
         print(f"  dequant warp 5: first weight chunk at {int(r[6])}  wait chunk {int(r[0])}  load+dequant {int(r[1])}  "
               f"wait slot {int(r[2])}  tcgen05.st {int(r[3])}  wait::st {int(r[4])}  total {int(r[7])}")

@@ -64,6 +64,11 @@ def main():
         rows.append(r.row(peaks))
         ops.check()
 
+    def want(*names) -> bool:
+        """Whether any of these kernels will run: sections allocate their inputs only then (a capture of one kernel
+        under a profiler should hold that kernel's few hundred MB, not the whole set)."""
+        return not only or any(n in only for n in names)
+
     # linear layers
     wqkv = _w4(ops, q_dim + 2 * kv_dim, H)
     qkv = torch.zeros(M, q_dim + 2 * kv_dim, dtype=torch.float16, device="cuda")
@@ -86,40 +91,42 @@ def main():
     resid = torch.randn(M, H, device="cuda")
     wn = torch.ones(H, dtype=torch.float16, device="cuda")
     xn = torch.zeros(M, H, dtype=torch.float16, device="cuda")
-    n_pl = ops.linear_partial(wd, xi, M, planes)
+    n_pl = ops.linear_partial(wd, xi, M, planes) if want("add_rmsnorm") else 1
     run("add_rmsnorm", lambda: ops.add_rmsnorm(resid, planes, n_pl, None, wn, xn, M, 1e-6),
         M * H * (4 + 4 + 4 * n_pl + 2))
     # attention over a paged cache
-    bs = 16
-    nblk = (a.ctx + bs - 1) // bs
-    kv = (torch.randn(M * nblk + 1, 2, nkv, bs, hd, device="cuda") * 0.3).half()
-    bt = torch.randperm(M * nblk, device="cuda").int().view(M, nblk).contiguous()
-    lens = torch.full((M,), a.ctx, dtype=torch.int32, device="cuda")
-    ao = torch.zeros(M, q_dim, dtype=torch.float16, device="cuda")
-    for splits in (1, 2, 4):
-        scratch = torch.zeros(M * nh * splits * (hd + 2), device="cuda")
-        run(f"attn_decode_s{splits}",
-            lambda s=splits, sc=scratch: ops.attn_decode(qkv, kv, bt, lens, ao, M, nh, nkv, hd, bs, 1 / math.sqrt(hd),
-                                                          sc, s),
-            M * a.ctx * nkv * hd * 2 * 2)
-    pos = torch.full((M,), a.ctx - 1, dtype=torch.int32, device="cuda")
-    slots = (bt[:, -1].long() * bs + (a.ctx - 1) % bs).contiguous()
-    inv = ref.inv_freq(hd, c.rope_theta).cuda()
-    run("rope_kv_write", lambda: ops.rope_kv_write(qkv, kv, pos, slots, inv, M, nh, nkv, hd, bs),
-        M * (q_dim + 2 * kv_dim) * 2 * 2)
+    if want("attn_decode_s1", "attn_decode_s2", "attn_decode_s4", "rope_kv_write"):
+        bs = 16
+        nblk = (a.ctx + bs - 1) // bs
+        kv = (torch.randn(M * nblk + 1, 2, nkv, bs, hd, device="cuda") * 0.3).half()
+        bt = torch.randperm(M * nblk, device="cuda").int().view(M, nblk).contiguous()
+        lens = torch.full((M,), a.ctx, dtype=torch.int32, device="cuda")
+        ao = torch.zeros(M, q_dim, dtype=torch.float16, device="cuda")
+        for splits in (1, 2, 4):
+            scratch = torch.zeros(M * nh * splits * (hd + 2), device="cuda")
+            run(f"attn_decode_s{splits}",
+                lambda s=splits, sc=scratch: ops.attn_decode(qkv, kv, bt, lens, ao, M, nh, nkv, hd, bs, 1 / math.sqrt(hd),
+                                                              sc, s),
+                M * a.ctx * nkv * hd * 2 * 2)
+        pos = torch.full((M,), a.ctx - 1, dtype=torch.int32, device="cuda")
+        slots = (bt[:, -1].long() * bs + (a.ctx - 1) % bs).contiguous()
+        inv = ref.inv_freq(hd, c.rope_theta).cuda()
+        run("rope_kv_write", lambda: ops.rope_kv_write(qkv, kv, pos, slots, inv, M, nh, nkv, hd, bs),
+            M * (q_dim + 2 * kv_dim) * 2 * 2)
     # lm_head + selection
-    V = c.vocab_size // tp
-    wl = ops.make_linear([{"dtype": "float16", "data": (torch.randn(V, H, device="cuda") * 0.02).half(),
-                           "shape": (V, H)}], H, 128)
-    logits = torch.zeros(M, V, dtype=torch.float16, device="cuda")
-    run("lm_head_gemm", lambda: ops.linear(wl, x, M, logits), V * H * 2 + M * V * 2, 2 * M * V * H)
-    out = torch.zeros(M, dtype=torch.int32, device="cuda")
-    run("argmax", lambda: ops.argmax(logits, out, M), M * V * 2)
-    temp = torch.full((M,), 0.8, device="cuda")
-    tk = torch.full((M,), 50, dtype=torch.int32, device="cuda")
-    tpp = torch.full((M,), 0.9, device="cuda")
-    seeds = torch.arange(M, dtype=torch.int64, device="cuda")
-    run("sample_topk_topp", lambda: ops.sample(logits, out, M, temp, tk, tpp, seeds, 1), M * V * 2 * 6)
+    if want("lm_head_gemm", "argmax", "sample_topk_topp"):
+        V = c.vocab_size // tp
+        wl = ops.make_linear([{"dtype": "float16", "data": (torch.randn(V, H, device="cuda") * 0.02).half(),
+                               "shape": (V, H)}], H, 128)
+        logits = torch.zeros(M, V, dtype=torch.float16, device="cuda")
+        run("lm_head_gemm", lambda: ops.linear(wl, x, M, logits), V * H * 2 + M * V * 2, 2 * M * V * H)
+        out = torch.zeros(M, dtype=torch.int32, device="cuda")
+        run("argmax", lambda: ops.argmax(logits, out, M), M * V * 2)
+        temp = torch.full((M,), 0.8, device="cuda")
+        tk = torch.full((M,), 50, dtype=torch.int32, device="cuda")
+        tpp = torch.full((M,), 0.9, device="cuda")
+        seeds = torch.arange(M, dtype=torch.int64, device="cuda")
+        run("sample_topk_topp", lambda: ops.sample(logits, out, M, temp, tk, tpp, seeds, 1), M * V * 2 * 6)
     hdr = f"{'kernel':22s} {'us':>9s} {'GB/s':>9s} {'of HBM':>7s} {'TFLOP/s':>9s} {'of tensor':>9s}"
     print(f"shape {a.shape}, tokens {M}, tp {tp}, peaks {peaks}")
     print(hdr)

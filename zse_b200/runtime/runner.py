@@ -228,8 +228,15 @@ class ModelRunner:
         self._stage_adapters(per_tok_adapter, total, total)
         greedy = self._stage_sampling(sampling or [GREEDY] * n_rows, n_rows) if select else True
         self._staging_end()
+        ev = None
+        if self.step_events is not None:         # a caller times the passes (speculative verification runs through here)
+            ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+            ev[0].record()
         with self._nvtx(f"prefill[{total} tokens, {S} seqs]"):
             self.model.forward(b, cache.slab, total, "prefill", S, max_q, n_rows)
+        if ev is not None:
+            ev[1].record()
+            self.step_events.append(ev)
         self.timings["prefill_passes"] += 1
         self._step += 1
         for sid, toks, start in items:
