@@ -66,6 +66,8 @@ def parse_args():
     ap.add_argument("--trace-kernels", default=None, metavar="FILE",
                     help="after the result line, run five more steps under the CUPTI activity tracer and write rank "
                          "0's per-kernel device times to FILE (a diagnostic: not part of any reported number)")
+    ap.add_argument("--spec-k", type=int, default=None,
+                    help="override the workload's number of draft tokens per step (0: plain decoding of the same requests)")
     ap.add_argument("--workload", default="batch64", choices=sorted(WORKLOADS),
                     help="batch64: 64 requests, prompts uniform in [128, 2048] (the headline); single: one request "
                          "with a 512-token prompt on the 7B shape (the case the reference publishes); spec32b: n-gram "
@@ -213,7 +215,9 @@ def run_ours(args):
     from zse_b200.sched.request import RequestState
 
     path = model_file(args, rank, barrier)
-    wl = WORKLOADS[args.workload]
+    wl = dict(WORKLOADS[args.workload])
+    if args.spec_k is not None:
+        wl["spec_k"] = args.spec_k
     per_step = 1 + wl["spec_k"]                      # most tokens a request can gain in one engine step
     need_tokens = max(wl["out"], (args.steps + args.warmup) * per_step + 48)
     longest = wl["prompt"][-1]
@@ -334,7 +338,7 @@ def run_ours(args):
             "vs_baseline": vs_baseline, "dtype": "fp16", "data": "synthetic",
             "config": {"model": f"{args.model}-shaped INT4 group-128 (random N(0,0.02)-like weights)",
                        "global_batch": S, "seq_len": wl["seq_len"],
-                       "workload": args.workload,
+                       "workload": args.workload, "speculative_k": wl["spec_k"],
                        "parallelism": f"tp{world}", "kv_cache": "paged fp16", "tp_collectives": cfg.comm_backend,
                        "cuda_graphs": cfg.use_cuda_graphs,
                        "l2_policy": "inputs larger than L2: each step streams all INT4 weights and the KV cache",

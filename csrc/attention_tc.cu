@@ -44,7 +44,8 @@ struct TcArgs {
   __half* out;
   int ldo, max_blocks, nh, nkv, block_size;
   float scale_log2;
-  int v_desc_swap;          // debugging aid: exchange the two strides of the MN-major descriptor
+  int packed;               // > 0: chunks of at most 16 rows; the CTA owns ONE kv head and packs the `packed` query
+                            // heads that share it as 16-row slots of its 128 rows (keys and values read once per group)
   Status* status;
 };
 
@@ -62,7 +63,7 @@ __device__ __forceinline__ uint64_t make_desc_sw128_mn(uint32_t smem_addr, uint3
 
 __global__ void __launch_bounds__(kTcThreads, 2)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_kv,
-                       const TcArgs a) {
+                       const __grid_constant__ CUtensorMap tmap_q16, const TcArgs a) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* q_s = smem;
@@ -75,7 +76,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
   const int q_begin = a.cu_q[seq], q_len = a.cu_q[seq + 1] - q_begin;
   if (qt * kTcRows >= q_len) return;                     // before any barrier or TMEM use: the whole CTA leaves
   const int pos0 = a.q_pos0[seq];
-  const int kvh = head / (a.nh / a.nkv);
+  const int G = a.packed;                                // query heads per kv head in packed mode (else 0)
+  const int kvh = G > 0 ? head : head / (a.nh / a.nkv);  // packed: blockIdx.y walks the kv heads
   const int last_row = min(q_len, qt * kTcRows + kTcRows) - 1;
   const int kv_len = pos0 + last_row + 1;                // keys visible to the last query row of this CTA
   const int n_tiles = (kv_len + kTcKv - 1) / kTcKv;
@@ -92,7 +94,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     mbar_init(&bars->o_full, 1);
     bars->abort_flag = 0;
     mbar_fence_init();
-    prefetch_tmap(&tmap_q);
+    prefetch_tmap(G > 0 ? &tmap_q16 : &tmap_q);
     prefetch_tmap(&tmap_kv);
   }
   // V must never hold a NaN bit pattern where a probability is zero (0 * NaN): clear it once; afterwards it only ever
@@ -114,10 +116,20 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     // ------------------------------------------------------------------ producer
     if (lane == 0) {
       pdl_wait();                                      // q and the cache rows of this chunk come from the previous kernels
-      mbar_arrive_expect_tx(&bars->q_full, kTcTileBytes);
-      const int y = q_begin + qt * kTcRows;
-      tma_load_2d(q_s, &tmap_q, head * kTcHd, y, &bars->q_full);
-      tma_load_2d(q_s + kTcTileBytes / 2, &tmap_q, head * kTcHd + 64, y, &bars->q_full);
+      if (G > 0) {
+        // slot s = rows 16 s .. 16 s + 15 = the chunk's (at most 16) rows of query head kvh * G + s
+        mbar_arrive_expect_tx(&bars->q_full, uint32_t(G) * 4096u);
+        for (int sl = 0; sl < G; ++sl) {
+          const int x = (kvh * G + sl) * kTcHd;
+          tma_load_2d(q_s + sl * 2048, &tmap_q16, x, q_begin, &bars->q_full);
+          tma_load_2d(q_s + kTcTileBytes / 2 + sl * 2048, &tmap_q16, x + 64, q_begin, &bars->q_full);
+        }
+      } else {
+        mbar_arrive_expect_tx(&bars->q_full, kTcTileBytes);
+        const int y = q_begin + qt * kTcRows;
+        tma_load_2d(q_s, &tmap_q, head * kTcHd, y, &bars->q_full);
+        tma_load_2d(q_s + kTcTileBytes / 2, &tmap_q, head * kTcHd + 64, y, &bars->q_full);
+      }
       uint32_t ph = 1;                                 // "empty" barriers: the first wait passes
       for (int t = 0; t < n_tiles; ++t) {
         // which 16-token groups of this tile exist (the last tile may be short)
@@ -155,8 +167,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
       constexpr uint32_t idesc_pv = make_idesc_f16(kTcRows, kTcHd) | (1u << 16);       // B is MN-major
       const uint64_t q_desc = make_desc_sw128(smem_u32(q_s));
       const uint64_t k_desc = make_desc_sw128(smem_u32(k_s));
-      const uint32_t mn64 = a.v_desc_swap ? 1024u : uint32_t(kTcTileBytes / 2);
-      const uint32_t k8 = a.v_desc_swap ? uint32_t(kTcTileBytes / 2) : 1024u;
+      // V [keys][head_dim] as the MN-major B operand: 64 head_dim elements per 128-byte row, eight keys per 1024 bytes,
+      // the second half of head_dim 16 KB further on
+      const uint32_t mn64 = uint32_t(kTcTileBytes / 2), k8 = 1024u;
       bool ok = mbar_wait(&bars->q_full, 0, abort_flag, a.status, 43, 0);
       uint32_t ph = 0;
       for (int t = 0; t < n_tiles && ok; ++t) {
@@ -188,7 +201,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
   } else {
     // ------------------------------------------------------------------ softmax + epilogue: thread = query row
     const int r = warp * 32 + lane;                   // row inside the CTA = TMEM lane
-    const int row = qt * kTcRows + r;                 // row inside the sequence's chunk
+    const int slot = r >> 4;                          // packed mode: which query head of the group
+    const int row = G > 0 ? (r & 15) : qt * kTcRows + r;      // row inside the sequence's chunk
+    const int out_head = G > 0 ? kvh * G + slot : head;
+    const bool row_live = row < q_len && (G == 0 || slot < G);
     const int limit = pos0 + row;                     // last key this row may see
     const uint32_t lane_addr = uint32_t(warp * 32) << 16;
     float m_used = -INFINITY, l = 0.f;
@@ -265,9 +281,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     tc_fence_after_sync();
     if (ok) {
       // every lane takes part in the warp-wide tcgen05.ld (rows past the chunk included); only the stores are per row
-      const bool live = row < q_len;
+      const bool live = row_live;
       const float inv = l > 0.f ? 1.f / l : 0.f;
-      __half* dst = a.out + size_t(q_begin + (live ? row : 0)) * a.ldo + size_t(head) * kTcHd;
+      __half* dst = a.out + size_t(q_begin + (live ? row : 0)) * a.ldo + size_t(live ? out_head : 0) * kTcHd;
 #pragma unroll 1
       for (int c = 0; c < 8; ++c) {
         uint32_t o[16];
@@ -313,8 +329,13 @@ extern "C" int zse_attn_prefill_tc(const void* q, int ldq, int total_rows, const
   if ((reinterpret_cast<uintptr_t>(q) & 15) || (reinterpret_cast<uintptr_t>(kv_layer) & 15) ||
       (reinterpret_cast<uintptr_t>(out) & 15))
     return ZSE_ERR_ALIGN;
-  CUtensorMap tq, tkv;
+  CUtensorMap tq, tkv, tq16;
   if (int rc = get_tmap(q, uint64_t(total_rows), uint64_t(ldq), uint32_t(kTcRows), &tq)) return rc;
+  if (int rc = get_tmap(q, uint64_t(total_rows), uint64_t(ldq), 16u, &tq16)) return rc;
+  // chunks of at most 16 rows (speculative verification, short tails): one CTA per kv head serves the whole group of
+  // query heads, so keys and values are read once per group instead of once per query head
+  const int group = nh / nkv;
+  const int packed = (max_q_len <= 16 && group <= 8 && variant != 2) ? group : 0;
   if (int rc = get_tmap(kv_layer, uint64_t(num_blocks) * 2 * nkv * block_size, uint64_t(kTcHd), 16u, &tkv)) return rc;
   static bool attr[kMaxDevices] = {};
   const int dev_slot = current_device_slot();
@@ -326,10 +347,10 @@ extern "C" int zse_attn_prefill_tc(const void* q, int ldq, int total_rows, const
   }
   TcArgs a{reinterpret_cast<const int*>(block_tables), reinterpret_cast<const int*>(cu_q),
            reinterpret_cast<const int*>(q_pos0), reinterpret_cast<__half*>(out), ldo, max_blocks, nh, nkv, block_size,
-           scale * 1.4426950408889634f, variant, reinterpret_cast<Status*>(status)};
-  dim3 grid((max_q_len + kTcRows - 1) / kTcRows, nh, num_seqs);
+           scale * 1.4426950408889634f, packed, reinterpret_cast<Status*>(status)};
+  dim3 grid((max_q_len + kTcRows - 1) / kTcRows, packed > 0 ? nkv : nh, num_seqs);
   return launch_pdl(attn_prefill_tc_kernel, grid, dim3(kTcThreads), size_t(kTcSmemBytes),
-                    reinterpret_cast<cudaStream_t>(stream), tq, tkv, a) == cudaSuccess
+                    reinterpret_cast<cudaStream_t>(stream), tq, tkv, tq16, a) == cudaSuccess
              ? 0
              : ZSE_ERR_LAUNCH;
 }

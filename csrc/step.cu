@@ -113,6 +113,9 @@ extern "C" int zse_step_forward(const ZseStepModel* m, const ZseStepBuffers* b, 
   Pass p{m, b, stream, M, 0, 0};
   const int H = m->hidden, hd = m->head_dim, nh = m->num_heads, nkv = m->num_kv_heads;
   const int qkv_ld = (nh + 2 * nkv) * hd;
+  // blocks in one layer of the pool [layers][blocks][2][nkv][block_size][hd]
+  const int64_t per_block = int64_t(2) * nkv * block_size * hd;
+  const int kv_blocks = per_block > 0 ? int(kv_layer_stride / per_block) : 0;
   p.did(zse_embedding(m->embed, b->ids, b->residual, M, H, m->vocab_rows, m->embed_scale, b->status, stream));
   int planes = 0, slot = 0;
   for (int li = 0; li < m->num_layers && p.ok(); ++li) {
@@ -143,6 +146,10 @@ extern "C" int zse_step_forward(const ZseStepModel* m, const ZseStepBuffers* b, 
       p.did(zse_attn_decode(b->qkv, qkv_ld, kv_layer, b->block_tables, b->max_blocks, b->seq_lens, b->attn_out,
                             nh * hd, b->attn_scratch, num_seqs, nh, nkv, hd, block_size, attn_splits, m->scale, stream),
             attn_splits > 1 ? 2 : 1);
+    else if (m->attn_tc && hd == 128 && kv_blocks > 0)
+      p.did(zse_attn_prefill_tc(b->qkv, qkv_ld, M, kv_layer, kv_blocks, b->block_tables, b->max_blocks, b->cu_q,
+                                b->q_pos0, b->attn_out, nh * hd, num_seqs, max_q_len, nh, nkv, hd, block_size, m->scale,
+                                0, b->status, stream));
     else
       p.did(zse_attn_prefill(b->qkv, qkv_ld, kv_layer, b->block_tables, b->max_blocks, b->cu_q, b->q_pos0, b->attn_out,
                              nh * hd, num_seqs, max_q_len, nh, nkv, hd, block_size, m->scale, stream));

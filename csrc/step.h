@@ -26,7 +26,8 @@ typedef struct {
 } ZseStepLayer;
 
 typedef struct {
-  int32_t num_layers, hidden, num_heads, num_kv_heads, head_dim, inter, vocab_rows, rotary_dim, sm_count, reserved;
+  int32_t num_layers, hidden, num_heads, num_kv_heads, head_dim, inter, vocab_rows, rotary_dim, sm_count;
+  int32_t attn_tc; /* != 0: prefill attention of head_dim 128 on the tcgen05 kernel (zse_attn_prefill_tc) */
   float eps, scale, embed_scale, reserved_f;
   const void* embed;      /* fp16 [vocab_rows, hidden] */
   const void* final_norm; /* fp16 [hidden] */

@@ -402,24 +402,31 @@ def test_attn_prefill_chunks(ops, hd, nh, nkv, bs):
     assert (out.float() - want.float()).abs().max() < 3e-3
 
 
-@pytest.mark.parametrize("nh,nkv,bs,variant", [(8, 2, 16, 0), (5, 1, 32, 0), (4, 4, 64, 0), (8, 2, 16, 1)])
-def test_attn_prefill_on_tcgen05(ops, nh, nkv, bs, variant):
+@pytest.mark.parametrize("nh,nkv,bs,q_lens,pos0,mode", [
+    (8, 2, 16, [300, 70, 5, 128], [0, 100, 37, 256], 0),          # long chunks: one CTA per 128 rows of one head
+    (5, 1, 32, [300, 70, 5, 128], [0, 100, 37, 256], 0),
+    (4, 4, 64, [300, 70, 5, 128], [0, 100, 37, 256], 0),
+    (10, 2, 16, [5, 16, 1, 9], [37, 100, 0, 300], 0),              # chunks of <= 16 rows: query heads packed per kv head
+    (8, 1, 16, [4, 4, 4], [500, 17, 129], 0),                      # eight query heads on one kv head
+    (10, 2, 16, [5, 16, 1, 9], [37, 100, 0, 300], 2),              # the same chunks without packing
+])
+def test_attn_prefill_on_tcgen05(ops, nh, nkv, bs, q_lens, pos0, mode):
     """The tcgen05 prefill kernel (S = Q K^T and O = P V on the tensor cores, probabilities through TMEM, V as an
     MN-major operand straight from the cache layout) against the fp32 oracle: a fresh prompt longer than two key tiles,
-    a chunk on top of cached tokens that starts inside a tile, a short verify chunk, a chunk of exactly one tile."""
+    a chunk on top of cached tokens that starts inside a tile, a short verify chunk, a chunk of exactly one tile; and
+    verification-sized chunks, where one CTA serves all query heads of a kv head."""
     from zse_b200.ops import native
     hd = 128
-    q_lens, pos0 = [300, 70, 5, 128], [0, 100, 37, 256]
     S = len(q_lens)
     totals = [a + b for a, b in zip(q_lens, pos0)]
     kv, bt = _make_cache(S, totals, nkv, hd, bs, 160 * 16 // bs)
-    cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32, device="cuda")
+    cu = torch.tensor([0] + [int(v) for v in torch.tensor(q_lens).cumsum(0)], dtype=torch.int32, device="cuda")
     p0 = torch.tensor(pos0, dtype=torch.int32, device="cuda")
     total = sum(q_lens)
     q = torch.randn(total, (nh + 2 * nkv) * hd, device="cuda").half()
     out = torch.full((total + 3, nh * hd), 7.0, dtype=torch.float16, device="cuda")
     native.attn_prefill_tc(q, q.stride(0), total, kv, bt, cu, p0, out, out.stride(0), S, max(q_lens), nh, nkv, hd, bs,
-                           1 / math.sqrt(hd), ops.status.ptr, variant)
+                           1 / math.sqrt(hd), ops.status.ptr, mode)
     torch.cuda.synchronize()
     ops.check()
     want = ref.attn_prefill(q[:, : nh * hd], kv, bt, cu, p0, nh, nkv, hd, bs, 1 / math.sqrt(hd))

@@ -72,6 +72,21 @@ def _compile(nvcc: str, src: str, obj: str, verbose: bool, extra: tuple = ()) ->
     os.replace(obj + ".tmp", obj)
 
 
+def _prune() -> None:
+    """Drops cached objects that no linked library refers to any more (every edit of a source leaves one behind)."""
+    keep = set()
+    for f in os.listdir(OUT_DIR) if os.path.isdir(OUT_DIR) else []:
+        if f.endswith(".stamp"):
+            with open(os.path.join(OUT_DIR, f)) as fh:
+                keep |= set(fh.read().split())
+    for f in os.listdir(OBJ_DIR) if os.path.isdir(OBJ_DIR) else []:
+        if f.endswith(".o") and f not in keep:
+            try:
+                os.unlink(os.path.join(OBJ_DIR, f))
+            except OSError:
+                pass
+
+
 def build(force: bool = False, verbose: bool = False) -> str:
     """Compile what changed and (re)link.  Returns the library path."""
     nvcc = nvcc_path()
@@ -97,6 +112,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
     os.replace(LIB_PATH + ".tmp", LIB_PATH)
     with open(stamp, "w") as f:
         f.write(want)
+    _prune()
     return LIB_PATH
 
 
@@ -133,6 +149,7 @@ def build_variant(name: str, verbose: bool = False) -> str:
     os.replace(out + ".tmp", out)
     with open(stamp, "w") as f:
         f.write(want)
+    _prune()
     return out
 
 

@@ -34,7 +34,7 @@ class _Layer(Structure):
 
 class _Model(Structure):
     _fields_ = [(n, c_int32) for n in ("num_layers", "hidden", "num_heads", "num_kv_heads", "head_dim", "inter",
-                                       "vocab_rows", "rotary_dim", "sm_count", "reserved")] + \
+                                       "vocab_rows", "rotary_dim", "sm_count", "attn_tc")] + \
                [(n, c_float) for n in ("eps", "scale", "embed_scale", "reserved_f")] + \
                [("embed", c_void_p), ("final_norm", c_void_p), ("inv_freq", c_void_p), ("lm_head", _Linear),
                 ("layers", POINTER(_Layer)), ("rope_table", c_void_p), ("max_position", c_int32),
@@ -80,7 +80,8 @@ class NativeStep:
         self._model = _Model(
             num_layers=len(model.layers), hidden=c.hidden_size, num_heads=p.num_heads, num_kv_heads=p.num_kv_heads,
             head_dim=c.head_dim, inter=p.inter_size, vocab_rows=model.embed.shape[0],
-            rotary_dim=model.inv_freq.numel() * 2, sm_count=model.ops.sm_count, eps=c.rms_norm_eps, scale=model.scale,
+            rotary_dim=model.inv_freq.numel() * 2, sm_count=model.ops.sm_count,
+            attn_tc=int(bool(getattr(model.ops, "attn_prefill_tc", False))), eps=c.rms_norm_eps, scale=model.scale,
             embed_scale=model.embed_scale, embed=model.embed.data_ptr(), final_norm=model.norm.data_ptr(),
             inv_freq=model.inv_freq.data_ptr(), lm_head=_linear(model.lm_head), layers=self._layers,
             rope_table=None if model.rope_table is None else model.rope_table.data_ptr(),

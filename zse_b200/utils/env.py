@@ -33,8 +33,8 @@ KNOWN: Dict[str, Tuple[str, str]] = {
                          "(sum of the bits; 0: the tiled kernel everywhere; 8 measured slower than the separate "
                          "add+norm kernel on one GPU, so it is off by default)"),
     "ZSE_W8_RESIDENT": ("1", "keep INT8 weights 8 bits wide on the device (0: expand them to fp16 at load)"),
-    "ZSE_ATTN_PREFILL_TC": ("0", "prefill attention of head_dim 128 models on the tcgen05 kernel (csrc/attention_tc.cu) "
-                                 "instead of the mma.sync one"),
+    "ZSE_ATTN_PREFILL_TC": ("1", "prefill attention of head_dim 128 models on the tcgen05 kernel (csrc/attention_tc.cu); "
+                                 "0: the mma.sync kernel for every shape"),
     "ZSE_NATIVE_LIB": ("", "path of the native library to load instead of the ordinary build (instrumented variants)"),
     "ZSE_PDL": ("1", "programmatic dependent launch between the kernels of a pass (read by the native library)"),
     "ZSE_TP_PDL": ("0", "programmatic dependent launch for the exchange kernels too (read by the native library)"),
