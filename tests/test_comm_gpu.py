@@ -235,7 +235,8 @@ def _k1_ctx(tp, m_cap, H):
 
 @pytest.mark.gpu
 @pytest.mark.parametrize("M,H,K,int8", [(1, 1024, 512, False), (7, 1024, 1792, False), (64, 5120, 640, False),
-                                        (33, 2560, 1024, True), (64, 5120, 1792, False)])
+                                        (33, 2560, 1024, True), (64, 5120, 1792, False), (4, 1024, 128, False),
+                                        (8, 1024, 256, False)])
 def test_projection_residual_norm_in_one_kernel_single_rank(ops, M, H, K, int8):
     """kDecAllReduceNorm with one rank: projection, residual add and RMSNorm are one launch (no peers to wait for)."""
     from zse_b200.ops import native
@@ -266,7 +267,7 @@ def test_projection_residual_norm_in_one_kernel_single_rank(ops, M, H, K, int8):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("tp,M,H,K", [(2, 5, 1024, 512), (4, 64, 1024, 1024), (8, 40, 5120, 640)])
+@pytest.mark.parametrize("tp,M,H,K", [(2, 5, 1024, 512), (4, 64, 1024, 1024), (8, 40, 5120, 640), (8, 4, 1024, 128)])
 def test_one_kernel_all_reduce_with_peers_that_have_delivered(ops, tp, M, H, K):
     """The multi-rank data path on one GPU without any kernel waiting for another: this rank's launch finds the other
     ranks' rows already in its inbox and their counters already at the target (written here by the host), sends its

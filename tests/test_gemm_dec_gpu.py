@@ -42,7 +42,8 @@ def _rel(a, b):
 
 # (M, N, K): split plans with 1..8 segments, odd tile counts (N = 128 * odd), a stream plan (more than 74 tile pairs)
 SHAPES = [(1, 256, 256), (5, 128, 512), (16, 384, 1024), (17, 640, 2048), (33, 896, 5120), (64, 1024, 4096),
-          (64, 5120, 640), (48, 2560, 1792), (64, 19456, 384), (31, 20480, 256), (64, 200, 256), (8, 19328, 640)]
+          (64, 5120, 640), (48, 2560, 1792), (64, 19456, 384), (31, 20480, 256), (64, 200, 256), (8, 19328, 640),
+          (7, 1024, 128), (64, 384, 128), (4, 20480, 128)]        # a single K stage: shards of narrow layers at TP8
 
 
 @pytest.mark.parametrize("M,N,K", SHAPES)
@@ -65,7 +66,7 @@ def test_dec_fp16_and_fp32_epilogues(ops, ws, M, N, K):
 
 
 @pytest.mark.parametrize("M,I,K", [(1, 128, 256), (9, 192, 512), (64, 1024, 1024), (40, 1728, 5120), (64, 9600, 256),
-                                   (23, 9664, 384)])
+                                   (23, 9664, 384), (5, 256, 128)])
 def test_dec_swiglu(ops, ws, M, I, K):
     g, gd = _parts(I, K, 3)
     u, ud = _parts(I, K, 4)
@@ -80,7 +81,7 @@ def test_dec_swiglu(ops, ws, M, I, K):
 
 
 @pytest.mark.parametrize("M,nh,nkv,K,bs", [(1, 4, 1, 512, 16), (7, 5, 1, 640, 16), (64, 8, 2, 1024, 32),
-                                           (33, 40, 8, 256, 16)])
+                                           (33, 40, 8, 256, 16), (4, 1, 1, 128, 16)])
 def test_dec_qkv_rope_kv_write(ops, ws, M, nh, nkv, K, bs):
     hd = 128
     N = (nh + 2 * nkv) * hd
