@@ -212,10 +212,10 @@ class FusedComm(NcclComm):
         self._push_ready = False
         # Decode-sized passes: the row-parallel projection, the all-reduce, the residual add and the next RMSNorm are ONE
         # kernel (csrc/gemm_w4_dec.cu, kDecAllReduceNorm); it uses the same inboxes and counters as the push exchange.
-        # measured per decode step of the 14B shape: one kernel 6.55 vs 6.60 ms on two GPUs, 5.45 vs 5.07 on four,
-        # 5.14 vs 4.85 on eight (the kernel's tail - a grid-wide hand-over through L2 - costs more than the second launch)
-        k1 = env.text("ZSE_TP_FUSED_K1").strip().lower()
-        self.fused_k1 = (world <= 2) if k1 in ("auto", "") else k1 not in ("0", "false", "off", "no")
+        # measured per decode step of the 14B shape, one kernel vs two: 6.66 vs 6.20 ms on two GPUs, 5.45 vs 5.07 on
+        # four, 5.14 vs 4.85 on eight (the kernel's tail - a grid-wide hand-over through L2 - costs more than the second
+        # launch), so the two-kernel form is the default
+        self.fused_k1 = env.flag("ZSE_TP_FUSED_K1")
         self.k1_calls = 0
         if self.push or self.fused_k1:
             self._init_push(symm, grp, world, rank, device, hidden_size, want_mm)

@@ -21,9 +21,9 @@ KNOWN: Dict[str, Tuple[str, str]] = {
     "ZSE_KERNEL_CACHE": ("~/.cache/zse_b200/kernels", "directory of the kernel language's cubin cache"),
     "ZSE_TP_MULTIMEM": ("1", "use NVSwitch multimem loads in the fused exchange where the fabric offers them"),
     "ZSE_TP_PUSH": ("0", "let the row-parallel GEMM push its rows to the peers from its epilogue"),
-    "ZSE_TP_FUSED_K1": ("auto", "decode-sized passes: row-parallel GEMM + all-reduce + residual + RMSNorm as ONE kernel "
-                                "(1), as GEMM + one exchange kernel (0), or by measurement (auto: one kernel on two "
-                                "GPUs, two kernels from four GPUs on)"),
+    "ZSE_TP_FUSED_K1": ("0", "decode-sized passes: row-parallel GEMM + all-reduce + residual + RMSNorm as ONE kernel "
+                             "(1) or as GEMM + one exchange kernel (0, the default: measured faster on 2, 4 and 8 "
+                             "GPUs)"),
     "ZSE_TP_TWO_SHOT_ROWS": (str(1 << 30), "passes of at least this many rows take the two-shot reduce-scatter kernel"),
     "ZSE_TP_NCCL_ROWS": ("256", "passes of at least this many rows take NCCL instead of the fused exchange"),
     "ZSE_TP_FUSED_SP_ROWS": ("128", "fused collectives: passes of at least this many rows scatter the row-parallel GEMM's "
