@@ -93,3 +93,72 @@ def test_missing_rank_makes_the_others_give_up_and_the_group_recovers():
             for row in range(rows):
                 assert np.array_equal(again[r][c][row], _ordered_sum(partials[2 + c, :, row]))
     assert not x.status
+
+
+# ---- the exchange for passes of many rows: scatter in the GEMM's epilogue, reduce on the owner, gather in the prologue
+def _run_scatter_gather(tp, rows, calls, slots, speeds, skip_rank=None, wait_limit_s=1.0, gather=True):
+    from zse_b200.parallel.protocol_model import ScatterGatherExchange
+    H = 12
+    ex = ScatterGatherExchange(tp, rows, H, block=4, units=3, slots=slots, wait_limit_s=wait_limit_s)
+    rng = np.random.default_rng(3)
+    parts = (rng.standard_normal((calls, tp, rows, H)) * 0.5).astype(np.float16)
+    seen = [[None] * calls for _ in range(tp)]
+    oks = [[True] * calls for _ in range(tp)]
+
+    def rank_fn(r):
+        for c in range(calls):
+            pause = (lambda where, d=speeds[r]: time.sleep(d)) if speeds[r] else None
+            if r != skip_rank:
+                ex.scatter(r, c, parts[c, r], pause)
+            ok = ex.reduce_gather(r, c, pause)
+            if gather:
+                ok = ex.gather_wait(r) and ok
+            oks[r][c] = ok
+            seen[r][c] = ex.xg[r].copy()          # what the next GEMM of this rank reads
+
+    threads = [threading.Thread(target=rank_fn, args=(r,)) for r in range(tp)]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join(60)
+    return ex, parts, seen, oks
+
+
+def test_scatter_gather_two_slots_with_ranks_of_very_different_speed():
+    tp, rows, calls = 3, 22, 6
+    ex, parts, seen, oks = _run_scatter_gather(tp, rows, calls, slots=2, speeds=[0.0, 0.004, 0.0])
+    assert not ex.status and not ex.overruns and all(all(o) for o in oks)
+    for c in range(calls):
+        want = parts[c].astype(np.float32).sum(axis=0)
+        for r in range(tp):
+            assert np.allclose(seen[r][c], want, atol=2e-2), (c, r)
+            assert np.array_equal(seen[r][c], seen[0][c])          # every rank gathered the same rows
+    assert int(ex.arrive.sum()) == 0                               # every counter was taken down again
+    assert list(ex.epoch) == [calls] * tp and np.all(ex.gflag == calls)
+
+
+def test_scatter_gather_is_ordered_by_the_gather_wait():
+    """What lets an owner take its counters down: nobody scatters again before having waited for every block of the
+    call before.  Without that wait a fast rank's next scatter lands in counters and rows a slow owner still uses."""
+    tp, rows, calls = 3, 22, 6
+    bad = 0
+    for attempt in range(3):
+        ex, parts, seen, oks = _run_scatter_gather(tp, rows, calls, slots=1, speeds=[0.0, 0.006, 0.0],
+                                                   wait_limit_s=0.3, gather=False)
+        wrong = any(not np.allclose(seen[r][c], parts[c].astype(np.float32).sum(axis=0), atol=2e-2)
+                    for c in range(calls) for r in range(tp))
+        if wrong or ex.overruns or ex.status:
+            bad += 1
+    assert bad >= 1
+    # with the wait, even a single slot holds (the wait is a full barrier between calls); the second slot is margin
+    ex, parts, seen, oks = _run_scatter_gather(tp, rows, calls, slots=1, speeds=[0.0, 0.004, 0.0])
+    assert not ex.status and not ex.overruns
+    for c in range(calls):
+        assert np.allclose(seen[1][c], parts[c].astype(np.float32).sum(axis=0), atol=2e-2)
+
+
+def test_scatter_gather_gives_up_when_a_rank_never_delivers():
+    tp, rows = 3, 10
+    ex, parts, seen, oks = _run_scatter_gather(tp, rows, 1, slots=2, speeds=[0, 0, 0], skip_rank=2, wait_limit_s=0.2)
+    assert ex.status and all(s.peer == 2 for s in ex.status if s.rank in (0, 1))
+    assert not all(all(o) for o in oks)            # somebody reported the failure instead of hanging

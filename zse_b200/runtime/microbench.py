@@ -113,6 +113,17 @@ def main():
         inv = ref.inv_freq(hd, c.rope_theta).cuda()
         run("rope_kv_write", lambda: ops.rope_kv_write(qkv, kv, pos, slots, inv, M, nh, nkv, hd, bs),
             M * (q_dim + 2 * kv_dim) * 2 * 2)
+    # batched LoRA: every token routed to one of 32 rank-16 adapters on a q_proj-sized projection
+    if want("lora_apply"):
+        n_ad, r_lora = 32, 16
+        a_tab = (torch.randn(n_ad, r_lora, H, device="cuda") * 0.01).half()
+        b_tab = (torch.randn(n_ad, q_dim, r_lora, device="cuda") * 0.01).half()
+        ad_ids = (torch.arange(M, device="cuda", dtype=torch.int32) % n_ad).contiguous()
+        ad_scales = torch.full((n_ad,), 2.0, device="cuda")
+        y_lora = torch.zeros(M, q_dim, dtype=torch.float16, device="cuda")
+        touched = min(M, n_ad) * (r_lora * H + q_dim * r_lora) * 2          # adapter matrices that are read at all
+        run("lora_apply", lambda: ops.lora_apply(x, a_tab, b_tab, ad_ids, ad_scales, y_lora, M, H, q_dim, r_lora),
+            touched + M * (H + 2 * q_dim) * 2, 2 * M * r_lora * (H + q_dim))
     # lm_head + selection
     if want("lm_head_gemm", "argmax", "sample_topk_topp"):
         V = c.vocab_size // tp
