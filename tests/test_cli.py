@@ -171,3 +171,18 @@ def test_info_lists_environment_switches(monkeypatch):
             if f.endswith(".py") and f != "env.py":
                 used |= set(re.findall(r"env\.(?:flag|integer|text)\(\"(ZSE_[A-Z0-9_]+)\"", open(os.path.join(d, f)).read()))
     assert used and used <= set(env.KNOWN)
+
+
+def test_bench_reference_arm_prints_its_unavailable_line():
+    """`bench.py --impl reference` must print one JSON line with `impl` and `unavailable` and exit 0 on a machine where
+    the reference cannot be timed (every workload of it is closed: see baseline/run_reference.py)."""
+    import json
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    for extra in ([], ["--workload", "single"], ["--gpus", "2"]):
+        r = subprocess.run([sys.executable, os.path.join(root, "bench.py"), "--impl", "reference", "--steps", "2",
+                            "--warmup", "1"] + extra, capture_output=True, text=True, timeout=120)
+        assert r.returncode == 0, r.stderr[-2000:]
+        line = json.loads(r.stdout.strip().splitlines()[-1])
+        assert line["impl"] == "reference" and isinstance(line["unavailable"], str) and "\n" not in line["unavailable"]
