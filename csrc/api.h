@@ -213,6 +213,11 @@ int zse_tp_sp_sum_norm_gather(void* ctx, void* residual, const void* weight, int
 int zse_tp_sp_sum_norm_gather_emulated(void* ctx, const uint64_t* residuals, const void* weight, int M, float eps,
                                        int slot, void* status, void* stream);
 int zse_tp_sp_wait(void* ctx, int M, int rank_override, void* status, void* stream);
+// All-gather of vocabulary-sharded logits rows over NVLink (peer stores + per-row flags): buf_ptrs[r] = rank r's gathered
+// rows [2][rows_cap][tp * width] fp16, flag_ptrs[r] = its flags [2][tp][rows_cap] u32, both symmetric memory.
+int zse_tp_ctx_set_gather(void* ctx, int rows_cap, int width, const uint64_t* buf_ptrs, const uint64_t* flag_ptrs);
+int zse_tp_gather_rows(void* ctx, const void* logits, int ld, int M, int slot, void* status, void* stream);
+int zse_tp_gather_rows_emulated(void* ctx, const uint64_t* logits, int ld, int M, int slot, void* status, void* stream);
 int zse_tp_argmax(void* ctx, const void* logits, int ld, void* out, int M, int V_local, int vocab_stride,
                   int slot, void* status, void* stream);
 int zse_tp_argmax_emulated(void* ctx, const uint64_t* logits, int ld, const uint64_t* outs, int M, int V_local,

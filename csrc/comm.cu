@@ -546,6 +546,44 @@ __global__ void __launch_bounds__(1024) tp_argmax_kernel(const TpArgmaxArgs a) {
 }
 
 
+// ---- all-gather of vocabulary-sharded logits (sampling with temperature under tensor parallelism) ---------------
+// One CTA per logits row: it stores this rank's shard [W] of the row into columns rank * W .. of EVERY rank's gathered
+// buffer (16-byte peer stores), raises the row's flag for this source on every rank, then waits (bounded) until all tp
+// sources have raised theirs here and takes the flags down - when the launch is over, this rank holds the full rows.
+// Two slots alternate between calls, as in the other exchanges.  Replaces ncclAllGather + concatenation of the
+// reference-style path (NcclComm.gather_logits); shards must be equally wide with W a multiple of 8.
+struct TpGatherArgs {
+  const __half* src[kMaxTp];       // per emulated rank: local logits [M, ld]
+  int rank[kMaxTp];
+  __half* buf[kMaxTp];             // buf[k]: rank k's gathered rows [2][rows_cap][tp * W] as mapped here
+  uint32_t* flags[kMaxTp];         // flags[k]: rank k's flags [2][tp][rows_cap]
+  int ld, W, tp, rows_cap, slot;
+  Status* status;
+};
+
+__global__ void __launch_bounds__(512) tp_gather_rows_kernel(const TpGatherArgs a) {
+  __shared__ int ok_flag;
+  const int er = blockIdx.y, rank = a.rank[er], row = blockIdx.x;
+  if (threadIdx.x == 0) ok_flag = 1;
+  const uint4* src = reinterpret_cast<const uint4*>(a.src[er] + size_t(row) * a.ld);
+  const size_t row_off = (size_t(a.slot) * a.rows_cap + row) * (size_t(a.tp) * a.W) + size_t(rank) * a.W;
+  for (int c = threadIdx.x; c < a.W / 8; c += blockDim.x) {
+    const uint4 v = src[c];
+#pragma unroll
+    for (int k = 0; k < kMaxTp; ++k)
+      if (k < a.tp) reinterpret_cast<uint4*>(a.buf[k] + row_off)[c] = v;
+  }
+  __syncthreads();
+  const size_t base = size_t(a.slot) * a.tp * a.rows_cap;
+  if (threadIdx.x < a.tp) {
+    __threadfence_system();
+    st_relaxed_sys(a.flags[threadIdx.x] + base + size_t(rank) * a.rows_cap + row, 1u);
+    if (!wait_flag(a.flags[rank] + base + size_t(threadIdx.x) * a.rows_cap + row, a.status, 39, threadIdx.x))
+      ok_flag = 0;
+  }
+  __syncthreads();
+}
+
 // ---- sequence-parallel exchange for passes of many rows: the reduce + all-gather half (see SpTable) -------------
 // One CTA per token row; rows this rank does not own leave at once.  The owner waits (bounded) until every source's
 // counter for the row's 64-row block holds `units`, adds the tp fp16 rows of its inbox in rank order, adds its fp32
@@ -733,6 +771,10 @@ struct zse_tp_ctx {
   uint32_t* sp_state[kMaxTp] = {};   // sp_state[r]: rank r's local words {epoch, exit ticket, -, -, tickets[nblk_cap]}
   __half* mc_xg = nullptr;
   int sp_own_cap = 0, sp_nblk_cap = 0;
+  // logits all-gather (set by zse_tp_ctx_set_gather)
+  __half* g_buf[kMaxTp] = {};
+  uint32_t* g_flags[kMaxTp] = {};
+  int g_rows_cap = 0, g_width = 0;
 };
 
 extern "C" void* zse_tp_ctx_create(int tp, int rank, int m_cap, int H, const uint64_t* data_ptrs,
@@ -901,6 +943,68 @@ extern "C" int zse_tp_sp_wait(void* ctx, int M, int rank_override, void* status,
   tp_sp_wait_kernel<<<1, kRedThreads, 0, reinterpret_cast<cudaStream_t>(stream)>>>(sp.gflag[sp.rank], sp.state, nb,
                                                                                  reinterpret_cast<Status*>(status));
   return cudaGetLastError() == cudaSuccess ? 0 : ZSE_ERR_LAUNCH;
+}
+
+// Buffers of the logits all-gather: per rank r its gathered rows [2][rows_cap][tp * width] fp16 and flags
+// [2][tp][rows_cap] u32 (zero at start), both in symmetric memory.
+extern "C" int zse_tp_ctx_set_gather(void* ctx, int rows_cap, int width, const uint64_t* buf_ptrs,
+                                     const uint64_t* flag_ptrs) {
+  zse_tp_ctx* c = reinterpret_cast<zse_tp_ctx*>(ctx);
+  if (c == nullptr || rows_cap <= 0 || width <= 0 || width % 8) return ZSE_ERR_SHAPE;
+  c->g_rows_cap = rows_cap;
+  c->g_width = width;
+  for (int r = 0; r < c->table.tp; ++r) {
+    c->g_buf[r] = reinterpret_cast<__half*>(buf_ptrs[r]);
+    c->g_flags[r] = reinterpret_cast<uint32_t*>(flag_ptrs[r]);
+  }
+  return 0;
+}
+
+static int fill_gather_args(const zse_tp_ctx* c, TpGatherArgs& a, int ld, int M, int slot, void* status) {
+  if (c == nullptr || c->g_buf[0] == nullptr || M <= 0 || M > c->g_rows_cap || ld % 8 || ld < c->g_width)
+    return ZSE_ERR_SHAPE;
+  for (int r = 0; r < c->table.tp; ++r) {
+    a.buf[r] = c->g_buf[r];
+    a.flags[r] = c->g_flags[r];
+  }
+  a.ld = ld;
+  a.W = c->g_width;
+  a.tp = c->table.tp;
+  a.rows_cap = c->g_rows_cap;
+  a.slot = slot & 1;
+  a.status = reinterpret_cast<Status*>(status);
+  return 0;
+}
+
+// After the launch, rows [0, M) of slot `slot` of this rank's gathered buffer hold the logits of all ranks
+// (columns r * width .. (r + 1) * width from rank r).
+extern "C" int zse_tp_gather_rows(void* ctx, const void* logits, int ld, int M, int slot, void* status, void* stream) {
+  zse_tp_ctx* c = reinterpret_cast<zse_tp_ctx*>(ctx);
+  TpGatherArgs a{};
+  if (int rc = fill_gather_args(c, a, ld, M, slot, status)) return rc;
+  if (reinterpret_cast<uintptr_t>(logits) & 15) return ZSE_ERR_ALIGN;
+  a.src[0] = reinterpret_cast<const __half*>(logits);
+  a.rank[0] = c->rank;
+  tp_gather_rows_kernel<<<dim3(M, 1), 512, 0, reinterpret_cast<cudaStream_t>(stream)>>>(a);
+  return cudaGetLastError() == cudaSuccess ? 0 : ZSE_ERR_LAUNCH;
+}
+
+// All ranks of a single-GPU test in one cooperative launch (blockIdx.y = rank): every CTA is resident, so the waits
+// between the emulated ranks are waits inside one kernel.
+extern "C" int zse_tp_gather_rows_emulated(void* ctx, const uint64_t* logits, int ld, int M, int slot, void* status,
+                                           void* stream) {
+  zse_tp_ctx* c = reinterpret_cast<zse_tp_ctx*>(ctx);
+  TpGatherArgs a{};
+  if (int rc = fill_gather_args(c, a, ld, M, slot, status)) return rc;
+  for (int r = 0; r < c->table.tp; ++r) {
+    a.src[r] = reinterpret_cast<const __half*>(logits[r]);
+    a.rank[r] = r;
+  }
+  void* params[] = {&a};
+  return cudaLaunchCooperativeKernel((const void*)tp_gather_rows_kernel, dim3(M, c->table.tp), dim3(512), params, 0,
+                                     reinterpret_cast<cudaStream_t>(stream)) == cudaSuccess
+             ? 0
+             : ZSE_ERR_LAUNCH;
 }
 
 // Programmatic dependent launch for the reduce kernels: off unless ZSE_TP_PDL=1.  Measured on 2 GPUs: a reduce kernel

@@ -58,21 +58,31 @@ def main():
         dist.barrier()
     # sampling without a seed: the default seed must not depend on the process, or the ranks pick different tokens
     os.environ["ZSE_TP_PUSH"], os.environ["ZSE_TP_FUSED_K1"], os.environ["ZSE_TP_FUSED_SP_ROWS"] = "0", "1", "128"
-    cfg = EngineConfig(tp_size=world, device_index=local, max_seq_len=512, max_batch_seqs=8, max_batch_tokens=1024,
-                       prefill_chunk_size=512, quiet=True, comm_backend="fused")
-    comm = make_comm("fused", rank, world, dev, hidden_size=synth.SHAPES[shape]["hidden_size"],
-                     max_tokens=cfg.max_batch_tokens)
-    eng = ZStreamerEngine(path, config=cfg, comm=comm, tp_rank=rank)
-    ids = [eng.add_request_tokens(p, max_tokens=10, temperature=0.9, top_k=40, stop_tokens=[], request_id=f"s{i}")
-           for i, p in enumerate(prompts)]
-    eng.run_until_done()
-    sampled = [eng.get_result(i).output_tokens for i in ids]
-    eng.destroy()
-    torch.cuda.synchronize()
-    dist.barrier()
-    gathered_s = [None] * world
-    dist.all_gather_object(gathered_s, sampled)
-    assert all(g == gathered_s[0] for g in gathered_s), "ranks sampled different tokens"
+    # ... and the logits reach every rank either through the peer-store gather kernel or through ncclAllGather: with the
+    # same seeds both must sample the same tokens
+    by_gather = {}
+    for fused_gather in ("1", "0"):
+        os.environ["ZSE_TP_FUSED_GATHER"] = fused_gather
+        cfg = EngineConfig(tp_size=world, device_index=local, max_seq_len=512, max_batch_seqs=8, max_batch_tokens=1024,
+                           prefill_chunk_size=512, quiet=True, comm_backend="fused")
+        comm = make_comm("fused", rank, world, dev, hidden_size=synth.SHAPES[shape]["hidden_size"],
+                         max_tokens=cfg.max_batch_tokens)
+        eng = ZStreamerEngine(path, config=cfg, comm=comm, tp_rank=rank)
+        ids = [eng.add_request_tokens(p, max_tokens=10, temperature=0.9, top_k=40, stop_tokens=[], request_id=f"s{i}")
+               for i, p in enumerate(prompts)]
+        eng.run_until_done()
+        sampled = [eng.get_result(i).output_tokens for i in ids]
+        used_kernel = getattr(comm, "_gbuf", None) is not None
+        eng.destroy()
+        torch.cuda.synchronize()
+        dist.barrier()
+        gathered_s = [None] * world
+        dist.all_gather_object(gathered_s, sampled)
+        assert all(g == gathered_s[0] for g in gathered_s), "ranks sampled different tokens"
+        by_gather[fused_gather] = (sampled, used_kernel)
+    vocab_even = vocab % world == 0 and (vocab // world) % 8 == 0
+    assert by_gather["1"][1] == vocab_even and not by_gather["0"][1]
+    assert by_gather["1"][0] == by_gather["0"][0], "the gather kernel and ncclAllGather lead to different samples"
     same_fused = sum(a == b for a, b in zip(results["fused"], results["single"]))
     same_nccl = sum(a == b for a, b in zip(results["nccl"], results["single"]))
     same_push = sum(a == b for a, b in zip(results["push"], results["single"]))

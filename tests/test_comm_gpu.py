@@ -318,6 +318,33 @@ def _rel_close(a, b, tol=4e-3):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("tp,M,W", [(2, 5, 512), (4, 64, 1000), (8, 33, 19008)])
+def test_logits_all_gather_emulated_ranks(tp, M, W):
+    """Every emulated rank stores its vocabulary shard of the logits rows into every rank's buffer and waits for the
+    others (one cooperative launch plays all ranks): all ranks end with the concatenation, call after call."""
+    from zse_b200.ops import native
+    ctx, keep = _emulated_ctx(tp, 64, 1024)
+    rows_cap = 64
+    bufs = [torch.zeros(2 * rows_cap * tp * W, dtype=torch.float16, device="cuda") for _ in range(tp)]
+    flags = [torch.zeros(2 * tp * rows_cap, dtype=torch.int32, device="cuda") for _ in range(tp)]
+    native.tp_ctx_set_gather(ctx, rows_cap, W, [t.data_ptr() for t in bufs], [t.data_ptr() for t in flags])
+    status = native.Status("cuda")
+    for call in range(3):
+        slot = call & 1
+        ld = W + 8 * (call + 1)                                  # rows of the local logits may be padded
+        shards = [torch.randn(M, ld, device="cuda").half() for _ in range(tp)]
+        native.tp_gather_rows_emulated(ctx, shards, ld, M, slot, status.ptr)
+        torch.cuda.synchronize()
+        status.check()
+        want = torch.cat([t[:, :W] for t in shards], dim=1)
+        for r in range(tp):
+            got = bufs[r].view(2, rows_cap, tp * W)[slot, :M]
+            assert torch.equal(got, want), (call, r)
+        assert all(int(f.abs().sum()) == 0 for f in flags)       # every flag was taken down again
+    native.tp_ctx_destroy(ctx)
+
+
+@pytest.mark.gpu
 def test_tp_argmax_emulated_ranks():
     from zse_b200.ops import native
     tp, M, V_local = 4, 6, 1000

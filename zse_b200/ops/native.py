@@ -131,6 +131,9 @@ _SIGS = {
     "zse_tp_sp_wait": (c_int, [c_void_p, c_int, c_int, c_void_p, c_void_p]),
     "zse_tp_sum_add_rmsnorm_emulated": (c_int, [c_void_p, POINTER(c_uint64), c_void_p, POINTER(c_uint64), c_int,
                                                 c_float, c_int, c_int, c_void_p, c_void_p]),
+    "zse_tp_ctx_set_gather": (c_int, [c_void_p, c_int, c_int, POINTER(c_uint64), POINTER(c_uint64)]),
+    "zse_tp_gather_rows": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
+    "zse_tp_gather_rows_emulated": (c_int, [c_void_p, POINTER(c_uint64), c_int, c_int, c_int, c_void_p, c_void_p]),
     "zse_tp_argmax": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
     "zse_tp_argmax_emulated": (c_int, [c_void_p, POINTER(c_uint64), c_int, POINTER(c_uint64), c_int, c_int, c_int,
                                        c_int, c_void_p, c_void_p]),
@@ -534,6 +537,20 @@ def tp_sum_add_rmsnorm_emulated(ctx, residuals, weight, outs, M, eps, slot, expe
     _ck(load().zse_tp_sum_add_rmsnorm_emulated(ctx, _u64s([t.data_ptr() for t in residuals]), _p(weight),
                                                _u64s([t.data_ptr() for t in outs]), M, eps, slot, expected_add,
                                                status, _stream()), "tp_sum_add_rmsnorm_emulated")
+
+
+def tp_ctx_set_gather(ctx, rows_cap, width, buf_ptrs, flag_ptrs):
+    _ck(load().zse_tp_ctx_set_gather(ctx, rows_cap, width, _u64s(buf_ptrs), _u64s(flag_ptrs)), "tp_ctx_set_gather", 0)
+
+
+def tp_gather_rows(ctx, logits, ld, M, slot, status):
+    """All-gather of vocabulary-sharded logits rows into this rank's symmetric buffer (csrc/comm.cu)."""
+    _ck(load().zse_tp_gather_rows(ctx, _p(logits), ld, M, slot, status, _stream()), "tp_gather_rows")
+
+
+def tp_gather_rows_emulated(ctx, logits, ld, M, slot, status):
+    _ck(load().zse_tp_gather_rows_emulated(ctx, _u64s([t.data_ptr() for t in logits]), ld, M, slot, status, _stream()),
+        "tp_gather_rows_emulated")
 
 
 def tp_argmax(ctx, logits, ld, out, M, V_local, vocab_stride, slot, status):

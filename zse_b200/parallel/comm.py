@@ -374,6 +374,41 @@ class FusedComm(NcclComm):
                           bounds[1][0] - bounds[0][0] if self.world > 1 else plan.vocab_size, 0,
                           runner.model.ops.status.ptr)
 
+    def gather_logits(self, runner, n_rows: int) -> torch.Tensor:
+        """Full-vocabulary logits rows on every rank without a library call: every rank stores its shard into every
+        rank's symmetric buffer and waits for the others (csrc/comm.cu, tp_gather_rows_kernel).  Needs equally wide
+        shards (a multiple of 8 columns); anything else takes the NCCL path of the base class."""
+        b, plan = runner.buf, runner.model.plan
+        vocab, W = runner.model.config.vocab_size, plan.vocab_size
+        if W * self.world != vocab or W % 8 or b.logits.stride(0) % 8 or not env.flag("ZSE_TP_FUSED_GATHER"):
+            return super().gather_logits(runner, n_rows)
+        if getattr(self, "_gbuf", None) is None:
+            if torch.cuda.is_current_stream_capturing():     # set-up is a collective: never inside a capture
+                return super().gather_logits(runner, n_rows)
+            self._init_gather(b.logits.shape[0], W)
+        if n_rows > self._g_rows:
+            return super().gather_logits(runner, n_rows)
+        slot = self._g_calls & 1
+        self._n.tp_gather_rows(self._ctx, b.logits, b.logits.stride(0), n_rows, slot, runner.model.ops.status.ptr)
+        self._g_calls += 1
+        return self._g_view[slot][:n_rows]
+
+    def _init_gather(self, rows_cap: int, width: int) -> None:
+        import torch.distributed._symmetric_memory as symm
+        grp = self.group or dist.group.WORLD
+        align = lambda n: (n + 255) // 256 * 256
+        data = 2 * rows_cap * self.world * width * 2
+        total = align(data) + align(2 * self.world * rows_cap * 4)
+        self._gbuf = symm.empty(total, dtype=torch.uint8, device=self.device)
+        self._gbuf.zero_()
+        self._ghdl = symm.rendezvous(self._gbuf, grp)
+        torch.cuda.synchronize(self.device)
+        dist.barrier(group=grp)
+        ptrs = [int(p) for p in self._ghdl.buffer_ptrs]
+        self._n.tp_ctx_set_gather(self._ctx, rows_cap, width, ptrs, [p + align(data) for p in ptrs])
+        self._g_rows, self._g_calls = rows_cap, 0
+        self._g_view = self._gbuf[:data].view(torch.float16).view(2, rows_cap, self.world * width)
+
     def close(self) -> None:
         if self._ctx:
             self._n.tp_ctx_destroy(self._ctx)

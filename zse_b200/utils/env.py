@@ -24,6 +24,8 @@ KNOWN: Dict[str, Tuple[str, str]] = {
     "ZSE_TP_FUSED_K1": ("0", "decode-sized passes: row-parallel GEMM + all-reduce + residual + RMSNorm as ONE kernel "
                              "(1) or as GEMM + one exchange kernel (0, the default: measured faster on 2, 4 and 8 "
                              "GPUs)"),
+    "ZSE_TP_FUSED_GATHER": ("1", "fused collectives: sampling with temperature gathers the vocabulary shards of the logits "
+                                 "with peer stores instead of ncclAllGather"),
     "ZSE_TP_TWO_SHOT_ROWS": (str(1 << 30), "passes of at least this many rows take the two-shot reduce-scatter kernel"),
     "ZSE_TP_NCCL_ROWS": ("256", "passes of at least this many rows take NCCL instead of the fused exchange"),
     "ZSE_TP_FUSED_SP_ROWS": ("128", "fused collectives: passes of at least this many rows scatter the row-parallel GEMM's "
