@@ -323,7 +323,10 @@ class FusedComm(NcclComm):
         self.k1_calls += 1
 
     def can_push(self, w, M: int) -> bool:
-        return self._push_ready and w.kind == "w4t" and M <= self.push_rows and w.N == self.H and w.bias is None
+        # the older exchange in the epilogue of the tiled GEMM (ZSE_TP_PUSH=1) is validated on two and four ranks; on
+        # eight it produced wrong tokens (cause not found), and the decode kernel's own exchange replaces it there
+        return (self._push_ready and self.world <= 4 and w.kind == "w4t" and M <= self.push_rows and w.N == self.H
+                and w.bias is None)
 
     def linear_push(self, ops, w, x, M: int) -> int:
         """Row-parallel INT4 GEMM with the exchange in its epilogue; returns the CTA count for sum_add_rmsnorm."""
