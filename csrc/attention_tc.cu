@@ -215,6 +215,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
       if (!__all_sync(0xffffffffu, mbar_wait(&bars->s_full, ph, abort_flag, a.status, 47, t))) { ok = false; break; }
       tc_fence_after_sync();
       const int k0 = t * kTcKv;
+      // which 16-key groups of the tile exist: a block table entry < 0 is a hole (a block the cache has dropped); its
+      // keys were not loaded and must not be seen.  Chunk c of the loops below is exactly group c.
+      uint32_t groups = 0;
+#pragma unroll
+      for (int g = 0; g < 8; ++g) {
+        const int tok = k0 + g * 16;
+        if (tok < kv_len && my_bt[tok / a.block_size] >= 0) groups |= 1u << g;
+      }
       // pass 1: row maximum of the visible scores
       float mx = -INFINITY;
 #pragma unroll 1
@@ -222,9 +230,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
         uint32_t v[16];
         ZSE_TMEM_LD_X16(v, tm_s + lane_addr + c * 16);
         tc_wait_ld();
+        if ((groups >> c) & 1u) {
 #pragma unroll
-        for (int i = 0; i < 16; ++i)
-          if (k0 + c * 16 + i <= limit) mx = fmaxf(mx, __uint_as_float(v[i]));
+          for (int i = 0; i < 16; ++i)
+            if (k0 + c * 16 + i <= limit) mx = fmaxf(mx, __uint_as_float(v[i]));
+        }
       }
       mx *= a.scale_log2;                              // scale > 0: the maximum commutes with it
       // move the reference maximum only when some row of the warp needs it (tcgen05.ld/st are warp-wide)
@@ -257,11 +267,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
         ZSE_TMEM_LD_X16(v, tm_s + lane_addr + c * 16);
         tc_wait_ld();
         uint32_t pk[8];
+        const int lim_c = ((groups >> c) & 1u) ? limit : -1;          // a hole: no key of this chunk is visible
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
           const int k = k0 + c * 16 + 2 * i;
-          const float p0 = k <= limit ? exp2f(__uint_as_float(v[2 * i]) * a.scale_log2 - m_ref) : 0.f;
-          const float p1 = k + 1 <= limit ? exp2f(__uint_as_float(v[2 * i + 1]) * a.scale_log2 - m_ref) : 0.f;
+          const float p0 = k <= lim_c ? exp2f(__uint_as_float(v[2 * i]) * a.scale_log2 - m_ref) : 0.f;
+          const float p1 = k + 1 <= lim_c ? exp2f(__uint_as_float(v[2 * i + 1]) * a.scale_log2 - m_ref) : 0.f;
           psum += p0 + p1;
           pk[i] = pack_half2(p0, p1);
         }
