@@ -71,7 +71,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
   uint8_t* v_s = smem + 2 * kTcTileBytes;
   TcBars* bars = reinterpret_cast<TcBars*>(smem + 3 * kTcTileBytes);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int qt = blockIdx.x, head = blockIdx.y, seq = blockIdx.z;
+  // the last query tile of a chunk sees the most keys: hand the heavy tiles out first, so that the light ones fill
+  // the tail of the grid (causal work per tile grows linearly with its index)
+  const int qt = int(gridDim.x) - 1 - int(blockIdx.x), head = blockIdx.y, seq = blockIdx.z;
   pdl_launch_dependents();
   const int q_begin = a.cu_q[seq], q_len = a.cu_q[seq + 1] - q_begin;
   if (qt * kTcRows >= q_len) return;                     // before any barrier or TMEM use: the whole CTA leaves

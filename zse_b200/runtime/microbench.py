@@ -113,6 +113,28 @@ def main():
         inv = ref.inv_freq(hd, c.rope_theta).cuda()
         run("rope_kv_write", lambda: ops.rope_kv_write(qkv, kv, pos, slots, inv, M, nh, nkv, hd, bs),
             M * (q_dim + 2 * kv_dim) * 2 * 2)
+    # chunked-prefill attention: sequences of 2048 tokens (or one shorter one), causal, from position 0
+    if want("attn_prefill_tc", "attn_prefill_mma") and hd == 128:
+        from ..ops import native as _native
+        q_len = min(M, 2048)
+        n_seq = max(1, M // q_len)
+        pbs = 16
+        nb = (q_len + pbs - 1) // pbs
+        kvp = (torch.randn(n_seq * nb + 1, 2, nkv, pbs, hd, device="cuda") * 0.3).half()
+        btp = torch.randperm(n_seq * nb, device="cuda").int().view(n_seq, nb).contiguous()
+        cu = torch.arange(0, (n_seq + 1) * q_len, q_len, dtype=torch.int32, device="cuda")
+        p0 = torch.zeros(n_seq, dtype=torch.int32, device="cuda")
+        total = n_seq * q_len
+        qp = (torch.randn(total, q_dim + 2 * kv_dim, device="cuda") * 0.5).half()
+        op = torch.zeros(total, q_dim, dtype=torch.float16, device="cuda")
+        causal_flops = 4 * hd * nh * n_seq * (q_len * (q_len + 1) // 2)
+        kv_bytes = n_seq * q_len * nkv * hd * 2 * 2 + total * q_dim * 2 * 2
+        run("attn_prefill_tc",
+            lambda: _native.attn_prefill_tc(qp, qp.stride(0), total, kvp, btp, cu, p0, op, op.stride(0), n_seq, q_len, nh,
+                                            nkv, hd, pbs, 1 / math.sqrt(hd), ops.status.ptr), kv_bytes, causal_flops)
+        run("attn_prefill_mma",
+            lambda: _native.attn_prefill_ext(qp, qp.stride(0), kvp, btp, cu, p0, op, op.stride(0), n_seq, q_len, nh, nkv,
+                                             hd, pbs, 1 / math.sqrt(hd)), kv_bytes, causal_flops)
     # batched LoRA: every token routed to one of 32 rank-16 adapters on a q_proj-sized projection
     if want("lora_apply"):
         n_ad, r_lora = 32, 16
