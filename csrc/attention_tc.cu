@@ -13,7 +13,9 @@
 // TMEM per CTA: 128 columns S / P + 128 columns O; shared memory: Q, one K and one V tile (96 KB); two CTAs share an
 // SM, so one CTA's softmax overlaps the other's MMAs.  K is released as soon as S is complete and V as soon as the
 // P V product is, so the next tile's loads run under the current tile's softmax.
-// Every wait is bounded and reports through the status word; on a failure the CTA frees its TMEM and leaves.
+// Every wait is bounded and reports through the status word; on a failure the CTA frees its TMEM and leaves.  The waits
+// of the per-tile chain (MMA issuer and softmax threads) poll without the suspend hint: a suspended thread wakes up
+// microseconds after its barrier flips, and a tile passes four such hand-overs.
 //
 // Replaces the reference's flash_attention_prefill kernel (zse-engine/zse_engine/orchestrator/kernels.py:859-957) for
 // the shapes it covers; attention.cu::attn_prefill_kernel (mma.sync) keeps the rest (other head sizes, soft-capped
@@ -60,6 +62,26 @@ __device__ __forceinline__ uint64_t make_desc_sw128_mn(uint32_t smem_addr, uint3
   d |= uint64_t(2) << 61;                              // SWIZZLE_128B
   return d;
 }
+
+
+// 64 consecutive 32-bit columns of the thread's TMEM lane in one instruction (the loads of a tile are few and wide:
+// a tcgen05.ld + wait::ld round trip costs several hundred cycles whatever its width).
+#define ZSE_TMEM_LD_X64(r, taddr)                                                                                  \
+  asm volatile(                                                                                                    \
+      "tcgen05.ld.sync.aligned.32x32b.x64.b32 "                                                                    \
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31," \
+      "%32,%33,%34,%35,%36,%37,%38,%39,%40,%41,%42,%43,%44,%45,%46,%47,%48,%49,%50,%51,%52,%53,%54,%55,%56,%57,%58,%59,%60,%61," \
+      "%62,%63}, [%64];"                                                                                           \
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),    \
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),       \
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),      \
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]), "=r"(r[32]),      \
+        "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]), "=r"(r[40]),      \
+        "=r"(r[41]), "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]), "=r"(r[48]),      \
+        "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]), "=r"(r[56]),      \
+        "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]), "=r"(r[63])                     \
+      : "r"(taddr)                                                                                                 \
+      : "memory")
 
 __global__ void __launch_bounds__(kTcThreads, 2)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_kv,
@@ -172,13 +194,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
       // V [keys][head_dim] as the MN-major B operand: 64 head_dim elements per 128-byte row, eight keys per 1024 bytes,
       // the second half of head_dim 16 KB further on
       const uint32_t mn64 = uint32_t(kTcTileBytes / 2), k8 = 1024u;
-      bool ok = mbar_wait(&bars->q_full, 0, abort_flag, a.status, 43, 0);
+      bool ok = mbar_wait_spin(&bars->q_full, 0, abort_flag, a.status, 43, 0);
       uint32_t ph = 0;
       for (int t = 0; t < n_tiles && ok; ++t) {
-        if (!mbar_wait(&bars->k_full, ph, abort_flag, a.status, 44, t)) break;
+        if (!mbar_wait_spin(&bars->k_full, ph, abort_flag, a.status, 44, t)) break;
         // the probabilities of the previous tile live in the columns this product overwrites: let P V finish reading
         // them first (v_empty of tile t-1 is committed behind that product)
-        if (t > 0 && !mbar_wait(&bars->v_empty, ph ^ 1, abort_flag, a.status, 49, t)) break;
+        if (t > 0 && !mbar_wait_spin(&bars->v_empty, ph ^ 1, abort_flag, a.status, 49, t)) break;
         tc_fence_after_sync();
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
@@ -187,8 +209,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
         }
         tc_commit(&bars->s_full);                     // S complete (and every earlier MMA, i.e. the previous P V)
         tc_commit(&bars->k_empty);
-        if (!mbar_wait(&bars->v_full, ph, abort_flag, a.status, 45, t)) break;
-        if (!mbar_wait(&bars->p_full, ph, abort_flag, a.status, 46, t)) break;
+        if (!mbar_wait_spin(&bars->v_full, ph, abort_flag, a.status, 45, t)) break;
+        if (!mbar_wait_spin(&bars->p_full, ph, abort_flag, a.status, 46, t)) break;
         tc_fence_after_sync();
 #pragma unroll
         for (int j = 0; j < 8; ++j) {                 // 16 keys per step: two groups of eight cache rows
@@ -213,29 +235,41 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     uint32_t ph = 0;
     bool ok = true;
     for (int t = 0; t < n_tiles; ++t) {
-      // one verdict per warp: the tcgen05.ld / st below are warp-wide
-      if (!__all_sync(0xffffffffu, mbar_wait(&bars->s_full, ph, abort_flag, a.status, 47, t))) { ok = false; break; }
-      tc_fence_after_sync();
       const int k0 = t * kTcKv;
       // which 16-key groups of the tile exist: a block table entry < 0 is a hole (a block the cache has dropped); its
-      // keys were not loaded and must not be seen.  Chunk c of the loops below is exactly group c.
-      uint32_t groups = 0;
-#pragma unroll
-      for (int g = 0; g < 8; ++g) {
-        const int tok = k0 + g * 16;
-        if (tok < kv_len && my_bt[tok / a.block_size] >= 0) groups |= 1u << g;
-      }
-      // pass 1: row maximum of the visible scores
+      // keys were not loaded and must not be seen.  Looked up while S is still being computed.
+      const int g_tok = k0 + (lane & 7) * 16;         // lanes 0..7 look one group up each
+      const uint32_t groups =
+          __ballot_sync(0xffffffffu, g_tok < kv_len && my_bt[g_tok / a.block_size] >= 0) & 0xFFu;
+      // one verdict per warp: the tcgen05.ld / st below are warp-wide
+      if (!__all_sync(0xffffffffu, mbar_wait_spin(&bars->s_full, ph, abort_flag, a.status, 47, t))) { ok = false; break; }
+      tc_fence_after_sync();
+      // Most tiles lie entirely below the diagonal and have no holes: every row of the warp sees every key, and the
+      // per-element masking (a third of the instructions of this loop) is skipped.
+      const bool full = __all_sync(0xffffffffu, groups == 0xFFu && k0 + kTcKv - 1 <= limit);
+      // pass 1: row maximum of the visible scores (two loads of 64 columns)
       float mx = -INFINITY;
 #pragma unroll 1
-      for (int c = 0; c < 8; ++c) {
-        uint32_t v[16];
-        ZSE_TMEM_LD_X16(v, tm_s + lane_addr + c * 16);
+      for (int h = 0; h < 2; ++h) {
+        uint32_t v[64];
+        ZSE_TMEM_LD_X64(v, tm_s + lane_addr + h * 64);
         tc_wait_ld();
-        if ((groups >> c) & 1u) {
+        if (full) {
+          float m0 = mx, m1 = -INFINITY, m2 = -INFINITY, m3 = -INFINITY;      // four chains instead of one
 #pragma unroll
-          for (int i = 0; i < 16; ++i)
-            if (k0 + c * 16 + i <= limit) mx = fmaxf(mx, __uint_as_float(v[i]));
+          for (int i = 0; i < 64; i += 4) {
+            m0 = fmaxf(m0, __uint_as_float(v[i]));
+            m1 = fmaxf(m1, __uint_as_float(v[i + 1]));
+            m2 = fmaxf(m2, __uint_as_float(v[i + 2]));
+            m3 = fmaxf(m3, __uint_as_float(v[i + 3]));
+          }
+          mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+        } else {
+#pragma unroll
+          for (int i = 0; i < 64; ++i) {
+            const bool seen = ((groups >> (h * 4 + (i >> 4))) & 1u) && (k0 + h * 64 + i <= limit);
+            mx = seen ? fmaxf(mx, __uint_as_float(v[i])) : mx;
+          }
         }
       }
       mx *= a.scale_log2;                              // scale > 0: the maximum commutes with it
@@ -247,13 +281,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
         if (t > 0) {
           // s_full of this tile means every earlier MMA has completed, the previous P V included: O is stable
 #pragma unroll 1
-          for (int c = 0; c < 8; ++c) {
-            uint32_t o[16];
-            ZSE_TMEM_LD_X16(o, tm_o + lane_addr + c * 16);
+          for (int h = 0; h < 2; ++h) {
+            uint32_t o[64];
+            ZSE_TMEM_LD_X64(o, tm_o + lane_addr + h * 64);
             tc_wait_ld();
 #pragma unroll
-            for (int i = 0; i < 16; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-            ZSE_TMEM_ST_X16(tm_o + lane_addr + c * 16, o);
+            for (int i = 0; i < 64; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            ZSE_TMEM_ST_X32(tm_o + lane_addr + h * 64, o);
+            ZSE_TMEM_ST_X32(tm_o + lane_addr + h * 64 + 32, (o + 32));
           }
           tc_wait_st();
         }
@@ -264,24 +299,36 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
       const float m_ref = (m_used == -INFINITY) ? 0.f : m_used;
       float psum = 0.f;
 #pragma unroll 1
-      for (int c = 0; c < 8; ++c) {
-        uint32_t v[16];
-        ZSE_TMEM_LD_X16(v, tm_s + lane_addr + c * 16);
+      for (int h = 0; h < 2; ++h) {
+        uint32_t v[64];
+        ZSE_TMEM_LD_X64(v, tm_s + lane_addr + h * 64);
         tc_wait_ld();
-        uint32_t pk[8];
-        const int lim_c = ((groups >> c) & 1u) ? limit : -1;          // a hole: no key of this chunk is visible
+        uint32_t pk[32];
+        if (full) {
+          float s0 = 0.f, s1 = 0.f;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          const int k = k0 + c * 16 + 2 * i;
-          const float p0 = k <= lim_c ? exp2f(__uint_as_float(v[2 * i]) * a.scale_log2 - m_ref) : 0.f;
-          const float p1 = k + 1 <= lim_c ? exp2f(__uint_as_float(v[2 * i + 1]) * a.scale_log2 - m_ref) : 0.f;
-          psum += p0 + p1;
-          pk[i] = pack_half2(p0, p1);
+          for (int i = 0; i < 32; ++i) {
+            const float p0 = exp2f(fmaf(__uint_as_float(v[2 * i]), a.scale_log2, -m_ref));
+            const float p1 = exp2f(fmaf(__uint_as_float(v[2 * i + 1]), a.scale_log2, -m_ref));
+            s0 += p0;
+            s1 += p1;
+            pk[i] = pack_half2(p0, p1);
+          }
+          psum += s0 + s1;
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            // a hole: no key of its 16-key group is visible
+            const int lim_g = ((groups >> (h * 4 + (i >> 3))) & 1u) ? limit : -1;
+            const int k = k0 + h * 64 + 2 * i;
+            const float p0 = k <= lim_g ? exp2f(__uint_as_float(v[2 * i]) * a.scale_log2 - m_ref) : 0.f;
+            const float p1 = k + 1 <= lim_g ? exp2f(__uint_as_float(v[2 * i + 1]) * a.scale_log2 - m_ref) : 0.f;
+            psum += p0 + p1;
+            pk[i] = pack_half2(p0, p1);
+          }
         }
-        // P columns c*8 .. c*8+7 lie under score columns that this pass has already read
-        asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"r"(tm_p + lane_addr + c * 8),
-                     "r"(pk[0]), "r"(pk[1]), "r"(pk[2]), "r"(pk[3]), "r"(pk[4]), "r"(pk[5]), "r"(pk[6]), "r"(pk[7])
-                     : "memory");
+        // P columns h*32 .. h*32+31 lie under score columns that this pass has already read
+        ZSE_TMEM_ST_X32(tm_p + lane_addr + h * 32, pk);
       }
       l += psum;
       tc_wait_st();
@@ -290,7 +337,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
       ph ^= 1;
     }
     // ---- epilogue: O / l -> fp16 rows
-    if (ok) ok = __all_sync(0xffffffffu, mbar_wait(&bars->o_full, 0, abort_flag, a.status, 48, 0));
+    if (ok) ok = __all_sync(0xffffffffu, mbar_wait_spin(&bars->o_full, 0, abort_flag, a.status, 48, 0));
     tc_fence_after_sync();
     if (ok) {
       // every lane takes part in the warp-wide tcgen05.ld (rows past the chunk included); only the stores are per row
@@ -298,22 +345,20 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
       const float inv = l > 0.f ? 1.f / l : 0.f;
       __half* dst = a.out + size_t(q_begin + (live ? row : 0)) * a.ldo + size_t(live ? out_head : 0) * kTcHd;
 #pragma unroll 1
-      for (int c = 0; c < 8; ++c) {
-        uint32_t o[16];
-        ZSE_TMEM_LD_X16(o, tm_o + lane_addr + c * 16);
+      for (int h = 0; h < 2; ++h) {
+        uint32_t o[64];
+        ZSE_TMEM_LD_X64(o, tm_o + lane_addr + h * 64);
         tc_wait_ld();
-        uint4 w0, w1;
-        w0.x = pack_half2(__uint_as_float(o[0]) * inv, __uint_as_float(o[1]) * inv);
-        w0.y = pack_half2(__uint_as_float(o[2]) * inv, __uint_as_float(o[3]) * inv);
-        w0.z = pack_half2(__uint_as_float(o[4]) * inv, __uint_as_float(o[5]) * inv);
-        w0.w = pack_half2(__uint_as_float(o[6]) * inv, __uint_as_float(o[7]) * inv);
-        w1.x = pack_half2(__uint_as_float(o[8]) * inv, __uint_as_float(o[9]) * inv);
-        w1.y = pack_half2(__uint_as_float(o[10]) * inv, __uint_as_float(o[11]) * inv);
-        w1.z = pack_half2(__uint_as_float(o[12]) * inv, __uint_as_float(o[13]) * inv);
-        w1.w = pack_half2(__uint_as_float(o[14]) * inv, __uint_as_float(o[15]) * inv);
         if (live) {
-          *reinterpret_cast<uint4*>(dst + c * 16) = w0;
-          *reinterpret_cast<uint4*>(dst + c * 16 + 8) = w1;
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            uint4 w;
+            w.x = pack_half2(__uint_as_float(o[8 * c]) * inv, __uint_as_float(o[8 * c + 1]) * inv);
+            w.y = pack_half2(__uint_as_float(o[8 * c + 2]) * inv, __uint_as_float(o[8 * c + 3]) * inv);
+            w.z = pack_half2(__uint_as_float(o[8 * c + 4]) * inv, __uint_as_float(o[8 * c + 5]) * inv);
+            w.w = pack_half2(__uint_as_float(o[8 * c + 6]) * inv, __uint_as_float(o[8 * c + 7]) * inv);
+            *reinterpret_cast<uint4*>(dst + h * 64 + c * 8) = w;
+          }
         }
       }
     }
