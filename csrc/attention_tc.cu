@@ -46,10 +46,23 @@ struct TcArgs {
   __half* out;
   int ldo, max_blocks, nh, nkv, block_size;
   float scale_log2;
+  int box_rows;             // cache rows per K/V load: 16, 32 or 64, the largest that divides the block size
   int packed;               // > 0: chunks of at most 16 rows; the CTA owns ONE kv head and packs the `packed` query
                             // heads that share it as 16-row slots of its 128 rows (keys and values read once per group)
   Status* status;
+  long long* timing;        // instrumented builds (ZSE_ATTN_TIMING): clock64() stamps of CTA (0, 0, 0), else unused
 };
+
+// Instrumented builds: stamp `slot` of key tile `t` (16 slots per tile, the first 24 tiles of the heaviest CTA).
+#ifdef ZSE_ATTN_TIMING
+#define ATIME(t, slot)                                                                                   \
+  do {                                                                                                   \
+    if (a.timing != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (t) < 24)       \
+      a.timing[(t) * 16 + (slot)] = clock64();                                                           \
+  } while (0)
+#else
+#define ATIME(t, slot)
+#endif
 
 // MN-major operand in shared memory, 128-byte swizzle: rows of the K dimension are 128 bytes (64 MN elements) long,
 // groups of eight K rows lie `k8_bytes` apart, the next 64 MN elements `mn64_bytes` apart.
@@ -66,6 +79,13 @@ __device__ __forceinline__ uint64_t make_desc_sw128_mn(uint32_t smem_addr, uint3
 
 // 64 consecutive 32-bit columns of the thread's TMEM lane in one instruction (the loads of a tile are few and wide:
 // a tcgen05.ld + wait::ld round trip costs several hundred cycles whatever its width).
+// 2^x on the special-function unit, one instruction (exp2f() adds range handling around it that softmax does not need)
+__device__ __forceinline__ float ex2_fast(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
 #define ZSE_TMEM_LD_X64(r, taddr)                                                                                  \
   asm volatile(                                                                                                    \
       "tcgen05.ld.sync.aligned.32x32b.x64.b32 "                                                                    \
@@ -137,9 +157,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
   volatile int* abort_flag = &bars->abort_flag;
 
   if (warp == 4) {
-    // ------------------------------------------------------------------ producer
+    // ------------------------------------------------------------------ producer (the whole warp)
+    // One thread issuing the 32 loads of a key tile (16 cache rows x 64 columns each) takes ~2.7 k cycles, and looking
+    // eight block-table entries up one after the other another ~3.5 k: more than the rest of the tile's chain.  So the
+    // warp shares the work: lane 2 g + half looks up group g of the NEXT tile while the current one is in flight, and
+    // issues one K and one V load; 16 loads leave in one warp-wide instruction.
+    pdl_wait();                                        // q and the cache rows of this chunk come from the previous kernels
     if (lane == 0) {
-      pdl_wait();                                      // q and the cache rows of this chunk come from the previous kernels
       if (G > 0) {
         // slot s = rows 16 s .. 16 s + 15 = the chunk's (at most 16) rows of query head kvh * G + s
         mbar_arrive_expect_tx(&bars->q_full, uint32_t(G) * 4096u);
@@ -154,35 +178,52 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
         tma_load_2d(q_s, &tmap_q, head * kTcHd, y, &bars->q_full);
         tma_load_2d(q_s + kTcTileBytes / 2, &tmap_q, head * kTcHd + 64, y, &bars->q_full);
       }
-      uint32_t ph = 1;                                 // "empty" barriers: the first wait passes
-      for (int t = 0; t < n_tiles; ++t) {
-        // which 16-token groups of this tile exist (the last tile may be short)
-        int rows[8];
-        int n_valid = 0;
-        for (int g = 0; g < 8; ++g) {
-          const int tok = t * kTcKv + g * 16;
-          int pb = -1;
-          if (tok < kv_len) pb = my_bt[tok / a.block_size];
-          rows[g] = pb >= 0 ? ((pb * 2) * a.nkv + kvh) * a.block_size + tok % a.block_size : -1;
-          n_valid += pb >= 0 ? 1 : 0;
-        }
-        const int v_off = a.nkv * a.block_size;        // rows between the K half and the V half of a block
-        if (!mbar_wait(&bars->k_empty, ph, abort_flag, a.status, 41, t)) break;
-        mbar_arrive_expect_tx(&bars->k_full, uint32_t(n_valid) * 4096u);
-        for (int g = 0; g < 8; ++g) {
-          if (rows[g] < 0) continue;
-          tma_load_2d(k_s + g * 2048, &tmap_kv, 0, rows[g], &bars->k_full);
-          tma_load_2d(k_s + kTcTileBytes / 2 + g * 2048, &tmap_kv, 64, rows[g], &bars->k_full);
-        }
-        if (!mbar_wait(&bars->v_empty, ph, abort_flag, a.status, 42, t)) break;
-        mbar_arrive_expect_tx(&bars->v_full, uint32_t(n_valid) * 4096u);
-        for (int g = 0; g < 8; ++g) {
-          if (rows[g] < 0) continue;
-          tma_load_2d(v_s + g * 2048, &tmap_kv, 0, rows[g] + v_off, &bars->v_full);
-          tma_load_2d(v_s + kTcTileBytes / 2 + g * 2048, &tmap_kv, 64, rows[g] + v_off, &bars->v_full);
-        }
-        ph ^= 1;
+    }
+    // a load covers `box_rows` consecutive tokens of one block (64 columns of them): 128 / box_rows groups per tile,
+    // two loads per group
+    const int br = a.box_rows, n_groups = kTcKv / br;
+    const int g = lane >> 1, half = lane & 1;          // lanes past 2 * n_groups issue nothing
+    const int v_off = a.nkv * a.block_size;            // rows between the K half and the V half of a block
+    const uint32_t box_bytes = uint32_t(br) * 128u;
+    // first cache row of group g of tile t (a hole or past the end: -1)
+    auto group_row = [&](int t) {
+      const int tok = t * kTcKv + g * br;
+      int pb = -1;
+      if (g < n_groups && t < n_tiles && tok < kv_len) pb = my_bt[tok / a.block_size];
+      return pb >= 0 ? ((pb * 2) * a.nkv + kvh) * a.block_size + tok % a.block_size : -1;
+    };
+    int row_next = group_row(0);
+    uint32_t ph = 1;                                   // "empty" barriers: the first wait passes
+    for (int t = 0; t < n_tiles; ++t) {
+      const int row0 = row_next;
+      const bool issue = row0 >= 0;
+      const uint32_t n_loads = __popc(__ballot_sync(0xffffffffu, issue));
+      row_next = group_row(t + 1);                     // in flight while this tile's loads are issued
+      bool ok = true;
+      if (lane == 0) ok = mbar_wait_spin(&bars->k_empty, ph, abort_flag, a.status, 41, t);
+      if (!__shfl_sync(0xffffffffu, ok, 0)) break;
+      if (lane == 0) {
+        ATIME(t, 10);
+        mbar_arrive_expect_tx(&bars->k_full, n_loads * box_bytes);
       }
+      __syncwarp();
+      if (issue) tma_load_2d(k_s + half * (kTcTileBytes / 2) + g * box_bytes, &tmap_kv, half * 64, row0, &bars->k_full);
+      __syncwarp();
+      if (lane == 0) {
+        ATIME(t, 11);
+        ok = mbar_wait_spin(&bars->v_empty, ph, abort_flag, a.status, 42, t);
+      }
+      if (!__shfl_sync(0xffffffffu, ok, 0)) break;
+      if (lane == 0) {
+        ATIME(t, 12);
+        mbar_arrive_expect_tx(&bars->v_full, n_loads * box_bytes);
+      }
+      __syncwarp();
+      if (issue)
+        tma_load_2d(v_s + half * (kTcTileBytes / 2) + g * box_bytes, &tmap_kv, half * 64, row0 + v_off, &bars->v_full);
+      __syncwarp();
+      if (lane == 0) ATIME(t, 13);
+      ph ^= 1;
     }
   } else if (warp == 5) {
     // ------------------------------------------------------------------ MMA issuer
@@ -198,9 +239,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
       uint32_t ph = 0;
       for (int t = 0; t < n_tiles && ok; ++t) {
         if (!mbar_wait_spin(&bars->k_full, ph, abort_flag, a.status, 44, t)) break;
+        ATIME(t, 0);
         // the probabilities of the previous tile live in the columns this product overwrites: let P V finish reading
         // them first (v_empty of tile t-1 is committed behind that product)
         if (t > 0 && !mbar_wait_spin(&bars->v_empty, ph ^ 1, abort_flag, a.status, 49, t)) break;
+        ATIME(t, 1);
         tc_fence_after_sync();
 #pragma unroll
         for (int j = 0; j < 8; ++j) {
@@ -209,8 +252,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
         }
         tc_commit(&bars->s_full);                     // S complete (and every earlier MMA, i.e. the previous P V)
         tc_commit(&bars->k_empty);
+        ATIME(t, 2);
         if (!mbar_wait_spin(&bars->v_full, ph, abort_flag, a.status, 45, t)) break;
+        ATIME(t, 3);
         if (!mbar_wait_spin(&bars->p_full, ph, abort_flag, a.status, 46, t)) break;
+        ATIME(t, 4);
         tc_fence_after_sync();
 #pragma unroll
         for (int j = 0; j < 8; ++j) {                 // 16 keys per step: two groups of eight cache rows
@@ -218,6 +264,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
           umma_ts(tm_o, tm_p + j * 8, v_desc, idesc_pv, (t != 0) || (j != 0));
         }
         tc_commit(&bars->v_empty);
+        ATIME(t, 5);
         if (t == n_tiles - 1) tc_commit(&bars->o_full);
         ph ^= 1;
       }
@@ -243,10 +290,48 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
           __ballot_sync(0xffffffffu, g_tok < kv_len && my_bt[g_tok / a.block_size] >= 0) & 0xFFu;
       // one verdict per warp: the tcgen05.ld / st below are warp-wide
       if (!__all_sync(0xffffffffu, mbar_wait_spin(&bars->s_full, ph, abort_flag, a.status, 47, t))) { ok = false; break; }
+      if (threadIdx.x == 0) ATIME(t, 6);
       tc_fence_after_sync();
       // Most tiles lie entirely below the diagonal and have no holes: every row of the warp sees every key, and the
       // per-element masking (a third of the instructions of this loop) is skipped.
       const bool full = __all_sync(0xffffffffu, groups == 0xFFu && k0 + kTcKv - 1 <= limit);
+      // One pass instead of two when the running maximum is likely to hold: probabilities are computed against the
+      // maximum in use while the new maximum is tracked; they are kept in registers, and stored only if no row of the
+      // warp outgrew its reference by more than 2^8 (else the scores, still intact in TMEM, go through the two passes).
+      if (full && __all_sync(0xffffffffu, m_used > -INFINITY)) {
+        uint32_t pk[64];
+        float s0 = 0.f, s1 = 0.f, x0 = -INFINITY, x1 = -INFINITY;
+#pragma unroll
+        for (int h = 0; h < 4; ++h) {                  // 32 columns at a time: 64 + 32 live registers
+          uint32_t v[32];
+          ZSE_TMEM_LD_X16(v, tm_s + lane_addr + h * 32);
+          ZSE_TMEM_LD_X16((v + 16), tm_s + lane_addr + h * 32 + 16);
+          tc_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 16; ++i) {
+            const float e0 = fmaf(__uint_as_float(v[2 * i]), a.scale_log2, -m_used);
+            const float e1 = fmaf(__uint_as_float(v[2 * i + 1]), a.scale_log2, -m_used);
+            x0 = fmaxf(x0, e0);
+            x1 = fmaxf(x1, e1);
+            const float p0 = ex2_fast(e0), p1 = ex2_fast(e1);
+            s0 += p0;
+            s1 += p1;
+            pk[h * 16 + i] = pack_half2(p0, p1);
+          }
+        }
+        if (!__any_sync(0xffffffffu, fmaxf(x0, x1) > 8.f)) {
+          ZSE_TMEM_ST_X32(tm_p + lane_addr, pk);
+          ZSE_TMEM_ST_X32(tm_p + lane_addr + 32, (pk + 32));
+          l += s0 + s1;
+          if (threadIdx.x == 0) ATIME(t, 7);
+          tc_wait_st();
+          tc_fence_before_sync();
+          mbar_arrive(&bars->p_full);
+          if (threadIdx.x == 0) ATIME(t, 8);
+          ph ^= 1;
+          continue;
+        }
+      }
       // pass 1: row maximum of the visible scores (two loads of 64 columns)
       float mx = -INFINITY;
 #pragma unroll 1
@@ -277,7 +362,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
       const bool grow = mx > m_used + 8.f;
       if (__any_sync(0xffffffffu, grow)) {
         const float m_new = fmaxf(m_used, mx);
-        const float alpha = (m_used == -INFINITY) ? 0.f : exp2f(m_used - m_new);
+        const float alpha = (m_used == -INFINITY) ? 0.f : ex2_fast(m_used - m_new);
         if (t > 0) {
           // s_full of this tile means every earlier MMA has completed, the previous P V included: O is stable
 #pragma unroll 1
@@ -308,8 +393,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
           float s0 = 0.f, s1 = 0.f;
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
-            const float p0 = exp2f(fmaf(__uint_as_float(v[2 * i]), a.scale_log2, -m_ref));
-            const float p1 = exp2f(fmaf(__uint_as_float(v[2 * i + 1]), a.scale_log2, -m_ref));
+            const float p0 = ex2_fast(fmaf(__uint_as_float(v[2 * i]), a.scale_log2, -m_ref));
+            const float p1 = ex2_fast(fmaf(__uint_as_float(v[2 * i + 1]), a.scale_log2, -m_ref));
             s0 += p0;
             s1 += p1;
             pk[i] = pack_half2(p0, p1);
@@ -321,8 +406,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
             // a hole: no key of its 16-key group is visible
             const int lim_g = ((groups >> (h * 4 + (i >> 3))) & 1u) ? limit : -1;
             const int k = k0 + h * 64 + 2 * i;
-            const float p0 = k <= lim_g ? exp2f(__uint_as_float(v[2 * i]) * a.scale_log2 - m_ref) : 0.f;
-            const float p1 = k + 1 <= lim_g ? exp2f(__uint_as_float(v[2 * i + 1]) * a.scale_log2 - m_ref) : 0.f;
+            const float p0 = k <= lim_g ? ex2_fast(__uint_as_float(v[2 * i]) * a.scale_log2 - m_ref) : 0.f;
+            const float p1 = k + 1 <= lim_g ? ex2_fast(__uint_as_float(v[2 * i + 1]) * a.scale_log2 - m_ref) : 0.f;
             psum += p0 + p1;
             pk[i] = pack_half2(p0, p1);
           }
@@ -331,9 +416,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
         ZSE_TMEM_ST_X32(tm_p + lane_addr + h * 32, pk);
       }
       l += psum;
+      if (threadIdx.x == 0) ATIME(t, 9);
       tc_wait_st();
       tc_fence_before_sync();
       mbar_arrive(&bars->p_full);
+      if (threadIdx.x == 0) ATIME(t, 8);
       ph ^= 1;
     }
     // ---- epilogue: O / l -> fp16 rows
@@ -372,6 +459,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
 
 using namespace zse;
 
+// Debug hook (only meaningful in builds with ZSE_ATTN_TIMING): device buffer of 24 x 16 cycle stamps.
+static long long* g_attn_tc_timing = nullptr;
+extern "C" void zse_attn_prefill_tc_set_timing(void* dev_buffer) {
+  g_attn_tc_timing = reinterpret_cast<long long*>(dev_buffer);
+}
+
 // out[q_begin + r, head * 128 ...] = softmax(q K^T * scale, causal) V for every sequence's chunk of query rows.
 //   q [total_rows, ldq] fp16 (head h at columns h * 128), kv_layer [num_blocks][2][nkv][block_size][128] fp16,
 //   block_tables [num_seqs][max_blocks], cu_q [num_seqs + 1], q_pos0 [num_seqs] (position of each chunk's first row).
@@ -394,7 +487,9 @@ extern "C" int zse_attn_prefill_tc(const void* q, int ldq, int total_rows, const
   // query heads, so keys and values are read once per group instead of once per query head
   const int group = nh / nkv;
   const int packed = (max_q_len <= 16 && group <= 8 && variant != 2) ? group : 0;
-  if (int rc = get_tmap(kv_layer, uint64_t(num_blocks) * 2 * nkv * block_size, uint64_t(kTcHd), 16u, &tkv)) return rc;
+  const int box_rows = block_size % 64 == 0 ? 64 : block_size % 32 == 0 ? 32 : 16;
+  if (int rc = get_tmap(kv_layer, uint64_t(num_blocks) * 2 * nkv * block_size, uint64_t(kTcHd), uint32_t(box_rows), &tkv))
+    return rc;
   static bool attr[kMaxDevices] = {};
   const int dev_slot = current_device_slot();
   if (!attr[dev_slot]) {
@@ -405,7 +500,7 @@ extern "C" int zse_attn_prefill_tc(const void* q, int ldq, int total_rows, const
   }
   TcArgs a{reinterpret_cast<const int*>(block_tables), reinterpret_cast<const int*>(cu_q),
            reinterpret_cast<const int*>(q_pos0), reinterpret_cast<__half*>(out), ldo, max_blocks, nh, nkv, block_size,
-           scale * 1.4426950408889634f, packed, reinterpret_cast<Status*>(status)};
+           scale * 1.4426950408889634f, box_rows, packed, reinterpret_cast<Status*>(status), g_attn_tc_timing};
   dim3 grid((max_q_len + kTcRows - 1) / kTcRows, packed > 0 ? nkv : nh, num_seqs);
   return launch_pdl(attn_prefill_tc_kernel, grid, dim3(kTcThreads), size_t(kTcSmemBytes),
                     reinterpret_cast<cudaStream_t>(stream), tq, tkv, tq16, a) == cudaSuccess

@@ -90,10 +90,9 @@ __device__ __forceinline__ uint4 multimem_ld_reduce_f16x8(const void* mc_ptr) {
 // Bounded wait until *flag is raised, then takes it down.  Returns false on timeout.
 __device__ __forceinline__ bool wait_flag(uint32_t* flag, Status* st, unsigned where, unsigned detail) {
   if (ld_acquire_sys(flag) == 0u) {
-    const uint64_t t0 = globaltimer_ns();
-    unsigned spins = 0;
+    SpinClock clk;
     while (ld_acquire_sys(flag) == 0u) {
-      if ((++spins & 0x3F) == 0 && globaltimer_ns() - t0 > kWaitLimitNs) {
+      if (clk.expired(0x3F)) {
         report(st, kPeerTimeout, where, detail);
         return false;
       }
@@ -394,10 +393,9 @@ tp_sum_add_rmsnorm_kernel(const TpSumArgs a) {
     const uint32_t target = a.state[rank][a.slot] + a.expected_add;
     const uint32_t* ctr = a.arrive[rank] + a.slot * tp + threadIdx.x;
     if (int32_t(ld_acquire_sys(ctr) - target) < 0) {
-      const uint64_t t0 = globaltimer_ns();
-      unsigned spins = 0;
+      SpinClock clk;
       while (int32_t(ld_acquire_sys(ctr) - target) < 0) {
-        if ((++spins & 0x3F) == 0 && globaltimer_ns() - t0 > kWaitLimitNs) {
+        if (clk.expired(0x3F)) {
           report(a.status, kPeerTimeout, 34, threadIdx.x);
           ok_flag = 0;
           break;
@@ -627,10 +625,9 @@ tp_sp_sum_norm_gather_kernel(const TpSpArgs a) {
     if (threadIdx.x < tp) {
       const uint32_t* ctr = sp.arrive[rank] + (size_t(sp.slot) * tp + threadIdx.x) * sp.nblk_cap + b;
       if (int32_t(ld_acquire_sys(ctr) - a.units) < 0) {
-        const uint64_t t0 = globaltimer_ns();
-        unsigned spins = 0;
+        SpinClock clk;
         while (int32_t(ld_acquire_sys(ctr) - a.units) < 0) {
-          if ((++spins & 0x3F) == 0 && globaltimer_ns() - t0 > kWaitLimitNs) {
+          if (clk.expired(0x3F)) {
             report(a.status, kPeerTimeout, 37, threadIdx.x);
             ok_flag = 0;
             break;
@@ -734,10 +731,9 @@ tp_sp_wait_kernel(const uint32_t* flags, const uint32_t* epoch_word, int n_block
   const uint32_t want = *reinterpret_cast<const volatile uint32_t*>(epoch_word);
   for (int b = threadIdx.x; b < n_blocks; b += kRedThreads) {
     if (ld_acquire_sys(flags + b) == want) continue;
-    const uint64_t t0 = globaltimer_ns();
-    unsigned spins = 0;
+    SpinClock clk;
     while (ld_acquire_sys(flags + b) != want) {
-      if ((++spins & 0x3F) == 0 && globaltimer_ns() - t0 > kWaitLimitNs) {
+      if (clk.expired(0x3F)) {
         report(status, kPeerTimeout, 38, b);
         break;
       }

@@ -96,16 +96,33 @@ __device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parit
   return ok != 0;
 }
 
+// Deadline of a bounded spin.  The global timer is slow to read (of the order of a microsecond), so a wait consults it
+// only every `mask + 1` polls and starts its clock at the first such reading: a wait that ends soon never reads it.
+struct SpinClock {
+  uint64_t t0 = 0;
+  unsigned spins = 0;
+  __device__ __forceinline__ bool expired(unsigned mask) {
+    if ((++spins & mask) != 0) return false;
+    const uint64_t now = globaltimer_ns();
+    if (t0 == 0) t0 = now;
+    return now - t0 > kWaitLimitNs;
+  }
+};
+
 // Bounded wait.  Returns false when it gave up (timeout, or another thread of the CTA aborted).
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, Status* st,
                                           unsigned where, unsigned detail) {
   if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = globaltimer_ns();
+  // the global timer is slow to read (of the order of a microsecond): it is first read after 16 unsuccessful polls, never
+  // on the path of a wait that ends soon
+  uint64_t t0 = 0;
   unsigned spins = 0;
   while (!mbar_try_wait_hint(bar, parity, 20000u)) {
     if ((++spins & 0xF) == 0) {
       if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > kWaitLimitNs) {
+      const uint64_t now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      if (now - t0 > kWaitLimitNs) {
         report(st, kWaitTimeout, where, detail);
         *abort_flag = 1;
         __threadfence_block();
@@ -121,12 +138,14 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
 __device__ __forceinline__ bool mbar_wait_spin(uint64_t* bar, uint32_t parity, volatile int* abort_flag, Status* st,
                                                unsigned where, unsigned detail) {
   if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = globaltimer_ns();
+  uint64_t t0 = 0;                                    // first read after 256 polls (see mbar_wait)
   unsigned spins = 0;
   while (!mbar_try_wait(bar, parity)) {
     if ((++spins & 0xFF) == 0) {
       if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > kWaitLimitNs) {
+      const uint64_t now = globaltimer_ns();
+      if (t0 == 0) t0 = now;
+      if (now - t0 > kWaitLimitNs) {
         report(st, kWaitTimeout, where, detail);
         *abort_flag = 1;
         __threadfence_block();

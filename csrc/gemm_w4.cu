@@ -124,10 +124,9 @@ __device__ __forceinline__ bool gather_wait_tile(const GatherWait& g, int t0, in
   for (int t = t0; t < t0 + nt && t < M && ok; t += kSpRowBlock) {
     const uint32_t* f = g.flags + t / kSpRowBlock;
     if (w4_ld_acquire_sys(f) == want) continue;
-    const uint64_t begin = globaltimer_ns();
-    unsigned spins = 0;
+    SpinClock clk;
     while (w4_ld_acquire_sys(f) != want) {
-      if ((++spins & 0x3F) == 0 && (*abort_flag || globaltimer_ns() - begin > kWaitLimitNs)) {
+      if (clk.expired(0x3F) || ((clk.spins & 0x3F) == 0 && *abort_flag)) {
         report(st, kPeerTimeout, 36, unsigned(t / kSpRowBlock));
         *abort_flag = 1;
         ok = false;

@@ -241,12 +241,12 @@ __device__ __forceinline__ void dec_dequant_w8_part(const uint4& w, __half2 s2, 
 __device__ __forceinline__ bool dec_wait_flag(const uint32_t* flag, uint32_t want, volatile int* abort_flag, Status* st,
                                               unsigned where, unsigned detail) {
   if (ld_acquire_gpu_u32(flag) == want) return true;
-  const uint64_t t0 = globaltimer_ns();
-  unsigned spins = 0;
+  SpinClock clk;
   while (ld_acquire_gpu_u32(flag) != want) {
-    if ((++spins & 0x3F) == 0) {
+    const bool late = clk.expired(0x3F);
+    if ((clk.spins & 0x3F) == 0) {
       if (*abort_flag) return false;
-      if (globaltimer_ns() - t0 > kWaitLimitNs) {
+      if (late) {
         report(st, kWaitTimeout, where, detail);
         *abort_flag = 1;
         __threadfence_block();
@@ -718,10 +718,9 @@ __device__ __forceinline__ void dec_allreduce_norm_tail(const DecArgs& a, DecBar
       const uint32_t target = local ? base * uint32_t(kDecWorkerWarps) : base;
       const uint32_t* ctr = pt.arrive[pt.rank] + pt.slot * tp + et;
       if (int32_t(dec_ld_acquire(ctr, local) - target) < 0) {
-        const uint64_t t0 = globaltimer_ns();
-        unsigned spins = 0;
+        SpinClock clk;
         while (int32_t(dec_ld_acquire(ctr, local) - target) < 0) {
-          if ((++spins & 0x3F) == 0 && (*abort_flag || globaltimer_ns() - t0 > kWaitLimitNs)) {
+          if (clk.expired(0x3F) || ((clk.spins & 0x3F) == 0 && *abort_flag)) {
             report(a.status, kPeerTimeout, 35, et);
             ok = false;
             break;

@@ -120,7 +120,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
 # libzse_b200.<name>.so.  ZSE_NATIVE_LIB=<path> makes a process load one (zse_b200/runtime/kernel_counters.py does).
 VARIANTS = {
     # per-role cycle counters (clock64) in the INT4 GEMM kernels, written to a buffer set by zse_gemm_w4*_set_timing
-    "timing": ("-DZSE_DEC_TIMING", "-DZSE_W4_TIMING"),
+    "timing": ("-DZSE_DEC_TIMING", "-DZSE_W4_TIMING", "-DZSE_ATTN_TIMING"),
 }
 
 

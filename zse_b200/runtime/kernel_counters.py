@@ -1,4 +1,5 @@
-"""Per-role cycle counters of the decode GEMM (csrc/gemm_w4_dec.cu) from the instrumented library variant.
+"""Per-role cycle counters of the decode GEMM (csrc/gemm_w4_dec.cu) and a per-tile timeline of the tcgen05 prefill
+attention (csrc/attention_tc.cu) from the instrumented library variant.
 
 The ordinary library carries no instrumentation.  ``python -m zse_b200.ops.build --variant timing`` links the same
 sources with ``-DZSE_DEC_TIMING`` into ``zse_b200/_C/libzse_b200.timing.so``; in that build every role of one CTA
@@ -11,6 +12,12 @@ cost of the tail that follows the last MMA) were taken, and how they can be take
 
     python -m zse_b200.ops.build --variant timing
     python -m zse_b200.runtime.kernel_counters --shape qwen2.5-14b --tokens 64 --tp 1
+    python -m zse_b200.runtime.kernel_counters --kernel attn_prefill_tc --tokens 2048
+
+With ``--kernel attn_prefill_tc`` (built with ``-DZSE_ATTN_TIMING``) the heaviest CTA of a causal chunk stamps, for each
+key tile, when its three roles passed each barrier: the loader (K slot free, K issued, V slot free, V issued), the MMA
+thread (K landed, P of the previous tile consumed, Q K^T issued, V landed, P ready, P V issued) and the first softmax
+warp (S complete, probabilities computed, P published).  The table shows which link of the chain a tile waits on.
 
 There is no counterpart in the reference (its kernels carry no counters).
 """
@@ -27,6 +34,7 @@ def main(argv=None) -> int:
     ap.add_argument("--shape", default="qwen2.5-14b")
     ap.add_argument("--tokens", type=int, default=64)
     ap.add_argument("--tp", type=int, default=1, help="shard the projections as this tensor-parallel degree would")
+    ap.add_argument("--kernel", default="gemm_w4_dec", choices=("gemm_w4_dec", "attn_prefill_tc"))
     a = ap.parse_args(argv)
 
     from ..ops import build as B
@@ -43,6 +51,8 @@ def main(argv=None) -> int:
 
     ops = CudaOps("cuda")
     lib = native.load()
+    if a.kernel == "attn_prefill_tc":
+        return _attn_timeline(a, ops, lib, native, synth)
     lib.zse_gemm_w4_dec_set_timing.argtypes = [ctypes.c_void_p]
     tbuf = torch.zeros(25 * 8 + 64, dtype=torch.int64, device="cuda")
     lib.zse_gemm_w4_dec_set_timing(tbuf.data_ptr())
@@ -117,6 +127,48 @@ def main(argv=None) -> int:
     run("down_proj -> fp32 plane", H, I // tp // 128 * 128, 2)
     run("o_proj + residual + RMSNorm in the kernel", H, sh["num_heads"] * hd // tp, 4)
     run("down_proj + residual + RMSNorm in the kernel", H, I // tp // 128 * 128, 4)
+    return 0
+
+
+def _attn_timeline(a, ops, lib, native, synth) -> int:
+    """One causal chunk of ``--tokens`` rows from position 0 (block size 16, shuffled block table): stamps of the CTA
+    that owns the last query tile of head 0, relative to the moment its first K tile landed."""
+    import math
+    import torch
+    sh = synth.SHAPES[a.shape]
+    nh, nkv = sh["num_heads"], sh["num_kv_heads"]
+    hd = sh.get("head_dim", sh["hidden_size"] // nh)
+    q_len, bs = a.tokens, 16
+    nb = (q_len + bs - 1) // bs
+    kv = (torch.randn(nb + 1, 2, nkv, bs, hd, device="cuda") * 0.3).half()
+    bt = torch.randperm(nb, device="cuda").int().view(1, nb).contiguous()
+    cu = torch.tensor([0, q_len], dtype=torch.int32, device="cuda")
+    p0 = torch.zeros(1, dtype=torch.int32, device="cuda")
+    q = (torch.randn(q_len, (nh + 2 * nkv) * hd, device="cuda") * 0.5).half()
+    out = torch.zeros(q_len, nh * hd, dtype=torch.float16, device="cuda")
+    tbuf = torch.zeros(24 * 16, dtype=torch.int64, device="cuda")
+    lib.zse_attn_prefill_tc_set_timing.argtypes = [ctypes.c_void_p]
+
+    def fn():
+        native.attn_prefill_tc(q, q.stride(0), q_len, kv, bt, cu, p0, out, out.stride(0), 1, q_len, nh, nkv, hd, bs,
+                               1 / math.sqrt(hd), ops.status.ptr)
+
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    ops.check()
+    lib.zse_attn_prefill_tc_set_timing(tbuf.data_ptr())
+    fn()
+    torch.cuda.synchronize()
+    lib.zse_attn_prefill_tc_set_timing(None)
+    t = tbuf.cpu().view(24, 16)
+    base = int(t[0, 0])
+    names = ("K landed", "prev P read", "QK^T issued", "V landed", "P ready", "PV issued", "S complete", "probs done",
+             "P published", "(two-pass) done", "K slot free", "K issued", "V slot free", "V issued")
+    print("cycles since the first K tile landed; columns: " + " | ".join(f"{i}={n}" for i, n in enumerate(names)))
+    for tile in range(min(24, (q_len + 127) // 128)):
+        row = [int(t[tile, i]) - base if int(t[tile, i]) else -1 for i in range(14)]
+        print(f"tile {tile:2d}: " + " ".join(f"{v:7d}" for v in row))
     return 0
 
 

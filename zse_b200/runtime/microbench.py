@@ -37,6 +37,7 @@ def main():
     ap.add_argument("--tp", type=int, default=1)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--only", default="", help="comma separated kernel names")
+    ap.add_argument("--kv-block", type=int, default=16, help="tokens per KV block in the prefill-attention rows")
     ap.add_argument("--json", default="")
     ap.add_argument("--w4-mode", type=int, default=0, help="INT4 GEMM CTA shape: 0 planner, 1 wide, 2 narrow (2 per SM)")
     a = ap.parse_args()
@@ -118,7 +119,7 @@ def main():
         from ..ops import native as _native
         q_len = min(M, 2048)
         n_seq = max(1, M // q_len)
-        pbs = 16
+        pbs = a.kv_block
         nb = (q_len + pbs - 1) // pbs
         kvp = (torch.randn(n_seq * nb + 1, 2, nkv, pbs, hd, device="cuda") * 0.3).half()
         btp = torch.randperm(n_seq * nb, device="cuda").int().view(n_seq, nb).contiguous()
