@@ -185,20 +185,21 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     const int g = lane >> 1, half = lane & 1;          // lanes past 2 * n_groups issue nothing
     const int v_off = a.nkv * a.block_size;            // rows between the K half and the V half of a block
     const uint32_t box_bytes = uint32_t(br) * 128u;
-    // first cache row of group g of tile t (a hole or past the end: -1)
-    auto group_row = [&](int t) {
+    // block of group g of tile t (a hole or past the end: -1).  Only the load is issued here; its result is first
+    // touched one tile later, so the latency of the table lookup never sits in the chain.
+    auto group_block = [&](int t) {
       const int tok = t * kTcKv + g * br;
-      int pb = -1;
-      if (g < n_groups && t < n_tiles && tok < kv_len) pb = my_bt[tok / a.block_size];
-      return pb >= 0 ? ((pb * 2) * a.nkv + kvh) * a.block_size + tok % a.block_size : -1;
+      return (g < n_groups && t < n_tiles && tok < kv_len) ? my_bt[tok / a.block_size] : -1;
     };
-    int row_next = group_row(0);
+    int pb_next = group_block(0);
     uint32_t ph = 1;                                   // "empty" barriers: the first wait passes
     for (int t = 0; t < n_tiles; ++t) {
-      const int row0 = row_next;
+      const int pb = pb_next;
+      const int tok = t * kTcKv + g * br;
+      const int row0 = pb >= 0 ? ((pb * 2) * a.nkv + kvh) * a.block_size + tok % a.block_size : -1;
       const bool issue = row0 >= 0;
       const uint32_t n_loads = __popc(__ballot_sync(0xffffffffu, issue));
-      row_next = group_row(t + 1);                     // in flight while this tile's loads are issued
+      pb_next = group_block(t + 1);                    // in flight while this tile's loads are issued
       bool ok = true;
       if (lane == 0) ok = mbar_wait_spin(&bars->k_empty, ph, abort_flag, a.status, 41, t);
       if (!__shfl_sync(0xffffffffu, ok, 0)) break;
@@ -289,7 +290,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
       const uint32_t groups =
           __ballot_sync(0xffffffffu, g_tok < kv_len && my_bt[g_tok / a.block_size] >= 0) & 0xFFu;
       // one verdict per warp: the tcgen05.ld / st below are warp-wide
-      if (!__all_sync(0xffffffffu, mbar_wait_spin(&bars->s_full, ph, abort_flag, a.status, 47, t))) { ok = false; break; }
+      if (!__all_sync(0xffffffffu, mbar_wait(&bars->s_full, ph, abort_flag, a.status, 47, t))) { ok = false; break; }
       if (threadIdx.x == 0) ATIME(t, 6);
       tc_fence_after_sync();
       // Most tiles lie entirely below the diagonal and have no holes: every row of the warp sees every key, and the

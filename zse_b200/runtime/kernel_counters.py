@@ -35,6 +35,7 @@ def main(argv=None) -> int:
     ap.add_argument("--tokens", type=int, default=64)
     ap.add_argument("--tp", type=int, default=1, help="shard the projections as this tensor-parallel degree would")
     ap.add_argument("--kernel", default="gemm_w4_dec", choices=("gemm_w4_dec", "attn_prefill_tc"))
+    ap.add_argument("--kv-block", type=int, default=16, help="tokens per KV block (attn_prefill_tc)")
     a = ap.parse_args(argv)
 
     from ..ops import build as B
@@ -131,14 +132,14 @@ def main(argv=None) -> int:
 
 
 def _attn_timeline(a, ops, lib, native, synth) -> int:
-    """One causal chunk of ``--tokens`` rows from position 0 (block size 16, shuffled block table): stamps of the CTA
+    """One causal chunk of ``--tokens`` rows from position 0 (``--kv-block`` tokens per block, shuffled block table): stamps of the CTA
     that owns the last query tile of head 0, relative to the moment its first K tile landed."""
     import math
     import torch
     sh = synth.SHAPES[a.shape]
     nh, nkv = sh["num_heads"], sh["num_kv_heads"]
     hd = sh.get("head_dim", sh["hidden_size"] // nh)
-    q_len, bs = a.tokens, 16
+    q_len, bs = a.tokens, a.kv_block
     nb = (q_len + bs - 1) // bs
     kv = (torch.randn(nb + 1, 2, nkv, bs, hd, device="cuda") * 0.3).half()
     bt = torch.randperm(nb, device="cuda").int().view(1, nb).contiguous()
