@@ -79,6 +79,8 @@ int zse_rope_kv_write(void* qkv, void* kv_layer, const void* positions_i32, cons
 int zse_swiglu(const void* gate_up_f16, void* out_f16, int M, int I, int gelu, void* stream);
 int zse_bias_add(void* x_f16, const void* bias_f16, int M, int N, void* stream);
 // dst[r, :] = src[rows_i64[r], :] for r < n (fp16 rows of H elements, H and ld multiples of 8)
+// Diagnostic: `ctas` CTAs read `bytes` of `buf` `repeats` times (16-byte loads past L1); the caller times the launch.
+int zse_read_probe(const void* buf, long long bytes, int repeats, int ctas, void* sink_u32, void* stream);
 int zse_gather_rows_f16(const void* src_f16, int ld, const void* rows_i64, void* dst_f16, int n, int H, int src_rows,
                         void* status, void* stream);
 

@@ -34,7 +34,7 @@ constexpr int kTcTileBytes = kTcKv * kTcHd * 2;                      // 32 KB: [
 constexpr int kTcSmemBytes = 3 * kTcTileBytes + 1024 + 256;           // Q, K, V + alignment + barriers
 
 struct TcBars {
-  uint64_t q_full, k_full, k_empty, v_full, v_empty, s_full, p_full, o_full;
+  uint64_t q_full, k_full, v_full, v_empty, s_full, p_full;
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -130,12 +130,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
   if (threadIdx.x == 0) {
     mbar_init(&bars->q_full, 1);
     mbar_init(&bars->k_full, 1);
-    mbar_init(&bars->k_empty, 1);
     mbar_init(&bars->v_full, 1);
     mbar_init(&bars->v_empty, 1);
     mbar_init(&bars->s_full, 1);
     mbar_init(&bars->p_full, 128);
-    mbar_init(&bars->o_full, 1);
     bars->abort_flag = 0;
     mbar_fence_init();
     prefetch_tmap(G > 0 ? &tmap_q16 : &tmap_q);
@@ -194,6 +192,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     int pb_next = group_block(0);
     uint32_t ph = 1;                                   // "empty" barriers: the first wait passes
     for (int t = 0; t < n_tiles; ++t) {
+      if (lane == 0) ATIME(t, 14);
       const int pb = pb_next;
       const int tok = t * kTcKv + g * br;
       const int row0 = pb >= 0 ? ((pb * 2) * a.nkv + kvh) * a.block_size + tok % a.block_size : -1;
@@ -201,7 +200,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
       const uint32_t n_loads = __popc(__ballot_sync(0xffffffffu, issue));
       pb_next = group_block(t + 1);                    // in flight while this tile's loads are issued
       bool ok = true;
-      if (lane == 0) ok = mbar_wait_spin(&bars->k_empty, ph, abort_flag, a.status, 41, t);
+      if (lane == 0) ATIME(t, 15);
+      // the K slot is free once Q K^T of the previous tile is complete: the event `s_full` already announces (a second
+      // tcgen05.commit for the loader alone was seen ~1 k cycles later than the first)
+      if (lane == 0 && t > 0) ok = mbar_wait_spin(&bars->s_full, ph, abort_flag, a.status, 41, t);
       if (!__shfl_sync(0xffffffffu, ok, 0)) break;
       if (lane == 0) {
         ATIME(t, 10);
@@ -252,7 +254,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
           umma_ss(tm_s, q_desc + adv, k_desc + adv, idesc_qk, j != 0);
         }
         tc_commit(&bars->s_full);                     // S complete (and every earlier MMA, i.e. the previous P V)
-        tc_commit(&bars->k_empty);
         ATIME(t, 2);
         if (!mbar_wait_spin(&bars->v_full, ph, abort_flag, a.status, 45, t)) break;
         ATIME(t, 3);
@@ -266,7 +267,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
         }
         tc_commit(&bars->v_empty);
         ATIME(t, 5);
-        if (t == n_tiles - 1) tc_commit(&bars->o_full);
         ph ^= 1;
       }
     }
@@ -425,7 +425,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
       ph ^= 1;
     }
     // ---- epilogue: O / l -> fp16 rows
-    if (ok) ok = __all_sync(0xffffffffu, mbar_wait_spin(&bars->o_full, 0, abort_flag, a.status, 48, 0));
+    // O is complete when P V of the last tile is: the event `v_empty` announces for that tile
+    if (ok)
+      ok = __all_sync(0xffffffffu,
+                      mbar_wait_spin(&bars->v_empty, uint32_t(n_tiles - 1) & 1u, abort_flag, a.status, 48, 0));
     tc_fence_after_sync();
     if (ok) {
       // every lane takes part in the warp-wide tcgen05.ld (rows past the chunk included); only the stores are per row

@@ -407,6 +407,36 @@ extern "C" int zse_gather_rows_f16(const void* src, int ld, const void* rows_i64
                     reinterpret_cast<Status*>(status)) == cudaSuccess ? 0 : ZSE_ERR_LAUNCH;
 }
 
+// Read-bandwidth probe: every CTA walks the whole buffer `repeats` times with 16-byte loads that bypass L1.  With a
+// buffer that fits in L2 this measures what the L2 -> SM path delivers to all SMs at once - the ceiling of a kernel
+// whose operand is re-read by every CTA (the activation tile of the decode GEMMs, the K/V tiles of prefill attention).
+// CTA b starts at a different offset so that the CTAs do not walk in lock step.
+__global__ void __launch_bounds__(512) read_probe_kernel(const uint4* buf, size_t n16, int repeats, unsigned* sink) {
+  unsigned acc = 0;
+  const size_t per_cta = n16 / gridDim.x;
+  for (int r = 0; r < repeats; ++r) {
+    const size_t start = ((size_t(blockIdx.x) + size_t(r)) % gridDim.x) * per_cta;
+    for (size_t i = threadIdx.x; i < per_cta; i += 4 * blockDim.x) {
+      // four independent loads in flight per thread
+      uint4 v0 = __ldcg(buf + start + i), v1 = make_uint4(0, 0, 0, 0), v2 = v1, v3 = v1;
+      if (i + blockDim.x < per_cta) v1 = __ldcg(buf + start + i + blockDim.x);
+      if (i + 2 * blockDim.x < per_cta) v2 = __ldcg(buf + start + i + 2 * blockDim.x);
+      if (i + 3 * blockDim.x < per_cta) v3 = __ldcg(buf + start + i + 3 * blockDim.x);
+      acc += v0.x ^ v1.y ^ v2.z ^ v3.w;
+    }
+  }
+  if (acc == 0x9E3779B9u) *sink = acc;                // keeps the loads alive; practically never true
+}
+
+// Diagnostic (no counterpart in the reference): reads `bytes` of `buf` `repeats` times with `ctas` CTAs in total, each
+// CTA a different slice per repeat.  The caller times it.
+extern "C" int zse_read_probe(const void* buf, long long bytes, int repeats, int ctas, void* sink, void* stream) {
+  if (bytes < 16 * 512 || repeats <= 0 || ctas <= 0 || (reinterpret_cast<uintptr_t>(buf) & 15)) return ZSE_ERR_SHAPE;
+  read_probe_kernel<<<unsigned(ctas), 512, 0, ST(stream)>>>(reinterpret_cast<const uint4*>(buf), size_t(bytes) / 16,
+                                                           repeats, reinterpret_cast<unsigned*>(sink));
+  return LAUNCH_OK();
+}
+
 extern "C" int zse_bias_add(void* x, const void* bias, int M, int N, void* stream) {
   const size_t total = size_t(M) * N;
   if (!total) return 0;

@@ -132,6 +132,7 @@ _SIGS = {
     "zse_tp_sum_add_rmsnorm_emulated": (c_int, [c_void_p, POINTER(c_uint64), c_void_p, POINTER(c_uint64), c_int,
                                                 c_float, c_int, c_int, c_void_p, c_void_p]),
     "zse_tp_ctx_set_gather": (c_int, [c_void_p, c_int, c_int, POINTER(c_uint64), POINTER(c_uint64)]),
+    "zse_read_probe": (c_int, [c_void_p, c_int64, c_int, c_int, c_void_p, c_void_p]),
     "zse_tp_gather_rows": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p]),
     "zse_tp_gather_rows_emulated": (c_int, [c_void_p, POINTER(c_uint64), c_int, c_int, c_int, c_void_p, c_void_p]),
     "zse_tp_argmax": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p]),
@@ -353,6 +354,11 @@ def softcap(x, M, V, cap):
 
 def swiglu(gate_up, out, M, I, gelu=False):
     _ck(load().zse_swiglu(_p(gate_up), _p(out), M, I, int(gelu), _stream()), "swiglu")
+
+
+def read_probe(buf, nbytes, repeats, ctas, sink):
+    """Diagnostic: ``ctas`` CTAs read ``nbytes`` of ``buf`` ``repeats`` times (csrc/elementwise.cu)."""
+    _ck(load().zse_read_probe(_p(buf), nbytes, repeats, ctas, _p(sink), _stream()), "read_probe")
 
 
 def bias_add(x, bias, M, N):

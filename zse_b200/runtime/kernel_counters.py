@@ -165,10 +165,11 @@ def _attn_timeline(a, ops, lib, native, synth) -> int:
     t = tbuf.cpu().view(24, 16)
     base = int(t[0, 0])
     names = ("K landed", "prev P read", "QK^T issued", "V landed", "P ready", "PV issued", "S complete", "probs done",
-             "P published", "(two-pass) done", "K slot free", "K issued", "V slot free", "V issued")
+             "P published", "(two-pass) done", "K slot free", "K issued", "V slot free", "V issued", "loader: tile begins",
+             "loader: next lookup issued")
     print("cycles since the first K tile landed; columns: " + " | ".join(f"{i}={n}" for i, n in enumerate(names)))
     for tile in range(min(24, (q_len + 127) // 128)):
-        row = [int(t[tile, i]) - base if int(t[tile, i]) else -1 for i in range(14)]
+        row = [int(t[tile, i]) - base if int(t[tile, i]) else -1 for i in range(16)]
         print(f"tile {tile:2d}: " + " ".join(f"{v:7d}" for v in row))
     return 0
 

@@ -95,6 +95,16 @@ def main():
     n_pl = ops.linear_partial(wd, xi, M, planes) if want("add_rmsnorm") else 1
     run("add_rmsnorm", lambda: ops.add_rmsnorm(resid, planes, n_pl, None, wn, xn, M, 1e-6),
         M * H * (4 + 4 + 4 * n_pl + 2))
+    # what the memory system delivers to all SMs at once: a 32 MB buffer that stays in L2 read 32 times (each CTA another
+    # slice each time), and 1 GB read once from DRAM.  The first is the ceiling of every operand that all CTAs re-read.
+    if want("l2_read_32mb", "hbm_read_1gb"):
+        from ..ops import native as _nat
+        sink = torch.zeros(1, dtype=torch.int32, device="cuda")
+        small = torch.ones(32 << 20, dtype=torch.uint8, device="cuda")
+        run("l2_read_32mb", lambda: _nat.read_probe(small, small.numel(), 32, 4 * ops.sm_count, sink), 32 * small.numel())
+        big = torch.ones(1 << 30, dtype=torch.uint8, device="cuda")
+        run("hbm_read_1gb", lambda: _nat.read_probe(big, big.numel(), 1, 4 * ops.sm_count, sink), big.numel())
+        del small, big
     # attention over a paged cache
     if want("attn_decode_s1", "attn_decode_s2", "attn_decode_s4", "rope_kv_write"):
         bs = 16
