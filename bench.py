@@ -270,8 +270,15 @@ def run_ours(args):
     # time to first token of every request (all of them arrive at once, so queueing behind the others counts)
     ttfts = sorted((r.first_token_time - r.arrival_time) * 1000.0 for r in eng.scheduler.active_requests()
                    if r.first_token_time is not None)
+    def step_checked():
+        """One engine step; an error that the engine attributes to its requests (a device status, a failed launch) ends
+        the run here instead of surfacing later as missing tokens."""
+        res = eng.step()
+        if res.errors:
+            raise RuntimeError(f"engine step failed: {res.errors[0]}")
+
     for _ in range(args.warmup):
-        eng.step()
+        step_checked()
     barrier()
     torch.cuda.synchronize()
     runner = eng.runner
@@ -284,7 +291,7 @@ def run_ours(args):
         torch.cuda.profiler.start()
     t_start = time.perf_counter()
     for _ in range(args.steps):
-        eng.step()
+        step_checked()
     torch.cuda.synchronize()
     t_e2e = time.perf_counter() - t_start
     if args.profile_region:
