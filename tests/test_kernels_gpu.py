@@ -504,3 +504,18 @@ def test_lora_shrink_expand(ops):
             want = want + ref.lora_delta(x[t:t + 1], a[i], b[i], float(scales[i]))[0]
         assert (y[t, 64:].float() - want).abs().max() < 5e-3
         assert torch.equal(y[t, :64], y0[t, :64])
+
+
+def test_read_probe_runs_and_rejects_bad_arguments(ops):
+    """The bandwidth probe of the microbenchmark: a launch over a small buffer completes without touching its sink,
+    and sizes it cannot split are refused on the host."""
+    from zse_b200.ops import native
+    buf = torch.ones(1 << 20, dtype=torch.uint8, device="cuda")
+    sink = torch.zeros(1, dtype=torch.int32, device="cuda")
+    native.read_probe(buf, buf.numel(), 3, 16, sink)
+    torch.cuda.synchronize()
+    assert int(sink.item()) == 0
+    with pytest.raises(Exception):
+        native.read_probe(buf, 1024, 1, 16, sink)          # fewer than 512 loads of 16 bytes
+    with pytest.raises(Exception):
+        native.read_probe(buf, buf.numel(), 0, 16, sink)
