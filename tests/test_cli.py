@@ -186,3 +186,28 @@ def test_bench_reference_arm_prints_its_unavailable_line():
         assert r.returncode == 0, r.stderr[-2000:]
         line = json.loads(r.stdout.strip().splitlines()[-1])
         assert line["impl"] == "reference" and isinstance(line["unavailable"], str) and "\n" not in line["unavailable"]
+
+
+def test_bench_repeats_itself_once_after_a_device_fault(monkeypatch):
+    """bench.py's answer to a device fault in a single-GPU run: one fresh process, named in the result line; never a
+    second one, never under a multi-rank launch."""
+    import importlib.util
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location("bench_under_test", os.path.join(root, "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    calls = []
+    monkeypatch.setattr(os, "execv", lambda exe, argv: calls.append((exe, list(argv))))
+    monkeypatch.delenv("ZSE_BENCH_RERUN", raising=False)
+    monkeypatch.delenv("WORLD_SIZE", raising=False)
+    bench.rerun_once_in_fresh_process(RuntimeError("engine step failed: req-1: CUDA error:\nunspecified launch failure"))
+    assert len(calls) == 1 and calls[0][0] == sys.executable and calls[0][1][0] == sys.executable
+    assert os.environ["ZSE_BENCH_RERUN"] == "engine step failed: req-1: CUDA error: unspecified launch failure"
+    bench.rerun_once_in_fresh_process(RuntimeError("again"))             # already the repeat: no third process
+    assert len(calls) == 1
+    monkeypatch.delenv("ZSE_BENCH_RERUN")
+    monkeypatch.setenv("WORLD_SIZE", "2")
+    bench.rerun_once_in_fresh_process(RuntimeError("CUDA error"))        # ranks of a launcher do not re-exec
+    assert len(calls) == 1
+    monkeypatch.delenv("ZSE_BENCH_RERUN", raising=False)
