@@ -2,9 +2,12 @@
 //
 // One CTA owns 128 query rows of one head of one sequence and walks the keys in tiles of 128 tokens:
 //   S = Q K^T     tcgen05.mma, both operands in shared memory (K-major, 128-byte swizzle, brought by TMA - the K tile
-//                 of a head is eight 16-token boxes fetched through the sequence's block table), S in TMEM
-//   softmax       128 threads, thread i owns TMEM lane i = query row i: two passes over its 128 scores with
-//                 tcgen05.ld (row maximum, then exp2 and the fp16 probabilities), no cross-thread reduction at all
+//                 of a head is made of boxes of 16, 32 or 64 tokens, whatever divides the block size, fetched through
+//                 the sequence's block table by a loader warp, one lane per box), S in TMEM
+//   softmax       128 threads, thread i owns TMEM lane i = query row i, no cross-thread reduction at all.  Usually one
+//                 pass with tcgen05.ld: probabilities against the maximum in use while the new maximum is tracked;
+//                 two passes (row maximum, then exp2 and the fp16 probabilities) when some row of the warp outgrew
+//                 its reference, and where masking applies (the diagonal tile, tiles with dropped blocks)
 //   O += P V      tcgen05.mma with P as the A operand FROM TMEM (written by tcgen05.st over the scores it replaces) and
 //                 V from shared memory as an MN-major operand - the cache stores V as [token][head_dim], which is
 //                 exactly that layout, so nothing is transposed; O accumulates in TMEM across the tiles
@@ -12,10 +15,12 @@
 // well inside fp16), so the rescaling pass over O (tcgen05.ld, multiply, tcgen05.st) is rare after the first tiles.
 // TMEM per CTA: 128 columns S / P + 128 columns O; shared memory: Q, one K and one V tile (96 KB); two CTAs share an
 // SM, so one CTA's softmax overlaps the other's MMAs.  K is released as soon as S is complete and V as soon as the
-// P V product is, so the next tile's loads run under the current tile's softmax.
+// P V product is, so the next tile's loads run under the current tile's softmax.  One tcgen05.commit per event: the
+// barrier that tells the softmax warps that S is complete also tells the loader that the K slot is free, and the one
+// that frees the V slot tells the epilogue that O is complete.
 // Every wait is bounded and reports through the status word; on a failure the CTA frees its TMEM and leaves.  The waits
-// of the per-tile chain (MMA issuer and softmax threads) poll without the suspend hint: a suspended thread wakes up
-// microseconds after its barrier flips, and a tile passes four such hand-overs.
+// of the MMA issuer and the loader poll without the suspend hint: a suspended thread wakes up microseconds after its
+// barrier flips, and a tile passes several such hand-overs.
 //
 // Replaces the reference's flash_attention_prefill kernel (zse-engine/zse_engine/orchestrator/kernels.py:859-957) for
 // the shapes it covers; attention.cu::attn_prefill_kernel (mma.sync) keeps the rest (other head sizes, soft-capped
@@ -29,7 +34,7 @@ namespace zse {
 constexpr int kTcRows = 128;          // query rows per CTA (UMMA M)
 constexpr int kTcKv = 128;            // keys per tile (UMMA N of S, K of P V)
 constexpr int kTcHd = 128;
-constexpr int kTcThreads = 192;       // warps 0-3 softmax, warp 4 producer, warp 5 MMA issuer
+constexpr int kTcThreads = 192;       // warps 0-3 softmax, warp 4 loader, warp 5 MMA issuer
 constexpr int kTcTileBytes = kTcKv * kTcHd * 2;                      // 32 KB: [2 halves of 64 columns][128 rows][128 B]
 constexpr int kTcSmemBytes = 3 * kTcTileBytes + 1024 + 256;           // Q, K, V + alignment + barriers
 
