@@ -224,7 +224,7 @@ class _Thread:
             return f32(v[0][e.index])
         if isinstance(e, ir.Cast):
             if e.to == "int":
-                return int(math.trunc(v[0]))
+                return int(math.trunc(float(v[0])))        # numpy.float32 has no __trunc__
             return _to_scalar(v[0], e.to)
         if isinstance(e, ir.Compare):
             a, b = v
