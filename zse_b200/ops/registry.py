@@ -6,7 +6,7 @@ first use, ``launch(name, grid, block, *args)`` runs one.  Here every kernel is 
 library that is built once (``ops/build.py``: per-source object cache keyed by content hash), so "compiling" a name
 means loading that library, and each name resolves to the host entry point (``ops/native.py``) that serves the role
 of the reference kernel - often one fused kernel stands for several of the reference's.  Entry points choose their own
-grid and block from the problem shape; ``launch`` therefore ignores the two tuples it is handed.
+grid and block from the problem shape; ``launch`` therefore refuses a geometry that is handed to it.
 """
 from __future__ import annotations
 
@@ -38,12 +38,17 @@ KERNEL_TABLE: Dict[str, Tuple[str, str]] = {
     "logit_softcap": ("softcap", ""),
     "paged_attention": ("attn_decode", "mma.sync m16n8k16 QK^T and PV over the paged cache (a decode query group is at "
                                        "most 16 rows), cp.async rings, split over the sequence"),
-    "prefill_attention": ("attn_prefill", "mma.sync m16n8k16, causal, reads earlier chunks from the paged cache"),
+    "prefill_attention": ("attn_prefill", "mma.sync m16n8k16, causal, reads earlier chunks from the paged cache; for "
+                                          "head_dim 128 the engine takes attn_prefill_tc instead (tcgen05, "
+                                          "probabilities through TMEM)"),
     "tiled_fp16_matmul": ("gemm_f16", "tcgen05 + TMA, operands in shared memory, accumulators in TMEM"),
     "tiled_dequant_matmul_int4": ("gemm_w4", "tcgen05: nibbles dequantised in registers and written to TMEM with "
                                              "tcgen05.st as the A operand, accumulators in TMEM; passes of at most "
                                              "64 tokens can take the persistent kernel gemm_w4_dec"),
-    "tiled_dequant_matmul_int8": ("dequant_w8", "INT8 weights are expanded once at load and run through gemm_f16"),
+    "tiled_dequant_matmul_int8": ("gemm_w8_dec", "tcgen05, the INT4 decode kernel's pipeline with 8-bit chunks: weights "
+                                                 "stay INT8 in memory and are dequantised into TMEM; passes of more "
+                                                 "than 64 tokens expand the layer into a shared fp16 scratch with "
+                                                 "dequant_w8_tiled and run gemm_f16"),
     "dequant_gemv_int4": ("gemm_w4", "M <= 2 takes the CUDA-core GEMV inside the same entry point"),
     "batched_dequant_gemv_int4": ("gemm_w4", "small batches take the narrow tensor-core tile"),
     "fused_gate_up_gemv_int4": ("gemm_w4", "epilogue 1: gate and up rows interleaved, activation applied in the epilogue"),
