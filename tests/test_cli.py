@@ -211,3 +211,26 @@ def test_bench_repeats_itself_once_after_a_device_fault(monkeypatch):
     bench.rerun_once_in_fresh_process(RuntimeError("CUDA error"))        # ranks of a launcher do not re-exec
     assert len(calls) == 1
     monkeypatch.delenv("ZSE_BENCH_RERUN", raising=False)
+
+
+def test_bench_defaults_follow_the_driver_contract(monkeypatch):
+    """With no flags: one GPU, at least three warm-up steps, the headline workload on the 14B shape with 64 requests;
+    the other workloads bring their own model and request count unless the caller names them."""
+    import importlib.util
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location("bench_args_under_test", os.path.join(root, "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    monkeypatch.setattr(sys, "argv", ["bench.py"])
+    a = bench.parse_args()
+    assert (a.gpus, a.impl, a.workload) == (1, "ours", "batch64") and a.warmup >= 3 and a.steps >= a.warmup
+    assert a.model == "qwen2.5-14b" and a.requests == 64 and a.comm is None and not a.no_graphs
+    monkeypatch.setattr(sys, "argv", ["bench.py", "--gpus", "8", "--steps", "7", "--warmup", "3", "--workload", "single"])
+    a = bench.parse_args()
+    assert (a.gpus, a.steps, a.warmup) == (8, 7, 3) and a.model == "qwen2.5-7b" and a.requests == 1
+    monkeypatch.setattr(sys, "argv", ["bench.py", "--workload", "lora72b", "--requests", "160"])
+    a = bench.parse_args()
+    assert a.model == "qwen2.5-72b" and a.requests == 160
+    assert set(bench.WORKLOADS) == {"batch64", "single", "spec32b", "lora72b"}
+    assert bench.WORKLOADS["spec32b"]["spec_k"] == 4 and bench.WORKLOADS["batch64"]["spec_k"] == 0
