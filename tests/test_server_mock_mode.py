@@ -1,0 +1,198 @@
+"""The HTTP API of a server that has no model loaded ("mock" mode of the reference's tests/test_server.py): every route
+is registered and answers through the same router, authentication and accounting as with an engine, so the whole API
+surface can be exercised in milliseconds - requests are handed to the router directly, no socket is opened."""
+import asyncio
+import json
+
+import pytest
+
+from zse_b200.server.app import ZSEServer
+from zse_b200.server.router import Request
+
+ADMIN = {"authorization": "Bearer admin-secret"}
+
+
+def call(srv, method, path, body=None, headers=None, query=None):
+    raw = json.dumps(body).encode() if body is not None else b""
+    req = Request(method, path, dict(headers or {}), raw, dict(query or {}))
+    resp = asyncio.new_event_loop().run_until_complete(srv.router.handle(req))
+    data = json.loads(resp.body) if resp.body and resp.headers.get("Content-Type", "").startswith("application/json") \
+        else resp.body
+    return resp.status, data
+
+
+@pytest.fixture()
+def srv():
+    s = ZSEServer(model_path=None, admin_key="admin-secret", db_path=":memory:", model_name="mock-model", quiet=True,
+                  enable_rag=False)
+    yield s
+    s.database.close()
+
+
+@pytest.fixture()
+def locked():
+    s = ZSEServer(model_path=None, admin_key="admin-secret", db_path=":memory:", model_name="mock-model", quiet=True,
+                  enable_rag=False, require_auth=True)
+    yield s
+    s.database.close()
+
+
+def new_key(srv, **kw):
+    status, out = call(srv, "POST", "/v1/admin/keys/create", dict(name="k", **kw), ADMIN)
+    assert status == 201
+    return out
+
+
+# ---- health, models, completions --------------------------------------------------------------------------------
+def test_health_reports_mock_mode(srv):
+    for path in ("/health", "/v1/health"):
+        status, out = call(srv, "GET", path)
+        assert status == 200 and out == {"status": "ok", "model": "mock-model", "engine": "mock"}
+    assert srv.engine is None
+
+
+def test_models_list_names_the_served_model(srv):
+    status, out = call(srv, "GET", "/v1/models")
+    assert status == 200 and out["object"] == "list"
+    assert [m["id"] for m in out["data"]][0] == "mock-model"
+
+
+def test_chat_completion_has_the_openai_shape(srv):
+    status, out = call(srv, "POST", "/v1/chat/completions",
+                       {"model": "mock-model", "messages": [{"role": "user", "content": "hi"}]})
+    assert status == 200 and out["object"] == "chat.completion" and out["model"] == "mock-model"
+    assert out["id"].startswith("chatcmpl-") and isinstance(out["created"], int)
+    choice = out["choices"][0]
+    assert choice["index"] == 0 and choice["finish_reason"] == "stop"
+    assert choice["message"] == {"role": "assistant", "content": "This is a mock response (no model loaded)."}
+    u = out["usage"]
+    assert u["total_tokens"] == u["prompt_tokens"] + u["completion_tokens"] and u["completion_tokens"] == 8
+
+
+def test_text_completion_has_the_openai_shape(srv):
+    status, out = call(srv, "POST", "/v1/completions", {"prompt": "once upon a time", "max_tokens": 4})
+    assert status == 200 and out["object"] == "text_completion"
+    assert out["choices"][0]["text"].startswith("This is a mock response") and out["id"].startswith("cmpl-")
+
+
+def test_bad_requests_are_refused_before_generation(srv):
+    assert call(srv, "POST", "/v1/chat/completions", {"model": "m"})[0] == 400                 # no messages
+    assert call(srv, "POST", "/v1/chat/completions", {"messages": []})[0] == 400
+    assert call(srv, "POST", "/v1/completions", {"model": "m"})[0] == 400                      # no prompt
+    status, out = call(srv, "POST", "/v1/chat/completions",
+                       {"messages": [{"role": "user", "content": "x"}], "temperature": "hot"})
+    assert status == 400 and out["error"]["type"] == "invalid_request_error"
+    req = Request("POST", "/v1/chat/completions", {}, b"{not json", {})
+    resp = asyncio.new_event_loop().run_until_complete(srv.router.handle(req))
+    assert resp.status == 400
+    assert call(srv, "GET", "/v1/chat/completions")[0] == 405
+    assert call(srv, "GET", "/v1/nothing/here")[0] == 404
+
+
+# ---- keys -------------------------------------------------------------------------------------------------------
+def test_admin_routes_need_the_admin_key(srv):
+    assert call(srv, "POST", "/v1/admin/keys/create", {"name": "x"})[0] == 403
+    assert call(srv, "GET", "/v1/admin/keys/list", headers={"authorization": "Bearer wrong"})[0] == 403
+    key = new_key(srv)
+    assert call(srv, "GET", "/v1/admin/stats", headers={"authorization": "Bearer " + key["key"]})[0] == 403
+    assert call(srv, "GET", "/v1/admin/stats", headers=ADMIN)[0] == 200
+
+
+def test_key_lifecycle_create_list_update_revoke(srv):
+    out = new_key(srv, rate_limit_rpm=7, allowed_models="mock-model")
+    assert out["key"].startswith("sk-zse-") and out["prefix"] == out["key"][:14] and out["rate_limit_rpm"] == 7
+    status, listed = call(srv, "GET", "/v1/admin/keys/list", headers=ADMIN)
+    assert status == 200 and len(listed["keys"]) == 1 and "key" not in listed["keys"][0]       # shown once only
+    assert call(srv, "POST", "/v1/admin/keys/update", {"id": out["id"], "rate_limit_rpm": 99}, ADMIN) == \
+        (200, {"updated": True})
+    assert call(srv, "GET", "/v1/admin/keys/list", headers=ADMIN)[1]["keys"][0]["rate_limit_rpm"] == 99
+    assert call(srv, "POST", "/v1/admin/keys/update", {"rate_limit_rpm": 1}, ADMIN)[0] == 400  # no id
+    assert call(srv, "POST", "/v1/admin/keys/update", {"id": 555, "rate_limit_rpm": 1}, ADMIN)[0] == 404
+    assert call(srv, "POST", "/v1/admin/keys/revoke", {}, ADMIN)[0] == 400
+    assert call(srv, "POST", "/v1/admin/keys/revoke", {"id": out["id"]}, ADMIN) == (200, {"revoked": True})
+    assert call(srv, "POST", "/v1/admin/keys/revoke", {"id": out["id"]}, ADMIN)[0] == 404
+    second = new_key(srv)
+    assert call(srv, "POST", "/v1/admin/keys/revoke", {"prefix": second["prefix"]}, ADMIN)[0] == 200
+    assert [k["is_active"] for k in call(srv, "GET", "/v1/admin/keys/list", headers=ADMIN)[1]["keys"]] == [False, False]
+
+
+def test_an_open_server_takes_requests_without_a_key_but_checks_a_key_that_is_shown(srv):
+    body = {"messages": [{"role": "user", "content": "x"}]}
+    assert call(srv, "POST", "/v1/chat/completions", body)[0] == 200
+    assert call(srv, "POST", "/v1/chat/completions", body, {"authorization": "Bearer sk-zse-bogus"})[0] == 401
+    key = new_key(srv)
+    assert call(srv, "POST", "/v1/chat/completions", body, {"authorization": "Bearer " + key["key"]})[0] == 200
+
+
+def test_a_locked_server_wants_a_valid_key_for_the_api_but_not_for_health(locked):
+    body = {"messages": [{"role": "user", "content": "x"}]}
+    status, out = call(locked, "POST", "/v1/chat/completions", body)
+    assert status == 401 and "Missing Authorization" in out["error"]["message"]
+    assert call(locked, "GET", "/v1/models")[0] == 401
+    assert call(locked, "GET", "/health")[0] == 200 and call(locked, "GET", "/v1/health")[0] == 200
+    key = new_key(locked)
+    auth = {"authorization": "Bearer " + key["key"]}
+    assert call(locked, "POST", "/v1/chat/completions", body, auth)[0] == 200
+    assert call(locked, "GET", "/v1/models", headers=auth)[0] == 200
+    assert call(locked, "POST", "/v1/chat/completions", body, ADMIN)[0] == 200                  # the admin key passes
+    call(locked, "POST", "/v1/admin/keys/revoke", {"id": key["id"]}, ADMIN)
+    assert call(locked, "POST", "/v1/chat/completions", body, auth)[0] == 401
+
+
+def test_model_allow_list_and_rate_limit_apply_to_completions(locked):
+    body = {"model": "mock-model", "messages": [{"role": "user", "content": "x"}]}
+    narrow = new_key(locked, allowed_models="other-model")
+    status, out = call(locked, "POST", "/v1/chat/completions", body, {"authorization": "Bearer " + narrow["key"]})
+    assert status == 403 and "not allowed" in out["error"]["message"]
+    limited = new_key(locked, rate_limit_rpm=2)
+    auth = {"authorization": "Bearer " + limited["key"]}
+    locked.database.record_usage(limited["id"], 1, 1)
+    assert call(locked, "POST", "/v1/chat/completions", body, auth)[0] == 200
+    locked.database.record_usage(limited["id"], 1, 1)
+    status, out = call(locked, "POST", "/v1/chat/completions", body, auth)
+    assert status == 429 and out["error"]["type"] == "rate_limit_error"
+
+
+# ---- statistics and dashboard sessions --------------------------------------------------------------------------
+def test_stats_and_usage_without_an_engine(srv):
+    key = new_key(srv)
+    srv.database.record_usage(key["id"], 10, 5, model="mock-model", latency_ms=50.0)
+    status, out = call(srv, "GET", "/v1/admin/stats", headers=ADMIN)
+    assert status == 200 and out["num_keys"] == 1 and out["usage"]["total_tokens"] == 15 and "engine" not in out
+    status, out = call(srv, "GET", "/v1/admin/usage", headers=ADMIN, query={"key_id": str(key["id"])})
+    assert status == 200 and out["total_requests"] == 1 and out["avg_latency_ms"] == 50.0
+    assert call(srv, "GET", "/v1/admin/usage", headers=ADMIN, query={"key_id": "999"})[1]["total_requests"] == 0
+
+
+def test_dashboard_sessions_round_trip(srv):
+    key = new_key(srv)
+    auth = {"authorization": "Bearer " + key["key"]}
+    assert call(srv, "POST", "/v1/dashboard/session")[0] == 401                                 # a key is needed here
+    status, out = call(srv, "POST", "/v1/dashboard/session", headers=auth)
+    assert status == 201 and len(out["session_id"]) == 16
+    sid = out["session_id"]
+    assert call(srv, "POST", f"/v1/dashboard/session/{sid}/message", {"role": "user"}, auth)[0] == 400
+    assert call(srv, "POST", f"/v1/dashboard/session/{sid}/message", {"role": "user", "content": "hello"}, auth)[0] == 201
+    call(srv, "POST", f"/v1/dashboard/session/{sid}/message",
+         {"role": "assistant", "content": "hi there", "model": "mock-model"}, auth)
+    status, out = call(srv, "GET", f"/v1/dashboard/session/{sid}", headers=auth)
+    assert status == 200 and [(m["role"], m["content"]) for m in out["messages"]] == \
+        [("user", "hello"), ("assistant", "hi there")]
+    status, out = call(srv, "GET", "/v1/dashboard/sessions", headers=auth)
+    assert status == 200 and [(s["session_id"], s["messages"]) for s in out["sessions"]] == [(sid, 2)]
+    other = new_key(srv)
+    status, out = call(srv, "GET", "/v1/dashboard/sessions", headers={"authorization": "Bearer " + other["key"]})
+    assert out["sessions"] == []                                                                # a key sees its own
+    assert len(call(srv, "GET", "/v1/dashboard/sessions", headers=ADMIN)[1]["sessions"]) == 1   # the admin sees all
+    assert call(srv, "DELETE", f"/v1/dashboard/session/{sid}", headers=auth) == (200, {"deleted": 2})
+    assert call(srv, "GET", f"/v1/dashboard/session/{sid}", headers=auth)[1]["messages"] == []
+
+
+# ---- static files -----------------------------------------------------------------------------------------------
+def test_the_dashboard_is_served_from_the_root(srv):
+    status, body = call(srv, "GET", "/")
+    assert status == 200 and b"<html" in body.lower()
+    status, body = call(srv, "GET", "/app.js")
+    assert status == 200 and len(body) > 1000
+    assert call(srv, "GET", "/style.css")[0] == 200
+    assert call(srv, "GET", "/../app.py")[0] in (403, 404)
