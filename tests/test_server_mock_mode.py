@@ -196,3 +196,67 @@ def test_the_dashboard_is_served_from_the_root(srv):
     assert status == 200 and len(body) > 1000
     assert call(srv, "GET", "/style.css")[0] == 200
     assert call(srv, "GET", "/../app.py")[0] in (403, 404)
+
+
+# ---- LoRA routes without an engine, and with a stand-in manager -------------------------------------------------
+def test_lora_routes_without_an_engine(srv):
+    assert call(srv, "GET", "/v1/lora/list") == (200, {"adapters": []})
+    assert call(srv, "GET", "/v1/lora/stats") == (200, {"num_adapters": 0})
+    assert call(srv, "POST", "/v1/lora/load", {"adapter_id": "a", "path": "/x"})[0] == 403      # admin only
+    status, out = call(srv, "POST", "/v1/lora/load", {"adapter_id": "a", "path": "/x"}, ADMIN)
+    assert status == 503 and "no engine" in out["error"]["message"]
+    assert call(srv, "POST", "/v1/lora/unload", {"adapter_id": "a"})[0] == 403
+    assert call(srv, "POST", "/v1/lora/unload", {"adapter_id": "a"}, ADMIN)[0] == 400
+
+
+class _FakeAdapter:
+    adapter_id, rank, alpha, target_modules, num_layers, total_bytes = "a1", 8, 16.0, ["q_proj"], 2, 4096
+
+
+class _FakeManager:
+    def __init__(self):
+        self.loaded = {}
+
+    def list_adapters(self):
+        return [{"adapter_id": k} for k in self.loaded]
+
+    def stats(self):
+        return {"num_adapters": len(self.loaded)}
+
+    def load_adapter(self, aid, path):
+        if aid in self.loaded:
+            raise ValueError(f"adapter '{aid}' is already loaded")
+        self.loaded[aid] = path
+        return _FakeAdapter()
+
+    def unload_adapter(self, aid):
+        return self.loaded.pop(aid, None) is not None
+
+
+class _FakeEngine:
+    tokenizer = None
+
+    def __init__(self):
+        self.lora_manager = _FakeManager()
+
+
+def test_lora_load_and_unload_through_the_routes(tmp_path):
+    eng = _FakeEngine()
+    s = ZSEServer(engine=eng, admin_key="admin-secret", db_path=":memory:", quiet=True, enable_rag=False)
+    try:
+        f = tmp_path / "a.zse-lora"
+        f.write_bytes(b"x")
+        assert call(s, "POST", "/v1/lora/load", {"adapter_id": "a1"}, ADMIN)[0] == 400           # path missing
+        assert call(s, "POST", "/v1/lora/load", {"adapter_id": "a1", "path": str(tmp_path / "none")}, ADMIN)[0] == 404
+        status, out = call(s, "POST", "/v1/lora/load", {"adapter_id": "a1", "path": str(f)}, ADMIN)
+        assert status == 201 and out == {"adapter_id": "a1", "rank": 8, "alpha": 16.0, "target_modules": ["q_proj"],
+                                          "num_layers": 2, "bytes": 4096}
+        status, out = call(s, "POST", "/v1/lora/load", {"adapter_id": "a1", "path": str(f)}, ADMIN)
+        assert status == 400 and "already loaded" in out["error"]["message"]
+        assert call(s, "GET", "/v1/lora/list")[1] == {"adapters": [{"adapter_id": "a1"}]}
+        assert call(s, "GET", "/v1/lora/stats")[1] == {"num_adapters": 1}
+        assert call(s, "POST", "/v1/lora/unload", {"adapter_id": "a1"}, ADMIN) == (200, {"unloaded": "a1"})
+        assert call(s, "POST", "/v1/lora/unload", {"adapter_id": "a1"}, ADMIN)[0] == 404
+        assert call(s, "GET", "/health")[1]["engine"] == "running"
+    finally:
+        s.database.close()
