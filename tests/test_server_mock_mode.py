@@ -54,14 +54,17 @@ def test_health_reports_mock_mode(srv):
 def test_models_list_names_the_served_model(srv):
     status, out = call(srv, "GET", "/v1/models")
     assert status == 200 and out["object"] == "list"
-    assert [m["id"] for m in out["data"]][0] == "mock-model"
+    assert [m["id"] for m in out["data"]] == ["mock-model"]
+    m = out["data"][0]
+    assert m["object"] == "model" and m["owned_by"] == "zse" and m["permission"] == [] and isinstance(m["created"], int)
 
 
 def test_chat_completion_has_the_openai_shape(srv):
     status, out = call(srv, "POST", "/v1/chat/completions",
                        {"model": "mock-model", "messages": [{"role": "user", "content": "hi"}]})
     assert status == 200 and out["object"] == "chat.completion" and out["model"] == "mock-model"
-    assert out["id"].startswith("chatcmpl-") and isinstance(out["created"], int)
+    assert out["id"].startswith("chatcmpl-") and len(out["id"]) == len("chatcmpl-") + 24 and isinstance(out["created"], int)
+    int(out["id"][len("chatcmpl-"):], 16)
     choice = out["choices"][0]
     assert choice["index"] == 0 and choice["finish_reason"] == "stop"
     assert choice["message"] == {"role": "assistant", "content": "This is a mock response (no model loaded)."}
@@ -258,5 +261,8 @@ def test_lora_load_and_unload_through_the_routes(tmp_path):
         assert call(s, "POST", "/v1/lora/unload", {"adapter_id": "a1"}, ADMIN) == (200, {"unloaded": "a1"})
         assert call(s, "POST", "/v1/lora/unload", {"adapter_id": "a1"}, ADMIN)[0] == 404
         assert call(s, "GET", "/health")[1]["engine"] == "running"
+        # every loaded adapter is also a model name "<model>:<adapter>"
+        call(s, "POST", "/v1/lora/load", {"adapter_id": "a2", "path": str(f)}, ADMIN)
+        assert [m["id"] for m in call(s, "GET", "/v1/models")[1]["data"]] == ["zse-model", "zse-model:a2"]
     finally:
         s.database.close()
