@@ -234,3 +234,22 @@ def test_bench_defaults_follow_the_driver_contract(monkeypatch):
     assert a.model == "qwen2.5-72b" and a.requests == 160
     assert set(bench.WORKLOADS) == {"batch64", "single", "spec32b", "lora72b"}
     assert bench.WORKLOADS["spec32b"]["spec_k"] == 4 and bench.WORKLOADS["batch64"]["spec_k"] == 0
+
+
+def test_diagnostic_tools_describe_their_options_without_a_gpu():
+    """`microbench` and `kernel_counters` parse their arguments before they touch a device: `--help` works anywhere and
+    names the options the profile summaries use."""
+    import subprocess
+    import sys
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, PYTHONPATH=root)
+    for module, options in (("zse_b200.runtime.microbench", ("--shape", "--tokens", "--only", "--kv-block", "--tp")),
+                            ("zse_b200.runtime.kernel_counters", ("--shape", "--tokens", "--tp", "--kernel", "--kv-block"))):
+        r = subprocess.run([sys.executable, "-m", module, "--help"], capture_output=True, text=True, timeout=120,
+                           env=env, cwd=root)
+        assert r.returncode == 0, r.stderr[-1500:]
+        for opt in options:
+            assert opt in r.stdout, (module, opt)
+    r = subprocess.run([sys.executable, "-m", "zse_b200.runtime.kernel_counters", "--kernel", "nonsense"],
+                       capture_output=True, text=True, timeout=120, env=env, cwd=root)
+    assert r.returncode == 2 and "invalid choice" in r.stderr
