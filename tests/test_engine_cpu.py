@@ -338,3 +338,66 @@ def test_uniform_sliding_window_matches_oracle(tmp_path):
     for o, w in zip(_run(eng, prompts, 12), want):
         assert o.output_tokens == w
     eng.destroy()
+
+
+def test_a_device_fault_ends_the_requests_and_marks_the_engine(model_path):
+    """A kernel fault reported by the runtime (injected here on the host: the runner's decode raises what torch raises)
+    finishes the running requests with an error, leaves the engine answering, and is visible as `fatal_error` - and as
+    a 503 of the server's health route - so that a supervisor restarts the worker.  An ordinary error of one pass does
+    not mark the engine."""
+    import asyncio
+    import json
+
+    from zse_b200.sched.batch_runner import is_device_fault
+    from zse_b200.server.app import ZSEServer
+    from zse_b200.server.router import Request
+    assert is_device_fault(RuntimeError("CUDA error: unspecified launch failure\nSearch for ..."))
+    assert is_device_fault(RuntimeError("CUDA error: an illegal memory access was encountered"))
+    assert not is_device_fault(RuntimeError("CUDA error: out of memory"))
+    assert not is_device_fault(ValueError("CUDA error: unspecified launch failure"))
+    assert not is_device_fault(RuntimeError("device reported: wait timed out (block 3, site 1, detail 5)"))
+
+    eng = ZStreamerEngine(model_path, config=_cfg())
+    srv = ZSEServer(engine=eng, db_path=":memory:", quiet=True, enable_rag=False)
+
+    def health():
+        resp = asyncio.new_event_loop().run_until_complete(srv.router.handle(Request("GET", "/health")))
+        return resp.status, json.loads(resp.body)
+
+    prompts = _prompts(eng.model_config.vocab_size, 3)
+    ids = [eng.add_request_tokens(p, max_tokens=8, temperature=0.0, stop_tokens=[]) for p in prompts]
+    for _ in range(3):
+        eng.step()
+    assert eng.fatal_error is None and health() == (200, {"status": "ok", "model": "zse-model", "engine": "running"})
+
+    real_decode = eng.runner.decode
+    calls = {"n": 0}
+
+    def one_bad_pass(*a, **kw):                      # an error that is NOT a device fault: the engine stays healthy
+        calls["n"] += 1
+        raise ValueError("bad argument in this pass")
+
+    eng.runner.decode = one_bad_pass
+    res = eng.step()
+    assert res.errors and eng.fatal_error is None
+    assert all(eng.get_result(i).finish_reason == FinishReason.ERROR for i in ids)
+
+    more = [eng.add_request_tokens(p, max_tokens=8, temperature=0.0, stop_tokens=[]) for p in prompts]
+
+    def faulting(*a, **kw):
+        raise RuntimeError("CUDA error: unspecified launch failure\nCUDA kernel errors might be asynchronously reported")
+
+    eng.runner.decode = faulting
+    for _ in range(6):
+        eng.step()
+        if eng.fatal_error:
+            break
+    assert eng.fatal_error and "unspecified launch failure" in eng.fatal_error and "\n" not in eng.fatal_error
+    outs = [eng.get_result(i) for i in more]
+    assert all(o.finish_reason == FinishReason.ERROR and "launch failure" in o.error for o in outs)
+    status, body = health()
+    assert status == 503 and body["status"] == "error" and body["engine"] == "failed" and "launch failure" in body["error"]
+    eng.runner.decode = real_decode
+    assert eng.step() is not None                    # the loop itself keeps running
+    srv.database.close()
+    eng.destroy()

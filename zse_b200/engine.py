@@ -298,6 +298,13 @@ class ZStreamerEngine:
     def has_work(self) -> bool:
         return self._scheduler.num_active > 0 or self._scheduler.num_waiting > 0
 
+    @property
+    def fatal_error(self) -> Optional[str]:
+        """The device fault that ended this process's CUDA context, if there was one (None while the engine is
+        healthy).  Requests submitted afterwards finish with an error; the server's health route reports it so that a
+        supervisor can restart the worker."""
+        return self._batch_runner.fatal_error
+
     def run(self, idle_sleep_ms: float = 1.0, idle_sleep_s: Optional[float] = None) -> None:
         """Serving loop (call from a dedicated thread); returns after ``stop()``.  ``idle_sleep_ms`` as in the
         reference (zse-engine/zse_engine/zstreamer/engine.py:541); ``idle_sleep_s`` overrides it."""

@@ -60,9 +60,19 @@ class _InFlight:
     pending: object                           # callable: waits for the step's tokens
 
 
+def is_device_fault(exc: BaseException) -> bool:
+    """Errors after which the device context of the process cannot be used again (a kernel fault reported by the CUDA
+    runtime), as opposed to errors of one request or one pass (a bad argument, a bounded wait that ran out)."""
+    text = str(exc)
+    return isinstance(exc, RuntimeError) and "CUDA error" in text and any(
+        w in text for w in ("launch failure", "illegal memory access", "illegal instruction", "misaligned address",
+                            "device-side assert", "unspecified"))
+
+
 class BatchRunner:
     def __init__(self, runner: ModelRunner, scheduler: Scheduler, spec_runner=None, lora_manager=None,
                  pipeline_decode: bool = False):
+        self.fatal_error: Optional[str] = None   # set by the first device fault; the engine must then be restarted
         self._pipeline = bool(pipeline_decode)
         self._inflight: Optional[_InFlight] = None
         self.ahead_launches = 0          # decode steps launched before the step ahead of them had been read
@@ -144,6 +154,10 @@ class BatchRunner:
     def _fail(self, r: InferenceRequest, exc: Exception, res: StepResult) -> None:
         self._sched.on_request_error(r, f"{type(exc).__name__}: {exc}")
         res.errors.append(f"{r.request_id}: {exc}")
+        if self.fatal_error is None and is_device_fault(exc):
+            # the CUDA context of this process is gone: every later launch fails the same way.  The engine keeps
+            # answering (requests finish with an error), says so through `fatal_error`, and has to be restarted
+            self.fatal_error = " ".join(f"{type(exc).__name__}: {exc}".split())[:300]
 
     # ---- prefill ----------------------------------------------------------------------------------------
     def _run_prefill(self, plan: SchedulerOutput, res: StepResult) -> None:

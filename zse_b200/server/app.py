@@ -107,6 +107,10 @@ class ZSEServer:
         return await handler(request)
 
     async def _health(self, request: Request) -> Response:
+        fatal = getattr(self._engine, "fatal_error", None) if self._engine is not None else None
+        if fatal:          # the engine lost its device context: tell the supervisor (503) instead of pretending
+            return Response.json_response({"status": "error", "model": self.model_name, "engine": "failed",
+                                           "error": fatal}, 503)
         return Response.json_response({"status": "ok", "model": self.model_name,
                                        "engine": "running" if self._engine is not None else "mock"})
 
