@@ -253,3 +253,42 @@ def test_diagnostic_tools_describe_their_options_without_a_gpu():
     r = subprocess.run([sys.executable, "-m", "zse_b200.runtime.kernel_counters", "--kernel", "nonsense"],
                        capture_output=True, text=True, timeout=120, env=env, cwd=root)
     assert r.returncode == 2 and "invalid choice" in r.stderr
+
+
+def test_serve_leaves_with_a_non_zero_code_after_a_device_fault(monkeypatch, capsys):
+    """`zse serve` watches the engine: once it reports a device fault the command prints it and returns 3, so that a
+    supervisor starts a fresh process.  The server here is a stand-in whose engine "faults" after half a second."""
+    import argparse
+    import threading
+    import time as _time
+
+    import zse_b200.cli as cli
+    import zse_b200.server.app as app
+
+    class Engine:
+        fatal_error = None
+
+    class Server:
+        def __init__(self, *a, **kw):
+            self.engine = Engine()
+            self.closed = False
+            threading.Timer(0.5, lambda: setattr(self.engine, "fatal_error",
+                                                  "RuntimeError: CUDA error: unspecified launch failure")).start()
+
+        async def start(self):
+            return None
+
+        def close(self):
+            self.closed = True
+
+    made = []
+    monkeypatch.setattr(app, "ZSEServer", lambda *a, **kw: made.append(Server()) or made[-1])
+    monkeypatch.setattr(cli.signal, "signal", lambda *a: None)          # not the main thread's business in a test
+    ns = argparse.Namespace(model=None, host="127.0.0.1", port=0, admin_key="adm", db_path=":memory:",
+                            model_name="m", quiet=True, tp_size=1, max_seq_len=0, max_batch_seqs=4,
+                            prefill_chunk_size=512, speculative_k=0, speculative_mode="ngram", no_graphs=False,
+                            comm="fused", cpu=True, require_auth=False)
+    t0 = _time.monotonic()
+    rc = cli._cmd_serve(ns)
+    assert rc == 3 and made[0].closed and 0.4 < _time.monotonic() - t0 < 10
+    assert "device fault, shutting down" in capsys.readouterr().err

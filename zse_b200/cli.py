@@ -39,15 +39,29 @@ def _cmd_serve(a) -> int:
     def shutdown(*_):
         loop.call_soon_threadsafe(loop.stop)
 
+    rc = [0]
+
+    def watch_engine():
+        # a device fault ends the CUDA context of this process for good: leave with a non-zero code, so that whatever
+        # supervises the server (systemd, a container runtime) starts a fresh one, instead of answering 503 for ever
+        fatal = getattr(server.engine, "fatal_error", None) if server.engine is not None else None
+        if fatal:
+            print(f"[zse] device fault, shutting down: {fatal}", file=sys.stderr)
+            rc[0] = 3
+            loop.stop()
+            return
+        loop.call_later(1.0, watch_engine)
+
     signal.signal(signal.SIGINT, shutdown)
     signal.signal(signal.SIGTERM, shutdown)
     try:
         loop.run_until_complete(server.start())
+        loop.call_later(1.0, watch_engine)
         loop.run_forever()
     finally:
         server.close()
         loop.close()
-    return 0
+    return rc[0]
 
 
 def _cmd_convert(a) -> int:
