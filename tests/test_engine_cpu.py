@@ -401,3 +401,22 @@ def test_a_device_fault_ends_the_requests_and_marks_the_engine(model_path):
     assert eng.step() is not None                    # the loop itself keeps running
     srv.database.close()
     eng.destroy()
+
+
+def test_metrics_route_reports_the_engine(model_path):
+    import asyncio
+
+    from zse_b200.server.app import ZSEServer
+    from zse_b200.server.router import Request
+    eng = ZStreamerEngine(model_path, config=_cfg())
+    srv = ZSEServer(engine=eng, db_path=":memory:", quiet=True, enable_rag=False)
+    _run(eng, _prompts(eng.model_config.vocab_size, 3), 5)
+    resp = asyncio.new_event_loop().run_until_complete(srv.router.handle(Request("GET", "/metrics")))
+    vals = {l.split(" ")[0]: float(l.split(" ")[1]) for l in resp.body.decode().splitlines() if l and l[0] != "#"}
+    assert resp.status == 200 and vals["zse_engine_up"] == 1
+    assert vals["zse_requests_total"] == 3 and vals["zse_tokens_generated_total"] == 15 and vals["zse_steps_total"] > 0
+    assert vals["zse_requests_active"] == 0 and vals["zse_requests_waiting"] == 0
+    assert vals["zse_kv_blocks"] == eng.kv_cache.num_total_blocks and vals["zse_kv_blocks_used"] == 0
+    assert vals["zse_ttft_p50_milliseconds"] > 0
+    srv.database.close()
+    eng.destroy()

@@ -266,3 +266,28 @@ def test_lora_load_and_unload_through_the_routes(tmp_path):
         assert [m["id"] for m in call(s, "GET", "/v1/models")[1]["data"]] == ["zse-model", "zse-model:a2"]
     finally:
         s.database.close()
+
+
+# ---- /metrics ---------------------------------------------------------------------------------------------------
+def _metrics(text):
+    out = {}
+    for line in text.decode().splitlines():
+        if line and not line.startswith("#"):
+            name, value = line.split(" ")
+            out[name] = float(value)
+    return out
+
+
+def test_metrics_in_prometheus_text_format(srv, locked):
+    key = new_key(srv)
+    srv.database.record_usage(key["id"], 10, 5)
+    req = Request("GET", "/metrics")
+    resp = asyncio.new_event_loop().run_until_complete(srv.router.handle(req))
+    assert resp.status == 200 and resp.headers["Content-Type"].startswith("text/plain; version=0.0.4")
+    text = resp.body.decode()
+    assert "# TYPE zse_engine_up gauge" in text and "# HELP zse_api_tokens_total" in text and text.endswith("\n")
+    m = _metrics(resp.body)
+    assert m["zse_engine_up"] == 0 and m["zse_api_requests_total"] == 1 and m["zse_api_tokens_total"] == 15
+    # where keys are required the numbers are for the admin only
+    assert call(locked, "GET", "/metrics")[0] == 403
+    assert call(locked, "GET", "/metrics", headers=ADMIN)[0] == 200

@@ -9,8 +9,9 @@ from .router import Request, Response
 
 
 class AdminAPI:
-    def __init__(self, db, auth, engine=None):
+    def __init__(self, db, auth, engine=None, require_auth: bool = False):
         self._db, self._auth, self._engine = db, auth, engine
+        self.require_auth = require_auth
 
     def register(self, router) -> None:
         router.post("/v1/admin/keys/create", self.create_key)
@@ -18,6 +19,7 @@ class AdminAPI:
         router.post("/v1/admin/keys/revoke", self.revoke_key)
         router.post("/v1/admin/keys/update", self.update_key)
         router.get("/v1/admin/stats", self.stats)
+        router.get("/metrics", self.metrics)
         router.get("/v1/admin/usage", self.usage)
         router.post("/v1/dashboard/session", self.session_create)
         router.get("/v1/dashboard/sessions", self.session_list)
@@ -85,6 +87,50 @@ class AdminAPI:
                 out["speculative"] = spec.stats()
             out["init_times"] = getattr(e, "init_times", {})
         return Response.json_response(out)
+
+    async def metrics(self, request: Request) -> Response:
+        """Counters and gauges of the engine in the Prometheus text exposition format (no counterpart in the reference,
+        whose numbers are only available as JSON from ``/v1/admin/stats``).  On a server that requires keys the route
+        wants the admin key; otherwise it is open, like ``/health``."""
+        if getattr(self, "require_auth", False) and (r := self._deny(request)) is not None:
+            return r
+        rows = []          # (name, type, help, value)
+
+        def add(name, kind, text, value):
+            rows.append((name, kind, text, float(value)))
+
+        e = self._engine
+        fatal = getattr(e, "fatal_error", None) if e is not None else None
+        add("zse_engine_up", "gauge", "1 while the engine can run requests, 0 without an engine or after a device fault",
+            0 if (e is None or fatal) else 1)
+        if e is not None and hasattr(e, "stats"):
+            st = e.stats()
+            add("zse_requests_total", "counter", "requests finished", getattr(st, "total_requests", 0))
+            add("zse_tokens_generated_total", "counter", "tokens generated", getattr(st, "total_tokens_generated", 0))
+            add("zse_steps_total", "counter", "engine steps that ran a batch", getattr(st, "total_steps", 0))
+            add("zse_uptime_seconds", "gauge", "seconds since the first step", getattr(st, "uptime_s", 0.0))
+            add("zse_requests_waiting", "gauge", "requests in the queue", getattr(st, "queue_depth", 0))
+            add("zse_requests_active", "gauge", "requests being prefilled or decoded", getattr(st, "active_requests", 0))
+            add("zse_ttft_p50_milliseconds", "gauge", "median time to first token", getattr(st, "p50_ttft_ms", 0.0))
+            add("zse_ttft_p99_milliseconds", "gauge", "99th percentile of time to first token",
+                getattr(st, "p99_ttft_ms", 0.0))
+            add("zse_tpot_p50_milliseconds", "gauge", "median time per output token", getattr(st, "p50_tpot_ms", 0.0))
+            add("zse_batch_tokens_avg", "gauge", "tokens generated per step on average", getattr(st, "avg_batch_size", 0.0))
+            if hasattr(e, "kv_cache"):
+                kv = e.kv_cache.stats()
+                add("zse_kv_blocks", "gauge", "KV cache blocks in the pool", kv.total_blocks)
+                add("zse_kv_blocks_used", "gauge", "KV cache blocks in use", kv.allocated_blocks)
+                add("zse_kv_sequences", "gauge", "sequences holding KV blocks", kv.num_sequences)
+                add("zse_kv_evictions_total", "counter", "KV blocks evicted under memory pressure", kv.eviction_count)
+                add("zse_kv_prefix_hits_total", "counter", "prompt blocks served from the prefix cache", kv.dedup_hits)
+        usage = self._db.get_usage_stats()
+        add("zse_api_requests_total", "counter", "requests accounted to API keys", usage["total_requests"])
+        add("zse_api_tokens_total", "counter", "tokens accounted to API keys", usage["total_tokens"])
+        lines = []
+        for name, kind, text, value in rows:
+            lines += [f"# HELP {name} {text}", f"# TYPE {name} {kind}",
+                      f"{name} {int(value) if value == int(value) else repr(value)}"]
+        return Response.text("\n".join(lines) + "\n", content_type="text/plain; version=0.0.4; charset=utf-8")
 
     async def usage(self, request: Request) -> Response:
         if (r := self._deny(request)) is not None:

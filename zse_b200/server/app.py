@@ -46,7 +46,7 @@ class ZSEServer:
         self.router.get("/v1/health", self._health)
         self._openai = OpenAIAPI(self._engine, model_name, tok, db=self._db)
         self._openai.register(self.router)
-        AdminAPI(self._db, self._auth, self._engine).register(self.router)
+        AdminAPI(self._db, self._auth, self._engine, require_auth=require_auth).register(self.router)
         LoRAAPI(self._engine, self._auth).register(self.router)
         self._rag_engine = None
         if enable_rag:
