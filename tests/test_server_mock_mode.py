@@ -291,3 +291,18 @@ def test_metrics_in_prometheus_text_format(srv, locked):
     # where keys are required the numbers are for the admin only
     assert call(locked, "GET", "/metrics")[0] == 403
     assert call(locked, "GET", "/metrics", headers=ADMIN)[0] == 200
+
+
+def test_session_save_route_of_the_reference(srv):
+    key = new_key(srv)
+    auth = {"authorization": "Bearer " + key["key"]}
+    body = {"session_id": "s-1", "role": "user", "content": "hello", "model": "mock-model"}
+    assert call(srv, "POST", "/v1/dashboard/session/save", body)[0] == 401
+    assert call(srv, "POST", "/v1/dashboard/session/save", body, auth) == (200, {"ok": True})
+    assert call(srv, "POST", "/v1/dashboard/session/save", dict(body, content=""), auth)[0] == 400
+    assert call(srv, "POST", "/v1/dashboard/session/save", {"role": "user", "content": "x"}, auth)[0] == 400
+    call(srv, "POST", "/v1/dashboard/session/save", dict(body, role="assistant", content="hi", lora_id="ad"), auth)
+    msgs = call(srv, "GET", "/v1/dashboard/session/s-1", headers=auth)[1]["messages"]
+    assert [(m["role"], m["content"]) for m in msgs] == [("user", "hello"), ("assistant", "hi")]
+    # "save" is a route of its own, not a session id
+    assert call(srv, "GET", "/v1/dashboard/session/save", headers=auth)[1]["messages"] == []

@@ -22,6 +22,7 @@ class AdminAPI:
         router.get("/metrics", self.metrics)
         router.get("/v1/admin/usage", self.usage)
         router.post("/v1/dashboard/session", self.session_create)
+        router.post("/v1/dashboard/session/save", self.session_save)      # before the {session_id} patterns
         router.get("/v1/dashboard/sessions", self.session_list)
         router.get("/v1/dashboard/session/{session_id}", self.session_get)
         router.post("/v1/dashboard/session/{session_id}/message", self.session_add_message)
@@ -173,6 +174,19 @@ class AdminAPI:
                                     str(b.get("model", "")), b.get("lora_id"))
         return Response.json_response({"id": mid}, 201)
 
+    async def session_save(self, request: Request) -> Response:
+        """``POST /v1/dashboard/session/save {session_id, role, content, model?, lora_id?}`` - the reference's form of
+        adding a message, the session named in the body (zse-engine/zse_engine/server/api_admin.py:265-289)."""
+        res = self._auth.authenticate(request.authorization)
+        if not res.authenticated:
+            return Response.error(res.error, res.status_code)
+        b = request.json if isinstance(request.json, dict) else {}
+        sid, role, content = str(b.get("session_id", "")), str(b.get("role", "")), str(b.get("content", ""))
+        if not sid or not role or not content:
+            return Response.error("session_id, role, and content are required")
+        self._db.save_message(res.key.id, sid, role, content, str(b.get("model", "")), b.get("lora_id"))
+        return Response.json_response({"ok": True})
+
     async def session_delete(self, request: Request) -> Response:
         if self._key_id(request) is None:
             return Response.error("authentication required", 401)
@@ -188,4 +202,4 @@ class AdminAPI:
     handle_list_sessions = session_list
     handle_get_session = session_get
     handle_delete_session = session_delete
-    handle_save_message = session_add_message
+    handle_save_message = session_save
