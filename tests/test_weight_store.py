@@ -277,3 +277,17 @@ def test_package_level_names():
         assert not [n for n in names if not hasattr(m, n)], mod
     with pytest.raises(AttributeError):
         importlib.import_module("zse_b200.runtime").NoSuchThing
+
+
+def test_top_level_names_are_lazy():
+    """`import zse_b200` stays cheap (no torch); the main classes resolve on first use."""
+    import os
+    import subprocess
+    import sys
+    code = ("import sys, zse_b200; assert 'torch' not in sys.modules; "
+            "assert zse_b200.ZSEEngine.__name__ == 'ZSEEngine' and zse_b200.ZStreamerEngine and zse_b200.EngineConfig; "
+            "assert 'ZSEServer' in dir(zse_b200)\n"
+            "try:\n    zse_b200.not_a_name\nexcept AttributeError:\n    print('ok')")
+    r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=240,
+                       cwd=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    assert r.returncode == 0 and r.stdout.strip() == "ok", r.stderr[-1500:]
