@@ -17,12 +17,14 @@ This is the counterpart of the reference's ``zse_compiler`` package (zse-compile
 one target instead of three.  The engine's hot kernels are hand-written CUDA (``csrc/``); this package is for the
 surrounding element-wise and reduction work a user wants to add without writing C++."""
 from ..runtime.device import DeviceInfo, detect_backend, get_devices
-from ..runtime.profiler import AutoTuner, KernelProfiler
+from ..runtime.profiler import AutoTuner, KernelProfile, KernelProfiler, TuneResult
 from .compiler import CompiledKernel, RuntimeCompiler
 from .dtypes import (DType, Tensor, bfloat16, empty, float16, float32, int4, int8, int16, int32, uint4, uint8, uint16,
                      uint32, zeros)
 from .emulate import KernelRaceError, RaceTracker
-from .errors import KernelCompileError, KernelError, KernelLaunchError, KernelSyntaxError, KernelTypeError
+from .codegen import BaseCodegen, CUDACodegen
+from .errors import (KernelCompileError, KernelError, KernelLaunchError, KernelSyntaxError, KernelTypeError,
+                     SourceLocation)
 from .infer import infer as infer_types
 from .parser import validate_kernel
 
@@ -36,5 +38,6 @@ from .primitives import __all__ as _prims
 __all__ = ["kernel", "fuse", "KernelFunction", "DType", "Tensor", "empty", "zeros", "float16", "float32", "bfloat16",
            "int32", "int16", "int8", "uint32", "uint16", "uint8", "int4", "uint4", "detect_backend", "get_devices",
            "DeviceInfo", "GPUMemory", "RuntimeCompiler", "CompiledKernel", "KernelLauncher", "LaunchConfig", "PrepackedArgs",
-           "KernelProfiler", "AutoTuner", "KernelError", "KernelSyntaxError", "KernelTypeError", "KernelCompileError",
+           "KernelProfiler", "KernelProfile", "AutoTuner", "TuneResult", "SourceLocation", "BaseCodegen", "CUDACodegen",
+           "KernelError", "KernelSyntaxError", "KernelTypeError", "KernelCompileError",
            "KernelLaunchError", "KernelRaceError", "RaceTracker"] + list(_prims)

@@ -429,3 +429,22 @@ class CudaEmitter:
 
 def generate_cuda(k: TypedKernel, line_info: bool = False) -> str:
     return CudaEmitter(line_info).generate(k)
+
+
+class BaseCodegen:
+    """The reference's generator object (zse-compiler/zse_compiler/codegen/base.py:36-60): ``generate(kernel)`` returns
+    the source text.  ``kernel`` is a typed kernel, or a ``@kernel`` function (typed with its default element types).
+    There is one target here, so the base class already produces CUDA."""
+    backend = "cuda"
+
+    def __init__(self, line_info: bool = False):
+        self.line_info = line_info
+
+    def generate(self, kernel) -> str:
+        typed = kernel.typed(None) if hasattr(kernel, "typed") else kernel
+        return generate_cuda(typed, self.line_info)
+
+
+class CUDACodegen(BaseCodegen):
+    """CUDA C for sm_100a (zse-compiler/zse_compiler/codegen/cuda.py:40-488 is the reference's generator)."""
+

@@ -18,6 +18,15 @@ class DType:
     def nbytes(self) -> float:
         return self.bits / 8
 
+    def size_bytes(self) -> int:
+        """Whole bytes one element occupies (4-bit types round up to 1), the reference's accessor
+        (zse-compiler/zse_compiler/types/dtypes.py:14-15)."""
+        return (self.bits + 7) // 8
+
+    @property
+    def size_bits(self) -> int:
+        return self.bits
+
     @property
     def is_float(self) -> bool:
         return self.kind == "float"
@@ -106,6 +115,37 @@ class Tensor(metaclass=_TensorMeta):
     @property
     def data_ptr(self) -> int:
         return int(self.data.data_ptr()) if self.data is not None else 0
+
+    # descriptor helpers of the reference (zse-compiler/zse_compiler/types/tensor.py:69-107)
+    @property
+    def device(self) -> str:
+        return str(self.data.device) if self.data is not None else "cpu"
+
+    @property
+    def strides(self) -> Tuple[int, ...]:
+        """Row-major strides in elements (descriptors are always dense)."""
+        out, acc = [], 1
+        for dim in reversed(self.shape):
+            out.append(acc)
+            acc *= dim
+        return tuple(reversed(out))
+
+    def is_contiguous(self) -> bool:
+        return self.data is None or not hasattr(self.data, "is_contiguous") or bool(self.data.is_contiguous())
+
+    def reshape(self, *new_shape: int) -> "Tensor":
+        """A descriptor of the same storage under another shape (the element count must match)."""
+        if len(new_shape) == 1 and isinstance(new_shape[0], (tuple, list)):
+            new_shape = tuple(new_shape[0])
+        n = 1
+        for dim in new_shape:
+            n *= int(dim)
+        if n != self.numel:
+            raise ValueError(f"Cannot reshape {self.shape} ({self.numel} elements) to {tuple(new_shape)} ({n} elements)")
+        data = self.data
+        if data is not None and self.dtype.torch_name and hasattr(data, "reshape"):
+            data = data.reshape(tuple(int(d) for d in new_shape))
+        return Tensor(tuple(new_shape), self.dtype, data)
 
     def __repr__(self) -> str:
         return f"Tensor(shape={self.shape}, dtype={self.dtype}, {'allocated' if self.data is not None else 'no storage'})"

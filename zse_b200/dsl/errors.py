@@ -2,7 +2,21 @@
 (zse-compiler/zse_compiler/errors.py:13-92)."""
 from __future__ import annotations
 
+from dataclasses import dataclass
 from typing import Optional
+
+
+@dataclass
+class SourceLocation:
+    """A place in the Python source of a kernel (zse-compiler/zse_compiler/errors.py:13-26); ``KernelError`` carries the
+    same facts as ``filename`` / ``lineno`` / ``source_line`` and returns them in this form from ``location``."""
+    file: str
+    line: int
+    col: int = 0
+    text: str = ""
+
+    def __str__(self) -> str:
+        return f"{self.file}:{self.line}" + (f"\n  {self.text.strip()}" if self.text else "")
 
 
 class KernelError(Exception):
@@ -16,6 +30,12 @@ class KernelError(Exception):
         if source_line:
             text += "\n    " + source_line.strip()
         super().__init__(text)
+
+    @property
+    def location(self) -> Optional[SourceLocation]:
+        if self.lineno is None:
+            return None
+        return SourceLocation(self.filename or "<kernel>", int(self.lineno), 0, self.source_line or "")
 
 
 class KernelSyntaxError(KernelError):

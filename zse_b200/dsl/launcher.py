@@ -9,7 +9,7 @@ from __future__ import annotations
 
 import ctypes
 from dataclasses import dataclass
-from typing import Any, List, Sequence, Tuple
+from typing import Any, List, Optional, Sequence, Tuple
 
 from . import dtypes
 from .compiler import CompiledKernel, _check, _driver
@@ -110,6 +110,41 @@ class PrepackedArgs:
         new = pack_args([self._ctypes[index]], [value], [self._elems[index]])[0]
         self.values[index].value = new.value            # same storage, so ``array`` stays valid
 
+    # ---- the reference's way of building and updating the array (launcher.py:251-318 there) -------------------------
+    @classmethod
+    def from_args(cls, *args) -> "PrepackedArgs":
+        """From values alone: tensors (descriptors, torch tensors) and raw addresses become pointers, ints ``int``,
+        floats ``float``.  The typed constructor above additionally checks element types against the kernel."""
+        ctypes_of, args = [], list(args)
+        for i, a in enumerate(args):
+            if isinstance(a, dtypes.Tensor) or hasattr(a, "data_ptr"):
+                ctypes_of.append("void*")
+                if isinstance(a, dtypes.Tensor) and a.data is None:
+                    args[i] = int(a.data_ptr)          # a bare description: its address (0) is filled in by set_ptr
+            elif isinstance(a, bool):
+                ctypes_of.append("bool")
+            elif isinstance(a, int):
+                ctypes_of.append("int")
+            elif isinstance(a, float):
+                ctypes_of.append("float")
+            else:
+                raise TypeError(f"Unsupported arg type: {type(a)}")
+        return cls(ctypes_of, list(args))
+
+    def set_ptr(self, index: int, ptr_value: int) -> None:
+        self.values[index].value = int(ptr_value)
+
+    def set_int(self, index: int, value: int) -> None:
+        self.values[index].value = int(value)
+
+    def set_float(self, index: int, value: float) -> None:
+        self.values[index].value = float(value)
+
+    @property
+    def arg_array(self):
+        """The ``void**`` array handed to the driver (stable for the life of the object)."""
+        return self.array
+
     def __len__(self) -> int:
         return len(self.values)
 
@@ -119,6 +154,13 @@ class PrepackedArgs:
 
 
 class KernelLauncher:
+    def sync(self, compiled: Optional[CompiledKernel] = None) -> None:
+        """Waits for everything launched so far (launches are asynchronous).  Without a device there is nothing to
+        wait for."""
+        import torch
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
+
     def launch_prepacked(self, compiled: CompiledKernel, config: LaunchConfig, prepacked: PrepackedArgs,
                          stream=None) -> None:
         self.launch(compiled, config, prepacked.values, stream)

@@ -105,6 +105,82 @@ class GPUMemory:
     def get_total_memory(self) -> int:
         return int(torch.cuda.mem_get_info(self.device)[1]) if self.device.type == "cuda" else 0
 
+    # ---- raw addresses (zse-compiler/zse_compiler/runtime/memory.py:176-354) --------------------------------------
+    # The reference hands out bare device and pinned-host addresses; here each address is backed by a torch byte tensor
+    # that this object keeps alive until the matching free.
+    def _raw_tables(self):
+        if not hasattr(self, "_raw"):
+            self._raw: Dict[int, torch.Tensor] = {}
+            self._pinned: Dict[int, torch.Tensor] = {}
+        return self._raw, self._pinned
+
+    def malloc_raw(self, nbytes: int) -> int:
+        if nbytes <= 0:
+            return 0
+        raw, _ = self._raw_tables()
+        t = torch.empty(int(nbytes), dtype=torch.uint8, device=self.device)
+        raw[int(t.data_ptr())] = t
+        self._allocated += int(nbytes)
+        self._peak = max(self._peak, self._allocated)
+        return int(t.data_ptr())
+
+    def free_raw(self, ptr: int) -> None:
+        raw, _ = self._raw_tables()
+        t = raw.pop(int(ptr), None)
+        if t is not None:
+            self._allocated -= t.numel()
+
+    def _raw_view(self, ptr: int, nbytes: int) -> torch.Tensor:
+        """The bytes ``[ptr, ptr + nbytes)`` of one of this object's raw allocations."""
+        raw, _ = self._raw_tables()
+        for base, t in raw.items():
+            if base <= ptr and ptr + nbytes <= base + t.numel():
+                return t[ptr - base: ptr - base + nbytes]
+        raise ValueError(f"{nbytes} bytes at {ptr:#x} are not inside an allocation of malloc_raw")
+
+    @staticmethod
+    def _host_view(ptr: int, nbytes: int) -> torch.Tensor:
+        import ctypes
+        return torch.frombuffer((ctypes.c_ubyte * int(nbytes)).from_address(int(ptr)), dtype=torch.uint8)
+
+    def copy_host_to_device_raw(self, host_data: bytes, dst_ptr: int, nbytes: int) -> None:
+        if nbytes > 0:
+            src = torch.frombuffer(bytearray(host_data[:nbytes]), dtype=torch.uint8)
+            self._raw_view(int(dst_ptr), int(nbytes)).copy_(src)
+
+    def copy_host_to_device_raw_ptr(self, src_ptr: int, dst_ptr: int, nbytes: int) -> None:
+        if nbytes > 0:
+            self._raw_view(int(dst_ptr), int(nbytes)).copy_(self._host_view(src_ptr, nbytes))
+
+    def copy_host_to_device_async_raw_ptr(self, src_ptr: int, dst_ptr: int, nbytes: int, stream=None) -> None:
+        """Returns at once when the source is pinned; the caller synchronises ``stream`` before reusing the buffer."""
+        if nbytes <= 0:
+            return
+        dst, src = self._raw_view(int(dst_ptr), int(nbytes)), self._host_view(src_ptr, nbytes)
+        if self.device.type == "cuda" and stream is not None and hasattr(stream, "synchronize"):
+            with torch.cuda.stream(stream):
+                dst.copy_(src, non_blocking=True)
+        else:
+            dst.copy_(src, non_blocking=True)
+
+    def pinned_alloc(self, nbytes: int) -> int:
+        if nbytes <= 0:
+            return 0
+        _, pinned = self._raw_tables()
+        t = self.allocate_pinned(nbytes)
+        pinned[int(t.data_ptr())] = t
+        return int(t.data_ptr())
+
+    def pinned_free(self, ptr: int) -> None:
+        self._raw_tables()[1].pop(int(ptr), None)
+
+    def destroy_stream(self, stream) -> None:
+        """Streams are torch objects here and go away with their last reference; waits for the stream's work first."""
+        self.synchronize_stream(stream)
+
+    def synchronize_stream(self, stream=None) -> None:
+        self.synchronize(stream if hasattr(stream, "synchronize") else None)
+
     @property
     def allocated_bytes(self) -> int:
         return self._allocated

@@ -10,6 +10,7 @@ reference requires divisibility), and ``lm_head`` shards are gathered properly.
 """
 from __future__ import annotations
 
+import ctypes
 import multiprocessing
 import os
 import socket
@@ -193,6 +194,29 @@ class NcclCommunicator:
 
     def __repr__(self) -> str:
         return f"NcclCommunicator(rank={self.rank}, nranks={self.nranks})"
+
+
+NCCL_UNIQUE_ID_BYTES = 128
+
+
+class NcclUniqueId(ctypes.Structure):
+    """The reference's 128-byte id record (zse-compiler/zse_compiler/runtime/nccl.py:69-71).  Here the id that ranks
+    share is the rendezvous address; ``from_address`` / ``address`` move it in and out of the record, for code that
+    passes ids around in this form."""
+    _fields_ = [("internal", ctypes.c_char * NCCL_UNIQUE_ID_BYTES)]
+
+    @classmethod
+    def from_address_string(cls, address) -> "NcclUniqueId":
+        raw = address if isinstance(address, (bytes, bytearray)) else str(address).encode()
+        if len(raw) >= NCCL_UNIQUE_ID_BYTES:
+            raise ValueError("the rendezvous address does not fit a 128-byte id")
+        uid = cls()
+        uid.internal = bytes(raw)
+        return uid
+
+    @property
+    def address(self) -> bytes:
+        return bytes(self.internal).split(b"\x00", 1)[0]
 
 
 def get_unique_id(backend: str = "cuda") -> bytes:

@@ -10,7 +10,8 @@ def __getattr__(name):
             "WeightStore": ("weight_stream", "WeightStore"), "GPUWeight": ("weight_stream", "GPUWeight"),
             "CUDAGraphRunner": ("graph", "CUDAGraphRunner"), "NativeStep": ("step_driver", "NativeStep"),
             "FastDecoder": ("step_driver", "FastDecoder"), "KernelProfiler": ("profiler", "KernelProfiler"),
-            "AutoTuner": ("profiler", "AutoTuner")}
+            "AutoTuner": ("profiler", "AutoTuner"), "KernelProfile": ("profiler", "KernelProfile"),
+            "TuneResult": ("profiler", "TuneResult"), "ProfileResult": ("profiler", "ProfileResult")}
     if name == "ZSEEngine":
         from ..engine import ZSEEngine
         return ZSEEngine

@@ -23,6 +23,29 @@ class DeviceInfo:
     def is_blackwell(self) -> bool:
         return self.compute_capability[0] == 10
 
+    # the reference's field names (zse-compiler/zse_compiler/runtime/device.py:14-40)
+    backend = "cuda"
+
+    @property
+    def vram_total_bytes(self) -> int:
+        return self.total_memory
+
+    @property
+    def vram_free_bytes(self) -> int:
+        return self.free_memory
+
+    @property
+    def vram_total_gb(self) -> float:
+        return self.total_memory / (1024 ** 3)
+
+    @property
+    def vram_free_gb(self) -> float:
+        return self.free_memory / (1024 ** 3)
+
+    @property
+    def num_sms(self) -> int:
+        return self.sm_count
+
 
 def detect_backend() -> str:
     return "cuda" if torch.cuda.is_available() else "cpu"

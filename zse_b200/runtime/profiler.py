@@ -61,6 +61,56 @@ class ProfileResult:
         return d
 
 
+@dataclass
+class KernelProfile:
+    """Time of one compiled kernel under one launch configuration, the record of the reference's profiler
+    (zse-compiler/zse_compiler/runtime/profiler.py:14-38)."""
+    kernel_name: str
+    backend: str
+    elapsed_ms: float            # per launch
+    grid: tuple
+    block: tuple
+    num_runs: int = 1
+    total_flops: Optional[int] = None
+
+    @property
+    def throughput_gflops(self) -> Optional[float]:
+        """GFLOP/s, once the caller has set ``total_flops`` (None before)."""
+        if self.total_flops is None or self.elapsed_ms <= 0:
+            return None
+        return self.total_flops / (self.elapsed_ms * 1e6)
+
+    def bandwidth_gb_s(self, total_bytes: int) -> float:
+        return 0.0 if self.elapsed_ms <= 0 else (total_bytes / 1e9) / (self.elapsed_ms / 1e3)
+
+    def __repr__(self) -> str:
+        return f"KernelProfile('{self.kernel_name}', {self.elapsed_ms:.3f}ms, grid={self.grid}, block={self.block})"
+
+
+BLOCK_SIZES_1D = [32, 64, 128, 256, 512, 1024]
+BLOCK_SIZES_2D = [(8, 8), (16, 8), (8, 16), (16, 16), (32, 8), (8, 32), (32, 16), (16, 32), (32, 32)]
+
+
+@dataclass
+class TuneResult:
+    """Outcome of a sweep over launch configurations (zse-compiler/zse_compiler/runtime/autotune.py:24-60)."""
+    kernel_name: str
+    best_config: object          # dsl.LaunchConfig
+    best_time_ms: float
+    all_results: List[KernelProfile]
+
+    def summary(self) -> str:
+        lines = [f"Auto-tune results for '{self.kernel_name}':", f"{'Config':<20} {'Time (ms)':<12} {'Speedup':<10}",
+                 "-" * 42]
+        worst = max((r.elapsed_ms for r in self.all_results), default=1.0)
+        for r in sorted(self.all_results, key=lambda x: x.elapsed_ms):
+            block = f"{r.block[0]}" + (f"x{r.block[1]}" if len(r.block) > 1 and r.block[1] > 1 else "")
+            speed = worst / r.elapsed_ms if r.elapsed_ms > 0 else 0.0
+            mark = "  <- best" if r.elapsed_ms == self.best_time_ms else ""
+            lines.append(f"  block={block:<12} {r.elapsed_ms:<12.3f} {speed:<10.2f}x{mark}")
+        return "\n".join(lines)
+
+
 class KernelProfiler:
     def __init__(self, device="cuda", warmup: int = 3, iters: int = 20, flush_l2: bool = True):
         self.device = torch.device(device)
@@ -89,6 +139,37 @@ class KernelProfiler:
             samples.append(a.elapsed_time(b))
         return ProfileResult(name, statistics.median(samples), min(samples), self.iters, nbytes, flops, dict(extra))
 
+    def profile(self, kernel, config, args: tuple, warmup_runs: int = 3, profile_runs: int = 10,
+                launcher=None) -> KernelProfile:
+        """The reference's call (zse-compiler/zse_compiler/runtime/profiler.py:47-128): a COMPILED kernel of the
+        kernel language, a ``LaunchConfig`` and the argument values.  ``args`` may be a ``PrepackedArgs`` or plain
+        values (tensors, ints, floats).  Timed with CUDA events around each launch on a GPU; where there is none (or
+        with a stand-in ``launcher`` in tests) with the wall clock, as the reference does for its other back ends."""
+        import time as _time
+        from ..dsl.launcher import KernelLauncher, PrepackedArgs
+        launcher = launcher or KernelLauncher()
+        packed = args if isinstance(args, PrepackedArgs) else PrepackedArgs.from_args(*args)
+        run = lambda: launcher.launch_prepacked(kernel, config, packed)
+        for _ in range(max(0, warmup_runs)):
+            run()
+        on_gpu = self.device.type == "cuda" and torch.cuda.is_available()
+        samples = []
+        for _ in range(max(1, profile_runs)):
+            if on_gpu:
+                self._cold()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                run()
+                b.record()
+                torch.cuda.synchronize(self.device)
+                samples.append(a.elapsed_time(b))
+            else:
+                t0 = _time.perf_counter()
+                run()
+                samples.append((_time.perf_counter() - t0) * 1000.0)
+        return KernelProfile(getattr(kernel, "name", "kernel"), "cuda" if on_gpu else "host",
+                             statistics.median(samples), tuple(config.grid), tuple(config.block), len(samples))
+
 
 class AutoTuner:
     """``tune(name, make_fn, candidates)``: ``make_fn(candidate)`` returns the launch closure; the fastest candidate
@@ -113,3 +194,47 @@ class AutoTuner:
         win = min(ok, key=lambda r: r["ms"])
         self.best[name] = {"best": win["candidate"], "ms": win["ms"], "all": results}
         return self.best[name]
+
+    # ---- the reference's sweeps over a compiled kernel (zse-compiler/zse_compiler/runtime/autotune.py:80-170) ---------
+    def _sweep(self, kernel, args, configs, what: str, launcher=None) -> TuneResult:
+        from ..dsl.errors import KernelError
+        results = []
+        for cfg in configs:
+            try:
+                results.append(self.profiler.profile(kernel, cfg, args, warmup_runs=self.profiler.warmup,
+                                                     profile_runs=self.profiler.iters, launcher=launcher))
+            except (ValueError, RuntimeError, KernelError):
+                continue                      # a configuration the kernel or the device refuses is not eligible
+        if not results:
+            raise RuntimeError(f"No valid configurations found for {what}")
+        best = min(results, key=lambda r: r.elapsed_ms)
+        from ..dsl.launcher import LaunchConfig
+        return TuneResult(getattr(kernel, "name", "kernel"), LaunchConfig(best.grid, best.block), best.elapsed_ms,
+                          results)
+
+    def tune_1d(self, kernel, args: tuple, total_threads: int, block_sizes: Optional[List[int]] = None,
+                launcher=None) -> TuneResult:
+        """Block sizes that divide ``total_threads``; the grid follows."""
+        from ..dsl.errors import KernelError
+        from ..dsl.launcher import LaunchConfig
+        configs = []
+        for bs in (block_sizes or BLOCK_SIZES_1D):
+            if bs <= total_threads and total_threads % bs == 0:
+                try:
+                    configs.append(LaunchConfig((total_threads // bs,), (bs,)))
+                except KernelError:
+                    pass
+        return self._sweep(kernel, args, configs, f"{total_threads} threads", launcher)
+
+    def tune_2d(self, kernel, args: tuple, grid_shape, block_sizes=None, launcher=None) -> TuneResult:
+        """Two-dimensional blocks over ``grid_shape = (rows, cols)`` elements (x covers the columns)."""
+        from ..dsl.errors import KernelError
+        from ..dsl.launcher import LaunchConfig
+        rows, cols = grid_shape
+        configs = []
+        for bx, by in (block_sizes or BLOCK_SIZES_2D):
+            try:
+                configs.append(LaunchConfig(((cols + bx - 1) // bx, (rows + by - 1) // by), (bx, by)))
+            except KernelError:
+                pass
+        return self._sweep(kernel, args, configs, f"a {rows} x {cols} grid", launcher)

@@ -124,4 +124,52 @@ def try_build(model, buffers) -> Optional[NativeStep]:
         return NativeStep(model, buffers)
     except (ValueError, AttributeError):
         return None
-FastDecoder = NativeStep      # the reference's name for its C decode launcher (zse-engine/zse_engine/orchestrator/fast_dispatch.py:341-609)
+class FastDecoder:
+    """The reference's handle on its C decode launcher (zse-engine/zse_engine/orchestrator/fast_dispatch.py:405-609):
+    ``compile()`` once, ``setup(...)`` with the model state, then ``decode_step(...)`` per token; ``available`` says
+    whether the native path can be used.  Here the launcher is the step driver of the native library:
+
+        fd = FastDecoder()
+        fd.compile()                       # loads (and if needed builds) the library
+        fd.setup(model, buffers)           # a DecoderModel and its StepBuffers
+        fd.decode_step(kv_slab, num_seqs)  # one decode pass over the staged batch; 0 on success
+
+    ``FastDecoder(model, buffers)`` does the first three at once."""
+
+    def __init__(self, model=None, buffers=None):
+        self._step: Optional[NativeStep] = None
+        self._compiled = False
+        if model is not None:
+            self.compile()
+            self.setup(model, buffers)
+
+    def compile(self) -> bool:
+        try:
+            native.load()
+            self._compiled = True
+        except Exception:
+            self._compiled = False
+        return self._compiled
+
+    @property
+    def available(self) -> bool:
+        return self._step is not None
+
+    def setup(self, model, buffers=None, *_, **__) -> bool:
+        """``model`` / ``buffers`` as ``ModelRunner`` holds them (``runner.model``, ``runner.buf``).  Models the driver
+        does not cover (CPU, tensor parallelism, adapters, sliding windows) leave ``available`` False."""
+        self._step = try_build(model, buffers) if (self._compiled and buffers is not None) else None
+        return self.available
+
+    def decode_step(self, kv: "torch.Tensor", num_seqs: int, attn_splits: int = 1) -> int:
+        """One decode pass for the ``num_seqs`` rows staged in the step buffers; 0 on success, -1 when the native path
+        is not available (the caller then uses ``DecoderModel.forward``)."""
+        if self._step is None:
+            return -1
+        self._step.forward(kv, num_seqs, True, num_seqs, 1, num_seqs, attn_splits)
+        return 0
+
+    def forward(self, *args, **kwargs) -> None:
+        if self._step is None:
+            raise RuntimeError("the native step driver is not available for this model")
+        self._step.forward(*args, **kwargs)
