@@ -14,7 +14,12 @@ def _to(dev, args):
     return tuple(a.clone().to(dev) if isinstance(a, torch.Tensor) else a for a in args)
 
 
-@pytest.mark.parametrize("name", sorted(K.ALL))
+# Written after the last GPU session of their author: emulated against torch (with the race check) and compiled for
+# sm_100a in tests/test_dsl_kernels.py, to be added here once they have been launched on hardware.
+EMULATED_AND_COMPILED_ONLY = {"paged_attention", "tiled_dequant_matmul_int4"}
+
+
+@pytest.mark.parametrize("name", sorted(set(K.ALL) - EMULATED_AND_COMPILED_ONLY))
 def test_launch_matches_emulation(name):
     kern, grid, block, args, checks = cases()[name]
     dev_args = _to("cuda", args)

@@ -72,11 +72,42 @@ def cases():
     n = T * (nh + 2 * nkv) * (hd // 2)
     out["rope_kv_write"] = (K.rope_kv_write, ((n + 31) // 32,), (32,), (qkv, cache, pos, slots, inv, T, nh, nkv, hd, bs),
                             [(qkv, want_q, 2e-3), (cache, want_c, 2e-3)])
+    # decode attention over a paged cache: three sequences (one of them with a dropped block), GQA 4:2, head_dim 64
+    nh, nkv, hd, bs, S, mb = 4, 2, 64, 4, 3, 5
+    lens = torch.tensor([9, 1, 17], dtype=torch.int32)
+    cache = (torch.randn(12, 2, nkv, bs, hd, generator=g) * 0.5).half()
+    bt = torch.tensor([[3, 7, 1, -1, -1], [0, -1, -1, -1, -1], [5, -1, 2, 9, 4]], dtype=torch.int32)   # -1 inside: a hole
+    ld = (nh + 2 * nkv) * hd
+    qkv = torch.randn(S, ld, generator=g).half()
+    o = torch.zeros(S, nh * hd, dtype=torch.float16)
+    want = torch.zeros(S, nh, hd)
+    for sq in range(S):
+        for h in range(nh):
+            keys, vals = [], []
+            for t in range(int(lens[sq])):
+                b = int(bt[sq, t // bs])
+                if b >= 0:
+                    keys.append(cache[b, 0, h // (nh // nkv), t % bs].float())
+                    vals.append(cache[b, 1, h // (nh // nkv), t % bs].float())
+            kk, vv = torch.stack(keys), torch.stack(vals)
+            pr = torch.softmax((kk @ qkv[sq, h * hd:(h + 1) * hd].float()) / 8.0, 0)
+            want[sq, h] = pr @ vv
+    out["paged_attention"] = (K.paged_attention, (S, nh), (32,),
+                              (o, qkv, cache, bt, lens, nh, nkv, hd, bs, mb, ld, 1 / 8.0),
+                              [(o, want.reshape(S, nh * hd), 3e-3)])
+    # shared-memory tiled INT4 GEMM with ragged edges in M and N
+    xm = torch.randn(21, 256, generator=g).half()
+    p, s, z, deq = _int4(37, 256, seed=2)
+    o = torch.zeros(21, 37, dtype=torch.float16)
+    out["tiled_dequant_matmul_int4"] = (K.tiled_dequant_matmul_int4, (3, 2), (16, 16), (xm, p, s, z, o, 21, 37, 256),
+                                        [(o, xm.float() @ deq.T, 8e-3)])
     return out
 
 
 def test_library_covers_the_inference_kernels():
     assert set(cases()) == set(K.ALL)
+    assert K.bgemv_int4_wave32 is K.gemv_int4_warp and K.fused_rope_kv_write is K.rope_kv_write
+    assert set(K.REFERENCE_NAMES.values()) <= set(K.ALL) and not set(K.REFERENCE_NAMES) & set(K.ALL)
 
 
 @pytest.mark.parametrize("name", sorted(K.ALL))

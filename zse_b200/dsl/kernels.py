@@ -9,9 +9,9 @@ nibble first, asymmetric groups of 128 with fp16 scale and zero point; INT8: sym
 activations ``[M, K]``, outputs ``[M, N]``."""
 from __future__ import annotations
 
-from . import (Tensor, block_dim, block_id, block_reduce_sum, cos, exp, float16, global_id, int8, int32, kernel,
-               lane_id, local_array, reinterpret, rsqrt, sin, thread_id, uint8, uint32, unpack_uint4, warp_reduce_max,
-               warp_reduce_sum)
+from . import (Tensor, block_dim, block_id, block_reduce_sum, cos, exp, float16, float32, global_id, int8, int32,
+               kernel, lane_id, local_array, max_val, reinterpret, rsqrt, shared_memory, sin, syncthreads, thread_id,
+               uint8, uint32, unpack_uint4, warp_reduce_max, warp_reduce_sum)
 
 
 @kernel
@@ -199,9 +199,93 @@ def rope_kv_write(qkv: Tensor[float16], cache: Tensor[float16], positions: Tenso
                 cache[dst + i + half] = b
 
 
+@kernel
+def paged_attention(out: Tensor[float16], q: Tensor[float16], cache: Tensor[float16], block_table: Tensor[int32],
+                    seq_lens: Tensor[int32], nh: int, nkv: int, hd: int, block_size: int, max_blocks: int,
+                    ldq: int, scale: float):
+    """Decode attention over the paged cache ``[blocks, 2, nkv, block_size, hd]`` of one layer: one warp per (sequence,
+    query head), launched as grid (num_seqs, nh) x block 32.  A lane holds ``hd / 32`` elements (hd a multiple of 32, at
+    most 256) of the query, of the running output and of each key / value row; the score of a token is a butterfly sum
+    over the warp, the softmax runs online (maximum and sum carried along, no score vector anywhere), and a block-table
+    entry below zero - a block the cache dropped - is skipped.  ``q`` rows are ``ldq`` elements apart (the fused QKV
+    buffer can be passed as it is); ``out`` is ``[num_seqs, nh * hd]``."""
+    seq = block_id(0)
+    head = block_id(1)
+    lane = lane_id()
+    per = hd // 32
+    kvh = head // (nh // nkv)
+    n = seq_lens[seq]
+    qv = local_array(8, float32)
+    acc = local_array(8, float32)
+    for j in range(per):
+        qv[j] = q[seq * ldq + head * hd + lane * per + j] * scale
+        acc[j] = 0.0
+    m = -1e30
+    total = 0.0
+    for t in range(n):
+        blk = block_table[seq * max_blocks + t // block_size]
+        row = (((max_val(blk, 0) * 2) * nkv + kvh) * block_size + t % block_size) * hd
+        part = 0.0
+        for j in range(per):
+            part += qv[j] * cache[row + lane * per + j]
+        score = warp_reduce_sum(part)             # every lane takes part, whether or not the block exists
+        if blk >= 0:
+            m_new = max_val(m, score)
+            alpha = exp(m - m_new)
+            p = exp(score - m_new)
+            total = total * alpha + p
+            vrow = row + nkv * block_size * hd    # the V half of the block
+            for j in range(per):
+                acc[j] = acc[j] * alpha + p * cache[vrow + lane * per + j]
+            m = m_new
+    for j in range(per):
+        out[(seq * nh + head) * hd + lane * per + j] = acc[j] / total if total > 0.0 else 0.0
+
+
+@kernel
+def tiled_dequant_matmul_int4(x: Tensor[float16], packed: Tensor[uint8], scales: Tensor[float16],
+                              zeros: Tensor[float16], out: Tensor[float16], m_rows: int, n_rows: int, k: int):
+    """out[m, n] = sum_k x[m, k] * w[n, k] with 16 x 16 output tiles: a block of 16 x 16 threads stages a 16 x 16 tile
+    of activations and a 16 x 16 tile of DEQUANTISED weights in shared memory per step of 16 along K, so every value is
+    fetched from global memory once per tile instead of once per output.  Launched as grid (ceil(N / 16), ceil(M / 16))
+    x block (16, 16); edges are padded with zeros.  (CUDA cores only: the engine's own INT4 GEMMs are the tcgen05
+    kernels of ``csrc/``.)"""
+    tx = thread_id(0)
+    ty = thread_id(1)
+    col = block_id(0) * 16 + tx                   # weight row = output column
+    row = block_id(1) * 16 + ty
+    xs = shared_memory((16, 16), float32)
+    ws = shared_memory((16, 16), float32)
+    acc = 0.0
+    for k0 in range(0, k, 16):
+        # thread (tx, ty) stages x[row, k0 + tx] and w[block's row ty, k0 + tx]
+        kk = k0 + tx
+        xs[ty * 16 + tx] = x[row * k + kk] * 1.0 if row < m_rows and kk < k else 0.0
+        wn = block_id(0) * 16 + ty
+        wv = 0.0
+        if wn < n_rows and kk < k:
+            byte = packed[wn * (k // 2) + kk // 2]
+            nib = (byte >> (4 * (kk % 2))) & 15
+            g = wn * (k // 128) + kk // 128
+            wv = nib * scales[g] + zeros[g]
+        ws[ty * 16 + tx] = wv
+        syncthreads()
+        for i in range(16):
+            acc += xs[ty * 16 + i] * ws[tx * 16 + i]
+        syncthreads()
+    if row < m_rows and col < n_rows:
+        out[row * n_rows + col] = acc
+
+
 def _collect():
     from .kernel import KernelFunction
     return {name: obj for name, obj in globals().items() if isinstance(obj, KernelFunction)}
 
 
 ALL = _collect()
+
+# The reference's names for kernels that exist here under another one (its wave-64 and MFMA variants are for AMD parts
+# and have no counterpart): zse-engine/zse_engine/orchestrator/portable_kernels.py:638, 737.
+bgemv_int4_wave32 = gemv_int4_warp
+fused_rope_kv_write = rope_kv_write
+REFERENCE_NAMES = {"bgemv_int4_wave32": "gemv_int4_warp", "fused_rope_kv_write": "rope_kv_write"}
