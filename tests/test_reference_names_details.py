@@ -168,6 +168,21 @@ def test_generator_objects_and_error_locations():
     assert str(zse.SourceLocation("a.py", 3)) == "a.py:3"
 
 
+def test_parse_error_formatting_shows_the_line_in_context():
+    from zse_b200.dsl.errors import format_parse_error, get_kernel_source_lines
+    lines = get_kernel_source_lines(fill_one)
+    assert lines[0].startswith("@zse.kernel") and lines[1].startswith("def fill_one(") and "a[i] = 1.0" in lines[4]
+    assert get_kernel_source_lines(fill_one._func) == lines and get_kernel_source_lines(len) == []
+    text = format_parse_error(fill_one, 4, "something is wrong here")
+    rows = text.split("\n")
+    assert rows[0] == "Parse error in 'fill_one', line 4:" and rows[-1] == "  Error: something is wrong here"
+    marked = [r for r in rows if r.startswith("  >>")]
+    assert len(marked) == 1 and "  4|" in marked[0] and "if i < n" in marked[0]
+    assert len(rows) == 2 + 5                                      # two lines of context on either side
+    assert format_parse_error(fill_one, 0, "m") == "Parse error in 'fill_one': m"
+    assert format_parse_error(len, 3, "m") == "Parse error in 'len': m"
+
+
 def test_unique_id_record_carries_the_rendezvous_address():
     from zse_b200.parallel.tensor_parallel import NCCL_UNIQUE_ID_BYTES, NcclUniqueId, get_unique_id
     uid = get_unique_id("cpu")

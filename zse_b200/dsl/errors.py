@@ -56,3 +56,30 @@ class KernelCompileError(KernelError):
 
 class KernelLaunchError(KernelError):
     """A launch configuration outside the device's limits, or a driver call that failed."""
+
+
+def get_kernel_source_lines(func) -> list:
+    """The dedented source lines of a kernel function; an empty list when the source cannot be read
+    (zse-compiler/zse_compiler/errors.py:69-75)."""
+    import inspect
+    import textwrap
+    func = getattr(func, "_func", func)               # a decorated kernel or the plain function
+    try:
+        return textwrap.dedent(inspect.getsource(func)).split("\n")
+    except (OSError, TypeError):
+        return []
+
+
+def format_parse_error(func, node_line: int, message: str, context: int = 2) -> str:
+    """A message with the offending line of the kernel (1-based, relative to the function) and ``context`` lines on
+    either side, for tools that report several problems at once; ``KernelError`` itself carries file and line
+    (zse-compiler/zse_compiler/errors.py:78-92)."""
+    name = getattr(func, "__name__", getattr(func, "name", "kernel"))
+    lines = get_kernel_source_lines(func)
+    if not lines or node_line <= 0 or node_line > len(lines):
+        return f"Parse error in '{name}': {message}"
+    out = [f"Parse error in '{name}', line {node_line}:"]
+    for i in range(max(0, node_line - 1 - context), min(len(lines), node_line + context)):
+        out.append(f"  {'>>' if i == node_line - 1 else '  '} {i + 1:3d}| {lines[i]}")
+    out.append(f"  Error: {message}")
+    return "\n".join(out)
