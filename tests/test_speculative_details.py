@@ -289,3 +289,22 @@ def test_repetition_penalty_moves_mass_away_from_seen_tokens():
     more = sum(s.sample(x, temperature=1.0, repetition_penalty=2.0, past_tokens={0: 8}) == 0 for _ in range(n)) / n
     assert abs(base - 0.5) < 0.05 and pen < base - 0.1 and more < pen            # p^(1 + log2(count)) grows with count
     assert s.sample(x, temperature=0.0, repetition_penalty=2.0, past_tokens={0: 1}) == 1
+
+
+def test_sampler_takes_the_reference_form_raw_fp16_bytes_and_a_vocabulary_size():
+    row = np.full(12, -4.0, dtype=np.float16)
+    row[5] = 3.0
+    row[10] = 9.0                                             # padding beyond the vocabulary of 8: must not count
+    data = row.tobytes()
+    s = Sampler(seed=0)
+    assert s.greedy(data, 8) == 5 and s.greedy(logits_bytes=data, vocab_size=8) == 5 and Sampler.greedy(data) == 10
+    assert s.sample(data, vocab_size=8, temperature=0.0) == 5
+    assert s.sample(logits_bytes=data, vocab_size=8, temperature=0.0) == 5
+    assert s.sample(torch.from_numpy(row.astype(np.float32)), temperature=0.0, vocab_size=8) == 5
+    with pytest.raises(ValueError, match="Expected 32 bytes"):
+        s.greedy(data, 16)
+    # past tokens as a plain set (the reference allows it): every member counts once
+    x = torch.tensor([2.0, 2.0])
+    n = 1500
+    frac = sum(s.sample(x, temperature=1.0, repetition_penalty=2.0, past_tokens={0}) == 0 for _ in range(n)) / n
+    assert frac < 0.4

@@ -72,7 +72,8 @@ class ArchAdapter:
                      "self_attn.o_proj.weight", "mlp.gate_proj.weight", "mlp.up_proj.weight",
                      "mlp.down_proj.weight", "input_layernorm.weight", "post_attention_layernorm.weight")
 
-    def config_from_hf(self, hf: dict) -> ModelConfig:
+    def config_from_hf(self, hf_config: dict) -> ModelConfig:
+        hf = hf_config
         raise NotImplementedError
 
     def _common(self, hf: dict, arch: str, *, max_seq: int, theta: float, eps: float, tie: bool,
@@ -99,7 +100,8 @@ class ArchAdapter:
     def should_quantize(self, tensor_name: str) -> bool:
         return _default_should_quantize(tensor_name)
 
-    def tensor_load_order(self, names: List[str]) -> List[str]:
+    def tensor_load_order(self, tensor_names: List[str]) -> List[str]:
+        names = tensor_names
         return sorted(names)
 
     def layer_tensors(self, config: ModelConfig, layer: int) -> List[str]:
@@ -114,7 +116,8 @@ class ArchAdapter:
             out.append("lm_head.weight")
         return out
 
-    def validate_config(self, c: ModelConfig) -> List[str]:
+    def validate_config(self, config: ModelConfig) -> List[str]:
+        c = config
         w = []
         if c.hidden_size % c.num_heads:
             w.append(f"hidden_size ({c.hidden_size}) not divisible by num_heads ({c.num_heads})")

@@ -9,7 +9,8 @@ class Gemma2Adapter(ArchAdapter):
     LAYER_TENSORS = ArchAdapter.LAYER_TENSORS + ("pre_feedforward_layernorm.weight",
                                                  "post_feedforward_layernorm.weight")
 
-    def config_from_hf(self, hf):
+    def config_from_hf(self, hf_config):
+        hf = hf_config
         c = self._common(hf, "gemma2", max_seq=8192, theta=10000.0, eps=1e-6, tie=True, explicit_head_dim=True)
         c.rope_scaling = None
         c.hidden_activation = hf.get("hidden_activation", "gelu_pytorch_tanh")

@@ -17,7 +17,8 @@ _AUDIO_KEYS = ("audio_embed_dim", "audio_samples_per_token", "output_proj_dims",
 class Gemma4Adapter(ArchAdapter):
     ARCH_NAME = "gemma4"
 
-    def config_from_hf(self, hf):
+    def config_from_hf(self, hf_config):
+        hf = hf_config
         tc = hf.get("text_config", hf)
         rope = tc.get("rope_parameters", {}) or {}
         sliding, full = rope.get("sliding_attention", {}) or {}, rope.get("full_attention", {}) or {}
@@ -74,7 +75,8 @@ class Gemma4Adapter(ArchAdapter):
             t.append("self_attn.v_proj.weight")
         return t
 
-    def validate_config(self, c):
+    def validate_config(self, config):
+        c = config
         w = super().validate_config(c)
         if c.global_head_dim and c.global_head_dim != c.head_dim:
             w.append(f"mixed head_dim: sliding {c.head_dim}, full-attention {c.global_head_dim}")

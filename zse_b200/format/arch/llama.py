@@ -6,7 +6,8 @@ from .base import ArchAdapter, register_adapter
 class LlamaAdapter(ArchAdapter):
     ARCH_NAME = "llama"
 
-    def config_from_hf(self, hf):
+    def config_from_hf(self, hf_config):
+        hf = hf_config
         return self._common(hf, self.ARCH_NAME, max_seq=4096, theta=10000.0, eps=1e-5, tie=False,
                             explicit_head_dim=True)
 
@@ -15,7 +16,8 @@ class LlamaAdapter(ArchAdapter):
 class MistralAdapter(LlamaAdapter):
     ARCH_NAME = "mistral"
 
-    def config_from_hf(self, hf):
+    def config_from_hf(self, hf_config):
+        hf = hf_config
         c = super().config_from_hf(hf)
         if c.sliding_window is None:
             c.sliding_window = 4096

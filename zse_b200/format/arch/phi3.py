@@ -9,7 +9,8 @@ class Phi3Adapter(ArchAdapter):
     LAYER_TENSORS = ("self_attn.qkv_proj.weight", "self_attn.o_proj.weight", "mlp.gate_up_proj.weight",
                      "mlp.down_proj.weight", "input_layernorm.weight", "post_attention_layernorm.weight")
 
-    def config_from_hf(self, hf):
+    def config_from_hf(self, hf_config):
+        hf = hf_config
         c = self._common(hf, "phi3", max_seq=4096, theta=10000.0, eps=1e-5, tie=False, explicit_head_dim=False)
         # Phi-4-mini rotates only the leading part of each head (pairs (i, i + rot/2) inside that part)
         f = hf.get("partial_rotary_factor", (hf.get("rope_parameters") or {}).get("partial_rotary_factor"))

@@ -76,17 +76,17 @@ class LoRAAdapter:
     def scaling(self) -> float:
         return float(self.alpha) / float(self.rank) if self.rank else 0.0
 
-    def add_weight(self, layer: int, module: str, w: LoRAWeight) -> None:
-        self.weights[(layer, module)] = w
+    def add_weight(self, layer_idx: int, module_name: str, weight: LoRAWeight) -> None:
+        self.weights[(layer_idx, module_name)] = weight
 
-    def get_weight(self, layer: int, module: str) -> Optional[LoRAWeight]:
-        return self.weights.get((layer, module))
+    def get_weight(self, layer_idx: int, module_name: str) -> Optional[LoRAWeight]:
+        return self.weights.get((layer_idx, module_name))
 
     def has_module(self, module: str) -> bool:
         return module in self.target_modules
 
-    def has_weight(self, layer: int, module: str) -> bool:
-        return (layer, module) in self.weights
+    def has_weight(self, layer_idx: int, module_name: str) -> bool:
+        return (layer_idx, module_name) in self.weights
 
     @property
     def num_weight_pairs(self) -> int:

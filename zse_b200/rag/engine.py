@@ -34,11 +34,11 @@ class RAGEngine:
         self._rebuild_all()
 
     # ---- wiring ---------------------------------------------------------------------------------------------
-    def set_model_runner(self, engine, enable_dense_by_default: bool = True) -> None:
-        """``engine``: the serving engine (``embed_tokens`` / ``last_token_logits``).  The name follows the reference,
-        which hands its ModelRunner over here."""
-        self._dense = DenseEmbedder(engine, self._tok)
-        self._reranker = LLMReranker(engine, self._tok)
+    def set_model_runner(self, model_runner, enable_dense_by_default: bool = True) -> None:
+        """``model_runner``: the serving engine (``embed_tokens`` / ``last_token_logits``).  Name and parameter follow the
+        reference, which hands its ModelRunner over here."""
+        self._dense = DenseEmbedder(model_runner, self._tok)
+        self._reranker = LLMReranker(model_runner, self._tok)
         self._dense_default = enable_dense_by_default
 
     @property

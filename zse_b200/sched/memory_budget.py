@@ -57,11 +57,11 @@ class MemoryBudget:
     def utilization(self) -> float:
         return self.committed_blocks / self._total if self._total else 1.0
 
-    def can_admit(self, req: InferenceRequest) -> bool:
+    def can_admit(self, request: InferenceRequest) -> bool:
         with self._lock:
-            if req.request_id in self._commits:
+            if request.request_id in self._commits:
                 return True
-            return self._estimate(req).total <= self._total - self._reserve - self.committed_blocks
+            return self._estimate(request).total <= self._total - self._reserve - self.committed_blocks
 
     def can_admit_n(self, requests) -> int:
         """How many of ``requests``, taken in order, fit next to what is committed already
@@ -93,19 +93,19 @@ class MemoryBudget:
         """False when the request could never run, even on an empty cache."""
         return self._tokens_to_blocks(req.prompt_len + req.params.max_tokens) <= self._total - self._reserve
 
-    def reserve(self, req: InferenceRequest) -> None:
+    def reserve(self, request: InferenceRequest) -> None:
         with self._lock:
-            self._commits.setdefault(req.request_id, self._estimate(req))
+            self._commits.setdefault(request.request_id, self._estimate(request))
 
     def release(self, request_id: str) -> None:
         with self._lock:
             self._commits.pop(request_id, None)
 
-    def update_decode_progress(self, request_id: str, num_generated: int) -> None:
+    def update_decode_progress(self, request_id: str, tokens_generated: int) -> None:
         with self._lock:
             c = self._commits.get(request_id)
             if c is not None:
-                c.decode_blocks = self._tokens_to_blocks(num_generated) + 1
+                c.decode_blocks = self._tokens_to_blocks(tokens_generated) + 1
 
     def resize(self, total_blocks: int) -> None:
         with self._lock:

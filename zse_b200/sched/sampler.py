@@ -20,10 +20,26 @@ class Sampler:
     def __init__(self, seed: Optional[int] = None):
         self._rng = random.Random(seed)
 
-    def sample(self, logits, temperature: float = 1.0, top_k: int = 0, top_p: float = 1.0,
-               repetition_penalty: float = 1.0, past_tokens: Optional[Dict[int, int]] = None,
-               seed: Optional[int] = None) -> int:
+    @staticmethod
+    def _logits(logits, vocab_size: Optional[int]) -> torch.Tensor:
+        """A tensor, an array, or - the reference's form - the raw fp16 bytes of a row together with ``vocab_size``
+        (rows may be padded: only the first ``vocab_size`` values count)."""
+        if isinstance(logits, (bytes, bytearray, memoryview)):
+            import numpy as np
+            n = len(logits) // 2 if vocab_size is None else int(vocab_size)
+            if len(logits) < 2 * n:
+                raise ValueError(f"Expected {2 * n} bytes, got {len(logits)}")
+            return torch.from_numpy(np.frombuffer(logits, dtype=np.float16, count=n).astype(np.float32))
         x = torch.as_tensor(logits).float().flatten()
+        return x if vocab_size is None else x[: int(vocab_size)]
+
+    def sample(self, logits=None, temperature: float = 1.0, top_k: int = 0, top_p: float = 1.0,
+               repetition_penalty: float = 1.0, past_tokens=None, seed: Optional[int] = None,
+               vocab_size: Optional[int] = None, logits_bytes=None) -> int:
+        """``past_tokens``: token -> count, or a plain collection of token ids (each counted once)."""
+        x = self._logits(logits_bytes if logits is None else logits, vocab_size)
+        if past_tokens is not None and not isinstance(past_tokens, dict):
+            past_tokens = {int(t): 1 for t in past_tokens}
         if repetition_penalty != 1.0 and past_tokens:
             x = ref.apply_repetition_penalty(x, past_tokens, repetition_penalty)
         if temperature <= 0.0 or top_k == 1:
@@ -35,5 +51,5 @@ class Sampler:
         return int(min(int(torch.searchsorted(c, torch.tensor(u, dtype=c.dtype))), p.numel() - 1))
 
     @staticmethod
-    def greedy(logits) -> int:
-        return int(torch.as_tensor(logits).float().argmax())
+    def greedy(logits=None, vocab_size: Optional[int] = None, logits_bytes=None) -> int:
+        return int(Sampler._logits(logits_bytes if logits is None else logits, vocab_size).argmax())

@@ -115,8 +115,8 @@ class Response:
         return cls(status, json.dumps(obj).encode("utf-8"), {"Content-Type": "application/json"})
 
     @classmethod
-    def text(cls, text: str, status: int = 200, content_type: str = "text/plain; charset=utf-8") -> "Response":
-        return cls(status, text.encode("utf-8"), {"Content-Type": content_type})
+    def text(cls, content: str, status: int = 200, content_type: str = "text/plain; charset=utf-8") -> "Response":
+        return cls(status, content.encode("utf-8"), {"Content-Type": content_type})
 
     @classmethod
     def error(cls, message: str, status: int = 400, code: Optional[str] = None) -> "Response":
@@ -155,23 +155,23 @@ class Router:
         self._middleware: List[Middleware] = []
         self._static: List[Tuple[str, str]] = []
 
-    def add(self, method: str, pattern: str, handler: Handler) -> None:
-        self._routes.append(Route(method, pattern, handler))
+    def add(self, method: str, path: str, handler: Handler) -> None:
+        self._routes.append(Route(method, path, handler))
 
-    def get(self, pattern: str, handler: Handler) -> None:
-        self.add("GET", pattern, handler)
+    def get(self, path: str, handler: Handler) -> None:
+        self.add("GET", path, handler)
 
-    def post(self, pattern: str, handler: Handler) -> None:
-        self.add("POST", pattern, handler)
+    def post(self, path: str, handler: Handler) -> None:
+        self.add("POST", path, handler)
 
-    def put(self, pattern: str, handler: Handler) -> None:
-        self.add("PUT", pattern, handler)
+    def put(self, path: str, handler: Handler) -> None:
+        self.add("PUT", path, handler)
 
-    def delete(self, pattern: str, handler: Handler) -> None:
-        self.add("DELETE", pattern, handler)
+    def delete(self, path: str, handler: Handler) -> None:
+        self.add("DELETE", path, handler)
 
-    def use(self, mw: Middleware) -> None:
-        self._middleware.append(mw)
+    def use(self, middleware: Middleware) -> None:
+        self._middleware.append(middleware)
 
     def static(self, url_prefix: str, directory: str) -> None:
         self._static.append((url_prefix.rstrip("/") + "/", os.path.abspath(directory)))
