@@ -291,3 +291,41 @@ def test_top_level_names_are_lazy():
     r = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=240,
                        cwd=os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
     assert r.returncode == 0 and r.stdout.strip() == "ok", r.stderr[-1500:]
+
+
+def test_streamed_load_falls_back_and_says_why(monkeypatch, capsys, tmp_path):
+    """`open_mirror`: off for CPU devices and when switched off; a failure of the streamed pass (made up here: the
+    mirror's constructor raises) yields None - the caller copies tensor by tensor - with the reason in the load
+    statistics, and with ZSE_DEBUG_LOAD=1 also on stderr with the traceback."""
+    from zse_b200.runtime import weight_stream as ws
+    loader = _model(tmp_path, "tiny")
+    assert ws.open_mirror(loader, "cpu") is None
+    made = []
+
+    class Broken:
+        def __init__(self, loader, device):
+            made.append(str(device))
+            raise OSError("cannot lock 512 MB of host memory")
+
+    monkeypatch.setattr(ws, "DeviceMirror", Broken)
+    monkeypatch.setenv("ZSE_STREAM_WEIGHTS", "0")
+    assert ws.open_mirror(loader, "cuda:0") is None and made == []                  # switched off: not even tried
+    monkeypatch.setenv("ZSE_STREAM_WEIGHTS", "1")
+    stats = {}
+    assert ws.open_mirror(loader, "cuda:0", stats) is None and made == ["cuda:0"]
+    assert stats == {"stream_error": "cannot lock 512 MB of host memory"}
+    assert capsys.readouterr().err == ""                                             # quiet by default
+    monkeypatch.setenv("ZSE_DEBUG_LOAD", "1")
+    assert ws.open_mirror(loader, "cuda:0") is None
+    err = capsys.readouterr().err
+    assert "Traceback" in err and "streamed weight load failed (OSError" in err and "tensor by tensor" in err
+
+    class Fine:
+        seconds, size = 0.5, 10 ** 9
+
+        def __init__(self, loader, device):
+            pass
+
+    monkeypatch.setattr(ws, "DeviceMirror", Fine)
+    stats = {}
+    assert isinstance(ws.open_mirror(loader, "cuda:0", stats), Fine) and stats == {"stream_s": 0.5, "stream_gbs": 2.0}

@@ -180,11 +180,9 @@ class DecoderModel:
         # the weight section goes to the device in one streamed pass (every tensor-parallel rank mirrors the section and
         # cuts its shard out on the device: the page cache serves all ranks, and a rank's shard of a row-parallel
         # projection is a column range that no contiguous read could deliver anyway)
-        if dev.type == "cuda" and env.flag("ZSE_STREAM_WEIGHTS"):
-            from ..runtime.weight_stream import DeviceMirror
-            mirror = DeviceMirror(loader, dev)
-            self.load_stats["stream_s"] = round(mirror.seconds, 3)
-            self.load_stats["stream_gbs"] = round(mirror.size / max(mirror.seconds, 1e-9) / 1e9, 2)
+        if dev.type == "cuda":
+            from ..runtime.weight_stream import open_mirror
+            mirror = open_mirror(loader, dev, self.load_stats)       # None: switched off, or failed -> per-tensor copies
         _part = lambda name, rows=None, cols=None: _entry_part(loader, name, rows, cols, mirror)
         e_embed = loader.weight_index.find("embed_tokens.weight")
         if mirror is not None and e_embed.dtype == "float16":

@@ -109,6 +109,32 @@ class DeviceMirror:
         self.base = None
 
 
+def open_mirror(loader, device, stats: Optional[dict] = None) -> Optional["DeviceMirror"]:
+    """The streamed copy of the weight section, or None when it is switched off (``ZSE_STREAM_WEIGHTS=0``), the device
+    is not a GPU, or the streamed pass failed - the caller then copies tensor by tensor, as the reference falls back
+    from its streamed path (zse-engine/zse_engine/orchestrator/weight_loader.py:188-199).  With ``ZSE_DEBUG_LOAD=1`` the
+    failure is printed with its traceback; ``stats`` receives the throughput or the reason."""
+    dev = torch.device(device)
+    if dev.type != "cuda" or not env.flag("ZSE_STREAM_WEIGHTS"):
+        return None
+    try:
+        mirror = DeviceMirror(loader, dev)
+    except (OSError, RuntimeError, TimeoutError, MemoryError) as exc:
+        if stats is not None:
+            stats["stream_error"] = " ".join(str(exc).split())[:200] or type(exc).__name__
+        if env.flag("ZSE_DEBUG_LOAD"):
+            import sys
+            import traceback
+            traceback.print_exc()
+            print(f"[zse] streamed weight load failed ({type(exc).__name__}: {exc}); copying tensor by tensor",
+                  file=sys.stderr)
+        return None
+    if stats is not None:
+        stats["stream_s"] = round(mirror.seconds, 3)
+        stats["stream_gbs"] = round(mirror.size / max(mirror.seconds, 1e-9) / 1e9, 2)
+    return mirror
+
+
 class HostMirror:
     """The same interface over the file mapping, for a CPU device: tensors are views of the mapped pages."""
 

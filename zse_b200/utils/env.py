@@ -40,6 +40,8 @@ KNOWN: Dict[str, Tuple[str, str]] = {
     "ZSE_ATTN_PREFILL_TC": ("1", "prefill attention of head_dim 128 models on the tcgen05 kernel (csrc/attention_tc.cu); "
                                  "0: the mma.sync kernel for every shape"),
     "ZSE_NATIVE_LIB": ("", "path of the native library to load instead of the ordinary build (instrumented variants)"),
+    "ZSE_DEBUG_LOAD": ("0", "print the traceback when the streamed weight load fails and the loader falls back to "
+                       "per-tensor copies"),
     "ZSE_PDL": ("1", "programmatic dependent launch between the kernels of a pass (read by the native library); 0 is a "
                 "diagnostic setting for per-kernel timing, not a serving configuration"),
     "ZSE_TP_PDL": ("0", "programmatic dependent launch for the exchange kernels too (read by the native library)"),
