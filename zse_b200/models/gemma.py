@@ -82,10 +82,9 @@ class GemmaDecoderModel(DecoderModel):
             return np_to_dev(v, dev)
 
         mirror = None
-        if dev.type == "cuda" and tp == 1 and env.flag("ZSE_STREAM_WEIGHTS"):
-            from ..runtime.weight_stream import DeviceMirror
-            mirror = DeviceMirror(loader, dev)
-            self.load_stats["stream_s"] = round(mirror.seconds, 3)
+        if dev.type == "cuda" and tp == 1:
+            from ..runtime.weight_stream import open_mirror
+            mirror = open_mirror(loader, dev, self.load_stats)       # None: switched off, or failed -> per-tensor copies
         part = lambda name, rows=None, cols=None: _entry_part(loader, name, rows, cols, mirror)
         self.embed = np_to_dev(loader.view_data(loader.weight_index.find("embed_tokens.weight")), dev)
         self.norm = norm_w("norm.weight")
