@@ -33,7 +33,6 @@ from ..format.config import LayerSpec, ModelConfig
 from ..format.loader import ZSELoader
 from ..ops.backend import LinearWeight, np_to_dev
 from .decoder import DecoderModel, StepBuffers, _entry_part, _vec
-from ..utils import env
 
 
 @dataclass
