@@ -27,7 +27,6 @@ from ..format.config import ModelConfig
 from ..ops import reference as ref
 from ..ops.backend import LinearWeight, TorchOps, make_ops, np_to_dev
 from ..parallel.shard_plan import ShardPlan, make_plan
-from ..utils import env
 
 SUPPORTED_ARCHS = ("llama", "mistral", "qwen2", "phi3", "gemma2", "gemma4")
 
