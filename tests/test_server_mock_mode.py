@@ -306,3 +306,55 @@ def test_session_save_route_of_the_reference(srv):
     assert [(m["role"], m["content"]) for m in msgs] == [("user", "hello"), ("assistant", "hi")]
     # "save" is a route of its own, not a session id
     assert call(srv, "GET", "/v1/dashboard/session/save", headers=auth)[1]["messages"] == []
+
+
+# ---- retrieval routes without a model (lexical search only) -----------------------------------------------------
+@pytest.fixture()
+def rag_srv():
+    s = ZSEServer(model_path=None, admin_key="admin-secret", db_path=":memory:", model_name="mock-model", quiet=True,
+                  enable_rag=True)
+    yield s
+    s.database.close()
+
+
+def test_document_lifecycle_and_lexical_search(rag_srv):
+    import base64
+    s = rag_srv
+    assert call(s, "GET", "/v1/rag/documents") == (200, {"documents": []})
+    assert call(s, "POST", "/v1/rag/upload", {"text": "no name"})[0] == 400
+    assert call(s, "POST", "/v1/rag/upload", {"filename": "a.txt"})[0] == 400
+    assert call(s, "POST", "/v1/rag/upload", {"filename": "a.txt", "content": "not base64!!"})[0] == 400
+    text_a = "The paged key value cache stores attention keys in fixed size blocks. " * 6
+    text_b = "Speculative decoding drafts several tokens and verifies them in one pass. " * 6
+    status, a = call(s, "POST", "/v1/rag/upload", {"filename": "cache.txt", "text": text_a})
+    assert status == 201 and a["chunk_count"] >= 1 and a["doc_type"] == "text"
+    status, b = call(s, "POST", "/v1/rag/upload",
+                     {"filename": "spec.md", "content": base64.b64encode(text_b.encode()).decode()})
+    assert status == 201 and b["doc_id"] != a["doc_id"]
+    docs = call(s, "GET", "/v1/rag/documents")[1]["documents"]
+    assert sorted(d["name"] for d in docs) == ["cache.txt", "spec.md"]
+    status, doc = call(s, "GET", f"/v1/rag/document/{a['doc_id']}")
+    assert status == 200 and doc["name"] == "cache.txt" and doc["chunks"][0]["content"].startswith("The paged key")
+    assert call(s, "GET", "/v1/rag/document/9999")[0] == 404 and call(s, "GET", "/v1/rag/document/abc")[0] == 404
+    # search: BM25 only (no model to embed with)
+    assert call(s, "POST", "/v1/rag/search", {})[0] == 400
+    status, out = call(s, "POST", "/v1/rag/search", {"query": "speculative drafts tokens", "top_k": 3})
+    assert status == 200 and out["query"] == "speculative drafts tokens" and out["results"]
+    assert out["results"][0]["doc_name"] == "spec.md"
+    status, out = call(s, "POST", "/v1/rag/search", {"query": "paged cache blocks", "top_k": 1})
+    assert len(out["results"]) == 1 and out["results"][0]["doc_name"] == "cache.txt"
+    stats = call(s, "GET", "/v1/rag/stats")[1]
+    assert stats["documents"] == 2 and stats["chunks"] >= 2 and stats["dense_enabled"] is False
+    # replace, then delete
+    status, r = call(s, "PUT", f"/v1/rag/document/{a['doc_id']}",
+                     {"filename": "cache.txt", "text": "Entirely different words about tokenizers and vocabularies. " * 5})
+    assert status == 200
+    assert call(s, "PUT", "/v1/rag/document/9999", {"filename": "x.txt", "text": "y"})[0] == 404
+    out = call(s, "POST", "/v1/rag/search", {"query": "tokenizers vocabularies", "top_k": 2})[1]
+    assert out["results"][0]["doc_name"] == "cache.txt"
+    assert call(s, "DELETE", f"/v1/rag/document/{b['doc_id']}") == (200, {"deleted": b["doc_id"]})
+    assert call(s, "DELETE", f"/v1/rag/document/{b['doc_id']}")[0] == 404
+    assert len(call(s, "GET", "/v1/rag/documents")[1]["documents"]) == 1
+    # dense back-fill is for the admin, and has nothing to embed with here
+    assert call(s, "POST", "/v1/rag/backfill_dense")[0] == 403
+    assert call(s, "POST", "/v1/rag/backfill_dense", headers=ADMIN) == (200, {"embedded": 0})
