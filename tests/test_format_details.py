@@ -1,0 +1,183 @@
+"""More of the format layer, piece by piece: architecture detection and the adapter registry, both spellings of the RoPE
+settings in HuggingFace configs, what gets quantised, the tensors a layer must have, config-derived sizes, the
+safetensors reader the converter is built on, and the section checksum (the reference's tests/test_zse_format.py and
+test_convert_pipeline.py cover the same ground on its side)."""
+import json
+import struct
+import zlib
+
+import numpy as np
+import pytest
+
+from zse_b200.format import synth
+from zse_b200.format.arch.base import (ArchAdapter, detect_architecture, get_adapter, register_adapter, rope_settings,
+                                       supported_architectures)
+from zse_b200.format.convert import (build_tensor_map, find_safetensor_files, read_safetensors_metadata,
+                                     read_safetensors_tensor, read_safetensors_tensor_raw, write_safetensors)
+from zse_b200.format.header import compute_crc32
+
+
+# ---- architecture detection and registry ------------------------------------------------------------------------
+@pytest.mark.parametrize("architectures,model_type,want", [
+    (["LlamaForCausalLM"], "llama", "llama"),
+    (["MistralForCausalLM"], "mistral", "mistral"),
+    (["Qwen2ForCausalLM"], "qwen2", "qwen2"),
+    (["Phi3ForCausalLM"], "phi3", "phi3"),
+    (["Gemma2ForCausalLM"], "gemma2", "gemma2"),
+    (["Gemma4ForConditionalGeneration"], "gemma4", "gemma4"),       # "gemma4" is tested before the plain "gemma"
+    (None, "qwen2", "qwen2"),                                       # no class name: the model type decides
+    ([], "llama", "llama"),
+])
+def test_architecture_is_detected_from_class_name_or_model_type(architectures, model_type, want):
+    assert detect_architecture({"architectures": architectures, "model_type": model_type}) == want
+
+
+def test_unknown_architectures_are_refused_with_what_was_seen():
+    with pytest.raises(ValueError, match="cannot detect the architecture.*BertModel.*bert"):
+        detect_architecture({"architectures": ["BertModel"], "model_type": "bert"})
+    with pytest.raises(ValueError, match="unknown architecture 'bert'; supported: .*llama"):
+        get_adapter("bert")
+    assert {"llama", "mistral", "qwen2", "phi3", "gemma2", "gemma4"} <= set(supported_architectures())
+    assert supported_architectures() == sorted(supported_architectures())
+    assert get_adapter("qwen2").ARCH_NAME == "qwen2"
+
+
+def test_an_adapter_registered_by_a_user_is_found(monkeypatch):
+    from zse_b200.format.arch import base
+    monkeypatch.setattr(base, "_REGISTRY", dict(base._REGISTRY))           # leave the real registry alone
+
+    @register_adapter
+    class Mine(ArchAdapter):
+        ARCH_NAME = "my-arch"
+
+    assert "my-arch" in supported_architectures() and isinstance(get_adapter("my-arch"), Mine)
+    assert detect_architecture({"model_type": "my-arch"}) == "my-arch"
+
+
+# ---- RoPE settings ----------------------------------------------------------------------------------------------
+def test_rope_settings_in_both_spellings():
+    assert rope_settings({}, 10000.0) == (10000.0, None)
+    assert rope_settings({"rope_theta": 1e6}, 10000.0) == (1e6, None)
+    llama3 = {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+              "original_max_position_embeddings": 8192}
+    theta, scaling = rope_settings({"rope_theta": 5e5, "rope_scaling": llama3}, 10000.0)
+    assert theta == 5e5 and scaling == llama3
+    # transformers 5: base and scaling parameters together under rope_parameters
+    theta, scaling = rope_settings({"rope_parameters": {"rope_theta": 5e5, **llama3}}, 10000.0)
+    assert theta == 5e5 and scaling == llama3
+    assert rope_settings({"rope_parameters": {"rope_theta": 1e6, "rope_type": "default"}}, 1.0) == (1e6, None)
+    assert rope_settings({"rope_scaling": {"type": "linear", "factor": 2.0}}, 7.0) == (7.0, {"type": "linear", "factor": 2.0})
+    assert rope_settings({"rope_scaling": {"type": "default"}}, 7.0) == (7.0, None)
+
+
+# ---- tensor names, quantisation, load order ---------------------------------------------------------------------
+def test_tensor_names_lose_their_model_prefix_and_norms_stay_fp16():
+    a = get_adapter("llama")
+    assert a.map_tensor_name("model.layers.3.self_attn.q_proj.weight") == "layers.3.self_attn.q_proj.weight"
+    assert a.map_tensor_name("lm_head.weight") == "lm_head.weight"
+    assert a.should_quantize("layers.0.self_attn.q_proj.weight") and a.should_quantize("layers.0.mlp.down_proj.weight")
+    for keep in ("embed_tokens.weight", "norm.weight", "layers.0.input_layernorm.weight",
+                 "layers.0.self_attn.q_proj.bias"):
+        assert not a.should_quantize(keep), keep
+    assert a.tensor_load_order(["b", "a", "c"]) == ["a", "b", "c"]
+    assert a.tensor_load_order(tensor_names=["z", "y"]) == ["y", "z"]
+
+
+def test_expected_tensors_follow_the_config():
+    c = synth.shape_config("tiny")
+    a = get_adapter(c.arch)
+    names = a.expected_tensors(c)
+    assert names[0] == "embed_tokens.weight" and "norm.weight" in names
+    assert ("lm_head.weight" in names) == (not c.tie_word_embeddings)
+    per_layer = a.layer_tensors(c, 0)
+    assert {"self_attn.q_proj.weight", "self_attn.o_proj.weight", "mlp.gate_proj.weight", "mlp.down_proj.weight",
+            "input_layernorm.weight"} <= set(per_layer)
+    assert sum(n.startswith("layers.1.") for n in names) == len(per_layer)
+    g4 = synth.shape_config("tiny-gemma4")
+    ga = get_adapter("gemma4")
+    assert not ga.should_quantize("layers.0.self_attn.q_norm.weight")
+    assert any("q_norm" in t for t in ga.layer_tensors(g4, 0))
+
+
+def test_config_validation_warns_instead_of_failing():
+    import dataclasses
+    c = synth.shape_config("tiny")
+    a = get_adapter(c.arch)
+    assert a.validate_config(c) == [] and a.validate_config(config=c) == []
+    odd = dataclasses.replace(c, num_heads=c.num_heads + 1)
+    w = a.validate_config(odd)
+    assert any("not divisible by num_heads" in x for x in w) and any("not divisible by num_kv_heads" in x for x in w)
+    yarn = dataclasses.replace(c, rope_scaling={"rope_type": "yarn", "factor": 4.0})
+    assert any("'yarn' is not applied" in x for x in a.validate_config(yarn))
+    for kind in ("linear", "llama3", "default"):
+        assert a.validate_config(dataclasses.replace(c, rope_scaling={"rope_type": kind, "factor": 2.0})) == []
+
+
+# ---- config-derived sizes ---------------------------------------------------------------------------------------
+def test_cache_bytes_and_parameter_counts_of_the_7b_shape():
+    c = synth.shape_config("qwen2.5-7b")
+    assert c.kv_head_dim == c.head_dim == 128 and not c.is_gemma and c.layer_kind(5) == "full_attention"
+    assert c.kv_cache_bytes_per_token == 2 * c.num_kv_heads * 128 * 2 == 2048
+    assert c.total_kv_cache_bytes_per_token == 2048 * c.num_layers
+    q, kv, H, I = c.num_heads * 128, c.num_kv_heads * 128, c.hidden_size, c.intermediate_size
+    assert c.linear_param_count() == c.num_layers * (H * q + 2 * H * kv + q * H + 3 * H * I)
+    size = c.estimate_model_size_bytes()
+    params = c.linear_param_count()
+    # INT4 with groups of 128: half a byte per weight + 4 bytes of scale and zero per group + fp16 embeddings and norms
+    assert size == params // 2 + (params // 128) * 4 + c.vocab_size * H * 2 * (1 if c.tie_word_embeddings else 2) \
+        + c.num_layers * H * 2 * 2
+    assert 4.5e9 < size < 6.5e9                                                 # ~5.5 GB: the published file size
+    g = synth.shape_config("tiny-gemma2")
+    assert g.is_gemma and {g.layer_kind(i) for i in range(g.num_layers)} <= {"full_attention", "sliding_attention"}
+
+
+# ---- the safetensors reader -------------------------------------------------------------------------------------
+def test_safetensors_round_trip_in_three_element_types(tmp_path):
+    rng = np.random.default_rng(0)
+    a32 = rng.standard_normal((4, 6)).astype(np.float32)
+    a16 = rng.standard_normal((3, 5)).astype(np.float16)
+    path = str(tmp_path / "m.safetensors")
+    write_safetensors(path, {"a32": a32, "a16": a16})
+    meta, base = read_safetensors_metadata(path)
+    (n,) = struct.unpack("<Q", open(path, "rb").read(8))
+    assert base == 8 + n and set(meta) - {"__metadata__"} == {"a32", "a16"}
+    assert meta["a32"]["dtype"] == "F32" and meta["a32"]["shape"] == [4, 6] and meta["a16"]["dtype"] == "F16"
+    raw, dtype, shape = read_safetensors_tensor_raw(path, meta["a16"], base)
+    assert (dtype, shape) == ("F16", (3, 5)) and raw == a16.tobytes()
+    got, shape = read_safetensors_tensor(path, meta["a32"], base)
+    assert shape == (4, 6) and got.dtype == np.float32 and np.array_equal(got.reshape(4, 6), a32)
+    got16, _ = read_safetensors_tensor(path, meta["a16"], base)
+    assert np.array_equal(got16.reshape(3, 5), a16.astype(np.float32))
+    # bfloat16 files: the upper half of the float32 pattern
+    bpath = str(tmp_path / "b.safetensors")
+    write_safetensors(bpath, {"w": a32}, bf16=True)
+    bmeta, bbase = read_safetensors_metadata(bpath)
+    assert bmeta["w"]["dtype"] == "BF16"
+    back, _ = read_safetensors_tensor(bpath, bmeta["w"], bbase)
+    assert np.abs(back.reshape(4, 6) - a32).max() < 0.02 and np.all((back.view(np.uint32) & 0xFFFF) == 0)
+    with pytest.raises(ValueError, match="unsupported safetensors dtype"):
+        read_safetensors_tensor(path, {**meta["a32"], "dtype": "F8_E4M3"}, base)
+
+
+def test_shards_are_found_in_order_and_mapped_by_tensor_name(tmp_path):
+    with pytest.raises(FileNotFoundError, match="no .safetensors files"):
+        find_safetensor_files(str(tmp_path))
+    one = np.ones((2, 2), dtype=np.float32)
+    write_safetensors(str(tmp_path / "model-00002-of-00002.safetensors"), {"b": one * 2})
+    write_safetensors(str(tmp_path / "model-00001-of-00002.safetensors"), {"a": one, "c": one * 3})
+    (tmp_path / "config.json").write_text("{}")
+    files = find_safetensor_files(str(tmp_path))
+    assert [f.rsplit("/", 1)[1] for f in files] == ["model-00001-of-00002.safetensors", "model-00002-of-00002.safetensors"]
+    tmap = build_tensor_map(files)
+    assert set(tmap) == {"a", "b", "c"} and tmap["b"][0] == files[1] and tmap["c"][0] == files[0]
+    path, info, base = tmap["c"]
+    got, shape = read_safetensors_tensor(path, info, base)
+    assert shape == (2, 2) and np.all(got == 3.0)
+
+
+# ---- checksums --------------------------------------------------------------------------------------------------
+def test_section_checksum_is_crc32():
+    assert compute_crc32(b"") == 0
+    assert compute_crc32(b"123456789") == 0xCBF43926                            # the standard check value
+    data = bytes(range(256)) * 10
+    assert compute_crc32(data) == zlib.crc32(data) & 0xFFFFFFFF == compute_crc32(memoryview(data))
