@@ -469,3 +469,57 @@ def test_sse_completion_chunks_and_done():
     assert end["choices"][0] == {"index": 0, "text": "", "finish_reason": "stop"}
     assert sse.sse_done() == b"data: [DONE]\n\n" == sse.SSE_DONE
     assert sse.sse_event({"a": "b\nc"}) == b'data: {"a": "b\\nc"}\n\n'            # a newline never splits an event
+
+
+# ---- chat layouts -----------------------------------------------------------------------------------------------
+CONVERSATION = [{"role": "system", "content": "Be brief."}, {"role": "user", "content": "Hi"},
+                {"role": "assistant", "content": "Hello."}, {"role": "user", "content": "Bye"}]
+
+
+def test_chat_layouts_of_the_model_families():
+    from zse_b200.server.api_openai import (TEMPLATES, format_chatml, format_gemma, format_llama, format_llama3,
+                                            format_phi3)
+    assert set(TEMPLATES) == {"chatml", "llama", "llama3", "phi3", "gemma"}
+    assert format_chatml(CONVERSATION) == (
+        "<|im_start|>system\nBe brief.<|im_end|>\n<|im_start|>user\nHi<|im_end|>\n"
+        "<|im_start|>assistant\nHello.<|im_end|>\n<|im_start|>user\nBye<|im_end|>\n<|im_start|>assistant\n")
+    assert format_llama(CONVERSATION) == (
+        "[INST] <<SYS>>\nBe brief.\n<</SYS>>\n\nHi [/INST] Hello. </s>[INST] Bye [/INST]")
+    assert format_llama([{"role": "user", "content": "Hi"}]) == "[INST] Hi [/INST]"
+    assert format_llama3(CONVERSATION[1:2]) == (
+        "<|start_header_id|>user<|end_header_id|>\n\nHi<|eot_id|><|start_header_id|>assistant<|end_header_id|>\n\n")
+    assert format_phi3(CONVERSATION[1:3]) == "<|user|>\nHi<|end|>\n<|assistant|>\nHello.<|end|>\n<|assistant|>\n"
+    g = format_gemma(CONVERSATION[1:])
+    assert g == ("<start_of_turn>user\nHi<end_of_turn>\n<start_of_turn>model\nHello.<end_of_turn>\n"
+                 "<start_of_turn>user\nBye<end_of_turn>\n<start_of_turn>model\n")        # "assistant" is "model" there
+    for fmt in TEMPLATES.values():                                                # every layout ends at the model's turn
+        assert fmt([{"content": "no role given"}])                                # ... and defaults the role to user
+
+
+def test_layout_follows_the_tokenizer_before_the_architecture():
+    from zse_b200.server.api_openai import template_for_arch
+
+    class Tok:
+        def __init__(self, *tokens):
+            self.tokens = set(tokens)
+
+        def token_to_id(self, t):
+            return 1 if t in self.tokens else None
+
+    assert template_for_arch("llama", Tok("<|im_start|>")) == "chatml"
+    assert template_for_arch("llama", Tok("<|start_header_id|>", "<|eot_id|>")) == "llama3"   # Llama 3 files
+    assert template_for_arch("llama", Tok()) == "llama" and template_for_arch("mistral") == "llama"
+    assert template_for_arch("qwen2") == "chatml"
+    assert template_for_arch("phi3", Tok("<|assistant|>", "<|end|>")) == "phi3"
+    assert template_for_arch("phi3") == "chatml"                # without the marker tokens the markers would be text
+    assert template_for_arch("gemma2") == "gemma" and template_for_arch("gemma4") == "gemma"
+    assert template_for_arch("") == "chatml" and template_for_arch("something-new") == "chatml"
+
+
+def test_markers_end_the_visible_text():
+    from zse_b200.server.api_openai import CHAT_MARKERS, strip_markers
+    assert {"<|im_end|>", "<|im_start|>", "<|eot_id|>", "<end_of_turn>", "</s>"} <= set(CHAT_MARKERS)
+    assert strip_markers("Hello there.<|im_end|>\n<|im_start|>user") == "Hello there."
+    assert strip_markers("Answer  \n</s>trailing") == "Answer"
+    assert strip_markers("two<end_of_turn>and<|eot_id|>more") == "two"
+    assert strip_markers("nothing to cut  ") == "nothing to cut"
