@@ -181,3 +181,60 @@ def test_section_checksum_is_crc32():
     assert compute_crc32(b"123456789") == 0xCBF43926                            # the standard check value
     data = bytes(range(256)) * 10
     assert compute_crc32(data) == zlib.crc32(data) & 0xFFFFFFFF == compute_crc32(memoryview(data))
+
+
+# ---- raw-bytes quantiser entry points and alignment helpers ---------------------------------------------------------
+def test_raw_bytes_entry_points_follow_the_array_quantiser():
+    import numpy as np
+    from zse_b200.format import fast_quant
+    from zse_b200.format import quantize as Q
+    rng = np.random.default_rng(3)
+    w = rng.standard_normal(300).astype(np.float32)                               # 2 full groups and a tail of 44
+    vals, scales = fast_quant.quantize_tensor_int8_fast(w.tobytes() + b"junk-after-the-tensor", "F32", 300)
+    v2, s2 = Q.quantize_int8_arrays(w, 128)
+    assert vals == np.asarray(v2).tobytes() and scales == np.asarray(s2).tobytes()
+    back = Q.dequantize_tensor_int8(np.frombuffer(vals, np.int8), np.frombuffer(scales, np.float16), (300,))
+    assert np.abs(back - w).max() <= np.abs(w).max() / 127 * 0.51 + 1e-3
+    p, s, z = fast_quant.quantize_tensor_fast(w.astype(np.float16).tobytes(), "F16", 300)
+    p2, s2, z2 = Q.quantize_int4_arrays(w.astype(np.float16).astype(np.float32), 128)
+    assert (p, s, z) == (np.asarray(p2).tobytes(), np.asarray(s2).tobytes(), np.asarray(z2).tobytes())
+    assert len(p) == Q.compute_packed_size(300)[0] and len(s) == len(z) == Q.compute_packed_size(300)[1]
+
+
+def test_fp16_conversion_of_each_source_type():
+    import numpy as np
+    from zse_b200.format import fast_quant
+    from zse_b200.format.quantize import quantize_fp16
+    w = np.array([1.0, -2.5, 0.333251953125, 1000.0], dtype=np.float32)           # all exact in fp16 and in bf16's range
+    want = w.astype(np.float16).tobytes()
+    assert fast_quant.convert_to_fp16_fast(w.tobytes(), "F32", 4) == want == quantize_fp16(w)
+    assert fast_quant.convert_to_fp16_fast(w.astype(np.float64).tobytes(), "F64", 4) == want
+    assert fast_quant.convert_to_fp16_fast(want + b"\0\0", "F16", 4) == want      # fp16 passes through, cut to size
+    bf = (w.view(np.uint32) >> 16).astype(np.uint16)                              # truncated bfloat16
+    got = np.frombuffer(fast_quant.convert_to_fp16_fast(bf.tobytes(), "BF16", 4), np.float16)
+    assert got.tolist()[:2] == [1.0, -2.5] and got[3] == 1000.0
+    assert abs(float(got[2]) - 0.3333) < 2e-3                                     # bf16 kept 8 bits of it
+    assert fast_quant.convert_to_fp16_fast(w.tobytes(), "F32", 2) == want[:4]
+
+
+def test_repack_to_the_64_by_8_tiles_places_each_byte():
+    import numpy as np
+    from zse_b200.format import fast_quant
+    from zse_b200.format.quantize import untile_int4_64x8
+    n, k = 70, 48                                                                 # 2 row tiles (one ragged), 3 k tiles
+    raw = (np.arange(n * k // 2) % 251).astype(np.uint8)
+    t = np.frombuffer(fast_quant.repack_int4_tiled(raw.tobytes(), n, k), np.uint8)
+    assert t.size == 2 * 3 * 64 * 8
+    tiles = t.reshape(2, 3, 64, 8)
+    src = raw.reshape(n, k // 2)
+    assert (tiles[0, 1, 5] == src[5, 8:16]).all() and (tiles[1, 2, 3] == src[67, 16:24]).all()
+    assert tiles[1, :, 6:].sum() == 0                                             # rows 70..127 are padding
+    assert (untile_int4_64x8(t, n, k) == raw).all()
+
+
+def test_alignment_helpers():
+    from zse_b200.format.spec import align_offset, align_up, pad_to_alignment
+    assert [align_up(x, 64) for x in (0, 1, 63, 64, 65)] == [0, 64, 64, 64, 128]
+    assert align_offset(4097, 4096) == align_up(4097, 4096) == 8192
+    assert pad_to_alignment(64, 64) == b"" and pad_to_alignment(60, 64) == b"\0" * 4
+    assert len(pad_to_alignment(1, 4096)) == 4095

@@ -57,9 +57,5 @@ def align_up(offset: int, alignment: int) -> int:
     return (offset + alignment - 1) // alignment * alignment
 
 
-# names the reference exposes
-align_offset = align_up
-
-
 def pad_to_alignment(offset: int, alignment: int) -> bytes:
     return bytes(align_up(offset, alignment) - offset)
