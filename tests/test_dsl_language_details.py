@@ -276,3 +276,77 @@ def test_these_kernels_compile_for_sm_100a(tmp_path, monkeypatch):
         ck = comp.compile(k.source(line_info=True), k.name)
         assert ck.cubin[:4] == b"\x7fELF" and not ck.from_cache, k.name
     assert comp.stats["compiled"] == len(kernels)
+
+
+# ---- the type pass and the IR walkers ---------------------------------------------------------------------------------
+@zse.kernel
+def typed(x: zse.Tensor, y: zse.Tensor[zse.float16], out: zse.Tensor, n: int, s: float):
+    i = zse.global_id(0)
+    acc = 0
+    for j in range(n):
+        acc += x[j] * s
+    h = y[i]
+    b = i < n and acc > 0.0
+    if b:
+        out[i] = acc + h
+
+
+def test_scalar_ranks_and_widening():
+    from zse_b200.dsl.infer import promote, widen
+    assert widen("half") == widen("bf16") == "float" and widen("int") == "int"
+    assert promote("bool", "int") == "int" and promote("int", "uint") == "uint" and promote("uint", "float") == "float"
+    assert promote("half", "int") == "float" and promote("bool", "bool") == "bool"
+    assert promote("float", "int") == promote("int", "float")
+    with pytest.raises(zse.KernelTypeError, match="cannot combine"):
+        promote("int", "fragment")
+
+
+def test_a_local_takes_the_widest_type_assigned_to_it():
+    t = zse.infer_types(typed.ir, {"x": "float32"})
+    assert t.var_types == {"n": "int", "s": "float", "i": "int", "acc": "float", "j": "int", "h": "float", "b": "bool"}
+    assert t.ptr_elem == {"x": "float32", "y": "float16", "out": "float32"}       # the annotation wins for y
+    assert t.uses == {"global_id"}
+    assert [t.param_ctype(p) for p in typed.ir.params] == ["float*", "__half*", "float*", "int", "float"]
+    half = zse.infer_types(typed.ir, {"x": "float16", "out": "bfloat16", "y": "float32"})
+    assert half.ptr_elem == {"x": "float16", "y": "float16", "out": "bfloat16"}
+    assert half.var_types["acc"] == "float"                                        # fp16 elements widen in arithmetic
+    assert [half.param_ctype(p) for p in typed.ir.params][:3] == ["__half*", "__half*", "__nv_bfloat16*"]
+
+
+def test_ir_walkers_visit_nested_bodies():
+    from zse_b200.dsl import ir
+    stmts = [type(s).__name__ for s in ir.walk_stmts(typed.ir.body)]
+    assert stmts == ["Assign", "Assign", "For", "Assign", "Assign", "Assign", "If", "Store"]
+    exprs = list(ir.walk_exprs(typed.ir.body))
+    kinds = [type(e).__name__ for e in exprs]
+    assert kinds.count("Load") == 2 and kinds.count("Call") == 1 and kinds.count("BoolOp") == 1
+    assert kinds.count("Compare") == 2 and kinds.count("BinOp") == 3
+    assert {e.name for e in exprs if isinstance(e, ir.Var)} >= {"n", "acc", "j", "s", "i", "b", "h"}
+    first_if = next(s for s in ir.walk_stmts(typed.ir.body) if isinstance(s, ir.If))
+    assert [type(e).__name__ for e in ir.walk_exprs(first_if.cond)] == ["Var"]    # an expression walks itself too
+
+
+def _uses_helper(x: zse.Tensor, n: int):
+    i = zse.global_id(0)
+    if i < n:
+        x[i] = my_helper(x[i])            # noqa: F821  (not a primitive: a warning, the parser refuses it later)
+
+
+def _has_default(x: zse.Tensor, n: int = 4):
+    x[0] = n
+
+
+def _has_lambda(x: zse.Tensor):
+    f = lambda v: v                       # noqa: E731
+    x[0] = 1.0
+
+
+def test_validation_warns_about_unknown_calls_and_refuses_python_only_constructs():
+    warnings = zse.validate_kernel(_uses_helper)
+    assert len(warnings) == 1 and "my_helper" in warnings[0] and "line" in warnings[0]
+    assert typed.warnings == []
+    with pytest.raises(zse.KernelSyntaxError, match="default arguments"):
+        zse.validate_kernel(_has_default)
+    with pytest.raises(zse.KernelSyntaxError, match="lambda") as exc:
+        zse.validate_kernel(_has_lambda)
+    assert "f = lambda v: v" in str(exc.value)                                     # the offending line is quoted
