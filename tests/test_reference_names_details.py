@@ -193,6 +193,12 @@ def test_unique_id_record_carries_the_rendezvous_address():
         NcclUniqueId.from_address_string("x" * 200)
 
 
+def test_one_process_communicator_setup_is_refused_with_a_pointer():
+    from zse_b200.parallel.tensor_parallel import comm_init_all
+    with pytest.raises(RuntimeError, match="tp_launch"):
+        comm_init_all(2)
+
+
 # ---- the C-launcher handle --------------------------------------------------------------------------------------
 def test_fast_decoder_lifecycle_without_a_gpu(tmp_path):
     from zse_b200.format import ZSELoader, synth

@@ -226,6 +226,15 @@ def get_unique_id(backend: str = "cuda") -> bytes:
         return f"127.0.0.1:{s.getsockname()[1]}".encode()
 
 
+def comm_init_all(ndev: int, backend: str = "cuda"):
+    """The reference builds every rank's communicator inside one process here
+    (zse-compiler/zse_compiler/runtime/nccl.py:134-165, ``ncclCommInitAll``) and drives the GPUs from threads.  This
+    package runs one process per GPU, so there is nothing of that shape to return: the call says so and names the
+    entry points that start the ranks."""
+    raise RuntimeError(f"comm_init_all({ndev}): ranks are separate processes here, one per GPU; start them with "
+                       "tp_launch(tp_size, rank_fn) or TPEngine, which hand every rank its communicator")
+
+
 def _tp_worker(rank, tp_size, uid, backend, rank_fn, result_q, error_q):
     try:
         result_q.put((rank, rank_fn(rank, tp_size, uid, backend)))
