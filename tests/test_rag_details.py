@@ -269,3 +269,98 @@ def test_csv_layer():
     assert "¤£0=Groningen¤" in doc.compressed and doc.compressed.endswith("short|")   # a short row is padded
     assert doc.compressed_tokens == len(doc.compressed) < doc.original_tokens == len(text)
     assert compress_csv("only,a,header\n").doc_type == "text"
+
+
+# ---- the store's accessors ------------------------------------------------------------------------------------------------
+def _filled_store(path=None):
+    from zse_b200.rag.parser import Chunk
+    from zse_b200.rag.store import RAGStore
+    e = TokenEmbedder(WordTok())
+    store = RAGStore(path)
+    texts = {"fruit": ["apples and pears", "plums and cherries"], "tools": ["hammers and saws"]}
+    ids = {}
+    for name, parts in texts.items():
+        chunks = [Chunk(t, t.replace(" and ", "&"), {"chunk_index": i, "page": i + 1}, 3, 1) for i, t in enumerate(parts)]
+        ids[name] = store.add_document(name, "text", chunks, [e.embed(t) for t in parts],
+                                       [set(e.tokenize(t)) for t in parts], {"source": name + ".txt"})
+    for ch in store.all_chunks():
+        e.add_to_bm25(ch.content, ch.id)
+    return store, e, ids
+
+
+def test_store_reads_documents_and_chunks_back():
+    store, e, ids = _filled_store()
+    docs = store.list_documents()
+    assert [(d.name, d.chunk_count, d.original_tokens, d.compressed_tokens) for d in docs] == [
+        ("fruit", 2, 6, 2), ("tools", 1, 3, 1)]
+    assert docs[0].metadata == {"source": "fruit.txt"} and docs[0].savings_pct == pytest.approx(200 / 3)
+    assert store.get_document(ids["tools"]).name == "tools" and store.get_document(999) is None
+    chunks = store.get_chunks(ids["fruit"])
+    assert [c.chunk_index for c in chunks] == [0, 1] and chunks[1].content == "plums and cherries"
+    assert chunks[1].compressed == "plums&cherries" and chunks[1].metadata["page"] == 2
+    assert chunks[0].token_count == 1 and not chunks[0].has_dense and chunks[0].embedding == e.embed("apples and pears")
+    assert [c.id for c in store.all_chunks()] == [1, 2, 3]
+    assert store.get_chunk_text(3) == "hammers and saws" and store.get_chunk_text(44) is None
+    rows = store.get_chunks_by_ids([3, 1, 77])
+    assert set(rows) == {1, 3} and rows[3][1] == "tools" and rows[1][0].content == "apples and pears"
+    assert store.get_chunks_by_ids([]) == {}
+    many = store.get_chunks_by_ids(range(1, 1200))                                # more ids than one statement takes
+    assert set(many) == {1, 2, 3}
+
+
+def test_dense_vectors_are_optional_per_chunk():
+    store, _, _ = _filled_store()
+    assert store.all_chunk_ids_missing_dense() == [1, 2, 3] and store.get_dense_vectors([1, 2, 3]) == {}
+    store.set_dense_vector(2, b"\x01\x02")
+    assert store.all_chunk_ids_missing_dense() == [1, 3]
+    assert store.get_dense_vectors([1, 2, 3]) == {2: b"\x01\x02"}
+    assert store.get_chunks_by_ids([2])[2][0].has_dense
+    assert store.stats()["dense_chunks"] == 1 and store.stats()["chunks"] == 3
+
+
+def test_index_and_vectors_can_be_rebuilt_from_the_stored_text():
+    store, e, _ = _filled_store()
+    tok_and = e.tokenize("and")[0]
+    assert store.index.candidates([tok_and]) == {1, 2, 3}
+    store.index.clear()
+    assert store.index.candidates([tok_and]) == set() and store.stats()["index_tokens"] == 0
+    store.rebuild_inverted_index(e)
+    assert store.index.candidates([tok_and]) == {1, 2, 3}
+    assert store.index.candidates(e.tokenize("hammers")) == {3}
+    before = store.get_chunks_by_ids([1])[1][0].embedding
+    e.update_idf([set(e.tokenize(c.content)) for c in store.all_chunks()])        # "and" is now a common word
+    store.reembed_all(e)
+    after = store.get_chunks_by_ids([1])[1][0].embedding
+    assert after != before and after == e.embed("apples and pears")
+    store.set_embedding(1, b"")
+    assert store.get_chunks_by_ids([1])[1][0].embedding == b""
+
+
+def test_lexical_search_blends_both_signals_and_honours_candidates():
+    store, e, ids = _filled_store()
+    hits = store.search(e.embed("plums"), e, "plums", top_k=5)
+    assert [h.chunk_id for h in hits] == [2] and hits[0].doc_name == "fruit"
+    assert hits[0].bm25_score == 1.0 and 0 < hits[0].cosine_score < 1 and hits[0].dense_score == 0.0
+    assert hits[0].rerank_score is None
+    assert hits[0].score == pytest.approx(0.5 * 1.0 + 0.5 * hits[0].cosine_score)
+    rec = hits[0].chunk
+    assert (rec.id, rec.doc_id, rec.chunk_index, rec.content) == (2, ids["fruit"], 1, "plums and cherries")
+    both = store.search(e.embed("and"), e, "and", top_k=2)
+    assert len(both) == 2                                                          # top_k cuts three hits to two
+    only = store.search(e.embed("and"), e, "and", candidate_ids={3})
+    assert [h.chunk_id for h in only] == [3]
+    assert store.search(e.embed("zebra"), e, "zebra") == []
+    assert store.search(e.embed("plums"), e, "plums", min_score=0.99) == []
+
+
+def test_removing_a_document_takes_its_chunks_and_index_entries(tmp_path):
+    path = str(tmp_path / "rag.db")
+    store, e, ids = _filled_store(path)
+    assert store.remove_document(ids["fruit"]) is True and store.remove_document(ids["fruit"]) is False
+    assert [c.id for c in store.all_chunks()] == [3] and store.index.candidates(e.tokenize("apples")) == set()
+    st = store.stats()
+    assert (st["documents"], st["chunks"], st["original_tokens"], st["compressed_tokens"]) == (1, 1, 3, 1)
+    assert st["token_savings_pct"] == 66.7
+    from zse_b200.rag.store import RAGStore
+    again = RAGStore(path)                                                         # the file keeps what is left
+    assert [d.name for d in again.list_documents()] == ["tools"] and again.stats()["index_tokens"] == 0
