@@ -238,3 +238,64 @@ def test_alignment_helpers():
     assert align_offset(4097, 4096) == align_up(4097, 4096) == 8192
     assert pad_to_alignment(64, 64) == b"" and pad_to_alignment(60, 64) == b"\0" * 4
     assert len(pad_to_alignment(1, 4096)) == 4095
+
+
+# ---- writer and loader: raw appends and typed views ------------------------------------------------------------------
+def test_raw_appends_come_back_through_the_typed_views(tmp_path):
+    import numpy as np
+    from zse_b200.format import ZSELoader, ZSEWriter, synth
+    from zse_b200.format import quantize as Q
+    from zse_b200.format.spec import Flags
+    rng = np.random.default_rng(11)
+    w4 = rng.standard_normal((8, 128)).astype(np.float32)
+    w8 = rng.standard_normal((4, 128)).astype(np.float32)
+    wf = rng.standard_normal((3, 5)).astype(np.float16)
+    path = str(tmp_path / "raw.zse")
+    with ZSEWriter(path) as wr:
+        wr.set_config(synth.shape_config("tiny"))
+        wr.set_tokenizer(b"")                                                     # an empty tokenizer section is legal
+        wr.begin_weights()
+        p, s, z = Q.quantize_int4_arrays(w4, 128)
+        wr.add_weight_raw("a.weight", w4.shape, p, s, z)
+        q8, s8 = Q.quantize_int8_arrays(w8, 128)
+        wr.add_weight_raw_int8("b.weight", w8.shape, q8, s8)
+        wr.add_weight_raw_fp16("c.weight", wf.shape, wf)
+    with ZSELoader(path) as l:
+        assert l.header.flags & Flags.HAS_TOKENIZER and l.file_descriptor >= 0
+        ea, eb, ec = (l.weight_index.find(n) for n in ("a.weight", "b.weight", "c.weight"))
+        assert (ea.dtype, eb.dtype, ec.dtype) == ("int4", "int8", "float16")
+        assert all(e.data_offset % 64 == 0 for e in (ea, eb, ec))                 # every tensor starts aligned
+        assert ea.end_offset <= eb.data_offset and eb.end_offset <= ec.data_offset
+        assert l.view_data(ea).dtype == np.uint8 and (l.view_data(ea) == np.asarray(p).reshape(-1)).all()
+        assert (l.int4_rowmajor(ea) == l.view_data(ea)).all()
+        assert (l.view_scales(ea) == np.asarray(s)).all() and (l.view_zeros(ea) == np.asarray(z)).all()
+        assert l.view_data(eb).dtype == np.int8 and (l.view_data(eb) == np.asarray(q8).reshape(-1)).all()
+        assert (l.view_scales(eb) == np.asarray(s8)).all() and l.get_weight_zeros(eb) == b""
+        assert l.view_data(ec).shape == (3, 5) and (l.view_data(ec) == wf).all()
+        assert l.get_weight_scales(ec) == b"" and l.get_weight_data(ec) == wf.tobytes()
+        mm, off = l.get_mmap_pointer_and_offset(ec)
+        assert bytes(mm[off:off + ec.data_nbytes]) == wf.tobytes()                # an absolute file offset
+        assert off == l.weight_data_section()[0] + ec.data_offset
+        assert np.abs(l.get_weight_as_float(ea) - w4).max() < 0.3 and np.abs(l.get_weight_as_float(eb) - w8).max() < 0.03
+        assert "int4: 1" in l.summary() and "int8: 1" in l.summary() and "float16: 1" in l.summary()
+    assert l.file_descriptor == -1                                                 # closed
+
+
+def test_an_aborted_writer_leaves_no_readable_file(tmp_path):
+    import numpy as np
+    from zse_b200.format import ZSELoader, ZSEWriter, synth
+    path = str(tmp_path / "cut.zse")
+    with pytest.raises(RuntimeError, match="stop"):
+        with ZSEWriter(path) as wr:
+            wr.set_config(synth.shape_config("tiny"))
+            wr.begin_weights()
+            wr.add_weight("x.weight", np.ones((2, 128), np.float32), (2, 128))
+            raise RuntimeError("stop")
+    wr.finalize()                                                                  # after abort: nothing more is written
+    with pytest.raises(ValueError):
+        ZSELoader(path)                                                            # the header was never filled in
+    with pytest.raises(ValueError, match="set_config"):
+        ZSEWriter(str(tmp_path / "early.zse")).begin_weights()
+    (tmp_path / "empty.zse").write_bytes(b"")
+    with pytest.raises(ValueError, match="empty"):
+        ZSELoader(str(tmp_path / "empty.zse"))
