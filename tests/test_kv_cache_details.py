@@ -282,3 +282,44 @@ def test_metadata_of_an_empty_batch_and_upload_to_cpu():
     src[0].append(3)
     assert built.block_tables == [[1, 2]]                                          # a copy of the page-table state
     assert isinstance(built, AttentionMetadata)
+
+
+# ---- page table and manager: the accessors -----------------------------------------------------------------------------
+def test_page_table_accessors_skip_evicted_blocks():
+    from zse_b200.cache.page_table import PageTable
+    p = pool(n=6, bs=16)
+    pt = PageTable(p)
+    pt.create_sequence(7)
+    pt.append_tokens(7, 40)                                                       # 3 blocks: 16 + 16 + 8
+    assert pt.get_entry_or_none(7) is pt.get_entry(7) and pt.get_entry_or_none(8) is None
+    assert pt.get_all_sequences() == [7] and pt.blocks_needed(7, 8) == 0 and pt.blocks_needed(7, 9) == 1
+    e = pt.get_entry(7)
+    assert (e.num_blocks, e.num_live_blocks) == (3, 3) and [b.num_tokens for b in pt.get_blocks(7)] == [16, 16, 8]
+    gone = pt.evict_block(7, 0)
+    assert gone is not None and pt.evict_block(7, 0) is None and pt.evict_block(7, 9) is None
+    assert (e.num_blocks, e.num_live_blocks, e.tokens_evicted) == (3, 2, 16)
+    assert pt.get_block_ids(7)[0] == -1 and len(pt.get_blocks(7)) == 2 and pt.get_blocks(99) == []
+    assert pt.stats() == {"num_sequences": 1, "total_tokens": 40, "total_blocks": 2}
+    assert p.num_free == 4
+    assert len(pt.remove_sequence(7)) == 2 and p.num_free == 6 and pt.remove_sequence(7) == []
+
+
+def test_manager_evicts_idle_sequences_before_active_ones():
+    from zse_b200.cache.cache_manager import KVCacheManager
+    from zse_b200.format import synth
+    m = KVCacheManager(synth.shape_config("tiny"), num_blocks=6, block_size=16, enable_dedup=False)
+    assert m.max_tokens_capacity == 96 and m.num_total_blocks == 6
+    m.allocate_sequence(1, num_tokens=32)
+    m.allocate_sequence(2, num_tokens=32)
+    m.mark_active(1)
+    m.mark_idle(2)
+    assert m.num_free_blocks == 2 and m.evict_if_needed(2) is True and m.num_free_blocks == 2   # enough already
+    assert m.evict_if_needed(4) is True and m.num_free_blocks >= 4
+    assert m.get_block_ids(2).count(-1) == 2 and m.get_block_ids(1).count(-1) == 0             # the idle one paid
+    assert m.evict_if_needed(6) is True                                           # then the active one has to
+    assert m.get_block_ids(1).count(-1) == 2 and m.num_free_blocks == 6
+    assert m.evict_if_needed(7) is False                                          # more than the pool holds
+    m.free_sequence(1)
+    m.free_sequence(2)
+    m.free_sequence(2)
+    assert m.num_sequences == 0 and m.num_free_blocks == 6
