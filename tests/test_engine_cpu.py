@@ -1,6 +1,7 @@
 """The serving engine end to end on the CPU path: continuous batching, chunked prefill, prefix sharing, preemption,
 speculative decoding and sampling must all give the tokens of the fp32 oracle model run one sequence at a time
 (greedy), as in the reference's own end-to-end checks (zse-engine/tests/test_zstreamer.py, test_engine.py)."""
+import os
 import random
 
 import pytest
@@ -420,3 +421,30 @@ def test_metrics_route_reports_the_engine(model_path):
     assert vals["zse_ttft_p50_milliseconds"] > 0
     srv.database.close()
     eng.destroy()
+
+
+def test_engine_config_from_the_environment(monkeypatch):
+    """Every field reads ``ZSE_<FIELD>`` with the field's own type; keyword overrides come last and None means
+    'not given'."""
+    from zse_b200.config import EngineConfig
+    for name in list(os.environ):
+        if name.startswith("ZSE_"):
+            monkeypatch.delenv(name)
+    assert EngineConfig.from_env() == EngineConfig()
+    monkeypatch.setenv("ZSE_TP_SIZE", "4")
+    monkeypatch.setenv("ZSE_KV_FRACTION", "0.25")
+    monkeypatch.setenv("ZSE_PIPELINE_DECODE", "off")
+    monkeypatch.setenv("ZSE_USE_CUDA_GRAPHS", "No")
+    monkeypatch.setenv("ZSE_ENABLE_PREEMPTION", "TRUE")
+    monkeypatch.setenv("ZSE_SPECULATIVE_MODE", "self")
+    monkeypatch.setenv("ZSE_INT4_LAYOUT", "tiled64x8")
+    monkeypatch.setenv("ZSE_HEADROOM_RATIO", "0.75")
+    c = EngineConfig.from_env(max_batch_seqs=16, device=None, tp_size=None)
+    assert (c.tp_size, c.kv_fraction, c.pipeline_decode, c.use_cuda_graphs, c.enable_preemption) == \
+        (4, 0.25, False, False, True)
+    assert (c.speculative_mode, c.int4_layout, c.headroom_ratio, c.max_batch_seqs, c.device) == \
+        ("self", "tiled64x8", 0.75, 16, None)
+    assert EngineConfig.from_env(tp_size=2).tp_size == 2                           # a given keyword beats the variable
+    monkeypatch.setenv("ZSE_MAX_SEQ_LEN", "many")
+    with pytest.raises(ValueError):
+        EngineConfig.from_env()
