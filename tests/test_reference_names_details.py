@@ -214,3 +214,20 @@ def test_fast_decoder_lifecycle_without_a_gpu(tmp_path):
     assert fd.setup(model, object()) is False and fd.available is False
     with pytest.raises(RuntimeError, match="not available"):
         fd.forward(None, 1, True, 1, 1, 1, 1)
+
+
+# ---- roofline arithmetic of a timing record -------------------------------------------------------------------------
+def test_profile_rows_divide_by_the_given_peaks():
+    from zse_b200.runtime.profiler import ProfileResult, measured_peaks
+    r = ProfileResult("copy", ms=0.5, ms_min=0.4, launches=10, bytes=2_000_000_000, flops=0, extra={"ctas": 148})
+    assert r.gbs == pytest.approx(4000.0) and r.tflops == 0.0
+    row = r.row({"hbm_gbs": 8000.0, "tflops": 1000.0})
+    assert row == {"name": "copy", "us": 500.0, "us_min": 400.0, "GB/s": 4000.0, "TFLOP/s": 0.0, "frac_hbm": 0.5,
+                   "frac_tensor": None, "ctas": 148}
+    g = ProfileResult("gemm", ms=2.0, ms_min=2.0, launches=1, bytes=0, flops=1_000_000_000_000)
+    assert g.tflops == pytest.approx(500.0) and g.row({"hbm_gbs": 8000.0, "tflops": 1000.0})["frac_tensor"] == 0.5
+    assert "frac_hbm" not in g.row()
+    assert ProfileResult("none", 0.0, 0.0, 0, 10, 10).gbs == 0.0                  # no time, no rate
+    p = measured_peaks()
+    assert p["source"] in ("measured", "fallback") and 3000 < p["hbm_gbs"] < 9000 and 500 < p["tflops"] < 2500
+    assert p["tflops_sustained"] <= p["tflops"] * 1.05

@@ -306,3 +306,23 @@ def test_default_sampling_seed_is_the_same_in_every_process():
         assert out.returncode == 0, out.stderr[-2000:]
         seeds.add(out.stdout.strip())
     assert len(seeds) == 1 and seeds.pop().isdigit()
+
+
+def test_a_failed_request_is_finished_with_its_error_and_leaves_the_batch():
+    s = _sched(max_prefill_per_step=4, decode_per_prefill=0)
+    for name in ("ok", "bad"):
+        s.add_request(_req(name))
+    out = s.schedule_step()
+    assert (out.num_prefill_tokens, out.num_decode_tokens, out.total_tokens) == (16, 0, 16) and not out.is_idle
+    _finish_prefill(s, out)
+    assert sorted(r.request_id for r in s.active_requests()) == ["bad", "ok"]
+    bad = next(r for r in s.active_requests() if r.request_id == "bad")
+    s.on_request_error(bad, "device said no")
+    s.on_request_error(bad, "second report")                                     # the first finish reason stays
+    assert bad.is_finished and bad.finish_reason == FinishReason.ERROR and bad.error == "second report"
+    out = s.schedule_step()
+    assert [r.request_id for r in out.decode_requests] == ["ok"] and out.num_decode_tokens == 1
+    assert [r.request_id for r in s.active_requests()] == ["ok"] and s.stats()["total_finished"] == 1
+    listing = s.active_requests()
+    listing.clear()                                                               # a copy: the scheduler keeps its own
+    assert s.num_active == 1
