@@ -166,3 +166,39 @@ def test_literal_string_escapes_one_by_one():
     assert decode_literal(rb"\777") == b"\xff"                                  # high bits are dropped
     assert decode_literal(b"line \\\ncontinues \\\r\nhere") == b"line continues here"
     assert decode_literal(rb"\q") == b"q" and decode_literal(b"ends with \\") == b"ends with "
+
+
+# ---- the document model: what a page is made of ---------------------------------------------------------------------
+def _obj(n, body, stream=None):
+    if stream is None:
+        return b"%d 0 obj\n%s\nendobj\n" % (n, body)
+    return b"%d 0 obj\n<< %s /Length %d >>\nstream\n%s\nendstream\nendobj\n" % (n, body, len(stream), stream)
+
+
+def test_a_page_names_its_contents_fonts_and_images():
+    from zse_b200.rag.pdf import PDFDocument
+    cmap = b"1 beginbfchar\n<0041> <0058>\nendbfchar"
+    raw = b"%PDF-1.4\n" + b"".join([
+        _obj(1, b"<< /Type /Catalog /Pages 2 0 R >>"),
+        _obj(2, b"<< /Type /Pages /Kids [3 0 R] /Count 1 /Resources 4 0 R >>"),      # resources come from the parent
+        _obj(3, b"<< /Type /Page /Parent 2 0 R /Contents 5 0 R >>"),
+        _obj(4, b"<< /Font << /F1 6 0 R /F2 7 0 R >> /XObject << /Im1 9 0 R /Fm1 10 0 R >> >>"),
+        _obj(5, b"[ 11 0 R 12 0 R 99 0 R ]"),                                          # contents as an array object
+        _obj(6, b"<< /Type /Font /Subtype /Type0 /Encoding /Identity-H /ToUnicode 8 0 R >>"),
+        _obj(7, b"<< /Type /Font /Subtype /Type1 /BaseFont /Helvetica >>"),
+        _obj(8, b"", cmap),
+        _obj(9, b"/Type /XObject /Subtype /Image /Width 1 /Height 1 /Filter /DCTDecode", b"\xff\xd8jpeg-bytes"),
+        _obj(10, b"/Type /XObject /Subtype /Form", b"q Q"),
+        _obj(11, b"", b"BT (first) Tj ET"),
+        _obj(12, b"", b"BT (second) Tj ET"),
+    ]) + b"%%EOF\n"
+    doc = PDFDocument(raw)
+    assert doc.pages() == [3] and doc.enc is None
+    assert doc.page_content(3) == b"BT (first) Tj ET\nBT (second) Tj ET"           # the missing object 99 is skipped
+    fonts = doc.page_fonts(3)
+    assert set(fonts) == {b"F1", b"F2"} and fonts[b"F1"].two_byte and not fonts[b"F2"].two_byte
+    assert fonts[b"F1"].decode(b"\x00\x41") == "X" and fonts[b"F2"].decode(b"A") == "A"
+    images = doc.page_images(3)
+    assert images == [(b"\xff\xd8jpeg-bytes", "jpeg")]                              # the form XObject is not an image
+    with pytest.raises(PDFError, match="not a PDF"):
+        PDFDocument(b"plain text")
