@@ -446,6 +446,11 @@ def test_lora_manager_reference_entry_points(tmp_path):
             for l in range(eng.model_config.num_layers)}
     m.load_adapter_from_dict("d", 2, 4.0, eng.model_config.num_layers, ["v_proj"], data)
     assert m.num_adapters == 2 and m.has_adapter("r") and m.get_adapter("d").rank == 2 and "slot" in m.summary()
+    # the prefix-cache name of an adapter: 0 for the base model, distinct per adapter, new after a reload
+    salts = {i: m.cache_salt(i) for i in ("r", "d")}
+    assert m.cache_salt(None) == m.cache_salt("") == m.cache_salt("not-loaded") == 0
+    assert salts["r"] != salts["d"] and all(v > 0 and v & 1 for v in salts.values())
+    assert m.cache_salt("r") == salts["r"]                                         # stable while it stays loaded
     rid = eng.add_request_tokens([1, 2, 3, 4], max_tokens=4, temperature=0.0, stop_tokens=[], lora_id="d")
     eng.run_until_done()
     assert len(eng.get_result(rid).output_tokens) == 4
