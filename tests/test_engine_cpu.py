@@ -135,6 +135,12 @@ def test_speculative_decoding_is_exact(model_path, oracle, mode):
     assert outs[1].output_tokens == oracle.greedy(prompts[1], 16)
     st = eng.stats()
     assert st.total_tokens_generated == 32
+    spec = eng._spec_runner
+    sst = spec.stats()
+    assert spec.seq_steps > 0 and 1.0 <= spec.tokens_per_step <= 4.0               # k = 3: at most k + 1 per pass
+    assert spec.speedup_factor == spec.tokens_per_step and "k=3" in spec.summary()
+    assert 0 <= sst["accepted"] <= sst["drafted"] and spec.tokens_emitted <= 32
+    spec.forget("no-such-request")                                                 # unknown ids are fine
     eng.destroy(); plain_eng.destroy()
 
 
